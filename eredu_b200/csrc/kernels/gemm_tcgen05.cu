@@ -1,0 +1,355 @@
+// Dense bf16 linear layer  Y[M,N] = X[M,K] · W[N,K]^T  on the 5th-gen tensor cores.
+//
+// Design ("weight-stationary, swap-AB"): the 128-row weight tile is the MMA's M operand and the
+// token tile (16..256 rows of X) is the MMA's N operand, so that one kernel covers decode
+// (M = 1..64 tokens, a pure weight-streaming problem) and prefill (thousands of tokens).
+//   * TMA (cp.async.bulk.tensor, 128B swizzle, no multicast) streams W and X tiles into a
+//     multi-stage shared-memory ring; one thread issues tcgen05.mma; accumulators live in TMEM;
+//     four epilogue warps read them back with tcgen05.ld.
+//   * DUAL mode multiplies the same X tile against two weight tiles (gate rows and up rows of a
+//     concatenated [2I,K] matrix) into two TMEM regions and the epilogue writes silu(g)*u — the
+//     SwiGLU activation never round-trips through HBM.
+//   * Split-K for the decode regime runs as a thread-block cluster along z: every CTA of the
+//     cluster accumulates a K slice, the partials are exchanged through distributed shared
+//     memory and each CTA reduces and stores a share of the token columns. No atomics, no
+//     global scratch, bitwise deterministic.
+//   * Epilogue fusions: bias, residual add, SwiGLU, bf16 or fp32 output.
+//
+// Replaces the reference's dense matmul call sites (eredu-architectures/src/llama.rs:270-286,
+// 418-431; eredu/src/backend/mlx/nn/parallel.rs:794-796) and its silu(gate)*up composition
+// (eredu/src/backend/mlx/nn/layers.rs:21-24).
+#include <cooperative_groups.h>
+
+#include "../common/launch_count.h"
+#include "../common/ptx.cuh"
+#include "../common/tma_host.h"
+
+namespace cg = cooperative_groups;
+
+namespace eredu {
+
+struct GemmParams {
+  void* y;               // [M, ldy] bf16 or fp32
+  const void* residual;  // optional [M, ldr] bf16, added after activation
+  const void* bias;      // optional [N] bf16 (DUAL: [2*N_out], gate part then up part)
+  int M, N, K;           // N = output columns (DUAL: columns of the activation output)
+  int ldy, ldr;
+  int dual_row_offset;  // DUAL: row of W where the "up" matrix starts
+  int out_fp32;
+  int* status;
+};
+
+template <int TN, bool DUAL>
+struct GemmCfg {
+  static constexpr int kATile = 128 * 64 * 2;
+  static constexpr int kBTile = TN * 64 * 2;
+  static constexpr int kStageBytes = kATile * (DUAL ? 2 : 1) + kBTile;
+  static constexpr int kBudget = (TN <= 32 && !DUAL) ? 100 * 1024 : 196 * 1024;
+  static constexpr int kStagesRaw = kBudget / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kAccCols = TN * (DUAL ? 2 : 1);
+  static constexpr int kTmemCols = kAccCols <= 32 ? 32 : kAccCols <= 64 ? 64 : kAccCols <= 128 ? 128 : kAccCols <= 256 ? 256 : 512;
+  static constexpr int kCtrlBytes = 1024;
+  static constexpr int kSmemBytes = 1024 + kCtrlBytes + kStages * kStageBytes;
+  static_assert(kStages >= 2, "pipeline too shallow");
+};
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
+
+template <bool DUAL>
+__device__ __forceinline__ void epilogue_store(const GemmParams& p, float g, float u, int m, int n) {
+  if (p.bias != nullptr) {
+    const __nv_bfloat16* b = static_cast<const __nv_bfloat16*>(p.bias);
+    g += __bfloat162float(b[n]);
+    if (DUAL) u += __bfloat162float(b[p.N + n]);
+  }
+  float v = DUAL ? silu_f(g) * u : g;
+  if (p.residual != nullptr) {
+    v += __bfloat162float(static_cast<const __nv_bfloat16*>(p.residual)[static_cast<size_t>(m) * p.ldr + n]);
+  }
+  if (p.out_fp32) {
+    static_cast<float*>(p.y)[static_cast<size_t>(m) * p.ldy + n] = v;
+  } else {
+    static_cast<__nv_bfloat16*>(p.y)[static_cast<size_t>(m) * p.ldy + n] = __float2bfloat16(v);
+  }
+}
+
+template <int TN, bool DUAL, bool SPLIT>
+__global__ void __launch_bounds__(192, 1)
+gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, GemmParams p) {
+  using Cfg = GemmCfg<TN, DUAL>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem);            // [kStages]
+  uint64_t* empty_bar = full_bar + Cfg::kStages;                     // [kStages]
+  uint64_t* accum_bar = empty_bar + Cfg::kStages;                    // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);  // [1]
+  uint8_t* stages = smem + Cfg::kCtrlBytes;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tile_n = blockIdx.x;
+  const int tile_m = blockIdx.y;
+  const int nsplit = SPLIT ? gridDim.z : 1;
+  const int split = SPLIT ? blockIdx.z : 0;
+
+  const int kblocks = (p.K + 63) >> 6;
+  const int kb_per = (kblocks + nsplit - 1) / nsplit;
+  const int kb0 = split * kb_per;
+  const int kb1 = min(kblocks, kb0 + kb_per);
+  const int niter = max(0, kb1 - kb0);
+
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(accum_bar, 1);
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      const uint64_t pol_w = l2_policy_evict_first();
+      const uint64_t pol_x = l2_policy_evict_last();
+      int issued = 0;
+      bool ok = true;
+      for (int it = 0; it < niter && ok; ++it) {
+        const int s = it % Cfg::kStages;
+        const uint32_t ph = (it / Cfg::kStages) & 1;
+        ok = mbar_wait(&empty_bar[s], ph ^ 1, p.status, kStatusSmemEmptyTimeout);
+        if (!ok) break;
+        uint8_t* a = stages + s * Cfg::kStageBytes;
+        const int kx = (kb0 + it) * 64;
+        mbar_arrive_expect_tx(&full_bar[s], Cfg::kStageBytes);
+        tma_load_2d_hint(a, &tmW, kx, tile_n * 128, &full_bar[s], pol_w);
+        if (DUAL) tma_load_2d_hint(a + Cfg::kATile, &tmW, kx, p.dual_row_offset + tile_n * 128, &full_bar[s], pol_w);
+        tma_load_2d_hint(a + Cfg::kATile * (DUAL ? 2 : 1), &tmX, kx, tile_m * TN, &full_bar[s], pol_x);
+        issued = it + 1;
+      }
+      if (!ok) {
+        // Give up cleanly: wait (bounded) for the copies still in flight before shared memory dies.
+        const int first = max(0, issued - Cfg::kStages);
+        for (int it = first; it < issued; ++it) {
+          mbar_wait(&full_bar[it % Cfg::kStages], (it / Cfg::kStages) & 1, nullptr, 0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(128, TN);
+      bool ok = true;
+      for (int it = 0; it < niter; ++it) {
+        const int s = it % Cfg::kStages;
+        const uint32_t ph = (it / Cfg::kStages) & 1;
+        ok = mbar_wait(&full_bar[s], ph, p.status, kStatusTmaFullTimeout);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t a_addr = smem_u32(stages + s * Cfg::kStageBytes);
+        const uint64_t da = umma_desc_k_sw128(a_addr);
+        const uint64_t da2 = umma_desc_k_sw128(a_addr + Cfg::kATile);
+        const uint64_t db = umma_desc_k_sw128(a_addr + Cfg::kATile * (DUAL ? 2 : 1));
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
+          umma_f16(tmem_base, da + 2 * k, db + 2 * k, idesc, acc);
+          if (DUAL) umma_f16(tmem_base + TN, da2 + 2 * k, db + 2 * k, idesc, acc);
+        }
+        umma_commit(&empty_bar[s]);
+      }
+      if (ok) umma_commit(accum_bar);
+    }
+  }
+  __syncwarp();  // lanes 1..31 of the producer / MMA warps rejoin lane 0 before any block or cluster barrier
+
+  // ------------------------------------------------------------ epilogue (warps 2..5)
+  const int q = warp & 3;  // TMEM lane quarter this warp may read
+  const int row = q * 32 + lane;
+  const int n = tile_n * 128 + row;
+  const int m_base = tile_m * TN;
+  bool acc_ok = false;
+  float* red = reinterpret_cast<float*>(stages);  // SPLIT: [DUAL?2:1][TN][128] fp32, aliases the ring
+
+  if (warp >= 2) {
+    acc_ok = (niter > 0) && mbar_wait(accum_bar, 0, p.status, kStatusAccumTimeout);
+    acc_ok = __all_sync(0xffffffffu, acc_ok);
+    tc_fence_after_sync();
+    if (acc_ok) {
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 0; c0 < TN; c0 += 16) {
+        uint32_t g[16];
+        uint32_t u[16];
+        tmem_ld16(taddr + c0, g);
+        if (DUAL) tmem_ld16(taddr + TN + c0, u);
+        tmem_wait_ld();
+        if (SPLIT) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            red[(c0 + j) * 128 + row] = __uint_as_float(g[j]);
+            if (DUAL) red[(TN + c0 + j) * 128 + row] = __uint_as_float(u[j]);
+          }
+        } else if (n < p.N) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m = m_base + c0 + j;
+            if (m < p.M) epilogue_store<DUAL>(p, __uint_as_float(g[j]), DUAL ? __uint_as_float(u[j]) : 0.f, m, n);
+          }
+        }
+      }
+    }
+  }
+
+  if (SPLIT) {
+    // Every thread of every CTA of the cluster reaches both barriers, whatever happened above.
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    if (warp >= 2 && n < p.N) {
+      const int m_end = min(TN, p.M - m_base);
+      for (int c = split; c < m_end; c += nsplit) {
+        float g = 0.f, u = 0.f;
+        for (int r = 0; r < nsplit; ++r) {
+          const float* peer = cluster.map_shared_rank(red, r);
+          g += peer[c * 128 + row];
+          if (DUAL) u += peer[(TN + c) * 128 + row];
+        }
+        epilogue_store<DUAL>(p, g, u, m_base + c, n);
+      }
+    }
+    cluster.sync();
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+template <int TN, bool DUAL, bool SPLIT>
+static cudaError_t launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, int n_tiles,
+                               int m_tiles, int nsplit, cudaStream_t stream) {
+  using Cfg = GemmCfg<TN, DUAL>;
+  auto kern = gemm_wt_kernel<TN, DUAL, SPLIT>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(n_tiles, m_tiles, nsplit);
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  int nattr = 0;
+  if (SPLIT) {
+    attr[nattr].id = cudaLaunchAttributeClusterDimension;
+    attr[nattr].val.clusterDim.x = 1;
+    attr[nattr].val.clusterDim.y = 1;
+    attr[nattr].val.clusterDim.z = nsplit;
+    ++nattr;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = nattr;
+  return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p);
+}
+
+template <int TN, bool DUAL>
+static cudaError_t launch_gemm_split(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p,
+                                     int n_tiles, int m_tiles, int nsplit, cudaStream_t stream) {
+  if (nsplit > 1) {
+    if constexpr (TN <= 64) return launch_gemm<TN, DUAL, true>(tmW, tmX, p, n_tiles, m_tiles, nsplit, stream);
+  }
+  return launch_gemm<TN, DUAL, false>(tmW, tmX, p, n_tiles, m_tiles, 1, stream);
+}
+
+}  // namespace eredu
+
+using namespace eredu;
+
+// Number of K splits the launcher would use (exposed for tests and tuning).
+extern "C" int eredu_gemm_pick_split(int M, int N, int K, int sm_count) {
+  const int tn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  if (tn > 64) return 1;
+  const int tiles = ((N + 127) / 128) * ((M + tn - 1) / tn);
+  const int kblocks = (K + 63) / 64;
+  int s = 1;
+  while (s < 8 && tiles * s * 2 <= 2 * sm_count && kblocks / (s * 2) >= 2) s *= 2;
+  return s;
+}
+
+// Y = X W^T (+bias) (+residual), or with dual != 0: Y = silu(X Wg^T) * (X Wu^T) where Wg = W[0:N],
+// Wu = W[dual_row_offset : dual_row_offset+N]. X: [M,K] bf16 (row stride ldx), W: [rows,K] bf16 (row
+// stride ldw). `force_split` > 0 overrides the split-K heuristic (1,2,4,8). Returns a cudaError_t
+// or a negative tensor-map error.
+extern "C" int eredu_gemm_bf16(const void* X, const void* W, void* Y, const void* residual, const void* bias, int M,
+                               int N, int K, int ldx, int ldw, int ldy, int ldr, int w_rows, int dual,
+                               int dual_row_offset, int out_fp32, int force_split, int sm_count, int* status,
+                               cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const int tn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  CUtensorMap tmW, tmX;
+  int r = make_tma_2d(&tmW, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w_rows, K, ldw, 128, 64);
+  if (r != 0) return -100 + r;
+  r = make_tma_2d(&tmX, X, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, ldx, tn, 64);
+  if (r != 0) return -200 + r;
+  GemmParams p;
+  p.y = Y;
+  p.residual = residual;
+  p.bias = bias;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.ldy = ldy;
+  p.ldr = ldr;
+  p.dual_row_offset = dual_row_offset;
+  p.out_fp32 = out_fp32;
+  p.status = status;
+  const int n_tiles = (N + 127) / 128;
+  const int m_tiles = (M + tn - 1) / tn;
+  int nsplit = force_split > 0 ? force_split : eredu_gemm_pick_split(M, N, K, sm_count > 0 ? sm_count : 148);
+  const int kblocks = (K + 63) / 64;
+  while (nsplit > 1 && (kblocks + nsplit - 1) / nsplit * (nsplit - 1) >= kblocks) nsplit >>= 1;  // no empty split
+  cudaError_t e;
+#define ER_DISPATCH(TN_)                                                                     \
+  case TN_:                                                                                  \
+    e = dual ? launch_gemm_split<TN_, true>(tmW, tmX, p, n_tiles, m_tiles, nsplit, stream)   \
+             : launch_gemm_split<TN_, false>(tmW, tmX, p, n_tiles, m_tiles, nsplit, stream); \
+    break;
+  switch (tn) {
+    ER_DISPATCH(16)
+    ER_DISPATCH(32)
+    ER_DISPATCH(64)
+    ER_DISPATCH(128)
+    default:
+      // DUAL with 256-token tiles would need 512 TMEM columns and a 2-stage ring; use 128-token tiles.
+      if (dual) {
+        CUtensorMap tmX2;
+        r = make_tma_2d(&tmX2, X, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, ldx, 128, 64);
+        if (r != 0) return -200 + r;
+        e = launch_gemm_split<128, true>(tmW, tmX2, p, n_tiles, (M + 127) / 128, 1, stream);
+      } else {
+        e = launch_gemm_split<256, false>(tmW, tmX, p, n_tiles, m_tiles, 1, stream);
+      }
+      break;
+  }
+#undef ER_DISPATCH
+  eredu_count_launches(1);
+  return static_cast<int>(e);
+}

@@ -1,0 +1,242 @@
+"""Model configuration: normalisation of Hugging Face ``config.json`` and GGUF metadata.
+
+Defaults and field fall-backs follow the reference's Llama/Qwen config readers
+(eredu-architectures/src/llama/config.rs:82-101,206-312,402-454; eredu/src/backend/mlx/architectures/qwen/dense.rs:99-127).
+"""
+from __future__ import annotations
+
+import json
+from dataclasses import dataclass, field, asdict
+from pathlib import Path
+from typing import Any
+
+DENSE_TYPES = {"llama", "mistral", "qwen2", "qwen3"}
+MOE_TYPES = {"qwen3_moe", "mixtral", "gpt_oss", "deepseek_v3", "lfm2_moe", "nemotron_h"}
+
+
+@dataclass
+class ModelConfig:
+    model_type: str = "llama"
+    vocab_size: int = 32000
+    hidden_size: int = 4096
+    intermediate_size: int = 11008
+    num_hidden_layers: int = 32
+    num_attention_heads: int = 32
+    num_key_value_heads: int = 32
+    head_dim: int = 128
+    rms_norm_eps: float = 1e-5
+    rope_theta: float = 10000.0
+    rope_scaling: dict | None = None
+    rope_traditional: bool = False  # interleaved pairs (GGUF / llama.cpp convention)
+    partial_rotary_factor: float = 1.0
+    max_position_embeddings: int = 2048
+    tie_word_embeddings: bool = True
+    attention_bias: bool = False
+    mlp_bias: bool = False
+    sliding_window: int | None = None
+    layer_types: list[str] | None = None  # per-layer "full_attention" | "sliding_attention"
+    qk_norm: bool = False  # per-head q/k RMSNorm (Qwen3)
+    norm_weight_offset: float = 0.0  # Gemma stores (w - 1)
+    embedding_scale: float = 1.0
+    # MoE
+    num_experts: int = 0
+    num_experts_per_tok: int = 0
+    moe_intermediate_size: int = 0
+    norm_topk_prob: bool = True
+    router_scoring: str = "softmax"  # softmax | sigmoid | sqrt_softplus | topk_softmax
+    shared_expert_intermediate_size: int = 0
+    decoder_sparse_step: int = 1
+    mlp_only_layers: list[int] = field(default_factory=list)
+    swiglu_limit: float = 0.0
+    attention_sinks: bool = False
+    # quantisation recorded in the checkpoint
+    quantization: dict | None = None
+    eos_token_id: Any = None
+    bos_token_id: Any = None
+    torch_dtype: str = "bfloat16"
+    extra: dict = field(default_factory=dict)
+
+    @property
+    def is_moe(self) -> bool:
+        return self.num_experts > 0
+
+    @property
+    def rotary_dim(self) -> int:
+        r = int(self.head_dim * self.partial_rotary_factor)
+        return r - (r % 2)
+
+    def layer_is_moe(self, layer: int) -> bool:
+        if not self.is_moe or layer in self.mlp_only_layers:
+            return False
+        return (layer + 1) % max(1, self.decoder_sparse_step) == 0
+
+    def layer_window(self, layer: int) -> int:
+        if self.sliding_window is None or self.sliding_window <= 0:
+            return 0
+        if self.layer_types is not None:
+            return self.sliding_window if self.layer_types[layer] == "sliding_attention" else 0
+        return self.sliding_window
+
+    def to_hf_dict(self) -> dict:
+        d = {k: v for k, v in asdict(self).items() if k not in ("extra", "qk_norm", "rope_traditional",
+                                                                "norm_weight_offset", "embedding_scale",
+                                                                "router_scoring", "attention_sinks", "quantization")}
+        d["architectures"] = [{"llama": "LlamaForCausalLM", "mistral": "MistralForCausalLM",
+                               "qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM",
+                               "qwen3_moe": "Qwen3MoeForCausalLM"}.get(self.model_type, "LlamaForCausalLM")]
+        if not self.is_moe:
+            for k in ("num_experts", "num_experts_per_tok", "moe_intermediate_size", "norm_topk_prob",
+                      "shared_expert_intermediate_size", "decoder_sparse_step", "mlp_only_layers", "swiglu_limit"):
+                d.pop(k, None)
+        if self.quantization is not None:
+            d["quantization"] = dict(self.quantization)
+            d["quantization_config"] = dict(self.quantization)
+        d.update(self.extra)
+        return d
+
+    # -------------------------------------------------------------------------------------- HF
+    @classmethod
+    def from_hf_dict(cls, d: dict) -> "ModelConfig":
+        mt = d.get("model_type", "llama")
+        if "text_config" in d and isinstance(d["text_config"], dict):
+            inner = dict(d["text_config"])
+            inner.setdefault("model_type", mt)
+            for k in ("quantization", "quantization_config", "eos_token_id", "tie_word_embeddings"):
+                if k in d and k not in inner:
+                    inner[k] = d[k]
+            d = inner
+            mt = d.get("model_type", mt)
+        heads = int(d.get("num_attention_heads", 32))
+        hidden = int(d.get("hidden_size", 4096))
+        kv = int(d.get("num_key_value_heads") or 0) or heads
+        head_dim = int(d.get("head_dim") or 0) or hidden // heads
+        cfg = cls(
+            model_type=mt,
+            vocab_size=int(d.get("vocab_size", 32000)),
+            hidden_size=hidden,
+            intermediate_size=int(d.get("intermediate_size", 4 * hidden)),
+            num_hidden_layers=int(d.get("num_hidden_layers", 32)),
+            num_attention_heads=heads,
+            num_key_value_heads=kv,
+            head_dim=head_dim,
+            rms_norm_eps=float(d.get("rms_norm_eps", 1e-5 if mt in ("llama", "mistral") else 1e-6)),
+            rope_theta=float(d.get("rope_theta", 10000.0)),
+            rope_scaling=d.get("rope_scaling"),
+            partial_rotary_factor=float(d.get("partial_rotary_factor", 1.0)),
+            max_position_embeddings=int(d.get("max_position_embeddings", 2048)),
+            tie_word_embeddings=bool(d.get("tie_word_embeddings", True)),
+            attention_bias=bool(d.get("attention_bias", mt == "qwen2")),
+            mlp_bias=bool(d.get("mlp_bias", False)),
+            sliding_window=d.get("sliding_window") if d.get("use_sliding_window", mt == "mistral") or mt == "mistral"
+            else None,
+            layer_types=d.get("layer_types"),
+            qk_norm=mt in ("qwen3", "qwen3_moe"),
+            num_experts=int(d.get("num_experts", d.get("num_local_experts", 0)) or 0),
+            num_experts_per_tok=int(d.get("num_experts_per_tok", 0) or 0),
+            moe_intermediate_size=int(d.get("moe_intermediate_size", 0) or 0),
+            norm_topk_prob=bool(d.get("norm_topk_prob", mt == "mixtral")),
+            shared_expert_intermediate_size=int(d.get("shared_expert_intermediate_size", 0) or 0),
+            decoder_sparse_step=int(d.get("decoder_sparse_step", 1) or 1),
+            mlp_only_layers=list(d.get("mlp_only_layers", []) or []),
+            swiglu_limit=float(d.get("swiglu_limit", 0.0) or 0.0),
+            quantization=d.get("quantization") or d.get("quantization_config"),
+            eos_token_id=d.get("eos_token_id"),
+            bos_token_id=d.get("bos_token_id"),
+            torch_dtype=str(d.get("torch_dtype", d.get("dtype", "bfloat16"))),
+        )
+        if mt == "mixtral":
+            cfg.moe_intermediate_size = cfg.moe_intermediate_size or cfg.intermediate_size
+            cfg.router_scoring = "topk_softmax"
+        return cfg
+
+    @classmethod
+    def from_pretrained(cls, path: str | Path) -> "ModelConfig":
+        with open(Path(path) / "config.json") as f:
+            return cls.from_hf_dict(json.load(f))
+
+    # -------------------------------------------------------------------------------------- GGUF
+    @classmethod
+    def from_gguf_metadata(cls, md: dict, has_output_weight: bool) -> "ModelConfig":
+        arch = md.get("general.architecture", "llama")
+
+        def g(key, default=None):
+            return md.get(f"{arch}.{key}", default)
+
+        hidden = int(g("embedding_length"))
+        heads = int(g("attention.head_count"))
+        kv = g("attention.head_count_kv", heads)
+        if isinstance(kv, (list, tuple)):
+            kv = kv[0]
+        kv = int(kv) or heads
+        head_dim = int(g("attention.key_length", hidden // heads))
+        vocab = g("vocab_size")
+        if vocab is None:
+            vocab = len(md.get("tokenizer.ggml.tokens", [])) or 32000
+        scaling = None
+        st = g("rope.scaling.type")
+        if st and st != "none":
+            scaling = {"rope_type": st, "factor": float(g("rope.scaling.factor", 1.0)),
+                       "original_max_position_embeddings": int(g("rope.scaling.original_context_length", 0) or 0)}
+        model_type = {"llama": "llama", "qwen2": "qwen2", "qwen3": "qwen3", "qwen3moe": "qwen3_moe",
+                      "mistral": "mistral"}.get(arch, arch)
+        return cls(
+            model_type=model_type,
+            vocab_size=int(vocab),
+            hidden_size=hidden,
+            intermediate_size=int(g("feed_forward_length", 4 * hidden)),
+            num_hidden_layers=int(g("block_count")),
+            num_attention_heads=heads,
+            num_key_value_heads=kv,
+            head_dim=head_dim,
+            rms_norm_eps=float(g("attention.layer_norm_rms_epsilon", 1e-5)),
+            rope_theta=float(g("rope.freq_base", 10000.0)),
+            rope_scaling=scaling,
+            rope_traditional=model_type in ("llama", "mistral"),
+            max_position_embeddings=int(g("context_length", 2048)),
+            tie_word_embeddings=not has_output_weight,
+            sliding_window=g("attention.sliding_window"),
+            qk_norm=model_type in ("qwen3", "qwen3_moe"),
+            attention_bias=model_type == "qwen2",
+            num_experts=int(g("expert_count", 0) or 0),
+            num_experts_per_tok=int(g("expert_used_count", 0) or 0),
+            moe_intermediate_size=int(g("expert_feed_forward_length", 0) or 0),
+            eos_token_id=md.get("tokenizer.ggml.eos_token_id"),
+            bos_token_id=md.get("tokenizer.ggml.bos_token_id"),
+        )
+
+
+# Shapes named by the benchmark configurations.
+def llama3_8b() -> ModelConfig:
+    return ModelConfig(model_type="llama", vocab_size=128256, hidden_size=4096, intermediate_size=14336,
+                       num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                       rms_norm_eps=1e-5, rope_theta=500000.0, max_position_embeddings=8192,
+                       tie_word_embeddings=False)
+
+
+def llama3_70b() -> ModelConfig:
+    return ModelConfig(model_type="llama", vocab_size=128256, hidden_size=8192, intermediate_size=28672,
+                       num_hidden_layers=80, num_attention_heads=64, num_key_value_heads=8, head_dim=128,
+                       rms_norm_eps=1e-5, rope_theta=500000.0, max_position_embeddings=8192,
+                       tie_word_embeddings=False)
+
+
+def qwen3_30b_a3b() -> ModelConfig:
+    return ModelConfig(model_type="qwen3_moe", vocab_size=151936, hidden_size=2048, intermediate_size=6144,
+                       num_hidden_layers=48, num_attention_heads=32, num_key_value_heads=4, head_dim=128,
+                       rms_norm_eps=1e-6, rope_theta=1000000.0, max_position_embeddings=40960,
+                       tie_word_embeddings=False, qk_norm=True, num_experts=128, num_experts_per_tok=8,
+                       moe_intermediate_size=768, norm_topk_prob=True)
+
+
+def tiny_llama() -> ModelConfig:
+    return ModelConfig(model_type="llama", vocab_size=32000, hidden_size=256, intermediate_size=688,
+                       num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                       rms_norm_eps=1e-5, rope_theta=10000.0, max_position_embeddings=2048,
+                       tie_word_embeddings=True, torch_dtype="float32")
+
+
+def draft_llama_16l() -> ModelConfig:
+    return ModelConfig(model_type="llama", vocab_size=128256, hidden_size=2048, intermediate_size=8192,
+                       num_hidden_layers=16, num_attention_heads=32, num_key_value_heads=8, head_dim=64,
+                       rms_norm_eps=1e-5, rope_theta=500000.0, max_position_embeddings=8192,
+                       tie_word_embeddings=False)

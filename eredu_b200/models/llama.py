@@ -1,0 +1,392 @@
+"""Decoder-only transformer of the Llama family: Llama / Mistral / Qwen2 / Qwen3 dense and, through a
+pluggable MoE block, Qwen3-MoE / Mixtral-style sparse models.
+
+Block semantics follow eredu-architectures/src/llama.rs:289-345,418-431,472-495 (pre-norm,
+``h = x + o_proj(attn(rope(q), rope(k), v))``, ``y = h + down(silu(gate(n(h))) * up(n(h)))``, scale
+1/sqrt(head_dim), RoPE before the cache append, logits of the last prompt position only) and
+architectures/qwen/dense.rs:739-790 (per-head q/k RMSNorm before RoPE, qkv bias for Qwen2).
+
+The execution plan is B200-specific: q/k/v and gate/up weights are fused at load so that a layer is
+``rmsnorm -> qkv GEMM -> norm+rope+KV-append -> paged attention -> o_proj GEMM(+residual) -> rmsnorm ->
+gate_up GEMM(+SwiGLU) -> down GEMM(+residual)`` - eight launches, residual adds and the activation living
+in GEMM epilogues. Under tensor parallelism the two row-parallel GEMMs run through the fused
+GEMM + all-reduce path of :mod:`eredu_b200.parallel.tp`.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Callable, Optional
+
+import torch
+
+from .. import ops
+from .config import ModelConfig
+from .rope import rope_tables
+
+
+@dataclass
+class ForwardBatch:
+    """Device-side description of one model step (prefill chunk(s) or decode tokens)."""
+    token_ids: torch.Tensor            # [M] int32
+    positions: torch.Tensor            # [M] int32
+    slots: torch.Tensor                # [M] int64: page * 16 + offset into the KV pool, -1 = skip
+    block_table: torch.Tensor          # [B, max_pages] int32
+    seq_lens: torch.Tensor             # [B] int32, kv length after this step
+    is_prefill: bool
+    cu_q: Optional[torch.Tensor] = None        # prefill: [B+1] int32
+    max_q_len: int = 1
+    q_per_seq: int = 1                 # decode / verify: query tokens per sequence
+    logit_rows: Optional[torch.Tensor] = None  # rows of the hidden state that need logits ([R] int64), None = all
+    splits: int = 1                    # decode split-KV factor
+    scratch: Optional[tuple] = None    # decode split-KV scratch
+    hidden_in: Optional[torch.Tensor] = None   # pipeline stages > 0: incoming activations instead of token ids
+
+
+@dataclass
+class LayerWeights:
+    attn_norm: torch.Tensor
+    wqkv: torch.Tensor
+    wo: torch.Tensor
+    ffn_norm: torch.Tensor
+    w_gate_up: Optional[torch.Tensor] = None
+    w_down: Optional[torch.Tensor] = None
+    bqkv: Optional[torch.Tensor] = None
+    bo: Optional[torch.Tensor] = None
+    q_norm: Optional[torch.Tensor] = None
+    k_norm: Optional[torch.Tensor] = None
+    sinks: Optional[torch.Tensor] = None
+    moe: object = None       # MoE block (callable) for sparse layers
+    qlin: dict = field(default_factory=dict)  # quantised linears by role: "qkv", "o", "gate_up", "down"
+
+
+class CausalLM:
+    """Weights + forward of one model replica / shard. Not an nn.Module: inference only, explicit tensors."""
+
+    def __init__(self, cfg: ModelConfig, device, dtype, parallel=None):
+        from ..parallel.context import ParallelContext
+
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.par = parallel or ParallelContext.single()
+        tp = self.par.tp_size
+        self.n_q_local, self.n_kv_local, self.kv_rep = self.par.attention_partition(cfg.num_attention_heads,
+                                                                                    cfg.num_key_value_heads)
+        self.inter_local = cfg.intermediate_size // tp if cfg.intermediate_size % tp == 0 else None
+        self.layers: list[LayerWeights] = []
+        self.first_layer, self.last_layer = self.par.layer_range(cfg.num_hidden_layers)
+        self.embed: Optional[torch.Tensor] = None
+        self.final_norm: Optional[torch.Tensor] = None
+        self.lm_head: Optional[torch.Tensor] = None  # [V_local, H]
+        self.vocab_start = 0
+        inv, factor = rope_tables(cfg)
+        self.inv_freq = inv.to(self.device)
+        self.attn_factor = factor
+        self.scale = 1.0 / math.sqrt(cfg.head_dim)
+        self.tp_ops = None  # set by parallel.tp when tp_size > 1
+
+    # ------------------------------------------------------------------------------------------ layer
+    def _linear(self, lw: LayerWeights, role: str, x, w, bias=None, residual=None):
+        q = lw.qlin.get(role)
+        if q is not None:
+            return q(x, bias=bias, residual=residual)
+        return ops.linear(x, w, bias=bias, residual=residual)
+
+    def _row_linear(self, lw: LayerWeights, role: str, x, w, residual, bias=None):
+        """Row-parallel projection: local GEMM, sum over the TP group, residual added once."""
+        if self.par.tp_size == 1:
+            return self._linear(lw, role, x, w, bias=bias, residual=residual)
+        q = lw.qlin.get(role)
+        if q is not None:
+            partial = q(x)
+            return self.tp_ops.all_reduce(partial, residual=residual, bias=bias)
+        return self.tp_ops.row_linear(x, w, residual=residual, bias=bias)
+
+    def layer_forward(self, li: int, lw: LayerWeights, h, batch: ForwardBatch, kv):
+        cfg = self.cfg
+        normed, _ = ops.rmsnorm(h, lw.attn_norm, cfg.rms_norm_eps, weight_offset=cfg.norm_weight_offset)
+        qkv = self._linear(lw, "qkv", normed, lw.wqkv, bias=lw.bqkv)
+        k_cache, v_cache = kv.layer(li)
+        q = ops.rope_kv(qkv, batch.positions, batch.slots, self.inv_freq, k_cache, v_cache, self.n_q_local,
+                        self.n_kv_local, cfg.head_dim, rot=cfg.rotary_dim, interleaved=cfg.rope_traditional,
+                        attn_factor=self.attn_factor, q_norm_w=lw.q_norm, k_norm_w=lw.k_norm, norm_eps=cfg.rms_norm_eps,
+                        norm_w_off=cfg.norm_weight_offset)
+        window = cfg.layer_window(li)
+        if batch.is_prefill:
+            attn = ops.attention_prefill(q, k_cache, v_cache, batch.block_table, batch.seq_lens, batch.cu_q,
+                                         batch.max_q_len, self.scale, window=window, sinks=lw.sinks)
+        else:
+            attn = ops.attention_decode(q, k_cache, v_cache, batch.block_table, batch.seq_lens, batch.q_per_seq,
+                                        self.scale, splits=batch.splits, window=window, sinks=lw.sinks,
+                                        scratch=batch.scratch)
+        attn = attn.view(attn.shape[0], -1)
+        h = self._row_linear(lw, "o", attn, lw.wo, residual=h, bias=lw.bo)
+        normed, _ = ops.rmsnorm(h, lw.ffn_norm, cfg.rms_norm_eps, weight_offset=cfg.norm_weight_offset)
+        if lw.moe is not None:
+            return lw.moe(normed, residual=h)
+        qgu = lw.qlin.get("gate_up")
+        if qgu is not None:
+            act = ops.silu_mul(qgu(normed), qgu.out_features // 2, cfg.swiglu_limit)
+        else:
+            act = ops.gated_linear(normed, lw.w_gate_up, lw.w_gate_up.shape[0] // 2)
+        return self._row_linear(lw, "down", act, lw.w_down, residual=h)
+
+    # ------------------------------------------------------------------------------------------ model
+    def embed_tokens(self, token_ids):
+        h = ops.embedding(token_ids, self.embed, 0, self.cfg.embedding_scale)
+        return h
+
+    def forward_hidden(self, batch: ForwardBatch, kv):
+        if self.par.owns_embedding():
+            h = self.embed_tokens(batch.token_ids)
+        else:
+            h = batch.hidden_in
+        for i, lw in enumerate(self.layers):
+            h = self.layer_forward(self.first_layer + i, lw, h, batch, kv)
+        return h
+
+    def logits(self, h, rows=None):
+        if rows is not None:
+            h = h.index_select(0, rows)
+        normed, _ = ops.rmsnorm(h.contiguous(), self.final_norm, self.cfg.rms_norm_eps,
+                                weight_offset=self.cfg.norm_weight_offset)
+        local = ops.linear(normed, self.lm_head, out_dtype=torch.float32)
+        if self.par.tp_size > 1 and self.lm_head.shape[0] != self.cfg.vocab_size:
+            return self.tp_ops.all_gather_logits(local, self.cfg.vocab_size)
+        return local
+
+    def forward(self, batch: ForwardBatch, kv):
+        """Returns fp32 logits [R, V] on the last pipeline stage, the hidden state otherwise."""
+        h = self.forward_hidden(batch, kv)
+        if not self.par.owns_output_head():
+            return h
+        return self.logits(h, batch.logit_rows)
+
+    # ------------------------------------------------------------------------------------------ weights
+    def num_local_layers(self) -> int:
+        return self.last_layer - self.first_layer
+
+    def weight_bytes(self) -> int:
+        total = 0
+        seen = set()
+
+        def add(t):
+            nonlocal total
+            if isinstance(t, torch.Tensor) and t.data_ptr() not in seen:
+                seen.add(t.data_ptr())
+                total += t.numel() * t.element_size()
+
+        for t in (self.embed, self.final_norm, self.lm_head):
+            add(t)
+        for lw in self.layers:
+            for v in vars(lw).values():
+                add(v)
+            for q in lw.qlin.values():
+                for t in q.tensors():
+                    add(t)
+            if lw.moe is not None:
+                for t in lw.moe.tensors():
+                    add(t)
+        return total
+
+
+# ---------------------------------------------------------------------------------------------- builders
+def _tp_rows(t: torch.Tensor, rank: int, size: int) -> torch.Tensor:
+    n = t.shape[0] // size
+    return t[rank * n:(rank + 1) * n]
+
+
+def _tp_cols(t: torch.Tensor, rank: int, size: int) -> torch.Tensor:
+    n = t.shape[1] // size
+    return t[:, rank * n:(rank + 1) * n]
+
+
+def shard_attention(cfg: ModelConfig, par, wq, wk, wv, wo, bq=None, bk=None, bv=None):
+    """Tensor-parallel slices of the attention projections; a GQA group is the atomic unit and KV heads are
+    replicated when there are fewer of them than ranks (nn/parallel.rs:104-183 defines the group rule; the
+    replication extends it to tp > n_kv)."""
+    D = cfg.head_dim
+    tp, r = par.tp_size, par.tp_rank
+    n_q_local, n_kv_local, rep = par.attention_partition(cfg.num_attention_heads, cfg.num_key_value_heads)
+    q0 = r * n_q_local
+    kv0 = (r // rep) * n_kv_local if rep > 1 else r * n_kv_local
+    wq_l = wq[q0 * D:(q0 + n_q_local) * D]
+    wk_l = wk[kv0 * D:(kv0 + n_kv_local) * D]
+    wv_l = wv[kv0 * D:(kv0 + n_kv_local) * D]
+    wo_l = wo[:, q0 * D:(q0 + n_q_local) * D]
+    b = None
+    if bq is not None:
+        b = torch.cat((bq[q0 * D:(q0 + n_q_local) * D], bk[kv0 * D:(kv0 + n_kv_local) * D],
+                       bv[kv0 * D:(kv0 + n_kv_local) * D]))
+    return torch.cat((wq_l, wk_l, wv_l), 0), wo_l, b
+
+
+def build_from_tensors(cfg: ModelConfig, get: Callable[[str], torch.Tensor], has: Callable[[str], bool], device, dtype,
+                       parallel=None, moe_factory=None, quantizer=None) -> CausalLM:
+    """Populate a model from HF-named tensors. ``get(name)`` returns a CPU (or device) tensor; slicing for
+    tensor/pipeline parallelism happens here so that a rank only uploads what it owns."""
+    model = CausalLM(cfg, device, dtype, parallel)
+    par = model.par
+    tp, r = par.tp_size, par.tp_rank
+
+    def up(t, dt=None):
+        return t.to(device=model.device, dtype=dt or dtype).contiguous()
+
+    if par.owns_embedding() or (par.owns_output_head() and cfg.tie_word_embeddings):
+        model.embed = up(get("model.embed_tokens.weight"))
+    if par.owns_output_head():
+        model.final_norm = up(get("model.norm.weight"), torch.float32)
+        head = get("lm_head.weight") if (not cfg.tie_word_embeddings and has("lm_head.weight")) else None
+        if head is None:
+            head = get("model.embed_tokens.weight")
+        if tp > 1 and cfg.vocab_size % tp == 0:
+            head = _tp_rows(head, r, tp)
+            model.vocab_start = r * (cfg.vocab_size // tp)
+            model.lm_head = up(head)
+        else:
+            model.lm_head = model.embed if (head is None or (cfg.tie_word_embeddings and model.embed is not None
+                                                             and not has("lm_head.weight"))) else up(head)
+    for li in range(model.first_layer, model.last_layer):
+        p = f"model.layers.{li}."
+        wq, wk, wv, wo = (get(p + f"self_attn.{n}_proj.weight") for n in "qkvo")
+        bq = bk = bv = None
+        if has(p + "self_attn.q_proj.bias"):
+            bq, bk, bv = (get(p + f"self_attn.{n}_proj.bias") for n in "qkv")
+        wqkv, wo_l, bqkv = shard_attention(cfg, par, wq, wk, wv, wo, bq, bk, bv)
+        lw = LayerWeights(
+            attn_norm=up(get(p + "input_layernorm.weight"), torch.float32),
+            wqkv=up(wqkv), wo=up(wo_l),
+            ffn_norm=up(get(p + "post_attention_layernorm.weight"), torch.float32),
+            bqkv=up(bqkv) if bqkv is not None else None,
+        )
+        if has(p + "self_attn.o_proj.bias"):
+            lw.bo = up(get(p + "self_attn.o_proj.bias"))
+        if cfg.qk_norm and has(p + "self_attn.q_norm.weight"):
+            lw.q_norm = up(get(p + "self_attn.q_norm.weight"), torch.float32)
+            lw.k_norm = up(get(p + "self_attn.k_norm.weight"), torch.float32)
+        if has(p + "self_attn.sinks"):
+            n_q_local = model.n_q_local
+            lw.sinks = up(get(p + "self_attn.sinks")[r * n_q_local:(r + 1) * n_q_local], torch.float32)
+        if cfg.layer_is_moe(li):
+            assert moe_factory is not None, "MoE layer needs a moe_factory"
+            lw.moe = moe_factory(model, li, get, has)
+        else:
+            wg, wu, wd = (get(p + f"mlp.{n}_proj.weight") for n in ("gate", "up", "down"))
+            if tp > 1:
+                wg, wu, wd = _tp_rows(wg, r, tp), _tp_rows(wu, r, tp), _tp_cols(wd, r, tp)
+            lw.w_gate_up = up(torch.cat((wg, wu), 0))
+            lw.w_down = up(wd)
+        if quantizer is not None:
+            quantizer(model, li, lw)
+        model.layers.append(lw)
+    return model
+
+
+def random_state(cfg: ModelConfig, seed: int = 0, std: float = 0.02, dtype=torch.float32, device="cpu") -> dict:
+    """Seeded HF-named random checkpoint: N(0, std) matrices, unit norms. Deterministic per tensor name, so
+    any subset (a pipeline stage, a TP slice source) can be generated independently."""
+    import zlib
+
+    out: dict[str, torch.Tensor] = {}
+
+    def mat(name, *shape):
+        g = torch.Generator(device="cpu")
+        g.manual_seed((seed * 1000003 + zlib.crc32(name.encode())) & 0x7FFFFFFFFFFF)
+        out[name] = (torch.randn(*shape, generator=g, dtype=torch.float32) * std).to(dtype=dtype, device=device)
+
+    def ones(name, n):
+        out[name] = torch.ones(n, dtype=dtype, device=device)
+
+    H, D = cfg.hidden_size, cfg.head_dim
+    mat("model.embed_tokens.weight", cfg.vocab_size, H)
+    ones("model.norm.weight", H)
+    if not cfg.tie_word_embeddings:
+        mat("lm_head.weight", cfg.vocab_size, H)
+    for li in range(cfg.num_hidden_layers):
+        p = f"model.layers.{li}."
+        ones(p + "input_layernorm.weight", H)
+        ones(p + "post_attention_layernorm.weight", H)
+        mat(p + "self_attn.q_proj.weight", cfg.num_attention_heads * D, H)
+        mat(p + "self_attn.k_proj.weight", cfg.num_key_value_heads * D, H)
+        mat(p + "self_attn.v_proj.weight", cfg.num_key_value_heads * D, H)
+        mat(p + "self_attn.o_proj.weight", H, cfg.num_attention_heads * D)
+        if cfg.attention_bias:
+            mat(p + "self_attn.q_proj.bias", cfg.num_attention_heads * D)
+            mat(p + "self_attn.k_proj.bias", cfg.num_key_value_heads * D)
+            mat(p + "self_attn.v_proj.bias", cfg.num_key_value_heads * D)
+        if cfg.qk_norm:
+            ones(p + "self_attn.q_norm.weight", D)
+            ones(p + "self_attn.k_norm.weight", D)
+        if cfg.layer_is_moe(li):
+            mat(p + "mlp.gate.weight", cfg.num_experts, H)
+            for e in range(cfg.num_experts):
+                mat(p + f"mlp.experts.{e}.gate_proj.weight", cfg.moe_intermediate_size, H)
+                mat(p + f"mlp.experts.{e}.up_proj.weight", cfg.moe_intermediate_size, H)
+                mat(p + f"mlp.experts.{e}.down_proj.weight", H, cfg.moe_intermediate_size)
+        else:
+            mat(p + "mlp.gate_proj.weight", cfg.intermediate_size, H)
+            mat(p + "mlp.up_proj.weight", cfg.intermediate_size, H)
+            mat(p + "mlp.down_proj.weight", H, cfg.intermediate_size)
+    return out
+
+
+def build_random(cfg: ModelConfig, device, dtype, seed: int = 0, parallel=None, moe_factory=None, quantizer=None,
+                 std: float = 0.02) -> CausalLM:
+    """Random-init model of the given shape, generated tensor by tensor on the target device (used by the
+    benchmarks: no checkpoint on disk, no full fp32 copy on the host)."""
+    import zlib
+
+    dev = torch.device(device)
+
+    def get(name: str) -> torch.Tensor:
+        shape = _shape_of(cfg, name)
+        if name.endswith("norm.weight") or name.endswith("layernorm.weight"):
+            return torch.ones(shape, dtype=torch.float32, device=dev)
+        g = torch.Generator(device=dev)
+        g.manual_seed((seed * 1000003 + zlib.crc32(name.encode())) & 0x7FFFFFFFFFFF)
+        t = torch.randn(shape, generator=g, dtype=torch.float32 if dev.type == "cpu" else torch.bfloat16, device=dev)
+        return (t * std).to(dtype)
+
+    def has(name: str) -> bool:
+        return _shape_of(cfg, name) is not None
+
+    return build_from_tensors(cfg, get, has, device, dtype, parallel, moe_factory, quantizer)
+
+
+def _shape_of(cfg: ModelConfig, name: str):
+    H, D = cfg.hidden_size, cfg.head_dim
+    if name == "model.embed_tokens.weight":
+        return (cfg.vocab_size, H)
+    if name == "lm_head.weight":
+        return None if cfg.tie_word_embeddings else (cfg.vocab_size, H)
+    if name == "model.norm.weight":
+        return (H,)
+    parts = name.split(".")
+    if parts[:2] != ["model", "layers"]:
+        return None
+    li = int(parts[2])
+    rest = ".".join(parts[3:])
+    table = {
+        "input_layernorm.weight": (H,), "post_attention_layernorm.weight": (H,),
+        "self_attn.q_proj.weight": (cfg.num_attention_heads * D, H),
+        "self_attn.k_proj.weight": (cfg.num_key_value_heads * D, H),
+        "self_attn.v_proj.weight": (cfg.num_key_value_heads * D, H),
+        "self_attn.o_proj.weight": (H, cfg.num_attention_heads * D),
+    }
+    if cfg.attention_bias:
+        table.update({"self_attn.q_proj.bias": (cfg.num_attention_heads * D,),
+                      "self_attn.k_proj.bias": (cfg.num_key_value_heads * D,),
+                      "self_attn.v_proj.bias": (cfg.num_key_value_heads * D,)})
+    if cfg.qk_norm:
+        table.update({"self_attn.q_norm.weight": (D,), "self_attn.k_norm.weight": (D,)})
+    if cfg.layer_is_moe(li):
+        table["mlp.gate.weight"] = (cfg.num_experts, H)
+        if rest.startswith("mlp.experts."):
+            kind = parts[-2]
+            I = cfg.moe_intermediate_size
+            return {"gate_proj": (I, H), "up_proj": (I, H), "down_proj": (H, I)}.get(kind)
+    else:
+        I = cfg.intermediate_size
+        table.update({"mlp.gate_proj.weight": (I, H), "mlp.up_proj.weight": (I, H), "mlp.down_proj.weight": (H, I)})
+    return table.get(rest)

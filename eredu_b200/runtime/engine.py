@@ -1,0 +1,356 @@
+"""Batch execution engine: chunked prefill, CUDA-graph decode, device-side sampling and bookkeeping.
+
+The reference submits one lazy graph per token and blocks on a host read of the sampled id
+(eredu-core/src/backend.rs:834-912, eredu/src/backend/mlx/session.rs:816-1019). Here a decode step is a
+captured CUDA graph: model forward -> fused sampler -> ``decode_advance`` (token feedback, positions, KV
+slot, RNG position, penalty history — all on the device), so replaying step n+1 needs nothing from the
+host. The host only *observes* tokens through an asynchronous copy into pinned memory.
+
+Under tensor parallelism every rank runs this engine in lock-step on identical inputs; logits are
+identical on all ranks after the gather, the sampler is deterministic, so every rank commits the same
+token without a broadcast (the reference uses two all-sums and a host sync per step for this:
+eredu/src/backend/mlx/runtime/distributed/parallel.rs:46-105).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..models.llama import CausalLM, ForwardBatch
+from ..ops.sampling import ROW_DTYPE, SamplingParams, pack_rows
+from .kv_cache import PAGE, PagedKVCache
+
+
+@dataclass
+class Sequence:
+    seq_id: int
+    prompt: list[int]
+    sampling: SamplingParams = field(default_factory=SamplingParams)
+    max_new_tokens: int = 256
+    eos_ids: tuple = ()
+    output: list[int] = field(default_factory=list)
+    pages: list[int] = field(default_factory=list)
+    kv_len: int = 0            # tokens whose K/V are in the cache
+    finished: bool = False
+    finish_reason: Optional[str] = None
+    slot: int = -1             # row in the decode batch
+
+    @property
+    def total_len(self) -> int:
+        return len(self.prompt) + len(self.output)
+
+
+class Engine:
+    def __init__(self, model: CausalLM, max_batch: int = 32, max_seq_len: int = 4096, num_pages: Optional[int] = None,
+                 use_cuda_graph: Optional[bool] = None, prefill_chunk: int = 8192, hist_cap: int = 1024):
+        self.model = model
+        self.cfg = model.cfg
+        self.device = model.device
+        self.max_batch = max_batch
+        self.max_seq_len = max_seq_len
+        self.max_pages = PagedKVCache.pages_for(max_seq_len)
+        if num_pages is None:
+            num_pages = max_batch * self.max_pages + 1
+        self.kv = PagedKVCache(model.num_local_layers(), model.n_kv_local, self.cfg.head_dim, num_pages, model.dtype,
+                               self.device, first_layer=model.first_layer)
+        self.cuda = self.device.type == "cuda"
+        self.use_graph = self.cuda if use_cuda_graph is None else (use_cuda_graph and self.cuda)
+        self.prefill_chunk = prefill_chunk
+        self.hist_cap = hist_cap
+        self._next_id = 0
+        self._graphs: dict = {}
+        self._decode_state = None
+        self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count if self.cuda else 1
+
+    # ------------------------------------------------------------------------------------------ requests
+    def new_sequence(self, prompt, sampling=None, max_new_tokens=256, eos_ids=()) -> Sequence:
+        seq = Sequence(self._next_id, list(prompt), sampling or SamplingParams(), max_new_tokens, tuple(eos_ids))
+        self._next_id += 1
+        if len(seq.prompt) + max_new_tokens > self.max_seq_len:
+            raise ValueError(f"prompt ({len(seq.prompt)}) + max_new_tokens ({max_new_tokens}) exceeds "
+                             f"max_seq_len {self.max_seq_len}")
+        # Reserve every page the request can need up front: the block table is then static for the
+        # whole decode and the captured graph never needs a host update.
+        seq.pages = list(self.kv.allocator.alloc(PagedKVCache.pages_for(len(seq.prompt) + max_new_tokens)))
+        return seq
+
+    def release(self, seq: Sequence) -> None:
+        if seq.pages:
+            self.kv.allocator.release(seq.pages)
+            seq.pages = []
+
+    # ------------------------------------------------------------------------------------------ helpers
+    def _t(self, data, dtype):
+        t = torch.as_tensor(data, dtype=dtype)
+        if self.cuda:
+            t = t.pin_memory().to(self.device, non_blocking=True)
+        return t
+
+    def _block_table(self, seqs) -> torch.Tensor:
+        bt = np.zeros((len(seqs), self.max_pages), dtype=np.int32)
+        for i, s in enumerate(seqs):
+            bt[i, :len(s.pages)] = s.pages
+        return self._t(bt, torch.int32)
+
+    def _sample(self, logits, seqs, positions, history=None):
+        """Sample one token per row. CUDA: fused kernel; CPU: the oracle chain."""
+        if self.cuda:
+            rows = pack_rows([s.sampling for s in seqs], positions,
+                             hist_lens=[min(len(s.output), self.hist_cap) for s in seqs],
+                             stream_ids=[s.seq_id for s in seqs])
+            hist = None
+            if any(s.sampling.repeat_penalty != 1.0 or s.sampling.frequency_penalty != 0.0
+                   or s.sampling.presence_penalty != 0.0 for s in seqs):
+                h = np.zeros((len(seqs), self.hist_cap), dtype=np.int32)
+                for i, s in enumerate(seqs):
+                    tail = s.output[-self.hist_cap:]
+                    h[i, :len(tail)] = tail
+                hist = self._t(h, torch.int32)
+            rows_t = self._t(rows.view(np.uint8).reshape(len(seqs), ROW_DTYPE.itemsize), torch.uint8)
+            return ops.sample(logits.contiguous(), rows_t, history=hist)
+        toks = []
+        for i, s in enumerate(seqs):
+            tok, _ = ops.sample_ref(logits[i], s.sampling, positions[i], history=s.output, stream=s.seq_id)
+            toks.append(tok)
+        return torch.tensor(toks, dtype=torch.int32)
+
+    # ------------------------------------------------------------------------------------------ prefill
+    @torch.no_grad()
+    def prefill(self, seqs: list[Sequence]) -> torch.Tensor:
+        """Run the prompts through the model (chunked), sample the first token of each. Returns [B] int32."""
+        groups, cur, cur_tokens = [], [], 0
+        for s in seqs:
+            n = len(s.prompt) - s.kv_len
+            if cur and cur_tokens + n > self.prefill_chunk:
+                groups.append(cur)
+                cur, cur_tokens = [], 0
+            cur.append(s)
+            cur_tokens += n
+        if cur:
+            groups.append(cur)
+        outs = []
+        for g in groups:
+            outs.append(self._prefill_group(g))
+        return torch.cat(outs)
+
+    def _prefill_group(self, seqs):
+        toks, pos, slots, cu, lens = [], [], [], [0], []
+        max_q = 0
+        for s in seqs:
+            new = s.prompt[s.kv_len:]
+            n = len(new)
+            p = np.arange(s.kv_len, s.kv_len + n)
+            pages = np.asarray(s.pages, dtype=np.int64)
+            toks.extend(new)
+            pos.append(p)
+            slots.append(pages[p // PAGE] * PAGE + (p % PAGE))
+            cu.append(cu[-1] + n)
+            lens.append(s.kv_len + n)
+            max_q = max(max_q, n)
+        batch = ForwardBatch(
+            token_ids=self._t(np.asarray(toks, dtype=np.int32), torch.int32),
+            positions=self._t(np.concatenate(pos).astype(np.int32), torch.int32),
+            slots=self._t(np.concatenate(slots), torch.int64),
+            block_table=self._block_table(seqs),
+            seq_lens=self._t(np.asarray(lens, dtype=np.int32), torch.int32),
+            is_prefill=True,
+            cu_q=self._t(np.asarray(cu, dtype=np.int32), torch.int32),
+            max_q_len=max_q,
+            logit_rows=self._t(np.asarray(cu[1:], dtype=np.int64) - 1, torch.int64),
+        )
+        logits = self.model.forward(batch, self.kv)
+        for s, n in zip(seqs, lens):
+            s.kv_len = n
+        tokens = self._sample(logits, seqs, [len(s.prompt) for s in seqs])
+        return tokens
+
+    # ------------------------------------------------------------------------------------------ decode
+    def start_decode(self, seqs: list[Sequence], first_tokens: torch.Tensor) -> None:
+        """Load the decode state of a batch into the static device buffers (one H2D per buffer)."""
+        B = len(seqs)
+        assert B <= self.max_batch
+        dev = self.device
+        pos = np.asarray([s.kv_len for s in seqs], dtype=np.int32)
+        pages = [np.asarray(s.pages, dtype=np.int64) for s in seqs]
+        slots = np.asarray([pg[p // PAGE] * PAGE + (p % PAGE) for pg, p in zip(pages, pos)], dtype=np.int64)
+        rows = pack_rows([s.sampling for s in seqs], [int(p) + 1 for p in pos],
+                         hist_lens=[min(len(s.output), self.hist_cap) for s in seqs],
+                         stream_ids=[s.seq_id for s in seqs])
+        need_hist = any(s.sampling.repeat_penalty != 1.0 or s.sampling.frequency_penalty != 0.0
+                        or s.sampling.presence_penalty != 0.0 for s in seqs)
+        hist = None
+        if need_hist:
+            h = np.zeros((B, self.hist_cap), dtype=np.int32)
+            for i, s in enumerate(seqs):
+                tail = s.output[-self.hist_cap:]
+                h[i, :len(tail)] = tail
+            hist = self._t(h, torch.int32)
+        max_len = int(pos.max()) + 1 + max(s.max_new_tokens for s in seqs)
+        splits = ops.decode_splits(B, self.model.n_kv_local, max_len, self.sm_count) if self.cuda else 1
+        st = {
+            "B": B,
+            "seqs": list(seqs),
+            "token_ids": first_tokens.to(dev, torch.int32).clone(),
+            "positions": self._t(pos, torch.int32),
+            "seq_lens": self._t(pos + 1, torch.int32),
+            "slots": self._t(slots, torch.int64),
+            "block_table": self._block_table(seqs),
+            "active": self._t(np.ones(B, dtype=np.int32), torch.int32),
+            "rows": self._t(rows.view(np.uint8).reshape(B, ROW_DTYPE.itemsize), torch.uint8),
+            "history": hist,
+            "sampled": torch.zeros(B, dtype=torch.int32, device=dev),
+            "splits": splits,
+            "scratch": ops.decode_scratch(B, 1, self.model.n_q_local, self.cfg.head_dim, splits, dev)
+            if (self.cuda and splits > 1) else None,
+            "graph": None,
+            "host_tokens": torch.zeros(B, dtype=torch.int32).pin_memory() if self.cuda else None,
+            "host_in": torch.zeros(B, dtype=torch.int32).pin_memory() if self.cuda else None,
+        }
+        self._decode_state = st
+        for i, s in enumerate(seqs):
+            s.slot = i
+
+    def _decode_body(self, st):
+        batch = ForwardBatch(token_ids=st["token_ids"], positions=st["positions"], slots=st["slots"],
+                             block_table=st["block_table"], seq_lens=st["seq_lens"], is_prefill=False, q_per_seq=1,
+                             splits=st["splits"], scratch=st["scratch"])
+        logits = self.model.forward(batch, self.kv)
+        ops.sample(logits, st["rows"], history=st["history"], out=st["sampled"])
+        hist = st["history"]
+        code = ops.native.lib().eredu_decode_advance(
+            st["sampled"].data_ptr(), st["token_ids"].data_ptr(), st["positions"].data_ptr(),
+            st["seq_lens"].data_ptr(), st["slots"].data_ptr(), st["block_table"].data_ptr(),
+            st["block_table"].stride(0), st["active"].data_ptr(), st["rows"].data_ptr(), ROW_DTYPE.itemsize // 4,
+            None if hist is None else hist.data_ptr(), 0 if hist is None else hist.stride(0), st["B"],
+            ops.native.stream_ptr(self.device))
+        ops.native.check(code, "eredu_decode_advance")
+
+    @torch.no_grad()
+    def decode_step(self, host_tokens: Optional[torch.Tensor] = None, sync: bool = True) -> Optional[torch.Tensor]:
+        """One decode step for the batch loaded by :meth:`start_decode`.
+
+        ``host_tokens`` (pinned int32 [B]) overrides the device-side token feedback: the step then includes
+        the host->device copy of its inputs. With ``sync`` the sampled ids are copied back and returned.
+        """
+        st = self._decode_state
+        if not self.cuda:
+            return self._decode_step_cpu(st)
+        if host_tokens is not None:
+            st["token_ids"].copy_(host_tokens, non_blocking=True)
+        if self.use_graph:
+            if st["graph"] is None:
+                # warm-up run outside capture (lazy kernel attribute setup), then restore the state it advanced
+                saved = {k: st[k].clone() for k in ("token_ids", "positions", "seq_lens", "slots", "rows")}
+                saved_h = st["history"].clone() if st["history"] is not None else None
+                s = torch.cuda.Stream(device=self.device)
+                s.wait_stream(torch.cuda.current_stream(self.device))
+                with torch.cuda.stream(s):
+                    self._decode_body(st)
+                torch.cuda.current_stream(self.device).wait_stream(s)
+                torch.cuda.synchronize(self.device)
+                for k, v in saved.items():
+                    st[k].copy_(v)
+                if saved_h is not None:
+                    st["history"].copy_(saved_h)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    self._decode_body(st)
+                # capture does not execute: state is still the pre-step state
+                st["graph"] = g
+            st["graph"].replay()
+        else:
+            self._decode_body(st)
+        if not sync:
+            return None
+        st["host_tokens"].copy_(st["sampled"], non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        return st["host_tokens"]
+
+    def _decode_step_cpu(self, st):
+        seqs = st["seqs"]
+        batch = ForwardBatch(token_ids=st["token_ids"], positions=st["positions"], slots=st["slots"],
+                             block_table=st["block_table"], seq_lens=st["seq_lens"], is_prefill=False, q_per_seq=1)
+        logits = self.model.forward(batch, self.kv)
+        pos = st["positions"].tolist()
+        toks = self._sample(logits, seqs, [p + 1 for p in pos])
+        active = st["active"].bool()
+        st["sampled"] = toks
+        newpos = st["positions"] + 1
+        bt = st["block_table"].long()
+        page = bt.gather(1, (newpos.long() // PAGE)[:, None]).squeeze(1)
+        st["token_ids"] = torch.where(active, toks, st["token_ids"])
+        st["positions"] = torch.where(active, newpos, st["positions"])
+        st["seq_lens"] = torch.where(active, newpos + 1, st["seq_lens"])
+        st["slots"] = torch.where(active, page * PAGE + (newpos.long() % PAGE), torch.full_like(page, -1))
+        return toks
+
+    def commit(self, tokens) -> list[bool]:
+        """Record one sampled token per running sequence (host side); returns per-sequence 'just finished'."""
+        st = self._decode_state
+        done = []
+        changed = False
+        for i, s in enumerate(st["seqs"]):
+            if s.finished:
+                done.append(False)
+                continue
+            tok = int(tokens[i])
+            s.output.append(tok)
+            s.kv_len += 1
+            fin = False
+            if tok in s.eos_ids:
+                s.finished, s.finish_reason, fin = True, "eos", True
+            elif len(s.output) >= s.max_new_tokens:
+                s.finished, s.finish_reason, fin = True, "max_tokens", True
+            if fin:
+                changed = True
+            done.append(fin)
+        if changed:
+            act = np.asarray([0 if s.finished else 1 for s in st["seqs"]], dtype=np.int32)
+            if self.cuda:
+                st["active"].copy_(self._t(act, torch.int32))
+            else:
+                st["active"] = torch.as_tensor(act)
+        return done
+
+    # ------------------------------------------------------------------------------------------ generate
+    @torch.no_grad()
+    def generate(self, prompts: list[list[int]], sampling: Optional[SamplingParams] = None, max_new_tokens: int = 64,
+                 eos_ids=(), on_token=None) -> list[list[int]]:
+        """Greedy / stochastic generation for a batch of token-id prompts. ``on_token(seq_index, token)`` is called
+        as tokens are committed."""
+        seqs = [self.new_sequence(p, sampling, max_new_tokens, eos_ids) for p in prompts]
+        try:
+            first = self.prefill(seqs)
+            first_host = first.tolist()
+            for i, (s, t) in enumerate(zip(seqs, first_host)):
+                s.output.append(int(t))
+                if on_token:
+                    on_token(i, int(t))
+                if int(t) in s.eos_ids:
+                    s.finished, s.finish_reason = True, "eos"
+                elif len(s.output) >= s.max_new_tokens:
+                    s.finished, s.finish_reason = True, "max_tokens"
+            if not all(s.finished for s in seqs):
+                self.start_decode(seqs, first)
+                if any(s.finished for s in seqs):
+                    act = np.asarray([0 if s.finished else 1 for s in seqs], dtype=np.int32)
+                    self._decode_state["active"] = self._t(act, torch.int32)
+                while not all(s.finished for s in seqs):
+                    toks = self.decode_step()
+                    was = [s.finished for s in seqs]
+                    self.commit(toks.tolist())
+                    if on_token:
+                        for i, s in enumerate(seqs):
+                            if not was[i]:
+                                on_token(i, s.output[-1])
+            if self.cuda:
+                ops.native.check_status(self.device)
+            return [list(s.output) for s in seqs]
+        finally:
+            for s in seqs:
+                self.release(s)
+            self._decode_state = None

@@ -1,0 +1,77 @@
+"""Independent dense (non-paged, no cache) PyTorch implementation of the Llama-family forward used as the
+oracle for the engine: full recompute of the whole sequence at every step."""
+import math
+
+import torch
+import torch.nn.functional as F
+
+from eredu_b200.models.rope import rope_tables
+
+
+def rms(x, w, eps, off=0.0):
+    return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * (w + off)
+
+
+def rope(x, pos, inv_freq, factor, interleaved, rot):
+    # x: [T, heads, D]
+    ang = pos.float()[:, None] * inv_freq[None, :]
+    cos, sin = (ang.cos() * factor)[:, None, :], (ang.sin() * factor)[:, None, :]
+    xr, xp = x[..., :rot], x[..., rot:]
+    if interleaved:
+        a, b = xr[..., 0::2], xr[..., 1::2]
+        out = torch.stack((a * cos - b * sin, b * cos + a * sin), -1).flatten(-2)
+    else:
+        a, b = xr[..., : rot // 2], xr[..., rot // 2:]
+        out = torch.cat((a * cos - b * sin, b * cos + a * sin), -1)
+    return torch.cat((out, xp), -1)
+
+
+def forward_logits(cfg, sd, tokens, moe_fn=None):
+    """sd: HF-named fp32 state dict; tokens: list[int]. Returns logits [T, V] (fp32)."""
+    sd = {k: v.float() for k, v in sd.items()}
+    T = len(tokens)
+    D, Hq, Hkv = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads
+    inv, factor = rope_tables(cfg)
+    pos = torch.arange(T)
+    h = sd["model.embed_tokens.weight"][torch.tensor(tokens)] * cfg.embedding_scale
+    for li in range(cfg.num_hidden_layers):
+        p = f"model.layers.{li}."
+        x = rms(h, sd[p + "input_layernorm.weight"], cfg.rms_norm_eps, cfg.norm_weight_offset)
+        q = F.linear(x, sd[p + "self_attn.q_proj.weight"], sd.get(p + "self_attn.q_proj.bias")).view(T, Hq, D)
+        k = F.linear(x, sd[p + "self_attn.k_proj.weight"], sd.get(p + "self_attn.k_proj.bias")).view(T, Hkv, D)
+        v = F.linear(x, sd[p + "self_attn.v_proj.weight"], sd.get(p + "self_attn.v_proj.bias")).view(T, Hkv, D)
+        if p + "self_attn.q_norm.weight" in sd:
+            q = rms(q, sd[p + "self_attn.q_norm.weight"], cfg.rms_norm_eps)
+            k = rms(k, sd[p + "self_attn.k_norm.weight"], cfg.rms_norm_eps)
+        q = rope(q, pos, inv, factor, cfg.rope_traditional, cfg.rotary_dim)
+        k = rope(k, pos, inv, factor, cfg.rope_traditional, cfg.rotary_dim)
+        g = Hq // Hkv
+        k, v = k.repeat_interleave(g, 1), v.repeat_interleave(g, 1)
+        s = torch.einsum("qhd,khd->hqk", q, k) / math.sqrt(D)
+        mask = pos[None, :] <= pos[:, None]
+        w = cfg.layer_window(li)
+        if w > 0:
+            mask = mask & (pos[None, :] > pos[:, None] - w)
+        s = s.masked_fill(~mask[None], float("-inf"))
+        a = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), v).reshape(T, Hq * D)
+        h = h + F.linear(a, sd[p + "self_attn.o_proj.weight"])
+        x = rms(h, sd[p + "post_attention_layernorm.weight"], cfg.rms_norm_eps, cfg.norm_weight_offset)
+        if cfg.layer_is_moe(li):
+            h = h + moe_fn(cfg, sd, li, x)
+        else:
+            gate = F.linear(x, sd[p + "mlp.gate_proj.weight"])
+            up = F.linear(x, sd[p + "mlp.up_proj.weight"])
+            h = h + F.linear(F.silu(gate) * up, sd[p + "mlp.down_proj.weight"])
+    x = rms(h, sd["model.norm.weight"], cfg.rms_norm_eps, cfg.norm_weight_offset)
+    head = sd.get("lm_head.weight", sd["model.embed_tokens.weight"])
+    return F.linear(x, head)
+
+
+def greedy(cfg, sd, prompt, n, moe_fn=None):
+    toks = list(prompt)
+    out = []
+    for _ in range(n):
+        t = int(torch.argmax(forward_logits(cfg, sd, toks, moe_fn)[-1]))
+        out.append(t)
+        toks.append(t)
+    return out
