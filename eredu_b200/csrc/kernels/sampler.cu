@@ -179,9 +179,10 @@ __device__ __forceinline__ float load_logit(const SamplerParams& p, const float*
 }
 
 __global__ void __launch_bounds__(kSampThreads) sampler_kernel(SamplerParams p) {
-  __shared__ BlockScratch scr;
-  __shared__ int hist[256];
-  __shared__ unsigned long long cand[kCand];
+  __shared__ __align__(16) BlockScratch scr;
+  __shared__ __align__(16) int hist[256];
+  __shared__ __align__(16) uint32_t cand_key[kCand];
+  __shared__ __align__(16) uint32_t cand_idx[kCand];
   __shared__ int sh_count;
   __shared__ uint32_t sh_prefix;
   __shared__ int sh_krem;
@@ -189,7 +190,13 @@ __global__ void __launch_bounds__(kSampThreads) sampler_kernel(SamplerParams p) 
 
   const int r = blockIdx.x;
   const int tid = threadIdx.x;
-  const SamplerRow cfg = p.rows[r];
+  SamplerRow cfg;
+  {
+    const int* src = reinterpret_cast<const int*>(p.rows + r);
+    int* dst = reinterpret_cast<int*>(&cfg);
+#pragma unroll
+    for (int i = 0; i < static_cast<int>(sizeof(SamplerRow) / 4); ++i) dst[i] = src[i];
+  }
   float* row = p.logits + static_cast<size_t>(r) * p.V;
   const uint32_t* allow = p.allow ? p.allow + static_cast<size_t>(r) * p.allow_stride : nullptr;
   float* prow = p.probs ? p.probs + static_cast<size_t>(r) * p.V : nullptr;
@@ -318,31 +325,41 @@ __global__ void __launch_bounds__(kSampThreads) sampler_kernel(SamplerParams p) 
 
   // ---- 4. gather candidates (key >= threshold), sort descending by (key, then smaller index first)
   if (tid == 0) sh_count = 0;
-  cand[tid] = 0ull;
+  cand_key[tid] = 0u;
+  cand_idx[tid] = 0xFFFFFFFFu;
   __syncthreads();
   for (int i = tid; i < V; i += kSampThreads) {
     const uint32_t k = f2key(load_logit(p, row, allow, i));
     if (k >= thr_key && k > f2key(-INFINITY)) {
       const int slot = atomicAdd(&sh_count, 1);
-      if (slot < kCand) cand[slot] = (static_cast<unsigned long long>(k) << 32) | (0xFFFFFFFFu - static_cast<uint32_t>(i));
+      if (slot < kCand) {
+        cand_key[slot] = k;
+        cand_idx[slot] = static_cast<uint32_t>(i);
+      }
     }
   }
   __syncthreads();
+  // bitonic sort, descending by key, ties by ascending index (empty slots: key 0 sorts last)
   for (int k = 2; k <= kCand; k <<= 1) {
     for (int j = k >> 1; j > 0; j >>= 1) {
       const int ixj = tid ^ j;
       if (ixj > tid) {
-        const unsigned long long a = cand[tid], b = cand[ixj];
+        const uint32_t ka = cand_key[tid], kb = cand_key[ixj];
+        const uint32_t ia = cand_idx[tid], ib = cand_idx[ixj];
+        const bool a_before_b = (ka > kb) || (ka == kb && ia < ib);  // a ranks ahead of b
         const bool desc = (tid & k) == 0;
-        if (desc ? (a < b) : (a > b)) { cand[tid] = b; cand[ixj] = a; }
+        if (desc ? !a_before_b : a_before_b) {
+          cand_key[tid] = kb; cand_idx[tid] = ib;
+          cand_key[ixj] = ka; cand_idx[ixj] = ia;
+        }
       }
       __syncthreads();
     }
   }
   const int ncand = min(sh_count, kCand);
   const bool valid = tid < ncand;
-  const float x = valid ? key2f(static_cast<uint32_t>(cand[tid] >> 32)) : -INFINITY;
-  const int tok = valid ? static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(cand[tid] & 0xFFFFFFFFull)) : 0;
+  const float x = valid ? key2f(cand_key[tid]) : -INFINITY;
+  const int tok = valid ? static_cast<int>(cand_idx[tid]) : 0;
 
   // ---- 5. top-p at temperature 1 on the top-k survivors
   const float p1 = valid ? __expf(x - vmax) : 0.f;
@@ -398,7 +415,13 @@ __global__ void __launch_bounds__(kSampThreads) spec_verify_kernel(VerifyParams 
   __shared__ BlockScratch scr;
   __shared__ int sh_pick;
   const int b = blockIdx.x, tid = threadIdx.x;
-  const SamplerRow cfg = p.rows[b];
+  SamplerRow cfg;
+  {
+    const int* src = reinterpret_cast<const int*>(p.rows + b);
+    int* dst = reinterpret_cast<int*>(&cfg);
+#pragma unroll
+    for (int i = 0; i < static_cast<int>(sizeof(SamplerRow) / 4); ++i) dst[i] = src[i];
+  }
   const int V = p.V;
   const float* pt = p.p_t + static_cast<size_t>(b) * (p.n_draft + 1) * V;
   const float* pd = p.p_d + static_cast<size_t>(b) * p.n_draft * V;

@@ -153,12 +153,111 @@ def sample_ref(logits: torch.Tensor, sp: SamplingParams, position: int, history=
 
 
 # ------------------------------------------------------------------------------------------ kernels
+def _philox_uniform_t(seed_lo, seed_hi, stream, position, purpose: int) -> torch.Tensor:
+    """Tensor twin of :func:`philox_uniform` (int64 arithmetic on the device, no host sync)."""
+    M32 = 0xFFFFFFFF
+    c0, c1 = position.long() & M32, stream.long() & M32
+    c2 = torch.full_like(c0, purpose)
+    c3 = torch.full_like(c0, 0x45524544)
+    k0, k1 = seed_lo.long() & M32, seed_hi.long() & M32
+
+    def mulhilo(a: int, b):
+        # 32x32 -> (hi, lo) without overflowing int64: split b into 16-bit halves
+        b_lo, b_hi = b & 0xFFFF, b >> 16
+        p0 = a * b_lo                      # < 2^48
+        p1 = a * b_hi                      # < 2^48
+        lo = (p0 + ((p1 & 0xFFFF) << 16))
+        hi = (p1 >> 16) + (lo >> 32)
+        return hi & M32, lo & M32
+
+    for _ in range(10):
+        hi0, lo0 = mulhilo(0xD2511F53, c0)
+        hi1, lo1 = mulhilo(0xCD9E8D57, c2)
+        c0, c1, c2, c3 = (hi1 ^ c1 ^ k0) & M32, lo1, (hi0 ^ c3 ^ k1) & M32, lo0
+        k0 = (k0 + 0x9E3779B9) & M32
+        k1 = (k1 + 0xBB67AE85) & M32
+    return (c0 >> 8).to(torch.float32) * (1.0 / 16777216.0)
+
+
+def _rows_fields(rows: torch.Tensor):
+    r32 = rows.view(torch.int32)
+    f32 = rows.view(torch.float32)
+    return {"temperature": f32[:, 0], "top_p": f32[:, 1], "min_p": f32[:, 2], "repeat_penalty": f32[:, 3],
+            "frequency_penalty": f32[:, 4], "presence_penalty": f32[:, 5], "top_k": r32[:, 6],
+            "repeat_last_n": r32[:, 7], "hist_len": r32[:, 8], "position": r32[:, 9], "seed_lo": r32[:, 10],
+            "seed_hi": r32[:, 11], "stream_id": r32[:, 12]}
+
+
+def sample_tensor_ops(logits, rows, history=None, allow=None, probs=None, out=None):
+    """The sampler chain written with tensor operations only (sort based, no host synchronisation, CUDA-graph
+    safe). Same semantics and the same position-addressed uniforms as the fused kernel; used for rows with
+    temperature > 0 on the GPU."""
+    R, V = logits.shape
+    f = _rows_fields(rows)
+    x = logits
+    if allow is not None:
+        words = allow.view(-1, allow.shape[-1]).long() & 0xFFFFFFFF
+        bits = ((words[:, :, None] >> torch.arange(32, device=x.device)) & 1).reshape(words.shape[0], -1)[:, :V]
+        x = x.masked_fill(bits.expand(R, V) == 0, float("-inf"))
+    if history is not None:
+        H = history.shape[1]
+        idx = torch.arange(H, device=x.device)[None, :]
+        hl, rl = f["hist_len"][:, None], f["repeat_last_n"][:, None]
+        start = torch.where(rl < 0, torch.zeros_like(hl), (hl - rl).clamp(min=0))
+        inwin = (idx >= start) & (idx < hl)
+        toks = history.long().clamp(0, V - 1)
+        counts = torch.zeros(R, V, device=x.device).scatter_add_(1, toks, inwin.float())
+        seen = counts > 0
+        rp = f["repeat_penalty"][:, None]
+        pen = torch.where(x > 0, x / rp, x * rp)
+        x = torch.where(seen, pen, x)
+        x = x - torch.where(seen, f["frequency_penalty"][:, None] * counts + f["presence_penalty"][:, None],
+                            torch.zeros_like(x))
+    greedy = f["temperature"] == 0
+    sx, order = torch.sort(x, dim=-1, descending=True, stable=True)
+    rank = torch.arange(V, device=x.device)[None, :]
+    k = f["top_k"][:, None]
+    use_k = (k > 0) & (k < V)
+    kth = sx.gather(1, (k.long() - 1).clamp(0, V - 1))
+    keep = torch.where(use_k, sx >= kth, torch.ones_like(sx, dtype=torch.bool))
+    xs = sx.masked_fill(~keep, float("-inf"))
+    p1 = torch.softmax(xs, -1)
+    before = torch.cumsum(p1, -1) - p1
+    tp = f["top_p"][:, None]
+    keep = keep & ((tp >= 1.0) | (before <= tp.clamp(min=0)))
+    keep = keep & ((sx - sx[:, :1]) >= torch.log(f["min_p"].clamp(min=1e-38))[:, None]) | (rank == 0)
+    temp = torch.where(greedy, torch.ones_like(f["temperature"]), f["temperature"])[:, None]
+    w = torch.softmax(sx.masked_fill(~keep, float("-inf")) / temp, -1)
+    onehot = (rank == 0).float()
+    w = torch.where(greedy[:, None], onehot, w)
+    u = _philox_uniform_t(f["seed_lo"], f["seed_hi"], f["stream_id"], f["position"], 0)
+    cum = torch.cumsum(w, -1)
+    hit = (cum > (u * cum[:, -1])[:, None]) & (w > 0)
+    first = torch.where(hit.any(-1), hit.float().argmax(-1), (w > 0).float().cumsum(-1).argmax(-1))
+    tok = order.gather(1, first[:, None]).squeeze(1).to(torch.int32)
+    if out is None:
+        out = tok
+    else:
+        out.copy_(tok)
+    if probs is not None:
+        probs.zero_().scatter_(1, order, w)
+    return out
+
+
 def sample(logits: torch.Tensor, rows: torch.Tensor, history: torch.Tensor | None = None,
            allow: torch.Tensor | None = None, probs: torch.Tensor | None = None,
-           out: torch.Tensor | None = None) -> torch.Tensor:
-    """logits: [R, V] fp32 CUDA (modified in place by penalties); rows: packed SamplerRow bytes [R, 56]."""
+           out: torch.Tensor | None = None, all_greedy: bool | None = None) -> torch.Tensor:
+    """logits: [R, V] fp32 CUDA (modified in place by penalties); rows: packed SamplerRow bytes [R, 56].
+
+    Greedy rows run in the fused kernel. The fused kernel's stochastic path is kept off the GPU (it raised a
+    misaligned-address fault on B200 whose cause has not been found by reading the source); batches that
+    contain a row with temperature > 0 use :func:`sample_tensor_ops`, which has the same semantics."""
     assert logits.is_cuda and logits.dtype == torch.float32 and logits.is_contiguous()
     R, V = logits.shape
+    if all_greedy is None:
+        all_greedy = bool((_rows_fields(rows)["temperature"] == 0).all().item())
+    if not all_greedy:
+        return sample_tensor_ops(logits, rows, history, allow, probs, out)
     if out is None:
         out = torch.empty(R, dtype=torch.int32, device=logits.device)
     allow_stride = 0

@@ -111,7 +111,8 @@ class Engine:
                     h[i, :len(tail)] = tail
                 hist = self._t(h, torch.int32)
             rows_t = self._t(rows.view(np.uint8).reshape(len(seqs), ROW_DTYPE.itemsize), torch.uint8)
-            return ops.sample(logits.contiguous(), rows_t, history=hist)
+            return ops.sample(logits.contiguous(), rows_t, history=hist,
+                              all_greedy=all(s.sampling.greedy for s in seqs))
         toks = []
         for i, s in enumerate(seqs):
             tok, _ = ops.sample_ref(logits[i], s.sampling, positions[i], history=s.output, stream=s.seq_id)
@@ -204,6 +205,7 @@ class Engine:
             "history": hist,
             "sampled": torch.zeros(B, dtype=torch.int32, device=dev),
             "splits": splits,
+            "all_greedy": all(s.sampling.greedy for s in seqs),
             "scratch": ops.decode_scratch(B, 1, self.model.n_q_local, self.cfg.head_dim, splits, dev)
             if (self.cuda and splits > 1) else None,
             "graph": None,
@@ -219,7 +221,7 @@ class Engine:
                              block_table=st["block_table"], seq_lens=st["seq_lens"], is_prefill=False, q_per_seq=1,
                              splits=st["splits"], scratch=st["scratch"])
         logits = self.model.forward(batch, self.kv)
-        ops.sample(logits, st["rows"], history=st["history"], out=st["sampled"])
+        ops.sample(logits, st["rows"], history=st["history"], out=st["sampled"], all_greedy=st["all_greedy"])
         hist = st["history"]
         code = ops.native.lib().eredu_decode_advance(
             st["sampled"].data_ptr(), st["token_ids"].data_ptr(), st["positions"].data_ptr(),
