@@ -1,0 +1,137 @@
+"""``LoadedModel``: the user-facing entry point (load -> generate / chat / stream).
+
+Counterpart of ``LoadedModel::{load, generate_tokens, prepare_chat, generate_prepared_chat}``
+(eredu/src/api/loaded.rs:154-612, api/portable.rs:138-250) and ``ModelLoadOptions``
+(eredu/src/backend/mlx/config.rs:13-49).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Iterator, Optional
+
+import torch
+
+from ..formats.checkpoint import GgufSource, SafetensorsSource, TensorSource, open_checkpoint
+from ..models.llama import CausalLM, build_from_tensors
+from ..ops.sampling import SamplingParams
+from ..runtime.engine import Engine
+
+
+@dataclass
+class QuantizationOptions:
+    """Load-time weight quantisation (``--quantize BITS --quantization-mode affine|mxfp4 --quantization-group-size``)."""
+    bits: int = 4
+    group_size: int = 64
+    mode: str = "affine"
+
+
+@dataclass
+class ModelLoadOptions:
+    device: str = "cuda" if torch.cuda.is_available() else "cpu"
+    dtype: Optional[torch.dtype] = None          # None: bf16 on CUDA, fp32 on CPU
+    quantization: Optional[QuantizationOptions] = None
+    parallel: object = None                      # ParallelContext
+    mapped_shards: int = 4
+    max_batch: int = 8
+    max_seq_len: int = 4096
+    kv_pages: Optional[int] = None
+    native_gguf: bool = True                     # keep Q4_K/Q6_K/... blocks and run the native kernels
+    use_cuda_graph: Optional[bool] = None
+
+
+class LoadedModel:
+    def __init__(self, model: CausalLM, engine: Engine, source: TensorSource, tokenizer=None, path=None):
+        self.model = model
+        self.engine = engine
+        self.source = source
+        self.tokenizer = tokenizer
+        self.path = path
+        self.config = model.cfg
+
+    # ------------------------------------------------------------------------------------------ load
+    @classmethod
+    def load(cls, path: str | Path, options: Optional[ModelLoadOptions] = None) -> "LoadedModel":
+        opt = options or ModelLoadOptions()
+        src = open_checkpoint(path, opt.mapped_shards)
+        device = torch.device(opt.device)
+        dtype = opt.dtype or (torch.bfloat16 if device.type == "cuda" else torch.float32)
+        moe_factory = None
+        if src.cfg.is_moe:
+            from ..models.moe import make_moe_factory
+
+            moe_factory = make_moe_factory(src)
+        quantizer = None
+        if device.type == "cuda":
+            from ..ops.quant import make_quantizer
+
+            quantizer = make_quantizer(src, opt)
+        model = build_from_tensors(src.cfg, src.get, src.has, device, dtype, opt.parallel, moe_factory, quantizer)
+        if opt.parallel is not None and opt.parallel.tp_size > 1:
+            from ..parallel import tp
+
+            tp.attach(model, opt.parallel)
+        engine = Engine(model, max_batch=opt.max_batch, max_seq_len=opt.max_seq_len, num_pages=opt.kv_pages,
+                        use_cuda_graph=opt.use_cuda_graph)
+        tokenizer = None
+        try:
+            from ..text.tokenizer import load_tokenizer
+
+            tokenizer = load_tokenizer(path, src)
+        except Exception:
+            tokenizer = None
+        return cls(model, engine, src, tokenizer, Path(path))
+
+    # ------------------------------------------------------------------------------------------ tokens
+    def encode(self, text: str) -> list[int]:
+        if self.tokenizer is None:
+            raise RuntimeError("this checkpoint has no tokenizer")
+        return self.tokenizer.encode(text)
+
+    def decode(self, ids) -> str:
+        if self.tokenizer is None:
+            raise RuntimeError("this checkpoint has no tokenizer")
+        return self.tokenizer.decode(list(ids))
+
+    def eos_ids(self) -> tuple:
+        e = self.config.eos_token_id
+        if e is None:
+            return ()
+        return tuple(e) if isinstance(e, (list, tuple)) else (int(e),)
+
+    def generate_tokens(self, prompt_ids, sampling: Optional[SamplingParams] = None, max_new_tokens: int = 256,
+                        stop_on_eos: bool = True) -> Iterator[int]:
+        """Raw token iterator (``generate_tokens``, api/portable.rs:224): yields ids as they are committed."""
+        out: list[int] = []
+        self.engine.generate([list(prompt_ids)], sampling or SamplingParams(), max_new_tokens,
+                             eos_ids=self.eos_ids() if stop_on_eos else (), on_token=lambda i, t: out.append(t))
+        yield from out
+
+    def generate(self, prompts, sampling: Optional[SamplingParams] = None, max_new_tokens: int = 256):
+        return self.engine.generate([list(p) for p in prompts], sampling or SamplingParams(), max_new_tokens,
+                                    eos_ids=self.eos_ids())
+
+    @torch.no_grad()
+    def prefill_logits(self, prompt_ids) -> torch.Tensor:
+        """Logits of the last prompt position (fp32, [V]) - the probe the parity harness compares."""
+        import numpy as np
+
+        from ..models.llama import ForwardBatch
+        from ..runtime.kv_cache import PAGE
+
+        eng = self.engine
+        seq = eng.new_sequence(list(prompt_ids), max_new_tokens=1)
+        try:
+            n = len(seq.prompt)
+            p = np.arange(n)
+            pages = np.asarray(seq.pages, dtype=np.int64)
+            batch = ForwardBatch(
+                token_ids=eng._t(np.asarray(seq.prompt, dtype=np.int32), torch.int32),
+                positions=eng._t(p.astype(np.int32), torch.int32),
+                slots=eng._t(pages[p // PAGE] * PAGE + (p % PAGE), torch.int64),
+                block_table=eng._block_table([seq]), seq_lens=eng._t(np.asarray([n], dtype=np.int32), torch.int32),
+                is_prefill=True, cu_q=eng._t(np.asarray([0, n], dtype=np.int32), torch.int32), max_q_len=n,
+                logit_rows=eng._t(np.asarray([n - 1], dtype=np.int64), torch.int64))
+            return self.model.forward(batch, eng.kv)[0].float().cpu()
+        finally:
+            eng.release(seq)
