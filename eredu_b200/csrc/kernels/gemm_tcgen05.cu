@@ -21,6 +21,7 @@
 #include <cooperative_groups.h>
 
 #include "../common/launch_count.h"
+#include "../common/peer.cuh"
 #include "../common/ptx.cuh"
 #include "../common/tma_host.h"
 
@@ -37,7 +38,19 @@ struct GemmParams {
   int dual_row_offset;  // DUAL: row of W where the "up" matrix starts
   int out_fp32;
   int* status;
+  int col_offset;  // COMM_AG: column of the gathered output where this rank's N columns start
+  PeerComm comm;   // COMM modes only
 };
+
+// Collective fused into the epilogue (tensor parallelism over NVLink peer memory, small token counts):
+//   COMM_AR: every rank holds a K-slice; partial tiles are pushed to all peers' staging slots as they
+//            leave TMEM, published per tile with release flags, and each rank sums the `size` partials in
+//            rank order (bitwise identical on all ranks), adds bias/residual once and stores the result.
+//   COMM_AG: every rank holds an N-slice; finished tiles are stored straight into every peer's gathered
+//            output at the rank's column offset.
+enum { COMM_NONE = 0, COMM_AR = 1, COMM_AG = 2 };
+
+__device__ __forceinline__ void epi_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 template <int TN, bool DUAL>
 struct GemmCfg {
@@ -74,7 +87,26 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, float g, flo
   }
 }
 
-template <int TN, bool DUAL, bool SPLIT>
+template <int COMM>
+__device__ __forceinline__ void comm_emit(const GemmParams& p, int parity, float g, int m, int n) {
+  if (COMM == COMM_AR) {
+    const size_t idx = static_cast<size_t>(m) * p.N + n;
+    for (int peer = 0; peer < p.comm.size; ++peer) {
+      reinterpret_cast<float*>(peer_slot(p.comm, peer, parity, p.comm.rank))[idx] = g;
+    }
+  } else {
+    float v = g;
+    if (p.bias != nullptr) v += __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[n]);
+    const size_t idx = static_cast<size_t>(m) * p.ldy + p.col_offset + n;
+    for (int peer = 0; peer < p.comm.size; ++peer) {
+      uint8_t* out = p.comm.base[peer] + p.comm.out_off;
+      if (p.out_fp32) reinterpret_cast<float*>(out)[idx] = v;
+      else reinterpret_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16(v);
+    }
+  }
+}
+
+template <int TN, bool DUAL, bool SPLIT, int COMM>
 __global__ void __launch_bounds__(192, 1)
 gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, GemmParams p) {
   using Cfg = GemmCfg<TN, DUAL>;
@@ -98,6 +130,9 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   const int kb0 = split * kb_per;
   const int kb1 = min(kblocks, kb0 + kb_per);
   const int niter = max(0, kb1 - kb0);
+  unsigned int seq = 0;
+  if (COMM != COMM_NONE) seq = *p.comm.seq;
+  const int parity = static_cast<int>(seq & 1u);
 
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tmW);
@@ -206,7 +241,13 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int m = m_base + c0 + j;
-            if (m < p.M) epilogue_store<DUAL>(p, __uint_as_float(g[j]), DUAL ? __uint_as_float(u[j]) : 0.f, m, n);
+            if (m < p.M) {
+              if (COMM == COMM_NONE) {
+                epilogue_store<DUAL>(p, __uint_as_float(g[j]), DUAL ? __uint_as_float(u[j]) : 0.f, m, n);
+              } else {
+                comm_emit<COMM>(p, parity, __uint_as_float(g[j]), m, n);
+              }
+            }
           }
         }
       }
@@ -226,10 +267,38 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           g += peer[c * 128 + row];
           if (DUAL) u += peer[(TN + c) * 128 + row];
         }
-        epilogue_store<DUAL>(p, g, u, m_base + c, n);
+        if (COMM == COMM_NONE) epilogue_store<DUAL>(p, g, u, m_base + c, n);
+        else comm_emit<COMM>(p, parity, g, m_base + c, n);
       }
     }
     cluster.sync();
+  }
+
+  if (COMM != COMM_NONE) {
+    // ---- publish this CTA's share, wait for the peers' same share, finish
+    const int flag_id = ((tile_n * gridDim.y + tile_m) * (SPLIT ? 8 : 1) + split) % kMaxFlags;
+    if (warp >= 2) {
+      const int et = threadIdx.x - 64;  // 0..127
+      __threadfence_system();
+      epi_barrier();
+      if (et < p.comm.size) st_release_sys(peer_flag(p.comm, et, parity, p.comm.rank, flag_id), seq + 1u);
+      bool ok = true;
+      if (et < p.comm.size) ok = wait_flag(p.comm, parity, et, flag_id, seq + 1u, p.status);
+      (void)ok;
+      epi_barrier();
+      if (COMM == COMM_AR && n < p.N) {
+        const int m_end = min(TN, p.M - m_base);
+        for (int c = SPLIT ? split : 0; c < m_end; c += (SPLIT ? nsplit : 1)) {
+          const int m = m_base + c;
+          float v = 0.f;
+          for (int src = 0; src < p.comm.size; ++src) {
+            const float* slot = reinterpret_cast<const float*>(peer_slot(p.comm, p.comm.rank, parity, src));
+            v += ld_cg_f32(slot + static_cast<size_t>(m) * p.N + n);
+          }
+          epilogue_store<false>(p, v, 0.f, m, n);
+        }
+      }
+    }
   }
 
   tc_fence_before_sync();
@@ -238,13 +307,14 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     __syncwarp();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
+  if (COMM != COMM_NONE && threadIdx.x == 0) finish_call(p.comm, seq, gridDim.x * gridDim.y * gridDim.z);
 }
 
-template <int TN, bool DUAL, bool SPLIT>
+template <int TN, bool DUAL, bool SPLIT, int COMM = COMM_NONE>
 static cudaError_t launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, int n_tiles,
                                int m_tiles, int nsplit, cudaStream_t stream) {
   using Cfg = GemmCfg<TN, DUAL>;
-  auto kern = gemm_wt_kernel<TN, DUAL, SPLIT>;
+  auto kern = gemm_wt_kernel<TN, DUAL, SPLIT, COMM>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
@@ -270,13 +340,13 @@ static cudaError_t launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, c
   return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p);
 }
 
-template <int TN, bool DUAL>
+template <int TN, bool DUAL, int COMM = COMM_NONE>
 static cudaError_t launch_gemm_split(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p,
                                      int n_tiles, int m_tiles, int nsplit, cudaStream_t stream) {
   if (nsplit > 1) {
-    if constexpr (TN <= 64) return launch_gemm<TN, DUAL, true>(tmW, tmX, p, n_tiles, m_tiles, nsplit, stream);
+    if constexpr (TN <= 64) return launch_gemm<TN, DUAL, true, COMM>(tmW, tmX, p, n_tiles, m_tiles, nsplit, stream);
   }
-  return launch_gemm<TN, DUAL, false>(tmW, tmX, p, n_tiles, m_tiles, 1, stream);
+  return launch_gemm<TN, DUAL, false, COMM>(tmW, tmX, p, n_tiles, m_tiles, 1, stream);
 }
 
 }  // namespace eredu
@@ -350,6 +420,66 @@ extern "C" int eredu_gemm_bf16(const void* X, const void* W, void* Y, const void
       break;
   }
 #undef ER_DISPATCH
+  eredu_count_launches(1);
+  return static_cast<int>(e);
+}
+
+// Row-parallel (mode 1: GEMM + all-reduce) or column-parallel (mode 2: GEMM + all-gather) linear layer of a
+// tensor-parallel group, collective fused into the epilogue over NVLink peer memory. M <= 64 tokens.
+//   mode 1: X [M, K_local], W [N, K_local]; Y [M, N] (local, bf16/fp32) = sum over ranks (+bias +residual).
+//   mode 2: X [M, K], W [N_local, K]; the gathered [M, ldy] result lands in every rank's symmetric `out`
+//           region at column `col_offset` (+bias); Y is unused.
+// `comm` points to a host PeerComm (see eredu_comm_create). Every rank of the group must call this with the
+// same shapes in the same order.
+extern "C" int eredu_gemm_bf16_comm(const void* X, const void* W, void* Y, const void* residual, const void* bias,
+                                    int M, int N, int K, int ldx, int ldw, int ldy, int ldr, int w_rows, int out_fp32,
+                                    int mode, int col_offset, const void* comm, int force_split, int sm_count,
+                                    int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (M > 64 || comm == nullptr || (mode != COMM_AR && mode != COMM_AG)) return -1;
+  const PeerComm* pc = static_cast<const PeerComm*>(comm);
+  const int tn = M <= 16 ? 16 : M <= 32 ? 32 : 64;
+  CUtensorMap tmW, tmX;
+  int r = make_tma_2d(&tmW, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w_rows, K, ldw, 128, 64);
+  if (r != 0) return -100 + r;
+  r = make_tma_2d(&tmX, X, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, ldx, tn, 64);
+  if (r != 0) return -200 + r;
+  GemmParams p;
+  p.y = Y;
+  p.residual = residual;
+  p.bias = bias;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.ldy = ldy;
+  p.ldr = ldr;
+  p.dual_row_offset = 0;
+  p.out_fp32 = out_fp32;
+  p.status = status;
+  p.col_offset = col_offset;
+  p.comm = *pc;
+  const int n_tiles = (N + 127) / 128;
+  const int m_tiles = 1;
+  if (mode == COMM_AR && static_cast<long long>(M) * N * 4 > pc->slot_bytes) return -2;
+  int nsplit = force_split > 0 ? force_split : eredu_gemm_pick_split(M, N, K, sm_count > 0 ? sm_count : 148);
+  const int kblocks = (K + 63) / 64;
+  while (nsplit > 1 && (kblocks + nsplit - 1) / nsplit * (nsplit - 1) >= kblocks) nsplit >>= 1;
+  if (n_tiles * 8 > kMaxFlags) return -3;
+  cudaError_t e;
+#define ER_COMM(TN_)                                                                                        \
+  case TN_:                                                                                                 \
+    e = mode == COMM_AR ? launch_gemm_split<TN_, false, COMM_AR>(tmW, tmX, p, n_tiles, m_tiles, nsplit, stream) \
+                        : launch_gemm_split<TN_, false, COMM_AG>(tmW, tmX, p, n_tiles, m_tiles, nsplit, stream); \
+    break;
+  switch (tn) {
+    ER_COMM(16)
+    ER_COMM(32)
+    default:
+      e = mode == COMM_AR ? launch_gemm_split<64, false, COMM_AR>(tmW, tmX, p, n_tiles, m_tiles, nsplit, stream)
+                          : launch_gemm_split<64, false, COMM_AG>(tmW, tmX, p, n_tiles, m_tiles, nsplit, stream);
+      break;
+  }
+#undef ER_COMM
   eredu_count_launches(1);
   return static_cast<int>(e);
 }

@@ -151,10 +151,9 @@ class CausalLM:
             h = h.index_select(0, rows)
         normed, _ = ops.rmsnorm(h.contiguous(), self.final_norm, self.cfg.rms_norm_eps,
                                 weight_offset=self.cfg.norm_weight_offset)
-        local = ops.linear(normed, self.lm_head, out_dtype=torch.float32)
         if self.par.tp_size > 1 and self.lm_head.shape[0] != self.cfg.vocab_size:
-            return self.tp_ops.all_gather_logits(local, self.cfg.vocab_size)
-        return local
+            return self.tp_ops.gathered_logits(normed, self.lm_head, self.cfg.vocab_size, self.vocab_start)
+        return ops.linear(normed, self.lm_head, out_dtype=torch.float32)
 
     def forward(self, batch: ForwardBatch, kv):
         """Returns fp32 logits [R, V] on the last pipeline stage, the hidden state otherwise."""

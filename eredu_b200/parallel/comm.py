@@ -1,0 +1,115 @@
+"""Symmetric peer memory for one parallel group: allocation, CUDA-IPC exchange, tensor views.
+
+One process per GPU. The buffer is a raw ``cudaMalloc`` allocation (so that its IPC handle maps the whole
+region), zeroed, exchanged with ``torch.distributed.all_gather_object`` and mapped into every peer. Tensor views
+of regions are created through ``__cuda_array_interface__`` (no copy).
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_int, c_longlong, c_void_p, POINTER
+
+import torch
+
+from ..ops import native
+from ..ops.native import I, L, P
+
+native.register("eredu_peer_alloc", I, [L, POINTER(c_void_p)])
+native.register("eredu_peer_free", I, [P])
+native.register("eredu_ipc_handle_bytes", I, [])
+native.register("eredu_ipc_get_handle", I, [P, P])
+native.register("eredu_ipc_open", I, [P, POINTER(c_void_p)])
+native.register("eredu_ipc_close", I, [P])
+native.register("eredu_comm_create", P, [POINTER(c_void_p), I, I, L, L, P])
+native.register("eredu_comm_destroy", None, [P])
+native.register("eredu_comm_buffer_bytes", L, [L, L])
+native.register("eredu_comm_out_offset", L, [P])
+native.register("eredu_comm_data_offset", L, [P, I, I])
+native.register("eredu_allreduce_twoshot", I, [P, L, P, P, P, I, I, I, I, P, P])
+native.register("eredu_allgather", I, [P, P, L, I, P, P])
+native.register("eredu_peer_barrier", I, [P, P, P])
+native.register("eredu_gemm_bf16_comm", I, [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, I, I, P, P])
+
+
+class _RawCuda:
+    """Minimal ``__cuda_array_interface__`` carrier for a raw device pointer."""
+
+    def __init__(self, ptr: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False), "version": 2}
+
+
+_TYPESTR = {torch.float32: "<f4", torch.int32: "<i4", torch.uint8: "|u1", torch.int16: "<i2", torch.float16: "<f2"}
+
+
+def view_raw(ptr: int, shape, dtype: torch.dtype, device) -> torch.Tensor:
+    """Tensor aliasing raw device memory (bf16 goes through an int16 view)."""
+    if dtype == torch.bfloat16:
+        return torch.as_tensor(_RawCuda(ptr, shape, "<i2"), device=device).view(torch.bfloat16)
+    return torch.as_tensor(_RawCuda(ptr, shape, _TYPESTR[dtype]), device=device)
+
+
+class PeerGroup:
+    """Symmetric buffer of one group + the host ``PeerComm`` handed to the fused kernels."""
+
+    def __init__(self, group, device: torch.device, slot_bytes: int, out_bytes: int, x_bytes: int = 0):
+        import torch.distributed as dist
+
+        self.group = group
+        self.device = device
+        self.rank = dist.get_rank(group)
+        self.size = dist.get_world_size(group)
+        lib = native.lib()
+        self.lib = lib
+        out_total = ((out_bytes + 255) // 256 * 256) + ((x_bytes + 255) // 256 * 256)
+        self.bytes = int(lib.eredu_comm_buffer_bytes(slot_bytes, out_total))
+        own = c_void_p()
+        native.check(lib.eredu_peer_alloc(self.bytes, ctypes.byref(own)), "eredu_peer_alloc")
+        self.own = own.value
+        hbytes = lib.eredu_ipc_handle_bytes()
+        handle = ctypes.create_string_buffer(hbytes)
+        native.check(lib.eredu_ipc_get_handle(self.own, handle), "cudaIpcGetMemHandle")
+        handles = [None] * self.size
+        dist.all_gather_object(handles, bytes(handle.raw), group=group)
+        self.bases = []
+        self._opened = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                self.bases.append(self.own)
+                continue
+            p = c_void_p()
+            native.check(lib.eredu_ipc_open(ctypes.create_string_buffer(h, hbytes), ctypes.byref(p)),
+                         f"cudaIpcOpenMemHandle(rank {r})")
+            self.bases.append(p.value)
+            self._opened.append(p.value)
+        self.local_words = torch.zeros(2, dtype=torch.int32, device=device)
+        arr = (c_void_p * self.size)(*self.bases)
+        self.comm = lib.eredu_comm_create(arr, self.rank, self.size, slot_bytes, out_total, self.local_words.data_ptr())
+        if not self.comm:
+            raise RuntimeError("eredu_comm_create failed")
+        self.out_off = int(lib.eredu_comm_out_offset(self.comm))
+        self.out_bytes = (out_bytes + 255) // 256 * 256
+        self.x_off = self.out_off + self.out_bytes
+        self.x_bytes = x_bytes
+        self.slot_bytes = slot_bytes
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)  # every peer has mapped every buffer before anyone launches a kernel
+
+    def out_view(self, shape, dtype) -> torch.Tensor:
+        return view_raw(self.own + self.out_off, shape, dtype, self.device)
+
+    def x_view(self, shape, dtype) -> torch.Tensor:
+        return view_raw(self.own + self.x_off, shape, dtype, self.device)
+
+    def barrier(self):
+        st = native.status_word(self.device)
+        native.check(self.lib.eredu_peer_barrier(self.comm, st.data_ptr(), native.stream_ptr(self.device)),
+                     "eredu_peer_barrier")
+
+    def close(self):
+        if getattr(self, "comm", None):
+            torch.cuda.synchronize(self.device)
+            self.lib.eredu_comm_destroy(self.comm)
+            self.comm = None
+            for p in self._opened:
+                self.lib.eredu_ipc_close(p)
+            self.lib.eredu_peer_free(self.own)

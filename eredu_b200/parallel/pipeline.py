@@ -1,0 +1,100 @@
+"""Pipeline parallelism: contiguous layer ranges per stage, activations handed stage to stage with NCCL p2p.
+
+Semantics follow eredu/src/backend/mlx/architectures/distributed/pipeline.rs:5665-5714,6357-6510: the first
+stage embeds, every stage runs its contiguous layers, the last stage applies the final norm and the head;
+``[tokens, hidden]`` activations travel ``send``/``recv`` between neighbouring stages; sampling happens on the
+last stage and the chosen ids are distributed to the other stages. There is no micro-batch schedule inside one
+forward; different requests can occupy different stages through the scheduler.
+
+The hand-off stays on NCCL p2p (gloo on CPU ranks); with CUDA it is issued on a side stream and ordered with
+events so that the copy engine overlaps the next kernels of the sending stage.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ..runtime.engine import Engine
+
+WIRE_MAGIC = 0x45524455  # frames carry [magic, rows, cols] so a desynchronised peer is detected, not trusted
+
+
+class _StageModel:
+    """Wraps a model shard so that ``forward`` receives from the previous stage and sends to the next one."""
+
+    def __init__(self, model, par):
+        self.inner = model
+        self.par = par
+        self.cfg = model.cfg
+        self.device = model.device
+        self.dtype = model.dtype
+        self.n_kv_local = model.n_kv_local
+        self.n_q_local = model.n_q_local
+        self.first_layer = model.first_layer
+        topo = par.topology
+        self.prev = topo.pipeline_predecessor(par.rank)
+        self.next = topo.pipeline_successor(par.rank)
+        self.side = torch.cuda.Stream(device=model.device) if model.device.type == "cuda" else None
+        self.stats = {"sent": 0, "received": 0, "bytes": 0}
+
+    def num_local_layers(self):
+        return self.inner.num_local_layers()
+
+    def _header(self, rows, cols):
+        return torch.tensor([WIRE_MAGIC, rows, cols], dtype=torch.int64, device=self.device)
+
+    def forward(self, batch, kv):
+        M = batch.token_ids.shape[0]
+        H = self.cfg.hidden_size
+        if self.prev is not None:
+            hdr = torch.empty(3, dtype=torch.int64, device=self.device)
+            dist.recv(hdr, src=self.prev)
+            magic, rows, cols = (int(v) for v in hdr.tolist())
+            if magic != WIRE_MAGIC or rows != M or cols != H:
+                raise RuntimeError(f"pipeline frame mismatch: got ({magic:#x}, {rows}, {cols}), expected ({M}, {H})")
+            h = torch.empty((M, H), dtype=self.dtype, device=self.device)
+            dist.recv(h, src=self.prev)
+            batch.hidden_in = h
+            self.stats["received"] += 1
+        out = self.inner.forward(batch, kv)
+        if self.next is None:
+            return out
+        out = out.contiguous()
+        if self.side is not None:
+            self.side.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(self.side):
+                dist.send(self._header(M, H), dst=self.next)
+                dist.send(out, dst=self.next)
+            out.record_stream(self.side)
+        else:
+            dist.send(self._header(M, H), dst=self.next)
+            dist.send(out, dst=self.next)
+        self.stats["sent"] += 1
+        self.stats["bytes"] += out.numel() * out.element_size()
+        return None
+
+
+class PipelineRunner:
+    def __init__(self, model, par, max_batch=8, max_seq_len=4096, num_pages=None):
+        self.par = par
+        self.stage = _StageModel(model, par)
+        self.engine = Engine(self.stage, max_batch=max_batch, max_seq_len=max_seq_len, num_pages=num_pages,
+                             use_cuda_graph=False)
+        self.engine.token_sync = self._sync_tokens
+        topo = par.topology
+        members = topo.axis_members(par.rank, "pipeline")
+        self.last_rank = members[-1]
+        self.pp_group = par.pp_group
+
+    def _sync_tokens(self, tokens, n):
+        dev = self.stage.device
+        if tokens is None:
+            tokens = torch.empty(n, dtype=torch.int32, device=dev)
+        else:
+            tokens = tokens.to(dev, torch.int32).contiguous()
+        if self.par.pp_size > 1:
+            dist.broadcast(tokens, src=self.last_rank, group=self.pp_group)
+        return tokens
+
+    def generate(self, prompts, sampling=None, max_new_tokens=64, eos_ids=()):
+        return self.engine.generate(prompts, sampling, max_new_tokens, eos_ids)

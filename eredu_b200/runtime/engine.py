@@ -65,6 +65,9 @@ class Engine:
         self._graphs: dict = {}
         self._decode_state = None
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count if self.cuda else 1
+        # Pipeline parallelism: ``forward`` returns None on stages without the output head and ``token_sync``
+        # distributes the tokens sampled on the last stage (set by parallel.pipeline.PipelineRunner).
+        self.token_sync = None
 
     # ------------------------------------------------------------------------------------------ requests
     def new_sequence(self, prompt, sampling=None, max_new_tokens=256, eos_ids=()) -> Sequence:
@@ -166,7 +169,11 @@ class Engine:
         logits = self.model.forward(batch, self.kv)
         for s, n in zip(seqs, lens):
             s.kv_len = n
-        tokens = self._sample(logits, seqs, [len(s.prompt) for s in seqs])
+        tokens = None
+        if logits is not None:
+            tokens = self._sample(logits, seqs, [len(s.prompt) for s in seqs])
+        if self.token_sync is not None:
+            tokens = self.token_sync(tokens, len(seqs))
         return tokens
 
     # ------------------------------------------------------------------------------------------ decode
@@ -221,7 +228,10 @@ class Engine:
                              block_table=st["block_table"], seq_lens=st["seq_lens"], is_prefill=False, q_per_seq=1,
                              splits=st["splits"], scratch=st["scratch"])
         logits = self.model.forward(batch, self.kv)
-        ops.sample(logits, st["rows"], history=st["history"], out=st["sampled"], all_greedy=st["all_greedy"])
+        if logits is not None:
+            ops.sample(logits, st["rows"], history=st["history"], out=st["sampled"], all_greedy=st["all_greedy"])
+        if self.token_sync is not None:
+            st["sampled"].copy_(self.token_sync(st["sampled"] if logits is not None else None, st["B"]))
         hist = st["history"]
         code = ops.native.lib().eredu_decode_advance(
             st["sampled"].data_ptr(), st["token_ids"].data_ptr(), st["positions"].data_ptr(),
@@ -278,7 +288,11 @@ class Engine:
                              block_table=st["block_table"], seq_lens=st["seq_lens"], is_prefill=False, q_per_seq=1)
         logits = self.model.forward(batch, self.kv)
         pos = st["positions"].tolist()
-        toks = self._sample(logits, seqs, [p + 1 for p in pos])
+        toks = None
+        if logits is not None:
+            toks = self._sample(logits, seqs, [p + 1 for p in pos])
+        if self.token_sync is not None:
+            toks = self.token_sync(toks, len(seqs))
         active = st["active"].bool()
         st["sampled"] = toks
         newpos = st["positions"] + 1

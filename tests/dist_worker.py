@@ -1,0 +1,88 @@
+"""Multi-process worker used by the distributed tests (one OS process per rank, rendezvous on 127.0.0.1).
+
+usage: dist_worker.py <scenario> <out_json>   with RANK / WORLD_SIZE / MASTER_ADDR / MASTER_PORT in the env.
+"""
+import dataclasses
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from eredu_b200.models import config as C  # noqa: E402
+from eredu_b200.models.llama import build_from_tensors, random_state  # noqa: E402
+from eredu_b200.ops import SamplingParams  # noqa: E402
+from eredu_b200.parallel.context import ParallelContext  # noqa: E402
+from eredu_b200.parallel.topology import ParallelTopology  # noqa: E402
+from eredu_b200.runtime.engine import Engine  # noqa: E402
+
+
+def tiny_cfg(gpu: bool):
+    cfg = C.tiny_llama()
+    if gpu:
+        return dataclasses.replace(cfg, hidden_size=1024, num_attention_heads=8, num_key_value_heads=2, head_dim=128,
+                                   intermediate_size=2048, vocab_size=4096, num_hidden_layers=3,
+                                   tie_word_embeddings=False)
+    return dataclasses.replace(cfg, vocab_size=512, num_attention_heads=4, num_key_value_heads=2)
+
+
+def main():
+    scenario, out_path = sys.argv[1], sys.argv[2]
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    gpu = scenario.startswith("gpu")
+    if gpu:
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+        dev = torch.device("cuda", torch.cuda.current_device())
+        dist.init_process_group("nccl", device_id=dev)
+        dtype = torch.bfloat16
+    else:
+        dev = torch.device("cpu")
+        dist.init_process_group("gloo")
+        dtype = torch.float32
+    result = {"rank": rank}
+    cfg = tiny_cfg(gpu)
+    sd = random_state(cfg, seed=0, std=0.05)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 33)]
+    sp = SamplingParams(temperature=0.0)
+
+    if "tp" in scenario and "pp" not in scenario:
+        from eredu_b200.parallel import tp
+
+        par = ParallelContext.from_env(ParallelTopology(tensor=world))
+        model = build_from_tensors(cfg, sd.__getitem__, sd.__contains__, dev, dtype, par)
+        backend = "nccl" if "nccl" in scenario else "peer"
+        tp.attach(model, par, max_tokens=256, backend=backend)
+        eng = Engine(model, max_batch=4, max_seq_len=128)
+        if "prefill" in scenario:
+            long_prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (100, 70)]
+            result["tokens"] = eng.generate(long_prompts, sp, max_new_tokens=4)
+        else:
+            result["tokens"] = eng.generate(prompts, sp, max_new_tokens=12)
+        if gpu:
+            from eredu_b200.ops import native
+
+            native.check_status(dev)
+    elif "pp" in scenario:
+        from eredu_b200.parallel.pipeline import PipelineRunner
+
+        tp_size = 2 if "tp2" in scenario else 1
+        par = ParallelContext.from_env(ParallelTopology(pipeline=world // tp_size, tensor=tp_size))
+        model = build_from_tensors(cfg, sd.__getitem__, sd.__contains__, dev, dtype, par)
+        if tp_size > 1:
+            from eredu_b200.parallel import tp
+
+            tp.attach(model, par, max_tokens=256, backend="nccl" if not gpu else "peer")
+        runner = PipelineRunner(model, par, max_batch=4, max_seq_len=128)
+        result["tokens"] = runner.generate(prompts, sp, max_new_tokens=10)
+    dist.barrier()
+    with open(f"{out_path}.{rank}", "w") as f:
+        json.dump(result, f)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,37 @@
+"""Host-side logic of the parallel runtime on CPU ranks (gloo, world size 2 and 4): tensor-parallel sharding
+(GQA groups, KV-head replication, vocabulary-parallel head) and pipeline stages reproduce the single-rank tokens."""
+import pytest
+import torch
+
+from eredu_b200.models.llama import build_from_tensors, random_state
+from eredu_b200.ops import SamplingParams
+from eredu_b200.runtime.engine import Engine
+
+from dist_util import run_ranks
+from dist_worker import tiny_cfg
+
+
+def _oracle(n_new, prompts_lens=(9, 33)):
+    cfg = tiny_cfg(False)
+    sd = random_state(cfg, seed=0, std=0.05)
+    model = build_from_tensors(cfg, sd.__getitem__, sd.__contains__, "cpu", torch.float32)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in prompts_lens]
+    return Engine(model, max_batch=4, max_seq_len=128).generate(prompts, SamplingParams(temperature=0.0), n_new)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_tensor_parallel_matches_single_rank(world, tmp_path):
+    # world 4 > 2 kv heads: every kv head is replicated on two ranks
+    res = run_ranks("cpu_tp_nccl", world, tmp_path)
+    want = _oracle(12)
+    for r in res:
+        assert r["tokens"] == want
+
+
+@pytest.mark.parametrize("scenario,world", [("cpu_pp", 2), ("cpu_pp_tp2", 4)])
+def test_pipeline_parallel_matches_single_rank(scenario, world, tmp_path):
+    res = run_ranks(scenario, world, tmp_path)
+    want = _oracle(10)
+    for r in res:
+        assert r["tokens"] == want
