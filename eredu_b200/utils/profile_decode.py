@@ -1,0 +1,66 @@
+"""Run a few eager decode steps (and optionally a prefill) of a Llama-shaped model between
+``torch.cuda.profiler.start()`` / ``stop()`` so that a profiler attached with ``--profile-from-start off``
+captures exactly one step.
+
+    python -m eredu_b200.utils.profile_decode --layers 4 --batch 32 --ctx 2048
+    ncu --profile-from-start off --metrics gpu__time_duration.sum --clock-control none --csv \\
+        --log-file launches.csv python -m eredu_b200.utils.profile_decode --layers 4 --batch 32 --ctx 2048
+"""
+from __future__ import annotations
+
+import argparse
+import dataclasses
+
+import numpy as np
+import torch
+
+from ..models import config as C
+from ..models.llama import build_random
+from ..ops import SamplingParams, native
+from ..runtime.engine import Engine
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--layers", type=int, default=4)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--ctx", type=int, default=2048)
+    ap.add_argument("--model", default="llama3-8b", choices=["llama3-8b", "llama3-70b"])
+    ap.add_argument("--phase", default="decode", choices=["decode", "prefill"])
+    ap.add_argument("--steps", type=int, default=1)
+    args = ap.parse_args()
+    cfg = C.llama3_8b() if args.model == "llama3-8b" else C.llama3_70b()
+    cfg = dataclasses.replace(cfg, num_hidden_layers=args.layers)
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    model = build_random(cfg, dev, torch.bfloat16, seed=0)
+    eng = Engine(model, max_batch=args.batch, max_seq_len=args.ctx + 64, use_cuda_graph=False)
+    rng = np.random.default_rng(0)
+    prompts = [rng.integers(0, cfg.vocab_size, args.ctx).tolist() for _ in range(args.batch)]
+    seqs = [eng.new_sequence(p, SamplingParams(), max_new_tokens=32) for p in prompts]
+    if args.phase == "prefill":
+        eng.prefill(seqs[:1])
+        torch.cuda.synchronize()
+        for s in seqs[:1]:
+            s.kv_len = 0
+        torch.cuda.profiler.start()
+        eng.prefill(seqs[:1])
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+    else:
+        first = eng.prefill(seqs)
+        eng.start_decode(seqs, first)
+        for _ in range(3):
+            eng.decode_step(sync=True)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        for _ in range(args.steps):
+            eng.decode_step(sync=True)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+    native.check_status(dev)
+    print("ok", args)
+
+
+if __name__ == "__main__":
+    main()

@@ -29,6 +29,23 @@ def tiny_cfg(gpu: bool):
     return dataclasses.replace(cfg, vocab_size=512, num_attention_heads=4, num_key_value_heads=2)
 
 
+def probe_logits(eng, model, prompt):
+    """(decode-step logits of the last prompt token after prefilling the rest) as a CPU fp32 list."""
+    from eredu_b200.models.llama import ForwardBatch
+
+    seq = eng.new_sequence(prompt[:-1], max_new_tokens=4)
+    eng.prefill([seq])
+    eng.start_decode([seq], torch.tensor([prompt[-1]], dtype=torch.int32))
+    st = eng._decode_state
+    batch = ForwardBatch(token_ids=st["token_ids"], positions=st["positions"], slots=st["slots"],
+                         block_table=st["block_table"], seq_lens=st["seq_lens"], is_prefill=False, q_per_seq=1,
+                         splits=st["splits"], scratch=st["scratch"])
+    logits = model.forward(batch, eng.kv)[0].float().cpu()
+    eng.release(seq)
+    eng._decode_state = None
+    return logits.tolist()
+
+
 def main():
     scenario, out_path = sys.argv[1], sys.argv[2]
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -65,6 +82,8 @@ def main():
         if gpu:
             from eredu_b200.ops import native
 
+            probe = torch.randint(0, cfg.vocab_size, (100,), generator=torch.Generator().manual_seed(7)).tolist()
+            result["logits"] = probe_logits(eng, model, probe)
             native.check_status(dev)
     elif "pp" in scenario:
         from eredu_b200.parallel.pipeline import PipelineRunner
