@@ -9,6 +9,7 @@
 //
 // Both kernels use the exact blockwise online-softmax recurrence (running max m, running sum l,
 // rescaled accumulator) with bf16 tensor-core MMAs and fp32 state.
+#include "../common/launch.h"
 #include "../common/launch_count.h"
 #include "../common/ptx.cuh"
 
@@ -27,6 +28,7 @@ struct AttnParams {
   const float* sinks;       // optional [n_q_heads] attention-sink logits
   float* part_o;            // decode scratch [B*rows_total, splits, D]
   float* part_ml;           // decode scratch [B*rows_total, splits, 2]
+  int* counters;            // decode scratch [B * n_kv_heads], zero between launches (split arrival tickets)
   int max_pages;
   int n_q_heads, n_kv_heads;
   int q_per_seq;  // decode: query tokens per sequence
@@ -81,6 +83,8 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(AttnParams p) {
   uint8_t* k_s = q_s + BM * D * 2;            // [2][BN][D]
   uint8_t* v_s = k_s + 2 * BN * D * 2;        // [2][BN][D]
 
+  pdl_wait();
+  pdl_launch_dependents();
   const int b = blockIdx.z, h = blockIdx.y, qt = blockIdx.x;
   const int q_begin = p.cu_q[b];
   const int q_len = p.cu_q[b + 1] - q_begin;
@@ -274,6 +278,9 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnParams p) {
   uint8_t* q_s = smem;                   // [ROWS][D] bf16
   uint8_t* ring = smem + ROWS * D * 2;   // [4 warps][NSTAGE][K page, V page]
 
+  __shared__ int s_last;
+  pdl_wait();
+  pdl_launch_dependents();
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, tig = lane & 3;
@@ -473,27 +480,59 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnParams p) {
       }
     }
   }
-}
-
-// Combine the per-split partial results. grid = total query rows (B * q_per_seq * n_q_heads), D threads.
-template <int D>
-__global__ void __launch_bounds__(D) attn_decode_reduce_kernel(AttnParams p, int total_rows) {
-  const int qrow = blockIdx.x;
-  if (qrow >= total_rows) return;
-  const int d = threadIdx.x;
-  const int head = qrow % p.n_q_heads;
-  float M = -INFINITY;
-  for (int s = 0; s < p.splits; ++s) M = fmaxf(M, p.part_ml[(static_cast<size_t>(qrow) * p.splits + s) * 2]);
-  const float Ms = (M == -INFINITY) ? 0.f : M;
-  float L = 0.f, acc = 0.f;
-  for (int s = 0; s < p.splits; ++s) {
-    const size_t idx = static_cast<size_t>(qrow) * p.splits + s;
-    const float e = exp2f(p.part_ml[idx * 2] - Ms);
-    L += p.part_ml[idx * 2 + 1] * e;
-    acc += p.part_o[idx * D + d] * e;
+  if (p.splits > 1) {
+    // The last split to arrive for this (sequence, kv head) combines all partials: no second launch.
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const int ticket = atomicAdd(&p.counters[b * gridDim.y + kvh], 1);
+      s_last = (ticket == p.splits - 1) ? 1 : 0;
+      if (s_last) p.counters[b * gridDim.y + kvh] = 0;
+    }
+    __syncthreads();
+    if (s_last) {
+      __threadfence();
+      // per (row, split) weights first (rows * splits <= 32 * 64 values, in the free merge area), then the
+      // D-wide accumulation with independent loads
+      float* wgt = mo;                       // [rows][splits]  exp2(m_s - M)
+      float* linv = mo + ROWS * 64;          // [rows]          1 / L
+      __syncthreads();
+      for (int row = threadIdx.x; row < rows; row += 128) {
+        const int t = p.t0 + row / group, hg = row % group;
+        const int head = kvh * group + hg;
+        const size_t qrow = static_cast<size_t>(b * p.q_per_seq + t) * p.n_q_heads + head;
+        float M = -INFINITY;
+        for (int sp = 0; sp < p.splits; ++sp) M = fmaxf(M, __ldcg(&p.part_ml[(qrow * p.splits + sp) * 2]));
+        const float Ms = (M == -INFINITY) ? 0.f : M;
+        float L = 0.f;
+        for (int sp = 0; sp < p.splits; ++sp) {
+          const size_t idx = qrow * p.splits + sp;
+          const float e = exp2f(__ldcg(&p.part_ml[idx * 2]) - Ms);
+          wgt[row * 64 + sp] = e;
+          L += __ldcg(&p.part_ml[idx * 2 + 1]) * e;
+        }
+        if (p.sinks != nullptr) L += exp2f(p.sinks[head] * 1.4426950408889634f - Ms);
+        linv[row] = L > 0.f ? 1.f / L : 0.f;
+      }
+      __syncthreads();
+      for (int i = threadIdx.x; i < rows * D; i += 128) {
+        const int row = i / D, d = i % D;
+        const int t = p.t0 + row / group, hg = row % group;
+        const size_t qrow = static_cast<size_t>(b * p.q_per_seq + t) * p.n_q_heads + kvh * group + hg;
+        const float* po = p.part_o + qrow * p.splits * D + d;
+        float acc = 0.f;
+        int sp = 0;
+        for (; sp + 4 <= p.splits; sp += 4) {
+          const float a0 = __ldcg(po + (sp + 0) * D), a1 = __ldcg(po + (sp + 1) * D);
+          const float a2 = __ldcg(po + (sp + 2) * D), a3 = __ldcg(po + (sp + 3) * D);
+          acc += a0 * wgt[row * 64 + sp] + a1 * wgt[row * 64 + sp + 1] + a2 * wgt[row * 64 + sp + 2] +
+                 a3 * wgt[row * 64 + sp + 3];
+        }
+        for (; sp < p.splits; ++sp) acc += __ldcg(po + sp * D) * wgt[row * 64 + sp];
+        p.out[qrow * D + d] = __float2bfloat16(acc * linv[row]);
+      }
+    }
   }
-  if (p.sinks != nullptr) L += exp2f(p.sinks[head] * 1.4426950408889634f - Ms);
-  p.out[static_cast<size_t>(qrow) * D + d] = __float2bfloat16(L > 0.f ? acc / L : 0.f);
 }
 
 template <int D>
@@ -545,7 +584,7 @@ extern "C" int eredu_attn_prefill(const void* q, const void* k_cache, const void
                            static_cast<int>(prefill_smem<128>()));
       cfg = true;
     }
-    attn_prefill_kernel<128><<<grid, 128, prefill_smem<128>(), stream>>>(p);
+    launch_pdl(attn_prefill_kernel<128>, grid, dim3(128), prefill_smem<128>(), stream, p);
   } else if (head_dim == 64) {
     static bool cfg = false;
     if (!cfg) {
@@ -553,7 +592,7 @@ extern "C" int eredu_attn_prefill(const void* q, const void* k_cache, const void
                            static_cast<int>(prefill_smem<64>()));
       cfg = true;
     }
-    attn_prefill_kernel<64><<<grid, 128, prefill_smem<64>(), stream>>>(p);
+    launch_pdl(attn_prefill_kernel<64>, grid, dim3(128), prefill_smem<64>(), stream, p);
   } else {
     return -1;
   }
@@ -569,16 +608,17 @@ static void launch_decode(const AttnParams& p, dim3 grid, cudaStream_t stream) {
                          static_cast<int>(decode_smem<D, MT>()));
     cfg = true;
   }
-  attn_decode_kernel<D, MT><<<grid, 128, decode_smem<D, MT>(), stream>>>(p);
+  launch_pdl(attn_decode_kernel<D, MT>, grid, dim3(128), decode_smem<D, MT>(), stream, p);
   eredu_count_launches(1);
 }
 
 // q: [batch * q_per_seq, n_q_heads, D]; every sequence contributes exactly q_per_seq query tokens whose
 // positions are the last q_per_seq positions of its kv (causal among themselves). part_o / part_ml are
-// caller-provided fp32 scratch (see eredu_attn_decode_scratch_elems), unused when splits == 1.
+// caller-provided fp32 scratch (see eredu_attn_decode_scratch_elems) and `counters` a zeroed int32
+// [batch * n_kv_heads] array (left zeroed again on return); all unused when splits == 1.
 extern "C" int eredu_attn_decode(const void* q, const void* k_cache, const void* v_cache, void* out,
                                  const int* block_table, const int* seq_lens, const float* sinks, float* part_o,
-                                 float* part_ml, int batch, int q_per_seq, int max_pages, int n_q_heads,
+                                 float* part_ml, int* counters, int batch, int q_per_seq, int max_pages, int n_q_heads,
                                  int n_kv_heads, int head_dim, int splits, int window, float scale,
                                  cudaStream_t stream) {
   AttnParams p = {};
@@ -591,11 +631,12 @@ extern "C" int eredu_attn_decode(const void* q, const void* k_cache, const void*
   p.sinks = sinks;
   p.part_o = part_o;
   p.part_ml = part_ml;
+  p.counters = counters;
   p.max_pages = max_pages;
   p.n_q_heads = n_q_heads;
   p.n_kv_heads = n_kv_heads;
   p.q_per_seq = q_per_seq;
-  p.splits = splits < 1 ? 1 : splits;
+  p.splits = splits < 1 ? 1 : (splits > 64 ? 64 : splits);
   p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
   const int group = n_q_heads / n_kv_heads;
@@ -613,12 +654,6 @@ extern "C" int eredu_attn_decode(const void* q, const void* k_cache, const void*
       if (rows <= 16) launch_decode<64, 1>(p, grid, stream);
       else launch_decode<64, 2>(p, grid, stream);
     }
-  }
-  if (p.splits > 1) {
-    const int total_rows = batch * q_per_seq * n_q_heads;
-    if (head_dim == 128) attn_decode_reduce_kernel<128><<<total_rows, 128, 0, stream>>>(p, total_rows);
-    else attn_decode_reduce_kernel<64><<<total_rows, 64, 0, stream>>>(p, total_rows);
-    eredu_count_launches(1);
   }
   return static_cast<int>(cudaGetLastError());
 }

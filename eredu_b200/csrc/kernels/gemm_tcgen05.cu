@@ -20,6 +20,7 @@
 // (eredu/src/backend/mlx/nn/layers.rs:21-24).
 #include <cooperative_groups.h>
 
+#include "../common/launch.h"
 #include "../common/launch_count.h"
 #include "../common/peer.cuh"
 #include "../common/ptx.cuh"
@@ -39,6 +40,14 @@ struct GemmParams {
   int out_fp32;
   int* status;
   int col_offset;  // COMM_AG: column of the gathered output where this rank's N columns start
+  // RMSNorm folded around the GEMMs of a decoder block (norm weights are pre-multiplied into W):
+  //   consumer: y[m,:] = rsqrt(sum_j ssq_in[m, j] * norm_inv_dim + norm_eps) * (x[m,:] W^T)
+  //   producer: ssq_out[m, tile_n] = sum over this tile's columns of (stored y[m, n])^2
+  const float* ssq_in;
+  int ssq_parts;
+  float norm_eps;
+  float norm_inv_dim;
+  float* ssq_out;
   PeerComm comm;   // COMM modes only
 };
 
@@ -69,8 +78,11 @@ struct GemmCfg {
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
 
+// Applies row scale, bias, activation and residual, stores, and returns the value as stored (after rounding).
 template <bool DUAL>
-__device__ __forceinline__ void epilogue_store(const GemmParams& p, float g, float u, int m, int n) {
+__device__ __forceinline__ float epilogue_store(const GemmParams& p, float g, float u, int m, int n, float scale) {
+  g *= scale;
+  if (DUAL) u *= scale;
   if (p.bias != nullptr) {
     const __nv_bfloat16* b = static_cast<const __nv_bfloat16*>(p.bias);
     g += __bfloat162float(b[n]);
@@ -82,20 +94,22 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, float g, flo
   }
   if (p.out_fp32) {
     static_cast<float*>(p.y)[static_cast<size_t>(m) * p.ldy + n] = v;
-  } else {
-    static_cast<__nv_bfloat16*>(p.y)[static_cast<size_t>(m) * p.ldy + n] = __float2bfloat16(v);
+    return v;
   }
+  const __nv_bfloat16 r = __float2bfloat16(v);
+  static_cast<__nv_bfloat16*>(p.y)[static_cast<size_t>(m) * p.ldy + n] = r;
+  return __bfloat162float(r);
 }
 
 template <int COMM>
-__device__ __forceinline__ void comm_emit(const GemmParams& p, int parity, float g, int m, int n) {
+__device__ __forceinline__ void comm_emit(const GemmParams& p, int parity, float g, int m, int n, float scale) {
   if (COMM == COMM_AR) {
     const size_t idx = static_cast<size_t>(m) * p.N + n;
     for (int peer = 0; peer < p.comm.size; ++peer) {
       reinterpret_cast<float*>(peer_slot(p.comm, peer, parity, p.comm.rank))[idx] = g;
     }
   } else {
-    float v = g;
+    float v = g * scale;
     if (p.bias != nullptr) v += __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[n]);
     const size_t idx = static_cast<size_t>(m) * p.ldy + p.col_offset + n;
     for (int peer = 0; peer < p.comm.size; ++peer) {
@@ -130,9 +144,6 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   const int kb0 = split * kb_per;
   const int kb1 = min(kblocks, kb0 + kb_per);
   const int niter = max(0, kb1 - kb0);
-  unsigned int seq = 0;
-  if (COMM != COMM_NONE) seq = *p.comm.seq;
-  const int parity = static_cast<int>(seq & 1u);
 
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tmW);
@@ -153,6 +164,12 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // Everything above touched only this CTA's own resources; wait for the producer kernels here.
+  pdl_wait();
+  pdl_launch_dependents();
+  unsigned int seq = 0;
+  if (COMM != COMM_NONE) seq = *p.comm.seq;
+  const int parity = static_cast<int>(seq & 1u);
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -218,7 +235,51 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   bool acc_ok = false;
   float* red = reinterpret_cast<float*>(stages);  // SPLIT: [DUAL?2:1][TN][128] fp32, aliases the ring
 
+  __shared__ float s_scale[TN];
+  __shared__ float s_ssq[4][TN];
+  const int et = threadIdx.x - 64;  // epilogue thread index 0..127 (warps 2..5)
+  const bool in_n = n < p.N;
+
+  // Final value of element (column c of the tile, this thread's row): store it (or hand it to the
+  // collective) and add its square to the per-column sum kept for a following RMSNorm. Executed by whole warps.
+  auto finish = [&](float g, float u, int c, bool valid) {
+    const int m = m_base + c;
+    const bool ok = valid && in_n && m < p.M;
+    float v = 0.f;
+    if (ok) {
+      const float sc = (p.ssq_in != nullptr) ? s_scale[c] : 1.f;
+      if (COMM == COMM_NONE) v = epilogue_store<DUAL>(p, g, u, m, n, sc);
+      else comm_emit<COMM>(p, parity, g, m, n, sc);
+    }
+    if (COMM == COMM_NONE && p.ssq_out != nullptr) {
+      float sq = v * v;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+      if (lane == 0) s_ssq[q][c] = sq;
+    }
+  };
+  // After every owned column went through finish(): publish the per-row partial sums of squares.
+  auto publish_ssq = [&](int c_first, int c_step) {
+    if (p.ssq_out == nullptr) return;
+    epi_barrier();
+    for (int c = et; c < TN; c += 128) {
+      if (c >= c_first && (c - c_first) % c_step == 0 && m_base + c < p.M)
+        p.ssq_out[static_cast<size_t>(m_base + c) * gridDim.x + tile_n] = s_ssq[0][c] + s_ssq[1][c] + s_ssq[2][c] + s_ssq[3][c];
+    }
+  };
+
   if (warp >= 2) {
+    if (p.ssq_in != nullptr) {
+      for (int c = et; c < TN; c += 128) {
+        float t = 0.f;
+        if (m_base + c < p.M) {
+          const float* src = p.ssq_in + static_cast<size_t>(m_base + c) * p.ssq_parts;
+          for (int j = 0; j < p.ssq_parts; ++j) t += src[j];
+        }
+        s_scale[c] = rsqrtf(t * p.norm_inv_dim + p.norm_eps);
+      }
+      epi_barrier();
+    }
     acc_ok = (niter > 0) && mbar_wait(accum_bar, 0, p.status, kStatusAccumTimeout);
     acc_ok = __all_sync(0xffffffffu, acc_ok);
     tc_fence_after_sync();
@@ -237,28 +298,20 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             red[(c0 + j) * 128 + row] = __uint_as_float(g[j]);
             if (DUAL) red[(TN + c0 + j) * 128 + row] = __uint_as_float(u[j]);
           }
-        } else if (n < p.N) {
+        } else {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int m = m_base + c0 + j;
-            if (m < p.M) {
-              if (COMM == COMM_NONE) {
-                epilogue_store<DUAL>(p, __uint_as_float(g[j]), DUAL ? __uint_as_float(u[j]) : 0.f, m, n);
-              } else {
-                comm_emit<COMM>(p, parity, __uint_as_float(g[j]), m, n);
-              }
-            }
-          }
+          for (int j = 0; j < 16; ++j) finish(__uint_as_float(g[j]), DUAL ? __uint_as_float(u[j]) : 0.f, c0 + j, true);
         }
       }
     }
+    if (!SPLIT && COMM == COMM_NONE) publish_ssq(0, 1);
   }
 
   if (SPLIT) {
     // Every thread of every CTA of the cluster reaches both barriers, whatever happened above.
     cg::cluster_group cluster = cg::this_cluster();
     cluster.sync();
-    if (warp >= 2 && n < p.N) {
+    if (warp >= 2) {
       const int m_end = min(TN, p.M - m_base);
       for (int c = split; c < m_end; c += nsplit) {
         float g = 0.f, u = 0.f;
@@ -267,9 +320,9 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           g += peer[c * 128 + row];
           if (DUAL) u += peer[(TN + c) * 128 + row];
         }
-        if (COMM == COMM_NONE) epilogue_store<DUAL>(p, g, u, m_base + c, n);
-        else comm_emit<COMM>(p, parity, g, m_base + c, n);
+        finish(g, u, c, true);
       }
+      if (COMM == COMM_NONE) publish_ssq(split, nsplit);
     }
     cluster.sync();
   }
@@ -278,25 +331,32 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     // ---- publish this CTA's share, wait for the peers' same share, finish
     const int flag_id = ((tile_n * gridDim.y + tile_m) * (SPLIT ? 8 : 1) + split) % kMaxFlags;
     if (warp >= 2) {
-      const int et = threadIdx.x - 64;  // 0..127
       __threadfence_system();
       epi_barrier();
       if (et < p.comm.size) st_release_sys(peer_flag(p.comm, et, parity, p.comm.rank, flag_id), seq + 1u);
-      bool ok = true;
-      if (et < p.comm.size) ok = wait_flag(p.comm, parity, et, flag_id, seq + 1u, p.status);
-      (void)ok;
+      if (et < p.comm.size) wait_flag(p.comm, parity, et, flag_id, seq + 1u, p.status);
       epi_barrier();
-      if (COMM == COMM_AR && n < p.N) {
+      if (COMM == COMM_AR) {
         const int m_end = min(TN, p.M - m_base);
-        for (int c = SPLIT ? split : 0; c < m_end; c += (SPLIT ? nsplit : 1)) {
+        const int c_first = SPLIT ? split : 0, c_step = SPLIT ? nsplit : 1;
+        for (int c = c_first; c < m_end; c += c_step) {
           const int m = m_base + c;
           float v = 0.f;
-          for (int src = 0; src < p.comm.size; ++src) {
-            const float* slot = reinterpret_cast<const float*>(peer_slot(p.comm, p.comm.rank, parity, src));
-            v += ld_cg_f32(slot + static_cast<size_t>(m) * p.N + n);
+          if (in_n) {
+            for (int src = 0; src < p.comm.size; ++src) {
+              const float* slot = reinterpret_cast<const float*>(peer_slot(p.comm, p.comm.rank, parity, src));
+              v += ld_cg_f32(slot + static_cast<size_t>(m) * p.N + n);
+            }
+            v = epilogue_store<false>(p, v, 0.f, m, n, 1.f);
           }
-          epilogue_store<false>(p, v, 0.f, m, n);
+          if (p.ssq_out != nullptr) {
+            float sq = in_n ? v * v : 0.f;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+            if (lane == 0) s_ssq[q][c] = sq;
+          }
         }
+        publish_ssq(c_first, c_step);
       }
     }
   }
@@ -326,8 +386,13 @@ static cudaError_t launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, c
   cfg.blockDim = dim3(192, 1, 1);
   cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   int nattr = 0;
+  if (pdl_enabled()) {
+    attr[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[nattr].val.programmaticStreamSerializationAllowed = 1;
+    ++nattr;
+  }
   if (SPLIT) {
     attr[nattr].id = cudaLaunchAttributeClusterDimension;
     attr[nattr].val.clusterDim.x = 1;
@@ -366,11 +431,14 @@ extern "C" int eredu_gemm_pick_split(int M, int N, int K, int sm_count) {
 
 // Y = X W^T (+bias) (+residual), or with dual != 0: Y = silu(X Wg^T) * (X Wu^T) where Wg = W[0:N],
 // Wu = W[dual_row_offset : dual_row_offset+N]. X: [M,K] bf16 (row stride ldx), W: [rows,K] bf16 (row
-// stride ldw). `force_split` > 0 overrides the split-K heuristic (1,2,4,8). Returns a cudaError_t
-// or a negative tensor-map error.
+// stride ldw). `force_split` > 0 overrides the split-K heuristic (1,2,4,8). With `ssq_in` the output rows are
+// scaled by rsqrt(sum(ssq_in[m, 0:ssq_parts]) / norm_dim + norm_eps) (RMSNorm whose weights were folded into
+// W); with `ssq_out` ([M, ceil(N/128)] fp32) the kernel also writes per-tile sums of squares of the stored
+// output for the next such GEMM. Returns a cudaError_t or a negative tensor-map error.
 extern "C" int eredu_gemm_bf16(const void* X, const void* W, void* Y, const void* residual, const void* bias, int M,
                                int N, int K, int ldx, int ldw, int ldy, int ldr, int w_rows, int dual,
                                int dual_row_offset, int out_fp32, int force_split, int sm_count, int* status,
+                               const float* ssq_in, int ssq_parts, float norm_eps, int norm_dim, float* ssq_out,
                                cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   const int tn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
@@ -391,6 +459,12 @@ extern "C" int eredu_gemm_bf16(const void* X, const void* W, void* Y, const void
   p.dual_row_offset = dual_row_offset;
   p.out_fp32 = out_fp32;
   p.status = status;
+  p.col_offset = 0;
+  p.ssq_in = ssq_in;
+  p.ssq_parts = ssq_parts;
+  p.norm_eps = norm_eps;
+  p.norm_inv_dim = norm_dim > 0 ? 1.0f / static_cast<float>(norm_dim) : 0.f;
+  p.ssq_out = ssq_out;
   const int n_tiles = (N + 127) / 128;
   const int m_tiles = (M + tn - 1) / tn;
   int nsplit = force_split > 0 ? force_split : eredu_gemm_pick_split(M, N, K, sm_count > 0 ? sm_count : 148);
@@ -434,7 +508,8 @@ extern "C" int eredu_gemm_bf16(const void* X, const void* W, void* Y, const void
 extern "C" int eredu_gemm_bf16_comm(const void* X, const void* W, void* Y, const void* residual, const void* bias,
                                     int M, int N, int K, int ldx, int ldw, int ldy, int ldr, int w_rows, int out_fp32,
                                     int mode, int col_offset, const void* comm, int force_split, int sm_count,
-                                    int* status, cudaStream_t stream) {
+                                    int* status, const float* ssq_in, int ssq_parts, float norm_eps, int norm_dim,
+                                    float* ssq_out, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (M > 64 || comm == nullptr || (mode != COMM_AR && mode != COMM_AG)) return -1;
   const PeerComm* pc = static_cast<const PeerComm*>(comm);
@@ -457,6 +532,11 @@ extern "C" int eredu_gemm_bf16_comm(const void* X, const void* W, void* Y, const
   p.out_fp32 = out_fp32;
   p.status = status;
   p.col_offset = col_offset;
+  p.ssq_in = ssq_in;
+  p.ssq_parts = ssq_parts;
+  p.norm_eps = norm_eps;
+  p.norm_inv_dim = norm_dim > 0 ? 1.0f / static_cast<float>(norm_dim) : 0.f;
+  p.ssq_out = ssq_out;
   p.comm = *pc;
   const int n_tiles = (N + 127) / 128;
   const int m_tiles = 1;

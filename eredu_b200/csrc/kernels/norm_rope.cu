@@ -5,6 +5,7 @@
 //                                                      runtime/cache/kv.rs:2781-2860)
 //   * embedding gather with vocab-parallel masking    (nn/parallel.rs:980-1018)
 //   * silu(gate) * up for paths whose GEMM cannot fuse it (nn/layers.rs:21-24)
+#include "../common/launch.h"
 #include "../common/launch_count.h"
 #include "../common/ptx.cuh"
 
@@ -24,6 +25,8 @@ __global__ void __launch_bounds__(THREADS) rmsnorm_kernel(const __nv_bfloat16* _
                                                            __nv_bfloat16* __restrict__ h_out, int H, float eps,
                                                            float w_off) {
   __shared__ float red[32];
+  pdl_wait();
+  pdl_launch_dependents();
   const size_t row = blockIdx.x;
   const int nch = H >> 3;
   const uint4* xr = reinterpret_cast<const uint4*>(x + row * H);
@@ -109,6 +112,8 @@ struct RopeParams {
 // grid (M, n_q + 2 n_kv), D/2 threads: thread i owns one rotation pair (or a pass-through pair).
 __global__ void rope_kv_kernel(RopeParams p) {
   __shared__ float red[8];
+  pdl_wait();
+  pdl_launch_dependents();
   const int m = blockIdx.x, head = blockIdx.y;
   const int i = threadIdx.x;
   const int half = p.D >> 1;
@@ -167,13 +172,20 @@ __global__ void rope_kv_kernel(RopeParams p) {
 }
 
 // out[m, :] = table[ids[m] - vocab_start, :] when the id falls in [vocab_start, vocab_start + rows), else 0.
+// ssq_out (optional, [M]) receives the sum of squares of the stored row, for an RMSNorm fused into the
+// first GEMM of the first layer.
 __global__ void embedding_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
-                                 __nv_bfloat16* __restrict__ out, int H, int vocab_start, int rows, float scale) {
+                                 __nv_bfloat16* __restrict__ out, int H, int vocab_start, int rows, float scale,
+                                 float* __restrict__ ssq_out) {
+  __shared__ float red[8];
+  pdl_wait();
+  pdl_launch_dependents();
   const size_t m = blockIdx.x;
   const int id = ids[m] - vocab_start;
   const bool ok = id >= 0 && id < rows;
   const uint4* src = reinterpret_cast<const uint4*>(table + static_cast<size_t>(ok ? id : 0) * H);
   uint4* dst = reinterpret_cast<uint4*>(out + m * H);
+  float ss = 0.f;
   for (int c = threadIdx.x; c < (H >> 3); c += blockDim.x) {
     uint4 v = ok ? src[c] : make_uint4(0, 0, 0, 0);
     if (scale != 1.f) {
@@ -183,12 +195,27 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const __nv_bfloat1
       v.w = pack_bf16x2(bf16_lo(v.w) * scale, bf16_hi(v.w) * scale);
     }
     dst[c] = v;
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) ss += bf16_lo(u[j]) * bf16_lo(u[j]) + bf16_hi(u[j]) * bf16_hi(u[j]);
+  }
+  if (ssq_out != nullptr) {
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.f;
+      for (int w = 0; w < static_cast<int>(blockDim.x >> 5); ++w) t += red[w];
+      ssq_out[m] = t;
+    }
   }
 }
 
 // y[m, i] = silu(x[m, i]) * x[m, I + i], optional clamp of both branches (swiglu_limit).
 __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, int I, int ldx,
                                 float limit) {
+  pdl_wait();
+  pdl_launch_dependents();
   const size_t m = blockIdx.y;
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= (I >> 3)) return;
@@ -219,6 +246,8 @@ __global__ void decode_advance_kernel(const int* __restrict__ sampled, int* __re
                                       long long* __restrict__ slots, const int* __restrict__ block_table,
                                       int max_pages, const int* __restrict__ active, int* __restrict__ sampler_rows,
                                       int row_ints, int* __restrict__ history, int hist_stride, int B) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= B) return;
   if (active != nullptr && active[b] == 0) {
@@ -258,11 +287,11 @@ extern "C" int eredu_rmsnorm(const void* x, const void* residual, const float* w
   auto Y = static_cast<__nv_bfloat16*>(y);
   auto Ho = static_cast<__nv_bfloat16*>(h_out);
   const int nch = H / 8;
-  if (nch <= 128) rmsnorm_kernel<128, 1><<<M, 128, 0, stream>>>(X, R, w, Y, Ho, H, eps, w_off);
-  else if (nch <= 256) rmsnorm_kernel<256, 1><<<M, 256, 0, stream>>>(X, R, w, Y, Ho, H, eps, w_off);
-  else if (nch <= 512) rmsnorm_kernel<256, 2><<<M, 256, 0, stream>>>(X, R, w, Y, Ho, H, eps, w_off);
-  else if (nch <= 1024) rmsnorm_kernel<256, 4><<<M, 256, 0, stream>>>(X, R, w, Y, Ho, H, eps, w_off);
-  else rmsnorm_kernel<256, 8><<<M, 256, 0, stream>>>(X, R, w, Y, Ho, H, eps, w_off);
+  if (nch <= 128) launch_pdl(rmsnorm_kernel<128, 1>, dim3(M), dim3(128), 0, stream, X, R, w, Y, Ho, H, eps, w_off);
+  else if (nch <= 256) launch_pdl(rmsnorm_kernel<256, 1>, dim3(M), dim3(256), 0, stream, X, R, w, Y, Ho, H, eps, w_off);
+  else if (nch <= 512) launch_pdl(rmsnorm_kernel<256, 2>, dim3(M), dim3(256), 0, stream, X, R, w, Y, Ho, H, eps, w_off);
+  else if (nch <= 1024) launch_pdl(rmsnorm_kernel<256, 4>, dim3(M), dim3(256), 0, stream, X, R, w, Y, Ho, H, eps, w_off);
+  else launch_pdl(rmsnorm_kernel<256, 8>, dim3(M), dim3(256), 0, stream, X, R, w, Y, Ho, H, eps, w_off);
   eredu_count_launches(1);
   return static_cast<int>(cudaGetLastError());
 }
@@ -292,17 +321,17 @@ extern "C" int eredu_rope_kv(const void* qkv, void* q_out, void* k_cache, void* 
   p.attn_factor = attn_factor;
   p.norm_eps = norm_eps;
   p.norm_w_off = norm_w_off;
-  rope_kv_kernel<<<dim3(M, n_q + 2 * n_kv), D / 2, 0, stream>>>(p);
+  launch_pdl(rope_kv_kernel, dim3(M, n_q + 2 * n_kv), dim3(D / 2), 0, stream, p);
   eredu_count_launches(1);
   return static_cast<int>(cudaGetLastError());
 }
 
 extern "C" int eredu_embedding(const int* ids, const void* table, void* out, int M, int H, int vocab_start, int rows,
-                               float scale, cudaStream_t stream) {
+                               float scale, float* ssq_out, cudaStream_t stream) {
   if (M <= 0) return 0;
   if (H % 8 != 0) return -1;
-  embedding_kernel<<<M, 256, 0, stream>>>(ids, static_cast<const __nv_bfloat16*>(table),
-                                          static_cast<__nv_bfloat16*>(out), H, vocab_start, rows, scale);
+  launch_pdl(embedding_kernel, dim3(M), dim3(256), 0, stream, ids, static_cast<const __nv_bfloat16*>(table),
+             static_cast<__nv_bfloat16*>(out), H, vocab_start, rows, scale, ssq_out);
   eredu_count_launches(1);
   return static_cast<int>(cudaGetLastError());
 }
@@ -311,8 +340,8 @@ extern "C" int eredu_silu_mul(const void* x, void* y, int M, int I, int ldx, flo
   if (M <= 0) return 0;
   if (I % 8 != 0) return -1;
   dim3 grid((I / 8 + 255) / 256, M);
-  silu_mul_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), I,
-                                            ldx, limit);
+  launch_pdl(silu_mul_kernel, grid, dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(x),
+             static_cast<__nv_bfloat16*>(y), I, ldx, limit);
   eredu_count_launches(1);
   return static_cast<int>(cudaGetLastError());
 }
@@ -322,9 +351,8 @@ extern "C" int eredu_decode_advance(const int* sampled, int* token_ids, int* pos
                                     int* sampler_rows, int row_ints, int* history, int hist_stride, int B,
                                     cudaStream_t stream) {
   if (B <= 0) return 0;
-  decode_advance_kernel<<<(B + 127) / 128, 128, 0, stream>>>(sampled, token_ids, positions, seq_lens, slots,
-                                                             block_table, max_pages, active, sampler_rows, row_ints,
-                                                             history, hist_stride, B);
+  launch_pdl(decode_advance_kernel, dim3((B + 127) / 128), dim3(128), 0, stream, sampled, token_ids, positions,
+             seq_lens, slots, block_table, max_pages, active, sampler_rows, row_ints, history, hist_stride, B);
   eredu_count_launches(1);
   return static_cast<int>(cudaGetLastError());
 }

@@ -16,6 +16,7 @@
 // scans them. With top-k disabled and top-p < 1 the candidate set is the 1024 largest logits with
 // probabilities normalised over the full vocabulary. With both disabled the kernel samples the
 // full (min-p filtered) vocabulary in index order.
+#include "../common/launch.h"
 #include "../common/launch_count.h"
 #include "../common/ptx.cuh"
 
@@ -188,6 +189,8 @@ __global__ void __launch_bounds__(kSampThreads) sampler_kernel(SamplerParams p) 
   __shared__ int sh_krem;
   __shared__ int sh_pick;
 
+  pdl_wait();
+  pdl_launch_dependents();
   const int r = blockIdx.x;
   const int tid = threadIdx.x;
   SamplerRow cfg;
@@ -414,6 +417,8 @@ struct VerifyParams {
 __global__ void __launch_bounds__(kSampThreads) spec_verify_kernel(VerifyParams p) {
   __shared__ BlockScratch scr;
   __shared__ int sh_pick;
+  pdl_wait();
+  pdl_launch_dependents();
   const int b = blockIdx.x, tid = threadIdx.x;
   SamplerRow cfg;
   {
@@ -527,7 +532,7 @@ extern "C" int eredu_sample(float* logits, const unsigned int* allow, int allow_
   p.tokens = tokens;
   p.probs = probs;
   p.V = V;
-  sampler_kernel<<<n_rows, kSampThreads, 0, stream>>>(p);
+  launch_pdl(sampler_kernel, dim3(n_rows), dim3(kSampThreads), 0, stream, p);
   eredu_count_launches(1);
   return static_cast<int>(cudaGetLastError());
 }
@@ -543,7 +548,7 @@ extern "C" int eredu_spec_verify(const float* p_t, const float* p_d, const int* 
   p.out = out;
   p.n_draft = n_draft;
   p.V = V;
-  spec_verify_kernel<<<batch, kSampThreads, 0, stream>>>(p);
+  launch_pdl(spec_verify_kernel, dim3(batch), dim3(kSampThreads), 0, stream, p);
   eredu_count_launches(1);
   return static_cast<int>(cudaGetLastError());
 }

@@ -57,6 +57,8 @@ class LayerWeights:
     k_norm: Optional[torch.Tensor] = None
     sinks: Optional[torch.Tensor] = None
     moe: object = None       # MoE block (callable) for sparse layers
+    fold_attn: bool = False  # attn_norm weights are folded into wqkv (RMSNorm fused into the GEMM)
+    fold_ffn: bool = False   # ffn_norm weights are folded into w_gate_up
     qlin: dict = field(default_factory=dict)  # quantised linears by role: "qkv", "o", "gate_up", "down"
 
 
@@ -85,6 +87,7 @@ class CausalLM:
         self.attn_factor = factor
         self.scale = 1.0 / math.sqrt(cfg.head_dim)
         self.tp_ops = None  # set by parallel.tp when tp_size > 1
+        self.head_folded = False
 
     # ------------------------------------------------------------------------------------------ layer
     def _linear(self, lw: LayerWeights, role: str, x, w, bias=None, residual=None):
@@ -103,10 +106,49 @@ class CausalLM:
             return self.tp_ops.all_reduce(partial, residual=residual, bias=bias)
         return self.tp_ops.row_linear(x, w, residual=residual, bias=bias)
 
-    def layer_forward(self, li: int, lw: LayerWeights, h, batch: ForwardBatch, kv):
+    FUSED_NORM_MAX_TOKENS = 64
+
+    def _normed_linear(self, h, ssq, folded: bool, norm_w, w, lw, role, bias=None, gated_inter=0):
+        """RMSNorm followed by a column-parallel GEMM. With folded norm weights the scale is applied in the GEMM
+        epilogue from the producer's partial sums of squares (decode) or by a weight-free normalisation kernel
+        (prefill); otherwise the plain rmsnorm kernel runs first."""
         cfg = self.cfg
-        normed, _ = ops.rmsnorm(h, lw.attn_norm, cfg.rms_norm_eps, weight_offset=cfg.norm_weight_offset)
-        qkv = self._linear(lw, "qkv", normed, lw.wqkv, bias=lw.bqkv)
+        q = lw.qlin.get(role)
+        if folded and q is None:
+            if ssq is not None and h.shape[0] <= self.FUSED_NORM_MAX_TOKENS:
+                if gated_inter:
+                    return ops.gated_linear(h, w, gated_inter, bias=bias, row_ssq=ssq, norm_eps=cfg.rms_norm_eps)
+                return ops.linear(h, w, bias=bias, row_ssq=ssq, norm_eps=cfg.rms_norm_eps)
+            normed, _ = ops.rmsnorm(h, self._ones(h.shape[1]), cfg.rms_norm_eps)
+        else:
+            normed, _ = ops.rmsnorm(h, norm_w, cfg.rms_norm_eps, weight_offset=cfg.norm_weight_offset)
+        if q is not None:
+            y = q(normed, bias=bias)
+            return ops.silu_mul(y, q.out_features // 2, cfg.swiglu_limit) if gated_inter else y
+        if gated_inter:
+            return ops.gated_linear(normed, w, gated_inter, bias=bias)
+        return ops.linear(normed, w, bias=bias)
+
+    def _ones(self, n):
+        t = getattr(self, "_ones_cache", None)
+        if t is None or t.shape[0] != n:
+            t = torch.ones(n, dtype=torch.float32, device=self.device)
+            self._ones_cache = t
+        return t
+
+    def _row_linear_ssq(self, lw, role, x, w, residual, bias, want_ssq):
+        """Row-parallel projection that can also return the partial sums of squares of its output rows."""
+        if (not want_ssq or lw.qlin.get(role) is not None or x.shape[0] > self.FUSED_NORM_MAX_TOKENS
+                or (self.par.tp_size > 1 and not getattr(self.tp_ops, 'supports_ssq', False))):
+            return self._row_linear(lw, role, x, w, residual=residual, bias=bias), None
+        if self.par.tp_size == 1:
+            return ops.linear(x, w, bias=bias, residual=residual, want_ssq=True)
+        return self.tp_ops.row_linear(x, w, residual=residual, bias=bias, want_ssq=True)
+
+    def layer_forward(self, li: int, lw: LayerWeights, h, batch: ForwardBatch, kv, ssq=None, next_folded=False):
+        """One decoder block. ``ssq``: partial sums of squares of h's rows (or None); returns (h, ssq')."""
+        cfg = self.cfg
+        qkv = self._normed_linear(h, ssq, lw.fold_attn, lw.attn_norm, lw.wqkv, lw, "qkv", bias=lw.bqkv)
         k_cache, v_cache = kv.layer(li)
         q = ops.rope_kv(qkv, batch.positions, batch.slots, self.inv_freq, k_cache, v_cache, self.n_q_local,
                         self.n_kv_local, cfg.head_dim, rot=cfg.rotary_dim, interleaved=cfg.rope_traditional,
@@ -121,46 +163,76 @@ class CausalLM:
                                         self.scale, splits=batch.splits, window=window, sinks=lw.sinks,
                                         scratch=batch.scratch)
         attn = attn.view(attn.shape[0], -1)
-        h = self._row_linear(lw, "o", attn, lw.wo, residual=h, bias=lw.bo)
-        normed, _ = ops.rmsnorm(h, lw.ffn_norm, cfg.rms_norm_eps, weight_offset=cfg.norm_weight_offset)
+        h, ssq = self._row_linear_ssq(lw, "o", attn, lw.wo, h, lw.bo, lw.fold_ffn)
         if lw.moe is not None:
-            return lw.moe(normed, residual=h)
-        qgu = lw.qlin.get("gate_up")
-        if qgu is not None:
-            act = ops.silu_mul(qgu(normed), qgu.out_features // 2, cfg.swiglu_limit)
-        else:
-            act = ops.gated_linear(normed, lw.w_gate_up, lw.w_gate_up.shape[0] // 2)
-        return self._row_linear(lw, "down", act, lw.w_down, residual=h)
+            normed, _ = ops.rmsnorm(h, lw.ffn_norm, cfg.rms_norm_eps, weight_offset=cfg.norm_weight_offset)
+            return lw.moe(normed, residual=h), None
+        inter = (lw.qlin["gate_up"].out_features if "gate_up" in lw.qlin else lw.w_gate_up.shape[0]) // 2
+        act = self._normed_linear(h, ssq, lw.fold_ffn, lw.ffn_norm, lw.w_gate_up, lw, "gate_up", gated_inter=inter)
+        return self._row_linear_ssq(lw, "down", act, lw.w_down, h, None, next_folded)
 
     # ------------------------------------------------------------------------------------------ model
-    def embed_tokens(self, token_ids):
-        h = ops.embedding(token_ids, self.embed, 0, self.cfg.embedding_scale)
-        return h
-
     def forward_hidden(self, batch: ForwardBatch, kv):
+        """Runs this shard's layers. Returns (h, ssq) - ssq is None unless the next consumer folds its norm."""
+        fused = bool(self.layers) and self.layers[0].fold_attn and batch.token_ids.shape[0] <= self.FUSED_NORM_MAX_TOKENS
+        ssq = None
         if self.par.owns_embedding():
-            h = self.embed_tokens(batch.token_ids)
+            if fused:
+                h, ssq = ops.embedding(batch.token_ids, self.embed, 0, self.cfg.embedding_scale, want_ssq=True)
+            else:
+                h = ops.embedding(batch.token_ids, self.embed, 0, self.cfg.embedding_scale)
         else:
             h = batch.hidden_in
+        n = len(self.layers)
         for i, lw in enumerate(self.layers):
-            h = self.layer_forward(self.first_layer + i, lw, h, batch, kv)
-        return h
+            nxt = self.layers[i + 1].fold_attn if i + 1 < n else (self.head_folded and self.par.owns_output_head())
+            h, ssq = self.layer_forward(self.first_layer + i, lw, h, batch, kv, ssq, nxt)
+        return h, ssq
 
-    def logits(self, h, rows=None):
+    def logits(self, h, rows=None, ssq=None):
         if rows is not None:
             h = h.index_select(0, rows)
-        normed, _ = ops.rmsnorm(h.contiguous(), self.final_norm, self.cfg.rms_norm_eps,
-                                weight_offset=self.cfg.norm_weight_offset)
+            ssq = ssq.index_select(0, rows) if ssq is not None else None
+        h = h.contiguous()
+        if self.head_folded:
+            if ssq is None or h.shape[0] > self.FUSED_NORM_MAX_TOKENS:
+                h, _ = ops.rmsnorm(h, self._ones(h.shape[1]), self.cfg.rms_norm_eps)
+                ssq = None
+        else:
+            h, _ = ops.rmsnorm(h, self.final_norm, self.cfg.rms_norm_eps, weight_offset=self.cfg.norm_weight_offset)
+            ssq = None
+        eps = self.cfg.rms_norm_eps
         if self.par.tp_size > 1 and self.lm_head.shape[0] != self.cfg.vocab_size:
-            return self.tp_ops.gathered_logits(normed, self.lm_head, self.cfg.vocab_size, self.vocab_start)
-        return ops.linear(normed, self.lm_head, out_dtype=torch.float32)
+            return self.tp_ops.gathered_logits(h, self.lm_head, self.cfg.vocab_size, self.vocab_start, row_ssq=ssq,
+                                               norm_eps=eps)
+        return ops.linear(h, self.lm_head, out_dtype=torch.float32, row_ssq=ssq, norm_eps=eps)
 
     def forward(self, batch: ForwardBatch, kv):
         """Returns fp32 logits [R, V] on the last pipeline stage, the hidden state otherwise."""
-        h = self.forward_hidden(batch, kv)
+        h, ssq = self.forward_hidden(batch, kv)
         if not self.par.owns_output_head():
             return h
-        return self.logits(h, batch.logit_rows)
+        return self.logits(h, batch.logit_rows, ssq)
+
+    def fold_norms(self) -> None:
+        """Multiply the RMSNorm weight vectors into the K dimension of the GEMM that consumes the normalised
+        activations (qkv, gate_up, lm_head), so that the normalisation reduces to a per-row scale applied in the
+        GEMM epilogue. Dense bf16 weights on CUDA only; quantised and MoE consumers keep the explicit kernel."""
+        off = self.cfg.norm_weight_offset
+        for lw in self.layers:
+            if "qkv" not in lw.qlin and not lw.fold_attn:
+                lw.wqkv = (lw.wqkv.float() * (lw.attn_norm + off)[None, :]).to(self.dtype).contiguous()
+                lw.fold_attn = True
+            if lw.moe is None and "gate_up" not in lw.qlin and lw.w_gate_up is not None and not lw.fold_ffn:
+                lw.w_gate_up = (lw.w_gate_up.float() * (lw.ffn_norm + off)[None, :]).to(self.dtype).contiguous()
+                lw.fold_ffn = True
+        if self.lm_head is not None and self.final_norm is not None and not self.head_folded:
+            folded = torch.empty_like(self.lm_head)
+            step = 16384
+            for r0 in range(0, self.lm_head.shape[0], step):
+                folded[r0:r0 + step] = (self.lm_head[r0:r0 + step].float() * (self.final_norm + off)[None, :]).to(self.dtype)
+            self.lm_head = folded  # a separate tensor even when the head was tied to the embedding
+            self.head_folded = True
 
     # ------------------------------------------------------------------------------------------ weights
     def num_local_layers(self) -> int:
@@ -222,7 +294,7 @@ def shard_attention(cfg: ModelConfig, par, wq, wk, wv, wo, bq=None, bk=None, bv=
 
 
 def build_from_tensors(cfg: ModelConfig, get: Callable[[str], torch.Tensor], has: Callable[[str], bool], device, dtype,
-                       parallel=None, moe_factory=None, quantizer=None) -> CausalLM:
+                       parallel=None, moe_factory=None, quantizer=None, fold_norms: bool = True) -> CausalLM:
     """Populate a model from HF-named tensors. ``get(name)`` returns a CPU (or device) tensor; slicing for
     tensor/pipeline parallelism happens here so that a rank only uploads what it owns."""
     model = CausalLM(cfg, device, dtype, parallel)
@@ -279,6 +351,8 @@ def build_from_tensors(cfg: ModelConfig, get: Callable[[str], torch.Tensor], has
         if quantizer is not None:
             quantizer(model, li, lw)
         model.layers.append(lw)
+    if model.device.type == "cuda" and dtype == torch.bfloat16 and fold_norms:
+        model.fold_norms()
     return model
 
 

@@ -38,10 +38,29 @@ def gated_linear_ref(x, w_gate_up, inter, bias=None, out_dtype=None):
     return (F.silu(y[..., :inter]) * y[..., inter:]).to(out_dtype or x.dtype)
 
 
-def linear(x, w, bias=None, residual=None, out_dtype=None, out=None, force_split=0):
-    """y = x @ w.T (+ bias) (+ residual). x: [M, K], w: [N, K]."""
+def _norm_args(x, row_ssq, norm_eps, want_ssq, n_out):
+    """(ssq_in ptr, parts, eps, dim, ssq_out tensor) for the RMSNorm fusion of the GEMM epilogue."""
+    ssq_out = None
+    if want_ssq:
+        ssq_out = torch.empty((x.shape[0], (n_out + 127) // 128), dtype=torch.float32, device=x.device)
+    if row_ssq is None:
+        return None, 0, 0.0, 0, ssq_out
+    assert row_ssq.dtype == torch.float32 and row_ssq.is_contiguous() and row_ssq.shape[0] == x.shape[0]
+    return row_ssq, row_ssq.shape[1], float(norm_eps), x.shape[1], ssq_out
+
+
+def linear(x, w, bias=None, residual=None, out_dtype=None, out=None, force_split=0, row_ssq=None, norm_eps=0.0,
+           want_ssq=False):
+    """y = x @ w.T (+ bias) (+ residual). x: [M, K], w: [N, K].
+
+    ``row_ssq`` ([M, parts] fp32 partial sums of squares of x's rows): the output rows are scaled by
+    ``rsqrt(sum(row_ssq) / K + norm_eps)`` - an RMSNorm whose weight vector was folded into ``w``.
+    ``want_ssq``: also return per-128-column-tile sums of squares of the stored output ([M, ceil(N/128)])."""
     if not x.is_cuda:
-        return linear_ref(x, w, bias, residual, out_dtype)
+        if row_ssq is not None:
+            x = x.float() * torch.rsqrt(row_ssq.sum(-1, keepdim=True) / x.shape[1] + norm_eps)
+        y = linear_ref(x, w, bias, residual, out_dtype or w.dtype)
+        return (y, y.float().pow(2).sum(-1, keepdim=True)) if want_ssq else y
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "CUDA linear is bf16"
     M, K = x.shape
     N = w.shape[0]
@@ -50,30 +69,35 @@ def linear(x, w, bias=None, residual=None, out_dtype=None, out=None, force_split
     assert x.stride(1) == 1 and w.stride(1) == 1
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    ssq_in, parts, eps, dim, ssq_out = _norm_args(x, row_ssq, norm_eps, want_ssq, N)
     if M == 0:
-        return out
+        return (out, ssq_out) if want_ssq else out
     code = lib().eredu_gemm_bf16(
         ptr(x), ptr(w), ptr(out), ptr(residual), ptr(bias), M, N, K, x.stride(0), w.stride(0), out.stride(0),
         residual.stride(0) if residual is not None else 0, w.shape[0], 0, 0, 1 if out_dtype == torch.float32 else 0,
-        force_split, _sm_count(x.device), ptr(status_word(x.device)), stream_ptr(x.device))
+        force_split, _sm_count(x.device), ptr(status_word(x.device)), ptr(ssq_in), parts, eps, dim, ptr(ssq_out),
+        stream_ptr(x.device))
     check(code, "eredu_gemm_bf16")
-    return out
+    return (out, ssq_out) if want_ssq else out
 
 
-def gated_linear(x, w_gate_up, inter, bias=None, out=None, force_split=0):
-    """Fused SwiGLU up-projection: one GEMM kernel, activation applied in the epilogue."""
+def gated_linear(x, w_gate_up, inter, bias=None, out=None, force_split=0, row_ssq=None, norm_eps=0.0):
+    """Fused SwiGLU up-projection: one GEMM kernel, activation applied in the epilogue (``row_ssq``: see linear)."""
     if not x.is_cuda:
-        return gated_linear_ref(x, w_gate_up, inter, bias)
+        if row_ssq is not None:
+            x = x.float() * torch.rsqrt(row_ssq.sum(-1, keepdim=True) / x.shape[1] + norm_eps)
+        return gated_linear_ref(x, w_gate_up, inter, bias, w_gate_up.dtype)
     assert x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16
     M, K = x.shape
     if out is None:
         out = torch.empty((M, inter), dtype=torch.bfloat16, device=x.device)
     if M == 0:
         return out
+    ssq_in, parts, eps, dim, _ = _norm_args(x, row_ssq, norm_eps, False, inter)
     code = lib().eredu_gemm_bf16(
         ptr(x), ptr(w_gate_up), ptr(out), None, ptr(bias), M, inter, K, x.stride(0), w_gate_up.stride(0),
         out.stride(0), 0, w_gate_up.shape[0], 1, inter, 0, force_split, _sm_count(x.device),
-        ptr(status_word(x.device)), stream_ptr(x.device))
+        ptr(status_word(x.device)), ptr(ssq_in), parts, eps, dim, None, stream_ptr(x.device))
     check(code, "eredu_gemm_bf16(dual)")
     return out
 
@@ -214,13 +238,14 @@ def decode_splits(batch, n_kv, max_kv_len, sm_count=148):
     """Split-KV factor: enough CTAs to fill the GPU, at least 4 pages (64 tokens) per split."""
     ctas = max(1, batch * n_kv)
     pages = max(1, (max_kv_len + PAGE - 1) // PAGE)
-    want = max(1, (2 * sm_count) // ctas)
-    return int(max(1, min(want, pages // 4 if pages >= 4 else 1, 64)))
+    want = max(1, sm_count // ctas)
+    return int(max(1, min(want, pages // 8 if pages >= 8 else 1, 32)))
 
 
 def attention_decode(q, k_cache, v_cache, block_table, seq_lens, q_per_seq, scale, splits=1, window=0, sinks=None,
                      scratch=None, out=None):
-    """q: [B * q_per_seq, n_q, D]. ``scratch`` = (part_o, part_ml) fp32 buffers when splits > 1."""
+    """q: [B * q_per_seq, n_q, D]. ``scratch`` = (part_o, part_ml, counters) from :func:`decode_scratch` when
+    splits > 1 (fp32 partials and zeroed int32 arrival tickets)."""
     if not q.is_cuda:
         return attention_ref(q, k_cache, v_cache, block_table, seq_lens, [q_per_seq] * seq_lens.shape[0], scale,
                              window, sinks)
@@ -229,14 +254,15 @@ def attention_decode(q, k_cache, v_cache, block_table, seq_lens, q_per_seq, scal
     n_q, D = q.shape[1], q.shape[2]
     if out is None:
         out = torch.empty_like(q)
-    part_o = part_ml = None
+    part_o = part_ml = counters = None
     if splits > 1:
         if scratch is None:
             scratch = decode_scratch(B, q_per_seq, n_q, D, splits, q.device)
-        part_o, part_ml = scratch
+        part_o, part_ml, counters = scratch
         assert part_o.numel() >= B * q_per_seq * n_q * splits * D and part_ml.numel() >= B * q_per_seq * n_q * splits * 2
+        assert counters.numel() >= B * k_cache.shape[1] and counters.dtype == torch.int32
     code = lib().eredu_attn_decode(ptr(q), ptr(k_cache), ptr(v_cache), ptr(out), ptr(block_table), ptr(seq_lens),
-                                   ptr(sinks), ptr(part_o), ptr(part_ml), B, q_per_seq, block_table.stride(0), n_q,
+                                   ptr(sinks), ptr(part_o), ptr(part_ml), ptr(counters), B, q_per_seq, block_table.stride(0), n_q,
                                    k_cache.shape[1], D, splits, window, scale, stream_ptr(q.device))
     check(code, "eredu_attn_decode")
     return out
@@ -245,23 +271,28 @@ def attention_decode(q, k_cache, v_cache, block_table, seq_lens, q_per_seq, scal
 def decode_scratch(batch, q_per_seq, n_q, head_dim, splits, device):
     rows = batch * q_per_seq * n_q
     return (torch.empty(rows * splits * head_dim, dtype=torch.float32, device=device),
-            torch.empty(rows * splits * 2, dtype=torch.float32, device=device))
+            torch.empty(rows * splits * 2, dtype=torch.float32, device=device),
+            torch.zeros(batch * n_q, dtype=torch.int32, device=device))
 
 
 # ------------------------------------------------------------------------------------------ embedding / activation
-def embedding(ids, table, vocab_start=0, scale=1.0):
+def embedding(ids, table, vocab_start=0, scale=1.0, want_ssq=False):
+    """Rows of ``table`` for ``ids`` (zero rows for ids outside this shard). ``want_ssq``: also the per-row sum of
+    squares ([M, 1] fp32) consumed by a GEMM with a folded RMSNorm."""
     if not table.is_cuda:
         local = ids.long() - vocab_start
         ok = (local >= 0) & (local < table.shape[0])
         out = table[local.clamp(0, table.shape[0] - 1)] * ok[:, None].to(table.dtype)
-        return out * scale if scale != 1.0 else out
+        out = out * scale if scale != 1.0 else out
+        return (out, out.float().pow(2).sum(-1, keepdim=True)) if want_ssq else out
     assert ids.dtype == torch.int32 and table.dtype == torch.bfloat16
     M, H = ids.shape[0], table.shape[1]
     out = torch.empty((M, H), dtype=table.dtype, device=table.device)
-    code = lib().eredu_embedding(ptr(ids), ptr(table), ptr(out), M, H, vocab_start, table.shape[0], scale,
+    ssq = torch.empty((M, 1), dtype=torch.float32, device=table.device) if want_ssq else None
+    code = lib().eredu_embedding(ptr(ids), ptr(table), ptr(out), M, H, vocab_start, table.shape[0], scale, ptr(ssq),
                                  stream_ptr(table.device))
     check(code, "eredu_embedding")
-    return out
+    return (out, ssq) if want_ssq else out
 
 
 def silu_mul(x, inter, limit=0.0):

@@ -21,6 +21,8 @@ from .comm import PeerGroup
 
 
 class PeerTPOps:
+    supports_ssq = True
+
     def __init__(self, par, device, hidden: int, vocab: int, max_tokens: int = 8192, max_logit_rows: int = 64):
         self.par = par
         self.device = torch.device(device)
@@ -33,18 +35,21 @@ class PeerTPOps:
         self.lib = native.lib()
 
     # ---------------------------------------------------------------- row-parallel linear (+ all-reduce)
-    def row_linear(self, x, w, residual=None, bias=None):
+    def row_linear(self, x, w, residual=None, bias=None, want_ssq=False):
         M, K = x.shape
         N = w.shape[0]
         st = native.status_word(self.device)
         if M <= 64:
             y = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+            ssq = torch.empty((M, (N + 127) // 128), dtype=torch.float32, device=x.device) if want_ssq else None
             code = self.lib.eredu_gemm_bf16_comm(
                 x.data_ptr(), w.data_ptr(), y.data_ptr(), native.ptr(residual), native.ptr(bias), M, N, K,
                 x.stride(0), w.stride(0), y.stride(0), residual.stride(0) if residual is not None else 0, w.shape[0],
-                0, 1, 0, self.pg.comm, 0, self.sm, st.data_ptr(), native.stream_ptr(self.device))
+                0, 1, 0, self.pg.comm, 0, self.sm, st.data_ptr(), None, 0, 0.0, 0, native.ptr(ssq),
+                native.stream_ptr(self.device))
             native.check(code, "eredu_gemm_bf16_comm(all-reduce)")
-            return y
+            return (y, ssq) if want_ssq else y
+        assert not want_ssq
         assert M <= self.max_tokens, f"{M} tokens exceed the symmetric buffer ({self.max_tokens})"
         partial = self.pg.x_view((M, N), torch.bfloat16)
         ops.linear(x, w, out=partial)
@@ -66,7 +71,7 @@ class PeerTPOps:
         return self._twoshot(M, N, residual, bias)
 
     # ---------------------------------------------------------------- vocabulary-parallel head (+ all-gather)
-    def gathered_logits(self, normed, lm_head_local, vocab: int, col_offset: int):
+    def gathered_logits(self, normed, lm_head_local, vocab: int, col_offset: int, row_ssq=None, norm_eps=0.0):
         M, K = normed.shape
         Nl = lm_head_local.shape[0]
         st = native.status_word(self.device)
@@ -75,7 +80,8 @@ class PeerTPOps:
             code = self.lib.eredu_gemm_bf16_comm(
                 normed.data_ptr(), lm_head_local.data_ptr(), None, None, None, M, Nl, K, normed.stride(0),
                 lm_head_local.stride(0), vocab, 0, Nl, 1, 2, col_offset, self.pg.comm, 0, self.sm, st.data_ptr(),
-                native.stream_ptr(self.device))
+                native.ptr(row_ssq), 0 if row_ssq is None else row_ssq.shape[1], float(norm_eps),
+                K if row_ssq is not None else 0, None, native.stream_ptr(self.device))
             native.check(code, "eredu_gemm_bf16_comm(all-gather)")
             return out.clone()
         raise ValueError("logits are computed for at most 64 rows per step")
@@ -91,9 +97,10 @@ class NcclTPOps:
         self.par = par
         self.device = torch.device(device)
 
-    def row_linear(self, x, w, residual=None, bias=None):
+    def row_linear(self, x, w, residual=None, bias=None, want_ssq=False):
         import torch.distributed as dist
 
+        assert not want_ssq
         y = ops.linear(x, w)
         dist.all_reduce(y, group=self.par.tp_group)
         if bias is not None:
@@ -113,10 +120,10 @@ class NcclTPOps:
             y = y + residual
         return y
 
-    def gathered_logits(self, normed, lm_head_local, vocab: int, col_offset: int):
+    def gathered_logits(self, normed, lm_head_local, vocab: int, col_offset: int, row_ssq=None, norm_eps=0.0):
         import torch.distributed as dist
 
-        local = ops.linear(normed, lm_head_local, out_dtype=torch.float32)
+        local = ops.linear(normed, lm_head_local, out_dtype=torch.float32, row_ssq=row_ssq, norm_eps=norm_eps)
         parts = [torch.empty_like(local) for _ in range(self.par.tp_size)]
         dist.all_gather(parts, local.contiguous(), group=self.par.tp_group)
         return torch.cat(parts, dim=-1)
