@@ -48,6 +48,11 @@ struct GemmParams {
   float norm_eps;
   float norm_inv_dim;
   float* ssq_out;
+  // Grouped (MoE) mode: blockIdx.y indexes a work item {expert, first row, row count, -} built on the device;
+  // the expert's weights start at row expert * w_rows_per_expert of W, its tokens are rows [row0, row0+rows)
+  // of X and Y. Items with rows == 0 exit at once.
+  const int* work;
+  int w_rows_per_expert;
   PeerComm comm;   // COMM modes only
 };
 
@@ -66,7 +71,9 @@ struct GemmCfg {
   static constexpr int kATile = 128 * 64 * 2;
   static constexpr int kBTile = TN * 64 * 2;
   static constexpr int kStageBytes = kATile * (DUAL ? 2 : 1) + kBTile;
-  static constexpr int kBudget = (TN <= 32 && !DUAL) ? 100 * 1024 : 196 * 1024;
+  // Decode-sized tiles keep shared memory under half an SM so that two CTAs are co-resident: the whole grid
+  // (<= 296 CTAs) then runs as one wave and HBM bandwidth is shared evenly instead of paying a partial wave.
+  static constexpr int kBudget = (TN <= 32) ? (DUAL ? 3 * kStageBytes : 100 * 1024) : 196 * 1024;
   static constexpr int kStagesRaw = kBudget / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kAccCols = TN * (DUAL ? 2 : 1);
@@ -136,6 +143,17 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   const int lane = threadIdx.x & 31;
   const int tile_n = blockIdx.x;
   const int tile_m = blockIdx.y;
+  int m_base = tile_m * TN;   // first token row of this tile
+  int m_limit = p.M;          // rows >= m_limit are not stored
+  int w_row0 = tile_n * 128;  // first weight row of this tile
+  if (p.work != nullptr) {
+    pdl_wait();  // the work table comes from the routing kernels
+    const int4 item = reinterpret_cast<const int4*>(p.work)[tile_m];
+    if (item.z <= 0) return;  // uniform over the CTA (and over its cluster: same blockIdx.y)
+    m_base = item.y;
+    m_limit = item.y + item.z;
+    w_row0 += item.x * p.w_rows_per_expert;
+  }
   const int nsplit = SPLIT ? gridDim.z : 1;
   const int split = SPLIT ? blockIdx.z : 0;
 
@@ -186,9 +204,9 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         uint8_t* a = stages + s * Cfg::kStageBytes;
         const int kx = (kb0 + it) * 64;
         mbar_arrive_expect_tx(&full_bar[s], Cfg::kStageBytes);
-        tma_load_2d_hint(a, &tmW, kx, tile_n * 128, &full_bar[s], pol_w);
-        if (DUAL) tma_load_2d_hint(a + Cfg::kATile, &tmW, kx, p.dual_row_offset + tile_n * 128, &full_bar[s], pol_w);
-        tma_load_2d_hint(a + Cfg::kATile * (DUAL ? 2 : 1), &tmX, kx, tile_m * TN, &full_bar[s], pol_x);
+        tma_load_2d_hint(a, &tmW, kx, w_row0, &full_bar[s], pol_w);
+        if (DUAL) tma_load_2d_hint(a + Cfg::kATile, &tmW, kx, p.dual_row_offset + w_row0, &full_bar[s], pol_w);
+        tma_load_2d_hint(a + Cfg::kATile * (DUAL ? 2 : 1), &tmX, kx, m_base, &full_bar[s], pol_x);
         issued = it + 1;
       }
       if (!ok) {
@@ -231,7 +249,6 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   const int q = warp & 3;  // TMEM lane quarter this warp may read
   const int row = q * 32 + lane;
   const int n = tile_n * 128 + row;
-  const int m_base = tile_m * TN;
   bool acc_ok = false;
   float* red = reinterpret_cast<float*>(stages);  // SPLIT: [DUAL?2:1][TN][128] fp32, aliases the ring
 
@@ -244,7 +261,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   // collective) and add its square to the per-column sum kept for a following RMSNorm. Executed by whole warps.
   auto finish = [&](float g, float u, int c, bool valid) {
     const int m = m_base + c;
-    const bool ok = valid && in_n && m < p.M;
+    const bool ok = valid && in_n && m < m_limit;
     float v = 0.f;
     if (ok) {
       const float sc = (p.ssq_in != nullptr) ? s_scale[c] : 1.f;
@@ -263,7 +280,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     if (p.ssq_out == nullptr) return;
     epi_barrier();
     for (int c = et; c < TN; c += 128) {
-      if (c >= c_first && (c - c_first) % c_step == 0 && m_base + c < p.M)
+      if (c >= c_first && (c - c_first) % c_step == 0 && m_base + c < m_limit)
         p.ssq_out[static_cast<size_t>(m_base + c) * gridDim.x + tile_n] = s_ssq[0][c] + s_ssq[1][c] + s_ssq[2][c] + s_ssq[3][c];
     }
   };
@@ -272,7 +289,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     if (p.ssq_in != nullptr) {
       for (int c = et; c < TN; c += 128) {
         float t = 0.f;
-        if (m_base + c < p.M) {
+        if (m_base + c < m_limit) {
           const float* src = p.ssq_in + static_cast<size_t>(m_base + c) * p.ssq_parts;
           for (int j = 0; j < p.ssq_parts; ++j) t += src[j];
         }
@@ -312,7 +329,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     cg::cluster_group cluster = cg::this_cluster();
     cluster.sync();
     if (warp >= 2) {
-      const int m_end = min(TN, p.M - m_base);
+      const int m_end = min(TN, m_limit - m_base);
       for (int c = split; c < m_end; c += nsplit) {
         float g = 0.f, u = 0.f;
         for (int r = 0; r < nsplit; ++r) {
@@ -337,7 +354,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       if (et < p.comm.size) wait_flag(p.comm, parity, et, flag_id, seq + 1u, p.status);
       epi_barrier();
       if (COMM == COMM_AR) {
-        const int m_end = min(TN, p.M - m_base);
+        const int m_end = min(TN, m_limit - m_base);
         const int c_first = SPLIT ? split : 0, c_step = SPLIT ? nsplit : 1;
         for (int c = c_first; c < m_end; c += c_step) {
           const int m = m_base + c;
@@ -465,6 +482,8 @@ extern "C" int eredu_gemm_bf16(const void* X, const void* W, void* Y, const void
   p.norm_eps = norm_eps;
   p.norm_inv_dim = norm_dim > 0 ? 1.0f / static_cast<float>(norm_dim) : 0.f;
   p.ssq_out = ssq_out;
+  p.work = nullptr;
+  p.w_rows_per_expert = 0;
   const int n_tiles = (N + 127) / 128;
   const int m_tiles = (M + tn - 1) / tn;
   int nsplit = force_split > 0 ? force_split : eredu_gemm_pick_split(M, N, K, sm_count > 0 ? sm_count : 148);
@@ -537,6 +556,8 @@ extern "C" int eredu_gemm_bf16_comm(const void* X, const void* W, void* Y, const
   p.norm_eps = norm_eps;
   p.norm_inv_dim = norm_dim > 0 ? 1.0f / static_cast<float>(norm_dim) : 0.f;
   p.ssq_out = ssq_out;
+  p.work = nullptr;
+  p.w_rows_per_expert = 0;
   p.comm = *pc;
   const int n_tiles = (N + 127) / 128;
   const int m_tiles = 1;
@@ -560,6 +581,60 @@ extern "C" int eredu_gemm_bf16_comm(const void* X, const void* W, void* Y, const
       break;
   }
 #undef ER_COMM
+  eredu_count_launches(1);
+  return static_cast<int>(e);
+}
+
+// Grouped (mixture-of-experts) linear layer. X: [rows_cap, K] token rows already permuted so that each
+// expert's tokens are contiguous; W: [n_experts * rows_per_expert, K] (expert-major); `work`: device table of
+// n_work int4 items {expert, row0, rows, 0} (rows <= tile, rows == 0 = unused item), built without a host
+// round trip; `tile` = 16/32/64/128: token rows per item. dual: gate rows then up rows inside each expert
+// block (dual_row_offset = N). Y: [rows_cap, N].
+extern "C" int eredu_gemm_bf16_grouped(const void* X, const void* W, void* Y, const int* work, int n_work, int tile,
+                                       int rows_cap, int N, int K, int ldx, int ldw, int ldy, int w_rows_total,
+                                       int w_rows_per_expert, int dual, int force_split, int sm_count, int* status,
+                                       cudaStream_t stream) {
+  if (n_work <= 0 || N <= 0 || K <= 0) return 0;
+  CUtensorMap tmW, tmX;
+  int r = make_tma_2d(&tmW, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w_rows_total, K, ldw, 128, 64);
+  if (r != 0) return -100 + r;
+  r = make_tma_2d(&tmX, X, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_cap, K, ldx, tile, 64);
+  if (r != 0) return -200 + r;
+  GemmParams p = {};
+  p.y = Y;
+  p.M = rows_cap;
+  p.N = N;
+  p.K = K;
+  p.ldy = ldy;
+  p.dual_row_offset = N;
+  p.status = status;
+  p.work = work;
+  p.w_rows_per_expert = w_rows_per_expert;
+  const int n_tiles = (N + 127) / 128;
+  const int kblocks = (K + 63) / 64;
+  int nsplit = 1;
+  if (tile <= 64) {
+    nsplit = force_split > 0 ? force_split : 1;
+    if (force_split <= 0) {
+      const int sm = sm_count > 0 ? sm_count : 148;
+      while (nsplit < 8 && n_tiles * n_work * nsplit * 2 <= 2 * sm && kblocks / (nsplit * 2) >= 2) nsplit *= 2;
+    }
+    while (nsplit > 1 && (kblocks + nsplit - 1) / nsplit * (nsplit - 1) >= kblocks) nsplit >>= 1;
+  }
+  cudaError_t e;
+#define ER_GROUPED(TN_)                                                                      \
+  case TN_:                                                                                  \
+    e = dual ? launch_gemm_split<TN_, true>(tmW, tmX, p, n_tiles, n_work, nsplit, stream)    \
+             : launch_gemm_split<TN_, false>(tmW, tmX, p, n_tiles, n_work, nsplit, stream);  \
+    break;
+  switch (tile) {
+    ER_GROUPED(16)
+    ER_GROUPED(32)
+    ER_GROUPED(64)
+    ER_GROUPED(128)
+    default: return -1;
+  }
+#undef ER_GROUPED
   eredu_count_launches(1);
   return static_cast<int>(e);
 }

@@ -1,0 +1,278 @@
+// Mixture-of-experts routing and data movement, all on the device (no host synchronisation anywhere):
+//   route   : router logits -> scores (softmax | sigmoid | sqrt-softplus | top-k-then-softmax) (+ selection
+//             bias) -> top-k ids + weights (optional renormalisation, scale)
+//   plan    : routes of the locally owned experts -> per-expert segments, row positions, GEMM work items
+//   gather  : token rows -> expert-contiguous rows (the routing permute)
+//   combine : out[t] = residual[t] + sum_k w[t,k] * y[pos(t,k)]  summed in slot order (deterministic)
+//
+// Semantics follow eredu/src/backend/mlx/nn/moe.rs:433-507,652-738 (router variants, renormalisation,
+// weighted route sum in stable slot order) and safemlx/src/ops/moe.rs:36-106 (sort by expert, gather rows,
+// grouped GEMM, scatter back). The reference synchronises the host for route compaction
+// (runtime/distributed/expert.rs:575) and for the count matrix (:805-808); here both stay on the device.
+#include "../common/launch.h"
+#include "../common/launch_count.h"
+#include "../common/ptx.cuh"
+
+namespace eredu {
+
+enum { SCORE_SOFTMAX = 0, SCORE_SIGMOID = 1, SCORE_SQRT_SOFTPLUS = 2, SCORE_TOPK_SOFTMAX = 3 };
+
+// One warp per token, up to 512 experts (16 per lane).
+__global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ sel_bias,
+                                                         int* __restrict__ ids, float* __restrict__ weights, int T, int E,
+                                                         int k, int scoring, int renorm, float scale) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (t >= T) return;
+  constexpr int PER = 16;
+  float score[PER];   // value reported as the route weight
+  float select[PER];  // value used for selection (score + bias)
+  const float* row = logits + static_cast<size_t>(t) * E;
+  float mx = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int e = lane + 32 * j;
+    score[j] = e < E ? row[e] : -INFINITY;
+    mx = fmaxf(mx, score[j]);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if (scoring == SCORE_SOFTMAX) {
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      score[j] = (lane + 32 * j < E) ? __expf(score[j] - mx) : 0.f;
+      sum += score[j];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float inv = 1.f / sum;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) score[j] *= inv;
+  } else if (scoring == SCORE_SIGMOID) {
+#pragma unroll
+    for (int j = 0; j < PER; ++j) score[j] = (lane + 32 * j < E) ? 1.f / (1.f + __expf(-score[j])) : -INFINITY;
+  } else if (scoring == SCORE_SQRT_SOFTPLUS) {
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const float x = score[j];
+      score[j] = (lane + 32 * j < E) ? sqrtf(x > 20.f ? x : log1pf(__expf(x))) : -INFINITY;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int e = lane + 32 * j;
+    select[j] = (e < E) ? score[j] + (sel_bias != nullptr ? sel_bias[e] : 0.f) : -INFINITY;
+  }
+  float wsum = 0.f;
+  float my_w = 0.f;  // lane i keeps the weight of slot i
+  int my_id = 0;
+  for (int slot = 0; slot < k; ++slot) {
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int e = lane + 32 * j;
+      if (select[j] > best || (select[j] == best && e < best_e)) { best = select[j]; best_e = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+    }
+    // owner lane reports the score and retires the expert
+    float w = 0.f;
+    if ((best_e & 31) == lane) {
+#pragma unroll
+      for (int j = 0; j < PER; ++j) {
+        if (lane + 32 * j == best_e) { w = score[j]; select[j] = -INFINITY; }
+      }
+    }
+    w = __shfl_sync(0xffffffffu, w, best_e & 31);
+    if (lane == (slot & 31)) { my_w = w; my_id = best_e; }
+    wsum += w;
+    if (slot >= 31) break;  // k <= 32
+  }
+  if (scoring == SCORE_TOPK_SOFTMAX) {
+    // softmax over the selected logits only
+    float m2 = lane < k ? my_w : -INFINITY;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m2 = fmaxf(m2, __shfl_xor_sync(0xffffffffu, m2, o));
+    float ex = lane < k ? __expf(my_w - m2) : 0.f;
+    float s2 = ex;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+    my_w = ex / s2;
+  } else if (renorm) {
+    my_w = my_w / fmaxf(wsum, 1e-20f);
+  }
+  if (lane < k) {
+    ids[static_cast<size_t>(t) * k + lane] = my_id;
+    weights[static_cast<size_t>(t) * k + lane] = my_w * scale;
+  }
+}
+
+// Single CTA. routes = T*k. Experts [e0, e1) are local. Outputs:
+//   seg[0..n_local]      : first row of each local expert's segment (seg[n_local] = number of local routes)
+//   route_pos[r]         : row of route r in the permuted buffers, -1 when its expert is not local
+//   row_token[pos]       : token index of the row
+//   work[n_work_cap] int4: {local expert, row0, rows, 0} one item per `tile` rows of a segment, rest zeroed
+//   counts[2]            : {local routes, work items used}
+__global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ ids, int routes, int k, int e0, int e1,
+                                                         int tile, int* __restrict__ seg, int* __restrict__ route_pos,
+                                                         int* __restrict__ row_token, int4* __restrict__ work,
+                                                         int n_work_cap, int* __restrict__ counts) {
+  __shared__ int cnt[512];
+  __shared__ int start[513];
+  __shared__ int cursor[512];
+  __shared__ int item0[513];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int n_local = e1 - e0;
+  for (int i = threadIdx.x; i < n_local; i += blockDim.x) cnt[i] = 0;
+  __syncthreads();
+  for (int r = threadIdx.x; r < routes; r += blockDim.x) {
+    const int e = ids[r] - e0;
+    if (e >= 0 && e < n_local) atomicAdd(&cnt[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0, items = 0;
+    for (int e = 0; e < n_local; ++e) {
+      start[e] = acc;
+      item0[e] = items;
+      acc += cnt[e];
+      items += (cnt[e] + tile - 1) / tile;
+    }
+    start[n_local] = acc;
+    item0[n_local] = items;
+    counts[0] = acc;
+    counts[1] = items;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i <= n_local; i += blockDim.x) {
+    seg[i] = start[i];
+    if (i < n_local) cursor[i] = 0;
+  }
+  for (int i = threadIdx.x; i < n_work_cap; i += blockDim.x) work[i] = make_int4(0, 0, 0, 0);
+  __syncthreads();
+  for (int e = threadIdx.x; e < n_local; e += blockDim.x) {
+    const int n_items = item0[e + 1] - item0[e];
+    for (int j = 0; j < n_items; ++j) {
+      const int idx = item0[e] + j;
+      if (idx < n_work_cap) work[idx] = make_int4(e, start[e] + j * tile, min(tile, cnt[e] - j * tile), 0);
+    }
+  }
+  for (int r = threadIdx.x; r < routes; r += blockDim.x) {
+    const int e = ids[r] - e0;
+    int pos = -1;
+    if (e >= 0 && e < n_local) {
+      pos = start[e] + atomicAdd(&cursor[e], 1);
+      row_token[pos] = r / k;
+    }
+    route_pos[r] = pos;
+  }
+}
+
+// xp[pos, :] = x[row_token[pos], :] for pos < counts[0]. grid = rows_cap CTAs.
+__global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ row_token,
+                                  const int* __restrict__ counts, __nv_bfloat16* __restrict__ xp, int H) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int pos = blockIdx.x;
+  if (pos >= counts[0]) return;
+  const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row_token[pos]) * H);
+  uint4* dst = reinterpret_cast<uint4*>(xp + static_cast<size_t>(pos) * H);
+  for (int c = threadIdx.x; c < (H >> 3); c += blockDim.x) dst[c] = src[c];
+}
+
+// out[t, :] = (residual[t, :]) + (extra[t, :]) + sum_k w[t,k] * y[route_pos[t*k + slot], :]  (local routes only),
+// slots in ascending order. grid = T CTAs.
+__global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ route_pos,
+                                   const float* __restrict__ weights, const __nv_bfloat16* __restrict__ residual,
+                                   const __nv_bfloat16* __restrict__ extra, __nv_bfloat16* __restrict__ out, int k, int H) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const size_t t = blockIdx.x;
+  for (int c = threadIdx.x; c < (H >> 3); c += blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int slot = 0; slot < k; ++slot) {
+      const int pos = route_pos[t * k + slot];
+      if (pos < 0) continue;
+      const float w = weights[t * k + slot];
+      const uint4 v = reinterpret_cast<const uint4*>(y + static_cast<size_t>(pos) * H)[c];
+      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc[2 * j] += w * bf16_lo(u[j]);
+        acc[2 * j + 1] += w * bf16_hi(u[j]);
+      }
+    }
+    const __nv_bfloat16* adds[2] = {residual, extra};
+#pragma unroll
+    for (int a = 0; a < 2; ++a) {
+      if (adds[a] != nullptr) {
+        const uint4 v = reinterpret_cast<const uint4*>(adds[a] + t * H)[c];
+        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          acc[2 * j] += bf16_lo(u[j]);
+          acc[2 * j + 1] += bf16_hi(u[j]);
+        }
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]);
+    o.w = pack_bf16x2(acc[6], acc[7]);
+    reinterpret_cast<uint4*>(out + t * H)[c] = o;
+  }
+}
+
+}  // namespace eredu
+
+using namespace eredu;
+
+extern "C" int eredu_moe_route(const float* logits, const float* sel_bias, int* ids, float* weights, int T, int E, int k,
+                               int scoring, int renorm, float scale, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (E > 512 || k > 32 || k > E) return -1;
+  launch_pdl(moe_route_kernel, dim3((T + 3) / 4), dim3(128), 0, stream, logits, sel_bias, ids, weights, T, E, k, scoring,
+             renorm, scale);
+  eredu_count_launches(1);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int eredu_moe_plan(const int* ids, int routes, int k, int e0, int e1, int tile, int* seg, int* route_pos,
+                              int* row_token, int* work, int n_work_cap, int* counts, cudaStream_t stream) {
+  if (e1 - e0 > 512 || e1 <= e0) return -1;
+  launch_pdl(moe_plan_kernel, dim3(1), dim3(1024), 0, stream, ids, routes, k, e0, e1, tile, seg, route_pos, row_token,
+             reinterpret_cast<int4*>(work), n_work_cap, counts);
+  eredu_count_launches(1);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int eredu_moe_gather(const void* x, const int* row_token, const int* counts, void* xp, int rows_cap, int H,
+                                cudaStream_t stream) {
+  if (rows_cap <= 0) return 0;
+  if (H % 8 != 0) return -1;
+  launch_pdl(moe_gather_kernel, dim3(rows_cap), dim3(128), 0, stream, static_cast<const __nv_bfloat16*>(x), row_token,
+             counts, static_cast<__nv_bfloat16*>(xp), H);
+  eredu_count_launches(1);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int eredu_moe_combine(const void* y, const int* route_pos, const float* weights, const void* residual,
+                                 const void* extra, void* out, int T, int k, int H, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (H % 8 != 0) return -1;
+  launch_pdl(moe_combine_kernel, dim3(T), dim3(128), 0, stream, static_cast<const __nv_bfloat16*>(y), route_pos, weights,
+             static_cast<const __nv_bfloat16*>(residual), static_cast<const __nv_bfloat16*>(extra),
+             static_cast<__nv_bfloat16*>(out), k, H);
+  eredu_count_launches(1);
+  return static_cast<int>(cudaGetLastError());
+}

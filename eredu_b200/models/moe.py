@@ -1,0 +1,106 @@
+"""Sparse mixture-of-experts block (Qwen3-MoE / Mixtral / GPT-OSS style routed SwiGLU experts).
+
+Router: dense ``[E, H]`` projection -> scores -> top-k -> optional renormalisation
+(eredu/src/backend/mlx/nn/moe.rs:433-507,652-656; config architectures/qwen/dense.rs:934-951). Expert bank layout:
+``gate_up [E, 2I, H]`` (gate rows then up rows per expert) and ``down [E, H, I]``
+(runtime/checkpoint/load.rs:1109-1150; split HF keys ``mlp.experts.{e}.{gate,up,down}_proj.weight`` :1073-1104).
+
+Expert parallelism: every rank of the expert group owns a contiguous range of experts. With replicated
+activations (attention ran tensor-parallel on the same ranks) each rank routes all tokens identically, runs its
+own experts and the partial outputs are summed over the group (the reference's production path,
+runtime/distributed/expert.rs:703-766) - here through the peer-memory all-reduce with the residual folded in.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..ops import moe as moe_ops
+
+
+class MoEBlock:
+    def __init__(self, cfg, router_w, w_gate_up, w_down, e0: int, n_experts: int, ep_ops=None, ep_size: int = 1,
+                 shared=None, router_bias=None):
+        self.cfg = cfg
+        self.router_w = router_w          # [E, H]
+        self.w_gate_up = w_gate_up        # [E_local, 2I, H]
+        self.w_down = w_down              # [E_local, H, I]
+        self.e0 = e0
+        self.n_experts = n_experts
+        self.ep_ops = ep_ops
+        self.ep_size = ep_size
+        self.shared = shared              # optional (w_gate_up [2Is, H], w_down [H, Is]) dense shared expert
+        self.router_bias = router_bias
+        self.stats = {"calls": 0}
+
+    def tensors(self):
+        out = [self.router_w, self.w_gate_up, self.w_down]
+        if self.shared is not None:
+            out.extend(self.shared)
+        return out
+
+    def route(self, x):
+        cfg = self.cfg
+        logits = ops.linear(x, self.router_w, out_dtype=torch.float32)
+        return moe_ops.route(logits.contiguous(), cfg.num_experts_per_tok, cfg.router_scoring, cfg.norm_topk_prob, 1.0,
+                             self.router_bias)
+
+    def __call__(self, x, residual=None):
+        """x: normalised hidden states [T, H]; returns residual + MoE(x)."""
+        self.stats["calls"] += 1
+        ids, w = self.route(x)
+        extra = None
+        if self.shared is not None:
+            sgu, sd = self.shared
+            extra = ops.linear(ops.gated_linear(x, sgu, sgu.shape[0] // 2), sd)
+        if self.ep_size == 1:
+            return moe_ops.experts_forward(x, ids, w, self.w_gate_up, self.w_down, self.e0, residual=residual,
+                                           extra=extra, limit=self.cfg.swiglu_limit)
+        # shared experts are replicated: add them on one rank only so that the group sum counts them once
+        partial = moe_ops.experts_forward(x, ids, w, self.w_gate_up, self.w_down, self.e0, residual=None,
+                                          extra=extra if self.e0 == 0 else None, limit=self.cfg.swiglu_limit)
+        return self.ep_ops.all_reduce(partial, residual=residual)
+
+
+def make_moe_factory(src=None, router_std_scale: bool = False):
+    """Factory ``(model, layer, get, has) -> MoEBlock`` used by ``build_from_tensors``. Only the experts owned by
+    this rank are read and uploaded."""
+
+    def factory(model, li, get, has):
+        cfg = model.cfg
+        par = model.par
+        p = f"model.layers.{li}.mlp."
+        dev, dt = model.device, model.dtype
+        e0, e1 = par.expert_range(cfg.num_experts) if par.ep_size > 1 else (0, cfg.num_experts)
+        router = get(p + "gate.weight").to(device=dev, dtype=dt).contiguous()
+        if has(p + "experts.gate_up_proj"):
+            gu = get(p + "experts.gate_up_proj")[e0:e1]
+            dn = get(p + "experts.down_proj")[e0:e1]
+        elif has(p + "experts.gate_exps.weight"):  # GGUF stacked banks
+            g = get(p + "experts.gate_exps.weight")[e0:e1]
+            u = get(p + "experts.up_exps.weight")[e0:e1]
+            gu = torch.cat((g, u), dim=1)
+            dn = get(p + "experts.down_exps.weight")[e0:e1]
+        else:
+            gu = torch.stack([torch.cat((get(p + f"experts.{e}.gate_proj.weight"), get(p + f"experts.{e}.up_proj.weight")), 0)
+                              for e in range(e0, e1)], 0)
+            dn = torch.stack([get(p + f"experts.{e}.down_proj.weight") for e in range(e0, e1)], 0)
+        gu = gu.to(device=dev, dtype=dt).contiguous()
+        dn = dn.to(device=dev, dtype=dt).contiguous()
+        shared = None
+        if has(p + "shared_expert.gate_proj.weight"):
+            sgu = torch.cat((get(p + "shared_expert.gate_proj.weight"), get(p + "shared_expert.up_proj.weight")), 0)
+            shared = (sgu.to(device=dev, dtype=dt).contiguous(),
+                      get(p + "shared_expert.down_proj.weight").to(device=dev, dtype=dt).contiguous())
+        block = MoEBlock(cfg, router, gu, dn, e0, cfg.num_experts, ep_size=par.ep_size, shared=shared)
+        block._model = model
+        return block
+
+    return factory
+
+
+def attach_ep(model, ep_ops) -> None:
+    """Give every MoE block of a model shard the collective used to sum partial expert outputs."""
+    for lw in model.layers:
+        if lw.moe is not None:
+            lw.moe.ep_ops = ep_ops

@@ -1,0 +1,146 @@
+"""Mixture-of-experts operators: routing, permute, grouped expert GEMMs, weighted combine.
+
+CUDA tensors run the kernels of ``csrc/kernels/moe.cu`` and the grouped mode of the tcgen05 GEMM; CPU tensors
+run the PyTorch reference with the same semantics (eredu/src/backend/mlx/nn/moe.rs:433-507,652-738,1061-1163).
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from . import native
+from .core import _sm_count, linear
+from .native import I, P, check, lib, ptr, status_word, stream_ptr
+
+native.register("eredu_moe_route", I, [P, P, P, P, I, I, I, I, I, native.F, P])
+native.register("eredu_moe_plan", I, [P, I, I, I, I, I, P, P, P, P, I, P, P])
+native.register("eredu_moe_gather", I, [P, P, P, P, I, I, P])
+native.register("eredu_moe_combine", I, [P, P, P, P, P, P, I, I, I, P])
+native.register("eredu_gemm_bf16_grouped", I, [P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, I, P, P])
+
+SCORING = {"softmax": 0, "sigmoid": 1, "sqrt_softplus": 2, "topk_softmax": 3}
+
+
+def route_ref(logits, k, scoring="softmax", renorm=True, scale=1.0, sel_bias=None):
+    x = logits.float()
+    if scoring == "softmax":
+        score = torch.softmax(x, -1)
+    elif scoring == "sigmoid":
+        score = torch.sigmoid(x)
+    elif scoring == "sqrt_softplus":
+        score = torch.sqrt(F.softplus(x))
+    else:
+        score = x
+    select = score + (sel_bias.float() if sel_bias is not None else 0.0)
+    ids = torch.topk(select, k, dim=-1).indices
+    w = score.gather(-1, ids)
+    if scoring == "topk_softmax":
+        w = torch.softmax(w, -1)
+    elif renorm:
+        w = w / w.sum(-1, keepdim=True).clamp(min=1e-20)
+    return ids.to(torch.int32), (w * scale).float()
+
+
+def route(logits, k, scoring="softmax", renorm=True, scale=1.0, sel_bias=None):
+    """Router logits [T, E] fp32 -> (ids [T, k] int32, weights [T, k] fp32)."""
+    if not logits.is_cuda:
+        return route_ref(logits, k, scoring, renorm, scale, sel_bias)
+    T, E = logits.shape
+    assert logits.dtype == torch.float32 and logits.is_contiguous()
+    ids = torch.empty((T, k), dtype=torch.int32, device=logits.device)
+    w = torch.empty((T, k), dtype=torch.float32, device=logits.device)
+    code = lib().eredu_moe_route(ptr(logits), ptr(sel_bias), ptr(ids), ptr(w), T, E, k, SCORING[scoring],
+                                 1 if renorm else 0, scale, stream_ptr(logits.device))
+    check(code, "eredu_moe_route")
+    return ids, w
+
+
+def experts_ref(x, ids, weights, w_gate_up, w_down, e0=0, limit=0.0):
+    """Reference expert computation for local experts [e0, e0 + E_local): sum_k w * down_e(silu(gate_e x) * up_e x)."""
+    T, H = x.shape
+    E_local, two_i, _ = w_gate_up.shape
+    inter = two_i // 2
+    out = torch.zeros((T, H), dtype=torch.float32, device=x.device)
+    xf = x.float()
+    for slot in range(ids.shape[1]):
+        for e in range(E_local):
+            sel = (ids[:, slot].long() == e + e0).nonzero().squeeze(1)
+            if sel.numel() == 0:
+                continue
+            y = xf[sel] @ w_gate_up[e].float().t()
+            g, u = y[:, :inter], y[:, inter:]
+            if limit > 0:
+                g, u = g.clamp(max=limit), u.clamp(-limit, limit)
+            act = (F.silu(g) * u).to(x.dtype).float()
+            o = (act @ w_down[e].float().t()).to(x.dtype).float()
+            out[sel] += weights[sel, slot, None] * o
+    return out
+
+
+class ExpertPlan:
+    """Device-side routing plan for the local experts of one MoE layer invocation."""
+
+    def __init__(self, ids, k, e0, e1, tile, rows_cap):
+        dev = ids.device
+        routes = ids.numel()
+        n_local = e1 - e0
+        self.tile = tile
+        self.rows_cap = rows_cap
+        self.n_work = (rows_cap + tile - 1) // tile + n_local
+        self.seg = torch.empty(n_local + 1, dtype=torch.int32, device=dev)
+        self.route_pos = torch.empty(routes, dtype=torch.int32, device=dev)
+        self.row_token = torch.empty(max(rows_cap, 1), dtype=torch.int32, device=dev)
+        self.work = torch.empty((self.n_work, 4), dtype=torch.int32, device=dev)
+        self.counts = torch.empty(2, dtype=torch.int32, device=dev)
+        code = lib().eredu_moe_plan(ptr(ids), routes, k, e0, e1, tile, ptr(self.seg), ptr(self.route_pos),
+                                    ptr(self.row_token), ptr(self.work), self.n_work, ptr(self.counts),
+                                    stream_ptr(dev))
+        check(code, "eredu_moe_plan")
+
+
+def pick_tile(expected_rows_per_expert: float) -> int:
+    for t in (16, 32, 64, 128):
+        if expected_rows_per_expert <= t:
+            return t
+    return 128
+
+
+def experts_forward(x, ids, weights, w_gate_up, w_down, e0=0, residual=None, extra=None, limit=0.0, rows_cap=None):
+    """Local-expert MoE computation. x: [T, H] bf16; ids / weights: [T, k]; w_gate_up: [E_local, 2I, H];
+    w_down: [E_local, H, I]. Returns residual + extra + sum over local routes (bf16 [T, H])."""
+    if not x.is_cuda:
+        out = experts_ref(x, ids, weights, w_gate_up, w_down, e0, limit)
+        if residual is not None:
+            out = out + residual.float()
+        if extra is not None:
+            out = out + extra.float()
+        return out.to(x.dtype)
+    T, H = x.shape
+    k = ids.shape[1]
+    E_local, two_i, _ = w_gate_up.shape
+    inter = two_i // 2
+    routes = T * k
+    rows_cap = rows_cap or routes
+    tile = pick_tile(routes / max(1, E_local))
+    plan = ExpertPlan(ids, k, e0, e0 + E_local, tile, rows_cap)
+    dev = x.device
+    xp = torch.empty((rows_cap, H), dtype=x.dtype, device=dev)
+    check(lib().eredu_moe_gather(ptr(x), ptr(plan.row_token), ptr(plan.counts), ptr(xp), rows_cap, H, stream_ptr(dev)),
+          "eredu_moe_gather")
+    act = torch.empty((rows_cap, inter), dtype=x.dtype, device=dev)
+    st = status_word(dev)
+    sm = _sm_count(dev)
+    wgu = w_gate_up.view(E_local * two_i, H)
+    code = lib().eredu_gemm_bf16_grouped(ptr(xp), ptr(wgu), ptr(act), ptr(plan.work), plan.n_work, tile, rows_cap, inter,
+                                         H, H, H, inter, E_local * two_i, two_i, 1, 0, sm, ptr(st), stream_ptr(dev))
+    check(code, "eredu_gemm_bf16_grouped(gate_up)")
+    y = torch.empty((rows_cap, H), dtype=x.dtype, device=dev)
+    wd = w_down.view(E_local * H, inter)
+    code = lib().eredu_gemm_bf16_grouped(ptr(act), ptr(wd), ptr(y), ptr(plan.work), plan.n_work, tile, rows_cap, H,
+                                         inter, inter, inter, H, E_local * H, H, 0, 0, sm, ptr(st), stream_ptr(dev))
+    check(code, "eredu_gemm_bf16_grouped(down)")
+    out = torch.empty((T, H), dtype=x.dtype, device=dev)
+    code = lib().eredu_moe_combine(ptr(y), ptr(plan.route_pos), ptr(weights), ptr(residual), ptr(extra), ptr(out), T, k,
+                                   H, stream_ptr(dev))
+    check(code, "eredu_moe_combine")
+    return out
