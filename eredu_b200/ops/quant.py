@@ -1,0 +1,267 @@
+"""Quantised linear layers: affine group quantisation (MLX-LM checkpoints, load-time quantisation) and GGUF block
+quants, executed by the tcgen05 dequant-GEMM (``csrc/kernels/qgemm_tcgen05.cu``).
+
+Format contract (eredu/src/backend/mlx/runtime/checkpoint/quantization.rs:1-8,137-232): ``name.weight`` uint32
+``[out, in*bits/32]`` little-endian bit stream, ``name.scales`` / ``name.biases`` ``[out, in/group]``,
+``w ~ scale * q + bias``. GGUF types map to affine (bits, group) as in eredu-gguf/src/convert.rs:124-152.
+
+In device memory the codes live in a *kernel layout* (made once at load, the checkpoint bytes are untouched):
+4-bit codes as bytes ``[N, K/2]`` with the eight nibbles of each u32 interleaved (n0,n2,n4,n6,n1,n3,n5,n7); every
+other width (2/3/5/6/8 bits) in an 8-bit container ``[N, K]``; scales and biases bf16, transposed to ``[K/group, N]``.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import native
+from .core import _sm_count, linear
+from .native import F, I, P, check, lib, ptr, status_word, stream_ptr
+
+native.register("eredu_qgemm", I, [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P])
+native.register("eredu_dequant_affine", I, [P, P, P, P, I, I, I, I, P])
+
+_NIBBLE_ORDER = (0, 2, 4, 6, 1, 3, 5, 7)  # kernel position p holds logical nibble _NIBBLE_ORDER[p]
+
+
+def unpack_bitstream(packed: torch.Tensor, bits: int) -> torch.Tensor:
+    """uint32/int32 words [N, K*bits/32] (little-endian bit stream) -> codes uint8 [N, K]."""
+    N, W = packed.shape
+    words = packed.to(torch.int64) & 0xFFFFFFFF
+    K = W * 32 // bits
+    idx = torch.arange(K, device=packed.device, dtype=torch.int64) * bits
+    wi, sh = idx // 32, idx % 32
+    lo = words[:, wi] >> sh
+    nxt = words[:, (wi + 1).clamp(max=W - 1)]
+    hi = torch.where((sh + bits) > 32, nxt << (32 - sh), torch.zeros_like(nxt))
+    return ((lo | hi) & ((1 << bits) - 1)).to(torch.uint8)
+
+
+def codes_to_kernel4(codes: torch.Tensor) -> torch.Tensor:
+    """4-bit codes uint8 [N, K] -> kernel-layout bytes [N, K/2]."""
+    N, K = codes.shape
+    c = codes.view(N, K // 8, 8).to(torch.int32)
+    order = torch.tensor(_NIBBLE_ORDER, device=codes.device)
+    c = c[:, :, order]  # position p <- logical nibble order[p]
+    by = c[:, :, 0::2] | (c[:, :, 1::2] << 4)
+    return by.to(torch.uint8).reshape(N, K // 2).contiguous()
+
+
+def affine_quantize_tensor(w: torch.Tensor, bits: int, group: int):
+    """Load-time affine quantisation on the weight's device (vectorised form of the host reference quantiser:
+    edge-anchored scale, bias at the larger-magnitude extreme). Returns (codes uint8 [N,K], scales, biases bf16
+    [N, K/group])."""
+    N, K = w.shape
+    n_bins = float((1 << bits) - 1)
+    out_codes = torch.empty((N, K), dtype=torch.uint8, device=w.device)
+    scales = torch.empty((N, K // group), dtype=torch.bfloat16, device=w.device)
+    biases = torch.empty_like(scales)
+    step = max(1, (1 << 24) // K)
+    for r0 in range(0, N, step):
+        x = w[r0:r0 + step].float().view(-1, K // group, group)
+        lo, hi = x.amin(-1), x.amax(-1)
+        mask = lo.abs() > hi.abs()
+        scale = ((hi - lo) / n_bins).clamp(min=1e-7)
+        scale = torch.where(mask, scale, -scale)
+        edge = torch.where(mask, lo, hi)
+        q0 = torch.round(edge / scale)
+        scale = torch.where(q0 != 0, edge / torch.where(q0 != 0, q0, torch.ones_like(q0)), scale)
+        bias = torch.where(q0 == 0, torch.zeros_like(edge), edge)
+        scale = scale.bfloat16()
+        bias = bias.bfloat16()
+        q = torch.round((x - bias.float()[..., None]) / scale.float()[..., None]).clamp(0, n_bins)
+        out_codes[r0:r0 + step] = q.to(torch.uint8).view(-1, K)
+        scales[r0:r0 + step] = scale
+        biases[r0:r0 + step] = bias
+    return out_codes, scales, biases
+
+
+class QuantLinear:
+    """y = x @ dequant(Wq).T (+bias) (+residual)."""
+
+    def __init__(self, codes: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor, bits: int, group: int, device):
+        """codes: uint8 [N, K] (one code per byte); scales / biases: [N, K/group] (any float dtype)."""
+        N, K = codes.shape
+        self.out_features, self.in_features = N, K
+        self.bits = bits
+        self.group = group
+        self.kbits = 4 if bits == 4 else 8
+        dev = torch.device(device)
+        codes = codes.to(dev)
+        self.wq = codes_to_kernel4(codes) if self.kbits == 4 else codes.contiguous()
+        self.scales_t = scales.to(dev, torch.bfloat16).t().contiguous()
+        self.biases_t = biases.to(dev, torch.bfloat16).t().contiguous()
+        self.device = dev
+
+    # ------------------------------------------------------------------ constructors
+    @classmethod
+    def from_dense(cls, w: torch.Tensor, bits: int = 4, group: int = 64):
+        codes, s, b = affine_quantize_tensor(w, bits, group)
+        return cls(codes, s, b, bits, group, w.device)
+
+    @classmethod
+    def from_packed(cls, packed: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor, bits: int, group: int, device):
+        return cls(unpack_bitstream(packed.to(device), bits), scales, biases, bits, group, device)
+
+    @staticmethod
+    def concat_rows(parts: list["QuantLinear"]) -> "QuantLinear":
+        """Fuse row-wise (q|k|v, gate|up). Parts with different widths / groups meet in the 8-bit container at
+        the smallest group size (scales repeated), which keeps every code and scale exact."""
+        first = parts[0]
+        same = all(p.kbits == first.kbits and p.group == first.group for p in parts)
+        out = object.__new__(QuantLinear)
+        out.in_features = first.in_features
+        out.out_features = sum(p.out_features for p in parts)
+        out.device = first.device
+        if same:
+            out.kbits, out.bits, out.group = first.kbits, first.bits, first.group
+            out.wq = torch.cat([p.wq for p in parts], 0)
+            out.scales_t = torch.cat([p.scales_t for p in parts], 1).contiguous()
+            out.biases_t = torch.cat([p.biases_t for p in parts], 1).contiguous()
+            return out
+        g = min(p.group for p in parts)
+        out.kbits, out.bits, out.group = 8, 8, g
+        out.wq = torch.cat([p.codes() for p in parts], 0)
+        out.scales_t = torch.cat([p.scales_t.repeat_interleave(p.group // g, 0) for p in parts], 1).contiguous()
+        out.biases_t = torch.cat([p.biases_t.repeat_interleave(p.group // g, 0) for p in parts], 1).contiguous()
+        return out
+
+    def slice_rows(self, r0: int, r1: int) -> "QuantLinear":
+        out = object.__new__(QuantLinear)
+        out.__dict__.update(self.__dict__)
+        out.out_features = r1 - r0
+        out.wq = self.wq[r0:r1].contiguous()
+        out.scales_t = self.scales_t[:, r0:r1].contiguous()
+        out.biases_t = self.biases_t[:, r0:r1].contiguous()
+        return out
+
+    def slice_cols(self, k0: int, k1: int) -> "QuantLinear":
+        """Input-dimension slice (row-parallel shard); boundaries must fall on 64-element and group boundaries."""
+        assert k0 % 64 == 0 and k1 % 64 == 0 and k0 % self.group == 0 and k1 % self.group == 0
+        out = object.__new__(QuantLinear)
+        out.__dict__.update(self.__dict__)
+        out.in_features = k1 - k0
+        per = 2 if self.kbits == 4 else 1
+        out.wq = self.wq[:, k0 // per:k1 // per].contiguous()
+        out.scales_t = self.scales_t[k0 // self.group:k1 // self.group].contiguous()
+        out.biases_t = self.biases_t[k0 // self.group:k1 // self.group].contiguous()
+        return out
+
+    # ------------------------------------------------------------------ views
+    def tensors(self):
+        return [self.wq, self.scales_t, self.biases_t]
+
+    def nbytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.tensors())
+
+    def codes(self) -> torch.Tensor:
+        """uint8 [N, K], one code per byte (logical order)."""
+        if self.kbits == 8:
+            return self.wq
+        N = self.out_features
+        by = self.wq.view(N, -1, 4).to(torch.int32)  # 4 bytes = 8 kernel positions
+        pos = torch.stack((by & 0xF, by >> 4), -1).reshape(N, -1, 8)  # kernel positions 0..7
+        inv = torch.empty(8, dtype=torch.long)
+        for p, logical in enumerate(_NIBBLE_ORDER):
+            inv[logical] = p
+        return pos[:, :, inv.to(pos.device)].reshape(N, self.in_features).to(torch.uint8)
+
+    def dequantize(self, dtype=torch.float32) -> torch.Tensor:
+        c = self.codes().float().view(self.out_features, -1, self.group)
+        s = self.scales_t.t().float()[..., None]
+        b = self.biases_t.t().float()[..., None]
+        return (c * s + b).view(self.out_features, self.in_features).to(dtype)
+
+    # ------------------------------------------------------------------ forward
+    DENSE_FALLBACK_TOKENS = 256
+
+    def __call__(self, x, bias=None, residual=None, out=None, out_dtype=None):
+        if not x.is_cuda:
+            y = torch.nn.functional.linear(x.float(), self.dequantize(), None if bias is None else bias.float())
+            if residual is not None:
+                y = y + residual.float()
+            return y.to(out_dtype or x.dtype)
+        M, K = x.shape
+        N = self.out_features
+        assert K == self.in_features and x.dtype == torch.bfloat16 and x.stride(1) == 1
+        out_dtype = out_dtype or torch.bfloat16
+        dev = x.device
+        if M > self.DENSE_FALLBACK_TOKENS:
+            w = torch.empty((N, K), dtype=torch.bfloat16, device=dev)
+            check(lib().eredu_dequant_affine(ptr(self.wq), ptr(self.scales_t), ptr(self.biases_t), ptr(w), N, K,
+                                             self.kbits, self.group, stream_ptr(dev)), "eredu_dequant_affine")
+            return linear(x, w, bias=bias, residual=residual, out_dtype=out_dtype, out=out)
+        if out is None:
+            out = torch.empty((M, N), dtype=out_dtype, device=dev)
+        code = lib().eredu_qgemm(ptr(x), ptr(self.wq), ptr(self.scales_t), ptr(self.biases_t), ptr(out), ptr(residual),
+                                 ptr(bias), M, N, K, x.stride(0), out.stride(0),
+                                 residual.stride(0) if residual is not None else 0, self.kbits, self.group,
+                                 1 if out_dtype == torch.float32 else 0, 0, _sm_count(dev), ptr(status_word(dev)),
+                                 stream_ptr(dev))
+        check(code, "eredu_qgemm")
+        return out
+
+
+def make_quantizer(src, opt):
+    """Hook for ``build_from_tensors``: replaces the dense projections of a layer by :class:`QuantLinear`.
+
+    * ``opt.quantization`` set: load-time affine quantisation of the (already tensor-parallel sliced) dense weights;
+    * GGUF source with block-quantised tensors and ``opt.native_gguf``: the file's own codes and scales are used
+      (Q4_0 / Q4_1 / Q4_K as 4-bit group 32, Q8_0 as 8-bit group 32, Q2_K..Q6_K in the 8-bit container).
+    Returns None when neither applies."""
+    qopt = getattr(opt, "quantization", None)
+    gguf_native = bool(getattr(opt, "native_gguf", False)) and hasattr(src, "to_affine") and any(
+        src.quant_info(f"model.layers.0.{n}.weight") is not None
+        for n in ("self_attn.q_proj", "mlp.down_proj", "mlp.gate_proj"))
+    if qopt is None and not gguf_native:
+        return None
+
+    def from_source(model, name, rows=None, cols=None):
+        packed, scales, biases, bits, group = src.to_affine(name)
+        q = QuantLinear.from_packed(packed, scales.float(), biases.float(), bits, group, model.device)
+        if rows is not None:
+            q = q.slice_rows(*rows)
+        if cols is not None:
+            q = q.slice_cols(*cols)
+        return q
+
+    def hook(model, li, lw):
+        par = model.par
+        tp, r = par.tp_size, par.tp_rank
+        cfg = model.cfg
+        if qopt is not None:
+            if qopt.mode != "affine":
+                raise NotImplementedError("load-time quantisation mode " + qopt.mode)
+            bits, group = qopt.bits, qopt.group_size
+            for role, attr in (("qkv", "wqkv"), ("o", "wo"), ("gate_up", "w_gate_up"), ("down", "w_down")):
+                w = getattr(lw, attr)
+                if w is None or w.shape[1] % group != 0 or w.shape[1] % 64 != 0:
+                    continue  # ineligible: stays dense (quantization.rs:24-38)
+                lw.qlin[role] = QuantLinear.from_dense(w, bits, group)
+                setattr(lw, attr, None)
+            return
+        p = f"model.layers.{li}."
+        D = cfg.head_dim
+        nq, nkv, rep = model.n_q_local, model.n_kv_local, model.kv_rep
+        q0 = r * nq
+        kv0 = (r // rep) * nkv if rep > 1 else r * nkv
+        try:
+            parts = [from_source(model, p + "self_attn.q_proj.weight", rows=(q0 * D, (q0 + nq) * D)),
+                     from_source(model, p + "self_attn.k_proj.weight", rows=(kv0 * D, (kv0 + nkv) * D)),
+                     from_source(model, p + "self_attn.v_proj.weight", rows=(kv0 * D, (kv0 + nkv) * D))]
+            lw.qlin["qkv"] = QuantLinear.concat_rows(parts)
+            lw.wqkv = None
+            lw.qlin["o"] = from_source(model, p + "self_attn.o_proj.weight", cols=(q0 * D, (q0 + nq) * D))
+            lw.wo = None
+            if lw.moe is None:
+                I_ = cfg.intermediate_size
+                lo, hi = r * (I_ // tp), (r + 1) * (I_ // tp)
+                lw.qlin["gate_up"] = QuantLinear.concat_rows([
+                    from_source(model, p + "mlp.gate_proj.weight", rows=(lo, hi)),
+                    from_source(model, p + "mlp.up_proj.weight", rows=(lo, hi))])
+                lw.w_gate_up = None
+                lw.qlin["down"] = from_source(model, p + "mlp.down_proj.weight", cols=(lo, hi))
+                lw.w_down = None
+        except (RuntimeError, AssertionError):
+            pass  # a tensor without an affine form (dense / IQ): the dense weights already loaded stay in use
+
+    return hook

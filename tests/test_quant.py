@@ -1,0 +1,98 @@
+"""Quantised linears: layouts (CPU) and the tcgen05 dequant-GEMM (GPU) against dequantise-then-matmul in fp32."""
+import numpy as np
+import pytest
+import torch
+
+from eredu_b200.lib import _eredu_host as H
+from eredu_b200.ops.quant import (QuantLinear, affine_quantize_tensor, codes_to_kernel4, unpack_bitstream)
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4, 5, 6, 8])
+def test_unpack_bitstream_matches_host_codec(bits):
+    rng = np.random.default_rng(bits)
+    w = (rng.standard_normal((6, 256)) * 0.1).astype(np.float32)
+    packed, scales, biases = H.affine_quantize(w, bits, 64 if bits != 6 else 16, "bf16")
+    codes = unpack_bitstream(torch.from_numpy(packed.astype(np.int64)).to(torch.int32), bits)
+    assert np.array_equal(codes.numpy(), H.unpack_codes(packed, bits))
+
+
+def test_kernel_layout_round_trip_and_device_quantizer_matches_host():
+    torch.manual_seed(0)
+    w = torch.randn(16, 512) * 0.05
+    codes, s, b = affine_quantize_tensor(w, 4, 64)
+    ql = QuantLinear(codes, s, b, 4, 64, "cpu")
+    assert torch.equal(ql.codes(), codes)
+    assert ql.wq.shape == (16, 256)
+    hp, hs, hb = H.affine_quantize(w.numpy(), 4, 64, "bf16")
+    assert np.array_equal(H.unpack_codes(hp, 4), codes.numpy())
+    assert np.allclose(hs, s.float().numpy()) and np.allclose(hb, b.float().numpy())
+    deq = ql.dequantize()
+    assert float((deq - w).abs().max()) < 0.02
+    x = torch.randn(3, 512)
+    assert torch.allclose(ql(x), x @ deq.t(), atol=1e-4)
+    # row / column slices and mixed-width fusion keep every value
+    a = ql.slice_rows(4, 12).slice_cols(128, 384)
+    assert torch.equal(a.dequantize(), deq[4:12, 128:384])
+    c8, s8, b8 = affine_quantize_tensor(w[:8], 6, 16)
+    fused = QuantLinear.concat_rows([ql, QuantLinear(c8, s8, b8, 6, 16, "cpu")])
+    assert fused.kbits == 8 and fused.group == 16
+    assert torch.equal(fused.dequantize()[:16], deq)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("bits,group", [(4, 64), (4, 32), (4, 128), (8, 32), (6, 16), (4, 16)])
+@pytest.mark.parametrize("M", [1, 7, 32, 50, 128, 300])
+def test_qgemm_matches_dequantized_matmul(bits, group, M):
+    torch.manual_seed(bits * 1000 + group + M)
+    N, K = 640, 1024
+    w = (torch.randn(N, K, device="cuda") * 0.05).bfloat16()
+    ql = QuantLinear.from_dense(w, bits, group)
+    x = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    res = torch.randn(M, N, device="cuda").bfloat16()
+    bias = torch.randn(N, device="cuda").bfloat16()
+    y = ql(x, bias=bias, residual=res)
+    deq = ql.dequantize(torch.float32)
+    ref = x.float() @ deq.t() + bias.float() + res.float()
+    rel = float((y.float() - ref).norm() / ref.norm())
+    assert rel < 1e-2, rel
+    from eredu_b200.ops import native
+    native.check_status(torch.device("cuda", torch.cuda.current_device()))
+
+
+@pytest.mark.gpu
+def test_qgemm_shapes_of_the_70b_shard_and_fp32_out():
+    torch.manual_seed(0)
+    for N, K in ((1280, 8192), (8192, 1024), (7168, 8192), (8192, 3584)):
+        w = (torch.randn(N, K, device="cuda") * 0.02).bfloat16()
+        ql = QuantLinear.from_dense(w, 4, 64)
+        for M in (1, 8):
+            x = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+            y = ql(x, out_dtype=torch.float32)
+            ref = x.float() @ ql.dequantize().t()
+            assert float((y - ref).norm() / ref.norm()) < 1e-2
+        assert abs(ql.nbytes() / (N * K) - (0.5 + 4 / 64)) < 1e-6
+
+
+@pytest.mark.gpu
+def test_gguf_q4k_q6k_model_runs_on_native_codes(tmp_path):
+    import dataclasses
+
+    from eredu_b200.api import LoadedModel, ModelLoadOptions
+    from eredu_b200.formats import checkpoint as ck
+    from eredu_b200.models import config as C
+    from eredu_b200.models.llama import random_state
+
+    cfg = dataclasses.replace(C.tiny_llama(), hidden_size=512, num_attention_heads=8, num_key_value_heads=2, head_dim=64,
+                              intermediate_size=1024, vocab_size=1024, num_hidden_layers=2, tie_word_embeddings=False)
+    sd = random_state(cfg, seed=0, std=0.05)
+    path = tmp_path / "m.gguf"
+    ck.save_gguf_checkpoint(path, cfg, sd, type_for=lambda n: "Q6_K" if ("attn_v" in n or "ffn_down" in n) else
+                            ("F32" if ("token_embd" in n or n.startswith("output")) else "Q4_K"))
+    native = LoadedModel.load(path, ModelLoadOptions(device="cuda", max_batch=1, max_seq_len=128, native_gguf=True))
+    dense = LoadedModel.load(path, ModelLoadOptions(device="cuda", max_batch=1, max_seq_len=128, native_gguf=False))
+    assert "qkv" in native.model.layers[0].qlin and native.model.layers[0].qlin["qkv"].kbits == 8
+    assert native.model.layers[0].qlin["o"].kbits == 4 and not dense.model.layers[0].qlin
+    prompt = list(range(3, 40))
+    a, b = native.prefill_logits(prompt), dense.prefill_logits(prompt)
+    rel = float((a - b).norm() / b.norm())
+    assert rel < 0.05 and torch.nn.functional.cosine_similarity(a, b, dim=0) > 0.995
