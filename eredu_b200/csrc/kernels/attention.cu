@@ -657,3 +657,48 @@ extern "C" int eredu_attn_decode(const void* q, const void* k_cache, const void*
   }
   return static_cast<int>(cudaGetLastError());
 }
+
+// ---------------------------------------------------------------------------------------------- no-allocation variant
+#include "attention_noalloc.h"
+
+namespace {
+constexpr size_t kNoAllocCounterBytes = EREDU_NOALLOC_MAX_GROUPS * sizeof(int);
+constexpr size_t kNoAllocMlBytes = static_cast<size_t>(EREDU_NOALLOC_MAX_ROW_SPLITS) * 2 * sizeof(float);
+constexpr size_t kNoAllocOBytes = static_cast<size_t>(EREDU_NOALLOC_MAX_ROW_SPLITS) * 128 * sizeof(float);
+}  // namespace
+
+// Scratch of eredu_attn_decode_static: [arrival counters | (max, sum) pairs | partial outputs].
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocCounterBytes + kNoAllocMlBytes + kNoAllocOBytes];
+
+extern "C" int eredu_attn_decode_static(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                        const int* block_table, const int* seq_lens, const float* sinks, int batch,
+                                        int q_per_seq, int max_pages, int n_q_heads, int n_kv_heads, int head_dim,
+                                        int splits, int window, float scale, cudaStream_t stream) {
+  if (splits < 1) splits = 1;
+  if (splits > 64) splits = 64;
+  if (head_dim != 64 && head_dim != 128) return -1;
+  const long long row_splits = static_cast<long long>(batch) * q_per_seq * n_q_heads * splits;
+  if (row_splits > EREDU_NOALLOC_MAX_ROW_SPLITS || static_cast<long long>(batch) * n_kv_heads > EREDU_NOALLOC_MAX_GROUPS)
+    return -2;
+  // The array's name is only a host-side handle: resolve its device address once per device.
+  static unsigned char* base[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= 64) return -1;
+  if (base[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    base[dev] = static_cast<unsigned char*>(p);
+  }
+  int* counters = reinterpret_cast<int*>(base[dev]);
+  float* part_ml = reinterpret_cast<float*>(base[dev] + kNoAllocCounterBytes);
+  float* part_o = reinterpret_cast<float*>(base[dev] + kNoAllocCounterBytes + kNoAllocMlBytes);
+  if (splits > 1) {
+    e = cudaMemsetAsync(counters, 0, static_cast<size_t>(batch) * n_kv_heads * sizeof(int), stream);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  return eredu_attn_decode(q, k_cache, v_cache, out, block_table, seq_lens, sinks, part_o, part_ml, counters, batch,
+                           q_per_seq, max_pages, n_q_heads, n_kv_heads, head_dim, splits, window, scale, stream);
+}
