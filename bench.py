@@ -123,7 +123,8 @@ def main() -> int:
 
     cfg = C.llama3_8b() if args.model == "llama3-8b" else C.tiny_llama()
     K, W, B, P = args.steps, max(args.warmup, 3), args.batch, args.prompt_len
-    budget = 2 * (W + K) + 32
+    HOLD = 150
+    budget = 2 * (W + K + HOLD) + 32
     model = build_random(cfg, dev, torch.bfloat16, seed=0, parallel=par)
     if world > 1:
         from eredu_b200.parallel import tp
@@ -170,12 +171,18 @@ def main() -> int:
         seqs = [eng.new_sequence(p, greedy, max_new_tokens=budget) for p in batch_prompts]
         first = eng.prefill(seqs)
         eng.start_decode(seqs, first)
+        # clocks are sampled from before the warm-up (nvidia-smi needs a moment to start) until the timed region
+        # ends; the GPU is under the same load during both
+        sampler = ClockSampler(local_rank)
+        sampler.start()
         for _ in range(W):
             eng.decode_step(sync=False)
+        torch.cuda.synchronize(dev)
+        for _ in range(HOLD):  # a fixed count (identical on every rank) of load-holding steps while nvidia-smi starts
+            eng.decode_step(sync=False)
+        torch.cuda.synchronize(dev)
         launches0 = native.launch_count()
-        sampler = ClockSampler(local_rank)
         barrier()
-        sampler.start()
         if not e2e:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()

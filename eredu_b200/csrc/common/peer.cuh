@@ -41,6 +41,11 @@ __device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int* p
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+__device__ __forceinline__ unsigned int ld_relaxed_sys_u32(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
 __device__ __forceinline__ float ld_cg_f32(const float* p) {
   float v;
   asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
@@ -64,12 +69,14 @@ __device__ __forceinline__ bool wait_flag(const PeerComm& c, int parity, int src
   const unsigned int* f = peer_flag(c, c.rank, parity, src, idx);
   if (static_cast<int>(ld_acquire_sys_u32(f) - want) >= 0) return true;
   const long long t0 = clock64();
-  while (static_cast<int>(ld_acquire_sys_u32(f) - want) < 0) {
+  // poll with relaxed loads, acquire once at the end
+  while (static_cast<int>(ld_relaxed_sys_u32(f) - want) < 0) {
     if (clock64() - t0 > kWaitCycleLimit) {
       report_status(status, kStatusPeerFlagTimeout);
       return false;
     }
   }
+  asm volatile("fence.acq_rel.sys;" ::: "memory");
   return true;
 }
 

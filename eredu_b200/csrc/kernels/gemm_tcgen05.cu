@@ -58,8 +58,8 @@ struct GemmParams {
 
 // Collective fused into the epilogue (tensor parallelism over NVLink peer memory, small token counts):
 //   COMM_AR: every rank holds a K-slice; partial tiles are pushed to all peers' staging slots as they
-//            leave TMEM, published per tile with release flags, and each rank sums the `size` partials in
-//            rank order (bitwise identical on all ranks), adds bias/residual once and stores the result.
+//            leave TMEM as 8-byte {bf16x2, sequence tag} words (no fence, no flag), and each rank sums the
+//            `size` partials in rank order (bitwise identical on all ranks), adds bias/residual once and stores.
 //   COMM_AG: every rank holds an N-slice; finished tiles are stored straight into every peer's gathered
 //            output at the rank's column offset.
 enum { COMM_NONE = 0, COMM_AR = 1, COMM_AG = 2 };
@@ -73,7 +73,7 @@ struct GemmCfg {
   static constexpr int kStageBytes = kATile * (DUAL ? 2 : 1) + kBTile;
   // Decode-sized tiles keep shared memory under half an SM so that two CTAs are co-resident: the whole grid
   // (<= 296 CTAs) then runs as one wave and HBM bandwidth is shared evenly instead of paying a partial wave.
-  static constexpr int kBudget = (TN <= 32) ? (DUAL ? 3 * kStageBytes : 100 * 1024) : 196 * 1024;
+  static constexpr int kBudget = (TN <= 32) ? (DUAL ? 3 * kStageBytes : 100 * 1024) : (TN == 64 && !DUAL) ? 100 * 1024 : 196 * 1024;
   static constexpr int kStagesRaw = kBudget / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kAccCols = TN * (DUAL ? 2 : 1);
@@ -108,22 +108,17 @@ __device__ __forceinline__ float epilogue_store(const GemmParams& p, float g, fl
   return __bfloat162float(r);
 }
 
+// COMM_AG: the finished value goes straight into every peer's gathered output.
 template <int COMM>
 __device__ __forceinline__ void comm_emit(const GemmParams& p, int parity, float g, int m, int n, float scale) {
-  if (COMM == COMM_AR) {
-    const size_t idx = static_cast<size_t>(m) * p.N + n;
-    for (int peer = 0; peer < p.comm.size; ++peer) {
-      reinterpret_cast<float*>(peer_slot(p.comm, peer, parity, p.comm.rank))[idx] = g;
-    }
-  } else {
-    float v = g * scale;
-    if (p.bias != nullptr) v += __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[n]);
-    const size_t idx = static_cast<size_t>(m) * p.ldy + p.col_offset + n;
-    for (int peer = 0; peer < p.comm.size; ++peer) {
-      uint8_t* out = p.comm.base[peer] + p.comm.out_off;
-      if (p.out_fp32) reinterpret_cast<float*>(out)[idx] = v;
-      else reinterpret_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16(v);
-    }
+  (void)parity;
+  float v = g * scale;
+  if (p.bias != nullptr) v += __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[n]);
+  const size_t idx = static_cast<size_t>(m) * p.ldy + p.col_offset + n;
+  for (int peer = 0; peer < p.comm.size; ++peer) {
+    uint8_t* out = p.comm.base[peer] + p.comm.out_off;
+    if (p.out_fp32) reinterpret_cast<float*>(out)[idx] = v;
+    else reinterpret_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16(v);
   }
 }
 
@@ -309,7 +304,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         tmem_ld16(taddr + c0, g);
         if (DUAL) tmem_ld16(taddr + TN + c0, u);
         tmem_wait_ld();
-        if (SPLIT) {
+        if (SPLIT || COMM == COMM_AR) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             red[(c0 + j) * 128 + row] = __uint_as_float(g[j]);
@@ -324,12 +319,48 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     if (!SPLIT && COMM == COMM_NONE) publish_ssq(0, 1);
   }
 
+  // Columns (tokens) of the tile whose final value this CTA produces: all of them, or with cluster split-K
+  // every nsplit-th one (COMM_AR: every nsplit-th PAIR of columns, because partials travel as bf16x2).
+  const int m_end = min(TN, m_limit - m_base);
   if (SPLIT) {
     // Every thread of every CTA of the cluster reaches both barriers, whatever happened above.
     cg::cluster_group cluster = cg::this_cluster();
     cluster.sync();
+  }
+  if (COMM == COMM_AR) {
+    // ---- all-reduce, "LL" style: every partial pair is one 8-byte word {bf16x2 value, sequence tag} stored
+    // into each peer's staging slot; a word is complete when its tag matches, so there is no fence, no flag and
+    // no barrier between the tensor-core tile and the reduction.
     if (warp >= 2) {
-      const int m_end = min(TN, m_limit - m_base);
+      cg::cluster_group cluster = cg::this_cluster();
+      const uint32_t tag = seq + 1u;
+      const int p_first = SPLIT ? split : 0, p_step = SPLIT ? nsplit : 1;
+      for (int pi = p_first; 2 * pi < m_end; pi += p_step) {
+        float g0 = 0.f, g1 = 0.f;
+        if (SPLIT) {
+          for (int r = 0; r < nsplit; ++r) {
+            const float* peer = cluster.map_shared_rank(red, r);
+            g0 += peer[(2 * pi) * 128 + row];
+            g1 += peer[(2 * pi + 1) * 128 + row];
+          }
+        } else {
+          g0 = red[(2 * pi) * 128 + row];
+          g1 = red[(2 * pi + 1) * 128 + row];
+        }
+        if (in_n) {
+          const uint32_t packed = pack_bf16x2(g0, g1);
+          const size_t word = (static_cast<size_t>(m_base / 2 + pi) * p.N + n) * 8;
+          for (int peer = 0; peer < p.comm.size; ++peer) {
+            asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(peer_slot(p.comm, peer, parity, p.comm.rank) + word),
+                         "r"(packed), "r"(tag)
+                         : "memory");
+          }
+        }
+      }
+    }
+  } else if (SPLIT) {
+    if (warp >= 2) {
+      cg::cluster_group cluster = cg::this_cluster();
       for (int c = split; c < m_end; c += nsplit) {
         float g = 0.f, u = 0.f;
         for (int r = 0; r < nsplit; ++r) {
@@ -341,40 +372,88 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       }
       if (COMM == COMM_NONE) publish_ssq(split, nsplit);
     }
+  }
+  if (SPLIT) {
+    cg::cluster_group cluster = cg::this_cluster();
     cluster.sync();
   }
 
-  if (COMM != COMM_NONE) {
-    // ---- publish this CTA's share, wait for the peers' same share, finish
-    const int flag_id = ((tile_n * gridDim.y + tile_m) * (SPLIT ? 8 : 1) + split) % kMaxFlags;
+  if (COMM == COMM_AR) {
     if (warp >= 2) {
-      __threadfence_system();
-      epi_barrier();
-      if (et < p.comm.size) st_release_sys(peer_flag(p.comm, et, parity, p.comm.rank, flag_id), seq + 1u);
-      if (et < p.comm.size) wait_flag(p.comm, parity, et, flag_id, seq + 1u, p.status);
-      epi_barrier();
-      if (COMM == COMM_AR) {
-        const int m_end = min(TN, m_limit - m_base);
-        const int c_first = SPLIT ? split : 0, c_step = SPLIT ? nsplit : 1;
-        for (int c = c_first; c < m_end; c += c_step) {
-          const int m = m_base + c;
-          float v = 0.f;
-          if (in_n) {
-            for (int src = 0; src < p.comm.size; ++src) {
-              const float* slot = reinterpret_cast<const float*>(peer_slot(p.comm, p.comm.rank, parity, src));
-              v += ld_cg_f32(slot + static_cast<size_t>(m) * p.N + n);
-            }
-            v = epilogue_store<false>(p, v, 0.f, m, n, 1.f);
-          }
-          if (p.ssq_out != nullptr) {
-            float sq = in_n ? v * v : 0.f;
+      const uint32_t tag = seq + 1u;
+      const int p_first = SPLIT ? split : 0, p_step = SPLIT ? nsplit : 1;
+      for (int pi = p_first; 2 * pi < m_end; pi += p_step) {
+        float v0 = 0.f, v1 = 0.f;
+        if (in_n) {
+          const size_t word = (static_cast<size_t>(m_base / 2 + pi) * p.N + n) * 8;
+          uint32_t val[kMaxRanks];
+          uint32_t missing = (1u << p.comm.size) - 1u;
+          const long long t0 = clock64();
+          while (missing != 0u) {
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-            if (lane == 0) s_ssq[q][c] = sq;
+            for (int src = 0; src < kMaxRanks; ++src) {
+              if (src < p.comm.size && ((missing >> src) & 1u)) {
+                uint32_t lo, hi;
+                asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];"
+                             : "=r"(lo), "=r"(hi)
+                             : "l"(peer_slot(p.comm, p.comm.rank, parity, src) + word)
+                             : "memory");
+                if (hi == tag) {
+                  val[src] = lo;
+                  missing &= ~(1u << src);
+                }
+              }
+            }
+            if (missing != 0u && clock64() - t0 > kWaitCycleLimit) {
+              report_status(p.status, kStatusPeerFlagTimeout);
+              break;
+            }
+          }
+#pragma unroll
+          for (int src = 0; src < kMaxRanks; ++src) {  // rank order: every rank computes the same bits
+            if (src < p.comm.size && !((missing >> src) & 1u)) {
+              v0 += bf16_lo(val[src]);
+              v1 += bf16_hi(val[src]);
+            }
+          }
+          v0 = epilogue_store<false>(p, v0, 0.f, m_base + 2 * pi, n, 1.f);
+          v1 = (2 * pi + 1 < m_end) ? epilogue_store<false>(p, v1, 0.f, m_base + 2 * pi + 1, n, 1.f) : 0.f;
+        }
+        if (p.ssq_out != nullptr) {
+          float s0 = in_n ? v0 * v0 : 0.f, s1 = in_n ? v1 * v1 : 0.f;
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) {
+            s0 += __shfl_xor_sync(0xffffffffu, s0, o);
+            s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+          }
+          if (lane == 0) {
+            s_ssq[q][2 * pi] = s0;
+            if (2 * pi + 1 < TN) s_ssq[q][2 * pi + 1] = s1;
           }
         }
-        publish_ssq(c_first, c_step);
       }
+      // publish the sums of squares of the columns this CTA finished (pairs p_first, p_first + p_step, ...)
+      if (p.ssq_out != nullptr) {
+        epi_barrier();
+        for (int c = et; c < m_end; c += 128) {
+          const int pi = c >> 1;
+          if (pi >= p_first && (pi - p_first) % p_step == 0)
+            p.ssq_out[static_cast<size_t>(m_base + c) * gridDim.x + tile_n] = s_ssq[0][c] + s_ssq[1][c] + s_ssq[2][c] + s_ssq[3][c];
+        }
+      }
+    }
+  } else if (COMM == COMM_AG) {
+    // ---- all-gather: publish this CTA's stores with one flag per peer, wait for the peers' same tile
+    const int flag_id = ((tile_n * gridDim.y + tile_m) * (SPLIT ? 8 : 1) + split) % kMaxFlags;
+    const bool has_share = (SPLIT ? split : 0) < m_end;
+    if (warp >= 2 && has_share) {
+      epi_barrier();
+      if (et < p.comm.size) {
+        __threadfence_system();
+        st_release_sys(peer_flag(p.comm, et, parity, p.comm.rank, flag_id), seq + 1u);
+        wait_flag(p.comm, parity, et, flag_id, seq + 1u, p.status);
+      }
+      epi_barrier();
     }
   }
 
@@ -561,7 +640,7 @@ extern "C" int eredu_gemm_bf16_comm(const void* X, const void* W, void* Y, const
   p.comm = *pc;
   const int n_tiles = (N + 127) / 128;
   const int m_tiles = 1;
-  if (mode == COMM_AR && static_cast<long long>(M) * N * 4 > pc->slot_bytes) return -2;
+  if (mode == COMM_AR && static_cast<long long>((M + 1) / 2) * N * 8 > pc->slot_bytes) return -2;
   int nsplit = force_split > 0 ? force_split : eredu_gemm_pick_split(M, N, K, sm_count > 0 ? sm_count : 148);
   const int kblocks = (K + 63) / 64;
   while (nsplit > 1 && (kblocks + nsplit - 1) / nsplit * (nsplit - 1) >= kblocks) nsplit >>= 1;

@@ -66,7 +66,35 @@ def main():
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 33)]
     sp = SamplingParams(temperature=0.0)
 
-    if "tp" in scenario and "pp" not in scenario:
+    if scenario == "gpu_tpops":
+        from eredu_b200.ops import native
+        from eredu_b200.parallel.tp import PeerTPOps
+
+        par = ParallelContext.from_env(ParallelTopology(tensor=world))
+        H, KF, V = 1024, 2048, 4096
+        ops_ = PeerTPOps(par, dev, H, V, max_tokens=1024)
+        gen = torch.Generator().manual_seed(123)
+        W = (torch.randn(H, KF, generator=gen) * 0.03).bfloat16()
+        head = (torch.randn(V, H, generator=gen) * 0.03).bfloat16()
+        errs = {}
+        for M in (1, 8, 33, 64, 99, 512, 1000):
+            X = (torch.randn(M, KF, generator=gen) * 0.5).bfloat16()
+            R = torch.randn(M, H, generator=gen).bfloat16()
+            Bv = torch.randn(H, generator=gen).bfloat16()
+            ref = X.float() @ W.float().t() + R.float() + Bv.float()
+            kl = KF // world
+            y = ops_.row_linear(X[:, rank * kl:(rank + 1) * kl].contiguous().to(dev), W[:, rank * kl:(rank + 1) * kl].contiguous().to(dev),
+                                residual=R.to(dev), bias=Bv.to(dev))
+            errs[f"ar{M}"] = float((y.float().cpu() - ref).norm() / ref.norm())
+            if M <= 64:
+                vl = V // world
+                Xh = (torch.randn(M, H, generator=gen) * 0.5).bfloat16()
+                lg = ops_.gathered_logits(Xh.to(dev), head[rank * vl:(rank + 1) * vl].contiguous().to(dev), V, rank * vl)
+                ref2 = Xh.float() @ head.float().t()
+                errs[f"ag{M}"] = float((lg.cpu() - ref2).norm() / ref2.norm())
+        native.check_status(dev)
+        result["errs"] = errs
+    elif "tp" in scenario and "pp" not in scenario:
         from eredu_b200.parallel import tp
 
         par = ParallelContext.from_env(ParallelTopology(tensor=world))

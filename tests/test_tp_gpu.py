@@ -45,3 +45,14 @@ def test_peer_fused_tp_matches_single_gpu_and_nccl(world, tmp_path):
         assert r["logits"] == peer[0]["logits"]  # every rank holds bitwise identical logits
         assert r["tokens"] == peer[0]["tokens"]
     assert _rel(torch.tensor(nccl[0]["logits"]), ref) <= 0.02
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_peer_collective_ops_against_full_matmul(world, tmp_path):
+    """Row-parallel GEMM + all-reduce (fused one-shot for <= 64 tokens, two-shot above) and the head's GEMM +
+    all-gather, each rank holding a K / vocabulary shard, against the unsharded fp32 product."""
+    _need(world)
+    res = run_ranks("gpu_tpops", world, tmp_path, extra_env={"NCCL_NVLS_ENABLE": "0"})
+    for r in res:
+        for name, e in r["errs"].items():
+            assert e < 1e-2, (r["rank"], name, e)
