@@ -135,3 +135,60 @@ class LoadedModel:
             return self.model.forward(batch, eng.kv)[0].float().cpu()
         finally:
             eng.release(seq)
+
+    # ------------------------------------------------------------------------------------------ chat
+    def prepare_chat(self, messages, tools=None, tool_choice=None, thinking: str = "auto", stop=None,
+                     allow_unparsed_reasoning: bool = False, **template_kwargs):
+        """Render a conversation with the checkpoint's chat template (``prepare_chat``, api/loaded.rs:426)."""
+        from ..text.chat import prepare_chat
+
+        tb = self.tokenizer
+        return prepare_chat(messages, template=tb.chat_template if tb else None, bos_token=tb.bos_token if tb else "",
+                            eos_token=tb.eos_token if tb else "", tools=tools, tool_choice=tool_choice,
+                            thinking=thinking, stop=stop, allow_unparsed_reasoning=allow_unparsed_reasoning,
+                            **template_kwargs)
+
+    def generate_prepared_chat(self, prepared, sampling: Optional[SamplingParams] = None, max_new_tokens: int = 256,
+                               on_event=None, cancellation=None, raw: bool = False):
+        """Generate a reply for a :class:`PreparedChat`, streaming semantic events (reasoning, text, tool-call
+        start / arguments / end, finished) to ``on_event`` (``generate_prepared_chat``, api/loaded.rs:154-227).
+        Returns a dict with text, reasoning, tool_calls, finish_reason, token ids and timing."""
+        import time
+
+        from ..runtime.streaming import CommittedTokenPipeline, FinishReason
+        from ..text.tokenizer import TextDecoder
+
+        if self.tokenizer is None:
+            raise RuntimeError("this checkpoint has no tokenizer")
+        prompt_ids = self.tokenizer.encode(prepared.prompt)
+        eos = set(self.eos_ids()) | set(self.tokenizer.eos_ids)
+        pipe = CommittedTokenPipeline(TextDecoder(self.tokenizer), None if raw else prepared.plan, prepared.stop, on_event,
+                                      prepared.tool_choice.max_parallel_calls)
+        t0 = time.perf_counter()
+        first_token_at = [None]
+        tokens: list[int] = []
+
+        def on_token(i, tok):
+            if first_token_at[0] is None:
+                first_token_at[0] = time.perf_counter()
+            if tok in eos:
+                return FinishReason.EOS
+            tokens.append(tok)
+            pipe.push(tok)
+            if pipe.finished:
+                return pipe.finished
+            if cancellation is not None and cancellation.is_cancelled():
+                return FinishReason.CANCELLED
+            return None
+
+        self.engine.generate([prompt_ids], sampling or SamplingParams(), max_new_tokens, eos_ids=(), on_token=on_token)
+        reason = self.engine.last_finish_reasons[0] or FinishReason.MAX_TOKENS
+        pipe.finish(reason)
+        t1 = time.perf_counter()
+        ttft = (first_token_at[0] or t1) - t0
+        n = len(tokens)
+        return {"text": "".join(pipe.text_out), "reasoning": "".join(pipe.reasoning_out), "tool_calls": pipe.tool_calls,
+                "finish_reason": pipe.finished, "tokens": tokens, "prompt_tokens": len(prompt_ids),
+                "timing": {"generation_time": t1 - t0, "time_to_first_token": ttft,
+                           "decode_token_rate": (n - 1) / max(1e-9, (t1 - t0) - ttft) if n > 1 else 0.0,
+                           "token_rate": n / max(1e-9, t1 - t0)}}

@@ -337,7 +337,8 @@ class Engine:
     def generate(self, prompts: list[list[int]], sampling: Optional[SamplingParams] = None, max_new_tokens: int = 64,
                  eos_ids=(), on_token=None) -> list[list[int]]:
         """Greedy / stochastic generation for a batch of token-id prompts. ``on_token(seq_index, token)`` is called
-        as tokens are committed."""
+        as tokens are committed; a truthy return value ends that sequence with the value as its finish reason.
+        ``self.last_finish_reasons`` holds the per-sequence reasons afterwards."""
         seqs = [self.new_sequence(p, sampling, max_new_tokens, eos_ids) for p in prompts]
         try:
             first = self.prefill(seqs)
@@ -345,7 +346,10 @@ class Engine:
             for i, (s, t) in enumerate(zip(seqs, first_host)):
                 s.output.append(int(t))
                 if on_token:
-                    on_token(i, int(t))
+                    why = on_token(i, int(t))
+                    if why:
+                        s.finished, s.finish_reason = True, str(why)
+                        continue
                 if int(t) in s.eos_ids:
                     s.finished, s.finish_reason = True, "eos"
                 elif len(s.output) >= s.max_new_tokens:
@@ -360,11 +364,21 @@ class Engine:
                     was = [s.finished for s in seqs]
                     self.commit(toks.tolist())
                     if on_token:
+                        stopped = False
                         for i, s in enumerate(seqs):
                             if not was[i]:
-                                on_token(i, s.output[-1])
+                                why = on_token(i, s.output[-1])
+                                if why and not s.finished:  # stop sequence, cancellation, grammar complete
+                                    s.finished, s.finish_reason, stopped = True, str(why), True
+                        if stopped:
+                            act = np.asarray([0 if s.finished else 1 for s in seqs], dtype=np.int32)
+                            if self.cuda:
+                                self._decode_state["active"].copy_(self._t(act, torch.int32))
+                            else:
+                                self._decode_state["active"] = torch.as_tensor(act)
             if self.cuda:
                 ops.native.check_status(self.device)
+            self.last_finish_reasons = [s.finish_reason for s in seqs]
             return [list(s.output) for s in seqs]
         finally:
             for s in seqs:

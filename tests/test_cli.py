@@ -1,0 +1,49 @@
+"""CLI: flag parsing / validation, sampling default resolution, and one end-to-end run on CPU with telemetry."""
+import dataclasses
+import json
+
+import pytest
+import torch
+
+from eredu_b200.cli.main import build_parser, main, resolve_sampling, validate_args
+from test_text_streaming import make_bundle
+
+
+def test_flag_validation():
+    p = build_parser()
+    a = p.parse_args(["-m", "x", "hi", "--quantize", "4", "--quantization-group-size", "64"])
+    validate_args(a)
+    for bad in (["--quantize", "7"], ["--quantization-group-size", "48"], ["-n", "0"], ["--device", "tpu"],
+                ["--allow-mixed-revisions", "--require-same-revision"]):
+        with pytest.raises(SystemExit):
+            validate_args(p.parse_args(["-m", "x", "hi"] + bad))
+
+
+def test_sampling_defaults_follow_checkpoint_config():
+    p = build_parser()
+    a = p.parse_args(["-m", "x", "hi"])
+    s = resolve_sampling(a, {})
+    assert s.temperature == 0.0 and s.top_k == 40 and s.top_p == 0.95 and abs(s.min_p - 0.05) < 1e-9
+    s = resolve_sampling(a, {"do_sample": True, "temperature": 0.6})
+    assert s.temperature == 0.6 and s.top_k == 50 and s.top_p == 1.0 and s.min_p == 0.0
+    a = p.parse_args(["-m", "x", "hi", "-t", "0.8", "--top-p", "0.9", "--seed", "7"])
+    s = resolve_sampling(a, {"do_sample": True, "temperature": 0.6, "top_p": 0.5})
+    assert s.temperature == 0.8 and s.top_p == 0.9 and s.seed == 7
+
+
+def test_cli_end_to_end_cpu(tmp_path, capsys):
+    from eredu_b200.formats import checkpoint as ck
+    from eredu_b200.models import config as C
+    from eredu_b200.models.llama import random_state
+
+    b = make_bundle(tmp_path)
+    cfg = dataclasses.replace(C.tiny_llama(), vocab_size=b.vocab_size(), eos_token_id=b.eos_ids[0])
+    ck.save_safetensors_checkpoint(tmp_path, cfg, random_state(cfg, seed=0, std=0.05), torch.float32)
+    tel = tmp_path / "tel.json"
+    rc = main(["-m", str(tmp_path), "hello", "--device", "cpu", "-n", "8", "--timing", "--telemetry-json", str(tel)])
+    assert rc == 0
+    out = capsys.readouterr()
+    assert "TTFT" in out.err
+    t = json.loads(tel.read_text())
+    assert t["generated_tokens"] <= 8 and t["prompt_tokens"] > 0 and t["stop_reason"] in ("max_tokens", "eos")
+    assert t["weights_bytes"] > 0 and t["plan"]["device"] == "cpu" and "host" in t["hardware"]
