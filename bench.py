@@ -86,7 +86,9 @@ def main() -> int:
     ap.add_argument("--impl", default="eredu_b200", choices=["eredu_b200", "reference"])
     ap.add_argument("--batch", type=int, default=32)
     ap.add_argument("--prompt-len", type=int, default=2048)
-    ap.add_argument("--model", default="llama3-8b", choices=["llama3-8b", "tiny"])
+    ap.add_argument("--model", default="llama3-8b", choices=["llama3-8b", "llama3-70b", "qwen3-30b-a3b", "tiny"])
+    ap.add_argument("--quantize", type=int, default=0, help="load-time affine quantisation bits (0 = bf16 weights)")
+    ap.add_argument("--group-size", type=int, default=64)
     ap.add_argument("--ttft-runs", type=int, default=5)
     ap.add_argument("--skip-b1", action="store_true")
     args = ap.parse_args()
@@ -114,18 +116,33 @@ def main() -> int:
             return 2
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    cfg = {"llama3-8b": C.llama3_8b, "llama3-70b": C.llama3_70b, "qwen3-30b-a3b": C.qwen3_30b_a3b,
+           "tiny": C.tiny_llama}[args.model]()
+    is_moe = cfg.num_experts > 0
     par = None
     if world > 1:
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=dev)
-        par = ParallelContext.from_env(ParallelTopology(tensor=world))
-
-    cfg = C.llama3_8b() if args.model == "llama3-8b" else C.tiny_llama()
+        # sparse models: attention tensor-parallel and experts expert-parallel over the same GPUs
+        topo = ParallelTopology(tensor=world, expert=world, expert_over_tensor=True) if is_moe else ParallelTopology(tensor=world)
+        par = ParallelContext.from_env(topo)
     K, W, B, P = args.steps, max(args.warmup, 3), args.batch, args.prompt_len
     HOLD = 150
     budget = 2 * (W + K + HOLD) + 32
-    model = build_random(cfg, dev, torch.bfloat16, seed=0, parallel=par)
+    moe_factory = quantizer = None
+    if is_moe:
+        from eredu_b200.models.moe import make_moe_factory
+
+        moe_factory = make_moe_factory()
+    if args.quantize:
+        from types import SimpleNamespace
+
+        from eredu_b200.ops.quant import make_quantizer
+
+        quantizer = make_quantizer(None, SimpleNamespace(quantization=SimpleNamespace(
+            bits=args.quantize, group_size=args.group_size, mode="affine"), native_gguf=False))
+    model = build_random(cfg, dev, torch.bfloat16, seed=0, parallel=par, moe_factory=moe_factory, quantizer=quantizer)
     if world > 1:
         from eredu_b200.parallel import tp
 
@@ -246,11 +263,12 @@ def main() -> int:
         "higher_is_better": True,
         "scaling": "strong",
         "vs_baseline": None,
-        "dtype": "bf16",
+        "dtype": "bf16" if not args.quantize else f"bf16 activations, {args.quantize}-bit affine weights (group {args.group_size})",
         "data": "synthetic (uniform-random token prompts, random-init N(0,0.02) weights)",
         "impl": "eredu_b200",
-        "config": {"model": "llama-3-8b-shaped" if args.model == "llama3-8b" else "tiny-llama", "global_batch": B,
-                   "seq_len": P, "decode_steps": K, "parallelism": f"tp{world}", "kv_page_tokens": 16,
+        "config": {"model": args.model + "-shaped", "global_batch": B,
+                   "seq_len": P, "decode_steps": K, "parallelism": f"tp{world}" + (f"+ep{world}" if is_moe else ""),
+                   "kv_page_tokens": 16,
                    "l2": "per-step inputs (weight shard + KV pages) exceed L2; no flush needed",
                    "timing": "CUDA events around K CUDA-graph decode steps, max over ranks"},
         "decode_tokens_per_s_b1": round(K / (ms_1 / 1e3), 2) if ms_1 else None,

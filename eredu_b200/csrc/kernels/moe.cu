@@ -11,6 +11,7 @@
 // (runtime/distributed/expert.rs:575) and for the count matrix (:805-808); here both stay on the device.
 #include "../common/launch.h"
 #include "../common/launch_count.h"
+#include "../common/peer.cuh"
 #include "../common/ptx.cuh"
 
 namespace eredu {
@@ -233,6 +234,120 @@ __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const in
   }
 }
 
+// Expert-parallel combine fused with the all-reduce over the expert group (replicated-token expert
+// parallelism: every rank routed all tokens and ran its own experts). Each thread forms the weighted sum of
+// its token's LOCAL routes for 8 columns, pushes it to every peer's staging slot as four 8-byte
+// {bf16x2, sequence tag} words (two 16-byte stores; every 8-byte half validates itself, so no fence, flag or
+// barrier is needed), then collects the same words from all ranks out of its own slots, sums them in rank order
+// (bitwise identical on every rank), adds the residual once and stores. T <= 64 tokens (decode / verify steps).
+// grid = (T, ceil(H / 8 / 128)).
+__global__ void __launch_bounds__(128) moe_combine_ar_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ route_pos,
+                                                              const float* __restrict__ weights,
+                                                              const __nv_bfloat16* __restrict__ residual,
+                                                              const __nv_bfloat16* __restrict__ extra,
+                                                              __nv_bfloat16* __restrict__ out, int k, int H, PeerComm comm,
+                                                              int* status) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const unsigned int seq = *reinterpret_cast<volatile unsigned int*>(comm.seq);
+  const int parity = static_cast<int>(seq & 1u);
+  const uint32_t tag = seq + 1u;
+  const size_t t = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c < (H >> 3)) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int slot = 0; slot < k; ++slot) {
+      const int pos = route_pos[t * k + slot];
+      if (pos < 0) continue;
+      const float w = weights[t * k + slot];
+      const uint4 v = reinterpret_cast<const uint4*>(y + static_cast<size_t>(pos) * H)[c];
+      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc[2 * j] += w * bf16_lo(u[j]);
+        acc[2 * j + 1] += w * bf16_hi(u[j]);
+      }
+    }
+    if (extra != nullptr) {
+      const uint4 v = reinterpret_cast<const uint4*>(extra + t * H)[c];
+      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc[2 * j] += bf16_lo(u[j]);
+        acc[2 * j + 1] += bf16_hi(u[j]);
+      }
+    }
+    uint32_t pk[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) pk[j] = pack_bf16x2(acc[2 * j], acc[2 * j + 1]);
+    const size_t word = (t * (H >> 1) + static_cast<size_t>(c) * 4) * 8;  // byte offset of this thread's four words
+    for (int peer = 0; peer < comm.size; ++peer) {
+      uint8_t* dst = peer_slot(comm, peer, parity, comm.rank) + word;
+      asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(pk[0]), "r"(tag), "r"(pk[1]), "r"(tag)
+                   : "memory");
+      asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 16), "r"(pk[2]), "r"(tag), "r"(pk[3]),
+                   "r"(tag)
+                   : "memory");
+    }
+    uint32_t val[kMaxRanks][4];
+    uint32_t missing = (1u << comm.size) - 1u;
+    const long long t0 = clock64();
+    while (missing != 0u) {
+#pragma unroll
+      for (int src = 0; src < kMaxRanks; ++src) {
+        if (src < comm.size && ((missing >> src) & 1u)) {
+          const uint8_t* from = peer_slot(comm, comm.rank, parity, src) + word;
+          uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+          asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "l"(from) : "memory");
+          asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3)
+                       : "l"(from + 16)
+                       : "memory");
+          if (a1 == tag && a3 == tag && b1 == tag && b3 == tag) {
+            val[src][0] = a0;
+            val[src][1] = a2;
+            val[src][2] = b0;
+            val[src][3] = b2;
+            missing &= ~(1u << src);
+          }
+        }
+      }
+      if (missing != 0u && clock64() - t0 > kWaitCycleLimit) {
+        report_status(status, kStatusPeerFlagTimeout);
+        break;
+      }
+    }
+    float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int src = 0; src < kMaxRanks; ++src) {
+      if (src < comm.size && !((missing >> src) & 1u)) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          sum[2 * j] += bf16_lo(val[src][j]);
+          sum[2 * j + 1] += bf16_hi(val[src][j]);
+        }
+      }
+    }
+    if (residual != nullptr) {
+      const uint4 v = reinterpret_cast<const uint4*>(residual + t * H)[c];
+      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        sum[2 * j] += bf16_lo(u[j]);
+        sum[2 * j + 1] += bf16_hi(u[j]);
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(sum[0], sum[1]);
+    o.y = pack_bf16x2(sum[2], sum[3]);
+    o.z = pack_bf16x2(sum[4], sum[5]);
+    o.w = pack_bf16x2(sum[6], sum[7]);
+    reinterpret_cast<uint4*>(out + t * H)[c] = o;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) finish_call(comm, seq, gridDim.x * gridDim.y);
+}
+
 }  // namespace eredu
 
 using namespace eredu;
@@ -273,6 +388,23 @@ extern "C" int eredu_moe_combine(const void* y, const int* route_pos, const floa
   launch_pdl(moe_combine_kernel, dim3(T), dim3(128), 0, stream, static_cast<const __nv_bfloat16*>(y), route_pos, weights,
              static_cast<const __nv_bfloat16*>(residual), static_cast<const __nv_bfloat16*>(extra),
              static_cast<__nv_bfloat16*>(out), k, H);
+  eredu_count_launches(1);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Combine + all-reduce over the expert group in one kernel (see moe_combine_ar_kernel). `comm` is the peer
+// communication context of the group; T * H * 4 bytes must fit one staging slot.
+extern "C" int eredu_moe_combine_ar(const void* y, const int* route_pos, const float* weights, const void* residual,
+                                    const void* extra, void* out, int T, int k, int H, const void* comm, int* status,
+                                    cudaStream_t stream) {
+  if (T <= 0) return 0;
+  const PeerComm* c = static_cast<const PeerComm*>(comm);
+  if (H % 8 != 0 || c == nullptr) return -1;
+  if (static_cast<long long>(T) * H * 4 > c->slot_bytes) return -2;
+  const int chunks = H / 8;
+  launch_pdl(moe_combine_ar_kernel, dim3(T, (chunks + 127) / 128), dim3(128), 0, stream,
+             static_cast<const __nv_bfloat16*>(y), route_pos, weights, static_cast<const __nv_bfloat16*>(residual),
+             static_cast<const __nv_bfloat16*>(extra), static_cast<__nv_bfloat16*>(out), k, H, *c, status);
   eredu_count_launches(1);
   return static_cast<int>(cudaGetLastError());
 }

@@ -57,8 +57,13 @@ class MoEBlock:
             return moe_ops.experts_forward(x, ids, w, self.w_gate_up, self.w_down, self.e0, residual=residual,
                                            extra=extra, limit=self.cfg.swiglu_limit)
         # shared experts are replicated: add them on one rank only so that the group sum counts them once
+        own_extra = extra if self.e0 == 0 else None
+        comm = getattr(self.ep_ops, "fused_comm", lambda tokens, hidden: None)(x.shape[0], x.shape[1]) if x.is_cuda else None
+        if comm is not None:  # decode-sized step: combine and all-reduce are one kernel over peer memory
+            return moe_ops.experts_forward(x, ids, w, self.w_gate_up, self.w_down, self.e0, residual=residual,
+                                           extra=own_extra, limit=self.cfg.swiglu_limit, comm=comm)
         partial = moe_ops.experts_forward(x, ids, w, self.w_gate_up, self.w_down, self.e0, residual=None,
-                                          extra=extra if self.e0 == 0 else None, limit=self.cfg.swiglu_limit)
+                                          extra=own_extra, limit=self.cfg.swiglu_limit)
         return self.ep_ops.all_reduce(partial, residual=residual)
 
 

@@ -16,6 +16,7 @@ native.register("eredu_moe_route", I, [P, P, P, P, I, I, I, I, I, native.F, P])
 native.register("eredu_moe_plan", I, [P, I, I, I, I, I, P, P, P, P, I, P, P])
 native.register("eredu_moe_gather", I, [P, P, P, P, I, I, P])
 native.register("eredu_moe_combine", I, [P, P, P, P, P, P, I, I, I, P])
+native.register("eredu_moe_combine_ar", I, [P, P, P, P, P, P, I, I, I, P, P, P])
 native.register("eredu_gemm_bf16_grouped", I, [P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, I, P, P])
 
 SCORING = {"softmax": 0, "sigmoid": 1, "sqrt_softplus": 2, "topk_softmax": 3}
@@ -105,9 +106,12 @@ def pick_tile(expected_rows_per_expert: float) -> int:
     return 128
 
 
-def experts_forward(x, ids, weights, w_gate_up, w_down, e0=0, residual=None, extra=None, limit=0.0, rows_cap=None):
+def experts_forward(x, ids, weights, w_gate_up, w_down, e0=0, residual=None, extra=None, limit=0.0, rows_cap=None,
+                    comm=None):
     """Local-expert MoE computation. x: [T, H] bf16; ids / weights: [T, k]; w_gate_up: [E_local, 2I, H];
-    w_down: [E_local, H, I]. Returns residual + extra + sum over local routes (bf16 [T, H])."""
+    w_down: [E_local, H, I]. Returns residual + extra + sum over local routes (bf16 [T, H]). With ``comm`` (a peer
+    communication context of the expert group) the combine kernel also sums the partial outputs of all ranks:
+    ``extra`` is then counted once per rank that passes it, ``residual`` once in total."""
     if not x.is_cuda:
         out = experts_ref(x, ids, weights, w_gate_up, w_down, e0, limit)
         if residual is not None:
@@ -140,6 +144,11 @@ def experts_forward(x, ids, weights, w_gate_up, w_down, e0=0, residual=None, ext
                                          inter, inter, inter, H, E_local * H, H, 0, 0, sm, ptr(st), stream_ptr(dev))
     check(code, "eredu_gemm_bf16_grouped(down)")
     out = torch.empty((T, H), dtype=x.dtype, device=dev)
+    if comm is not None:
+        code = lib().eredu_moe_combine_ar(ptr(y), ptr(plan.route_pos), ptr(weights), ptr(residual), ptr(extra), ptr(out),
+                                          T, k, H, comm, ptr(st), stream_ptr(dev))
+        check(code, "eredu_moe_combine_ar")
+        return out
     code = lib().eredu_moe_combine(ptr(y), ptr(plan.route_pos), ptr(weights), ptr(residual), ptr(extra), ptr(out), T, k,
                                    H, stream_ptr(dev))
     check(code, "eredu_moe_combine")

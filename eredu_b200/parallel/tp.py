@@ -64,6 +64,11 @@ class PeerTPOps:
         native.check(code, "eredu_allreduce_twoshot")
         return y
 
+    def fused_comm(self, tokens: int, hidden: int):
+        """The communication context for kernels that fold the group sum into their own epilogue (the expert
+        combine), or None when the partials do not fit one staging slot."""
+        return self.pg.comm if tokens * hidden * 4 <= self.pg.slot_bytes else None
+
     def all_reduce(self, partial, residual=None, bias=None):
         """Sum a local bf16 partial over the group (used after quantised row-parallel GEMMs)."""
         M, N = partial.shape
@@ -137,4 +142,9 @@ def attach(model, par, max_tokens: int = 8192, backend: str = "peer"):
         model.tp_ops = PeerTPOps(par, model.device, model.cfg.hidden_size, model.cfg.vocab_size, max_tokens)
     else:
         model.tp_ops = NcclTPOps(par, model.device)
+    if par.ep_size > 1 and par.ep_group is par.tp_group:
+        # experts are spread over the same ranks as the attention heads: one collective context serves both
+        from ..models.moe import attach_ep
+
+        attach_ep(model, model.tp_ops)
     return model

@@ -29,6 +29,17 @@ def tiny_cfg(gpu: bool):
     return dataclasses.replace(cfg, vocab_size=512, num_attention_heads=4, num_key_value_heads=2)
 
 
+def moe_cfg(gpu: bool):
+    base = dataclasses.replace(C.tiny_llama(), model_type="qwen3_moe", qk_norm=True, vocab_size=512, num_experts=8,
+                               num_experts_per_tok=2, moe_intermediate_size=64, norm_topk_prob=True,
+                               tie_word_embeddings=False, rms_norm_eps=1e-6)
+    if gpu:
+        return dataclasses.replace(base, hidden_size=1024, num_attention_heads=8, num_key_value_heads=2, head_dim=128,
+                                   moe_intermediate_size=256, vocab_size=4096, num_hidden_layers=3, num_experts=16,
+                                   num_experts_per_tok=4)
+    return dataclasses.replace(base, num_attention_heads=4, num_key_value_heads=2)
+
+
 def probe_logits(eng, model, prompt):
     """(decode-step logits of the last prompt token after prefilling the rest) as a CPU fp32 list."""
     from eredu_b200.models.llama import ForwardBatch
@@ -94,6 +105,24 @@ def main():
                 errs[f"ag{M}"] = float((lg.cpu() - ref2).norm() / ref2.norm())
         native.check_status(dev)
         result["errs"] = errs
+    elif "ep" in scenario:
+        # attention tensor-parallel and experts expert-parallel over the same ranks
+        from eredu_b200.models.moe import make_moe_factory
+        from eredu_b200.parallel import tp
+
+        cfg = moe_cfg(gpu)
+        sd = random_state(cfg, seed=0, std=0.08)
+        par = ParallelContext.from_env(ParallelTopology(tensor=world, expert=world, expert_over_tensor=True))
+        model = build_from_tensors(cfg, sd.__getitem__, sd.__contains__, dev, dtype, par, moe_factory=make_moe_factory())
+        tp.attach(model, par, max_tokens=256, backend="nccl" if "nccl" in scenario else "peer")
+        eng = Engine(model, max_batch=4, max_seq_len=128)
+        result["tokens"] = eng.generate(prompts, sp, max_new_tokens=10)
+        if gpu:
+            from eredu_b200.ops import native
+
+            probe = torch.randint(0, cfg.vocab_size, (100,), generator=torch.Generator().manual_seed(7)).tolist()
+            result["logits"] = probe_logits(eng, model, probe)
+            native.check_status(dev)
     elif "tp" in scenario and "pp" not in scenario:
         from eredu_b200.parallel import tp
 

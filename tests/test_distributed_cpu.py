@@ -8,7 +8,7 @@ from eredu_b200.ops import SamplingParams
 from eredu_b200.runtime.engine import Engine
 
 from dist_util import run_ranks
-from dist_worker import tiny_cfg
+from dist_worker import moe_cfg, tiny_cfg
 
 
 def _oracle(n_new, prompts_lens=(9, 33)):
@@ -33,5 +33,22 @@ def test_tensor_parallel_matches_single_rank(world, tmp_path):
 def test_pipeline_parallel_matches_single_rank(scenario, world, tmp_path):
     res = run_ranks(scenario, world, tmp_path)
     want = _oracle(10)
+    for r in res:
+        assert r["tokens"] == want
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_over_tensor_ranks_matches_single_rank(world, tmp_path):
+    """Attention tensor-parallel + experts expert-parallel on the same ranks (replicated tokens, partial expert
+    outputs summed over the group) reproduce the single-rank MoE model's tokens."""
+    from eredu_b200.models.moe import make_moe_factory
+
+    res = run_ranks("cpu_ep_nccl", world, tmp_path)
+    cfg = moe_cfg(False)
+    sd = random_state(cfg, seed=0, std=0.08)
+    model = build_from_tensors(cfg, sd.__getitem__, sd.__contains__, "cpu", torch.float32, moe_factory=make_moe_factory())
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 33)]
+    want = Engine(model, max_batch=4, max_seq_len=128).generate(prompts, SamplingParams(temperature=0.0), 10)
     for r in res:
         assert r["tokens"] == want

@@ -8,7 +8,7 @@ from eredu_b200.ops import SamplingParams
 from eredu_b200.runtime.engine import Engine
 
 from dist_util import run_ranks
-from dist_worker import probe_logits, tiny_cfg
+from dist_worker import moe_cfg, probe_logits, tiny_cfg
 
 pytestmark = pytest.mark.gpu
 
@@ -56,3 +56,26 @@ def test_peer_collective_ops_against_full_matmul(world, tmp_path):
     for r in res:
         for name, e in r["errs"].items():
             assert e < 1e-2, (r["rank"], name, e)
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_expert_parallel_fused_combine_matches_single_gpu(world, tmp_path):
+    """Qwen3-MoE-shaped model, attention TP + experts EP over the same GPUs: the combine + all-reduce kernel over
+    peer memory against the single-GPU model and the NCCL all-reduce of partial expert outputs."""
+    from eredu_b200.models.moe import make_moe_factory
+
+    _need(world)
+    env = {"NCCL_NVLS_ENABLE": "0"}
+    peer = run_ranks("gpu_ep_peer", world, tmp_path, extra_env=env)
+    nccl = run_ranks("gpu_ep_nccl", world, tmp_path, extra_env=env)
+    cfg = moe_cfg(True)
+    sd = random_state(cfg, seed=0, std=0.08)
+    model = build_from_tensors(cfg, sd.__getitem__, sd.__contains__, "cuda:0", torch.bfloat16, moe_factory=make_moe_factory())
+    eng = Engine(model, max_batch=4, max_seq_len=128)
+    probe = torch.randint(0, cfg.vocab_size, (100,), generator=torch.Generator().manual_seed(7)).tolist()
+    ref = torch.tensor(probe_logits(eng, model, probe))
+    for r in peer:
+        lg = torch.tensor(r["logits"])
+        assert _rel(lg, ref) <= 0.03
+        assert r["logits"] == peer[0]["logits"] and r["tokens"] == peer[0]["tokens"]
+    assert _rel(torch.tensor(nccl[0]["logits"]), ref) <= 0.03
