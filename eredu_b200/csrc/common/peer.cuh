@@ -19,7 +19,7 @@
 namespace eredu {
 
 constexpr int kMaxRanks = 8;
-constexpr int kMaxFlags = 4096;
+constexpr int kMaxFlags = 8192;
 
 struct PeerComm {
   uint8_t* base[kMaxRanks];  // peer r's symmetric buffer as mapped in this process (base[rank] = own)

@@ -25,6 +25,7 @@
 #include "../common/peer.cuh"
 #include "../common/ptx.cuh"
 #include "../common/tma_host.h"
+#include "gemm_persistent.h"
 
 namespace cg = cooperative_groups;
 
@@ -53,6 +54,9 @@ struct GemmParams {
   // of X and Y. Items with rows == 0 exit at once.
   const int* work;
   int w_rows_per_expert;
+  // Large token tiles: the epilogue goes through shared memory so that the output (and the residual) move as
+  // 16-byte row chunks instead of one 2-byte element per thread. Needs 16-byte aligned rows (host-checked).
+  int staged;
   PeerComm comm;   // COMM modes only
 };
 
@@ -251,6 +255,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   __shared__ float s_ssq[4][TN];
   const int et = threadIdx.x - 64;  // epilogue thread index 0..127 (warps 2..5)
   const bool in_n = n < p.N;
+  constexpr bool kCanStage = (TN >= 64) && !SPLIT && COMM == COMM_NONE;
 
   // Final value of element (column c of the tile, this thread's row): store it (or hand it to the
   // collective) and add its square to the per-column sum kept for a following RMSNorm. Executed by whole warps.
@@ -310,13 +315,76 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             red[(c0 + j) * 128 + row] = __uint_as_float(g[j]);
             if (DUAL) red[(TN + c0 + j) * 128 + row] = __uint_as_float(u[j]);
           }
+        } else if (kCanStage && p.staged) {
+          // value before the residual, fp32, [column][row]: conflict-free writes, coalesced second pass
+          float bg = 0.f, bu = 0.f;
+          if (p.bias != nullptr && in_n) {
+            const __nv_bfloat16* b = static_cast<const __nv_bfloat16*>(p.bias);
+            bg = __bfloat162float(b[n]);
+            if (DUAL) bu = __bfloat162float(b[p.N + n]);
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float sc = (p.ssq_in != nullptr) ? s_scale[c0 + j] : 1.f;
+            const float gg = __uint_as_float(g[j]) * sc + bg;
+            red[(c0 + j) * 128 + row] = DUAL ? silu_f(gg) * (__uint_as_float(u[j]) * sc + bu) : gg;
+          }
         } else {
 #pragma unroll
           for (int j = 0; j < 16; ++j) finish(__uint_as_float(g[j]), DUAL ? __uint_as_float(u[j]) : 0.f, c0 + j, true);
         }
       }
     }
-    if (!SPLIT && COMM == COMM_NONE) publish_ssq(0, 1);
+    if (kCanStage && p.staged) {
+      epi_barrier();  // the whole tile is staged (or the accumulator never arrived: nothing is stored)
+      if (acc_ok) {
+        const int m_cnt = min(TN, m_limit - m_base);
+        const int limit = (m_cnt * 16 + 31) & ~31;  // 16 chunks of 8 columns per token row; warp-uniform bound
+        const __nv_bfloat16* res = static_cast<const __nv_bfloat16*>(p.residual);
+        __nv_bfloat16* yout = static_cast<__nv_bfloat16*>(p.y);
+        constexpr int kBatch = 4;
+        for (int ch0 = et; ch0 < limit; ch0 += 128 * kBatch) {
+          uint4 rv[kBatch];
+          bool ok[kBatch];
+#pragma unroll
+          for (int b = 0; b < kBatch; ++b) {
+            const int ch = ch0 + 128 * b;
+            const int c = ch >> 4, gn = tile_n * 128 + (ch & 15) * 8;
+            ok[b] = ch < limit && c < m_cnt && gn < p.N;
+            rv[b] = make_uint4(0u, 0u, 0u, 0u);
+            if (ok[b] && res != nullptr) rv[b] = *reinterpret_cast<const uint4*>(res + static_cast<size_t>(m_base + c) * p.ldr + gn);
+          }
+#pragma unroll
+          for (int b = 0; b < kBatch; ++b) {
+            const int ch = ch0 + 128 * b;
+            if (ch >= limit) break;  // warp-uniform
+            const int c = ch >> 4, n0 = (ch & 15) * 8;
+            const float4 a0 = *reinterpret_cast<const float4*>(red + c * 128 + n0);
+            const float4 a1 = *reinterpret_cast<const float4*>(red + c * 128 + n0 + 4);
+            const uint32_t r[4] = {rv[b].x, rv[b].y, rv[b].z, rv[b].w};
+            uint4 o;
+            o.x = pack_bf16x2(a0.x + bf16_lo(r[0]), a0.y + bf16_hi(r[0]));
+            o.y = pack_bf16x2(a0.z + bf16_lo(r[1]), a0.w + bf16_hi(r[1]));
+            o.z = pack_bf16x2(a1.x + bf16_lo(r[2]), a1.y + bf16_hi(r[2]));
+            o.w = pack_bf16x2(a1.z + bf16_lo(r[3]), a1.w + bf16_hi(r[3]));
+            if (ok[b]) *reinterpret_cast<uint4*>(yout + static_cast<size_t>(m_base + c) * p.ldy + tile_n * 128 + n0) = o;
+            if (p.ssq_out != nullptr) {
+              const uint32_t w[4] = {o.x, o.y, o.z, o.w};
+              float sq = 0.f;
+              if (ok[b]) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) sq += bf16_lo(w[j]) * bf16_lo(w[j]) + bf16_hi(w[j]) * bf16_hi(w[j]);
+              }
+#pragma unroll
+              for (int o2 = 8; o2 > 0; o2 >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o2);
+              if ((lane & 15) == 0 && c < m_cnt) p.ssq_out[static_cast<size_t>(m_base + c) * gridDim.x + tile_n] = sq;
+            }
+          }
+        }
+      }
+    } else if (!SPLIT && COMM == COMM_NONE) {
+      publish_ssq(0, 1);
+    }
   }
 
   // Columns (tokens) of the tile whose final value this CTA produces: all of them, or with cluster split-K
@@ -514,6 +582,22 @@ static cudaError_t launch_gemm_split(const CUtensorMap& tmW, const CUtensorMap& 
 
 using namespace eredu;
 
+// EREDU_GEMM_PERSISTENT=0 keeps prefill-sized GEMMs on the one-tile-per-CTA kernel (for A/B measurements).
+static bool persistent_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = std::getenv("EREDU_GEMM_PERSISTENT");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+
+static bool staged_epilogue_ok(const void* Y, const void* residual, int N, int ldy, int ldr, int out_fp32) {
+  if (out_fp32 || N % 8 != 0 || ldy % 8 != 0 || (reinterpret_cast<uintptr_t>(Y) & 15) != 0) return false;
+  if (residual != nullptr && (ldr % 8 != 0 || (reinterpret_cast<uintptr_t>(residual) & 15) != 0)) return false;
+  return true;
+}
+
 // Number of K splits the launcher would use (exposed for tests and tuning).
 extern "C" int eredu_gemm_pick_split(int M, int N, int K, int sm_count) {
   const int tn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
@@ -538,6 +622,12 @@ extern "C" int eredu_gemm_bf16(const void* X, const void* W, void* Y, const void
                                cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   const int tn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  if (tn == 256 && !out_fp32 && force_split <= 1 && persistent_enabled()) {
+    // prefill-sized: persistent kernel with double-buffered accumulators
+    const int pr = launch_gemm_persistent(X, W, Y, residual, bias, M, N, K, ldx, ldw, ldy, ldr, w_rows, dual, dual_row_offset,
+                                          sm_count, status, ssq_in, ssq_parts, norm_eps, norm_dim, ssq_out, stream);
+    if (pr != kPersistentUnsupported) return pr;
+  }
   CUtensorMap tmW, tmX;
   int r = make_tma_2d(&tmW, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w_rows, K, ldw, 128, 64);
   if (r != 0) return -100 + r;
@@ -563,11 +653,13 @@ extern "C" int eredu_gemm_bf16(const void* X, const void* W, void* Y, const void
   p.ssq_out = ssq_out;
   p.work = nullptr;
   p.w_rows_per_expert = 0;
+  p.staged = 0;
   const int n_tiles = (N + 127) / 128;
   const int m_tiles = (M + tn - 1) / tn;
   int nsplit = force_split > 0 ? force_split : eredu_gemm_pick_split(M, N, K, sm_count > 0 ? sm_count : 148);
   const int kblocks = (K + 63) / 64;
   while (nsplit > 1 && (kblocks + nsplit - 1) / nsplit * (nsplit - 1) >= kblocks) nsplit >>= 1;  // no empty split
+  p.staged = staged_epilogue_ok(Y, residual, N, ldy, ldr, out_fp32) && tn >= 64 && nsplit == 1;
   cudaError_t e;
 #define ER_DISPATCH(TN_)                                                                     \
   case TN_:                                                                                  \
@@ -637,6 +729,7 @@ extern "C" int eredu_gemm_bf16_comm(const void* X, const void* W, void* Y, const
   p.ssq_out = ssq_out;
   p.work = nullptr;
   p.w_rows_per_expert = 0;
+  p.staged = 0;
   p.comm = *pc;
   const int n_tiles = (N + 127) / 128;
   const int m_tiles = 1;
@@ -644,7 +737,7 @@ extern "C" int eredu_gemm_bf16_comm(const void* X, const void* W, void* Y, const
   int nsplit = force_split > 0 ? force_split : eredu_gemm_pick_split(M, N, K, sm_count > 0 ? sm_count : 148);
   const int kblocks = (K + 63) / 64;
   while (nsplit > 1 && (kblocks + nsplit - 1) / nsplit * (nsplit - 1) >= kblocks) nsplit >>= 1;
-  if (n_tiles * 8 > kMaxFlags) return -3;
+  if (mode == COMM_AG && n_tiles * (nsplit > 1 ? 8 : 1) > kMaxFlags) return -3;
   cudaError_t e;
 #define ER_COMM(TN_)                                                                                        \
   case TN_:                                                                                                 \
@@ -700,6 +793,7 @@ extern "C" int eredu_gemm_bf16_grouped(const void* X, const void* W, void* Y, co
     }
     while (nsplit > 1 && (kblocks + nsplit - 1) / nsplit * (nsplit - 1) >= kblocks) nsplit >>= 1;
   }
+  p.staged = staged_epilogue_ok(Y, nullptr, N, ldy, 0, 0) && tile >= 64 && nsplit == 1;
   cudaError_t e;
 #define ER_GROUPED(TN_)                                                                      \
   case TN_:                                                                                  \

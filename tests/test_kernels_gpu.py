@@ -63,6 +63,44 @@ def test_gemm_fp32_out_and_strided(M):
     assert y.dtype == torch.float32 and rel_l2(y, ref) < 1e-2
 
 
+@pytest.mark.parametrize("M,N,K", [(100, 1024, 512), (129, 1000, 320), (300, 1096, 1024), (777, 4096, 512), (1500, 640, 2048),
+                                   (4100, 2048, 1088)])
+def test_gemm_fused_epilogue_large_m(M, N, K):
+    """Prefill-sized GEMMs (staged / persistent kernels): RMSNorm row scale in, bias, residual, sums of squares out."""
+    torch.manual_seed(M + N)
+    x = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
+    w = (torch.randn(N, K, device=DEV) * 0.05).bfloat16()
+    b = torch.randn(N, device=DEV).bfloat16()
+    r = torch.randn(M, N, device=DEV).bfloat16()
+    parts = 3
+    ssq = (x.float().pow(2).sum(-1, keepdim=True) / parts).repeat(1, parts).contiguous()
+    y, ssq_out = ops.linear(x, w, bias=b, residual=r, row_ssq=ssq, norm_eps=1e-5, want_ssq=True)
+    check_status()
+    scale = torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-5)
+    ref = (x.float() @ w.float().t()) * scale + b.float() + r.float()
+    assert rel_l2(y, ref) < 1e-2
+    want = y.float().pow(2).sum(-1)
+    assert torch.allclose(ssq_out.sum(-1), want, rtol=2e-3, atol=1e-3)
+    y2 = ops.linear(x, w)  # plain path, same kernels
+    assert rel_l2(y2, x.float() @ w.float().t()) < 1e-2
+    check_status()
+
+
+@pytest.mark.parametrize("M,K,I", [(300, 1024, 1408), (1000, 512, 832), (2300, 2048, 1472)])
+def test_gated_gemm_large_m(M, K, I):
+    torch.manual_seed(M)
+    x = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
+    w = (torch.randn(2 * I, K, device=DEV) * 0.05).bfloat16()
+    b = (torch.randn(2 * I, device=DEV) * 0.1).bfloat16()
+    ssq = x.float().pow(2).sum(-1, keepdim=True).contiguous()
+    y = ops.gated_linear(x, w, I, bias=b, row_ssq=ssq, norm_eps=1e-6)
+    check_status()
+    xs = x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-6)
+    z = xs @ w.float().t() + b.float()
+    ref = torch.nn.functional.silu(z[:, :I]) * z[:, I:]
+    assert rel_l2(y, ref) < 1.5e-2
+
+
 @pytest.mark.parametrize("M,split", [(1, 0), (8, 1), (8, 2), (32, 4), (64, 0), (100, 0), (300, 0)])
 def test_gated_gemm(M, split):
     K, I = 1024, 1408
