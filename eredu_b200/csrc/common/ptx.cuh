@@ -109,6 +109,16 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
         "r"(smem_u32(bar))
       : "memory");
 }
+// Bring a tile into L2 only (no shared-memory destination, no completion to wait for).
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(map)),
+               "r"(x), "r"(y)
+               : "memory");
+}
+// Bring `bytes` (multiple of 16, 16-byte aligned) of global memory into L2.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* gptr, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gptr), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {
   uint64_t p;
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
@@ -217,9 +227,20 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
 
 // Programmatic dependent launch: a kernel launched with the PDL attribute may start before its
 // predecessor finishes; it must call pdl_wait() before touching the predecessor's outputs.
+//
+// Where the dependents are released is a build-time choice. EREDU_PDL_EARLY=1: at the first instruction of every
+// kernel, so the next kernel's CTAs become resident (and run their prologue and weight prefetch) a whole kernel
+// ahead; its own wait still orders it after this kernel has completed, and transitively after everything before.
+// EREDU_PDL_EARLY=0: after this kernel's own wait.
+#ifndef EREDU_PDL_EARLY
+#define EREDU_PDL_EARLY 0
+#endif
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_early() {
+  if (EREDU_PDL_EARLY) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
 __device__ __forceinline__ void pdl_launch_dependents() {
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (!EREDU_PDL_EARLY) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
 }  // namespace eredu

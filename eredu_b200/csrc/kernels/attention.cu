@@ -12,6 +12,7 @@
 #include "../common/launch.h"
 #include "../common/launch_count.h"
 #include "../common/ptx.cuh"
+#include "../common/trace.cuh"
 
 namespace eredu {
 
@@ -83,6 +84,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(AttnParams p) {
   uint8_t* k_s = q_s + BM * D * 2;            // [2][BN][D]
   uint8_t* v_s = k_s + 2 * BN * D * 2;        // [2][BN][D]
 
+  pdl_launch_early();
   pdl_wait();
   pdl_launch_dependents();
   const int b = blockIdx.z, h = blockIdx.y, qt = blockIdx.x;
@@ -279,20 +281,23 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnParams p) {
   uint8_t* ring = smem + ROWS * D * 2;   // [4 warps][NSTAGE][K page, V page]
 
   __shared__ int s_last;
-  pdl_wait();
-  pdl_launch_dependents();
+  pdl_launch_early();
+  trace_mark(kTraceAttnDecode, kTraceStart);
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, tig = lane & 3;
   const int group = p.n_q_heads / p.n_kv_heads;
   const int rows = p.t_count * group;
+  const int* bt = p.block_table + static_cast<size_t>(b) * p.max_pages;
+  pdl_wait();
+  trace_mark(kTraceAttnDecode, kTraceAfterWait);
+  pdl_launch_dependents();
   const int kv_len = p.seq_lens[b];
   const int npages = (kv_len + kPage - 1) / kPage;
   int pps = (npages + p.splits - 1) / p.splits;
   pps = (pps + 3) & ~3;
   const int page0 = split * pps;
   const int page1 = min(npages, page0 + pps);
-  const int* bt = p.block_table + static_cast<size_t>(b) * p.max_pages;
 
   for (int i = threadIdx.x; i < ROWS * CH; i += 128) {
     const int r = i / CH, c = i % CH;
@@ -533,6 +538,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnParams p) {
       }
     }
   }
+  trace_mark(kTraceAttnDecode, kTraceEnd);
 }
 
 template <int D>
@@ -551,6 +557,8 @@ static size_t decode_smem() {
 using namespace eredu;
 
 // Bytes of fp32 scratch (part_o, part_ml) a decode launch with `splits` > 1 needs.
+EREDU_TRACE_INSTALLER(attention)
+
 extern "C" void eredu_attn_decode_scratch_elems(int batch, int q_per_seq, int n_q_heads, int head_dim, int splits,
                                                 long long* part_o_elems, long long* part_ml_elems) {
   const long long rows = static_cast<long long>(batch) * q_per_seq * n_q_heads;

@@ -19,6 +19,7 @@
 #include "../common/launch_count.h"
 #include "../common/ptx.cuh"
 #include "../common/tma_host.h"
+#include "../common/trace.cuh"
 
 namespace eredu {
 
@@ -55,6 +56,8 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)
 template <bool DUAL>
 __global__ void __launch_bounds__(192, 1)
 gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, PGemmParams p) {
+  pdl_launch_early();
+  trace_mark(kTraceGemmPersistent, kTraceStart);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem);   // [kStages]  TMA -> MMA
@@ -97,6 +100,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_con
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   pdl_wait();
+  trace_mark(kTraceGemmPersistent, kTraceAfterWait);
   pdl_launch_dependents();
 
   if (warp == 0) {
@@ -277,6 +281,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_con
     __syncwarp();
     tmem_dealloc(tmem_base, 512);
   }
+  trace_mark(kTraceGemmPersistent, kTraceEnd);
 }
 
 }  // namespace
@@ -332,3 +337,5 @@ int launch_gemm_persistent(const void* X, const void* W, void* Y, const void* re
 }
 
 }  // namespace eredu
+
+EREDU_TRACE_INSTALLER(gemm_persistent)

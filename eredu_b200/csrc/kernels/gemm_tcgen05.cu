@@ -25,6 +25,7 @@
 #include "../common/peer.cuh"
 #include "../common/ptx.cuh"
 #include "../common/tma_host.h"
+#include "../common/trace.cuh"
 #include "gemm_persistent.h"
 
 namespace cg = cooperative_groups;
@@ -57,6 +58,10 @@ struct GemmParams {
   // Large token tiles: the epilogue goes through shared memory so that the output (and the residual) move as
   // 16-byte row chunks instead of one 2-byte element per thread. Needs 16-byte aligned rows (host-checked).
   int staged;
+  // Weights that no kernel of the stream rewrites (every model weight): their first tiles are fetched, and the
+  // rest prefetched into L2, BEFORE the kernel waits for its producer under programmatic dependent launch, so
+  // the weight stream of this kernel overlaps the tail of the previous one.
+  int w_static;
   PeerComm comm;   // COMM modes only
 };
 
@@ -90,8 +95,14 @@ struct GemmCfg {
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
 
 // Applies row scale, bias, activation and residual, stores, and returns the value as stored (after rounding).
+__device__ __forceinline__ float residual_at(const GemmParams& p, int m, int n) {
+  return __bfloat162float(static_cast<const __nv_bfloat16*>(p.residual)[static_cast<size_t>(m) * p.ldr + n]);
+}
+
+// `rv`: the residual value of the element (0 when there is none), loaded by the caller ahead of time so that
+// the load does not sit between two dependent stores.
 template <bool DUAL>
-__device__ __forceinline__ float epilogue_store(const GemmParams& p, float g, float u, int m, int n, float scale) {
+__device__ __forceinline__ float epilogue_store(const GemmParams& p, float g, float u, int m, int n, float scale, float rv) {
   g *= scale;
   if (DUAL) u *= scale;
   if (p.bias != nullptr) {
@@ -99,10 +110,7 @@ __device__ __forceinline__ float epilogue_store(const GemmParams& p, float g, fl
     g += __bfloat162float(b[n]);
     if (DUAL) u += __bfloat162float(b[p.N + n]);
   }
-  float v = DUAL ? silu_f(g) * u : g;
-  if (p.residual != nullptr) {
-    v += __bfloat162float(static_cast<const __nv_bfloat16*>(p.residual)[static_cast<size_t>(m) * p.ldr + n]);
-  }
+  float v = (DUAL ? silu_f(g) * u : g) + rv;
   if (p.out_fp32) {
     static_cast<float*>(p.y)[static_cast<size_t>(m) * p.ldy + n] = v;
     return v;
@@ -130,6 +138,8 @@ template <int TN, bool DUAL, bool SPLIT, int COMM>
 __global__ void __launch_bounds__(192, 1)
 gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, GemmParams p) {
   using Cfg = GemmCfg<TN, DUAL>;
+  pdl_launch_early();
+  trace_mark(kTraceGemm, kTraceStart);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem);            // [kStages]
@@ -181,8 +191,29 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  // Everything above touched only this CTA's own resources; wait for the producer kernels here.
+  // Weight tiles do not depend on the producer kernels: start them before the wait.
+  int n_pre = 0;
+  if (p.w_static && p.work == nullptr) {
+    n_pre = min(niter, Cfg::kStages);
+    if (warp == 0 && lane == 0) {
+      const uint64_t pol_w = l2_policy_evict_first();
+      for (int it = 0; it < niter; ++it) {
+        const int kx = (kb0 + it) * 64;
+        if (it < n_pre) {
+          uint8_t* a = stages + it * Cfg::kStageBytes;
+          mbar_arrive_expect_tx(&full_bar[it], Cfg::kStageBytes);
+          tma_load_2d_hint(a, &tmW, kx, w_row0, &full_bar[it], pol_w);
+          if (DUAL) tma_load_2d_hint(a + Cfg::kATile, &tmW, kx, p.dual_row_offset + w_row0, &full_bar[it], pol_w);
+        } else if (p.w_static > 1) {
+          tma_prefetch_l2_2d(&tmW, kx, w_row0);
+          if (DUAL) tma_prefetch_l2_2d(&tmW, kx, p.dual_row_offset + w_row0);
+        }
+      }
+    }
+  }
+  // Everything above touched only this CTA's own resources and constant weights; wait for the producer kernels here.
   pdl_wait();
+  trace_mark(kTraceGemm, kTraceAfterWait);
   pdl_launch_dependents();
   unsigned int seq = 0;
   if (COMM != COMM_NONE) seq = *p.comm.seq;
@@ -193,18 +224,20 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     if (lane == 0) {
       const uint64_t pol_w = l2_policy_evict_first();
       const uint64_t pol_x = l2_policy_evict_last();
-      int issued = 0;
+      int issued = n_pre;
       bool ok = true;
       for (int it = 0; it < niter && ok; ++it) {
         const int s = it % Cfg::kStages;
         const uint32_t ph = (it / Cfg::kStages) & 1;
-        ok = mbar_wait(&empty_bar[s], ph ^ 1, p.status, kStatusSmemEmptyTimeout);
-        if (!ok) break;
         uint8_t* a = stages + s * Cfg::kStageBytes;
         const int kx = (kb0 + it) * 64;
-        mbar_arrive_expect_tx(&full_bar[s], Cfg::kStageBytes);
-        tma_load_2d_hint(a, &tmW, kx, w_row0, &full_bar[s], pol_w);
-        if (DUAL) tma_load_2d_hint(a + Cfg::kATile, &tmW, kx, p.dual_row_offset + w_row0, &full_bar[s], pol_w);
+        if (it >= n_pre) {  // the first n_pre stages already hold (or are receiving) their weight tiles
+          ok = mbar_wait(&empty_bar[s], ph ^ 1, p.status, kStatusSmemEmptyTimeout);
+          if (!ok) break;
+          mbar_arrive_expect_tx(&full_bar[s], Cfg::kStageBytes);
+          tma_load_2d_hint(a, &tmW, kx, w_row0, &full_bar[s], pol_w);
+          if (DUAL) tma_load_2d_hint(a + Cfg::kATile, &tmW, kx, p.dual_row_offset + w_row0, &full_bar[s], pol_w);
+        }
         tma_load_2d_hint(a + Cfg::kATile * (DUAL ? 2 : 1), &tmX, kx, m_base, &full_bar[s], pol_x);
         issued = it + 1;
       }
@@ -226,6 +259,8 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         const uint32_t ph = (it / Cfg::kStages) & 1;
         ok = mbar_wait(&full_bar[s], ph, p.status, kStatusTmaFullTimeout);
         if (!ok) break;
+        if (it == 0) trace_mark_thread(kTraceGemm, 3, 32);       // first operands landed
+        if (it == niter - 1) trace_mark_thread(kTraceGemm, 4, 32);  // last operands landed
         tc_fence_after_sync();
         const uint32_t a_addr = smem_u32(stages + s * Cfg::kStageBytes);
         const uint64_t da = umma_desc_k_sw128(a_addr);
@@ -256,16 +291,25 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   const int et = threadIdx.x - 64;  // epilogue thread index 0..127 (warps 2..5)
   const bool in_n = n < p.N;
   constexpr bool kCanStage = (TN >= 64) && !SPLIT && COMM == COMM_NONE;
+  // Columns (tokens) of the tile whose final value this CTA produces: all of them, or with cluster split-K
+  // every nsplit-th one (COMM_AR: every nsplit-th PAIR of columns, because partials travel as bf16x2).
+  const int m_end = min(TN, m_limit - m_base);
+  const int own_first = SPLIT ? split : 0, own_step = SPLIT ? nsplit : 1;
+  constexpr int kPre = 8;
+  float rpre[2 * kPre];
+#pragma unroll
+  for (int j = 0; j < 2 * kPre; ++j) rpre[j] = 0.f;
+  const bool has_res = p.residual != nullptr && in_n;
 
   // Final value of element (column c of the tile, this thread's row): store it (or hand it to the
   // collective) and add its square to the per-column sum kept for a following RMSNorm. Executed by whole warps.
-  auto finish = [&](float g, float u, int c, bool valid) {
+  auto finish = [&](float g, float u, int c, bool valid, float rv) {
     const int m = m_base + c;
     const bool ok = valid && in_n && m < m_limit;
     float v = 0.f;
     if (ok) {
       const float sc = (p.ssq_in != nullptr) ? s_scale[c] : 1.f;
-      if (COMM == COMM_NONE) v = epilogue_store<DUAL>(p, g, u, m, n, sc);
+      if (COMM == COMM_NONE) v = epilogue_store<DUAL>(p, g, u, m, n, sc, rv);
       else comm_emit<COMM>(p, parity, g, m, n, sc);
     }
     if (COMM == COMM_NONE && p.ssq_out != nullptr) {
@@ -297,8 +341,24 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       }
       epi_barrier();
     }
+    // Residual values of the first kPre columns (COMM_AR: column pairs) this thread will finish: the loads are
+    // in flight while the tensor cores work, instead of one dependent load per finished column.
+    if (has_res) {
+#pragma unroll
+      for (int j = 0; j < kPre; ++j) {
+        if (COMM == COMM_AR) {
+          const int c = 2 * (own_first + j * own_step);
+          if (c < m_end) rpre[2 * j] = residual_at(p, m_base + c, n);
+          if (c + 1 < m_end) rpre[2 * j + 1] = residual_at(p, m_base + c + 1, n);
+        } else if (SPLIT) {
+          const int c = own_first + j * own_step;
+          if (c < m_end) rpre[j] = residual_at(p, m_base + c, n);
+        }
+      }
+    }
     acc_ok = (niter > 0) && mbar_wait(accum_bar, 0, p.status, kStatusAccumTimeout);
     acc_ok = __all_sync(0xffffffffu, acc_ok);
+    trace_mark_thread(kTraceGemm, 5, 64);  // accumulator complete
     tc_fence_after_sync();
     if (acc_ok) {
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
@@ -330,8 +390,11 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             red[(c0 + j) * 128 + row] = DUAL ? silu_f(gg) * (__uint_as_float(u[j]) * sc + bu) : gg;
           }
         } else {
+          float rr[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) finish(__uint_as_float(g[j]), DUAL ? __uint_as_float(u[j]) : 0.f, c0 + j, true);
+          for (int j = 0; j < 16; ++j) rr[j] = (has_res && c0 + j < m_end) ? residual_at(p, m_base + c0 + j, n) : 0.f;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) finish(__uint_as_float(g[j]), DUAL ? __uint_as_float(u[j]) : 0.f, c0 + j, true, rr[j]);
         }
       }
     }
@@ -387,13 +450,12 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     }
   }
 
-  // Columns (tokens) of the tile whose final value this CTA produces: all of them, or with cluster split-K
-  // every nsplit-th one (COMM_AR: every nsplit-th PAIR of columns, because partials travel as bf16x2).
-  const int m_end = min(TN, m_limit - m_base);
   if (SPLIT) {
     // Every thread of every CTA of the cluster reaches both barriers, whatever happened above.
     cg::cluster_group cluster = cg::this_cluster();
+    trace_mark_thread(kTraceGemm, 6, 64);  // partials staged
     cluster.sync();
+    trace_mark_thread(kTraceGemm, 7, 64);  // cluster barrier 1 passed
   }
   if (COMM == COMM_AR) {
     // ---- all-reduce, "LL" style: every partial pair is one 8-byte word {bf16x2 value, sequence tag} stored
@@ -406,10 +468,17 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       for (int pi = p_first; 2 * pi < m_end; pi += p_step) {
         float g0 = 0.f, g1 = 0.f;
         if (SPLIT) {
-          for (int r = 0; r < nsplit; ++r) {
-            const float* peer = cluster.map_shared_rank(red, r);
-            g0 += peer[(2 * pi) * 128 + row];
-            g1 += peer[(2 * pi + 1) * 128 + row];
+          float a0[8], a1[8];
+#pragma unroll
+          for (int r = 0; r < 8; ++r) {
+            const float* peer = cluster.map_shared_rank(red, r < nsplit ? r : 0);
+            a0[r] = (r < nsplit) ? peer[(2 * pi) * 128 + row] : 0.f;
+            a1[r] = (r < nsplit) ? peer[(2 * pi + 1) * 128 + row] : 0.f;
+          }
+#pragma unroll
+          for (int r = 0; r < 8; ++r) {
+            g0 += a0[r];
+            g1 += a1[r];
           }
         } else {
           g0 = red[(2 * pi) * 128 + row];
@@ -429,29 +498,70 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   } else if (SPLIT) {
     if (warp >= 2) {
       cg::cluster_group cluster = cg::this_cluster();
-      for (int c = split; c < m_end; c += nsplit) {
-        float g = 0.f, u = 0.f;
-        for (int r = 0; r < nsplit; ++r) {
-          const float* peer = cluster.map_shared_rank(red, r);
-          g += peer[c * 128 + row];
-          if (DUAL) u += peer[(TN + c) * 128 + row];
+      const float* peers[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) peers[r] = cluster.map_shared_rank(red, r < nsplit ? r : 0);
+      // all remote loads of a column are issued together; the sum runs in cluster-rank order (deterministic)
+      auto reduce_col = [&](int c, float& g, float& u) {
+        float pg[8], pu[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          pg[r] = (r < nsplit) ? peers[r][c * 128 + row] : 0.f;
+          if (DUAL) pu[r] = (r < nsplit) ? peers[r][(TN + c) * 128 + row] : 0.f;
         }
-        finish(g, u, c, true);
+        g = 0.f;
+        u = 0.f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          g += pg[r];
+          if (DUAL) u += pu[r];
+        }
+      };
+#pragma unroll
+      for (int j = 0; j < kPre; ++j) {
+        const int c = split + j * nsplit;
+        if (c < m_end) {  // warp-uniform
+          float g, u;
+          reduce_col(c, g, u);
+          finish(g, u, c, true, rpre[j]);
+        }
+      }
+      for (int c = split + kPre * nsplit; c < m_end; c += nsplit) {
+        float g, u;
+        reduce_col(c, g, u);
+        finish(g, u, c, true, has_res ? residual_at(p, m_base + c, n) : 0.f);
       }
       if (COMM == COMM_NONE) publish_ssq(split, nsplit);
     }
   }
   if (SPLIT) {
     cg::cluster_group cluster = cg::this_cluster();
+    trace_mark_thread(kTraceGemm, 8, 64);  // reduced and stored
     cluster.sync();
+    trace_mark_thread(kTraceGemm, 9, 64);  // cluster barrier 2 passed
   }
 
   if (COMM == COMM_AR) {
     if (warp >= 2) {
       const uint32_t tag = seq + 1u;
       const int p_first = SPLIT ? split : 0, p_step = SPLIT ? nsplit : 1;
-      for (int pi = p_first; 2 * pi < m_end; pi += p_step) {
+      int jj = 0;
+      for (int pi = p_first; 2 * pi < m_end; pi += p_step, ++jj) {
         float v0 = 0.f, v1 = 0.f;
+        // residual of this pair: prefetched for the first kPre pairs (select without dynamic register indexing)
+        float r0 = 0.f, r1 = 0.f;
+        if (jj < kPre) {
+#pragma unroll
+          for (int j = 0; j < kPre; ++j) {
+            if (j == jj) {
+              r0 = rpre[2 * j];
+              r1 = rpre[2 * j + 1];
+            }
+          }
+        } else if (has_res) {
+          r0 = residual_at(p, m_base + 2 * pi, n);
+          if (2 * pi + 1 < m_end) r1 = residual_at(p, m_base + 2 * pi + 1, n);
+        }
         if (in_n) {
           const size_t word = (static_cast<size_t>(m_base / 2 + pi) * p.N + n) * 8;
           uint32_t val[kMaxRanks];
@@ -484,8 +594,8 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
               v1 += bf16_hi(val[src]);
             }
           }
-          v0 = epilogue_store<false>(p, v0, 0.f, m_base + 2 * pi, n, 1.f);
-          v1 = (2 * pi + 1 < m_end) ? epilogue_store<false>(p, v1, 0.f, m_base + 2 * pi + 1, n, 1.f) : 0.f;
+          v0 = epilogue_store<false>(p, v0, 0.f, m_base + 2 * pi, n, 1.f, r0);
+          v1 = (2 * pi + 1 < m_end) ? epilogue_store<false>(p, v1, 0.f, m_base + 2 * pi + 1, n, 1.f, r1) : 0.f;
         }
         if (p.ssq_out != nullptr) {
           float s0 = in_n ? v0 * v0 : 0.f, s1 = in_n ? v1 * v1 : 0.f;
@@ -532,6 +642,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
   if (COMM != COMM_NONE && threadIdx.x == 0) finish_call(p.comm, seq, gridDim.x * gridDim.y * gridDim.z);
+  trace_mark(kTraceGemm, kTraceEnd);
 }
 
 template <int TN, bool DUAL, bool SPLIT, int COMM = COMM_NONE>
@@ -582,6 +693,8 @@ static cudaError_t launch_gemm_split(const CUtensorMap& tmW, const CUtensorMap& 
 
 using namespace eredu;
 
+EREDU_TRACE_INSTALLER(gemm)
+
 // EREDU_GEMM_PERSISTENT=0 keeps prefill-sized GEMMs on the one-tile-per-CTA kernel (for A/B measurements).
 static bool persistent_enabled() {
   static int v = -1;
@@ -590,6 +703,16 @@ static bool persistent_enabled() {
     v = (e != nullptr && e[0] == '0') ? 0 : 1;
   }
   return v == 1;
+}
+
+static int prefetch_level(long long weight_bytes) {
+  static int forced = -2;
+  if (forced == -2) {
+    const char* e = std::getenv("EREDU_GEMM_PREFETCH");
+    forced = (e != nullptr && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : -1;
+  }
+  if (forced >= 0) return forced;
+  return weight_bytes <= (16LL << 20) ? 2 : 1;
 }
 
 static bool staged_epilogue_ok(const void* Y, const void* residual, int N, int ldy, int ldr, int out_fp32) {
@@ -605,6 +728,8 @@ extern "C" int eredu_gemm_pick_split(int M, int N, int K, int sm_count) {
   const int tiles = ((N + 127) / 128) * ((M + tn - 1) / tn);
   const int kblocks = (K + 63) / 64;
   int s = 1;
+  // Split while the grid still fits two CTAs per SM: besides streaming the weights in parallel, a split CTA
+  // finishes only every s-th token column, and the serial per-column epilogue is what a small GEMM pays for.
   while (s < 8 && tiles * s * 2 <= 2 * sm_count && kblocks / (s * 2) >= 2) s *= 2;
   return s;
 }
@@ -619,7 +744,7 @@ extern "C" int eredu_gemm_bf16(const void* X, const void* W, void* Y, const void
                                int N, int K, int ldx, int ldw, int ldy, int ldr, int w_rows, int dual,
                                int dual_row_offset, int out_fp32, int force_split, int sm_count, int* status,
                                const float* ssq_in, int ssq_parts, float norm_eps, int norm_dim, float* ssq_out,
-                               cudaStream_t stream) {
+                               int flags, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   const int tn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
   if (tn == 256 && !out_fp32 && force_split <= 1 && persistent_enabled()) {
@@ -654,6 +779,10 @@ extern "C" int eredu_gemm_bf16(const void* X, const void* W, void* Y, const void
   p.work = nullptr;
   p.w_rows_per_expert = 0;
   p.staged = 0;
+  // flag bit 0: W was produced by a preceding kernel of the stream (no early fetch at all). Otherwise the ring's
+  // first stages are fetched before the dependency wait (level 1), and for matrices that fit L2 many times over
+  // the remaining tiles are prefetched into L2 as well (level 2). EREDU_GEMM_PREFETCH overrides the level.
+  p.w_static = (flags & 1) ? 0 : prefetch_level(static_cast<long long>(w_rows) * K * 2);
   const int n_tiles = (N + 127) / 128;
   const int m_tiles = (M + tn - 1) / tn;
   int nsplit = force_split > 0 ? force_split : eredu_gemm_pick_split(M, N, K, sm_count > 0 ? sm_count : 148);
@@ -730,6 +859,7 @@ extern "C" int eredu_gemm_bf16_comm(const void* X, const void* W, void* Y, const
   p.work = nullptr;
   p.w_rows_per_expert = 0;
   p.staged = 0;
+  p.w_static = prefetch_level(static_cast<long long>(w_rows) * K * 2);
   p.comm = *pc;
   const int n_tiles = (N + 127) / 128;
   const int m_tiles = 1;

@@ -22,6 +22,7 @@ enum { SCORE_SOFTMAX = 0, SCORE_SIGMOID = 1, SCORE_SQRT_SOFTPLUS = 2, SCORE_TOPK
 __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ sel_bias,
                                                          int* __restrict__ ids, float* __restrict__ weights, int T, int E,
                                                          int k, int scoring, int renorm, float scale) {
+  pdl_launch_early();
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
@@ -130,6 +131,7 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ 
   __shared__ int start[513];
   __shared__ int cursor[512];
   __shared__ int item0[513];
+  pdl_launch_early();
   pdl_wait();
   pdl_launch_dependents();
   const int n_local = e1 - e0;
@@ -181,6 +183,7 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ 
 // xp[pos, :] = x[row_token[pos], :] for pos < counts[0]. grid = rows_cap CTAs.
 __global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ row_token,
                                   const int* __restrict__ counts, __nv_bfloat16* __restrict__ xp, int H) {
+  pdl_launch_early();
   pdl_wait();
   pdl_launch_dependents();
   const int pos = blockIdx.x;
@@ -195,6 +198,7 @@ __global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ x, const int
 __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ route_pos,
                                    const float* __restrict__ weights, const __nv_bfloat16* __restrict__ residual,
                                    const __nv_bfloat16* __restrict__ extra, __nv_bfloat16* __restrict__ out, int k, int H) {
+  pdl_launch_early();
   pdl_wait();
   pdl_launch_dependents();
   const size_t t = blockIdx.x;
@@ -247,6 +251,7 @@ __global__ void __launch_bounds__(128) moe_combine_ar_kernel(const __nv_bfloat16
                                                               const __nv_bfloat16* __restrict__ extra,
                                                               __nv_bfloat16* __restrict__ out, int k, int H, PeerComm comm,
                                                               int* status) {
+  pdl_launch_early();
   pdl_wait();
   pdl_launch_dependents();
   const unsigned int seq = *reinterpret_cast<volatile unsigned int*>(comm.seq);

@@ -8,6 +8,7 @@
 #include "../common/launch.h"
 #include "../common/launch_count.h"
 #include "../common/ptx.cuh"
+#include "../common/trace.cuh"
 
 namespace eredu {
 
@@ -25,7 +26,10 @@ __global__ void __launch_bounds__(THREADS) rmsnorm_kernel(const __nv_bfloat16* _
                                                            __nv_bfloat16* __restrict__ h_out, int H, float eps,
                                                            float w_off) {
   __shared__ float red[32];
+  pdl_launch_early();
+  trace_mark(kTraceRmsNorm, kTraceStart);
   pdl_wait();
+  trace_mark(kTraceRmsNorm, kTraceAfterWait);
   pdl_launch_dependents();
   const size_t row = blockIdx.x;
   const int nch = H >> 3;
@@ -112,7 +116,10 @@ struct RopeParams {
 // grid (M, n_q + 2 n_kv), D/2 threads: thread i owns one rotation pair (or a pass-through pair).
 __global__ void rope_kv_kernel(RopeParams p) {
   __shared__ float red[8];
+  pdl_launch_early();
+  trace_mark(kTraceRope, kTraceStart);
   pdl_wait();
+  trace_mark(kTraceRope, kTraceAfterWait);
   pdl_launch_dependents();
   const int m = blockIdx.x, head = blockIdx.y;
   const int i = threadIdx.x;
@@ -178,7 +185,10 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const __nv_bfloat1
                                  __nv_bfloat16* __restrict__ out, int H, int vocab_start, int rows, float scale,
                                  float* __restrict__ ssq_out) {
   __shared__ float red[8];
+  pdl_launch_early();
+  trace_mark(kTraceEmbedding, kTraceStart);
   pdl_wait();
+  trace_mark(kTraceEmbedding, kTraceAfterWait);
   pdl_launch_dependents();
   const size_t m = blockIdx.x;
   const int id = ids[m] - vocab_start;
@@ -214,7 +224,10 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const __nv_bfloat1
 // y[m, i] = silu(x[m, i]) * x[m, I + i], optional clamp of both branches (swiglu_limit).
 __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, int I, int ldx,
                                 float limit) {
+  pdl_launch_early();
+  trace_mark(kTraceSiluMul, kTraceStart);
   pdl_wait();
+  trace_mark(kTraceSiluMul, kTraceAfterWait);
   pdl_launch_dependents();
   const size_t m = blockIdx.y;
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -246,7 +259,10 @@ __global__ void decode_advance_kernel(const int* __restrict__ sampled, int* __re
                                       long long* __restrict__ slots, const int* __restrict__ block_table,
                                       int max_pages, const int* __restrict__ active, int* __restrict__ sampler_rows,
                                       int row_ints, int* __restrict__ history, int hist_stride, int B) {
+  pdl_launch_early();
+  trace_mark(kTraceAdvance, kTraceStart);
   pdl_wait();
+  trace_mark(kTraceAdvance, kTraceAfterWait);
   pdl_launch_dependents();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= B) return;
@@ -277,6 +293,8 @@ __global__ void decode_advance_kernel(const int* __restrict__ sampled, int* __re
 }  // namespace eredu
 
 using namespace eredu;
+
+EREDU_TRACE_INSTALLER(norm_rope)
 
 extern "C" int eredu_rmsnorm(const void* x, const void* residual, const float* w, void* y, void* h_out, int M, int H,
                              float eps, float w_off, cudaStream_t stream) {

@@ -199,6 +199,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_early();
   pdl_wait();
   pdl_launch_dependents();
 
@@ -380,6 +381,7 @@ static cudaError_t dispatch_q(int tn, const CUtensorMap& tmQ, const CUtensorMap&
 template <int FMT>
 __global__ void __launch_bounds__(256) dequant_matrix_kernel(const uint8_t* __restrict__ wq, QGemmParams p,
                                                              __nv_bfloat16* __restrict__ out) {
+  pdl_launch_early();
   pdl_wait();
   pdl_launch_dependents();
   const int kb = blockIdx.x, r = threadIdx.x >> 1, half = threadIdx.x & 1;

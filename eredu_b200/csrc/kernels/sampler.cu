@@ -19,6 +19,7 @@
 #include "../common/launch.h"
 #include "../common/launch_count.h"
 #include "../common/ptx.cuh"
+#include "../common/trace.cuh"
 
 namespace eredu {
 
@@ -189,7 +190,10 @@ __global__ void __launch_bounds__(kSampThreads) sampler_kernel(SamplerParams p) 
   __shared__ int sh_krem;
   __shared__ int sh_pick;
 
+  pdl_launch_early();
+  trace_mark(kTraceSampler, kTraceStart);
   pdl_wait();
+  trace_mark(kTraceSampler, kTraceAfterWait);
   pdl_launch_dependents();
   const int r = blockIdx.x;
   const int tid = threadIdx.x;
@@ -417,7 +421,10 @@ struct VerifyParams {
 __global__ void __launch_bounds__(kSampThreads) spec_verify_kernel(VerifyParams p) {
   __shared__ BlockScratch scr;
   __shared__ int sh_pick;
+  pdl_launch_early();
+  trace_mark(kTraceSampler, kTraceStart);
   pdl_wait();
+  trace_mark(kTraceSampler, kTraceAfterWait);
   pdl_launch_dependents();
   const int b = blockIdx.x, tid = threadIdx.x;
   SamplerRow cfg;
@@ -515,6 +522,8 @@ __global__ void __launch_bounds__(kSampThreads) spec_verify_kernel(VerifyParams 
 }  // namespace eredu
 
 using namespace eredu;
+
+EREDU_TRACE_INSTALLER(sampler)
 
 extern "C" int eredu_sampler_row_bytes() { return static_cast<int>(sizeof(SamplerRow)); }
 

@@ -50,12 +50,14 @@ def _norm_args(x, row_ssq, norm_eps, want_ssq, n_out):
 
 
 def linear(x, w, bias=None, residual=None, out_dtype=None, out=None, force_split=0, row_ssq=None, norm_eps=0.0,
-           want_ssq=False):
+           want_ssq=False, dynamic_weight=False):
     """y = x @ w.T (+ bias) (+ residual). x: [M, K], w: [N, K].
 
     ``row_ssq`` ([M, parts] fp32 partial sums of squares of x's rows): the output rows are scaled by
     ``rsqrt(sum(row_ssq) / K + norm_eps)`` - an RMSNorm whose weight vector was folded into ``w``.
-    ``want_ssq``: also return per-128-column-tile sums of squares of the stored output ([M, ceil(N/128)])."""
+    ``want_ssq``: also return per-128-column-tile sums of squares of the stored output ([M, ceil(N/128)]).
+    ``dynamic_weight``: ``w`` was written by a kernel enqueued just before this call (e.g. a dequantised scratch
+    matrix); the kernel then does not fetch weight tiles ahead of its stream dependency."""
     if not x.is_cuda:
         if row_ssq is not None:
             x = x.float() * torch.rsqrt(row_ssq.sum(-1, keepdim=True) / x.shape[1] + norm_eps)
@@ -76,7 +78,7 @@ def linear(x, w, bias=None, residual=None, out_dtype=None, out=None, force_split
         ptr(x), ptr(w), ptr(out), ptr(residual), ptr(bias), M, N, K, x.stride(0), w.stride(0), out.stride(0),
         residual.stride(0) if residual is not None else 0, w.shape[0], 0, 0, 1 if out_dtype == torch.float32 else 0,
         force_split, _sm_count(x.device), ptr(status_word(x.device)), ptr(ssq_in), parts, eps, dim, ptr(ssq_out),
-        stream_ptr(x.device))
+        1 if dynamic_weight else 0, stream_ptr(x.device))
     check(code, "eredu_gemm_bf16")
     return (out, ssq_out) if want_ssq else out
 
@@ -97,7 +99,7 @@ def gated_linear(x, w_gate_up, inter, bias=None, out=None, force_split=0, row_ss
     code = lib().eredu_gemm_bf16(
         ptr(x), ptr(w_gate_up), ptr(out), None, ptr(bias), M, inter, K, x.stride(0), w_gate_up.stride(0),
         out.stride(0), 0, w_gate_up.shape[0], 1, inter, 0, force_split, _sm_count(x.device),
-        ptr(status_word(x.device)), ptr(ssq_in), parts, eps, dim, None, stream_ptr(x.device))
+        ptr(status_word(x.device)), ptr(ssq_in), parts, eps, dim, None, 0, stream_ptr(x.device))
     check(code, "eredu_gemm_bf16(dual)")
     return out
 
@@ -235,7 +237,8 @@ def attention_prefill(q, k_cache, v_cache, block_table, seq_lens, cu_q, max_q_le
 
 
 def decode_splits(batch, n_kv, max_kv_len, sm_count=148):
-    """Split-KV factor: enough CTAs to fill the GPU, at least 4 pages (64 tokens) per split."""
+    """Split-KV factor: enough CTAs to fill the GPU once (a second wave costs more than it returns: the CTAs of the
+    following kernel are already resident under programmatic dependent launch), at least 8 pages per split."""
     ctas = max(1, batch * n_kv)
     pages = max(1, (max_kv_len + PAGE - 1) // PAGE)
     want = max(1, sm_count // ctas)

@@ -19,7 +19,7 @@ P, I, F, L = c_void_p, c_int, c_float, c_longlong
 _SIGNATURES = {
     # name: (restype, [argtypes])
     "eredu_gemm_pick_split": (I, [I, I, I, I]),
-    "eredu_gemm_bf16": (I, [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, I, P, P, I, F, I, P, P]),
+    "eredu_gemm_bf16": (I, [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, I, P, P, I, F, I, P, I, P]),
     "eredu_attn_prefill": (I, [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P]),
     "eredu_attn_decode": (I, [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P]),
     "eredu_attn_decode_scratch_elems": (None, [I, I, I, I, I, POINTER(L), POINTER(L)]),

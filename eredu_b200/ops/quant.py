@@ -189,7 +189,7 @@ class QuantLinear:
             w = torch.empty((N, K), dtype=torch.bfloat16, device=dev)
             check(lib().eredu_dequant_affine(ptr(self.wq), ptr(self.scales_t), ptr(self.biases_t), ptr(w), N, K,
                                              self.kbits, self.group, stream_ptr(dev)), "eredu_dequant_affine")
-            return linear(x, w, bias=bias, residual=residual, out_dtype=out_dtype, out=out)
+            return linear(x, w, bias=bias, residual=residual, out_dtype=out_dtype, out=out, dynamic_weight=True)
         if out is None:
             out = torch.empty((M, N), dtype=out_dtype, device=dev)
         code = lib().eredu_qgemm(ptr(x), ptr(self.wq), ptr(self.scales_t), ptr(self.biases_t), ptr(out), ptr(residual),
