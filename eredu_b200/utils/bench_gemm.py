@@ -1,0 +1,102 @@
+"""GEMM micro-benchmarks on one GPU (CUDA events, warm-up, numerics checked against an fp32 product).
+
+    python -m eredu_b200.utils.bench_gemm prefill     # prefill-sized shapes against cuBLAS (torch.matmul / addmm)
+    python -m eredu_b200.utils.bench_gemm chain       # decode-sized GEMMs as a dependent chain inside a CUDA graph
+
+``prefill`` covers the dense projections of a Llama-3-8B layer at 2048 and 8192 tokens (and their TP=8 slices):
+plain, + residual, and fused SwiGLU (cuBLAS arm: one GEMM plus ``silu(g) * u`` as PyTorch element-wise ops).
+``chain`` shows what one decode-step GEMM costs when it depends on the previous kernel, with and without the
+residual, the sum-of-squares output and cluster split-K.
+"""
+from __future__ import annotations
+
+import json
+import sys
+
+import torch
+
+from .. import ops
+
+DEV = torch.device("cuda:0")
+
+
+def _time(fn, n=10, warm=3):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / n * 1e3
+
+
+def prefill():
+    g = torch.Generator(device=DEV).manual_seed(0)
+    shapes = [(8192, 6144, 4096, 0), (8192, 4096, 4096, 1), (8192, 14336, 4096, 2), (8192, 4096, 14336, 1),
+              (8192, 4096, 512, 1), (8192, 4096, 1792, 1), (2048, 4096, 4096, 1), (2048, 14336, 4096, 2),
+              (2048, 4096, 14336, 1), (128, 4096, 4096, 1), (64, 4096, 4096, 1)]
+    for M, N, K, kind in shapes:
+        x = (torch.randn(M, K, device=DEV, generator=g) * 0.5).bfloat16()
+        w = (torch.randn(N * 2 if kind == 2 else N, K, device=DEV, generator=g) * 0.03).bfloat16()
+        r = torch.randn(M, N, device=DEV, generator=g).bfloat16() if kind == 1 else None
+        if kind == 2:
+            fn = lambda: ops.gated_linear(x, w, N)  # noqa: E731
+            gu = x.float() @ w.float().t()
+            ref = torch.nn.functional.silu(gu[:, :N]) * gu[:, N:]
+            lib = lambda: (lambda z: torch.nn.functional.silu(z[:, :N]) * z[:, N:])(x @ w.t())  # noqa: E731
+            flops = 2 * M * 2 * N * K
+        else:
+            fn = lambda: ops.linear(x, w, residual=r)  # noqa: E731
+            ref = x.float() @ w.float().t() + (r.float() if r is not None else 0)
+            lib = (lambda: torch.addmm(r, x, w.t())) if r is not None else (lambda: x @ w.t())  # noqa: E731
+            flops = 2 * M * N * K
+        err = float((fn().float() - ref).norm() / ref.norm())
+        us, us_lib = _time(fn), _time(lib)
+        print(json.dumps({"M": M, "N": N, "K": K, "epilogue": ["none", "residual", "swiglu"][kind], "us": round(us, 1),
+                          "tflops": round(flops / us / 1e6, 1), "cublas_us": round(us_lib, 1),
+                          "cublas_tflops": round(flops / us_lib / 1e6, 1), "rel_err": round(err, 5)}))
+
+
+def _chain(M, N, K, res, ssq, split, n=64, dual=False):
+    g = torch.Generator(device=DEV).manual_seed(0)
+    x = (torch.randn(M, K, device=DEV, generator=g) * 0.5).bfloat16()
+    ws = [(torch.randn(2 * N if dual else N, K, device=DEV, generator=g) * 0.02).bfloat16() for _ in range(8)]
+    y = torch.zeros(M, N, device=DEV, dtype=torch.bfloat16)
+
+    def run():
+        cur = y
+        for i in range(n):
+            if dual:
+                cur = ops.gated_linear(x, ws[i % 8], N, force_split=split)
+            elif ssq:
+                cur, _ = ops.linear(x, ws[i % 8], residual=cur if res else None, force_split=split, want_ssq=True)
+            else:
+                cur = ops.linear(x, ws[i % 8], residual=cur if res else None, force_split=split)
+        return cur
+
+    run()
+    torch.cuda.synchronize()
+    graph, stream = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        run()
+        with torch.cuda.graph(graph, stream=stream):
+            run()
+    torch.cuda.synchronize()
+    return _time(graph.replay) / n
+
+
+def chain():
+    for M, N, K in [(32, 4096, 512), (32, 4096, 1792), (32, 768, 4096), (1, 4096, 512)]:
+        for res, ssq, split in [(0, 0, 1), (1, 0, 1), (1, 1, 1), (0, 0, 4), (1, 0, 4), (1, 1, 4), (1, 1, 8)]:
+            print(json.dumps({"M": M, "N": N, "K": K, "residual": res, "ssq_out": ssq, "split": split,
+                              "us_per_gemm": round(_chain(M, N, K, res, ssq, split), 2)}))
+    for split in (1, 4, 8):
+        print(json.dumps({"swiglu": 1, "M": 32, "N": 1792, "K": 4096, "split": split,
+                          "us_per_gemm": round(_chain(32, 1792, 4096, 0, 0, split, dual=True), 2)}))
+
+
+if __name__ == "__main__":
+    {"prefill": prefill, "chain": chain}[sys.argv[1] if len(sys.argv) > 1 else "prefill"]()
