@@ -105,6 +105,87 @@ __global__ void peer_barrier_kernel(PeerComm c, int* status) {
   if (threadIdx.x == 0) finish_call(c, seq, gridDim.x);
 }
 
+// One-shot all-reduce of a small [M, N] bf16 partial (decode steps: M * N * 4 bytes fit one staging slot). Every
+// thread pushes 8 values to every peer as four self-validating 8-byte words {bf16x2, sequence tag}, then collects
+// the same words of all ranks from its own slots and sums them in rank order (bitwise identical everywhere),
+// adds bias and residual once and stores: no flag, no fence, no barrier.
+__global__ void __launch_bounds__(128) allreduce_ll_kernel(PeerComm c, const __nv_bfloat16* __restrict__ partial, int ldp,
+                                                            const __nv_bfloat16* __restrict__ residual, int ldr,
+                                                            const __nv_bfloat16* __restrict__ bias,
+                                                            __nv_bfloat16* __restrict__ y, int ldy, int M, int N, int* status) {
+  const unsigned int seq = *reinterpret_cast<volatile unsigned int*>(c.seq);
+  const int parity = static_cast<int>(seq & 1u);
+  const uint32_t tag = seq + 1u;
+  const int chunks_per_row = N >> 3;
+  const int id = blockIdx.x * blockDim.x + threadIdx.x;
+  if (id < M * chunks_per_row) {
+    const int m = id / chunks_per_row, n0 = (id % chunks_per_row) * 8;
+    const uint4 pv = *reinterpret_cast<const uint4*>(partial + static_cast<size_t>(m) * ldp + n0);
+    const size_t word = static_cast<size_t>(id) * 32;  // four 8-byte words per thread
+    for (int peer = 0; peer < c.size; ++peer) {
+      uint8_t* dst = peer_slot(c, peer, parity, c.rank) + word;
+      asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(pv.x), "r"(tag), "r"(pv.y), "r"(tag) : "memory");
+      asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 16), "r"(pv.z), "r"(tag), "r"(pv.w), "r"(tag) : "memory");
+    }
+    uint4 rv = make_uint4(0u, 0u, 0u, 0u);
+    if (residual != nullptr) rv = *reinterpret_cast<const uint4*>(residual + static_cast<size_t>(m) * ldr + n0);
+    uint32_t val[kMaxRanks][4];
+    uint32_t missing = (1u << c.size) - 1u;
+    const long long t0 = clock64();
+    while (missing != 0u) {
+#pragma unroll
+      for (int src = 0; src < kMaxRanks; ++src) {
+        if (src < c.size && ((missing >> src) & 1u)) {
+          const uint8_t* from = peer_slot(c, c.rank, parity, src) + word;
+          uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+          asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "l"(from) : "memory");
+          asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "l"(from + 16) : "memory");
+          if (a1 == tag && a3 == tag && b1 == tag && b3 == tag) {
+            val[src][0] = a0;
+            val[src][1] = a2;
+            val[src][2] = b0;
+            val[src][3] = b2;
+            missing &= ~(1u << src);
+          }
+        }
+      }
+      if (missing != 0u && clock64() - t0 > kWaitCycleLimit) {
+        report_status(status, kStatusPeerFlagTimeout);
+        break;
+      }
+    }
+    float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int src = 0; src < kMaxRanks; ++src) {
+      if (src < c.size && !((missing >> src) & 1u)) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          sum[2 * j] += bf16_lo(val[src][j]);
+          sum[2 * j + 1] += bf16_hi(val[src][j]);
+        }
+      }
+    }
+    const uint32_t r[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      sum[2 * j] += bf16_lo(r[j]);
+      sum[2 * j + 1] += bf16_hi(r[j]);
+    }
+    if (bias != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sum[j] += __bfloat162float(bias[n0 + j]);
+    }
+    uint4 o;
+    o.x = pack_bf16x2(sum[0], sum[1]);
+    o.y = pack_bf16x2(sum[2], sum[3]);
+    o.z = pack_bf16x2(sum[4], sum[5]);
+    o.w = pack_bf16x2(sum[6], sum[7]);
+    *reinterpret_cast<uint4*>(y + static_cast<size_t>(m) * ldy + n0) = o;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) finish_call(c, seq, gridDim.x);
+}
+
 }  // namespace eredu
 
 using namespace eredu;
@@ -197,6 +278,21 @@ extern "C" int eredu_allgather(const void* comm, const void* src, long long byte
 extern "C" int eredu_peer_barrier(const void* comm, int* status, cudaStream_t stream) {
   const PeerComm* c = static_cast<const PeerComm*>(comm);
   peer_barrier_kernel<<<1, 32, 0, stream>>>(*c, status);
+  eredu_count_launches(1);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// One-shot ("LL") all-reduce of a local [M, N] bf16 partial, for M * N * 4 bytes <= one staging slot (decode and
+// verify steps). y = sum over ranks (+bias +residual). Returns -2 when the partial is too large (use the two-shot).
+extern "C" int eredu_allreduce_ll(const void* comm, const void* partial, int ldp, const void* residual, int ldr,
+                                  const void* bias, void* y, int ldy, int M, int N, int* status, cudaStream_t stream) {
+  const PeerComm* c = static_cast<const PeerComm*>(comm);
+  if (N % 8 != 0 || ldp % 8 != 0 || ldy % 8 != 0 || (residual != nullptr && ldr % 8 != 0)) return -1;
+  if (static_cast<long long>(M) * N * 4 > c->slot_bytes) return -2;
+  const int items = M * (N / 8);
+  allreduce_ll_kernel<<<(items + 127) / 128, 128, 0, stream>>>(
+      *c, static_cast<const __nv_bfloat16*>(partial), ldp, static_cast<const __nv_bfloat16*>(residual), ldr,
+      static_cast<const __nv_bfloat16*>(bias), static_cast<__nv_bfloat16*>(y), ldy, M, N, status);
   eredu_count_launches(1);
   return static_cast<int>(cudaGetLastError());
 }

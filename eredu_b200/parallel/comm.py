@@ -26,6 +26,7 @@ native.register("eredu_comm_buffer_bytes", L, [L, L])
 native.register("eredu_comm_out_offset", L, [P])
 native.register("eredu_comm_data_offset", L, [P, I, I])
 native.register("eredu_allreduce_twoshot", I, [P, L, P, P, P, I, I, I, I, P, P])
+native.register("eredu_allreduce_ll", I, [P, P, I, P, I, P, P, I, I, I, P, P])
 native.register("eredu_allgather", I, [P, P, L, I, P, P])
 native.register("eredu_peer_barrier", I, [P, P, P])
 native.register("eredu_gemm_bf16_comm", I, [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, I, I, P, P, I,

@@ -72,6 +72,14 @@ class PeerTPOps:
     def all_reduce(self, partial, residual=None, bias=None):
         """Sum a local bf16 partial over the group (used after quantised row-parallel GEMMs)."""
         M, N = partial.shape
+        if M * N * 4 <= self.pg.slot_bytes and partial.stride(1) == 1:
+            st = native.status_word(self.device)
+            y = torch.empty((M, N), dtype=torch.bfloat16, device=self.device)
+            code = self.lib.eredu_allreduce_ll(self.pg.comm, partial.data_ptr(), partial.stride(0), native.ptr(residual),
+                                               residual.stride(0) if residual is not None else 0, native.ptr(bias),
+                                               y.data_ptr(), y.stride(0), M, N, st.data_ptr(), native.stream_ptr(self.device))
+            native.check(code, "eredu_allreduce_ll")
+            return y
         self.pg.x_view((M, N), torch.bfloat16).copy_(partial)
         return self._twoshot(M, N, residual, bias)
 

@@ -103,6 +103,14 @@ def main():
                 lg = ops_.gathered_logits(Xh.to(dev), head[rank * vl:(rank + 1) * vl].contiguous().to(dev), V, rank * vl)
                 ref2 = Xh.float() @ head.float().t()
                 errs[f"ag{M}"] = float((lg.cpu() - ref2).norm() / ref2.norm())
+        # standalone all-reduce of a local partial (quantised row-parallel linears): one-shot for decode-sized
+        # inputs, two-shot above
+        for M in (1, 32, 64, 200):
+            full = torch.randn(world, M, H, generator=gen).bfloat16()
+            R = torch.randn(M, H, generator=gen).bfloat16()
+            y = ops_.all_reduce(full[rank].to(dev), residual=R.to(dev))
+            ref = full.float().sum(0) + R.float()
+            errs[f"allreduce{M}"] = float((y.float().cpu() - ref).norm() / ref.norm())
         native.check_status(dev)
         result["errs"] = errs
     elif "ep" in scenario:
@@ -127,7 +135,15 @@ def main():
         from eredu_b200.parallel import tp
 
         par = ParallelContext.from_env(ParallelTopology(tensor=world))
-        model = build_from_tensors(cfg, sd.__getitem__, sd.__contains__, dev, dtype, par)
+        quantizer = None
+        if "quant" in scenario:  # load-time 4-bit affine quantisation of every rank's slice
+            from types import SimpleNamespace
+
+            from eredu_b200.ops.quant import make_quantizer
+
+            quantizer = make_quantizer(None, SimpleNamespace(quantization=SimpleNamespace(bits=4, group_size=64, mode="affine"),
+                                                             native_gguf=False))
+        model = build_from_tensors(cfg, sd.__getitem__, sd.__contains__, dev, dtype, par, quantizer=quantizer)
         backend = "nccl" if "nccl" in scenario else "peer"
         tp.attach(model, par, max_tokens=256, backend=backend)
         eng = Engine(model, max_batch=4, max_seq_len=128)

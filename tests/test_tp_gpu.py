@@ -79,3 +79,27 @@ def test_expert_parallel_fused_combine_matches_single_gpu(world, tmp_path):
         assert _rel(lg, ref) <= 0.03
         assert r["logits"] == peer[0]["logits"] and r["tokens"] == peer[0]["tokens"]
     assert _rel(torch.tensor(nccl[0]["logits"]), ref) <= 0.03
+
+
+@pytest.mark.parametrize("world", [2])
+def test_quantised_tensor_parallel_matches_single_gpu(world, tmp_path):
+    """4-bit (group 64) weights quantised per rank slice: row-parallel partials summed by the one-shot all-reduce.
+    Column slices quantise exactly like the matching columns of the whole matrix (groups run along the input
+    axis and the slices are group aligned), so TP and single-GPU logits agree to bf16 summation order."""
+    from types import SimpleNamespace
+
+    from eredu_b200.ops.quant import make_quantizer
+
+    _need(world)
+    res = run_ranks("gpu_tp_quant_peer", world, tmp_path, extra_env={"NCCL_NVLS_ENABLE": "0"})
+    cfg = tiny_cfg(True)
+    sd = random_state(cfg, seed=0, std=0.05)
+    quantizer = make_quantizer(None, SimpleNamespace(quantization=SimpleNamespace(bits=4, group_size=64, mode="affine"),
+                                                     native_gguf=False))
+    model = build_from_tensors(cfg, sd.__getitem__, sd.__contains__, "cuda:0", torch.bfloat16, quantizer=quantizer)
+    eng = Engine(model, max_batch=4, max_seq_len=128)
+    probe = torch.randint(0, cfg.vocab_size, (100,), generator=torch.Generator().manual_seed(7)).tolist()
+    ref = torch.tensor(probe_logits(eng, model, probe))
+    for r in res:
+        lg = torch.tensor(r["logits"])
+        assert _rel(lg, ref) <= 0.03 and r["logits"] == res[0]["logits"]
