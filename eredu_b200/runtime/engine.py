@@ -124,11 +124,16 @@ class Engine:
 
     # ------------------------------------------------------------------------------------------ prefill
     @torch.no_grad()
-    def prefill(self, seqs: list[Sequence]) -> torch.Tensor:
-        """Run the prompts through the model (chunked), sample the first token of each. Returns [B] int32."""
+    def prefill(self, seqs: list[Sequence], limits: Optional[list[int]] = None) -> torch.Tensor:
+        """Run the prompts through the model (chunked), sample the first token of each. Returns [B] int32.
+        ``limits[i]`` caps the number of prompt tokens processed for sequence i in this call (chunked prefill driven
+        by a scheduler); the token sampled for a sequence whose prompt is not finished yet is meaningless."""
+        self._limits = {s.seq_id: int(n) for s, n in zip(seqs, limits)} if limits is not None else None
         groups, cur, cur_tokens = [], [], 0
         for s in seqs:
             n = len(s.prompt) - s.kv_len
+            if self._limits is not None:
+                n = min(n, self._limits[s.seq_id])
             if cur and cur_tokens + n > self.prefill_chunk:
                 groups.append(cur)
                 cur, cur_tokens = [], 0
@@ -137,8 +142,13 @@ class Engine:
         if cur:
             groups.append(cur)
         outs = []
-        for g in groups:
-            outs.append(self._prefill_group(g))
+        try:
+            for g in groups:
+                outs.append(self._prefill_group(g))
+        finally:
+            self._limits = None
+        if any(o is None for o in outs):
+            return None
         return torch.cat(outs)
 
     def _prefill_group(self, seqs):
@@ -146,6 +156,8 @@ class Engine:
         max_q = 0
         for s in seqs:
             new = s.prompt[s.kv_len:]
+            if getattr(self, "_limits", None) is not None:
+                new = new[:self._limits[s.seq_id]]
             n = len(new)
             p = np.arange(s.kv_len, s.kv_len + n)
             pages = np.asarray(s.pages, dtype=np.int64)
@@ -223,6 +235,102 @@ class Engine:
         for i, s in enumerate(seqs):
             s.slot = i
 
+    # ------------------------------------------------------------------------------------------ slot-based decode
+    def open_decode(self, penalties: bool = False, max_context: Optional[int] = None) -> None:
+        """Create a decode state with ``max_batch`` slots, all free. Sequences :meth:`join` and :meth:`leave`
+        between steps by small copies into the static device buffers, so a captured graph stays valid while the
+        batch membership changes (continuous batching)."""
+        B = self.max_batch
+        dev = self.device
+        rows = pack_rows([SamplingParams(temperature=0.0)] * B, [1] * B, hist_lens=[0] * B, stream_ids=[0] * B)
+        max_len = max_context or self.max_seq_len
+        splits = ops.decode_splits(B, self.model.n_kv_local, max_len, self.sm_count) if self.cuda else 1
+        st = {
+            "B": B, "seqs": [None] * B, "slotted": True,
+            "token_ids": torch.zeros(B, dtype=torch.int32, device=dev),
+            "positions": torch.zeros(B, dtype=torch.int32, device=dev),
+            "seq_lens": torch.ones(B, dtype=torch.int32, device=dev),
+            "slots": torch.full((B,), -1, dtype=torch.int64, device=dev),
+            "block_table": torch.zeros((B, self.max_pages), dtype=torch.int32, device=dev),
+            "active": torch.zeros(B, dtype=torch.int32, device=dev),
+            "rows": self._t(rows.view(np.uint8).reshape(B, ROW_DTYPE.itemsize), torch.uint8),
+            "history": torch.zeros((B, self.hist_cap), dtype=torch.int32, device=dev) if penalties else None,
+            "sampled": torch.zeros(B, dtype=torch.int32, device=dev),
+            "splits": splits, "all_greedy": True,
+            "scratch": ops.decode_scratch(B, 1, self.model.n_q_local, self.cfg.head_dim, splits, dev)
+            if (self.cuda and splits > 1) else None,
+            "graph": None, "graphs": {},
+            "host_tokens": torch.zeros(B, dtype=torch.int32).pin_memory() if self.cuda else None,
+            "host_in": torch.zeros(B, dtype=torch.int32).pin_memory() if self.cuda else None,
+        }
+        self._decode_state = st
+
+    def free_slots(self) -> list[int]:
+        return [i for i, s in enumerate(self._decode_state["seqs"]) if s is None]
+
+    def join(self, seq: Sequence, first_token: int) -> int:
+        """Put a prefilled sequence into a free slot; ``first_token`` is its next input token."""
+        st = self._decode_state
+        free = self.free_slots()
+        if not free:
+            raise RuntimeError("no free decode slot")
+        i = free[0]
+        pos = seq.kv_len
+        pages = np.asarray(seq.pages, dtype=np.int64)
+        bt = np.zeros(self.max_pages, dtype=np.int32)
+        bt[:len(seq.pages)] = seq.pages
+        row = pack_rows([seq.sampling], [pos + 1], hist_lens=[min(len(seq.output), self.hist_cap)], stream_ids=[seq.seq_id])
+        st["token_ids"][i] = int(first_token)
+        st["positions"][i] = pos
+        st["seq_lens"][i] = pos + 1
+        st["slots"][i] = int(pages[pos // PAGE] * PAGE + pos % PAGE)
+        st["block_table"][i].copy_(self._t(bt, torch.int32))
+        st["rows"][i].copy_(self._t(row.view(np.uint8).reshape(ROW_DTYPE.itemsize), torch.uint8))
+        st["active"][i] = 1
+        if st["history"] is not None:
+            h = np.zeros(self.hist_cap, dtype=np.int32)
+            tail = seq.output[-self.hist_cap:]
+            h[:len(tail)] = tail
+            st["history"][i].copy_(self._t(h, torch.int32))
+        needs_hist = (seq.sampling.repeat_penalty != 1.0 or seq.sampling.frequency_penalty != 0.0
+                      or seq.sampling.presence_penalty != 0.0)
+        if needs_hist and st["history"] is None:
+            raise RuntimeError("this decode state was opened without penalty history (open_decode(penalties=True))")
+        st["seqs"][i] = seq
+        seq.slot = i
+        self._refresh_mode(st)
+        return i
+
+    def leave(self, seq: Sequence) -> None:
+        st = self._decode_state
+        i = seq.slot
+        if i < 0 or st["seqs"][i] is not seq:
+            return
+        st["seqs"][i] = None
+        seq.slot = -1
+        st["active"][i] = 0
+        st["slots"][i] = -1
+        st["seq_lens"][i] = 1
+        st["positions"][i] = 0
+        st["block_table"][i].zero_()
+        self._refresh_mode(st)
+
+    def set_step_mask(self, stepping: list[bool]) -> None:
+        """Which occupied slots take part in the next step (a scheduler may hold a request back for one step)."""
+        st = self._decode_state
+        act = np.asarray([1 if (s is not None and not s.finished and on) else 0 for s, on in zip(st["seqs"], stepping)],
+                         dtype=np.int32)
+        if self.cuda:
+            st["active"].copy_(self._t(act, torch.int32))
+        else:
+            st["active"] = torch.as_tensor(act)
+
+    def _refresh_mode(self, st) -> None:
+        greedy = all(s is None or s.sampling.greedy for s in st["seqs"])
+        if greedy != st["all_greedy"]:
+            st["all_greedy"] = greedy
+            st["graph"] = st["graphs"].get(greedy)  # graphs are captured per sampler path
+
     def _decode_body(self, st):
         batch = ForwardBatch(token_ids=st["token_ids"], positions=st["positions"], slots=st["slots"],
                              block_table=st["block_table"], seq_lens=st["seq_lens"], is_prefill=False, q_per_seq=1,
@@ -273,6 +381,8 @@ class Engine:
                     self._decode_body(st)
                 # capture does not execute: state is still the pre-step state
                 st["graph"] = g
+                if "graphs" in st:
+                    st["graphs"][st["all_greedy"]] = g
             st["graph"].replay()
         else:
             self._decode_body(st)
@@ -283,7 +393,8 @@ class Engine:
         return st["host_tokens"]
 
     def _decode_step_cpu(self, st):
-        seqs = st["seqs"]
+        idle = Sequence(0, [0], SamplingParams(temperature=0.0))
+        seqs = [s if s is not None else idle for s in st["seqs"]]
         batch = ForwardBatch(token_ids=st["token_ids"], positions=st["positions"], slots=st["slots"],
                              block_table=st["block_table"], seq_lens=st["seq_lens"], is_prefill=False, q_per_seq=1)
         logits = self.model.forward(batch, self.kv)
@@ -309,8 +420,9 @@ class Engine:
         st = self._decode_state
         done = []
         changed = False
+        stepped = st.get("stepped")
         for i, s in enumerate(st["seqs"]):
-            if s.finished:
+            if s is None or s.finished or (stepped is not None and not stepped[i]):
                 done.append(False)
                 continue
             tok = int(tokens[i])
@@ -325,7 +437,7 @@ class Engine:
                 changed = True
             done.append(fin)
         if changed:
-            act = np.asarray([0 if s.finished else 1 for s in st["seqs"]], dtype=np.int32)
+            act = np.asarray([0 if (s is None or s.finished) else 1 for s in st["seqs"]], dtype=np.int32)
             if self.cuda:
                 st["active"].copy_(self._t(act, torch.int32))
             else:

@@ -113,6 +113,23 @@ def main():
             errs[f"allreduce{M}"] = float((y.float().cpu() - ref).norm() / ref.norm())
         native.check_status(dev)
         result["errs"] = errs
+    elif scenario == "cpu_server":
+        # every rank serves the same request stream on its own replica; the step plans must agree word for word
+        from eredu_b200.runtime.server import ConsensusError, Server, TorchTransport
+
+        model = build_from_tensors(cfg, sd.__getitem__, sd.__contains__, dev, dtype)
+        srv = Server(Engine(model, max_batch=3, max_seq_len=128), transport=TorchTransport(), prefill_chunk=16)
+        ids = [srv.submit(p, sp, 6) for p in prompts]
+        srv.run_until_idle(max_steps=200)
+        result["tokens"] = [srv.result(i).tokens for i in ids]
+        # now the ranks diverge: rank 1 sees a request the others do not
+        srv.submit(prompts[0][: 5 + rank], sp, 3)
+        try:
+            srv.run_until_idle(max_steps=50)
+            result["diverged"] = "none"
+        except ConsensusError:
+            result["diverged"] = "ConsensusError"
+        result["poisoned"] = bool(srv.sched.poisoned)
     elif "ep" in scenario:
         # attention tensor-parallel and experts expert-parallel over the same ranks
         from eredu_b200.models.moe import make_moe_factory
