@@ -36,6 +36,8 @@ struct QGemmParams {
   int M, N, K;
   int ldy, ldr;
   int group;
+  int group_shift;  // log2(group) when the group size is a power of two, else -1 (general division)
+  int sb_rows;      // > 0: scales / biases of a K block arrive by TMA as sb_rows x 128 tiles next to the packed weights
   int out_fp32;
   int* status;
 };
@@ -48,19 +50,28 @@ struct QRaw {
   static constexpr int kBytes = 128 * kRowBytes;
 };
 
+// Two rings. The packed weights (with the activation tile of the same K block) land in a DEEP ring of small
+// slots: at 4 bits a K block is only 4 KB per tile, and HBM needs tens of KB in flight per SM to run at full
+// bandwidth. The dequantised bf16 operand tiles live in a SHALLOW ring of 16 KB slots that only has to cover the
+// dequant -> MMA hand-off.
 template <int TN, int FMT>
 struct QCfg {
   static constexpr int kATile = 128 * 64 * 2;
   static constexpr int kBTile = TN * 64 * 2;
   static constexpr int kRaw = QRaw<FMT>::kBytes;
-  static constexpr int kStageBytes = kATile + kBTile + ((kRaw + 1023) / 1024) * 1024;
-  static constexpr int kBudget = TN <= 32 ? 104 * 1024 : 190 * 1024;
-  static constexpr int kStagesRaw = kBudget / kStageBytes;
-  static constexpr int kStages = kStagesRaw > 6 ? 6 : kStagesRaw;
+  static constexpr int kSbBytes = 4 * 128 * 2;  // up to 4 groups per 64-wide K block, one bf16 per weight row
+  static constexpr int kRawSlot = ((kRaw + kBTile + 2 * kSbBytes + 1023) / 1024) * 1024;  // [X][packed][scales][biases]
+  // decode-sized tiles stay under half an SM's shared memory: two resident CTAs per SM (twice the dequant warps,
+  // one full wave for grids of up to 296 CTAs)
+  static constexpr int kAStages = 4;
+  static constexpr int kBudget = TN <= 32 ? 108 * 1024 : 200 * 1024;
+  static constexpr int kRawStagesMax = (kBudget - kAStages * kATile) / kRawSlot;
+  static constexpr int kRawStages = kRawStagesMax > 16 ? 16 : kRawStagesMax;
   static constexpr int kTmemCols = TN <= 32 ? 32 : TN <= 64 ? 64 : TN <= 128 ? 128 : 256;
   static constexpr int kCtrlBytes = 1024;
-  static constexpr int kSmemBytes = 1024 + kCtrlBytes + kStages * kStageBytes;
-  static_assert(kStages >= 2, "pipeline too shallow");
+  static constexpr int kSmemBytes = 1024 + kCtrlBytes + kAStages * kATile + kRawStages * kRawSlot;
+  static_assert(kRawStages >= 2, "pipeline too shallow");
+  static_assert(kBTile % 1024 == 0, "the packed bytes must start 1024-byte aligned behind the X tile");
 };
 
 constexpr int kDequantWarps = 8;
@@ -81,23 +92,72 @@ __device__ __forceinline__ void store_chunk(uint8_t* a_tile, int r, int c, uint4
 // 256 dequant threads: thread t owns row t>>1 and the 32-weight half t&1 of the 64-wide K block.
 // AFFINE4 kernel layout: inside each u32 the nibbles are stored in the order (n0,n2,n4,n6,n1,n3,n5,n7) so that
 // one lop3 with 0x000F000F yields the bf16 pair (128+n_{2i}, 128+n_{2i+1}) without any byte shuffling.
+__device__ __forceinline__ int group_of(const QGemmParams& p, int k) {
+  return p.group_shift >= 0 ? (k >> p.group_shift) : (k / p.group);
+}
+
+// Scale and bias (as bf16x2 splats) of the group that holds element k of row n; zero outside the matrix.
+__device__ __forceinline__ void load_scale_bias(const QGemmParams& p, int n, int k, uint32_t& s2, uint32_t& b2) {
+  uint32_t s = 0, b = 0;
+  if (n < p.N && k < p.K) {
+    const size_t idx = static_cast<size_t>(group_of(p, k)) * p.N + n;
+    s = reinterpret_cast<const uint16_t*>(p.scales_t)[idx];
+    b = reinterpret_cast<const uint16_t*>(p.biases_t)[idx];
+  }
+  s2 = s | (s << 16);
+  b2 = b | (b << 16);
+}
+
+// `s_sm` / `b_sm` (non-null): this K block's scales and biases in shared memory, [group within the block][128 rows],
+// delivered by TMA together with the packed weights, so no global load sits inside the dequant loop.
 template <int FMT>
 __device__ __forceinline__ void dequant_half_row(const QGemmParams& p, const uint8_t* raw, uint8_t* a_tile, int r, int half,
-                                                 int n, int kb) {
+                                                 int n, int kb, const uint16_t* s_sm = nullptr, const uint16_t* b_sm = nullptr) {
   const int k0 = kb * 64 + half * 32;
   const bool live = n < p.N && k0 < p.K;
-  if (FMT == QF_AFFINE4) {
+  if (FMT == QF_AFFINE4 && s_sm != nullptr && p.group >= 32) {
+    // fast path: one scale / bias pair for the whole half-row, read from shared memory; no group bookkeeping
+    const uint4 w4 = *reinterpret_cast<const uint4*>(raw + r * 32 + half * 16);
+    const uint32_t words[4] = {w4.x, w4.y, w4.z, w4.w};
+    const int gl = p.group < 64 ? half : 0;
+    const uint32_t s2 = __byte_perm(s_sm[gl * 128 + r], 0, 0x1010);  // bf16 -> (bf16, bf16)
+    const uint32_t b2 = __byte_perm(b_sm[gl * 128 + r], 0, 0x1010);
+    uint8_t* row = a_tile + r * 128;
+    const int sw = r & 7;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const uint32_t x = words[w];
+      uint4 o;
+      uint32_t p0 = (x & 0x000F000Fu) | 0x43004300u;          // (128 + n_2i, 128 + n_2i+1)
+      uint32_t p1 = ((x >> 4) & 0x000F000Fu) | 0x43004300u;
+      uint32_t p2 = ((x >> 8) & 0x000F000Fu) | 0x43004300u;
+      uint32_t p3 = ((x >> 12) & 0x000F000Fu) | 0x43004300u;
+      asm("sub.bf16x2 %0, %0, %1;" : "+r"(p0) : "r"(0x43004300u));
+      asm("sub.bf16x2 %0, %0, %1;" : "+r"(p1) : "r"(0x43004300u));
+      asm("sub.bf16x2 %0, %0, %1;" : "+r"(p2) : "r"(0x43004300u));
+      asm("sub.bf16x2 %0, %0, %1;" : "+r"(p3) : "r"(0x43004300u));
+      o.x = bf16x2_fma(p0, s2, b2);
+      o.y = bf16x2_fma(p1, s2, b2);
+      o.z = bf16x2_fma(p2, s2, b2);
+      o.w = bf16x2_fma(p3, s2, b2);
+      *reinterpret_cast<uint4*>(row + (((half * 4 + w) ^ sw) << 4)) = o;
+    }
+  } else if (FMT == QF_AFFINE4) {
     const uint4 w4 = *reinterpret_cast<const uint4*>(raw + r * 32 + half * 16);
     const uint32_t words[4] = {w4.x, w4.y, w4.z, w4.w};
     uint32_t s2 = 0, b2 = 0;
     int cur_group = -1;
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
-      const int g = (k0 + w * 8) / p.group;
+      const int g = group_of(p, k0 + w * 8);
       if (g != cur_group) {
         cur_group = g;
         uint32_t s = 0, b = 0;
-        if (live) {
+        if (s_sm != nullptr) {
+          const int gl = p.group < 64 ? ((half * 32 + w * 8) >> p.group_shift) : 0;
+          s = s_sm[gl * 128 + r];
+          b = b_sm[gl * 128 + r];
+        } else if (live) {
           s = reinterpret_cast<const uint16_t*>(p.scales_t)[static_cast<size_t>(g) * p.N + n];
           b = reinterpret_cast<const uint16_t*>(p.biases_t)[static_cast<size_t>(g) * p.N + n];
         }
@@ -128,11 +188,15 @@ __device__ __forceinline__ void dequant_half_row(const QGemmParams& p, const uin
       uint32_t* ov = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
       for (int hw = 0; hw < 2; ++hw) {
-        const int g = (k0 + c * 8 + hw * 4) / p.group;
+        const int g = group_of(p, k0 + c * 8 + hw * 4);
         if (g != cur_group) {
           cur_group = g;
           uint32_t s = 0, b = 0;
-          if (live) {
+          if (s_sm != nullptr) {
+            const int gl = p.group < 64 ? ((half * 32 + c * 8 + hw * 4) >> p.group_shift) : 0;
+            s = s_sm[gl * 128 + r];
+            b = b_sm[gl * 128 + r];
+          } else if (live) {
             s = reinterpret_cast<const uint16_t*>(p.scales_t)[static_cast<size_t>(g) * p.N + n];
             b = reinterpret_cast<const uint16_t*>(p.biases_t)[static_cast<size_t>(g) * p.N + n];
           }
@@ -157,18 +221,21 @@ __device__ __forceinline__ void dequant_half_row(const QGemmParams& p, const uin
 // warps: 0 TMA producer, 1 MMA issuer (+TMEM alloc), 2..5 epilogue, 6..13 dequant.
 template <int TN, int FMT, bool SPLIT>
 __global__ void __launch_bounds__(kQThreads, 1)
-qgemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmX, QGemmParams p) {
+qgemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmX,
+             const __grid_constant__ CUtensorMap tmS, const __grid_constant__ CUtensorMap tmB, QGemmParams p) {
   using Cfg = QCfg<TN, FMT>;
+  constexpr int R = Cfg::kRawStages, A = Cfg::kAStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* raw_full = reinterpret_cast<uint64_t*>(smem);  // TMA landed (packed weights + X tile)
-  uint64_t* a_full = raw_full + Cfg::kStages;              // bf16 operand tile written (8 warp arrivals)
-  uint64_t* empty_bar = a_full + Cfg::kStages;             // MMAs of the stage retired
-  uint64_t* accum_bar = empty_bar + Cfg::kStages;
+  uint64_t* raw_full = reinterpret_cast<uint64_t*>(smem);  // [R] TMA landed (packed weights + X tile)
+  uint64_t* raw_empty = raw_full + R;                      // [R] the MMAs that read the slot's X tile retired
+  uint64_t* a_full = raw_empty + R;                        // [A] bf16 operand tile written (8 warp arrivals)
+  uint64_t* a_empty = a_full + A;                          // [A] the MMAs that read the operand tile retired
+  uint64_t* accum_bar = a_empty + A;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
-  uint8_t* stages = smem + Cfg::kCtrlBytes;
-  // stage layout: [A bf16 tile 16 KB][X tile][raw packed bytes]
-  constexpr int kXOff = Cfg::kATile, kRawOff = Cfg::kATile + Cfg::kBTile;
+  uint8_t* a_ring = smem + Cfg::kCtrlBytes;                // [A][16 KB] K-major SW128 operand tiles
+  uint8_t* raw_ring = a_ring + A * Cfg::kATile;            // [R][X tile | packed weights]
+  constexpr int kRawOff = Cfg::kBTile, kScaleOff = Cfg::kBTile + Cfg::kRaw, kBiasOff = kScaleOff + Cfg::kSbBytes;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile_n = blockIdx.x, tile_m = blockIdx.y;
@@ -182,10 +249,13 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmX);
-    for (int s = 0; s < Cfg::kStages; ++s) {
+    for (int s = 0; s < R; ++s) {
       mbar_init(&raw_full[s], 1);
+      mbar_init(&raw_empty[s], 1);
+    }
+    for (int s = 0; s < A; ++s) {
       mbar_init(&a_full[s], kDequantWarps);
-      mbar_init(&empty_bar[s], 1);
+      mbar_init(&a_empty[s], 1);
     }
     mbar_init(accum_bar, 1);
     fence_mbar_init();
@@ -210,21 +280,25 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
       int issued = 0;
       bool ok = true;
       for (int it = 0; it < niter; ++it) {
-        const int s = it % Cfg::kStages;
-        const uint32_t ph = (it / Cfg::kStages) & 1;
-        ok = mbar_wait(&empty_bar[s], ph ^ 1, p.status, kStatusSmemEmptyTimeout);
+        const int s = it % R;
+        const uint32_t ph = (it / R) & 1;
+        ok = mbar_wait(&raw_empty[s], ph ^ 1, p.status, kStatusSmemEmptyTimeout);
         if (!ok) break;
-        uint8_t* st = stages + s * Cfg::kStageBytes;
+        uint8_t* st = raw_ring + s * Cfg::kRawSlot;
         const int kb = kb0 + it;
-        mbar_arrive_expect_tx(&raw_full[s], Cfg::kRaw + Cfg::kBTile);
+        mbar_arrive_expect_tx(&raw_full[s], Cfg::kRaw + Cfg::kBTile + 2 * p.sb_rows * 256);
         // packed weights: byte tensor [N, row_bytes]; x coordinate in bytes (a multiple of 32)
         tma_load_2d_hint(st + kRawOff, &tmQ, kb * QRaw<FMT>::kBox0, tile_n * 128, &raw_full[s], pol_w);
-        tma_load_2d_hint(st + kXOff, &tmX, kb * 64, tile_m * TN, &raw_full[s], pol_x);
+        tma_load_2d_hint(st, &tmX, kb * 64, tile_m * TN, &raw_full[s], pol_x);
+        if (p.sb_rows > 0) {
+          const int grow = (kb * 64) >> p.group_shift;
+          tma_load_2d_hint(st + kScaleOff, &tmS, tile_n * 128, grow, &raw_full[s], pol_w);
+          tma_load_2d_hint(st + kBiasOff, &tmB, tile_n * 128, grow, &raw_full[s], pol_w);
+        }
         issued = it + 1;
       }
       if (!ok) {
-        for (int it = max(0, issued - Cfg::kStages); it < issued; ++it)
-          mbar_wait(&raw_full[it % Cfg::kStages], (it / Cfg::kStages) & 1, nullptr, 0);
+        for (int it = max(0, issued - R); it < issued; ++it) mbar_wait(&raw_full[it % R], (it / R) & 1, nullptr, 0);
       }
     }
   } else if (warp == 1) {
@@ -232,38 +306,42 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
       constexpr uint32_t idesc = umma_idesc_bf16(128, TN);
       bool ok = true;
       for (int it = 0; it < niter; ++it) {
-        const int s = it % Cfg::kStages;
-        const uint32_t ph = (it / Cfg::kStages) & 1;
-        ok = mbar_wait(&raw_full[s], ph, p.status, kStatusTmaFullTimeout) &&
-             mbar_wait(&a_full[s], ph, p.status, kStatusTmaFullTimeout);
+        const int rs = it % R, as = it % A;
+        ok = mbar_wait(&raw_full[rs], (it / R) & 1, p.status, kStatusTmaFullTimeout) &&
+             mbar_wait(&a_full[as], (it / A) & 1, p.status, kStatusTmaFullTimeout);
         if (!ok) break;
         tc_fence_after_sync();
-        const uint32_t a_addr = smem_u32(stages + s * Cfg::kStageBytes);
-        const uint64_t da = umma_desc_k_sw128(a_addr);
-        const uint64_t db = umma_desc_k_sw128(a_addr + kXOff);
+        const uint64_t da = umma_desc_k_sw128(smem_u32(a_ring + as * Cfg::kATile));
+        const uint64_t db = umma_desc_k_sw128(smem_u32(raw_ring + rs * Cfg::kRawSlot));
 #pragma unroll
         for (int k = 0; k < 4; ++k) umma_f16(tmem_base, da + 2 * k, db + 2 * k, idesc, (it > 0 || k > 0) ? 1u : 0u);
-        umma_commit(&empty_bar[s]);
+        umma_commit(&a_empty[as]);
+        umma_commit(&raw_empty[rs]);
       }
       if (ok) umma_commit(accum_bar);
     }
   } else if (warp >= 6) {
     // ------------------------------------------------------------ dequant warps
+    // 256 threads: thread t converts the 32-weight half t&1 of row t>>1 of every K block. (Giving each warp whole
+    // blocks of its own - fewer hand-offs, more work per wait - measured slower: the conversion of one half-row
+    // is a dependent chain, and eight warps sharing a block overlap those chains better.)
     const int dt = threadIdx.x - 6 * 32;  // 0..255
     const int r = dt >> 1, half = dt & 1;
     const int n = tile_n * 128 + r;
     bool ok = true;
     for (int it = 0; it < niter; ++it) {
-      const int s = it % Cfg::kStages;
-      const uint32_t ph = (it / Cfg::kStages) & 1;
-      ok = mbar_wait(&raw_full[s], ph, p.status, kStatusTmaFullTimeout);
+      const int rs = it % R, as = it % A;
+      ok = mbar_wait(&raw_full[rs], (it / R) & 1, p.status, kStatusTmaFullTimeout) &&
+           mbar_wait(&a_empty[as], ((it / A) & 1) ^ 1, p.status, kStatusSmemEmptyTimeout);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      uint8_t* st = stages + s * Cfg::kStageBytes;
-      dequant_half_row<FMT>(p, st + kRawOff, st, r, half, n, kb0 + it);
+      const uint8_t* slot = raw_ring + rs * Cfg::kRawSlot;
+      const uint16_t* s_sm = p.sb_rows > 0 ? reinterpret_cast<const uint16_t*>(slot + kScaleOff) : nullptr;
+      const uint16_t* b_sm = p.sb_rows > 0 ? reinterpret_cast<const uint16_t*>(slot + kBiasOff) : nullptr;
+      dequant_half_row<FMT>(p, slot + kRawOff, a_ring + as * Cfg::kATile, r, half, n, kb0 + it, s_sm, b_sm);
       fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core's async proxy
       __syncwarp();
-      if (lane == 0) mbar_arrive(&a_full[s]);
+      if (lane == 0) mbar_arrive(&a_full[as]);
     }
   }
   __syncwarp();
@@ -273,7 +351,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
   const int row = q * 32 + lane;
   const int n = tile_n * 128 + row;
   const int m_base = tile_m * TN;
-  float* red = reinterpret_cast<float*>(stages);  // SPLIT: [TN][128] fp32, aliases the ring after the main loop
+  float* red = reinterpret_cast<float*>(a_ring);  // SPLIT: [TN][128] fp32, aliases the operand ring after the main loop
 
   auto store = [&](float v, int m) {
     if (p.bias != nullptr) v += __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[n]);
@@ -328,8 +406,8 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
 }
 
 template <int TN, int FMT, bool SPLIT>
-static cudaError_t launch_q(const CUtensorMap& tmQ, const CUtensorMap& tmX, const QGemmParams& p, int n_tiles, int m_tiles,
-                            int nsplit, cudaStream_t stream) {
+static cudaError_t launch_q(const CUtensorMap& tmQ, const CUtensorMap& tmX, const CUtensorMap& tmS, const CUtensorMap& tmB,
+                            const QGemmParams& p, int n_tiles, int m_tiles, int nsplit, cudaStream_t stream) {
   using Cfg = QCfg<TN, FMT>;
   auto kern = qgemm_kernel<TN, FMT, SPLIT>;
   static bool configured = false;
@@ -359,20 +437,21 @@ static cudaError_t launch_q(const CUtensorMap& tmQ, const CUtensorMap& tmX, cons
   }
   cfg.attrs = attr;
   cfg.numAttrs = nattr;
-  return cudaLaunchKernelEx(&cfg, kern, tmQ, tmX, p);
+  return cudaLaunchKernelEx(&cfg, kern, tmQ, tmX, tmS, tmB, p);
 }
 
 template <int FMT>
-static cudaError_t dispatch_q(int tn, const CUtensorMap& tmQ, const CUtensorMap& tmX, const QGemmParams& p, int n_tiles,
-                              int m_tiles, int nsplit, cudaStream_t stream) {
+static cudaError_t dispatch_q(int tn, const CUtensorMap& tmQ, const CUtensorMap& tmX, const CUtensorMap& tmS,
+                              const CUtensorMap& tmB, const QGemmParams& p, int n_tiles, int m_tiles, int nsplit,
+                              cudaStream_t stream) {
   switch (tn) {
-    case 16: return nsplit > 1 ? launch_q<16, FMT, true>(tmQ, tmX, p, n_tiles, m_tiles, nsplit, stream)
-                               : launch_q<16, FMT, false>(tmQ, tmX, p, n_tiles, m_tiles, 1, stream);
-    case 32: return nsplit > 1 ? launch_q<32, FMT, true>(tmQ, tmX, p, n_tiles, m_tiles, nsplit, stream)
-                               : launch_q<32, FMT, false>(tmQ, tmX, p, n_tiles, m_tiles, 1, stream);
-    case 64: return nsplit > 1 ? launch_q<64, FMT, true>(tmQ, tmX, p, n_tiles, m_tiles, nsplit, stream)
-                               : launch_q<64, FMT, false>(tmQ, tmX, p, n_tiles, m_tiles, 1, stream);
-    default: return launch_q<128, FMT, false>(tmQ, tmX, p, n_tiles, m_tiles, 1, stream);
+    case 16: return nsplit > 1 ? launch_q<16, FMT, true>(tmQ, tmX, tmS, tmB, p, n_tiles, m_tiles, nsplit, stream)
+                               : launch_q<16, FMT, false>(tmQ, tmX, tmS, tmB, p, n_tiles, m_tiles, 1, stream);
+    case 32: return nsplit > 1 ? launch_q<32, FMT, true>(tmQ, tmX, tmS, tmB, p, n_tiles, m_tiles, nsplit, stream)
+                               : launch_q<32, FMT, false>(tmQ, tmX, tmS, tmB, p, n_tiles, m_tiles, 1, stream);
+    case 64: return nsplit > 1 ? launch_q<64, FMT, true>(tmQ, tmX, tmS, tmB, p, n_tiles, m_tiles, nsplit, stream)
+                               : launch_q<64, FMT, false>(tmQ, tmX, tmS, tmB, p, n_tiles, m_tiles, 1, stream);
+    default: return launch_q<128, FMT, false>(tmQ, tmX, tmS, tmB, p, n_tiles, m_tiles, 1, stream);
   }
 }
 
@@ -417,6 +496,7 @@ extern "C" int eredu_dequant_affine(const void* wq, const void* scales_t, const 
   p.N = N;
   p.K = K;
   p.group = group;
+  p.group_shift = (group & (group - 1)) == 0 ? __builtin_ctz(static_cast<unsigned>(group)) : -1;
   dim3 grid(K / 64, (N + 127) / 128);
   if (bits == 4)
     launch_pdl(dequant_matrix_kernel<QF_AFFINE4>, grid, dim3(256), 0, stream, static_cast<const uint8_t*>(wq), p,
@@ -457,8 +537,20 @@ extern "C" int eredu_qgemm(const void* X, const void* wq, const void* scales_t, 
   p.ldy = ldy;
   p.ldr = ldr;
   p.group = group;
+  p.group_shift = (group & (group - 1)) == 0 ? __builtin_ctz(static_cast<unsigned>(group)) : -1;
   p.out_fp32 = out_fp32;
   p.status = status;
+  // scales / biases by TMA: power-of-two groups (1, 2 or 4 per 64-wide K block, or one row shared by several
+  // blocks) and 16-byte aligned rows of the transposed tables
+  CUtensorMap tmS = tmX, tmB = tmX;
+  p.sb_rows = 0;
+  if (p.group_shift >= 0 && group >= 16 && N % 8 == 0) {
+    const int rows = group >= 64 ? 1 : 64 / group;
+    const uint64_t table_rows = static_cast<uint64_t>(K / group);
+    if (make_tma_2d(&tmS, scales_t, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, table_rows, N, N, rows, 128, CU_TENSOR_MAP_SWIZZLE_NONE) == 0 &&
+        make_tma_2d(&tmB, biases_t, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, table_rows, N, N, rows, 128, CU_TENSOR_MAP_SWIZZLE_NONE) == 0)
+      p.sb_rows = rows;
+  }
   const int n_tiles = (N + 127) / 128;
   const int m_tiles = (M + tn - 1) / tn;
   const int kblocks = K / 64;
@@ -471,8 +563,8 @@ extern "C" int eredu_qgemm(const void* X, const void* wq, const void* scales_t, 
     }
     while (nsplit > 1 && (kblocks + nsplit - 1) / nsplit * (nsplit - 1) >= kblocks) nsplit >>= 1;
   }
-  cudaError_t e = bits == 4 ? dispatch_q<QF_AFFINE4>(tn, tmQ, tmX, p, n_tiles, m_tiles, nsplit, stream)
-                            : dispatch_q<QF_AFFINE8>(tn, tmQ, tmX, p, n_tiles, m_tiles, nsplit, stream);
+  cudaError_t e = bits == 4 ? dispatch_q<QF_AFFINE4>(tn, tmQ, tmX, tmS, tmB, p, n_tiles, m_tiles, nsplit, stream)
+                            : dispatch_q<QF_AFFINE8>(tn, tmQ, tmX, tmS, tmB, p, n_tiles, m_tiles, nsplit, stream);
   eredu_count_launches(1);
   return static_cast<int>(e);
 }
