@@ -235,6 +235,32 @@ class Engine:
         for i, s in enumerate(seqs):
             s.slot = i
 
+    # ------------------------------------------------------------------------------------------ host-driven steps
+    @torch.no_grad()
+    def feed_logits(self, seq: Sequence, tokens: list[int]) -> torch.Tensor:
+        """Append ``tokens`` to the sequence's cache and return the logits after the last one ([V], on the model's
+        device). For samplers that must see every distribution on the host (grammar masks, Mirostat)."""
+        n = len(tokens)
+        p = np.arange(seq.kv_len, seq.kv_len + n)
+        pages = np.asarray(seq.pages, dtype=np.int64)
+        batch = ForwardBatch(
+            token_ids=self._t(np.asarray(tokens, dtype=np.int32), torch.int32),
+            positions=self._t(p.astype(np.int32), torch.int32),
+            slots=self._t(pages[p // PAGE] * PAGE + (p % PAGE), torch.int64),
+            block_table=self._block_table([seq]), seq_lens=self._t(np.asarray([seq.kv_len + n], dtype=np.int32), torch.int32),
+            is_prefill=True, cu_q=self._t(np.asarray([0, n], dtype=np.int32), torch.int32), max_q_len=n,
+            logit_rows=self._t(np.asarray([n - 1], dtype=np.int64), torch.int64))
+        logits = self.model.forward(batch, self.kv)
+        seq.kv_len += n
+        return logits[0]
+
+    def prefill_logits(self, seqs: list[Sequence]) -> list[torch.Tensor]:
+        return [self.feed_logits(s, s.prompt[s.kv_len:]) for s in seqs]
+
+    def step_logits(self, seq: Sequence, token: int) -> torch.Tensor:
+        seq.output.append(int(token))
+        return self.feed_logits(seq, [int(token)])
+
     # ------------------------------------------------------------------------------------------ slot-based decode
     def open_decode(self, penalties: bool = False, max_context: Optional[int] = None) -> None:
         """Create a decode state with ``max_batch`` slots, all free. Sequences :meth:`join` and :meth:`leave`

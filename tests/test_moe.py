@@ -116,3 +116,23 @@ def test_moe_model_gpu_logits():
     ref = forward_logits(cfg, sd, prompt, moe_fn=moe_oracle)[-1]
     rel = float((got - ref).norm() / ref.norm())
     assert rel < 0.03 and torch.nn.functional.cosine_similarity(got, ref, dim=0) > 0.999
+
+
+def test_mixtral_naming_and_router_cpu():
+    """Mixtral checkpoints: ``block_sparse_moe.{gate, experts.N.w1/w3/w2}``, top-k-then-softmax routing."""
+    cfg = dataclasses.replace(tiny_moe_cfg(), model_type="mixtral", qk_norm=False, router_scoring="topk_softmax",
+                              norm_topk_prob=False)
+    sd = random_state(cfg, seed=3, std=0.08)
+    mix = {}
+    for k, v in sd.items():
+        k2 = k.replace(".mlp.gate.weight", ".block_sparse_moe.gate.weight")
+        k2 = k2.replace(".mlp.experts.", ".block_sparse_moe.experts.")
+        k2 = k2.replace(".gate_proj.weight", ".w1.weight") if "block_sparse_moe.experts" in k2 else k2
+        k2 = k2.replace(".up_proj.weight", ".w3.weight") if "block_sparse_moe.experts" in k2 else k2
+        k2 = k2.replace(".down_proj.weight", ".w2.weight") if "block_sparse_moe.experts" in k2 else k2
+        mix[k2] = v
+    model = build_from_tensors(cfg, mix.__getitem__, mix.__contains__, "cpu", torch.float32, moe_factory=make_moe_factory())
+    eng = Engine(model, max_batch=1, max_seq_len=64)
+    prompt = torch.randint(0, cfg.vocab_size, (11,), generator=torch.Generator().manual_seed(5)).tolist()
+    out = eng.generate([prompt], SamplingParams(temperature=0.0), max_new_tokens=6)[0]
+    assert out == greedy(cfg, sd, prompt, 6, moe_fn=moe_oracle)
