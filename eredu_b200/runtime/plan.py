@@ -1,0 +1,319 @@
+"""Artifact inspection, resource estimates, admission and the automatic execution planner.
+
+Counterparts: eredu-core/src/artifact.rs:484-516 (header-only inspection, preparation policy), inspection.rs:10-260
+(``ModelInspectionReport`` with issue codes and ``is_loadable``), capability.rs:107-560 (``estimate_runtime_state``:
+KV bytes per token, admission), execution.rs:9-318 (``ExecutionPlan`` schema version 2: device, topology,
+residency, weight transformation, expert cache, drafting, mapped shards) and automatic.rs:96-830
+(``HardwareProfile``, ``ModelResourceProfile``, ``AutomaticPlanner::plan``).
+
+The planner is written for one node of B200s (180 GB HBM3e each, every peer at full NVLink bandwidth through
+NVSwitch): it prefers the smallest tensor-parallel degree whose shards, KV pool and workspace fit, puts experts on the
+tensor ranks for sparse models, and only then falls back to load-time 4-bit weights and host-resident layers.
+"""
+from __future__ import annotations
+
+import json
+from dataclasses import asdict, dataclass, field
+from pathlib import Path
+from typing import Optional
+
+from ..models.config import DENSE_TYPES, MOE_TYPES, ModelConfig
+
+EXECUTION_PLAN_SCHEMA_VERSION = 2
+DEFAULT_MAX_MAPPED_SHARDS = 4
+SUPPORTED_TYPES = DENSE_TYPES | {"qwen3_moe", "mixtral"}
+
+
+# ---------------------------------------------------------------------------------------------- inspection
+@dataclass
+class InspectionIssue:
+    code: str
+    severity: str      # "error" | "warning" | "info"
+    message: str
+
+
+@dataclass
+class ModelInspectionReport:
+    path: str
+    format: str                      # "safetensors" | "gguf"
+    model_type: str
+    config: Optional[ModelConfig]
+    tensor_count: int = 0
+    tensor_bytes: int = 0
+    parameter_count: int = 0
+    dtypes: dict = field(default_factory=dict)      # dtype / quant type -> bytes
+    quantization: Optional[dict] = None
+    has_tokenizer: bool = False
+    issues: list = field(default_factory=list)
+
+    @property
+    def is_loadable(self) -> bool:
+        return not any(i.severity == "error" for i in self.issues)
+
+    def to_dict(self) -> dict:
+        d = asdict(self)
+        d["config"] = asdict(self.config) if self.config is not None else None
+        d["is_loadable"] = self.is_loadable
+        return d
+
+
+def inspect_artifact(path) -> ModelInspectionReport:
+    """Header-only inspection: no tensor payload is read or mapped."""
+    from ..formats.checkpoint import GGML_NAME
+    from ..lib import _eredu_host as H
+
+    path = Path(path)
+    issues: list[InspectionIssue] = []
+    if path.is_dir():
+        if not (path / "config.json").exists():
+            return ModelInspectionReport(str(path), "safetensors", "unknown", None,
+                                         issues=[InspectionIssue("missing_config", "error", "config.json not found")])
+        cfg = ModelConfig.from_pretrained(path)
+        try:
+            store = H.SafetensorsStore(str(path), 1)
+        except Exception as e:
+            return ModelInspectionReport(str(path), "safetensors", cfg.model_type, cfg,
+                                         issues=[InspectionIssue("unreadable_weights", "error", str(e))])
+        rep = ModelInspectionReport(str(path), "safetensors", cfg.model_type, cfg, quantization=cfg.quantization,
+                                    has_tokenizer=(path / "tokenizer.json").exists())
+        itemsize = {"F32": 4, "F16": 2, "BF16": 2, "I32": 4, "U32": 4, "I64": 8, "U8": 1, "I8": 1, "F64": 8, "BOOL": 1,
+                    "I16": 2, "U16": 2, "F8_E4M3": 1, "F8_E5M2": 1}
+        keys = set(store.keys())
+        for k in keys:
+            info = store.info(k)
+            n = 1
+            for s in info["shape"]:
+                n *= int(s)
+            nb = n * itemsize.get(info["dtype"], 1)
+            rep.tensor_count += 1
+            rep.tensor_bytes += nb
+            rep.dtypes[info["dtype"]] = rep.dtypes.get(info["dtype"], 0) + nb
+            if not k.endswith((".scales", ".biases")):
+                bits = (cfg.quantization or {}).get("bits") if (k[:-7] + ".scales") in keys and k.endswith(".weight") else None
+                rep.parameter_count += n * (32 // int(bits)) if bits else n
+        required = ["model.embed_tokens.weight", "model.norm.weight", "model.layers.0.self_attn.q_proj.weight"]
+        for name in required:
+            if name not in keys:
+                issues.append(InspectionIssue("missing_tensor", "error", f"required tensor {name} is absent"))
+        if not cfg.tie_word_embeddings and "lm_head.weight" not in keys:
+            issues.append(InspectionIssue("missing_tensor", "error", "untied model without lm_head.weight"))
+    elif path.is_file():
+        try:
+            reader = H.GgufReader(str(path))
+        except Exception as e:
+            return ModelInspectionReport(str(path), "gguf", "unknown", None,
+                                         issues=[InspectionIssue("unreadable_gguf", "error", str(e))])
+        md = reader.metadata() if callable(reader.metadata) else reader.metadata
+        tensors = reader.tensors()
+        names = {t["name"] if isinstance(t, dict) else t[0] for t in tensors}
+        cfg = ModelConfig.from_gguf_metadata(md, "output.weight" in names)
+        rep = ModelInspectionReport(str(path), "gguf", cfg.model_type, cfg, has_tokenizer="tokenizer.ggml.tokens" in md)
+        for t in tensors:
+            info = t if isinstance(t, dict) else {"name": t[0], "type": t[1], "shape": t[2], "nbytes": t[3]}
+            n = 1
+            for s in info["shape"]:
+                n *= int(s)
+            rep.tensor_count += 1
+            rep.tensor_bytes += int(info.get("nbytes", 0))
+            tname = GGML_NAME.get(int(info["type"]), f"type{info['type']}")
+            rep.dtypes[tname] = rep.dtypes.get(tname, 0) + int(info.get("nbytes", 0))
+            rep.parameter_count += n
+        if "token_embd.weight" not in names:
+            issues.append(InspectionIssue("missing_tensor", "error", "token_embd.weight is absent"))
+    else:
+        return ModelInspectionReport(str(path), "unknown", "unknown", None,
+                                     issues=[InspectionIssue("not_found", "error", f"{path} does not exist")])
+    if cfg.model_type not in SUPPORTED_TYPES:
+        sev = "error"
+        issues.append(InspectionIssue("unsupported_architecture", sev, f"model type {cfg.model_type!r} has no adapter here"
+                                      + (" (recognised sparse family)" if cfg.model_type in MOE_TYPES else "")))
+    if cfg.head_dim not in (64, 128):
+        issues.append(InspectionIssue("head_dim", "warning", f"head_dim {cfg.head_dim}: attention kernels cover 64 and 128; "
+                                      "other sizes run the reference path"))
+    if not rep.has_tokenizer:
+        issues.append(InspectionIssue("no_tokenizer", "info", "no tokenizer found: only token-id APIs are available"))
+    rep.issues = issues
+    return rep
+
+
+# ---------------------------------------------------------------------------------------------- resource profile
+@dataclass
+class ModelResourceProfile:
+    weight_bytes: int                 # as stored in the checkpoint (or after the planned transformation)
+    kv_bytes_per_token: int           # all layers, K and V, at the cache dtype
+    layers: int
+    sliding_layers: int = 0
+    sliding_window: int = 0
+    expert_bytes: int = 0             # part of weight_bytes that belongs to routed experts
+    workspace_bytes: int = 2 << 30    # activations, logits, collective buffers, allocator slack
+
+
+def estimate_runtime_state(cfg: ModelConfig, weight_bytes: Optional[int] = None, cache_dtype_bytes: int = 2) -> ModelResourceProfile:
+    """KV bytes per token and static weight bytes of a decoder (``estimate_runtime_state``, capability.rs)."""
+    H, D = cfg.hidden_size, cfg.head_dim
+    L = cfg.num_hidden_layers
+    kv_tok = 2 * cfg.num_key_value_heads * D * cache_dtype_bytes * L
+    attn = (cfg.num_attention_heads * D * H) * 2 + (cfg.num_key_value_heads * D * H) * 2
+    dense_mlp = 3 * H * cfg.intermediate_size
+    expert = 3 * H * cfg.moe_intermediate_size * cfg.num_experts if cfg.is_moe else 0
+    moe_layers = sum(1 for li in range(L) if cfg.layer_is_moe(li))
+    params = L * attn + (L - moe_layers) * dense_mlp + moe_layers * (expert + cfg.num_experts * H)
+    params += cfg.vocab_size * H * (1 if cfg.tie_word_embeddings else 2)
+    wb = weight_bytes if weight_bytes is not None else params * 2
+    sliding = sum(1 for li in range(L) if cfg.layer_window(li) > 0)
+    share = (moe_layers * expert) / max(1, params)
+    return ModelResourceProfile(int(wb), int(kv_tok), L, sliding, int(cfg.sliding_window or 0), int(wb * share))
+
+
+def kv_bytes_for(profile: ModelResourceProfile, context: int, batch: int) -> int:
+    """KV pool bytes for ``batch`` sequences of ``context`` tokens (sliding layers hold at most their window)."""
+    per_layer = profile.kv_bytes_per_token // max(1, profile.layers)
+    full = profile.layers - profile.sliding_layers
+    tokens_sliding = min(context, profile.sliding_window) if profile.sliding_window else context
+    return batch * per_layer * (full * context + profile.sliding_layers * tokens_sliding)
+
+
+@dataclass
+class AdmissionDecision:
+    admitted: bool
+    reason: str = ""
+    max_context: int = 0
+
+
+def apply_admission_policy(profile: ModelResourceProfile, device_free_bytes: int, context: int, batch: int = 1,
+                           tensor_parallel: int = 1) -> AdmissionDecision:
+    """Refuse a request whose KV cache cannot fit next to the weights (fail before any payload I/O)."""
+    free = device_free_bytes - profile.weight_bytes // tensor_parallel - profile.workspace_bytes
+    need = kv_bytes_for(profile, context, batch) // tensor_parallel
+    per_tok = max(1, profile.kv_bytes_per_token // tensor_parallel) * batch
+    if free <= 0:
+        return AdmissionDecision(False, "weights and workspace alone exceed the device budget", 0)
+    if need > free:
+        return AdmissionDecision(False, f"KV cache needs {need} bytes, {free} available", int(free // per_tok))
+    return AdmissionDecision(True, "", int(free // per_tok))
+
+
+# ---------------------------------------------------------------------------------------------- execution plan
+@dataclass
+class ExecutionPlan:
+    device: dict                                   # {"backend": "cuda-sm100a", "device": "gpu:0"}
+    topology: dict                                 # {"data": 1, "pipeline": 1, "tensor": n, "expert": n, "expert_over_tensor": bool}
+    residency: dict                                # {"mode": "fully_resident"} | {"mode": "layerwise_host", ...}
+    weight_transformation: dict                    # {"mode": "preserve_checkpoint"} | {"mode": "affine", "bits", "group_size"}
+    max_mapped_shards: int = DEFAULT_MAX_MAPPED_SHARDS
+    expert_cache: Optional[dict] = None
+    drafting: dict = field(default_factory=lambda: {"mode": "disabled"})
+    kv_cache: dict = field(default_factory=lambda: {"mode": "device", "block_size_tokens": 16})
+    required_capabilities: dict = field(default_factory=lambda: {"exact_completion": True, "collectives": False,
+                                                                 "transfers": False, "persistent_cache": False})
+    schema_version: int = EXECUTION_PLAN_SCHEMA_VERSION
+    rationale: list = field(default_factory=list)
+
+    def validate(self) -> None:
+        if self.schema_version != EXECUTION_PLAN_SCHEMA_VERSION:
+            raise ValueError(f"execution plan schema {self.schema_version} (supported: {EXECUTION_PLAN_SCHEMA_VERSION})")
+        if self.max_mapped_shards <= 0:
+            raise ValueError("max_mapped_shards must be positive")
+        if not str(self.device.get("backend", "")).strip() or not str(self.device.get("device", "")).strip():
+            raise ValueError("device plan needs a backend and a device")
+        for axis in ("data", "pipeline", "tensor", "expert"):
+            if int(self.topology.get(axis, 1)) < 1:
+                raise ValueError(f"{axis} parallel size must be >= 1")
+        d = self.drafting
+        if d.get("mode") in ("embedded", "external") and int(d.get("max_draft_tokens", 0)) <= 0:
+            raise ValueError("drafting needs max_draft_tokens > 0")
+        if d.get("mode") == "external" and not str(d.get("model", "")).strip():
+            raise ValueError("external drafting needs a model")
+        if self.residency.get("mode") not in ("fully_resident", "layerwise_host", "dense_disk_stream"):
+            raise ValueError(f"unknown residency mode {self.residency.get('mode')!r}")
+        if self.weight_transformation.get("mode") not in ("preserve_checkpoint", "affine", "mxfp4"):
+            raise ValueError("unknown weight transformation")
+
+    def to_json(self) -> str:
+        return json.dumps(asdict(self), indent=1)
+
+    @classmethod
+    def from_json(cls, text: str) -> "ExecutionPlan":
+        plan = cls(**json.loads(text))
+        plan.validate()
+        return plan
+
+
+@dataclass
+class HardwareProfile:
+    device_count: int = 1
+    device_memory_bytes: int = 180 * 10**9
+    device_free_bytes: Optional[int] = None
+    host_memory_bytes: int = 0
+    peer_access: bool = True          # every GPU reaches every peer (NVSwitch)
+    name: str = "NVIDIA B200"
+
+    @classmethod
+    def discover(cls) -> "HardwareProfile":
+        from .telemetry import hardware_profile
+
+        hp = hardware_profile("cuda:0")
+        dev = hp.get("device", {})
+        return cls(int(dev.get("device_count", 1) or 1), int(dev.get("memory_bytes", 0) or 0) or 180 * 10**9,
+                   int(dev.get("free_bytes", 0) or 0) or None, int(hp["host"].get("memory_bytes", 0)), True,
+                   str(dev.get("name", "cpu")))
+
+
+class AutomaticPlanner:
+    """Chooses topology, weight transformation and residency for a model on this node."""
+
+    def __init__(self, hardware: HardwareProfile, memory_fraction: float = 0.92):
+        self.hw = hardware
+        self.fraction = memory_fraction
+
+    def plan(self, cfg: ModelConfig, profile: ModelResourceProfile, context: int = 4096, batch: int = 1,
+             draft_model: Optional[str] = None, allow_quantization: bool = True, prefer_devices: Optional[int] = None) -> ExecutionPlan:
+        budget = int((self.hw.device_free_bytes or self.hw.device_memory_bytes) * self.fraction)
+        why: list[str] = []
+
+        def fits(weight_bytes: int, tp: int) -> bool:
+            need = weight_bytes // tp + kv_bytes_for(profile, context, batch) // tp + profile.workspace_bytes
+            return need <= budget
+
+        degrees = [d for d in (1, 2, 4, 8) if d <= self.hw.device_count and cfg.num_attention_heads % d == 0
+                   and (cfg.num_key_value_heads % d == 0 or d % cfg.num_key_value_heads == 0)]
+        if prefer_devices:
+            degrees = [d for d in degrees if d >= prefer_devices] or degrees
+        transformation = {"mode": "preserve_checkpoint"}
+        residency = {"mode": "fully_resident"}
+        weight_bytes = profile.weight_bytes
+        tp = next((d for d in degrees if fits(weight_bytes, d)), None)
+        if tp is None and allow_quantization and not cfg.quantization:
+            q_bytes = int(profile.weight_bytes * (4.5 / 16.0))   # 4-bit codes + bf16 scale and bias per 64
+            tp = next((d for d in degrees if fits(q_bytes, d)), None)
+            if tp is not None:
+                transformation = {"mode": "affine", "bits": 4, "group_size": 64}
+                weight_bytes = q_bytes
+                why.append("bf16 weights do not fit at any tensor-parallel degree: load-time 4-bit (group 64)")
+        if tp is None:
+            tp = degrees[-1]
+            layer_bytes = weight_bytes // max(1, profile.layers) // tp
+            kv = kv_bytes_for(profile, context, batch) // tp
+            window = max(1, int((budget - kv - profile.workspace_bytes) // max(1, layer_bytes)))
+            residency = {"mode": "layerwise_host", "device_layer_window": min(window, profile.layers),
+                         "device_budget_bytes": budget, "host_budget_bytes": self.hw.host_memory_bytes or None}
+            why.append(f"weights exceed device memory even at tp={tp}: layers stay in pinned host memory, "
+                       f"{residency['device_layer_window']} at a time on the device")
+        else:
+            why.append(f"smallest tensor-parallel degree that fits weights + KV ({context} tokens x {batch}) + workspace: {tp}")
+        topo = {"data": 1, "pipeline": 1, "tensor": tp, "expert": tp if cfg.is_moe else 1,
+                "expert_over_tensor": bool(cfg.is_moe and tp > 1)}
+        if cfg.is_moe and tp > 1:
+            why.append("sparse model: experts are spread over the tensor ranks (replicated tokens, one combine + all-reduce)")
+        drafting = {"mode": "disabled"}
+        if draft_model:
+            drafting = {"mode": "external", "model": draft_model, "placement": {"mode": "target"}, "max_draft_tokens": 4,
+                        "lookahead": False, "adaptive_lookahead": False}
+        plan = ExecutionPlan(device={"backend": "cuda-sm100a", "device": "gpu:0" if tp == 1 else f"gpu:0-{tp - 1}"},
+                             topology=topo, residency=residency, weight_transformation=transformation, drafting=drafting,
+                             required_capabilities={"exact_completion": True, "collectives": tp > 1,
+                                                    "transfers": residency["mode"] != "fully_resident",
+                                                    "persistent_cache": False},
+                             rationale=why)
+        plan.validate()
+        return plan

@@ -1,0 +1,73 @@
+"""Inspection reports, resource estimates, admission and the automatic planner (CPU, no payload I/O)."""
+import dataclasses
+import json
+
+import pytest
+import torch
+
+from eredu_b200.formats import checkpoint as ck
+from eredu_b200.models import config as C
+from eredu_b200.models.llama import random_state
+from eredu_b200.runtime import plan as P
+
+
+def test_inspection_reports(tmp_path):
+    cfg = dataclasses.replace(C.tiny_llama(), vocab_size=512)
+    sd = random_state(cfg, seed=0)
+    ck.save_safetensors_checkpoint(tmp_path / "st", cfg, sd, torch.float32)
+    rep = P.inspect_artifact(tmp_path / "st")
+    assert rep.is_loadable and rep.format == "safetensors" and rep.model_type == "llama"
+    assert rep.parameter_count == sum(v.numel() for v in sd.values()) and rep.dtypes == {"F32": rep.tensor_bytes}
+    assert any(i.code == "no_tokenizer" for i in rep.issues)
+    ck.save_gguf_checkpoint(tmp_path / "m.gguf", cfg, sd, "F32")
+    g = P.inspect_artifact(tmp_path / "m.gguf")
+    assert g.is_loadable and g.format == "gguf" and g.parameter_count == rep.parameter_count
+    # unsupported family and missing tensors are errors, found without touching a payload
+    bad = dataclasses.replace(cfg, model_type="deepseek_v3")
+    ck.save_safetensors_checkpoint(tmp_path / "bad", bad, {k: v for k, v in sd.items() if "embed_tokens" not in k}, torch.float32)
+    b = P.inspect_artifact(tmp_path / "bad")
+    assert not b.is_loadable and {"unsupported_architecture", "missing_tensor"} <= {i.code for i in b.issues}
+    assert not P.inspect_artifact(tmp_path / "nope").is_loadable
+    json.dumps(rep.to_dict())
+
+
+def test_estimates_and_admission():
+    cfg = C.llama3_8b()
+    prof = P.estimate_runtime_state(cfg)
+    assert prof.kv_bytes_per_token == 2 * 8 * 128 * 2 * 32            # 128 KiB per token
+    assert abs(prof.weight_bytes - 16.06e9) < 0.1e9
+    ok = P.apply_admission_policy(prof, 180 * 10**9, context=8192, batch=32)
+    assert ok.admitted and ok.max_context > 8192
+    no = P.apply_admission_policy(prof, 24 * 10**9, context=65536, batch=32)
+    assert not no.admitted and "KV cache" in no.reason
+    moe = P.estimate_runtime_state(C.qwen3_30b_a3b())
+    assert 55e9 < moe.weight_bytes < 65e9 and moe.expert_bytes > 0.9 * moe.weight_bytes * 0.9
+    win = dataclasses.replace(cfg, sliding_window=1024, model_type="mistral")
+    pw = P.estimate_runtime_state(win)
+    assert P.kv_bytes_for(pw, 8192, 1) == 1024 * pw.kv_bytes_per_token
+
+
+def test_planner_choices():
+    hw8 = P.HardwareProfile(device_count=8)
+    planner = P.AutomaticPlanner(hw8)
+    p8b = planner.plan(C.llama3_8b(), P.estimate_runtime_state(C.llama3_8b()), context=4096, batch=32)
+    assert p8b.topology["tensor"] == 1 and p8b.residency["mode"] == "fully_resident"
+    assert p8b.weight_transformation["mode"] == "preserve_checkpoint" and p8b.schema_version == 2
+    c70 = C.llama3_70b()
+    p70 = planner.plan(c70, P.estimate_runtime_state(c70), context=8192, batch=32)
+    assert p70.topology["tensor"] == 2 and p70.required_capabilities["collectives"]
+    moe = C.qwen3_30b_a3b()
+    pm = planner.plan(moe, P.estimate_runtime_state(moe), context=2048, batch=32, prefer_devices=8)
+    assert pm.topology == {"data": 1, "pipeline": 1, "tensor": 8, "expert": 8, "expert_over_tensor": True}
+    one = P.AutomaticPlanner(P.HardwareProfile(device_count=1, device_memory_bytes=80 * 10**9))
+    q = one.plan(c70, P.estimate_runtime_state(c70), context=4096, batch=8)
+    assert q.weight_transformation == {"mode": "affine", "bits": 4, "group_size": 64} and q.topology["tensor"] == 1
+    small = P.AutomaticPlanner(P.HardwareProfile(device_count=1, device_memory_bytes=24 * 10**9))
+    h = small.plan(c70, P.estimate_runtime_state(c70), context=2048, batch=1)
+    assert h.residency["mode"] == "layerwise_host" and h.residency["device_layer_window"] >= 1
+    d = planner.plan(C.llama3_8b(), P.estimate_runtime_state(C.llama3_8b()), draft_model="draft-16l")
+    assert d.drafting["mode"] == "external" and d.drafting["max_draft_tokens"] == 4
+    again = P.ExecutionPlan.from_json(p70.to_json())
+    assert again.topology == p70.topology
+    with pytest.raises(ValueError):
+        P.ExecutionPlan.from_json(p70.to_json().replace('"schema_version": 2', '"schema_version": 1'))
