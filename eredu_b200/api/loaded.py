@@ -38,6 +38,8 @@ class ModelLoadOptions:
     kv_pages: Optional[int] = None
     native_gguf: bool = True                     # keep Q4_K/Q6_K/... blocks and run the native kernels
     use_cuda_graph: Optional[bool] = None
+    weight_residency: str = "device"             # "device" | "layerwise_host" (--layerwise-host)
+    device_layer_window: int = 1                 # layers resident on the device at a time in layerwise_host mode
 
 
 class LoadedModel:
@@ -66,7 +68,22 @@ class LoadedModel:
             from ..ops.quant import make_quantizer
 
             quantizer = make_quantizer(src, opt)
-        model = build_from_tensors(src.cfg, src.get, src.has, device, dtype, opt.parallel, moe_factory, quantizer)
+        residency = None
+        on_layer = None
+        if opt.weight_residency == "layerwise_host":
+            from ..runtime.weight_residency import LayerwiseHostResidency
+
+            def on_layer(m, li, lw):
+                nonlocal residency
+                if residency is None:
+                    residency = LayerwiseHostResidency(m, opt.device_layer_window, defer=True)
+                residency.adopt_layer(lw)
+        elif opt.weight_residency != "device":
+            raise ValueError(f"unknown weight residency {opt.weight_residency!r}")
+        model = build_from_tensors(src.cfg, src.get, src.has, device, dtype, opt.parallel, moe_factory, quantizer,
+                                   on_layer=on_layer)
+        if residency is not None:
+            residency.finalize()
         if opt.parallel is not None and opt.parallel.tp_size > 1:
             from ..parallel import tp
 

@@ -124,7 +124,9 @@ def main(argv=None) -> int:
         quant = QuantizationOptions(bits=bits, group_size=a.quantization_group_size, mode=a.quantization_mode)
     t0 = time.perf_counter()
     lm = LoadedModel.load(model_path, ModelLoadOptions(device=device, quantization=quant, mapped_shards=a.mapped_shards,
-                                                       max_batch=1, max_seq_len=max(4096, a.max_tokens + 2048)))
+                                                       max_batch=1, max_seq_len=max(4096, a.max_tokens + 2048),
+                                                       weight_residency="layerwise_host" if a.layerwise_host else "device",
+                                                       device_layer_window=a.device_layer_window))
     load_time = time.perf_counter() - t0
     gen_cfg = lm.tokenizer.generation_config if lm.tokenizer else {}
     sp = resolve_sampling(a, gen_cfg)

@@ -88,6 +88,7 @@ class CausalLM:
         self.scale = 1.0 / math.sqrt(cfg.head_dim)
         self.tp_ops = None  # set by parallel.tp when tp_size > 1
         self.head_folded = False
+        self.residency = None  # set by runtime.weight_residency when the layers live in host memory
 
     # ------------------------------------------------------------------------------------------ layer
     def _linear(self, lw: LayerWeights, role: str, x, w, bias=None, residual=None):
@@ -186,7 +187,11 @@ class CausalLM:
         n = len(self.layers)
         for i, lw in enumerate(self.layers):
             nxt = self.layers[i + 1].fold_attn if i + 1 < n else (self.head_folded and self.par.owns_output_head())
+            if self.residency is not None:
+                self.residency.acquire(i)
             h, ssq = self.layer_forward(self.first_layer + i, lw, h, batch, kv, ssq, nxt)
+            if self.residency is not None:
+                self.residency.release(i)
         return h, ssq
 
     def logits(self, h, rows=None, ssq=None):
@@ -220,12 +225,7 @@ class CausalLM:
         GEMM epilogue. Dense bf16 weights on CUDA only; quantised and MoE consumers keep the explicit kernel."""
         off = self.cfg.norm_weight_offset
         for lw in self.layers:
-            if "qkv" not in lw.qlin and not lw.fold_attn:
-                lw.wqkv = (lw.wqkv.float() * (lw.attn_norm + off)[None, :]).to(self.dtype).contiguous()
-                lw.fold_attn = True
-            if lw.moe is None and "gate_up" not in lw.qlin and lw.w_gate_up is not None and not lw.fold_ffn:
-                lw.w_gate_up = (lw.w_gate_up.float() * (lw.ffn_norm + off)[None, :]).to(self.dtype).contiguous()
-                lw.fold_ffn = True
+            self.fold_layer_norms(lw)
         if self.lm_head is not None and self.final_norm is not None and not self.head_folded:
             folded = torch.empty_like(self.lm_head)
             step = 16384
@@ -233,6 +233,15 @@ class CausalLM:
                 folded[r0:r0 + step] = (self.lm_head[r0:r0 + step].float() * (self.final_norm + off)[None, :]).to(self.dtype)
             self.lm_head = folded  # a separate tensor even when the head was tied to the embedding
             self.head_folded = True
+
+    def fold_layer_norms(self, lw) -> None:
+        off = self.cfg.norm_weight_offset
+        if "qkv" not in lw.qlin and not lw.fold_attn and lw.wqkv is not None:
+            lw.wqkv = (lw.wqkv.float() * (lw.attn_norm + off)[None, :]).to(self.dtype).contiguous()
+            lw.fold_attn = True
+        if lw.moe is None and "gate_up" not in lw.qlin and lw.w_gate_up is not None and not lw.fold_ffn:
+            lw.w_gate_up = (lw.w_gate_up.float() * (lw.ffn_norm + off)[None, :]).to(self.dtype).contiguous()
+            lw.fold_ffn = True
 
     # ------------------------------------------------------------------------------------------ weights
     def num_local_layers(self) -> int:
@@ -294,7 +303,7 @@ def shard_attention(cfg: ModelConfig, par, wq, wk, wv, wo, bq=None, bk=None, bv=
 
 
 def build_from_tensors(cfg: ModelConfig, get: Callable[[str], torch.Tensor], has: Callable[[str], bool], device, dtype,
-                       parallel=None, moe_factory=None, quantizer=None, fold_norms: bool = True) -> CausalLM:
+                       parallel=None, moe_factory=None, quantizer=None, fold_norms: bool = True, on_layer=None) -> CausalLM:
     """Populate a model from HF-named tensors. ``get(name)`` returns a CPU (or device) tensor; slicing for
     tensor/pipeline parallelism happens here so that a rank only uploads what it owns."""
     model = CausalLM(cfg, device, dtype, parallel)
@@ -351,6 +360,11 @@ def build_from_tensors(cfg: ModelConfig, get: Callable[[str], torch.Tensor], has
         if quantizer is not None:
             quantizer(model, li, lw)
         model.layers.append(lw)
+        if on_layer is not None:
+            # the caller takes the layer away (host residency): fold its norms while it is still on the device
+            if model.device.type == "cuda" and dtype == torch.bfloat16 and fold_norms:
+                model.fold_layer_norms(lw)
+            on_layer(model, li, lw)
     if model.device.type == "cuda" and dtype == torch.bfloat16 and fold_norms:
         model.fold_norms()
     return model

@@ -388,7 +388,10 @@ class Engine:
         if host_tokens is not None:
             st["token_ids"].copy_(host_tokens, non_blocking=True)
         if self.use_graph:
-            if st["graph"] is None:
+            if getattr(self.model, "residency", None) is not None:
+                # host-resident layers stream through device slots on a copy stream: the step runs eagerly
+                self._decode_body(st)
+            elif st["graph"] is None:
                 # warm-up run outside capture (lazy kernel attribute setup), then restore the state it advanced
                 saved = {k: st[k].clone() for k in ("token_ids", "positions", "seq_lens", "slots", "rows")}
                 saved_h = st["history"].clone() if st["history"] is not None else None
@@ -409,7 +412,8 @@ class Engine:
                 st["graph"] = g
                 if "graphs" in st:
                     st["graphs"][st["all_greedy"]] = g
-            st["graph"].replay()
+            if getattr(self.model, "residency", None) is None:
+                st["graph"].replay()
         else:
             self._decode_body(st)
         if not sync:

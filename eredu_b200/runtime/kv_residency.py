@@ -1,0 +1,164 @@
+"""KV-cache residency: a pinned host tier behind the device page pool.
+
+Counterpart of ``CacheResidencyPolicy::Paged(PagedCacheOptions{block_size_tokens, device_budget_bytes,
+host_budget_bytes, recent_device_blocks, eviction, ...})`` and the ``CacheResidencyManager`` (eredu/src/backend/mlx/
+runtime/cache/residency.rs:60-135 options; block store, tiers, transfer stream, leases) together with the portable
+accounting of eredu-core/src/cache.rs:48-450 (device / host / transfer byte reservations) and cache/storage.rs (the
+device <-> host phase machine).
+
+Unit of transfer: all pages of one sequence ("park" / "resume"). Parking gathers the sequence's pages of every layer
+into one contiguous staging tensor on the device (a single gather kernel per pool), copies it to pinned host memory
+on a transfer stream and returns the device pages to the pool; resuming allocates fresh device pages and scatters
+the data back. The page ids change, the contents do not: a resumed sequence continues bit-identically.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from .kv_cache import PAGE
+
+
+@dataclass
+class PagedCacheOptions:
+    block_size_tokens: int = PAGE
+    device_budget_bytes: Optional[int] = None
+    host_budget_bytes: Optional[int] = None
+    recent_device_blocks: int = 0        # newest blocks of a parked sequence that stay on the device (0 = none)
+    eviction: str = "lru"                # which running sequence is parked first under pressure: lru | largest
+
+
+@dataclass
+class ParkedSequence:
+    k_host: torch.Tensor                 # [layers, pages, n_kv, PAGE, D] pinned
+    v_host: torch.Tensor
+    pages: int
+    reserved_pages: int                  # pages the sequence had reserved (prompt + budget), restored on resume
+    event: object = None                 # transfer completion (CUDA event) or None
+
+
+class KVHostTier:
+    def __init__(self, engine, options: Optional[PagedCacheOptions] = None):
+        self.engine = engine
+        self.kv = engine.kv
+        self.opt = options or PagedCacheOptions()
+        if self.opt.block_size_tokens != PAGE:
+            raise ValueError(f"the device pool uses {PAGE}-token pages")
+        self.cuda = engine.cuda
+        self.stream = torch.cuda.Stream(device=engine.device) if self.cuda else None
+        self.parked: dict[int, ParkedSequence] = {}
+        self.host_bytes = 0
+        self.stats = {"parked": 0, "resumed": 0, "bytes_to_host": 0, "bytes_to_device": 0, "refused": 0}
+        self._clock = 0
+        self._last_use: dict[int, int] = {}
+
+    # ------------------------------------------------------------------------------------------ accounting
+    def page_bytes(self) -> int:
+        k = self.kv.k
+        return 2 * k.shape[0] * k.shape[2] * k.shape[3] * k.shape[4] * k.element_size()
+
+    def touch(self, seq) -> None:
+        self._clock += 1
+        self._last_use[seq.seq_id] = self._clock
+
+    def victim(self, candidates):
+        """The sequence to park first among ``candidates`` under the configured policy."""
+        cands = [s for s in candidates if s.pages and s.seq_id not in self.parked]
+        if not cands:
+            return None
+        if self.opt.eviction == "largest":
+            return max(cands, key=lambda s: s.kv_len)
+        return min(cands, key=lambda s: self._last_use.get(s.seq_id, 0))
+
+    # ------------------------------------------------------------------------------------------ park / resume
+    @torch.no_grad()
+    def park(self, seq) -> bool:
+        """Move the sequence's cached pages to the host tier and free its device pages. False when the host budget
+        would be exceeded (nothing changes)."""
+        if seq.seq_id in self.parked:
+            return True
+        used = (seq.kv_len + PAGE - 1) // PAGE
+        nbytes = used * self.page_bytes()
+        if self.opt.host_budget_bytes is not None and self.host_bytes + nbytes > self.opt.host_budget_bytes:
+            self.stats["refused"] += 1
+            return False
+        dev = self.engine.device
+        idx = torch.as_tensor(seq.pages[:used], dtype=torch.long, device=dev)
+        shape = (self.kv.k.shape[0], used) + tuple(self.kv.k.shape[2:])
+        pin = self.cuda
+        k_host = torch.empty(shape, dtype=self.kv.k.dtype, pin_memory=pin)
+        v_host = torch.empty(shape, dtype=self.kv.v.dtype, pin_memory=pin)
+        event = None
+        if used:
+            k_stage = self.kv.k.index_select(1, idx)     # gather on the compute stream: ordered after the last step
+            v_stage = self.kv.v.index_select(1, idx)
+            if self.cuda:
+                ready = torch.cuda.Event()
+                ready.record(torch.cuda.current_stream(dev))
+                with torch.cuda.stream(self.stream):
+                    self.stream.wait_event(ready)
+                    k_host.copy_(k_stage, non_blocking=True)
+                    v_host.copy_(v_stage, non_blocking=True)
+                    k_stage.record_stream(self.stream)
+                    v_stage.record_stream(self.stream)
+                    event = torch.cuda.Event()
+                    event.record(self.stream)
+            else:
+                k_host.copy_(k_stage)
+                v_host.copy_(v_stage)
+        self.parked[seq.seq_id] = ParkedSequence(k_host, v_host, used, len(seq.pages), event)
+        self.engine.kv.allocator.release(seq.pages)
+        seq.pages = []
+        self.host_bytes += nbytes
+        self.stats["parked"] += 1
+        self.stats["bytes_to_host"] += nbytes
+        return True
+
+    @torch.no_grad()
+    def resume(self, seq) -> bool:
+        """Bring a parked sequence back. False when the device pool has too few free pages (it stays parked)."""
+        p = self.parked.get(seq.seq_id)
+        if p is None:
+            return True
+        if self.kv.allocator.free_pages() < p.reserved_pages:
+            self.stats["refused"] += 1
+            return False
+        pages = list(self.kv.allocator.alloc(p.reserved_pages))
+        dev = self.engine.device
+        if p.pages:
+            idx = torch.as_tensor(pages[:p.pages], dtype=torch.long, device=dev)
+            if self.cuda:
+                with torch.cuda.stream(self.stream):
+                    if p.event is not None:
+                        self.stream.wait_event(p.event)
+                    k_dev = p.k_host.to(dev, non_blocking=True)
+                    v_dev = p.v_host.to(dev, non_blocking=True)
+                    done = torch.cuda.Event()
+                    done.record(self.stream)
+                torch.cuda.current_stream(dev).wait_event(done)
+                k_dev.record_stream(torch.cuda.current_stream(dev))
+                v_dev.record_stream(torch.cuda.current_stream(dev))
+            else:
+                k_dev, v_dev = p.k_host, p.v_host
+            self.kv.k.index_copy_(1, idx, k_dev)
+            self.kv.v.index_copy_(1, idx, v_dev)
+        seq.pages = pages
+        nbytes = p.pages * self.page_bytes()
+        self.host_bytes -= nbytes
+        self.stats["resumed"] += 1
+        self.stats["bytes_to_device"] += nbytes
+        del self.parked[seq.seq_id]
+        self.touch(seq)
+        return True
+
+    def drop(self, seq) -> None:
+        """Forget a parked sequence (cancelled while parked)."""
+        p = self.parked.pop(seq.seq_id, None)
+        if p is not None:
+            self.host_bytes -= p.pages * self.page_bytes()
+
+    def report(self) -> dict:
+        return dict(self.stats, parked_now=len(self.parked), host_bytes=self.host_bytes,
+                    device_free_pages=self.kv.allocator.free_pages())

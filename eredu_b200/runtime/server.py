@@ -72,9 +72,11 @@ class ServedRequest:
 
 class Server:
     def __init__(self, engine: Engine, transport=None, max_step_tokens: int = 8192, max_waiting: int = 1024,
-                 prefill_chunk: int = 2048, penalties: bool = False, fault_hook: Optional[Callable[[str, int], bool]] = None):
+                 prefill_chunk: int = 2048, penalties: bool = False, fault_hook: Optional[Callable[[str, int], bool]] = None,
+                 kv_tier=None):
         self.engine = engine
         self.transport = transport
+        self.kv_tier = kv_tier   # KVHostTier: running requests are parked in host memory when the page pool runs out
         self.sched = H.Scheduler(engine.max_batch, max_step_tokens, max_waiting, prefill_chunk)
         self.requests: dict[int, ServedRequest] = {}
         self.drain_cycle = 0
@@ -86,12 +88,29 @@ class Server:
                on_token=None, deadline: float = 0.0) -> int:
         rid = int(self.sched.submit(len(prompt), max_new_tokens, deadline))
         try:
-            seq = self.engine.new_sequence(prompt, sampling, max_new_tokens, eos_ids)
+            seq = self._new_sequence_under_pressure(prompt, sampling, max_new_tokens, eos_ids)
         except Exception:
             self.sched.cancel(rid)
             raise
         self.requests[rid] = ServedRequest(rid, seq, on_token, submit_time=time.perf_counter())
         return rid
+
+    def _new_sequence_under_pressure(self, prompt, sampling, max_new_tokens, eos_ids):
+        """Reserve pages for a new request; when the pool is exhausted and a host tier exists, park running
+        requests (policy: the tier's eviction order) until the reservation succeeds."""
+        while True:
+            try:
+                return self.engine.new_sequence(prompt, sampling, max_new_tokens, eos_ids)
+            except (MemoryError, RuntimeError) as e:
+                if self.kv_tier is None or (isinstance(e, RuntimeError) and "exhausted" not in str(e)):
+                    raise
+                running = [r.seq for r in self.requests.values() if r.seq.slot >= 0 and not r.seq.finished]
+                victim = self.kv_tier.victim(running)
+                if victim is None:
+                    raise
+                self.engine.leave(victim)
+                if not self.kv_tier.park(victim):
+                    raise
 
     def cancel(self, request_id: int) -> None:
         self.sched.cancel(request_id)
@@ -158,6 +177,18 @@ class Server:
         # ---- one decode step for every planned running request
         if decodes:
             planned = {int(w.request_id): w for w in decodes}
+            if self.kv_tier is not None:
+                # parked requests come back when pages and a slot are free; otherwise they make no progress this step
+                for rid in list(planned):
+                    r = self.requests[rid]
+                    if r.seq.seq_id in self.kv_tier.parked:
+                        if eng.free_slots() and self.kv_tier.resume(r.seq):
+                            eng.join(r.seq, r.tokens[-1])
+                        else:
+                            status[int(planned[rid].work_id)] = (0, 0, False, False)
+                            del planned[rid]
+                for rid in planned:
+                    self.kv_tier.touch(self.requests[rid].seq)
             st = eng._decode_state
             mask = [s is not None and any(r.seq is s for r in (self.requests[i] for i in planned)) for s in st["seqs"]]
             eng.set_step_mask(mask)
@@ -217,7 +248,10 @@ class Server:
     def _retire_terminal(self) -> None:
         """Free the slot and the pages of every request the scheduler has finished, cancelled or failed."""
         for rid, r in self.requests.items():
-            if r.seq.pages and self.sched.request(rid)["state"] in ("finished", "cancelled", "failed"):
+            parked = self.kv_tier is not None and r.seq.seq_id in self.kv_tier.parked
+            if (r.seq.pages or parked) and self.sched.request(rid)["state"] in ("finished", "cancelled", "failed"):
+                if parked:
+                    self.kv_tier.drop(r.seq)
                 state = self.sched.request(rid)
                 if r.finish_reason is None:
                     r.finish_reason = state["finish_reason"] or state["state"]
