@@ -98,5 +98,23 @@ def chain():
                           "us_per_gemm": round(_chain(32, 1792, 4096, 0, 0, split, dual=True), 2)}))
 
 
+def one(M: int, N: int, K: int, kind: str = "residual", reps: int = 3):
+    """A single shape, a few launches: the small case a profiler capture runs on (operands above the 126 MB L2 for
+    the sizes used in profiles/)."""
+    g = torch.Generator(device=DEV).manual_seed(0)
+    x = (torch.randn(M, K, device=DEV, generator=g) * 0.5).bfloat16()
+    w = (torch.randn(N * 2 if kind == "swiglu" else N, K, device=DEV, generator=g) * 0.03).bfloat16()
+    r = torch.randn(M, N, device=DEV, generator=g).bfloat16() if kind == "residual" else None
+    fn = (lambda: ops.gated_linear(x, w, N)) if kind == "swiglu" else (lambda: ops.linear(x, w, residual=r))
+    us = _time(fn, n=reps, warm=2)
+    flops = 2 * M * N * K * (2 if kind == "swiglu" else 1)
+    print(json.dumps({"M": M, "N": N, "K": K, "epilogue": kind, "us": round(us, 1), "tflops": round(flops / us / 1e6, 1),
+                      "weight_GBs": round(w.numel() * 2 / us / 1e3, 1)}))
+
+
 if __name__ == "__main__":
-    {"prefill": prefill, "chain": chain}[sys.argv[1] if len(sys.argv) > 1 else "prefill"]()
+    mode = sys.argv[1] if len(sys.argv) > 1 else "prefill"
+    if mode == "one":
+        one(int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4]), sys.argv[5] if len(sys.argv) > 5 else "residual")
+    else:
+        {"prefill": prefill, "chain": chain}[mode]()
