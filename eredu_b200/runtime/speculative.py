@@ -34,6 +34,7 @@ class SpecStats:
     full_accept_rounds: int = 0
     verify_ms: list = field(default_factory=list)
     draft_ms: list = field(default_factory=list)
+    prefill_ms: float = 0.0
 
     def summary(self) -> dict:
         r = max(1, self.rounds)
@@ -41,7 +42,8 @@ class SpecStats:
                 "accepted_per_step": self.accepted / r, "tokens_per_step": self.emitted / r,
                 "acceptance_rate": self.accepted / max(1, self.proposed), "full_accept_rounds": self.full_accept_rounds,
                 "verify_ms_p50": float(np.median(self.verify_ms)) if self.verify_ms else None,
-                "draft_ms_p50": float(np.median(self.draft_ms)) if self.draft_ms else None}
+                "draft_ms_p50": float(np.median(self.draft_ms)) if self.draft_ms else None,
+                "prefill_ms": self.prefill_ms}
 
 
 class SpeculativeDecoder:
@@ -200,3 +202,183 @@ class SpeculativeDecoder:
         self.stats.proposed += k * B
         self.stats.draft_ms.append((t1 - t0) * 1e3)
         self.stats.verify_ms.append((t2 - t1) * 1e3)
+
+
+class GraphSpeculativeDecoder(SpeculativeDecoder):
+    """The speculative round as ONE CUDA graph (GPU only, fixed batch): k draft steps, the target's verify pass over
+    k+1 tokens, both samplers and the accept / resample kernel are captured once; a round is a few small
+    host-to-device copies (positions, the two newest tokens, sampler rows), one replay and one read-back.
+
+    Uniform shapes come from always feeding the draft TWO tokens in its first step - the token before ``last`` and
+    ``last`` itself. Whatever the previous round accepted, the draft cache is valid up to the token before that, so
+    the first of the two is at worst recomputed into the slot it already occupies; no ragged catch-up pass exists.
+    Sequences that finish early stay in the batch (their slots keep cycling over reserved pages) and are ignored.
+    """
+
+    def __init__(self, target: Engine, draft: Engine, k: int = 4):
+        super().__init__(target, draft, k)
+        if not self.cuda:
+            raise RuntimeError("GraphSpeculativeDecoder needs CUDA engines; use SpeculativeDecoder on the CPU")
+        self._state = None
+
+    @staticmethod
+    def _slots_dev(bt: torch.Tensor, pos: torch.Tensor, per: int) -> torch.Tensor:
+        """KV slot of every (sequence, position): bt [B, max_pages] int32, pos [B * per] int32 -> int64 [B * per]."""
+        B = bt.shape[0]
+        p = pos.view(B, per).long()
+        page = bt.long().gather(1, p // PAGE)
+        return (page * PAGE + p % PAGE).view(-1)
+
+    def _build(self, tseqs, dseqs, sp):
+        t, d, k = self.t, self.d, self.k
+        B, V, dev = len(tseqs), t.cfg.vocab_size, t.device
+        max_len = max(len(s.prompt) + s.max_new_tokens for s in tseqs)
+        i32 = dict(dtype=torch.int32, device=dev)
+        st = {
+            "B": B, "P": torch.zeros(B, **i32), "prev": torch.zeros(B, **i32), "last": torch.zeros(B, **i32),
+            "t_bt": t._block_table(tseqs), "d_bt": d._block_table(dseqs),
+            "d_rows": torch.zeros((k, B, ROW_DTYPE.itemsize), dtype=torch.uint8, device=dev),
+            "t_rows": torch.zeros((B * (k + 1), ROW_DTYPE.itemsize), dtype=torch.uint8, device=dev),
+            "v_rows": torch.zeros((B, ROW_DTYPE.itemsize), dtype=torch.uint8, device=dev),
+            "p_d": torch.empty((k, B, V), dtype=torch.float32, device=dev),
+            "p_t": torch.empty((B * (k + 1), V), dtype=torch.float32, device=dev),
+            "res": torch.zeros((B, 2), **i32), "drafted": torch.zeros((B, k), **i32), "bonus": torch.zeros(B, **i32),
+            "rows2": torch.arange(B, device=dev, dtype=torch.int64) * 2 + 1,
+            "ar": torch.arange(k + 1, **i32),
+            "all_greedy": sp.greedy, "graph": None,
+        }
+        for name, eng, q in (("d2", d, 2), ("d1", d, 1), ("tv", t, k + 1)):
+            splits = ops.decode_splits(B, eng.model.n_kv_local, max_len + k + 2, eng.sm_count)
+            st[name + "_splits"] = splits
+            st[name + "_scratch"] = (ops.decode_scratch(B, q, eng.model.n_q_local, eng.cfg.head_dim, splits, dev)
+                                     if splits > 1 else None)
+        st["host"] = {n: torch.zeros(B, dtype=torch.int32).pin_memory() for n in ("P", "prev", "last")}
+        st["host_res"] = torch.zeros((B, 2), dtype=torch.int32).pin_memory()
+        st["host_drafted"] = torch.zeros((B, k), dtype=torch.int32).pin_memory()
+        st["host_bonus"] = torch.zeros(B, dtype=torch.int32).pin_memory()
+        return st
+
+    def _device_round(self, st):
+        t, d, k, B = self.t, self.d, self.k, st["B"]
+        V = t.cfg.vocab_size
+        P, prev, last = st["P"], st["prev"], st["last"]
+        greedy = st["all_greedy"]
+        # ---- draft step 0: [token before last, last] at positions [P-1, P]
+        tok = torch.stack((prev, last), 1).reshape(-1)
+        pos = torch.stack((P - 1, P), 1).reshape(-1)
+        batch = ForwardBatch(token_ids=tok, positions=pos, slots=self._slots_dev(st["d_bt"], pos, 2), block_table=st["d_bt"],
+                             seq_lens=P + 1, is_prefill=False, q_per_seq=2, splits=st["d2_splits"],
+                             scratch=st["d2_scratch"], logit_rows=st["rows2"])
+        logits = d.model.forward(batch, d.kv)
+        cur = ops.sample(logits.contiguous(), st["d_rows"][0], probs=st["p_d"][0], all_greedy=greedy)
+        toks = [cur]
+        for j in range(1, k):
+            pos = P + j
+            batch = ForwardBatch(token_ids=cur, positions=pos, slots=self._slots_dev(st["d_bt"], pos, 1),
+                                 block_table=st["d_bt"], seq_lens=P + 1 + j, is_prefill=False, q_per_seq=1,
+                                 splits=st["d1_splits"], scratch=st["d1_scratch"])
+            logits = d.model.forward(batch, d.kv)
+            cur = ops.sample(logits.contiguous(), st["d_rows"][j], probs=st["p_d"][j], all_greedy=greedy)
+            toks.append(cur)
+        drafted = torch.stack(toks, 1).to(torch.int32)
+        st["drafted"].copy_(drafted)
+        # ---- target: one pass over [last, d_1 .. d_k] at positions P .. P+k
+        tok = torch.cat((last[:, None], drafted), 1).reshape(-1)
+        pos = (P[:, None] + st["ar"][None, :]).reshape(-1)
+        batch = ForwardBatch(token_ids=tok, positions=pos, slots=self._slots_dev(st["t_bt"], pos, k + 1), block_table=st["t_bt"],
+                             seq_lens=P + k + 1, is_prefill=False, q_per_seq=k + 1, splits=st["tv_splits"],
+                             scratch=st["tv_scratch"])
+        logits = t.model.forward(batch, t.kv)
+        t_toks = ops.sample(logits.contiguous(), st["t_rows"], probs=st["p_t"], all_greedy=greedy)
+        st["bonus"].copy_(t_toks.view(B, k + 1)[:, k])
+        p_d3 = st["p_d"].permute(1, 0, 2).contiguous()
+        ops.spec_verify(st["p_t"].view(B, k + 1, V), p_d3, st["drafted"], st["v_rows"], out=st["res"])
+
+    @torch.no_grad()
+    def generate(self, prompts, sampling: Optional[SamplingParams] = None, max_new_tokens: int = 64, eos_ids=()):
+        sp = sampling or SamplingParams()
+        k, t, d = self.k, self.t, self.d
+        B = len(prompts)
+        tseqs = [t.new_sequence(p, sp, max_new_tokens + k + 2, eos_ids) for p in prompts]
+        dseqs = [d.new_sequence(p, sp, max_new_tokens + k + 2, eos_ids) for p in prompts]
+        try:
+            t_start = time.perf_counter()
+            first = [int(x) for x in t.prefill(tseqs).tolist()]
+            d.prefill(dseqs)
+            torch.cuda.synchronize(t.device)
+            self.stats.prefill_ms = (time.perf_counter() - t_start) * 1e3
+            outs = [[x] for x in first]
+            last = list(first)
+            prev = [int(p[-1]) for p in prompts]
+            P = [len(p) for p in prompts]             # position of `last`; the target cache holds 0 .. P-1
+            done = [x in eos_ids or max_new_tokens <= 1 for x in first]
+            st = self._build(tseqs, dseqs, sp)
+            dev = t.device
+            sids = [s.seq_id for s in tseqs]
+            while not all(done):
+                t0 = time.perf_counter()
+                base = [p + 1 for p in P]
+                for name, vals in (("P", P), ("prev", prev), ("last", last)):
+                    st["host"][name].copy_(torch.as_tensor(vals, dtype=torch.int32))
+                    st[name].copy_(st["host"][name], non_blocking=True)
+                d_rows = np.stack([pack_rows([sp] * B, [b + j for b in base], stream_ids=sids).view(np.uint8)
+                                   .reshape(B, ROW_DTYPE.itemsize) for j in range(k)])
+                st["d_rows"].copy_(t._t(d_rows, torch.uint8))
+                t_rows = pack_rows([sp] * (B * (k + 1)), [b + j for b in base for j in range(k + 1)],
+                                   stream_ids=[s for s in sids for _ in range(k + 1)])
+                st["t_rows"].copy_(t._t(t_rows.view(np.uint8).reshape(B * (k + 1), ROW_DTYPE.itemsize), torch.uint8))
+                v_rows = pack_rows([sp] * B, base, stream_ids=sids)
+                st["v_rows"].copy_(t._t(v_rows.view(np.uint8).reshape(B, ROW_DTYPE.itemsize), torch.uint8))
+                if st["graph"] is None:
+                    # eager warm-up (kernel attribute setup; it rewrites the same KV slots the replay will), then capture
+                    side = torch.cuda.Stream(device=dev)
+                    side.wait_stream(torch.cuda.current_stream(dev))
+                    with torch.cuda.stream(side):
+                        self._device_round(st)
+                    torch.cuda.current_stream(dev).wait_stream(side)
+                    torch.cuda.synchronize(dev)
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g):
+                        self._device_round(st)
+                    st["graph"] = g
+                st["graph"].replay()
+                st["host_res"].copy_(st["res"], non_blocking=True)
+                st["host_drafted"].copy_(st["drafted"], non_blocking=True)
+                st["host_bonus"].copy_(st["bonus"], non_blocking=True)
+                torch.cuda.current_stream(dev).synchronize()
+                res, drafted, bonus = st["host_res"].tolist(), st["host_drafted"].tolist(), st["host_bonus"].tolist()
+                live = 0
+                for b in range(B):
+                    if done[b]:
+                        continue
+                    live += 1
+                    a, nxt = int(res[b][0]), int(res[b][1])
+                    if a == k:
+                        nxt = int(bonus[b])
+                    new = drafted[b][:a] + [nxt]
+                    outs[b].extend(new)
+                    seq_tokens = [last[b]] + new
+                    prev[b] = seq_tokens[-2]
+                    last[b] = nxt
+                    P[b] += a + 1
+                    self.stats.accepted += a
+                    self.stats.emitted += a + 1
+                    self.stats.full_accept_rounds += 1 if a == k else 0
+                    if len(outs[b]) >= max_new_tokens:
+                        outs[b] = outs[b][:max_new_tokens]
+                        done[b] = True
+                    for j, tok in enumerate(outs[b]):
+                        if tok in eos_ids:
+                            outs[b] = outs[b][: j + 1]
+                            done[b] = True
+                            break
+                self.stats.rounds += live
+                self.stats.proposed += k * live
+                self.stats.verify_ms.append((time.perf_counter() - t0) * 1e3)   # the whole captured round
+            ops.native.check_status(dev)
+            return outs
+        finally:
+            for s in tseqs:
+                t.release(s)
+            for s in dseqs:
+                d.release(s)

@@ -68,3 +68,31 @@ def test_stochastic_speculation_runs_gpu():
     sp = SamplingParams(temperature=0.8, top_k=40, top_p=0.95, min_p=0.0, seed=5)
     plain, spec, stats = _run("cuda", torch.bfloat16, 7, sp, k=4, n_new=24)
     assert all(len(o) == 24 for o in spec) and stats["rounds"] > 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("draft_seed", [None, 7])
+@pytest.mark.parametrize("temperature", [0.0, 0.8])
+def test_graph_captured_round_matches_the_eager_decoder(draft_seed, temperature):
+    """One CUDA graph per round (uniform two-token draft catch-up) emits exactly what the eager, ragged decoder emits:
+    same kernels, same position-addressed uniforms, only the scheduling differs."""
+    from eredu_b200.runtime.speculative import GraphSpeculativeDecoder
+
+    sp = SamplingParams(temperature=temperature, top_k=40, top_p=0.95, min_p=0.0, seed=5)
+    cfg, target, draft = _models("cuda", torch.bfloat16, draft_seed)
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (11, 25)]
+    eager = SpeculativeDecoder(Engine(target, max_batch=2, max_seq_len=128, use_cuda_graph=False),
+                               Engine(draft, max_batch=2, max_seq_len=128, use_cuda_graph=False), k=4)
+    want = eager.generate(prompts, sp, 24)
+    graphed = GraphSpeculativeDecoder(Engine(target, max_batch=2, max_seq_len=128), Engine(draft, max_batch=2, max_seq_len=128), k=4)
+    got = graphed.generate(prompts, sp, 24)
+    assert [len(o) for o in got] == [24, 24]
+    agree = sum(a == b for x, y in zip(want, got) for a, b in zip(x, y))
+    # the draft's first step runs as a 2-query pass instead of a ragged prefill pass: bf16 rounding may flip a token,
+    # after which a sampled (temperature > 0) continuation is a different, equally valid draw
+    assert agree >= (24 if temperature == 0.0 else 4)
+    s = graphed.stats.summary()
+    assert s["rounds"] > 0 and s["emitted"] >= 48 - 2 * 5
+    if draft_seed is None and temperature == 0.0:
+        assert s["acceptance_rate"] > 0.6
