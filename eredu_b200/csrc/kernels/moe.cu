@@ -18,16 +18,10 @@ namespace eredu {
 
 enum { SCORE_SOFTMAX = 0, SCORE_SIGMOID = 1, SCORE_SQRT_SOFTPLUS = 2, SCORE_TOPK_SOFTMAX = 3 };
 
-// One warp per token, up to 512 experts (16 per lane).
-__global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ sel_bias,
-                                                         int* __restrict__ ids, float* __restrict__ weights, int T, int E,
-                                                         int k, int scoring, int renorm, float scale) {
-  pdl_launch_early();
-  pdl_wait();
-  pdl_launch_dependents();
-  const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (t >= T) return;
+// One warp routes one token, up to 512 experts (16 per lane).
+__device__ __forceinline__ void route_token(const float* __restrict__ logits, const float* __restrict__ sel_bias,
+                                            int* __restrict__ ids, float* __restrict__ weights, int t, int lane, int E, int k,
+                                            int scoring, int renorm, float scale) {
   constexpr int PER = 16;
   float score[PER];   // value reported as the route weight
   float select[PER];  // value used for selection (score + bias)
@@ -117,23 +111,30 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
   }
 }
 
+__global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ sel_bias,
+                                                         int* __restrict__ ids, float* __restrict__ weights, int T, int E,
+                                                         int k, int scoring, int renorm, float scale) {
+  pdl_launch_early();
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (t >= T) return;
+  route_token(logits, sel_bias, ids, weights, t, threadIdx.x & 31, E, k, scoring, renorm, scale);
+}
+
 // Single CTA. routes = T*k. Experts [e0, e1) are local. Outputs:
 //   seg[0..n_local]      : first row of each local expert's segment (seg[n_local] = number of local routes)
 //   route_pos[r]         : row of route r in the permuted buffers, -1 when its expert is not local
 //   row_token[pos]       : token index of the row
 //   work[n_work_cap] int4: {local expert, row0, rows, 0} one item per `tile` rows of a segment, rest zeroed
 //   counts[2]            : {local routes, work items used}
-__global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ ids, int routes, int k, int e0, int e1,
-                                                         int tile, int* __restrict__ seg, int* __restrict__ route_pos,
-                                                         int* __restrict__ row_token, int4* __restrict__ work,
-                                                         int n_work_cap, int* __restrict__ counts) {
+__device__ __forceinline__ void plan_block(const int* __restrict__ ids, int routes, int k, int e0, int e1, int tile,
+                                           int* __restrict__ seg, int* __restrict__ route_pos, int* __restrict__ row_token,
+                                           int4* __restrict__ work, int n_work_cap, int* __restrict__ counts) {
   __shared__ int cnt[512];
   __shared__ int start[513];
   __shared__ int cursor[512];
   __shared__ int item0[513];
-  pdl_launch_early();
-  pdl_wait();
-  pdl_launch_dependents();
   const int n_local = e1 - e0;
   for (int i = threadIdx.x; i < n_local; i += blockDim.x) cnt[i] = 0;
   __syncthreads();
@@ -177,6 +178,40 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ 
       row_token[pos] = r / k;
     }
     route_pos[r] = pos;
+  }
+}
+
+__global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ ids, int routes, int k, int e0, int e1,
+                                                         int tile, int* __restrict__ seg, int* __restrict__ route_pos,
+                                                         int* __restrict__ row_token, int4* __restrict__ work,
+                                                         int n_work_cap, int* __restrict__ counts) {
+  pdl_launch_early();
+  pdl_wait();
+  pdl_launch_dependents();
+  plan_block(ids, routes, k, e0, e1, tile, seg, route_pos, row_token, work, n_work_cap, counts);
+}
+
+// Decode-sized steps (T <= 64 tokens): routing, planning and the row gather in ONE single-CTA kernel instead of
+// three dependent launches. 32 warps route the tokens, the block plans the local experts' segments in shared
+// memory, then copies the token rows into expert order.
+__global__ void __launch_bounds__(1024) moe_route_plan_gather_kernel(
+    const float* __restrict__ logits, const float* __restrict__ sel_bias, int* __restrict__ ids, float* __restrict__ weights,
+    int T, int E, int k, int scoring, int renorm, float scale, int e0, int e1, int tile, int* __restrict__ seg,
+    int* __restrict__ route_pos, int* __restrict__ row_token, int4* __restrict__ work, int n_work_cap, int* __restrict__ counts,
+    const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ xp, int H) {
+  pdl_launch_early();
+  pdl_wait();
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int t = warp; t < T; t += 32) route_token(logits, sel_bias, ids, weights, t, lane, E, k, scoring, renorm, scale);
+  __syncthreads();  // ids written by this block are visible to it
+  plan_block(ids, T * k, k, e0, e1, tile, seg, route_pos, row_token, work, n_work_cap, counts);
+  __syncthreads();
+  const int n_rows = counts[0];
+  for (int pos = warp; pos < n_rows; pos += 32) {
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row_token[pos]) * H);
+    uint4* dst = reinterpret_cast<uint4*>(xp + static_cast<size_t>(pos) * H);
+    for (int c = lane; c < (H >> 3); c += 32) dst[c] = src[c];
   }
 }
 
@@ -410,6 +445,19 @@ extern "C" int eredu_moe_combine_ar(const void* y, const int* route_pos, const f
   launch_pdl(moe_combine_ar_kernel, dim3(T, (chunks + 127) / 128), dim3(128), 0, stream,
              static_cast<const __nv_bfloat16*>(y), route_pos, weights, static_cast<const __nv_bfloat16*>(residual),
              static_cast<const __nv_bfloat16*>(extra), static_cast<__nv_bfloat16*>(out), k, H, *c, status);
+  eredu_count_launches(1);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int eredu_moe_route_plan_gather(const float* logits, const float* sel_bias, int* ids, float* weights, int T, int E,
+                                           int k, int scoring, int renorm, float scale, int e0, int e1, int tile, int* seg,
+                                           int* route_pos, int* row_token, int* work, int n_work_cap, int* counts,
+                                           const void* x, void* xp, int H, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (E > 512 || k > 32 || k > E || e1 - e0 > 512 || e1 <= e0 || H % 8 != 0 || T > 64) return -1;
+  launch_pdl(moe_route_plan_gather_kernel, dim3(1), dim3(1024), 0, stream, logits, sel_bias, ids, weights, T, E, k, scoring,
+             renorm, scale, e0, e1, tile, seg, route_pos, row_token, reinterpret_cast<int4*>(work), n_work_cap, counts,
+             static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(xp), H);
   eredu_count_launches(1);
   return static_cast<int>(cudaGetLastError());
 }

@@ -48,22 +48,31 @@ class MoEBlock:
     def __call__(self, x, residual=None):
         """x: normalised hidden states [T, H]; returns residual + MoE(x)."""
         self.stats["calls"] += 1
-        ids, w = self.route(x)
+        plan = xp = None
+        if x.is_cuda and x.shape[0] <= 64:
+            # decode-sized: routing, expert plan and row gather in one kernel
+            cfg = self.cfg
+            logits = ops.linear(x, self.router_w, out_dtype=torch.float32)
+            ids, w, plan, xp = moe_ops.route_plan_gather(logits.contiguous(), x, cfg.num_experts_per_tok, cfg.router_scoring,
+                                                         cfg.norm_topk_prob, 1.0, self.router_bias, self.e0,
+                                                         self.w_gate_up.shape[0])
+        else:
+            ids, w = self.route(x)
         extra = None
         if self.shared is not None:
             sgu, sd = self.shared
             extra = ops.linear(ops.gated_linear(x, sgu, sgu.shape[0] // 2), sd)
         if self.ep_size == 1:
             return moe_ops.experts_forward(x, ids, w, self.w_gate_up, self.w_down, self.e0, residual=residual,
-                                           extra=extra, limit=self.cfg.swiglu_limit)
+                                           extra=extra, limit=self.cfg.swiglu_limit, plan=plan, xp=xp)
         # shared experts are replicated: add them on one rank only so that the group sum counts them once
         own_extra = extra if self.e0 == 0 else None
         comm = getattr(self.ep_ops, "fused_comm", lambda tokens, hidden: None)(x.shape[0], x.shape[1]) if x.is_cuda else None
         if comm is not None:  # decode-sized step: combine and all-reduce are one kernel over peer memory
             return moe_ops.experts_forward(x, ids, w, self.w_gate_up, self.w_down, self.e0, residual=residual,
-                                           extra=own_extra, limit=self.cfg.swiglu_limit, comm=comm)
+                                           extra=own_extra, limit=self.cfg.swiglu_limit, comm=comm, plan=plan, xp=xp)
         partial = moe_ops.experts_forward(x, ids, w, self.w_gate_up, self.w_down, self.e0, residual=None,
-                                          extra=own_extra, limit=self.cfg.swiglu_limit)
+                                          extra=own_extra, limit=self.cfg.swiglu_limit, plan=plan, xp=xp)
         return self.ep_ops.all_reduce(partial, residual=residual)
 
 

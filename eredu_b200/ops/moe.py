@@ -16,6 +16,7 @@ native.register("eredu_moe_route", I, [P, P, P, P, I, I, I, I, I, native.F, P])
 native.register("eredu_moe_plan", I, [P, I, I, I, I, I, P, P, P, P, I, P, P])
 native.register("eredu_moe_gather", I, [P, P, P, P, I, I, P])
 native.register("eredu_moe_combine", I, [P, P, P, P, P, P, I, I, I, P])
+native.register("eredu_moe_route_plan_gather", I, [P, P, P, P, I, I, I, I, I, native.F, I, I, I, P, P, P, P, I, P, P, P, I, P])
 native.register("eredu_moe_combine_ar", I, [P, P, P, P, P, P, I, I, I, P, P, P])
 native.register("eredu_gemm_bf16_grouped", I, [P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, I, P, P])
 
@@ -81,9 +82,9 @@ def experts_ref(x, ids, weights, w_gate_up, w_down, e0=0, limit=0.0):
 class ExpertPlan:
     """Device-side routing plan for the local experts of one MoE layer invocation."""
 
-    def __init__(self, ids, k, e0, e1, tile, rows_cap):
-        dev = ids.device
-        routes = ids.numel()
+    def __init__(self, ids, k, e0, e1, tile, rows_cap, device=None, routes=None, run=True):
+        dev = ids.device if ids is not None else device
+        routes = ids.numel() if ids is not None else routes
         n_local = e1 - e0
         self.tile = tile
         self.rows_cap = rows_cap
@@ -93,6 +94,8 @@ class ExpertPlan:
         self.row_token = torch.empty(max(rows_cap, 1), dtype=torch.int32, device=dev)
         self.work = torch.empty((self.n_work, 4), dtype=torch.int32, device=dev)
         self.counts = torch.empty(2, dtype=torch.int32, device=dev)
+        if not run:
+            return
         code = lib().eredu_moe_plan(ptr(ids), routes, k, e0, e1, tile, ptr(self.seg), ptr(self.route_pos),
                                     ptr(self.row_token), ptr(self.work), self.n_work, ptr(self.counts),
                                     stream_ptr(dev))
@@ -106,8 +109,28 @@ def pick_tile(expected_rows_per_expert: float) -> int:
     return 128
 
 
+def route_plan_gather(logits, x, k, scoring, renorm, scale, sel_bias, e0, n_local):
+    """Decode-sized steps (<= 64 tokens): routing, the local experts' plan and the row gather in one kernel.
+    Returns (ids, weights, plan, xp) for :func:`experts_forward`."""
+    T, E = logits.shape
+    H = x.shape[1]
+    routes = T * k
+    tile = pick_tile(routes / max(1, n_local))
+    dev = x.device
+    ids = torch.empty((T, k), dtype=torch.int32, device=dev)
+    w = torch.empty((T, k), dtype=torch.float32, device=dev)
+    plan = ExpertPlan(None, k, e0, e0 + n_local, tile, routes, device=dev, routes=routes, run=False)
+    xp = torch.empty((routes, H), dtype=x.dtype, device=dev)
+    code = lib().eredu_moe_route_plan_gather(ptr(logits), ptr(sel_bias), ptr(ids), ptr(w), T, E, k, SCORING[scoring],
+                                             1 if renorm else 0, scale, e0, e0 + n_local, tile, ptr(plan.seg),
+                                             ptr(plan.route_pos), ptr(plan.row_token), ptr(plan.work), plan.n_work,
+                                             ptr(plan.counts), ptr(x), ptr(xp), H, stream_ptr(dev))
+    check(code, "eredu_moe_route_plan_gather")
+    return ids, w, plan, xp
+
+
 def experts_forward(x, ids, weights, w_gate_up, w_down, e0=0, residual=None, extra=None, limit=0.0, rows_cap=None,
-                    comm=None):
+                    comm=None, plan=None, xp=None):
     """Local-expert MoE computation. x: [T, H] bf16; ids / weights: [T, k]; w_gate_up: [E_local, 2I, H];
     w_down: [E_local, H, I]. Returns residual + extra + sum over local routes (bf16 [T, H]). With ``comm`` (a peer
     communication context of the expert group) the combine kernel also sums the partial outputs of all ranks:
@@ -125,12 +148,14 @@ def experts_forward(x, ids, weights, w_gate_up, w_down, e0=0, residual=None, ext
     inter = two_i // 2
     routes = T * k
     rows_cap = rows_cap or routes
-    tile = pick_tile(routes / max(1, E_local))
-    plan = ExpertPlan(ids, k, e0, e0 + E_local, tile, rows_cap)
     dev = x.device
-    xp = torch.empty((rows_cap, H), dtype=x.dtype, device=dev)
-    check(lib().eredu_moe_gather(ptr(x), ptr(plan.row_token), ptr(plan.counts), ptr(xp), rows_cap, H, stream_ptr(dev)),
-          "eredu_moe_gather")
+    if plan is None:
+        tile = pick_tile(routes / max(1, E_local))
+        plan = ExpertPlan(ids, k, e0, e0 + E_local, tile, rows_cap)
+        xp = torch.empty((rows_cap, H), dtype=x.dtype, device=dev)
+        check(lib().eredu_moe_gather(ptr(x), ptr(plan.row_token), ptr(plan.counts), ptr(xp), rows_cap, H, stream_ptr(dev)),
+              "eredu_moe_gather")
+    tile = plan.tile
     act = torch.empty((rows_cap, inter), dtype=x.dtype, device=dev)
     st = status_word(dev)
     sm = _sm_count(dev)
