@@ -545,68 +545,97 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     if (warp >= 2) {
       const uint32_t tag = seq + 1u;
       const int p_first = SPLIT ? split : 0, p_step = SPLIT ? nsplit : 1;
-      int jj = 0;
-      for (int pi = p_first; 2 * pi < m_end; pi += p_step, ++jj) {
-        float v0 = 0.f, v1 = 0.f;
-        // residual of this pair: prefetched for the first kPre pairs (select without dynamic register indexing)
-        float r0 = 0.f, r1 = 0.f;
-        if (jj < kPre) {
+      // Pairs are collected four at a time: the first poll of a chunk issues every (pair, source rank) load before
+      // any tag is looked at, so one memory round trip usually brings all 32 words; stragglers are re-polled.
+      constexpr int kPB = 4;
+      for (int pi0 = p_first; 2 * pi0 < m_end; pi0 += kPB * p_step) {
+        float r0[kPB], r1[kPB];
+        uint32_t lo[kPB][kMaxRanks], miss[kPB];
+        size_t word[kPB];
 #pragma unroll
-          for (int j = 0; j < kPre; ++j) {
-            if (j == jj) {
-              r0 = rpre[2 * j];
-              r1 = rpre[2 * j + 1];
-            }
-          }
-        } else if (has_res) {
-          r0 = residual_at(p, m_base + 2 * pi, n);
-          if (2 * pi + 1 < m_end) r1 = residual_at(p, m_base + 2 * pi + 1, n);
+        for (int j = 0; j < kPB; ++j) {
+          const int pi = pi0 + j * p_step;
+          const bool live = in_n && 2 * pi < m_end;
+          miss[j] = live ? (1u << p.comm.size) - 1u : 0u;
+          word[j] = (static_cast<size_t>(m_base / 2 + pi) * p.N + n) * 8;
+          r0[j] = (live && has_res) ? residual_at(p, m_base + 2 * pi, n) : 0.f;
+          r1[j] = (live && has_res && 2 * pi + 1 < m_end) ? residual_at(p, m_base + 2 * pi + 1, n) : 0.f;
         }
-        if (in_n) {
-          const size_t word = (static_cast<size_t>(m_base / 2 + pi) * p.N + n) * 8;
-          uint32_t val[kMaxRanks];
-          uint32_t missing = (1u << p.comm.size) - 1u;
-          const long long t0 = clock64();
-          while (missing != 0u) {
+        {
+          uint32_t hi[kPB][kMaxRanks];
+#pragma unroll
+          for (int j = 0; j < kPB; ++j) {
 #pragma unroll
             for (int src = 0; src < kMaxRanks; ++src) {
-              if (src < p.comm.size && ((missing >> src) & 1u)) {
-                uint32_t lo, hi;
+              lo[j][src] = 0u;
+              hi[j][src] = ~tag;
+              if ((miss[j] >> src) & 1u) {
                 asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];"
-                             : "=r"(lo), "=r"(hi)
-                             : "l"(peer_slot(p.comm, p.comm.rank, parity, src) + word)
+                             : "=r"(lo[j][src]), "=r"(hi[j][src])
+                             : "l"(peer_slot(p.comm, p.comm.rank, parity, src) + word[j])
                              : "memory");
-                if (hi == tag) {
-                  val[src] = lo;
-                  missing &= ~(1u << src);
+              }
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < kPB; ++j) {
+#pragma unroll
+            for (int src = 0; src < kMaxRanks; ++src) {
+              if (hi[j][src] == tag) miss[j] &= ~(1u << src);
+            }
+          }
+        }
+        const long long t0 = clock64();
+#pragma unroll
+        for (int j = 0; j < kPB; ++j) {
+          while (miss[j] != 0u) {
+#pragma unroll
+            for (int src = 0; src < kMaxRanks; ++src) {
+              if ((miss[j] >> src) & 1u) {
+                uint32_t l2, h2;
+                asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];"
+                             : "=r"(l2), "=r"(h2)
+                             : "l"(peer_slot(p.comm, p.comm.rank, parity, src) + word[j])
+                             : "memory");
+                if (h2 == tag) {
+                  lo[j][src] = l2;
+                  miss[j] &= ~(1u << src);
                 }
               }
             }
-            if (missing != 0u && clock64() - t0 > kWaitCycleLimit) {
+            if (miss[j] != 0u && clock64() - t0 > kWaitCycleLimit) {
               report_status(p.status, kStatusPeerFlagTimeout);
               break;
             }
           }
-#pragma unroll
-          for (int src = 0; src < kMaxRanks; ++src) {  // rank order: every rank computes the same bits
-            if (src < p.comm.size && !((missing >> src) & 1u)) {
-              v0 += bf16_lo(val[src]);
-              v1 += bf16_hi(val[src]);
-            }
-          }
-          v0 = epilogue_store<false>(p, v0, 0.f, m_base + 2 * pi, n, 1.f, r0);
-          v1 = (2 * pi + 1 < m_end) ? epilogue_store<false>(p, v1, 0.f, m_base + 2 * pi + 1, n, 1.f, r1) : 0.f;
         }
-        if (p.ssq_out != nullptr) {
-          float s0 = in_n ? v0 * v0 : 0.f, s1 = in_n ? v1 * v1 : 0.f;
 #pragma unroll
-          for (int o = 16; o > 0; o >>= 1) {
-            s0 += __shfl_xor_sync(0xffffffffu, s0, o);
-            s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+        for (int j = 0; j < kPB; ++j) {
+          const int pi = pi0 + j * p_step;
+          if (2 * pi >= m_end) break;  // warp-uniform
+          float v0 = 0.f, v1 = 0.f;
+          if (in_n) {
+#pragma unroll
+            for (int src = 0; src < kMaxRanks; ++src) {  // rank order: every rank computes the same bits
+              if (src < p.comm.size && !((miss[j] >> src) & 1u)) {
+                v0 += bf16_lo(lo[j][src]);
+                v1 += bf16_hi(lo[j][src]);
+              }
+            }
+            v0 = epilogue_store<false>(p, v0, 0.f, m_base + 2 * pi, n, 1.f, r0[j]);
+            v1 = (2 * pi + 1 < m_end) ? epilogue_store<false>(p, v1, 0.f, m_base + 2 * pi + 1, n, 1.f, r1[j]) : 0.f;
           }
-          if (lane == 0) {
-            s_ssq[q][2 * pi] = s0;
-            if (2 * pi + 1 < TN) s_ssq[q][2 * pi + 1] = s1;
+          if (p.ssq_out != nullptr) {
+            float s0 = in_n ? v0 * v0 : 0.f, s1 = in_n ? v1 * v1 : 0.f;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+              s0 += __shfl_xor_sync(0xffffffffu, s0, o);
+              s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+            }
+            if (lane == 0) {
+              s_ssq[q][2 * pi] = s0;
+              if (2 * pi + 1 < TN) s_ssq[q][2 * pi + 1] = s1;
+            }
           }
         }
       }

@@ -207,7 +207,7 @@ __global__ void __launch_bounds__(1024) moe_route_plan_gather_kernel(
   __syncthreads();  // ids written by this block are visible to it
   plan_block(ids, T * k, k, e0, e1, tile, seg, route_pos, row_token, work, n_work_cap, counts);
   __syncthreads();
-  const int n_rows = counts[0];
+  const int n_rows = xp != nullptr ? counts[0] : 0;  // large steps gather with the many-CTA kernel instead
   for (int pos = warp; pos < n_rows; pos += 32) {
     const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row_token[pos]) * H);
     uint4* dst = reinterpret_cast<uint4*>(xp + static_cast<size_t>(pos) * H);

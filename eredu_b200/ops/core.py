@@ -236,12 +236,17 @@ def attention_prefill(q, k_cache, v_cache, block_table, seq_lens, cu_q, max_q_le
     return out
 
 
+import os as _os
+
+_SPLIT_WAVES = int(_os.environ.get("EREDU_DECODE_SPLIT_WAVES", "2"))   # CTAs per SM the split-KV grid aims for
+
+
 def decode_splits(batch, n_kv, max_kv_len, sm_count=148):
     """Split-KV factor: enough CTAs to fill the GPU once (a second wave costs more than it returns: the CTAs of the
     following kernel are already resident under programmatic dependent launch), at least 8 pages per split."""
     ctas = max(1, batch * n_kv)
     pages = max(1, (max_kv_len + PAGE - 1) // PAGE)
-    want = max(1, sm_count // ctas)
+    want = max(1, (_SPLIT_WAVES * sm_count) // ctas)
     return int(max(1, min(want, pages // 8 if pages >= 8 else 1, 32)))
 
 

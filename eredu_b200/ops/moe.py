@@ -121,11 +121,16 @@ def route_plan_gather(logits, x, k, scoring, renorm, scale, sel_bias, e0, n_loca
     w = torch.empty((T, k), dtype=torch.float32, device=dev)
     plan = ExpertPlan(None, k, e0, e0 + n_local, tile, routes, device=dev, routes=routes, run=False)
     xp = torch.empty((routes, H), dtype=x.dtype, device=dev)
+    # one CTA copies the rows itself only when there are few of them (expected local routes <= 64)
+    inline_gather = routes * n_local <= 64 * E
     code = lib().eredu_moe_route_plan_gather(ptr(logits), ptr(sel_bias), ptr(ids), ptr(w), T, E, k, SCORING[scoring],
                                              1 if renorm else 0, scale, e0, e0 + n_local, tile, ptr(plan.seg),
                                              ptr(plan.route_pos), ptr(plan.row_token), ptr(plan.work), plan.n_work,
-                                             ptr(plan.counts), ptr(x), ptr(xp), H, stream_ptr(dev))
+                                             ptr(plan.counts), ptr(x), ptr(xp) if inline_gather else None, H, stream_ptr(dev))
     check(code, "eredu_moe_route_plan_gather")
+    if not inline_gather:
+        check(lib().eredu_moe_gather(ptr(x), ptr(plan.row_token), ptr(plan.counts), ptr(xp), routes, H, stream_ptr(dev)),
+              "eredu_moe_gather")
     return ids, w, plan, xp
 
 
