@@ -131,12 +131,82 @@ def run_speculative(args, eng, model, cfg, prompts, dev, world, rank) -> int:
     return 0
 
 
+def run_torch_baseline(args) -> int:
+    """Stand-in for the reference arm that cannot be built here: stock PyTorch operators (cuBLAS GEMMs, library
+    attention, NCCL collectives) on the same shapes, batch, context and timing protocol; decode only."""
+    import torch
+
+    from baseline.torch_llama import TorchLlamaTP
+    from eredu_b200.models import config as C   # shapes only
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = {"llama3-8b": C.llama3_8b, "llama3-70b": C.llama3_70b, "tiny": C.tiny_llama}[args.model]()
+    K, W, B, P = args.steps, max(args.warmup, 3), args.batch, args.prompt_len
+    model = TorchLlamaTP(cfg, dev, rank, world, None, max_len=P + 64, batch=B)
+    model.prefill_fill(P)
+    tokens = torch.randint(0, cfg.vocab_size, (B,), device=dev)
+    pos = torch.full((B,), P, device=dev, dtype=torch.long)
+    kv_len = P + 1   # fixed context: the timed steps all attend to P + 1 positions
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            out = model.decode_step(tokens, pos, kv_len)
+    torch.cuda.current_stream(dev).wait_stream(side)
+    torch.cuda.synchronize(dev)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = model.decode_step(tokens, pos, kv_len)
+        tokens.copy_(out)
+    for _ in range(W):
+        graph.replay()
+    torch.cuda.synchronize(dev)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        import torch.distributed as dist
+
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if rank == 0:
+        print(json.dumps({"impl": "torch-baseline", "metric": "decode_tokens_per_s", "value": round(B * K / (ms / 1e3), 2),
+                          "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(ms / K, 4),
+                          "higher_is_better": True, "dtype": "bf16", "data": "synthetic (random weights and cache)",
+                          "config": {"model": args.model + "-shaped", "global_batch": B, "seq_len": P, "parallelism": f"tp{world}",
+                                     "stack": "F.linear (cuBLAS) + F.scaled_dot_product_attention + NCCL all-reduce / all-gather, CUDA graph",
+                                     "kv": "contiguous cache, fixed context of seq_len + 1"}}))
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
-    ap.add_argument("--impl", default="eredu_b200", choices=["eredu_b200", "reference"])
+    ap.add_argument("--impl", default="eredu_b200", choices=["eredu_b200", "reference", "torch-baseline"],
+                    help="torch-baseline: the same decode step from stock PyTorch / cuBLAS / NCCL only (baseline/torch_llama.py)")
     ap.add_argument("--batch", type=int, default=32)
     ap.add_argument("--prompt-len", type=int, default=2048)
     ap.add_argument("--model", default="llama3-8b", choices=["llama3-8b", "llama3-70b", "qwen3-30b-a3b", "tiny"])
@@ -155,6 +225,9 @@ def main() -> int:
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
         return 0
+
+    if args.impl == "torch-baseline":
+        return run_torch_baseline(args)
 
     import numpy as np
     import torch
