@@ -40,6 +40,9 @@ class ModelLoadOptions:
     use_cuda_graph: Optional[bool] = None
     weight_residency: str = "device"             # "device" | "layerwise_host" (--layerwise-host)
     device_layer_window: int = 1                 # layers resident on the device at a time in layerwise_host mode
+    expert_cache: bool = False                   # routed experts in host memory behind a bounded device bank
+    expert_cache_device_budget_bytes: Optional[int] = None   # per sparse layer; None: a quarter of the experts
+    expert_cache_eviction: str = "lru"
 
 
 class LoadedModel:
@@ -84,6 +87,14 @@ class LoadedModel:
                                    on_layer=on_layer)
         if residency is not None:
             residency.finalize()
+        if opt.expert_cache and src.cfg.is_moe:
+            from ..runtime.expert_cache import attach_expert_cache
+
+            if opt.expert_cache_device_budget_bytes:
+                attach_expert_cache(model, device_budget_bytes=opt.expert_cache_device_budget_bytes,
+                                    eviction=opt.expert_cache_eviction)
+            else:
+                attach_expert_cache(model, slots=max(1, src.cfg.num_experts // 4), eviction=opt.expert_cache_eviction)
         if opt.parallel is not None and opt.parallel.tp_size > 1:
             from ..parallel import tp
 

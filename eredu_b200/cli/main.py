@@ -126,7 +126,10 @@ def main(argv=None) -> int:
     lm = LoadedModel.load(model_path, ModelLoadOptions(device=device, quantization=quant, mapped_shards=a.mapped_shards,
                                                        max_batch=1, max_seq_len=max(4096, a.max_tokens + 2048),
                                                        weight_residency="layerwise_host" if a.layerwise_host else "device",
-                                                       device_layer_window=a.device_layer_window))
+                                                       device_layer_window=a.device_layer_window,
+                                                       expert_cache=a.expert_cache,
+                                                       expert_cache_device_budget_bytes=a.expert_cache_device_budget_bytes,
+                                                       expert_cache_eviction=a.expert_cache_eviction))
     load_time = time.perf_counter() - t0
     gen_cfg = lm.tokenizer.generation_config if lm.tokenizer else {}
     sp = resolve_sampling(a, gen_cfg)

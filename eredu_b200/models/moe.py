@@ -48,6 +48,18 @@ class MoEBlock:
     def __call__(self, x, residual=None):
         """x: normalised hidden states [T, H]; returns residual + MoE(x)."""
         self.stats["calls"] += 1
+        cache = getattr(self, "expert_cache", None)
+        if cache is not None:
+            # experts live in host memory behind a bounded device bank: route, then let the cache run the experts
+            ids, w = self.route(x)
+            extra = None
+            if self.shared is not None:
+                sgu, sd = self.shared
+                extra = ops.linear(ops.gated_linear(x, sgu, sgu.shape[0] // 2), sd)
+            if self.ep_size == 1:
+                return cache.forward(x, ids, w, residual=residual, extra=extra, limit=self.cfg.swiglu_limit)
+            partial = cache.forward(x, ids, w, extra=extra if self.e0 == 0 else None, limit=self.cfg.swiglu_limit)
+            return self.ep_ops.all_reduce(partial, residual=residual)
         plan = xp = None
         if x.is_cuda and x.shape[0] <= 64:
             # decode-sized: routing, expert plan and row gather in one kernel
