@@ -103,3 +103,21 @@ def test_quantised_tensor_parallel_matches_single_gpu(world, tmp_path):
     for r in res:
         lg = torch.tensor(r["logits"])
         assert _rel(lg, ref) <= 0.03 and r["logits"] == res[0]["logits"]
+
+
+@pytest.mark.parametrize("scenario,world", [("gpu_pp", 2), ("gpu_pp_tp2", 4)])
+def test_pipeline_parallel_gpu(scenario, world, tmp_path):
+    """Two pipeline stages (alone and over tensor-parallel pairs): activations travel over NCCL p2p with checked
+    frame headers, the last stage samples and broadcasts; every rank reports the single-GPU tokens."""
+    _need(world)
+    res = run_ranks(scenario, world, tmp_path, extra_env={"NCCL_NVLS_ENABLE": "0"})
+    cfg = tiny_cfg(True)
+    sd = random_state(cfg, seed=0, std=0.05)
+    model = build_from_tensors(cfg, sd.__getitem__, sd.__contains__, "cuda:0", torch.bfloat16)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 33)]
+    want = Engine(model, max_batch=4, max_seq_len=128).generate(prompts, SamplingParams(temperature=0.0), 10)
+    for r in res:
+        assert r["tokens"] == res[0]["tokens"]
+        agree = sum(a == b for x, y in zip(want, r["tokens"]) for a, b in zip(x, y))
+        assert agree >= 14      # bf16: the stage split changes nothing numerically, tensor-parallel sums may flip a late token
