@@ -58,6 +58,12 @@ struct GemmParams {
   // Large token tiles: the epilogue goes through shared memory so that the output (and the residual) move as
   // 16-byte row chunks instead of one 2-byte element per thread. Needs 16-byte aligned rows (host-checked).
   int staged;
+  // Gated activation of DUAL tiles: 0 = silu(g) * u (SwiGLU); 1 = g * sigmoid(1.702 g) * (u + 1) (GPT-OSS). With
+  // act_limit > 0 the gate is clamped from above and the linear branch to [-limit, limit] first
+  // (eredu/src/backend/mlx/architectures/gpt_oss/model.rs:748-753; nn/moe.rs swiglu_limit).
+  int act;
+  float act_limit;
+  int bias_expert_stride;  // grouped mode: elements between two experts' bias vectors (0 = one shared vector)
   // Weights that no kernel of the stream rewrites (every model weight): their first tiles are fetched, and the
   // rest prefetched into L2, BEFORE the kernel waits for its producer under programmatic dependent launch, so
   // the weight stream of this kernel overlaps the tail of the previous one.
@@ -94,6 +100,15 @@ struct GemmCfg {
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
 
+__device__ __forceinline__ float gated_act(const GemmParams& p, float g, float u) {
+  if (p.act_limit > 0.f) {
+    g = fminf(g, p.act_limit);
+    u = fminf(fmaxf(u, -p.act_limit), p.act_limit);
+  }
+  if (p.act == 1) return g / (1.0f + __expf(-1.702f * g)) * (u + 1.0f);
+  return silu_f(g) * u;
+}
+
 // Applies row scale, bias, activation and residual, stores, and returns the value as stored (after rounding).
 __device__ __forceinline__ float residual_at(const GemmParams& p, int m, int n) {
   return __bfloat162float(static_cast<const __nv_bfloat16*>(p.residual)[static_cast<size_t>(m) * p.ldr + n]);
@@ -110,7 +125,7 @@ __device__ __forceinline__ float epilogue_store(const GemmParams& p, float g, fl
     g += __bfloat162float(b[n]);
     if (DUAL) u += __bfloat162float(b[p.N + n]);
   }
-  float v = (DUAL ? silu_f(g) * u : g) + rv;
+  float v = (DUAL ? gated_act(p, g, u) : g) + rv;
   if (p.out_fp32) {
     static_cast<float*>(p.y)[static_cast<size_t>(m) * p.ldy + n] = v;
     return v;
@@ -162,6 +177,8 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     m_base = item.y;
     m_limit = item.y + item.z;
     w_row0 += item.x * p.w_rows_per_expert;
+    if (p.bias != nullptr)
+      p.bias = static_cast<const __nv_bfloat16*>(p.bias) + static_cast<size_t>(item.x) * p.bias_expert_stride;
   }
   const int nsplit = SPLIT ? gridDim.z : 1;
   const int split = SPLIT ? blockIdx.z : 0;
@@ -387,7 +404,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           for (int j = 0; j < 16; ++j) {
             const float sc = (p.ssq_in != nullptr) ? s_scale[c0 + j] : 1.f;
             const float gg = __uint_as_float(g[j]) * sc + bg;
-            red[(c0 + j) * 128 + row] = DUAL ? silu_f(gg) * (__uint_as_float(u[j]) * sc + bu) : gg;
+            red[(c0 + j) * 128 + row] = DUAL ? gated_act(p, gg, __uint_as_float(u[j]) * sc + bu) : gg;
           }
         } else {
           float rr[16];
@@ -808,6 +825,9 @@ extern "C" int eredu_gemm_bf16(const void* X, const void* W, void* Y, const void
   p.work = nullptr;
   p.w_rows_per_expert = 0;
   p.staged = 0;
+  p.act = 0;
+  p.act_limit = 0.f;
+  p.bias_expert_stride = 0;
   // flag bit 0: W was produced by a preceding kernel of the stream (no early fetch at all). Otherwise the ring's
   // first stages are fetched before the dependency wait (level 1), and for matrices that fit L2 many times over
   // the remaining tiles are prefetched into L2 as well (level 2). EREDU_GEMM_PREFETCH overrides the level.
@@ -888,6 +908,9 @@ extern "C" int eredu_gemm_bf16_comm(const void* X, const void* W, void* Y, const
   p.work = nullptr;
   p.w_rows_per_expert = 0;
   p.staged = 0;
+  p.act = 0;
+  p.act_limit = 0.f;
+  p.bias_expert_stride = 0;
   p.w_static = prefetch_level(static_cast<long long>(w_rows) * K * 2);
   p.comm = *pc;
   const int n_tiles = (N + 127) / 128;
@@ -924,6 +947,7 @@ extern "C" int eredu_gemm_bf16_comm(const void* X, const void* W, void* Y, const
 extern "C" int eredu_gemm_bf16_grouped(const void* X, const void* W, void* Y, const int* work, int n_work, int tile,
                                        int rows_cap, int N, int K, int ldx, int ldw, int ldy, int w_rows_total,
                                        int w_rows_per_expert, int dual, int force_split, int sm_count, int* status,
+                                       const void* bias, int bias_expert_stride, int act, float act_limit,
                                        cudaStream_t stream) {
   if (n_work <= 0 || N <= 0 || K <= 0) return 0;
   CUtensorMap tmW, tmX;
@@ -941,6 +965,10 @@ extern "C" int eredu_gemm_bf16_grouped(const void* X, const void* W, void* Y, co
   p.status = status;
   p.work = work;
   p.w_rows_per_expert = w_rows_per_expert;
+  p.bias = bias;  // per expert: [w_rows_per_expert] (dual: gate part then up part), bias_expert_stride apart
+  p.bias_expert_stride = bias_expert_stride;
+  p.act = act;
+  p.act_limit = act_limit;
   const int n_tiles = (N + 127) / 128;
   const int kblocks = (K + 63) / 64;
   int nsplit = 1;

@@ -83,7 +83,8 @@ class ModelConfig:
                                                                 "router_scoring", "attention_sinks", "quantization")}
         d["architectures"] = [{"llama": "LlamaForCausalLM", "mistral": "MistralForCausalLM",
                                "qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM",
-                               "qwen3_moe": "Qwen3MoeForCausalLM"}.get(self.model_type, "LlamaForCausalLM")]
+                               "qwen3_moe": "Qwen3MoeForCausalLM", "mixtral": "MixtralForCausalLM",
+                               "gpt_oss": "GptOssForCausalLM"}.get(self.model_type, "LlamaForCausalLM")]
         if not self.is_moe:
             for k in ("num_experts", "num_experts_per_tok", "moe_intermediate_size", "norm_topk_prob",
                       "shared_expert_intermediate_size", "decoder_sparse_step", "mlp_only_layers", "swiglu_limit"):
@@ -147,6 +148,19 @@ class ModelConfig:
         if mt == "mixtral":
             cfg.moe_intermediate_size = cfg.moe_intermediate_size or cfg.intermediate_size
             cfg.router_scoring = "topk_softmax"
+        if mt == "gpt_oss":
+            # eredu/src/backend/mlx/architectures/gpt_oss/model.rs:64-170: every layer is sparse, top-k then softmax
+            # over the selected logits, attention sinks and biases, alternating sliding / full layers, clamp 7.0
+            cfg.num_experts = int(d.get("num_local_experts", cfg.num_experts) or cfg.num_experts)
+            cfg.num_experts_per_tok = int(d.get("num_experts_per_tok", d.get("experts_per_token", 4)) or 4)
+            cfg.moe_intermediate_size = cfg.moe_intermediate_size or cfg.intermediate_size
+            cfg.router_scoring = "topk_softmax"
+            cfg.norm_topk_prob = False
+            cfg.attention_bias = bool(d.get("attention_bias", True))
+            cfg.attention_sinks = True
+            cfg.swiglu_limit = float(d.get("swiglu_limit", 7.0) or 7.0)
+            cfg.sliding_window = d.get("sliding_window", cfg.sliding_window)
+            cfg.tie_word_embeddings = bool(d.get("tie_word_embeddings", False))
         return cfg
 
     @classmethod

@@ -20,7 +20,7 @@ from ..ops import moe as moe_ops
 
 class MoEBlock:
     def __init__(self, cfg, router_w, w_gate_up, w_down, e0: int, n_experts: int, ep_ops=None, ep_size: int = 1,
-                 shared=None, router_bias=None):
+                 shared=None, router_bias=None, router_linear_bias=None, gu_bias=None, down_bias=None, act="swiglu"):
         self.cfg = cfg
         self.router_w = router_w          # [E, H]
         self.w_gate_up = w_gate_up        # [E_local, 2I, H]
@@ -30,18 +30,23 @@ class MoEBlock:
         self.ep_ops = ep_ops
         self.ep_size = ep_size
         self.shared = shared              # optional (w_gate_up [2Is, H], w_down [H, Is]) dense shared expert
-        self.router_bias = router_bias
+        self.router_bias = router_bias                # selection-only bias (added to the scores used for top-k)
+        self.router_linear_bias = router_linear_bias  # bias of the router projection itself (GPT-OSS)
+        self.gu_bias = gu_bias                        # [E_local, 2I] per-expert bias, gate part then up part
+        self.down_bias = down_bias                    # [E_local, H]
+        self.act = act
         self.stats = {"calls": 0}
 
     def tensors(self):
         out = [self.router_w, self.w_gate_up, self.w_down]
+        out.extend(t for t in (self.router_linear_bias, self.gu_bias, self.down_bias) if t is not None)
         if self.shared is not None:
             out.extend(self.shared)
         return out
 
     def route(self, x):
         cfg = self.cfg
-        logits = ops.linear(x, self.router_w, out_dtype=torch.float32)
+        logits = ops.linear(x, self.router_w, bias=self.router_linear_bias, out_dtype=torch.float32)
         return moe_ops.route(logits.contiguous(), cfg.num_experts_per_tok, cfg.router_scoring, cfg.norm_topk_prob, 1.0,
                              self.router_bias)
 
@@ -64,7 +69,7 @@ class MoEBlock:
         if x.is_cuda and x.shape[0] <= 64:
             # decode-sized: routing, expert plan and row gather in one kernel
             cfg = self.cfg
-            logits = ops.linear(x, self.router_w, out_dtype=torch.float32)
+            logits = ops.linear(x, self.router_w, bias=self.router_linear_bias, out_dtype=torch.float32)
             ids, w, plan, xp = moe_ops.route_plan_gather(logits.contiguous(), x, cfg.num_experts_per_tok, cfg.router_scoring,
                                                          cfg.norm_topk_prob, 1.0, self.router_bias, self.e0,
                                                          self.w_gate_up.shape[0])
@@ -76,15 +81,18 @@ class MoEBlock:
             extra = ops.linear(ops.gated_linear(x, sgu, sgu.shape[0] // 2), sd)
         if self.ep_size == 1:
             return moe_ops.experts_forward(x, ids, w, self.w_gate_up, self.w_down, self.e0, residual=residual,
-                                           extra=extra, limit=self.cfg.swiglu_limit, plan=plan, xp=xp)
+                                           extra=extra, limit=self.cfg.swiglu_limit, plan=plan, xp=xp, gu_bias=self.gu_bias,
+                                           down_bias=self.down_bias, act=self.act)
         # shared experts are replicated: add them on one rank only so that the group sum counts them once
         own_extra = extra if self.e0 == 0 else None
         comm = getattr(self.ep_ops, "fused_comm", lambda tokens, hidden: None)(x.shape[0], x.shape[1]) if x.is_cuda else None
         if comm is not None:  # decode-sized step: combine and all-reduce are one kernel over peer memory
             return moe_ops.experts_forward(x, ids, w, self.w_gate_up, self.w_down, self.e0, residual=residual,
-                                           extra=own_extra, limit=self.cfg.swiglu_limit, comm=comm, plan=plan, xp=xp)
+                                           extra=own_extra, limit=self.cfg.swiglu_limit, comm=comm, plan=plan, xp=xp,
+                                           gu_bias=self.gu_bias, down_bias=self.down_bias, act=self.act)
         partial = moe_ops.experts_forward(x, ids, w, self.w_gate_up, self.w_down, self.e0, residual=None,
-                                          extra=own_extra, limit=self.cfg.swiglu_limit, plan=plan, xp=xp)
+                                          extra=own_extra, limit=self.cfg.swiglu_limit, plan=plan, xp=xp, gu_bias=self.gu_bias,
+                                           down_bias=self.down_bias, act=self.act)
         return self.ep_ops.all_reduce(partial, residual=residual)
 
 
@@ -107,6 +115,8 @@ def make_moe_factory(src=None, router_std_scale: bool = False):
             block = MoEBlock(cfg, router, gu, dn, e0, cfg.num_experts, ep_size=par.ep_size)
             block._model = model
             return block
+        if has(p + "router.weight"):
+            return _gpt_oss_block(model, li, get, has, e0, e1)
         router = get(p + "gate.weight").to(device=dev, dtype=dt).contiguous()
         if has(p + "experts.gate_up_proj"):
             gu = get(p + "experts.gate_up_proj")[e0:e1]
@@ -132,6 +142,44 @@ def make_moe_factory(src=None, router_std_scale: bool = False):
         return block
 
     return factory
+
+
+def _gpt_oss_block(model, li, get, has, e0, e1):
+    """GPT-OSS sparse block: router with a linear bias, experts with biases and the clamped (u + 1) * g * sigmoid(1.702 g)
+    gate. Checkpoint layout (eredu/src/backend/mlx/architectures/gpt_oss/checkpoint.rs): ``mlp.router.{weight,bias}``;
+    ``mlp.experts.gate_up_proj`` [E, H, 2I] with gate and up INTERLEAVED on the last axis (+ ``_bias`` [E, 2I]),
+    ``mlp.experts.down_proj`` [E, I, H] (+ ``_bias`` [E, H]); or the MXFP4 form ``*_blocks`` u8 [E, rows, K/32, 16] with
+    ``*_scales`` u8 [E, rows, K/32] (E8M0), which is decoded to the compute dtype at load."""
+    import numpy as np
+
+    from ..lib import _eredu_host as H
+
+    cfg, dev, dt = model.cfg, model.device, model.dtype
+    p = f"model.layers.{li}.mlp."
+
+    def bank(name):
+        """[E_local, rows, K] in the compute dtype, rows = output features."""
+        if has(p + f"experts.{name}_blocks"):
+            blocks = get(p + f"experts.{name}_blocks")[e0:e1]
+            scales = get(p + f"experts.{name}_scales")[e0:e1]
+            E, rows = blocks.shape[0], blocks.shape[1]
+            packed = np.ascontiguousarray(blocks.cpu().numpy()).reshape(E * rows, -1).view(np.uint32)
+            sc = np.ascontiguousarray(scales.cpu().numpy()).reshape(E * rows, -1)
+            w = torch.from_numpy(np.asarray(H.mxfp4_dequantize(packed, sc))).reshape(E, rows, -1)
+            return w
+        return get(p + f"experts.{name}")[e0:e1].transpose(1, 2)     # stored input-major: [E, K, rows]
+
+    gu = bank("gate_up_proj").float()                                # [E, 2I, H], rows interleaved gate / up
+    gu = torch.cat((gu[:, 0::2], gu[:, 1::2]), dim=1)                # -> gate rows then up rows
+    dn = bank("down_proj")
+    gub = get(p + "experts.gate_up_proj_bias")[e0:e1].float()
+    gub = torch.cat((gub[:, 0::2], gub[:, 1::2]), dim=1)
+    dnb = get(p + "experts.down_proj_bias")[e0:e1]
+    up = lambda t: t.to(device=dev, dtype=dt).contiguous()           # noqa: E731
+    block = MoEBlock(cfg, up(get(p + "router.weight")), up(gu), up(dn), e0, cfg.num_experts, ep_size=model.par.ep_size,
+                     router_linear_bias=up(get(p + "router.bias")), gu_bias=up(gub), down_bias=up(dnb), act="oss_glu")
+    block._model = model
+    return block
 
 
 def attach_ep(model, ep_ops) -> None:

@@ -18,7 +18,7 @@ native.register("eredu_moe_gather", I, [P, P, P, P, I, I, P])
 native.register("eredu_moe_combine", I, [P, P, P, P, P, P, I, I, I, P])
 native.register("eredu_moe_route_plan_gather", I, [P, P, P, P, I, I, I, I, I, native.F, I, I, I, P, P, P, P, I, P, P, P, I, P])
 native.register("eredu_moe_combine_ar", I, [P, P, P, P, P, P, I, I, I, P, P, P])
-native.register("eredu_gemm_bf16_grouped", I, [P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, I, P, P])
+native.register("eredu_gemm_bf16_grouped", I, [P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, I, P, P, I, I, native.F, P])
 
 SCORING = {"softmax": 0, "sigmoid": 1, "sqrt_softplus": 2, "topk_softmax": 3}
 
@@ -57,8 +57,22 @@ def route(logits, k, scoring="softmax", renorm=True, scale=1.0, sel_bias=None):
     return ids, w
 
 
-def experts_ref(x, ids, weights, w_gate_up, w_down, e0=0, limit=0.0):
-    """Reference expert computation for local experts [e0, e0 + E_local): sum_k w * down_e(silu(gate_e x) * up_e x)."""
+ACTS = {"swiglu": 0, "oss_glu": 1}
+
+
+def gated_act_ref(g, u, act="swiglu", limit=0.0):
+    """silu(g) * u, or the GPT-OSS gate g * sigmoid(1.702 g) * (u + 1); with ``limit`` the gate is clamped from above
+    and the linear branch to [-limit, limit] first."""
+    if limit > 0:
+        g, u = g.clamp(max=limit), u.clamp(-limit, limit)
+    if act == "oss_glu":
+        return g * torch.sigmoid(1.702 * g) * (u + 1.0)
+    return F.silu(g) * u
+
+
+def experts_ref(x, ids, weights, w_gate_up, w_down, e0=0, limit=0.0, gu_bias=None, down_bias=None, act="swiglu"):
+    """Reference expert computation for local experts [e0, e0 + E_local): sum_k w * down_e(act(gate_e x, up_e x)).
+    ``gu_bias`` [E_local, 2I] (gate part then up part) and ``down_bias`` [E_local, H] are per-expert biases."""
     T, H = x.shape
     E_local, two_i, _ = w_gate_up.shape
     inter = two_i // 2
@@ -70,11 +84,14 @@ def experts_ref(x, ids, weights, w_gate_up, w_down, e0=0, limit=0.0):
             if sel.numel() == 0:
                 continue
             y = xf[sel] @ w_gate_up[e].float().t()
+            if gu_bias is not None:
+                y = y + gu_bias[e].float()
             g, u = y[:, :inter], y[:, inter:]
-            if limit > 0:
-                g, u = g.clamp(max=limit), u.clamp(-limit, limit)
-            act = (F.silu(g) * u).to(x.dtype).float()
-            o = (act @ w_down[e].float().t()).to(x.dtype).float()
+            a = gated_act_ref(g, u, act, limit).to(x.dtype).float()
+            o = a @ w_down[e].float().t()
+            if down_bias is not None:
+                o = o + down_bias[e].float()
+            o = o.to(x.dtype).float()
             out[sel] += weights[sel, slot, None] * o
     return out
 
@@ -135,13 +152,13 @@ def route_plan_gather(logits, x, k, scoring, renorm, scale, sel_bias, e0, n_loca
 
 
 def experts_forward(x, ids, weights, w_gate_up, w_down, e0=0, residual=None, extra=None, limit=0.0, rows_cap=None,
-                    comm=None, plan=None, xp=None):
+                    comm=None, plan=None, xp=None, gu_bias=None, down_bias=None, act="swiglu"):
     """Local-expert MoE computation. x: [T, H] bf16; ids / weights: [T, k]; w_gate_up: [E_local, 2I, H];
     w_down: [E_local, H, I]. Returns residual + extra + sum over local routes (bf16 [T, H]). With ``comm`` (a peer
     communication context of the expert group) the combine kernel also sums the partial outputs of all ranks:
     ``extra`` is then counted once per rank that passes it, ``residual`` once in total."""
     if not x.is_cuda:
-        out = experts_ref(x, ids, weights, w_gate_up, w_down, e0, limit)
+        out = experts_ref(x, ids, weights, w_gate_up, w_down, e0, limit, gu_bias, down_bias, act)
         if residual is not None:
             out = out + residual.float()
         if extra is not None:
@@ -166,12 +183,14 @@ def experts_forward(x, ids, weights, w_gate_up, w_down, e0=0, residual=None, ext
     sm = _sm_count(dev)
     wgu = w_gate_up.view(E_local * two_i, H)
     code = lib().eredu_gemm_bf16_grouped(ptr(xp), ptr(wgu), ptr(act), ptr(plan.work), plan.n_work, tile, rows_cap, inter,
-                                         H, H, H, inter, E_local * two_i, two_i, 1, 0, sm, ptr(st), stream_ptr(dev))
+                                         H, H, H, inter, E_local * two_i, two_i, 1, 0, sm, ptr(st), ptr(gu_bias),
+                                         two_i if gu_bias is not None else 0, ACTS[act], float(limit), stream_ptr(dev))
     check(code, "eredu_gemm_bf16_grouped(gate_up)")
     y = torch.empty((rows_cap, H), dtype=x.dtype, device=dev)
     wd = w_down.view(E_local * H, inter)
     code = lib().eredu_gemm_bf16_grouped(ptr(act), ptr(wd), ptr(y), ptr(plan.work), plan.n_work, tile, rows_cap, H,
-                                         inter, inter, inter, H, E_local * H, H, 0, 0, sm, ptr(st), stream_ptr(dev))
+                                         inter, inter, inter, H, E_local * H, H, 0, 0, sm, ptr(st), ptr(down_bias),
+                                         H if down_bias is not None else 0, 0, 0.0, stream_ptr(dev))
     check(code, "eredu_gemm_bf16_grouped(down)")
     out = torch.empty((T, H), dtype=x.dtype, device=dev)
     if comm is not None:

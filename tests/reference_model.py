@@ -53,8 +53,13 @@ def forward_logits(cfg, sd, tokens, moe_fn=None):
         if w > 0:
             mask = mask & (pos[None, :] > pos[:, None] - w)
         s = s.masked_fill(~mask[None], float("-inf"))
-        a = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), v).reshape(T, Hq * D)
-        h = h + F.linear(a, sd[p + "self_attn.o_proj.weight"])
+        if p + "self_attn.sinks" in sd:   # a learned per-head logit that only takes probability mass
+            sink = sd[p + "self_attn.sinks"].view(Hq, 1, 1).expand(Hq, T, 1)
+            probs = torch.softmax(torch.cat((s, sink), -1), -1)[..., :-1]
+        else:
+            probs = torch.softmax(s, -1)
+        a = torch.einsum("hqk,khd->qhd", probs, v).reshape(T, Hq * D)
+        h = h + F.linear(a, sd[p + "self_attn.o_proj.weight"], sd.get(p + "self_attn.o_proj.bias"))
         x = rms(h, sd[p + "post_attention_layernorm.weight"], cfg.rms_norm_eps, cfg.norm_weight_offset)
         if cfg.layer_is_moe(li):
             h = h + moe_fn(cfg, sd, li, x)
