@@ -10,7 +10,7 @@ from dataclasses import dataclass, field, asdict
 from pathlib import Path
 from typing import Any
 
-DENSE_TYPES = {"llama", "mistral", "qwen2", "qwen3"}
+DENSE_TYPES = {"llama", "mistral", "qwen2", "qwen3", "phi3"}
 MOE_TYPES = {"qwen3_moe", "mixtral", "gpt_oss", "deepseek_v3", "lfm2_moe", "nemotron_h"}
 
 
@@ -83,7 +83,7 @@ class ModelConfig:
                                                                 "router_scoring", "attention_sinks", "quantization")}
         d["architectures"] = [{"llama": "LlamaForCausalLM", "mistral": "MistralForCausalLM",
                                "qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM",
-                               "qwen3_moe": "Qwen3MoeForCausalLM", "mixtral": "MixtralForCausalLM",
+                               "qwen3_moe": "Qwen3MoeForCausalLM", "mixtral": "MixtralForCausalLM", "phi3": "Phi3ForCausalLM",
                                "gpt_oss": "GptOssForCausalLM"}.get(self.model_type, "LlamaForCausalLM")]
         if not self.is_moe:
             for k in ("num_experts", "num_experts_per_tok", "moe_intermediate_size", "norm_topk_prob",

@@ -329,8 +329,18 @@ def build_from_tensors(cfg: ModelConfig, get: Callable[[str], torch.Tensor], has
                                                              and not has("lm_head.weight"))) else up(head)
     for li in range(model.first_layer, model.last_layer):
         p = f"model.layers.{li}."
-        wq, wk, wv, wo = (get(p + f"self_attn.{n}_proj.weight") for n in "qkvo")
         bq = bk = bv = None
+        if has(p + "self_attn.qkv_proj.weight"):
+            # Phi-3 style checkpoints store q, k and v as one matrix and gate / up as another
+            qn, kn = cfg.num_attention_heads * cfg.head_dim, cfg.num_key_value_heads * cfg.head_dim
+            fused = get(p + "self_attn.qkv_proj.weight")
+            wq, wk, wv = fused[:qn], fused[qn:qn + kn], fused[qn + kn:qn + 2 * kn]
+            wo = get(p + "self_attn.o_proj.weight")
+            if has(p + "self_attn.qkv_proj.bias"):
+                fb = get(p + "self_attn.qkv_proj.bias")
+                bq, bk, bv = fb[:qn], fb[qn:qn + kn], fb[qn + kn:qn + 2 * kn]
+        else:
+            wq, wk, wv, wo = (get(p + f"self_attn.{n}_proj.weight") for n in "qkvo")
         if has(p + "self_attn.q_proj.bias"):
             bq, bk, bv = (get(p + f"self_attn.{n}_proj.bias") for n in "qkv")
         wqkv, wo_l, bqkv = shard_attention(cfg, par, wq, wk, wv, wo, bq, bk, bv)
@@ -352,7 +362,12 @@ def build_from_tensors(cfg: ModelConfig, get: Callable[[str], torch.Tensor], has
             assert moe_factory is not None, "MoE layer needs a moe_factory"
             lw.moe = moe_factory(model, li, get, has)
         else:
-            wg, wu, wd = (get(p + f"mlp.{n}_proj.weight") for n in ("gate", "up", "down"))
+            if has(p + "mlp.gate_up_proj.weight"):
+                fused = get(p + "mlp.gate_up_proj.weight")
+                wg, wu = fused[: cfg.intermediate_size], fused[cfg.intermediate_size:]
+                wd = get(p + "mlp.down_proj.weight")
+            else:
+                wg, wu, wd = (get(p + f"mlp.{n}_proj.weight") for n in ("gate", "up", "down"))
             if tp > 1:
                 wg, wu, wd = _tp_rows(wg, r, tp), _tp_rows(wu, r, tp), _tp_cols(wd, r, tp)
             lw.w_gate_up = up(torch.cat((wg, wu), 0))

@@ -84,3 +84,35 @@ def test_stochastic_sampling_is_position_addressed():
     c = Engine(model, max_batch=1, max_seq_len=64).generate([prompt], dataclasses.replace(sp, seed=43),
                                                             max_new_tokens=10)[0]
     assert a != c
+
+
+def test_phi3_fused_projection_checkpoints():
+    """Phi-3 stores q|k|v and gate|up as single matrices: same tokens as the split layout."""
+    import dataclasses
+
+    import torch
+
+    from eredu_b200.models import config as C
+    from eredu_b200.models.llama import build_from_tensors, random_state
+    from eredu_b200.ops import SamplingParams
+    from eredu_b200.runtime.engine import Engine
+
+    cfg = dataclasses.replace(C.tiny_llama(), vocab_size=512, model_type="phi3", tie_word_embeddings=False)
+    sd = random_state(cfg, seed=0, std=0.05)
+    fused = {}
+    for k, v in sd.items():
+        if ".self_attn.q_proj.weight" in k:
+            base = k[: -len("q_proj.weight")]
+            fused[base + "qkv_proj.weight"] = torch.cat((sd[base + "q_proj.weight"], sd[base + "k_proj.weight"], sd[base + "v_proj.weight"]), 0)
+        elif ".mlp.gate_proj.weight" in k:
+            base = k[: -len("gate_proj.weight")]
+            fused[base + "gate_up_proj.weight"] = torch.cat((sd[base + "gate_proj.weight"], sd[base + "up_proj.weight"]), 0)
+        elif any(t in k for t in (".k_proj.", ".v_proj.", ".up_proj.")):
+            continue
+        else:
+            fused[k] = v
+    prompt = list(range(5, 25))
+    sp = SamplingParams(temperature=0.0)
+    a = Engine(build_from_tensors(cfg, sd.__getitem__, sd.__contains__, "cpu", torch.float32), 1, 64).generate([prompt], sp, 6)
+    b = Engine(build_from_tensors(cfg, fused.__getitem__, fused.__contains__, "cpu", torch.float32), 1, 64).generate([prompt], sp, 6)
+    assert a == b
