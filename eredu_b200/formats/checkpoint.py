@@ -248,8 +248,23 @@ class SafetensorsSource(TensorSource):
         return t
 
     def get(self, name: str) -> torch.Tensor:
+        qi = self.quant_info(name)
+        if qi is not None and qi["kind"] == "affine":
+            # MLX-LM packed tensor: uint32 code words + per-group scales / biases -> dense fp32 (w = scale * q + bias)
+            packed, scales, biases, bits, group = self.to_affine(name)
+            dense = H.affine_dequantize(packed.numpy().view(np.uint32), scales.float().numpy(), biases.float().numpy(),
+                                        bits, group)
+            return torch.from_numpy(np.asarray(dense))
         info = self.store.info(name)
         return self._wrap(self.store.tensor(name), info["dtype"])
+
+    def to_affine(self, name: str):
+        """(packed int32 [N, K*bits/32], scales, biases, bits, group) of a packed tensor, as stored."""
+        qi = self.quant_info(name)
+        if qi is None or qi["biases"] is None:
+            raise RuntimeError(f"{name} is not an affine-packed tensor")
+        raw = lambda k: self._wrap(self.store.tensor(k), self.store.info(k)["dtype"])   # noqa: E731
+        return raw(name).view(torch.int32), raw(qi["scales"]), raw(qi["biases"]), qi["bits"], qi["group_size"]
 
     def get_rows(self, name: str, start: int, stop: int) -> torch.Tensor:
         """Rank-selective read: only rows [start, stop) are touched (and paged in)."""

@@ -4,6 +4,7 @@ import os
 
 import numpy as np
 import pytest
+import torch
 
 from eredu_b200.lib import _eredu_host as H
 
@@ -186,3 +187,39 @@ def test_mxfp4_round_trip():
     exact = np.array([[0.5, -1.0, 1.5, 2.0, -3.0, 4.0, 6.0, 0.0] * 4], dtype=np.float32)
     p, s = H.mxfp4_quantize(exact)
     assert np.array_equal(H.mxfp4_dequantize(p, s), exact)
+
+
+def test_quantize_checkpoint_tool_round_trip(tmp_path):
+    """quantize_checkpoint writes MLX-LM packed tensors + both config keys; the packed directory loads and runs, its
+    dense reading equals the host dequantiser, already-packed sources are refused."""
+    import dataclasses
+    import json
+
+    from eredu_b200.api import LoadedModel, ModelLoadOptions
+    from eredu_b200.formats import checkpoint as ck
+    from eredu_b200.formats.quantize import eligible, quantize_checkpoint
+    from eredu_b200.lib import _eredu_host as H
+    from eredu_b200.models import config as C
+    from eredu_b200.models.llama import random_state
+
+    cfg = dataclasses.replace(C.tiny_llama(), vocab_size=512, intermediate_size=704)
+    sd = random_state(cfg, seed=0, std=0.05)
+    ck.save_safetensors_checkpoint(tmp_path / "src", cfg, sd, torch.float32)
+    rep = quantize_checkpoint(tmp_path / "src", tmp_path / "q4", bits=4, group_size=64)
+    assert rep["quantized"] == cfg.num_hidden_layers * 7 and rep["bytes_after"] < rep["bytes_before"]
+    qcfg = json.loads((tmp_path / "q4" / "config.json").read_text())
+    assert qcfg["quantization"] == qcfg["quantization_config"] == {"group_size": 64, "bits": 4, "mode": "affine"}
+    src = ck.open_checkpoint(tmp_path / "q4")
+    name = "model.layers.0.mlp.down_proj.weight"
+    packed, scales, biases, bits, group = src.to_affine(name)
+    assert packed.shape == (cfg.hidden_size, cfg.intermediate_size * 4 // 32) and (bits, group) == (4, 64)
+    hp, hs, hb = H.affine_quantize(sd[name].numpy(), 4, 64, "f16")
+    assert np.array_equal(packed.numpy().view(np.uint32), hp)
+    dense = src.get(name)
+    assert float((dense - sd[name]).abs().max()) < float(sd[name].abs().max()) / 7       # within one 4-bit step
+    assert torch.equal(src.get("model.norm.weight"), sd["model.norm.weight"])              # norms stay dense
+    assert not eligible("model.embed_tokens.weight", (512, 256), "F32", 64) and not eligible("x.weight", (8, 48), "F32", 64)
+    lm = LoadedModel.load(tmp_path / "q4", ModelLoadOptions(device="cpu", max_batch=1, max_seq_len=64))
+    assert len(lm.generate([list(range(10))], None, 5)[0]) == 5
+    with pytest.raises(ValueError):
+        quantize_checkpoint(tmp_path / "q4", tmp_path / "again")
