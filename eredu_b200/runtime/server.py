@@ -44,6 +44,20 @@ class TorchTransport:
         self.size = dist.get_world_size(group)
         self.device = torch.device(device)
 
+    def all_gather_varlen(self, words: list[int]) -> list[list[int]]:
+        """Every rank's word list (lengths may differ), in rank order."""
+        n = torch.tensor([len(words)], dtype=torch.int64, device=self.device)
+        lens = [torch.zeros_like(n) for _ in range(self.size)]
+        self.dist.all_gather(lens, n, group=self.group)
+        lens = [int(x.item()) for x in lens]
+        width = max(lens + [1])
+        t = torch.zeros(width, dtype=torch.int64, device=self.device)
+        if words:
+            t[:len(words)] = torch.tensor(words, dtype=torch.int64, device=self.device)
+        out = [torch.zeros_like(t) for _ in range(self.size)]
+        self.dist.all_gather(out, t, group=self.group)
+        return [o[:k].tolist() for o, k in zip(out, lens)]
+
     def all_gather_words(self, words: list[int]) -> list[int]:
         # lengths first: a rank with a different plan may also have a different frame length
         n = torch.tensor([len(words)], dtype=torch.int64, device=self.device)
@@ -80,6 +94,7 @@ class Server:
         self.sched = H.Scheduler(engine.max_batch, max_step_tokens, max_waiting, prefill_chunk)
         self.requests: dict[int, ServedRequest] = {}
         self.drain_cycle = 0
+        self._pending_cancels: set = set()
         self.fault_hook = fault_hook  # (kind, request_id) -> True injects a request-local failure on this rank
         engine.open_decode(penalties=penalties)
 
@@ -113,7 +128,28 @@ class Server:
                     raise
 
     def cancel(self, request_id: int) -> None:
-        self.sched.cancel(request_id)
+        """Cooperative cancellation. Single rank: takes effect now (or when the request's in-flight work completes).
+        With a transport the request is only recorded; at the next step boundary every rank learns the union of all
+        ranks' cancellations and applies it before planning, so the plans keep agreeing
+        (eredu/src/backend/mlx/distributed.rs:216-241)."""
+        if self.transport is None:
+            self.sched.cancel(request_id)
+            self._retire_terminal()
+        else:
+            self._pending_cancels.add(int(request_id))
+
+    def _exchange_cancels(self) -> None:
+        if self.transport is None:
+            return
+        try:
+            everyone = self.transport.all_gather_varlen(sorted(self._pending_cancels))
+        except Exception as e:
+            self.sched.poison(f"cancellation exchange failed: {e}")
+            raise ConsensusError(str(e)) from e
+        self._pending_cancels.clear()
+        for rid in sorted({r for ranks in everyone for r in ranks}):
+            if rid in self.requests:
+                self.sched.cancel(rid)
         self._retire_terminal()
 
     def pending(self) -> bool:
@@ -141,6 +177,7 @@ class Server:
     # ------------------------------------------------------------------------------------------ one step
     def step(self, now: Optional[float] = None) -> int:
         """Plan, agree, execute and complete one step. Returns the number of work items executed."""
+        self._exchange_cancels()
         plan = self.sched.plan_step(time.monotonic() if now is None else now)
         self._retire_terminal()  # deadline cancellations decided while planning
         if not plan:

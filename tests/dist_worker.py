@@ -122,6 +122,15 @@ def main():
         ids = [srv.submit(p, sp, 6) for p in prompts]
         srv.run_until_idle(max_steps=200)
         result["tokens"] = [srv.result(i).tokens for i in ids]
+        # a cancellation issued on ONE rank reaches every rank at the same step boundary
+        cid = srv.submit(prompts[1], sp, 40)
+        keep = srv.submit(prompts[0], sp, 8)
+        for _ in range(4):
+            srv.step()
+        if rank == world - 1:
+            srv.cancel(cid)
+        srv.run_until_idle(max_steps=300)
+        result["cancelled"] = [srv.result(cid).finish_reason, len(srv.result(cid).tokens), srv.result(keep).tokens]
         # now the ranks diverge: rank 1 sees a request the others do not
         srv.submit(prompts[0][: 5 + rank], sp, 3)
         try:

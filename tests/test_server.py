@@ -85,5 +85,8 @@ def test_cancel_deadline_failure_and_streaming_stop():
 def test_consensus_across_ranks(world, tmp_path):
     res = run_ranks("cpu_server", world, tmp_path)
     assert all(r["tokens"] == res[0]["tokens"] for r in res)
+    # the request cancelled on the last rank ended as cancelled on every rank after the same number of tokens
+    assert all(r["cancelled"] == res[0]["cancelled"] for r in res)
+    assert res[0]["cancelled"][0] == "cancelled" and res[0]["cancelled"][1] < 40 and len(res[0]["cancelled"][2]) == 8
     assert all(r["diverged"] == "ConsensusError" for r in res)
     assert all(r["poisoned"] for r in res)
