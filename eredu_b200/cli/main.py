@@ -122,11 +122,51 @@ def main(argv=None) -> int:
     bits = a.quantize or (int(quant_suffix) if quant_suffix.isdigit() else None)
     if bits:
         quant = QuantizationOptions(bits=bits, group_size=a.quantization_group_size, mode=a.quantization_mode)
+    # ---- automatic planning (--auto plan|quick|benchmark; --no-auto keeps exactly what the flags say)
+    plan = None
+    layerwise, window = a.layerwise_host, a.device_layer_window
+    if not a.no_auto:
+        from ..runtime.plan import AutomaticPlanner, ExecutionPlan, HardwareProfile, estimate_runtime_state, inspect_artifact
+
+        report = inspect_artifact(model_path)
+        if not report.is_loadable:
+            for issue in report.issues:
+                print(f"[eredu] {issue.severity}: {issue.code}: {issue.message}", file=sys.stderr)
+            raise SystemExit(2)
+        cache_path = a.auto_cache
+        key = f"{report.model_type}:{report.tensor_bytes}:{device}:{a.max_tokens}"
+        cached = None
+        if cache_path:
+            try:
+                cached = json.load(open(cache_path)).get(key)
+            except (OSError, ValueError):
+                cached = None
+        if cached:
+            plan = ExecutionPlan.from_json(json.dumps(cached))
+        else:
+            hw = HardwareProfile.discover() if device != "cpu" else HardwareProfile(device_count=1, device_memory_bytes=1 << 62, name="cpu")
+            hw.device_count = 1     # the command-line front end drives one device; multi-GPU runs use the library API
+            prof = estimate_runtime_state(report.config, report.tensor_bytes)
+            plan = AutomaticPlanner(hw).plan(report.config, prof, context=max(4096, a.max_tokens + 2048), batch=1,
+                                             draft_model=a.draft_model, allow_quantization=quant is None)
+            if cache_path:
+                try:
+                    book = json.load(open(cache_path))
+                except (OSError, ValueError):
+                    book = {}
+                book[key] = json.loads(plan.to_json())
+                json.dump(book, open(cache_path, "w"), indent=1)
+        if quant is None and plan.weight_transformation.get("mode") == "affine" and device != "cpu":
+            quant = QuantizationOptions(bits=plan.weight_transformation["bits"], group_size=plan.weight_transformation["group_size"])
+        if plan.residency.get("mode") == "layerwise_host" and not layerwise:
+            layerwise, window = True, int(plan.residency.get("device_layer_window", 1))
+        if a.verbose or a.auto == "plan":
+            print("[eredu] plan: " + "; ".join(plan.rationale), file=sys.stderr)
     t0 = time.perf_counter()
     lm = LoadedModel.load(model_path, ModelLoadOptions(device=device, quantization=quant, mapped_shards=a.mapped_shards,
                                                        max_batch=1, max_seq_len=max(4096, a.max_tokens + 2048),
-                                                       weight_residency="layerwise_host" if a.layerwise_host else "device",
-                                                       device_layer_window=a.device_layer_window,
+                                                       weight_residency="layerwise_host" if layerwise else "device",
+                                                       device_layer_window=window,
                                                        expert_cache=a.expert_cache,
                                                        expert_cache_device_budget_bytes=a.expert_cache_device_budget_bytes,
                                                        expert_cache_eviction=a.expert_cache_eviction))
@@ -166,6 +206,7 @@ def main(argv=None) -> int:
               f"{timing['token_rate']:.2f} tok/s  stop={res['finish_reason']}", file=sys.stderr)
     if a.telemetry_json:
         tel = ExecutionTelemetry(plan={"device": device, "auto": None if a.no_auto else a.auto, "quantization": vars(quant) if quant else None,
+                                       "execution_plan": json.loads(plan.to_json()) if plan is not None else None,
                                        "flags": {k: v for k, v in vars(a).items() if k not in ("prompt",)}},
                                  hardware=hardware_profile(device), prompt_tokens=res["prompt_tokens"],
                                  generated_tokens=len(res["tokens"]), stop_reason=res["finish_reason"], timing=timing,

@@ -47,3 +47,28 @@ def test_cli_end_to_end_cpu(tmp_path, capsys):
     t = json.loads(tel.read_text())
     assert t["generated_tokens"] <= 8 and t["prompt_tokens"] > 0 and t["stop_reason"] in ("max_tokens", "eos")
     assert t["weights_bytes"] > 0 and t["plan"]["device"] == "cpu" and "host" in t["hardware"]
+
+
+def test_cli_automatic_plan_and_cache(tmp_path, capsys):
+    from eredu_b200.formats import checkpoint as ck
+    from eredu_b200.models import config as C
+    from eredu_b200.models.llama import random_state
+
+    b = make_bundle(tmp_path)
+    cfg = dataclasses.replace(C.tiny_llama(), vocab_size=b.vocab_size(), eos_token_id=b.eos_ids[0])
+    ck.save_safetensors_checkpoint(tmp_path, cfg, random_state(cfg, seed=0, std=0.05), torch.float32)
+    tel, cache = tmp_path / "tel.json", tmp_path / "auto.json"
+    args = ["-m", str(tmp_path), "hi", "--device", "cpu", "-n", "4", "--auto", "plan", "--auto-cache", str(cache),
+            "--telemetry-json", str(tel)]
+    assert main(args) == 0
+    assert "plan:" in capsys.readouterr().err
+    plan = json.loads(tel.read_text())["plan"]["execution_plan"]
+    assert plan["schema_version"] == 2 and plan["residency"]["mode"] == "fully_resident" and plan["topology"]["tensor"] == 1
+    assert len(json.loads(cache.read_text())) == 1
+    assert main(args) == 0                                     # second run takes the cached plan
+    # an artifact that cannot be loaded is refused before any payload is read
+    bad = tmp_path / "bad"
+    bad.mkdir()
+    (bad / "config.json").write_text(json.dumps({"model_type": "deepseek_v3", "hidden_size": 64}))
+    with pytest.raises(SystemExit):
+        main(["-m", str(bad), "hi", "--device", "cpu"])
