@@ -176,10 +176,21 @@ class LoadedModel:
                             thinking=thinking, stop=stop, allow_unparsed_reasoning=allow_unparsed_reasoning,
                             **template_kwargs)
 
+    def constraint_for(self, kind: str, spec):
+        """Grammar constraint over this model's tokenizer: ``kind`` is "json_schema", "lark" or "regex"
+        (response_format / structured tool arguments; eredu/src/backend/mlx/runtime/chat/constraints.rs)."""
+        from ..ops.controlled import GrammarConstraint
+
+        if self.tokenizer is None:
+            raise RuntimeError("this checkpoint has no tokenizer")
+        return GrammarConstraint(self.tokenizer, kind, spec)
+
     def generate_prepared_chat(self, prepared, sampling: Optional[SamplingParams] = None, max_new_tokens: int = 256,
-                               on_event=None, cancellation=None, raw: bool = False):
+                               on_event=None, cancellation=None, raw: bool = False, mirostat=None, constraint=None):
         """Generate a reply for a :class:`PreparedChat`, streaming semantic events (reasoning, text, tool-call
         start / arguments / end, finished) to ``on_event`` (``generate_prepared_chat``, api/loaded.rs:154-227).
+        ``mirostat`` (an :class:`ops.controlled.MirostatV2`) and ``constraint`` (a :class:`GrammarConstraint`, e.g.
+        from :meth:`constraint_for`) switch to the host-driven controlled sampler.
         Returns a dict with text, reasoning, tool_calls, finish_reason, token ids and timing."""
         import time
 
@@ -209,8 +220,18 @@ class LoadedModel:
                 return FinishReason.CANCELLED
             return None
 
-        self.engine.generate([prompt_ids], sampling or SamplingParams(), max_new_tokens, eos_ids=(), on_token=on_token)
-        reason = self.engine.last_finish_reasons[0] or FinishReason.MAX_TOKENS
+        if mirostat is not None or constraint is not None:
+            from ..ops.controlled import controlled_generate
+
+            _, why = controlled_generate(self.engine, prompt_ids, sampling, max_new_tokens, tuple(eos), constraint,
+                                         mirostat, on_token=lambda tok: on_token(0, tok))
+            reason = {"eos": FinishReason.EOS, "max_tokens": FinishReason.MAX_TOKENS,
+                      "grammar_complete": FinishReason.GRAMMAR_COMPLETE}.get(why, why)
+            if first_token_at[0] is None:
+                first_token_at[0] = time.perf_counter()
+        else:
+            self.engine.generate([prompt_ids], sampling or SamplingParams(), max_new_tokens, eos_ids=(), on_token=on_token)
+            reason = self.engine.last_finish_reasons[0] or FinishReason.MAX_TOKENS
         pipe.finish(reason)
         t1 = time.perf_counter()
         ttft = (first_token_at[0] or t1) - t0

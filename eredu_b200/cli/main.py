@@ -67,6 +67,9 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--mapped-shards", type=int, default=4)
     p.add_argument("--raw", action="store_true", help="no chat template: the prompt is fed verbatim")
     p.add_argument("--tools", default=None, metavar="PATH")
+    p.add_argument("--json-schema", default=None, metavar="PATH", help="constrain the reply to this JSON schema")
+    p.add_argument("--grammar", default=None, metavar="PATH", help="constrain the reply to this Lark grammar")
+    p.add_argument("--regex", default=None, help="constrain the reply to this regular expression")
     p.add_argument("--tool-choice", choices=["none", "auto", "required"], default="auto")
     p.add_argument("--max-parallel-tool-calls", type=int, default=None)
     p.add_argument("--stop", action="append", default=[], metavar="TEXT")
@@ -197,7 +200,23 @@ def main(argv=None) -> int:
         prepared = lm.prepare_chat([{"role": "user", "content": prompt}], tools=tools,
                                    tool_choice=ToolChoice(a.tool_choice, a.max_parallel_tool_calls), thinking=a.thinking,
                                    stop=a.stop, allow_unparsed_reasoning=a.allow_unparsed_reasoning)
-    res = lm.generate_prepared_chat(prepared, sp, a.max_tokens, on_event=on_event, raw=a.raw)
+    mirostat = None
+    if a.mirostat_v2:
+        from ..ops.controlled import MirostatV2
+
+        if sp.temperature <= 0:
+            raise SystemExit("--mirostat-v2 requires an effective temperature greater than zero")
+        mirostat = MirostatV2(a.mirostat_tau, a.mirostat_eta, sp.temperature, sp.seed, sp.repeat_penalty, sp.repeat_last_n,
+                              sp.frequency_penalty, sp.presence_penalty)
+    constraint = None
+    given = [(k, v) for k, v in (("json_schema", a.json_schema), ("lark", a.grammar), ("regex", a.regex)) if v]
+    if len(given) > 1:
+        raise SystemExit("give at most one of --json-schema, --grammar, --regex")
+    if given:
+        kind, val = given[0]
+        constraint = lm.constraint_for(kind, val if kind == "regex" else open(val).read())
+    res = lm.generate_prepared_chat(prepared, sp, a.max_tokens, on_event=on_event, raw=a.raw, mirostat=mirostat,
+                                    constraint=constraint)
     sys.stdout.write("\n")
     timing = dict(res["timing"], load_time=load_time)
     if a.timing or a.verbose:

@@ -171,11 +171,15 @@ def _ll_tokenizer(tok):
     return _LL_CACHE[key]
 
 
-def constrained_generate(engine, prompt: list[int], constraint: GrammarConstraint, sampling: Optional[SamplingParams] = None,
-                         max_new_tokens: int = 256, eos_ids=(), mirostat: Optional[MirostatV2] = None):
-    """Single-sequence generation under a grammar (and optionally Mirostat): every step's logits go through the
-    constraint's mask before sampling; the grammar's own end stops the request. Returns (tokens, finish_reason).
+def controlled_generate(engine, prompt: list[int], sampling: Optional[SamplingParams] = None, max_new_tokens: int = 256,
+                        eos_ids=(), constraint: Optional[GrammarConstraint] = None, mirostat: Optional[MirostatV2] = None,
+                        on_token=None):
+    """Single-sequence generation with a stateful sampler: a grammar, Mirostat, or both. Every step's logits go
+    through the constraint's mask before sampling; the grammar's own end stops the request. ``on_token(token)`` may
+    return a finish reason to stop early (stop strings, cancellation). Returns (tokens, finish_reason).
     Runs the model through ``engine`` one decode step at a time (host-driven: the mask depends on the last token)."""
+    from .sampling import sample_ref
+
     sp = sampling or SamplingParams(temperature=0.0)
     seq = engine.new_sequence(prompt, sp, max_new_tokens, eos_ids)
     out: list[int] = []
@@ -183,23 +187,28 @@ def constrained_generate(engine, prompt: list[int], constraint: GrammarConstrain
     try:
         logits = engine.prefill_logits([seq])[0]
         for step in range(max_new_tokens):
-            allow = constraint.allow_mask(logits.shape[-1])
-            # EOS is legal exactly where the grammar accepts an end
-            for e in eos_ids:
-                allow[e] = constraint.is_accepting()
+            allow = None
+            if constraint is not None:
+                allow = constraint.allow_mask(logits.shape[-1])
+                for e in eos_ids:                     # EOS is legal exactly where the grammar accepts an end
+                    allow[e] = constraint.is_accepting()
             pos = len(prompt) + step
             if mirostat is not None:
                 tok = mirostat.sample(logits, pos, seq.seq_id, allow)
             else:
-                from .sampling import sample_ref
-
                 tok, _ = sample_ref(logits.float().cpu(), sp, pos, history=out, allow=allow, stream=seq.seq_id)
             if tok in eos_ids:
                 reason = "eos"
                 break
-            constraint.commit(tok)
+            if constraint is not None:
+                constraint.commit(tok)
             out.append(tok)
-            if constraint.is_complete():
+            if on_token is not None:
+                early = on_token(tok)
+                if early:
+                    reason = early
+                    break
+            if constraint is not None and constraint.is_complete():
                 reason = "grammar_complete"
                 break
             if step + 1 == max_new_tokens:
@@ -208,3 +217,9 @@ def constrained_generate(engine, prompt: list[int], constraint: GrammarConstrain
     finally:
         engine.release(seq)
     return out, reason
+
+
+def constrained_generate(engine, prompt: list[int], constraint: GrammarConstraint, sampling: Optional[SamplingParams] = None,
+                         max_new_tokens: int = 256, eos_ids=(), mirostat: Optional[MirostatV2] = None):
+    """:func:`controlled_generate` with a mandatory grammar."""
+    return controlled_generate(engine, prompt, sampling, max_new_tokens, eos_ids, constraint, mirostat)

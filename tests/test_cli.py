@@ -72,3 +72,30 @@ def test_cli_automatic_plan_and_cache(tmp_path, capsys):
     (bad / "config.json").write_text(json.dumps({"model_type": "deepseek_v3", "hidden_size": 64}))
     with pytest.raises(SystemExit):
         main(["-m", str(bad), "hi", "--device", "cpu"])
+
+
+def test_cli_mirostat_and_regex_constraint(tmp_path, capsys):
+    pytest.importorskip("llguidance")
+    from eredu_b200.formats import checkpoint as ck
+    from eredu_b200.models import config as C
+    from eredu_b200.models.llama import random_state
+
+    b = make_bundle(tmp_path)
+    cfg = dataclasses.replace(C.tiny_llama(), vocab_size=b.vocab_size(), eos_token_id=b.eos_ids[0])
+    ck.save_safetensors_checkpoint(tmp_path, cfg, random_state(cfg, seed=0, std=0.05), torch.float32)
+    base = ["-m", str(tmp_path), "hello", "--device", "cpu", "--no-auto", "--raw"]
+    tel = tmp_path / "t.json"
+    assert main(base + ["-n", "6", "--mirostat-v2", "-t", "0.9", "--seed", "3", "--telemetry-json", str(tel)]) == 0
+    first = capsys.readouterr().out
+    assert json.loads(tel.read_text())["generated_tokens"] <= 6
+    assert main(base + ["-n", "6", "--mirostat-v2", "-t", "0.9", "--seed", "3"]) == 0
+    assert capsys.readouterr().out == first                    # seeded: reproducible
+    with pytest.raises(SystemExit):
+        main(base + ["--mirostat-v2", "-t", "0"])
+    # a regular expression bounds the reply: whatever the random model prefers, the text matches it
+    assert main(base + ["-n", "12", "--regex", "(ab|ba){1,3}", "--telemetry-json", str(tel)]) == 0
+    text = capsys.readouterr().out.strip()
+    import re
+
+    assert re.fullmatch("(ab|ba){1,3}", text), text
+    assert json.loads(tel.read_text())["stop_reason"] in ("grammar_complete", "eos")
