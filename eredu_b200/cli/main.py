@@ -48,7 +48,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--presence-penalty", type=float, default=0.0)
     p.add_argument("--seed", type=int, default=0)
     p.add_argument("--quantize", type=int, default=None, metavar="BITS")
-    p.add_argument("--quantization-mode", choices=["affine", "mxfp4"], default="affine")
+    p.add_argument("--quantization-mode", choices=["affine", "mxfp4", "fp8"], default="affine")
     p.add_argument("--quantization-group-size", type=int, default=64)
     p.add_argument("--layerwise-host", action="store_true")
     p.add_argument("--dense-disk-stream", action="store_true")
@@ -85,6 +85,8 @@ def build_parser() -> argparse.ArgumentParser:
 def validate_args(a) -> None:
     if a.max_tokens <= 0:
         raise SystemExit("--max-tokens must be positive")
+    if a.quantization_mode == "fp8" and a.quantize not in (None, 8):
+        raise SystemExit("--quantization-mode fp8 stores 8-bit E4M3 codes: use --quantize 8")
     if a.quantize is not None and a.quantize not in (2, 3, 4, 5, 6, 8):
         raise SystemExit("--quantize must be one of 2, 3, 4, 5, 6, 8")
     if a.quantization_group_size != 16 and a.quantization_group_size % 32 != 0:

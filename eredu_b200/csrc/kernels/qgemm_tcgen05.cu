@@ -12,9 +12,13 @@
 //   QF_AFFINE4: codes [N, K/2] bytes; inside each u32 the eight nibbles are stored as (n0,n2,n4,n6,n1,n3,n5,n7)
 //   QF_AFFINE8: codes [N, K] bytes (also the container for 2/3/5/6-bit codes and for GGUF Q5/Q6 blocks)
 //   scales / biases bf16, transposed to [K/group, N] so that a K block's 128 values are contiguous.
+//   QF_FP8: E4M3 bytes [N, K] with one fp32 scale per weight row per 128 input columns, table [K/128, N]
+//     (the 128x128 block scales of an FP8 checkpoint expanded along the rows, so that tensor-parallel row slices
+//     need no alignment; weight = e4m3 * scale, eredu/src/backend/mlx/nn/fp8.rs:330-345). Activations stay bf16.
 // GGUF Q4_0/Q4_1/Q4_K map to QF_AFFINE4 with group 32, Q8_0 to QF_AFFINE8 (conversion rule:
 // eredu-gguf/src/convert.rs:124-152); the codes are the file's codes, only the layout changes.
 #include <cooperative_groups.h>
+#include <cuda_fp16.h>
 
 #include "../common/launch.h"
 #include "../common/launch_count.h"
@@ -25,7 +29,7 @@ namespace cg = cooperative_groups;
 
 namespace eredu {
 
-enum { QF_AFFINE4 = 0, QF_AFFINE8 = 3 };
+enum { QF_AFFINE4 = 0, QF_AFFINE8 = 3, QF_FP8 = 5 };
 
 struct QGemmParams {
   void* y;
@@ -33,6 +37,7 @@ struct QGemmParams {
   const void* bias;
   const __nv_bfloat16* scales_t;  // affine: [K/group, N]
   const __nv_bfloat16* biases_t;  // affine: [K/group, N]
+  const float* scales_f32;        // QF_FP8: [K/128, N]
   int M, N, K;
   int ldy, ldr;
   int group;
@@ -176,6 +181,30 @@ __device__ __forceinline__ void dequant_half_row(const QGemmParams& p, const uin
       }
       store_chunk(a_tile, r, half * 4 + w, o);
     }
+  } else if (FMT == QF_FP8) {  // 64 E4M3 bytes per row per K block, this thread takes 32; one scale for all of them
+    const uint4 lo = *reinterpret_cast<const uint4*>(raw + r * 64 + half * 32);
+    const uint4 hi = *reinterpret_cast<const uint4*>(raw + r * 64 + half * 32 + 16);
+    const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+    float sc = 0.f;
+    if (s_sm != nullptr) sc = reinterpret_cast<const float*>(s_sm)[r];
+    else if (live) sc = p.scales_f32[static_cast<size_t>(k0 >> 7) * p.N + n];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint4 o;
+      uint32_t* ov = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+      for (int hw = 0; hw < 2; ++hw) {
+        const uint32_t x = words[c * 2 + hw];
+        uint32_t h01, h23;
+        asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h01) : "h"(static_cast<uint16_t>(x & 0xFFFFu)));
+        asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h23) : "h"(static_cast<uint16_t>(x >> 16)));
+        const float2 f01 = __half22float2(*reinterpret_cast<const __half2*>(&h01));
+        const float2 f23 = __half22float2(*reinterpret_cast<const __half2*>(&h23));
+        ov[hw * 2] = pack_bf16x2(f01.x * sc, f01.y * sc);
+        ov[hw * 2 + 1] = pack_bf16x2(f23.x * sc, f23.y * sc);
+      }
+      store_chunk(a_tile, r, half * 4 + c, o);
+    }
   } else {  // QF_AFFINE8: 64 bytes per row per K block, this thread takes 32 of them
     const uint4 lo = *reinterpret_cast<const uint4*>(raw + r * 64 + half * 32);
     const uint4 hi = *reinterpret_cast<const uint4*>(raw + r * 64 + half * 32 + 16);
@@ -286,14 +315,14 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         if (!ok) break;
         uint8_t* st = raw_ring + s * Cfg::kRawSlot;
         const int kb = kb0 + it;
-        mbar_arrive_expect_tx(&raw_full[s], Cfg::kRaw + Cfg::kBTile + 2 * p.sb_rows * 256);
+        mbar_arrive_expect_tx(&raw_full[s], Cfg::kRaw + Cfg::kBTile + (FMT == QF_FP8 ? p.sb_rows * 512 : 2 * p.sb_rows * 256));
         // packed weights: byte tensor [N, row_bytes]; x coordinate in bytes (a multiple of 32)
         tma_load_2d_hint(st + kRawOff, &tmQ, kb * QRaw<FMT>::kBox0, tile_n * 128, &raw_full[s], pol_w);
         tma_load_2d_hint(st, &tmX, kb * 64, tile_m * TN, &raw_full[s], pol_x);
         if (p.sb_rows > 0) {
           const int grow = (kb * 64) >> p.group_shift;
           tma_load_2d_hint(st + kScaleOff, &tmS, tile_n * 128, grow, &raw_full[s], pol_w);
-          tma_load_2d_hint(st + kBiasOff, &tmB, tile_n * 128, grow, &raw_full[s], pol_w);
+          if (FMT != QF_FP8) tma_load_2d_hint(st + kBiasOff, &tmB, tile_n * 128, grow, &raw_full[s], pol_w);
         }
         issued = it + 1;
       }
@@ -487,39 +516,47 @@ __global__ void __launch_bounds__(256) dequant_matrix_kernel(const uint8_t* __re
 
 using namespace eredu;
 
-extern "C" int eredu_dequant_affine(const void* wq, const void* scales_t, const void* biases_t, void* out, int N, int K,
-                                    int bits, int group, cudaStream_t stream) {
-  if ((bits != 4 && bits != 8) || K % 64 != 0 || group <= 0 || K % group != 0) return -1;
+static int dequant_impl(int fmt, const void* wq, const void* scales_t, const void* biases_t, void* out, int N, int K, int group,
+                        cudaStream_t stream) {
+  if (K % 64 != 0 || group <= 0 || K % group != 0) return -1;
   QGemmParams p = {};
   p.scales_t = static_cast<const __nv_bfloat16*>(scales_t);
   p.biases_t = static_cast<const __nv_bfloat16*>(biases_t);
+  p.scales_f32 = static_cast<const float*>(scales_t);
   p.N = N;
   p.K = K;
   p.group = group;
   p.group_shift = (group & (group - 1)) == 0 ? __builtin_ctz(static_cast<unsigned>(group)) : -1;
   dim3 grid(K / 64, (N + 127) / 128);
-  if (bits == 4)
-    launch_pdl(dequant_matrix_kernel<QF_AFFINE4>, grid, dim3(256), 0, stream, static_cast<const uint8_t*>(wq), p,
-               static_cast<__nv_bfloat16*>(out));
-  else
-    launch_pdl(dequant_matrix_kernel<QF_AFFINE8>, grid, dim3(256), 0, stream, static_cast<const uint8_t*>(wq), p,
-               static_cast<__nv_bfloat16*>(out));
+  const uint8_t* w = static_cast<const uint8_t*>(wq);
+  __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
+  if (fmt == QF_AFFINE4) launch_pdl(dequant_matrix_kernel<QF_AFFINE4>, grid, dim3(256), 0, stream, w, p, o);
+  else if (fmt == QF_FP8) launch_pdl(dequant_matrix_kernel<QF_FP8>, grid, dim3(256), 0, stream, w, p, o);
+  else launch_pdl(dequant_matrix_kernel<QF_AFFINE8>, grid, dim3(256), 0, stream, w, p, o);
   eredu_count_launches(1);
   return static_cast<int>(cudaGetLastError());
 }
 
+extern "C" int eredu_dequant_affine(const void* wq, const void* scales_t, const void* biases_t, void* out, int N, int K,
+                                    int bits, int group, cudaStream_t stream) {
+  if (bits != 4 && bits != 8) return -1;
+  return dequant_impl(bits == 4 ? QF_AFFINE4 : QF_AFFINE8, wq, scales_t, biases_t, out, N, K, group, stream);
+}
 
-// Y = X dequant(Wq)^T (+bias) (+residual). `wq`: packed codes in kernel layout ([N, K/2] bytes for 4-bit with the
-// nibbles of every u32 interleaved (n0,n2,n4,n6,n1,n3,n5,n7); [N, K] bytes for 8-bit); scales_t / biases_t: bf16
-// [K/group, N]. bits: 4 or 8. K must be a multiple of 64 and of the group size.
-extern "C" int eredu_qgemm(const void* X, const void* wq, const void* scales_t, const void* biases_t, void* Y,
-                           const void* residual, const void* bias, int M, int N, int K, int ldx, int ldy, int ldr, int bits,
-                           int group, int out_fp32, int force_split, int sm_count, int* status, cudaStream_t stream) {
+// Block-scaled E4M3 weights [N, K] with the fp32 row-scale table [K/128, N] -> bf16 [N, K].
+extern "C" int eredu_dequant_fp8(const void* wq, const void* scales_f32_t, void* out, int N, int K, cudaStream_t stream) {
+  if (K % 128 != 0) return -1;
+  return dequant_impl(QF_FP8, wq, scales_f32_t, nullptr, out, N, K, 128, stream);
+}
+
+static int qgemm_impl(int fmt, const void* X, const void* wq, const void* scales_t, const void* biases_t, void* Y,
+                      const void* residual, const void* bias, int M, int N, int K, int ldx, int ldy, int ldr, int group,
+                      int out_fp32, int force_split, int sm_count, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if ((bits != 4 && bits != 8) || K % 64 != 0 || group <= 0 || K % group != 0 || (group != 16 && group % 32 != 0)) return -1;
+  if (K % 64 != 0 || group <= 0 || K % group != 0 || (group != 16 && group % 32 != 0)) return -1;
   const int tn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
-  const int row_bytes = bits == 4 ? K / 2 : K;
-  const int box0 = bits == 4 ? 32 : 64;
+  const int row_bytes = fmt == QF_AFFINE4 ? K / 2 : K;
+  const int box0 = fmt == QF_AFFINE4 ? 32 : 64;
   CUtensorMap tmQ, tmX;
   int r = make_tma_2d(&tmQ, wq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, row_bytes, row_bytes, 128, box0, CU_TENSOR_MAP_SWIZZLE_NONE);
   if (r != 0) return -100 + r;
@@ -531,6 +568,7 @@ extern "C" int eredu_qgemm(const void* X, const void* wq, const void* scales_t, 
   p.bias = bias;
   p.scales_t = static_cast<const __nv_bfloat16*>(scales_t);
   p.biases_t = static_cast<const __nv_bfloat16*>(biases_t);
+  p.scales_f32 = static_cast<const float*>(scales_t);
   p.M = M;
   p.N = N;
   p.K = K;
@@ -544,7 +582,11 @@ extern "C" int eredu_qgemm(const void* X, const void* wq, const void* scales_t, 
   // blocks) and 16-byte aligned rows of the transposed tables
   CUtensorMap tmS = tmX, tmB = tmX;
   p.sb_rows = 0;
-  if (p.group_shift >= 0 && group >= 16 && N % 8 == 0) {
+  if (fmt == QF_FP8) {
+    if (N % 4 == 0 && make_tma_2d(&tmS, scales_t, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, static_cast<uint64_t>(K / 128), N, N, 1, 128,
+                                  CU_TENSOR_MAP_SWIZZLE_NONE) == 0)
+      p.sb_rows = 1;
+  } else if (p.group_shift >= 0 && group >= 16 && N % 8 == 0) {
     const int rows = group >= 64 ? 1 : 64 / group;
     const uint64_t table_rows = static_cast<uint64_t>(K / group);
     if (make_tma_2d(&tmS, scales_t, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, table_rows, N, N, rows, 128, CU_TENSOR_MAP_SWIZZLE_NONE) == 0 &&
@@ -563,8 +605,30 @@ extern "C" int eredu_qgemm(const void* X, const void* wq, const void* scales_t, 
     }
     while (nsplit > 1 && (kblocks + nsplit - 1) / nsplit * (nsplit - 1) >= kblocks) nsplit >>= 1;
   }
-  cudaError_t e = bits == 4 ? dispatch_q<QF_AFFINE4>(tn, tmQ, tmX, tmS, tmB, p, n_tiles, m_tiles, nsplit, stream)
-                            : dispatch_q<QF_AFFINE8>(tn, tmQ, tmX, tmS, tmB, p, n_tiles, m_tiles, nsplit, stream);
+  cudaError_t e = fmt == QF_AFFINE4 ? dispatch_q<QF_AFFINE4>(tn, tmQ, tmX, tmS, tmB, p, n_tiles, m_tiles, nsplit, stream)
+                  : fmt == QF_FP8   ? dispatch_q<QF_FP8>(tn, tmQ, tmX, tmS, tmB, p, n_tiles, m_tiles, nsplit, stream)
+                                    : dispatch_q<QF_AFFINE8>(tn, tmQ, tmX, tmS, tmB, p, n_tiles, m_tiles, nsplit, stream);
   eredu_count_launches(1);
   return static_cast<int>(e);
+}
+
+// Y = X dequant(Wq)^T (+bias) (+residual). `wq`: packed codes in kernel layout ([N, K/2] bytes for 4-bit with the
+// nibbles of every u32 interleaved (n0,n2,n4,n6,n1,n3,n5,n7); [N, K] bytes for 8-bit); scales_t / biases_t: bf16
+// [K/group, N]. bits: 4 or 8. K must be a multiple of 64 and of the group size.
+extern "C" int eredu_qgemm(const void* X, const void* wq, const void* scales_t, const void* biases_t, void* Y,
+                           const void* residual, const void* bias, int M, int N, int K, int ldx, int ldy, int ldr, int bits,
+                           int group, int out_fp32, int force_split, int sm_count, int* status, cudaStream_t stream) {
+  if (bits != 4 && bits != 8) return -1;
+  return qgemm_impl(bits == 4 ? QF_AFFINE4 : QF_AFFINE8, X, wq, scales_t, biases_t, Y, residual, bias, M, N, K, ldx, ldy, ldr,
+                    group, out_fp32, force_split, sm_count, status, stream);
+}
+
+// Y = X (e4m3(Wq) * scale)^T (+bias) (+residual) for block-scaled FP8 weights: wq E4M3 bytes [N, K], scales_f32_t fp32
+// [K/128, N]. K must be a multiple of 128.
+extern "C" int eredu_qgemm_fp8(const void* X, const void* wq, const void* scales_f32_t, void* Y, const void* residual,
+                               const void* bias, int M, int N, int K, int ldx, int ldy, int ldr, int out_fp32, int force_split,
+                               int sm_count, int* status, cudaStream_t stream) {
+  if (K % 128 != 0) return -1;
+  return qgemm_impl(QF_FP8, X, wq, scales_f32_t, nullptr, Y, residual, bias, M, N, K, ldx, ldy, ldr, 128, out_fp32, force_split,
+                    sm_count, status, stream);
 }

@@ -29,11 +29,11 @@ GGML_NAME = {v: k for k, v in GGML.items()}
 
 _ST_DTYPES = {torch.float32: "F32", torch.float16: "F16", torch.bfloat16: "BF16", torch.int32: "I32",
               torch.int64: "I64", torch.uint8: "U8", torch.int8: "I8", torch.bool: "BOOL", torch.float64: "F64",
-              torch.int16: "I16"}
+              torch.int16: "I16", torch.float8_e4m3fn: "F8_E4M3"}
 _ST_TO_TORCH = {"F32": torch.float32, "F16": torch.float16, "BF16": torch.bfloat16, "I32": torch.int32,
                 "I64": torch.int64, "U8": torch.uint8, "I8": torch.int8, "BOOL": torch.bool, "F64": torch.float64,
                 "I16": torch.int16, "U32": torch.int32, "U16": torch.int16, "F8_E4M3": torch.float8_e4m3fn,
-                "F8_E5M2": torch.float8_e5m2}
+                "F8_E5M2": torch.float8_e5m2, "F8_E8M0": torch.uint8}
 
 # ---------------------------------------------------------------------------------------------- names
 _LAYER_MAP = {
@@ -100,6 +100,8 @@ def _np(t: torch.Tensor):
     t = t.detach().cpu().contiguous()
     if t.dtype == torch.bfloat16:
         return t.view(torch.int16).numpy().view(np.uint16)
+    if t.dtype == torch.float8_e4m3fn:
+        return t.view(torch.uint8).numpy()
     return t.numpy()
 
 
@@ -113,7 +115,8 @@ def save_safetensors_checkpoint(path: str | Path, cfg: ModelConfig, state: dict,
     (path / "config.json").write_text(json.dumps(d, indent=1))
     items = []
     for name, t in state.items():
-        if t.is_floating_point() and t.dtype != dtype and not name.endswith((".scales", ".biases")):
+        if (t.is_floating_point() and t.dtype not in (dtype, torch.float8_e4m3fn)
+                and not name.endswith((".scales", ".biases", ".weight_scale_inv", ".weight_scale"))):
             t = t.to(dtype)
         items.append((name, _ST_DTYPES[t.dtype], list(t.shape), _np(t)))
     if shard_bytes is None:
@@ -247,7 +250,35 @@ class SafetensorsSource(TensorSource):
             t = t.view(want)
         return t
 
+    def fp8_scale_name(self, name: str) -> Optional[str]:
+        """Name of the block-scale tensor that goes with an E4M3 weight (HF ``quant_method: fp8`` checkpoints:
+        ``<base>.weight`` F8_E4M3 + ``<base>.weight_scale_inv`` [ceil(N/128), ceil(K/128)]), else None."""
+        if not name.endswith(".weight"):
+            return None
+        for suffix in ("_scale_inv", "_scale"):
+            if name + suffix in self._keys and self.store.info(name)["dtype"] == "F8_E4M3":
+                return name + suffix
+        return None
+
+    def to_fp8(self, name: str):
+        """(E4M3 bytes as uint8 [N, K], fp32 block scales [ceil(N/128), ceil(K/128)]) of a block-scaled weight.
+        Scales stored as E8M0 exponent bytes are decoded to 2^(e-127) (eredu/src/backend/mlx/nn/fp8.rs:74-92)."""
+        sname = self.fp8_scale_name(name)
+        if sname is None:
+            raise RuntimeError(f"{name} is not a block-scaled FP8 tensor")
+        w = self._wrap(self.store.tensor(name), "U8")
+        sinfo = self.store.info(sname)
+        sc = self._wrap(self.store.tensor(sname), sinfo["dtype"])
+        if sinfo["dtype"] in ("U8", "F8_E8M0"):
+            sc = torch.pow(2.0, sc.to(torch.float32) - 127.0)
+        return w, sc.to(torch.float32)
+
     def get(self, name: str) -> torch.Tensor:
+        if self.fp8_scale_name(name) is not None:
+            w, sc = self.to_fp8(name)
+            N, K = w.shape
+            full = sc.repeat_interleave(128, 0)[:N].repeat_interleave(128, 1)[:, :K]
+            return w.view(torch.float8_e4m3fn).to(torch.float32) * full
         qi = self.quant_info(name)
         if qi is not None and qi["kind"] == "affine":
             # MLX-LM packed tensor: uint32 code words + per-group scales / biases -> dense fp32 (w = scale * q + bias)

@@ -11,6 +11,8 @@ other width (2/3/5/6/8 bits) in an 8-bit container ``[N, K]``; scales and biases
 """
 from __future__ import annotations
 
+from typing import Optional
+
 import torch
 
 from . import native
@@ -19,6 +21,8 @@ from .native import F, I, P, check, lib, ptr, status_word, stream_ptr
 
 native.register("eredu_qgemm", I, [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P])
 native.register("eredu_dequant_affine", I, [P, P, P, P, I, I, I, I, P])
+native.register("eredu_qgemm_fp8", I, [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P])
+native.register("eredu_dequant_fp8", I, [P, P, P, I, I, P])
 
 _NIBBLE_ORDER = (0, 2, 4, 6, 1, 3, 5, 7)  # kernel position p holds logical nibble _NIBBLE_ORDER[p]
 
@@ -201,6 +205,89 @@ class QuantLinear:
         return out
 
 
+class Fp8Linear:
+    """y = x @ (e4m3(Wq) * block_scale).T (+bias) (+residual): block-scaled FP8 weights (128 x 128 blocks) kept in
+    E4M3 on the device and decoded inside the tcgen05 pipeline; activations stay bf16. The block scales are expanded
+    along the output rows into an fp32 table [K/128, N], so row slices and row concatenations need no alignment."""
+
+    DENSE_FALLBACK_TOKENS = 256
+    bits, kbits, group = 8, 8, 128
+
+    def __init__(self, w8: torch.Tensor, block_scale: torch.Tensor, device, row_scales_t: Optional[torch.Tensor] = None):
+        """w8: E4M3 bytes (uint8 or float8_e4m3fn) [N, K]; block_scale fp32 [ceil(N/128), ceil(K/128)]
+        (or ``row_scales_t`` [K/128, N] directly)."""
+        N, K = w8.shape
+        if K % 128 != 0:
+            raise ValueError("block-FP8 weights need an input width that is a multiple of 128")
+        dev = torch.device(device)
+        self.out_features, self.in_features = N, K
+        self.device = dev
+        self.wq = (w8.view(torch.uint8) if w8.dtype != torch.uint8 else w8).to(dev).contiguous()
+        if row_scales_t is None:
+            row_scales_t = block_scale.to(torch.float32).repeat_interleave(128, 0)[:N].t()
+        self.scales_t = row_scales_t.to(dev, torch.float32).contiguous()
+        assert self.scales_t.shape == (K // 128, N)
+
+    @classmethod
+    def from_dense(cls, w: torch.Tensor):
+        """Quantise a dense weight: per 128 x 128 block, scale = amax / 448, codes = round-to-nearest E4M3."""
+        N, K = w.shape
+        wf = w.float()
+        nb, kb = (N + 127) // 128, K // 128
+        pad = torch.zeros((nb * 128, K), dtype=torch.float32, device=w.device)
+        pad[:N] = wf
+        blocks = pad.view(nb, 128, kb, 128)
+        scale = blocks.abs().amax(dim=(1, 3)).clamp_min(1e-12) / 448.0
+        codes = (blocks / scale[:, None, :, None]).view(nb * 128, K)[:N].to(torch.float8_e4m3fn)
+        return cls(codes, scale, w.device)
+
+    @staticmethod
+    def concat_rows(parts: list["Fp8Linear"]) -> "Fp8Linear":
+        return Fp8Linear(torch.cat([p.wq for p in parts], 0), None, parts[0].device,
+                         row_scales_t=torch.cat([p.scales_t for p in parts], 1))
+
+    def slice_rows(self, r0: int, r1: int) -> "Fp8Linear":
+        return Fp8Linear(self.wq[r0:r1], None, self.device, row_scales_t=self.scales_t[:, r0:r1])
+
+    def slice_cols(self, k0: int, k1: int) -> "Fp8Linear":
+        assert k0 % 128 == 0 and k1 % 128 == 0
+        return Fp8Linear(self.wq[:, k0:k1], None, self.device, row_scales_t=self.scales_t[k0 // 128:k1 // 128])
+
+    def tensors(self):
+        return [self.wq, self.scales_t]
+
+    def nbytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.tensors())
+
+    def dequantize(self, dtype=torch.float32) -> torch.Tensor:
+        s = self.scales_t.t().repeat_interleave(128, 1)
+        return (self.wq.view(torch.float8_e4m3fn).to(torch.float32) * s).to(dtype)
+
+    def __call__(self, x, bias=None, residual=None, out=None, out_dtype=None):
+        if not x.is_cuda:
+            y = torch.nn.functional.linear(x.float(), self.dequantize(), None if bias is None else bias.float())
+            if residual is not None:
+                y = y + residual.float()
+            return y.to(out_dtype or x.dtype)
+        M, K = x.shape
+        N = self.out_features
+        assert K == self.in_features and x.dtype == torch.bfloat16 and x.stride(1) == 1
+        out_dtype = out_dtype or torch.bfloat16
+        dev = x.device
+        if M > self.DENSE_FALLBACK_TOKENS:
+            w = torch.empty((N, K), dtype=torch.bfloat16, device=dev)
+            check(lib().eredu_dequant_fp8(ptr(self.wq), ptr(self.scales_t), ptr(w), N, K, stream_ptr(dev)), "eredu_dequant_fp8")
+            return linear(x, w, bias=bias, residual=residual, out_dtype=out_dtype, out=out, dynamic_weight=True)
+        if out is None:
+            out = torch.empty((M, N), dtype=out_dtype, device=dev)
+        code = lib().eredu_qgemm_fp8(ptr(x), ptr(self.wq), ptr(self.scales_t), ptr(out), ptr(residual), ptr(bias), M, N, K,
+                                     x.stride(0), out.stride(0), residual.stride(0) if residual is not None else 0,
+                                     1 if out_dtype == torch.float32 else 0, 0, _sm_count(dev), ptr(status_word(dev)),
+                                     stream_ptr(dev))
+        check(code, "eredu_qgemm_fp8")
+        return out
+
+
 def make_quantizer(src, opt):
     """Hook for ``build_from_tensors``: replaces the dense projections of a layer by :class:`QuantLinear`.
 
@@ -212,10 +299,22 @@ def make_quantizer(src, opt):
     gguf_native = bool(getattr(opt, "native_gguf", False)) and hasattr(src, "to_affine") and any(
         src.quant_info(f"model.layers.0.{n}.weight") is not None
         for n in ("self_attn.q_proj", "mlp.down_proj", "mlp.gate_proj"))
-    if qopt is None and not gguf_native:
+    fp8_native = hasattr(src, "fp8_scale_name") and any(
+        src.fp8_scale_name(f"model.layers.0.{n}.weight") is not None
+        for n in ("self_attn.q_proj", "mlp.down_proj", "mlp.gate_proj"))
+    if qopt is None and not gguf_native and not fp8_native:
         return None
 
     def from_source(model, name, rows=None, cols=None):
+        if fp8_native and src.fp8_scale_name(name) is not None:
+            w8, sc = src.to_fp8(name)
+            N = w8.shape[0]
+            rs = sc.repeat_interleave(128, 0)[:N].t()
+            r0, r1 = rows if rows is not None else (0, N)
+            c0, c1 = cols if cols is not None else (0, w8.shape[1])
+            if c0 % 128 or c1 % 128:
+                raise RuntimeError("column slice does not fall on FP8 block boundaries")
+            return Fp8Linear(w8[r0:r1, c0:c1], None, model.device, row_scales_t=rs[c0 // 128:c1 // 128, r0:r1])
         packed, scales, biases, bits, group = src.to_affine(name)
         q = QuantLinear.from_packed(packed, scales.float(), biases.float(), bits, group, model.device)
         if rows is not None:
@@ -229,6 +328,14 @@ def make_quantizer(src, opt):
         tp, r = par.tp_size, par.tp_rank
         cfg = model.cfg
         if qopt is not None:
+            if qopt.mode == "fp8":
+                for role, attr in (("qkv", "wqkv"), ("o", "wo"), ("gate_up", "w_gate_up"), ("down", "w_down")):
+                    w = getattr(lw, attr)
+                    if w is None or w.shape[1] % 128 != 0:
+                        continue
+                    lw.qlin[role] = Fp8Linear.from_dense(w)
+                    setattr(lw, attr, None)
+                return
             if qopt.mode != "affine":
                 raise NotImplementedError("load-time quantisation mode " + qopt.mode)
             bits, group = qopt.bits, qopt.group_size
@@ -248,16 +355,16 @@ def make_quantizer(src, opt):
             parts = [from_source(model, p + "self_attn.q_proj.weight", rows=(q0 * D, (q0 + nq) * D)),
                      from_source(model, p + "self_attn.k_proj.weight", rows=(kv0 * D, (kv0 + nkv) * D)),
                      from_source(model, p + "self_attn.v_proj.weight", rows=(kv0 * D, (kv0 + nkv) * D))]
-            lw.qlin["qkv"] = QuantLinear.concat_rows(parts)
+            lw.qlin["qkv"] = type(parts[0]).concat_rows(parts)
             lw.wqkv = None
             lw.qlin["o"] = from_source(model, p + "self_attn.o_proj.weight", cols=(q0 * D, (q0 + nq) * D))
             lw.wo = None
             if lw.moe is None:
                 I_ = cfg.intermediate_size
                 lo, hi = r * (I_ // tp), (r + 1) * (I_ // tp)
-                lw.qlin["gate_up"] = QuantLinear.concat_rows([
-                    from_source(model, p + "mlp.gate_proj.weight", rows=(lo, hi)),
-                    from_source(model, p + "mlp.up_proj.weight", rows=(lo, hi))])
+                gu = [from_source(model, p + "mlp.gate_proj.weight", rows=(lo, hi)),
+                      from_source(model, p + "mlp.up_proj.weight", rows=(lo, hi))]
+                lw.qlin["gate_up"] = type(gu[0]).concat_rows(gu)
                 lw.w_gate_up = None
                 lw.qlin["down"] = from_source(model, p + "mlp.down_proj.weight", cols=(lo, hi))
                 lw.w_down = None
