@@ -83,7 +83,12 @@ class LoadedModel:
                 residency.adopt_layer(lw)
         elif opt.weight_residency != "device":
             raise ValueError(f"unknown weight residency {opt.weight_residency!r}")
-        model = build_from_tensors(src.cfg, src.get, src.has, device, dtype, opt.parallel, moe_factory, quantizer,
+        get, has = src.get, src.has
+        if src.cfg.model_type in ("lfm2", "lfm2_moe"):
+            from ..models.lfm2 import canonical_access
+
+            get, has = canonical_access(get, has)
+        model = build_from_tensors(src.cfg, get, has, device, dtype, opt.parallel, moe_factory, quantizer,
                                    on_layer=on_layer)
         if residency is not None:
             residency.finalize()

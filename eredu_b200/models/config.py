@@ -10,7 +10,7 @@ from dataclasses import dataclass, field, asdict
 from pathlib import Path
 from typing import Any
 
-DENSE_TYPES = {"llama", "mistral", "qwen2", "qwen3", "phi3"}
+DENSE_TYPES = {"llama", "mistral", "qwen2", "qwen3", "phi3", "lfm2"}
 MOE_TYPES = {"qwen3_moe", "mixtral", "gpt_oss", "deepseek_v3", "lfm2_moe", "nemotron_h"}
 
 
@@ -34,7 +34,9 @@ class ModelConfig:
     attention_bias: bool = False
     mlp_bias: bool = False
     sliding_window: int | None = None
-    layer_types: list[str] | None = None  # per-layer "full_attention" | "sliding_attention"
+    layer_types: list[str] | None = None  # per-layer "full_attention" | "sliding_attention" | "conv" (LFM2)
+    conv_l_cache: int = 3    # LFM2 short-convolution kernel width
+    conv_bias: bool = False  # LFM2: biases on the convolution and its two projections
     qk_norm: bool = False  # per-head q/k RMSNorm (Qwen3)
     norm_weight_offset: float = 0.0  # Gemma stores (w - 1)
     embedding_scale: float = 1.0
@@ -70,6 +72,14 @@ class ModelConfig:
             return False
         return (layer + 1) % max(1, self.decoder_sparse_step) == 0
 
+    def layer_is_conv(self, layer: int) -> bool:
+        """LFM2 hybrid schedule: the layer's operator is the gated short convolution instead of attention."""
+        return self.layer_types is not None and self.layer_types[layer] == "conv"
+
+    @property
+    def is_hybrid(self) -> bool:
+        return self.layer_types is not None and "conv" in self.layer_types
+
     def layer_window(self, layer: int) -> int:
         if self.sliding_window is None or self.sliding_window <= 0:
             return 0
@@ -84,7 +94,15 @@ class ModelConfig:
         d["architectures"] = [{"llama": "LlamaForCausalLM", "mistral": "MistralForCausalLM",
                                "qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM",
                                "qwen3_moe": "Qwen3MoeForCausalLM", "mixtral": "MixtralForCausalLM", "phi3": "Phi3ForCausalLM",
-                               "gpt_oss": "GptOssForCausalLM"}.get(self.model_type, "LlamaForCausalLM")]
+                               "gpt_oss": "GptOssForCausalLM", "lfm2": "Lfm2ForCausalLM",
+                               "lfm2_moe": "Lfm2MoeForCausalLM"}.get(self.model_type, "LlamaForCausalLM")]
+        if self.model_type in ("lfm2", "lfm2_moe"):
+            d["norm_eps"] = self.rms_norm_eps
+            d["conv_L_cache"] = d.pop("conv_l_cache")
+            d["block_auto_adjust_ff_dim"] = False
+        else:
+            d.pop("conv_l_cache", None)
+            d.pop("conv_bias", None)
         if not self.is_moe:
             for k in ("num_experts", "num_experts_per_tok", "moe_intermediate_size", "norm_topk_prob",
                       "shared_expert_intermediate_size", "decoder_sparse_step", "mlp_only_layers", "swiglu_limit"):
@@ -145,6 +163,28 @@ class ModelConfig:
             bos_token_id=d.get("bos_token_id"),
             torch_dtype=str(d.get("torch_dtype", d.get("dtype", "bfloat16"))),
         )
+        if mt in ("lfm2", "lfm2_moe"):
+            # eredu/src/backend/mlx/architectures/lfm2/model.rs:193-418: hybrid schedule of gated short convolutions
+            # and q/k-normalised GQA attention; dense FFN width optionally re-derived from block_ff_dim
+            cfg.rms_norm_eps = float(d.get("norm_eps", 1e-5))
+            rp = d.get("rope_parameters") or {}
+            cfg.rope_theta = float(rp.get("rope_theta", d.get("rope_theta") or 1_000_000.0))
+            cfg.tie_word_embeddings = bool(d.get("tie_word_embeddings", d.get("tie_embedding", True)))
+            cfg.qk_norm = True
+            cfg.conv_l_cache = int(d.get("conv_L_cache", 3))
+            cfg.conv_bias = bool(d.get("conv_bias", False))
+            if cfg.layer_types is None and d.get("full_attn_idxs") is not None:
+                full = set(d["full_attn_idxs"])
+                cfg.layer_types = ["full_attention" if i in full else "conv" for i in range(cfg.num_hidden_layers)]
+            if cfg.layer_types is None or len(cfg.layer_types) != cfg.num_hidden_layers:
+                raise ValueError("LFM2 config needs one layer_types entry per layer")
+            if mt == "lfm2":
+                size = int(d.get("block_ff_dim") or cfg.intermediate_size)
+                if bool(d.get("block_auto_adjust_ff_dim", True)):
+                    mult, of = float(d.get("block_ffn_dim_multiplier", 1.0)), int(d.get("block_multiple_of", 256))
+                    size = int(mult * (2 * size // 3))
+                    size = of * ((size + of - 1) // of)
+                cfg.intermediate_size = size
         if mt == "mixtral":
             cfg.moe_intermediate_size = cfg.moe_intermediate_size or cfg.intermediate_size
             cfg.router_scoring = "topk_softmax"

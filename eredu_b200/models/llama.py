@@ -46,8 +46,8 @@ class ForwardBatch:
 @dataclass
 class LayerWeights:
     attn_norm: torch.Tensor
-    wqkv: torch.Tensor
-    wo: torch.Tensor
+    wqkv: Optional[torch.Tensor]
+    wo: Optional[torch.Tensor]
     ffn_norm: torch.Tensor
     w_gate_up: Optional[torch.Tensor] = None
     w_down: Optional[torch.Tensor] = None
@@ -60,6 +60,14 @@ class LayerWeights:
     fold_attn: bool = False  # attn_norm weights are folded into wqkv (RMSNorm fused into the GEMM)
     fold_ffn: bool = False   # ffn_norm weights are folded into w_gate_up
     qlin: dict = field(default_factory=dict)  # quantised linears by role: "qkv", "o", "gate_up", "down"
+    # LFM2 "conv" layers: gated short convolution instead of attention (wqkv / wo are None); attn_norm is the
+    # operator norm and fold_attn then refers to conv_in
+    conv_in: Optional[torch.Tensor] = None    # [3C, H]: B | C | X projections
+    conv_w: Optional[torch.Tensor] = None     # [C, L] fp32 depthwise kernel
+    conv_out: Optional[torch.Tensor] = None   # [H, C]
+    conv_in_b: Optional[torch.Tensor] = None
+    conv_b: Optional[torch.Tensor] = None
+    conv_out_b: Optional[torch.Tensor] = None
 
 
 class CausalLM:
@@ -149,6 +157,13 @@ class CausalLM:
     def layer_forward(self, li: int, lw: LayerWeights, h, batch: ForwardBatch, kv, ssq=None, next_folded=False):
         """One decoder block. ``ssq``: partial sums of squares of h's rows (or None); returns (h, ssq')."""
         cfg = self.cfg
+        if lw.conv_w is not None:
+            proj = self._normed_linear(h, ssq, lw.fold_attn, lw.attn_norm, lw.conv_in, lw, "conv_in", bias=lw.conv_in_b)
+            y = ops.short_conv(proj, lw.conv_w, lw.conv_b, kv.conv_layer(li), batch.block_table,
+                               batch.cu_q if batch.is_prefill else None, batch.q_per_seq, batch.positions, batch.slots,
+                               batch.max_q_len)
+            h, ssq = self._row_linear_ssq(lw, "conv_out", y, lw.conv_out, h, lw.conv_out_b, lw.fold_ffn)
+            return self._ffn(lw, h, ssq, next_folded)
         qkv = self._normed_linear(h, ssq, lw.fold_attn, lw.attn_norm, lw.wqkv, lw, "qkv", bias=lw.bqkv)
         k_cache, v_cache = kv.layer(li)
         q = ops.rope_kv(qkv, batch.positions, batch.slots, self.inv_freq, k_cache, v_cache, self.n_q_local,
@@ -165,6 +180,11 @@ class CausalLM:
                                         scratch=batch.scratch)
         attn = attn.view(attn.shape[0], -1)
         h, ssq = self._row_linear_ssq(lw, "o", attn, lw.wo, h, lw.bo, lw.fold_ffn)
+        return self._ffn(lw, h, ssq, next_folded)
+
+    def _ffn(self, lw: LayerWeights, h, ssq, next_folded):
+        """Second half of a block: norm -> dense SwiGLU or sparse experts -> residual."""
+        cfg = self.cfg
         if lw.moe is not None:
             normed, _ = ops.rmsnorm(h, lw.ffn_norm, cfg.rms_norm_eps, weight_offset=cfg.norm_weight_offset)
             return lw.moe(normed, residual=h), None
@@ -238,6 +258,9 @@ class CausalLM:
         off = self.cfg.norm_weight_offset
         if "qkv" not in lw.qlin and not lw.fold_attn and lw.wqkv is not None:
             lw.wqkv = (lw.wqkv.float() * (lw.attn_norm + off)[None, :]).to(self.dtype).contiguous()
+            lw.fold_attn = True
+        if "conv_in" not in lw.qlin and not lw.fold_attn and lw.conv_in is not None:
+            lw.conv_in = (lw.conv_in.float() * (lw.attn_norm + off)[None, :]).to(self.dtype).contiguous()
             lw.fold_attn = True
         if lw.moe is None and "gate_up" not in lw.qlin and lw.w_gate_up is not None and not lw.fold_ffn:
             lw.w_gate_up = (lw.w_gate_up.float() * (lw.ffn_norm + off)[None, :]).to(self.dtype).contiguous()
@@ -330,6 +353,17 @@ def build_from_tensors(cfg: ModelConfig, get: Callable[[str], torch.Tensor], has
     for li in range(model.first_layer, model.last_layer):
         p = f"model.layers.{li}."
         bq = bk = bv = None
+        if cfg.layer_is_conv(li):
+            lw = _build_conv_layer(model, cfg, p, get, has, up)
+            _build_ffn(model, cfg, li, p, lw, get, has, up, moe_factory)
+            if quantizer is not None:
+                quantizer(model, li, lw)
+            model.layers.append(lw)
+            if on_layer is not None:
+                if model.device.type == "cuda" and dtype == torch.bfloat16 and fold_norms:
+                    model.fold_layer_norms(lw)
+                on_layer(model, li, lw)
+            continue
         if has(p + "self_attn.qkv_proj.weight"):
             # Phi-3 style checkpoints store q, k and v as one matrix and gate / up as another
             qn, kn = cfg.num_attention_heads * cfg.head_dim, cfg.num_key_value_heads * cfg.head_dim
@@ -358,20 +392,7 @@ def build_from_tensors(cfg: ModelConfig, get: Callable[[str], torch.Tensor], has
         if has(p + "self_attn.sinks"):
             n_q_local = model.n_q_local
             lw.sinks = up(get(p + "self_attn.sinks")[r * n_q_local:(r + 1) * n_q_local], torch.float32)
-        if cfg.layer_is_moe(li):
-            assert moe_factory is not None, "MoE layer needs a moe_factory"
-            lw.moe = moe_factory(model, li, get, has)
-        else:
-            if has(p + "mlp.gate_up_proj.weight"):
-                fused = get(p + "mlp.gate_up_proj.weight")
-                wg, wu = fused[: cfg.intermediate_size], fused[cfg.intermediate_size:]
-                wd = get(p + "mlp.down_proj.weight")
-            else:
-                wg, wu, wd = (get(p + f"mlp.{n}_proj.weight") for n in ("gate", "up", "down"))
-            if tp > 1:
-                wg, wu, wd = _tp_rows(wg, r, tp), _tp_rows(wu, r, tp), _tp_cols(wd, r, tp)
-            lw.w_gate_up = up(torch.cat((wg, wu), 0))
-            lw.w_down = up(wd)
+        _build_ffn(model, cfg, li, p, lw, get, has, up, moe_factory)
         if quantizer is not None:
             quantizer(model, li, lw)
         model.layers.append(lw)
@@ -383,6 +404,48 @@ def build_from_tensors(cfg: ModelConfig, get: Callable[[str], torch.Tensor], has
     if model.device.type == "cuda" and dtype == torch.bfloat16 and fold_norms:
         model.fold_norms()
     return model
+
+
+def _build_ffn(model, cfg, li, p, lw, get, has, up, moe_factory) -> None:
+    par = model.par
+    tp, r = par.tp_size, par.tp_rank
+    if cfg.layer_is_moe(li):
+        assert moe_factory is not None, "MoE layer needs a moe_factory"
+        lw.moe = moe_factory(model, li, get, has)
+        return
+    if has(p + "mlp.gate_up_proj.weight"):
+        fused = get(p + "mlp.gate_up_proj.weight")
+        wg, wu = fused[: cfg.intermediate_size], fused[cfg.intermediate_size:]
+        wd = get(p + "mlp.down_proj.weight")
+    else:
+        wg, wu, wd = (get(p + f"mlp.{n}_proj.weight") for n in ("gate", "up", "down"))
+    if tp > 1:
+        wg, wu, wd = _tp_rows(wg, r, tp), _tp_rows(wu, r, tp), _tp_cols(wd, r, tp)
+    lw.w_gate_up = up(torch.cat((wg, wu), 0))
+    lw.w_down = up(wd)
+
+
+def _build_conv_layer(model, cfg, p, get, has, up) -> LayerWeights:
+    """LFM2 short-convolution layer. Tensor parallelism slices the channels: the B, C and X blocks of ``in_proj``
+    row-wise, the depthwise kernel by channel and ``out_proj`` column-wise (row-parallel, summed over the group)."""
+    par = model.par
+    tp, r = par.tp_size, par.tp_rank
+    C = cfg.hidden_size
+    w_in, w_conv, w_out = get(p + "conv.in_proj.weight"), get(p + "conv.conv.weight"), get(p + "conv.out_proj.weight")
+    w_conv = w_conv.reshape(C, -1)
+    lo, hi = (r * (C // tp), (r + 1) * (C // tp)) if tp > 1 else (0, C)
+    blocks = [w_in[i * C + lo:i * C + hi] for i in range(3)]
+    lw = LayerWeights(attn_norm=up(get(p + "input_layernorm.weight"), torch.float32), wqkv=None, wo=None,
+                      ffn_norm=up(get(p + "post_attention_layernorm.weight"), torch.float32))
+    lw.conv_in = up(torch.cat(blocks, 0))
+    lw.conv_w = up(w_conv[lo:hi], torch.float32)
+    lw.conv_out = up(w_out[:, lo:hi])
+    if has(p + "conv.in_proj.bias"):
+        b_in = get(p + "conv.in_proj.bias")
+        lw.conv_in_b = up(torch.cat([b_in[i * C + lo:i * C + hi] for i in range(3)], 0))
+        lw.conv_b = up(get(p + "conv.conv.bias")[lo:hi], torch.float32)
+        lw.conv_out_b = up(get(p + "conv.out_proj.bias"))
+    return lw
 
 
 def random_state(cfg: ModelConfig, seed: int = 0, std: float = 0.02, dtype=torch.float32, device="cpu") -> dict:
@@ -409,6 +472,17 @@ def random_state(cfg: ModelConfig, seed: int = 0, std: float = 0.02, dtype=torch
         p = f"model.layers.{li}."
         ones(p + "input_layernorm.weight", H)
         ones(p + "post_attention_layernorm.weight", H)
+        if cfg.layer_is_conv(li):
+            mat(p + "conv.in_proj.weight", 3 * H, H)
+            mat(p + "conv.conv.weight", H, 1, cfg.conv_l_cache)
+            out[p + "conv.conv.weight"] = out[p + "conv.conv.weight"] * (0.5 / std)
+            mat(p + "conv.out_proj.weight", H, H)
+            if cfg.conv_bias:
+                mat(p + "conv.in_proj.bias", 3 * H)
+                mat(p + "conv.conv.bias", H)
+                mat(p + "conv.out_proj.bias", H)
+            _random_ffn(cfg, li, p, mat)
+            continue
         mat(p + "self_attn.q_proj.weight", cfg.num_attention_heads * D, H)
         mat(p + "self_attn.k_proj.weight", cfg.num_key_value_heads * D, H)
         mat(p + "self_attn.v_proj.weight", cfg.num_key_value_heads * D, H)
@@ -420,17 +494,22 @@ def random_state(cfg: ModelConfig, seed: int = 0, std: float = 0.02, dtype=torch
         if cfg.qk_norm:
             ones(p + "self_attn.q_norm.weight", D)
             ones(p + "self_attn.k_norm.weight", D)
-        if cfg.layer_is_moe(li):
-            mat(p + "mlp.gate.weight", cfg.num_experts, H)
-            for e in range(cfg.num_experts):
-                mat(p + f"mlp.experts.{e}.gate_proj.weight", cfg.moe_intermediate_size, H)
-                mat(p + f"mlp.experts.{e}.up_proj.weight", cfg.moe_intermediate_size, H)
-                mat(p + f"mlp.experts.{e}.down_proj.weight", H, cfg.moe_intermediate_size)
-        else:
-            mat(p + "mlp.gate_proj.weight", cfg.intermediate_size, H)
-            mat(p + "mlp.up_proj.weight", cfg.intermediate_size, H)
-            mat(p + "mlp.down_proj.weight", H, cfg.intermediate_size)
+        _random_ffn(cfg, li, p, mat)
     return out
+
+
+def _random_ffn(cfg, li, p, mat) -> None:
+    H = cfg.hidden_size
+    if cfg.layer_is_moe(li):
+        mat(p + "mlp.gate.weight", cfg.num_experts, H)
+        for e in range(cfg.num_experts):
+            mat(p + f"mlp.experts.{e}.gate_proj.weight", cfg.moe_intermediate_size, H)
+            mat(p + f"mlp.experts.{e}.up_proj.weight", cfg.moe_intermediate_size, H)
+            mat(p + f"mlp.experts.{e}.down_proj.weight", H, cfg.moe_intermediate_size)
+    else:
+        mat(p + "mlp.gate_proj.weight", cfg.intermediate_size, H)
+        mat(p + "mlp.up_proj.weight", cfg.intermediate_size, H)
+        mat(p + "mlp.down_proj.weight", H, cfg.intermediate_size)
 
 
 def build_random(cfg: ModelConfig, device, dtype, seed: int = 0, parallel=None, moe_factory=None, quantizer=None,
@@ -469,6 +548,18 @@ def _shape_of(cfg: ModelConfig, name: str):
         return None
     li = int(parts[2])
     rest = ".".join(parts[3:])
+    if cfg.layer_is_conv(li):
+        conv = {"input_layernorm.weight": (H,), "post_attention_layernorm.weight": (H,),
+                "conv.in_proj.weight": (3 * H, H), "conv.conv.weight": (H, 1, cfg.conv_l_cache),
+                "conv.out_proj.weight": (H, H)}
+        if cfg.conv_bias:
+            conv.update({"conv.in_proj.bias": (3 * H,), "conv.conv.bias": (H,), "conv.out_proj.bias": (H,)})
+        if rest in conv:
+            return conv[rest]
+        if rest.startswith("self_attn.") or rest.startswith("conv."):
+            return None
+    elif rest.startswith("conv."):
+        return None
     table = {
         "input_layernorm.weight": (H,), "post_attention_layernorm.weight": (H,),
         "self_attn.q_proj.weight": (cfg.num_attention_heads * D, H),

@@ -339,13 +339,16 @@ def make_quantizer(src, opt):
             if qopt.mode != "affine":
                 raise NotImplementedError("load-time quantisation mode " + qopt.mode)
             bits, group = qopt.bits, qopt.group_size
-            for role, attr in (("qkv", "wqkv"), ("o", "wo"), ("gate_up", "w_gate_up"), ("down", "w_down")):
+            for role, attr in (("qkv", "wqkv"), ("o", "wo"), ("gate_up", "w_gate_up"), ("down", "w_down"),
+                               ("conv_in", "conv_in"), ("conv_out", "conv_out")):
                 w = getattr(lw, attr)
                 if w is None or w.shape[1] % group != 0 or w.shape[1] % 64 != 0:
                     continue  # ineligible: stays dense (quantization.rs:24-38)
                 lw.qlin[role] = QuantLinear.from_dense(w, bits, group)
                 setattr(lw, attr, None)
             return
+        if lw.conv_w is not None:
+            return  # short-convolution layers keep their dense projections
         p = f"model.layers.{li}."
         D = cfg.head_dim
         nq, nkv, rep = model.n_q_local, model.n_kv_local, model.kv_rep

@@ -31,6 +31,7 @@ class _StageModel:
         self.n_kv_local = model.n_kv_local
         self.n_q_local = model.n_q_local
         self.first_layer = model.first_layer
+        self.last_layer = model.last_layer
         topo = par.topology
         self.prev = topo.pipeline_predecessor(par.rank)
         self.next = topo.pipeline_successor(par.rank)

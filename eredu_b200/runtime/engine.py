@@ -55,8 +55,14 @@ class Engine:
         self.max_pages = PagedKVCache.pages_for(max_seq_len)
         if num_pages is None:
             num_pages = max_batch * self.max_pages + 1
+        local = range(model.first_layer, model.last_layer)
+        conv_layers = [li for li in local if self.cfg.layer_is_conv(li)]
         self.kv = PagedKVCache(model.num_local_layers(), model.n_kv_local, self.cfg.head_dim, num_pages, model.dtype,
-                               self.device, first_layer=model.first_layer)
+                               self.device, first_layer=model.first_layer,
+                               attention_layers=[li for li in local if not self.cfg.layer_is_conv(li)],
+                               conv_layers=conv_layers,
+                               conv_channels=self.cfg.hidden_size // model.par.tp_size if conv_layers else 0,
+                               conv_hist=self.cfg.conv_l_cache - 1)
         self.cuda = self.device.type == "cuda"
         self.use_graph = self.cuda if use_cuda_graph is None else (use_cuda_graph and self.cuda)
         self.prefill_chunk = prefill_chunk

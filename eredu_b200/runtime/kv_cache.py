@@ -37,12 +37,24 @@ class PageAllocator:
 
 class PagedKVCache:
     def __init__(self, n_layers: int, n_kv_heads: int, head_dim: int, num_pages: int, dtype, device,
-                 first_layer: int = 0):
-        self.n_layers, self.n_kv_heads, self.head_dim = n_layers, n_kv_heads, head_dim
+                 first_layer: int = 0, attention_layers=None, conv_layers=None, conv_channels: int = 0, conv_hist: int = 0):
+        """``attention_layers`` / ``conv_layers``: global indices of the layers that keep K/V pages respectively a
+        short-convolution state (hybrid models); by default every one of the ``n_layers`` layers keeps K/V.
+        The convolution state pool [layer, page, conv_hist, channels] is indexed by a sequence's first page."""
+        self.n_kv_heads, self.head_dim = n_kv_heads, head_dim
         self.num_pages = num_pages
         self.first_layer = first_layer
-        self.k = torch.zeros((n_layers, num_pages, n_kv_heads, PAGE, head_dim), dtype=dtype, device=device)
+        if attention_layers is None:
+            attention_layers = list(range(first_layer, first_layer + n_layers))
+        self._kv_index = {li: i for i, li in enumerate(attention_layers)}
+        self.n_layers = len(attention_layers)
+        self.k = torch.zeros((self.n_layers, num_pages, n_kv_heads, PAGE, head_dim), dtype=dtype, device=device)
         self.v = torch.zeros_like(self.k)
+        self._conv_index = {li: i for i, li in enumerate(conv_layers or [])}
+        self.conv_state = None
+        if self._conv_index:
+            self.conv_state = torch.zeros((len(self._conv_index), num_pages, conv_hist, conv_channels), dtype=dtype,
+                                          device=device)
         try:
             from ..lib import _eredu_host  # type: ignore
 
@@ -51,11 +63,15 @@ class PagedKVCache:
             self.allocator = PageAllocator(num_pages)
 
     def layer(self, li: int):
-        i = li - self.first_layer
+        i = self._kv_index[li]
         return self.k[i], self.v[i]
 
+    def conv_layer(self, li: int):
+        return self.conv_state[self._conv_index[li]]
+
     def bytes(self) -> int:
-        return 2 * self.k.numel() * self.k.element_size()
+        extra = self.conv_state.numel() * self.conv_state.element_size() if self.conv_state is not None else 0
+        return 2 * self.k.numel() * self.k.element_size() + extra
 
     @staticmethod
     def pages_for(tokens: int) -> int:

@@ -37,6 +37,7 @@ class ParkedSequence:
     pages: int
     reserved_pages: int                  # pages the sequence had reserved (prompt + budget), restored on resume
     event: object = None                 # transfer completion (CUDA event) or None
+    conv_state: object = None            # hybrid models: the short-convolution state of every conv layer [layers, hist, C]
 
 
 class KVHostTier:
@@ -108,7 +109,10 @@ class KVHostTier:
             else:
                 k_host.copy_(k_stage)
                 v_host.copy_(v_stage)
-        self.parked[seq.seq_id] = ParkedSequence(k_host, v_host, used, len(seq.pages), event)
+        conv = None
+        if self.kv.conv_state is not None and seq.pages:
+            conv = self.kv.conv_state[:, seq.pages[0]].to("cpu")   # the state is named by the sequence's first page
+        self.parked[seq.seq_id] = ParkedSequence(k_host, v_host, used, len(seq.pages), event, conv)
         self.engine.kv.allocator.release(seq.pages)
         seq.pages = []
         self.host_bytes += nbytes
@@ -144,6 +148,8 @@ class KVHostTier:
                 k_dev, v_dev = p.k_host, p.v_host
             self.kv.k.index_copy_(1, idx, k_dev)
             self.kv.v.index_copy_(1, idx, v_dev)
+        if p.conv_state is not None:
+            self.kv.conv_state[:, pages[0]] = p.conv_state.to(dev)
         seq.pages = pages
         nbytes = p.pages * self.page_bytes()
         self.host_bytes -= nbytes

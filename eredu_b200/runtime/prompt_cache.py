@@ -218,6 +218,8 @@ def save_prompt_cache(engine, seq, directory, checkpoint_fingerprint: str, prefi
                       block_tokens: int = 256, namespace: Optional[str] = None, replace_existing: bool = False) -> Path:
     """Persist the K/V of the first ``prefix_tokens`` cached tokens of ``seq`` (default: all cached tokens).
     Every rank of a distributed run calls this with the same arguments and writes its own directory."""
+    if engine.cfg.is_hybrid:
+        raise Incompatible("prompt caches of hybrid (convolution-state) models are not supported")
     from ..formats.checkpoint import _np
     from ..lib import _eredu_host as H
 

@@ -51,6 +51,9 @@ class SpeculativeDecoder:
     reference's ``MtpConfig`` (4 draft tokens, eredu-core/src/generation.rs:339-360)."""
 
     def __init__(self, target: Engine, draft: Engine, k: int = 4):
+        if target.cfg.is_hybrid or draft.cfg.is_hybrid:
+            # rejected proposals would have to be rolled out of the recurrent convolution state as well
+            raise NotImplementedError("speculative decoding is not available for hybrid (convolution-state) models")
         assert target.cfg.vocab_size == draft.cfg.vocab_size, "draft and target must share the vocabulary"
         self.t, self.d, self.k = target, draft, k
         self.stats = SpecStats()
@@ -216,6 +219,9 @@ class GraphSpeculativeDecoder(SpeculativeDecoder):
     """
 
     def __init__(self, target: Engine, draft: Engine, k: int = 4):
+        if target.cfg.is_hybrid or draft.cfg.is_hybrid:
+            # rejected proposals would have to be rolled out of the recurrent convolution state as well
+            raise NotImplementedError("speculative decoding is not available for hybrid (convolution-state) models")
         super().__init__(target, draft, k)
         if not self.cuda:
             raise RuntimeError("GraphSpeculativeDecoder needs CUDA engines; use SpeculativeDecoder on the CPU")

@@ -37,6 +37,17 @@ def forward_logits(cfg, sd, tokens, moe_fn=None):
     for li in range(cfg.num_hidden_layers):
         p = f"model.layers.{li}."
         x = rms(h, sd[p + "input_layernorm.weight"], cfg.rms_norm_eps, cfg.norm_weight_offset)
+        if cfg.layer_is_conv(li):
+            # LFM2 gated short convolution: causal depthwise conv1d over B * X, gated by C
+            Cc = cfg.hidden_size
+            pj = F.linear(x, sd[p + "conv.in_proj.weight"], sd.get(p + "conv.in_proj.bias"))
+            bx = (pj[:, :Cc] * pj[:, 2 * Cc:]).t()[None]
+            L = cfg.conv_l_cache
+            y = F.conv1d(F.pad(bx, (L - 1, 0)), sd[p + "conv.conv.weight"].view(Cc, 1, L), sd.get(p + "conv.conv.bias"),
+                         groups=Cc)[0].t()
+            h = h + F.linear(pj[:, Cc:2 * Cc] * y, sd[p + "conv.out_proj.weight"], sd.get(p + "conv.out_proj.bias"))
+            h = _ffn(cfg, sd, li, p, h, moe_fn)
+            continue
         q = F.linear(x, sd[p + "self_attn.q_proj.weight"], sd.get(p + "self_attn.q_proj.bias")).view(T, Hq, D)
         k = F.linear(x, sd[p + "self_attn.k_proj.weight"], sd.get(p + "self_attn.k_proj.bias")).view(T, Hkv, D)
         v = F.linear(x, sd[p + "self_attn.v_proj.weight"], sd.get(p + "self_attn.v_proj.bias")).view(T, Hkv, D)
@@ -60,16 +71,19 @@ def forward_logits(cfg, sd, tokens, moe_fn=None):
             probs = torch.softmax(s, -1)
         a = torch.einsum("hqk,khd->qhd", probs, v).reshape(T, Hq * D)
         h = h + F.linear(a, sd[p + "self_attn.o_proj.weight"], sd.get(p + "self_attn.o_proj.bias"))
-        x = rms(h, sd[p + "post_attention_layernorm.weight"], cfg.rms_norm_eps, cfg.norm_weight_offset)
-        if cfg.layer_is_moe(li):
-            h = h + moe_fn(cfg, sd, li, x)
-        else:
-            gate = F.linear(x, sd[p + "mlp.gate_proj.weight"])
-            up = F.linear(x, sd[p + "mlp.up_proj.weight"])
-            h = h + F.linear(F.silu(gate) * up, sd[p + "mlp.down_proj.weight"])
+        h = _ffn(cfg, sd, li, p, h, moe_fn)
     x = rms(h, sd["model.norm.weight"], cfg.rms_norm_eps, cfg.norm_weight_offset)
     head = sd.get("lm_head.weight", sd["model.embed_tokens.weight"])
     return F.linear(x, head)
+
+
+def _ffn(cfg, sd, li, p, h, moe_fn):
+    x = rms(h, sd[p + "post_attention_layernorm.weight"], cfg.rms_norm_eps, cfg.norm_weight_offset)
+    if cfg.layer_is_moe(li):
+        return h + moe_fn(cfg, sd, li, x)
+    gate = F.linear(x, sd[p + "mlp.gate_proj.weight"])
+    up = F.linear(x, sd[p + "mlp.up_proj.weight"])
+    return h + F.linear(F.silu(gate) * up, sd[p + "mlp.down_proj.weight"])
 
 
 def greedy(cfg, sd, prompt, n, moe_fn=None):
