@@ -193,10 +193,17 @@ def run_torch_baseline(args) -> int:
                           "config": {"model": args.model + "-shaped", "global_batch": B, "seq_len": P, "parallelism": f"tp{world}",
                                      "stack": "F.linear (cuBLAS) + F.scaled_dot_product_attention + NCCL all-reduce / all-gather, CUDA graph",
                                      "kv": "contiguous cache, fixed context of seq_len + 1"}}))
+    # The captured graph holds NCCL kernels: release it and drain the device before the communicator goes away
+    # (tearing the process group down under a live graph did not return on eight ranks).
+    del graph
+    torch.cuda.synchronize(dev)
     if world > 1:
         import torch.distributed as dist
 
-        dist.destroy_process_group()
+        dist.barrier()
+        torch.cuda.synchronize(dev)
+        sys.stdout.flush()
+        os._exit(0)
     return 0
 
 

@@ -46,6 +46,7 @@ class ModelConfig:
     moe_intermediate_size: int = 0
     norm_topk_prob: bool = True
     router_scoring: str = "softmax"  # softmax | sigmoid | sqrt_softplus | topk_softmax
+    routed_scaling_factor: float = 1.0  # multiplies the routing weights after renormalisation
     shared_expert_intermediate_size: int = 0
     decoder_sparse_step: int = 1
     mlp_only_layers: list[int] = field(default_factory=list)
@@ -90,12 +91,17 @@ class ModelConfig:
     def to_hf_dict(self) -> dict:
         d = {k: v for k, v in asdict(self).items() if k not in ("extra", "qk_norm", "rope_traditional",
                                                                 "norm_weight_offset", "embedding_scale",
-                                                                "router_scoring", "attention_sinks", "quantization")}
+                                                                "router_scoring", "attention_sinks", "quantization",
+                                                                "routed_scaling_factor")}
         d["architectures"] = [{"llama": "LlamaForCausalLM", "mistral": "MistralForCausalLM",
                                "qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM",
                                "qwen3_moe": "Qwen3MoeForCausalLM", "mixtral": "MixtralForCausalLM", "phi3": "Phi3ForCausalLM",
                                "gpt_oss": "GptOssForCausalLM", "lfm2": "Lfm2ForCausalLM",
                                "lfm2_moe": "Lfm2MoeForCausalLM"}.get(self.model_type, "LlamaForCausalLM")]
+        if self.routed_scaling_factor != 1.0 or self.model_type == "lfm2_moe":
+            d["routed_scaling_factor"] = self.routed_scaling_factor
+        if self.model_type == "lfm2_moe":
+            d["num_dense_layers"] = len(self.mlp_only_layers)
         if self.model_type in ("lfm2", "lfm2_moe"):
             d["norm_eps"] = self.rms_norm_eps
             d["conv_L_cache"] = d.pop("conv_l_cache")
@@ -158,6 +164,7 @@ class ModelConfig:
             decoder_sparse_step=int(d.get("decoder_sparse_step", 1) or 1),
             mlp_only_layers=list(d.get("mlp_only_layers", []) or []),
             swiglu_limit=float(d.get("swiglu_limit", 0.0) or 0.0),
+            routed_scaling_factor=float(d.get("routed_scaling_factor", 1.0) or 1.0),
             quantization=d.get("quantization") or d.get("quantization_config"),
             eos_token_id=d.get("eos_token_id"),
             bos_token_id=d.get("bos_token_id"),
@@ -178,6 +185,14 @@ class ModelConfig:
                 cfg.layer_types = ["full_attention" if i in full else "conv" for i in range(cfg.num_hidden_layers)]
             if cfg.layer_types is None or len(cfg.layer_types) != cfg.num_hidden_layers:
                 raise ValueError("LFM2 config needs one layer_types entry per layer")
+            if mt == "lfm2_moe":
+                # model.rs:264-290,1010-1046: the first num_dense_layers layers keep the dense FFN, the others route
+                # with a sigmoid router (optional selection bias), optional renormalisation and a routing scale
+                cfg.router_scoring = "sigmoid"
+                cfg.norm_topk_prob = bool(d.get("norm_topk_prob", False))
+                cfg.routed_scaling_factor = float(d.get("routed_scaling_factor", 1.0))
+                cfg.mlp_only_layers = list(range(int(d.get("num_dense_layers", 0) or 0)))
+                cfg.extra["use_expert_bias"] = bool(d.get("use_expert_bias", False))
             if mt == "lfm2":
                 size = int(d.get("block_ff_dim") or cfg.intermediate_size)
                 if bool(d.get("block_auto_adjust_ff_dim", True)):

@@ -21,6 +21,7 @@ _REST = {
     "mlp.up_proj.weight": "feed_forward.w3.weight",
     "mlp.down_proj.weight": "feed_forward.w2.weight",
     "mlp.gate.weight": "feed_forward.gate.weight",
+    "mlp.expert_bias": "feed_forward.expert_bias",
 }
 _EXPERT = re.compile(r"^mlp\.experts\.(\d+)\.(gate|up|down)_proj\.weight$")
 _EXPERT_W = {"gate": "w1", "up": "w3", "down": "w2"}

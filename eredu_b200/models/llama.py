@@ -502,6 +502,8 @@ def _random_ffn(cfg, li, p, mat) -> None:
     H = cfg.hidden_size
     if cfg.layer_is_moe(li):
         mat(p + "mlp.gate.weight", cfg.num_experts, H)
+        if cfg.extra.get("use_expert_bias"):
+            mat(p + "mlp.expert_bias", cfg.num_experts)
         for e in range(cfg.num_experts):
             mat(p + f"mlp.experts.{e}.gate_proj.weight", cfg.moe_intermediate_size, H)
             mat(p + f"mlp.experts.{e}.up_proj.weight", cfg.moe_intermediate_size, H)

@@ -39,7 +39,7 @@ class MoEBlock:
 
     def tensors(self):
         out = [self.router_w, self.w_gate_up, self.w_down]
-        out.extend(t for t in (self.router_linear_bias, self.gu_bias, self.down_bias) if t is not None)
+        out.extend(t for t in (self.router_bias, self.router_linear_bias, self.gu_bias, self.down_bias) if t is not None)
         if self.shared is not None:
             out.extend(self.shared)
         return out
@@ -47,8 +47,8 @@ class MoEBlock:
     def route(self, x):
         cfg = self.cfg
         logits = ops.linear(x, self.router_w, bias=self.router_linear_bias, out_dtype=torch.float32)
-        return moe_ops.route(logits.contiguous(), cfg.num_experts_per_tok, cfg.router_scoring, cfg.norm_topk_prob, 1.0,
-                             self.router_bias)
+        return moe_ops.route(logits.contiguous(), cfg.num_experts_per_tok, cfg.router_scoring, cfg.norm_topk_prob,
+                             cfg.routed_scaling_factor, self.router_bias)
 
     def __call__(self, x, residual=None):
         """x: normalised hidden states [T, H]; returns residual + MoE(x)."""
@@ -71,7 +71,8 @@ class MoEBlock:
             cfg = self.cfg
             logits = ops.linear(x, self.router_w, bias=self.router_linear_bias, out_dtype=torch.float32)
             ids, w, plan, xp = moe_ops.route_plan_gather(logits.contiguous(), x, cfg.num_experts_per_tok, cfg.router_scoring,
-                                                         cfg.norm_topk_prob, 1.0, self.router_bias, self.e0,
+                                                         cfg.norm_topk_prob, cfg.routed_scaling_factor, self.router_bias,
+                                                         self.e0,
                                                          self.w_gate_up.shape[0])
         else:
             ids, w = self.route(x)
@@ -137,7 +138,10 @@ def make_moe_factory(src=None, router_std_scale: bool = False):
             sgu = torch.cat((get(p + "shared_expert.gate_proj.weight"), get(p + "shared_expert.up_proj.weight")), 0)
             shared = (sgu.to(device=dev, dtype=dt).contiguous(),
                       get(p + "shared_expert.down_proj.weight").to(device=dev, dtype=dt).contiguous())
-        block = MoEBlock(cfg, router, gu, dn, e0, cfg.num_experts, ep_size=par.ep_size, shared=shared)
+        sel_bias = None
+        if has(p + "expert_bias"):   # LFM2-MoE: added to the scores for the selection only
+            sel_bias = get(p + "expert_bias").to(device=dev, dtype=torch.float32).contiguous()
+        block = MoEBlock(cfg, router, gu, dn, e0, cfg.num_experts, ep_size=par.ep_size, shared=shared, router_bias=sel_bias)
         block._model = model
         return block
 

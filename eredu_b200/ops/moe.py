@@ -178,17 +178,17 @@ def experts_forward(x, ids, weights, w_gate_up, w_down, e0=0, residual=None, ext
         check(lib().eredu_moe_gather(ptr(x), ptr(plan.row_token), ptr(plan.counts), ptr(xp), rows_cap, H, stream_ptr(dev)),
               "eredu_moe_gather")
     tile = plan.tile
-    act = torch.empty((rows_cap, inter), dtype=x.dtype, device=dev)
+    gated = torch.empty((rows_cap, inter), dtype=x.dtype, device=dev)
     st = status_word(dev)
     sm = _sm_count(dev)
     wgu = w_gate_up.view(E_local * two_i, H)
-    code = lib().eredu_gemm_bf16_grouped(ptr(xp), ptr(wgu), ptr(act), ptr(plan.work), plan.n_work, tile, rows_cap, inter,
+    code = lib().eredu_gemm_bf16_grouped(ptr(xp), ptr(wgu), ptr(gated), ptr(plan.work), plan.n_work, tile, rows_cap, inter,
                                          H, H, H, inter, E_local * two_i, two_i, 1, 0, sm, ptr(st), ptr(gu_bias),
                                          two_i if gu_bias is not None else 0, ACTS[act], float(limit), stream_ptr(dev))
     check(code, "eredu_gemm_bf16_grouped(gate_up)")
     y = torch.empty((rows_cap, H), dtype=x.dtype, device=dev)
     wd = w_down.view(E_local * H, inter)
-    code = lib().eredu_gemm_bf16_grouped(ptr(act), ptr(wd), ptr(y), ptr(plan.work), plan.n_work, tile, rows_cap, H,
+    code = lib().eredu_gemm_bf16_grouped(ptr(gated), ptr(wd), ptr(y), ptr(plan.work), plan.n_work, tile, rows_cap, H,
                                          inter, inter, inter, H, E_local * H, H, 0, 0, sm, ptr(st), ptr(down_bias),
                                          H if down_bias is not None else 0, 0, 0.0, stream_ptr(dev))
     check(code, "eredu_gemm_bf16_grouped(down)")

@@ -382,6 +382,13 @@ class Engine:
         ops.native.check(code, "eredu_decode_advance")
 
     @torch.no_grad()
+    def _host_driven(self) -> bool:
+        """True when a forward pass needs the host between kernels (layerwise host residency, expert cache)."""
+        m = self.model
+        if getattr(m, "residency", None) is not None:
+            return True
+        return any(getattr(getattr(lw, "moe", None), "expert_cache", None) is not None for lw in getattr(m, "layers", []))
+
     def decode_step(self, host_tokens: Optional[torch.Tensor] = None, sync: bool = True) -> Optional[torch.Tensor]:
         """One decode step for the batch loaded by :meth:`start_decode`.
 
@@ -394,8 +401,12 @@ class Engine:
         if host_tokens is not None:
             st["token_ids"].copy_(host_tokens, non_blocking=True)
         if self.use_graph:
-            if getattr(self.model, "residency", None) is not None:
-                # host-resident layers stream through device slots on a copy stream: the step runs eagerly
+            eager = st.get("eager")
+            if eager is None:
+                eager = st["eager"] = self._host_driven()
+            if eager:
+                # host-resident layers stream through device slots on a copy stream, and an expert cache reads the
+                # routed ids on the host: such steps cannot be captured and run eagerly
                 self._decode_body(st)
             elif st["graph"] is None:
                 # warm-up run outside capture (lazy kernel attribute setup), then restore the state it advanced
@@ -418,7 +429,7 @@ class Engine:
                 st["graph"] = g
                 if "graphs" in st:
                     st["graphs"][st["all_greedy"]] = g
-            if getattr(self.model, "residency", None) is None:
+            if not eager:
                 st["graph"].replay()
         else:
             self._decode_body(st)

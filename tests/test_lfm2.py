@@ -155,3 +155,38 @@ def test_lfm2_engine_on_gpu_matches_cpu_oracle():
     ref = cpu.generate(prompts, SamplingParams(temperature=0.0), max_new_tokens=6)
     agree = sum(a == b for o, r in zip(outs, ref) for a, b in zip(o, r))
     assert agree >= 14, (outs, ref)
+
+
+def test_lfm2_moe_matches_oracle(tmp_path):
+    from eredu_b200.api import LoadedModel, ModelLoadOptions
+    from eredu_b200.formats import checkpoint as ck
+    from eredu_b200.models.lfm2 import to_checkpoint_names
+    from eredu_b200.ops import moe as M
+
+    cfg = lfm2_cfg(model_type="lfm2_moe", num_dense_layers=2, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=32,
+                   norm_topk_prob=True, routed_scaling_factor=1.5, use_expert_bias=True)
+    assert [cfg.layer_is_moe(i) for i in range(5)] == [False, False, True, True, True] and cfg.router_scoring == "sigmoid"
+    sd = random_state(cfg, seed=9, std=0.08)
+    for k in list(sd):
+        if k.endswith("expert_bias"):
+            sd[k] = sd[k] * 10.0          # large enough to change which experts win
+
+    def moe_fn(cfg_, sd_, li, x):
+        p = f"model.layers.{li}.mlp."
+        ids, w = M.route_ref(x @ sd_[p + "gate.weight"].t(), 2, "sigmoid", True, 1.5, sd_[p + "expert_bias"])
+        out = torch.zeros_like(x)
+        for t in range(x.shape[0]):
+            for s_ in range(2):
+                e = int(ids[t, s_])
+                g = x[t] @ sd_[p + f"experts.{e}.gate_proj.weight"].t()
+                u = x[t] @ sd_[p + f"experts.{e}.up_proj.weight"].t()
+                out[t] += w[t, s_] * ((torch.nn.functional.silu(g) * u) @ sd_[p + f"experts.{e}.down_proj.weight"].t())
+        return out
+
+    ck.save_safetensors_checkpoint(tmp_path, cfg, to_checkpoint_names(sd), torch.float32)
+    lm = LoadedModel.load(tmp_path, ModelLoadOptions(device="cpu", max_batch=2, max_seq_len=64))
+    assert lm.model.layers[2].moe is not None and lm.model.layers[2].moe.router_bias is not None
+    assert lm.model.layers[0].moe is None and lm.model.layers[3].conv_w is not None
+    prompt = list(range(7, 30))
+    out = lm.generate([prompt], SamplingParams(temperature=0.0), max_new_tokens=6)[0]
+    assert out == greedy(cfg, sd, prompt, 6, moe_fn=moe_fn)

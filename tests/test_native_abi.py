@@ -1,0 +1,188 @@
+"""The Python <-> C ABI of the CUDA library, checked without a GPU.
+
+1. Every ``extern "C"`` entry point declared in the CUDA sources has a ctypes registration with the same number
+   and kinds of parameters (pointer / int / float / long long), and every registration names an exported symbol.
+2. The CUDA branches of the operator wrappers run on CPU tensors against a recording stub of the library
+   (tensors report ``is_cuda``, launches are no-ops): argument counts and kinds of every call are checked and
+   Python-level mistakes in code that otherwise only runs on a GPU surface here.
+"""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+import eredu_b200
+from eredu_b200 import ops
+from eredu_b200.ops import native
+
+CSRC = Path(eredu_b200.__file__).resolve().parent / "csrc"
+
+
+def _import_all_registrations():
+    import eredu_b200.ops.conv  # noqa: F401
+    import eredu_b200.ops.moe  # noqa: F401
+    import eredu_b200.ops.quant  # noqa: F401
+    import eredu_b200.ops.sampling  # noqa: F401
+    try:
+        import eredu_b200.parallel.comm  # noqa: F401
+        import eredu_b200.parallel.tp  # noqa: F401
+        import eredu_b200.utils.trace  # noqa: F401
+    except Exception:
+        pass
+
+
+def _kind(ctype_decl: str) -> str:
+    t = ctype_decl.strip()
+    if "*" in t or "cudaStream_t" in t or "PeerComm" in t and "*" in t:
+        return "P"
+    base = re.sub(r"\b(const|unsigned|signed)\b", "", t).split()
+    if not base:
+        return "?"
+    base = " ".join(base[:-1]) if len(base) > 1 else base[0]
+    return {"int": "I", "float": "F", "long long": "L", "uint32_t": "I", "int64_t": "L", "size_t": "L",
+            "unsigned": "I", "bool": "I", "double": "D", "uint64_t": "L", "int32_t": "I"}.get(base.strip(), "?")
+
+
+def c_declarations():
+    out = {}
+    pat = re.compile(r'extern\s+"C"\s+([\w\s\*]+?)\s+(eredu_\w+)\s*\(([^)]*)\)\s*\{', re.S)
+    for src in sorted(CSRC.rglob("*.cu")):
+        text = re.sub(r"//[^\n]*", "", src.read_text())
+        for ret, name, args in pat.findall(text):
+            args = " ".join(args.split())
+            kinds = [] if args in ("", "void") else [_kind(a) for a in args.split(",")]
+            out[name] = (ret.strip(), kinds, src.name)
+    return out
+
+
+_CT = {ctypes.c_void_p: "P", ctypes.c_int: "I", ctypes.c_float: "F", ctypes.c_longlong: "L"}
+
+
+def _reg_kind(t) -> str:
+    if t in _CT:
+        return _CT[t]
+    if isinstance(t, type) and issubclass(t, ctypes._Pointer):
+        return "P"
+    return "?"
+
+
+def test_registered_signatures_match_the_c_declarations():
+    _import_all_registrations()
+    decls = c_declarations()
+    assert len(decls) > 30
+    problems = []
+    for name, (res, argtypes) in native._SIGNATURES.items():
+        if name not in decls:
+            problems.append(f"{name}: registered but not declared extern \"C\" in any CUDA source")
+            continue
+        _, kinds, src = decls[name]
+        reg = [_reg_kind(t) for t in argtypes]
+        if len(reg) != len(kinds):
+            problems.append(f"{name} ({src}): {len(kinds)} C parameters, {len(reg)} registered")
+        elif any(a != b for a, b in zip(reg, kinds) if "?" not in (a, b)):
+            problems.append(f"{name} ({src}): C kinds {''.join(kinds)} vs registered {''.join(reg)}")
+    assert not problems, "\n".join(problems)
+
+
+class _StubLib:
+    """Stands in for the loaded library: checks each call against its registration and launches nothing."""
+
+    def __init__(self):
+        self.calls = []
+
+    def __getattr__(self, name):
+        if name.startswith("__"):
+            raise AttributeError(name)
+        if name not in native._SIGNATURES:
+            raise AssertionError(f"{name} is called but was never registered")
+        res, argtypes = native._SIGNATURES[name]
+
+        def call(*args):
+            assert len(args) == len(argtypes), f"{name}: {len(args)} arguments for {len(argtypes)} parameters"
+            for i, (a, t) in enumerate(zip(args, argtypes)):
+                k = _reg_kind(t)
+                if k == "P":
+                    assert a is None or isinstance(a, int) or hasattr(a, "_obj") or isinstance(a, ctypes._Pointer), \
+                        f"{name} argument {i}: {type(a).__name__} given for a pointer"
+                elif k in ("I", "L"):
+                    assert isinstance(a, int) and not isinstance(a, float), f"{name} argument {i}: {a!r} given for an integer"
+                elif k == "F":
+                    assert isinstance(a, (int, float)), f"{name} argument {i}: {a!r} given for a float"
+            self.calls.append(name)
+            if name == "eredu_sampler_row_bytes":
+                return 64
+            if name == "eredu_gemm_pick_split":
+                return 1
+            return 0 if res is not None else None
+
+        return call
+
+
+@pytest.fixture
+def dry_cuda(monkeypatch):
+    """CPU tensors claim to be CUDA tensors and the library is a stub: the wrappers' GPU branches execute."""
+    _import_all_registrations()
+    stub = _StubLib()
+    status = torch.zeros(1, dtype=torch.int32)
+    monkeypatch.setattr(torch.Tensor, "is_cuda", property(lambda self: True), raising=False)
+    import eredu_b200.ops.conv as conv_mod
+    import eredu_b200.ops.core as core_mod
+    import eredu_b200.ops.moe as moe_mod
+    import eredu_b200.ops.quant as quant_mod
+    import eredu_b200.ops.sampling as samp_mod
+
+    for mod in (native, conv_mod, core_mod, moe_mod, quant_mod, samp_mod):
+        for attr, val in (("lib", lambda: stub), ("stream_ptr", lambda device=None: 0),
+                          ("status_word", lambda device=None: status), ("_sm_count", lambda device=None: 148),
+                          ("check_status", lambda device=None: None)):
+            if hasattr(mod, attr):
+                monkeypatch.setattr(mod, attr, val)
+    return stub
+
+
+def test_dense_and_quantised_wrappers_dry_run(dry_cuda):
+    from eredu_b200.ops.quant import Fp8Linear, QuantLinear
+
+    bf = torch.bfloat16
+    x = torch.randn(8, 256).to(bf)
+    w = torch.randn(384, 256).to(bf)
+    ops.linear(x, w, bias=torch.zeros(384, dtype=bf), residual=torch.zeros(8, 384, dtype=bf))
+    ops.linear(x, w, out_dtype=torch.float32)
+    ops.gated_linear(x, w, 192)
+    ops.silu_mul(torch.randn(8, 384).to(bf), 192, 7.0)
+    ops.rmsnorm(x, torch.ones(256), 1e-5)
+    assert {"eredu_gemm_bf16", "eredu_silu_mul", "eredu_rmsnorm"} <= set(dry_cuda.calls)
+    for bits, group in ((4, 64), (8, 32)):
+        q = QuantLinear.from_dense(w.float(), bits, group)
+        q(x, bias=torch.zeros(384, dtype=bf), residual=torch.zeros(8, 384, dtype=bf))
+        q(torch.randn(300, 256).to(bf))                      # whole-matrix dequant + dense GEMM
+    f8 = Fp8Linear.from_dense(w.float())
+    f8(x, residual=torch.zeros(8, 384, dtype=bf))
+    f8(torch.randn(300, 256).to(bf), out_dtype=torch.float32)
+    assert {"eredu_qgemm", "eredu_dequant_affine", "eredu_qgemm_fp8", "eredu_dequant_fp8"} <= set(dry_cuda.calls)
+
+
+def test_moe_and_conv_wrappers_dry_run(dry_cuda):
+    from eredu_b200.ops import moe as M
+
+    bf = torch.bfloat16
+    T, H, E, I_, k = 6, 128, 8, 64, 2
+    x = torch.randn(T, H).to(bf)
+    logits = torch.randn(T, E)
+    gu = torch.randn(E, 2 * I_, H).to(bf)
+    dn = torch.randn(E, H, I_).to(bf)
+    ids, w = M.route(logits, k, "softmax", True, 1.0, None)
+    M.experts_forward(x, ids, w, gu, dn, 0, residual=x)
+    M.experts_forward(x, ids, w, gu, dn, 0, gu_bias=torch.zeros(E, 2 * I_, dtype=bf), down_bias=torch.zeros(E, H, dtype=bf),
+                      act="oss_glu", limit=7.0)
+    ids2, w2, plan, xp = M.route_plan_gather(logits, x, k, "sigmoid", True, 1.5, torch.zeros(E), 0, E)
+    M.experts_forward(x, ids2, w2, gu, dn, 0, plan=plan, xp=xp)
+    assert {"eredu_moe_route", "eredu_moe_plan", "eredu_moe_gather", "eredu_gemm_bf16_grouped", "eredu_moe_combine",
+            "eredu_moe_route_plan_gather"} <= set(dry_cuda.calls)
+    C_, L = 64, 3
+    ops.short_conv(torch.randn(5, 3 * C_).to(bf), torch.randn(C_, L), None, torch.zeros(4, L - 1, C_, dtype=bf),
+                   torch.zeros(1, 2, dtype=torch.int32), torch.tensor([0, 5], dtype=torch.int32), 1,
+                   torch.arange(5, dtype=torch.int32), torch.zeros(5, dtype=torch.int64), max_q_len=5)
+    assert "eredu_short_conv" in dry_cuda.calls
