@@ -191,10 +191,13 @@ class LoadedModel:
         return GrammarConstraint(self.tokenizer, kind, spec)
 
     def generate_prepared_chat(self, prepared, sampling: Optional[SamplingParams] = None, max_new_tokens: int = 256,
-                               on_event=None, cancellation=None, raw: bool = False, mirostat=None, constraint=None):
+                               on_event=None, cancellation=None, raw: bool = False, mirostat=None, constraint=None,
+                               draft: Optional["LoadedModel"] = None, draft_tokens: int = 3):
         """Generate a reply for a :class:`PreparedChat`, streaming semantic events (reasoning, text, tool-call
         start / arguments / end, finished) to ``on_event`` (``generate_prepared_chat``, api/loaded.rs:154-227).
-        ``mirostat`` (an :class:`ops.controlled.MirostatV2`) and ``constraint`` (a :class:`GrammarConstraint`, e.g.
+        ``draft`` (another loaded model with the same vocabulary) turns on speculative decoding with ``draft_tokens``
+        proposals per round (``generate_prepared_chat_mtp``, api/loaded.rs:238; the committed tokens are exactly those
+        plain decoding would emit). ``mirostat`` (an :class:`ops.controlled.MirostatV2`) and ``constraint`` (a :class:`GrammarConstraint`, e.g.
         from :meth:`constraint_for`) switch to the host-driven controlled sampler.
         Returns a dict with text, reasoning, tool_calls, finish_reason, token ids and timing."""
         import time
@@ -234,6 +237,13 @@ class LoadedModel:
                       "grammar_complete": FinishReason.GRAMMAR_COMPLETE}.get(why, why)
             if first_token_at[0] is None:
                 first_token_at[0] = time.perf_counter()
+        elif draft is not None:
+            from ..runtime.speculative import SpeculativeDecoder
+
+            spec = SpeculativeDecoder(self.engine, draft.engine, k=draft_tokens)
+            spec.generate([prompt_ids], sampling or SamplingParams(), max_new_tokens, eos_ids=(), on_token=on_token)
+            reason = spec.last_finish_reasons[0] or FinishReason.MAX_TOKENS
+            self.last_speculative_stats = spec.stats.summary()
         else:
             self.engine.generate([prompt_ids], sampling or SamplingParams(), max_new_tokens, eos_ids=(), on_token=on_token)
             reason = self.engine.last_finish_reasons[0] or FinishReason.MAX_TOKENS

@@ -217,8 +217,16 @@ def main(argv=None) -> int:
     if given:
         kind, val = given[0]
         constraint = lm.constraint_for(kind, val if kind == "regex" else open(val).read())
+    draft = None
+    if a.draft_model:
+        if mirostat is not None or constraint is not None:
+            raise SystemExit("--draft-model cannot be combined with --mirostat-v2 or a grammar constraint")
+        draft = LoadedModel.load(a.draft_model, ModelLoadOptions(device=device, max_batch=1,
+                                                                  max_seq_len=max(4096, a.max_tokens + 2048)))
+        if draft.config.vocab_size != lm.config.vocab_size:
+            raise SystemExit("--draft-model must share the target's vocabulary")
     res = lm.generate_prepared_chat(prepared, sp, a.max_tokens, on_event=on_event, raw=a.raw, mirostat=mirostat,
-                                    constraint=constraint)
+                                    constraint=constraint, draft=draft, draft_tokens=a.mtp_draft_tokens)
     sys.stdout.write("\n")
     timing = dict(res["timing"], load_time=load_time)
     if a.timing or a.verbose:
@@ -232,6 +240,13 @@ def main(argv=None) -> int:
                                  hardware=hardware_profile(device), prompt_tokens=res["prompt_tokens"],
                                  generated_tokens=len(res["tokens"]), stop_reason=res["finish_reason"], timing=timing,
                                  weights_bytes=lm.model.weight_bytes(), kv_bytes=lm.engine.kv.bytes())
+        if draft is not None:
+            tel.plan["speculative"] = getattr(lm, "last_speculative_stats", None)
+        if a.expert_cache_benchmark or a.expert_cache:
+            tel.plan["expert_cache"] = [lw.moe.expert_cache.report() for lw in lm.model.layers
+                                        if lw.moe is not None and getattr(lw.moe, "expert_cache", None) is not None]
+        if lm.model.residency is not None:
+            tel.plan["weight_residency"] = lm.model.residency.report()
         tel.write(a.telemetry_json)
     return 0
 

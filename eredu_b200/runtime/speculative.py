@@ -106,9 +106,26 @@ class SpeculativeDecoder:
     # ------------------------------------------------------------------------------------------ generation
     @torch.no_grad()
     def generate(self, prompts: list[list[int]], sampling: Optional[SamplingParams] = None, max_new_tokens: int = 64,
-                 eos_ids=()) -> list[list[int]]:
+                 eos_ids=(), on_token=None) -> list[list[int]]:
+        """``on_token(i, token)`` sees every committed token of sequence i in order (a round commits several at once);
+        a truthy return value ends that sequence after the token and is kept in ``last_finish_reasons``."""
         sp = sampling or SamplingParams()
         k = self.k
+        self.last_finish_reasons = [None] * len(prompts)
+        seen = [0] * len(prompts)
+
+        def publish(i, outs, done):
+            if on_token is None:
+                return
+            while seen[i] < len(outs[i]):
+                why = on_token(i, outs[i][seen[i]])
+                seen[i] += 1
+                if why:
+                    outs[i] = outs[i][:seen[i]]
+                    done[i] = True
+                    self.last_finish_reasons[i] = why
+                    return
+
         tseqs = [self.t.new_sequence(p, sp, max_new_tokens + k + 2, eos_ids) for p in prompts]
         dseqs = [self.d.new_sequence(p, sp, max_new_tokens + k + 2, eos_ids) for p in prompts]
         try:
@@ -118,6 +135,8 @@ class SpeculativeDecoder:
             pending = [[int(t)] for t in first]       # committed tokens missing from the draft cache
             last = [int(t) for t in first]            # leading uncached target input
             done = [int(t) in eos_ids or max_new_tokens <= 1 for t in first]
+            for i in range(len(prompts)):
+                publish(i, outs, done)
             while not all(done):
                 live = [i for i, f in enumerate(done) if not f]
                 self._round([tseqs[i] for i in live], [dseqs[i] for i in live], live, outs, pending, last, sp)
@@ -130,6 +149,7 @@ class SpeculativeDecoder:
                             outs[i] = outs[i][: j + 1]
                             done[i] = True
                             break
+                    publish(i, outs, done)
             if self.cuda:
                 ops.native.check_status(self.t.device)
             return outs

@@ -99,3 +99,26 @@ def test_cli_mirostat_and_regex_constraint(tmp_path, capsys):
 
     assert re.fullmatch("(ab|ba){1,3}", text), text
     assert json.loads(tel.read_text())["stop_reason"] in ("grammar_complete", "eos")
+
+
+def test_cli_draft_model_gives_the_same_text(tmp_path, capsys):
+    from eredu_b200.formats import checkpoint as ck
+    from eredu_b200.models import config as C
+    from eredu_b200.models.llama import random_state
+
+    tgt, drf = tmp_path / "target", tmp_path / "draft"
+    for path, layers, seed in ((tgt, 2, 0), (drf, 1, 0)):
+        path.mkdir()
+        b = make_bundle(path)
+        cfg = dataclasses.replace(C.tiny_llama(), vocab_size=b.vocab_size(), eos_token_id=b.eos_ids[0], num_hidden_layers=layers)
+        ck.save_safetensors_checkpoint(path, cfg, random_state(cfg, seed=seed, std=0.05), torch.float32)
+    base = ["-m", str(tgt), "hello there", "--device", "cpu", "--no-auto", "--raw", "-n", "12", "-t", "0"]
+    assert main(base) == 0
+    plain = capsys.readouterr().out
+    tel = tmp_path / "t.json"
+    assert main(base + ["--draft-model", str(drf), "--mtp-draft-tokens", "3", "--telemetry-json", str(tel)]) == 0
+    assert capsys.readouterr().out == plain
+    spec = json.loads(tel.read_text())["plan"]["speculative"]
+    assert spec["rounds"] > 0 and spec["proposed"] >= spec["accepted"]
+    with pytest.raises(SystemExit):
+        main(base + ["--draft-model", str(drf), "--mirostat-v2", "-t", "0.7"])

@@ -186,3 +186,29 @@ def test_moe_and_conv_wrappers_dry_run(dry_cuda):
                    torch.zeros(1, 2, dtype=torch.int32), torch.tensor([0, 5], dtype=torch.int32), 1,
                    torch.arange(5, dtype=torch.int32), torch.zeros(5, dtype=torch.int64), max_q_len=5)
     assert "eredu_short_conv" in dry_cuda.calls
+
+
+def test_moe_block_and_expert_cache_dry_run(dry_cuda):
+    import dataclasses
+
+    from eredu_b200.models import config as C
+    from eredu_b200.models.moe import MoEBlock
+    from eredu_b200.runtime.expert_cache import ExpertCache
+
+    bf = torch.bfloat16
+    cfg = dataclasses.replace(C.tiny_llama(), model_type="qwen3_moe", num_experts=8, num_experts_per_tok=2,
+                              moe_intermediate_size=64, hidden_size=128)
+    H, E, I_ = 128, 8, 64
+    blk = MoEBlock(cfg, torch.randn(E, H).to(bf), torch.randn(E, 2 * I_, H).to(bf), torch.randn(E, H, I_).to(bf), 0, E)
+    for T in (4, 100):                       # decode-sized (fused route + plan + gather) and prefill-sized steps
+        x = torch.randn(T, H).to(bf)
+        y = blk(x, residual=x)
+        assert y.shape == (T, H)
+    oss = MoEBlock(cfg, torch.randn(E, H).to(bf), torch.randn(E, 2 * I_, H).to(bf), torch.randn(E, H, I_).to(bf), 0, E,
+                   router_linear_bias=torch.zeros(E, dtype=bf), gu_bias=torch.zeros(E, 2 * I_, dtype=bf),
+                   down_bias=torch.zeros(E, H, dtype=bf), act="oss_glu")
+    oss(torch.randn(4, H).to(bf), residual=torch.randn(4, H).to(bf))
+    # expert cache: the ids the stub leaves behind are arbitrary, the bookkeeping must cope with any of them
+    blk.expert_cache = ExpertCache(blk.w_gate_up, blk.w_down, 3, "lru", 0)
+    x = torch.randn(4, H).to(bf)
+    assert blk(x, residual=x).shape == (4, H)
