@@ -38,8 +38,12 @@ class ModelLoadOptions:
     kv_pages: Optional[int] = None
     native_gguf: bool = True                     # keep Q4_K/Q6_K/... blocks and run the native kernels
     use_cuda_graph: Optional[bool] = None
-    weight_residency: str = "device"             # "device" | "layerwise_host" (--layerwise-host)
+    weight_residency: str = "device"             # "device" | "layerwise_host" | "dense_disk_stream"
     device_layer_window: int = 1                 # layers resident on the device at a time in layerwise_host mode
+    dense_host_lookahead: int = 2                # dense_disk_stream: imminent layers kept materialised on the host
+    dense_background_queue: int = 2              # dense_disk_stream: pending background disk reads
+    dense_spill_dir: Optional[str] = None        # dense_disk_stream: where the prepared layers are written (default: temp)
+    host_budget_bytes: Optional[int] = None      # dense_disk_stream: byte cap of the host copies
     expert_cache: bool = False                   # routed experts in host memory behind a bounded device bank
     expert_cache_device_budget_bytes: Optional[int] = None   # per sparse layer; None: a quarter of the experts
     expert_cache_eviction: str = "lru"
@@ -80,6 +84,15 @@ class LoadedModel:
                 nonlocal residency
                 if residency is None:
                     residency = LayerwiseHostResidency(m, opt.device_layer_window, defer=True)
+                residency.adopt_layer(lw)
+        elif opt.weight_residency == "dense_disk_stream":
+            from ..runtime.weight_residency import DiskStreamResidency
+
+            def on_layer(m, li, lw):
+                nonlocal residency
+                if residency is None:
+                    residency = DiskStreamResidency(m, opt.dense_host_lookahead, opt.dense_background_queue,
+                                                    opt.dense_spill_dir, opt.host_budget_bytes, defer=True)
                 residency.adopt_layer(lw)
         elif opt.weight_residency != "device":
             raise ValueError(f"unknown weight residency {opt.weight_residency!r}")

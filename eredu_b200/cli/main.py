@@ -85,6 +85,10 @@ def build_parser() -> argparse.ArgumentParser:
 def validate_args(a) -> None:
     if a.max_tokens <= 0:
         raise SystemExit("--max-tokens must be positive")
+    if a.dense_disk_stream and a.layerwise_host:
+        raise SystemExit("--dense-disk-stream conflicts with --layerwise-host")
+    if a.dense_disk_stream and (a.dense_host_lookahead < 1 or a.dense_background_queue < 1):
+        raise SystemExit("--dense-host-lookahead and --dense-background-queue must be at least 1")
     if a.quantization_mode == "fp8" and a.quantize not in (None, 8):
         raise SystemExit("--quantization-mode fp8 stores 8-bit E4M3 codes: use --quantize 8")
     if a.quantize is not None and a.quantize not in (2, 3, 4, 5, 6, 8):
@@ -170,7 +174,11 @@ def main(argv=None) -> int:
     t0 = time.perf_counter()
     lm = LoadedModel.load(model_path, ModelLoadOptions(device=device, quantization=quant, mapped_shards=a.mapped_shards,
                                                        max_batch=1, max_seq_len=max(4096, a.max_tokens + 2048),
-                                                       weight_residency="layerwise_host" if layerwise else "device",
+                                                       weight_residency=("dense_disk_stream" if a.dense_disk_stream else
+                                                                         "layerwise_host" if layerwise else "device"),
+                                                       dense_host_lookahead=a.dense_host_lookahead,
+                                                       dense_background_queue=a.dense_background_queue,
+                                                       host_budget_bytes=a.host_budget_bytes,
                                                        device_layer_window=window,
                                                        expert_cache=a.expert_cache,
                                                        expert_cache_device_budget_bytes=a.expert_cache_device_budget_bytes,

@@ -71,3 +71,42 @@ def test_layerwise_host_through_the_load_api(tmp_path):
                                                      weight_residency="layerwise_host", device_layer_window=2))
     assert lm.model.residency is not None and lm.generate([prompt], None, 6) == want
     assert lm.model.residency.report()["loads"] > 4
+
+
+def test_dense_disk_stream_cpu(tmp_path):
+    from eredu_b200.runtime.weight_residency import DiskStreamResidency
+
+    cfg = dataclasses.replace(C.tiny_llama(), vocab_size=512, num_hidden_layers=6)
+    sd = random_state(cfg, seed=0, std=0.05)
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 21)]
+    sp = SamplingParams(temperature=0.0)
+    want = Engine(build_from_tensors(cfg, sd.__getitem__, sd.__contains__, "cpu", torch.float32), max_batch=2,
+                  max_seq_len=64).generate(prompts, sp, 8)
+    model = build_from_tensors(cfg, sd.__getitem__, sd.__contains__, "cpu", torch.float32)
+    res = DiskStreamResidency(model, host_lookahead=2, background_queue=2, spill_dir=tmp_path)
+    assert len(list(tmp_path.glob("layer-*.bin"))) == 6 and all(lw.wqkv is None for lw in model.layers)
+    got = Engine(model, max_batch=2, max_seq_len=64).generate(prompts, sp, 8)
+    assert got == want
+    rep = res.report()
+    assert rep["mode"] == "dense_disk_stream" and rep["max_host_layers"] <= 2 + 1 + 1   # window + one being published
+    assert rep["host_layers_now"] <= 3 and rep["evictions"] > 0 and rep["bytes_read"] > 0
+    assert rep["background_reads"] > rep["demand_reads"]          # the readers stayed ahead of the compute
+    res.close()
+    with pytest.raises(ValueError):
+        DiskStreamResidency(model, host_lookahead=0)
+
+
+def test_dense_disk_stream_load_option(tmp_path):
+    from eredu_b200.api import LoadedModel, ModelLoadOptions
+    from eredu_b200.formats import checkpoint as ck
+
+    cfg = dataclasses.replace(C.tiny_llama(), vocab_size=512, num_hidden_layers=4)
+    ck.save_safetensors_checkpoint(tmp_path / "m", cfg, random_state(cfg, seed=1, std=0.05), torch.float32)
+    a = LoadedModel.load(tmp_path / "m", ModelLoadOptions(device="cpu", max_batch=1, max_seq_len=64))
+    b = LoadedModel.load(tmp_path / "m", ModelLoadOptions(device="cpu", max_batch=1, max_seq_len=64,
+                                                          weight_residency="dense_disk_stream", dense_host_lookahead=1,
+                                                          dense_background_queue=1, dense_spill_dir=str(tmp_path / "spill")))
+    prompt = list(range(4, 30))
+    assert torch.equal(a.prefill_logits(prompt), b.prefill_logits(prompt))
+    assert b.model.residency.report()["mode"] == "dense_disk_stream"
