@@ -222,8 +222,12 @@ class LoadedModel:
             raise RuntimeError("this checkpoint has no tokenizer")
         prompt_ids = self.tokenizer.encode(prepared.prompt)
         eos = set(self.eos_ids()) | set(self.tokenizer.eos_ids)
-        pipe = CommittedTokenPipeline(TextDecoder(self.tokenizer), None if raw else prepared.plan, prepared.stop, on_event,
-                                      prepared.tool_choice.max_parallel_calls)
+        from ..text.dialects import pipeline_for
+
+        plan = None if raw else prepared.plan
+        show_special = bool(plan is not None and plan.render_special_tokens)
+        pipe = pipeline_for(plan)(TextDecoder(self.tokenizer, skip_special_tokens=not show_special), plan, prepared.stop,
+                                  on_event, prepared.tool_choice.max_parallel_calls)
         t0 = time.perf_counter()
         first_token_at = [None]
         tokens: list[int] = []

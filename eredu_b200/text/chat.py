@@ -34,6 +34,8 @@ class ParserPlan:
     tool_open: Optional[str] = None          # e.g. "<tool_call>"
     tool_close: Optional[str] = None
     allow_unparsed_reasoning: bool = False
+    dialect: str = "generic"                 # generic | lfm2 (Python-style call lists) | harmony (GPT-OSS channels)
+    render_special_tokens: bool = False      # the structural tags are special tokens: the detokeniser must show them
 
 
 @dataclass
@@ -79,6 +81,14 @@ def detect_plan(template: str, rendered: str, tools, thinking: str = "auto", all
         plan.starts_in_reasoning = tail.rstrip().endswith("<think>")
     if thinking == "off":
         plan.starts_in_reasoning = False
+    if "<|channel|>" in template and "<|message|>" in template:
+        # Harmony (GPT-OSS): channels carry reasoning, reply and tool calls; the dialect parser owns all of it
+        plan.dialect, plan.render_special_tokens = "harmony", True
+        return plan
+    if "<|tool_call_start|>" in template:
+        plan.dialect, plan.render_special_tokens = "lfm2", True
+        plan.tool_open, plan.tool_close = "<|tool_call_start|>", "<|tool_call_end|>"
+        return plan
     if tools:
         if "<tool_call>" in template:
             plan.tool_open, plan.tool_close = "<tool_call>", "</tool_call>"
