@@ -221,6 +221,12 @@ class DiskStreamResidency(LayerwiseHostResidency):
         import queue
         import threading
 
+        from ..lib import _eredu_host as H
+
+        # tier accounting lives in the C++ ledger: every layer is a windowed unit whose home copy is the spill file
+        self.ledger = H.ResidencyLedger(-1, -1 if self.host_budget_bytes is None else int(self.host_budget_bytes), -1, "lru")
+        for li in range(len(self.units)):
+            self.ledger.add_unit(f"layer.{li}", self._layer_bytes(li), "windowed", "disk")
         self.jobs: "queue.Queue" = queue.Queue(maxsize=self.background_queue)
         self.workers = [threading.Thread(target=self._worker, daemon=True) for _ in range(min(2, self.background_queue))]
         for w in self.workers:
@@ -246,6 +252,11 @@ class DiskStreamResidency(LayerwiseHostResidency):
 
     def _publish(self, li: int, tensors: list, background: bool) -> None:
         with self.lock:
+            name = f"layer.{li}"
+            if not self.ledger.is_resident(name, "host"):
+                self.ledger.reserve(name, "host")
+                self.ledger.resolve_transfer(name, "host", self.ledger.begin_transfer(name, "host"), "disk")
+            self.ledger.record_prefetch("host", "hit" if background else "miss")
             self.host[li] = tensors
             if li in self.host_order:
                 self.host_order.remove(li)
@@ -291,6 +302,7 @@ class DiskStreamResidency(LayerwiseHostResidency):
                     self.ready[slot].synchronize()   # its host->device copy may still be reading the buffers
                 del self.host[li]
                 self.host_order.remove(li)
+                self.ledger.evict(f"layer.{li}", "host")
                 self.units[li] = [(obj, attr, None) for obj, attr, _ in self.units[li]]
                 self.disk["evictions"] += 1
 
@@ -330,6 +342,13 @@ class DiskStreamResidency(LayerwiseHostResidency):
     def _load(self, li: int) -> None:
         host = self._host_tensors(li)
         self.units[li] = [(obj, attr, h) for (obj, attr, _), h in zip(self.units[li], host)]
+        prev = self.loaded[self._slot_of(li)]
+        with self.lock:
+            if prev >= 0 and prev != li and self.ledger.is_resident(f"layer.{prev}", "device"):
+                self.ledger.evict(f"layer.{prev}", "device")
+            if not self.ledger.is_resident(f"layer.{li}", "device"):
+                self.ledger.reserve(f"layer.{li}", "device")
+                self.ledger.resolve_transfer(f"layer.{li}", "device", self.ledger.begin_transfer(f"layer.{li}", "device"), "host")
         super()._load(li)
 
     def acquire(self, i: int) -> None:
@@ -342,7 +361,8 @@ class DiskStreamResidency(LayerwiseHostResidency):
 
     def report(self) -> dict:
         return dict(super().report(), mode="dense_disk_stream", host_lookahead=self.host_lookahead,
-                    background_queue=self.background_queue, host_layers_now=len(self.host), **self.disk)
+                    background_queue=self.background_queue, host_layers_now=len(self.host), ledger=self.ledger.report(),
+                    **self.disk)
 
     def close(self) -> None:
         for _ in getattr(self, "workers", []):

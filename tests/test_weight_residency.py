@@ -92,6 +92,10 @@ def test_dense_disk_stream_cpu(tmp_path):
     assert rep["mode"] == "dense_disk_stream" and rep["max_host_layers"] <= 2 + 1 + 1   # window + one being published
     assert rep["host_layers_now"] <= 3 and rep["evictions"] > 0 and rep["bytes_read"] > 0
     assert rep["background_reads"] > rep["demand_reads"]          # the readers stayed ahead of the compute
+    led = rep["ledger"]
+    assert led["host"]["resident_units"] == rep["host_layers_now"] and led["device"]["resident_units"] <= 2
+    assert led["transfers"]["disk_to_host"]["count"] == rep["background_reads"] + rep["demand_reads"]
+    assert led["transfers"]["host_to_device"]["bytes"] == rep["bytes_loaded"] and led["disk"]["resident_units"] == 6
     res.close()
     with pytest.raises(ValueError):
         DiskStreamResidency(model, host_lookahead=0)
