@@ -97,6 +97,7 @@ class CausalLM:
         self.tp_ops = None  # set by parallel.tp when tp_size > 1
         self.head_folded = False
         self.residency = None  # set by runtime.weight_residency when the layers live in host memory
+        self.observer = None   # runtime.inspection.ActivationObserver for observed (eager) passes
 
     # ------------------------------------------------------------------------------------------ layer
     def _linear(self, lw: LayerWeights, role: str, x, w, bias=None, residual=None):
@@ -187,6 +188,8 @@ class CausalLM:
         cfg = self.cfg
         if lw.moe is not None:
             normed, _ = ops.rmsnorm(h, lw.ffn_norm, cfg.rms_norm_eps, weight_offset=cfg.norm_weight_offset)
+            if self.observer is not None:
+                return lw.moe.observed_call(normed, h, self.observer), None
             return lw.moe(normed, residual=h), None
         inter = (lw.qlin["gate_up"].out_features if "gate_up" in lw.qlin else lw.w_gate_up.shape[0]) // 2
         act = self._normed_linear(h, ssq, lw.fold_ffn, lw.ffn_norm, lw.w_gate_up, lw, "gate_up", gated_inter=inter)
@@ -205,6 +208,9 @@ class CausalLM:
         else:
             h = batch.hidden_in
         n = len(self.layers)
+        obs = self.observer
+        if obs is not None and self.par.owns_embedding():
+            obs.observe("model.embed_tokens", h)
         for i, lw in enumerate(self.layers):
             nxt = self.layers[i + 1].fold_attn if i + 1 < n else (self.head_folded and self.par.owns_output_head())
             if self.residency is not None:
@@ -212,6 +218,12 @@ class CausalLM:
             h, ssq = self.layer_forward(self.first_layer + i, lw, h, batch, kv, ssq, nxt)
             if self.residency is not None:
                 self.residency.release(i)
+            if obs is not None:
+                name = f"model.layers.{self.first_layer + i}.output"
+                repl = obs.intervene(name, h)
+                if repl is not None:
+                    h, ssq = repl.to(h.dtype), None     # the producer's row sums no longer describe the activation
+                obs.observe(name, h)
         return h, ssq
 
     def logits(self, h, rows=None, ssq=None):

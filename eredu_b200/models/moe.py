@@ -50,6 +50,37 @@ class MoEBlock:
         return moe_ops.route(logits.contiguous(), cfg.num_experts_per_tok, cfg.router_scoring, cfg.norm_topk_prob,
                              cfg.routed_scaling_factor, self.router_bias)
 
+    def observed_call(self, x, residual, observer):
+        """Unfused pass that materialises what an activation observer is shown (routing ids, scores, weights, routed /
+        shared / combined outputs); numerically the same block."""
+        from ..runtime.inspection import MoeRoutingObservation
+
+        cfg = self.cfg
+        logits = ops.linear(x, self.router_w, bias=self.router_linear_bias, out_dtype=torch.float32)
+        ids, w = moe_ops.route(logits.contiguous(), cfg.num_experts_per_tok, cfg.router_scoring, cfg.norm_topk_prob,
+                               cfg.routed_scaling_factor, self.router_bias)
+        _, raw = moe_ops.route_ref(logits, cfg.num_experts_per_tok, cfg.router_scoring, False, 1.0, self.router_bias)
+        shared = None
+        if self.shared is not None:
+            sgu, sd = self.shared
+            shared = ops.linear(ops.gated_linear(x, sgu, sgu.shape[0] // 2), sd)
+        cache = getattr(self, "expert_cache", None)
+        if cache is not None:
+            local = cache.forward(x, ids, w, limit=cfg.swiglu_limit)
+        else:
+            local = moe_ops.experts_forward(x, ids, w, self.w_gate_up, self.w_down, self.e0, limit=cfg.swiglu_limit,
+                                            gu_bias=self.gu_bias, down_bias=self.down_bias, act=self.act)
+        reduced = self.ep_ops.all_reduce(local.clone()) if self.ep_size > 1 else None
+        routed = reduced if reduced is not None else local
+        combined = routed.float() + (shared.float() if shared is not None else 0.0)
+        prefix = f"model.layers.{getattr(self, 'layer_index', '?')}.mlp"
+        observer.observe_moe_routing(MoeRoutingObservation(
+            prefix=prefix, selected_experts=ids, selected_scores=raw, routing_weights=w, routed_output=routed,
+            num_experts=self.n_experts, local_routed_output=local if reduced is not None else None,
+            reduced_routed_output=reduced, shared_output=shared, combined_output=combined.to(x.dtype)))
+        out = combined + (residual.float() if residual is not None else 0.0)
+        return out.to(x.dtype)
+
     def __call__(self, x, residual=None):
         """x: normalised hidden states [T, H]; returns residual + MoE(x)."""
         self.stats["calls"] += 1
@@ -115,6 +146,7 @@ def make_moe_factory(src=None, router_std_scale: bool = False):
             dn = torch.stack([get(mx + f"experts.{e}.w2.weight") for e in range(e0, e1)], 0).to(device=dev, dtype=dt).contiguous()
             block = MoEBlock(cfg, router, gu, dn, e0, cfg.num_experts, ep_size=par.ep_size)
             block._model = model
+            block.layer_index = li
             return block
         if has(p + "router.weight"):
             return _gpt_oss_block(model, li, get, has, e0, e1)
@@ -143,6 +175,7 @@ def make_moe_factory(src=None, router_std_scale: bool = False):
             sel_bias = get(p + "expert_bias").to(device=dev, dtype=torch.float32).contiguous()
         block = MoEBlock(cfg, router, gu, dn, e0, cfg.num_experts, ep_size=par.ep_size, shared=shared, router_bias=sel_bias)
         block._model = model
+        block.layer_index = li
         return block
 
     return factory
@@ -183,6 +216,7 @@ def _gpt_oss_block(model, li, get, has, e0, e1):
     block = MoEBlock(cfg, up(get(p + "router.weight")), up(gu), up(dn), e0, cfg.num_experts, ep_size=model.par.ep_size,
                      router_linear_bias=up(get(p + "router.bias")), gu_bias=up(gub), down_bias=up(dnb), act="oss_glu")
     block._model = model
+    block.layer_index = li
     return block
 
 

@@ -385,7 +385,7 @@ class Engine:
     def _host_driven(self) -> bool:
         """True when a forward pass needs the host between kernels (layerwise host residency, expert cache)."""
         m = self.model
-        if getattr(m, "residency", None) is not None:
+        if getattr(m, "residency", None) is not None or getattr(getattr(m, "inner", m), "observer", None) is not None:
             return True
         return any(getattr(getattr(lw, "moe", None), "expert_cache", None) is not None for lw in getattr(m, "layers", []))
 

@@ -1,0 +1,56 @@
+"""Activation observer: named block outputs, interventions, MoE routing records; observed passes change nothing."""
+import dataclasses
+
+import torch
+
+from eredu_b200.models import config as C
+from eredu_b200.models.llama import build_from_tensors, random_state
+from eredu_b200.models.moe import make_moe_factory
+from eredu_b200.ops import SamplingParams
+from eredu_b200.runtime.engine import Engine
+from eredu_b200.runtime.inspection import ActivationObserver, RecordingObserver, observed
+
+
+def test_observer_sees_block_outputs_and_can_intervene():
+    cfg = dataclasses.replace(C.tiny_llama(), vocab_size=300, num_hidden_layers=3)
+    sd = random_state(cfg, seed=0, std=0.05)
+    model = build_from_tensors(cfg, sd.__getitem__, sd.__contains__, "cpu", torch.float32)
+    eng = Engine(model, max_batch=1, max_seq_len=64)
+    prompt = list(range(5, 25))
+    plain = eng.generate([prompt], SamplingParams(temperature=0.0), 6)[0]
+    rec = RecordingObserver()
+    with observed(model, rec):
+        seen = eng.generate([prompt], SamplingParams(temperature=0.0), 6)[0]
+    assert seen == plain and model.observer is None
+    assert set(rec.tensors) == {"model.embed_tokens"} | {f"model.layers.{i}.output" for i in range(3)}
+    assert rec.tensors["model.layers.2.output"].shape[-1] == cfg.hidden_size
+
+    class ZeroLayer1(ActivationObserver):
+        def intervene(self, name, value):
+            return torch.zeros_like(value) if name == "model.layers.1.output" else None
+
+    with observed(model, ZeroLayer1()):
+        changed = eng.generate([prompt], SamplingParams(temperature=0.0), 6)[0]
+    assert changed != plain
+    assert eng.generate([prompt], SamplingParams(temperature=0.0), 6)[0] == plain       # nothing sticks
+
+
+def test_moe_routing_observation():
+    cfg = dataclasses.replace(C.tiny_llama(), model_type="qwen3_moe", qk_norm=True, vocab_size=300, num_experts=8,
+                              num_experts_per_tok=2, moe_intermediate_size=64, norm_topk_prob=True, num_hidden_layers=2,
+                              tie_word_embeddings=False)
+    sd = random_state(cfg, seed=1, std=0.08)
+    model = build_from_tensors(cfg, sd.__getitem__, sd.__contains__, "cpu", torch.float32, moe_factory=make_moe_factory())
+    eng = Engine(model, max_batch=1, max_seq_len=64)
+    prompt = list(range(9, 20))
+    plain = eng.generate([prompt], SamplingParams(temperature=0.0), 4)[0]
+    rec = RecordingObserver(names=[])
+    with observed(model, rec):
+        assert eng.generate([prompt], SamplingParams(temperature=0.0), 4)[0] == plain
+    first = rec.routing[0]
+    assert first.prefix == "model.layers.0.mlp" and first.num_experts == 8
+    assert first.selected_experts.shape == (len(prompt), 2) and first.routing_weights.shape == (len(prompt), 2)
+    assert torch.allclose(first.routing_weights.sum(-1), torch.ones(len(prompt)), atol=1e-5)
+    assert bool((first.selected_scores <= 1).all()) and first.routed_output.shape == (len(prompt), cfg.hidden_size)
+    assert first.shared_output is None and first.reduced_routed_output is None
+    assert len(rec.routing) == 2 * (1 + 3)          # two sparse layers x (prefill + three decode steps)
