@@ -47,6 +47,8 @@ class ModelConfig:
     norm_topk_prob: bool = True
     router_scoring: str = "softmax"  # softmax | sigmoid | sqrt_softplus | topk_softmax
     routed_scaling_factor: float = 1.0  # multiplies the routing weights after renormalisation
+    n_group: int = 1        # group-limited routing: experts in n_group groups, only the topk_group best stay eligible
+    topk_group: int = 1
     shared_expert_intermediate_size: int = 0
     decoder_sparse_step: int = 1
     mlp_only_layers: list[int] = field(default_factory=list)
@@ -92,7 +94,9 @@ class ModelConfig:
         d = {k: v for k, v in asdict(self).items() if k not in ("extra", "qk_norm", "rope_traditional",
                                                                 "norm_weight_offset", "embedding_scale",
                                                                 "router_scoring", "attention_sinks", "quantization",
-                                                                "routed_scaling_factor")}
+                                                                "routed_scaling_factor", "n_group", "topk_group")}
+        if self.n_group > 1:
+            d["n_group"], d["topk_group"] = self.n_group, self.topk_group
         d["architectures"] = [{"llama": "LlamaForCausalLM", "mistral": "MistralForCausalLM",
                                "qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM",
                                "qwen3_moe": "Qwen3MoeForCausalLM", "mixtral": "MixtralForCausalLM", "phi3": "Phi3ForCausalLM",
@@ -165,6 +169,8 @@ class ModelConfig:
             mlp_only_layers=list(d.get("mlp_only_layers", []) or []),
             swiglu_limit=float(d.get("swiglu_limit", 0.0) or 0.0),
             routed_scaling_factor=float(d.get("routed_scaling_factor", 1.0) or 1.0),
+            n_group=int(d.get("n_group", 1) or 1),
+            topk_group=int(d.get("topk_group", 1) or 1),
             quantization=d.get("quantization") or d.get("quantization_config"),
             eos_token_id=d.get("eos_token_id"),
             bos_token_id=d.get("bos_token_id"),

@@ -48,7 +48,7 @@ class MoEBlock:
         cfg = self.cfg
         logits = ops.linear(x, self.router_w, bias=self.router_linear_bias, out_dtype=torch.float32)
         return moe_ops.route(logits.contiguous(), cfg.num_experts_per_tok, cfg.router_scoring, cfg.norm_topk_prob,
-                             cfg.routed_scaling_factor, self.router_bias)
+                             cfg.routed_scaling_factor, self.router_bias, cfg.n_group, cfg.topk_group)
 
     def observed_call(self, x, residual, observer):
         """Unfused pass that materialises what an activation observer is shown (routing ids, scores, weights, routed /
@@ -58,7 +58,7 @@ class MoEBlock:
         cfg = self.cfg
         logits = ops.linear(x, self.router_w, bias=self.router_linear_bias, out_dtype=torch.float32)
         ids, w = moe_ops.route(logits.contiguous(), cfg.num_experts_per_tok, cfg.router_scoring, cfg.norm_topk_prob,
-                               cfg.routed_scaling_factor, self.router_bias)
+                               cfg.routed_scaling_factor, self.router_bias, cfg.n_group, cfg.topk_group)
         _, raw = moe_ops.route_ref(logits, cfg.num_experts_per_tok, cfg.router_scoring, False, 1.0, self.router_bias)
         shared = None
         if self.shared is not None:
@@ -97,7 +97,7 @@ class MoEBlock:
             partial = cache.forward(x, ids, w, extra=extra if self.e0 == 0 else None, limit=self.cfg.swiglu_limit)
             return self.ep_ops.all_reduce(partial, residual=residual)
         plan = xp = None
-        if x.is_cuda and x.shape[0] <= 64:
+        if x.is_cuda and x.shape[0] <= 64 and self.cfg.n_group <= 1:
             # decode-sized: routing, expert plan and row gather in one kernel
             cfg = self.cfg
             logits = ops.linear(x, self.router_w, bias=self.router_linear_bias, out_dtype=torch.float32)

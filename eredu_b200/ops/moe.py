@@ -23,7 +23,13 @@ native.register("eredu_gemm_bf16_grouped", I, [P, P, P, P, I, I, I, I, I, I, I, 
 SCORING = {"softmax": 0, "sigmoid": 1, "sqrt_softplus": 2, "topk_softmax": 3}
 
 
-def route_ref(logits, k, scoring="softmax", renorm=True, scale=1.0, sel_bias=None):
+def route_ref(logits, k, scoring="softmax", renorm=True, scale=1.0, sel_bias=None, n_group=1, topk_group=1,
+              norm_eps=0.0, routing_indices=None):
+    """Reference router (eredu/src/backend/mlx/nn/moe.rs:433-507,652-702). Scores -> (+ selection bias) -> top-k, with the
+    group-limited form when ``n_group > 1`` (experts in n_group equal groups, a group's score is the sum of its two best
+    experts, only the topk_group best groups stay eligible) -> weights gathered from the UNBIASED scores -> optional
+    renormalisation (``norm_eps`` added to the sum) -> scale. ``routing_indices`` [T, k] replaces the selection
+    (hash routing: a table chooses the experts, the router only weights them)."""
     x = logits.float()
     if scoring == "softmax":
         score = torch.softmax(x, -1)
@@ -33,20 +39,36 @@ def route_ref(logits, k, scoring="softmax", renorm=True, scale=1.0, sel_bias=Non
         score = torch.sqrt(F.softplus(x))
     else:
         score = x
-    select = score + (sel_bias.float() if sel_bias is not None else 0.0)
-    ids = torch.topk(select, k, dim=-1).indices
+    if routing_indices is not None:
+        ids = routing_indices.long()
+    else:
+        select = score + (sel_bias.float() if sel_bias is not None else 0.0)
+        if n_group > 1 or topk_group > 1:
+            T, E = select.shape
+            if n_group <= 0 or topk_group <= 0 or topk_group > n_group or E % n_group != 0:
+                raise ValueError("invalid grouped MoE router configuration")
+            per = E // n_group
+            grouped = select.view(T, n_group, per)
+            group_scores = torch.topk(grouped, min(2, per), dim=-1).values.sum(-1)
+            keep = torch.topk(group_scores, topk_group, dim=-1).indices
+            mask = torch.zeros((T, n_group), dtype=torch.bool, device=select.device).scatter_(1, keep, True)
+            select = torch.where(mask[:, :, None].expand(T, n_group, per).reshape(T, E), select,
+                                 torch.full_like(select, float("-inf")))
+        ids = torch.topk(select, k, dim=-1).indices
     w = score.gather(-1, ids)
     if scoring == "topk_softmax":
         w = torch.softmax(w, -1)
     elif renorm:
-        w = w / w.sum(-1, keepdim=True).clamp(min=1e-20)
+        w = w / (w.sum(-1, keepdim=True) + norm_eps).clamp(min=1e-20)
     return ids.to(torch.int32), (w * scale).float()
 
 
-def route(logits, k, scoring="softmax", renorm=True, scale=1.0, sel_bias=None):
-    """Router logits [T, E] fp32 -> (ids [T, k] int32, weights [T, k] fp32)."""
-    if not logits.is_cuda:
-        return route_ref(logits, k, scoring, renorm, scale, sel_bias)
+def route(logits, k, scoring="softmax", renorm=True, scale=1.0, sel_bias=None, n_group=1, topk_group=1, norm_eps=0.0,
+          routing_indices=None):
+    """Router logits [T, E] fp32 -> (ids [T, k] int32, weights [T, k] fp32). Group-limited selection, a renormalisation
+    epsilon and table-driven (hash) routing run as tensor operations; the plain forms use the routing kernel."""
+    if not logits.is_cuda or n_group > 1 or topk_group > 1 or norm_eps != 0.0 or routing_indices is not None:
+        return route_ref(logits, k, scoring, renorm, scale, sel_bias, n_group, topk_group, norm_eps, routing_indices)
     T, E = logits.shape
     assert logits.dtype == torch.float32 and logits.is_contiguous()
     ids = torch.empty((T, k), dtype=torch.int32, device=logits.device)

@@ -136,3 +136,33 @@ def test_mixtral_naming_and_router_cpu():
     prompt = torch.randint(0, cfg.vocab_size, (11,), generator=torch.Generator().manual_seed(5)).tolist()
     out = eng.generate([prompt], SamplingParams(temperature=0.0), max_new_tokens=6)[0]
     assert out == greedy(cfg, sd, prompt, 6, moe_fn=moe_oracle)
+
+
+def test_group_limited_and_table_routing():
+    torch.manual_seed(0)
+    T, E, k = 16, 16, 4
+    logits = torch.randn(T, E)
+    bias = torch.randn(E) * 0.5
+    ids, w = M.route_ref(logits, k, "sigmoid", True, 2.5, bias, n_group=4, topk_group=2, norm_eps=1e-6)
+    score = torch.sigmoid(logits)
+    select = score + bias
+    for t in range(T):
+        groups = select[t].view(4, 4)
+        best = torch.topk(torch.topk(groups, 2, -1).values.sum(-1), 2).indices.tolist()
+        assert all(int(e) // 4 in best for e in ids[t])                       # only the two best groups are eligible
+        allowed = torch.cat([select[t, g * 4:(g + 1) * 4] for g in best])
+        assert sorted(select[t, ids[t].long()].tolist()) == sorted(torch.topk(allowed, k).values.tolist())
+        raw = score[t, ids[t].long()]                                          # weights come from the unbiased scores
+        assert torch.allclose(w[t], raw / (raw.sum() + 1e-6) * 2.5, atol=1e-6)
+    with pytest.raises(ValueError):
+        M.route_ref(logits, k, "sigmoid", True, 1.0, None, n_group=3, topk_group=1)
+    # table-driven routing: the ids are given, the router only weights them
+    table = torch.randint(0, E, (T, k))
+    ids2, w2 = M.route_ref(logits, k, "softmax", True, 1.0, None, routing_indices=table)
+    assert torch.equal(ids2.long(), table)
+    p = torch.softmax(logits, -1).gather(-1, table)
+    assert torch.allclose(w2, p / p.sum(-1, keepdim=True), atol=1e-6)
+    # configuration keys
+    cfg = C.ModelConfig.from_hf_dict({"model_type": "qwen3_moe", "num_experts": 16, "num_experts_per_tok": 4, "n_group": 4,
+                                      "topk_group": 2, "routed_scaling_factor": 2.5})
+    assert (cfg.n_group, cfg.topk_group, cfg.routed_scaling_factor) == (4, 2, 2.5)
