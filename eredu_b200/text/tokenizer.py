@@ -60,7 +60,12 @@ def _token_text(v):
 def _load_hf(path: Path) -> TokenizerBundle:
     from tokenizers import Tokenizer
 
-    tok = Tokenizer.from_file(str(path / "tokenizer.json"))
+    if (path / "tokenizer.json").exists():
+        tok = Tokenizer.from_file(str(path / "tokenizer.json"))
+    else:   # rank-ordered tiktoken vocabulary (Kimi): converted to the same fast byte-level BPE representation
+        from .tiktoken_import import load_tiktoken_dir
+
+        tok = load_tiktoken_dir(path)
     cfg = {}
     if (path / "tokenizer_config.json").exists():
         cfg = json.loads((path / "tokenizer_config.json").read_text())
@@ -129,7 +134,7 @@ def _gguf_tokenizer(md: dict) -> TokenizerBundle:
 
 def load_tokenizer(path, source=None) -> TokenizerBundle:
     path = Path(path)
-    if path.is_dir() and (path / "tokenizer.json").exists():
+    if path.is_dir() and ((path / "tokenizer.json").exists() or (path / "tiktoken.model").exists()):
         return _load_hf(path)
     md = getattr(source, "metadata", None)
     if md is not None:
