@@ -1,0 +1,67 @@
+"""Recurrent scans of hybrid (linear-attention) layers.
+
+``gated_delta_scan``: the gated delta rule (eredu/src/backend/mlx/nn/gated_delta.rs:135-183 step, :295-360 scan)::
+
+    S <- S * exp(g_t);  m = S^T k_t;  S <- S + k_t (beta_t (v_t - m))^T;  o_t = S^T q_t
+
+with the state ``S [B, H, Dk, Dv]`` in fp32. ``log_decay`` is ``[B, T, H]`` (one decay per head) or ``[B, T, H, Dk]`` (one
+per key channel). Feeding a sequence in chunks with the returned state gives the same outputs as one scan.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import native
+from .native import I, P, check, lib, ptr, stream_ptr
+
+native.register("eredu_gated_delta_scan", I, [P, P, P, P, P, P, P, I, I, I, I, I, I, P])
+
+
+def gated_delta_scan_ref(q, k, v, log_decay, beta, state: Optional[torch.Tensor] = None):
+    """PyTorch reference; returns (state fp32 [B, H, Dk, Dv], out [B, T, H, Dv] in q's dtype)."""
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+        raise ValueError("gated-delta query, key and value tensors must be rank 4")
+    if q.shape[:3] != k.shape[:3] or q.shape[:3] != v.shape[:3] or q.shape[3] != k.shape[3]:
+        raise ValueError("gated-delta query, key and value batch / sequence / head dimensions must match")
+    B, T, H, Dk = q.shape
+    Dv = v.shape[-1]
+    if log_decay.dim() not in (3, 4) or tuple(log_decay.shape[:3]) != (B, T, H) or (log_decay.dim() == 4 and log_decay.shape[3] != Dk):
+        raise ValueError(f"gated-delta log decay shape {tuple(log_decay.shape)} is incompatible with query shape {tuple(q.shape)}")
+    if tuple(beta.shape) != (B, T, H):
+        raise ValueError(f"gated-delta beta shape {tuple(beta.shape)} must equal {(B, T, H)}")
+    S = torch.zeros((B, H, Dk, Dv), dtype=torch.float32, device=q.device) if state is None else state.float().clone()
+    if tuple(S.shape) != (B, H, Dk, Dv):
+        raise ValueError(f"gated-delta state shape {tuple(S.shape)} must equal {(B, H, Dk, Dv)}")
+    outs = []
+    qf, kf, vf, bf = q.float(), k.float(), v.float(), beta.float()
+    decay = torch.exp(log_decay.float())
+    for t in range(T):
+        d = decay[:, t]
+        d = d[:, :, None, None] if d.dim() == 2 else d[:, :, :, None]
+        S = S * d
+        kt = kf[:, t][..., None]                                  # [B, H, Dk, 1]
+        mem = (S * kt).sum(-2)                                    # [B, H, Dv]
+        delta = (vf[:, t] - mem) * bf[:, t][..., None]
+        S = S + kt * delta[:, :, None, :]
+        outs.append((S * qf[:, t][..., None]).sum(-2))
+    return S, torch.stack(outs, 1).to(q.dtype)
+
+
+def gated_delta_scan(q, k, v, log_decay, beta, state: Optional[torch.Tensor] = None):
+    """CUDA: one kernel for the whole chunk (bf16 q / k / v, Dk of 64 or 128); otherwise the reference."""
+    if not q.is_cuda or q.dtype != torch.bfloat16 or q.shape[-1] not in (64, 128):
+        return gated_delta_scan_ref(q, k, v, log_decay, beta, state)
+    B, T, H, Dk = q.shape
+    Dv = v.shape[-1]
+    if tuple(beta.shape) != (B, T, H) or tuple(log_decay.shape[:3]) != (B, T, H):
+        raise ValueError("gated-delta beta / log decay shapes do not match the query")
+    S = torch.zeros((B, H, Dk, Dv), dtype=torch.float32, device=q.device) if state is None else state.float().contiguous().clone()
+    out = torch.empty((B, T, H, Dv), dtype=q.dtype, device=q.device)
+    g = log_decay.float().contiguous()
+    code = lib().eredu_gated_delta_scan(ptr(q.contiguous()), ptr(k.contiguous()), ptr(v.contiguous()), ptr(g),
+                                        ptr(beta.float().contiguous()), ptr(S), ptr(out), B, T, H, Dk, Dv,
+                                        1 if g.dim() == 4 else 0, stream_ptr(q.device))
+    check(code, "eredu_gated_delta_scan")
+    return S, out

@@ -24,6 +24,7 @@ def _import_all_registrations():
     import eredu_b200.ops.conv  # noqa: F401
     import eredu_b200.ops.moe  # noqa: F401
     import eredu_b200.ops.quant  # noqa: F401
+    import eredu_b200.ops.recurrent  # noqa: F401
     import eredu_b200.ops.sampling  # noqa: F401
     try:
         import eredu_b200.parallel.comm  # noqa: F401
