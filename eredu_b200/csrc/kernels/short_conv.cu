@@ -28,6 +28,8 @@ struct ShortConvParams {
   const long long* slots;     // [M] KV slot of every token; negative = inactive row
   __nv_bfloat16* out;         // [M, C]
   int ldp, ld_bt, q_per_seq, C, B;
+  int mode;   // 0: gated (LFM2): input B * X, output C * y.  1: plain: input proj[:, x_off + c], output silu(y)
+  int x_off;
 };
 
 __device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16(v)); }
@@ -62,6 +64,12 @@ __global__ void __launch_bounds__(128) short_conv_kernel(ShortConvParams p) {
 
   auto bx_of = [&](int t, float& v0, float& v1) {  // B * X of chunk row t, rounded like the stored state
     const __nv_bfloat16* row = p.proj + static_cast<size_t>(r0 + t) * p.ldp + c;
+    if (p.mode == 1) {
+      const uint32_t xx = *reinterpret_cast<const uint32_t*>(row + p.x_off);
+      v0 = bf16_lo(xx);
+      v1 = bf16_hi(xx);
+      return;
+    }
     const uint32_t bb = *reinterpret_cast<const uint32_t*>(row);
     const uint32_t xx = *reinterpret_cast<const uint32_t*>(row + 2 * C);
     v0 = round_bf16(bf16_lo(bb) * bf16_lo(xx));
@@ -95,8 +103,14 @@ __global__ void __launch_bounds__(128) short_conv_kernel(ShortConvParams p) {
       y0 += w0[j] * win0[j];
       y1 += w1[j] * win1[j];
     }
-    const uint32_t cc = *reinterpret_cast<const uint32_t*>(p.proj + static_cast<size_t>(r0 + t) * p.ldp + C + c);
-    *reinterpret_cast<uint32_t*>(p.out + static_cast<size_t>(r0 + t) * C + c) = pack_bf16x2(bf16_lo(cc) * y0, bf16_hi(cc) * y1);
+    uint32_t packed;
+    if (p.mode == 1) {
+      packed = pack_bf16x2(y0 / (1.f + __expf(-y0)), y1 / (1.f + __expf(-y1)));
+    } else {
+      const uint32_t cc = *reinterpret_cast<const uint32_t*>(p.proj + static_cast<size_t>(r0 + t) * p.ldp + C + c);
+      packed = pack_bf16x2(bf16_lo(cc) * y0, bf16_hi(cc) * y1);
+    }
+    *reinterpret_cast<uint32_t*>(p.out + static_cast<size_t>(r0 + t) * C + c) = packed;
 #pragma unroll
     for (int j = 0; j + 1 < L - 1; ++j) {
       win0[j] = win0[j + 1];
@@ -134,14 +148,16 @@ __global__ void __launch_bounds__(128) short_conv_kernel(ShortConvParams p) {
 
 using namespace eredu;
 
-// out[M, C] = gated short convolution of proj[M, 3C]; state [pages, L-1, C] bf16 is read and updated in place.
+// out[M, C] = gated short convolution of proj[M, 3C] (mode 0) or silu(conv(proj[:, x_off : x_off + C])) (mode 1: the
+// causal depthwise convolution in front of a gated-delta layer); state [pages, L-1, C] bf16 is read and updated in place.
 // cu_q null: B sequences of q_per_seq tokens each (decode); else B sequences with token offsets cu_q (prefill chunks,
 // at most max_q_len tokens each). C even, L in 2..4.
 extern "C" int eredu_short_conv(const void* proj, int ldp, const float* w, const float* bias, void* state,
                                 const int* block_table, int ld_bt, const int* cu_q, int q_per_seq, const int* positions,
-                                const long long* slots, void* out, int C, int L, int B, int max_q_len, cudaStream_t stream) {
+                                const long long* slots, void* out, int C, int L, int B, int max_q_len, int mode, int x_off,
+                                cudaStream_t stream) {
   if (B <= 0 || C <= 0) return 0;
-  if (C % 2 != 0 || ldp % 2 != 0 || L < 2 || L > 4) return -1;
+  if (C % 2 != 0 || ldp % 2 != 0 || L < 2 || L > 4 || x_off % 2 != 0 || (mode != 0 && mode != 1)) return -1;
   ShortConvParams p = {};
   p.proj = static_cast<const __nv_bfloat16*>(proj);
   p.w = w;
@@ -157,6 +173,8 @@ extern "C" int eredu_short_conv(const void* proj, int ldp, const float* w, const
   p.q_per_seq = q_per_seq;
   p.C = C;
   p.B = B;
+  p.mode = mode;
+  p.x_off = x_off;
   const int longest = cu_q != nullptr ? max_q_len : q_per_seq;
   int nseg = (longest + 63) / 64;
   nseg = nseg < 1 ? 1 : nseg > 4096 ? 4096 : nseg;

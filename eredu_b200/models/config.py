@@ -11,7 +11,8 @@ from pathlib import Path
 from typing import Any
 
 DENSE_TYPES = {"llama", "mistral", "qwen2", "qwen3", "phi3", "lfm2"}
-MOE_TYPES = {"qwen3_moe", "mixtral", "gpt_oss", "deepseek_v3", "lfm2_moe", "nemotron_h"}
+MOE_TYPES = {"qwen3_moe", "mixtral", "gpt_oss", "deepseek_v3", "lfm2_moe", "nemotron_h", "qwen3_next", "qwen3_5_moe"}
+QWEN_HYBRID_TYPES = {"qwen3_next", "qwen3_5", "qwen3_5_moe", "qwen3_5_text", "qwen3_5_moe_text"}
 
 
 @dataclass
@@ -35,6 +36,14 @@ class ModelConfig:
     mlp_bias: bool = False
     sliding_window: int | None = None
     layer_types: list[str] | None = None  # per-layer "full_attention" | "sliding_attention" | "conv" (LFM2)
+    # Qwen3-Next / 3.5 hybrids: "linear_attention" layers are gated delta networks
+    linear_conv_kernel_dim: int = 4
+    linear_key_head_dim: int = 128
+    linear_value_head_dim: int = 128
+    linear_num_key_heads: int = 16
+    linear_num_value_heads: int = 32
+    attn_output_gate: bool = False   # q_proj also produces a per-channel sigmoid gate of the attention output
+    shared_expert_gate: bool = False  # the shared expert's output is scaled by sigmoid(x . w)
     conv_l_cache: int = 3    # LFM2 short-convolution kernel width
     conv_bias: bool = False  # LFM2: biases on the convolution and its two projections
     qk_norm: bool = False  # per-head q/k RMSNorm (Qwen3)
@@ -79,9 +88,13 @@ class ModelConfig:
         """LFM2 hybrid schedule: the layer's operator is the gated short convolution instead of attention."""
         return self.layer_types is not None and self.layer_types[layer] == "conv"
 
+    def layer_is_linear_attention(self, layer: int) -> bool:
+        """Qwen3-Next style schedule: the layer's operator is a gated delta network instead of softmax attention."""
+        return self.layer_types is not None and self.layer_types[layer] == "linear_attention"
+
     @property
     def is_hybrid(self) -> bool:
-        return self.layer_types is not None and "conv" in self.layer_types
+        return self.layer_types is not None and ("conv" in self.layer_types or "linear_attention" in self.layer_types)
 
     def layer_window(self, layer: int) -> int:
         if self.sliding_window is None or self.sliding_window <= 0:
@@ -101,7 +114,15 @@ class ModelConfig:
                                "qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM",
                                "qwen3_moe": "Qwen3MoeForCausalLM", "mixtral": "MixtralForCausalLM", "phi3": "Phi3ForCausalLM",
                                "gpt_oss": "GptOssForCausalLM", "lfm2": "Lfm2ForCausalLM",
-                               "lfm2_moe": "Lfm2MoeForCausalLM"}.get(self.model_type, "LlamaForCausalLM")]
+                               "lfm2_moe": "Lfm2MoeForCausalLM", "qwen3_next": "Qwen3NextForCausalLM",
+                               "qwen3_5_moe": "Qwen3_5MoeForCausalLM"}.get(self.model_type, "LlamaForCausalLM")]
+        if self.model_type not in QWEN_HYBRID_TYPES:
+            for k in ("linear_conv_kernel_dim", "linear_key_head_dim", "linear_value_head_dim", "linear_num_key_heads",
+                      "linear_num_value_heads"):
+                d.pop(k, None)
+        d.pop("shared_expert_gate", None)
+        if not self.attn_output_gate:
+            d.pop("attn_output_gate", None)
         if self.routed_scaling_factor != 1.0 or self.model_type == "lfm2_moe":
             d["routed_scaling_factor"] = self.routed_scaling_factor
         if self.model_type == "lfm2_moe":
@@ -176,6 +197,28 @@ class ModelConfig:
             bos_token_id=d.get("bos_token_id"),
             torch_dtype=str(d.get("torch_dtype", d.get("dtype", "bfloat16"))),
         )
+        if mt in QWEN_HYBRID_TYPES:
+            # eredu/src/backend/mlx/architectures/qwen/hybrid/qwen3_5.rs:254-323: three gated-delta layers per full
+            # attention layer, zero-centred RMSNorm weights, gated attention output, 25 % rotary, gated shared expert
+            cfg.qk_norm = True
+            cfg.norm_weight_offset = 1.0
+            cfg.attn_output_gate = bool(d.get("attn_output_gate", True))
+            rp = d.get("rope_parameters") or {}
+            cfg.partial_rotary_factor = float(rp.get("partial_rotary_factor", d.get("partial_rotary_factor", 0.25)))
+            cfg.rope_theta = float(rp.get("rope_theta", d.get("rope_theta", 10000000.0)))
+            for key in ("linear_conv_kernel_dim", "linear_key_head_dim", "linear_value_head_dim", "linear_num_key_heads",
+                        "linear_num_value_heads"):
+                if key in d:
+                    setattr(cfg, key, int(d[key]))
+            if cfg.layer_types is None:
+                every = int(d.get("full_attention_interval", 4))
+                cfg.layer_types = ["full_attention" if (i + 1) % every == 0 else "linear_attention"
+                                   for i in range(cfg.num_hidden_layers)]
+            if len(cfg.layer_types) != cfg.num_hidden_layers:
+                raise ValueError("hybrid Qwen config needs one layer_types entry per layer")
+            cfg.norm_topk_prob = bool(d.get("norm_topk_prob", True))
+            cfg.shared_expert_gate = cfg.shared_expert_intermediate_size > 0
+            cfg.tie_word_embeddings = bool(d.get("tie_word_embeddings", False))
         if mt in ("lfm2", "lfm2_moe"):
             # eredu/src/backend/mlx/architectures/lfm2/model.rs:193-418: hybrid schedule of gated short convolutions
             # and q/k-normalised GQA attention; dense FFN width optionally re-derived from block_ff_dim

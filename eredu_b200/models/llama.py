@@ -62,6 +62,14 @@ class LayerWeights:
     qlin: dict = field(default_factory=dict)  # quantised linears by role: "qkv", "o", "gate_up", "down"
     # LFM2 "conv" layers: gated short convolution instead of attention (wqkv / wo are None); attn_norm is the
     # operator norm and fold_attn then refers to conv_in
+    attn_gate: bool = False   # wqkv carries a fourth block: the per-channel sigmoid gate of the attention output
+    # Qwen3-Next "linear_attention" layers (gated delta network); fold_attn then refers to la_in
+    la_in: Optional[torch.Tensor] = None       # [2 key + value + value + Hv + Hv, H]: qkv | z | b | a
+    la_conv_w: Optional[torch.Tensor] = None   # [2 key + value, K] fp32
+    la_dt_bias: Optional[torch.Tensor] = None
+    la_A_log: Optional[torch.Tensor] = None
+    la_norm_w: Optional[torch.Tensor] = None   # [dv] gated RMSNorm weight (not zero-centred)
+    la_out: Optional[torch.Tensor] = None      # [H, value]
     conv_in: Optional[torch.Tensor] = None    # [3C, H]: B | C | X projections
     conv_w: Optional[torch.Tensor] = None     # [C, L] fp32 depthwise kernel
     conv_out: Optional[torch.Tensor] = None   # [H, C]
@@ -165,7 +173,16 @@ class CausalLM:
                                batch.max_q_len)
             h, ssq = self._row_linear_ssq(lw, "conv_out", y, lw.conv_out, h, lw.conv_out_b, lw.fold_ffn)
             return self._ffn(lw, h, ssq, next_folded)
+        if lw.la_in is not None:
+            from .qwen_next import linear_attention_forward
+
+            h, ssq = linear_attention_forward(self, li, lw, h, ssq, batch, kv)
+            return self._ffn(lw, h, ssq, next_folded)
         qkv = self._normed_linear(h, ssq, lw.fold_attn, lw.attn_norm, lw.wqkv, lw, "qkv", bias=lw.bqkv)
+        gate = None
+        if lw.attn_gate:
+            width = (self.n_q_local + 2 * self.n_kv_local) * cfg.head_dim
+            gate, qkv = qkv[:, width:], qkv[:, :width]
         k_cache, v_cache = kv.layer(li)
         q = ops.rope_kv(qkv, batch.positions, batch.slots, self.inv_freq, k_cache, v_cache, self.n_q_local,
                         self.n_kv_local, cfg.head_dim, rot=cfg.rotary_dim, interleaved=cfg.rope_traditional,
@@ -180,6 +197,8 @@ class CausalLM:
                                         self.scale, splits=batch.splits, window=window, sinks=lw.sinks,
                                         scratch=batch.scratch)
         attn = attn.view(attn.shape[0], -1)
+        if gate is not None:
+            attn = (attn.float() * torch.sigmoid(gate.float())).to(attn.dtype)
         h, ssq = self._row_linear_ssq(lw, "o", attn, lw.wo, h, lw.bo, lw.fold_ffn)
         return self._ffn(lw, h, ssq, next_folded)
 
@@ -270,6 +289,9 @@ class CausalLM:
         off = self.cfg.norm_weight_offset
         if "qkv" not in lw.qlin and not lw.fold_attn and lw.wqkv is not None:
             lw.wqkv = (lw.wqkv.float() * (lw.attn_norm + off)[None, :]).to(self.dtype).contiguous()
+            lw.fold_attn = True
+        if "la_in" not in lw.qlin and not lw.fold_attn and lw.la_in is not None:
+            lw.la_in = (lw.la_in.float() * (lw.attn_norm + off)[None, :]).to(self.dtype).contiguous()
             lw.fold_attn = True
         if "conv_in" not in lw.qlin and not lw.fold_attn and lw.conv_in is not None:
             lw.conv_in = (lw.conv_in.float() * (lw.attn_norm + off)[None, :]).to(self.dtype).contiguous()
@@ -365,8 +387,13 @@ def build_from_tensors(cfg: ModelConfig, get: Callable[[str], torch.Tensor], has
     for li in range(model.first_layer, model.last_layer):
         p = f"model.layers.{li}."
         bq = bk = bv = None
-        if cfg.layer_is_conv(li):
-            lw = _build_conv_layer(model, cfg, p, get, has, up)
+        if cfg.layer_is_conv(li) or cfg.layer_is_linear_attention(li):
+            if cfg.layer_is_conv(li):
+                lw = _build_conv_layer(model, cfg, p, get, has, up)
+            else:
+                from .qwen_next import build_linear_attention_layer
+
+                lw = build_linear_attention_layer(model, cfg, p, get, has, up)
             _build_ffn(model, cfg, li, p, lw, get, has, up, moe_factory)
             if quantizer is not None:
                 quantizer(model, li, lw)
@@ -387,15 +414,26 @@ def build_from_tensors(cfg: ModelConfig, get: Callable[[str], torch.Tensor], has
                 bq, bk, bv = fb[:qn], fb[qn:qn + kn], fb[qn + kn:qn + 2 * kn]
         else:
             wq, wk, wv, wo = (get(p + f"self_attn.{n}_proj.weight") for n in "qkvo")
+        w_gate = None
+        if cfg.attn_output_gate:
+            # q_proj rows are [query (D) | gate (D)] per head: the gate block moves behind q, k and v
+            if tp > 1:
+                raise NotImplementedError("tensor parallelism over gated attention is not implemented")
+            two = wq.view(cfg.num_attention_heads, 2 * cfg.head_dim, wq.shape[1])
+            wq = two[:, :cfg.head_dim].reshape(cfg.num_attention_heads * cfg.head_dim, -1)
+            w_gate = two[:, cfg.head_dim:].reshape(cfg.num_attention_heads * cfg.head_dim, -1)
         if has(p + "self_attn.q_proj.bias"):
             bq, bk, bv = (get(p + f"self_attn.{n}_proj.bias") for n in "qkv")
         wqkv, wo_l, bqkv = shard_attention(cfg, par, wq, wk, wv, wo, bq, bk, bv)
+        if w_gate is not None:
+            wqkv = torch.cat((wqkv, w_gate), 0)
         lw = LayerWeights(
             attn_norm=up(get(p + "input_layernorm.weight"), torch.float32),
             wqkv=up(wqkv), wo=up(wo_l),
             ffn_norm=up(get(p + "post_attention_layernorm.weight"), torch.float32),
             bqkv=up(bqkv) if bqkv is not None else None,
         )
+        lw.attn_gate = w_gate is not None
         if has(p + "self_attn.o_proj.bias"):
             lw.bo = up(get(p + "self_attn.o_proj.bias"))
         if cfg.qk_norm and has(p + "self_attn.q_norm.weight"):
@@ -484,6 +522,12 @@ def random_state(cfg: ModelConfig, seed: int = 0, std: float = 0.02, dtype=torch
         p = f"model.layers.{li}."
         ones(p + "input_layernorm.weight", H)
         ones(p + "post_attention_layernorm.weight", H)
+        if cfg.layer_is_linear_attention(li):
+            from .qwen_next import random_linear_attention_state
+
+            random_linear_attention_state(cfg, p, mat, out, std)
+            _random_ffn(cfg, li, p, mat)
+            continue
         if cfg.layer_is_conv(li):
             mat(p + "conv.in_proj.weight", 3 * H, H)
             mat(p + "conv.conv.weight", H, 1, cfg.conv_l_cache)
@@ -495,7 +539,7 @@ def random_state(cfg: ModelConfig, seed: int = 0, std: float = 0.02, dtype=torch
                 mat(p + "conv.out_proj.bias", H)
             _random_ffn(cfg, li, p, mat)
             continue
-        mat(p + "self_attn.q_proj.weight", cfg.num_attention_heads * D, H)
+        mat(p + "self_attn.q_proj.weight", cfg.num_attention_heads * D * (2 if cfg.attn_output_gate else 1), H)
         mat(p + "self_attn.k_proj.weight", cfg.num_key_value_heads * D, H)
         mat(p + "self_attn.v_proj.weight", cfg.num_key_value_heads * D, H)
         mat(p + "self_attn.o_proj.weight", H, cfg.num_attention_heads * D)
@@ -514,6 +558,12 @@ def _random_ffn(cfg, li, p, mat) -> None:
     H = cfg.hidden_size
     if cfg.layer_is_moe(li):
         mat(p + "mlp.gate.weight", cfg.num_experts, H)
+        if cfg.shared_expert_intermediate_size > 0:
+            for n, shape in (("gate", (cfg.shared_expert_intermediate_size, H)), ("up", (cfg.shared_expert_intermediate_size, H)),
+                             ("down", (H, cfg.shared_expert_intermediate_size))):
+                mat(p + f"mlp.shared_expert.{n}_proj.weight", *shape)
+            if cfg.shared_expert_gate:
+                mat(p + "mlp.shared_expert_gate.weight", 1, H)
         if cfg.extra.get("use_expert_bias"):
             mat(p + "mlp.expert_bias", cfg.num_experts)
         for e in range(cfg.num_experts):

@@ -20,7 +20,8 @@ from ..ops import moe as moe_ops
 
 class MoEBlock:
     def __init__(self, cfg, router_w, w_gate_up, w_down, e0: int, n_experts: int, ep_ops=None, ep_size: int = 1,
-                 shared=None, router_bias=None, router_linear_bias=None, gu_bias=None, down_bias=None, act="swiglu"):
+                 shared=None, router_bias=None, router_linear_bias=None, gu_bias=None, down_bias=None, act="swiglu",
+                 shared_gate_w=None):
         self.cfg = cfg
         self.router_w = router_w          # [E, H]
         self.w_gate_up = w_gate_up        # [E_local, 2I, H]
@@ -30,6 +31,7 @@ class MoEBlock:
         self.ep_ops = ep_ops
         self.ep_size = ep_size
         self.shared = shared              # optional (w_gate_up [2Is, H], w_down [H, Is]) dense shared expert
+        self.shared_gate_w = shared_gate_w  # optional [1, H]: the shared expert's output is scaled by sigmoid(x . w)
         self.router_bias = router_bias                # selection-only bias (added to the scores used for top-k)
         self.router_linear_bias = router_linear_bias  # bias of the router projection itself (GPT-OSS)
         self.gu_bias = gu_bias                        # [E_local, 2I] per-expert bias, gate part then up part
@@ -39,10 +41,21 @@ class MoEBlock:
 
     def tensors(self):
         out = [self.router_w, self.w_gate_up, self.w_down]
-        out.extend(t for t in (self.router_bias, self.router_linear_bias, self.gu_bias, self.down_bias) if t is not None)
+        out.extend(t for t in (self.router_bias, self.router_linear_bias, self.gu_bias, self.down_bias, self.shared_gate_w)
+                   if t is not None)
         if self.shared is not None:
             out.extend(self.shared)
         return out
+
+    def _shared_out(self, x):
+        """Dense shared expert (None without one), scaled by its sigmoid gate when the family has it."""
+        if self.shared is None:
+            return None
+        sgu, sd = self.shared
+        y = ops.linear(ops.gated_linear(x, sgu, sgu.shape[0] // 2), sd)
+        if self.shared_gate_w is not None:
+            y = (y.float() * torch.sigmoid(x.float() @ self.shared_gate_w.float().t())).to(y.dtype)
+        return y
 
     def route(self, x):
         cfg = self.cfg
@@ -60,10 +73,7 @@ class MoEBlock:
         ids, w = moe_ops.route(logits.contiguous(), cfg.num_experts_per_tok, cfg.router_scoring, cfg.norm_topk_prob,
                                cfg.routed_scaling_factor, self.router_bias, cfg.n_group, cfg.topk_group)
         _, raw = moe_ops.route_ref(logits, cfg.num_experts_per_tok, cfg.router_scoring, False, 1.0, self.router_bias)
-        shared = None
-        if self.shared is not None:
-            sgu, sd = self.shared
-            shared = ops.linear(ops.gated_linear(x, sgu, sgu.shape[0] // 2), sd)
+        shared = self._shared_out(x)
         cache = getattr(self, "expert_cache", None)
         if cache is not None:
             local = cache.forward(x, ids, w, limit=cfg.swiglu_limit)
@@ -88,10 +98,7 @@ class MoEBlock:
         if cache is not None:
             # experts live in host memory behind a bounded device bank: route, then let the cache run the experts
             ids, w = self.route(x)
-            extra = None
-            if self.shared is not None:
-                sgu, sd = self.shared
-                extra = ops.linear(ops.gated_linear(x, sgu, sgu.shape[0] // 2), sd)
+            extra = self._shared_out(x)
             if self.ep_size == 1:
                 return cache.forward(x, ids, w, residual=residual, extra=extra, limit=self.cfg.swiglu_limit)
             partial = cache.forward(x, ids, w, extra=extra if self.e0 == 0 else None, limit=self.cfg.swiglu_limit)
@@ -107,10 +114,7 @@ class MoEBlock:
                                                          self.w_gate_up.shape[0])
         else:
             ids, w = self.route(x)
-        extra = None
-        if self.shared is not None:
-            sgu, sd = self.shared
-            extra = ops.linear(ops.gated_linear(x, sgu, sgu.shape[0] // 2), sd)
+        extra = self._shared_out(x)
         if self.ep_size == 1:
             return moe_ops.experts_forward(x, ids, w, self.w_gate_up, self.w_down, self.e0, residual=residual,
                                            extra=extra, limit=self.cfg.swiglu_limit, plan=plan, xp=xp, gu_bias=self.gu_bias,
@@ -173,7 +177,11 @@ def make_moe_factory(src=None, router_std_scale: bool = False):
         sel_bias = None
         if has(p + "expert_bias"):   # LFM2-MoE: added to the scores for the selection only
             sel_bias = get(p + "expert_bias").to(device=dev, dtype=torch.float32).contiguous()
-        block = MoEBlock(cfg, router, gu, dn, e0, cfg.num_experts, ep_size=par.ep_size, shared=shared, router_bias=sel_bias)
+        shared_gate = None
+        if has(p + "shared_expert_gate.weight"):
+            shared_gate = get(p + "shared_expert_gate.weight").to(device=dev, dtype=dt).contiguous()
+        block = MoEBlock(cfg, router, gu, dn, e0, cfg.num_experts, ep_size=par.ep_size, shared=shared, router_bias=sel_bias,
+                         shared_gate_w=shared_gate)
         block._model = model
         block.layer_index = li
         return block

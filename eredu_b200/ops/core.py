@@ -167,7 +167,7 @@ def rope_kv_ref(qkv, positions, slots, inv_freq, k_cache, v_cache, n_q, n_kv, he
 def rope_kv(qkv, positions, slots, inv_freq, k_cache, v_cache, n_q, n_kv, head_dim, rot=None, interleaved=False,
             attn_factor=1.0, q_norm_w=None, k_norm_w=None, norm_eps=1e-6, norm_w_off=0.0, q_out=None):
     """Per-head q/k norm (optional) + RoPE on q and k, K/V scattered into their cache pages. Returns q [M,n_q,D]."""
-    if not qkv.is_cuda:
+    if not qkv.is_cuda or head_dim not in KERNEL_HEAD_DIMS:
         return rope_kv_ref(qkv, positions, slots, inv_freq, k_cache, v_cache, n_q, n_kv, head_dim, rot, interleaved,
                            attn_factor, q_norm_w, k_norm_w, norm_eps, norm_w_off)
     M = qkv.shape[0]
@@ -180,6 +180,11 @@ def rope_kv(qkv, positions, slots, inv_freq, k_cache, v_cache, n_q, n_kv, head_d
                                1 if interleaved else 0, attn_factor, norm_eps, norm_w_off, stream_ptr(qkv.device))
     check(code, "eredu_rope_kv")
     return q_out
+
+
+# Head sizes the attention and RoPE kernels are instantiated for; other sizes (256 in the Qwen3-Next family) run through
+# the tensor-operation references on either device, which read lengths on the host: such models decode eagerly.
+KERNEL_HEAD_DIMS = (64, 128)
 
 
 # ------------------------------------------------------------------------------------------ attention
@@ -221,7 +226,7 @@ def attention_ref(q, k_cache, v_cache, block_table, seq_lens, q_lens, scale, win
 
 def attention_prefill(q, k_cache, v_cache, block_table, seq_lens, cu_q, max_q_len, scale, window=0, sinks=None,
                       out=None):
-    if not q.is_cuda:
+    if not q.is_cuda or q.shape[2] not in KERNEL_HEAD_DIMS:
         q_lens = (cu_q[1:] - cu_q[:-1]).tolist()
         return attention_ref(q, k_cache, v_cache, block_table, seq_lens, q_lens, scale, window, sinks)
     assert q.dtype == torch.bfloat16 and q.is_contiguous()
@@ -254,7 +259,7 @@ def attention_decode(q, k_cache, v_cache, block_table, seq_lens, q_per_seq, scal
                      scratch=None, out=None):
     """q: [B * q_per_seq, n_q, D]. ``scratch`` = (part_o, part_ml, counters) from :func:`decode_scratch` when
     splits > 1 (fp32 partials and zeroed int32 arrival tickets)."""
-    if not q.is_cuda:
+    if not q.is_cuda or q.shape[2] not in KERNEL_HEAD_DIMS:
         return attention_ref(q, k_cache, v_cache, block_table, seq_lens, [q_per_seq] * seq_lens.shape[0], scale,
                              window, sinks)
     assert q.dtype == torch.bfloat16 and q.is_contiguous()

@@ -59,10 +59,18 @@ class Engine:
         conv_layers = [li for li in local if self.cfg.layer_is_conv(li)]
         self.kv = PagedKVCache(model.num_local_layers(), model.n_kv_local, self.cfg.head_dim, num_pages, model.dtype,
                                self.device, first_layer=model.first_layer,
-                               attention_layers=[li for li in local if not self.cfg.layer_is_conv(li)],
+                               attention_layers=[li for li in local if not (self.cfg.layer_is_conv(li)
+                                                                            or self.cfg.layer_is_linear_attention(li))],
                                conv_layers=conv_layers,
                                conv_channels=self.cfg.hidden_size // model.par.tp_size if conv_layers else 0,
                                conv_hist=self.cfg.conv_l_cache - 1)
+        la_layers = [li for li in local if self.cfg.layer_is_linear_attention(li)]
+        if la_layers:
+            c = self.cfg
+            self.kv.enable_linear_attention_state(
+                la_layers, slots=max(2 * max_batch, 8), conv_hist=c.linear_conv_kernel_dim - 1,
+                conv_channels=2 * c.linear_num_key_heads * c.linear_key_head_dim + c.linear_num_value_heads * c.linear_value_head_dim,
+                heads=c.linear_num_value_heads, dk=c.linear_key_head_dim, dv=c.linear_value_head_dim)
         self.cuda = self.device.type == "cuda"
         self.use_graph = self.cuda if use_cuda_graph is None else (use_cuda_graph and self.cuda)
         self.prefill_chunk = prefill_chunk
@@ -85,10 +93,18 @@ class Engine:
         # Reserve every page the request can need up front: the block table is then static for the
         # whole decode and the captured graph never needs a host update.
         seq.pages = list(self.kv.allocator.alloc(PagedKVCache.pages_for(len(seq.prompt) + max_new_tokens)))
+        if self.kv.page_to_slot is not None:
+            try:
+                self.kv.bind_state(seq.pages[0])
+            except RuntimeError:
+                self.kv.allocator.release(seq.pages)
+                seq.pages = []
+                raise
         return seq
 
     def release(self, seq: Sequence) -> None:
         if seq.pages:
+            self.kv.unbind_state(seq.pages[0])
             self.kv.allocator.release(seq.pages)
             seq.pages = []
 
@@ -385,6 +401,8 @@ class Engine:
     def _host_driven(self) -> bool:
         """True when a forward pass needs the host between kernels (layerwise host residency, expert cache)."""
         m = self.model
+        if self.cfg.head_dim not in (64, 128):
+            return True    # no attention kernel for this head size: the tensor-operation path reads lengths on the host
         if getattr(m, "residency", None) is not None or getattr(getattr(m, "inner", m), "observer", None) is not None:
             return True
         return any(getattr(getattr(lw, "moe", None), "expert_cache", None) is not None for lw in getattr(m, "layers", []))

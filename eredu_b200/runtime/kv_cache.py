@@ -61,6 +61,62 @@ class PagedKVCache:
             self.allocator = _eredu_host.BlockManager(num_pages)
         except Exception:
             self.allocator = PageAllocator(num_pages)
+        # Recurrent state of gated-delta layers: too large to keep per page, so sequences get a compact state slot and
+        # `page_to_slot` (indexed by a sequence's first page, read on the device) finds it.
+        self.la_conv_state = self.la_rec_state = self.page_to_slot = None
+        self._la_index: dict = {}
+        self._free_state_slots: list[int] = []
+
+    def enable_linear_attention_state(self, layers, slots: int, conv_hist: int, conv_channels: int, heads: int, dk: int, dv: int):
+        dev, dt = self.k.device, self.k.dtype
+        self._la_index = {li: i for i, li in enumerate(layers)}
+        n = len(self._la_index)
+        self.la_conv_state = torch.zeros((n, slots, conv_hist, conv_channels), dtype=dt, device=dev)
+        self.la_rec_state = torch.zeros((n, slots, heads, dk, dv), dtype=torch.float32, device=dev)
+        self.page_to_slot = torch.zeros(self.num_pages, dtype=torch.int32, device=dev)
+        self._free_state_slots = list(range(slots - 1, -1, -1))
+        self._slot_of_page: dict = {}
+
+    def bind_state(self, first_page: int) -> int:
+        """Give the sequence that starts at ``first_page`` a zeroed state slot."""
+        if self.page_to_slot is None:
+            return -1
+        if not self._free_state_slots:
+            raise RuntimeError("KV pool exhausted (no free recurrent-state slot)")
+        slot = self._free_state_slots.pop()
+        self._slot_of_page[int(first_page)] = slot
+        self.page_to_slot[int(first_page)] = slot
+        self.la_conv_state[:, slot].zero_()
+        self.la_rec_state[:, slot].zero_()
+        return slot
+
+    def unbind_state(self, first_page: int) -> None:
+        if self.page_to_slot is None:
+            return
+        slot = self._slot_of_page.pop(int(first_page), None)
+        if slot is not None:
+            self._free_state_slots.append(slot)
+
+    def detach_state(self, first_page: int) -> int:
+        """The sequence gives its pages up but keeps its state slot (parked in a host tier). Returns the slot or -1."""
+        if self.page_to_slot is None:
+            return -1
+        return self._slot_of_page.pop(int(first_page), -1)
+
+    def attach_state(self, slot: int, first_page: int) -> None:
+        """A detached slot follows the sequence's new first page."""
+        if self.page_to_slot is None or slot < 0:
+            return
+        self._slot_of_page[int(first_page)] = slot
+        self.page_to_slot[int(first_page)] = slot
+
+    def free_state_slot(self, slot: int) -> None:
+        if self.page_to_slot is not None and slot >= 0:
+            self._free_state_slots.append(slot)
+
+    def linear_attention_state(self, li: int):
+        i = self._la_index[li]
+        return self.la_conv_state[i], self.la_rec_state[i]
 
     def layer(self, li: int):
         i = self._kv_index[li]
@@ -71,6 +127,8 @@ class PagedKVCache:
 
     def bytes(self) -> int:
         extra = self.conv_state.numel() * self.conv_state.element_size() if self.conv_state is not None else 0
+        if self.la_rec_state is not None:
+            extra += self.la_rec_state.numel() * 4 + self.la_conv_state.numel() * self.la_conv_state.element_size()
         return 2 * self.k.numel() * self.k.element_size() + extra
 
     @staticmethod

@@ -38,6 +38,7 @@ class ParkedSequence:
     reserved_pages: int                  # pages the sequence had reserved (prompt + budget), restored on resume
     event: object = None                 # transfer completion (CUDA event) or None
     conv_state: object = None            # hybrid models: the short-convolution state of every conv layer [layers, hist, C]
+    state_slot: int = -1                 # gated-delta models: the recurrent-state slot the sequence keeps while parked
 
 
 class KVHostTier:
@@ -112,7 +113,8 @@ class KVHostTier:
         conv = None
         if self.kv.conv_state is not None and seq.pages:
             conv = self.kv.conv_state[:, seq.pages[0]].to("cpu")   # the state is named by the sequence's first page
-        self.parked[seq.seq_id] = ParkedSequence(k_host, v_host, used, len(seq.pages), event, conv)
+        self.parked[seq.seq_id] = ParkedSequence(k_host, v_host, used, len(seq.pages), event, conv,
+                                                 self.kv.detach_state(seq.pages[0]) if seq.pages else -1)
         self.engine.kv.allocator.release(seq.pages)
         seq.pages = []
         self.host_bytes += nbytes
@@ -150,6 +152,7 @@ class KVHostTier:
             self.kv.v.index_copy_(1, idx, v_dev)
         if p.conv_state is not None:
             self.kv.conv_state[:, pages[0]] = p.conv_state.to(dev)
+        self.kv.attach_state(p.state_slot, pages[0])         # gated-delta state stayed in its slot while parked
         seq.pages = pages
         nbytes = p.pages * self.page_bytes()
         self.host_bytes -= nbytes
@@ -164,6 +167,7 @@ class KVHostTier:
         p = self.parked.pop(seq.seq_id, None)
         if p is not None:
             self.host_bytes -= p.pages * self.page_bytes()
+            self.kv.free_state_slot(p.state_slot)
 
     def report(self) -> dict:
         return dict(self.stats, parked_now=len(self.parked), host_bytes=self.host_bytes,

@@ -21,7 +21,7 @@ from ..models.config import DENSE_TYPES, MOE_TYPES, ModelConfig
 
 EXECUTION_PLAN_SCHEMA_VERSION = 2
 DEFAULT_MAX_MAPPED_SHARDS = 4
-SUPPORTED_TYPES = DENSE_TYPES | {"qwen3_moe", "mixtral", "gpt_oss"}
+SUPPORTED_TYPES = DENSE_TYPES | {"qwen3_moe", "mixtral", "gpt_oss", "lfm2_moe", "qwen3_next", "qwen3_5_moe"}
 
 
 # ---------------------------------------------------------------------------------------------- inspection
@@ -146,13 +146,25 @@ class ModelResourceProfile:
     sliding_window: int = 0
     expert_bytes: int = 0             # part of weight_bytes that belongs to routed experts
     workspace_bytes: int = 2 << 30    # activations, logits, collective buffers, allocator slack
+    state_bytes_per_sequence: int = 0  # hybrid models: fixed recurrent / convolution state of one sequence
 
 
 def estimate_runtime_state(cfg: ModelConfig, weight_bytes: Optional[int] = None, cache_dtype_bytes: int = 2) -> ModelResourceProfile:
     """KV bytes per token and static weight bytes of a decoder (``estimate_runtime_state``, capability.rs)."""
     H, D = cfg.hidden_size, cfg.head_dim
     L = cfg.num_hidden_layers
-    kv_tok = 2 * cfg.num_key_value_heads * D * cache_dtype_bytes * L
+    # only softmax-attention layers keep K/V per token; convolution and gated-delta layers keep a fixed state
+    stateful = [li for li in range(L) if cfg.layer_is_conv(li) or cfg.layer_is_linear_attention(li)]
+    attn_layers = L - len(stateful)
+    kv_tok = 2 * cfg.num_key_value_heads * D * cache_dtype_bytes * attn_layers
+    state = 0
+    for li in stateful:
+        if cfg.layer_is_conv(li):
+            state += (cfg.conv_l_cache - 1) * H * cache_dtype_bytes
+        else:
+            conv_dim = 2 * cfg.linear_num_key_heads * cfg.linear_key_head_dim + cfg.linear_num_value_heads * cfg.linear_value_head_dim
+            state += (cfg.linear_conv_kernel_dim - 1) * conv_dim * cache_dtype_bytes
+            state += cfg.linear_num_value_heads * cfg.linear_key_head_dim * cfg.linear_value_head_dim * 4
     attn = (cfg.num_attention_heads * D * H) * 2 + (cfg.num_key_value_heads * D * H) * 2
     dense_mlp = 3 * H * cfg.intermediate_size
     expert = 3 * H * cfg.moe_intermediate_size * cfg.num_experts if cfg.is_moe else 0
@@ -162,7 +174,8 @@ def estimate_runtime_state(cfg: ModelConfig, weight_bytes: Optional[int] = None,
     wb = weight_bytes if weight_bytes is not None else params * 2
     sliding = sum(1 for li in range(L) if cfg.layer_window(li) > 0)
     share = (moe_layers * expert) / max(1, params)
-    return ModelResourceProfile(int(wb), int(kv_tok), L, sliding, int(cfg.sliding_window or 0), int(wb * share))
+    return ModelResourceProfile(int(wb), int(kv_tok), max(1, attn_layers), sliding, int(cfg.sliding_window or 0),
+                                int(wb * share), state_bytes_per_sequence=int(state))
 
 
 def kv_bytes_for(profile: ModelResourceProfile, context: int, batch: int) -> int:
@@ -170,7 +183,7 @@ def kv_bytes_for(profile: ModelResourceProfile, context: int, batch: int) -> int
     per_layer = profile.kv_bytes_per_token // max(1, profile.layers)
     full = profile.layers - profile.sliding_layers
     tokens_sliding = min(context, profile.sliding_window) if profile.sliding_window else context
-    return batch * per_layer * (full * context + profile.sliding_layers * tokens_sliding)
+    return batch * (per_layer * (full * context + profile.sliding_layers * tokens_sliding) + profile.state_bytes_per_sequence)
 
 
 @dataclass

@@ -37,6 +37,10 @@ def forward_logits(cfg, sd, tokens, moe_fn=None):
     for li in range(cfg.num_hidden_layers):
         p = f"model.layers.{li}."
         x = rms(h, sd[p + "input_layernorm.weight"], cfg.rms_norm_eps, cfg.norm_weight_offset)
+        if cfg.layer_is_linear_attention(li):
+            h = h + _gated_delta_layer(cfg, sd, p + "linear_attn.", x)
+            h = _ffn(cfg, sd, li, p, h, moe_fn)
+            continue
         if cfg.layer_is_conv(li):
             # LFM2 gated short convolution: causal depthwise conv1d over B * X, gated by C
             Cc = cfg.hidden_size
@@ -48,12 +52,17 @@ def forward_logits(cfg, sd, tokens, moe_fn=None):
             h = h + F.linear(pj[:, Cc:2 * Cc] * y, sd[p + "conv.out_proj.weight"], sd.get(p + "conv.out_proj.bias"))
             h = _ffn(cfg, sd, li, p, h, moe_fn)
             continue
-        q = F.linear(x, sd[p + "self_attn.q_proj.weight"], sd.get(p + "self_attn.q_proj.bias")).view(T, Hq, D)
+        gate = None
+        if cfg.attn_output_gate:
+            qg = F.linear(x, sd[p + "self_attn.q_proj.weight"]).view(T, Hq, 2 * D)
+            q, gate = qg[..., :D], qg[..., D:].reshape(T, Hq * D)
+        else:
+            q = F.linear(x, sd[p + "self_attn.q_proj.weight"], sd.get(p + "self_attn.q_proj.bias")).view(T, Hq, D)
         k = F.linear(x, sd[p + "self_attn.k_proj.weight"], sd.get(p + "self_attn.k_proj.bias")).view(T, Hkv, D)
         v = F.linear(x, sd[p + "self_attn.v_proj.weight"], sd.get(p + "self_attn.v_proj.bias")).view(T, Hkv, D)
         if p + "self_attn.q_norm.weight" in sd:
-            q = rms(q, sd[p + "self_attn.q_norm.weight"], cfg.rms_norm_eps)
-            k = rms(k, sd[p + "self_attn.k_norm.weight"], cfg.rms_norm_eps)
+            q = rms(q, sd[p + "self_attn.q_norm.weight"], cfg.rms_norm_eps, cfg.norm_weight_offset)
+            k = rms(k, sd[p + "self_attn.k_norm.weight"], cfg.rms_norm_eps, cfg.norm_weight_offset)
         q = rope(q, pos, inv, factor, cfg.rope_traditional, cfg.rotary_dim)
         k = rope(k, pos, inv, factor, cfg.rope_traditional, cfg.rotary_dim)
         g = Hq // Hkv
@@ -70,11 +79,43 @@ def forward_logits(cfg, sd, tokens, moe_fn=None):
         else:
             probs = torch.softmax(s, -1)
         a = torch.einsum("hqk,khd->qhd", probs, v).reshape(T, Hq * D)
+        if gate is not None:
+            a = a * torch.sigmoid(gate)
         h = h + F.linear(a, sd[p + "self_attn.o_proj.weight"], sd.get(p + "self_attn.o_proj.bias"))
         h = _ffn(cfg, sd, li, p, h, moe_fn)
     x = rms(h, sd["model.norm.weight"], cfg.rms_norm_eps, cfg.norm_weight_offset)
     head = sd.get("lm_head.weight", sd["model.embed_tokens.weight"])
     return F.linear(x, head)
+
+
+def _gated_delta_layer(cfg, sd, la, x):
+    """Qwen3-Next gated delta network over a whole sequence, written token by token."""
+    T = x.shape[0]
+    Hk, Hv, dk, dv = cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
+    K = cfg.linear_conv_kernel_dim
+    qkv = F.linear(x, sd[la + "in_proj_qkv.weight"])
+    z = F.linear(x, sd[la + "in_proj_z.weight"]).view(T, Hv, dv)
+    beta = torch.sigmoid(F.linear(x, sd[la + "in_proj_b.weight"]))
+    a = F.linear(x, sd[la + "in_proj_a.weight"])
+    C = qkv.shape[1]
+    conv = F.conv1d(F.pad(qkv.t()[None], (K - 1, 0)), sd[la + "conv1d.weight"].view(C, 1, K), groups=C)[0].t()
+    qkv = F.silu(conv)
+    q, k, v = qkv[:, :Hk * dk].view(T, Hk, dk), qkv[:, Hk * dk:2 * Hk * dk].view(T, Hk, dk), qkv[:, 2 * Hk * dk:].view(T, Hv, dv)
+    l2 = lambda t: t / torch.sqrt(t.pow(2).sum(-1, keepdim=True) + 1e-6)       # noqa: E731
+    q, k = l2(q) / math.sqrt(dk), l2(k)
+    r = Hv // Hk
+    q, k = q.repeat_interleave(r, 1), k.repeat_interleave(r, 1)
+    g = -torch.exp(sd[la + "A_log"]) * F.softplus(a + sd[la + "dt_bias"])
+    S = torch.zeros(Hv, dk, dv)
+    outs = []
+    for t in range(T):
+        S = S * torch.exp(g[t])[:, None, None]
+        mem = torch.einsum("hkv,hk->hv", S, k[t])
+        S = S + torch.einsum("hk,hv->hkv", k[t], (v[t] - mem) * beta[t][:, None])
+        outs.append(torch.einsum("hkv,hk->hv", S, q[t]))
+    o = torch.stack(outs)                                                     # [T, Hv, dv]
+    o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + cfg.rms_norm_eps) * sd[la + "norm.weight"]
+    return F.linear((o * F.silu(z)).reshape(T, Hv * dv), sd[la + "out_proj.weight"])
 
 
 def _ffn(cfg, sd, li, p, h, moe_fn):

@@ -71,3 +71,29 @@ def test_planner_choices():
     assert again.topology == p70.topology
     with pytest.raises(ValueError):
         P.ExecutionPlan.from_json(p70.to_json().replace('"schema_version": 2', '"schema_version": 1'))
+
+
+def test_hybrid_models_are_inspectable_and_sized_by_their_attention_layers(tmp_path):
+    import json
+
+    from eredu_b200.models.config import ModelConfig
+    from eredu_b200.runtime.plan import estimate_runtime_state, inspect_artifact, kv_bytes_for
+
+    d = {"model_type": "qwen3_next", "vocab_size": 1000, "hidden_size": 256, "num_hidden_layers": 8, "num_attention_heads": 4,
+         "num_key_value_heads": 2, "head_dim": 128, "linear_num_key_heads": 2, "linear_num_value_heads": 4,
+         "linear_key_head_dim": 64, "linear_value_head_dim": 64, "num_experts": 8, "num_experts_per_tok": 2,
+         "moe_intermediate_size": 64, "shared_expert_intermediate_size": 64}
+    cfg = ModelConfig.from_hf_dict(d)
+    prof = estimate_runtime_state(cfg)
+    assert prof.kv_bytes_per_token == 2 * 2 * 128 * 2 * 2               # two full-attention layers of eight
+    conv_dim = 2 * 2 * 64 + 4 * 64
+    assert prof.state_bytes_per_sequence == 6 * (3 * conv_dim * 2 + 4 * 64 * 64 * 4)
+    assert kv_bytes_for(prof, 100, 3) == 3 * (prof.kv_bytes_per_token * 100 + prof.state_bytes_per_sequence)
+    (tmp_path / "config.json").write_text(json.dumps(d))
+    rep = inspect_artifact(tmp_path)
+    assert all(i.code != "unsupported_architecture" for i in rep.issues)
+    lf = ModelConfig.from_hf_dict({"model_type": "lfm2", "vocab_size": 100, "hidden_size": 64, "intermediate_size": 128,
+                                   "num_hidden_layers": 3, "num_attention_heads": 2, "num_key_value_heads": 2,
+                                   "layer_types": ["conv", "full_attention", "conv"]})
+    p2 = estimate_runtime_state(lf)
+    assert p2.kv_bytes_per_token == 2 * 2 * 32 * 2 and p2.state_bytes_per_sequence == 2 * 2 * 64 * 2
