@@ -14,7 +14,7 @@ def pytest_configure(config):
 # GPU tests of these files were written after the last hardware run of the suite: they are collected after the files
 # whose GPU tests have already passed on a B200, so that `-x` stopping at a failure among them cannot hide the rest.
 _RUN_LAST = ("test_fp8.py", "test_lfm2.py", "test_gpt_oss.py", "test_expert_cache.py", "test_kv_residency.py",
-             "test_weight_residency.py", "test_recurrent.py")
+             "test_weight_residency.py", "test_recurrent.py", "test_qwen_next.py")
 
 
 def pytest_collection_modifyitems(config, items):

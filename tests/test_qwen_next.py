@@ -134,3 +134,26 @@ def test_guards():
     for s in seqs:
         eng.release(s)
     eng.release(eng.new_sequence([1, 2, 3], max_new_tokens=2))
+
+
+@pytest.mark.gpu
+def test_qwen_next_on_gpu_matches_cpu_oracle():
+    cfg = next_cfg(hidden_size=256, head_dim=64, linear_key_head_dim=64, linear_value_head_dim=64, vocab_size=512,
+                   moe_intermediate_size=64, shared_expert_intermediate_size=64)
+    sd = state_for(cfg, seed=4)
+    sd = {k: v * (0.6 if v.dim() == 2 else 1.0) for k, v in sd.items()}
+    model = build_from_tensors(cfg, lambda n: sd[n], sd.__contains__, "cuda", torch.bfloat16, moe_factory=make_moe_factory())
+    eng = Engine(model, max_batch=4, max_seq_len=128)
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 40, 21)]
+    seqs = [eng.new_sequence(p, max_new_tokens=8) for p in prompts]
+    logits = eng.prefill_logits(seqs)
+    for p, lg in zip(prompts, logits):
+        ref = forward_logits(cfg, sd, p, moe_fn=moe_oracle)[-1]
+        assert torch.nn.functional.cosine_similarity(lg.float().cpu(), ref, dim=0) > 0.99
+    for s in seqs:
+        eng.release(s)
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0), max_new_tokens=6)      # CUDA-graph decode
+    assert all(len(o) == 6 for o in outs)
+    from eredu_b200.ops import native
+    native.check_status(torch.device("cuda", torch.cuda.current_device()))
