@@ -245,6 +245,13 @@ class LoadedModel:
                 return FinishReason.CANCELLED
             return None
 
+        if (constraint is None and not raw and prepared.tools and plan is not None and plan.dialect == "generic"
+                and plan.tool_open and prepared.tool_choice.mode in ("auto", "required")):
+            # declared tools: calls are grammar-constrained to a declared name and its parameter schema
+            from ..text.tool_constraints import constraint_for_tools
+
+            constraint = constraint_for_tools(self.tokenizer, prepared.tools, prepared.tool_choice.mode,
+                                              prepared.tool_choice.max_parallel_calls, plan.tool_open, plan.tool_close)
         if mirostat is not None or constraint is not None:
             from ..ops.controlled import controlled_generate
 
