@@ -241,6 +241,20 @@ def main(argv=None) -> int:
         print(f"[eredu] load {load_time:.3f}s  generation {timing['generation_time']:.3f}s  TTFT "
               f"{timing['time_to_first_token']:.3f}s  decode {timing['decode_token_rate']:.2f} tok/s  total "
               f"{timing['token_rate']:.2f} tok/s  stop={res['finish_reason']}", file=sys.stderr)
+    components = None
+    if a.profile_components:
+        from ..runtime.inspection import ComponentProfiler, observed
+
+        prof = ComponentProfiler(lm.model.device)
+        ids = lm.tokenizer.encode(prepared.prompt) if lm.tokenizer is not None else [0]
+        with observed(lm.model, prof):
+            prof.start()
+            lm.prefill_logits(ids)
+            prof.finish()
+        components = prof.summary()
+        print("[eredu] prefill components (eager pass over the prompt):", file=sys.stderr)
+        for st in components["stages"]:
+            print(f"[eredu]   {st['name']:<28} {st['seconds'] * 1e3:9.3f} ms  {st['share'] * 100:5.1f} %", file=sys.stderr)
     if a.telemetry_json:
         tel = ExecutionTelemetry(plan={"device": device, "auto": None if a.no_auto else a.auto, "quantization": vars(quant) if quant else None,
                                        "execution_plan": json.loads(plan.to_json()) if plan is not None else None,
@@ -248,6 +262,8 @@ def main(argv=None) -> int:
                                  hardware=hardware_profile(device), prompt_tokens=res["prompt_tokens"],
                                  generated_tokens=len(res["tokens"]), stop_reason=res["finish_reason"], timing=timing,
                                  weights_bytes=lm.model.weight_bytes(), kv_bytes=lm.engine.kv.bytes())
+        if components is not None:
+            tel.counters["components"] = components
         if draft is not None:
             tel.plan["speculative"] = getattr(lm, "last_speculative_stats", None)
         if a.expert_cache_benchmark or a.expert_cache:

@@ -70,3 +70,40 @@ class observed:
 
     def __exit__(self, *exc):
         self.model.observer = self.prev
+
+
+class ComponentProfiler(ActivationObserver):
+    """Wall time between consecutive observation points of an observed pass: embedding, every block, and (via
+    :meth:`finish`) the output head. CUDA work is synchronised at each point, so the figures are per-component device
+    times of an eager pass, not of the graph-replayed decode step (``--profile-components``)."""
+
+    def __init__(self, device=None):
+        import time
+
+        self._now = time.perf_counter
+        self.device = device
+        self.stages: list[tuple[str, float]] = []
+        self._t = None
+
+    def _sync(self):
+        if self.device is not None and torch.device(self.device).type == "cuda":
+            torch.cuda.synchronize(self.device)
+
+    def start(self):
+        self._sync()
+        self._t = self._now()
+
+    def observe(self, name, value):
+        self._sync()
+        t = self._now()
+        if self._t is not None:
+            self.stages.append((name, t - self._t))
+        self._t = t
+
+    def finish(self, name="lm_head"):
+        self.observe(name, None)
+
+    def summary(self) -> dict:
+        total = sum(d for _, d in self.stages) or 1e-12
+        return {"total_seconds": total,
+                "stages": [{"name": n, "seconds": d, "share": d / total} for n, d in self.stages]}

@@ -122,3 +122,22 @@ def test_cli_draft_model_gives_the_same_text(tmp_path, capsys):
     assert spec["rounds"] > 0 and spec["proposed"] >= spec["accepted"]
     with pytest.raises(SystemExit):
         main(base + ["--draft-model", str(drf), "--mirostat-v2", "-t", "0.7"])
+
+
+def test_cli_profile_components(tmp_path, capsys):
+    from eredu_b200.formats import checkpoint as ck
+    from eredu_b200.models import config as C
+    from eredu_b200.models.llama import random_state
+
+    b = make_bundle(tmp_path)
+    cfg = dataclasses.replace(C.tiny_llama(), vocab_size=b.vocab_size(), eos_token_id=b.eos_ids[0], num_hidden_layers=3)
+    ck.save_safetensors_checkpoint(tmp_path, cfg, random_state(cfg, seed=0, std=0.05), torch.float32)
+    tel = tmp_path / "t.json"
+    assert main(["-m", str(tmp_path), "hello", "--device", "cpu", "--no-auto", "-n", "3", "--profile-components",
+                 "--telemetry-json", str(tel)]) == 0
+    err = capsys.readouterr().err
+    assert "model.layers.2.output" in err and "lm_head" in err
+    comp = json.loads(tel.read_text())["counters"]["components"]
+    names = [s["name"] for s in comp["stages"]]
+    assert names == ["model.embed_tokens", "model.layers.0.output", "model.layers.1.output", "model.layers.2.output", "lm_head"]
+    assert abs(sum(s["share"] for s in comp["stages"]) - 1.0) < 1e-6
