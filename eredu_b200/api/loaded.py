@@ -228,6 +228,7 @@ class LoadedModel:
         show_special = bool(plan is not None and plan.render_special_tokens)
         pipe = pipeline_for(plan)(TextDecoder(self.tokenizer, skip_special_tokens=not show_special), plan, prepared.stop,
                                   on_event, prepared.tool_choice.max_parallel_calls)
+        pipe.tools = prepared.tools           # parameter types of tagged-syntax calls come from the declarations
         t0 = time.perf_counter()
         first_token_at = [None]
         tokens: list[int] = []

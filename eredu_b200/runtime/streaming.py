@@ -176,6 +176,10 @@ class CommittedTokenPipeline:
             self._tool_fragment(text, out)
 
     def _tool_fragment(self, text: str, out: list):
+        if self.tool_json.text.lstrip().startswith("<") or (not self.tool_json.text.strip() and text.lstrip().startswith("<")):
+            self.tool_json.text += text        # tagged syntax: not JSON, collected verbatim until the closing tag
+            self._emit(SemanticEvent("tool_call_arguments", text, tool_index=self.tool_count - 1), out)
+            return
         value = self.tool_json.push(text)
         self._emit(SemanticEvent("tool_call_arguments", text, tool_index=self.tool_count - 1), out)
         if value is not None and self.plan.tool_close is None:
@@ -184,6 +188,20 @@ class CommittedTokenPipeline:
     def _close_tool(self, out: list):
         raw = self.tool_json.text.strip()
         name, args = None, None
+        if raw.startswith("<function="):
+            # Qwen tagged-parameter syntax: <function=NAME><parameter=KEY>VALUE</parameter>...</function>
+            from ..text.dialects import parse_tagged_call
+
+            try:
+                call = parse_tagged_call(raw, getattr(self, "tools", None))[0]
+                name, args = call["name"], call["arguments"]
+            except ValueError:
+                pass
+            self.tool_calls.append({"name": name, "arguments": args, "raw": raw})
+            self._emit(SemanticEvent("tool_call_end", tool_name=name, tool_index=self.tool_count - 1, arguments=args), out)
+            self.state = "text"
+            self._retarget()
+            return
         try:
             obj = json.loads(raw)
             if isinstance(obj, list) and obj:

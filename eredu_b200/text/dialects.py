@@ -68,6 +68,45 @@ def parse_python_calls(text: str) -> list[dict]:
     return calls
 
 
+_FUNCTION = re.compile(r"<function=([^>\s]+)>(.*?)(?:</function>|\Z)", re.S)
+_PARAMETER = re.compile(r"<parameter=([^>\s]+)>\n?(.*?)\n?</parameter>", re.S)
+
+
+def parse_tagged_call(raw: str, tools=None) -> list[dict]:
+    """Qwen tagged-parameter syntax inside a tool-call block::
+
+        <function=NAME>
+        <parameter=KEY>
+        VALUE
+        </parameter>
+        </function>
+
+    Values are text; a declared parameter of type integer / number / boolean / object / array / null (or a value
+    that only parses as JSON when no schema is known) is converted, strings stay as written."""
+    schemas = {}
+    for t in tools or []:
+        f = t.get("function", t)
+        schemas[f.get("name")] = (f.get("parameters") or {}).get("properties", {})
+    calls = []
+    for name, body in _FUNCTION.findall(raw):
+        props = schemas.get(name, {})
+        args = {}
+        for key, val in _PARAMETER.findall(body):
+            kind = (props.get(key) or {}).get("type")
+            if kind == "string":
+                args[key] = val
+                continue
+            try:
+                parsed = json.loads(val)
+            except json.JSONDecodeError:
+                parsed = val
+            args[key] = val if (kind is None and isinstance(parsed, str)) else parsed
+        calls.append({"name": name, "arguments": args})
+    if not calls:
+        raise ValueError("no <function=...> block found")
+    return calls
+
+
 class Lfm2Pipeline(CommittedTokenPipeline):
     """Generic pipeline with the tool body parsed as a Python call list: every call of the block becomes one tool
     call (the first one was announced when the block opened, the others are announced when it closes)."""

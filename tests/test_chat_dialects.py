@@ -92,3 +92,30 @@ def test_generic_plan_is_unchanged():
     plan = detect_plan("<tool_call>", "", tools=[{"name": "x"}])
     assert plan.dialect == "generic" and plan.tool_open == "<tool_call>" and not plan.render_special_tokens
     assert pipeline_for(None).__name__ == "CommittedTokenPipeline" and isinstance(ParserPlan().dialect, str)
+
+
+def test_qwen_tagged_parameter_calls():
+    from eredu_b200.runtime.streaming import CommittedTokenPipeline
+    from eredu_b200.text.dialects import parse_tagged_call
+
+    tools = [{"type": "function", "function": {"name": "write_file", "parameters": {"type": "object", "properties": {
+        "path": {"type": "string"}, "mode": {"type": "integer"}, "content": {"type": "string"}, "force": {"type": "boolean"}}}}}]
+    body = ("<function=write_file>\n<parameter=path>\n/tmp/a.txt\n</parameter>\n<parameter=mode>\n420\n</parameter>\n"
+            "<parameter=content>\n{\"not\": \"parsed\"}\nline two\n</parameter>\n<parameter=force>\ntrue\n</parameter>\n</function>")
+    call = parse_tagged_call(body, tools)[0]
+    assert call == {"name": "write_file", "arguments": {"path": "/tmp/a.txt", "mode": 420,
+                                                        "content": "{\"not\": \"parsed\"}\nline two", "force": True}}
+    loose = parse_tagged_call("<function=f><parameter=n>3</parameter><parameter=s>abc</parameter></function>")[0]
+    assert loose["arguments"] == {"n": 3, "s": "abc"}
+    with pytest.raises(ValueError):
+        parse_tagged_call("{}")
+    plan = detect_plan("<tool_call>", "", tools=tools)
+    pieces_text = "I will write it.<tool_call>\n" + body + "\n</tool_call>"
+    pieces = [pieces_text[i:i + 4] for i in range(0, len(pieces_text), 4)]
+    pipe = CommittedTokenPipeline(PieceDecoder(pieces), plan, (), None, None)
+    pipe.tools = tools
+    for i in range(len(pieces)):
+        pipe.push(i)
+    pipe.finish(FinishReason.EOS)
+    assert "".join(pipe.text_out) == "I will write it."
+    assert pipe.tool_calls[0]["name"] == "write_file" and pipe.tool_calls[0]["arguments"]["mode"] == 420
