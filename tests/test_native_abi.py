@@ -132,9 +132,10 @@ def dry_cuda(monkeypatch):
     import eredu_b200.ops.core as core_mod
     import eredu_b200.ops.moe as moe_mod
     import eredu_b200.ops.quant as quant_mod
+    import eredu_b200.ops.recurrent as rec_mod
     import eredu_b200.ops.sampling as samp_mod
 
-    for mod in (native, conv_mod, core_mod, moe_mod, quant_mod, samp_mod):
+    for mod in (native, conv_mod, core_mod, moe_mod, quant_mod, rec_mod, samp_mod):
         for attr, val in (("lib", lambda: stub), ("stream_ptr", lambda device=None: 0),
                           ("status_word", lambda device=None: status), ("_sm_count", lambda device=None: 148),
                           ("check_status", lambda device=None: None)):
@@ -213,3 +214,67 @@ def test_moe_block_and_expert_cache_dry_run(dry_cuda):
     blk.expert_cache = ExpertCache(blk.w_gate_up, blk.w_down, 3, "lru", 0)
     x = torch.randn(4, H).to(bf)
     assert blk(x, residual=x).shape == (4, H)
+
+
+@pytest.mark.parametrize("family", ["llama", "qwen3_moe", "gpt_oss", "lfm2", "qwen3_next"])
+def test_whole_model_forward_dry_run(dry_cuda, family):
+    """Prefill and decode passes of every family through the CUDA branches of the operator wrappers (stub library,
+    CPU tensors): argument kinds, shapes the wrappers assert on, and the Python glue between kernels."""
+    import dataclasses
+    import sys
+
+    from eredu_b200.models import config as C
+    from eredu_b200.models.llama import build_from_tensors, random_state
+    from eredu_b200.models.moe import make_moe_factory
+    from eredu_b200.runtime.engine import Engine
+
+    sys.path.insert(0, str(Path(__file__).parent))
+    bf = torch.bfloat16
+    kw = {}
+    if family == "llama":
+        cfg = dataclasses.replace(C.tiny_llama(), hidden_size=256, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                                  intermediate_size=512, vocab_size=512, num_hidden_layers=2)
+        sd = random_state(cfg, seed=0)
+    elif family == "qwen3_moe":
+        cfg = dataclasses.replace(C.tiny_llama(), model_type="qwen3_moe", qk_norm=True, hidden_size=256, num_attention_heads=4,
+                                  num_key_value_heads=2, head_dim=64, vocab_size=512, num_hidden_layers=2, num_experts=8,
+                                  num_experts_per_tok=2, moe_intermediate_size=64, tie_word_embeddings=False)
+        sd = random_state(cfg, seed=0)
+        kw["moe_factory"] = make_moe_factory()
+    elif family == "gpt_oss":
+        from test_gpt_oss import oss_cfg, oss_state
+
+        cfg = oss_cfg()
+        sd = oss_state(cfg)
+        kw["moe_factory"] = make_moe_factory()
+    elif family == "lfm2":
+        from test_lfm2 import lfm2_cfg
+
+        cfg = lfm2_cfg(hidden_size=256, intermediate_size=512, num_attention_heads=4, num_key_value_heads=2, vocab_size=512)
+        sd = random_state(cfg, seed=0)
+    else:
+        from test_qwen_next import next_cfg, state_for
+
+        cfg = next_cfg(hidden_size=256, head_dim=64, linear_key_head_dim=64, linear_value_head_dim=64, vocab_size=512)
+        sd = state_for(cfg)
+        kw["moe_factory"] = make_moe_factory()
+    model = build_from_tensors(cfg, lambda n: sd[n], sd.__contains__, "cpu", bf, **kw)
+    eng = Engine(model, max_batch=2, max_seq_len=64)
+    seqs = [eng.new_sequence(list(range(3, 3 + n)), max_new_tokens=4) for n in (5, 9)]
+    dry_cuda.calls.clear()
+    logits = eng.prefill_logits(seqs)
+    assert len(logits) == 2 and logits[0].shape[-1] == cfg.vocab_size
+    for sq in seqs:
+        eng.release(sq)
+    from eredu_b200.ops import SamplingParams
+
+    outs = eng.generate([list(range(3, 9)), list(range(4, 15))], SamplingParams(temperature=0.0), 3)   # decode-shaped passes
+    assert [len(o) for o in outs] == [3, 3]
+    calls = set(dry_cuda.calls)
+    assert {"eredu_gemm_bf16", "eredu_rmsnorm", "eredu_attn_prefill", "eredu_attn_decode", "eredu_rope_kv"} <= calls
+    if family in ("qwen3_moe", "gpt_oss", "qwen3_next"):
+        assert "eredu_gemm_bf16_grouped" in calls
+    if family == "lfm2":
+        assert "eredu_short_conv" in calls
+    if family == "qwen3_next":
+        assert {"eredu_short_conv", "eredu_gated_delta_scan"} <= calls
