@@ -57,6 +57,15 @@ def probe_logits(eng, model, prompt):
     return logits.tolist()
 
 
+def lfm2_cfg():
+    from eredu_b200.models.config import ModelConfig
+
+    return ModelConfig.from_hf_dict({
+        "model_type": "lfm2", "vocab_size": 300, "hidden_size": 64, "intermediate_size": 128, "block_auto_adjust_ff_dim": False,
+        "num_hidden_layers": 4, "num_attention_heads": 4, "num_key_value_heads": 2, "max_position_embeddings": 256,
+        "layer_types": ["conv", "full_attention", "conv", "full_attention"], "conv_L_cache": 3, "conv_bias": True})
+
+
 def main():
     scenario, out_path = sys.argv[1], sys.argv[2]
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -76,6 +85,12 @@ def main():
     g = torch.Generator().manual_seed(0)
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 33)]
     sp = SamplingParams(temperature=0.0)
+
+    if "lfm2" in scenario:      # hybrid family: short-convolution layers sharded by channel, attention by head group
+        cfg = lfm2_cfg()
+        sd = random_state(cfg, seed=0, std=0.08)
+        g = torch.Generator().manual_seed(0)
+        prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 33)]
 
     if scenario == "gpu_tpops":
         from eredu_b200.ops import native

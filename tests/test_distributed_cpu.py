@@ -8,7 +8,7 @@ from eredu_b200.ops import SamplingParams
 from eredu_b200.runtime.engine import Engine
 
 from dist_util import run_ranks
-from dist_worker import moe_cfg, tiny_cfg
+from dist_worker import lfm2_cfg, moe_cfg, tiny_cfg
 
 
 def _oracle(n_new, prompts_lens=(9, 33)):
@@ -50,5 +50,21 @@ def test_expert_parallel_over_tensor_ranks_matches_single_rank(world, tmp_path):
     g = torch.Generator().manual_seed(0)
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 33)]
     want = Engine(model, max_batch=4, max_seq_len=128).generate(prompts, SamplingParams(temperature=0.0), 10)
+    for r in res:
+        assert r["tokens"] == want
+
+
+@pytest.mark.parametrize("scenario,world", [("cpu_lfm2_tp_nccl", 2), ("cpu_lfm2_pp", 2)])
+def test_hybrid_family_under_tensor_and_pipeline_parallelism(scenario, world, tmp_path):
+    """LFM2: convolution channels and their recurrent state are split over the tensor ranks (row-parallel out_proj
+    summed over the group); pipeline stages own the state of their own layers."""
+    res = run_ranks(scenario, world, tmp_path)
+    cfg = lfm2_cfg()
+    sd = random_state(cfg, seed=0, std=0.08)
+    model = build_from_tensors(cfg, sd.__getitem__, sd.__contains__, "cpu", torch.float32)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 33)]
+    n_new = 12 if "tp" in scenario else 10
+    want = Engine(model, max_batch=4, max_seq_len=128).generate(prompts, SamplingParams(temperature=0.0), n_new)
     for r in res:
         assert r["tokens"] == want
