@@ -417,11 +417,10 @@ def build_from_tensors(cfg: ModelConfig, get: Callable[[str], torch.Tensor], has
         w_gate = None
         if cfg.attn_output_gate:
             # q_proj rows are [query (D) | gate (D)] per head: the gate block moves behind q, k and v
-            if tp > 1:
-                raise NotImplementedError("tensor parallelism over gated attention is not implemented")
             two = wq.view(cfg.num_attention_heads, 2 * cfg.head_dim, wq.shape[1])
             wq = two[:, :cfg.head_dim].reshape(cfg.num_attention_heads * cfg.head_dim, -1)
-            w_gate = two[:, cfg.head_dim:].reshape(cfg.num_attention_heads * cfg.head_dim, -1)
+            nq_l = model.n_q_local
+            w_gate = two[r * nq_l:(r + 1) * nq_l, cfg.head_dim:].reshape(nq_l * cfg.head_dim, -1)   # this rank's heads
         if has(p + "self_attn.q_proj.bias"):
             bq, bk, bv = (get(p + f"self_attn.{n}_proj.bias") for n in "qkv")
         wqkv, wo_l, bqkv = shard_attention(cfg, par, wq, wk, wv, wo, bq, bk, bv)

@@ -10,7 +10,8 @@ Per gated-delta layer and token:  [qkv | z | b | a] = in_proj(norm(x));  qkv <- 
 q, k <- l2norm;  q <- q / sqrt(dk);  beta = sigmoid(b);  g = -exp(A_log) * softplus(a + dt_bias);
 o = gated_delta_scan(q, k, v, g, beta);  y = out_proj(rmsnorm(o) * w * silu(z)).
 The convolution tail and the recurrent matrix of every sequence live in state slots of the KV cache object.
-Tensor parallelism is not implemented for these layers yet (single-rank and pipeline stages only).
+Under tensor parallelism a key head with its value heads is the unit of sharding; the output projection is
+row-parallel.
 """
 from __future__ import annotations
 
@@ -36,29 +37,47 @@ def split_fused_projections(cfg, qkvz: torch.Tensor, ba: torch.Tensor):
 def build_linear_attention_layer(model, cfg, p, get, has, up):
     from .llama import LayerWeights
 
-    if model.par.tp_size > 1:
-        raise NotImplementedError("tensor parallelism over gated-delta layers is not implemented")
     la = p + "linear_attn."
     if has(la + "in_proj_qkvz.weight"):
         qkv, z, b, a = split_fused_projections(cfg, get(la + "in_proj_qkvz.weight"), get(la + "in_proj_ba.weight"))
     else:
         qkv, z, b, a = (get(la + f"in_proj_{n}.weight") for n in ("qkv", "z", "b", "a"))
+    conv = get(la + "conv1d.weight")
+    conv = conv.reshape(conv.shape[0], -1)
+    dt_bias, a_log, w_out = get(la + "dt_bias"), get(la + "A_log"), get(la + "out_proj.weight")
+    tp, r = model.par.tp_size, model.par.tp_rank
+    if tp > 1:
+        # a key head with the value heads that share it is the unit: rank r owns key heads [r Hk/tp, (r+1) Hk/tp),
+        # their value heads, the matching convolution channels and decay parameters, and the columns of out_proj
+        Hk, Hv, dk, dv = cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
+        if Hk % tp != 0:
+            raise ValueError(f"{Hk} linear-attention key heads cannot be split over {tp} tensor ranks")
+        rep = Hv // Hk
+        k0, k1 = r * (Hk // tp), (r + 1) * (Hk // tp)
+        v0, v1 = k0 * rep, k1 * rep
+        key_dim = Hk * dk
+        rows = torch.cat((torch.arange(k0 * dk, k1 * dk), key_dim + torch.arange(k0 * dk, k1 * dk),
+                          2 * key_dim + torch.arange(v0 * dv, v1 * dv)))
+        qkv, conv = qkv[rows], conv[rows]
+        z, b, a = z[v0 * dv:v1 * dv], b[v0:v1], a[v0:v1]
+        dt_bias, a_log, w_out = dt_bias[v0:v1], a_log[v0:v1], w_out[:, v0 * dv:v1 * dv]
     lw = LayerWeights(attn_norm=up(get(p + "input_layernorm.weight"), torch.float32), wqkv=None, wo=None,
                       ffn_norm=up(get(p + "post_attention_layernorm.weight"), torch.float32))
     lw.la_in = up(torch.cat((qkv, z, b, a), 0))
-    conv = get(la + "conv1d.weight")
-    lw.la_conv_w = up(conv.reshape(conv.shape[0], -1), torch.float32)
-    lw.la_dt_bias = up(get(la + "dt_bias"), torch.float32)
-    lw.la_A_log = up(get(la + "A_log"), torch.float32)
+    lw.la_conv_w = up(conv, torch.float32)
+    lw.la_dt_bias = up(dt_bias, torch.float32)
+    lw.la_A_log = up(a_log, torch.float32)
     lw.la_norm_w = up(get(la + "norm.weight"), torch.float32)
-    lw.la_out = up(get(la + "out_proj.weight"))
+    lw.la_out = up(w_out)
     return lw
 
 
 def linear_attention_forward(model, li, lw, h, ssq, batch, kv):
     """The gated-delta operator of one layer; returns (h + out_proj(...), ssq')."""
     cfg = model.cfg
-    Hk, Hv, dk, dv = cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
+    tp = model.par.tp_size
+    Hk, Hv = cfg.linear_num_key_heads // tp, cfg.linear_num_value_heads // tp       # this rank's heads
+    dk, dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
     key_dim, value_dim = Hk * dk, Hv * dv
     conv_dim = 2 * key_dim + value_dim
     proj = model._normed_linear(h, ssq, lw.fold_attn, lw.attn_norm, lw.la_in, lw, "la_in")

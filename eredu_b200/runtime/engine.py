@@ -67,10 +67,12 @@ class Engine:
         la_layers = [li for li in local if self.cfg.layer_is_linear_attention(li)]
         if la_layers:
             c = self.cfg
+            tp = model.par.tp_size
             self.kv.enable_linear_attention_state(
                 la_layers, slots=max(2 * max_batch, 8), conv_hist=c.linear_conv_kernel_dim - 1,
-                conv_channels=2 * c.linear_num_key_heads * c.linear_key_head_dim + c.linear_num_value_heads * c.linear_value_head_dim,
-                heads=c.linear_num_value_heads, dk=c.linear_key_head_dim, dv=c.linear_value_head_dim)
+                conv_channels=(2 * c.linear_num_key_heads * c.linear_key_head_dim
+                               + c.linear_num_value_heads * c.linear_value_head_dim) // tp,
+                heads=c.linear_num_value_heads // tp, dk=c.linear_key_head_dim, dv=c.linear_value_head_dim)
         self.cuda = self.device.type == "cuda"
         self.use_graph = self.cuda if use_cuda_graph is None else (use_cuda_graph and self.cuda)
         self.prefill_chunk = prefill_chunk

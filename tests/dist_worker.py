@@ -92,6 +92,14 @@ def main():
         g = torch.Generator().manual_seed(0)
         prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 33)]
 
+    if "qnext" in scenario:     # Qwen3-Next style hybrid: gated-delta heads and experts spread over the same ranks
+        from test_qwen_next import next_cfg, state_for
+
+        cfg = next_cfg()
+        sd = state_for(cfg)
+        g = torch.Generator().manual_seed(0)
+        prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 33)]
+
     if scenario == "gpu_tpops":
         from eredu_b200.ops import native
         from eredu_b200.parallel.tp import PeerTPOps
@@ -159,8 +167,9 @@ def main():
         from eredu_b200.models.moe import make_moe_factory
         from eredu_b200.parallel import tp
 
-        cfg = moe_cfg(gpu)
-        sd = random_state(cfg, seed=0, std=0.08)
+        if "qnext" not in scenario:
+            cfg = moe_cfg(gpu)
+            sd = random_state(cfg, seed=0, std=0.08)
         par = ParallelContext.from_env(ParallelTopology(tensor=world, expert=world, expert_over_tensor=True))
         model = build_from_tensors(cfg, sd.__getitem__, sd.__contains__, dev, dtype, par, moe_factory=make_moe_factory())
         tp.attach(model, par, max_tokens=256, backend="nccl" if "nccl" in scenario else "peer")
