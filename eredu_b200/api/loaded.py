@@ -101,6 +101,10 @@ class LoadedModel:
             from ..models.lfm2 import canonical_access
 
             get, has = canonical_access(get, has)
+        elif src.cfg.model_type == "nemotron_h":
+            from ..models.nemotron_h import canonical_access
+
+            get, has = canonical_access(get, has)
         model = build_from_tensors(src.cfg, get, has, device, dtype, opt.parallel, moe_factory, quantizer,
                                    on_layer=on_layer)
         if residency is not None:

@@ -42,6 +42,16 @@ class ModelConfig:
     linear_value_head_dim: int = 128
     linear_num_key_heads: int = 16
     linear_num_value_heads: int = 32
+    # Nemotron-H: every layer is ONE mixer ("mamba" | "attention_only" | "mlp_only" | "moe_only" in layer_types)
+    mamba_num_heads: int = 0
+    mamba_head_dim: int = 0
+    ssm_state_size: int = 0
+    mamba_n_groups: int = 1
+    mamba_conv_kernel: int = 4
+    mamba_conv_bias: bool = True
+    mamba_proj_bias: bool = False
+    time_step_min: float = 0.001
+    use_rope: bool = True            # Nemotron-H attention carries no positional rotation
     attn_output_gate: bool = False   # q_proj also produces a per-channel sigmoid gate of the attention output
     shared_expert_gate: bool = False  # the shared expert's output is scaled by sigmoid(x . w)
     conv_l_cache: int = 3    # LFM2 short-convolution kernel width
@@ -80,6 +90,8 @@ class ModelConfig:
         return r - (r % 2)
 
     def layer_is_moe(self, layer: int) -> bool:
+        if self.model_type == "nemotron_h":
+            return self.layer_types[layer] == "moe_only"
         if not self.is_moe or layer in self.mlp_only_layers:
             return False
         return (layer + 1) % max(1, self.decoder_sparse_step) == 0
@@ -92,9 +104,21 @@ class ModelConfig:
         """Qwen3-Next style schedule: the layer's operator is a gated delta network instead of softmax attention."""
         return self.layer_types is not None and self.layer_types[layer] == "linear_attention"
 
+    def layer_is_mamba(self, layer: int) -> bool:
+        return self.layer_types is not None and self.layer_types[layer] == "mamba"
+
+    def layer_has_kv(self, layer: int) -> bool:
+        """The layer appends K/V pages (softmax attention); every other operator keeps a fixed state or none."""
+        if self.layer_types is None:
+            return True
+        return self.layer_types[layer] in ("full_attention", "sliding_attention", "attention_only")
+
+    def layer_has_recurrent_state(self, layer: int) -> bool:
+        return self.layer_types is not None and self.layer_types[layer] in ("linear_attention", "mamba")
+
     @property
     def is_hybrid(self) -> bool:
-        return self.layer_types is not None and ("conv" in self.layer_types or "linear_attention" in self.layer_types)
+        return self.layer_types is not None and any(t in ("conv", "linear_attention", "mamba") for t in self.layer_types)
 
     def layer_window(self, layer: int) -> int:
         if self.sliding_window is None or self.sliding_window <= 0:
@@ -116,6 +140,20 @@ class ModelConfig:
                                "gpt_oss": "GptOssForCausalLM", "lfm2": "Lfm2ForCausalLM",
                                "lfm2_moe": "Lfm2MoeForCausalLM", "qwen3_next": "Qwen3NextForCausalLM",
                                "qwen3_5_moe": "Qwen3_5MoeForCausalLM"}.get(self.model_type, "LlamaForCausalLM")]
+        for k in ("mamba_n_groups", "mamba_conv_kernel", "mamba_conv_bias", "use_rope"):
+            d.pop(k, None)
+        if self.model_type == "nemotron_h":
+            inv = {"mamba": "M", "attention_only": "*", "mlp_only": "-", "moe_only": "E"}
+            d["hybrid_override_pattern"] = "".join(inv[t] for t in self.layer_types)
+            d.pop("layer_types", None)
+            d.update(n_groups=self.mamba_n_groups, conv_kernel=self.mamba_conv_kernel, use_conv_bias=self.mamba_conv_bias,
+                     layer_norm_epsilon=self.rms_norm_eps, n_routed_experts=self.num_experts,
+                     moe_shared_expert_intermediate_size=self.shared_expert_intermediate_size, n_shared_experts=1,
+                     num_experts_per_tok=self.num_experts_per_tok, moe_intermediate_size=self.moe_intermediate_size,
+                     norm_topk_prob=self.norm_topk_prob)
+        else:
+            for k in ("mamba_num_heads", "mamba_head_dim", "ssm_state_size", "mamba_proj_bias", "time_step_min"):
+                d.pop(k, None)
         if self.model_type not in QWEN_HYBRID_TYPES:
             for k in ("linear_conv_kernel_dim", "linear_key_head_dim", "linear_value_head_dim", "linear_num_key_heads",
                       "linear_num_value_heads"):
@@ -197,6 +235,34 @@ class ModelConfig:
             bos_token_id=d.get("bos_token_id"),
             torch_dtype=str(d.get("torch_dtype", d.get("dtype", "bfloat16"))),
         )
+        if mt == "nemotron_h":
+            # eredu/src/backend/mlx/architectures/nemotron_h/model.rs:74-90 (pattern markers), :100-245 (fields)
+            marks = {"M": "mamba", "*": "attention_only", "-": "mlp_only", "E": "moe_only"}
+            pattern = str(d.get("hybrid_override_pattern", ""))
+            if not pattern or any(ch not in marks for ch in pattern):
+                raise ValueError("Nemotron-H needs a hybrid_override_pattern made of 'M', '*', '-' and 'E'")
+            cfg.layer_types = [marks[ch] for ch in pattern]
+            cfg.num_hidden_layers = len(pattern)
+            cfg.mamba_num_heads = int(d.get("mamba_num_heads", 128))
+            cfg.mamba_head_dim = int(d.get("mamba_head_dim", 64))
+            cfg.ssm_state_size = int(d.get("ssm_state_size", 128))
+            cfg.mamba_n_groups = int(d.get("n_groups", 8))
+            cfg.mamba_conv_kernel = int(d.get("conv_kernel", 4))
+            cfg.mamba_conv_bias = bool(d.get("use_conv_bias", True))
+            cfg.mamba_proj_bias = bool(d.get("mamba_proj_bias", d.get("use_bias", False)))
+            cfg.time_step_min = float(d.get("time_step_min", 0.001))
+            cfg.rms_norm_eps = float(d.get("layer_norm_epsilon", d.get("rms_norm_eps", 1e-5)))
+            cfg.head_dim = int(d.get("head_dim") or d.get("attention_head_dim") or cfg.head_dim)
+            cfg.use_rope = False
+            cfg.tie_word_embeddings = bool(d.get("tie_word_embeddings", False))
+            cfg.num_experts = int(d.get("n_routed_experts", 0) or 0)
+            cfg.num_experts_per_tok = int(d.get("num_experts_per_tok", 0) or 0)
+            cfg.moe_intermediate_size = int(d.get("moe_intermediate_size", 0) or 0)
+            cfg.shared_expert_intermediate_size = (int(d.get("moe_shared_expert_intermediate_size", 0) or 0)
+                                                   * max(1, int(d.get("n_shared_experts", 1) or 1))
+                                                   if cfg.num_experts else 0)
+            cfg.router_scoring = "sigmoid"
+            cfg.norm_topk_prob = bool(d.get("norm_topk_prob", True))
         if mt in QWEN_HYBRID_TYPES:
             # eredu/src/backend/mlx/architectures/qwen/hybrid/qwen3_5.rs:254-323: three gated-delta layers per full
             # attention layer, zero-centred RMSNorm weights, gated attention output, 25 % rotary, gated shared expert

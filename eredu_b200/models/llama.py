@@ -48,7 +48,7 @@ class LayerWeights:
     attn_norm: torch.Tensor
     wqkv: Optional[torch.Tensor]
     wo: Optional[torch.Tensor]
-    ffn_norm: torch.Tensor
+    ffn_norm: Optional[torch.Tensor]
     w_gate_up: Optional[torch.Tensor] = None
     w_down: Optional[torch.Tensor] = None
     bqkv: Optional[torch.Tensor] = None
@@ -62,6 +62,18 @@ class LayerWeights:
     qlin: dict = field(default_factory=dict)  # quantised linears by role: "qkv", "o", "gate_up", "down"
     # LFM2 "conv" layers: gated short convolution instead of attention (wqkv / wo are None); attn_norm is the
     # operator norm and fold_attn then refers to conv_in
+    # Nemotron-H: the layer is one mixer ("mamba" | "attention_only" | "mlp_only" | "moe_only"); attn_norm is its norm
+    block_kind: str = ""
+    m_in: Optional[torch.Tensor] = None        # Mamba-2 input projection [z | x B C | dt]
+    m_in_b: Optional[torch.Tensor] = None
+    m_conv_w: Optional[torch.Tensor] = None
+    m_conv_b: Optional[torch.Tensor] = None
+    m_A_log: Optional[torch.Tensor] = None
+    m_D: Optional[torch.Tensor] = None
+    m_dt_bias: Optional[torch.Tensor] = None
+    m_norm_w: Optional[torch.Tensor] = None
+    m_out: Optional[torch.Tensor] = None
+    m_out_b: Optional[torch.Tensor] = None
     attn_gate: bool = False   # wqkv carries a fourth block: the per-channel sigmoid gate of the attention output
     # Qwen3-Next "linear_attention" layers (gated delta network); fold_attn then refers to la_in
     la_in: Optional[torch.Tensor] = None       # [2 key + value + value + Hv + Hv, H]: qkv | z | b | a
@@ -99,6 +111,8 @@ class CausalLM:
         self.lm_head: Optional[torch.Tensor] = None  # [V_local, H]
         self.vocab_start = 0
         inv, factor = rope_tables(cfg)
+        if not cfg.use_rope:
+            inv = torch.zeros_like(inv)      # angle 0 everywhere: the RoPE step of the KV-append kernel is the identity
         self.inv_freq = inv.to(self.device)
         self.attn_factor = factor
         self.scale = 1.0 / math.sqrt(cfg.head_dim)
@@ -166,6 +180,10 @@ class CausalLM:
     def layer_forward(self, li: int, lw: LayerWeights, h, batch: ForwardBatch, kv, ssq=None, next_folded=False):
         """One decoder block. ``ssq``: partial sums of squares of h's rows (or None); returns (h, ssq')."""
         cfg = self.cfg
+        if lw.block_kind:
+            from .nemotron_h import block_forward
+
+            return block_forward(self, li, lw, h, batch, kv), None
         if lw.conv_w is not None:
             proj = self._normed_linear(h, ssq, lw.fold_attn, lw.attn_norm, lw.conv_in, lw, "conv_in", bias=lw.conv_in_b)
             y = ops.short_conv(proj, lw.conv_w, lw.conv_b, kv.conv_layer(li), batch.block_table,
@@ -287,6 +305,8 @@ class CausalLM:
 
     def fold_layer_norms(self, lw) -> None:
         off = self.cfg.norm_weight_offset
+        if lw.block_kind:
+            return       # single-mixer blocks keep their explicit norm
         if "qkv" not in lw.qlin and not lw.fold_attn and lw.wqkv is not None:
             lw.wqkv = (lw.wqkv.float() * (lw.attn_norm + off)[None, :]).to(self.dtype).contiguous()
             lw.fold_attn = True
@@ -387,6 +407,14 @@ def build_from_tensors(cfg: ModelConfig, get: Callable[[str], torch.Tensor], has
     for li in range(model.first_layer, model.last_layer):
         p = f"model.layers.{li}."
         bq = bk = bv = None
+        if cfg.model_type == "nemotron_h":
+            from .nemotron_h import build_block
+
+            lw = build_block(model, cfg, li, p, get, has, up, moe_factory)
+            model.layers.append(lw)
+            if on_layer is not None:
+                on_layer(model, li, lw)
+            continue
         if cfg.layer_is_conv(li) or cfg.layer_is_linear_attention(li):
             if cfg.layer_is_conv(li):
                 lw = _build_conv_layer(model, cfg, p, get, has, up)
@@ -519,6 +547,11 @@ def random_state(cfg: ModelConfig, seed: int = 0, std: float = 0.02, dtype=torch
         mat("lm_head.weight", cfg.vocab_size, H)
     for li in range(cfg.num_hidden_layers):
         p = f"model.layers.{li}."
+        if cfg.model_type == "nemotron_h":
+            from .nemotron_h import random_block_state
+
+            random_block_state(cfg, li, p, mat, out, std)
+            continue
         ones(p + "input_layernorm.weight", H)
         ones(p + "post_attention_layernorm.weight", H)
         if cfg.layer_is_linear_attention(li):

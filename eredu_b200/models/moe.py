@@ -52,7 +52,10 @@ class MoEBlock:
         if self.shared is None:
             return None
         sgu, sd = self.shared
-        y = ops.linear(ops.gated_linear(x, sgu, sgu.shape[0] // 2), sd)
+        if self.act in moe_ops.UNGATED:
+            y = ops.linear(torch.relu(ops.linear(x, sgu)).square_(), sd)
+        else:
+            y = ops.linear(ops.gated_linear(x, sgu, sgu.shape[0] // 2), sd)
         if self.shared_gate_w is not None:
             y = (y.float() * torch.sigmoid(x.float() @ self.shared_gate_w.float().t())).to(y.dtype)
         return y
@@ -76,7 +79,7 @@ class MoEBlock:
         shared = self._shared_out(x)
         cache = getattr(self, "expert_cache", None)
         if cache is not None:
-            local = cache.forward(x, ids, w, limit=cfg.swiglu_limit)
+            local = cache.forward(x, ids, w, limit=cfg.swiglu_limit, act=self.act)
         else:
             local = moe_ops.experts_forward(x, ids, w, self.w_gate_up, self.w_down, self.e0, limit=cfg.swiglu_limit,
                                             gu_bias=self.gu_bias, down_bias=self.down_bias, act=self.act)
@@ -100,8 +103,9 @@ class MoEBlock:
             ids, w = self.route(x)
             extra = self._shared_out(x)
             if self.ep_size == 1:
-                return cache.forward(x, ids, w, residual=residual, extra=extra, limit=self.cfg.swiglu_limit)
-            partial = cache.forward(x, ids, w, extra=extra if self.e0 == 0 else None, limit=self.cfg.swiglu_limit)
+                return cache.forward(x, ids, w, residual=residual, extra=extra, limit=self.cfg.swiglu_limit, act=self.act)
+            partial = cache.forward(x, ids, w, extra=extra if self.e0 == 0 else None, limit=self.cfg.swiglu_limit,
+                                    act=self.act)
             return self.ep_ops.all_reduce(partial, residual=residual)
         plan = xp = None
         if x.is_cuda and x.shape[0] <= 64 and self.cfg.n_group <= 1:
@@ -154,6 +158,9 @@ def make_moe_factory(src=None, router_std_scale: bool = False):
             return block
         if has(p + "router.weight"):
             return _gpt_oss_block(model, li, get, has, e0, e1)
+        nm = f"model.layers.{li}.mixer."
+        if has(nm + "gate.weight"):
+            return _nemotron_block(model, li, get, has, e0, e1)
         router = get(p + "gate.weight").to(device=dev, dtype=dt).contiguous()
         if has(p + "experts.gate_up_proj"):
             gu = get(p + "experts.gate_up_proj")[e0:e1]
@@ -223,6 +230,26 @@ def _gpt_oss_block(model, li, get, has, e0, e1):
     up = lambda t: t.to(device=dev, dtype=dt).contiguous()           # noqa: E731
     block = MoEBlock(cfg, up(get(p + "router.weight")), up(gu), up(dn), e0, cfg.num_experts, ep_size=model.par.ep_size,
                      router_linear_bias=up(get(p + "router.bias")), gu_bias=up(gub), down_bias=up(dnb), act="oss_glu")
+    block._model = model
+    block.layer_index = li
+    return block
+
+
+def _nemotron_block(model, li, get, has, e0, e1):
+    """Nemotron-H sparse mixer: sigmoid router with a score-correction bias (selection only), experts with a single up
+    projection and relu^2, an ungated relu^2 shared expert (architectures/nemotron_h/model.rs:1038-1290)."""
+    cfg, dev, dt = model.cfg, model.device, model.dtype
+    p = f"model.layers.{li}.mixer."
+    up = lambda t: t.to(device=dev, dtype=dt).contiguous()                         # noqa: E731
+    w_up = torch.stack([get(p + f"experts.{e}.up_proj.weight") for e in range(e0, e1)], 0)
+    w_dn = torch.stack([get(p + f"experts.{e}.down_proj.weight") for e in range(e0, e1)], 0)
+    sel = get(p + "gate.e_score_correction_bias").to(device=dev, dtype=torch.float32).contiguous() \
+        if has(p + "gate.e_score_correction_bias") else None
+    shared = None
+    if has(p + "shared_experts.up_proj.weight"):
+        shared = (up(get(p + "shared_experts.up_proj.weight")), up(get(p + "shared_experts.down_proj.weight")))
+    block = MoEBlock(cfg, up(get(p + "gate.weight")), up(w_up), up(w_dn), e0, cfg.num_experts, ep_size=model.par.ep_size,
+                     shared=shared, router_bias=sel, act="relu2")
     block._model = model
     block.layer_index = li
     return block

@@ -5,5 +5,5 @@ from .core import (PAGE, attention_decode, attention_prefill, attention_ref, dec
 from .sampling import (SamplingParams, pack_allow_mask, pack_rows, philox_uniform, process_logits_ref, rows_to_tensor,
                        sample, sample_ref, spec_verify, verify_ref)
 from .conv import short_conv, short_conv_ref
-from .recurrent import gated_delta_scan, gated_delta_scan_ref
+from .recurrent import gated_delta_scan, gated_delta_scan_ref, mamba2_scan, mamba2_scan_ref
 from . import native

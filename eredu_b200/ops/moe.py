@@ -80,6 +80,7 @@ def route(logits, k, scoring="softmax", renorm=True, scale=1.0, sel_bias=None, n
 
 
 ACTS = {"swiglu": 0, "oss_glu": 1}
+UNGATED = ("relu2",)   # activations of experts with a single up projection: w_gate_up is then [E, I, H]
 
 
 def gated_act_ref(g, u, act="swiglu", limit=0.0):
@@ -97,7 +98,7 @@ def experts_ref(x, ids, weights, w_gate_up, w_down, e0=0, limit=0.0, gu_bias=Non
     ``gu_bias`` [E_local, 2I] (gate part then up part) and ``down_bias`` [E_local, H] are per-expert biases."""
     T, H = x.shape
     E_local, two_i, _ = w_gate_up.shape
-    inter = two_i // 2
+    inter = two_i if act in UNGATED else two_i // 2
     out = torch.zeros((T, H), dtype=torch.float32, device=x.device)
     xf = x.float()
     for slot in range(ids.shape[1]):
@@ -108,8 +109,11 @@ def experts_ref(x, ids, weights, w_gate_up, w_down, e0=0, limit=0.0, gu_bias=Non
             y = xf[sel] @ w_gate_up[e].float().t()
             if gu_bias is not None:
                 y = y + gu_bias[e].float()
-            g, u = y[:, :inter], y[:, inter:]
-            a = gated_act_ref(g, u, act, limit).to(x.dtype).float()
+            if act in UNGATED:
+                a = torch.relu(y).square().to(x.dtype).float()
+            else:
+                g, u = y[:, :inter], y[:, inter:]
+                a = gated_act_ref(g, u, act, limit).to(x.dtype).float()
             o = a @ w_down[e].float().t()
             if down_bias is not None:
                 o = o + down_bias[e].float()
@@ -189,7 +193,8 @@ def experts_forward(x, ids, weights, w_gate_up, w_down, e0=0, residual=None, ext
     T, H = x.shape
     k = ids.shape[1]
     E_local, two_i, _ = w_gate_up.shape
-    inter = two_i // 2
+    ungated = act in UNGATED
+    inter = two_i if ungated else two_i // 2
     routes = T * k
     rows_cap = rows_cap or routes
     dev = x.device
@@ -205,9 +210,12 @@ def experts_forward(x, ids, weights, w_gate_up, w_down, e0=0, residual=None, ext
     sm = _sm_count(dev)
     wgu = w_gate_up.view(E_local * two_i, H)
     code = lib().eredu_gemm_bf16_grouped(ptr(xp), ptr(wgu), ptr(gated), ptr(plan.work), plan.n_work, tile, rows_cap, inter,
-                                         H, H, H, inter, E_local * two_i, two_i, 1, 0, sm, ptr(st), ptr(gu_bias),
-                                         two_i if gu_bias is not None else 0, ACTS[act], float(limit), stream_ptr(dev))
+                                         H, H, H, inter, E_local * two_i, two_i, 0 if ungated else 1, 0, sm, ptr(st),
+                                         ptr(gu_bias), two_i if gu_bias is not None else 0, 0 if ungated else ACTS[act],
+                                         float(limit), stream_ptr(dev))
     check(code, "eredu_gemm_bf16_grouped(gate_up)")
+    if ungated:
+        gated = torch.relu(gated).square_()      # relu^2 between the two grouped GEMMs (rows past the plan are unused)
     y = torch.empty((rows_cap, H), dtype=x.dtype, device=dev)
     wd = w_down.view(E_local * H, inter)
     code = lib().eredu_gemm_bf16_grouped(ptr(gated), ptr(wd), ptr(y), ptr(plan.work), plan.n_work, tile, rows_cap, H,

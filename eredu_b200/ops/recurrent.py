@@ -65,3 +65,28 @@ def gated_delta_scan(q, k, v, log_decay, beta, state: Optional[torch.Tensor] = N
                                         1 if g.dim() == 4 else 0, stream_ptr(q.device))
     check(code, "eredu_gated_delta_scan")
     return S, out
+
+
+def mamba2_scan_ref(x, B, C, dt, A, D, state: Optional[torch.Tensor] = None):
+    """Mamba-2 selective state-space recurrence, token by token (eredu/src/backend/mlx/architectures/nemotron_h/
+    model.rs:1929-1962): ``S <- S * exp(dt A) + x (dt B)^T;  y = S C + D x`` per head.
+
+    x [Bt, T, H, P]; B, C [Bt, T, H, N] (already expanded from groups to heads); dt [Bt, T, H] (after softplus and floor);
+    A [H] (negative); D [H]; state fp32 [Bt, H, P, N]. Returns (state, y [Bt, T, H, P] in x's dtype)."""
+    Bt, T, H, P = x.shape
+    N = B.shape[-1]
+    S = torch.zeros((Bt, H, P, N), dtype=torch.float32, device=x.device) if state is None else state.float().clone()
+    xf, Bf, Cf, dtf = x.float(), B.float(), C.float(), dt.float()
+    Af, Df = A.float().view(1, H, 1, 1), D.float().view(1, H, 1)
+    ys = []
+    for t in range(T):
+        d = dtf[:, t]                                                     # [Bt, H]
+        dA = torch.exp(d[:, :, None, None] * Af)
+        dBx = xf[:, t][..., None] * (d[:, :, None] * Bf[:, t])[:, :, None, :]
+        S = S * dA + dBx
+        ys.append((S * Cf[:, t][:, :, None, :]).sum(-1) + xf[:, t] * Df)
+    return S, torch.stack(ys, 1).to(x.dtype)
+
+
+# No CUDA kernel for the Mamba-2 scan yet: CUDA tensors run the same tensor operations.
+mamba2_scan = mamba2_scan_ref

@@ -57,13 +57,21 @@ class Engine:
             num_pages = max_batch * self.max_pages + 1
         local = range(model.first_layer, model.last_layer)
         conv_layers = [li for li in local if self.cfg.layer_is_conv(li)]
+        kv_layers = [li for li in local if self.cfg.layer_has_kv(li)]
         self.kv = PagedKVCache(model.num_local_layers(), model.n_kv_local, self.cfg.head_dim, num_pages, model.dtype,
                                self.device, first_layer=model.first_layer,
-                               attention_layers=[li for li in local if not (self.cfg.layer_is_conv(li)
-                                                                            or self.cfg.layer_is_linear_attention(li))],
+                               attention_layers=kv_layers,
                                conv_layers=conv_layers,
                                conv_channels=self.cfg.hidden_size // model.par.tp_size if conv_layers else 0,
                                conv_hist=self.cfg.conv_l_cache - 1)
+        mamba_layers = [li for li in local if self.cfg.layer_is_mamba(li)]
+        if mamba_layers:
+            from ..models.nemotron_h import mamba_dims
+
+            heads, _, _, conv_dim = mamba_dims(self.cfg)
+            self.kv.enable_linear_attention_state(mamba_layers, slots=max(2 * max_batch, 8),
+                                                  conv_hist=self.cfg.mamba_conv_kernel - 1, conv_channels=conv_dim, heads=heads,
+                                                  dk=self.cfg.mamba_head_dim, dv=self.cfg.ssm_state_size)
         la_layers = [li for li in local if self.cfg.layer_is_linear_attention(li)]
         if la_layers:
             c = self.cfg

@@ -96,7 +96,7 @@ class ExpertCache:
         return {e: self.slot_of[e] for e in experts}
 
     # ------------------------------------------------------------------------------------------ forward
-    def forward(self, x, ids, weights, residual=None, extra=None, limit: float = 0.0):
+    def forward(self, x, ids, weights, residual=None, extra=None, limit: float = 0.0, act: str = "swiglu"):
         """Same contract as :func:`ops.moe.experts_forward` for the local experts [e0, e0 + E_local)."""
         self.stats.calls += 1
         local = ids.long() - self.e0
@@ -114,7 +114,7 @@ class ExpertCache:
             pass_ids = torch.where(is_local, remap[local.clamp(0, self.n_experts - 1)], torch.full_like(ids, self.slots)).to(torch.int32)
             part = moe_ops.experts_forward(x, pass_ids, weights, self.bank_gu, self.bank_dn, 0,
                                            residual=residual if pi == 0 else None, extra=extra if pi == 0 else None,
-                                           limit=limit)
+                                           limit=limit, act=act)
             out = part if out is None else out + part
         return out
 
@@ -133,6 +133,8 @@ def attach_expert_cache(model, slots: int = 0, device_budget_bytes: int = 0, evi
         blk = lw.moe
         if blk is None:
             continue
+        if blk.gu_bias is not None or blk.down_bias is not None:
+            raise NotImplementedError("expert cache: per-expert biases are not carried through the slot bank yet")
         n = slots or ExpertCache.slots_for_budget(blk.w_gate_up, blk.w_down, device_budget_bytes)
         cache = ExpertCache(blk.w_gate_up, blk.w_down, n, eviction, blk.e0)
         blk.expert_cache = cache

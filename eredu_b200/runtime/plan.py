@@ -21,7 +21,7 @@ from ..models.config import DENSE_TYPES, MOE_TYPES, ModelConfig
 
 EXECUTION_PLAN_SCHEMA_VERSION = 2
 DEFAULT_MAX_MAPPED_SHARDS = 4
-SUPPORTED_TYPES = DENSE_TYPES | {"qwen3_moe", "mixtral", "gpt_oss", "lfm2_moe", "qwen3_next", "qwen3_5_moe"}
+SUPPORTED_TYPES = DENSE_TYPES | {"qwen3_moe", "mixtral", "gpt_oss", "lfm2_moe", "qwen3_next", "qwen3_5_moe", "nemotron_h"}
 
 
 # ---------------------------------------------------------------------------------------------- inspection
@@ -154,13 +154,17 @@ def estimate_runtime_state(cfg: ModelConfig, weight_bytes: Optional[int] = None,
     H, D = cfg.hidden_size, cfg.head_dim
     L = cfg.num_hidden_layers
     # only softmax-attention layers keep K/V per token; convolution and gated-delta layers keep a fixed state
-    stateful = [li for li in range(L) if cfg.layer_is_conv(li) or cfg.layer_is_linear_attention(li)]
-    attn_layers = L - len(stateful)
+    stateful = [li for li in range(L) if cfg.layer_is_conv(li) or cfg.layer_has_recurrent_state(li)]
+    attn_layers = sum(1 for li in range(L) if cfg.layer_has_kv(li))
     kv_tok = 2 * cfg.num_key_value_heads * D * cache_dtype_bytes * attn_layers
     state = 0
     for li in stateful:
         if cfg.layer_is_conv(li):
             state += (cfg.conv_l_cache - 1) * H * cache_dtype_bytes
+        elif cfg.layer_is_mamba(li):
+            inter = cfg.mamba_num_heads * cfg.mamba_head_dim
+            state += (cfg.mamba_conv_kernel - 1) * (inter + 2 * cfg.mamba_n_groups * cfg.ssm_state_size) * cache_dtype_bytes
+            state += cfg.mamba_num_heads * cfg.mamba_head_dim * cfg.ssm_state_size * 4
         else:
             conv_dim = 2 * cfg.linear_num_key_heads * cfg.linear_key_head_dim + cfg.linear_num_value_heads * cfg.linear_value_head_dim
             state += (cfg.linear_conv_kernel_dim - 1) * conv_dim * cache_dtype_bytes

@@ -36,6 +36,9 @@ def forward_logits(cfg, sd, tokens, moe_fn=None):
     h = sd["model.embed_tokens.weight"][torch.tensor(tokens)] * cfg.embedding_scale
     for li in range(cfg.num_hidden_layers):
         p = f"model.layers.{li}."
+        if cfg.model_type == "nemotron_h":
+            h = h + _nemotron_mixer(cfg, sd, li, p, rms(h, sd[p + "norm.weight"], cfg.rms_norm_eps), moe_fn)
+            continue
         x = rms(h, sd[p + "input_layernorm.weight"], cfg.rms_norm_eps, cfg.norm_weight_offset)
         if cfg.layer_is_linear_attention(li):
             h = h + _gated_delta_layer(cfg, sd, p + "linear_attn.", x)
@@ -86,6 +89,47 @@ def forward_logits(cfg, sd, tokens, moe_fn=None):
     x = rms(h, sd["model.norm.weight"], cfg.rms_norm_eps, cfg.norm_weight_offset)
     head = sd.get("lm_head.weight", sd["model.embed_tokens.weight"])
     return F.linear(x, head)
+
+
+def _nemotron_mixer(cfg, sd, li, p, x, moe_fn):
+    """One Nemotron-H mixer over a whole sequence (no cache): Mamba-2, attention without rotation, relu^2 MLP or experts."""
+    T = x.shape[0]
+    kind = cfg.layer_types[li]
+    mx = p + "mixer."
+    if kind == "mlp_only":
+        return F.linear(torch.relu(F.linear(x, sd[mx + "up_proj.weight"])) ** 2, sd[mx + "down_proj.weight"])
+    if kind == "moe_only":
+        return moe_fn(cfg, sd, li, x)
+    if kind == "attention_only":
+        D, Hq, Hkv = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads
+        q = F.linear(x, sd[mx + "q_proj.weight"]).view(T, Hq, D)
+        k = F.linear(x, sd[mx + "k_proj.weight"]).view(T, Hkv, D).repeat_interleave(Hq // Hkv, 1)
+        v = F.linear(x, sd[mx + "v_proj.weight"]).view(T, Hkv, D).repeat_interleave(Hq // Hkv, 1)
+        s_ = torch.einsum("qhd,khd->hqk", q, k) / math.sqrt(D)
+        s_ = s_.masked_fill(~(torch.arange(T)[None, :] <= torch.arange(T)[:, None])[None], float("-inf"))
+        a = torch.einsum("hqk,khd->qhd", torch.softmax(s_, -1), v).reshape(T, Hq * D)
+        return F.linear(a, sd[mx + "o_proj.weight"])
+    Hm, P, N, G, K = cfg.mamba_num_heads, cfg.mamba_head_dim, cfg.ssm_state_size, cfg.mamba_n_groups, cfg.mamba_conv_kernel
+    inter = Hm * P
+    conv_dim = inter + 2 * G * N
+    proj = F.linear(x, sd[mx + "in_proj.weight"])
+    gate, xbc, dt = proj[:, :inter], proj[:, inter:inter + conv_dim], proj[:, inter + conv_dim:]
+    xbc = F.silu(F.conv1d(F.pad(xbc.t()[None], (K - 1, 0)), sd[mx + "conv1d.weight"].view(conv_dim, 1, K),
+                          sd.get(mx + "conv1d.bias"), groups=conv_dim)[0].t())
+    xs = xbc[:, :inter].view(T, Hm, P)
+    Bm = xbc[:, inter:inter + G * N].view(T, G, N).repeat_interleave(Hm // G, 1)
+    Cm = xbc[:, inter + G * N:].view(T, G, N).repeat_interleave(Hm // G, 1)
+    dt = torch.clamp_min(F.softplus(dt + sd[mx + "dt_bias"]), cfg.time_step_min)
+    A = -torch.exp(sd[mx + "A_log"])
+    S = torch.zeros(Hm, P, N)
+    ys = []
+    for t in range(T):
+        S = S * torch.exp(dt[t] * A)[:, None, None] + torch.einsum("hp,hn->hpn", xs[t], dt[t][:, None] * Bm[t])
+        ys.append(torch.einsum("hpn,hn->hp", S, Cm[t]) + sd[mx + "D"][:, None] * xs[t])
+    y = torch.stack(ys).reshape(T, inter) * F.silu(gate)
+    y = y.view(T, G, inter // G)
+    y = (y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + cfg.rms_norm_eps)).reshape(T, inter) * sd[mx + "norm.weight"]
+    return F.linear(y, sd[mx + "out_proj.weight"])
 
 
 def _gated_delta_layer(cfg, sd, la, x):

@@ -216,7 +216,7 @@ def test_moe_block_and_expert_cache_dry_run(dry_cuda):
     assert blk(x, residual=x).shape == (4, H)
 
 
-@pytest.mark.parametrize("family", ["llama", "qwen3_moe", "gpt_oss", "lfm2", "qwen3_next"])
+@pytest.mark.parametrize("family", ["llama", "qwen3_moe", "gpt_oss", "lfm2", "qwen3_next", "nemotron_h"])
 def test_whole_model_forward_dry_run(dry_cuda, family):
     """Prefill and decode passes of every family through the CUDA branches of the operator wrappers (stub library,
     CPU tensors): argument kinds, shapes the wrappers assert on, and the Python glue between kernels."""
@@ -252,6 +252,12 @@ def test_whole_model_forward_dry_run(dry_cuda, family):
 
         cfg = lfm2_cfg(hidden_size=256, intermediate_size=512, num_attention_heads=4, num_key_value_heads=2, vocab_size=512)
         sd = random_state(cfg, seed=0)
+    elif family == "nemotron_h":
+        from test_nemotron_h import nh_cfg, state_for as nh_state
+
+        cfg = nh_cfg(hidden_size=256, head_dim=64, vocab_size=512, intermediate_size=256)
+        sd = nh_state(cfg)
+        kw["moe_factory"] = make_moe_factory()
     else:
         from test_qwen_next import next_cfg, state_for
 
@@ -272,9 +278,9 @@ def test_whole_model_forward_dry_run(dry_cuda, family):
     assert [len(o) for o in outs] == [3, 3]
     calls = set(dry_cuda.calls)
     assert {"eredu_gemm_bf16", "eredu_rmsnorm", "eredu_attn_prefill", "eredu_attn_decode", "eredu_rope_kv"} <= calls
-    if family in ("qwen3_moe", "gpt_oss", "qwen3_next"):
+    if family in ("qwen3_moe", "gpt_oss", "qwen3_next", "nemotron_h"):
         assert "eredu_gemm_bf16_grouped" in calls
-    if family == "lfm2":
+    if family in ("lfm2", "nemotron_h"):
         assert "eredu_short_conv" in calls
     if family == "qwen3_next":
         assert {"eredu_short_conv", "eredu_gated_delta_scan"} <= calls
