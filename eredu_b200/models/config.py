@@ -42,6 +42,12 @@ class ModelConfig:
     linear_value_head_dim: int = 128
     linear_num_key_heads: int = 16
     linear_num_value_heads: int = 32
+    # DeepSeek-V3 multi-head latent attention (kv_lora_rank > 0 turns it on)
+    q_lora_rank: int = 0
+    kv_lora_rank: int = 0
+    qk_nope_head_dim: int = 0
+    qk_rope_head_dim: int = 0
+    v_head_dim: int = 0
     # Nemotron-H: every layer is ONE mixer ("mamba" | "attention_only" | "mlp_only" | "moe_only" in layer_types)
     mamba_num_heads: int = 0
     mamba_head_dim: int = 0
@@ -85,7 +91,20 @@ class ModelConfig:
         return self.num_experts > 0
 
     @property
+    def is_mla(self) -> bool:
+        return self.kv_lora_rank > 0
+
+    @property
+    def kv_cache_dims(self) -> tuple:
+        """(heads, key width, value width) of one cached token per layer: MLA caches one shared latent + rotary key."""
+        if self.is_mla:
+            return 1, self.kv_lora_rank + self.qk_rope_head_dim, 1
+        return self.num_key_value_heads, self.head_dim, self.head_dim
+
+    @property
     def rotary_dim(self) -> int:
+        if self.is_mla:
+            return self.qk_rope_head_dim
         r = int(self.head_dim * self.partial_rotary_factor)
         return r - (r % 2)
 
@@ -142,6 +161,14 @@ class ModelConfig:
                                "qwen3_5_moe": "Qwen3_5MoeForCausalLM"}.get(self.model_type, "LlamaForCausalLM")]
         for k in ("mamba_n_groups", "mamba_conv_kernel", "mamba_conv_bias", "use_rope"):
             d.pop(k, None)
+        if self.model_type == "deepseek_v3":
+            d.update(n_routed_experts=self.num_experts, first_k_dense_replace=len(self.mlp_only_layers),
+                     n_shared_experts=(self.shared_expert_intermediate_size // max(1, self.moe_intermediate_size)),
+                     scoring_func=self.router_scoring, rope_interleave=self.rope_traditional, architectures=["DeepseekV3ForCausalLM"])
+            d.pop("head_dim", None)
+        else:
+            for k in ("q_lora_rank", "kv_lora_rank", "qk_nope_head_dim", "qk_rope_head_dim", "v_head_dim"):
+                d.pop(k, None)
         if self.model_type == "nemotron_h":
             inv = {"mamba": "M", "attention_only": "*", "mlp_only": "-", "moe_only": "E"}
             d["hybrid_override_pattern"] = "".join(inv[t] for t in self.layer_types)
@@ -235,6 +262,24 @@ class ModelConfig:
             bos_token_id=d.get("bos_token_id"),
             torch_dtype=str(d.get("torch_dtype", d.get("dtype", "bfloat16"))),
         )
+        if mt == "deepseek_v3":
+            # eredu/src/backend/mlx/architectures/deepseek_v3/model.rs:339-403: latent attention, dense-then-sparse
+            # schedule, sigmoid router with correction bias and group-limited top-k, shared experts
+            cfg.q_lora_rank = int(d.get("q_lora_rank") or 0)
+            cfg.kv_lora_rank = int(d.get("kv_lora_rank", 512))
+            cfg.qk_nope_head_dim = int(d.get("qk_nope_head_dim", 128))
+            cfg.qk_rope_head_dim = int(d.get("qk_rope_head_dim", 64))
+            cfg.v_head_dim = int(d.get("v_head_dim", 128))
+            cfg.head_dim = cfg.qk_nope_head_dim + cfg.qk_rope_head_dim
+            cfg.num_key_value_heads = cfg.num_attention_heads
+            cfg.rope_traditional = bool(d.get("rope_interleave", False))
+            cfg.num_experts = int(d.get("n_routed_experts", 0) or 0)
+            cfg.mlp_only_layers = list(range(int(d.get("first_k_dense_replace", 0) or 0)))
+            cfg.decoder_sparse_step = int(d.get("moe_layer_freq", 1) or 1)
+            cfg.shared_expert_intermediate_size = cfg.moe_intermediate_size * int(d.get("n_shared_experts", 0) or 0)
+            cfg.router_scoring = {"sigmoid": "sigmoid", "softmax": "softmax"}[d.get("scoring_func", "sigmoid")]
+            cfg.norm_topk_prob = bool(d.get("norm_topk_prob", True))
+            cfg.tie_word_embeddings = bool(d.get("tie_word_embeddings", False))
         if mt == "nemotron_h":
             # eredu/src/backend/mlx/architectures/nemotron_h/model.rs:74-90 (pattern markers), :100-245 (fields)
             marks = {"M": "mamba", "*": "attention_only", "-": "mlp_only", "E": "moe_only"}

@@ -74,6 +74,13 @@ class LayerWeights:
     m_norm_w: Optional[torch.Tensor] = None
     m_out: Optional[torch.Tensor] = None
     m_out_b: Optional[torch.Tensor] = None
+    # DeepSeek latent attention: mla_in = [q_a (or q) | kv_a] rows; fold_attn then refers to mla_in
+    mla_in: Optional[torch.Tensor] = None
+    mla_q_norm: Optional[torch.Tensor] = None
+    mla_q_b: Optional[torch.Tensor] = None
+    mla_kv_norm: Optional[torch.Tensor] = None
+    mla_w_uk: Optional[torch.Tensor] = None    # [heads_local, nope, kv_lora]
+    mla_w_uv: Optional[torch.Tensor] = None    # [heads_local, v, kv_lora]
     attn_gate: bool = False   # wqkv carries a fourth block: the per-channel sigmoid gate of the attention output
     # Qwen3-Next "linear_attention" layers (gated delta network); fold_attn then refers to la_in
     la_in: Optional[torch.Tensor] = None       # [2 key + value + value + Hv + Hv, H]: qkv | z | b | a
@@ -103,6 +110,8 @@ class CausalLM:
         tp = self.par.tp_size
         self.n_q_local, self.n_kv_local, self.kv_rep = self.par.attention_partition(cfg.num_attention_heads,
                                                                                     cfg.num_key_value_heads)
+        if cfg.is_mla:
+            self.n_kv_local = 1     # one latent row per token, replicated on every tensor rank
         self.inter_local = cfg.intermediate_size // tp if cfg.intermediate_size % tp == 0 else None
         self.layers: list[LayerWeights] = []
         self.first_layer, self.last_layer = self.par.layer_range(cfg.num_hidden_layers)
@@ -190,6 +199,11 @@ class CausalLM:
                                batch.cu_q if batch.is_prefill else None, batch.q_per_seq, batch.positions, batch.slots,
                                batch.max_q_len)
             h, ssq = self._row_linear_ssq(lw, "conv_out", y, lw.conv_out, h, lw.conv_out_b, lw.fold_ffn)
+            return self._ffn(lw, h, ssq, next_folded)
+        if lw.mla_in is not None:
+            from .deepseek import mla_forward
+
+            h, ssq = mla_forward(self, li, lw, h, ssq, batch, kv)
             return self._ffn(lw, h, ssq, next_folded)
         if lw.la_in is not None:
             from .qwen_next import linear_attention_forward
@@ -310,6 +324,9 @@ class CausalLM:
         if "qkv" not in lw.qlin and not lw.fold_attn and lw.wqkv is not None:
             lw.wqkv = (lw.wqkv.float() * (lw.attn_norm + off)[None, :]).to(self.dtype).contiguous()
             lw.fold_attn = True
+        if "mla_in" not in lw.qlin and not lw.fold_attn and lw.mla_in is not None:
+            lw.mla_in = (lw.mla_in.float() * (lw.attn_norm + off)[None, :]).to(self.dtype).contiguous()
+            lw.fold_attn = True
         if "la_in" not in lw.qlin and not lw.fold_attn and lw.la_in is not None:
             lw.la_in = (lw.la_in.float() * (lw.attn_norm + off)[None, :]).to(self.dtype).contiguous()
             lw.fold_attn = True
@@ -415,8 +432,12 @@ def build_from_tensors(cfg: ModelConfig, get: Callable[[str], torch.Tensor], has
             if on_layer is not None:
                 on_layer(model, li, lw)
             continue
-        if cfg.layer_is_conv(li) or cfg.layer_is_linear_attention(li):
-            if cfg.layer_is_conv(li):
+        if cfg.layer_is_conv(li) or cfg.layer_is_linear_attention(li) or cfg.is_mla:
+            if cfg.is_mla:
+                from .deepseek import build_mla_layer
+
+                lw = build_mla_layer(model, cfg, p, get, has, up)
+            elif cfg.layer_is_conv(li):
                 lw = _build_conv_layer(model, cfg, p, get, has, up)
             else:
                 from .qwen_next import build_linear_attention_layer
@@ -571,6 +592,12 @@ def random_state(cfg: ModelConfig, seed: int = 0, std: float = 0.02, dtype=torch
                 mat(p + "conv.out_proj.bias", H)
             _random_ffn(cfg, li, p, mat)
             continue
+        if cfg.is_mla:
+            from .deepseek import random_mla_state
+
+            random_mla_state(cfg, p, mat, ones)
+            _random_ffn(cfg, li, p, mat)
+            continue
         mat(p + "self_attn.q_proj.weight", cfg.num_attention_heads * D * (2 if cfg.attn_output_gate else 1), H)
         mat(p + "self_attn.k_proj.weight", cfg.num_key_value_heads * D, H)
         mat(p + "self_attn.v_proj.weight", cfg.num_key_value_heads * D, H)
@@ -591,9 +618,12 @@ def _random_ffn(cfg, li, p, mat) -> None:
     if cfg.layer_is_moe(li):
         mat(p + "mlp.gate.weight", cfg.num_experts, H)
         if cfg.shared_expert_intermediate_size > 0:
+            shared = "shared_experts" if cfg.model_type == "deepseek_v3" else "shared_expert"
             for n, shape in (("gate", (cfg.shared_expert_intermediate_size, H)), ("up", (cfg.shared_expert_intermediate_size, H)),
                              ("down", (H, cfg.shared_expert_intermediate_size))):
-                mat(p + f"mlp.shared_expert.{n}_proj.weight", *shape)
+                mat(p + f"mlp.{shared}.{n}_proj.weight", *shape)
+            if cfg.model_type == "deepseek_v3":
+                mat(p + "mlp.gate.e_score_correction_bias", cfg.num_experts)
             if cfg.shared_expert_gate:
                 mat(p + "mlp.shared_expert_gate.weight", 1, H)
         if cfg.extra.get("use_expert_bias"):

@@ -177,13 +177,15 @@ def make_moe_factory(src=None, router_std_scale: bool = False):
         gu = gu.to(device=dev, dtype=dt).contiguous()
         dn = dn.to(device=dev, dtype=dt).contiguous()
         shared = None
-        if has(p + "shared_expert.gate_proj.weight"):
-            sgu = torch.cat((get(p + "shared_expert.gate_proj.weight"), get(p + "shared_expert.up_proj.weight")), 0)
-            shared = (sgu.to(device=dev, dtype=dt).contiguous(),
-                      get(p + "shared_expert.down_proj.weight").to(device=dev, dtype=dt).contiguous())
+        for sh in ("shared_expert", "shared_experts"):      # Qwen / DeepSeek spellings
+            if has(p + f"{sh}.gate_proj.weight"):
+                sgu = torch.cat((get(p + f"{sh}.gate_proj.weight"), get(p + f"{sh}.up_proj.weight")), 0)
+                shared = (sgu.to(device=dev, dtype=dt).contiguous(),
+                          get(p + f"{sh}.down_proj.weight").to(device=dev, dtype=dt).contiguous())
         sel_bias = None
-        if has(p + "expert_bias"):   # LFM2-MoE: added to the scores for the selection only
-            sel_bias = get(p + "expert_bias").to(device=dev, dtype=torch.float32).contiguous()
+        for name in ("expert_bias", "gate.e_score_correction_bias"):   # LFM2-MoE / DeepSeek: selection-only score bias
+            if has(p + name):
+                sel_bias = get(p + name).to(device=dev, dtype=torch.float32).contiguous()
         shared_gate = None
         if has(p + "shared_expert_gate.weight"):
             shared_gate = get(p + "shared_expert_gate.weight").to(device=dev, dtype=dt).contiguous()

@@ -58,8 +58,9 @@ class Engine:
         local = range(model.first_layer, model.last_layer)
         conv_layers = [li for li in local if self.cfg.layer_is_conv(li)]
         kv_layers = [li for li in local if self.cfg.layer_has_kv(li)]
-        self.kv = PagedKVCache(model.num_local_layers(), model.n_kv_local, self.cfg.head_dim, num_pages, model.dtype,
-                               self.device, first_layer=model.first_layer,
+        _, key_dim, value_dim = self.cfg.kv_cache_dims
+        self.kv = PagedKVCache(model.num_local_layers(), model.n_kv_local, key_dim, num_pages, model.dtype,
+                               self.device, first_layer=model.first_layer, value_dim=value_dim,
                                attention_layers=kv_layers,
                                conv_layers=conv_layers,
                                conv_channels=self.cfg.hidden_size // model.par.tp_size if conv_layers else 0,
@@ -411,7 +412,7 @@ class Engine:
     def _host_driven(self) -> bool:
         """True when a forward pass needs the host between kernels (layerwise host residency, expert cache)."""
         m = self.model
-        if self.cfg.head_dim not in (64, 128):
+        if self.cfg.head_dim not in (64, 128) or self.cfg.is_mla:
             return True    # no attention kernel for this head size: the tensor-operation path reads lengths on the host
         if getattr(m, "residency", None) is not None or getattr(getattr(m, "inner", m), "observer", None) is not None:
             return True

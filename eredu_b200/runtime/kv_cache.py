@@ -8,6 +8,8 @@ Page 0 is never handed out: padded block-table entries point at it.
 """
 from __future__ import annotations
 
+from typing import Optional
+
 import torch
 
 PAGE = 16
@@ -37,7 +39,8 @@ class PageAllocator:
 
 class PagedKVCache:
     def __init__(self, n_layers: int, n_kv_heads: int, head_dim: int, num_pages: int, dtype, device,
-                 first_layer: int = 0, attention_layers=None, conv_layers=None, conv_channels: int = 0, conv_hist: int = 0):
+                 first_layer: int = 0, attention_layers=None, conv_layers=None, conv_channels: int = 0, conv_hist: int = 0,
+                 value_dim: Optional[int] = None):
         """``attention_layers`` / ``conv_layers``: global indices of the layers that keep K/V pages respectively a
         short-convolution state (hybrid models); by default every one of the ``n_layers`` layers keeps K/V.
         The convolution state pool [layer, page, conv_hist, channels] is indexed by a sequence's first page."""
@@ -49,7 +52,9 @@ class PagedKVCache:
         self._kv_index = {li: i for i, li in enumerate(attention_layers)}
         self.n_layers = len(attention_layers)
         self.k = torch.zeros((self.n_layers, num_pages, n_kv_heads, PAGE, head_dim), dtype=dtype, device=device)
-        self.v = torch.zeros_like(self.k)
+        # latent-attention models cache one row per token in ``k`` and nothing in ``v`` (value_dim 1 keeps the plumbing)
+        self.v = torch.zeros_like(self.k) if value_dim in (None, head_dim) else \
+            torch.zeros((self.n_layers, num_pages, n_kv_heads, PAGE, value_dim), dtype=dtype, device=device)
         self._conv_index = {li: i for i, li in enumerate(conv_layers or [])}
         self.conv_state = None
         if self._conv_index:
@@ -129,7 +134,7 @@ class PagedKVCache:
         extra = self.conv_state.numel() * self.conv_state.element_size() if self.conv_state is not None else 0
         if self.la_rec_state is not None:
             extra += self.la_rec_state.numel() * 4 + self.la_conv_state.numel() * self.la_conv_state.element_size()
-        return 2 * self.k.numel() * self.k.element_size() + extra
+        return (self.k.numel() + self.v.numel()) * self.k.element_size() + extra
 
     @staticmethod
     def pages_for(tokens: int) -> int:

@@ -59,7 +59,8 @@ class KVHostTier:
     # ------------------------------------------------------------------------------------------ accounting
     def page_bytes(self) -> int:
         k = self.kv.k
-        return 2 * k.shape[0] * k.shape[2] * k.shape[3] * k.shape[4] * k.element_size()
+        v = self.kv.v
+        return (k.shape[0] * k.shape[2] * k.shape[3] * k.shape[4] + v.shape[0] * v.shape[2] * v.shape[3] * v.shape[4]) * k.element_size()
 
     def touch(self, seq) -> None:
         self._clock += 1
@@ -91,7 +92,7 @@ class KVHostTier:
         shape = (self.kv.k.shape[0], used) + tuple(self.kv.k.shape[2:])
         pin = self.cuda
         k_host = torch.empty(shape, dtype=self.kv.k.dtype, pin_memory=pin)
-        v_host = torch.empty(shape, dtype=self.kv.v.dtype, pin_memory=pin)
+        v_host = torch.empty((self.kv.v.shape[0], used) + tuple(self.kv.v.shape[2:]), dtype=self.kv.v.dtype, pin_memory=pin)
         event = None
         if used:
             k_stage = self.kv.k.index_select(1, idx)     # gather on the compute stream: ordered after the last step

@@ -21,7 +21,7 @@ from ..models.config import DENSE_TYPES, MOE_TYPES, ModelConfig
 
 EXECUTION_PLAN_SCHEMA_VERSION = 2
 DEFAULT_MAX_MAPPED_SHARDS = 4
-SUPPORTED_TYPES = DENSE_TYPES | {"qwen3_moe", "mixtral", "gpt_oss", "lfm2_moe", "qwen3_next", "qwen3_5_moe", "nemotron_h"}
+SUPPORTED_TYPES = DENSE_TYPES | {"qwen3_moe", "mixtral", "gpt_oss", "lfm2_moe", "qwen3_next", "qwen3_5_moe", "nemotron_h", "deepseek_v3"}
 
 
 # ---------------------------------------------------------------------------------------------- inspection
@@ -157,6 +157,8 @@ def estimate_runtime_state(cfg: ModelConfig, weight_bytes: Optional[int] = None,
     stateful = [li for li in range(L) if cfg.layer_is_conv(li) or cfg.layer_has_recurrent_state(li)]
     attn_layers = sum(1 for li in range(L) if cfg.layer_has_kv(li))
     kv_tok = 2 * cfg.num_key_value_heads * D * cache_dtype_bytes * attn_layers
+    if cfg.is_mla:   # one compressed latent + rotary key per token and layer, shared by the heads
+        kv_tok = (cfg.kv_lora_rank + cfg.qk_rope_head_dim) * cache_dtype_bytes * attn_layers
     state = 0
     for li in stateful:
         if cfg.layer_is_conv(li):

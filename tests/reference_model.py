@@ -55,6 +55,10 @@ def forward_logits(cfg, sd, tokens, moe_fn=None):
             h = h + F.linear(pj[:, Cc:2 * Cc] * y, sd[p + "conv.out_proj.weight"], sd.get(p + "conv.out_proj.bias"))
             h = _ffn(cfg, sd, li, p, h, moe_fn)
             continue
+        if cfg.is_mla:
+            h = h + _mla_attention(cfg, sd, p + "self_attn.", x, pos, inv, factor)
+            h = _ffn(cfg, sd, li, p, h, moe_fn)
+            continue
         gate = None
         if cfg.attn_output_gate:
             qg = F.linear(x, sd[p + "self_attn.q_proj.weight"]).view(T, Hq, 2 * D)
@@ -89,6 +93,34 @@ def forward_logits(cfg, sd, tokens, moe_fn=None):
     x = rms(h, sd["model.norm.weight"], cfg.rms_norm_eps, cfg.norm_weight_offset)
     head = sd.get("lm_head.weight", sd["model.embed_tokens.weight"])
     return F.linear(x, head)
+
+
+def _mla_attention(cfg, sd, a, x, pos, inv, factor):
+    """DeepSeek latent attention in the plain (decompressed) form: per-head keys and values are materialised."""
+    T = x.shape[0]
+    Hq, nope, rp, vd = cfg.num_attention_heads, cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim
+    if cfg.q_lora_rank:
+        q = F.linear(rms(F.linear(x, sd[a + "q_a_proj.weight"]), sd[a + "q_a_layernorm.weight"], cfg.rms_norm_eps),
+                     sd[a + "q_b_proj.weight"])
+    else:
+        q = F.linear(x, sd[a + "q_proj.weight"])
+    q = q.view(T, Hq, nope + rp)
+    ckv = F.linear(x, sd[a + "kv_a_proj_with_mqa.weight"])
+    c, k_pe = ckv[:, :cfg.kv_lora_rank], ckv[:, cfg.kv_lora_rank:].view(T, 1, rp)
+    kv = F.linear(rms(c, sd[a + "kv_a_layernorm.weight"], cfg.rms_norm_eps), sd[a + "kv_b_proj.weight"]).view(T, Hq, nope + vd)
+    k_nope, v = kv[..., :nope], kv[..., nope:]
+    q_pe = rope(q[..., nope:], pos, inv, factor, cfg.rope_traditional, rp)
+    k_pe = rope(k_pe, pos, inv, factor, cfg.rope_traditional, rp)
+    qf = torch.cat((q[..., :nope], q_pe), -1)
+    kf = torch.cat((k_nope, k_pe.expand(T, Hq, rp)), -1)
+    sc = cfg.rope_scaling or {}
+    mult = 1.0
+    if sc.get("mscale_all_dim") and float(sc.get("factor", 1.0)) > 1.0:
+        mult = (0.1 * float(sc["mscale_all_dim"]) * math.log(float(sc["factor"])) + 1.0) ** 2
+    s_ = torch.einsum("qhd,khd->hqk", qf, kf) * ((nope + rp) ** -0.5 * mult)
+    s_ = s_.masked_fill(~(pos[None, :] <= pos[:, None])[None], float("-inf"))
+    o = torch.einsum("hqk,khd->qhd", torch.softmax(s_, -1), v).reshape(T, Hq * vd)
+    return F.linear(o, sd[a + "o_proj.weight"])
 
 
 def _nemotron_mixer(cfg, sd, li, p, x, moe_fn):

@@ -216,7 +216,7 @@ def test_moe_block_and_expert_cache_dry_run(dry_cuda):
     assert blk(x, residual=x).shape == (4, H)
 
 
-@pytest.mark.parametrize("family", ["llama", "qwen3_moe", "gpt_oss", "lfm2", "qwen3_next", "nemotron_h"])
+@pytest.mark.parametrize("family", ["llama", "qwen3_moe", "gpt_oss", "lfm2", "qwen3_next", "nemotron_h", "deepseek_v3"])
 def test_whole_model_forward_dry_run(dry_cuda, family):
     """Prefill and decode passes of every family through the CUDA branches of the operator wrappers (stub library,
     CPU tensors): argument kinds, shapes the wrappers assert on, and the Python glue between kernels."""
@@ -252,6 +252,13 @@ def test_whole_model_forward_dry_run(dry_cuda, family):
 
         cfg = lfm2_cfg(hidden_size=256, intermediate_size=512, num_attention_heads=4, num_key_value_heads=2, vocab_size=512)
         sd = random_state(cfg, seed=0)
+    elif family == "deepseek_v3":
+        from test_deepseek import ds_cfg, state_for as ds_state
+
+        cfg = ds_cfg(hidden_size=256, vocab_size=512, kv_lora_rank=64, qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32,
+                     q_lora_rank=64)
+        sd = ds_state(cfg)
+        kw["moe_factory"] = make_moe_factory()
     elif family == "nemotron_h":
         from test_nemotron_h import nh_cfg, state_for as nh_state
 
@@ -277,8 +284,10 @@ def test_whole_model_forward_dry_run(dry_cuda, family):
     outs = eng.generate([list(range(3, 9)), list(range(4, 15))], SamplingParams(temperature=0.0), 3)   # decode-shaped passes
     assert [len(o) for o in outs] == [3, 3]
     calls = set(dry_cuda.calls)
-    assert {"eredu_gemm_bf16", "eredu_rmsnorm", "eredu_attn_prefill", "eredu_attn_decode", "eredu_rope_kv"} <= calls
-    if family in ("qwen3_moe", "gpt_oss", "qwen3_next", "nemotron_h"):
+    assert {"eredu_gemm_bf16", "eredu_rmsnorm"} <= calls
+    if family != "deepseek_v3":     # latent attention has no kernel: tensor operations around the GEMMs
+        assert {"eredu_attn_prefill", "eredu_attn_decode", "eredu_rope_kv"} <= calls
+    if family in ("qwen3_moe", "gpt_oss", "qwen3_next", "nemotron_h", "deepseek_v3"):
         assert "eredu_gemm_bf16_grouped" in calls
     if family in ("lfm2", "nemotron_h"):
         assert "eredu_short_conv" in calls
