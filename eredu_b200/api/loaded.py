@@ -101,6 +101,10 @@ class LoadedModel:
             from ..models.lfm2 import canonical_access
 
             get, has = canonical_access(get, has)
+        elif src.cfg.model_type == "kimi_linear":
+            from ..models.kimi_linear import canonical_access
+
+            get, has = canonical_access(get, has)
         elif src.cfg.model_type == "nemotron_h":
             from ..models.nemotron_h import canonical_access
 

@@ -119,6 +119,9 @@ class ModelConfig:
         """LFM2 hybrid schedule: the layer's operator is the gated short convolution instead of attention."""
         return self.layer_types is not None and self.layer_types[layer] == "conv"
 
+    def layer_is_kda(self, layer: int) -> bool:
+        return self.layer_types is not None and self.layer_types[layer] == "kda"
+
     def layer_is_linear_attention(self, layer: int) -> bool:
         """Qwen3-Next style schedule: the layer's operator is a gated delta network instead of softmax attention."""
         return self.layer_types is not None and self.layer_types[layer] == "linear_attention"
@@ -133,11 +136,11 @@ class ModelConfig:
         return self.layer_types[layer] in ("full_attention", "sliding_attention", "attention_only")
 
     def layer_has_recurrent_state(self, layer: int) -> bool:
-        return self.layer_types is not None and self.layer_types[layer] in ("linear_attention", "mamba")
+        return self.layer_types is not None and self.layer_types[layer] in ("linear_attention", "mamba", "kda")
 
     @property
     def is_hybrid(self) -> bool:
-        return self.layer_types is not None and any(t in ("conv", "linear_attention", "mamba") for t in self.layer_types)
+        return self.layer_types is not None and any(t in ("conv", "linear_attention", "mamba", "kda") for t in self.layer_types)
 
     def layer_window(self, layer: int) -> int:
         if self.sliding_window is None or self.sliding_window <= 0:
@@ -161,12 +164,27 @@ class ModelConfig:
                                "qwen3_5_moe": "Qwen3_5MoeForCausalLM"}.get(self.model_type, "LlamaForCausalLM")]
         for k in ("mamba_n_groups", "mamba_conv_kernel", "mamba_conv_bias", "use_rope"):
             d.pop(k, None)
+        if self.model_type == "kimi_linear":
+            d["linear_attn_config"] = {
+                "kda_layers": [i + 1 for i, t in enumerate(self.layer_types) if t == "kda"],
+                "full_attn_layers": [i + 1 for i, t in enumerate(self.layer_types) if t != "kda"],
+                "num_heads": self.linear_num_value_heads, "head_dim": self.linear_value_head_dim,
+                "short_conv_kernel_size": self.linear_conv_kernel_dim}
+            d.pop("layer_types", None)
+            dense = [i for i in range(self.num_hidden_layers) if i in self.mlp_only_layers]
+            first = next((i for i in range(self.num_hidden_layers) if i not in dense), self.num_hidden_layers)
+            d.update(mla_use_nope=True, num_experts_per_token=self.num_experts_per_tok, moe_renormalize=self.norm_topk_prob,
+                     num_shared_experts=(self.shared_expert_intermediate_size // max(1, self.moe_intermediate_size)),
+                     moe_router_activation_func=self.router_scoring, num_expert_group=self.n_group, topk_group=self.topk_group,
+                     use_grouped_topk=self.n_group > 1, first_k_dense_replace=first, moe_layer_freq=1)
+            d.pop("head_dim", None)
+            d.pop("mlp_only_layers", None)
         if self.model_type == "deepseek_v3":
             d.update(n_routed_experts=self.num_experts, first_k_dense_replace=len(self.mlp_only_layers),
                      n_shared_experts=(self.shared_expert_intermediate_size // max(1, self.moe_intermediate_size)),
                      scoring_func=self.router_scoring, rope_interleave=self.rope_traditional, architectures=["DeepseekV3ForCausalLM"])
             d.pop("head_dim", None)
-        else:
+        elif self.model_type != "kimi_linear":
             for k in ("q_lora_rank", "kv_lora_rank", "qk_nope_head_dim", "qk_rope_head_dim", "v_head_dim"):
                 d.pop(k, None)
         if self.model_type == "nemotron_h":
@@ -181,7 +199,7 @@ class ModelConfig:
         else:
             for k in ("mamba_num_heads", "mamba_head_dim", "ssm_state_size", "mamba_proj_bias", "time_step_min"):
                 d.pop(k, None)
-        if self.model_type not in QWEN_HYBRID_TYPES:
+        if self.model_type not in QWEN_HYBRID_TYPES and self.model_type != "kimi_linear":
             for k in ("linear_conv_kernel_dim", "linear_key_head_dim", "linear_value_head_dim", "linear_num_key_heads",
                       "linear_num_value_heads"):
                 d.pop(k, None)
@@ -262,6 +280,40 @@ class ModelConfig:
             bos_token_id=d.get("bos_token_id"),
             torch_dtype=str(d.get("torch_dtype", d.get("dtype", "bfloat16"))),
         )
+        if mt == "kimi_linear":
+            # eredu/src/backend/mlx/architectures/kimi_linear/model.rs:160-235 (source keys), :330-450 (schedule)
+            la = d.get("linear_attn_config") or {}
+            kda = {int(i) - 1 for i in la.get("kda_layers", [])}                       # the lists are 1-based
+            full = {int(i) - 1 for i in la.get("full_attn_layers", [])}
+            L = cfg.num_hidden_layers
+            if (kda | full) != set(range(L)) or (kda & full):
+                raise ValueError("Kimi Linear kda_layers and full_attn_layers must partition the layers")
+            cfg.layer_types = ["kda" if i in kda else "full_attention" for i in range(L)]
+            cfg.linear_num_value_heads = cfg.linear_num_key_heads = int(la.get("num_heads", cfg.num_attention_heads))
+            cfg.linear_value_head_dim = cfg.linear_key_head_dim = int(la.get("head_dim", cfg.head_dim))
+            cfg.linear_conv_kernel_dim = int(la.get("short_conv_kernel_size", 4))
+            if not bool(d.get("mla_use_nope", False)):
+                raise ValueError("Kimi Linear currently requires mla_use_nope=true")
+            cfg.use_rope = False
+            cfg.q_lora_rank = int(d.get("q_lora_rank") or 0)
+            cfg.kv_lora_rank = int(d.get("kv_lora_rank", 512))
+            cfg.qk_nope_head_dim = int(d.get("qk_nope_head_dim", 128))
+            cfg.qk_rope_head_dim = int(d.get("qk_rope_head_dim", 64))
+            cfg.v_head_dim = int(d.get("v_head_dim", 128))
+            cfg.head_dim = cfg.qk_nope_head_dim + cfg.qk_rope_head_dim
+            cfg.num_key_value_heads = cfg.num_attention_heads
+            cfg.num_experts_per_tok = int(d.get("num_experts_per_token", d.get("num_experts_per_tok", 0)) or 0)
+            shared = int(d.get("num_shared_experts", d.get("n_shared_experts", 1)) or 0)
+            cfg.shared_expert_intermediate_size = cfg.moe_intermediate_size * shared if cfg.num_experts else 0
+            cfg.router_scoring = {"sigmoid": "sigmoid", "softmax": "softmax"}[d.get("moe_router_activation_func", "sigmoid")]
+            cfg.norm_topk_prob = bool(d.get("moe_renormalize", True))
+            if bool(d.get("use_grouped_topk", True)):
+                cfg.n_group = int(d.get("num_expert_group", d.get("n_group", 1)) or 1)
+                cfg.topk_group = int(d.get("topk_group", 1) or 1)
+            first, freq = int(d.get("first_k_dense_replace", 0) or 0), int(d.get("moe_layer_freq", 1) or 1)
+            cfg.mlp_only_layers = [i for i in range(L) if not (cfg.num_experts and i >= first and i % freq == 0)]
+            cfg.decoder_sparse_step = 1
+            cfg.tie_word_embeddings = bool(d.get("tie_word_embeddings", False))
         if mt == "deepseek_v3":
             # eredu/src/backend/mlx/architectures/deepseek_v3/model.rs:339-403: latent attention, dense-then-sparse
             # schedule, sigmoid router with correction bias and group-limited top-k, shared experts

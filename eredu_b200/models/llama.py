@@ -74,6 +74,14 @@ class LayerWeights:
     m_norm_w: Optional[torch.Tensor] = None
     m_out: Optional[torch.Tensor] = None
     m_out_b: Optional[torch.Tensor] = None
+    # Kimi Delta Attention: kda_in = [q | k | v | f_a | b | g_a] rows; fold_attn then refers to kda_in
+    kda_in: Optional[torch.Tensor] = None
+    kda_conv_w: Optional[torch.Tensor] = None
+    kda_f_b: Optional[torch.Tensor] = None
+    kda_g_b: Optional[torch.Tensor] = None
+    kda_A_log: Optional[torch.Tensor] = None
+    kda_dt_bias: Optional[torch.Tensor] = None
+    kda_o_norm: Optional[torch.Tensor] = None
     # DeepSeek latent attention: mla_in = [q_a (or q) | kv_a] rows; fold_attn then refers to mla_in
     mla_in: Optional[torch.Tensor] = None
     mla_q_norm: Optional[torch.Tensor] = None
@@ -200,6 +208,11 @@ class CausalLM:
                                batch.max_q_len)
             h, ssq = self._row_linear_ssq(lw, "conv_out", y, lw.conv_out, h, lw.conv_out_b, lw.fold_ffn)
             return self._ffn(lw, h, ssq, next_folded)
+        if lw.kda_in is not None:
+            from .kimi_linear import kda_forward
+
+            h, ssq = kda_forward(self, li, lw, h, ssq, batch, kv)
+            return self._ffn(lw, h, ssq, next_folded)
         if lw.mla_in is not None:
             from .deepseek import mla_forward
 
@@ -324,6 +337,9 @@ class CausalLM:
         if "qkv" not in lw.qlin and not lw.fold_attn and lw.wqkv is not None:
             lw.wqkv = (lw.wqkv.float() * (lw.attn_norm + off)[None, :]).to(self.dtype).contiguous()
             lw.fold_attn = True
+        if "kda_in" not in lw.qlin and not lw.fold_attn and lw.kda_in is not None:
+            lw.kda_in = (lw.kda_in.float() * (lw.attn_norm + off)[None, :]).to(self.dtype).contiguous()
+            lw.fold_attn = True
         if "mla_in" not in lw.qlin and not lw.fold_attn and lw.mla_in is not None:
             lw.mla_in = (lw.mla_in.float() * (lw.attn_norm + off)[None, :]).to(self.dtype).contiguous()
             lw.fold_attn = True
@@ -432,8 +448,12 @@ def build_from_tensors(cfg: ModelConfig, get: Callable[[str], torch.Tensor], has
             if on_layer is not None:
                 on_layer(model, li, lw)
             continue
-        if cfg.layer_is_conv(li) or cfg.layer_is_linear_attention(li) or cfg.is_mla:
-            if cfg.is_mla:
+        if cfg.layer_is_conv(li) or cfg.layer_is_linear_attention(li) or cfg.is_mla or cfg.layer_is_kda(li):
+            if cfg.layer_is_kda(li):
+                from .kimi_linear import build_kda_layer
+
+                lw = build_kda_layer(model, cfg, p, get, has, up)
+            elif cfg.is_mla:
                 from .deepseek import build_mla_layer
 
                 lw = build_mla_layer(model, cfg, p, get, has, up)
@@ -592,6 +612,12 @@ def random_state(cfg: ModelConfig, seed: int = 0, std: float = 0.02, dtype=torch
                 mat(p + "conv.out_proj.bias", H)
             _random_ffn(cfg, li, p, mat)
             continue
+        if cfg.layer_is_kda(li):
+            from .kimi_linear import random_kda_state
+
+            random_kda_state(cfg, p, mat, ones, out, std)
+            _random_ffn(cfg, li, p, mat)
+            continue
         if cfg.is_mla:
             from .deepseek import random_mla_state
 
@@ -618,11 +644,11 @@ def _random_ffn(cfg, li, p, mat) -> None:
     if cfg.layer_is_moe(li):
         mat(p + "mlp.gate.weight", cfg.num_experts, H)
         if cfg.shared_expert_intermediate_size > 0:
-            shared = "shared_experts" if cfg.model_type == "deepseek_v3" else "shared_expert"
+            shared = "shared_experts" if cfg.model_type in ("deepseek_v3", "kimi_linear") else "shared_expert"
             for n, shape in (("gate", (cfg.shared_expert_intermediate_size, H)), ("up", (cfg.shared_expert_intermediate_size, H)),
                              ("down", (H, cfg.shared_expert_intermediate_size))):
                 mat(p + f"mlp.{shared}.{n}_proj.weight", *shape)
-            if cfg.model_type == "deepseek_v3":
+            if cfg.model_type in ("deepseek_v3", "kimi_linear"):
                 mat(p + "mlp.gate.e_score_correction_bias", cfg.num_experts)
             if cfg.shared_expert_gate:
                 mat(p + "mlp.shared_expert_gate.weight", 1, H)

@@ -147,7 +147,7 @@ def make_moe_factory(src=None, router_std_scale: bool = False):
         dev, dt = model.device, model.dtype
         e0, e1 = par.expert_range(cfg.num_experts) if par.ep_size > 1 else (0, cfg.num_experts)
         mx = f"model.layers.{li}.block_sparse_moe."   # Mixtral naming: w1 = gate, w3 = up, w2 = down
-        if has(mx + "gate.weight"):
+        if has(mx + "gate.weight") and not has(p + "gate.weight"):
             router = get(mx + "gate.weight").to(device=dev, dtype=dt).contiguous()
             gu = torch.stack([torch.cat((get(mx + f"experts.{e}.w1.weight"), get(mx + f"experts.{e}.w3.weight")), 0)
                               for e in range(e0, e1)], 0).to(device=dev, dtype=dt).contiguous()

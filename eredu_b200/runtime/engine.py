@@ -73,6 +73,13 @@ class Engine:
             self.kv.enable_linear_attention_state(mamba_layers, slots=max(2 * max_batch, 8),
                                                   conv_hist=self.cfg.mamba_conv_kernel - 1, conv_channels=conv_dim, heads=heads,
                                                   dk=self.cfg.mamba_head_dim, dv=self.cfg.ssm_state_size)
+        kda_layers = [li for li in local if self.cfg.layer_is_kda(li)]
+        if kda_layers:
+            c = self.cfg
+            self.kv.enable_linear_attention_state(kda_layers, slots=max(2 * max_batch, 8), conv_hist=c.linear_conv_kernel_dim - 1,
+                                                  conv_channels=3 * c.linear_num_value_heads * c.linear_value_head_dim,
+                                                  heads=c.linear_num_value_heads, dk=c.linear_value_head_dim,
+                                                  dv=c.linear_value_head_dim)
         la_layers = [li for li in local if self.cfg.layer_is_linear_attention(li)]
         if la_layers:
             c = self.cfg

@@ -21,7 +21,7 @@ from ..models.config import DENSE_TYPES, MOE_TYPES, ModelConfig
 
 EXECUTION_PLAN_SCHEMA_VERSION = 2
 DEFAULT_MAX_MAPPED_SHARDS = 4
-SUPPORTED_TYPES = DENSE_TYPES | {"qwen3_moe", "mixtral", "gpt_oss", "lfm2_moe", "qwen3_next", "qwen3_5_moe", "nemotron_h", "deepseek_v3"}
+SUPPORTED_TYPES = DENSE_TYPES | {"qwen3_moe", "mixtral", "gpt_oss", "lfm2_moe", "qwen3_next", "qwen3_5_moe", "nemotron_h", "deepseek_v3", "kimi_linear"}
 
 
 # ---------------------------------------------------------------------------------------------- inspection
@@ -163,6 +163,10 @@ def estimate_runtime_state(cfg: ModelConfig, weight_bytes: Optional[int] = None,
     for li in stateful:
         if cfg.layer_is_conv(li):
             state += (cfg.conv_l_cache - 1) * H * cache_dtype_bytes
+        elif cfg.layer_is_kda(li):
+            P_ = cfg.linear_num_value_heads * cfg.linear_value_head_dim
+            state += (cfg.linear_conv_kernel_dim - 1) * 3 * P_ * cache_dtype_bytes
+            state += cfg.linear_num_value_heads * cfg.linear_value_head_dim ** 2 * 4
         elif cfg.layer_is_mamba(li):
             inter = cfg.mamba_num_heads * cfg.mamba_head_dim
             state += (cfg.mamba_conv_kernel - 1) * (inter + 2 * cfg.mamba_n_groups * cfg.ssm_state_size) * cache_dtype_bytes

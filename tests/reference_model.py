@@ -32,6 +32,8 @@ def forward_logits(cfg, sd, tokens, moe_fn=None):
     T = len(tokens)
     D, Hq, Hkv = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads
     inv, factor = rope_tables(cfg)
+    if not cfg.use_rope:
+        inv = torch.zeros_like(inv)
     pos = torch.arange(T)
     h = sd["model.embed_tokens.weight"][torch.tensor(tokens)] * cfg.embedding_scale
     for li in range(cfg.num_hidden_layers):
@@ -53,6 +55,10 @@ def forward_logits(cfg, sd, tokens, moe_fn=None):
             y = F.conv1d(F.pad(bx, (L - 1, 0)), sd[p + "conv.conv.weight"].view(Cc, 1, L), sd.get(p + "conv.conv.bias"),
                          groups=Cc)[0].t()
             h = h + F.linear(pj[:, Cc:2 * Cc] * y, sd[p + "conv.out_proj.weight"], sd.get(p + "conv.out_proj.bias"))
+            h = _ffn(cfg, sd, li, p, h, moe_fn)
+            continue
+        if cfg.layer_is_kda(li):
+            h = h + _kda_layer(cfg, sd, p + "self_attn.", x)
             h = _ffn(cfg, sd, li, p, h, moe_fn)
             continue
         if cfg.is_mla:
@@ -93,6 +99,37 @@ def forward_logits(cfg, sd, tokens, moe_fn=None):
     x = rms(h, sd["model.norm.weight"], cfg.rms_norm_eps, cfg.norm_weight_offset)
     head = sd.get("lm_head.weight", sd["model.embed_tokens.weight"])
     return F.linear(x, head)
+
+
+def _kda_layer(cfg, sd, a, x):
+    """Kimi Delta Attention over a whole sequence: per-channel decay, token by token."""
+    T = x.shape[0]
+    H, D, K = cfg.linear_num_value_heads, cfg.linear_value_head_dim, cfg.linear_conv_kernel_dim
+    P = H * D
+
+    def conv_silu(name):
+        y = F.linear(x, sd[a + f"{name}_proj.weight"])
+        return F.silu(F.conv1d(F.pad(y.t()[None], (K - 1, 0)), sd[a + f"{name}_conv1d.weight"].view(P, 1, K), groups=P)[0].t())
+
+    def rms_scaled(t, scale):
+        t = t.view(T, H, D)
+        return t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + 1e-6) * scale
+
+    q, k, v = rms_scaled(conv_silu("q"), 1.0 / D), rms_scaled(conv_silu("k"), D ** -0.5), conv_silu("v").view(T, H, D)
+    logits = F.linear(F.linear(x, sd[a + "f_a_proj.weight"]), sd[a + "f_b_proj.weight"]).view(T, H, D)
+    g = -torch.exp(sd[a + "A_log"].view(1, H, 1)) * F.softplus(logits + sd[a + "dt_bias"].view(1, H, D))
+    beta = torch.sigmoid(F.linear(x, sd[a + "b_proj.weight"]))
+    S = torch.zeros(H, D, D)
+    outs = []
+    for t in range(T):
+        S = S * torch.exp(g[t])[:, :, None]
+        mem = torch.einsum("hkv,hk->hv", S, k[t])
+        S = S + torch.einsum("hk,hv->hkv", k[t], (v[t] - mem) * beta[t][:, None])
+        outs.append(torch.einsum("hkv,hk->hv", S, q[t]))
+    o = torch.stack(outs)
+    o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + cfg.rms_norm_eps) * sd[a + "o_norm.weight"]
+    gate = torch.sigmoid(F.linear(F.linear(x, sd[a + "g_a_proj.weight"]), sd[a + "g_b_proj.weight"])).view(T, H, D)
+    return F.linear((o * gate).reshape(T, P), sd[a + "o_proj.weight"])
 
 
 def _mla_attention(cfg, sd, a, x, pos, inv, factor):

@@ -216,7 +216,7 @@ def test_moe_block_and_expert_cache_dry_run(dry_cuda):
     assert blk(x, residual=x).shape == (4, H)
 
 
-@pytest.mark.parametrize("family", ["llama", "qwen3_moe", "gpt_oss", "lfm2", "qwen3_next", "nemotron_h", "deepseek_v3"])
+@pytest.mark.parametrize("family", ["llama", "qwen3_moe", "gpt_oss", "lfm2", "qwen3_next", "nemotron_h", "deepseek_v3", "kimi_linear"])
 def test_whole_model_forward_dry_run(dry_cuda, family):
     """Prefill and decode passes of every family through the CUDA branches of the operator wrappers (stub library,
     CPU tensors): argument kinds, shapes the wrappers assert on, and the Python glue between kernels."""
@@ -259,6 +259,14 @@ def test_whole_model_forward_dry_run(dry_cuda, family):
                      q_lora_rank=64)
         sd = ds_state(cfg)
         kw["moe_factory"] = make_moe_factory()
+    elif family == "kimi_linear":
+        from test_kimi_linear import kimi_cfg, state_for as kimi_state
+
+        cfg = kimi_cfg(hidden_size=256, vocab_size=512, kv_lora_rank=64, qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32,
+                       linear_attn_config={"kda_layers": [1, 2, 3], "full_attn_layers": [4], "num_heads": 4, "head_dim": 64,
+                                           "short_conv_kernel_size": 4})
+        sd = kimi_state(cfg)
+        kw["moe_factory"] = make_moe_factory()
     elif family == "nemotron_h":
         from test_nemotron_h import nh_cfg, state_for as nh_state
 
@@ -285,11 +293,11 @@ def test_whole_model_forward_dry_run(dry_cuda, family):
     assert [len(o) for o in outs] == [3, 3]
     calls = set(dry_cuda.calls)
     assert {"eredu_gemm_bf16", "eredu_rmsnorm"} <= calls
-    if family != "deepseek_v3":     # latent attention has no kernel: tensor operations around the GEMMs
+    if family not in ("deepseek_v3", "kimi_linear"):     # latent attention has no kernel: tensor operations around the GEMMs
         assert {"eredu_attn_prefill", "eredu_attn_decode", "eredu_rope_kv"} <= calls
-    if family in ("qwen3_moe", "gpt_oss", "qwen3_next", "nemotron_h", "deepseek_v3"):
+    if family in ("qwen3_moe", "gpt_oss", "qwen3_next", "nemotron_h", "deepseek_v3", "kimi_linear"):
         assert "eredu_gemm_bf16_grouped" in calls
     if family in ("lfm2", "nemotron_h"):
         assert "eredu_short_conv" in calls
-    if family == "qwen3_next":
+    if family in ("qwen3_next", "kimi_linear"):
         assert {"eredu_short_conv", "eredu_gated_delta_scan"} <= calls
