@@ -57,6 +57,36 @@ class ModelInspectionReport:
         return d
 
 
+def required_tensors(cfg: ModelConfig) -> list[tuple]:
+    """Tensors whose absence makes a SafeTensors directory unloadable, as tuples of accepted spellings: the embedding,
+    the final norm and the main input projection of the first layer's operator, under the family's own names."""
+    p = "model.layers.0."
+    kind = cfg.layer_types[0] if cfg.layer_types else "full_attention"
+    if cfg.model_type == "nemotron_h":
+        first = {"mamba": "mixer.in_proj.weight", "attention_only": "mixer.q_proj.weight", "mlp_only": "mixer.up_proj.weight",
+                 "moe_only": "mixer.gate.weight"}[kind]
+        names = [("model.embed_tokens.weight",), ("model.norm.weight",), (p + first,)]
+        from ..models.nemotron_h import checkpoint_name
+
+        return [tuple(n for a in alt for n in (checkpoint_name(a), a)) for alt in names]
+    if kind == "conv":
+        first = (p + "conv.in_proj.weight",)
+    elif kind == "linear_attention":
+        first = (p + "linear_attn.in_proj_qkvz.weight", p + "linear_attn.in_proj_qkv.weight")
+    elif kind == "kda":
+        first = (p + "self_attn.f_a_proj.weight",)
+    elif cfg.is_mla:
+        first = (p + "self_attn.kv_a_proj_with_mqa.weight",)
+    else:
+        first = (p + "self_attn.q_proj.weight", p + "self_attn.qkv_proj.weight")
+    names = [("model.embed_tokens.weight",), ("model.norm.weight",), first]
+    if cfg.model_type in ("lfm2", "lfm2_moe"):
+        from ..models.lfm2 import checkpoint_name
+
+        return [tuple(n for a in alt for n in (checkpoint_name(a), a)) for alt in names]
+    return names
+
+
 def inspect_artifact(path) -> ModelInspectionReport:
     """Header-only inspection: no tensor payload is read or mapped."""
     from ..formats.checkpoint import GGML_NAME
@@ -68,7 +98,11 @@ def inspect_artifact(path) -> ModelInspectionReport:
         if not (path / "config.json").exists():
             return ModelInspectionReport(str(path), "safetensors", "unknown", None,
                                          issues=[InspectionIssue("missing_config", "error", "config.json not found")])
-        cfg = ModelConfig.from_pretrained(path)
+        try:
+            cfg = ModelConfig.from_pretrained(path)
+        except Exception as e:    # the config names a family but its fields do not describe a loadable model
+            return ModelInspectionReport(str(path), "safetensors", "unknown", None,
+                                         issues=[InspectionIssue("invalid_config", "error", f"config.json: {e}")])
         try:
             store = H.SafetensorsStore(str(path), 1)
         except Exception as e:
@@ -91,10 +125,9 @@ def inspect_artifact(path) -> ModelInspectionReport:
             if not k.endswith((".scales", ".biases")):
                 bits = (cfg.quantization or {}).get("bits") if (k[:-7] + ".scales") in keys and k.endswith(".weight") else None
                 rep.parameter_count += n * (32 // int(bits)) if bits else n
-        required = ["model.embed_tokens.weight", "model.norm.weight", "model.layers.0.self_attn.q_proj.weight"]
-        for name in required:
-            if name not in keys:
-                issues.append(InspectionIssue("missing_tensor", "error", f"required tensor {name} is absent"))
+        for alternatives in required_tensors(cfg):
+            if not any(name in keys for name in alternatives):
+                issues.append(InspectionIssue("missing_tensor", "error", f"required tensor {alternatives[0]} is absent"))
         if not cfg.tie_word_embeddings and "lm_head.weight" not in keys:
             issues.append(InspectionIssue("missing_tensor", "error", "untied model without lm_head.weight"))
     elif path.is_file():

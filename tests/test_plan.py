@@ -23,7 +23,7 @@ def test_inspection_reports(tmp_path):
     g = P.inspect_artifact(tmp_path / "m.gguf")
     assert g.is_loadable and g.format == "gguf" and g.parameter_count == rep.parameter_count
     # unsupported family and missing tensors are errors, found without touching a payload
-    bad = dataclasses.replace(cfg, model_type="kimi_linear")
+    bad = dataclasses.replace(cfg, model_type="gemma4")
     ck.save_safetensors_checkpoint(tmp_path / "bad", bad, {k: v for k, v in sd.items() if "embed_tokens" not in k}, torch.float32)
     b = P.inspect_artifact(tmp_path / "bad")
     assert not b.is_loadable and {"unsupported_architecture", "missing_tensor"} <= {i.code for i in b.issues}
@@ -97,3 +97,38 @@ def test_hybrid_models_are_inspectable_and_sized_by_their_attention_layers(tmp_p
                                    "layer_types": ["conv", "full_attention", "conv"]})
     p2 = estimate_runtime_state(lf)
     assert p2.kv_bytes_per_token == 2 * 2 * 32 * 2 and p2.state_bytes_per_sequence == 2 * 2 * 64 * 2
+
+
+def test_inspection_knows_every_family_layout(tmp_path):
+    """A freshly written checkpoint of each family inspects as loadable; a malformed config is reported, not raised."""
+    import json
+    import sys
+    from pathlib import Path
+
+    import torch
+
+    from eredu_b200.formats import checkpoint as ck
+    from eredu_b200.models.llama import random_state
+    from eredu_b200.runtime.plan import inspect_artifact
+
+    sys.path.insert(0, str(Path(__file__).parent))
+    from test_deepseek import ds_cfg
+    from test_kimi_linear import kimi_cfg
+    from test_lfm2 import lfm2_cfg
+    from test_nemotron_h import nh_cfg
+    from test_qwen_next import next_cfg
+
+    from eredu_b200.models import lfm2, nemotron_h
+
+    for name, cfg, rename in (("lfm2", lfm2_cfg(), lfm2.to_checkpoint_names), ("qnext", next_cfg(), None),
+                              ("nemotron", nh_cfg(), nemotron_h.to_checkpoint_names), ("dsv3", ds_cfg(), None),
+                              ("kimi", kimi_cfg(), None)):
+        sd = random_state(cfg, seed=0, std=0.05)
+        ck.save_safetensors_checkpoint(tmp_path / name, cfg, rename(sd) if rename else sd, torch.float32)
+        rep = inspect_artifact(tmp_path / name)
+        assert rep.is_loadable, (name, [(i.code, i.message) for i in rep.issues])
+    bad = tmp_path / "bad"
+    bad.mkdir()
+    (bad / "config.json").write_text(json.dumps({"model_type": "kimi_linear", "hidden_size": 64, "num_hidden_layers": 2}))
+    rep = inspect_artifact(bad)
+    assert not rep.is_loadable and rep.issues[0].code == "invalid_config"
