@@ -262,6 +262,12 @@ def main(argv=None) -> int:
                                  hardware=hardware_profile(device), prompt_tokens=res["prompt_tokens"],
                                  generated_tokens=len(res["tokens"]), stop_reason=res["finish_reason"], timing=timing,
                                  weights_bytes=lm.model.weight_bytes(), kv_bytes=lm.engine.kv.bytes())
+        from ..runtime.telemetry import allocator_metrics
+
+        tel.counters["memory"] = allocator_metrics(device)
+        store = getattr(lm.source, "store", None)
+        if store is not None and hasattr(store, "diagnostics"):
+            tel.counters["weight_store"] = dict(store.diagnostics())
         if components is not None:
             tel.counters["components"] = components
         if draft is not None:

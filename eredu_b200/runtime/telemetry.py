@@ -42,6 +42,36 @@ def hardware_profile(device: str = "cpu") -> dict:
     return prof
 
 
+def allocator_metrics(device: str = "cpu") -> dict:
+    """Device allocator and process memory figures after a run (the allocator / process sections of the reference's
+    execution telemetry, eredu-core/src/automatic.rs:360-368; residency.rs:681-760)."""
+    out: dict = {}
+    import torch
+
+    if device.startswith("cuda") and torch.cuda.is_available():
+        st = torch.cuda.memory_stats(device)
+        out["device"] = {"active_bytes": int(st.get("active_bytes.all.current", 0)),
+                         "peak_active_bytes": int(st.get("active_bytes.all.peak", 0)),
+                         "reserved_bytes": int(st.get("reserved_bytes.all.current", 0)),
+                         "peak_reserved_bytes": int(st.get("reserved_bytes.all.peak", 0)),
+                         "allocation_retries": int(st.get("num_alloc_retries", 0))}
+    try:
+        import psutil
+
+        m = psutil.Process().memory_info()
+        out["process"] = {"rss_bytes": int(m.rss), "vms_bytes": int(m.vms)}
+        try:
+            import resource
+
+            ru = resource.getrusage(resource.RUSAGE_SELF)
+            out["process"].update(max_rss_kib=int(ru.ru_maxrss), minor_faults=int(ru.ru_minflt), major_faults=int(ru.ru_majflt))
+        except Exception:
+            pass
+    except Exception:
+        pass
+    return out
+
+
 @dataclass
 class StageTiming:
     name: str

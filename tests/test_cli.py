@@ -47,6 +47,7 @@ def test_cli_end_to_end_cpu(tmp_path, capsys):
     t = json.loads(tel.read_text())
     assert t["generated_tokens"] <= 8 and t["prompt_tokens"] > 0 and t["stop_reason"] in ("max_tokens", "eos")
     assert t["weights_bytes"] > 0 and t["plan"]["device"] == "cpu" and "host" in t["hardware"]
+    assert t["counters"]["memory"]["process"]["rss_bytes"] > 0 and "weight_store" in t["counters"]
 
 
 def test_cli_automatic_plan_and_cache(tmp_path, capsys):
