@@ -97,6 +97,16 @@ class LoadedModel:
         elif opt.weight_residency != "device":
             raise ValueError(f"unknown weight residency {opt.weight_residency!r}")
         get, has = src.get, src.has
+        if src.cfg.extra.get("language_model_prefix") and has("model.language_model.embed_tokens.weight"):
+            # vision-language checkpoint used as a text model: the decoder sits under model.language_model.*, the towers
+            # are not loaded (requests with image / audio / video parts are refused by media.prepare_for_text_model)
+            base_get, base_has = get, has
+
+            def _lm(name):
+                return "model.language_model." + name[len("model."):] if name.startswith("model.") else name
+
+            get = lambda name: base_get(_lm(name)) if base_has(_lm(name)) else base_get(name)      # noqa: E731
+            has = lambda name: base_has(_lm(name)) or base_has(name)                                # noqa: E731
         if src.cfg.model_type in ("lfm2", "lfm2_moe"):
             from ..models.lfm2 import canonical_access
 

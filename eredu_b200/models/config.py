@@ -239,6 +239,10 @@ class ModelConfig:
                     inner[k] = d[k]
             d = inner
             mt = d.get("model_type", mt)
+            # the language model of a vision-language checkpoint is its text family (text-only use of Qwen3-VL)
+            mt = {"qwen3_vl_text": "qwen3", "qwen3_vl_moe_text": "qwen3_moe", "qwen3_vl": "qwen3", "qwen3_vl_moe": "qwen3_moe"}.get(mt, mt)
+            d["model_type"] = mt
+            d["_language_model_prefix"] = True
         heads = int(d.get("num_attention_heads", 32))
         hidden = int(d.get("hidden_size", 4096))
         kv = int(d.get("num_key_value_heads") or 0) or heads
@@ -412,6 +416,8 @@ class ModelConfig:
                     size = int(mult * (2 * size // 3))
                     size = of * ((size + of - 1) // of)
                 cfg.intermediate_size = size
+        if d.get("_language_model_prefix"):
+            cfg.extra["language_model_prefix"] = True   # tensors live under model.language_model.* next to a vision tower
         if mt == "mixtral":
             cfg.moe_intermediate_size = cfg.moe_intermediate_size or cfg.intermediate_size
             cfg.router_scoring = "topk_softmax"

@@ -116,3 +116,33 @@ def test_phi3_fused_projection_checkpoints():
     a = Engine(build_from_tensors(cfg, sd.__getitem__, sd.__contains__, "cpu", torch.float32), 1, 64).generate([prompt], sp, 6)
     b = Engine(build_from_tensors(cfg, fused.__getitem__, fused.__contains__, "cpu", torch.float32), 1, 64).generate([prompt], sp, 6)
     assert a == b
+
+
+def test_vision_language_checkpoint_as_text_model(tmp_path):
+    """Qwen3-VL style directory: nested text_config, decoder under model.language_model.*, a vision tower next to it."""
+    import json
+
+    from eredu_b200.api import LoadedModel, ModelLoadOptions
+    from eredu_b200.formats import checkpoint as ck
+
+    cfg = dataclasses.replace(C.tiny_llama(), model_type="qwen3", qk_norm=True, vocab_size=300, num_hidden_layers=2,
+                              tie_word_embeddings=False, rms_norm_eps=1e-6)
+    sd = random_state(cfg, seed=3, std=0.05)
+    stored = {("model.language_model." + k[len("model."):] if k.startswith("model.") else k): v for k, v in sd.items()}
+    stored["model.visual.patch_embed.proj.weight"] = torch.zeros(8, 3, 2, 2, 2)
+    ck.save_safetensors_checkpoint(tmp_path, cfg, stored, torch.float32)
+    text = json.loads((tmp_path / "config.json").read_text())
+    text["model_type"] = "qwen3_vl_text"
+    text["rope_scaling"] = {"rope_type": "default", "mrope_section": [2, 1, 1], "mrope_interleaved": True}
+    (tmp_path / "config.json").write_text(json.dumps({"model_type": "qwen3_vl", "text_config": text,
+                                                      "vision_config": {"depth": 2}, "tie_word_embeddings": False}))
+    lm = LoadedModel.load(tmp_path, ModelLoadOptions(device="cpu", max_batch=1, max_seq_len=64))
+    assert lm.config.model_type == "qwen3" and lm.config.qk_norm
+    prompt = list(range(5, 22))
+    assert torch.allclose(lm.prefill_logits(prompt), forward_logits(cfg, sd, prompt)[-1], atol=2e-4)
+    from eredu_b200 import media as MM
+    import numpy as np
+
+    req = MM.MultimodalRequest().text("what is this").image(MM.RgbImage(np.zeros((4, 4, 3), np.uint8)))
+    with pytest.raises(MM.MultimodalPreparationError):
+        MM.prepare_for_text_model(req, lm.encode)
