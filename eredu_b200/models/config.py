@@ -243,6 +243,19 @@ class ModelConfig:
             mt = {"qwen3_vl_text": "qwen3", "qwen3_vl_moe_text": "qwen3_moe", "qwen3_vl": "qwen3", "qwen3_vl_moe": "qwen3_moe"}.get(mt, mt)
             d["model_type"] = mt
             d["_language_model_prefix"] = True
+        # Transformers >= 5 writes RoPE settings as one ``rope_parameters`` object (theta inside it; optionally one
+        # object per layer type): fold it back into rope_theta / rope_scaling
+        rp = d.get("rope_parameters")
+        if isinstance(rp, dict) and rp:
+            if "rope_type" not in rp and "rope_theta" not in rp and isinstance(next(iter(rp.values())), dict):
+                rp = rp.get("full_attention") or next(iter(rp.values()))
+            d = dict(d)
+            if rp.get("rope_theta") is not None and d.get("rope_theta") is None:
+                d["rope_theta"] = rp["rope_theta"]
+            if d.get("rope_scaling") is None and rp.get("rope_type", "default") not in ("default", None):
+                d["rope_scaling"] = {k: v for k, v in rp.items() if k != "rope_theta"}
+            if rp.get("partial_rotary_factor") is not None and d.get("partial_rotary_factor") is None:
+                d["partial_rotary_factor"] = rp["partial_rotary_factor"]
         heads = int(d.get("num_attention_heads", 32))
         hidden = int(d.get("hidden_size", 4096))
         kv = int(d.get("num_key_value_heads") or 0) or heads

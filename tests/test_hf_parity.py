@@ -1,0 +1,84 @@
+"""Checkpoint parity against Hugging Face Transformers on CPU: a tiny randomly initialised model of each family is
+written with ``save_pretrained`` and loaded here from that directory; last-position logits must agree. This checks the
+reading of a real ``config.json``, the checkpoint tensor names and the block semantics against an implementation that
+shares no code with this repository."""
+import pytest
+import torch
+
+transformers = pytest.importorskip("transformers")
+
+from eredu_b200.api import LoadedModel, ModelLoadOptions
+
+
+def hf_model(cls_name, cfg_name, **kw):
+    cfg_cls = getattr(transformers, cfg_name)
+    cfg = cfg_cls(**kw)
+    torch.manual_seed(0)
+    model = getattr(transformers, cls_name)(cfg).eval().float()
+    # random initialisers leave norms at one and some biases at zero: perturb everything so that no term is silent
+    g = torch.Generator().manual_seed(1)
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            if p.dim() == 1:
+                p.add_(torch.randn(p.shape, generator=g) * 0.1)
+    return model
+
+
+def check(model, tmp_path, prompt_len=19, atol=2e-3, max_seq_len=64):
+    model.save_pretrained(tmp_path, safe_serialization=True)
+    vocab = model.config.vocab_size
+    prompt = torch.randint(0, vocab, (prompt_len,), generator=torch.Generator().manual_seed(2)).tolist()
+    with torch.no_grad():
+        ref = model(torch.tensor([prompt])).logits[0, -1].float()
+    lm = LoadedModel.load(tmp_path, ModelLoadOptions(device="cpu", max_batch=1, max_seq_len=max_seq_len))
+    got = lm.prefill_logits(prompt)
+    err = float((got - ref).abs().max())
+    assert err < atol * max(1.0, float(ref.abs().max())), err
+    # a second, chunked pass through the engine (prefill in pieces + decode-shaped steps) agrees with the full pass
+    seq = lm.engine.new_sequence(prompt[:-4], max_new_tokens=8)
+    lm.engine.prefill_logits([seq])
+    logits = None
+    for t in prompt[-4:]:
+        logits = lm.engine.step_logits(seq, t)
+    lm.engine.release(seq)
+    assert float((logits.float().cpu() - ref).abs().max()) < atol * max(1.0, float(ref.abs().max()))
+    return lm
+
+
+BASE = dict(vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+            num_key_value_heads=2, max_position_embeddings=128)
+
+
+def test_llama(tmp_path):
+    check(hf_model("LlamaForCausalLM", "LlamaConfig", **BASE, rope_theta=50000.0, tie_word_embeddings=False), tmp_path)
+
+
+def test_llama3_rope_scaling(tmp_path):
+    check(hf_model("LlamaForCausalLM", "LlamaConfig", **BASE, rope_scaling={
+        "rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+        "original_max_position_embeddings": 32}), tmp_path, prompt_len=50)
+
+
+def test_mistral_sliding_window(tmp_path):
+    check(hf_model("MistralForCausalLM", "MistralConfig", **BASE, sliding_window=8), tmp_path, prompt_len=30)
+
+
+def test_qwen2_bias(tmp_path):
+    check(hf_model("Qwen2ForCausalLM", "Qwen2Config", **BASE), tmp_path)
+
+
+def test_qwen3_qk_norm(tmp_path):
+    check(hf_model("Qwen3ForCausalLM", "Qwen3Config", **BASE, head_dim=32), tmp_path)
+
+
+def test_phi3_fused_projections(tmp_path):
+    check(hf_model("Phi3ForCausalLM", "Phi3Config", **BASE, pad_token_id=0), tmp_path)
+
+
+def test_qwen3_moe(tmp_path):
+    check(hf_model("Qwen3MoeForCausalLM", "Qwen3MoeConfig", **BASE, head_dim=32, num_experts=8, num_experts_per_tok=2,
+                   moe_intermediate_size=48, norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[]), tmp_path)
+
+
+def test_mixtral(tmp_path):
+    check(hf_model("MixtralForCausalLM", "MixtralConfig", **BASE, num_local_experts=4, num_experts_per_tok=2), tmp_path)
