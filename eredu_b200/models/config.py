@@ -352,11 +352,18 @@ class ModelConfig:
         if mt == "nemotron_h":
             # eredu/src/backend/mlx/architectures/nemotron_h/model.rs:74-90 (pattern markers), :100-245 (fields)
             marks = {"M": "mamba", "*": "attention_only", "-": "mlp_only", "E": "moe_only"}
-            pattern = str(d.get("hybrid_override_pattern", ""))
-            if not pattern or any(ch not in marks for ch in pattern):
-                raise ValueError("Nemotron-H needs a hybrid_override_pattern made of 'M', '*', '-' and 'E'")
-            cfg.layer_types = [marks[ch] for ch in pattern]
-            cfg.num_hidden_layers = len(pattern)
+            pattern = str(d.get("hybrid_override_pattern", "") or "")
+            blocks = d.get("layers_block_type")
+            if blocks:      # newer exports spell the schedule out as a list
+                names = {"mamba": "mamba", "attention": "attention_only", "mlp": "mlp_only", "moe": "moe_only"}
+                if any(b not in names for b in blocks):
+                    raise ValueError(f"Nemotron-H layers_block_type has unknown entries: {sorted(set(blocks) - set(names))}")
+                cfg.layer_types = [names[b] for b in blocks]
+            elif pattern and all(ch in marks for ch in pattern):
+                cfg.layer_types = [marks[ch] for ch in pattern]
+            else:
+                raise ValueError("Nemotron-H needs layers_block_type or a hybrid_override_pattern made of 'M', '*', '-' and 'E'")
+            cfg.num_hidden_layers = len(cfg.layer_types)
             cfg.mamba_num_heads = int(d.get("mamba_num_heads", 128))
             cfg.mamba_head_dim = int(d.get("mamba_head_dim", 64))
             cfg.ssm_state_size = int(d.get("ssm_state_size", 128))

@@ -243,8 +243,11 @@ def _nemotron_block(model, li, get, has, e0, e1):
     cfg, dev, dt = model.cfg, model.device, model.dtype
     p = f"model.layers.{li}.mixer."
     up = lambda t: t.to(device=dev, dtype=dt).contiguous()                         # noqa: E731
-    w_up = torch.stack([get(p + f"experts.{e}.up_proj.weight") for e in range(e0, e1)], 0)
-    w_dn = torch.stack([get(p + f"experts.{e}.down_proj.weight") for e in range(e0, e1)], 0)
+    if has(p + "experts.up_proj"):        # packed banks [E, I, H] / [E, H, I]
+        w_up, w_dn = get(p + "experts.up_proj")[e0:e1], get(p + "experts.down_proj")[e0:e1]
+    else:
+        w_up = torch.stack([get(p + f"experts.{e}.up_proj.weight") for e in range(e0, e1)], 0)
+        w_dn = torch.stack([get(p + f"experts.{e}.down_proj.weight") for e in range(e0, e1)], 0)
     sel = get(p + "gate.e_score_correction_bias").to(device=dev, dtype=torch.float32).contiguous() \
         if has(p + "gate.e_score_correction_bias") else None
     shared = None

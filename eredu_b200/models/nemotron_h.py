@@ -21,27 +21,32 @@ from .. import ops
 _LAYER = re.compile(r"^model\.layers\.(\d+)\.(.+)$")
 
 
-def checkpoint_name(canonical: str) -> str:
+def checkpoint_names(canonical: str) -> list[str]:
+    """Spellings of a canonical tensor name in Nemotron-H checkpoints: the original ``backbone.*`` tree and the
+    ``model.*`` tree of newer exports (``embeddings`` / ``norm_f`` instead of ``embed_tokens`` / ``norm``)."""
     if canonical == "model.embed_tokens.weight":
-        return "backbone.embeddings.weight"
+        return ["backbone.embeddings.weight", "backbone.embedding.weight", "model.embeddings.weight"]
     if canonical == "model.norm.weight":
-        return "backbone.norm_f.weight"
+        return ["backbone.norm_f.weight", "model.norm_f.weight"]
     m = _LAYER.match(canonical)
     if not m:
-        return canonical
-    return f"backbone.layers.{m.group(1)}.{m.group(2)}"
+        return []
+    return [f"backbone.layers.{m.group(1)}.{m.group(2)}"]
+
+
+def checkpoint_name(canonical: str) -> str:
+    alts = checkpoint_names(canonical)
+    return alts[0] if alts else canonical
 
 
 def canonical_access(get, has):
-    def g(name):
-        alt = checkpoint_name(name)
-        return get(alt) if alt != name and has(alt) else get(name)
+    def resolve(name):
+        for alt in checkpoint_names(name):
+            if has(alt):
+                return alt
+        return name
 
-    def h(name):
-        alt = checkpoint_name(name)
-        return (alt != name and has(alt)) or has(name)
-
-    return g, h
+    return (lambda name: get(resolve(name))), (lambda name: has(resolve(name)))
 
 
 def to_checkpoint_names(state: dict) -> dict:

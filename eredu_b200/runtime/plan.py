@@ -66,9 +66,9 @@ def required_tensors(cfg: ModelConfig) -> list[tuple]:
         first = {"mamba": "mixer.in_proj.weight", "attention_only": "mixer.q_proj.weight", "mlp_only": "mixer.up_proj.weight",
                  "moe_only": "mixer.gate.weight"}[kind]
         names = [("model.embed_tokens.weight",), ("model.norm.weight",), (p + first,)]
-        from ..models.nemotron_h import checkpoint_name
+        from ..models.nemotron_h import checkpoint_names
 
-        return [tuple(n for a in alt for n in (checkpoint_name(a), a)) for alt in names]
+        return [tuple(n for a in alt for n in (checkpoint_names(a) + [a])) for alt in names]
     if kind == "conv":
         first = (p + "conv.in_proj.weight",)
     elif kind == "linear_attention":

@@ -82,3 +82,65 @@ def test_qwen3_moe(tmp_path):
 
 def test_mixtral(tmp_path):
     check(hf_model("MixtralForCausalLM", "MixtralConfig", **BASE, num_local_experts=4, num_experts_per_tok=2), tmp_path)
+
+
+def test_gpt_oss(tmp_path):
+    m = hf_model("GptOssForCausalLM", "GptOssConfig", vocab_size=320, hidden_size=64, intermediate_size=64, num_hidden_layers=2,
+                 num_attention_heads=4, num_key_value_heads=2, head_dim=32, num_local_experts=4, num_experts_per_tok=2,
+                 sliding_window=8, max_position_embeddings=128, layer_types=["sliding_attention", "full_attention"],
+                 rope_scaling=None, rope_parameters={"rope_type": "default", "rope_theta": 10000.0})
+    check(m, tmp_path, prompt_len=30)
+
+
+def test_lfm2(tmp_path):
+    m = hf_model("Lfm2ForCausalLM", "Lfm2Config", vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=4,
+                 num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=128, conv_L_cache=3, conv_bias=False,
+                 layer_types=["conv", "conv", "full_attention", "conv"], block_auto_adjust_ff_dim=True, block_multiple_of=32,
+                 block_ffn_dim_multiplier=1.0, pad_token_id=0)
+    check(m, tmp_path)
+
+
+def test_deepseek_v3(tmp_path):
+    m = hf_model("DeepseekV3ForCausalLM", "DeepseekV3Config", vocab_size=320, hidden_size=64, intermediate_size=96,
+                 moe_intermediate_size=32, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=4, n_shared_experts=1,
+                 n_routed_experts=8, routed_scaling_factor=2.5, kv_lora_rank=16, q_lora_rank=24, qk_rope_head_dim=8,
+                 v_head_dim=16, qk_nope_head_dim=16, n_group=2, topk_group=1, num_experts_per_tok=2, first_k_dense_replace=1,
+                 norm_topk_prob=True, max_position_embeddings=128)
+    check(m, tmp_path)
+
+
+def test_lfm2_moe(tmp_path):
+    m = hf_model("Lfm2MoeForCausalLM", "Lfm2MoeConfig", vocab_size=320, hidden_size=64, intermediate_size=128,
+                 moe_intermediate_size=32, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2,
+                 max_position_embeddings=128, conv_L_cache=3, conv_bias=False, num_dense_layers=1, num_experts=8,
+                 num_experts_per_tok=2, use_expert_bias=True, routed_scaling_factor=1.5, norm_topk_prob=True,
+                 layer_types=["conv", "conv", "full_attention", "conv"], pad_token_id=0)
+    with torch.no_grad():
+        for name, p in m.named_parameters():
+            if name.endswith("expert_bias"):
+                p.copy_(torch.randn(p.shape, generator=torch.Generator().manual_seed(3)))
+        for name, b in m.named_buffers():
+            if name.endswith("expert_bias"):
+                b.copy_(torch.randn(b.shape, generator=torch.Generator().manual_seed(3)))
+    check(m, tmp_path)
+
+
+def test_qwen3_next(tmp_path):
+    m = hf_model("Qwen3NextForCausalLM", "Qwen3NextConfig", vocab_size=320, hidden_size=64, intermediate_size=128,
+                 num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=32, max_position_embeddings=128,
+                 linear_conv_kernel_dim=4, linear_key_head_dim=16, linear_value_head_dim=8, linear_num_key_heads=2,
+                 linear_num_value_heads=4, decoder_sparse_step=1, moe_intermediate_size=32, shared_expert_intermediate_size=48,
+                 num_experts_per_tok=2, num_experts=8, norm_topk_prob=True, mlp_only_layers=[],
+                 layer_types=["linear_attention", "linear_attention", "linear_attention", "full_attention"])
+    check(m, tmp_path)
+
+
+def test_nemotron_h(tmp_path):
+    m = hf_model("NemotronHForCausalLM", "NemotronHConfig", vocab_size=320, hidden_size=64, intermediate_size=96,
+                 num_attention_heads=4, num_key_value_heads=2, head_dim=16, max_position_embeddings=128,
+                 layers_block_type=["mamba", "moe", "mamba", "attention", "moe"], mamba_num_heads=8, mamba_head_dim=8,
+                 ssm_state_size=16, n_groups=2, conv_kernel=4, chunk_size=8, use_conv_bias=True, use_bias=False, mlp_bias=False,
+                 attention_bias=False, n_routed_experts=8, n_shared_experts=1, moe_intermediate_size=32,
+                 moe_shared_expert_intermediate_size=48, num_experts_per_tok=2, routed_scaling_factor=2.0, n_group=2,
+                 topk_group=1, norm_topk_prob=True)
+    check(m, tmp_path)
