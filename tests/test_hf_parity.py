@@ -26,7 +26,7 @@ def hf_model(cls_name, cfg_name, **kw):
 
 def check(model, tmp_path, prompt_len=19, atol=2e-3, max_seq_len=64):
     model.save_pretrained(tmp_path, safe_serialization=True)
-    vocab = model.config.vocab_size
+    vocab = getattr(model.config, "vocab_size", None) or model.config.text_config.vocab_size
     prompt = torch.randint(0, vocab, (prompt_len,), generator=torch.Generator().manual_seed(2)).tolist()
     with torch.no_grad():
         ref = model(torch.tensor([prompt])).logits[0, -1].float()
@@ -144,3 +144,26 @@ def test_nemotron_h(tmp_path):
                  moe_shared_expert_intermediate_size=48, num_experts_per_tok=2, routed_scaling_factor=2.0, n_group=2,
                  topk_group=1, norm_topk_prob=True)
     check(m, tmp_path)
+
+
+def test_yarn_linear_and_partial_rotary(tmp_path):
+    check(hf_model("Qwen2ForCausalLM", "Qwen2Config", **BASE, rope_scaling={
+        "rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 32, "beta_fast": 32, "beta_slow": 1}),
+        tmp_path / "yarn", prompt_len=60)
+    check(hf_model("LlamaForCausalLM", "LlamaConfig", **BASE, rope_scaling={"rope_type": "linear", "factor": 2.0}),
+          tmp_path / "linear", prompt_len=40)
+    check(hf_model("Phi3ForCausalLM", "Phi3Config", **BASE, pad_token_id=0, partial_rotary_factor=0.5), tmp_path / "partial")
+    check(hf_model("MistralForCausalLM", "MistralConfig", **BASE, head_dim=24, sliding_window=None), tmp_path / "headdim")
+
+
+def test_qwen3_vl_text_path(tmp_path):
+    cfg_cls = transformers.Qwen3VLConfig
+    text = dict(vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                num_key_value_heads=2, head_dim=32, max_position_embeddings=128,
+                rope_scaling={"rope_type": "default", "mrope_section": [8, 4, 4], "mrope_interleaved": True})
+    vision = dict(depth=1, hidden_size=32, intermediate_size=64, num_heads=2, patch_size=4, spatial_merge_size=2,
+                  temporal_patch_size=2, out_hidden_size=64, num_position_embeddings=16, deepstack_visual_indexes=[0])
+    cfg = cfg_cls(text_config=text, vision_config=vision, tie_word_embeddings=False)
+    torch.manual_seed(0)
+    model = transformers.Qwen3VLForConditionalGeneration(cfg).eval().float()
+    check(model, tmp_path)
