@@ -144,7 +144,15 @@ class LoadedModel:
             tokenizer = load_tokenizer(path, src)
         except Exception:
             tokenizer = None
-        return cls(model, engine, src, tokenizer, Path(path))
+        lm = cls(model, engine, src, tokenizer, Path(path))
+        vis = src.cfg.extra.get("vision")
+        if vis and src.has("model.visual.patch_embed.proj.weight") and (opt.parallel is None or opt.parallel.owns_embedding()):
+            from ..models.qwen_vl import VisionConfig, VisionTower
+
+            lm.vision = VisionTower(VisionConfig.from_dict(vis["vision_config"]), src.get, device, torch.float32
+                                    if device.type == "cpu" else dtype)
+            lm.vision_tokens = {k: vis.get(k) for k in ("image_token_id", "vision_start_token_id", "vision_end_token_id")}
+        return lm
 
     # ------------------------------------------------------------------------------------------ tokens
     def encode(self, text: str) -> list[int]:
@@ -199,6 +207,89 @@ class LoadedModel:
             return self.model.forward(batch, eng.kv)[0].float().cpu()
         finally:
             eng.release(seq)
+
+    # ------------------------------------------------------------------------------------------ multimodal
+    vision = None          # models.qwen_vl.VisionTower when the checkpoint carries an image tower
+    vision_tokens: dict = {}
+
+    def multimodal_inputs(self, segments: list, min_pixels: int = 64 * 32 * 32, max_pixels: int = 16384 * 32 * 32,
+                          wrap: bool = True):
+        """Token ids and tower features of a prompt made of text segments (``str`` or lists of token ids) and
+        ``media.RgbImage`` parts: every image becomes ``<vision_start> <image> x n <vision_end>`` and its merged patch
+        features replace the placeholder embeddings (``wrap=False``: the surrounding text, e.g. a rendered chat template,
+        already carries the start / end markers and only the placeholder run is inserted).
+        Returns (token_ids, multimodal dict for ``Engine.feed_logits``)."""
+        from ..media import MultimodalPreparationError, RgbImage
+        from ..models.qwen_vl import image_to_patches, mrope_positions
+
+        if self.vision is None:
+            if any(isinstance(s, RgbImage) for s in segments):
+                raise MultimodalPreparationError("this model accepts text only; the request carries ['image']")
+            ids = [t for s in segments for t in (self.encode(s) if isinstance(s, str) else list(s))]
+            return ids, None
+        vt, cfg = self.vision_tokens, self.vision.cfg
+        ids, patches, grids = [], [], []
+        for seg in segments:
+            if isinstance(seg, RgbImage):
+                p, g = image_to_patches(seg, cfg, min_pixels, max_pixels)
+                n = g[0] * (g[1] // cfg.spatial_merge_size) * (g[2] // cfg.spatial_merge_size)
+                if wrap and vt.get("vision_start_token_id") is not None:
+                    ids.append(int(vt["vision_start_token_id"]))
+                ids.extend([int(vt["image_token_id"])] * n)
+                if wrap and vt.get("vision_end_token_id") is not None:
+                    ids.append(int(vt["vision_end_token_id"]))
+                patches.append(p)
+                grids.append(g)
+            else:
+                ids.extend(self.encode(seg) if isinstance(seg, str) else [int(t) for t in seg])
+        if not grids:
+            return ids, None
+        feats, deep = self.vision.forward(torch.cat(patches, 0), grids)
+        img = int(vt["image_token_id"])
+        pos, delta = mrope_positions(ids, img, grids, cfg.spatial_merge_size)
+        rows = [i for i, t in enumerate(ids) if t == img]
+        return ids, {"rows": rows, "values": feats, "deepstack": deep, "rope_positions": pos, "rope_delta": delta}
+
+    def chat_segments(self, messages: list, images: list, placeholder: str = "<|image_pad|>", **template_kwargs) -> list:
+        """Render a conversation whose user content lists contain ``{"type": "image"}`` items with the chat template and
+        cut the prompt at the template's image placeholders: text pieces interleaved with ``images`` in order (for
+        :meth:`multimodal_inputs` with ``wrap=False``)."""
+        prepared = self.prepare_chat(messages, **template_kwargs)
+        pieces = prepared.prompt.split(placeholder)
+        if len(pieces) - 1 != len(images):
+            raise ValueError(f"the rendered prompt has {len(pieces) - 1} image placeholders for {len(images)} images")
+        segments = []
+        for i, piece in enumerate(pieces):
+            if piece:
+                segments.append(piece)
+            if i < len(images):
+                segments.append(images[i])
+        return segments
+
+    def generate_multimodal(self, segments: list, sampling: Optional[SamplingParams] = None, max_new_tokens: int = 128,
+                            on_token=None, **image_limits) -> list[int]:
+        """Greedy / sampled continuation of a prompt with images (host-driven: one eager step per token)."""
+        from ..ops.sampling import sample_ref
+
+        ids, mm = self.multimodal_inputs(segments, **image_limits)
+        sp = sampling or SamplingParams(temperature=0.0)
+        eos = set(self.eos_ids()) | (set(self.tokenizer.eos_ids) if self.tokenizer else set())
+        seq = self.engine.new_sequence(ids, sp, max_new_tokens, tuple(eos))
+        out: list[int] = []
+        try:
+            logits = self.engine.feed_logits(seq, ids, mm)
+            for step in range(max_new_tokens):
+                tok, _ = sample_ref(logits.float().cpu(), sp, len(ids) + step, history=out, stream=seq.seq_id)
+                if tok in eos:
+                    break
+                out.append(tok)
+                if on_token is not None and on_token(tok):
+                    break
+                if step + 1 < max_new_tokens:
+                    logits = self.engine.step_logits(seq, tok)
+        finally:
+            self.engine.release(seq)
+        return out
 
     # ------------------------------------------------------------------------------------------ chat
     def prepare_chat(self, messages, tools=None, tool_choice=None, thinking: str = "auto", stop=None,

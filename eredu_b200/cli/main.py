@@ -66,6 +66,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--expert-cache-benchmark", action="store_true")
     p.add_argument("--mapped-shards", type=int, default=4)
     p.add_argument("--raw", action="store_true", help="no chat template: the prompt is fed verbatim")
+    p.add_argument("--image", action="append", default=[], metavar="PATH", help="image part of the prompt (vision-language models)")
     p.add_argument("--tools", default=None, metavar="PATH")
     p.add_argument("--json-schema", default=None, metavar="PATH", help="constrain the reply to this JSON schema")
     p.add_argument("--grammar", default=None, metavar="PATH", help="constrain the reply to this Lark grammar")
@@ -199,6 +200,30 @@ def main(argv=None) -> int:
         elif ev.kind == "tool_call_end":
             sys.stdout.write(json.dumps({"tool_call": {"name": ev.tool_name, "arguments": ev.arguments}}) + "\n")
 
+    if a.image:
+        # vision-language prompt: the images come first in the user turn, generation is host-driven
+        from ..media import load_image
+
+        images = [load_image(p_) for p_ in a.image]
+        content = [{"type": "image"} for _ in images] + [{"type": "text", "text": prompt}]
+        segments = lm.chat_segments([{"role": "user", "content": content}], images, thinking=a.thinking) \
+            if (lm.tokenizer is not None and lm.tokenizer.chat_template and not a.raw) else images + [prompt]
+        from ..text.tokenizer import TextDecoder
+
+        dec = TextDecoder(lm.tokenizer)
+        t_gen = time.perf_counter()
+
+        def show(tok):
+            sys.stdout.write(dec.push(tok))
+            sys.stdout.flush()
+
+        toks = lm.generate_multimodal(segments, sp, a.max_tokens, on_token=show)
+        sys.stdout.write(dec.flush() + "\n")
+        if a.timing or a.verbose:
+            dt = time.perf_counter() - t_gen
+            print(f"[eredu] load {load_time:.3f}s  generation {dt:.3f}s  {len(toks) / max(dt, 1e-9):.2f} tok/s  images {len(images)}",
+                  file=sys.stderr)
+        return 0
     if a.raw or lm.tokenizer is None or not lm.tokenizer.chat_template:
         from ..text.chat import ParserPlan, PreparedChat
 

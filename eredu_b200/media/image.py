@@ -119,3 +119,13 @@ def rescale_and_normalize_rgb8(image: RgbImage, rescale_factor: float, mean, std
         raise MediaError(f"image normalisation needs three finite non-zero standard deviations, got {std.tolist()}")
     x = image.pixels.astype(np.float32) * np.float32(rescale_factor)
     return NormalizedImage(np.ascontiguousarray(((x - mean) / std).transpose(2, 0, 1)))
+
+
+def load_image(path) -> RgbImage:
+    """Decode an image file to RGB8 (needs Pillow; formats are whatever it reads)."""
+    try:
+        from PIL import Image
+    except ImportError as e:  # pragma: no cover
+        raise MediaError("decoding image files needs the Pillow package") from e
+    with Image.open(path) as im:
+        return RgbImage(np.asarray(im.convert("RGB"), dtype=np.uint8).copy())

@@ -232,6 +232,7 @@ class ModelConfig:
     def from_hf_dict(cls, d: dict) -> "ModelConfig":
         mt = d.get("model_type", "llama")
         if "text_config" in d and isinstance(d["text_config"], dict):
+            outer = d
             inner = dict(d["text_config"])
             inner.setdefault("model_type", mt)
             for k in ("quantization", "quantization_config", "eos_token_id", "tie_word_embeddings"):
@@ -243,6 +244,8 @@ class ModelConfig:
             mt = {"qwen3_vl_text": "qwen3", "qwen3_vl_moe_text": "qwen3_moe", "qwen3_vl": "qwen3", "qwen3_vl_moe": "qwen3_moe"}.get(mt, mt)
             d["model_type"] = mt
             d["_language_model_prefix"] = True
+            d["_vision"] = {k: outer[k] for k in ("vision_config", "image_token_id", "video_token_id", "vision_start_token_id",
+                                                  "vision_end_token_id") if k in outer}
         # Transformers >= 5 writes RoPE settings as one ``rope_parameters`` object (theta inside it; optionally one
         # object per layer type): fold it back into rope_theta / rope_scaling
         rp = d.get("rope_parameters")
@@ -252,7 +255,8 @@ class ModelConfig:
             d = dict(d)
             if rp.get("rope_theta") is not None and d.get("rope_theta") is None:
                 d["rope_theta"] = rp["rope_theta"]
-            if d.get("rope_scaling") is None and rp.get("rope_type", "default") not in ("default", None):
+            if d.get("rope_scaling") is None and (rp.get("rope_type", "default") not in ("default", None)
+                                                  or "mrope_section" in rp):
                 d["rope_scaling"] = {k: v for k, v in rp.items() if k != "rope_theta"}
             if rp.get("partial_rotary_factor") is not None and d.get("partial_rotary_factor") is None:
                 d["partial_rotary_factor"] = rp["partial_rotary_factor"]
@@ -438,6 +442,8 @@ class ModelConfig:
                 cfg.intermediate_size = size
         if d.get("_language_model_prefix"):
             cfg.extra["language_model_prefix"] = True   # tensors live under model.language_model.* next to a vision tower
+            if d.get("_vision", {}).get("vision_config"):
+                cfg.extra["vision"] = d["_vision"]
         if mt == "mixtral":
             cfg.moe_intermediate_size = cfg.moe_intermediate_size or cfg.intermediate_size
             cfg.router_scoring = "topk_softmax"

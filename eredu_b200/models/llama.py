@@ -41,6 +41,12 @@ class ForwardBatch:
     splits: int = 1                    # decode split-KV factor
     scratch: Optional[tuple] = None    # decode split-KV scratch
     hidden_in: Optional[torch.Tensor] = None   # pipeline stages > 0: incoming activations instead of token ids
+    # multimodal prompts (vision-language models): rows whose embedding is replaced by tower features, the DeepStack
+    # features added to those rows after the first decoder layers, and rotary positions that differ from the cache index
+    embed_rows: Optional[torch.Tensor] = None       # [n_vis] int64 rows of this batch
+    embed_values: Optional[torch.Tensor] = None     # [n_vis, H]
+    deepstack: Optional[list] = None                # list of [n_vis, H]: added after layer 0, 1, ...
+    rope_positions: Optional[torch.Tensor] = None   # [M] or [3, M]; None: ``positions``
 
 
 @dataclass
@@ -229,10 +235,11 @@ class CausalLM:
             width = (self.n_q_local + 2 * self.n_kv_local) * cfg.head_dim
             gate, qkv = qkv[:, width:], qkv[:, :width]
         k_cache, v_cache = kv.layer(li)
-        q = ops.rope_kv(qkv, batch.positions, batch.slots, self.inv_freq, k_cache, v_cache, self.n_q_local,
+        rope_pos = batch.positions if batch.rope_positions is None else batch.rope_positions
+        q = ops.rope_kv(qkv, rope_pos, batch.slots, self.inv_freq, k_cache, v_cache, self.n_q_local,
                         self.n_kv_local, cfg.head_dim, rot=cfg.rotary_dim, interleaved=cfg.rope_traditional,
                         attn_factor=self.attn_factor, q_norm_w=lw.q_norm, k_norm_w=lw.k_norm, norm_eps=cfg.rms_norm_eps,
-                        norm_w_off=cfg.norm_weight_offset)
+                        norm_w_off=cfg.norm_weight_offset, mrope_section=(cfg.rope_scaling or {}).get("mrope_section"))
         window = cfg.layer_window(li)
         if batch.is_prefill:
             attn = ops.attention_prefill(q, k_cache, v_cache, batch.block_table, batch.seq_lens, batch.cu_q,
@@ -271,6 +278,9 @@ class CausalLM:
                 h = ops.embedding(batch.token_ids, self.embed, 0, self.cfg.embedding_scale)
         else:
             h = batch.hidden_in
+        if batch.embed_rows is not None and self.par.owns_embedding():
+            h = h.index_copy(0, batch.embed_rows, batch.embed_values.to(h.dtype))
+            ssq = None                      # the embedding kernel's row sums no longer describe these rows
         n = len(self.layers)
         obs = self.observer
         if obs is not None and self.par.owns_embedding():
@@ -282,6 +292,9 @@ class CausalLM:
             h, ssq = self.layer_forward(self.first_layer + i, lw, h, batch, kv, ssq, nxt)
             if self.residency is not None:
                 self.residency.release(i)
+            if batch.deepstack is not None and self.first_layer + i < len(batch.deepstack):
+                h = h.index_add(0, batch.embed_rows, batch.deepstack[self.first_layer + i].to(h.dtype))
+                ssq = None
             if obs is not None:
                 name = f"model.layers.{self.first_layer + i}.output"
                 repl = obs.intervene(name, h)

@@ -129,7 +129,10 @@ def rmsnorm(x, weight, eps, residual=None, weight_offset=0.0):
 
 # ------------------------------------------------------------------------------------------ rope + kv append
 def rope_kv_ref(qkv, positions, slots, inv_freq, k_cache, v_cache, n_q, n_kv, head_dim, rot=None, interleaved=False,
-                attn_factor=1.0, q_norm_w=None, k_norm_w=None, norm_eps=1e-6, norm_w_off=0.0):
+                attn_factor=1.0, q_norm_w=None, k_norm_w=None, norm_eps=1e-6, norm_w_off=0.0, mrope_section=None):
+    """``positions`` [M], or [3, M] (temporal, height, width axes of multimodal prompts) with ``mrope_section``: frequency
+    index f then takes its angle from axis f % 3 while f < 3 * section[axis] (interleaved T H W T H W ... layout), the
+    temporal axis otherwise."""
     M = qkv.shape[0]
     D = head_dim
     rot = rot or D
@@ -143,7 +146,14 @@ def rope_kv_ref(qkv, positions, slots, inv_freq, k_cache, v_cache, n_q, n_kv, he
         return y.to(qkv.dtype).float()
 
     q, k = hnorm(q, q_norm_w), hnorm(k, k_norm_w)
-    ang = positions.float()[:, None] * inv_freq.float()[None, :]  # [M, rot/2]
+    if positions.dim() == 2:
+        axes = positions.float()[:, :, None] * inv_freq.float()[None, None, :]          # [3, M, rot/2]
+        ang = axes[0].clone()
+        for axis, offset in ((1, 1), (2, 2)):
+            idx = slice(offset, int(mrope_section[axis]) * 3, 3)
+            ang[:, idx] = axes[axis][:, idx]
+    else:
+        ang = positions.float()[:, None] * inv_freq.float()[None, :]  # [M, rot/2]
     cos, sin = (ang.cos() * attn_factor)[:, None, :], (ang.sin() * attn_factor)[:, None, :]
 
     def rotate(t):
@@ -165,11 +175,12 @@ def rope_kv_ref(qkv, positions, slots, inv_freq, k_cache, v_cache, n_q, n_kv, he
 
 
 def rope_kv(qkv, positions, slots, inv_freq, k_cache, v_cache, n_q, n_kv, head_dim, rot=None, interleaved=False,
-            attn_factor=1.0, q_norm_w=None, k_norm_w=None, norm_eps=1e-6, norm_w_off=0.0, q_out=None):
-    """Per-head q/k norm (optional) + RoPE on q and k, K/V scattered into their cache pages. Returns q [M,n_q,D]."""
-    if not qkv.is_cuda or head_dim not in KERNEL_HEAD_DIMS:
+            attn_factor=1.0, q_norm_w=None, k_norm_w=None, norm_eps=1e-6, norm_w_off=0.0, q_out=None, mrope_section=None):
+    """Per-head q/k norm (optional) + RoPE on q and k, K/V scattered into their cache pages. Returns q [M,n_q,D].
+    Three-axis positions ([3, M], prompts with images) take the tensor-operation path on either device."""
+    if not qkv.is_cuda or head_dim not in KERNEL_HEAD_DIMS or positions.dim() == 2:
         return rope_kv_ref(qkv, positions, slots, inv_freq, k_cache, v_cache, n_q, n_kv, head_dim, rot, interleaved,
-                           attn_factor, q_norm_w, k_norm_w, norm_eps, norm_w_off)
+                           attn_factor, q_norm_w, k_norm_w, norm_eps, norm_w_off, mrope_section)
     M = qkv.shape[0]
     rot = rot or head_dim
     assert positions.dtype == torch.int32 and slots.dtype == torch.int64 and inv_freq.dtype == torch.float32

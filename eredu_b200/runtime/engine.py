@@ -277,13 +277,28 @@ class Engine:
 
     # ------------------------------------------------------------------------------------------ host-driven steps
     @torch.no_grad()
-    def feed_logits(self, seq: Sequence, tokens: list[int]) -> torch.Tensor:
+    def feed_logits(self, seq: Sequence, tokens: list[int], multimodal=None) -> torch.Tensor:
         """Append ``tokens`` to the sequence's cache and return the logits after the last one ([V], on the model's
-        device). For samplers that must see every distribution on the host (grammar masks, Mirostat)."""
+        device). For samplers that must see every distribution on the host (grammar masks, Mirostat).
+
+        ``multimodal``: dict with ``rows`` (indices into ``tokens`` whose embeddings are replaced), ``values`` [n, H],
+        optional ``deepstack`` (list of [n, H]) and ``rope_positions`` [3, len(tokens)] for prompts with images; it sets
+        ``seq.rope_delta`` so that later text tokens continue after the largest position the images used."""
         n = len(tokens)
         p = np.arange(seq.kv_len, seq.kv_len + n)
         pages = np.asarray(seq.pages, dtype=np.int64)
-        batch = ForwardBatch(
+        extra = {}
+        delta = getattr(seq, "rope_delta", 0)
+        if multimodal is not None:
+            dev = self.device
+            extra = dict(embed_rows=torch.as_tensor(multimodal["rows"], dtype=torch.int64, device=dev),
+                         embed_values=multimodal["values"].to(dev),
+                         deepstack=[d.to(dev) for d in multimodal.get("deepstack") or []] or None,
+                         rope_positions=multimodal["rope_positions"].to(dev))
+            seq.rope_delta = int(multimodal.get("rope_delta", 0))
+        elif delta:
+            extra = dict(rope_positions=self._t((p + delta).astype(np.int32), torch.int32))
+        batch = ForwardBatch(**extra, 
             token_ids=self._t(np.asarray(tokens, dtype=np.int32), torch.int32),
             positions=self._t(p.astype(np.int32), torch.int32),
             slots=self._t(pages[p // PAGE] * PAGE + (p % PAGE), torch.int64),

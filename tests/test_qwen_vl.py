@@ -75,3 +75,70 @@ def test_mrope_positions_match_transformers():
     assert torch.equal(pos, ref[:, 0]) and delta == int(ref_delta)
     with pytest.raises(ValueError):
         mrope_positions([IMG] * 5, IMG, grids, 2)
+
+
+def test_image_prompt_logits_and_decode_match_transformers(tmp_path):
+    from eredu_b200.api import LoadedModel, ModelLoadOptions
+    from eredu_b200.media import MultimodalPreparationError, RgbImage
+
+    m = hf_vl()
+    m.save_pretrained(tmp_path, safe_serialization=True)
+    lm = LoadedModel.load(tmp_path, ModelLoadOptions(device="cpu", max_batch=1, max_seq_len=128))
+    assert lm.vision is not None and lm.vision_tokens["image_token_id"] == 300
+    rng = np.random.default_rng(0)
+    img_a = RgbImage(rng.integers(0, 255, (16, 24, 3), dtype=np.uint8))
+    img_b = RgbImage(rng.integers(0, 255, (8, 8, 3), dtype=np.uint8))
+    segments = [[5, 6, 7], img_a, [8, 9], img_b, [10, 11, 12]]
+    ids, mm = lm.multimodal_inputs(segments, min_pixels=64, max_pixels=10**6)
+    assert ids.count(300) == 6 + 1 and ids[3] == 302 and mm["values"].shape == (7, 64) and len(mm["deepstack"]) == 2
+    # the same pixels through Transformers: patches in its layout are exactly what our processor produced
+    from eredu_b200.models.qwen_vl import image_to_patches
+
+    pa, ga = image_to_patches(img_a, lm.vision.cfg, 64, 10**6)
+    pb, gb = image_to_patches(img_b, lm.vision.cfg, 64, 10**6)
+    with torch.no_grad():
+        out = m(input_ids=torch.tensor([ids]), pixel_values=torch.cat((pa, pb)), image_grid_thw=torch.tensor([ga, gb]),
+                mm_token_type_ids=torch.tensor([[1 if t == 300 else 0 for t in ids]]))
+    ref = out.logits[0, -1]
+    seq = lm.engine.new_sequence(ids, max_new_tokens=8)
+    got = lm.engine.feed_logits(seq, ids, mm)
+    assert torch.allclose(got.float().cpu(), ref, atol=2e-3), float((got.float().cpu() - ref).abs().max())
+    # decode after the images: positions continue at index + delta, as in Transformers' generation
+    with torch.no_grad():
+        gen = m.generate(input_ids=torch.tensor([ids]), pixel_values=torch.cat((pa, pb)), image_grid_thw=torch.tensor([ga, gb]),
+                         mm_token_type_ids=torch.tensor([[1 if t == 300 else 0 for t in ids]]),
+                         max_new_tokens=6, do_sample=False)[0, len(ids):].tolist()
+    lm.engine.release(seq)
+    ours = lm.generate_multimodal(segments, max_new_tokens=6, min_pixels=64, max_pixels=10**6)
+    assert ours == gen[:len(ours)] and len(ours) >= 1
+    # a text-only checkpoint refuses image parts
+    lm.vision = None
+    with pytest.raises(MultimodalPreparationError):
+        lm.multimodal_inputs(segments)
+
+
+def test_chat_segments_cut_the_prompt_at_image_placeholders(tmp_path):
+    from eredu_b200.api import LoadedModel
+    from eredu_b200.media import RgbImage, load_image
+
+    class FakeLM(LoadedModel):
+        def __init__(self):
+            pass
+
+        def prepare_chat(self, messages, **kw):
+            from types import SimpleNamespace
+
+            text = "".join("<|vision_start|><|image_pad|><|vision_end|>" if c["type"] == "image" else c["text"]
+                           for m in messages for c in m["content"])
+            return SimpleNamespace(prompt="<|im_start|>user\n" + text + "<|im_end|>")
+
+    a, b = RgbImage(np.zeros((2, 2, 3), np.uint8)), RgbImage(np.ones((2, 2, 3), np.uint8))
+    msgs = [{"role": "user", "content": [{"type": "image"}, {"type": "text", "text": "compare"}, {"type": "image"}]}]
+    segs = FakeLM().chat_segments(msgs, [a, b])
+    assert segs == ["<|im_start|>user\n<|vision_start|>", a, "<|vision_end|>compare<|vision_start|>", b, "<|vision_end|><|im_end|>"]
+    with pytest.raises(ValueError):
+        FakeLM().chat_segments(msgs, [a])
+    Image = pytest.importorskip("PIL.Image")
+    Image.fromarray(np.full((3, 5, 3), 200, np.uint8)).save(tmp_path / "x.png")
+    im = load_image(tmp_path / "x.png")
+    assert (im.height, im.width) == (3, 5) and int(im.pixels[0, 0, 0]) == 200
