@@ -149,9 +149,14 @@ class LoadedModel:
         if vis and src.has("model.visual.patch_embed.proj.weight") and (opt.parallel is None or opt.parallel.owns_embedding()):
             from ..models.qwen_vl import VisionConfig, VisionTower
 
-            lm.vision = VisionTower(VisionConfig.from_dict(vis["vision_config"]), src.get, device, torch.float32
-                                    if device.type == "cpu" else dtype)
-            lm.vision_tokens = {k: vis.get(k) for k in ("image_token_id", "vision_start_token_id", "vision_end_token_id")}
+            try:
+                lm.vision = VisionTower(VisionConfig.from_dict(vis["vision_config"]), src.get, device, torch.float32
+                                        if device.type == "cpu" else dtype)
+                lm.vision_tokens = {k: vis.get(k) for k in ("image_token_id", "vision_start_token_id", "vision_end_token_id")}
+            except (RuntimeError, KeyError, ValueError) as e:
+                # a tower this loader cannot bind (other family, truncated export): the model stays usable for text
+                # and image parts are refused with this reason
+                lm.vision, lm.vision_error = None, f"vision tower not loaded: {e}"
         return lm
 
     # ------------------------------------------------------------------------------------------ tokens
@@ -211,6 +216,7 @@ class LoadedModel:
     # ------------------------------------------------------------------------------------------ multimodal
     vision = None          # models.qwen_vl.VisionTower when the checkpoint carries an image tower
     vision_tokens: dict = {}
+    vision_error: str = ""
 
     def multimodal_inputs(self, segments: list, min_pixels: int = 64 * 32 * 32, max_pixels: int = 16384 * 32 * 32,
                           wrap: bool = True):
@@ -224,7 +230,8 @@ class LoadedModel:
 
         if self.vision is None:
             if any(isinstance(s, RgbImage) for s in segments):
-                raise MultimodalPreparationError("this model accepts text only; the request carries ['image']")
+                raise MultimodalPreparationError("this model accepts text only; the request carries ['image']"
+                                                 + (f" ({self.vision_error})" if self.vision_error else ""))
             ids = [t for s in segments for t in (self.encode(s) if isinstance(s, str) else list(s))]
             return ids, None
         vt, cfg = self.vision_tokens, self.vision.cfg
