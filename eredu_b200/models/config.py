@@ -99,6 +99,11 @@ class ModelConfig:
         """(heads, key width, value width) of one cached token per layer: MLA caches one shared latent + rotary key."""
         if self.is_mla:
             return 1, self.kv_lora_rank + self.qk_rope_head_dim, 1
+        if self.model_type == "gemma4":      # one pool wide enough for both layer types; layers use a slice of it
+            g = self.extra["gemma4"]
+            d = max(self.head_dim, int(g.get("global_head_dim") or 0))
+            n = max(self.num_key_value_heads, int(g.get("num_global_key_value_heads") or 0))
+            return n, d, d
         return self.num_key_value_heads, self.head_dim, self.head_dim
 
     @property
@@ -133,6 +138,9 @@ class ModelConfig:
         """The layer appends K/V pages (softmax attention); every other operator keeps a fixed state or none."""
         if self.layer_types is None:
             return True
+        if self.model_type == "gemma4":      # the KV-sharing tail reads an earlier layer's pages
+            shared = int(self.extra["gemma4"].get("num_kv_shared_layers") or 0)
+            return layer < self.num_hidden_layers - shared or shared == 0
         return self.layer_types[layer] in ("full_attention", "sliding_attention", "attention_only")
 
     def layer_has_recurrent_state(self, layer: int) -> bool:
@@ -241,7 +249,8 @@ class ModelConfig:
             d = inner
             mt = d.get("model_type", mt)
             # the language model of a vision-language checkpoint is its text family (text-only use of Qwen3-VL)
-            mt = {"qwen3_vl_text": "qwen3", "qwen3_vl_moe_text": "qwen3_moe", "qwen3_vl": "qwen3", "qwen3_vl_moe": "qwen3_moe"}.get(mt, mt)
+            mt = {"qwen3_vl_text": "qwen3", "qwen3_vl_moe_text": "qwen3_moe", "qwen3_vl": "qwen3", "qwen3_vl_moe": "qwen3_moe",
+                  "gemma4_text": "gemma4"}.get(mt, mt)
             d["model_type"] = mt
             d["_language_model_prefix"] = True
             d["_vision"] = {k: outer[k] for k in ("vision_config", "image_token_id", "video_token_id", "vision_start_token_id",
@@ -260,6 +269,10 @@ class ModelConfig:
                 d["rope_scaling"] = {k: v for k, v in rp.items() if k != "rope_theta"}
             if rp.get("partial_rotary_factor") is not None and d.get("partial_rotary_factor") is None:
                 d["partial_rotary_factor"] = rp["partial_rotary_factor"]
+        if mt == "gemma4_text":
+            mt = "gemma4"
+            d = dict(d, model_type=mt)
+        raw_rope_parameters = d.get("rope_parameters")
         heads = int(d.get("num_attention_heads", 32))
         hidden = int(d.get("hidden_size", 4096))
         kv = int(d.get("num_key_value_heads") or 0) or heads
@@ -301,6 +314,25 @@ class ModelConfig:
             bos_token_id=d.get("bos_token_id"),
             torch_dtype=str(d.get("torch_dtype", d.get("dtype", "bfloat16"))),
         )
+        if mt == "gemma4":
+            # eredu/src/backend/mlx/architectures/gemma4/model.rs:374-430: the family's own fields travel as a dict;
+            # the generic fields describe the sliding layers
+            keys = ("global_head_dim", "num_global_key_value_heads", "attention_k_eq_v", "num_kv_shared_layers",
+                    "use_double_wide_mlp", "hidden_size_per_layer_input", "vocab_size_per_layer_input", "enable_moe_block",
+                    "top_k_experts", "hidden_activation", "final_logit_softcapping")
+            cfg.extra["gemma4"] = {k: d.get(k) for k in keys}
+            cfg.extra["gemma4"]["rope_parameters"] = raw_rope_parameters
+            cfg.embedding_scale = float(cfg.hidden_size) ** 0.5
+            cfg.sliding_window = d.get("sliding_window")
+            cfg.rms_norm_eps = float(d.get("rms_norm_eps", 1e-6))
+            cfg.tie_word_embeddings = bool(d.get("tie_word_embeddings", True))
+            cfg.num_experts = int(d.get("num_experts") or 0) if d.get("enable_moe_block") else 0
+            cfg.num_experts_per_tok = int(d.get("top_k_experts") or 0)
+            cfg.rope_scaling = None
+            if cfg.layer_types is None or len(cfg.layer_types) != cfg.num_hidden_layers:
+                raise ValueError("Gemma 4 config needs one layer_types entry per layer")
+            if (d.get("hidden_activation") or "gelu_pytorch_tanh") != "gelu_pytorch_tanh":
+                raise ValueError("Gemma 4: only the gelu_pytorch_tanh activation is supported")
         if mt == "kimi_linear":
             # eredu/src/backend/mlx/architectures/kimi_linear/model.rs:160-235 (source keys), :330-450 (schedule)
             la = d.get("linear_attn_config") or {}

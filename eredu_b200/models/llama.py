@@ -47,6 +47,7 @@ class ForwardBatch:
     embed_values: Optional[torch.Tensor] = None     # [n_vis, H]
     deepstack: Optional[list] = None                # list of [n_vis, H]: added after layer 0, 1, ...
     rope_positions: Optional[torch.Tensor] = None   # [M] or [3, M]; None: ``positions``
+    per_layer_inputs: Optional[torch.Tensor] = None  # Gemma 4: [M, layers, P], filled by the model
 
 
 @dataclass
@@ -70,6 +71,7 @@ class LayerWeights:
     # operator norm and fold_attn then refers to conv_in
     # Nemotron-H: the layer is one mixer ("mamba" | "attention_only" | "mlp_only" | "moe_only"); attn_norm is its norm
     block_kind: str = ""
+    extra: Optional[dict] = None   # tensors of blocks that keep their own layout (Gemma 4)
     m_in: Optional[torch.Tensor] = None        # Mamba-2 input projection [z | x B C | dt]
     m_in_b: Optional[torch.Tensor] = None
     m_conv_w: Optional[torch.Tensor] = None
@@ -203,6 +205,10 @@ class CausalLM:
     def layer_forward(self, li: int, lw: LayerWeights, h, batch: ForwardBatch, kv, ssq=None, next_folded=False):
         """One decoder block. ``ssq``: partial sums of squares of h's rows (or None); returns (h, ssq')."""
         cfg = self.cfg
+        if lw.block_kind == "gemma4":
+            from .gemma4 import block_forward as gemma4_block
+
+            return gemma4_block(self, li, lw, h, batch, kv), None
         if lw.block_kind:
             from .nemotron_h import block_forward
 
@@ -278,6 +284,10 @@ class CausalLM:
                 h = ops.embedding(batch.token_ids, self.embed, 0, self.cfg.embedding_scale)
         else:
             h = batch.hidden_in
+        if getattr(self, "g4", None) is not None:
+            from .gemma4 import per_layer_inputs
+
+            batch.per_layer_inputs = per_layer_inputs(self, batch.token_ids, h)
         if batch.embed_rows is not None and self.par.owns_embedding():
             h = h.index_copy(0, batch.embed_rows, batch.embed_values.to(h.dtype))
             ssq = None                      # the embedding kernel's row sums no longer describe these rows
@@ -317,9 +327,14 @@ class CausalLM:
             ssq = None
         eps = self.cfg.rms_norm_eps
         if self.par.tp_size > 1 and self.lm_head.shape[0] != self.cfg.vocab_size:
-            return self.tp_ops.gathered_logits(h, self.lm_head, self.cfg.vocab_size, self.vocab_start, row_ssq=ssq,
-                                               norm_eps=eps)
-        return ops.linear(h, self.lm_head, out_dtype=torch.float32, row_ssq=ssq, norm_eps=eps)
+            out = self.tp_ops.gathered_logits(h, self.lm_head, self.cfg.vocab_size, self.vocab_start, row_ssq=ssq,
+                                              norm_eps=eps)
+        else:
+            out = ops.linear(h, self.lm_head, out_dtype=torch.float32, row_ssq=ssq, norm_eps=eps)
+        cap = (self.cfg.extra.get("gemma4") or {}).get("final_logit_softcapping")
+        if cap:
+            out = torch.tanh(out / float(cap)) * float(cap)
+        return out
 
     def forward(self, batch: ForwardBatch, kv):
         """Returns fp32 logits [R, V] on the last pipeline stage, the hidden state otherwise."""
@@ -384,6 +399,8 @@ class CausalLM:
             add(t)
         for lw in self.layers:
             for v in vars(lw).values():
+                add(v)
+            for v in (lw.extra or {}).values():
                 add(v)
             for q in lw.qlin.values():
                 for t in q.tensors():
@@ -450,6 +467,11 @@ def build_from_tensors(cfg: ModelConfig, get: Callable[[str], torch.Tensor], has
         else:
             model.lm_head = model.embed if (head is None or (cfg.tie_word_embeddings and model.embed is not None
                                                              and not has("lm_head.weight"))) else up(head)
+    if cfg.model_type == "gemma4":
+        from .gemma4 import build as build_gemma4
+
+        build_gemma4(model, cfg, get, has, up)
+        return model
     for li in range(model.first_layer, model.last_layer):
         p = f"model.layers.{li}."
         bq = bk = bv = None

@@ -434,7 +434,7 @@ class Engine:
     def _host_driven(self) -> bool:
         """True when a forward pass needs the host between kernels (layerwise host residency, expert cache)."""
         m = self.model
-        if self.cfg.head_dim not in (64, 128) or self.cfg.is_mla:
+        if self.cfg.head_dim not in (64, 128) or self.cfg.is_mla or self.cfg.model_type == "gemma4":
             return True    # no attention kernel for this head size: the tensor-operation path reads lengths on the host
         if getattr(m, "residency", None) is not None or getattr(getattr(m, "inner", m), "observer", None) is not None:
             return True

@@ -21,7 +21,7 @@ from ..models.config import DENSE_TYPES, MOE_TYPES, ModelConfig
 
 EXECUTION_PLAN_SCHEMA_VERSION = 2
 DEFAULT_MAX_MAPPED_SHARDS = 4
-SUPPORTED_TYPES = DENSE_TYPES | {"qwen3_moe", "mixtral", "gpt_oss", "lfm2_moe", "qwen3_next", "qwen3_5_moe", "nemotron_h", "deepseek_v3", "kimi_linear"}
+SUPPORTED_TYPES = DENSE_TYPES | {"qwen3_moe", "mixtral", "gpt_oss", "lfm2_moe", "qwen3_next", "qwen3_5_moe", "nemotron_h", "deepseek_v3", "kimi_linear", "gemma4"}
 
 
 # ---------------------------------------------------------------------------------------------- inspection

@@ -167,3 +167,28 @@ def test_qwen3_vl_text_path(tmp_path):
     torch.manual_seed(0)
     model = transformers.Qwen3VLForConditionalGeneration(cfg).eval().float()
     check(model, tmp_path)
+
+
+G4 = dict(vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=6, num_attention_heads=4, num_key_value_heads=2,
+          head_dim=16, global_head_dim=32, sliding_window=8, max_position_embeddings=128,
+          layer_types=["sliding_attention", "sliding_attention", "full_attention"] * 2, pad_token_id=0)
+
+
+@pytest.mark.parametrize("variant", ["plain", "shared_kv_ple", "k_eq_v", "moe"])
+def test_gemma4_text(tmp_path, variant):
+    kw = dict(G4, num_kv_shared_layers=0, hidden_size_per_layer_input=0, attention_k_eq_v=False, enable_moe_block=False)
+    if variant == "shared_kv_ple":
+        kw.update(num_kv_shared_layers=3, hidden_size_per_layer_input=8, vocab_size_per_layer_input=320, use_double_wide_mlp=True)
+    if variant == "k_eq_v":
+        kw.update(attention_k_eq_v=True, num_global_key_value_heads=1)
+    if variant == "moe":
+        kw.update(enable_moe_block=True, num_experts=4, top_k_experts=2, moe_intermediate_size=32)
+    m = hf_model("Gemma4ForCausalLM", "Gemma4TextConfig", **kw)
+    with torch.no_grad():
+        for name, b in m.named_buffers():
+            if name.endswith("layer_scalar"):
+                b.fill_(0.9)
+        for name, p in m.named_parameters():
+            if name.endswith(("router.scale", "per_expert_scale")):
+                p.add_(torch.randn(p.shape, generator=torch.Generator().manual_seed(5)) * 0.2)
+    check(m, tmp_path, prompt_len=30)
