@@ -8,6 +8,7 @@ streaming ...) are accepted, validated and recorded in the telemetry so that exi
 from __future__ import annotations
 
 import argparse
+import dataclasses
 import json
 import sys
 import time
@@ -24,6 +25,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--auto-benchmark-tokens", type=int, default=32)
     p.add_argument("--auto-benchmark-runs", type=int, default=1)
     p.add_argument("--auto-benchmark-timeout-seconds", type=int, default=300)
+    p.add_argument("--auto-trial-plan", default=None, help=argparse.SUPPRESS)   # set by --auto benchmark for its child runs
     p.add_argument("--draft-model", default=None)
     p.add_argument("--device", default="gpu:0", help="cpu | gpu:N")
     p.add_argument("--mlx-cache-limit-bytes", type=int, default=None)
@@ -119,6 +121,89 @@ def resolve_sampling(a, generation_config: dict):
         presence_penalty=a.presence_penalty, seed=a.seed)
 
 
+AUTO_BENCHMARK_PROMPT = "Write a short paragraph about the history of the telescope."
+
+
+def read_feedback(paths) -> list:
+    """Telemetry records of earlier runs (eredu-cli/src/main.rs:1383-1408): each file holds one record or an array."""
+    out = []
+    for path in paths:
+        try:
+            val = json.load(open(path))
+        except OSError as e:
+            raise SystemExit(f"failed to read automatic feedback {path}: {e}")
+        except ValueError as e:
+            raise SystemExit(f"failed to parse automatic feedback {path}: {e}")
+        out.extend(val if isinstance(val, list) else [val])
+    for t in out:
+        if not isinstance(t, dict):
+            raise SystemExit("automatic feedback must be telemetry objects")
+    return out
+
+
+def write_plan_cache(path, key, plan, rate) -> None:
+    try:
+        book = json.load(open(path))
+    except (OSError, ValueError):
+        book = {}
+    book[key] = {"plan": json.loads(plan.to_json()), "benchmark_token_rate": rate}
+    json.dump(book, open(path, "w"), indent=1)
+
+
+def benchmark_candidates(model_path: str, a, candidates: list, prompt: str) -> dict:
+    """Times every candidate plan in a fresh process (eredu-cli/src/main.rs:1516-1745): the child gets the serialized
+    plan through ``--auto-trial-plan`` and reports through ``--telemetry-json``; the selection metric is the median
+    decode rate over ``--auto-benchmark-runs`` runs. A candidate whose runs all fail (or time out) is kept in the report
+    with its error and is not eligible."""
+    import subprocess
+    import tempfile
+
+    from ..runtime.plan import _median
+
+    rows, best = [], None
+    with tempfile.TemporaryDirectory(prefix="eredu-auto-") as tmp:
+        for ci, plan in enumerate(candidates):
+            print(f"[eredu] automatic benchmark: candidate {ci + 1}/{len(candidates)} ({plan.residency.get('mode')}"
+                  f"{', expert cache' if plan.expert_cache else ''})", file=sys.stderr)
+            trials, rates = [], []
+            for run in range(a.auto_benchmark_runs):
+                plan_path, tel_path = f"{tmp}/plan-{ci}-{run}.json", f"{tmp}/tel-{ci}-{run}.json"
+                open(plan_path, "w").write(plan.to_json())
+                cmd = [sys.executable, "-m", "eredu_b200.cli", "--model", model_path, "--device", a.device, "--auto-trial-plan",
+                       plan_path, "--telemetry-json", tel_path, "--max-tokens", str(a.auto_benchmark_tokens), "--raw",
+                       "--mapped-shards", str(a.mapped_shards), prompt]
+                trial = {"run": run}
+                try:
+                    r = subprocess.run(cmd, stdin=subprocess.DEVNULL, stdout=subprocess.DEVNULL, stderr=subprocess.PIPE,
+                                       timeout=a.auto_benchmark_timeout_seconds)
+                    if r.returncode != 0:
+                        trial["error"] = f"exit {r.returncode}: " + r.stderr.decode(errors="replace").strip()[-400:]
+                    else:
+                        t = json.load(open(tel_path))
+                        timing = t.get("timing", {})
+                        rate = timing.get("decode_token_rate") or timing.get("token_rate") or 0.0
+                        trial.update(token_rate=rate, generated_tokens=t.get("generated_tokens"),
+                                     load_time=timing.get("load_time"), time_to_first_token=timing.get("time_to_first_token"))
+                        if rate > 0:
+                            rates.append(rate)
+                except subprocess.TimeoutExpired:
+                    trial["error"] = f"timed out after {a.auto_benchmark_timeout_seconds}s"
+                except (OSError, ValueError) as e:
+                    trial["error"] = str(e)
+                trials.append(trial)
+            med = _median(rates) if rates else None
+            rows.append({"plan": json.loads(plan.to_json()), "trials": trials, "median_token_rate": med})
+            if med is not None and (best is None or med > rows[best]["median_token_rate"]):
+                best = ci
+    if best is None:
+        raise SystemExit("every isolated automatic benchmark candidate failed:\n" +
+                         "\n".join(t.get("error", "") for r in rows for t in r["trials"]))
+    return {"schema_version": 2, "generated_tokens_per_trial": a.auto_benchmark_tokens, "runs_per_candidate": a.auto_benchmark_runs,
+            "timeout_seconds": a.auto_benchmark_timeout_seconds, "selection_metric": "median_decode_token_rate",
+            "selected": rows[best]["plan"], "selected_index": best, "selected_median_token_rate": rows[best]["median_token_rate"],
+            "candidates": rows, "_selected_plan": candidates[best]}
+
+
 def main(argv=None) -> int:
     a = build_parser().parse_args(argv)
     validate_args(a)
@@ -134,56 +219,95 @@ def main(argv=None) -> int:
         quant = QuantizationOptions(bits=bits, group_size=a.quantization_group_size, mode=a.quantization_mode)
     # ---- automatic planning (--auto plan|quick|benchmark; --no-auto keeps exactly what the flags say)
     plan = None
+    report = None
     layerwise, window = a.layerwise_host, a.device_layer_window
-    if not a.no_auto:
-        from ..runtime.plan import AutomaticPlanner, ExecutionPlan, HardwareProfile, estimate_runtime_state, inspect_artifact
+    if a.auto_trial_plan:
+        # a benchmark trial: the parent's serialized candidate is applied as is, nothing is replanned
+        from ..runtime.plan import ExecutionPlan
+
+        plan = ExecutionPlan.from_json(open(a.auto_trial_plan).read())
+    elif not a.no_auto:
+        from ..runtime.plan import (AutomaticPlanner, ExecutionPlan, HardwareProfile, candidate_plans, estimate_runtime_state,
+                                    inspect_artifact, select_from_feedback)
 
         report = inspect_artifact(model_path)
         if not report.is_loadable:
             for issue in report.issues:
                 print(f"[eredu] {issue.severity}: {issue.code}: {issue.message}", file=sys.stderr)
             raise SystemExit(2)
+        context = max(4096, a.max_tokens + 2048)
+        hw = HardwareProfile.discover() if device != "cpu" else HardwareProfile(device_count=1, device_memory_bytes=1 << 62, name="cpu")
+        hw.device_count = 1     # the command-line front end drives one device; multi-GPU runs use the library API
+        prof = estimate_runtime_state(report.config, report.tensor_bytes)
+        feedback = read_feedback(a.auto_feedback)
         cache_path = a.auto_cache
         key = f"{report.model_type}:{report.tensor_bytes}:{device}:{a.max_tokens}"
         cached = None
-        if cache_path:
+        if cache_path and a.auto != "benchmark":
             try:
                 cached = json.load(open(cache_path)).get(key)
             except (OSError, ValueError):
                 cached = None
-        if cached:
-            plan = ExecutionPlan.from_json(json.dumps(cached))
+        picked = select_from_feedback(feedback, report.model_type, report.tensor_bytes, device) if feedback else None
+        if picked is not None:
+            plan = picked[0]
+            plan.rationale = list(plan.rationale) + [f"selected using {picked[1]} matching runtime sample(s), median "
+                                                     f"{picked[2]:.2f} tok/s"]
+        elif cached:
+            plan = ExecutionPlan.from_json(json.dumps(cached.get("plan", cached)))
         else:
-            hw = HardwareProfile.discover() if device != "cpu" else HardwareProfile(device_count=1, device_memory_bytes=1 << 62, name="cpu")
-            hw.device_count = 1     # the command-line front end drives one device; multi-GPU runs use the library API
-            prof = estimate_runtime_state(report.config, report.tensor_bytes)
-            plan = AutomaticPlanner(hw).plan(report.config, prof, context=max(4096, a.max_tokens + 2048), batch=1,
+            plan = AutomaticPlanner(hw).plan(report.config, prof, context=context, batch=1,
                                              draft_model=a.draft_model, allow_quantization=quant is None)
+        bench_rate = None
+        if a.auto == "benchmark":
+            cands = candidate_plans(plan, report.config, prof, hw, context=context)
+            bench = benchmark_candidates(model_path, a, cands, prompt if a.prompt is not None else AUTO_BENCHMARK_PROMPT)
+            plan, bench_rate = bench.pop("_selected_plan"), bench["selected_median_token_rate"]
             if cache_path:
-                try:
-                    book = json.load(open(cache_path))
-                except (OSError, ValueError):
-                    book = {}
-                book[key] = json.loads(plan.to_json())
-                json.dump(book, open(cache_path, "w"), indent=1)
-        if quant is None and plan.weight_transformation.get("mode") == "affine" and device != "cpu":
-            quant = QuantizationOptions(bits=plan.weight_transformation["bits"], group_size=plan.weight_transformation["group_size"])
-        if plan.residency.get("mode") == "layerwise_host" and not layerwise:
+                write_plan_cache(cache_path, key, plan, bench_rate)
+            json.dump(bench, sys.stdout, indent=1)
+            sys.stdout.write("\n")
+            return 0
+        if cache_path and not cached and picked is None:
+            write_plan_cache(cache_path, key, plan, None)
+        if a.auto == "plan":
+            json.dump({"schema_version": 2, "model": {"path": model_path, "model_type": report.model_type,
+                                                      "tensor_bytes": report.tensor_bytes},
+                       "hardware": dataclasses.asdict(hw), "plan": json.loads(plan.to_json()),
+                       "explanation": {"summary": "; ".join(plan.rationale), "entries": list(plan.rationale)}}, sys.stdout, indent=1)
+            sys.stdout.write("\n")
+            return 0
+        print("[eredu] automatic plan: " + "; ".join(plan.rationale), file=sys.stderr)
+    dense_disk = a.dense_disk_stream
+    expert_cache, ec_budget, ec_eviction = a.expert_cache, a.expert_cache_device_budget_bytes, a.expert_cache_eviction
+    if plan is not None:
+        # explicit flags win over the plan: the plan only fills what the command line left at its default
+        wt = plan.weight_transformation
+        if quant is None and wt.get("mode") in ("affine", "mxfp4") and device != "cpu":
+            quant = QuantizationOptions(bits=wt.get("bits", 4), group_size=wt.get("group_size", 64), mode=wt["mode"])
+        mode = plan.residency.get("mode")
+        if mode == "layerwise_host" and not (layerwise or dense_disk):
             layerwise, window = True, int(plan.residency.get("device_layer_window", 1))
-        if a.verbose or a.auto == "plan":
-            print("[eredu] plan: " + "; ".join(plan.rationale), file=sys.stderr)
+        elif mode == "dense_disk_stream" and not (layerwise or dense_disk):
+            dense_disk = True
+            a.dense_host_lookahead = max(1, int(plan.residency.get("host_lookahead") or a.dense_host_lookahead))
+            a.dense_background_queue = max(1, int(plan.residency.get("background_queue") or a.dense_background_queue))
+        if plan.expert_cache and not expert_cache:
+            expert_cache = True
+            ec_budget = ec_budget or plan.expert_cache.get("device_budget_bytes")
+            ec_eviction = plan.expert_cache.get("eviction", ec_eviction)
     t0 = time.perf_counter()
     lm = LoadedModel.load(model_path, ModelLoadOptions(device=device, quantization=quant, mapped_shards=a.mapped_shards,
                                                        max_batch=1, max_seq_len=max(4096, a.max_tokens + 2048),
-                                                       weight_residency=("dense_disk_stream" if a.dense_disk_stream else
+                                                       weight_residency=("dense_disk_stream" if dense_disk else
                                                                          "layerwise_host" if layerwise else "device"),
                                                        dense_host_lookahead=a.dense_host_lookahead,
                                                        dense_background_queue=a.dense_background_queue,
                                                        host_budget_bytes=a.host_budget_bytes,
                                                        device_layer_window=window,
-                                                       expert_cache=a.expert_cache,
-                                                       expert_cache_device_budget_bytes=a.expert_cache_device_budget_bytes,
-                                                       expert_cache_eviction=a.expert_cache_eviction))
+                                                       expert_cache=expert_cache,
+                                                       expert_cache_device_budget_bytes=ec_budget,
+                                                       expert_cache_eviction=ec_eviction))
     load_time = time.perf_counter() - t0
     gen_cfg = lm.tokenizer.generation_config if lm.tokenizer else {}
     sp = resolve_sampling(a, gen_cfg)
@@ -281,7 +405,8 @@ def main(argv=None) -> int:
         for st in components["stages"]:
             print(f"[eredu]   {st['name']:<28} {st['seconds'] * 1e3:9.3f} ms  {st['share'] * 100:5.1f} %", file=sys.stderr)
     if a.telemetry_json:
-        tel = ExecutionTelemetry(plan={"device": device, "auto": None if a.no_auto else a.auto, "quantization": vars(quant) if quant else None,
+        tel = ExecutionTelemetry(plan={"device": device, "auto": None if a.no_auto else a.auto, "model_type": lm.config.model_type,
+                                       "tensor_bytes": report.tensor_bytes if report is not None else None, "quantization": vars(quant) if quant else None,
                                        "execution_plan": json.loads(plan.to_json()) if plan is not None else None,
                                        "flags": {k: v for k, v in vars(a).items() if k not in ("prompt",)}},
                                  hardware=hardware_profile(device), prompt_tokens=res["prompt_tokens"],

@@ -373,3 +373,99 @@ class AutomaticPlanner:
                              rationale=why)
         plan.validate()
         return plan
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Candidate enumeration and feedback (eredu-cli/src/main.rs:1259-1505 base / benchmark candidates;
+# eredu-core/src/automatic.rs:1185-1250 selection from prior telemetry)
+
+def _plan_key(plan: "ExecutionPlan | dict") -> str:
+    d = asdict(plan) if isinstance(plan, ExecutionPlan) else dict(plan)
+    d.pop("rationale", None)
+    return json.dumps(d, sort_keys=True)
+
+
+def candidate_plans(heuristic: ExecutionPlan, cfg: ModelConfig, profile: ModelResourceProfile, hw: HardwareProfile,
+                    context: int = 4096, batch: int = 1, memory_fraction: float = 0.92) -> list[ExecutionPlan]:
+    """Plans worth timing for this model on one device of this node: fully resident (when it fits), layer window from
+    pinned host memory (when the weights fit in host memory), dense streaming from disk; each bounded form also with
+    the expert cache for sparse models; the heuristic plan last. Duplicates are dropped, order is stable."""
+    device_budget = int((hw.device_free_bytes or hw.device_memory_bytes) * memory_fraction)
+    host_budget = int(hw.host_memory_bytes * 0.8) if hw.host_memory_bytes else 0
+    tp = int(heuristic.topology.get("tensor", 1))
+    need = profile.weight_bytes // tp + kv_bytes_for(profile, context, batch) // tp + profile.workspace_bytes
+    resident_fits = need <= device_budget
+    layerwise_fits = host_budget == 0 or profile.weight_bytes // tp <= host_budget
+    base = dict(device=dict(heuristic.device), topology=dict(heuristic.topology),
+                weight_transformation=dict(heuristic.weight_transformation), max_mapped_shards=heuristic.max_mapped_shards)
+    out, seen = [], set()
+
+    def push(plan: ExecutionPlan):
+        plan.validate()
+        k = _plan_key(plan)
+        if k not in seen:
+            seen.add(k)
+            out.append(plan)
+
+    forms = []
+    if resident_fits:
+        forms.append(({"mode": "fully_resident"}, False, "fully resident"))
+    if layerwise_fits:
+        forms.append(({"mode": "layerwise_host", "device_layer_window": 1, "device_budget_bytes": device_budget,
+                       "host_budget_bytes": host_budget or None}, True, "one layer at a time from pinned host memory"))
+    forms.append(({"mode": "dense_disk_stream", "device_budget_bytes": device_budget, "host_budget_bytes": host_budget or None,
+                   "host_lookahead": 2 if host_budget else 0, "background_queue": 2 if host_budget else 0}, True,
+                  "dense layers streamed from disk"))
+    for residency, bounded, why in forms:
+        caps = {"exact_completion": True, "collectives": tp > 1, "transfers": bounded, "persistent_cache": False}
+        push(ExecutionPlan(residency=residency, required_capabilities=caps, rationale=[f"candidate: {why}"], **base))
+        if bounded and cfg.is_moe:
+            push(ExecutionPlan(residency=residency, required_capabilities=caps,
+                               expert_cache={"eviction": "lru", "device_budget_bytes": device_budget // 2},
+                               rationale=[f"candidate: {why} + expert cache"], **base))
+    h = ExecutionPlan.from_json(heuristic.to_json())
+    if h.drafting.get("mode") != "disabled":
+        h.drafting = {"mode": "disabled"}      # drafting is a separate axis: candidates compare residency forms
+    push(h)
+    return out
+
+
+def _median(xs: list) -> float:
+    xs = sorted(xs)
+    m = len(xs) // 2
+    return xs[m] if len(xs) % 2 else 0.5 * (xs[m - 1] + xs[m])
+
+
+def select_from_feedback(telemetry: list, model_type: str, tensor_bytes: int, device: str,
+                         minimum_tokens: int = 1) -> Optional[tuple]:
+    """Best plan among earlier runs of this model on this device: telemetry records (dicts as written by
+    ``--telemetry-json``) are grouped by their execution plan, each group scored by the median decode rate (total
+    rate when a run had no decode phase). Returns ``(plan, samples, median_rate)`` or None when nothing matches."""
+    groups: dict[str, tuple] = {}
+    for t in telemetry:
+        p = (t.get("plan") or {})
+        ep = p.get("execution_plan")
+        if not ep or t.get("generated_tokens", 0) < minimum_tokens:
+            continue
+        if p.get("device") != device or p.get("model_type") not in (None, model_type):
+            continue
+        if p.get("tensor_bytes") not in (None, tensor_bytes) or ep.get("schema_version") != EXECUTION_PLAN_SCHEMA_VERSION:
+            continue
+        timing = t.get("timing") or {}
+        rate = timing.get("decode_token_rate") or 0.0
+        if not (isinstance(rate, (int, float)) and rate > 0 and rate == rate and rate != float("inf")):
+            rate = timing.get("token_rate") or 0.0
+        if not (isinstance(rate, (int, float)) and rate > 0 and rate == rate and rate != float("inf")):
+            continue
+        k = _plan_key(ep)
+        groups.setdefault(k, (ep, []))[1].append(float(rate))
+    best = None
+    for ep, rates in groups.values():
+        try:
+            plan = ExecutionPlan.from_json(json.dumps(ep))
+        except (ValueError, TypeError):
+            continue
+        med = _median(rates)
+        if best is None or med > best[2]:
+            best = (plan, len(rates), med)
+    return best

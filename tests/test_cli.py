@@ -59,14 +59,33 @@ def test_cli_automatic_plan_and_cache(tmp_path, capsys):
     cfg = dataclasses.replace(C.tiny_llama(), vocab_size=b.vocab_size(), eos_token_id=b.eos_ids[0])
     ck.save_safetensors_checkpoint(tmp_path, cfg, random_state(cfg, seed=0, std=0.05), torch.float32)
     tel, cache = tmp_path / "tel.json", tmp_path / "auto.json"
-    args = ["-m", str(tmp_path), "hi", "--device", "cpu", "-n", "4", "--auto", "plan", "--auto-cache", str(cache),
-            "--telemetry-json", str(tel)]
+    # --auto plan: the report goes to stdout, nothing is loaded or generated
+    assert main(["-m", str(tmp_path), "hi", "--device", "cpu", "--auto", "plan"]) == 0
+    rep = json.loads(capsys.readouterr().out)
+    assert rep["plan"]["schema_version"] == 2 and rep["plan"]["residency"]["mode"] == "fully_resident" and rep["explanation"]["summary"]
+    # --auto quick (the default): plan, then run with it; the plan is cached and recorded in the telemetry
+    args = ["-m", str(tmp_path), "hi", "--device", "cpu", "-n", "4", "--auto-cache", str(cache), "--telemetry-json", str(tel)]
     assert main(args) == 0
-    assert "plan:" in capsys.readouterr().err
-    plan = json.loads(tel.read_text())["plan"]["execution_plan"]
+    assert "automatic plan:" in capsys.readouterr().err
+    t = json.loads(tel.read_text())
+    plan = t["plan"]["execution_plan"]
     assert plan["schema_version"] == 2 and plan["residency"]["mode"] == "fully_resident" and plan["topology"]["tensor"] == 1
+    assert t["plan"]["model_type"] == "llama" and t["plan"]["tensor_bytes"] > 0
     assert len(json.loads(cache.read_text())) == 1
     assert main(args) == 0                                     # second run takes the cached plan
+    capsys.readouterr()
+    # --auto-feedback: earlier telemetry of this model decides; the faster plan (layer window, made up here) wins
+    slow = dict(t, timing=dict(t["timing"], decode_token_rate=10.0))
+    fast_plan = dict(plan, residency={"mode": "layerwise_host", "device_layer_window": 1})
+    fast = dict(t, plan=dict(t["plan"], execution_plan=fast_plan), timing=dict(t["timing"], decode_token_rate=50.0))
+    other = dict(fast, plan=dict(fast["plan"], model_type="qwen3"), timing=dict(t["timing"], decode_token_rate=500.0))
+    fb = tmp_path / "fb.json"
+    fb.write_text(json.dumps([slow, fast, fast, other]))
+    assert main(["-m", str(tmp_path), "hi", "--device", "cpu", "--auto", "plan", "--auto-feedback", str(fb)]) == 0
+    rep = json.loads(capsys.readouterr().out)
+    assert rep["plan"]["residency"]["mode"] == "layerwise_host" and "2 matching runtime sample" in rep["explanation"]["summary"]
+    with pytest.raises(SystemExit):
+        main(["-m", str(tmp_path), "hi", "--device", "cpu", "--auto-feedback", str(tmp_path / "missing.json")])
     # an artifact that cannot be loaded is refused before any payload is read
     bad = tmp_path / "bad"
     bad.mkdir()
@@ -142,3 +161,24 @@ def test_cli_profile_components(tmp_path, capsys):
     names = [s["name"] for s in comp["stages"]]
     assert names == ["model.embed_tokens", "model.layers.0.output", "model.layers.1.output", "model.layers.2.output", "lm_head"]
     assert abs(sum(s["share"] for s in comp["stages"]) - 1.0) < 1e-6
+
+
+def test_cli_automatic_benchmark(tmp_path, capsys):
+    """--auto benchmark times each admitted residency form in a fresh process and reports the fastest."""
+    from eredu_b200.formats import checkpoint as ck
+    from eredu_b200.models import config as C
+    from eredu_b200.models.llama import random_state
+
+    b = make_bundle(tmp_path)
+    cfg = dataclasses.replace(C.tiny_llama(), vocab_size=b.vocab_size(), eos_token_id=-1)
+    ck.save_safetensors_checkpoint(tmp_path, cfg, random_state(cfg, seed=0, std=0.05), torch.float32)
+    cache = tmp_path / "auto.json"
+    assert main(["-m", str(tmp_path), "--device", "cpu", "--auto", "benchmark", "--auto-benchmark-tokens", "6",
+                 "--auto-cache", str(cache), "hello"]) == 0
+    rep = json.loads(capsys.readouterr().out)
+    modes = [c["plan"]["residency"]["mode"] for c in rep["candidates"]]
+    assert modes[:3] == ["fully_resident", "layerwise_host", "dense_disk_stream"] and len(modes) == 3
+    assert all(c["median_token_rate"] and not any("error" in t for t in c["trials"]) for c in rep["candidates"]), rep
+    assert rep["selected"] == rep["candidates"][rep["selected_index"]]["plan"] and rep["selection_metric"] == "median_decode_token_rate"
+    entry = next(iter(json.loads(cache.read_text()).values()))
+    assert entry["plan"] == rep["selected"] and entry["benchmark_token_rate"] == rep["selected_median_token_rate"]
