@@ -135,9 +135,8 @@ def mamba_forward(model, li, lw, x, batch, kv):
     xbc = ops.short_conv(proj, lw.m_conv_w, lw.m_conv_b, conv_state, state_idx, batch.cu_q if batch.is_prefill else None,
                          batch.q_per_seq, batch.positions, batch.slots, batch.max_q_len, mode=1, x_off=d_mlp2 + inter)
     xs = xbc[:, :inter].view(M, heads, P)
-    rep = heads // groups
-    Bs = xbc[:, inter:inter + groups * N].view(M, groups, N).repeat_interleave(rep, dim=1)
-    Cs = xbc[:, inter + groups * N:].view(M, groups, N).repeat_interleave(rep, dim=1)
+    Bs = xbc[:, inter:inter + groups * N].reshape(M, groups, N)        # one B / C per group: the scan maps heads to groups
+    Cs = xbc[:, inter + groups * N:].reshape(M, groups, N)
     dt = torch.clamp_min(F.softplus(dt_raw + lw.m_dt_bias[None, :]), cfg.time_step_min)
     A = -torch.exp(lw.m_A_log)
     slots = state_idx.view(-1).long()
@@ -157,7 +156,7 @@ def mamba_forward(model, li, lw, x, batch, kv):
     else:
         Bn, T = slots.shape[0], batch.q_per_seq
         old = ssm_state.index_select(0, slots)
-        S, y = ops.mamba2_scan(xs.view(Bn, T, heads, P), Bs.view(Bn, T, heads, N), Cs.view(Bn, T, heads, N),
+        S, y = ops.mamba2_scan(xs.reshape(Bn, T, heads, P), Bs.view(Bn, T, groups, N), Cs.view(Bn, T, groups, N),
                                dt.view(Bn, T, heads), A, lw.m_D, old)
         active = (batch.slots.view(Bn, T)[:, 0] >= 0).view(Bn, 1, 1, 1)
         ssm_state.index_copy_(0, slots, torch.where(active, S, old))

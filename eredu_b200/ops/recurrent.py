@@ -17,6 +17,7 @@ from . import native
 from .native import I, P, check, lib, ptr, stream_ptr
 
 native.register("eredu_gated_delta_scan", I, [P, P, P, P, P, P, P, I, I, I, I, I, I, P])
+native.register("eredu_mamba2_scan", I, [P, P, P, P, P, P, P, P, I, I, I, I, I, I, P])
 
 
 def gated_delta_scan_ref(q, k, v, log_decay, beta, state: Optional[torch.Tensor] = None):
@@ -71,10 +72,15 @@ def mamba2_scan_ref(x, B, C, dt, A, D, state: Optional[torch.Tensor] = None):
     """Mamba-2 selective state-space recurrence, token by token (eredu/src/backend/mlx/architectures/nemotron_h/
     model.rs:1929-1962): ``S <- S * exp(dt A) + x (dt B)^T;  y = S C + D x`` per head.
 
-    x [Bt, T, H, P]; B, C [Bt, T, H, N] (already expanded from groups to heads); dt [Bt, T, H] (after softplus and floor);
-    A [H] (negative); D [H]; state fp32 [Bt, H, P, N]. Returns (state, y [Bt, T, H, P] in x's dtype)."""
+    x [Bt, T, H, P]; B, C [Bt, T, G, N] with G dividing H (one B / C per group of heads; G = H when already expanded);
+    dt [Bt, T, H] (after softplus and floor); A [H] (negative); D [H]; state fp32 [Bt, H, P, N]. Returns (state,
+    y [Bt, T, H, P] in x's dtype)."""
     Bt, T, H, P = x.shape
     N = B.shape[-1]
+    if B.shape[2] != H:
+        if H % B.shape[2]:
+            raise ValueError("Mamba-2 group count must divide the head count")
+        B, C = B.repeat_interleave(H // B.shape[2], 2), C.repeat_interleave(H // C.shape[2], 2)
     S = torch.zeros((Bt, H, P, N), dtype=torch.float32, device=x.device) if state is None else state.float().clone()
     xf, Bf, Cf, dtf = x.float(), B.float(), C.float(), dt.float()
     Af, Df = A.float().view(1, H, 1, 1), D.float().view(1, H, 1)
@@ -88,5 +94,20 @@ def mamba2_scan_ref(x, B, C, dt, A, D, state: Optional[torch.Tensor] = None):
     return S, torch.stack(ys, 1).to(x.dtype)
 
 
-# No CUDA kernel for the Mamba-2 scan yet: CUDA tensors run the same tensor operations.
-mamba2_scan = mamba2_scan_ref
+def mamba2_scan(x, B, C, dt, A, D, state: Optional[torch.Tensor] = None):
+    """CUDA: one kernel for the whole chunk (bf16 x / B / C, state size 64, 128 or 256); otherwise the reference."""
+    if not x.is_cuda or x.dtype != torch.bfloat16 or B.shape[-1] not in (64, 128, 256):
+        return mamba2_scan_ref(x, B, C, dt, A, D, state)
+    Bt, T, H, P_ = x.shape
+    G, N = B.shape[2], B.shape[3]
+    if tuple(C.shape) != tuple(B.shape) or tuple(B.shape[:2]) != (Bt, T) or H % G or tuple(dt.shape) != (Bt, T, H):
+        raise ValueError("Mamba-2 B / C / dt shapes do not match x")
+    S = torch.zeros((Bt, H, P_, N), dtype=torch.float32, device=x.device) if state is None else state.float().contiguous().clone()
+    if tuple(S.shape) != (Bt, H, P_, N):
+        raise ValueError(f"Mamba-2 state shape {tuple(S.shape)} must equal {(Bt, H, P_, N)}")
+    out = torch.empty((Bt, T, H, P_), dtype=x.dtype, device=x.device)
+    code = lib().eredu_mamba2_scan(ptr(x.contiguous()), ptr(B.to(torch.bfloat16).contiguous()), ptr(C.to(torch.bfloat16).contiguous()),
+                                   ptr(dt.float().contiguous()), ptr(A.float().contiguous()), ptr(D.float().contiguous()), ptr(S),
+                                   ptr(out), Bt, T, H, G, P_, N, stream_ptr(x.device))
+    check(code, "eredu_mamba2_scan")
+    return S, out

@@ -270,7 +270,7 @@ def test_whole_model_forward_dry_run(dry_cuda, family):
     elif family == "nemotron_h":
         from test_nemotron_h import nh_cfg, state_for as nh_state
 
-        cfg = nh_cfg(hidden_size=256, head_dim=64, vocab_size=512, intermediate_size=256)
+        cfg = nh_cfg(hidden_size=256, head_dim=64, vocab_size=512, intermediate_size=256, ssm_state_size=64)
         sd = nh_state(cfg)
         kw["moe_factory"] = make_moe_factory()
     else:
@@ -299,5 +299,7 @@ def test_whole_model_forward_dry_run(dry_cuda, family):
         assert "eredu_gemm_bf16_grouped" in calls
     if family in ("lfm2", "nemotron_h"):
         assert "eredu_short_conv" in calls
+    if family == "nemotron_h":
+        assert "eredu_mamba2_scan" in calls
     if family in ("qwen3_next", "kimi_linear"):
         assert {"eredu_short_conv", "eredu_gated_delta_scan"} <= calls
