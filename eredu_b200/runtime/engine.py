@@ -126,6 +126,14 @@ class Engine:
             self.kv.allocator.release(seq.pages)
             seq.pages = []
 
+    def snapshot_state(self, seq: Sequence):
+        """Recurrent state of a hybrid model's sequence at its current length (None when there is none to keep)."""
+        return self.kv.snapshot_state(seq.pages[0]) if seq.pages else None
+
+    def restore_state(self, seq: Sequence, snap) -> None:
+        if seq.pages:
+            self.kv.restore_state(seq.pages[0], snap)
+
     # ------------------------------------------------------------------------------------------ helpers
     def _t(self, data, dtype):
         t = torch.as_tensor(data, dtype=dtype)

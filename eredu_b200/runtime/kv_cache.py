@@ -119,6 +119,33 @@ class PagedKVCache:
         if self.page_to_slot is not None and slot >= 0:
             self._free_state_slots.append(slot)
 
+    # ---- recurrent-state snapshots: K/V pages roll back by a length change, the fixed-size states of hybrid layers
+    # (short-convolution history, gated-delta / Mamba matrices) have to be copied out and put back.
+    def has_recurrent_state(self) -> bool:
+        return self.conv_state is not None or self.page_to_slot is not None
+
+    def snapshot_state(self, first_page: int):
+        """Copies of this sequence's recurrent states (None for attention-only models)."""
+        if not self.has_recurrent_state():
+            return None
+        conv = self.conv_state[:, int(first_page)].clone() if self.conv_state is not None else None
+        la = None
+        if self.page_to_slot is not None:
+            slot = self._slot_of_page[int(first_page)]
+            la = (self.la_conv_state[:, slot].clone(), self.la_rec_state[:, slot].clone())
+        return conv, la
+
+    def restore_state(self, first_page: int, snap) -> None:
+        if snap is None:
+            return
+        conv, la = snap
+        if conv is not None:
+            self.conv_state[:, int(first_page)].copy_(conv)
+        if la is not None:
+            slot = self._slot_of_page[int(first_page)]
+            self.la_conv_state[:, slot].copy_(la[0])
+            self.la_rec_state[:, slot].copy_(la[1])
+
     def linear_attention_state(self, li: int):
         i = self._la_index[li]
         return self.la_conv_state[i], self.la_rec_state[i]

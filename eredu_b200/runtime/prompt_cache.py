@@ -10,6 +10,8 @@ Layout of a cache directory::
     manifest.json                         (rank 0 of a single-rank run)   or
     rank-pp{P}-tp{T}-ep{E}/manifest.json  (one directory per rank of a distributed run)
         layer-0000.safetensors ...        arrays  "k.{start}" / "v.{start}"  of shape [n_kv_local, tokens, head_dim]
+        state.safetensors                 hybrid models: "layer.{i}.convolution" / "layer.{i}.recurrent", the fixed-size
+                                          states after the last cached token (catalogued in ``state_tensors``)
 """
 from __future__ import annotations
 
@@ -148,7 +150,12 @@ class PromptCacheManifest:
             if os.path.isabs(b.shard) or ".." in Path(b.shard).parts:
                 raise Malformed(f"unsafe shard path {b.shard!r}")
             per_layer.setdefault(b.global_layer, []).append(b)
+        self._validate_state_tensors()
         for li in range(self.global_layer_start, self.global_layer_end):
+            if self.layer_layout[li - self.global_layer_start].get("kind") != "key_value":
+                if per_layer.get(li):
+                    raise Malformed(f"layer {li} keeps no K/V but has K/V blocks")
+                continue
             pos = 0
             for b in sorted(per_layer.get(li, []), key=lambda x: x.start):
                 if b.start != pos:
@@ -156,6 +163,26 @@ class PromptCacheManifest:
                 pos = b.end
             if pos != self.total_prefix_tokens:
                 raise Malformed(f"layer {li}: blocks cover {pos} of {self.total_prefix_tokens} tokens")
+
+    def _validate_state_tensors(self):
+        """Fixed-size recurrent states: exactly one entry per (layer, role) the layout declares, taken at the end of the
+        prefix, with a safe shard path and a payload hash."""
+        expected = set()
+        for i, layer in enumerate(self.layer_layout):
+            for role in layer.get("fixed_state", []):
+                expected.add((self.global_layer_start + i, role))
+        seen = set()
+        for e in self.state_tensors:
+            key = (e.get("layer"), e.get("role"))
+            if key in seen:
+                raise Malformed("fixed-state tensors contain duplicate owner/role entries")
+            seen.add(key)
+            if os.path.isabs(e.get("shard", "/")) or ".." in Path(e["shard"]).parts or not _is_sha256_hex(e.get("sha256")):
+                raise Malformed("invalid fixed-state tensor entry")
+            if e.get("tokens") != self.total_prefix_tokens:
+                raise Malformed("fixed-state tensor was not taken at the end of the prefix")
+        if seen != expected:
+            raise Malformed(f"fixed-state tensor count {len(seen)} does not match layout count {len(expected)}")
 
     def to_json(self) -> str:
         return json.dumps(asdict(self), indent=1)
@@ -183,7 +210,11 @@ class PromptCacheManifest:
 def architecture_fingerprint(cfg) -> str:
     """Everything that changes the meaning of cached K/V: head geometry, positional encoding, norms."""
     keys = ("model_type", "hidden_size", "num_hidden_layers", "num_attention_heads", "num_key_value_heads", "head_dim",
-            "rope_theta", "rope_scaling", "rms_norm_eps", "qk_norm", "sliding_window", "attention_bias")
+            "rope_theta", "rope_scaling", "rms_norm_eps", "qk_norm", "sliding_window", "attention_bias",
+            # hybrid families: which layers keep what state, and the state geometry
+            "layer_types", "conv_l_cache", "linear_conv_kernel_dim", "linear_num_key_heads", "linear_num_value_heads",
+            "linear_key_head_dim", "linear_value_head_dim", "mamba_num_heads", "mamba_head_dim", "ssm_state_size",
+            "mamba_conv_kernel", "kv_lora_rank", "qk_rope_head_dim")
     blob = json.dumps({k: getattr(cfg, k, None) for k in keys}, sort_keys=True, default=str)
     return hashlib.sha256(blob.encode()).hexdigest()
 
@@ -194,8 +225,17 @@ def model_identity(engine, checkpoint_fingerprint: str) -> dict:
     first = model.first_layer
     n_local = model.num_local_layers()
     window = getattr(cfg, "sliding_window", None)
-    layout = [{"kind": "key_value", "attention": ({"sliding": int(window)} if window else "full"),
-               "num_key_value_heads": int(model.n_kv_local), "head_dim": int(cfg.head_dim)} for _ in range(n_local)]
+    layout = []
+    for li in range(first, first + n_local):
+        if cfg.layer_has_kv(li):
+            layout.append({"kind": "key_value", "attention": ({"sliding": int(window)} if window else "full"),
+                           "num_key_value_heads": int(model.n_kv_local), "head_dim": int(cfg.head_dim)})
+        elif cfg.layer_is_conv(li):
+            layout.append({"kind": "recurrent", "fixed_state": ["convolution"]})
+        elif cfg.layer_has_recurrent_state(li):
+            layout.append({"kind": "recurrent", "fixed_state": ["convolution", "recurrent"]})
+        else:
+            layout.append({"kind": "stateless"})
     return dict(model_family=cfg.model_type.split("_")[0], effective_model_type=cfg.model_type,
                 checkpoint_fingerprint=checkpoint_fingerprint, architecture_fingerprint=architecture_fingerprint(cfg),
                 layer_count=cfg.num_hidden_layers, global_layer_start=first, global_layer_end=first + n_local,
@@ -218,8 +258,6 @@ def save_prompt_cache(engine, seq, directory, checkpoint_fingerprint: str, prefi
                       block_tokens: int = 256, namespace: Optional[str] = None, replace_existing: bool = False) -> Path:
     """Persist the K/V of the first ``prefix_tokens`` cached tokens of ``seq`` (default: all cached tokens).
     Every rank of a distributed run calls this with the same arguments and writes its own directory."""
-    if engine.cfg.is_hybrid:
-        raise Incompatible("prompt caches of hybrid (convolution-state) models are not supported")
     from ..formats.checkpoint import _np
     from ..lib import _eredu_host as H
 
@@ -228,6 +266,9 @@ def save_prompt_cache(engine, seq, directory, checkpoint_fingerprint: str, prefi
     n = seq.kv_len if prefix_tokens is None else int(prefix_tokens)
     if n <= 0 or n > seq.kv_len:
         raise PromptCacheError(f"cannot save {n} tokens of a sequence with {seq.kv_len} cached tokens")
+    if engine.kv.has_recurrent_state() and n != seq.kv_len:
+        # the convolution histories and recurrent matrices exist for the current length only
+        raise PromptCacheError(f"a hybrid model's cache is saved at the sequence's current length ({seq.kv_len}), not at {n}")
     if block_tokens % PAGE != 0:
         raise PromptCacheError(f"block size must be a multiple of the {PAGE}-token page")
     tokens = (seq.prompt + seq.output)[:n]
@@ -247,7 +288,32 @@ def save_prompt_cache(engine, seq, directory, checkpoint_fingerprint: str, prefi
                    "tensor_parallel_rank": topo.tensor_parallel[1] if topo.tensor_parallel else None,
                    "expert_parallel_rank": topo.expert_parallel[1] if topo.expert_parallel else None}
     blocks = []
+    state_entries = []
+    state_items = []
+    snap = engine.snapshot_state(seq)
+    if snap is not None:
+        conv, la = snap
+        per_layer_states = {}
+        if conv is not None:
+            for li, i in engine.kv._conv_index.items():
+                per_layer_states.setdefault(li, {})["convolution"] = conv[i]
+        if la is not None:
+            for li, i in engine.kv._la_index.items():
+                per_layer_states.setdefault(li, {})["convolution"] = la[0][i]
+                per_layer_states[li]["recurrent"] = la[1][i]
+        for li in sorted(per_layer_states):
+            for role, t in sorted(per_layer_states[li].items()):
+                t = t.contiguous().cpu()
+                name = f"layer.{li}.{role}"
+                state_items.append((name, _DT[t.dtype], list(t.shape), _np(t)))
+                state_entries.append({"layer": li, "role": role, "shard": "state.safetensors", "array": name,
+                                      "shape": list(t.shape), "dtype": _DT[t.dtype], "tokens": n,
+                                      "logical_bytes": t.numel() * t.element_size(),
+                                      "sha256": hashlib.sha256(_bytes_of(t)).hexdigest()})
+        H.write_safetensors(str(tmp / "state.safetensors"), state_items, {"format": "eredu-prompt-cache"})
     for li in range(ident["global_layer_start"], ident["global_layer_end"]):
+        if not engine.cfg.layer_has_kv(li):
+            continue
         k_pool, v_pool = engine.kv.layer(li)
         # [pages, n_kv, PAGE, D] -> [n_kv, pages * PAGE, D]
         k = k_pool[pages].permute(1, 0, 2, 3).reshape(k_pool.shape[1], -1, k_pool.shape[3])[:, :n]
@@ -267,7 +333,8 @@ def save_prompt_cache(engine, seq, directory, checkpoint_fingerprint: str, prefi
     content = hashlib.sha256((sha256_tokens(tokens) + ident["checkpoint_fingerprint"]).encode()).hexdigest()
     man = PromptCacheManifest(schema_version=PROMPT_CACHE_SCHEMA_VERSION, prefix_content_fingerprint=content,
                               block_size_tokens=block_tokens, batch_size=1, total_prefix_tokens=n,
-                              prefix_sha256=sha256_tokens(tokens), application_namespace=namespace, blocks=blocks, **ident)
+                              prefix_sha256=sha256_tokens(tokens), application_namespace=namespace, blocks=blocks,
+                              state_tensors=state_entries, **ident)
     man.validate()
     (tmp / "manifest.json").write_text(man.to_json())
     # publish atomically: readers either see the old cache or the complete new one
@@ -312,6 +379,9 @@ def load_prompt_cache(engine, directory, tokens, checkpoint_fingerprint: str, sa
     tokens = [int(t) for t in tokens]
     if n > len(tokens) or sha256_tokens(tokens[:n]) != man.prefix_sha256:
         raise Incompatible("the cached prefix is not a prefix of the request")
+    if man.state_tensors and len(tokens) <= n:
+        # recurrent states exist for exactly n tokens: the request must bring at least one more so that logits can be made
+        raise Incompatible("a hybrid model's cached prefix must be a strict prefix of the request")
     seq = engine.new_sequence(tokens, sampling, max_new_tokens, eos_ids)
     try:
         usable = min(n, len(tokens) - 1)
@@ -337,6 +407,25 @@ def load_prompt_cache(engine, directory, tokens, checkpoint_fingerprint: str, sa
             # pool[page, head, offset, :] = block[head, token, :]
             k_pool[page_ids, :, pos % PAGE] = kt[:, :end - b.start].transpose(0, 1).to(k_pool.dtype)
             v_pool[page_ids, :, pos % PAGE] = vt[:, :end - b.start].transpose(0, 1).to(v_pool.dtype)
+        if man.state_tensors:
+            st = H.SafetensorsStore(str(root / "state.safetensors"), 4)
+            first_page = seq.pages[0]
+            slot = engine.kv._slot_of_page.get(int(first_page)) if engine.kv.page_to_slot is not None else None
+            for e in man.state_tensors:
+                raw = np.asarray(st.tensor(e["array"]))
+                if verify_payload and hashlib.sha256(raw.tobytes()).hexdigest() != e["sha256"]:
+                    raise Corrupt(f"payload hash mismatch in state.safetensors:{e['array']}")
+                t = _to_tensor(raw, _DT_INV[e["dtype"]], e["shape"]).to(engine.device)
+                li = e["layer"]
+                if li in engine.kv._conv_index:
+                    dst = engine.kv.conv_state[engine.kv._conv_index[li], int(first_page)]
+                elif e["role"] == "convolution":
+                    dst = engine.kv.la_conv_state[engine.kv._la_index[li], slot]
+                else:
+                    dst = engine.kv.la_rec_state[engine.kv._la_index[li], slot]
+                if tuple(dst.shape) != tuple(t.shape):
+                    raise Incompatible(f"fixed-state tensor {e['array']} has shape {tuple(t.shape)}, the model keeps {tuple(dst.shape)}")
+                dst.copy_(t.to(dst.dtype))
         seq.kv_len = usable
     except Exception:
         engine.release(seq)

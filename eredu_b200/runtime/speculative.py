@@ -51,11 +51,12 @@ class SpeculativeDecoder:
     reference's ``MtpConfig`` (4 draft tokens, eredu-core/src/generation.rs:339-360)."""
 
     def __init__(self, target: Engine, draft: Engine, k: int = 4):
-        if target.cfg.is_hybrid or draft.cfg.is_hybrid:
-            # rejected proposals would have to be rolled out of the recurrent convolution state as well
-            raise NotImplementedError("speculative decoding is not available for hybrid (convolution-state) models")
         assert target.cfg.vocab_size == draft.cfg.vocab_size, "draft and target must share the vocabulary"
         self.t, self.d, self.k = target, draft, k
+        # Hybrid models: rejected proposals also have to leave the recurrent states. The draft keeps a snapshot after every
+        # draft step and goes back to the one that matches the accepted prefix; the target keeps one snapshot per round
+        # and, after a partial acceptance, re-feeds the accepted tokens from it (one extra pass in that case only).
+        self.t_hybrid, self.d_hybrid = target.kv.has_recurrent_state(), draft.kv.has_recurrent_state()
         self.stats = SpecStats()
         self.cuda = target.cuda
 
@@ -169,6 +170,7 @@ class SpeculativeDecoder:
         # ---- draft: k proposals per sequence
         drafted = [[] for _ in range(B)]
         p_d = []
+        d_snaps = []                          # hybrid draft: state after each draft step
         base = [s.kv_len + 1 for s in tseqs]  # position of the first drafted token (target kv_len = position of `last`)
         for j in range(k):
             if j == 0:
@@ -181,6 +183,8 @@ class SpeculativeDecoder:
                 logits = self._multi_token_step(self.d, dseqs, feed, all_rows=False, uniform=True)
                 for s in dseqs:
                     s.kv_len += 1
+            if self.d_hybrid:
+                d_snaps.append([self.d.snapshot_state(s) for s in dseqs])
             probs, toks = self._probs_and_tokens(self.d, logits, [sp] * B, [base[b] + j for b in range(B)],
                                                  [s.seq_id for s in tseqs])
             p_d.append(probs)
@@ -190,6 +194,7 @@ class SpeculativeDecoder:
         t1 = time.perf_counter()
         # ---- target: one pass over [last, d_1 .. d_k]
         feed = [[last[i]] + drafted[b] for b, i in enumerate(live)]
+        t_snaps = [self.t.snapshot_state(s) for s in tseqs] if self.t_hybrid else None
         logits = self._multi_token_step(self.t, tseqs, feed, all_rows=True, uniform=True)  # [B*(k+1), V]
         pos_rows = [base[b] + j for b in range(B) for j in range(k + 1)]
         sid_rows = [tseqs[b].seq_id for b in range(B) for _ in range(k + 1)]
@@ -208,12 +213,23 @@ class SpeculativeDecoder:
         sync()
         t2 = time.perf_counter()
         # ---- commit: accepted drafts + the token that ends the round
+        if self.t_hybrid:
+            # the verify pass pushed all k+1 tokens through the recurrent layers: where fewer were accepted, go back and
+            # feed only those (their K/V rows are rewritten with the same values)
+            redo = [b for b in range(B) if int(res[b][0]) < k]
+            if redo:
+                for b in redo:
+                    self.t.restore_state(tseqs[b], t_snaps[b])
+                self._multi_token_step(self.t, [tseqs[b] for b in redo], [feed[b][:1 + int(res[b][0])] for b in redo],
+                                       all_rows=False, uniform=False)
         for b, i in enumerate(live):
             a, nxt = int(res[b][0]), int(res[b][1])
             if a == k:
                 nxt = int(bonus[b])
             outs[i].extend(drafted[b][:a] + [nxt])
             tseqs[b].kv_len += 1 + a                      # `last` and the accepted drafts are now cached
+            if self.d_hybrid:
+                self.d.restore_state(dseqs[b], d_snaps[min(a, k - 1)][b])
             d_valid = dseqs[b].kv_len - (k - 1) + min(a, k - 1)   # draft cache holds last, d_1..d_{k-1}
             dseqs[b].kv_len = d_valid
             pending[i] = ([drafted[b][k - 1]] if a == k else []) + [nxt]

@@ -106,3 +106,54 @@ def test_manifest_validation(tmp_path):
     # replace_existing publishes a fresh cache
     PC.save_prompt_cache(eng, s, tmp_path / "pc", "x", block_tokens=16, replace_existing=True)
     assert PC.open_prompt_cache(d).total_prefix_tokens == 40
+
+
+@pytest.mark.parametrize("family", ["lfm2", "qwen3_next", "nemotron_h"])
+def test_hybrid_models_persist_their_recurrent_state(family, tmp_path):
+    """Convolution histories and recurrent matrices are stored as fixed-state tensors at the end of the prefix and come
+    back into the new sequence's state slot."""
+    from test_speculative import _hybrid
+
+    cfg, model = _hybrid(family, 0)
+    eng = Engine(model, max_batch=2, max_seq_len=160)
+    g = torch.Generator().manual_seed(2)
+    prefix = torch.randint(3, cfg.vocab_size, (41,), generator=g).tolist()
+    tail = torch.randint(3, cfg.vocab_size, (7,), generator=g).tolist()
+    sp = SamplingParams(temperature=0.0)
+    s0 = eng.new_sequence(prefix + tail, sp, max_new_tokens=8)
+    want = run(eng, s0, 6)
+    eng.release(s0)
+    s1 = eng.new_sequence(prefix, sp, max_new_tokens=4)
+    eng.prefill([s1])
+    with pytest.raises(PC.PromptCacheError):
+        PC.save_prompt_cache(eng, s1, tmp_path / "pc", "ckpt", prefix_tokens=32)     # states exist at length 41 only
+    d = PC.save_prompt_cache(eng, s1, tmp_path / "pc", "ckpt", block_tokens=16)
+    eng.release(s1)
+    man = PC.open_prompt_cache(d)
+    kinds = [l["kind"] for l in man.layer_layout]
+    assert "recurrent" in kinds and "key_value" in kinds
+    n_state = sum(len(l.get("fixed_state", [])) for l in man.layer_layout)
+    assert len(man.state_tensors) == n_state > 0 and all(e["tokens"] == 41 for e in man.state_tensors)
+    assert {b.global_layer for b in man.blocks} == {i for i, k in enumerate(kinds) if k == "key_value"}
+
+    _, model2 = _hybrid(family, 0)
+    eng2 = Engine(model2, max_batch=2, max_seq_len=160)
+    busy = eng2.new_sequence([3, 4, 5], sp, max_new_tokens=4)          # occupies the first state slot / pages
+    eng2.prefill([busy])
+    s2 = PC.load_prompt_cache(eng2, d, prefix + tail, "ckpt", sp, max_new_tokens=8)
+    assert s2.kv_len == 41 and run(eng2, s2, 6) == want
+    with pytest.raises(PC.Incompatible):
+        PC.load_prompt_cache(eng2, d, prefix, "ckpt", sp, 8)            # nothing left to prefill: no state for 40 tokens
+    # a state entry that is missing, duplicated or taken elsewhere makes the manifest malformed
+    mj = json.loads((d / "manifest.json").read_text())
+    for damage in (lambda m: m["state_tensors"].pop(), lambda m: m["state_tensors"].append(dict(m["state_tensors"][0])),
+                   lambda m: m["state_tensors"][0].__setitem__("tokens", 40)):
+        bad = json.loads(json.dumps(mj))
+        damage(bad)
+        with pytest.raises(PC.Malformed):
+            PC.PromptCacheManifest.from_json(json.dumps(bad)).validate()
+    raw = bytearray((d / "state.safetensors").read_bytes())
+    raw[-2] ^= 0x10
+    (d / "state.safetensors").write_bytes(bytes(raw))
+    with pytest.raises(PC.Corrupt):
+        PC.load_prompt_cache(eng2, d, prefix + tail, "ckpt", sp, 8)

@@ -96,3 +96,59 @@ def test_graph_captured_round_matches_the_eager_decoder(draft_seed, temperature)
     assert s["rounds"] > 0 and s["emitted"] >= 48 - 2 * 5
     if draft_seed is None and temperature == 0.0:
         assert s["acceptance_rate"] > 0.6
+
+
+def _hybrid(family, seed):
+    from eredu_b200.models.moe import make_moe_factory
+
+    if family == "lfm2":
+        from test_lfm2 import lfm2_cfg
+
+        cfg = lfm2_cfg()
+        sd = random_state(cfg, seed=seed, std=0.08)
+    elif family == "qwen3_next":
+        from test_qwen_next import next_cfg, state_for
+
+        cfg = next_cfg()
+        sd = state_for(cfg, seed=seed) if "seed" in state_for.__code__.co_varnames else state_for(cfg)
+    else:
+        from test_nemotron_h import nh_cfg, state_for
+
+        cfg = nh_cfg()
+        sd = state_for(cfg, seed=seed)
+    return cfg, build_from_tensors(cfg, sd.__getitem__, sd.__contains__, "cpu", torch.float32, moe_factory=make_moe_factory())
+
+
+@pytest.mark.parametrize("family", ["lfm2", "qwen3_next", "nemotron_h"])
+@pytest.mark.parametrize("same_draft", [True, False])
+def test_hybrid_models_roll_their_recurrent_state_back(family, same_draft):
+    """Convolution histories and recurrent matrices leave the rejected proposals behind: greedy speculative output is
+    the plain greedy output, with a draft that is always accepted and with one that almost never is."""
+    cfg, target = _hybrid(family, 0)
+    _, draft = (cfg, target) if same_draft else _hybrid(family, 5)
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(3, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 21)]
+    sp = SamplingParams(temperature=0.0)
+    plain = Engine(target, max_batch=2, max_seq_len=96).generate(prompts, sp, 20)
+    dec = SpeculativeDecoder(Engine(target, max_batch=2, max_seq_len=96, use_cuda_graph=False),
+                             Engine(draft, max_batch=2, max_seq_len=96, use_cuda_graph=False), k=3)
+    assert dec.t_hybrid and dec.d_hybrid
+    assert dec.generate(prompts, sp, 20) == plain
+    st = dec.stats.summary()
+    assert st["acceptance_rate"] == 1.0 if same_draft else st["acceptance_rate"] < 0.6
+
+
+def test_state_snapshot_round_trip():
+    cfg, model = _hybrid("qwen3_next", 0)
+    eng = Engine(model, max_batch=1, max_seq_len=64)
+    seq = eng.new_sequence([5, 6, 7, 8, 9], max_new_tokens=8)
+    eng.feed_logits(seq, [5, 6, 7, 8, 9])
+    snap = eng.snapshot_state(seq)
+    a = eng.step_logits(seq, 11)
+    eng.restore_state(seq, snap)
+    seq.kv_len -= 1
+    assert torch.equal(eng.step_logits(seq, 11), a)
+    eng.release(seq)
+    dense = Engine(_models("cpu", torch.float32, None)[1], max_batch=1, max_seq_len=64)
+    s2 = dense.new_sequence([1, 2, 3], max_new_tokens=4)
+    assert dense.snapshot_state(s2) is None and not dense.kv.has_recurrent_state()
