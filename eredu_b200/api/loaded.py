@@ -47,6 +47,7 @@ class ModelLoadOptions:
     expert_cache: bool = False                   # routed experts in host memory behind a bounded device bank
     expert_cache_device_budget_bytes: Optional[int] = None   # per sparse layer; None: a quarter of the experts
     expert_cache_eviction: str = "lru"
+    embedded_mtp: bool = True                    # bind the checkpoint's own prediction layer (when it has one) as a drafter
 
 
 class LoadedModel:
@@ -145,6 +146,15 @@ class LoadedModel:
         except Exception:
             tokenizer = None
         lm = cls(model, engine, src, tokenizer, Path(path))
+        lm.mtp, lm.mtp_error = None, None
+        if src.cfg.mtp_layers > 0 and opt.embedded_mtp and (opt.parallel is None or opt.parallel.tp_size * opt.parallel.pp_size * opt.parallel.ep_size == 1) \
+                and residency is None:
+            from ..models.mtp import build_embedded_mtp
+
+            try:
+                lm.mtp = build_embedded_mtp(src.cfg, get, has, model, device, dtype, moe_factory, quantizer)
+            except (RuntimeError, KeyError, ValueError) as e:
+                lm.mtp_error = f"embedded prediction layer not loaded: {e}"     # the model itself is unaffected
         vis = src.cfg.extra.get("vision")
         if vis and src.has("model.visual.patch_embed.proj.weight") and (opt.parallel is None or opt.parallel.owns_embedding()):
             from ..models.qwen_vl import VisionConfig, VisionTower
@@ -321,12 +331,13 @@ class LoadedModel:
 
     def generate_prepared_chat(self, prepared, sampling: Optional[SamplingParams] = None, max_new_tokens: int = 256,
                                on_event=None, cancellation=None, raw: bool = False, mirostat=None, constraint=None,
-                               draft: Optional["LoadedModel"] = None, draft_tokens: int = 3):
+                               draft: Optional["LoadedModel"] = None, draft_tokens: int = 3, embedded_mtp: bool = True):
         """Generate a reply for a :class:`PreparedChat`, streaming semantic events (reasoning, text, tool-call
         start / arguments / end, finished) to ``on_event`` (``generate_prepared_chat``, api/loaded.rs:154-227).
         ``draft`` (another loaded model with the same vocabulary) turns on speculative decoding with ``draft_tokens``
         proposals per round (``generate_prepared_chat_mtp``, api/loaded.rs:238; the committed tokens are exactly those
-        plain decoding would emit). ``mirostat`` (an :class:`ops.controlled.MirostatV2`) and ``constraint`` (a :class:`GrammarConstraint`, e.g.
+        plain decoding would emit). Without a draft model, a checkpoint that carries its own prediction layer
+        (``self.mtp``) drafts for itself unless ``embedded_mtp`` is false or ``draft_tokens`` is 0. ``mirostat`` (an :class:`ops.controlled.MirostatV2`) and ``constraint`` (a :class:`GrammarConstraint`, e.g.
         from :meth:`constraint_for`) switch to the host-driven controlled sampler.
         Returns a dict with text, reasoning, tool_calls, finish_reason, token ids and timing."""
         import time
@@ -385,6 +396,13 @@ class LoadedModel:
             spec.generate([prompt_ids], sampling or SamplingParams(), max_new_tokens, eos_ids=(), on_token=on_token)
             reason = spec.last_finish_reasons[0] or FinishReason.MAX_TOKENS
             self.last_speculative_stats = spec.stats.summary()
+        elif embedded_mtp and draft_tokens > 0 and getattr(self, "mtp", None) is not None:
+            from ..runtime.speculative import EmbeddedMtpDecoder
+
+            spec = EmbeddedMtpDecoder(self.engine, self.mtp, k=draft_tokens)
+            spec.generate([prompt_ids], sampling or SamplingParams(), max_new_tokens, eos_ids=(), on_token=on_token)
+            reason = spec.last_finish_reasons[0] or FinishReason.MAX_TOKENS
+            self.last_speculative_stats = dict(spec.stats.summary(), drafter="embedded")
         else:
             self.engine.generate([prompt_ids], sampling or SamplingParams(), max_new_tokens, eos_ids=(), on_token=on_token)
             reason = self.engine.last_finish_reasons[0] or FinishReason.MAX_TOKENS

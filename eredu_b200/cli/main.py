@@ -292,6 +292,10 @@ def main(argv=None) -> int:
             dense_disk = True
             a.dense_host_lookahead = max(1, int(plan.residency.get("host_lookahead") or a.dense_host_lookahead))
             a.dense_background_queue = max(1, int(plan.residency.get("background_queue") or a.dense_background_queue))
+        if plan.drafting.get("mode") == "disabled" and a.auto_trial_plan:
+            a.mtp_draft_tokens = 0                       # a trial measures exactly its plan
+        elif plan.drafting.get("mode") == "embedded" and a.auto_trial_plan:
+            a.mtp_draft_tokens = int(plan.drafting.get("max_draft_tokens", a.mtp_draft_tokens))
         if plan.expert_cache and not expert_cache:
             expert_cache = True
             ec_budget = ec_budget or plan.expert_cache.get("device_budget_bytes")
@@ -305,6 +309,7 @@ def main(argv=None) -> int:
                                                        dense_background_queue=a.dense_background_queue,
                                                        host_budget_bytes=a.host_budget_bytes,
                                                        device_layer_window=window,
+                                                       embedded_mtp=a.mtp_draft_tokens > 0 and not a.draft_model,
                                                        expert_cache=expert_cache,
                                                        expert_cache_device_budget_bytes=ec_budget,
                                                        expert_cache_eviction=ec_eviction))
@@ -383,7 +388,8 @@ def main(argv=None) -> int:
         if draft.config.vocab_size != lm.config.vocab_size:
             raise SystemExit("--draft-model must share the target's vocabulary")
     res = lm.generate_prepared_chat(prepared, sp, a.max_tokens, on_event=on_event, raw=a.raw, mirostat=mirostat,
-                                    constraint=constraint, draft=draft, draft_tokens=a.mtp_draft_tokens)
+                                    constraint=constraint, draft=draft, draft_tokens=a.mtp_draft_tokens,
+                                    embedded_mtp=a.mtp_draft_tokens > 0)
     sys.stdout.write("\n")
     timing = dict(res["timing"], load_time=load_time)
     if a.timing or a.verbose:
@@ -420,8 +426,8 @@ def main(argv=None) -> int:
             tel.counters["weight_store"] = dict(store.diagnostics())
         if components is not None:
             tel.counters["components"] = components
-        if draft is not None:
-            tel.plan["speculative"] = getattr(lm, "last_speculative_stats", None)
+        if getattr(lm, "last_speculative_stats", None) is not None:
+            tel.plan["speculative"] = lm.last_speculative_stats
         if a.expert_cache_benchmark or a.expert_cache:
             tel.plan["expert_cache"] = [lw.moe.expert_cache.report() for lw in lm.model.layers
                                         if lw.moe is not None and getattr(lw.moe, "expert_cache", None) is not None]

@@ -113,6 +113,11 @@ class ModelConfig:
         r = int(self.head_dim * self.partial_rotary_factor)
         return r - (r % 2)
 
+    @property
+    def mtp_layers(self) -> int:
+        """Number of checkpoint-embedded next-token prediction layers (Qwen3-Next ``mtp.*``, DeepSeek-V3 layer L)."""
+        return int(self.extra.get("mtp_num_hidden_layers") or self.extra.get("num_nextn_predict_layers") or 0)
+
     def layer_is_moe(self, layer: int) -> bool:
         if self.model_type == "nemotron_h":
             return self.layer_types[layer] == "moe_only"
@@ -472,6 +477,9 @@ class ModelConfig:
                     size = int(mult * (2 * size // 3))
                     size = of * ((size + of - 1) // of)
                 cfg.intermediate_size = size
+        for key in ("mtp_num_hidden_layers", "num_nextn_predict_layers"):
+            if int(d.get(key, 0) or 0) > 0:
+                cfg.extra[key] = int(d[key])     # checkpoint-embedded prediction layers (drafting only; the decoder ignores them)
         if d.get("_language_model_prefix"):
             cfg.extra["language_model_prefix"] = True   # tensors live under model.language_model.* next to a vision tower
             if d.get("_vision", {}).get("vision_config"):

@@ -48,6 +48,9 @@ class ForwardBatch:
     deepstack: Optional[list] = None                # list of [n_vis, H]: added after layer 0, 1, ...
     rope_positions: Optional[torch.Tensor] = None   # [M] or [3, M]; None: ``positions``
     per_layer_inputs: Optional[torch.Tensor] = None  # Gemma 4: [M, layers, P], filled by the model
+    # embedded prediction heads: keep the hidden state that enters the final norm (all rows) in ``hidden_out``
+    capture_hidden: bool = False
+    hidden_out: Optional[torch.Tensor] = None
 
 
 @dataclass
@@ -277,7 +280,7 @@ class CausalLM:
         """Runs this shard's layers. Returns (h, ssq) - ssq is None unless the next consumer folds its norm."""
         fused = bool(self.layers) and self.layers[0].fold_attn and batch.token_ids.shape[0] <= self.FUSED_NORM_MAX_TOKENS
         ssq = None
-        if self.par.owns_embedding():
+        if self.par.owns_embedding() and batch.hidden_in is None:
             if fused:
                 h, ssq = ops.embedding(batch.token_ids, self.embed, 0, self.cfg.embedding_scale, want_ssq=True)
             else:
@@ -339,6 +342,8 @@ class CausalLM:
     def forward(self, batch: ForwardBatch, kv):
         """Returns fp32 logits [R, V] on the last pipeline stage, the hidden state otherwise."""
         h, ssq = self.forward_hidden(batch, kv)
+        if batch.capture_hidden:
+            batch.hidden_out = h
         if not self.par.owns_output_head():
             return h
         return self.logits(h, batch.logit_rows, ssq)

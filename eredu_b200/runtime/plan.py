@@ -362,6 +362,9 @@ class AutomaticPlanner:
         if cfg.is_moe and tp > 1:
             why.append("sparse model: experts are spread over the tensor ranks (replicated tokens, one combine + all-reduce)")
         drafting = {"mode": "disabled"}
+        if cfg.mtp_layers > 0 and tp == 1 and residency["mode"] == "fully_resident":
+            drafting = {"mode": "embedded", "max_draft_tokens": 3, "lookahead": True, "adaptive_lookahead": True}
+            why.append("the checkpoint carries its own prediction layer: it drafts 3 tokens per round")
         if draft_model:
             drafting = {"mode": "external", "model": draft_model, "placement": {"mode": "target"}, "max_draft_tokens": 4,
                         "lookahead": False, "adaptive_lookahead": False}
@@ -416,16 +419,23 @@ def candidate_plans(heuristic: ExecutionPlan, cfg: ModelConfig, profile: ModelRe
     forms.append(({"mode": "dense_disk_stream", "device_budget_bytes": device_budget, "host_budget_bytes": host_budget or None,
                    "host_lookahead": 2 if host_budget else 0, "background_queue": 2 if host_budget else 0}, True,
                   "dense layers streamed from disk"))
+    embedded = heuristic.drafting.get("mode") == "embedded" or (cfg.mtp_layers > 0 and tp == 1)
     for residency, bounded, why in forms:
         caps = {"exact_completion": True, "collectives": tp > 1, "transfers": bounded, "persistent_cache": False}
-        push(ExecutionPlan(residency=residency, required_capabilities=caps, rationale=[f"candidate: {why}"], **base))
+        variants = [(None, why)]
         if bounded and cfg.is_moe:
-            push(ExecutionPlan(residency=residency, required_capabilities=caps,
-                               expert_cache={"eviction": "lru", "device_budget_bytes": device_budget // 2},
-                               rationale=[f"candidate: {why} + expert cache"], **base))
+            variants.append(({"eviction": "lru", "device_budget_bytes": device_budget // 2}, why + " + expert cache"))
+        for ec, label in variants:
+            push(ExecutionPlan(residency=residency, required_capabilities=caps, expert_cache=ec,
+                               rationale=[f"candidate: {label}"], **base))
+            if embedded and not bounded:     # the prediction layer is bound next to fully resident weights only
+                push(ExecutionPlan(residency=residency, required_capabilities=caps, expert_cache=ec,
+                                   drafting={"mode": "embedded", "max_draft_tokens": 3, "lookahead": True,
+                                             "adaptive_lookahead": True},
+                                   rationale=[f"candidate: {label} + embedded drafting"], **base))
     h = ExecutionPlan.from_json(heuristic.to_json())
-    if h.drafting.get("mode") != "disabled":
-        h.drafting = {"mode": "disabled"}      # drafting is a separate axis: candidates compare residency forms
+    if h.drafting.get("mode") == "external":
+        h.drafting = {"mode": "disabled"}      # an external draft model is the user's choice, not a candidate axis
     push(h)
     return out
 

@@ -66,7 +66,7 @@ class SpeculativeDecoder:
         pages = np.asarray(seq.pages, dtype=np.int64)
         return pages[positions // PAGE] * PAGE + (positions % PAGE)
 
-    def _multi_token_step(self, eng: Engine, seqs, tokens: list[list[int]], all_rows: bool, uniform: bool):
+    def _multi_token_step(self, eng: Engine, seqs, tokens: list[list[int]], all_rows: bool, uniform: bool, prepare=None):
         """Feed ``tokens[i]`` to sequence i starting at its kv_len. Returns logits of every fed row (all_rows) or
         of the last row of each sequence. Uniform token counts use the split-KV decode kernel, ragged counts the
         prefill kernel (both attend to the cached prefix)."""
@@ -86,6 +86,8 @@ class SpeculativeDecoder:
         else:
             batch = ForwardBatch(is_prefill=True, cu_q=eng._t(cu.astype(np.int32), torch.int32), max_q_len=max(lens),
                                  **common)
+        if prepare is not None:
+            prepare(batch)             # embedded heads: activations instead of token embeddings, hidden-state capture
         return eng.model.forward(batch, eng.kv)
 
     def _probs_and_tokens(self, eng: Engine, logits, sps, positions, stream_ids, want_tokens=True):
@@ -130,8 +132,7 @@ class SpeculativeDecoder:
         tseqs = [self.t.new_sequence(p, sp, max_new_tokens + k + 2, eos_ids) for p in prompts]
         dseqs = [self.d.new_sequence(p, sp, max_new_tokens + k + 2, eos_ids) for p in prompts]
         try:
-            first = self.t.prefill(tseqs).tolist()
-            self.d.prefill(dseqs)  # the draft's own first sample is discarded: the target decides
+            first = self._prefill(tseqs, dseqs)
             outs: list[list[int]] = [[int(t)] for t in first]
             pending = [[int(t)] for t in first]       # committed tokens missing from the draft cache
             last = [int(t) for t in first]            # leading uncached target input
@@ -160,18 +161,18 @@ class SpeculativeDecoder:
             for s in dseqs:
                 self.d.release(s)
 
-    def _round(self, tseqs, dseqs, live, outs, pending, last, sp):
-        k = self.k
-        B = len(tseqs)
-        V = self.t.cfg.vocab_size
-        dev = self.t.device
-        sync = (lambda: torch.cuda.synchronize(dev)) if self.cuda else (lambda: None)
-        t0 = time.perf_counter()
-        # ---- draft: k proposals per sequence
+    # ---- the three places where an embedded prediction head differs from an external draft model
+    def _prefill(self, tseqs, dseqs) -> list:
+        first = self.t.prefill(tseqs).tolist()
+        self.d.prefill(dseqs)  # the draft's own first sample is discarded: the target decides
+        return first
+
+    def _propose(self, tseqs, dseqs, live, pending, sp, base):
+        """k proposals per sequence. Returns (drafted [B][k], draft distributions [k] of [B, V], context for _settle)."""
+        k, B = self.k, len(tseqs)
         drafted = [[] for _ in range(B)]
         p_d = []
         d_snaps = []                          # hybrid draft: state after each draft step
-        base = [s.kv_len + 1 for s in tseqs]  # position of the first drafted token (target kv_len = position of `last`)
         for j in range(k):
             if j == 0:
                 feed = [pending[i] for i in live]
@@ -190,12 +191,36 @@ class SpeculativeDecoder:
             p_d.append(probs)
             for b, t in enumerate(toks.tolist()):
                 drafted[b].append(int(t))
+        return drafted, p_d, d_snaps
+
+    def _verify_forward(self, tseqs, feed):
+        return self._multi_token_step(self.t, tseqs, feed, all_rows=True, uniform=True)  # [B*(k+1), V]
+
+    def _settle(self, b, i, a, nxt, dseqs, drafted, pending, ctx):
+        """Draft-side bookkeeping of sequence b (request i) after ``a`` proposals were accepted and ``nxt`` ended the round."""
+        k = self.k
+        if self.d_hybrid:
+            self.d.restore_state(dseqs[b], ctx[min(a, k - 1)][b])
+        d_valid = dseqs[b].kv_len - (k - 1) + min(a, k - 1)   # draft cache holds last, d_1..d_{k-1}
+        dseqs[b].kv_len = d_valid
+        pending[i] = ([drafted[b][k - 1]] if a == k else []) + [nxt]
+
+    def _round(self, tseqs, dseqs, live, outs, pending, last, sp):
+        k = self.k
+        B = len(tseqs)
+        V = self.t.cfg.vocab_size
+        dev = self.t.device
+        sync = (lambda: torch.cuda.synchronize(dev)) if self.cuda else (lambda: None)
+        t0 = time.perf_counter()
+        # ---- draft: k proposals per sequence
+        base = [s.kv_len + 1 for s in tseqs]  # position of the first drafted token (target kv_len = position of `last`)
+        drafted, p_d, dctx = self._propose(tseqs, dseqs, live, pending, sp, base)
         sync()
         t1 = time.perf_counter()
         # ---- target: one pass over [last, d_1 .. d_k]
         feed = [[last[i]] + drafted[b] for b, i in enumerate(live)]
         t_snaps = [self.t.snapshot_state(s) for s in tseqs] if self.t_hybrid else None
-        logits = self._multi_token_step(self.t, tseqs, feed, all_rows=True, uniform=True)  # [B*(k+1), V]
+        logits = self._verify_forward(tseqs, feed)
         pos_rows = [base[b] + j for b in range(B) for j in range(k + 1)]
         sid_rows = [tseqs[b].seq_id for b in range(B) for _ in range(k + 1)]
         p_t, t_toks = self._probs_and_tokens(self.t, logits, [sp] * (B * (k + 1)), pos_rows, sid_rows)
@@ -228,11 +253,7 @@ class SpeculativeDecoder:
                 nxt = int(bonus[b])
             outs[i].extend(drafted[b][:a] + [nxt])
             tseqs[b].kv_len += 1 + a                      # `last` and the accepted drafts are now cached
-            if self.d_hybrid:
-                self.d.restore_state(dseqs[b], d_snaps[min(a, k - 1)][b])
-            d_valid = dseqs[b].kv_len - (k - 1) + min(a, k - 1)   # draft cache holds last, d_1..d_{k-1}
-            dseqs[b].kv_len = d_valid
-            pending[i] = ([drafted[b][k - 1]] if a == k else []) + [nxt]
+            self._settle(b, i, a, nxt, dseqs, drafted, pending, dctx)
             last[i] = nxt
             self.stats.accepted += a
             self.stats.emitted += a + 1
@@ -241,6 +262,114 @@ class SpeculativeDecoder:
         self.stats.proposed += k * B
         self.stats.draft_ms.append((t1 - t0) * 1e3)
         self.stats.verify_ms.append((t2 - t1) * 1e3)
+
+
+class EmbeddedMtpDecoder(SpeculativeDecoder):
+    """Speculative decoding with the checkpoint's own prediction layer as the drafter (``generate_prepared_chat_mtp``,
+    eredu/src/api/loaded.rs:238; executor eredu/src/backend/mlx/speculative/embedded.rs). The head model is a one-layer
+    engine next to the target; every draft row pairs a token with the hidden state of the position before it:
+
+    * prefill: the target keeps the hidden states of the prompt; the head's cache is filled from ``(h_i, t_{i+1})``;
+    * a round's first draft step feeds the accepted tokens of the previous round with the TARGET's hidden states from
+      the verify pass (the head's cache holds exact rows only), further steps chain the head's own output;
+    * the verify pass keeps its hidden states for the next round.
+
+    The head's cache entry for ``(h_i, t_{i+1})`` sits at position i, one behind the target's position of the token."""
+
+    def __init__(self, target: Engine, mtp, k: int = 3):
+        draft = Engine(mtp.model, max_batch=target.max_batch, max_seq_len=target.max_seq_len, use_cuda_graph=False)
+        super().__init__(target, draft, k)
+        self.mtp = mtp
+        self._pending_hidden: dict = {}      # target seq_id -> [len(pending), H] hidden rows that pair with `pending`
+        self._verify_hidden = None
+
+    def _capture(self, store: dict):
+        def prepare(batch):
+            batch.capture_hidden = True
+            store["batch"] = batch
+        return prepare
+
+    def _head_step(self, dseqs, tokens, hidden_rows, store, uniform):
+        """One pass of the head over ``tokens`` paired with ``hidden_rows`` (flat, same order). Logits of the last row of
+        every sequence; the head's output hidden states land in ``store``."""
+        def prepare(batch):
+            batch.hidden_in = self.mtp.fuse(batch.token_ids, hidden_rows)
+            batch.capture_hidden = True
+            store["batch"] = batch
+        return self._multi_token_step(self.d, dseqs, tokens, all_rows=False, uniform=uniform, prepare=prepare)
+
+    def _prefill(self, tseqs, dseqs) -> list:
+        prompts = [list(s.prompt) for s in tseqs]
+        cap: dict = {}
+        logits = self._multi_token_step(self.t, tseqs, prompts, all_rows=False, uniform=False, prepare=self._capture(cap))
+        hidden = cap["batch"].hidden_out
+        for s, p in zip(tseqs, prompts):
+            s.kv_len = len(p)
+        sps = [s.sampling for s in tseqs]
+        _, toks = self._probs_and_tokens(self.t, logits, sps, [len(p) for p in prompts], [s.seq_id for s in tseqs])
+        first = [int(t) for t in toks.tolist()]
+        # head cache: rows (h_i, t_{i+1}) for i < n - 1; the row (h_{n-1}, first) opens the first round
+        off, feed, rows = 0, [], []
+        for p in prompts:
+            feed.append(p[1:])
+            rows.append(hidden[off:off + len(p) - 1])
+            off += len(p)
+        if any(feed):
+            live = [i for i, f in enumerate(feed) if f]
+            self._head_step([dseqs[i] for i in live], [feed[i] for i in live], torch.cat([rows[i] for i in live]), {}, False)
+            for i in live:
+                dseqs[i].kv_len += len(feed[i])
+        off = 0
+        for s, p in zip(tseqs, prompts):
+            off += len(p)
+            self._pending_hidden[s.seq_id] = hidden[off - 1:off].clone()
+        return first
+
+    def _propose(self, tseqs, dseqs, live, pending, sp, base):
+        k, B = self.k, len(tseqs)
+        drafted = [[] for _ in range(B)]
+        p_d = []
+        chain = None
+        for j in range(k):
+            store: dict = {}
+            if j == 0:
+                feed = [pending[i] for i in live]
+                rows = torch.cat([self._pending_hidden[s.seq_id] for s in tseqs])
+                logits = self._head_step(dseqs, feed, rows, store, uniform=False)
+                for s, f in zip(dseqs, feed):
+                    s.kv_len += len(f)
+                ends = np.cumsum([len(f) for f in feed]) - 1
+                chain = store["batch"].hidden_out.index_select(0, self.d._t(ends.astype(np.int64), torch.int64))
+            else:
+                feed = [[drafted[b][-1]] for b in range(B)]
+                logits = self._head_step(dseqs, feed, chain, store, uniform=True)
+                for s in dseqs:
+                    s.kv_len += 1
+                chain = store["batch"].hidden_out
+            probs, toks = self._probs_and_tokens(self.d, logits, [sp] * B, [base[b] + j for b in range(B)],
+                                                 [s.seq_id for s in tseqs])
+            p_d.append(probs)
+            for b, t in enumerate(toks.tolist()):
+                drafted[b].append(int(t))
+        # the head's cache is exact up to the row that paired with the newest committed token; later rows were made from
+        # chained hidden states and are rewritten from the target's after the verify pass
+        return drafted, p_d, [s.kv_len - (k - 1) for s in dseqs]
+
+    def _verify_forward(self, tseqs, feed):
+        cap: dict = {}
+        logits = self._multi_token_step(self.t, tseqs, feed, all_rows=True, uniform=True, prepare=self._capture(cap))
+        self._verify_hidden = cap["batch"].hidden_out.view(len(tseqs), self.k + 1, -1)
+        return logits
+
+    def _settle(self, b, i, a, nxt, dseqs, drafted, pending, ctx):
+        dseqs[b].kv_len = ctx[b]
+        pending[i] = drafted[b][:a] + [nxt]
+        # row j of the verify pass is the hidden state behind its (j+1)-th output: d_1 pairs with row 0, ..., nxt with row a
+        self._pending_hidden[self._seq_ids[b]] = self._verify_hidden[b, :a + 1].clone()
+
+    def _round(self, tseqs, dseqs, live, outs, pending, last, sp):
+        self._seq_ids = [s.seq_id for s in tseqs]
+        super()._round(tseqs, dseqs, live, outs, pending, last, sp)
 
 
 class GraphSpeculativeDecoder(SpeculativeDecoder):

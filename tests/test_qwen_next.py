@@ -124,8 +124,7 @@ def test_guards():
     sd = state_for(cfg)
     model = build_from_tensors(cfg, sd.__getitem__, sd.__contains__, "cpu", torch.float32, moe_factory=make_moe_factory())
     eng = Engine(model, max_batch=1, max_seq_len=32, num_pages=64)       # more pages than state slots (8)
-    with pytest.raises(NotImplementedError):
-        SpeculativeDecoder(eng, eng, 2)
+    assert SpeculativeDecoder(eng, eng, 2).t_hybrid                        # hybrids speculate through state snapshots
     seqs = [eng.new_sequence([1, 2, 3], max_new_tokens=2) for _ in range(8)]
     free = eng.kv.allocator.free_pages()
     with pytest.raises(RuntimeError, match="state slot"):
