@@ -34,7 +34,7 @@ class ParserPlan:
     tool_open: Optional[str] = None          # e.g. "<tool_call>"
     tool_close: Optional[str] = None
     allow_unparsed_reasoning: bool = False
-    dialect: str = "generic"                 # generic | lfm2 (Python-style call lists) | harmony (GPT-OSS channels)
+    dialect: str = "generic"                 # generic | lfm2 | harmony | gemma | inkling | atem (text/dialects.py)
     render_special_tokens: bool = False      # the structural tags are special tokens: the detokeniser must show them
 
 
@@ -81,9 +81,25 @@ def detect_plan(template: str, rendered: str, tools, thinking: str = "auto", all
         plan.starts_in_reasoning = tail.rstrip().endswith("<think>")
     if thinking == "off":
         plan.starts_in_reasoning = False
+    if "<|message_model|>" in template and "<|content_text|>" in template:
+        plan.dialect, plan.render_special_tokens = "inkling", True
+        return plan
+    if "<|eom|>" in template and "<|eot|>" in template and "<|message|>" in template:
+        plan.dialect, plan.render_special_tokens = "atem", True
+        return plan
     if "<|channel|>" in template and "<|message|>" in template:
         # Harmony (GPT-OSS): channels carry reasoning, reply and tool calls; the dialect parser owns all of it
         plan.dialect, plan.render_special_tokens = "harmony", True
+        return plan
+    if "<|channel>" in template or "<|tool_call>" in template:
+        # Gemma 4: thought channel and structural-object tool calls, all tags are special tokens
+        from .dialects import GEMMA_CHANNEL_CLOSE, GEMMA_CHANNEL_OPEN, GEMMA_TOOL_CLOSE, GEMMA_TOOL_OPEN
+
+        plan.dialect, plan.render_special_tokens = "gemma", True
+        plan.reasoning_open, plan.reasoning_close = GEMMA_CHANNEL_OPEN + "thought\n", GEMMA_CHANNEL_CLOSE
+        plan.starts_in_reasoning = rendered.rstrip(" ").endswith(plan.reasoning_open) and thinking != "off"
+        if tools:
+            plan.tool_open, plan.tool_close = GEMMA_TOOL_OPEN, GEMMA_TOOL_CLOSE
         return plan
     if "<|tool_call_start|>" in template:
         plan.dialect, plan.render_special_tokens = "lfm2", True
@@ -115,5 +131,10 @@ def prepare_chat(messages: list, template: Optional[str] = None, bos_token: str 
     prompt = render_template(template, messages, tools=use_tools, add_generation_prompt=True, bos_token=bos_token or "",
                              eos_token=eos_token or "", **kwargs)
     plan = detect_plan(template, prompt, use_tools, thinking, allow_unparsed_reasoning)
-    return PreparedChat(prompt=prompt, plan=plan, stop=list(stop or []), tools=use_tools, tool_choice=tool_choice,
+    stops = list(stop or [])
+    if plan.dialect == "gemma":
+        from .dialects import GEMMA_STOPS
+
+        stops += [s for s in GEMMA_STOPS if s not in stops]
+    return PreparedChat(prompt=prompt, plan=plan, stop=stops, tools=use_tools, tool_choice=tool_choice,
                         template_signature=hashlib.sha256(template.encode()).hexdigest()[:16])

@@ -8,7 +8,20 @@
   (tool call issued). The ``analysis`` channel is reasoning, ``final`` is the reply, ``commentary`` addressed to
   ``functions.NAME`` is a tool call whose body is the JSON arguments (eredu/src/runtime/chat/harmony.rs).
 
-Both parsers keep the interface of :class:`eredu_b200.runtime.streaming.CommittedTokenPipeline` (``push`` /
+* Gemma 4: reasoning travels in ``<|channel>thought\n ... <channel|>``, a tool call is ``<|tool_call>call:NAME{key:value,
+  ...}<tool_call|>`` - an object with bare keys whose strings are delimited by the ``<|"|>`` token; ``<|tool_response>`` and
+  ``<turn|>`` end the turn (eredu/src/runtime/chat/gemma.rs:14-20, eredu/src/runtime/chat/mod.rs:982-1022).
+
+* Inkling: every model message is ``<|message_model|>`` + a content marker + body + ``<|end_message|>``; the marker is
+  ``<|content_thinking|>`` (reasoning), ``<|content_text|>`` (reply) or, after the tool's name,
+  ``<|content_invoke_tool_json|>`` with a ``{"name", "args"}`` object; ``<|content_model_end_sampling|>`` ends the turn
+  (eredu/src/runtime/chat/inkling.rs:17-22).
+* ATEM (Muse-Glimmer): messages are ``<|start|>HEADER<|message|>BODY`` closed by ``<|eom|>`` (more follow) or ``<|eot|>``
+  (turn over); the header's ``to=`` names the recipient: ``self`` is reasoning, ``user`` the reply, anything else a tool
+  whose body is ``<atem:function_calls><atem:invoke name=".."><atem:parameter name="..">VALUE</atem:parameter>..``
+  (eredu/src/runtime/chat/atem.rs:15-18).
+
+All parsers keep the interface of :class:`eredu_b200.runtime.streaming.CommittedTokenPipeline` (``push`` /
 ``finish`` / ``text_out`` / ``reasoning_out`` / ``tool_calls`` / ``finished``) and need the detokeniser to render
 special tokens.
 """
@@ -130,6 +143,139 @@ class Lfm2Pipeline(CommittedTokenPipeline):
                 self._emit(SemanticEvent("tool_call_start", tool_index=first + j), out)
             self.tool_calls.append({"name": c["name"], "arguments": c["arguments"], "raw": raw})
             self._emit(SemanticEvent("tool_call_end", tool_name=c["name"], tool_index=first + j, arguments=c["arguments"]), out)
+        self.state = "text"
+        self._retarget()
+
+
+GEMMA_CHANNEL_OPEN, GEMMA_CHANNEL_CLOSE = "<|channel>", "<channel|>"
+GEMMA_TOOL_OPEN, GEMMA_TOOL_CLOSE = "<|tool_call>", "<tool_call|>"
+GEMMA_STRING = '<|"|>'
+GEMMA_STOPS = ("<|tool_response>", "<turn|>")
+
+
+def parse_structural_object(text: str, string_delimiter: str = GEMMA_STRING):
+    """``{count:2,enabled:true,place:<|"|>Bogota<|"|>,tags:[<|"|>a<|"|>]}`` -> Python value. Keys are bare (up to the
+    colon), strings sit between two delimiter tokens and are taken verbatim, scalars are JSON scalars; duplicate keys and
+    trailing text are errors."""
+    pos = 0
+    n = len(text)
+
+    def ws():
+        nonlocal pos
+        while pos < n and text[pos].isspace():
+            pos += 1
+
+    def value():
+        nonlocal pos
+        ws()
+        if text.startswith(string_delimiter, pos):
+            end = text.find(string_delimiter, pos + len(string_delimiter))
+            if end < 0:
+                raise ValueError("unterminated string")
+            out = text[pos + len(string_delimiter):end]
+            pos = end + len(string_delimiter)
+            return out
+        if pos < n and text[pos] == "{":
+            return obj()
+        if pos < n and text[pos] == "[":
+            pos += 1
+            items = []
+            ws()
+            if pos < n and text[pos] == "]":
+                pos += 1
+                return items
+            while True:
+                items.append(value())
+                ws()
+                if pos < n and text[pos] == ",":
+                    pos += 1
+                    continue
+                if pos < n and text[pos] == "]":
+                    pos += 1
+                    return items
+                raise ValueError("expected ',' or ']' in array")
+        start = pos
+        while pos < n and text[pos] not in ",}]" and not text[pos].isspace():
+            pos += 1
+        raw = text[start:pos]
+        try:
+            val = json.loads(raw)
+        except json.JSONDecodeError:
+            raise ValueError(f"invalid scalar {raw!r}") from None
+        if isinstance(val, (dict, list, str)):
+            raise ValueError(f"invalid scalar {raw!r}")
+        return val
+
+    def obj():
+        nonlocal pos
+        ws()
+        if pos >= n or text[pos] != "{":
+            raise ValueError("expected '{'")
+        pos += 1
+        out: dict = {}
+        ws()
+        if pos < n and text[pos] == "}":
+            pos += 1
+            return out
+        while True:
+            ws()
+            colon = text.find(":", pos)
+            if colon < 0:
+                raise ValueError("expected ':' after a key")
+            key = text[pos:colon].strip()
+            if not key or any(c in key for c in "{}[],") or string_delimiter in key:
+                raise ValueError(f"invalid key {key!r}")
+            if key in out:
+                raise ValueError(f"duplicate key {key!r}")
+            pos = colon + 1
+            out[key] = value()
+            ws()
+            if pos < n and text[pos] == ",":
+                pos += 1
+                continue
+            if pos < n and text[pos] == "}":
+                pos += 1
+                return out
+            raise ValueError("expected ',' or '}' in object")
+
+    result = obj()
+    ws()
+    if pos != n:
+        raise ValueError("text after the object")
+    return result
+
+
+def parse_gemma_call(raw: str) -> dict:
+    """``call:NAME{...}`` -> ``{"name": NAME, "arguments": {...}}``."""
+    body = raw.strip()
+    if not body.startswith("call:"):
+        raise ValueError("a Gemma tool call starts with 'call:'")
+    brace = body.find("{")
+    if brace < 0:
+        raise ValueError("a Gemma tool call needs an argument object")
+    name = body[len("call:"):brace].strip()
+    if not name:
+        raise ValueError("a Gemma tool call needs a name")
+    return {"name": name, "arguments": parse_structural_object(body[brace:])}
+
+
+class GemmaPipeline(CommittedTokenPipeline):
+    """Generic pipeline (reasoning channel and call envelope come from the plan's tags) with the call payload in the
+    structural-object syntax. A channel other than ``thought`` is shown as written."""
+
+    def _tool_fragment(self, text: str, out: list):
+        self.tool_json.text += text
+        self._emit(SemanticEvent("tool_call_arguments", text, tool_index=self.tool_count - 1), out)
+
+    def _close_tool(self, out: list):
+        raw = self.tool_json.text.strip()
+        try:
+            call = parse_gemma_call(raw)
+        except ValueError:
+            call = {"name": None, "arguments": None}
+        self.tool_calls.append({"name": call["name"], "arguments": call["arguments"], "raw": raw})
+        self._emit(SemanticEvent("tool_call_end", tool_name=call["name"], tool_index=self.tool_count - 1,
+                                 arguments=call["arguments"]), out)
         self.state = "text"
         self._retarget()
 
@@ -277,7 +423,246 @@ class HarmonyPipeline:
         return out
 
 
+class _MarkerPipeline:
+    """Shared plumbing of the marker-driven dialects: the generated text is cut at a fixed set of marker strings;
+    subclasses decide what a marker means (``_marker``) and where text goes (``_content``)."""
+
+    MARKERS: tuple = ()
+
+    def __init__(self, decoder, plan=None, stop=(), on_event: Optional[Callable[[SemanticEvent], None]] = None,
+                 max_parallel_tool_calls: Optional[int] = None):
+        self.decoder, self.plan, self.on_event = decoder, plan, on_event
+        self.stop = [s for s in stop if s]
+        self.max_tools = max_parallel_tool_calls
+        self.finished: Optional[str] = None
+        self.text_out: list[str] = []
+        self.reasoning_out: list[str] = []
+        self.tool_calls: list[dict] = []
+        self.tool_count = 0
+        self.tools = None
+        self.matcher = PartialPatternBuffer(list(self.MARKERS) + self.stop)
+
+    def _emit(self, ev: SemanticEvent, out: list):
+        out.append(ev)
+        if self.on_event:
+            self.on_event(ev)
+
+    def _say(self, kind: str, text: str, out: list):
+        if not text:
+            return
+        (self.text_out if kind == "text" else self.reasoning_out).append(text)
+        self._emit(SemanticEvent(kind, text), out)
+
+    def _open_tool(self, name, out: list) -> bool:
+        if self.max_tools is not None and self.tool_count >= self.max_tools:
+            self.finished = FinishReason.GRAMMAR_COMPLETE
+            return False
+        self.tool_count += 1
+        self._emit(SemanticEvent("tool_call_start", tool_name=name, tool_index=self.tool_count - 1), out)
+        return True
+
+    def _end_tool(self, name, args, raw: str, out: list):
+        self.tool_calls.append({"name": name, "arguments": args, "raw": raw})
+        self._emit(SemanticEvent("tool_call_end", tool_name=name, tool_index=self.tool_count - 1, arguments=args), out)
+
+    def _feed(self, text: str, out: list):
+        while text and not self.finished:
+            released, hit = self.matcher.push(text)
+            text = ""
+            self._content(released, out)
+            if hit is None:
+                return
+            if hit in self.stop and hit not in self.MARKERS:
+                if self._stop_allowed():
+                    self.finished = FinishReason.STOP_SEQUENCE
+                    return
+                self._content(hit, out)
+            else:
+                self._marker(hit, out)
+            text = self.matcher.flush()
+
+    def _stop_allowed(self) -> bool:
+        return True
+
+    def push(self, token_id: int) -> list:
+        out: list = []
+        if not self.finished:
+            self._feed(self.decoder.push(token_id), out)
+        return out
+
+    def finish(self, reason: str) -> list:
+        out: list = []
+        if not self.finished:
+            tail = self.decoder.flush()
+            if tail:
+                self._feed(tail, out)
+        if not self.finished:
+            self._content(self.matcher.flush(), out)
+            self._close(out)
+        final = FinishReason.resolve([self.finished, reason]) if reason != FinishReason.CANCELLED else (self.finished or reason)
+        self.finished = final
+        self._emit(SemanticEvent("finished", finish_reason=final), out)
+        return out
+
+    def _close(self, out: list):
+        pass
+
+
+INK_MESSAGE, INK_TEXT, INK_THINKING = "<|message_model|>", "<|content_text|>", "<|content_thinking|>"
+INK_TOOL, INK_END, INK_END_SAMPLING = "<|content_invoke_tool_json|>", "<|end_message|>", "<|content_model_end_sampling|>"
+
+
+class InklingPipeline(_MarkerPipeline):
+    """The prompt ends with ``<|message_model|>``, so parsing starts in a message header (where a tool's name may stand)."""
+
+    MARKERS = (INK_MESSAGE, INK_TEXT, INK_THINKING, INK_TOOL, INK_END, INK_END_SAMPLING)
+
+    def __init__(self, *a, **kw):
+        super().__init__(*a, **kw)
+        self.state = "header"          # header | text | thinking | tool | between
+        self.header = ""
+        self.body = ""
+
+    def _content(self, text: str, out: list):
+        if not text:
+            return
+        if self.state == "header":
+            self.header += text
+        elif self.state == "text":
+            self._say("text", text, out)
+        elif self.state == "thinking":
+            self._say("reasoning", text, out)
+        elif self.state == "tool":
+            self.body += text
+            self._emit(SemanticEvent("tool_call_arguments", text, tool_index=self.tool_count - 1), out)
+
+    def _marker(self, m: str, out: list):
+        if m == INK_MESSAGE and self.state == "between":
+            self.state, self.header = "header", ""
+        elif m in (INK_TEXT, INK_THINKING) and self.state == "header":
+            self.state = "text" if m == INK_TEXT else "thinking"
+        elif m == INK_TOOL and self.state == "header":
+            if self._open_tool(self.header.strip() or None, out):
+                self.state, self.body = "tool", ""
+        elif m == INK_END and self.state in ("text", "thinking", "tool"):
+            if self.state == "tool":
+                self._finish_call(out)
+            self.state = "between"
+        elif m == INK_END_SAMPLING and self.state == "between":
+            self.finished = FinishReason.STOP_SEQUENCE
+        else:                           # a marker where the protocol has none: shown as written, never a state change
+            self._content(m, out)
+
+    def _finish_call(self, out: list):
+        raw = self.body.strip()
+        name, args = self.header.strip() or None, None
+        try:
+            obj = json.loads(raw)
+            if isinstance(obj, dict):
+                name = obj.get("name", name)
+                args = obj.get("args", obj.get("arguments"))
+        except json.JSONDecodeError:
+            pass
+        self._end_tool(name, args, raw, out)
+
+    def _close(self, out: list):
+        if self.state == "tool":
+            self._finish_call(out)
+
+
+ATEM_START, ATEM_MESSAGE, ATEM_EOM, ATEM_EOT = "<|start|>", "<|message|>", "<|eom|>", "<|eot|>"
+_ATEM_INVOKE = re.compile(r'<atem:invoke\s+name="([^"]*)"\s*>(.*?)</atem:invoke>', re.S)
+_ATEM_PARAM = re.compile(r'<atem:parameter\s+name="([^"]*)"\s*>(.*?)</atem:parameter>', re.S)
+
+
+def parse_atem_calls(body: str, tools=None) -> list[dict]:
+    """``<atem:function_calls>`` envelope -> calls. Values are XML-escaped text; a value becomes a JSON scalar / array /
+    object when it parses as one, unless the tool declares the parameter as a string."""
+    from xml.sax.saxutils import unescape
+
+    schemas = {}
+    for t in tools or []:
+        f = t.get("function", t)
+        schemas[f.get("name")] = (f.get("parameters") or {}).get("properties", {})
+    calls = []
+    for name, inner in _ATEM_INVOKE.findall(body):
+        name = unescape(name, {"&quot;": '"'})
+        props = schemas.get(name, {})
+        args = {}
+        for key, val in _ATEM_PARAM.findall(inner):
+            key, val = unescape(key, {"&quot;": '"'}), unescape(val, {"&quot;": '"', "&apos;": "'"})
+            if (props.get(key) or {}).get("type") == "string":
+                args[key] = val
+                continue
+            try:
+                args[key] = json.loads(val)
+            except json.JSONDecodeError:
+                args[key] = val
+        calls.append({"name": name, "arguments": args})
+    if not calls:
+        raise ValueError("no <atem:invoke> element found")
+    return calls
+
+
+class AtemPipeline(_MarkerPipeline):
+    """The prompt ends inside the assistant's header (after ``<|start|>assistant`` or just ``<|start|>``)."""
+
+    MARKERS = (ATEM_START, ATEM_MESSAGE, ATEM_EOM, ATEM_EOT)
+
+    def __init__(self, *a, **kw):
+        super().__init__(*a, **kw)
+        self.state = "header"          # header | body | between
+        self.header = ""
+        self.recipient = None
+        self.body = ""
+
+    def _content(self, text: str, out: list):
+        if not text:
+            return
+        if self.state == "header":
+            self.header += text
+        elif self.state == "body":
+            if self.recipient == "self":
+                self._say("reasoning", text, out)
+            elif self.recipient in (None, "user"):
+                self._say("text", text, out)
+            else:
+                self.body += text
+                self._emit(SemanticEvent("tool_call_arguments", text, tool_index=self.tool_count - 1), out)
+
+    def _marker(self, m: str, out: list):
+        if m == ATEM_MESSAGE and self.state == "header":
+            found = _RECIPIENT.search(self.header)
+            self.recipient = found.group(1) if found else None
+            self.state, self.body = "body", ""
+            if self.recipient not in (None, "self", "user") and not self._open_tool(self.recipient, out):
+                return
+        elif m in (ATEM_EOM, ATEM_EOT) and self.state == "body":
+            self._close(out)
+            self.state = "between"
+            if m == ATEM_EOT:
+                self.finished = FinishReason.EOS
+        elif m == ATEM_START and self.state == "between":
+            self.state, self.header = "header", ""
+        else:
+            self._content(m, out)
+
+    def _close(self, out: list):
+        if self.state != "body" or self.recipient in (None, "self", "user"):
+            return
+        raw = self.body.strip()
+        try:
+            calls = parse_atem_calls(raw, self.tools)
+        except ValueError:
+            calls = [{"name": self.recipient, "arguments": None}]
+        for j, c in enumerate(calls):
+            if j > 0 and not self._open_tool(c["name"], out):
+                break
+            self._end_tool(c["name"], c["arguments"], raw, out)
+
+
 def pipeline_for(plan) -> type:
     """Pipeline class for a parser plan's dialect."""
     dialect = getattr(plan, "dialect", "generic") if plan is not None else "generic"
-    return {"lfm2": Lfm2Pipeline, "harmony": HarmonyPipeline}.get(dialect, CommittedTokenPipeline)
+    return {"lfm2": Lfm2Pipeline, "harmony": HarmonyPipeline, "gemma": GemmaPipeline, "inkling": InklingPipeline,
+            "atem": AtemPipeline}.get(dialect, CommittedTokenPipeline)

@@ -119,3 +119,95 @@ def test_qwen_tagged_parameter_calls():
     pipe.finish(FinishReason.EOS)
     assert "".join(pipe.text_out) == "I will write it."
     assert pipe.tool_calls[0]["name"] == "write_file" and pipe.tool_calls[0]["arguments"]["mode"] == 420
+
+
+def test_gemma_channels_and_structural_object_calls():
+    from eredu_b200.text.chat import prepare_chat
+    from eredu_b200.text.dialects import GemmaPipeline, parse_gemma_call, parse_structural_object
+
+    assert parse_structural_object('{count:2,enabled:true,place:<|"|>Bogotá<|"|>,tags:[<|"|>東京<|"|>,<|"|>quote: " and slash \\\\<|"|>]}') == \
+        {"count": 2, "enabled": True, "place": "Bogotá", "tags": ["東京", 'quote: " and slash \\\\']}
+    assert parse_structural_object("{}") == {} and parse_structural_object('{ a : { b : [ ] , c : null } , d : -1.5e3 }') == \
+        {"a": {"b": [], "c": None}, "d": -1500.0}
+    for bad in ('{a:1,a:2}', '{a:<|"|>open}', '{a:1} x', '{a:one}', '{:1}', '[1]', '{a:1,}'):
+        with pytest.raises(ValueError):
+            parse_structural_object(bad)
+    assert parse_gemma_call('call:lookup-place{count:1}') == {"name": "lookup-place", "arguments": {"count": 1}}
+    for bad in ('lookup{a:1}', 'call:{a:1}', 'call:name'):
+        with pytest.raises(ValueError):
+            parse_gemma_call(bad)
+
+    template = "{{ bos_token }}{% for m in messages %}<|turn>{{ m.role }}\n{{ m.content }}<turn|>{% endfor %}<|turn>model\n{# <|channel> <|tool_call> #}"
+    tools = [{"type": "function", "function": {"name": "lookup-place", "parameters": {"type": "object", "properties": {}}}}]
+    prepared = prepare_chat([{"role": "user", "content": "hi"}], template, tools=tools)
+    plan = prepared.plan
+    assert plan.dialect == "gemma" and plan.render_special_tokens and pipeline_for(plan) is GemmaPipeline
+    assert plan.reasoning_open == "<|channel>thought\n" and plan.tool_open == "<|tool_call>" and "<turn|>" in prepared.stop
+    text = ('<|channel>thought\nNeed 🦀 context<channel|>Checking.'
+            '<|tool_call>call:lookup-place{count:2,enabled:true,place:<|"|>Bogotá<|"|>}<tool_call|>'
+            '<|tool_call>call:lookup-place{count:1,enabled:false,place:<|"|>東京<|"|>}<tool_call|><|tool_response>ignored')
+    for chunk in (1, 3, 7, 1000):
+        pipe, events = run(GemmaPipeline, plan, text, chunk=chunk, stop=prepared.stop)
+        assert "".join(pipe.reasoning_out) == "Need 🦀 context" and "".join(pipe.text_out) == "Checking."
+        assert [(c["name"], c["arguments"]) for c in pipe.tool_calls] == [
+            ("lookup-place", {"count": 2, "enabled": True, "place": "Bogotá"}),
+            ("lookup-place", {"count": 1, "enabled": False, "place": "東京"})]
+        assert pipe.finished == FinishReason.STOP_SEQUENCE
+        assert [e.kind for e in events if e.kind.startswith("tool_call_")].count("tool_call_end") == 2
+    # without tools the call tags are plain text; thinking off never starts inside the channel
+    quiet = prepare_chat([{"role": "user", "content": "hi"}], template, thinking="off").plan
+    assert quiet.dialect == "gemma" and quiet.tool_open is None and not quiet.starts_in_reasoning
+    pipe, _ = run(GemmaPipeline, plan, "<|tool_call>call:broken{a:<tool_call|>")
+    assert pipe.tool_calls[0]["name"] is None and pipe.tool_calls[0]["raw"] == "call:broken{a:"
+
+
+def test_inkling_messages():
+    from eredu_b200.text.dialects import InklingPipeline
+
+    plan = detect_plan("...<|message_model|>...<|content_text|>...", "", tools=None)
+    assert plan.dialect == "inkling" and pipeline_for(plan) is InklingPipeline and plan.render_special_tokens
+    text = ("<|content_thinking|>check both values, literally<|end_message|><|message_model|><|content_text|>I'll look them up."
+            "<|end_message|>"
+            '<|message_model|>lookup<|content_invoke_tool_json|>{"name":"lookup","args":{"value":7}}<|end_message|>'
+            '<|message_model|>lookup<|content_invoke_tool_json|>{"name":"lookup","args":{"value":11}}<|end_message|>'
+            "<|content_model_end_sampling|>never shown")
+    for chunk in (1, 4, 9, 1000):
+        pipe, events = run(InklingPipeline, plan, text, chunk=chunk)
+        assert "".join(pipe.reasoning_out) == "check both values, literally" and "".join(pipe.text_out) == "I'll look them up."
+        assert [(c["name"], c["arguments"]) for c in pipe.tool_calls] == [("lookup", {"value": 7}), ("lookup", {"value": 11})]
+        assert pipe.finished == FinishReason.STOP_SEQUENCE
+        kinds = [e.kind for e in events]
+        assert kinds.count("tool_call_start") == 2 and kinds[-1] == "finished"
+    # a token limit inside the thinking message keeps what was produced
+    pipe, _ = run(InklingPipeline, plan, "<|content_thinking|>partial thought", reason=FinishReason.MAX_TOKENS)
+    assert "".join(pipe.reasoning_out) == "partial thought" and pipe.finished == FinishReason.MAX_TOKENS
+    # a content marker inside a body is not a transition
+    pipe, _ = run(InklingPipeline, plan, "<|content_thinking|>a<|content_text|>b<|end_message|>")
+    assert "".join(pipe.reasoning_out) == "a<|content_text|>b"
+    pipe, _ = run(InklingPipeline, plan, "<|content_text|>x<|end_message|>" + "<|message_model|>t<|content_invoke_tool_json|>{}<|end_message|>" * 3,
+                  max_tools=2)
+    assert len(pipe.tool_calls) == 2 and pipe.finished == FinishReason.GRAMMAR_COMPLETE
+
+
+def test_atem_messages():
+    from eredu_b200.text.dialects import AtemPipeline, parse_atem_calls
+
+    plan = detect_plan("<|start|>..<|message|>..<|eom|>..<|eot|>", "", tools=None)
+    assert plan.dialect == "atem" and pipeline_for(plan) is AtemPipeline
+    envelope = ('<atem:function_calls>\n<atem:invoke name="weather.lookup">\n<atem:parameter name="days">3</atem:parameter>\n'
+                '<atem:parameter name="units">metric &amp; SI</atem:parameter>\n</atem:invoke>\n</atem:function_calls>')
+    assert parse_atem_calls(envelope) == [{"name": "weather.lookup", "arguments": {"days": 3, "units": "metric & SI"}}]
+    typed = [{"function": {"name": "weather.lookup", "parameters": {"properties": {"days": {"type": "string"}}}}}]
+    assert parse_atem_calls(envelope, typed)[0]["arguments"]["days"] == "3"
+    with pytest.raises(ValueError):
+        parse_atem_calls("<atem:function_calls></atem:function_calls>")
+    text = " to=self<|message|>reason<|eom|><|start|>assistant to=weather.lookup<|message|>" + envelope + "<|eot|>trailing"
+    for chunk in (1, 5, 1000):
+        pipe, events = run(AtemPipeline, plan, text, chunk=chunk)
+        assert "".join(pipe.reasoning_out) == "reason" and not pipe.text_out
+        assert pipe.tool_calls == [{"name": "weather.lookup", "arguments": {"days": 3, "units": "metric & SI"}, "raw": envelope}]
+        assert pipe.finished == FinishReason.EOS
+    pipe, _ = run(AtemPipeline, plan, " to=user<|message|>direct answer<|eot|>")
+    assert "".join(pipe.text_out) == "direct answer" and not pipe.tool_calls
+    pipe, _ = run(AtemPipeline, plan, " to=self<|message|>think<|eom|><|start|>assistant to=user<|message|>hello", reason=FinishReason.MAX_TOKENS)
+    assert "".join(pipe.reasoning_out) == "think" and "".join(pipe.text_out) == "hello" and pipe.finished == FinishReason.MAX_TOKENS
