@@ -6,6 +6,10 @@ runtime/cache/residency.rs:60-135 options; block store, tiers, transfer stream, 
 accounting of eredu-core/src/cache.rs:48-450 (device / host / transfer byte reservations) and cache/storage.rs (the
 device <-> host phase machine).
 
+With ``live_disk`` set, a third tier sits behind the host tier: when a park would exceed the host budget, the parked
+sequences that have waited longest are written to files in that directory (their host copies are dropped) and read back
+on resume (eredu-core/src/cache/storage.rs: device <-> host <-> disk phases).
+
 Unit of transfer: all pages of one sequence ("park" / "resume"). Parking gathers the sequence's pages of every layer
 into one contiguous staging tensor on the device (a single gather kernel per pool), copies it to pinned host memory
 on a transfer stream and returns the device pages to the pool; resuming allocates fresh device pages and scatters
@@ -28,6 +32,8 @@ class PagedCacheOptions:
     host_budget_bytes: Optional[int] = None
     recent_device_blocks: int = 0        # newest blocks of a parked sequence that stay on the device (0 = none)
     eviction: str = "lru"                # which running sequence is parked first under pressure: lru | largest
+    live_disk: Optional[str] = None      # directory of the disk tier behind the host tier (None: no disk tier)
+    disk_budget_bytes: Optional[int] = None
 
 
 @dataclass
@@ -39,6 +45,8 @@ class ParkedSequence:
     event: object = None                 # transfer completion (CUDA event) or None
     conv_state: object = None            # hybrid models: the short-convolution state of every conv layer [layers, hist, C]
     state_slot: int = -1                 # gated-delta models: the recurrent-state slot the sequence keeps while parked
+    disk_path: Optional[str] = None      # set while the pages live in the disk tier (k_host / v_host are None then)
+    order: int = 0                       # park order: the disk tier takes the longest-parked sequences first
 
 
 class KVHostTier:
@@ -52,7 +60,13 @@ class KVHostTier:
         self.stream = torch.cuda.Stream(device=engine.device) if self.cuda else None
         self.parked: dict[int, ParkedSequence] = {}
         self.host_bytes = 0
-        self.stats = {"parked": 0, "resumed": 0, "bytes_to_host": 0, "bytes_to_device": 0, "refused": 0}
+        self.disk_bytes = 0
+        self.stats = {"parked": 0, "resumed": 0, "bytes_to_host": 0, "bytes_to_device": 0, "refused": 0,
+                      "spilled": 0, "bytes_to_disk": 0, "bytes_from_disk": 0}
+        if self.opt.live_disk:
+            import os
+
+            os.makedirs(self.opt.live_disk, exist_ok=True)
         self._clock = 0
         self._last_use: dict[int, int] = {}
 
@@ -85,8 +99,9 @@ class KVHostTier:
         used = (seq.kv_len + PAGE - 1) // PAGE
         nbytes = used * self.page_bytes()
         if self.opt.host_budget_bytes is not None and self.host_bytes + nbytes > self.opt.host_budget_bytes:
-            self.stats["refused"] += 1
-            return False
+            if not self._spill(self.host_bytes + nbytes - self.opt.host_budget_bytes):
+                self.stats["refused"] += 1
+                return False
         dev = self.engine.device
         idx = torch.as_tensor(seq.pages[:used], dtype=torch.long, device=dev)
         shape = (self.kv.k.shape[0], used) + tuple(self.kv.k.shape[2:])
@@ -114,8 +129,9 @@ class KVHostTier:
         conv = None
         if self.kv.conv_state is not None and seq.pages:
             conv = self.kv.conv_state[:, seq.pages[0]].to("cpu")   # the state is named by the sequence's first page
+        self._clock += 1
         self.parked[seq.seq_id] = ParkedSequence(k_host, v_host, used, len(seq.pages), event, conv,
-                                                 self.kv.detach_state(seq.pages[0]) if seq.pages else -1)
+                                                 self.kv.detach_state(seq.pages[0]) if seq.pages else -1, order=self._clock)
         self.engine.kv.allocator.release(seq.pages)
         seq.pages = []
         self.host_bytes += nbytes
@@ -130,6 +146,9 @@ class KVHostTier:
         if p is None:
             return True
         if self.kv.allocator.free_pages() < p.reserved_pages:
+            self.stats["refused"] += 1
+            return False
+        if p.disk_path is not None and not self._unspill(p):
             self.stats["refused"] += 1
             return False
         pages = list(self.kv.allocator.alloc(p.reserved_pages))
@@ -167,9 +186,76 @@ class KVHostTier:
         """Forget a parked sequence (cancelled while parked)."""
         p = self.parked.pop(seq.seq_id, None)
         if p is not None:
-            self.host_bytes -= p.pages * self.page_bytes()
+            if p.disk_path is not None:
+                self.disk_bytes -= p.pages * self.page_bytes()
+                self._remove(p.disk_path)
+            else:
+                self.host_bytes -= p.pages * self.page_bytes()
             self.kv.free_state_slot(p.state_slot)
 
+    # ------------------------------------------------------------------------------------------ disk tier
+    @staticmethod
+    def _remove(path: str) -> None:
+        import os
+
+        try:
+            os.remove(path)
+        except OSError:
+            pass
+
+    def _spill(self, need: int) -> bool:
+        """Move host copies to the disk tier, longest-parked first, until ``need`` bytes are free. False when there is no
+        disk tier, its budget is too small, or the host tier holds too little to spill (nothing is left half-moved)."""
+        if not self.opt.live_disk:
+            return False
+        import os
+
+        order = sorted((p for p in self.parked.values() if p.disk_path is None and p.pages), key=lambda p: p.order)
+        plan, freed = [], 0
+        for p in order:
+            if freed >= need:
+                break
+            plan.append(p)
+            freed += p.pages * self.page_bytes()
+        if freed < need:
+            return False
+        if self.opt.disk_budget_bytes is not None and self.disk_bytes + freed > self.opt.disk_budget_bytes:
+            return False
+        for p in plan:
+            if p.event is not None:
+                p.event.synchronize()                     # the device-to-host copy must have landed before it is written out
+            sid = next(k for k, v in self.parked.items() if v is p)
+            path = os.path.join(self.opt.live_disk, f"sequence-{sid}-{p.order}.kv")
+            tmp = path + ".partial"
+            torch.save({"k": p.k_host, "v": p.v_host}, tmp)
+            os.replace(tmp, path)
+            nbytes = p.pages * self.page_bytes()
+            p.k_host = p.v_host = None
+            p.event = None
+            p.disk_path = path
+            self.host_bytes -= nbytes
+            self.disk_bytes += nbytes
+            self.stats["spilled"] += 1
+            self.stats["bytes_to_disk"] += nbytes
+        return True
+
+    def _unspill(self, p: ParkedSequence) -> bool:
+        """Read a spilled sequence back into (pinned) host memory; other host copies make room through the disk tier."""
+        nbytes = p.pages * self.page_bytes()
+        if self.opt.host_budget_bytes is not None and self.host_bytes + nbytes > self.opt.host_budget_bytes:
+            if not self._spill(self.host_bytes + nbytes - self.opt.host_budget_bytes):
+                return False
+        blob = torch.load(p.disk_path, map_location="cpu")
+        p.k_host = blob["k"].pin_memory() if self.cuda else blob["k"]
+        p.v_host = blob["v"].pin_memory() if self.cuda else blob["v"]
+        self._remove(p.disk_path)
+        p.disk_path = None
+        self.disk_bytes -= nbytes
+        self.host_bytes += nbytes
+        self.stats["bytes_from_disk"] += nbytes
+        return True
+
     def report(self) -> dict:
-        return dict(self.stats, parked_now=len(self.parked), host_bytes=self.host_bytes,
+        return dict(self.stats, parked_now=len(self.parked), host_bytes=self.host_bytes, disk_bytes=self.disk_bytes,
+                    on_disk_now=sum(1 for p in self.parked.values() if p.disk_path is not None),
                     device_free_pages=self.kv.allocator.free_pages())

@@ -95,3 +95,56 @@ def test_server_parks_under_pressure_and_finishes_everything():
     assert [srv.result(i).tokens for i in ids] == want
     assert tier.report()["parked_now"] == 0 and tier.report()["resumed"] == tier.report()["parked"]
     assert eng.kv.allocator.free_pages() == eng.kv.num_pages - 1
+
+
+def test_disk_tier_behind_the_host_tier(tmp_path):
+    """With a disk directory the host budget no longer refuses a park: the longest-parked sequence moves to a file and
+    comes back bit-identically."""
+    import os
+
+    eng, cfg = make_engine()
+    g = torch.Generator().manual_seed(8)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (33, 40, 21)]
+    sp = SamplingParams(temperature=0.0)
+    want = [eng.generate([p], sp, 6)[0] for p in prompts]
+    probe = KVHostTier(eng)
+    one = 3 * probe.page_bytes()                                   # 33..40 tokens = 3 pages each, 21 tokens = 2
+    tier = KVHostTier(eng, PagedCacheOptions(host_budget_bytes=one, live_disk=str(tmp_path / "kv")))
+    seqs, firsts = [], []
+    for p in prompts:
+        s = eng.new_sequence(p, sp, max_new_tokens=8)
+        firsts.append(eng.prefill([s]))
+        seqs.append(s)
+    assert tier.park(seqs[0]) and tier.report()["on_disk_now"] == 0
+    assert tier.park(seqs[1])                                      # the budget holds one: sequence 0 goes to disk
+    r = tier.report()
+    assert r["on_disk_now"] == 1 and r["spilled"] == 1 and r["host_bytes"] <= one and r["disk_bytes"] == one
+    assert len(os.listdir(tmp_path / "kv")) == 1
+    assert tier.park(seqs[2]) and tier.report()["on_disk_now"] == 2
+    for i in (0, 2, 1):                                            # resume in another order; 0 comes back from its file
+        assert tier.resume(seqs[i])
+        out = [int(firsts[i][0])]
+        seqs[i].output.append(out[0])
+        eng.start_decode([seqs[i]], firsts[i])
+        for _ in range(5):
+            toks = eng.decode_step()
+            eng.commit(toks.tolist())
+            out.append(int(toks[0]))
+        eng._decode_state = None
+        eng.release(seqs[i])
+        assert out == want[i]
+    r = tier.report()
+    assert r["parked_now"] == 0 and r["host_bytes"] == 0 and r["disk_bytes"] == 0 and os.listdir(tmp_path / "kv") == []
+    assert r["bytes_from_disk"] == r["bytes_to_disk"] > 0
+    # a disk budget that is too small refuses like a missing tier does; dropping a spilled sequence removes its file
+    small = KVHostTier(eng, PagedCacheOptions(host_budget_bytes=one, live_disk=str(tmp_path / "kv2"), disk_budget_bytes=1))
+    a = eng.new_sequence(prompts[0], sp, max_new_tokens=4)
+    b = eng.new_sequence(prompts[1], sp, max_new_tokens=4)
+    eng.prefill([a, b])
+    assert small.park(a) and not small.park(b) and small.report()["refused"] == 1 and b.pages
+    roomy = KVHostTier(eng, PagedCacheOptions(host_budget_bytes=one, live_disk=str(tmp_path / "kv3")))
+    c = eng.new_sequence(prompts[2], sp, max_new_tokens=4)
+    eng.prefill([c])
+    assert roomy.park(b) and roomy.park(c) and len(os.listdir(tmp_path / "kv3")) == 1
+    roomy.drop(b)
+    assert os.listdir(tmp_path / "kv3") == [] and roomy.report()["disk_bytes"] == 0
