@@ -98,7 +98,7 @@ class LoadedModel:
         elif opt.weight_residency != "device":
             raise ValueError(f"unknown weight residency {opt.weight_residency!r}")
         get, has = src.get, src.has
-        if src.cfg.extra.get("language_model_prefix") and has("model.language_model.embed_tokens.weight"):
+        if has("model.language_model.embed_tokens.weight") and not has("model.embed_tokens.weight"):
             # vision-language checkpoint used as a text model: the decoder sits under model.language_model.*, the towers
             # are not loaded (requests with image / audio / video parts are refused by media.prepare_for_text_model)
             base_get, base_has = get, has

@@ -11,7 +11,7 @@ from pathlib import Path
 from typing import Any
 
 DENSE_TYPES = {"llama", "mistral", "qwen2", "qwen3", "phi3", "lfm2"}
-MOE_TYPES = {"qwen3_moe", "mixtral", "gpt_oss", "deepseek_v3", "lfm2_moe", "nemotron_h", "qwen3_next", "qwen3_5_moe"}
+MOE_TYPES = {"qwen3_moe", "mixtral", "gpt_oss", "deepseek_v3", "lfm2_moe", "nemotron_h", "qwen3_next", "qwen3_5_moe", "qwen3_5_moe_text"}
 QWEN_HYBRID_TYPES = {"qwen3_next", "qwen3_5", "qwen3_5_moe", "qwen3_5_text", "qwen3_5_moe_text"}
 
 

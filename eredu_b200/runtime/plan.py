@@ -21,7 +21,7 @@ from ..models.config import DENSE_TYPES, MOE_TYPES, ModelConfig
 
 EXECUTION_PLAN_SCHEMA_VERSION = 2
 DEFAULT_MAX_MAPPED_SHARDS = 4
-SUPPORTED_TYPES = DENSE_TYPES | {"qwen3_moe", "mixtral", "gpt_oss", "lfm2_moe", "qwen3_next", "qwen3_5_moe", "nemotron_h", "deepseek_v3", "kimi_linear", "gemma4"}
+SUPPORTED_TYPES = DENSE_TYPES | {"qwen3_moe", "mixtral", "gpt_oss", "lfm2_moe", "qwen3_next", "qwen3_5", "qwen3_5_text", "qwen3_5_moe", "qwen3_5_moe_text", "nemotron_h", "deepseek_v3", "kimi_linear", "gemma4"}
 
 
 # ---------------------------------------------------------------------------------------------- inspection
@@ -125,8 +125,12 @@ def inspect_artifact(path) -> ModelInspectionReport:
             if not k.endswith((".scales", ".biases")):
                 bits = (cfg.quantization or {}).get("bits") if (k[:-7] + ".scales") in keys and k.endswith(".weight") else None
                 rep.parameter_count += n * (32 // int(bits)) if bits else n
+        # a decoder stored next to towers (vision-language exports, Qwen3.5) sits under model.language_model.*
+        def spellings(name):
+            return (name, "model.language_model." + name[len("model."):]) if name.startswith("model.") else (name,)
+
         for alternatives in required_tensors(cfg):
-            if not any(name in keys for name in alternatives):
+            if not any(sp in keys for name in alternatives for sp in spellings(name)):
                 issues.append(InspectionIssue("missing_tensor", "error", f"required tensor {alternatives[0]} is absent"))
         if not cfg.tie_word_embeddings and "lm_head.weight" not in keys:
             issues.append(InspectionIssue("missing_tensor", "error", "untied model without lm_head.weight"))

@@ -30,6 +30,10 @@ def check(model, tmp_path, prompt_len=19, atol=2e-3, max_seq_len=64):
     prompt = torch.randint(0, vocab, (prompt_len,), generator=torch.Generator().manual_seed(2)).tolist()
     with torch.no_grad():
         ref = model(torch.tensor([prompt])).logits[0, -1].float()
+    from eredu_b200.runtime.plan import inspect_artifact
+
+    report = inspect_artifact(tmp_path)            # header-only inspection agrees that this directory can be loaded
+    assert report.is_loadable, [(i.code, i.message) for i in report.issues]
     lm = LoadedModel.load(tmp_path, ModelLoadOptions(device="cpu", max_batch=1, max_seq_len=max_seq_len))
     got = lm.prefill_logits(prompt)
     err = float((got - ref).abs().max())
@@ -132,6 +136,21 @@ def test_qwen3_next(tmp_path):
                  linear_num_value_heads=4, decoder_sparse_step=1, moe_intermediate_size=32, shared_expert_intermediate_size=48,
                  num_experts_per_tok=2, num_experts=8, norm_topk_prob=True, mlp_only_layers=[],
                  layer_types=["linear_attention", "linear_attention", "linear_attention", "full_attention"])
+    check(m, tmp_path)
+
+
+@pytest.mark.parametrize("sparse", [False, True])
+def test_qwen3_5(tmp_path, sparse):
+    """Qwen3.5: split gated-delta projections, dense or sparse feed-forward, decoder under ``model.language_model``."""
+    common = dict(vocab_size=320, hidden_size=64, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+                  max_position_embeddings=128, linear_conv_kernel_dim=4, linear_key_head_dim=16, linear_value_head_dim=8,
+                  linear_num_key_heads=2, linear_num_value_heads=4,
+                  layer_types=["linear_attention", "linear_attention", "linear_attention", "full_attention"])
+    if sparse:
+        m = hf_model("Qwen3_5MoeForCausalLM", "Qwen3_5MoeTextConfig", moe_intermediate_size=32, shared_expert_intermediate_size=48,
+                     num_experts_per_tok=2, num_experts=8, **common)
+    else:
+        m = hf_model("Qwen3_5ForCausalLM", "Qwen3_5TextConfig", intermediate_size=128, **common)
     check(m, tmp_path)
 
 
