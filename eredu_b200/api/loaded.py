@@ -162,7 +162,8 @@ class LoadedModel:
             try:
                 lm.vision = VisionTower(VisionConfig.from_dict(vis["vision_config"]), src.get, device, torch.float32
                                         if device.type == "cpu" else dtype)
-                lm.vision_tokens = {k: vis.get(k) for k in ("image_token_id", "vision_start_token_id", "vision_end_token_id")}
+                lm.vision_tokens = {k: vis.get(k) for k in ("image_token_id", "video_token_id", "vision_start_token_id",
+                                                            "vision_end_token_id")}
             except (RuntimeError, KeyError, ValueError) as e:
                 # a tower this loader cannot bind (other family, truncated export): the model stays usable for text
                 # and image parts are refused with this reason
@@ -229,25 +230,46 @@ class LoadedModel:
     vision_error: str = ""
 
     def multimodal_inputs(self, segments: list, min_pixels: int = 64 * 32 * 32, max_pixels: int = 16384 * 32 * 32,
-                          wrap: bool = True):
+                          wrap: bool = True, video_limits: Optional[dict] = None):
         """Token ids and tower features of a prompt made of text segments (``str`` or lists of token ids) and
-        ``media.RgbImage`` parts: every image becomes ``<vision_start> <image> x n <vision_end>`` and its merged patch
+        ``media.RgbImage`` / ``media.Video`` parts (``video_limits``: keyword arguments of ``video_to_patches``; a video
+        becomes one timestamped, framed placeholder run per temporal group): every image becomes ``<vision_start> <image> x n <vision_end>`` and its merged patch
         features replace the placeholder embeddings (``wrap=False``: the surrounding text, e.g. a rendered chat template,
         already carries the start / end markers and only the placeholder run is inserted).
         Returns (token_ids, multimodal dict for ``Engine.feed_logits``)."""
         from ..media import MultimodalPreparationError, RgbImage
-        from ..models.qwen_vl import image_to_patches, mrope_positions
+        from ..media.request import Video
+        from ..models.qwen_vl import image_to_patches, mrope_positions, video_to_patches
 
         if self.vision is None:
-            if any(isinstance(s, RgbImage) for s in segments):
-                raise MultimodalPreparationError("this model accepts text only; the request carries ['image']"
+            kinds = sorted({"image" if isinstance(s, RgbImage) else "video" for s in segments if isinstance(s, (RgbImage, Video))})
+            if kinds:
+                raise MultimodalPreparationError(f"this model accepts text only; the request carries {kinds}"
                                                  + (f" ({self.vision_error})" if self.vision_error else ""))
             ids = [t for s in segments for t in (self.encode(s) if isinstance(s, str) else list(s))]
             return ids, None
         vt, cfg = self.vision_tokens, self.vision.cfg
-        ids, patches, grids = [], [], []
+        ids, patches, grids = [], [], []          # grids: what the tower sees; lm_grids: one entry per placeholder run
+        lm_grids = []
         for seg in segments:
-            if isinstance(seg, RgbImage):
+            if isinstance(seg, Video):
+                # every temporal group is announced by its time and framed like an image of its own
+                if vt.get("video_token_id") is None:
+                    raise MultimodalPreparationError("this checkpoint declares no video placeholder token")
+                p, g, stamps = video_to_patches(seg, cfg, **(video_limits or {}))
+                per = (g[1] // cfg.spatial_merge_size) * (g[2] // cfg.spatial_merge_size)
+                for stamp in stamps:
+                    if self.tokenizer is not None:
+                        ids.extend(self.encode(f"<{stamp:.1f} seconds>"))
+                    if vt.get("vision_start_token_id") is not None:
+                        ids.append(int(vt["vision_start_token_id"]))
+                    ids.extend([int(vt["video_token_id"])] * per)
+                    if vt.get("vision_end_token_id") is not None:
+                        ids.append(int(vt["vision_end_token_id"]))
+                    lm_grids.append((1, g[1], g[2]))
+                patches.append(p)
+                grids.append(g)
+            elif isinstance(seg, RgbImage):
                 p, g = image_to_patches(seg, cfg, min_pixels, max_pixels)
                 n = g[0] * (g[1] // cfg.spatial_merge_size) * (g[2] // cfg.spatial_merge_size)
                 if wrap and vt.get("vision_start_token_id") is not None:
@@ -257,14 +279,15 @@ class LoadedModel:
                     ids.append(int(vt["vision_end_token_id"]))
                 patches.append(p)
                 grids.append(g)
+                lm_grids.append(g)
             else:
                 ids.extend(self.encode(seg) if isinstance(seg, str) else [int(t) for t in seg])
         if not grids:
             return ids, None
         feats, deep = self.vision.forward(torch.cat(patches, 0), grids)
-        img = int(vt["image_token_id"])
-        pos, delta = mrope_positions(ids, img, grids, cfg.spatial_merge_size)
-        rows = [i for i, t in enumerate(ids) if t == img]
+        marks = {int(vt[k]) for k in ("image_token_id", "video_token_id") if vt.get(k) is not None}
+        pos, delta = mrope_positions(ids, marks, lm_grids, cfg.spatial_merge_size)
+        rows = [i for i, t in enumerate(ids) if t in marks]
         return ids, {"rows": rows, "values": feats, "deepstack": deep, "rope_positions": pos, "rope_delta": delta}
 
     def chat_segments(self, messages: list, images: list, placeholder: str = "<|image_pad|>", **template_kwargs) -> list:

@@ -194,22 +194,50 @@ def image_to_patches(image, cfg: VisionConfig, min_pixels: int = 64 * 32 * 32, m
     return torch.from_numpy(np.ascontiguousarray(x).reshape(gh * gw, C * Tp * P * P)), (1, gh, gw)
 
 
+def video_to_patches(video, cfg: VisionConfig, target_fps: float = 2.0, min_frames: int = 4, max_frames: int = 768,
+                     min_pixels: int = 128 * 32 * 32, max_pixels: int = 768 * 32 * 32, mean=(0.5, 0.5, 0.5), std=(0.5, 0.5, 0.5)):
+    """``media.Video`` -> (patches [t * gh * gw, C * Tp * P * P] in merge-block order per temporal group, (t, gh, gw),
+    timestamps): frames are sampled uniformly at ``target_fps`` (between ``min_frames`` and ``max_frames``), padded by
+    repeating the last one to whole temporal patches, resized together (the pixel budget is per frame) and grouped
+    ``temporal_patch_size`` at a time; every group gets the mean time of its first and last frame
+    (eredu/src/backend/mlx/architectures/qwen/vl/ video preparation; runtime/media/video.rs for the sampling rules)."""
+    from ..media import rescale_and_normalize_rgb8, resize_rgb8_bicubic
+    from ..media.video import pad_frame_indices, sampled_frame_count, temporal_group_timestamps, uniform_sample_indices
+
+    P, m, Tp = cfg.patch_size, cfg.spatial_merge_size, cfg.temporal_patch_size
+    total = len(video.frames)
+    count = sampled_frame_count(total, video.fps, target_fps, min(min_frames, total), max_frames)
+    indices = pad_frame_indices(uniform_sample_indices(total, count), Tp)
+    stamps = temporal_group_timestamps(indices, video.fps, Tp)
+    first = video.frames[0]
+    H, W = smart_resize(first.height, first.width, P * m, min_pixels, max_pixels)
+    frames = np.stack([rescale_and_normalize_rgb8(resize_rgb8_bicubic(video.frames[i], W, H), 1.0 / 255.0, mean, std).data
+                       for i in indices])                                                     # [T, C, H, W]
+    t, gh, gw = len(indices) // Tp, H // P, W // P
+    C = frames.shape[1]
+    x = frames.reshape(t, Tp, C, gh // m, m, P, gw // m, m, P)
+    x = x.transpose(0, 3, 6, 4, 7, 2, 1, 5, 8)
+    return torch.from_numpy(np.ascontiguousarray(x).reshape(t * gh * gw, C * Tp * P * P)), (t, gh, gw), stamps
+
+
 # ---------------------------------------------------------------------------------------------- decoder positions
-def mrope_positions(token_ids, image_token_id: int, grids, merge: int):
-    """Three-axis (t, h, w) rotary positions of a prompt whose image placeholders are runs of ``image_token_id``:
+def mrope_positions(token_ids, image_token_id, grids, merge: int):
+    """Three-axis (t, h, w) rotary positions of a prompt whose image placeholders are runs of ``image_token_id`` (an id,
+    or several: a video contributes one (1, h, w) grid per temporal group, each a run of the video placeholder):
     text tokens advance all three axes together; an image of t x (h/merge) x (w/merge) merged tokens keeps t at the
     run's start and spreads h and w over its grid; the next text token continues after the largest position used.
     Returns (positions int64 [3, T], delta) where a later decode token at index i has position i + delta on all axes."""
     pos = torch.zeros((3, len(token_ids)), dtype=torch.int64)
     i, nxt, g = 0, 0, 0
     T = len(token_ids)
+    marks = {int(image_token_id)} if isinstance(image_token_id, int) else {int(x) for x in image_token_id}
     while i < T:
-        if token_ids[i] == image_token_id:
+        if token_ids[i] in marks:
             t, h, w = grids[g]
             g += 1
             hh, ww = h // merge, w // merge
             n = t * hh * ww
-            if token_ids[i:i + n] != [image_token_id] * n:
+            if token_ids[i:i + n] != [token_ids[i]] * n:
                 raise ValueError("image placeholder run does not match the image grid")
             tt = torch.arange(t).view(t, 1, 1).expand(t, hh, ww).reshape(-1)
             ys = torch.arange(hh).view(1, hh, 1).expand(t, hh, ww).reshape(-1)

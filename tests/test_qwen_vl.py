@@ -142,3 +142,41 @@ def test_chat_segments_cut_the_prompt_at_image_placeholders(tmp_path):
     Image.fromarray(np.full((3, 5, 3), 200, np.uint8)).save(tmp_path / "x.png")
     im = load_image(tmp_path / "x.png")
     assert (im.height, im.width) == (3, 5) and int(im.pixels[0, 0, 0]) == 200
+
+
+def test_video_prompt_matches_transformers(tmp_path):
+    """A video is sampled, padded to whole temporal patches and enters the decoder as one framed placeholder run per
+    temporal group; tower features, three-axis positions and logits agree with Transformers on the same frames."""
+    from eredu_b200.api import LoadedModel, ModelLoadOptions
+    from eredu_b200.media.request import Video
+    from eredu_b200.media import RgbImage
+    from eredu_b200.models.qwen_vl import video_to_patches
+
+    m = hf_vl()
+    m.save_pretrained(tmp_path, safe_serialization=True)
+    lm = LoadedModel.load(tmp_path, ModelLoadOptions(device="cpu", max_batch=1, max_seq_len=256))
+    assert lm.vision_tokens["video_token_id"] == 301
+    rng = np.random.default_rng(1)
+    video = Video([RgbImage(rng.integers(0, 255, (16, 16, 3), dtype=np.uint8)) for _ in range(10)], fps=4.0)
+    limits = dict(target_fps=2.0, min_frames=2, max_frames=8, min_pixels=64, max_pixels=10**6)
+    patches, grid, stamps = video_to_patches(video, lm.vision.cfg, **limits)
+    # 10 frames at 4 fps for 2 fps -> 5 sampled (0, 2, 4, 7, 9 by round-half-even), padded to 6 -> 3 temporal groups
+    assert grid == (3, 4, 4) and patches.shape == (48, 3 * 2 * 4 * 4) and len(stamps) == 3
+    assert stamps == pytest.approx([(0 + 2) / 8, (4 + 7) / 8, (9 + 9) / 8])
+    img = RgbImage(rng.integers(0, 255, (8, 8, 3), dtype=np.uint8))
+    segments = [[5, 6], video, [7], img, [8, 9]]
+    ids, mm = lm.multimodal_inputs(segments, min_pixels=64, max_pixels=10**6, video_limits=limits)
+    assert ids.count(301) == 3 * 4 and ids.count(300) == 1 and ids.count(302) == 4 and mm["values"].shape == (13, 64)
+    pi, gi = image_to_patches(img, lm.vision.cfg, 64, 10**6)
+    types = torch.tensor([[1 if t == 300 else 2 if t == 301 else 0 for t in ids]])
+    with torch.no_grad():
+        out = m(input_ids=torch.tensor([ids]), pixel_values=pi, image_grid_thw=torch.tensor([gi]), pixel_values_videos=patches,
+                video_grid_thw=torch.tensor([grid]), mm_token_type_ids=types)
+        ref_pos, ref_delta = m.model.get_rope_index(torch.tensor([ids]), image_grid_thw=torch.tensor([gi]),
+                                                    video_grid_thw=torch.tensor([grid]), mm_token_type_ids=types)
+    assert torch.equal(mm["rope_positions"], ref_pos[:, 0]) and mm["rope_delta"] == int(ref_delta)
+    seq = lm.engine.new_sequence(ids, max_new_tokens=4)
+    got = lm.engine.feed_logits(seq, ids, mm)
+    lm.engine.release(seq)
+    assert torch.allclose(got.float().cpu(), out.logits[0, -1], atol=2e-3), float((got.float().cpu() - out.logits[0, -1]).abs().max())
+    assert len(lm.generate_multimodal(segments, max_new_tokens=3, min_pixels=64, max_pixels=10**6, video_limits=limits)) >= 1
