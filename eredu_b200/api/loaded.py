@@ -156,7 +156,17 @@ class LoadedModel:
             except (RuntimeError, KeyError, ValueError) as e:
                 lm.mtp_error = f"embedded prediction layer not loaded: {e}"     # the model itself is unaffected
         vis = src.cfg.extra.get("vision")
-        if vis and src.has("model.visual.patch_embed.proj.weight") and (opt.parallel is None or opt.parallel.owns_embedding()):
+        if vis and src.cfg.model_type == "gemma4" and src.has("model.vision_tower.patch_embedder.input_proj.weight") \
+                and (opt.parallel is None or opt.parallel.owns_embedding()):
+            from ..models.gemma4_vision import Gemma4VisionConfig, Gemma4VisionTower
+
+            try:
+                lm.vision = Gemma4VisionTower(Gemma4VisionConfig.from_dict(vis["vision_config"]), src.get, src.has, device,
+                                              torch.float32 if device.type == "cpu" else dtype)
+                lm.vision_tokens = {k: vis.get(k) for k in ("image_token_id", "video_token_id", "boi_token_id", "eoi_token_id")}
+            except (RuntimeError, KeyError, ValueError) as e:
+                lm.vision, lm.vision_error = None, f"vision tower not loaded: {e}"
+        elif vis and src.has("model.visual.patch_embed.proj.weight") and (opt.parallel is None or opt.parallel.owns_embedding()):
             from ..models.qwen_vl import VisionConfig, VisionTower
 
             try:
@@ -230,7 +240,7 @@ class LoadedModel:
     vision_error: str = ""
 
     def multimodal_inputs(self, segments: list, min_pixels: int = 64 * 32 * 32, max_pixels: int = 16384 * 32 * 32,
-                          wrap: bool = True, video_limits: Optional[dict] = None):
+                          wrap: bool = True, video_limits: Optional[dict] = None, image_limits: Optional[dict] = None):
         """Token ids and tower features of a prompt made of text segments (``str`` or lists of token ids) and
         ``media.RgbImage`` / ``media.Video`` parts (``video_limits``: keyword arguments of ``video_to_patches``; a video
         becomes one timestamped, framed placeholder run per temporal group): every image becomes ``<vision_start> <image> x n <vision_end>`` and its merged patch
@@ -248,6 +258,8 @@ class LoadedModel:
                                                  + (f" ({self.vision_error})" if self.vision_error else ""))
             ids = [t for s in segments for t in (self.encode(s) if isinstance(s, str) else list(s))]
             return ids, None
+        if self.config.model_type == "gemma4":
+            return self._gemma4_inputs(segments, wrap, **(image_limits or {}))
         vt, cfg = self.vision_tokens, self.vision.cfg
         ids, patches, grids = [], [], []          # grids: what the tower sees; lm_grids: one entry per placeholder run
         lm_grids = []
@@ -289,6 +301,42 @@ class LoadedModel:
         pos, delta = mrope_positions(ids, marks, lm_grids, cfg.spatial_merge_size)
         rows = [i for i, t in enumerate(ids) if t in marks]
         return ids, {"rows": rows, "values": feats, "deepstack": deep, "rope_positions": pos, "rope_delta": delta}
+
+    def _gemma4_inputs(self, segments: list, wrap: bool, max_soft_tokens: int = 280):
+        """Gemma 4: an image is ``<boi> <image> x n <eoi>``; the placeholders are embedded as the padding token (also for the
+        per-layer inputs), their rows take the tower's soft tokens, and the soft tokens of one image form a
+        bidirectional-attention group."""
+        from ..media import MultimodalPreparationError, RgbImage
+        from ..models.gemma4_vision import image_to_patches
+
+        vt = self.vision_tokens
+        pad = int((self.config.extra.get("gemma4") or {}).get("pad_token_id") or 0)
+        ids, rows, groups, feats = [], [], [], []
+        for seg in segments:
+            if isinstance(seg, RgbImage):
+                patches, pos, n = image_to_patches(seg, self.vision.cfg, max_soft_tokens)
+                soft = self.vision.forward(patches, pos)
+                if wrap and vt.get("boi_token_id") is not None:
+                    ids.append(int(vt["boi_token_id"]))
+                    groups.append(-1)
+                rows.extend(range(len(ids), len(ids) + n))
+                ids.extend([pad] * n)
+                groups.extend([len(feats)] * n)
+                feats.append(soft)
+                if wrap and vt.get("eoi_token_id") is not None:
+                    ids.append(int(vt["eoi_token_id"]))
+                    groups.append(-1)
+            elif isinstance(seg, (str, list, tuple)):
+                new = self.encode(seg) if isinstance(seg, str) else [int(t) for t in seg]
+                ids.extend(new)
+                groups.extend([-1] * len(new))
+            else:
+                raise MultimodalPreparationError(f"this model accepts text and images; the request carries {type(seg).__name__}")
+        if not feats:
+            return ids, None
+        bidir = groups if (self.config.extra.get("gemma4") or {}).get("use_bidirectional_attention") == "vision" else None
+        return ids, {"rows": rows, "values": torch.cat(feats, 0), "deepstack": None, "rope_positions": None, "rope_delta": 0,
+                     "bidir_groups": bidir, "placeholder_id": int(vt["image_token_id"])}
 
     def chat_segments(self, messages: list, images: list, placeholder: str = "<|image_pad|>", **template_kwargs) -> list:
         """Render a conversation whose user content lists contain ``{"type": "image"}`` items with the chat template and

@@ -258,7 +258,7 @@ class ModelConfig:
                   "gemma4_text": "gemma4"}.get(mt, mt)
             d["model_type"] = mt
             d["_language_model_prefix"] = True
-            d["_vision"] = {k: outer[k] for k in ("vision_config", "image_token_id", "video_token_id", "vision_start_token_id",
+            d["_vision"] = {k: outer[k] for k in ("vision_config", "image_token_id", "video_token_id", "boi_token_id", "eoi_token_id", "vision_start_token_id",
                                                   "vision_end_token_id") if k in outer}
         # Transformers >= 5 writes RoPE settings as one ``rope_parameters`` object (theta inside it; optionally one
         # object per layer type): fold it back into rope_theta / rope_scaling
@@ -324,7 +324,8 @@ class ModelConfig:
             # the generic fields describe the sliding layers
             keys = ("global_head_dim", "num_global_key_value_heads", "attention_k_eq_v", "num_kv_shared_layers",
                     "use_double_wide_mlp", "hidden_size_per_layer_input", "vocab_size_per_layer_input", "enable_moe_block",
-                    "top_k_experts", "hidden_activation", "final_logit_softcapping")
+                    "top_k_experts", "hidden_activation", "final_logit_softcapping", "use_bidirectional_attention",
+                    "pad_token_id")
             cfg.extra["gemma4"] = {k: d.get(k) for k in keys}
             cfg.extra["gemma4"]["rope_parameters"] = raw_rope_parameters
             cfg.embedding_scale = float(cfg.hidden_size) ** 0.5

@@ -157,7 +157,7 @@ def block_forward(model, li, lw, h, batch, kv):
         v_cache[page, :, off] = v[ok].to(v_cache.dtype)
     q_lens = (batch.cu_q[1:] - batch.cu_q[:-1]).tolist() if batch.is_prefill else [batch.q_per_seq] * batch.seq_lens.shape[0]
     attn = ops.attention_ref(q.to(dt), k_cache, v_cache, batch.block_table, batch.seq_lens, q_lens, 1.0,
-                             window=int(cfg.sliding_window or 0) if sliding else 0)
+                             window=int(cfg.sliding_window or 0) if sliding else 0, bidir=batch.bidir_groups)
     a = ops.linear(attn.reshape(M, Hq * D).to(dt), w["o"])
     h = h + _rms(a, w["post_attention_layernorm"], eps).to(dt)
 

@@ -48,6 +48,7 @@ class ForwardBatch:
     deepstack: Optional[list] = None                # list of [n_vis, H]: added after layer 0, 1, ...
     rope_positions: Optional[torch.Tensor] = None   # [M] or [3, M]; None: ``positions``
     per_layer_inputs: Optional[torch.Tensor] = None  # Gemma 4: [M, layers, P], filled by the model
+    bidir_groups: Optional[list] = None             # per sequence: int tensor [kv_len] of bidirectional-attention group ids
     # embedded prediction heads: keep the hidden state that enters the final norm (all rows) in ``hidden_out``
     capture_hidden: bool = False
     hidden_out: Optional[torch.Tensor] = None
@@ -287,13 +288,15 @@ class CausalLM:
                 h = ops.embedding(batch.token_ids, self.embed, 0, self.cfg.embedding_scale)
         else:
             h = batch.hidden_in
-        if getattr(self, "g4", None) is not None:
-            from .gemma4 import per_layer_inputs
-
-            batch.per_layer_inputs = per_layer_inputs(self, batch.token_ids, h)
         if batch.embed_rows is not None and self.par.owns_embedding():
             h = h.index_copy(0, batch.embed_rows, batch.embed_values.to(h.dtype))
             ssq = None                      # the embedding kernel's row sums no longer describe these rows
+        if getattr(self, "g4", None) is not None:
+            from .gemma4 import per_layer_inputs
+
+            # the per-layer token table sees the ids as fed (padding at soft-token rows), the projected part sees the
+            # activations after soft tokens took their rows
+            batch.per_layer_inputs = per_layer_inputs(self, batch.token_ids, h)
         n = len(self.layers)
         obs = self.observer
         if obs is not None and self.par.owns_embedding():

@@ -205,8 +205,10 @@ def _gather_kv(cache, block_table_row, kv_len):
     return pages.permute(1, 0, 2, 3).reshape(cache.shape[1], n_pages * PAGE, cache.shape[3])[:, :kv_len]
 
 
-def attention_ref(q, k_cache, v_cache, block_table, seq_lens, q_lens, scale, window=0, sinks=None):
-    """q: [total_q, n_q, D]; the last q_lens[b] positions of sequence b are its queries (causal)."""
+def attention_ref(q, k_cache, v_cache, block_table, seq_lens, q_lens, scale, window=0, sinks=None, bidir=None):
+    """q: [total_q, n_q, D]; the last q_lens[b] positions of sequence b are its queries (causal).
+    ``bidir``: per sequence None or an int tensor [kv_len] of group ids (negative: none); positions of one group see each
+    other in both directions, whatever the causal order and the window say (soft tokens of one image)."""
     total, n_q, D = q.shape
     n_kv = k_cache.shape[1]
     group = n_q // n_kv
@@ -224,6 +226,9 @@ def attention_ref(q, k_cache, v_cache, block_table, seq_lens, q_lens, scale, win
         mask = kpos <= qpos
         if window > 0:
             mask = mask & (kpos > qpos - window)
+        if bidir is not None and bidir[b] is not None:
+            grp = bidir[b].to(q.device)
+            mask = mask | ((grp[kv_len - ql:kv_len, None] == grp[None, :kv_len]) & (grp[kv_len - ql:kv_len, None] >= 0))
         s = s.masked_fill(~mask[None], float("-inf"))
         if sinks is not None:
             s = torch.cat((s, sinks.float()[:, None, None].expand(n_q, ql, 1)), dim=-1)

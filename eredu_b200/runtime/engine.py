@@ -290,7 +290,8 @@ class Engine:
         device). For samplers that must see every distribution on the host (grammar masks, Mirostat).
 
         ``multimodal``: dict with ``rows`` (indices into ``tokens`` whose embeddings are replaced), ``values`` [n, H],
-        optional ``deepstack`` (list of [n, H]) and ``rope_positions`` [3, len(tokens)] for prompts with images; it sets
+        optional ``deepstack`` (list of [n, H]), ``rope_positions`` [3, len(tokens)] and ``bidir_groups`` (one group id per
+        token, -1 for text: tokens of a group attend to each other in both directions) for prompts with images; it sets
         ``seq.rope_delta`` so that later text tokens continue after the largest position the images used."""
         n = len(tokens)
         p = np.arange(seq.kv_len, seq.kv_len + n)
@@ -301,8 +302,14 @@ class Engine:
             dev = self.device
             extra = dict(embed_rows=torch.as_tensor(multimodal["rows"], dtype=torch.int64, device=dev),
                          embed_values=multimodal["values"].to(dev),
-                         deepstack=[d.to(dev) for d in multimodal.get("deepstack") or []] or None,
-                         rope_positions=multimodal["rope_positions"].to(dev))
+                         deepstack=[d.to(dev) for d in multimodal.get("deepstack") or []] or None)
+            if multimodal.get("rope_positions") is not None:
+                extra["rope_positions"] = multimodal["rope_positions"].to(dev)
+            if multimodal.get("bidir_groups") is not None:
+                # group ids of the fed tokens; earlier positions of the sequence belong to no group
+                grp = torch.full((seq.kv_len + n,), -1, dtype=torch.int64, device=dev)
+                grp[seq.kv_len:] = torch.as_tensor(multimodal["bidir_groups"], dtype=torch.int64, device=dev)
+                extra["bidir_groups"] = [grp]
             seq.rope_delta = int(multimodal.get("rope_delta", 0))
         elif delta:
             extra = dict(rope_positions=self._t((p + delta).astype(np.int32), torch.int32))

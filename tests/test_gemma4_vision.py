@@ -78,3 +78,57 @@ def test_resize_rule_and_patch_layout():
     # patch 7 = row 1, column 1; inside a patch pixels run row-major with the channels last
     want = np.asarray(img.pixels, dtype=np.float32)[4:8, 4:8].reshape(-1) / 255.0
     assert np.allclose(patches[7].numpy(), want)
+
+
+@pytest.mark.parametrize("bidirectional", [True, False])
+def test_image_prompt_logits_match_transformers(tmp_path, bidirectional):
+    """Soft tokens replace the padding embedding of their rows (the per-layer inputs see the padding token); with
+    ``use_bidirectional_attention = "vision"`` the soft tokens of one image attend to each other in both directions, in the
+    sliding layers too."""
+    from eredu_b200.api import LoadedModel, ModelLoadOptions
+    from eredu_b200.media import RgbImage
+
+    global TEXT
+    saved = TEXT
+    TEXT = dict(TEXT, use_bidirectional_attention="vision" if bidirectional else None)
+    try:
+        m = hf_g4()
+    finally:
+        TEXT = saved
+    m.save_pretrained(tmp_path, safe_serialization=True)
+    lm = LoadedModel.load(tmp_path, ModelLoadOptions(device="cpu", max_batch=1, max_seq_len=128))
+    assert lm.vision is not None and lm.vision_tokens["image_token_id"] == 300 and lm.vision_tokens["boi_token_id"] == 303
+    rng = np.random.default_rng(0)
+    img_a = RgbImage(rng.integers(0, 255, (16, 24, 3), dtype=np.uint8))      # 4 x 6 patches -> 6 soft tokens
+    img_b = RgbImage(rng.integers(0, 255, (8, 8, 3), dtype=np.uint8))        # upscaled to the budget: 4 x 4 patches -> 4 soft tokens
+    segments = [[5, 6, 7], img_a, [8, 9], img_b, [10, 11, 12, 13]]
+    ids, mm = lm.multimodal_inputs(segments, image_limits=dict(max_soft_tokens=6))
+    assert len(mm["rows"]) == 10 and ids[3] == 303 and ids[10] == 304 and all(ids[r] == 0 for r in mm["rows"])
+    assert (mm["bidir_groups"] is not None) == bidirectional
+    # Transformers gets the same patches (padded to one length per batch entry, padding marked by position -1)
+    from eredu_b200.models.gemma4_vision import image_to_patches as g4_patches
+
+    pa, xa, _ = g4_patches(img_a, lm.vision.cfg, 6)
+    pb, xb, _ = g4_patches(img_b, lm.vision.cfg, 6)
+    pv = torch.zeros(2, 24, 48)
+    pp = torch.full((2, 24, 2), -1, dtype=torch.long)
+    pv[0], pp[0] = pa, xa
+    pv[1, :16], pp[1, :16] = pb, xb
+    hf_ids = list(ids)
+    for r in mm["rows"]:
+        hf_ids[r] = 300
+    types = torch.tensor([[1 if t == 300 else 0 for t in hf_ids]])
+    with torch.no_grad():
+        out = m(input_ids=torch.tensor([hf_ids]), pixel_values=pv, image_position_ids=pp, mm_token_type_ids=types)
+    ref = out.logits[0, -1]
+    seq = lm.engine.new_sequence(ids, max_new_tokens=4)
+    got = lm.engine.feed_logits(seq, ids, mm).float().cpu()
+    assert torch.allclose(got, ref, atol=2e-3), float((got - ref).abs().max())
+    # decode continues causally after the prompt
+    nxt = int(ref.argmax())
+    with torch.no_grad():
+        ref2 = m(input_ids=torch.tensor([hf_ids + [nxt]]), pixel_values=pv, image_position_ids=pp,
+                 mm_token_type_ids=torch.tensor([types[0].tolist() + [0]])).logits[0, -1]
+    got2 = lm.engine.step_logits(seq, nxt).float().cpu()
+    lm.engine.release(seq)
+    assert torch.allclose(got2, ref2, atol=2e-3), float((got2 - ref2).abs().max())
