@@ -65,32 +65,63 @@ def build_block(model, cfg, li, p, get, has, up, moe_factory):
     """One Nemotron-H block as LayerWeights (``block_kind`` names the mixer)."""
     from .llama import LayerWeights, shard_attention
 
-    if model.par.tp_size > 1:
-        raise NotImplementedError("tensor parallelism for Nemotron-H blocks is not implemented")
+    tp, r = model.par.tp_size, model.par.tp_rank
     kind = cfg.layer_types[li]
     lw = LayerWeights(attn_norm=up(get(p + "norm.weight"), torch.float32), wqkv=None, wo=None, ffn_norm=None)
     lw.block_kind = kind
     mx = p + "mixer."
     bias = lambda n: up(get(n)) if has(n) else None                                   # noqa: E731
     if kind == "mamba":
-        lw.m_in = up(get(mx + "in_proj.weight"))
-        lw.m_in_b = bias(mx + "in_proj.bias")
+        # Tensor parallelism splits the mixer by heads: a rank keeps H / tp heads with their gate and value channels,
+        # G / tp groups of B / C, its slice of the convolution, of the grouped norm and of the output projection's inputs
+        # (whole groups per rank, so the grouped RMSNorm stays local); the output projection is summed over the ranks.
+        H_all, G_all, N, P = cfg.mamba_num_heads, cfg.mamba_n_groups, cfg.ssm_state_size, cfg.mamba_head_dim
+        if tp > 1 and (H_all % tp or G_all % tp):
+            raise NotImplementedError(f"Mamba heads ({H_all}) and groups ({G_all}) must divide over {tp} tensor ranks")
+        inter_all = H_all * P
+        w_in = get(mx + "in_proj.weight")
+        if tp > 1 and w_in.shape[0] != 2 * inter_all + 2 * G_all * N + H_all:
+            raise NotImplementedError("tensor parallelism needs the plain [gate | x | B | C | dt] input projection")
+        hs, gs = H_all // tp, G_all // tp
+
+        def parts(t, lead: int):
+            """Rows of this rank from a tensor laid out as [lead blocks of `inter` | B | C | (dt)]."""
+            if tp == 1:
+                return t
+            out, off = [], 0
+            for _ in range(lead):
+                out.append(t[off + r * hs * P:off + (r + 1) * hs * P])
+                off += inter_all
+            for _ in range(2):
+                out.append(t[off + r * gs * N:off + (r + 1) * gs * N])
+                off += G_all * N
+            if t.shape[0] > off:
+                out.append(t[off + r * hs:off + (r + 1) * hs])
+            return torch.cat(out, 0)
+
+        head = (lambda t: t[r * hs:(r + 1) * hs]) if tp > 1 else (lambda t: t)
+        lw.m_in = up(parts(w_in, 2))
+        lw.m_in_b = up(parts(get(mx + "in_proj.bias"), 2)) if has(mx + "in_proj.bias") else None
         conv = get(mx + "conv1d.weight")
-        lw.m_conv_w = up(conv.reshape(conv.shape[0], -1), torch.float32)
-        lw.m_conv_b = up(get(mx + "conv1d.bias"), torch.float32) if has(mx + "conv1d.bias") else None
-        lw.m_A_log = up(get(mx + "A_log"), torch.float32)
-        lw.m_D = up(get(mx + "D"), torch.float32)
-        lw.m_dt_bias = up(get(mx + "dt_bias"), torch.float32)
-        lw.m_norm_w = up(get(mx + "norm.weight"), torch.float32)
-        lw.m_out = up(get(mx + "out_proj.weight"))
+        lw.m_conv_w = up(parts(conv.reshape(conv.shape[0], -1), 1), torch.float32)
+        lw.m_conv_b = up(parts(get(mx + "conv1d.bias"), 1), torch.float32) if has(mx + "conv1d.bias") else None
+        lw.m_A_log = up(head(get(mx + "A_log")), torch.float32)
+        lw.m_D = up(head(get(mx + "D")), torch.float32)
+        lw.m_dt_bias = up(head(get(mx + "dt_bias")), torch.float32)
+        nw, ow = get(mx + "norm.weight"), get(mx + "out_proj.weight")
+        lw.m_norm_w = up(nw[r * hs * P:(r + 1) * hs * P] if tp > 1 else nw, torch.float32)
+        lw.m_out = up(ow[:, r * hs * P:(r + 1) * hs * P] if tp > 1 else ow)
         lw.m_out_b = bias(mx + "out_proj.bias")
     elif kind == "attention_only":
         wq, wk, wv, wo = (get(mx + f"{n}_proj.weight") for n in "qkvo")
         wqkv, wo_l, _ = shard_attention(cfg, model.par, wq, wk, wv, wo)
         lw.wqkv, lw.wo = up(wqkv), up(wo_l)
     elif kind == "mlp_only":
-        lw.w_gate_up = up(get(mx + "up_proj.weight"))          # a single up projection: relu^2, no gate
-        lw.w_down = up(get(mx + "down_proj.weight"))
+        w_up, w_dn = get(mx + "up_proj.weight"), get(mx + "down_proj.weight")   # a single up projection: relu^2, no gate
+        if tp > 1:
+            n = w_up.shape[0] // tp
+            w_up, w_dn = w_up[r * n:(r + 1) * n], w_dn[:, r * n:(r + 1) * n]
+        lw.w_gate_up, lw.w_down = up(w_up), up(w_dn)
     else:
         lw.moe = moe_factory(model, li, get, has)
     return lw
@@ -103,7 +134,7 @@ def block_forward(model, li, lw, h, batch, kv):
     if kind == "mlp_only":
         a = ops.linear(x, lw.w_gate_up)
         a = torch.relu(a).square_()
-        return ops.linear(a, lw.w_down, residual=h)
+        return model._row_linear(lw, "down", a, lw.w_down, h)
     if kind == "moe_only":
         return lw.moe(x, residual=h)
     if kind == "attention_only":
@@ -117,13 +148,13 @@ def block_forward(model, li, lw, h, batch, kv):
         else:
             attn = ops.attention_decode(q, k_cache, v_cache, batch.block_table, batch.seq_lens, batch.q_per_seq, model.scale,
                                         splits=batch.splits, scratch=batch.scratch)
-        return ops.linear(attn.view(attn.shape[0], -1), lw.wo, residual=h)
-    return h + mamba_forward(model, li, lw, x, batch, kv)
+        return model._row_linear(lw, "o", attn.view(attn.shape[0], -1), lw.wo, h)
+    return mamba_forward(model, li, lw, x, batch, kv, h)
 
 
-def mamba_forward(model, li, lw, x, batch, kv):
+def mamba_forward(model, li, lw, x, batch, kv, residual):
     cfg = model.cfg
-    heads, groups, inter, conv_dim = mamba_dims(cfg)
+    heads, groups, inter, conv_dim = mamba_dims(cfg, model.par.tp_size)
     P, N = cfg.mamba_head_dim, cfg.ssm_state_size
     proj = ops.linear(x, lw.m_in, bias=lw.m_in_b)
     M = proj.shape[0]
@@ -166,7 +197,7 @@ def mamba_forward(model, li, lw, x, batch, kv):
     grouped = gated.view(M, groups, inter // groups)
     normed = (grouped * torch.rsqrt(grouped.square().mean(-1, keepdim=True) + cfg.rms_norm_eps)).view(M, inter)
     out = (normed.to(x.dtype) * lw.m_norm_w.to(x.dtype)[None, :])
-    return ops.linear(out, lw.m_out, bias=lw.m_out_b)
+    return model._row_linear(lw, "m_out", out, lw.m_out, residual, bias=lw.m_out_b)
 
 
 def random_block_state(cfg, li, p, mat, out, std):

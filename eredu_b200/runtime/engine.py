@@ -69,7 +69,7 @@ class Engine:
         if mamba_layers:
             from ..models.nemotron_h import mamba_dims
 
-            heads, _, _, conv_dim = mamba_dims(self.cfg)
+            heads, _, _, conv_dim = mamba_dims(self.cfg, model.par.tp_size)
             self.kv.enable_linear_attention_state(mamba_layers, slots=max(2 * max_batch, 8),
                                                   conv_hist=self.cfg.mamba_conv_kernel - 1, conv_channels=conv_dim, heads=heads,
                                                   dk=self.cfg.mamba_head_dim, dv=self.cfg.ssm_state_size)
