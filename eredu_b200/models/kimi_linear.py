@@ -48,27 +48,36 @@ def canonical_access(get, has):
 def build_kda_layer(model, cfg, p, get, has, up):
     from .llama import LayerWeights
 
-    if model.par.tp_size > 1:
-        raise NotImplementedError("tensor parallelism over KDA layers is not implemented")
+    # Tensor parallelism splits the layer by heads: q / k / v / beta rows, the convolution channels, the expanded decay
+    # and gate projections, the per-head rates and the output projection's inputs; the two low-rank bottlenecks (f_a,
+    # g_a) and the output norm are replicated, the output projection is summed over the ranks.
+    tp, r = model.par.tp_size, model.par.tp_rank
+    H, D = cfg.linear_num_value_heads, cfg.linear_value_head_dim
+    if H % tp:
+        raise NotImplementedError(f"{H} KDA heads do not divide over {tp} tensor ranks")
+    Hl = H // tp
+    rows = (lambda t, per: t[r * Hl * per:(r + 1) * Hl * per]) if tp > 1 else (lambda t, per: t)
     a = p + "self_attn."
     lw = LayerWeights(attn_norm=up(get(p + "input_layernorm.weight"), torch.float32), wqkv=None, wo=None,
                       ffn_norm=up(get(p + "post_attention_layernorm.weight"), torch.float32))
     # one input GEMM: [q | k | v | f_a | b | g_a]
-    lw.kda_in = up(torch.cat([get(a + f"{n}.weight") for n in ("q_proj", "k_proj", "v_proj", "f_a_proj", "b_proj", "g_a_proj")], 0))
-    conv = torch.cat([get(a + f"{n}_conv1d.weight") for n in "qkv"], 0)
+    lw.kda_in = up(torch.cat([rows(get(a + "q_proj.weight"), D), rows(get(a + "k_proj.weight"), D), rows(get(a + "v_proj.weight"), D),
+                              get(a + "f_a_proj.weight"), rows(get(a + "b_proj.weight"), 1), get(a + "g_a_proj.weight")], 0))
+    conv = torch.cat([rows(get(a + f"{n}_conv1d.weight"), D) for n in "qkv"], 0)
     lw.kda_conv_w = up(conv.reshape(conv.shape[0], -1), torch.float32)
-    lw.kda_f_b = up(get(a + "f_b_proj.weight"))
-    lw.kda_g_b = up(get(a + "g_b_proj.weight"))
-    lw.kda_A_log = up(get(a + "A_log").reshape(-1), torch.float32)          # one rate per head
-    lw.kda_dt_bias = up(get(a + "dt_bias").reshape(-1), torch.float32)      # one bias per channel
+    lw.kda_f_b = up(rows(get(a + "f_b_proj.weight"), D))
+    lw.kda_g_b = up(rows(get(a + "g_b_proj.weight"), D))
+    lw.kda_A_log = up(rows(get(a + "A_log").reshape(-1), 1), torch.float32)          # one rate per head
+    lw.kda_dt_bias = up(rows(get(a + "dt_bias").reshape(-1), D), torch.float32)      # one bias per channel
     lw.kda_o_norm = up(get(a + "o_norm.weight"), torch.float32)
-    lw.wo = up(get(a + "o_proj.weight"))
+    wo = get(a + "o_proj.weight")
+    lw.wo = up(wo[:, r * Hl * D:(r + 1) * Hl * D] if tp > 1 else wo)
     return lw
 
 
 def kda_forward(model, li, lw, h, ssq, batch, kv):
     cfg = model.cfg
-    H, D = cfg.linear_num_value_heads, cfg.linear_value_head_dim
+    H, D = cfg.linear_num_value_heads // model.par.tp_size, cfg.linear_value_head_dim
     P = H * D
     proj = model._normed_linear(h, ssq, lw.fold_attn, lw.attn_norm, lw.kda_in, lw, "kda_in")
     M = proj.shape[0]

@@ -76,9 +76,10 @@ class Engine:
         kda_layers = [li for li in local if self.cfg.layer_is_kda(li)]
         if kda_layers:
             c = self.cfg
+            kh = c.linear_num_value_heads // model.par.tp_size
             self.kv.enable_linear_attention_state(kda_layers, slots=max(2 * max_batch, 8), conv_hist=c.linear_conv_kernel_dim - 1,
-                                                  conv_channels=3 * c.linear_num_value_heads * c.linear_value_head_dim,
-                                                  heads=c.linear_num_value_heads, dk=c.linear_value_head_dim,
+                                                  conv_channels=3 * kh * c.linear_value_head_dim,
+                                                  heads=kh, dk=c.linear_value_head_dim,
                                                   dv=c.linear_value_head_dim)
         la_layers = [li for li in local if self.cfg.layer_is_linear_attention(li)]
         if la_layers:

@@ -108,6 +108,14 @@ def main():
         g = torch.Generator().manual_seed(0)
         prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 33)]
 
+    if "kimi" in scenario:      # Kimi Linear: KDA heads, latent-attention heads and experts over the same ranks
+        from test_kimi_linear import kimi_cfg, state_for as kimi_state
+
+        cfg = kimi_cfg()
+        sd = kimi_state(cfg)
+        g = torch.Generator().manual_seed(0)
+        prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 33)]
+
     if "dsv3" in scenario:      # DeepSeek-V3 style: latent attention heads and experts spread over the same ranks
         from test_deepseek import ds_cfg, state_for as ds_state
 
@@ -183,7 +191,7 @@ def main():
         from eredu_b200.models.moe import make_moe_factory
         from eredu_b200.parallel import tp
 
-        if "qnext" not in scenario and "dsv3" not in scenario and "nemo" not in scenario:
+        if "qnext" not in scenario and "dsv3" not in scenario and "nemo" not in scenario and "kimi" not in scenario:
             cfg = moe_cfg(gpu)
             sd = random_state(cfg, seed=0, std=0.08)
         par = ParallelContext.from_env(ParallelTopology(tensor=world, expert=world, expert_over_tensor=True))

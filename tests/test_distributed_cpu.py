@@ -87,6 +87,23 @@ def test_nemotron_h_over_tensor_and_expert_ranks(tmp_path):
         assert r["tokens"] == want
 
 
+def test_kimi_linear_over_tensor_and_expert_ranks(tmp_path):
+    """KDA layers split by heads (convolution channels, decay and gate expansions, recurrent state local to a rank),
+    latent attention by head, experts over the same two ranks."""
+    from eredu_b200.models.moe import make_moe_factory
+    from test_kimi_linear import kimi_cfg, state_for
+
+    res = run_ranks("cpu_kimi_ep_nccl", 2, tmp_path)
+    cfg = kimi_cfg()
+    sd = state_for(cfg)
+    model = build_from_tensors(cfg, sd.__getitem__, sd.__contains__, "cpu", torch.float32, moe_factory=make_moe_factory())
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 33)]
+    want = Engine(model, max_batch=4, max_seq_len=128).generate(prompts, SamplingParams(temperature=0.0), 10)
+    for r in res:
+        assert r["tokens"] == want
+
+
 def test_qwen_next_family_over_tensor_and_expert_ranks(tmp_path):
     """Gated-delta layers sharded by key-head group, gated attention by head, experts over the same two ranks."""
     from eredu_b200.models.moe import make_moe_factory
