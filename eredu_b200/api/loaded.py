@@ -451,7 +451,19 @@ class LoadedModel:
 
             constraint = constraint_for_tools(self.tokenizer, prepared.tools, prepared.tool_choice.mode,
                                               prepared.tool_choice.max_parallel_calls, plan.tool_open, plan.tool_close)
-        if mirostat is not None or constraint is not None:
+        if constraint is not None and mirostat is None and draft is not None:
+            # speculation under a grammar: proposals run the grammar ahead, rejected ones are rolled back
+            from ..runtime.speculative import SpeculativeDecoder
+
+            spec = SpeculativeDecoder(self.engine, draft.engine, k=draft_tokens)
+            _, why = spec.generate_constrained(prompt_ids, constraint, sampling, max_new_tokens, tuple(eos),
+                                               on_token=lambda tok: on_token(0, tok))
+            reason = {"eos": FinishReason.EOS, "max_tokens": FinishReason.MAX_TOKENS,
+                      "grammar_complete": FinishReason.GRAMMAR_COMPLETE}.get(why, why)
+            self.last_speculative_stats = dict(spec.stats.summary(), constrained=True)
+            if first_token_at[0] is None:
+                first_token_at[0] = time.perf_counter()
+        elif mirostat is not None or constraint is not None:
             from ..ops.controlled import controlled_generate
 
             _, why = controlled_generate(self.engine, prompt_ids, sampling, max_new_tokens, tuple(eos), constraint,

@@ -381,8 +381,8 @@ def main(argv=None) -> int:
         constraint = lm.constraint_for(kind, val if kind == "regex" else open(val).read())
     draft = None
     if a.draft_model:
-        if mirostat is not None or constraint is not None:
-            raise SystemExit("--draft-model cannot be combined with --mirostat-v2 or a grammar constraint")
+        if mirostat is not None:
+            raise SystemExit("--draft-model cannot be combined with --mirostat-v2")
         draft = LoadedModel.load(a.draft_model, ModelLoadOptions(device=device, max_batch=1,
                                                                   max_seq_len=max(4096, a.max_tokens + 2048)))
         if draft.config.vocab_size != lm.config.vocab_size:

@@ -161,6 +161,113 @@ class SpeculativeDecoder:
             for s in dseqs:
                 self.d.release(s)
 
+    # ------------------------------------------------------------------------------------------ grammar-constrained
+    @torch.no_grad()
+    def generate_constrained(self, prompt: list[int], constraint, sampling: Optional[SamplingParams] = None,
+                             max_new_tokens: int = 64, eos_ids=(), on_token=None):
+        """One sequence under a grammar (``ops.controlled.GrammarConstraint``): proposals are drawn from the draft's masked
+        distributions while a fork of the grammar state runs ahead, and the target's rows are masked with
+        the states along the proposed path before the usual accept / resample rule; only accepted tokens (and the one that
+        ends the round) are committed to the grammar (constraints.rs: fork / rollback for speculation). Returns
+        (tokens, finish_reason)."""
+        from ..ops.sampling import sample_ref
+
+        if self.t_hybrid or self.d_hybrid:
+            raise NotImplementedError("grammar-constrained speculation covers attention-only target and draft models")
+        sp = sampling or SamplingParams(temperature=0.0)
+        k = self.k
+        V = self.t.cfg.vocab_size
+        tseq = self.t.new_sequence(prompt, sp, max_new_tokens + k + 2, eos_ids)
+        dseq = self.d.new_sequence(prompt, sp, max_new_tokens + k + 2, eos_ids)
+        out: list[int] = []
+        reason = "max_tokens"
+
+        def masked(logits_row, position):
+            allow = constraint.allow_mask(V)
+            for e in eos_ids:
+                allow[e] = constraint.is_accepting()
+            return sample_ref(logits_row.float().cpu(), sp, position, allow=allow, stream=tseq.seq_id)
+
+        def emit(tok) -> bool:
+            """Commit one token everywhere; True when generation ends with it."""
+            nonlocal reason
+            if tok in eos_ids:
+                reason = "eos"
+                return True
+            constraint.commit(tok)
+            out.append(tok)
+            early = on_token(tok) if on_token is not None else None
+            if early:
+                reason = early
+                return True
+            if constraint.is_complete():
+                reason = "grammar_complete"
+                return True
+            return len(out) >= max_new_tokens
+
+        try:
+            logits = self.t.prefill_logits([tseq])[0]
+            self.d.prefill_logits([dseq])
+            tok, _ = masked(logits, len(prompt))
+            done = emit(tok)
+            pending = [tok]                       # committed tokens the draft has not seen
+            while not done:
+                base = tseq.kv_len + 1            # position of the first proposal; `out[-1]` is the target's next input
+                drafted, q_rows, masks = [], [], []
+                feed = pending
+                draft_len = dseq.kv_len
+                ahead = constraint.fork()         # the proposals advance a copy: a finished or refused path costs nothing
+
+                def ahead_mask():
+                    allow = ahead.allow_mask(V)
+                    for e in eos_ids:
+                        allow[e] = ahead.is_accepting()
+                    return allow
+
+                for j in range(k):
+                    lg = self._multi_token_step(self.d, [dseq], [feed], all_rows=False, uniform=False)[0]
+                    dseq.kv_len += len(feed)
+                    allow = ahead_mask()
+                    d_tok, q = sample_ref(lg.float().cpu(), sp, base + j, allow=allow, stream=tseq.seq_id)
+                    if d_tok in eos_ids:
+                        break                     # the draft wants to stop: let the target decide at this row
+                    masks.append(allow)
+                    drafted.append(d_tok)
+                    q_rows.append(q)
+                    ahead.commit(d_tok)
+                    feed = [d_tok]
+                    if ahead.is_complete():
+                        break
+                n = len(drafted)
+                # state after every proposal: masks the bonus row (nothing but the end is legal after a finished grammar)
+                tail = ahead_mask() if not (n and ahead.is_complete()) else masks[-1].new_zeros(V)
+                lg_t = self._multi_token_step(self.t, [tseq], [[out[-1]] + drafted], all_rows=True, uniform=False)
+                p_rows = [sample_ref(lg_t[j].float().cpu(), sp, base + j, allow=(masks + [tail])[j], stream=tseq.seq_id)[1]
+                          for j in range(n + 1)]
+                if n:
+                    a, nxt = ops.verify_ref(torch.stack(p_rows), torch.stack(q_rows), drafted, sp.seed, tseq.seq_id, base)
+                else:
+                    a, nxt = 0, sample_ref(lg_t[0].float().cpu(), sp, base, allow=tail, stream=tseq.seq_id)[0]
+                if a == n and n:
+                    nxt = sample_ref(lg_t[n].float().cpu(), sp, base + n, allow=tail, stream=tseq.seq_id)[0]
+                tseq.kv_len += 1 + a
+                fed = dseq.kv_len - draft_len - len(pending)              # proposals the draft itself has consumed
+                keep = min(a, fed)
+                dseq.kv_len = draft_len + len(pending) + keep
+                pending = drafted[keep:a] + [nxt]
+                self.stats.rounds += 1
+                self.stats.proposed += n
+                self.stats.accepted += a
+                self.stats.emitted += a + 1
+                for tok in drafted[:a] + [nxt]:
+                    done = emit(tok)
+                    if done:
+                        break
+            return out, reason
+        finally:
+            self.t.release(tseq)
+            self.d.release(dseq)
+
     # ---- the three places where an embedded prediction head differs from an external draft model
     def _prefill(self, tseqs, dseqs) -> list:
         first = self.t.prefill(tseqs).tolist()

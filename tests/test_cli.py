@@ -182,3 +182,28 @@ def test_cli_automatic_benchmark(tmp_path, capsys):
     assert rep["selected"] == rep["candidates"][rep["selected_index"]]["plan"] and rep["selection_metric"] == "median_decode_token_rate"
     entry = next(iter(json.loads(cache.read_text()).values()))
     assert entry["plan"] == rep["selected"] and entry["benchmark_token_rate"] == rep["selected_median_token_rate"]
+
+
+def test_cli_draft_model_with_a_grammar(tmp_path, capsys):
+    """--draft-model and --regex together: speculation under the grammar gives the text constrained decoding gives."""
+    pytest.importorskip("llguidance")
+    from eredu_b200.formats import checkpoint as ck
+    from eredu_b200.models import config as C
+    from eredu_b200.models.llama import random_state
+
+    tgt, drf = tmp_path / "t", tmp_path / "d"
+    for d, layers, seed in ((tgt, 2, 0), (drf, 1, 4)):
+        d.mkdir()
+        b = make_bundle(d)
+        cfg = dataclasses.replace(C.tiny_llama(), vocab_size=b.vocab_size(), eos_token_id=b.eos_ids[0], num_hidden_layers=layers)
+        ck.save_safetensors_checkpoint(d, cfg, random_state(cfg, seed=seed, std=0.05), torch.float32)
+    base = ["-m", str(tgt), "answer:", "--device", "cpu", "--no-auto", "--raw", "-n", "16", "-t", "0", "--regex", "(ab|ba){2,4}!"]
+    assert main(base) == 0
+    plain = capsys.readouterr().out
+    tel = tmp_path / "tel.json"
+    assert main(base + ["--draft-model", str(drf), "--telemetry-json", str(tel)]) == 0
+    assert capsys.readouterr().out == plain and plain.strip().endswith("!")
+    spec = json.loads(tel.read_text())["plan"]["speculative"]
+    assert spec["constrained"] and spec["rounds"] >= 1
+    with pytest.raises(SystemExit):
+        main(base + ["--draft-model", str(drf), "--mirostat-v2", "-t", "0.7"])

@@ -73,3 +73,41 @@ def test_grammar_constraint_masks_rollback_and_generation(tmp_path):
     if reason != "max_tokens":
         assert json.loads(text)["ok"] in (True, False)
     assert eng.kv.allocator.free_pages() == eng.kv.num_pages - 1
+
+
+@pytest.mark.parametrize("same_draft", [True, False])
+@pytest.mark.parametrize("spec", [("regex", r"(ab|ba){2,6}!"), ("json_schema", {"type": "object", "properties": {"ok": {"type": "boolean"}},
+                                                                                   "required": ["ok"], "additionalProperties": False})])
+def test_speculation_under_a_grammar_commits_what_plain_constrained_decoding_commits(tmp_path, same_draft, spec):
+    """Proposals run the grammar ahead, the state is rolled back, target rows are masked along the proposed path: greedy
+    output equals step-by-step constrained decoding whatever the draft proposes."""
+    from eredu_b200.runtime.speculative import SpeculativeDecoder
+
+    b = make_bundle(tmp_path)
+    cfg = dataclasses.replace(C.tiny_llama(), vocab_size=b.vocab_size(), eos_token_id=b.eos_ids[0])
+    sd = random_state(cfg, seed=0, std=0.05)
+    target = build_from_tensors(cfg, sd.__getitem__, sd.__contains__, "cpu", torch.float32)
+    dcfg = dataclasses.replace(cfg, num_hidden_layers=1)
+    dsd = random_state(dcfg, seed=9, std=0.05)
+    draft = target if same_draft else build_from_tensors(dcfg, dsd.__getitem__, dsd.__contains__, "cpu", torch.float32)
+    prompt = b.encode("answer:")
+    sp = SamplingParams(temperature=0.0)
+    want, want_reason = constrained_generate(Engine(target, max_batch=1, max_seq_len=128), prompt, GrammarConstraint(b, *spec), sp,
+                                             max_new_tokens=24, eos_ids=b.eos_ids)
+    dec = SpeculativeDecoder(Engine(target, max_batch=1, max_seq_len=128, use_cuda_graph=False),
+                             Engine(draft, max_batch=1, max_seq_len=128, use_cuda_graph=False), k=3)
+    seen = []
+    got, reason = dec.generate_constrained(prompt, GrammarConstraint(b, *spec), sp, max_new_tokens=24, eos_ids=b.eos_ids,
+                                           on_token=lambda t: seen.append(t))
+    assert got == want and reason == want_reason and seen == got
+    st = dec.stats.summary()
+    if same_draft and st["proposed"]:
+        assert st["acceptance_rate"] == 1.0
+    assert dec.t.kv.allocator.free_pages() == dec.t.kv.num_pages - 1 and dec.d.kv.allocator.free_pages() == dec.d.kv.num_pages - 1
+    # sampling keeps working (distribution-preserving, not draw-preserving): the grammar still holds
+    got2, reason2 = dec.generate_constrained(prompt, GrammarConstraint(b, *spec), SamplingParams(temperature=0.9, seed=2),
+                                             max_new_tokens=24, eos_ids=b.eos_ids)
+    check = GrammarConstraint(b, *spec)
+    for t in got2:
+        check.commit(t)                                            # raises on a token the grammar does not allow
+    assert reason2 in ("grammar_complete", "eos", "max_tokens")
