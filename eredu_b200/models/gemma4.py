@@ -72,11 +72,30 @@ def build(model, cfg, get, has, up):
     """Populate ``model.layers`` (one dict of tensors per layer in ``LayerWeights.extra``) and the per-layer-input tables."""
     from .llama import LayerWeights
 
-    if model.par.tp_size > 1:
-        raise NotImplementedError("tensor parallelism for Gemma 4 is not implemented")
     g = cfg.extra["gemma4"]
+    tp, r = model.par.tp_size, model.par.tp_rank
     geo = geometry(cfg)
-    model.g4 = {"geometry": geo, "inv_freq": {k: v.to(model.device) for k, v in rope_tables(cfg).items()}}
+    Hq = cfg.num_attention_heads
+    if tp > 1:
+        # Tensor parallelism: query heads are split evenly; a layer type's key / value heads are split when there are at
+        # least as many as ranks and otherwise the one head a rank's queries read is kept (replication); feed-forward
+        # and expert intermediates are split by rows / columns. Per-layer-input tables and norms are replicated. The
+        # sandwich norms act on complete sums, so every row-parallel projection is reduced before its norm.
+        if Hq % tp:
+            raise NotImplementedError(f"{Hq} attention heads do not divide over {tp} tensor ranks")
+        local = []
+        for sliding, D, nkv, k_eq_v, donor in geo:
+            if nkv % tp == 0:
+                kv0, kvn = r * (nkv // tp), nkv // tp
+            elif tp % nkv == 0:
+                kv0, kvn = r // (tp // nkv), 1
+            else:
+                raise NotImplementedError(f"{nkv} key / value heads cannot be laid out over {tp} tensor ranks")
+            local.append((sliding, D, kvn, k_eq_v, donor, kv0))
+    else:
+        local = [t + (0,) for t in geo]
+    model.g4_heads = Hq // tp
+    model.g4 = {"geometry": [t[:5] for t in local], "inv_freq": {k: v.to(model.device) for k, v in rope_tables(cfg).items()}}
     P = int(g.get("hidden_size_per_layer_input") or 0)
     if P:
         model.g4["embed_per_layer"] = up(get("model.embed_tokens_per_layer.weight"))
@@ -89,20 +108,36 @@ def build(model, cfg, get, has, up):
                                              "post_feedforward_layernorm")}
         w["scalar"] = f32("layer_scalar") if has(p + "layer_scalar") else None
         a = "self_attn."
-        w["q"], w["o"] = up(get(p + a + "q_proj.weight")), up(get(p + a + "o_proj.weight"))
+        _, D, kvn, _, _, kv0 = local[li]
+        Hl = Hq // tp
+        wq, wo = get(p + a + "q_proj.weight"), get(p + a + "o_proj.weight")
+        if tp > 1:
+            wq, wo = wq[r * Hl * D:(r + 1) * Hl * D], wo[:, r * Hl * D:(r + 1) * Hl * D]
+        w["q"], w["o"] = up(wq), up(wo)
         w["q_norm"], w["k_norm"] = f32(a + "q_norm.weight"), f32(a + "k_norm.weight")
         if geo[li][4] is None or has(p + a + "k_proj.weight"):
-            w["k"] = up(get(p + a + "k_proj.weight"))
-            w["v"] = up(get(p + a + "v_proj.weight")) if has(p + a + "v_proj.weight") else None
-        w["gate_up"] = up(torch.cat((get(p + "mlp.gate_proj.weight"), get(p + "mlp.up_proj.weight")), 0))
-        w["down"] = up(get(p + "mlp.down_proj.weight"))
+            kv_rows = (lambda t: t[kv0 * D:(kv0 + kvn) * D]) if tp > 1 else (lambda t: t)
+            w["k"] = up(kv_rows(get(p + a + "k_proj.weight")))
+            w["v"] = up(kv_rows(get(p + a + "v_proj.weight"))) if has(p + a + "v_proj.weight") else None
+        wg, wu, wd = get(p + "mlp.gate_proj.weight"), get(p + "mlp.up_proj.weight"), get(p + "mlp.down_proj.weight")
+        if tp > 1:
+            n = wg.shape[0] // tp
+            wg, wu, wd = wg[r * n:(r + 1) * n], wu[r * n:(r + 1) * n], wd[:, r * n:(r + 1) * n]
+        w["gate_up"] = up(torch.cat((wg, wu), 0))
+        w["down"] = up(wd)
         if P:
             w["ple_gate"], w["ple_out"] = up(get(p + "per_layer_input_gate.weight")), up(get(p + "per_layer_projection.weight"))
             w["ple_post"] = f32("post_per_layer_input_norm.weight")
         if g.get("enable_moe_block"):
             w["router_proj"] = up(get(p + "router.proj.weight"))
             w["router_scale"], w["expert_scale"] = f32("router.scale"), f32("router.per_expert_scale")
-            w["experts_gu"], w["experts_dn"] = up(get(p + "experts.gate_up_proj")), up(get(p + "experts.down_proj"))
+            egu, edn = get(p + "experts.gate_up_proj"), get(p + "experts.down_proj")          # [E, 2 I, H], [E, H, I]
+            if tp > 1:
+                ie = egu.shape[1] // 2
+                n = ie // tp
+                egu = torch.cat((egu[:, r * n:(r + 1) * n], egu[:, ie + r * n:ie + (r + 1) * n]), 1)
+                edn = edn[:, :, r * n:(r + 1) * n]
+            w["experts_gu"], w["experts_dn"] = up(egu), up(edn)
             for n in ("post_feedforward_layernorm_1", "post_feedforward_layernorm_2", "pre_feedforward_layernorm_2"):
                 w[n] = f32(n + ".weight")
         lw = LayerWeights(attn_norm=w["input_layernorm"], wqkv=None, wo=None, ffn_norm=None)
@@ -138,8 +173,14 @@ def block_forward(model, li, lw, h, batch, kv):
     eps = cfg.rms_norm_eps
     sliding, D, nkv, k_eq_v, donor = model.g4["geometry"][li]
     M = h.shape[0]
-    Hq = cfg.num_attention_heads
+    Hq = model.g4_heads
     dt = h.dtype
+    tp = model.par.tp_size
+
+    def reduced(partial):
+        """Sum of a row-parallel projection over the tensor ranks (the norms that follow need the complete value)."""
+        return model.tp_ops.all_reduce(partial.contiguous()) if tp > 1 else partial
+
     inv = model.g4["inv_freq"][cfg.layer_types[li]]
     x = _rms(h, w["input_layernorm"], eps).to(dt)
     q = _rope(_rms(ops.linear(x, w["q"]).view(M, Hq, D), w["q_norm"], eps), batch.positions, inv)
@@ -158,14 +199,14 @@ def block_forward(model, li, lw, h, batch, kv):
     q_lens = (batch.cu_q[1:] - batch.cu_q[:-1]).tolist() if batch.is_prefill else [batch.q_per_seq] * batch.seq_lens.shape[0]
     attn = ops.attention_ref(q.to(dt), k_cache, v_cache, batch.block_table, batch.seq_lens, q_lens, 1.0,
                              window=int(cfg.sliding_window or 0) if sliding else 0, bidir=batch.bidir_groups)
-    a = ops.linear(attn.reshape(M, Hq * D).to(dt), w["o"])
+    a = reduced(ops.linear(attn.reshape(M, Hq * D).to(dt), w["o"]))
     h = h + _rms(a, w["post_attention_layernorm"], eps).to(dt)
 
     res = h
     y = _rms(h, w["pre_feedforward_layernorm"], eps).to(dt)
     gu = ops.linear(y, w["gate_up"]).float()
     inter = gu.shape[1] // 2
-    y = ops.linear((F.gelu(gu[:, :inter], approximate="tanh") * gu[:, inter:]).to(dt), w["down"])
+    y = reduced(ops.linear((F.gelu(gu[:, :inter], approximate="tanh") * gu[:, inter:]).to(dt), w["down"]))
     if "router_proj" in w:
         y1 = _rms(y, w["post_feedforward_layernorm_1"], eps)
         r = _rms(res, None, eps) * w["router_scale"] * (cfg.hidden_size ** -0.5)
@@ -180,6 +221,7 @@ def block_forward(model, li, lw, h, batch, kv):
             ie = eu.shape[1] // 2
             out = ops.linear((F.gelu(eu[:, :ie], approximate="tanh") * eu[:, ie:]).to(dt), w["experts_dn"][e]).float()
             y2.index_add_(0, rows, out * top_w[rows, slot, None])
+        y2 = reduced(y2.to(dt)).float() if tp > 1 else y2
         y = (y1 + _rms(y2, w["post_feedforward_layernorm_2"], eps)).to(dt)
     h = res + _rms(y, w["post_feedforward_layernorm"], eps).to(dt)
 

@@ -116,6 +116,20 @@ def main():
         g = torch.Generator().manual_seed(0)
         prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 33)]
 
+    if "g4" in scenario:        # Gemma 4 from a checkpoint directory (EREDU_TEST_CKPT): per-type head geometry, sandwich norms
+        from eredu_b200.formats.checkpoint import open_checkpoint
+
+        src = open_checkpoint(os.environ["EREDU_TEST_CKPT"])
+        cfg = src.cfg
+
+        class _Tensors:
+            __getitem__ = staticmethod(src.get)
+            __contains__ = staticmethod(src.has)
+
+        sd = _Tensors()
+        g = torch.Generator().manual_seed(0)
+        prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 33)]
+
     if "dsv3" in scenario:      # DeepSeek-V3 style: latent attention heads and experts spread over the same ranks
         from test_deepseek import ds_cfg, state_for as ds_state
 

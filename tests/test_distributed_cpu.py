@@ -87,6 +87,40 @@ def test_nemotron_h_over_tensor_and_expert_ranks(tmp_path):
         assert r["tokens"] == want
 
 
+@pytest.mark.parametrize("variant", ["k_eq_v_moe", "shared_kv_ple"])
+def test_gemma4_tensor_parallel(variant, tmp_path, monkeypatch):
+    """Gemma 4 on two ranks: query heads split, one replicated global key / value head, feed-forward and expert rows split,
+    every row-parallel sum taken before its sandwich norm; tokens equal the single-rank run of the same checkpoint."""
+    transformers = pytest.importorskip("transformers")
+    from eredu_b200.api import LoadedModel, ModelLoadOptions
+
+    kw = dict(vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=6, num_attention_heads=4, num_key_value_heads=2,
+              head_dim=16, global_head_dim=32, sliding_window=8, max_position_embeddings=128, pad_token_id=0,
+              layer_types=["sliding_attention", "sliding_attention", "full_attention"] * 2, num_kv_shared_layers=0,
+              hidden_size_per_layer_input=0, attention_k_eq_v=False, enable_moe_block=False)
+    if variant == "k_eq_v_moe":
+        kw.update(attention_k_eq_v=True, num_global_key_value_heads=1, enable_moe_block=True, num_experts=4, top_k_experts=2,
+                  moe_intermediate_size=32)
+    else:
+        kw.update(num_kv_shared_layers=3, hidden_size_per_layer_input=8, vocab_size_per_layer_input=320, use_double_wide_mlp=True)
+    torch.manual_seed(0)
+    m = transformers.Gemma4ForCausalLM(transformers.Gemma4TextConfig(**kw)).eval().float()
+    with torch.no_grad():
+        for _, p in m.named_parameters():
+            if p.dim() == 1:
+                p.add_(torch.randn(p.shape, generator=torch.Generator().manual_seed(1)) * 0.1)
+    ckpt = tmp_path / "ckpt"
+    m.save_pretrained(ckpt, safe_serialization=True)
+    monkeypatch.setenv("EREDU_TEST_CKPT", str(ckpt))
+    res = run_ranks("cpu_g4_tp_nccl", 2, tmp_path)
+    lm = LoadedModel.load(ckpt, ModelLoadOptions(device="cpu", max_batch=4, max_seq_len=128))
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, lm.config.vocab_size, (n,), generator=g).tolist() for n in (9, 33)]
+    want = lm.engine.generate(prompts, SamplingParams(temperature=0.0), 12)
+    for r in res:
+        assert r["tokens"] == want
+
+
 def test_kimi_linear_over_tensor_and_expert_ranks(tmp_path):
     """KDA layers split by heads (convolution channels, decay and gate expansions, recurrent state local to a rank),
     latent attention by head, experts over the same two ranks."""
