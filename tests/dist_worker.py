@@ -251,7 +251,12 @@ def main():
 
         tp_size = 2 if "tp2" in scenario else 1
         par = ParallelContext.from_env(ParallelTopology(pipeline=world // tp_size, tensor=tp_size))
-        model = build_from_tensors(cfg, sd.__getitem__, sd.__contains__, dev, dtype, par)
+        factory = None
+        if cfg.is_moe:
+            from eredu_b200.models.moe import make_moe_factory
+
+            factory = make_moe_factory()
+        model = build_from_tensors(cfg, sd.__getitem__, sd.__contains__, dev, dtype, par, moe_factory=factory)
         if tp_size > 1:
             from eredu_b200.parallel import tp
 

@@ -121,6 +121,31 @@ def test_gemma4_tensor_parallel(variant, tmp_path, monkeypatch):
         assert r["tokens"] == want
 
 
+@pytest.mark.parametrize("family", ["nemo", "qnext", "dsv3", "kimi"])
+def test_hybrid_and_latent_families_under_pipeline_parallelism(family, tmp_path):
+    """Two pipeline stages: every stage keeps the K/V pages and recurrent states of its own layers only, activations
+    travel between the stages, tokens equal the single-rank run."""
+    from eredu_b200.models.moe import make_moe_factory
+
+    if family == "nemo":
+        from test_nemotron_h import nh_cfg as make_cfg, state_for
+    elif family == "qnext":
+        from test_qwen_next import next_cfg as make_cfg, state_for
+    elif family == "dsv3":
+        from test_deepseek import ds_cfg as make_cfg, state_for
+    else:
+        from test_kimi_linear import kimi_cfg as make_cfg, state_for
+    res = run_ranks(f"cpu_{family}_pp", 2, tmp_path)
+    cfg = make_cfg()
+    sd = state_for(cfg)
+    model = build_from_tensors(cfg, sd.__getitem__, sd.__contains__, "cpu", torch.float32, moe_factory=make_moe_factory())
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 33)]
+    want = Engine(model, max_batch=4, max_seq_len=128).generate(prompts, SamplingParams(temperature=0.0), 10)
+    for r in res:
+        assert r["tokens"] == want
+
+
 def test_kimi_linear_over_tensor_and_expert_ranks(tmp_path):
     """KDA layers split by heads (convolution channels, decay and gate expansions, recurrent state local to a rank),
     latent attention by head, experts over the same two ranks."""
