@@ -57,9 +57,22 @@ class ModelInspectionReport:
         return d
 
 
+# Checkpoints of the realtime speech stack: not text-generation models, each has a loader of its own.
+SPEECH_TYPES = {
+    "moshi": ("eredu_b200.models.moshi.MoshiLm.load (temporal + depth transformers; runtime.realtime drives sessions)",
+              ["decoder.model.embed_tokens.weight", "decoder.model.norm.weight", "depth_decoder.input_projections.weight",
+               "depth_decoder.lm_heads.weight"]),
+    "mimi": ("eredu_b200.codec.Mimi.load (streaming audio codec)",
+             ["encoder.layers.0.conv.weight", "decoder.layers.0.conv.weight", "quantizer.semantic_residual_vector_quantizer.input_proj.weight",
+              "quantizer.acoustic_residual_vector_quantizer.output_proj.weight"]),
+}
+
+
 def required_tensors(cfg: ModelConfig) -> list[tuple]:
     """Tensors whose absence makes a SafeTensors directory unloadable, as tuples of accepted spellings: the embedding,
     the final norm and the main input projection of the first layer's operator, under the family's own names."""
+    if cfg.model_type in SPEECH_TYPES:
+        return [(n,) for n in SPEECH_TYPES[cfg.model_type][1]]
     p = "model.layers.0."
     kind = cfg.layer_types[0] if cfg.layer_types else "full_attention"
     if cfg.model_type == "nemotron_h":
@@ -132,7 +145,7 @@ def inspect_artifact(path) -> ModelInspectionReport:
         for alternatives in required_tensors(cfg):
             if not any(sp in keys for name in alternatives for sp in spellings(name)):
                 issues.append(InspectionIssue("missing_tensor", "error", f"required tensor {alternatives[0]} is absent"))
-        if not cfg.tie_word_embeddings and "lm_head.weight" not in keys:
+        if cfg.model_type not in SPEECH_TYPES and not cfg.tie_word_embeddings and "lm_head.weight" not in keys:
             issues.append(InspectionIssue("missing_tensor", "error", "untied model without lm_head.weight"))
     elif path.is_file():
         try:
@@ -160,6 +173,11 @@ def inspect_artifact(path) -> ModelInspectionReport:
     else:
         return ModelInspectionReport(str(path), "unknown", "unknown", None,
                                      issues=[InspectionIssue("not_found", "error", f"{path} does not exist")])
+    if cfg.model_type in SPEECH_TYPES:
+        issues.append(InspectionIssue("speech_model", "error", f"{cfg.model_type} is not a text-generation model: load it with "
+                                      + SPEECH_TYPES[cfg.model_type][0]))
+        rep.issues = issues
+        return rep
     if cfg.model_type not in SUPPORTED_TYPES:
         sev = "error"
         issues.append(InspectionIssue("unsupported_architecture", sev, f"model type {cfg.model_type!r} has no adapter here"

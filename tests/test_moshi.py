@@ -175,3 +175,18 @@ def test_realtime_scheduler_is_fair_and_tracks_deadlines():
         sch.enqueue(b, 1)
     sch.forget_terminal_request(a)
     assert sch.request_status(a) is None and sch.request_status(b) == "finished"
+
+
+def test_inspection_names_the_speech_loaders(tmp_path):
+    from eredu_b200.runtime.plan import inspect_artifact
+
+    tiny(tmp_path)
+    rep = inspect_artifact(tmp_path)
+    assert rep.model_type == "moshi" and not rep.is_loadable and rep.tensor_count > 0
+    assert [i.code for i in rep.issues] == ["speech_model"] and "MoshiLm.load" in rep.issues[0].message
+    (tmp_path / "model.safetensors").unlink()
+    import safetensors.torch
+
+    safetensors.torch.save_file({"decoder.model.norm.weight": torch.zeros(4)}, str(tmp_path / "model.safetensors"))
+    codes = [i.code for i in inspect_artifact(tmp_path).issues]
+    assert codes.count("missing_tensor") == 3 and codes[-1] == "speech_model"
