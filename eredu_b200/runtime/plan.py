@@ -45,6 +45,7 @@ class ModelInspectionReport:
     quantization: Optional[dict] = None
     has_tokenizer: bool = False
     issues: list = field(default_factory=list)
+    text: dict = field(default_factory=dict)        # filled by api.inspection.inspect_text_model: readiness per text facility
 
     @property
     def is_loadable(self) -> bool:

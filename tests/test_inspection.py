@@ -54,3 +54,50 @@ def test_moe_routing_observation():
     assert bool((first.selected_scores <= 1).all()) and first.routed_output.shape == (len(prompt), cfg.hidden_size)
     assert first.shared_output is None and first.reduced_routed_output is None
     assert len(rec.routing) == 2 * (1 + 3)          # two sparse layers x (prefill + three decode steps)
+
+
+def test_text_side_inspection(tmp_path):
+    """Tokenizer, chat template, end-of-sequence ids, streaming markers and tool calling are probed by behaviour."""
+    import dataclasses
+    import json
+
+    import torch
+    from test_text_streaming import make_bundle
+
+    from eredu_b200.api import inspect_text_model
+    from eredu_b200.formats import checkpoint as ck
+    from eredu_b200.models import config as C
+    from eredu_b200.models.llama import random_state
+    from eredu_b200.runtime.plan import inspect_artifact
+
+    b = make_bundle(tmp_path)
+    cfg = dataclasses.replace(C.tiny_llama(), vocab_size=b.vocab_size(), eos_token_id=b.eos_ids[0])
+    ck.save_safetensors_checkpoint(tmp_path, cfg, random_state(cfg, seed=0, std=0.05), torch.float32)
+    rep = inspect_text_model(inspect_artifact(tmp_path))
+    assert rep.text["tokenizer"] == "ready" and rep.text["chat_template"] == "ready" and rep.text["eos"] == "ready"
+    assert rep.text["semantic_streaming"] == "ready" and rep.text["dialect"] == "generic"
+    assert rep.text["native_tools"] == "missing" and "template_ignores_tools" in [i.code for i in rep.issues]   # the template never shows tools
+    assert rep.is_loadable and "text" in rep.to_dict()
+    # a template that renders tools and names the call tags
+    tc = json.loads((tmp_path / "tokenizer_config.json").read_text())
+    tc["chat_template"] = ("{% if tools %}{% for t in tools %}{{ t.function.name }}{% endfor %}<tool_call></tool_call>{% endif %}"
+                           "{% for m in messages %}[{{ m.role }}]{{ m.content }}{% endfor %}[assistant]")
+    (tmp_path / "tokenizer_config.json").write_text(json.dumps(tc))
+    assert inspect_text_model(inspect_artifact(tmp_path)).text["native_tools"] == "ready"
+    # a dialect whose markers this tokenizer splits: streaming (and with it tool calling) is not usable
+    tc["chat_template"] = "{% for m in messages %}<|start|>{{ m.role }}<|message|>{{ m.content }}<|end|>{% endfor %}<|start|>assistant<|channel|>"
+    (tmp_path / "tokenizer_config.json").write_text(json.dumps(tc))
+    rep = inspect_text_model(inspect_artifact(tmp_path))
+    assert rep.text["dialect"] == "harmony" and rep.text["semantic_streaming"] == "invalid" and rep.text["native_tools"] != "ready"
+    assert "unresolved_structural_token" in [i.code for i in rep.issues]
+    # broken and absent templates, absent tokenizer
+    tc["chat_template"] = "{% for m in messages %}{{ m.content | no_such_filter }}{% endfor %}"
+    (tmp_path / "tokenizer_config.json").write_text(json.dumps(tc))
+    rep = inspect_text_model(inspect_artifact(tmp_path))
+    assert rep.text["chat_template"] == "invalid" and rep.text["native_tools"] == "unverified"
+    del tc["chat_template"]
+    (tmp_path / "tokenizer_config.json").write_text(json.dumps(tc))
+    assert inspect_text_model(inspect_artifact(tmp_path)).text["chat_template"] == "missing"
+    (tmp_path / "tokenizer.json").unlink()
+    rep = inspect_text_model(inspect_artifact(tmp_path))
+    assert rep.text["tokenizer"] in ("missing", "invalid") and not rep.is_loadable
