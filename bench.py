@@ -22,7 +22,7 @@ import sys
 import threading
 import time
 
-REFERENCE_UNAVAILABLE = ("reference is a Rust workspace on Apple MLX: `pip install /root/reference` -> 'not installable: "
+REFERENCE_UNAVAILABLE = ("reference is a Rust workspace on Apple MLX: pip install of its source tree -> 'not installable: "
                          "neither setup.py nor pyproject.toml'; no cargo/rustc here and its MLX source archive is missing")
 
 
