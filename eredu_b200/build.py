@@ -45,8 +45,8 @@ def _digest(path: Path, extra: str) -> str:
     h.update(path.read_bytes())
     for inc in sorted((CSRC / "common").glob("*")):
         h.update(inc.read_bytes())
-    if path.suffix == ".cpp":
-        for inc in sorted(path.parent.glob("*.h")) + sorted(path.parent.glob("*.hpp")):
+    for pattern in ("*.h", "*.hpp", "*.cuh"):      # headers that sit next to the source
+        for inc in sorted(path.parent.glob(pattern)):
             h.update(inc.read_bytes())
     return h.hexdigest()[:16]
 

@@ -73,13 +73,20 @@ __global__ void __launch_bounds__(512) allreduce_twoshot_kernel(PeerComm c, long
     o.z = pack_bf16x2(acc[4], acc[5]);
     o.w = pack_bf16x2(acc[6], acc[7]);
     for (int peer = 0; peer < c.size; ++peer) *reinterpret_cast<uint4*>(c.base[peer] + c.out_off + i * 16) = o;
+    if (y != nullptr) reinterpret_cast<uint4*>(y)[i] = o;  // this rank's own slice goes straight to y
   }
-  cta_peer_barrier(c, parity, seq, 1, status);  // every slice has landed everywhere
+  cta_peer_barrier(c, parity, seq, 1, status);  // CTA k of every peer has stored its chunks everywhere
   if (y != nullptr) {
-    const uint4* src = reinterpret_cast<const uint4*>(c.base[c.rank] + c.out_off);
-    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
-         i += static_cast<long long>(gridDim.x) * blockDim.x)
-      reinterpret_cast<uint4*>(y)[i] = ld_cg_u4(src + i);
+    // The barrier orders this CTA only against the same-index CTA of each peer, so the copy walks each peer's
+    // slice with the writer's own partition: CTA k reads exactly the chunks that CTA k of rank `src` stored.
+    const uint4* from = reinterpret_cast<const uint4*>(c.base[c.rank] + c.out_off);
+    for (int src = 0; src < c.size; ++src) {
+      if (src == c.rank) continue;
+      const long long slo = per * src, shi = min(total, slo + per);
+      for (long long i = slo + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < shi;
+           i += static_cast<long long>(gridDim.x) * blockDim.x)
+        reinterpret_cast<uint4*>(y)[i] = ld_cg_u4(from + i);
+    }
   }
   if (threadIdx.x == 0) finish_call(c, seq, gridDim.x);
 }

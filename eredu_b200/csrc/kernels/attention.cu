@@ -559,6 +559,20 @@ using namespace eredu;
 // Bytes of fp32 scratch (part_o, part_ml) a decode launch with `splits` > 1 needs.
 EREDU_TRACE_INSTALLER(attention)
 
+// cudaFuncSetAttribute is a per-device setting: one "configured" flag per device of the process.
+constexpr int kMaxDevices = 64;
+template <typename K>
+static bool configure_once(bool (&done)[kMaxDevices], K kernel, size_t smem) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return false;
+  if (!done[dev]) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+      return false;
+    done[dev] = true;
+  }
+  return true;
+}
+
 extern "C" void eredu_attn_decode_scratch_elems(int batch, int q_per_seq, int n_q_heads, int head_dim, int splits,
                                                 long long* part_o_elems, long long* part_ml_elems) {
   const long long rows = static_cast<long long>(batch) * q_per_seq * n_q_heads;
@@ -585,39 +599,29 @@ extern "C" int eredu_attn_prefill(const void* q, const void* k_cache, const void
   p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
   dim3 grid((max_q_len + 63) / 64, n_q_heads, batch);
+  cudaError_t e;
   if (head_dim == 128) {
-    static bool cfg = false;
-    if (!cfg) {
-      cudaFuncSetAttribute(attn_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           static_cast<int>(prefill_smem<128>()));
-      cfg = true;
-    }
-    launch_pdl(attn_prefill_kernel<128>, grid, dim3(128), prefill_smem<128>(), stream, p);
+    static bool cfg[kMaxDevices] = {};
+    if (!configure_once(cfg, attn_prefill_kernel<128>, prefill_smem<128>())) return -1;
+    e = launch_pdl(attn_prefill_kernel<128>, grid, dim3(128), prefill_smem<128>(), stream, p);
   } else if (head_dim == 64) {
-    static bool cfg = false;
-    if (!cfg) {
-      cudaFuncSetAttribute(attn_prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           static_cast<int>(prefill_smem<64>()));
-      cfg = true;
-    }
-    launch_pdl(attn_prefill_kernel<64>, grid, dim3(128), prefill_smem<64>(), stream, p);
+    static bool cfg[kMaxDevices] = {};
+    if (!configure_once(cfg, attn_prefill_kernel<64>, prefill_smem<64>())) return -1;
+    e = launch_pdl(attn_prefill_kernel<64>, grid, dim3(128), prefill_smem<64>(), stream, p);
   } else {
     return -1;
   }
   eredu_count_launches(1);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(e);
 }
 
 template <int D, int MT>
-static void launch_decode(const AttnParams& p, dim3 grid, cudaStream_t stream) {
-  static bool cfg = false;
-  if (!cfg) {
-    cudaFuncSetAttribute(attn_decode_kernel<D, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         static_cast<int>(decode_smem<D, MT>()));
-    cfg = true;
-  }
-  launch_pdl(attn_decode_kernel<D, MT>, grid, dim3(128), decode_smem<D, MT>(), stream, p);
+static cudaError_t launch_decode(const AttnParams& p, dim3 grid, cudaStream_t stream) {
+  static bool cfg[kMaxDevices] = {};
+  if (!configure_once(cfg, attn_decode_kernel<D, MT>, decode_smem<D, MT>())) return cudaErrorInvalidValue;
+  const cudaError_t e = launch_pdl(attn_decode_kernel<D, MT>, grid, dim3(128), decode_smem<D, MT>(), stream, p);
   eredu_count_launches(1);
+  return e;
 }
 
 // q: [batch * q_per_seq, n_q_heads, D]; every sequence contributes exactly q_per_seq query tokens whose
@@ -647,6 +651,7 @@ extern "C" int eredu_attn_decode(const void* q, const void* k_cache, const void*
   p.splits = splits < 1 ? 1 : (splits > 64 ? 64 : splits);
   p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
+  if (n_kv_heads <= 0 || n_q_heads <= 0 || n_q_heads % n_kv_heads != 0) return -1;
   const int group = n_q_heads / n_kv_heads;
   if (group > 32 || (head_dim != 128 && head_dim != 64)) return -1;
   const int t_per = group > 16 ? 1 : (32 / group < q_per_seq ? 32 / group : q_per_seq);
@@ -655,15 +660,12 @@ extern "C" int eredu_attn_decode(const void* q, const void* k_cache, const void*
     p.t0 = t0;
     p.t_count = (q_per_seq - t0 < t_per) ? q_per_seq - t0 : t_per;
     const int rows = p.t_count * group;
-    if (head_dim == 128) {
-      if (rows <= 16) launch_decode<128, 1>(p, grid, stream);
-      else launch_decode<128, 2>(p, grid, stream);
-    } else {
-      if (rows <= 16) launch_decode<64, 1>(p, grid, stream);
-      else launch_decode<64, 2>(p, grid, stream);
-    }
+    cudaError_t e;
+    if (head_dim == 128) e = rows <= 16 ? launch_decode<128, 1>(p, grid, stream) : launch_decode<128, 2>(p, grid, stream);
+    else e = rows <= 16 ? launch_decode<64, 1>(p, grid, stream) : launch_decode<64, 2>(p, grid, stream);
+    if (e != cudaSuccess) return static_cast<int>(e);
   }
-  return static_cast<int>(cudaGetLastError());
+  return 0;
 }
 
 // ---------------------------------------------------------------------------------------------- no-allocation variant
@@ -685,6 +687,7 @@ extern "C" int eredu_attn_decode_static(const void* q, const void* k_cache, cons
   if (splits < 1) splits = 1;
   if (splits > 64) splits = 64;
   if (head_dim != 64 && head_dim != 128) return -1;
+  if (batch <= 0 || q_per_seq <= 0 || n_kv_heads <= 0 || n_q_heads <= 0 || n_q_heads % n_kv_heads != 0) return -1;
   const long long row_splits = static_cast<long long>(batch) * q_per_seq * n_q_heads * splits;
   if (row_splits > EREDU_NOALLOC_MAX_ROW_SPLITS || static_cast<long long>(batch) * n_kv_heads > EREDU_NOALLOC_MAX_GROUPS)
     return -2;

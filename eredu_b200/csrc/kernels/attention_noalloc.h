@@ -16,7 +16,9 @@
 // The array costs about 4.1 MB of device memory on every GPU that loads the library, until the process exits.
 //
 // First call on a device: the library looks up the device address of its array (cudaGetSymbolAddress, with that
-// device current) and caches it. Make that first call outside any stream capture.
+// device current) and caches it. Make that first call outside any stream capture. A process that drives several
+// GPUs gets one array, one cached address and one kernel configuration per device; call with the device of the
+// pointers current.
 //
 // All calls share the one array and it keeps whatever the previous call left in it. The arrival counters are
 // cleared on the stream at the start of every call; the partials are fully rewritten before they are read.

@@ -13,8 +13,10 @@ from eredu_b200.runtime.expert_cache import ExpertCache, attach_expert_cache
 
 
 def moe_cfg(**kw):
-    return dataclasses.replace(C.tiny_llama(), model_type="qwen3_moe", qk_norm=True, vocab_size=512, num_experts=8,
-                               num_experts_per_tok=2, moe_intermediate_size=64, tie_word_embeddings=False, **kw)
+    fields = dict(model_type="qwen3_moe", qk_norm=True, vocab_size=512, num_experts=8, num_experts_per_tok=2,
+                  moe_intermediate_size=64, tie_word_embeddings=False)
+    fields.update(kw)
+    return dataclasses.replace(C.tiny_llama(), **fields)
 
 
 def _tokens(device, dtype, cfg, slots, eviction="lru"):

@@ -1,8 +1,9 @@
 """The allocation-free decode-attention entry point, called through its exported C symbol.
 
 It serves embedders that must not allocate device memory after start-up (fixed-budget serving loops, plug-ins that
-only receive raw pointers): the split-KV scratch lives in a fixed array inside the library. This test runs last so
-that a failure here cannot hide any other test's result; it also passes when run alone in a fresh process."""
+only receive raw pointers): the split-KV scratch lives in a fixed array inside the library. The file name sorts
+after every other test file, so a failure here cannot hide another test's result under ``-x``; the test also passes
+when run alone in a fresh process."""
 import ctypes
 import math
 
@@ -44,7 +45,9 @@ def test_static_scratch_entry_matches_the_allocating_one_twice_in_a_row():
         code = _call_static(lib, q, kc, vc, got, bt, sl, B, qps, n_q, n_kv, D, splits, scale)
         assert code == 0, code
         torch.cuda.synchronize()
-        rel = float((got.float() - want.float()).norm() / want.float().norm())
+        assert torch.equal(got, want), trial          # same kernel, same splits: the bits must agree
+        ref = ops.attention_ref(q, kc, vc, bt, sl, [qps] * B, scale)
+        rel = float((got.float() - ref.float()).norm() / ref.float().norm())
         assert rel < 1.5e-2, (trial, rel)
     # sizes beyond the built-in scratch are refused with a clear code, nothing is launched
     big = torch.empty(300 * 64, n_q, D, device=dev, dtype=torch.bfloat16)
