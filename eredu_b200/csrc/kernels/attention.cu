@@ -37,7 +37,69 @@ struct AttnParams {
   int splits;
   int window;  // 0 = full attention, else sliding window width
   float scale_log2;  // softmax scale * log2(e)
+  // Decode with the projection output taken as is (qkv != null): the kernel applies the per-head q/k RMSNorm and RoPE
+  // itself and appends the new K/V rows to their pages, so no separate RoPE / append launch precedes it.
+  const __nv_bfloat16* qkv;   // [B * q_per_seq, ld_qkv] = [q heads | k heads | v heads] x D
+  const int* positions;       // [B * q_per_seq] rotary position of every new token
+  const long long* slots;     // [B * q_per_seq] page * 16 + offset of every new token, < 0 = do not store
+  const float* inv_freq;      // [rot / 2]
+  const float* q_norm_w;      // optional [D]
+  const float* k_norm_w;      // optional [D]
+  int ld_qkv, rot, interleaved;
+  float attn_factor, norm_eps, norm_w_off;
 };
+
+// One head row of the projection output: optional RMSNorm over D (result rounded to bf16 like a module boundary),
+// rotation of the first `rot` dims by the token's position. Executed by one warp; lane l owns the pairs l, l + 32, ...
+// `store(i0, a, i1, b)` receives the finished element pairs.
+template <int D, typename Store>
+__device__ __forceinline__ void rope_head_row(const AttnParams& p, const __nv_bfloat16* src, const float* nw, int pos,
+                                              int lane, Store store) {
+  constexpr int PER = D / 64;  // pairs per lane
+  const int rh = p.rot >> 1;
+  float a[PER], b[PER];
+  int i0[PER], i1[PER];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int i = lane + 32 * j;
+    if (i < rh) {
+      i0[j] = p.interleaved ? 2 * i : i;
+      i1[j] = p.interleaved ? 2 * i + 1 : i + rh;
+    } else {  // pass-through tail beyond the rotary dims
+      i0[j] = p.rot + 2 * (i - rh);
+      i1[j] = i0[j] + 1;
+    }
+    a[j] = __bfloat162float(src[i0[j]]);
+    b[j] = __bfloat162float(src[i1[j]]);
+    ss += a[j] * a[j] + b[j] * b[j];
+  }
+  if (nw != nullptr) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float inv = rsqrtf(ss / static_cast<float>(D) + p.norm_eps);
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      a[j] = __bfloat162float(__float2bfloat16(a[j] * inv * (nw[i0[j]] + p.norm_w_off)));
+      b[j] = __bfloat162float(__float2bfloat16(b[j] * inv * (nw[i1[j]] + p.norm_w_off)));
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int i = lane + 32 * j;
+    if (i < rh) {
+      float sn, cs;
+      sincosf(static_cast<float>(pos) * p.inv_freq[i], &sn, &cs);
+      sn *= p.attn_factor;
+      cs *= p.attn_factor;
+      const float ra = a[j] * cs - b[j] * sn;
+      const float rb = b[j] * cs + a[j] * sn;
+      a[j] = ra;
+      b[j] = rb;
+    }
+    store(i0[j], a[j], i1[j], b[j]);
+  }
+}
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, int src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem)), "l"(gmem), "r"(src_bytes)
@@ -299,13 +361,18 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnParams p) {
   const int page0 = split * pps;
   const int page1 = min(npages, page0 + pps);
 
-  for (int i = threadIdx.x; i < ROWS * CH; i += 128) {
-    const int r = i / CH, c = i % CH;
-    const bool ok = r < rows;
-    const int t = p.t0 + (ok ? r / group : 0), hg = ok ? r % group : 0;
-    const __nv_bfloat16* src =
-        p.q + (static_cast<size_t>(b * p.q_per_seq + t) * p.n_q_heads + kvh * group + hg) * D + c * 8;
-    cp_async16(q_s + swz<D>(r, c), src, ok ? 16 : 0);
+  const bool fused = p.qkv != nullptr;
+  // Pages at or after the first new token's page must not be fetched before this CTA has appended the new rows.
+  const int first_new_page = (fused && p.t0 == 0) ? (kv_len - p.q_per_seq) / kPage : 0x7fffffff;
+  if (!fused) {
+    for (int i = threadIdx.x; i < ROWS * CH; i += 128) {
+      const int r = i / CH, c = i % CH;
+      const bool ok = r < rows;
+      const int t = p.t0 + (ok ? r / group : 0), hg = ok ? r % group : 0;
+      const __nv_bfloat16* src =
+          p.q + (static_cast<size_t>(b * p.q_per_seq + t) * p.n_q_heads + kvh * group + hg) * D + c * 8;
+      cp_async16(q_s + swz<D>(r, c), src, ok ? 16 : 0);
+    }
   }
   cp_async_commit();
 
@@ -336,11 +403,55 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnParams p) {
   }
 
   const int first = page0 + warp;
-  load_page(first, 0);
+  const bool early0 = first < first_new_page, early1 = first + 4 < first_new_page;
+  if (early0) load_page(first, 0);
   cp_async_commit();
-  load_page(first + 4, 1);
+  if (early1) load_page(first + 4, 1);
   cp_async_commit();
-  cp_async_wait<2>();  // the Q tile
+  if (fused) {
+    // ---- q rows: norm + RoPE straight into the swizzled tile (rows beyond `rows` are zero)
+    for (int r = warp; r < ROWS; r += 4) {
+      auto put = [&](int i0, float a, int i1, float bb) {
+        *reinterpret_cast<__nv_bfloat16*>(q_s + swz<D>(r, i0 >> 3) + (i0 & 7) * 2) = __float2bfloat16(a);
+        *reinterpret_cast<__nv_bfloat16*>(q_s + swz<D>(r, i1 >> 3) + (i1 & 7) * 2) = __float2bfloat16(bb);
+      };
+      if (r < rows) {
+        const int t = p.t0 + r / group, hg = r % group;
+        const size_t m = static_cast<size_t>(b) * p.q_per_seq + t;
+        rope_head_row<D>(p, p.qkv + m * p.ld_qkv + static_cast<size_t>(kvh * group + hg) * D, p.q_norm_w, p.positions[m],
+                         lane, put);
+      } else {
+        for (int i = lane; i < D / 2; i += 32) put(2 * i, 0.f, 2 * i + 1, 0.f);
+      }
+    }
+    // ---- new K / V rows whose page lies in this CTA's range: norm + RoPE on K, both appended to the cache
+    if (p.t0 == 0) {
+      for (int t = warp; t < p.q_per_seq; t += 4) {
+        const int pg = (kv_len - p.q_per_seq + t) / kPage;
+        const size_t m = static_cast<size_t>(b) * p.q_per_seq + t;
+        const long long slot = p.slots[m];
+        if (pg < page0 || pg >= page1 || slot < 0) continue;  // warp-uniform
+        const size_t dst = ((static_cast<size_t>(slot >> 4) * p.n_kv_heads + kvh) * kPage + static_cast<size_t>(slot & 15)) * D;
+        __nv_bfloat16* kd = const_cast<__nv_bfloat16*>(p.k_cache) + dst;
+        __nv_bfloat16* vd = const_cast<__nv_bfloat16*>(p.v_cache) + dst;
+        const __nv_bfloat16* krow = p.qkv + m * p.ld_qkv + static_cast<size_t>(p.n_q_heads + kvh) * D;
+        const __nv_bfloat16* vrow = p.qkv + m * p.ld_qkv + static_cast<size_t>(p.n_q_heads + p.n_kv_heads + kvh) * D;
+        rope_head_row<D>(p, krow, p.k_norm_w, p.positions[m], lane, [&](int i0, float a, int i1, float bb) {
+          kd[i0] = __float2bfloat16(a);
+          kd[i1] = __float2bfloat16(bb);
+        });
+        for (int i = lane; i < D / 2; i += 32)
+          reinterpret_cast<uint32_t*>(vd)[i] = reinterpret_cast<const uint32_t*>(vrow)[i];
+      }
+      __threadfence();  // the appended rows are read back below through cp.async (L2)
+    }
+    __syncthreads();
+  }
+  if (!early0) load_page(first, 0);
+  cp_async_commit();
+  if (!early1) load_page(first + 4, 1);
+  cp_async_commit();
+  cp_async_wait<4>();  // the Q tile (the oldest group)
   __syncthreads();
 
   const uint32_t q_base = smem_u32(q_s);
@@ -628,6 +739,25 @@ static cudaError_t launch_decode(const AttnParams& p, dim3 grid, cudaStream_t st
 // positions are the last q_per_seq positions of its kv (causal among themselves). part_o / part_ml are
 // caller-provided fp32 scratch (see eredu_attn_decode_scratch_elems) and `counters` a zeroed int32
 // [batch * n_kv_heads] array (left zeroed again on return); all unused when splits == 1.
+static int launch_decode_all(AttnParams p, int batch, int q_per_seq, int n_q_heads, int n_kv_heads, int head_dim,
+                             cudaStream_t stream) {
+  if (n_kv_heads <= 0 || n_q_heads <= 0 || n_q_heads % n_kv_heads != 0) return -1;
+  const int group = n_q_heads / n_kv_heads;
+  if (group > 32 || (head_dim != 128 && head_dim != 64)) return -1;
+  const int t_per = group > 16 ? 1 : (32 / group < q_per_seq ? 32 / group : q_per_seq);
+  dim3 grid(p.splits, n_kv_heads, batch);
+  for (int t0 = 0; t0 < q_per_seq; t0 += t_per) {
+    p.t0 = t0;
+    p.t_count = (q_per_seq - t0 < t_per) ? q_per_seq - t0 : t_per;
+    const int rows = p.t_count * group;
+    cudaError_t e;
+    if (head_dim == 128) e = rows <= 16 ? launch_decode<128, 1>(p, grid, stream) : launch_decode<128, 2>(p, grid, stream);
+    else e = rows <= 16 ? launch_decode<64, 1>(p, grid, stream) : launch_decode<64, 2>(p, grid, stream);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  return 0;
+}
+
 extern "C" int eredu_attn_decode(const void* q, const void* k_cache, const void* v_cache, void* out,
                                  const int* block_table, const int* seq_lens, const float* sinks, float* part_o,
                                  float* part_ml, int* counters, int batch, int q_per_seq, int max_pages, int n_q_heads,
@@ -651,21 +781,53 @@ extern "C" int eredu_attn_decode(const void* q, const void* k_cache, const void*
   p.splits = splits < 1 ? 1 : (splits > 64 ? 64 : splits);
   p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
-  if (n_kv_heads <= 0 || n_q_heads <= 0 || n_q_heads % n_kv_heads != 0) return -1;
-  const int group = n_q_heads / n_kv_heads;
-  if (group > 32 || (head_dim != 128 && head_dim != 64)) return -1;
-  const int t_per = group > 16 ? 1 : (32 / group < q_per_seq ? 32 / group : q_per_seq);
-  dim3 grid(p.splits, n_kv_heads, batch);
-  for (int t0 = 0; t0 < q_per_seq; t0 += t_per) {
-    p.t0 = t0;
-    p.t_count = (q_per_seq - t0 < t_per) ? q_per_seq - t0 : t_per;
-    const int rows = p.t_count * group;
-    cudaError_t e;
-    if (head_dim == 128) e = rows <= 16 ? launch_decode<128, 1>(p, grid, stream) : launch_decode<128, 2>(p, grid, stream);
-    else e = rows <= 16 ? launch_decode<64, 1>(p, grid, stream) : launch_decode<64, 2>(p, grid, stream);
-    if (e != cudaSuccess) return static_cast<int>(e);
-  }
-  return 0;
+  return launch_decode_all(p, batch, q_per_seq, n_q_heads, n_kv_heads, head_dim, stream);
+}
+
+// Decode attention that starts from the projection output: qkv [batch * q_per_seq, ld_qkv] = [q heads | k heads |
+// v heads] x D as the qkv GEMM wrote it. The kernel normalises (optional per-head RMSNorm weights) and rotates q and
+// the new k rows by `positions`, appends the new k / v rows at `slots` (page * 16 + offset; negative: not stored)
+// and attends - the RoPE + KV-append launch of the unfused path disappears. Every new row is appended by the one CTA
+// whose page range contains it, before that CTA fetches the page. Other arguments as eredu_attn_decode.
+extern "C" int eredu_attn_decode_rope(const void* qkv, int ld_qkv, void* k_cache, void* v_cache, void* out,
+                                      const int* block_table, const int* seq_lens, const float* sinks, float* part_o,
+                                      float* part_ml, int* counters, const int* positions, const long long* slots,
+                                      const float* inv_freq, const float* q_norm_w, const float* k_norm_w, int batch,
+                                      int q_per_seq, int max_pages, int n_q_heads, int n_kv_heads, int head_dim, int rot,
+                                      int interleaved, int splits, int window, float scale, float attn_factor,
+                                      float norm_eps, float norm_w_off, cudaStream_t stream) {
+  if (qkv == nullptr || positions == nullptr || slots == nullptr || inv_freq == nullptr) return -1;
+  if (rot <= 0 || rot > head_dim || rot % 2 != 0 || ld_qkv % 2 != 0) return -1;
+  AttnParams p = {};
+  p.qkv = static_cast<const __nv_bfloat16*>(qkv);
+  p.ld_qkv = ld_qkv;
+  p.k_cache = static_cast<const __nv_bfloat16*>(k_cache);
+  p.v_cache = static_cast<const __nv_bfloat16*>(v_cache);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.block_table = block_table;
+  p.seq_lens = seq_lens;
+  p.sinks = sinks;
+  p.part_o = part_o;
+  p.part_ml = part_ml;
+  p.counters = counters;
+  p.positions = positions;
+  p.slots = slots;
+  p.inv_freq = inv_freq;
+  p.q_norm_w = q_norm_w;
+  p.k_norm_w = k_norm_w;
+  p.rot = rot;
+  p.interleaved = interleaved;
+  p.attn_factor = attn_factor;
+  p.norm_eps = norm_eps;
+  p.norm_w_off = norm_w_off;
+  p.max_pages = max_pages;
+  p.n_q_heads = n_q_heads;
+  p.n_kv_heads = n_kv_heads;
+  p.q_per_seq = q_per_seq;
+  p.splits = splits < 1 ? 1 : (splits > 64 ? 64 : splits);
+  p.window = window;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  return launch_decode_all(p, batch, q_per_seq, n_q_heads, n_kv_heads, head_dim, stream);
 }
 
 // ---------------------------------------------------------------------------------------------- no-allocation variant

@@ -246,11 +246,21 @@ class CausalLM:
             gate, qkv = qkv[:, width:], qkv[:, :width]
         k_cache, v_cache = kv.layer(li)
         rope_pos = batch.positions if batch.rope_positions is None else batch.rope_positions
+        window = cfg.layer_window(li)
+        if not batch.is_prefill and rope_pos.dim() == 1 and qkv.is_cuda and cfg.head_dim in ops.KERNEL_HEAD_DIMS:
+            # decode / verify steps: q/k norm, RoPE and the KV append happen inside the attention kernel
+            attn = ops.attention_decode_rope(qkv, k_cache, v_cache, batch.block_table, batch.seq_lens, batch.q_per_seq,
+                                             self.scale, rope_pos, batch.slots, self.inv_freq, self.n_q_local,
+                                             self.n_kv_local, cfg.head_dim, rot=cfg.rotary_dim,
+                                             interleaved=cfg.rope_traditional, attn_factor=self.attn_factor,
+                                             q_norm_w=lw.q_norm, k_norm_w=lw.k_norm, norm_eps=cfg.rms_norm_eps,
+                                             norm_w_off=cfg.norm_weight_offset, splits=batch.splits, window=window,
+                                             sinks=lw.sinks, scratch=batch.scratch)
+            return self._attn_out(lw, attn, gate, h, next_folded)
         q = ops.rope_kv(qkv, rope_pos, batch.slots, self.inv_freq, k_cache, v_cache, self.n_q_local,
                         self.n_kv_local, cfg.head_dim, rot=cfg.rotary_dim, interleaved=cfg.rope_traditional,
                         attn_factor=self.attn_factor, q_norm_w=lw.q_norm, k_norm_w=lw.k_norm, norm_eps=cfg.rms_norm_eps,
                         norm_w_off=cfg.norm_weight_offset, mrope_section=(cfg.rope_scaling or {}).get("mrope_section"))
-        window = cfg.layer_window(li)
         if batch.is_prefill:
             attn = ops.attention_prefill(q, k_cache, v_cache, batch.block_table, batch.seq_lens, batch.cu_q,
                                          batch.max_q_len, self.scale, window=window, sinks=lw.sinks)
@@ -258,6 +268,10 @@ class CausalLM:
             attn = ops.attention_decode(q, k_cache, v_cache, batch.block_table, batch.seq_lens, batch.q_per_seq,
                                         self.scale, splits=batch.splits, window=window, sinks=lw.sinks,
                                         scratch=batch.scratch)
+        return self._attn_out(lw, attn, gate, h, next_folded)
+
+    def _attn_out(self, lw: LayerWeights, attn, gate, h, next_folded):
+        """Output projection of an attention block (optional sigmoid gate first), then the feed-forward half."""
         attn = attn.view(attn.shape[0], -1)
         if gate is not None:
             attn = (attn.float() * torch.sigmoid(gate.float())).to(attn.dtype)

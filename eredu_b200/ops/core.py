@@ -297,6 +297,35 @@ def attention_decode(q, k_cache, v_cache, block_table, seq_lens, q_per_seq, scal
     return out
 
 
+def attention_decode_rope(qkv, k_cache, v_cache, block_table, seq_lens, q_per_seq, scale, positions, slots, inv_freq,
+                          n_q, n_kv, head_dim, rot=None, interleaved=False, attn_factor=1.0, q_norm_w=None, k_norm_w=None,
+                          norm_eps=1e-6, norm_w_off=0.0, splits=1, window=0, sinks=None, scratch=None):
+    """Decode attention straight from the qkv projection output [B * q_per_seq, >= (n_q + 2 n_kv) * D]: per-head
+    q/k norm, RoPE and the KV append run inside the attention kernel (one launch instead of two). CPU tensors and
+    head sizes without a kernel compose the two reference operators."""
+    if not qkv.is_cuda or head_dim not in KERNEL_HEAD_DIMS or positions.dim() != 1:
+        q = rope_kv(qkv, positions, slots, inv_freq, k_cache, v_cache, n_q, n_kv, head_dim, rot, interleaved, attn_factor,
+                    q_norm_w, k_norm_w, norm_eps, norm_w_off)
+        return attention_decode(q, k_cache, v_cache, block_table, seq_lens, q_per_seq, scale, splits, window, sinks, scratch)
+    assert qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1
+    assert positions.dtype == torch.int32 and slots.dtype == torch.int64 and inv_freq.dtype == torch.float32
+    B = seq_lens.shape[0]
+    out = torch.empty((qkv.shape[0], n_q, head_dim), dtype=qkv.dtype, device=qkv.device)
+    part_o = part_ml = counters = None
+    if splits > 1:
+        if scratch is None:
+            scratch = decode_scratch(B, q_per_seq, n_q, head_dim, splits, qkv.device)
+        part_o, part_ml, counters = scratch
+        assert part_o.numel() >= B * q_per_seq * n_q * splits * head_dim and counters.numel() >= B * n_kv
+    code = lib().eredu_attn_decode_rope(ptr(qkv), qkv.stride(0), ptr(k_cache), ptr(v_cache), ptr(out), ptr(block_table),
+                                        ptr(seq_lens), ptr(sinks), ptr(part_o), ptr(part_ml), ptr(counters), ptr(positions),
+                                        ptr(slots), ptr(inv_freq), ptr(q_norm_w), ptr(k_norm_w), B, q_per_seq,
+                                        block_table.stride(0), n_q, n_kv, head_dim, rot or head_dim, 1 if interleaved else 0,
+                                        splits, window, scale, attn_factor, norm_eps, norm_w_off, stream_ptr(qkv.device))
+    check(code, "eredu_attn_decode_rope")
+    return out
+
+
 def decode_scratch(batch, q_per_seq, n_q, head_dim, splits, device):
     rows = batch * q_per_seq * n_q
     return (torch.empty(rows * splits * head_dim, dtype=torch.float32, device=device),

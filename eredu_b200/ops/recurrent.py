@@ -60,9 +60,11 @@ def gated_delta_scan(q, k, v, log_decay, beta, state: Optional[torch.Tensor] = N
         raise ValueError("gated-delta beta / log decay shapes do not match the query")
     S = torch.zeros((B, H, Dk, Dv), dtype=torch.float32, device=q.device) if state is None else state.float().contiguous().clone()
     out = torch.empty((B, T, H, Dv), dtype=q.dtype, device=q.device)
+    # every operand is bound to a name until the launch is queued: a temporary made by ``.contiguous()`` / ``.float()``
+    # would go back to the caching allocator at once and the next temporary could land on the same bytes
     g = log_decay.float().contiguous()
-    code = lib().eredu_gated_delta_scan(ptr(q.contiguous()), ptr(k.contiguous()), ptr(v.contiguous()), ptr(g),
-                                        ptr(beta.float().contiguous()), ptr(S), ptr(out), B, T, H, Dk, Dv,
+    qc, kc, vc, bc = q.contiguous(), k.to(q.dtype).contiguous(), v.to(q.dtype).contiguous(), beta.float().contiguous()
+    code = lib().eredu_gated_delta_scan(ptr(qc), ptr(kc), ptr(vc), ptr(g), ptr(bc), ptr(S), ptr(out), B, T, H, Dk, Dv,
                                         1 if g.dim() == 4 else 0, stream_ptr(q.device))
     check(code, "eredu_gated_delta_scan")
     return S, out
@@ -106,8 +108,10 @@ def mamba2_scan(x, B, C, dt, A, D, state: Optional[torch.Tensor] = None):
     if tuple(S.shape) != (Bt, H, P_, N):
         raise ValueError(f"Mamba-2 state shape {tuple(S.shape)} must equal {(Bt, H, P_, N)}")
     out = torch.empty((Bt, T, H, P_), dtype=x.dtype, device=x.device)
-    code = lib().eredu_mamba2_scan(ptr(x.contiguous()), ptr(B.to(torch.bfloat16).contiguous()), ptr(C.to(torch.bfloat16).contiguous()),
-                                   ptr(dt.float().contiguous()), ptr(A.float().contiguous()), ptr(D.float().contiguous()), ptr(S),
-                                   ptr(out), Bt, T, H, G, P_, N, stream_ptr(x.device))
+    # operands stay bound to names until the launch is queued (see gated_delta_scan)
+    xc, Bc, Cc = x.contiguous(), B.to(torch.bfloat16).contiguous(), C.to(torch.bfloat16).contiguous()
+    dtc, Ac, Dc = dt.float().contiguous(), A.float().contiguous(), D.float().contiguous()
+    code = lib().eredu_mamba2_scan(ptr(xc), ptr(Bc), ptr(Cc), ptr(dtc), ptr(Ac), ptr(Dc), ptr(S), ptr(out), Bt, T, H, G,
+                                   P_, N, stream_ptr(x.device))
     check(code, "eredu_mamba2_scan")
     return S, out

@@ -312,3 +312,46 @@ def test_spec_verify(temp):
         else:
             resid_ok = p_t3[b, acc].cpu()[int(out[b, 1])] > 0
             assert resid_ok
+
+
+@pytest.mark.parametrize("D,n_q,n_kv,qps,qknorm,interleaved,rot,splits", [
+    (128, 32, 8, 1, False, False, None, 1), (128, 32, 8, 1, False, False, None, 5), (128, 4, 1, 1, False, False, None, 4),
+    (128, 32, 8, 5, True, False, None, 3), (64, 4, 2, 1, True, True, None, 2), (128, 8, 2, 3, False, False, 64, 2),
+    (128, 64, 8, 3, False, False, None, 2)])
+def test_decode_attention_with_fused_rope_and_append(D, n_q, n_kv, qps, qknorm, interleaved, rot, splits):
+    """The decode kernel that takes the qkv projection output (q/k norm, RoPE and the KV append inside the kernel)
+    against the separate RoPE + append kernel followed by fp32 reference attention; the caches must end up equal."""
+    torch.manual_seed(D + n_q + qps + splits)
+    kv_lens = [517, 33, 2050, 16, 5, 700][: 6 if qps == 1 else 5]
+    kv_lens = [max(l, qps) for l in kv_lens]
+    B = len(kv_lens)
+    max_pages = max((l + 15) // 16 for l in kv_lens) + 1
+    n_pages = B * max_pages + 1
+    kc = torch.randn(n_pages, n_kv, 16, D, device=DEV).bfloat16()
+    vc = torch.randn(n_pages, n_kv, 16, D, device=DEV).bfloat16()
+    bt = (torch.randperm(n_pages - 1, device=DEV)[: B * max_pages].int() + 1).view(B, max_pages).contiguous()
+    sl = torch.tensor(kv_lens, device=DEV, dtype=torch.int32)
+    width = (n_q + 2 * n_kv) * D
+    qkv = torch.randn(B * qps, width + 64, device=DEV).bfloat16()[:, :width]       # row stride != width
+    pos = torch.cat([torch.arange(l - qps, l) for l in kv_lens]).to(DEV, torch.int32)
+    slots = torch.cat([bt[b, (torch.arange(l - qps, l) // 16).to(DEV)].long() * 16 + (torch.arange(l - qps, l) % 16).to(DEV)
+                       for b, l in enumerate(kv_lens)])
+    if B > 2 and qps == 1:
+        slots[2] = -1       # an inactive row: nothing is stored for it
+    inv = (1.0 / (10000.0 ** (torch.arange(0, (rot or D) // 2, device=DEV).float() / ((rot or D) // 2)))).contiguous()
+    qw = (torch.rand(D, device=DEV) + 0.5) if qknorm else None
+    kw = (torch.rand(D, device=DEV) + 0.5) if qknorm else None
+    scale = 1 / math.sqrt(D)
+    kc_ref, vc_ref = kc.clone(), vc.clone()
+    q_ref = ops.rope_kv(qkv, pos, slots, inv, kc_ref, vc_ref, n_q, n_kv, D, rot=rot, interleaved=interleaved,
+                        attn_factor=1.1, q_norm_w=qw, k_norm_w=kw, norm_eps=1e-6)
+    want = ops.attention_ref(q_ref, kc_ref, vc_ref, bt, sl, [qps] * B, scale)
+    got = ops.attention_decode_rope(qkv, kc, vc, bt, sl, qps, scale, pos, slots, inv, n_q, n_kv, D, rot=rot,
+                                    interleaved=interleaved, attn_factor=1.1, q_norm_w=qw, k_norm_w=kw, norm_eps=1e-6,
+                                    splits=splits)
+    torch.cuda.synchronize()
+    # same arithmetic in two kernels: at most a last-place bf16 difference where the compiler contracted differently
+    assert torch.equal(vc, vc_ref) and torch.allclose(kc.float(), kc_ref.float(), atol=0.04, rtol=0.01)
+    keep = (slots >= 0).view(B, qps).all(1).repeat_interleave(qps)
+    rel = float((got[keep].float() - want[keep].float()).norm() / want[keep].float().norm())
+    assert rel < 1.5e-2, rel

@@ -148,13 +148,18 @@ def test_lfm2_engine_on_gpu_matches_cpu_oracle():
         assert torch.nn.functional.cosine_similarity(lg.float().cpu(), ref, dim=0) > 0.995
     for s in seqs:
         eng.release(s)
-    # CUDA-graph decode agrees with the eager CPU engine on the same weights (greedy, short horizon)
+    # decode steps against the full-recompute oracle, teacher-forced (greedy tokens of a random model flip on bf16
+    # rounding alone, so the logits are compared, not the token strings): prefill n-1 tokens, decode the n-th
+    from dist_worker import probe_logits
+
+    for p in prompts:
+        ref = forward_logits(cfg, sd, p)[-1]
+        dec = torch.tensor(probe_logits(eng, model, p))
+        assert torch.nn.functional.cosine_similarity(dec, ref, dim=0) > 0.995
+    # the CUDA-graph decode loop and the eager one produce the same tokens
     outs = eng.generate(prompts, SamplingParams(temperature=0.0), max_new_tokens=6)
-    cpu = Engine(build_from_tensors(cfg, lambda n: sd[n].bfloat16().float(), sd.__contains__, "cpu", torch.float32),
-                 max_batch=4, max_seq_len=128)
-    ref = cpu.generate(prompts, SamplingParams(temperature=0.0), max_new_tokens=6)
-    agree = sum(a == b for o, r in zip(outs, ref) for a, b in zip(o, r))
-    assert agree >= 14, (outs, ref)
+    eager = Engine(model, max_batch=4, max_seq_len=128, use_cuda_graph=False)
+    assert eager.generate(prompts, SamplingParams(temperature=0.0), max_new_tokens=6) == outs
 
 
 def test_lfm2_moe_matches_oracle(tmp_path):
