@@ -232,15 +232,27 @@ extern "C" void* eredu_comm_create(void** bases, int rank, int size, long long s
   c->data_off = flag_bytes;
   c->slot_bytes = (slot_bytes + 255) / 256 * 256;
   c->out_off = c->data_off + 2LL * kMaxRanks * c->slot_bytes;
+  c->lam_bytes = (c->slot_bytes / 2 + 255) / 256 * 256;
+  c->lam_off = c->out_off + (out_bytes + 255) / 256 * 256;
   c->seq = local_words;
   c->done = local_words + 1;
-  (void)out_bytes;
   return c;
 }
 extern "C" void eredu_comm_destroy(void* c) { delete static_cast<PeerComm*>(c); }
 extern "C" long long eredu_comm_buffer_bytes(long long slot_bytes, long long out_bytes) {
   const long long sb = (slot_bytes + 255) / 256 * 256;
-  return 2LL * kMaxRanks * kMaxFlags * 4 + 2LL * kMaxRanks * sb + (out_bytes + 255) / 256 * 256;
+  const long long lam = (sb / 2 + 255) / 256 * 256;
+  return 2LL * kMaxRanks * kMaxFlags * 4 + 2LL * kMaxRanks * sb + (out_bytes + 255) / 256 * 256 + 2LL * kMaxRanks * lam;
+}
+// Fill the tag-free region of a freshly allocated symmetric buffer with its "empty" pattern. Call on the owner's
+// buffer before any peer maps it.
+extern "C" int eredu_comm_init_buffer(void* base, long long slot_bytes, long long out_bytes) {
+  const long long sb = (slot_bytes + 255) / 256 * 256;
+  const long long lam = (sb / 2 + 255) / 256 * 256;
+  const long long off = 2LL * kMaxRanks * kMaxFlags * 4 + 2LL * kMaxRanks * sb + (out_bytes + 255) / 256 * 256;
+  cudaError_t e = cudaMemset(static_cast<uint8_t*>(base) + off, 0xFF, static_cast<size_t>(2LL * kMaxRanks * lam));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  return static_cast<int>(cudaDeviceSynchronize());
 }
 extern "C" long long eredu_comm_out_offset(const void* c) { return static_cast<const PeerComm*>(c)->out_off; }
 extern "C" long long eredu_comm_data_offset(const void* c, int parity, int src) {

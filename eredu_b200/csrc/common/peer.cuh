@@ -10,6 +10,7 @@
 //   flags : [2 parity][kMaxRanks src][kMaxFlags] u32   sequence numbers
 //   data  : [2 parity][kMaxRanks src][slot_bytes]      staging area written by `src`
 //   out   : [out_bytes]                                gather target (final layout)
+//   lam   : [2 parity][kMaxRanks src][lam_bytes]       one-shot all-reduce words without tags (see below)
 // plus two local words (not touched by peers): seq (calls completed) and done (CTA exit counter).
 #pragma once
 #include <stdint.h>
@@ -29,6 +30,8 @@ struct PeerComm {
   long long data_off;
   long long out_off;
   long long slot_bytes;  // bytes per (parity, src) staging slot
+  long long lam_off;     // sentinel-initialised region of the tag-free one-shot all-reduce
+  long long lam_bytes;   // bytes per (parity, src) slot of that region
   unsigned int* seq;     // local
   unsigned int* done;    // local
 };
@@ -63,6 +66,18 @@ __device__ __forceinline__ unsigned int* peer_flag(const PeerComm& c, int peer, 
 __device__ __forceinline__ uint8_t* peer_slot(const PeerComm& c, int peer, int parity, int src) {
   return c.base[peer] + c.data_off + (static_cast<size_t>(parity) * kMaxRanks + src) * c.slot_bytes;
 }
+
+// Tag-free one-shot words ("Lamport" style): the region starts as all-ones words; a writer never sends that pattern
+// (a bf16 pair of two all-ones NaNs is replaced by canonical NaNs), so a 4-byte word is valid as soon as it differs
+// from the pattern - the whole word is payload. The single reader of a word writes the pattern back right after it
+// has read the value. The slot of that parity is written again two calls later; a peer can only be two calls ahead
+// after it has consumed this rank's words of the call in between, which this rank sends from a later kernel, so the
+// write-back always lands first.
+constexpr uint32_t kLamportEmpty = 0xFFFFFFFFu;
+__device__ __forceinline__ uint8_t* lamport_slot(const PeerComm& c, int peer, int parity, int src) {
+  return c.base[peer] + c.lam_off + (static_cast<size_t>(parity) * kMaxRanks + src) * c.lam_bytes;
+}
+__device__ __forceinline__ uint32_t lamport_payload(uint32_t v) { return v == kLamportEmpty ? 0x7FFF7FFFu : v; }
 
 // Bounded wait until the local flag written by `src` reaches `want`. Sequence numbers only grow.
 __device__ __forceinline__ bool wait_flag(const PeerComm& c, int parity, int src, int idx, unsigned int want, int* status) {

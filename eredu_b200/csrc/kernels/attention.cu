@@ -426,6 +426,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnParams p) {
     }
     // ---- new K / V rows whose page lies in this CTA's range: norm + RoPE on K, both appended to the cache
     if (p.t0 == 0) {
+      bool appended = false;
       for (int t = warp; t < p.q_per_seq; t += 4) {
         const int pg = (kv_len - p.q_per_seq + t) / kPage;
         const size_t m = static_cast<size_t>(b) * p.q_per_seq + t;
@@ -442,8 +443,11 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnParams p) {
         });
         for (int i = lane; i < D / 2; i += 32)
           reinterpret_cast<uint32_t*>(vd)[i] = reinterpret_cast<const uint32_t*>(vrow)[i];
+        appended = true;
       }
-      __threadfence();  // the appended rows are read back below through cp.async (L2)
+      // the appended rows are read back below through cp.async (L2); CTAs that appended nothing skip the fence, which
+      // would otherwise also wait for their page fetches already in flight
+      if (appended) __threadfence();
     }
     __syncthreads();
   }

@@ -15,6 +15,7 @@ GEMM + all-reduce path of :mod:`eredu_b200.parallel.tp`.
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass, field
 from typing import Callable, Optional
 
@@ -23,6 +24,10 @@ import torch
 from .. import ops
 from .config import ModelConfig
 from .rope import rope_tables
+
+
+# EREDU_FUSED_ROPE=0 keeps the separate RoPE + KV-append launch in front of decode attention (A/B measurements).
+FUSED_DECODE_ROPE = os.environ.get("EREDU_FUSED_ROPE", "1") != "0"
 
 
 @dataclass
@@ -247,7 +252,8 @@ class CausalLM:
         k_cache, v_cache = kv.layer(li)
         rope_pos = batch.positions if batch.rope_positions is None else batch.rope_positions
         window = cfg.layer_window(li)
-        if not batch.is_prefill and rope_pos.dim() == 1 and qkv.is_cuda and cfg.head_dim in ops.KERNEL_HEAD_DIMS:
+        if (not batch.is_prefill and rope_pos.dim() == 1 and qkv.is_cuda and cfg.head_dim in ops.KERNEL_HEAD_DIMS
+                and FUSED_DECODE_ROPE):
             # decode / verify steps: q/k norm, RoPE and the KV append happen inside the attention kernel
             attn = ops.attention_decode_rope(qkv, k_cache, v_cache, batch.block_table, batch.seq_lens, batch.q_per_seq,
                                              self.scale, rope_pos, batch.slots, self.inv_freq, self.n_q_local,

@@ -23,6 +23,7 @@ native.register("eredu_ipc_close", I, [P])
 native.register("eredu_comm_create", P, [POINTER(c_void_p), I, I, L, L, P])
 native.register("eredu_comm_destroy", None, [P])
 native.register("eredu_comm_buffer_bytes", L, [L, L])
+native.register("eredu_comm_init_buffer", I, [P, L, L])
 native.register("eredu_comm_out_offset", L, [P])
 native.register("eredu_comm_data_offset", L, [P, I, I])
 native.register("eredu_allreduce_twoshot", I, [P, L, P, P, P, I, I, I, I, P, P])
@@ -67,6 +68,7 @@ class PeerGroup:
         own = c_void_p()
         native.check(lib.eredu_peer_alloc(self.bytes, ctypes.byref(own)), "eredu_peer_alloc")
         self.own = own.value
+        native.check(lib.eredu_comm_init_buffer(self.own, slot_bytes, out_total), "eredu_comm_init_buffer")
         hbytes = lib.eredu_ipc_handle_bytes()
         handle = ctypes.create_string_buffer(hbytes)
         native.check(lib.eredu_ipc_get_handle(self.own, handle), "cudaIpcGetMemHandle")

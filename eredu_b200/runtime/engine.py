@@ -479,6 +479,7 @@ class Engine:
                 # warm-up run outside capture (lazy kernel attribute setup), then restore the state it advanced
                 saved = {k: st[k].clone() for k in ("token_ids", "positions", "seq_lens", "slots", "rows")}
                 saved_h = st["history"].clone() if st["history"] is not None else None
+                saved_rec = [(t, t.clone()) for t in self.kv.recurrent_tensors()]   # hybrid layers: not idempotent
                 s = torch.cuda.Stream(device=self.device)
                 s.wait_stream(torch.cuda.current_stream(self.device))
                 with torch.cuda.stream(s):
@@ -489,6 +490,8 @@ class Engine:
                     st[k].copy_(v)
                 if saved_h is not None:
                     st["history"].copy_(saved_h)
+                for t, copy in saved_rec:
+                    t.copy_(copy)
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g):
                     self._decode_body(st)

@@ -124,6 +124,12 @@ class PagedKVCache:
     def has_recurrent_state(self) -> bool:
         return self.conv_state is not None or self.page_to_slot is not None
 
+    def recurrent_tensors(self) -> list:
+        """Every fixed-size state tensor a forward pass mutates in place (empty for attention-only models). A step that
+        is run twice on the same inputs - a warm-up before graph capture - must put these back in between: unlike a
+        K/V append, advancing a recurrent state is not idempotent."""
+        return [t for t in (self.conv_state, self.la_conv_state, self.la_rec_state) if t is not None]
+
     def snapshot_state(self, first_page: int):
         """Copies of this sequence's recurrent states (None for attention-only models)."""
         if not self.has_recurrent_state():
