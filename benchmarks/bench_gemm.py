@@ -1,7 +1,7 @@
 """GEMM micro-benchmarks on one GPU (CUDA events, warm-up, numerics checked against an fp32 product).
 
-    python -m eredu_b200.utils.bench_gemm prefill     # prefill-sized shapes against cuBLAS (torch.matmul / addmm)
-    python -m eredu_b200.utils.bench_gemm chain       # decode-sized GEMMs as a dependent chain inside a CUDA graph
+    python -m benchmarks.bench_gemm prefill     # prefill-sized shapes against cuBLAS (torch.matmul / addmm)
+    python -m benchmarks.bench_gemm chain       # decode-sized GEMMs as a dependent chain inside a CUDA graph
 
 ``prefill`` covers the dense projections of a Llama-3-8B layer at 2048 and 8192 tokens (and their TP=8 slices):
 plain, + residual, and fused SwiGLU (cuBLAS arm: one GEMM plus ``silu(g) * u`` as PyTorch element-wise ops).
@@ -15,7 +15,7 @@ import sys
 
 import torch
 
-from .. import ops
+from eredu_b200 import ops
 
 DEV = torch.device("cuda:0")
 

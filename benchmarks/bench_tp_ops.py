@@ -2,7 +2,7 @@
 against the same GEMM followed by an NCCL all-reduce, both replayed from CUDA graphs, device-timed, max over ranks.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port 29544 \\
-        -m eredu_b200.utils.bench_tp_ops --hidden 4096 --inter 14336
+        -m benchmarks.bench_tp_ops --hidden 4096 --inter 14336
 """
 from __future__ import annotations
 
@@ -13,10 +13,10 @@ import os
 import torch
 import torch.distributed as dist
 
-from ..ops import native
-from ..parallel.context import ParallelContext
-from ..parallel.topology import ParallelTopology
-from ..parallel.tp import NcclTPOps, PeerTPOps
+from eredu_b200.ops import native
+from eredu_b200.parallel.context import ParallelContext
+from eredu_b200.parallel.topology import ParallelTopology
+from eredu_b200.parallel.tp import NcclTPOps, PeerTPOps
 
 
 def timed_graph(fn, iters=50, warm=5):

@@ -2,9 +2,9 @@
 ``torch.cuda.profiler.start()`` / ``stop()`` so that a profiler attached with ``--profile-from-start off``
 captures exactly one step.
 
-    python -m eredu_b200.utils.profile_decode --layers 4 --batch 32 --ctx 2048
+    python -m benchmarks.profile_decode --layers 4 --batch 32 --ctx 2048
     ncu --profile-from-start off --metrics gpu__time_duration.sum --clock-control none --csv \\
-        --log-file launches.csv python -m eredu_b200.utils.profile_decode --layers 4 --batch 32 --ctx 2048
+        --log-file launches.csv python -m benchmarks.profile_decode --layers 4 --batch 32 --ctx 2048
 """
 from __future__ import annotations
 
@@ -14,10 +14,10 @@ import dataclasses
 import numpy as np
 import torch
 
-from ..models import config as C
-from ..models.llama import build_random
-from ..ops import SamplingParams, native
-from ..runtime.engine import Engine
+from eredu_b200.models import config as C
+from eredu_b200.models.llama import build_random
+from eredu_b200.ops import SamplingParams, native
+from eredu_b200.runtime.engine import Engine
 
 
 def main():
@@ -43,7 +43,7 @@ def main():
                                   num_key_value_heads=max(1, cfg.num_key_value_heads // args.heads_div))
     moe_factory = None
     if cfg.is_moe:
-        from ..models.moe import make_moe_factory
+        from eredu_b200.models.moe import make_moe_factory
 
         moe_factory = make_moe_factory()
     dev = torch.device("cuda:0")
