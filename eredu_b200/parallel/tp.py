@@ -4,8 +4,9 @@ The reference runs ``matmul -> all_sum`` (eredu/src/backend/mlx/nn/parallel.rs:7
 ``all_gather`` of the logits (:1382-1409) as separate NCCL collectives. Here:
 
 * up to 64 tokens (decode, speculative verify): ONE kernel does the tcgen05 GEMM and the all-reduce — partial
-  tiles are pushed to every peer over NVLink as they leave TMEM, flags publish them tile by tile, each rank sums
-  in rank order (``eredu_gemm_bf16_comm`` mode 1); the logits use the same kernel in all-gather mode (mode 2);
+  tiles are pushed to every peer over NVLink as they leave TMEM, as 4-byte bf16x2 words into sentinel-initialised
+  slots (a word is valid once it differs from the sentinel: no tag, flag or fence), each rank sums in rank order
+  (``eredu_gemm_bf16_comm`` mode 1); the logits use the same kernel in all-gather mode (mode 2);
 * more tokens (prefill): the GEMM writes its bf16 partial into symmetric memory and a two-shot peer-memory
   all-reduce (reduce-scatter by P2P loads, all-gather by P2P stores, residual/bias folded in) finishes it.
 
