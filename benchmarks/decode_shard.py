@@ -28,6 +28,7 @@ def main():
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--trace", action="store_true")
+    ap.add_argument("--timeline", type=int, default=0, help="with --trace: print the first N marks of the traced step")
     a = ap.parse_args()
     base = C.llama3_8b()
     tp = a.tp_shape
@@ -61,8 +62,11 @@ def main():
         tr = DeviceTrace(dev)
         tr.reset()
         eng.decode_step(sync=False)
-        s = summarise(tr.records())
+        recs = tr.records()
+        s = summarise(recs)
         tr.close()
+        for t, k, ph in recs[:a.timeline]:
+            print(f"{t / 1e3:10.2f} us  {k:14s} {ph}")
         s.pop("timeline")
         out["trace"] = s
     print(json.dumps(out))

@@ -30,6 +30,8 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xptxas", "-v",
 ]
+# extra nvcc flags for one-off builds, e.g. EREDU_NVCC_EXTRA="-DEREDU_TRACE_FINE" for sub-step timeline marks
+NVCC_FLAGS += os.environ.get("EREDU_NVCC_EXTRA", "").split()
 CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-Wno-unused-function", "-fvisibility=hidden"]
 
 

@@ -47,7 +47,18 @@ struct AttnParams {
   const float* k_norm_w;      // optional [D]
   int ld_qkv, rot, interleaved;
   float attn_factor, norm_eps, norm_w_off;
+  // splits > 1: 1 = the `splits` CTAs of a (sequence, kv head) form a thread-block cluster and combine their partial
+  // results through distributed shared memory (no global scratch, no arrival tickets); 0 = scratch + last-arriver.
+  int cluster_reduce;
 };
+constexpr int kMaxFusedNew = 8;       // new tokens per sequence the fused (RoPE + append) decode path handles
+constexpr int kMaxClusterSplits = 8;  // portable cluster size
+
+__device__ __forceinline__ float ld_dsmem_f32(uint32_t cluster_addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr) : "memory");
+  return v;
+}
 
 // One head row of the projection output: optional RMSNorm over D (result rounded to bf16 like a module boundary),
 // rotation of the first `rot` dims by the token's position. Executed by one warp; lane l owns the pairs l, l + 32, ...
@@ -340,7 +351,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnParams p) {
   constexpr int PAGE_BYTES = kPage * D * 2;
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* q_s = smem;                   // [ROWS][D] bf16
-  uint8_t* ring = smem + ROWS * D * 2;   // [4 warps][NSTAGE][K page, V page]
+  uint8_t* newkv_s = smem + ROWS * D * 2;                    // [kMaxFusedNew][K row, V row] bf16 (fused path)
+  uint8_t* ring = newkv_s + kMaxFusedNew * 2 * D * 2;        // [4 warps][NSTAGE][K page, V page]
 
   __shared__ int s_last;
   pdl_launch_early();
@@ -362,8 +374,12 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnParams p) {
   const int page1 = min(npages, page0 + pps);
 
   const bool fused = p.qkv != nullptr;
-  // Pages at or after the first new token's page must not be fetched before this CTA has appended the new rows.
-  const int first_new_page = (fused && p.t0 == 0) ? (kv_len - p.q_per_seq) / kPage : 0x7fffffff;
+  // The launch that handles the first query tokens also appends the new K / V rows. A page fetched from the cache may
+  // then still hold the old bytes of a new row, so the rows are patched into the shared-memory copy of their page
+  // (from `newkv_s`) after it has landed: no fence and no ordering between the append and the page fetches is needed.
+  const bool appending = fused && p.t0 == 0;
+  const int new_pos0 = kv_len - p.q_per_seq;
+  const int first_new_page = appending ? new_pos0 / kPage : 0x7fffffff;
   if (!fused) {
     for (int i = threadIdx.x; i < ROWS * CH; i += 128) {
       const int r = i / CH, c = i % CH;
@@ -403,10 +419,9 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnParams p) {
   }
 
   const int first = page0 + warp;
-  const bool early0 = first < first_new_page, early1 = first + 4 < first_new_page;
-  if (early0) load_page(first, 0);
+  load_page(first, 0);
   cp_async_commit();
-  if (early1) load_page(first + 4, 1);
+  load_page(first + 4, 1);
   cp_async_commit();
   if (fused) {
     // ---- q rows: norm + RoPE straight into the swizzled tile (rows beyond `rows` are zero)
@@ -424,39 +439,37 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnParams p) {
         for (int i = lane; i < D / 2; i += 32) put(2 * i, 0.f, 2 * i + 1, 0.f);
       }
     }
-    // ---- new K / V rows whose page lies in this CTA's range: norm + RoPE on K, both appended to the cache
-    if (p.t0 == 0) {
-      bool appended = false;
+    // ---- new K / V rows whose page lies in this CTA's range: norm + RoPE on K; both go to the cache (for later
+    // steps) and to `newkv_s` (for this step's own use)
+    if (appending) {
       for (int t = warp; t < p.q_per_seq; t += 4) {
-        const int pg = (kv_len - p.q_per_seq + t) / kPage;
+        const int pg = (new_pos0 + t) / kPage;
         const size_t m = static_cast<size_t>(b) * p.q_per_seq + t;
         const long long slot = p.slots[m];
         if (pg < page0 || pg >= page1 || slot < 0) continue;  // warp-uniform
         const size_t dst = ((static_cast<size_t>(slot >> 4) * p.n_kv_heads + kvh) * kPage + static_cast<size_t>(slot & 15)) * D;
         __nv_bfloat16* kd = const_cast<__nv_bfloat16*>(p.k_cache) + dst;
         __nv_bfloat16* vd = const_cast<__nv_bfloat16*>(p.v_cache) + dst;
+        __nv_bfloat16* ks = reinterpret_cast<__nv_bfloat16*>(newkv_s) + static_cast<size_t>(t) * 2 * D;
         const __nv_bfloat16* krow = p.qkv + m * p.ld_qkv + static_cast<size_t>(p.n_q_heads + kvh) * D;
         const __nv_bfloat16* vrow = p.qkv + m * p.ld_qkv + static_cast<size_t>(p.n_q_heads + p.n_kv_heads + kvh) * D;
         rope_head_row<D>(p, krow, p.k_norm_w, p.positions[m], lane, [&](int i0, float a, int i1, float bb) {
-          kd[i0] = __float2bfloat16(a);
-          kd[i1] = __float2bfloat16(bb);
+          const __nv_bfloat16 ha = __float2bfloat16(a), hb = __float2bfloat16(bb);
+          kd[i0] = ha;
+          kd[i1] = hb;
+          ks[i0] = ha;
+          ks[i1] = hb;
         });
-        for (int i = lane; i < D / 2; i += 32)
-          reinterpret_cast<uint32_t*>(vd)[i] = reinterpret_cast<const uint32_t*>(vrow)[i];
-        appended = true;
+        for (int i = lane; i < D / 2; i += 32) {
+          const uint32_t vv = reinterpret_cast<const uint32_t*>(vrow)[i];
+          reinterpret_cast<uint32_t*>(vd)[i] = vv;
+          reinterpret_cast<uint32_t*>(ks + D)[i] = vv;
+        }
       }
-      // the appended rows are read back below through cp.async (L2); CTAs that appended nothing skip the fence, which
-      // would otherwise also wait for their page fetches already in flight
-      if (appended) __threadfence();
     }
-    __syncthreads();
   }
-  if (!early0) load_page(first, 0);
-  cp_async_commit();
-  if (!early1) load_page(first + 4, 1);
-  cp_async_commit();
-  cp_async_wait<4>();  // the Q tile (the oldest group)
-  __syncthreads();
+  cp_async_wait<2>();  // the Q tile (the oldest group)
+  __syncthreads();     // Q tile and new rows visible to every warp
 
   const uint32_t q_base = smem_u32(q_s);
   int it = 0;
@@ -465,6 +478,21 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnParams p) {
     cp_async_commit();
     cp_async_wait<2>();
     __syncwarp();
+    if (pg >= first_new_page) {
+      // this page holds rows appended in this step: overwrite them in the landed copy (16-byte chunks, lanes 0-15 the
+      // K row, 16-31 the V row; D / 8 chunks per row)
+      uint8_t* kst = my_ring + (it % NSTAGE) * 2 * PAGE_BYTES;
+      for (int t = 0; t < p.q_per_seq; ++t) {
+        const int pos = new_pos0 + t;
+        if (pos / kPage != pg || p.slots[static_cast<size_t>(b) * p.q_per_seq + t] < 0) continue;  // warp-uniform
+        const uint4* src = reinterpret_cast<const uint4*>(newkv_s + static_cast<size_t>(t) * 2 * D * 2);
+        for (int i = lane; i < 2 * CH; i += 32) {
+          const int which = i / CH, c = i % CH;
+          *reinterpret_cast<uint4*>(kst + which * PAGE_BYTES + swz<D>(pos & (kPage - 1), c)) = src[i];
+        }
+      }
+      __syncwarp();
+    }
     const uint32_t k_base = smem_u32(my_ring + (it % NSTAGE) * 2 * PAGE_BYTES);
     const uint32_t v_base = k_base + PAGE_BYTES;
 
@@ -548,10 +576,13 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnParams p) {
   cp_async_wait<0>();
   __syncthreads();  // every warp is done with its ring: reuse it for the merge
 
-  // ---- merge the 4 warps: mo[w][row][D] fp32, mm/ml[w][row]
+  // ---- merge the 4 warps: mo[w][row][D] fp32, mm/ml[w][row]; then this CTA's merged partial (cluster mode)
   float* mo = reinterpret_cast<float*>(ring);
   float* mm = mo + 4 * ROWS * D;
   float* ml = mm + 4 * ROWS;
+  float* part_s = ml + 4 * ROWS;   // [ROWS][D]
+  float* part_m = part_s + ROWS * D;
+  float* part_l = part_m + ROWS;
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
@@ -592,6 +623,12 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnParams p) {
       float Lf = L;
       if (p.sinks != nullptr) Lf += exp2f(p.sinks[head] * 1.4426950408889634f - Ms);
       p.out[qrow * D + d] = __float2bfloat16(Lf > 0.f ? acc / Lf : 0.f);
+    } else if (p.cluster_reduce) {
+      part_s[row * D + d] = acc;
+      if (d == 0) {
+        part_m[row] = M;
+        part_l[row] = L;
+      }
     } else {
       p.part_o[(qrow * p.splits + split) * D + d] = acc;
       if (d == 0) {
@@ -600,7 +637,43 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnParams p) {
       }
     }
   }
-  if (p.splits > 1) {
+  if (p.splits > 1 && p.cluster_reduce) {
+    // The splits of this (sequence, kv head) are one cluster: every CTA combines a share of the rows, reading the
+    // partials of all splits out of their shared memory.
+    cluster_arrive_release();
+    cluster_wait_acquire();
+    const uint32_t a_s = smem_u32(part_s), a_m = smem_u32(part_m), a_l = smem_u32(part_l);
+    for (int i = threadIdx.x + split * 128; i < rows * D; i += 128 * p.splits) {  // row-major: a warp stays in one row
+      const int row = i / D, d = i % D;
+      float M = -INFINITY;
+      float ms[kMaxClusterSplits], pv[kMaxClusterSplits], ls[kMaxClusterSplits];
+#pragma unroll
+      for (int sp = 0; sp < kMaxClusterSplits; ++sp) {
+        if (sp < p.splits) {
+          ms[sp] = ld_dsmem_f32(mapa_shared(a_m + row * 4, sp));
+          ls[sp] = ld_dsmem_f32(mapa_shared(a_l + row * 4, sp));
+          pv[sp] = ld_dsmem_f32(mapa_shared(a_s + (row * D + d) * 4, sp));
+          M = fmaxf(M, ms[sp]);
+        }
+      }
+      const float Ms = (M == -INFINITY) ? 0.f : M;
+      float L = 0.f, acc = 0.f;
+#pragma unroll
+      for (int sp = 0; sp < kMaxClusterSplits; ++sp) {
+        if (sp < p.splits) {
+          const float e = exp2f(ms[sp] - Ms);
+          L += ls[sp] * e;
+          acc += pv[sp] * e;
+        }
+      }
+      const int t = p.t0 + row / group, hg = row % group;
+      const int head = kvh * group + hg;
+      if (p.sinks != nullptr) L += exp2f(p.sinks[head] * 1.4426950408889634f - Ms);
+      p.out[(static_cast<size_t>(b * p.q_per_seq + t) * p.n_q_heads + head) * D + d] = __float2bfloat16(L > 0.f ? acc / L : 0.f);
+    }
+    cluster_arrive_release();  // done reading the peers' shared memory
+    cluster_wait_acquire();    // and nobody reads this CTA's any more
+  } else if (p.splits > 1) {
     // The last split to arrive for this (sequence, kv head) combines all partials: no second launch.
     __threadfence();
     __syncthreads();
@@ -663,8 +736,8 @@ static size_t prefill_smem() {
 template <int D, int MT>
 static size_t decode_smem() {
   const size_t ring = 4 * 3 * 2 * kPage * D * 2;
-  const size_t merge = (4 * 16 * MT * D + 2 * 4 * 16 * MT) * sizeof(float);
-  return 16 * MT * D * 2 + (ring > merge ? ring : merge);
+  const size_t merge = (4 * 16 * MT * D + 2 * 4 * 16 * MT + 16 * MT * D + 2 * 16 * MT) * sizeof(float);
+  return 16 * MT * D * 2 + kMaxFusedNew * 2 * D * 2 + (ring > merge ? ring : merge);
 }
 
 }  // namespace eredu
@@ -734,7 +807,28 @@ template <int D, int MT>
 static cudaError_t launch_decode(const AttnParams& p, dim3 grid, cudaStream_t stream) {
   static bool cfg[kMaxDevices] = {};
   if (!configure_once(cfg, attn_decode_kernel<D, MT>, decode_smem<D, MT>())) return cudaErrorInvalidValue;
-  const cudaError_t e = launch_pdl(attn_decode_kernel<D, MT>, grid, dim3(128), decode_smem<D, MT>(), stream, p);
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = grid;
+  lc.blockDim = dim3(128);
+  lc.dynamicSmemBytes = decode_smem<D, MT>();
+  lc.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int nattr = 0;
+  if (pdl_enabled()) {
+    attr[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[nattr].val.programmaticStreamSerializationAllowed = 1;
+    ++nattr;
+  }
+  if (p.cluster_reduce) {
+    attr[nattr].id = cudaLaunchAttributeClusterDimension;
+    attr[nattr].val.clusterDim.x = grid.x;  // the splits of one (sequence, kv head)
+    attr[nattr].val.clusterDim.y = 1;
+    attr[nattr].val.clusterDim.z = 1;
+    ++nattr;
+  }
+  lc.attrs = attr;
+  lc.numAttrs = nattr;
+  const cudaError_t e = cudaLaunchKernelEx(&lc, attn_decode_kernel<D, MT>, p);
   eredu_count_launches(1);
   return e;
 }
@@ -744,11 +838,16 @@ static cudaError_t launch_decode(const AttnParams& p, dim3 grid, cudaStream_t st
 // caller-provided fp32 scratch (see eredu_attn_decode_scratch_elems) and `counters` a zeroed int32
 // [batch * n_kv_heads] array (left zeroed again on return); all unused when splits == 1.
 static int launch_decode_all(AttnParams p, int batch, int q_per_seq, int n_q_heads, int n_kv_heads, int head_dim,
-                             cudaStream_t stream) {
+                             cudaStream_t stream, bool force_scratch = false) {
   if (n_kv_heads <= 0 || n_q_heads <= 0 || n_q_heads % n_kv_heads != 0) return -1;
   const int group = n_q_heads / n_kv_heads;
   if (group > 32 || (head_dim != 128 && head_dim != 64)) return -1;
   const int t_per = group > 16 ? 1 : (32 / group < q_per_seq ? 32 / group : q_per_seq);
+  if (p.qkv != nullptr && q_per_seq > kMaxFusedNew) return -1;
+  // Few splits: a cluster per (sequence, kv head) combines the partials in shared memory. More splits than a portable
+  // cluster holds (or a caller that asks for it by passing scratch and force_scratch): global scratch + last arriver.
+  p.cluster_reduce = (p.splits > 1 && p.splits <= kMaxClusterSplits && !force_scratch) ? 1 : 0;
+  if (p.splits > 1 && !p.cluster_reduce && (p.part_o == nullptr || p.part_ml == nullptr || p.counters == nullptr)) return -1;
   dim3 grid(p.splits, n_kv_heads, batch);
   for (int t0 = 0; t0 < q_per_seq; t0 += t_per) {
     p.t0 = t0;
@@ -762,11 +861,10 @@ static int launch_decode_all(AttnParams p, int batch, int q_per_seq, int n_q_hea
   return 0;
 }
 
-extern "C" int eredu_attn_decode(const void* q, const void* k_cache, const void* v_cache, void* out,
-                                 const int* block_table, const int* seq_lens, const float* sinks, float* part_o,
-                                 float* part_ml, int* counters, int batch, int q_per_seq, int max_pages, int n_q_heads,
-                                 int n_kv_heads, int head_dim, int splits, int window, float scale,
-                                 cudaStream_t stream) {
+static int attn_decode_impl(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
+                            const int* seq_lens, const float* sinks, float* part_o, float* part_ml, int* counters,
+                            int batch, int q_per_seq, int max_pages, int n_q_heads, int n_kv_heads, int head_dim,
+                            int splits, int window, float scale, cudaStream_t stream, bool force_scratch) {
   AttnParams p = {};
   p.q = static_cast<const __nv_bfloat16*>(q);
   p.k_cache = static_cast<const __nv_bfloat16*>(k_cache);
@@ -785,7 +883,18 @@ extern "C" int eredu_attn_decode(const void* q, const void* k_cache, const void*
   p.splits = splits < 1 ? 1 : (splits > 64 ? 64 : splits);
   p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
-  return launch_decode_all(p, batch, q_per_seq, n_q_heads, n_kv_heads, head_dim, stream);
+  return launch_decode_all(p, batch, q_per_seq, n_q_heads, n_kv_heads, head_dim, stream, force_scratch);
+}
+
+// Up to 8 splits combine inside a thread-block cluster and ignore the scratch arguments (they may be null); more
+// splits need them.
+extern "C" int eredu_attn_decode(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                 const int* block_table, const int* seq_lens, const float* sinks, float* part_o,
+                                 float* part_ml, int* counters, int batch, int q_per_seq, int max_pages, int n_q_heads,
+                                 int n_kv_heads, int head_dim, int splits, int window, float scale,
+                                 cudaStream_t stream) {
+  return attn_decode_impl(q, k_cache, v_cache, out, block_table, seq_lens, sinks, part_o, part_ml, counters, batch,
+                          q_per_seq, max_pages, n_q_heads, n_kv_heads, head_dim, splits, window, scale, stream, false);
 }
 
 // Decode attention that starts from the projection output: qkv [batch * q_per_seq, ld_qkv] = [q heads | k heads |
@@ -876,6 +985,7 @@ extern "C" int eredu_attn_decode_static(const void* q, const void* k_cache, cons
     e = cudaMemsetAsync(counters, 0, static_cast<size_t>(batch) * n_kv_heads * sizeof(int), stream);
     if (e != cudaSuccess) return static_cast<int>(e);
   }
-  return eredu_attn_decode(q, k_cache, v_cache, out, block_table, seq_lens, sinks, part_o, part_ml, counters, batch,
-                           q_per_seq, max_pages, n_q_heads, n_kv_heads, head_dim, splits, window, scale, stream);
+  // always the scratch form of the split reduction: that is the form whose scratch this entry point provides
+  return attn_decode_impl(q, k_cache, v_cache, out, block_table, seq_lens, sinks, part_o, part_ml, counters, batch,
+                          q_per_seq, max_pages, n_q_heads, n_kv_heads, head_dim, splits, window, scale, stream, true);
 }

@@ -262,13 +262,22 @@ import os as _os
 _SPLIT_WAVES = int(_os.environ.get("EREDU_DECODE_SPLIT_WAVES", "2"))   # CTAs per SM the split-KV grid aims for
 
 
+CLUSTER_SPLITS = 8      # splits the decode kernel combines through distributed shared memory (portable cluster size)
+FUSED_ROPE_MAX_NEW = 8  # new tokens per sequence the fused RoPE + append decode path takes
+
+
 def decode_splits(batch, n_kv, max_kv_len, sm_count=148):
     """Split-KV factor: enough CTAs to fill the GPU once (a second wave costs more than it returns: the CTAs of the
     following kernel are already resident under programmatic dependent launch), at least 8 pages per split."""
     ctas = max(1, batch * n_kv)
     pages = max(1, (max_kv_len + PAGE - 1) // PAGE)
     want = max(1, (_SPLIT_WAVES * sm_count) // ctas)
-    return int(max(1, min(want, pages // 8 if pages >= 8 else 1, 32)))
+    splits = int(max(1, min(want, pages // 8 if pages >= 8 else 1, 32)))
+    # up to CLUSTER_SPLITS splits combine inside a thread-block cluster (no scratch, no second pass over global memory):
+    # prefer that form while a split then still has at most 32 pages (8 per warp)
+    if splits > CLUSTER_SPLITS and pages <= 32 * CLUSTER_SPLITS:
+        splits = CLUSTER_SPLITS
+    return splits
 
 
 def attention_decode(q, k_cache, v_cache, block_table, seq_lens, q_per_seq, scale, splits=1, window=0, sinks=None,
@@ -284,7 +293,7 @@ def attention_decode(q, k_cache, v_cache, block_table, seq_lens, q_per_seq, scal
     if out is None:
         out = torch.empty_like(q)
     part_o = part_ml = counters = None
-    if splits > 1:
+    if splits > CLUSTER_SPLITS:
         if scratch is None:
             scratch = decode_scratch(B, q_per_seq, n_q, D, splits, q.device)
         part_o, part_ml, counters = scratch
@@ -303,7 +312,7 @@ def attention_decode_rope(qkv, k_cache, v_cache, block_table, seq_lens, q_per_se
     """Decode attention straight from the qkv projection output [B * q_per_seq, >= (n_q + 2 n_kv) * D]: per-head
     q/k norm, RoPE and the KV append run inside the attention kernel (one launch instead of two). CPU tensors and
     head sizes without a kernel compose the two reference operators."""
-    if not qkv.is_cuda or head_dim not in KERNEL_HEAD_DIMS or positions.dim() != 1:
+    if not qkv.is_cuda or head_dim not in KERNEL_HEAD_DIMS or positions.dim() != 1 or q_per_seq > FUSED_ROPE_MAX_NEW:
         q = rope_kv(qkv, positions, slots, inv_freq, k_cache, v_cache, n_q, n_kv, head_dim, rot, interleaved, attn_factor,
                     q_norm_w, k_norm_w, norm_eps, norm_w_off)
         return attention_decode(q, k_cache, v_cache, block_table, seq_lens, q_per_seq, scale, splits, window, sinks, scratch)
@@ -312,7 +321,7 @@ def attention_decode_rope(qkv, k_cache, v_cache, block_table, seq_lens, q_per_se
     B = seq_lens.shape[0]
     out = torch.empty((qkv.shape[0], n_q, head_dim), dtype=qkv.dtype, device=qkv.device)
     part_o = part_ml = counters = None
-    if splits > 1:
+    if splits > CLUSTER_SPLITS:
         if scratch is None:
             scratch = decode_scratch(B, q_per_seq, n_q, head_dim, splits, qkv.device)
         part_o, part_ml, counters = scratch

@@ -317,7 +317,8 @@ def test_spec_verify(temp):
 @pytest.mark.parametrize("D,n_q,n_kv,qps,qknorm,interleaved,rot,splits", [
     (128, 32, 8, 1, False, False, None, 1), (128, 32, 8, 1, False, False, None, 5), (128, 4, 1, 1, False, False, None, 4),
     (128, 32, 8, 5, True, False, None, 3), (64, 4, 2, 1, True, True, None, 2), (128, 8, 2, 3, False, False, 64, 2),
-    (128, 64, 8, 3, False, False, None, 2)])
+    (128, 64, 8, 3, False, False, None, 2), (128, 64, 8, 5, False, False, None, 4), (128, 32, 8, 1, False, False, None, 12),
+    (128, 32, 8, 4, True, False, None, 8)])
 def test_decode_attention_with_fused_rope_and_append(D, n_q, n_kv, qps, qknorm, interleaved, rot, splits):
     """The decode kernel that takes the qkv projection output (q/k norm, RoPE and the KV append inside the kernel)
     against the separate RoPE + append kernel followed by fp32 reference attention; the caches must end up equal."""
