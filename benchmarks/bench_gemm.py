@@ -2,6 +2,7 @@
 
     python -m benchmarks.bench_gemm prefill     # prefill-sized shapes against cuBLAS (torch.matmul / addmm)
     python -m benchmarks.bench_gemm chain       # decode-sized GEMMs as a dependent chain inside a CUDA graph
+    python -m benchmarks.bench_gemm decode      # the four projections of a decoder layer, TP=1 and TP=8 slices
 
 ``prefill`` covers the dense projections of a Llama-3-8B layer at 2048 and 8192 tokens (and their TP=8 slices):
 plain, + residual, and fused SwiGLU (cuBLAS arm: one GEMM plus ``silu(g) * u`` as PyTorch element-wise ops).
@@ -98,6 +99,20 @@ def chain():
                           "us_per_gemm": round(_chain(32, 1792, 4096, 0, 0, split, dual=True), 2)}))
 
 
+def decode():
+    """The four projections of a Llama-3-8B layer at 32 tokens and at 1 token, whole (TP=1) and as a TP=8 rank's slice,
+    each as a dependent chain inside a CUDA graph with the launcher's own split choice: us per GEMM and the weight
+    stream rate it amounts to."""
+    for tp in (1, 8):
+        for M in (32, 1):
+            for name, N, K, res, ssq, dual in [("qkv", 6144 // tp, 4096, 0, 0, False), ("o_proj", 4096, 4096 // tp, 1, 1, False),
+                                               ("gate_up", 14336 // tp, 4096, 0, 0, True), ("down", 4096, 14336 // tp, 1, 1, False)]:
+                us = _chain(M, N, K, res, ssq, 0, n=32, dual=dual)
+                wbytes = (2 if dual else 1) * N * K * 2
+                print(json.dumps({"tp": tp, "M": M, "gemm": name, "N": N, "K": K, "us_per_gemm": round(us, 2),
+                                  "weight_GBs": round(wbytes / us / 1e3, 1)}))
+
+
 def one(M: int, N: int, K: int, kind: str = "residual", reps: int = 3):
     """A single shape, a few launches: the small case a profiler capture runs on (operands above the 126 MB L2 for
     the sizes used in profiles/)."""
@@ -117,4 +132,4 @@ if __name__ == "__main__":
     if mode == "one":
         one(int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4]), sys.argv[5] if len(sys.argv) > 5 else "residual")
     else:
-        {"prefill": prefill, "chain": chain}[mode]()
+        {"prefill": prefill, "chain": chain, "decode": decode}[mode]()

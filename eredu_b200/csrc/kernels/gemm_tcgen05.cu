@@ -64,6 +64,7 @@ struct GemmParams {
   // rest prefetched into L2, BEFORE the kernel waits for its producer under programmatic dependent launch, so
   // the weight stream of this kernel overlaps the tail of the previous one.
   int w_static;
+  int nstages;     // depth of the operand ring (2..8): chosen by the launcher from the grid size and the split count
   PeerComm comm;   // COMM modes only
 };
 
@@ -89,15 +90,20 @@ struct GemmCfg {
   // Split-K partials of the cluster peers land here (one chunk per source CTA), outside the operand ring: a fast peer
   // may deliver while this CTA's tensor core still reads its ring.
   static constexpr int kRecvBytes = kAccCols * 128 * 4;
-  // Decode-sized tiles keep shared memory under half an SM so that two CTAs are co-resident: the whole grid
-  // (<= 296 CTAs) then runs as one wave and HBM bandwidth is shared evenly instead of paying a partial wave.
-  static constexpr int kBudget = (TN <= 32 || (TN == 64 && !DUAL)) ? 110 * 1024 : 200 * 1024;
-  static constexpr int stages(bool split) {
-    int n = (kBudget - 1024 - kCtrlBytes - (split ? kRecvBytes : 0)) / kStageBytes;
+  // A grid of more CTAs than SMs keeps decode-sized tiles under half an SM of shared memory so that two CTAs are
+  // co-resident: the whole grid (<= 296 CTAs) then runs as one wave and HBM bandwidth is shared evenly instead of paying
+  // a partial wave. A grid that fits the SMs once takes the deep ring: with one CTA per SM the bytes in flight per SM are
+  // what the ring holds, and a K slice that fits the ring is fetched entirely before the stream dependency resolves.
+  static constexpr int kSmallBudget = 110 * 1024, kBigBudget = 200 * 1024;
+  static constexpr int stages(bool split, bool one_wave) {
+    const int budget = (one_wave || !(TN <= 32 || (TN == 64 && !DUAL))) ? kBigBudget : kSmallBudget;
+    int n = (budget - 1024 - kCtrlBytes - (split ? kRecvBytes : 0)) / kStageBytes;
     return n > kMaxStages ? kMaxStages : n;
   }
-  static constexpr int smem_bytes(bool split) { return 1024 + kCtrlBytes + stages(split) * kStageBytes + (split ? kRecvBytes : 0); }
-  static_assert(stages(false) >= 2 && (TN > 64 || stages(true) >= 2), "pipeline too shallow");  // split-K: TN <= 64 only
+  static constexpr int smem_bytes(bool split, int nstages) {
+    return 1024 + kCtrlBytes + nstages * kStageBytes + (split ? kRecvBytes : 0);
+  }
+  static_assert(stages(false, false) >= 2 && (TN > 64 || stages(true, false) >= 2), "pipeline too shallow");  // split-K: TN <= 64 only
 };
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
@@ -115,42 +121,28 @@ __device__ __forceinline__ float residual_at(const GemmParams& p, int m, int n) 
   return __bfloat162float(static_cast<const __nv_bfloat16*>(p.residual)[static_cast<size_t>(m) * p.ldr + n]);
 }
 
-// Applies row scale, bias, activation and residual, stores, and returns the value as stored (after rounding).
-// `rv`: the residual value of the element (0 when there is none), loaded by the caller ahead of time so that
-// the load does not sit between two dependent stores.
-template <bool DUAL>
-__device__ __forceinline__ float epilogue_store(const GemmParams& p, const __nv_bfloat16* b, float g, float u, int m, int n,
-                                                float scale, float rv) {
-  g *= scale;
-  if (DUAL) u *= scale;
-  if (b != nullptr) {
-    g += __bfloat162float(b[n]);
-    if (DUAL) u += __bfloat162float(b[p.N + n]);
-  }
-  float v = (DUAL ? gated_act(p, g, u) : g) + rv;
-  if (p.out_fp32) {
-    static_cast<float*>(p.y)[static_cast<size_t>(m) * p.ldy + n] = v;
-    return v;
-  }
-  const __nv_bfloat16 r = __float2bfloat16(v);
-  static_cast<__nv_bfloat16*>(p.y)[static_cast<size_t>(m) * p.ldy + n] = r;
-  return __bfloat162float(r);
-}
-
-// COMM_AG: the finished value goes straight into every peer's gathered output.
-__device__ __forceinline__ void comm_emit_gather(const GemmParams& p, const __nv_bfloat16* bias, float g, int m, int n,
-                                                 float scale) {
-  float v = g * scale;
-  if (bias != nullptr) v += __bfloat162float(bias[n]);
-  const size_t idx = static_cast<size_t>(m) * p.ldy + p.col_offset + n;
+// Sums each of 8 per-lane values over the 32 lanes of a warp with 9 shuffles (instead of 40): halves of the value set are
+// exchanged while the lane distance shrinks. On return every lane holds the warp total of value index `which`
+// (= lane bits 4, 3, 2 read as a 3-bit number); the lanes with lane % 4 == 0 cover the 8 values once.
+__device__ __forceinline__ float warp_sum8(const float (&v)[8], int lane, int& which) {
+  float w[4], x[2];
+  const bool h16 = lane & 16, h8 = lane & 8, h4 = lane & 4;
 #pragma unroll
-  for (int peer = 0; peer < kMaxRanks; ++peer) {  // compile-time indices: the pointer table stays in the parameter bank
-    if (peer < p.comm.size) {
-      uint8_t* out = p.comm.base[peer] + p.comm.out_off;
-      if (p.out_fp32) reinterpret_cast<float*>(out)[idx] = v;
-      else reinterpret_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16(v);
-    }
+  for (int j = 0; j < 4; ++j) {
+    const float keep = h16 ? v[j + 4] : v[j], send = h16 ? v[j] : v[j + 4];
+    w[j] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
   }
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const float keep = h8 ? w[j + 2] : w[j], send = h8 ? w[j] : w[j + 2];
+    x[j] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+  }
+  const float keep = h4 ? x[1] : x[0], send = h4 ? x[0] : x[1];
+  float y = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+  y += __shfl_xor_sync(0xffffffffu, y, 2);
+  y += __shfl_xor_sync(0xffffffffu, y, 1);
+  which = (h16 ? 4 : 0) + (h8 ? 2 : 0) + (h4 ? 1 : 0);
+  return y;
 }
 
 // Split-K as a thread-block cluster along z. Token columns are owned in contiguous runs of cw = TN / nsplit: CTA `o`
@@ -165,7 +157,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                const __grid_constant__ GemmParams p) {
   using Cfg = GemmCfg<TN, DUAL>;
   constexpr int C2 = DUAL ? 2 : 1;
-  constexpr int kStages = Cfg::stages(SPLIT);
+  const int kStages = p.nstages;
   pdl_launch_early();
   trace_mark(kTraceGemm, kTraceStart);
   extern __shared__ uint8_t smem_raw[];
@@ -339,22 +331,51 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   for (int j = 0; j < kPre; ++j) rpre[j] = 0.f;
   const bool has_res = p.residual != nullptr && in_n;
 
-  // Final value of element (column c of the tile, this thread's row): store it (or hand it to the gather) and add its
-  // square to the per-column sum kept for a following RMSNorm. Executed by whole warps.
-  auto finish = [&](float g, float u, int c, float rv) {
-    const int m = m_base + c;
-    const bool ok = in_n && m < m_limit;
-    float v = 0.f;
-    if (ok) {
+  // Final values of this thread's row: stored (or handed to the gather), their squares added to the per-column sums kept
+  // for a following RMSNorm. Executed by whole warps.
+  // Eight consecutive columns [c0, c0 + 8) at once: all values first, then the stores, then ONE butterfly for the eight
+  // sums of squares - independent work the scheduler can overlap, instead of a dependent chain per column.
+  const float bias_g = (bias != nullptr && in_n) ? __bfloat162float(bias[n]) : 0.f;
+  const float bias_u = (DUAL && bias != nullptr && in_n) ? __bfloat162float(bias[p.N + n]) : 0.f;
+  auto finish8 = [&](const float (&g)[8], const float (&u)[8], const float (&rv)[8], int c0, int c_hi) {
+    float val[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int c = min(c0 + j, TN - 1);
       const float sc = (p.ssq_in != nullptr) ? s_scale[c] : 1.f;
-      if (COMM == COMM_AG) comm_emit_gather(p, bias, g, m, n, sc);
-      else v = epilogue_store<DUAL>(p, bias, g, u, m, n, sc, rv);
+      const float gg = g[j] * sc + bias_g;
+      float v = (DUAL ? gated_act(p, gg, u[j] * sc + bias_u) : gg) + rv[j];
+      if (!p.out_fp32 && COMM != COMM_AG) v = __bfloat162float(__float2bfloat16(v));
+      val[j] = v;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int c = c0 + j, m = m_base + c;
+      if (c < c_hi && in_n) {
+        if (COMM == COMM_AG) {
+          const size_t idx = static_cast<size_t>(m) * p.ldy + p.col_offset + n;
+#pragma unroll
+          for (int peer = 0; peer < kMaxRanks; ++peer) {
+            if (peer < p.comm.size) {
+              uint8_t* out = p.comm.base[peer] + p.comm.out_off;
+              if (p.out_fp32) reinterpret_cast<float*>(out)[idx] = val[j];
+              else reinterpret_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16(val[j]);
+            }
+          }
+        } else if (p.out_fp32) {
+          static_cast<float*>(p.y)[static_cast<size_t>(m) * p.ldy + n] = val[j];
+        } else {
+          static_cast<__nv_bfloat16*>(p.y)[static_cast<size_t>(m) * p.ldy + n] = __float2bfloat16(val[j]);
+        }
+      }
     }
     if (COMM != COMM_AG && p.ssq_out != nullptr) {
-      float sq = v * v;
+      float sq[8];
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-      if (lane == 0) s_ssq[q][c] = sq;
+      for (int j = 0; j < 8; ++j) sq[j] = (c0 + j < c_hi && in_n) ? val[j] * val[j] : 0.f;
+      int which;
+      const float total = warp_sum8(sq, lane, which);
+      if ((lane & 3) == 0 && c0 + which < TN) s_ssq[q][c0 + which] = total;
     }
   };
   // After the owned columns [c_lo, c_hi) went through finish(): publish the per-row partial sums of squares.
@@ -421,12 +442,19 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             stage[(c0 + j) * 128 + row] = DUAL ? gated_act(p, gg, __uint_as_float(u[j]) * sc + bu) : gg;
           }
         } else {
-          float rr[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) rr[j] = (has_res && c0 + j < m_end) ? residual_at(p, m_base + c0 + j, n) : 0.f;
+          for (int h = 0; h < 2; ++h) {
+            if (c0 + 8 * h < m_end) {  // warp-uniform
+              float g8[8], u8[8], r8[8];
 #pragma unroll
-          for (int j = 0; j < 16; ++j)
-            if (c0 + j < m_end) finish(__uint_as_float(g[j]), DUAL ? __uint_as_float(u[j]) : 0.f, c0 + j, rr[j]);  // warp-uniform
+              for (int j = 0; j < 8; ++j) {
+                g8[j] = __uint_as_float(g[8 * h + j]);
+                u8[j] = DUAL ? __uint_as_float(u[8 * h + j]) : 0.f;
+                r8[j] = (has_res && c0 + 8 * h + j < m_end) ? residual_at(p, m_base + c0 + 8 * h + j, n) : 0.f;
+              }
+              finish8(g8, u8, r8, c0 + 8 * h, m_end);
+            }
+          }
         }
       }
     }
@@ -612,35 +640,24 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           }
           first_pass = false;
         }
+        float g8[8], u8[8], r8[8];
 #pragma unroll
         for (int j = 0; j < kPB; ++j) {
-          const int c = c0 + 2 * j;
-          if (c >= own_hi) break;  // warp-uniform
           float v0 = 0.f, v1 = 0.f;
-          if (in_n) {
 #pragma unroll
-            for (int src = 0; src < kMaxRanks; ++src) {  // rank order: every rank computes the same bits
-              if (src < p.comm.size && !((miss[j] >> src) & 1u)) {
-                v0 += bf16_lo(val[j][src]);
-                v1 += bf16_hi(val[j][src]);
-              }
-            }
-            v0 = epilogue_store<false>(p, bias, v0, 0.f, m_base + c, n, 1.f, r0[j]);
-            v1 = (c + 1 < m_end) ? epilogue_store<false>(p, bias, v1, 0.f, m_base + c + 1, n, 1.f, r1[j]) : 0.f;
-          }
-          if (p.ssq_out != nullptr) {
-            float s0 = in_n ? v0 * v0 : 0.f, s1 = in_n ? v1 * v1 : 0.f;
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-              s0 += __shfl_xor_sync(0xffffffffu, s0, o);
-              s1 += __shfl_xor_sync(0xffffffffu, s1, o);
-            }
-            if (lane == 0) {
-              s_ssq[q][c] = s0;
-              if (c + 1 < TN) s_ssq[q][c + 1] = s1;
+          for (int src = 0; src < kMaxRanks; ++src) {  // rank order: every rank computes the same bits
+            if (src < p.comm.size && !((miss[j] >> src) & 1u)) {
+              v0 += bf16_lo(val[j][src]);
+              v1 += bf16_hi(val[j][src]);
             }
           }
+          g8[2 * j] = v0;
+          g8[2 * j + 1] = v1;
+          u8[2 * j] = u8[2 * j + 1] = 0.f;
+          r8[2 * j] = r0[j];
+          r8[2 * j + 1] = r1[j];
         }
+        finish8(g8, u8, r8, c0, own_hi);
       }
      }
       publish_ssq(own_lo, own_hi);
@@ -648,19 +665,16 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   } else if (SPLIT) {
     if (warp >= 2 && has_work) {
      if (acc_ok && red_ok) {
+      for (int c0 = own_lo; c0 < own_hi; c0 += 8) {  // warp-uniform
+        float g8[8], u8[8], r8[8];
 #pragma unroll
-      for (int j = 0; j < kPre; ++j) {
-        const int c = own_lo + j;
-        if (c < own_hi) {  // warp-uniform
-          float g, u;
-          reduced(c, g, u);
-          finish(g, u, c, rpre[j]);
+        for (int j = 0; j < 8; ++j) {
+          const int c = min(c0 + j, own_lo + cw - 1);  // columns past the owned run repeat the last one (not stored)
+          reduced(c, g8[j], u8[j]);
+          r8[j] = 0.f;
+          if (has_res) r8[j] = (c0 == own_lo) ? rpre[j] : ((c0 + j < own_hi) ? residual_at(p, m_base + c0 + j, n) : 0.f);
         }
-      }
-      for (int c = own_lo + kPre; c < own_hi; c += 1) {
-        float g, u;
-        reduced(c, g, u);
-        finish(g, u, c, has_res ? residual_at(p, m_base + c, n) : 0.f);
+        finish8(g8, u8, r8, c0, own_hi);
       }
      }
       if (COMM == COMM_NONE) publish_ssq(own_lo, own_hi);
@@ -696,12 +710,31 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 
 constexpr int kMaxGemmDevices = 64;
 
+static int sm_count_of_current_device() {
+  static int cached[kMaxGemmDevices] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxGemmDevices) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
 template <int TN, bool DUAL, bool SPLIT, int COMM = COMM_NONE>
 static cudaError_t launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, int n_tiles,
                                int m_tiles, int nsplit, cudaStream_t stream) {
   using Cfg = GemmCfg<TN, DUAL>;
   auto kern = gemm_wt_kernel<TN, DUAL, SPLIT, COMM>;
-  constexpr int kSmem = Cfg::smem_bytes(SPLIT);
+  const int kblocks_per_cta = ((p.K + 63) / 64 + nsplit - 1) / nsplit;
+  const bool one_wave = static_cast<long long>(n_tiles) * m_tiles * nsplit <= sm_count_of_current_device();
+  int nstages = Cfg::stages(SPLIT, one_wave);
+  if (nstages > kblocks_per_cta) nstages = kblocks_per_cta < 2 ? 2 : kblocks_per_cta;
+  GemmParams pp = p;
+  pp.nstages = nstages;
+  const int smem_now = Cfg::smem_bytes(SPLIT, nstages);
+  constexpr int kSmem = Cfg::smem_bytes(SPLIT, Cfg::stages(SPLIT, true));  // the largest this instantiation asks for
   static bool configured[kMaxGemmDevices] = {};  // the attribute is a per-device setting
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
@@ -715,7 +748,7 @@ static cudaError_t launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, c
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(n_tiles, m_tiles, nsplit);
   cfg.blockDim = dim3(192, 1, 1);
-  cfg.dynamicSmemBytes = kSmem;
+  cfg.dynamicSmemBytes = smem_now;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
   int nattr = 0;
@@ -733,7 +766,7 @@ static cudaError_t launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, c
   }
   cfg.attrs = attr;
   cfg.numAttrs = nattr;
-  return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p);
+  return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, pp);
 }
 
 template <int TN, bool DUAL, int COMM = COMM_NONE>
