@@ -20,7 +20,6 @@ enum KernelStatus : int {
   kStatusAccumTimeout = 3,      // epilogue never saw the accumulator commit
   kStatusPeerFlagTimeout = 4,   // a flag another GPU should have written never arrived
   kStatusBadArgument = 5,
-  kStatusClusterReduceTimeout = 6,  // split-K partials of a cluster peer never landed
 };
 
 // ~2 s at 1.9 GHz; long enough for any legitimate wait, short enough to keep the context usable.
@@ -89,17 +88,6 @@ __device__ __forceinline__ uint32_t mapa_shared(uint32_t smem_addr, uint32_t ran
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
   return r;
 }
-// Bulk copy of `bytes` (multiple of 16, both addresses 16-byte aligned) from this CTA's shared memory into the shared
-// memory of a CTA of the cluster; the bytes are counted on an mbarrier of the DESTINATION CTA. Not a TMA tensor load and
-// not a multicast: one source, one destination, both on this GPU.
-__device__ __forceinline__ void bulk_copy_to_cluster(uint32_t dst_cluster_addr, uint32_t src_cta_addr, uint32_t bytes,
-                                                     uint32_t mbar_cluster_addr) {
-  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                   dst_cluster_addr),
-               "r"(src_cta_addr), "r"(bytes), "r"(mbar_cluster_addr)
-               : "memory");
-}
-
 // ---------------------------------------------------------------- TMA (no multicast anywhere)
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");

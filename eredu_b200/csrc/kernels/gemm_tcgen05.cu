@@ -18,6 +18,8 @@
 // Replaces the reference's dense matmul call sites (eredu-architectures/src/llama.rs:270-286,
 // 418-431; eredu/src/backend/mlx/nn/parallel.rs:794-796) and its silu(gate)*up composition
 // (eredu/src/backend/mlx/nn/layers.rs:21-24).
+#include <cooperative_groups.h>
+
 #include "../common/launch.h"
 #include "../common/launch_count.h"
 #include "../common/peer.cuh"
@@ -25,6 +27,8 @@
 #include "../common/tma_host.h"
 #include "../common/trace.cuh"
 #include "gemm_persistent.h"
+
+namespace cg = cooperative_groups;
 
 namespace eredu {
 
@@ -64,14 +68,14 @@ struct GemmParams {
   // rest prefetched into L2, BEFORE the kernel waits for its producer under programmatic dependent launch, so
   // the weight stream of this kernel overlaps the tail of the previous one.
   int w_static;
-  int nstages;     // depth of the operand ring (2..8): chosen by the launcher from the grid size and the split count
   PeerComm comm;   // COMM modes only
 };
 
 // Collective fused into the epilogue (tensor parallelism over NVLink peer memory, small token counts):
-//   COMM_AR: every rank holds a K-slice; partial tiles are pushed to all peers' staging slots as they
-//            leave TMEM as 8-byte {bf16x2, sequence tag} words (no fence, no flag), and each rank sums the
-//            `size` partials in rank order (bitwise identical on all ranks), adds bias/residual once and stores.
+//   COMM_AR: every rank holds a K-slice; partial tiles are pushed to all peers' slots as they leave TMEM, as 4-byte
+//            bf16x2 words into a sentinel-initialised region (a word is valid once it differs from the sentinel: no
+//            tag, no fence, no flag - the whole word is payload), and each rank sums the `size` partials in rank
+//            order (bitwise identical on all ranks), adds bias/residual once and stores.
 //   COMM_AG: every rank holds an N-slice; finished tiles are stored straight into every peer's gathered
 //            output at the rank's column offset.
 enum { COMM_NONE = 0, COMM_AR = 1, COMM_AG = 2 };
@@ -83,27 +87,16 @@ struct GemmCfg {
   static constexpr int kATile = 128 * 64 * 2;
   static constexpr int kBTile = TN * 64 * 2;
   static constexpr int kStageBytes = kATile * (DUAL ? 2 : 1) + kBTile;
-  static constexpr int kMaxStages = 8;
+  // Decode-sized tiles keep shared memory under half an SM so that two CTAs are co-resident: the whole grid
+  // (<= 296 CTAs) then runs as one wave and HBM bandwidth is shared evenly instead of paying a partial wave.
+  static constexpr int kBudget = (TN <= 32) ? (DUAL ? 3 * kStageBytes : 100 * 1024) : (TN == 64 && !DUAL) ? 100 * 1024 : 196 * 1024;
+  static constexpr int kStagesRaw = kBudget / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kAccCols = TN * (DUAL ? 2 : 1);
   static constexpr int kTmemCols = kAccCols <= 32 ? 32 : kAccCols <= 64 ? 64 : kAccCols <= 128 ? 128 : kAccCols <= 256 ? 256 : 512;
   static constexpr int kCtrlBytes = 1024;
-  // Split-K partials of the cluster peers land here (one chunk per source CTA), outside the operand ring: a fast peer
-  // may deliver while this CTA's tensor core still reads its ring.
-  static constexpr int kRecvBytes = kAccCols * 128 * 4;
-  // A grid of more CTAs than SMs keeps decode-sized tiles under half an SM of shared memory so that two CTAs are
-  // co-resident: the whole grid (<= 296 CTAs) then runs as one wave and HBM bandwidth is shared evenly instead of paying
-  // a partial wave. A grid that fits the SMs once takes the deep ring: with one CTA per SM the bytes in flight per SM are
-  // what the ring holds, and a K slice that fits the ring is fetched entirely before the stream dependency resolves.
-  static constexpr int kSmallBudget = 110 * 1024, kBigBudget = 200 * 1024;
-  static constexpr int stages(bool split, bool one_wave) {
-    const int budget = (one_wave || !(TN <= 32 || (TN == 64 && !DUAL))) ? kBigBudget : kSmallBudget;
-    int n = (budget - 1024 - kCtrlBytes - (split ? kRecvBytes : 0)) / kStageBytes;
-    return n > kMaxStages ? kMaxStages : n;
-  }
-  static constexpr int smem_bytes(bool split, int nstages) {
-    return 1024 + kCtrlBytes + nstages * kStageBytes + (split ? kRecvBytes : 0);
-  }
-  static_assert(stages(false, false) >= 2 && (TN > 64 || stages(true, false) >= 2), "pipeline too shallow");  // split-K: TN <= 64 only
+  static constexpr int kSmemBytes = 1024 + kCtrlBytes + kStages * kStageBytes;
+  static_assert(kStages >= 2, "pipeline too shallow");
 };
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
@@ -117,58 +110,59 @@ __device__ __forceinline__ float gated_act(const GemmParams& p, float g, float u
   return silu_f(g) * u;
 }
 
+// Applies row scale, bias, activation and residual, stores, and returns the value as stored (after rounding).
 __device__ __forceinline__ float residual_at(const GemmParams& p, int m, int n) {
   return __bfloat162float(static_cast<const __nv_bfloat16*>(p.residual)[static_cast<size_t>(m) * p.ldr + n]);
 }
 
-// Sums each of 8 per-lane values over the 32 lanes of a warp with 9 shuffles (instead of 40): halves of the value set are
-// exchanged while the lane distance shrinks. On return every lane holds the warp total of value index `which`
-// (= lane bits 4, 3, 2 read as a 3-bit number); the lanes with lane % 4 == 0 cover the 8 values once.
-__device__ __forceinline__ float warp_sum8(const float (&v)[8], int lane, int& which) {
-  float w[4], x[2];
-  const bool h16 = lane & 16, h8 = lane & 8, h4 = lane & 4;
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const float keep = h16 ? v[j + 4] : v[j], send = h16 ? v[j] : v[j + 4];
-    w[j] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+// `rv`: the residual value of the element (0 when there is none), loaded by the caller ahead of time so that
+// the load does not sit between two dependent stores.
+template <bool DUAL>
+__device__ __forceinline__ float epilogue_store(const GemmParams& p, float g, float u, int m, int n, float scale, float rv) {
+  g *= scale;
+  if (DUAL) u *= scale;
+  if (p.bias != nullptr) {
+    const __nv_bfloat16* b = static_cast<const __nv_bfloat16*>(p.bias);
+    g += __bfloat162float(b[n]);
+    if (DUAL) u += __bfloat162float(b[p.N + n]);
   }
-#pragma unroll
-  for (int j = 0; j < 2; ++j) {
-    const float keep = h8 ? w[j + 2] : w[j], send = h8 ? w[j] : w[j + 2];
-    x[j] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+  float v = (DUAL ? gated_act(p, g, u) : g) + rv;
+  if (p.out_fp32) {
+    static_cast<float*>(p.y)[static_cast<size_t>(m) * p.ldy + n] = v;
+    return v;
   }
-  const float keep = h4 ? x[1] : x[0], send = h4 ? x[0] : x[1];
-  float y = keep + __shfl_xor_sync(0xffffffffu, send, 4);
-  y += __shfl_xor_sync(0xffffffffu, y, 2);
-  y += __shfl_xor_sync(0xffffffffu, y, 1);
-  which = (h16 ? 4 : 0) + (h8 ? 2 : 0) + (h4 ? 1 : 0);
-  return y;
+  const __nv_bfloat16 r = __float2bfloat16(v);
+  static_cast<__nv_bfloat16*>(p.y)[static_cast<size_t>(m) * p.ldy + n] = r;
+  return __bfloat162float(r);
 }
 
-// Split-K as a thread-block cluster along z. Token columns are owned in contiguous runs of cw = TN / nsplit: CTA `o`
-// finishes columns [o * cw, (o + 1) * cw). Every CTA stages its whole fp32 partial in shared memory in owner-major
-// order ([owner][gate | up][cw][128 rows]) and PUSHES owner o's chunk into o's receive area with one bulk
-// shared-to-shared copy counted on o's mbarrier; o then sums the chunks in cluster-rank order from its own shared memory
-// (bitwise deterministic, no atomics, no global scratch). One split cluster barrier brackets the exchange: the first half
-// makes the receive barriers visible before anyone pushes, the second keeps every CTA resident until its pushes landed.
+// COMM_AG: the finished value goes straight into every peer's gathered output.
+template <int COMM>
+__device__ __forceinline__ void comm_emit(const GemmParams& p, int parity, float g, int m, int n, float scale) {
+  (void)parity;
+  float v = g * scale;
+  if (p.bias != nullptr) v += __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[n]);
+  const size_t idx = static_cast<size_t>(m) * p.ldy + p.col_offset + n;
+  for (int peer = 0; peer < p.comm.size; ++peer) {
+    uint8_t* out = p.comm.base[peer] + p.comm.out_off;
+    if (p.out_fp32) reinterpret_cast<float*>(out)[idx] = v;
+    else reinterpret_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16(v);
+  }
+}
+
 template <int TN, bool DUAL, bool SPLIT, int COMM>
 __global__ void __launch_bounds__(192, 1)
-gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
-               const __grid_constant__ GemmParams p) {
+gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, GemmParams p) {
   using Cfg = GemmCfg<TN, DUAL>;
-  constexpr int C2 = DUAL ? 2 : 1;
-  const int kStages = p.nstages;
   pdl_launch_early();
   trace_mark(kTraceGemm, kTraceStart);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem);            // [kMaxStages]
-  uint64_t* empty_bar = full_bar + Cfg::kMaxStages;                  // [kMaxStages]
-  uint64_t* accum_bar = empty_bar + Cfg::kMaxStages;                 // [1]
-  uint64_t* red_bar = accum_bar + 1;                                 // [1] split-K chunks of the cluster peers
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(red_bar + 1);    // [1]
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem);            // [kStages]
+  uint64_t* empty_bar = full_bar + Cfg::kStages;                     // [kStages]
+  uint64_t* accum_bar = empty_bar + Cfg::kStages;                    // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);  // [1]
   uint8_t* stages = smem + Cfg::kCtrlBytes;
-  float* recv = reinterpret_cast<float*>(stages + kStages * Cfg::kStageBytes);  // SPLIT: [src][chunk]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -177,18 +171,33 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   int m_base = tile_m * TN;   // first token row of this tile
   int m_limit = p.M;          // rows >= m_limit are not stored
   int w_row0 = tile_n * 128;  // first weight row of this tile
+  if (p.work != nullptr) {
+    pdl_wait();  // the work table comes from the routing kernels
+    const int4 item = reinterpret_cast<const int4*>(p.work)[tile_m];
+    if (item.z <= 0) return;  // uniform over the CTA (and over its cluster: same blockIdx.y)
+    m_base = item.y;
+    m_limit = item.y + item.z;
+    w_row0 += item.x * p.w_rows_per_expert;
+    if (p.bias != nullptr)
+      p.bias = static_cast<const __nv_bfloat16*>(p.bias) + static_cast<size_t>(item.x) * p.bias_expert_stride;
+  }
   const int nsplit = SPLIT ? gridDim.z : 1;
   const int split = SPLIT ? blockIdx.z : 0;
+
+  const int kblocks = (p.K + 63) >> 6;
+  const int kb_per = (kblocks + nsplit - 1) / nsplit;
+  const int kb0 = split * kb_per;
+  const int kb1 = min(kblocks, kb0 + kb_per);
+  const int niter = max(0, kb1 - kb0);
 
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tmW);
     tma_prefetch_desc(&tmX);
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < Cfg::kStages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
     mbar_init(accum_bar, 1);
-    mbar_init(red_bar, 1);
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -199,31 +208,11 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  if (SPLIT) cluster_arrive_release();  // first half: this CTA's receive barrier exists
   const uint32_t tmem_base = *tmem_slot;
-
-  const __nv_bfloat16* bias = static_cast<const __nv_bfloat16*>(p.bias);
-  bool live = true;  // grouped mode: work items without rows do nothing (uniform over the CTA and its cluster)
-  if (p.work != nullptr) {
-    pdl_wait();  // the work table comes from the routing kernels
-    const int4 item = reinterpret_cast<const int4*>(p.work)[tile_m];
-    live = item.z > 0;
-    m_base = item.y;
-    m_limit = item.y + item.z;
-    w_row0 += item.x * p.w_rows_per_expert;
-    if (bias != nullptr) bias += static_cast<size_t>(item.x) * p.bias_expert_stride;
-  }
-
-  const int kblocks = (p.K + 63) >> 6;
-  const int kb_per = (kblocks + nsplit - 1) / nsplit;
-  const int kb0 = split * kb_per;
-  const int kb1 = min(kblocks, kb0 + kb_per);
-  const int niter = live ? max(0, kb1 - kb0) : 0;
-
   // Weight tiles do not depend on the producer kernels: start them before the wait.
   int n_pre = 0;
   if (p.w_static && p.work == nullptr) {
-    n_pre = min(niter, kStages);
+    n_pre = min(niter, Cfg::kStages);
     if (warp == 0 && lane == 0) {
       const uint64_t pol_w = l2_policy_evict_first();
       for (int it = 0; it < niter; ++it) {
@@ -256,8 +245,8 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       int issued = n_pre;
       bool ok = true;
       for (int it = 0; it < niter && ok; ++it) {
-        const int s = it % kStages;
-        const uint32_t ph = (it / kStages) & 1;
+        const int s = it % Cfg::kStages;
+        const uint32_t ph = (it / Cfg::kStages) & 1;
         uint8_t* a = stages + s * Cfg::kStageBytes;
         const int kx = (kb0 + it) * 64;
         if (it >= n_pre) {  // the first n_pre stages already hold (or are receiving) their weight tiles
@@ -267,13 +256,15 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           tma_load_2d_hint(a, &tmW, kx, w_row0, &full_bar[s], pol_w);
           if (DUAL) tma_load_2d_hint(a + Cfg::kATile, &tmW, kx, p.dual_row_offset + w_row0, &full_bar[s], pol_w);
         }
-        tma_load_2d_hint(a + Cfg::kATile * C2, &tmX, kx, m_base, &full_bar[s], pol_x);
+        tma_load_2d_hint(a + Cfg::kATile * (DUAL ? 2 : 1), &tmX, kx, m_base, &full_bar[s], pol_x);
         issued = it + 1;
       }
       if (!ok) {
         // Give up cleanly: wait (bounded) for the copies still in flight before shared memory dies.
-        const int first = max(0, issued - kStages);
-        for (int it = first; it < issued; ++it) mbar_wait(&full_bar[it % kStages], (it / kStages) & 1, nullptr, 0);
+        const int first = max(0, issued - Cfg::kStages);
+        for (int it = first; it < issued; ++it) {
+          mbar_wait(&full_bar[it % Cfg::kStages], (it / Cfg::kStages) & 1, nullptr, 0);
+        }
       }
     }
   } else if (warp == 1) {
@@ -282,17 +273,17 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       constexpr uint32_t idesc = umma_idesc_bf16(128, TN);
       bool ok = true;
       for (int it = 0; it < niter; ++it) {
-        const int s = it % kStages;
-        const uint32_t ph = (it / kStages) & 1;
+        const int s = it % Cfg::kStages;
+        const uint32_t ph = (it / Cfg::kStages) & 1;
         ok = mbar_wait(&full_bar[s], ph, p.status, kStatusTmaFullTimeout);
         if (!ok) break;
-        if (it == 0) trace_mark_thread(kTraceGemm, 3, 32);          // first operands landed
+        if (it == 0) trace_mark_thread(kTraceGemm, 3, 32);       // first operands landed
         if (it == niter - 1) trace_mark_thread(kTraceGemm, 4, 32);  // last operands landed
         tc_fence_after_sync();
         const uint32_t a_addr = smem_u32(stages + s * Cfg::kStageBytes);
         const uint64_t da = umma_desc_k_sw128(a_addr);
         const uint64_t da2 = umma_desc_k_sw128(a_addr + Cfg::kATile);
-        const uint64_t db = umma_desc_k_sw128(a_addr + Cfg::kATile * C2);
+        const uint64_t db = umma_desc_k_sw128(a_addr + Cfg::kATile * (DUAL ? 2 : 1));
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
@@ -311,79 +302,49 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   const int row = q * 32 + lane;
   const int n = tile_n * 128 + row;
   bool acc_ok = false;
-  float* stage = reinterpret_cast<float*>(stages);  // staged partial / staged tile, aliases the (drained) ring
+  float* red = reinterpret_cast<float*>(stages);  // SPLIT: [DUAL?2:1][TN][128] fp32, aliases the ring
 
   __shared__ float s_scale[TN];
   __shared__ float s_ssq[4][TN];
   const int et = threadIdx.x - 64;  // epilogue thread index 0..127 (warps 2..5)
   const bool in_n = n < p.N;
   constexpr bool kCanStage = (TN >= 64) && !SPLIT && COMM == COMM_NONE;
-  const int m_end = live ? min(TN, m_limit - m_base) : 0;
-  // Columns (tokens) of the tile whose final value this CTA produces.
-  const int cw = TN / nsplit;
-  const int own_lo = split * cw;
-  const int own_hi = min(m_end, own_lo + cw);
-  const bool has_work = own_lo < m_end;
-  const int chunk_floats = C2 * cw * 128;  // one owner's share of a staged partial
+  // Columns (tokens) of the tile whose final value this CTA produces: all of them, or with cluster split-K
+  // every nsplit-th one (COMM_AR: every nsplit-th PAIR of columns, because partials travel as bf16x2).
+  const int m_end = min(TN, m_limit - m_base);
+  const int own_first = SPLIT ? split : 0, own_step = SPLIT ? nsplit : 1;
   constexpr int kPre = 8;
-  float rpre[kPre];
+  float rpre[2 * kPre];
 #pragma unroll
-  for (int j = 0; j < kPre; ++j) rpre[j] = 0.f;
+  for (int j = 0; j < 2 * kPre; ++j) rpre[j] = 0.f;
   const bool has_res = p.residual != nullptr && in_n;
 
-  // Final values of this thread's row: stored (or handed to the gather), their squares added to the per-column sums kept
-  // for a following RMSNorm. Executed by whole warps.
-  // Eight consecutive columns [c0, c0 + 8) at once: all values first, then the stores, then ONE butterfly for the eight
-  // sums of squares - independent work the scheduler can overlap, instead of a dependent chain per column.
-  const float bias_g = (bias != nullptr && in_n) ? __bfloat162float(bias[n]) : 0.f;
-  const float bias_u = (DUAL && bias != nullptr && in_n) ? __bfloat162float(bias[p.N + n]) : 0.f;
-  auto finish8 = [&](const float (&g)[8], const float (&u)[8], const float (&rv)[8], int c0, int c_hi) {
-    float val[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int c = min(c0 + j, TN - 1);
+  // Final value of element (column c of the tile, this thread's row): store it (or hand it to the
+  // collective) and add its square to the per-column sum kept for a following RMSNorm. Executed by whole warps.
+  auto finish = [&](float g, float u, int c, bool valid, float rv) {
+    const int m = m_base + c;
+    const bool ok = valid && in_n && m < m_limit;
+    float v = 0.f;
+    if (ok) {
       const float sc = (p.ssq_in != nullptr) ? s_scale[c] : 1.f;
-      const float gg = g[j] * sc + bias_g;
-      float v = (DUAL ? gated_act(p, gg, u[j] * sc + bias_u) : gg) + rv[j];
-      if (!p.out_fp32 && COMM != COMM_AG) v = __bfloat162float(__float2bfloat16(v));
-      val[j] = v;
+      if (COMM == COMM_NONE) v = epilogue_store<DUAL>(p, g, u, m, n, sc, rv);
+      else comm_emit<COMM>(p, parity, g, m, n, sc);
     }
+    if (COMM == COMM_NONE && p.ssq_out != nullptr) {
+      float sq = v * v;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int c = c0 + j, m = m_base + c;
-      if (c < c_hi && in_n) {
-        if (COMM == COMM_AG) {
-          const size_t idx = static_cast<size_t>(m) * p.ldy + p.col_offset + n;
-#pragma unroll
-          for (int peer = 0; peer < kMaxRanks; ++peer) {
-            if (peer < p.comm.size) {
-              uint8_t* out = p.comm.base[peer] + p.comm.out_off;
-              if (p.out_fp32) reinterpret_cast<float*>(out)[idx] = val[j];
-              else reinterpret_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16(val[j]);
-            }
-          }
-        } else if (p.out_fp32) {
-          static_cast<float*>(p.y)[static_cast<size_t>(m) * p.ldy + n] = val[j];
-        } else {
-          static_cast<__nv_bfloat16*>(p.y)[static_cast<size_t>(m) * p.ldy + n] = __float2bfloat16(val[j]);
-        }
-      }
-    }
-    if (COMM != COMM_AG && p.ssq_out != nullptr) {
-      float sq[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) sq[j] = (c0 + j < c_hi && in_n) ? val[j] * val[j] : 0.f;
-      int which;
-      const float total = warp_sum8(sq, lane, which);
-      if ((lane & 3) == 0 && c0 + which < TN) s_ssq[q][c0 + which] = total;
+      for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+      if (lane == 0) s_ssq[q][c] = sq;
     }
   };
-  // After the owned columns [c_lo, c_hi) went through finish(): publish the per-row partial sums of squares.
-  auto publish_ssq = [&](int c_lo, int c_hi) {
+  // After every owned column went through finish(): publish the per-row partial sums of squares.
+  auto publish_ssq = [&](int c_first, int c_step) {
     if (p.ssq_out == nullptr) return;
     epi_barrier();
-    for (int c = c_lo + et; c < c_hi; c += 128)
-      p.ssq_out[static_cast<size_t>(m_base + c) * gridDim.x + tile_n] = s_ssq[0][c] + s_ssq[1][c] + s_ssq[2][c] + s_ssq[3][c];
+    for (int c = et; c < TN; c += 128) {
+      if (c >= c_first && (c - c_first) % c_step == 0 && m_base + c < m_limit)
+        p.ssq_out[static_cast<size_t>(m_base + c) * gridDim.x + tile_n] = s_ssq[0][c] + s_ssq[1][c] + s_ssq[2][c] + s_ssq[3][c];
+    }
   };
 
   if (warp >= 2) {
@@ -398,12 +359,20 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       }
       epi_barrier();
     }
-    // Residual values of the first owned columns: the loads are in flight while the tensor cores work, instead of one
-    // dependent load per finished column.
-    if (has_res && (SPLIT || COMM == COMM_AR)) {
+    // Residual values of the first kPre columns (COMM_AR: column pairs) this thread will finish: the loads are
+    // in flight while the tensor cores work, instead of one dependent load per finished column.
+    if (has_res) {
 #pragma unroll
-      for (int j = 0; j < kPre; ++j)
-        if (own_lo + j < own_hi) rpre[j] = residual_at(p, m_base + own_lo + j, n);
+      for (int j = 0; j < kPre; ++j) {
+        if (COMM == COMM_AR) {
+          const int c = 2 * (own_first + j * own_step);
+          if (c < m_end) rpre[2 * j] = residual_at(p, m_base + c, n);
+          if (c + 1 < m_end) rpre[2 * j + 1] = residual_at(p, m_base + c + 1, n);
+        } else if (SPLIT) {
+          const int c = own_first + j * own_step;
+          if (c < m_end) rpre[j] = residual_at(p, m_base + c, n);
+        }
+      }
     }
     acc_ok = (niter > 0) && mbar_wait(accum_bar, 0, p.status, kStatusAccumTimeout);
     acc_ok = __all_sync(0xffffffffu, acc_ok);
@@ -419,49 +388,38 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         if (DUAL) tmem_ld16(taddr + TN + c0, u);
         tmem_wait_ld();
         if (SPLIT || COMM == COMM_AR) {
-          // owner-major staging: [owner][gate | up][cw][128]
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const int c = c0 + j;
-            const int o = c / cw, cc = c - o * cw;
-            float* dst = stage + (static_cast<size_t>(o) * C2 * cw + cc) * 128 + row;
-            dst[0] = __uint_as_float(g[j]);
-            if (DUAL) dst[cw * 128] = __uint_as_float(u[j]);
+            red[(c0 + j) * 128 + row] = __uint_as_float(g[j]);
+            if (DUAL) red[(TN + c0 + j) * 128 + row] = __uint_as_float(u[j]);
           }
         } else if (kCanStage && p.staged) {
           // value before the residual, fp32, [column][row]: conflict-free writes, coalesced second pass
           float bg = 0.f, bu = 0.f;
-          if (bias != nullptr && in_n) {
-            bg = __bfloat162float(bias[n]);
-            if (DUAL) bu = __bfloat162float(bias[p.N + n]);
+          if (p.bias != nullptr && in_n) {
+            const __nv_bfloat16* b = static_cast<const __nv_bfloat16*>(p.bias);
+            bg = __bfloat162float(b[n]);
+            if (DUAL) bu = __bfloat162float(b[p.N + n]);
           }
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const float sc = (p.ssq_in != nullptr) ? s_scale[c0 + j] : 1.f;
             const float gg = __uint_as_float(g[j]) * sc + bg;
-            stage[(c0 + j) * 128 + row] = DUAL ? gated_act(p, gg, __uint_as_float(u[j]) * sc + bu) : gg;
+            red[(c0 + j) * 128 + row] = DUAL ? gated_act(p, gg, __uint_as_float(u[j]) * sc + bu) : gg;
           }
         } else {
+          float rr[16];
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            if (c0 + 8 * h < m_end) {  // warp-uniform
-              float g8[8], u8[8], r8[8];
+          for (int j = 0; j < 16; ++j) rr[j] = (has_res && c0 + j < m_end) ? residual_at(p, m_base + c0 + j, n) : 0.f;
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                g8[j] = __uint_as_float(g[8 * h + j]);
-                u8[j] = DUAL ? __uint_as_float(u[8 * h + j]) : 0.f;
-                r8[j] = (has_res && c0 + 8 * h + j < m_end) ? residual_at(p, m_base + c0 + 8 * h + j, n) : 0.f;
-              }
-              finish8(g8, u8, r8, c0 + 8 * h, m_end);
-            }
-          }
+          for (int j = 0; j < 16; ++j) finish(__uint_as_float(g[j]), DUAL ? __uint_as_float(u[j]) : 0.f, c0 + j, true, rr[j]);
         }
       }
     }
     if (kCanStage && p.staged) {
       epi_barrier();  // the whole tile is staged (or the accumulator never arrived: nothing is stored)
       if (acc_ok) {
-        const int m_cnt = m_end;
+        const int m_cnt = min(TN, m_limit - m_base);
         const int limit = (m_cnt * 16 + 31) & ~31;  // 16 chunks of 8 columns per token row; warp-uniform bound
         const __nv_bfloat16* res = static_cast<const __nv_bfloat16*>(p.residual);
         __nv_bfloat16* yout = static_cast<__nv_bfloat16*>(p.y);
@@ -482,8 +440,8 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             const int ch = ch0 + 128 * b;
             if (ch >= limit) break;  // warp-uniform
             const int c = ch >> 4, n0 = (ch & 15) * 8;
-            const float4 a0 = *reinterpret_cast<const float4*>(stage + c * 128 + n0);
-            const float4 a1 = *reinterpret_cast<const float4*>(stage + c * 128 + n0 + 4);
+            const float4 a0 = *reinterpret_cast<const float4*>(red + c * 128 + n0);
+            const float4 a1 = *reinterpret_cast<const float4*>(red + c * 128 + n0 + 4);
             const uint32_t r[4] = {rv[b].x, rv[b].y, rv[b].z, rv[b].w};
             uint4 o;
             o.x = pack_bf16x2(a0.x + bf16_lo(r[0]), a0.y + bf16_hi(r[0]));
@@ -505,128 +463,148 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           }
         }
       }
-    } else if (!SPLIT && COMM != COMM_AR) {
-      if (COMM == COMM_NONE) publish_ssq(0, m_end);
+    } else if (!SPLIT && COMM == COMM_NONE) {
+      publish_ssq(0, 1);
     }
   }
 
-  // ------------------------------------------------------------ split-K exchange (every thread of the cluster passes here)
-  bool red_ok = true;
   if (SPLIT) {
-    if (warp >= 2) {
-      fence_proxy_async_smem();  // the staged partial becomes visible to the bulk-copy engine
-      epi_barrier();
-    }
-    trace_mark_thread(kTraceGemm, 6, 64);  // partial staged
-    cluster_wait_acquire();                // every receive barrier of the cluster is initialised
-    if (warp >= 2) {
-      const uint32_t chunk_bytes = static_cast<uint32_t>(chunk_floats) * 4u;
-      if (acc_ok && et < nsplit && et != split && et * cw < m_end) {
-        // one bulk copy per owner with work: my chunk for owner `et` into its receive slot [split]
-        const uint32_t dst = mapa_shared(smem_u32(recv + static_cast<size_t>(split) * chunk_floats), et);
-        bulk_copy_to_cluster(dst, smem_u32(stage + static_cast<size_t>(et) * chunk_floats), chunk_bytes,
-                             mapa_shared(smem_u32(red_bar), et));
-      }
-      if (has_work) {
-        if (et == 0) mbar_arrive_expect_tx(red_bar, static_cast<uint32_t>(nsplit - 1) * chunk_bytes);
-        red_ok = mbar_wait(red_bar, 0, p.status, kStatusClusterReduceTimeout);
-        red_ok = __all_sync(0xffffffffu, red_ok);
-      }
-    }
-    trace_mark_thread(kTraceGemm, 7, 64);  // peers' chunks landed
-    cluster_arrive_release();              // second half: this CTA needs nothing more from its peers
+    // Every thread of every CTA of the cluster reaches both barriers, whatever happened above.
+    cg::cluster_group cluster = cg::this_cluster();
+    trace_mark_thread(kTraceGemm, 6, 64);  // partials staged
+    cluster.sync();
+    trace_mark_thread(kTraceGemm, 7, 64);  // cluster barrier 1 passed
   }
-
-  // Sum of the split partials of column c (this thread's row), in cluster-rank order.
-  auto reduced = [&](int c, float& g, float& u) {
-    const int cc = c - own_lo;
-    g = 0.f;
-    u = 0.f;
-    if (SPLIT) {
-#pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        if (r < nsplit) {
-          const float* src = (r == split ? stage + static_cast<size_t>(split) * chunk_floats
-                                         : recv + static_cast<size_t>(r) * chunk_floats) + cc * 128 + row;
-          g += src[0];
-          if (DUAL) u += src[cw * 128];
-        }
-      }
-    } else {
-      g = stage[c * 128 + row];
-      if (DUAL) u = stage[(cw + c) * 128 + row];
-    }
-  };
-
   if (COMM == COMM_AR) {
-    // ---- all-reduce over the tensor-parallel ranks, one shot: every finished pair of token columns travels as one
-    // 4-byte bf16x2 word into each peer's sentinel-initialised slot (no tag, no flag, no fence); each rank then sums the
-    // `size` words per element in rank order (bitwise identical everywhere), adds bias / residual once and stores.
-    // (has_work is uniform over the CTA: every epilogue warp reaches the barrier inside publish_ssq, whatever its waits said)
-    if (warp >= 2 && has_work) {
-     if (acc_ok && red_ok) {
-      for (int c = own_lo; c < own_hi; c += 2) {
-        float g0, g1, u0, u1;
-        reduced(c, g0, u0);
-        reduced(c + 1, g1, u1);  // column m_end (odd token count) is zero-filled: harmless
+    // ---- all-reduce, one shot: every partial pair of token columns is one 4-byte bf16x2 word stored into each
+    // peer's sentinel-initialised slot; a word is complete when it differs from the sentinel, so there is no fence,
+    // no flag and no barrier between the tensor-core tile and the reduction.
+    if (warp >= 2) {
+      cg::cluster_group cluster = cg::this_cluster();
+      const int p_first = SPLIT ? split : 0, p_step = SPLIT ? nsplit : 1;
+      for (int pi = p_first; 2 * pi < m_end; pi += p_step) {
+        float g0 = 0.f, g1 = 0.f;
+        if (SPLIT) {
+          float a0[8], a1[8];
+#pragma unroll
+          for (int r = 0; r < 8; ++r) {
+            const float* peer = cluster.map_shared_rank(red, r < nsplit ? r : 0);
+            a0[r] = (r < nsplit) ? peer[(2 * pi) * 128 + row] : 0.f;
+            a1[r] = (r < nsplit) ? peer[(2 * pi + 1) * 128 + row] : 0.f;
+          }
+#pragma unroll
+          for (int r = 0; r < 8; ++r) {
+            g0 += a0[r];
+            g1 += a1[r];
+          }
+        } else {
+          g0 = red[(2 * pi) * 128 + row];
+          g1 = red[(2 * pi + 1) * 128 + row];
+        }
         if (in_n) {
           const uint32_t packed = lamport_payload(pack_bf16x2(g0, g1));
-          const size_t word = (static_cast<size_t>((m_base + c) >> 1) * p.N + n) * 4;
-          const size_t mine = (static_cast<size_t>(parity) * kMaxRanks + p.comm.rank) * p.comm.lam_bytes + word;
-#pragma unroll
-          for (int peer = 0; peer < kMaxRanks; ++peer) {
-            if (peer < p.comm.size)
-              asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(p.comm.base[peer] + p.comm.lam_off + mine), "r"(packed) : "memory");
+          const size_t word = (static_cast<size_t>(m_base / 2 + pi) * p.N + n) * 4;
+          for (int peer = 0; peer < p.comm.size; ++peer) {
+            asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(lamport_slot(p.comm, peer, parity, p.comm.rank) + word),
+                         "r"(packed)
+                         : "memory");
           }
         }
       }
-      // Pairs are collected four at a time: the first poll of a batch issues every (pair, source rank) load before any
-      // word is looked at, so one memory round trip usually brings all 32 words; stragglers are re-polled.
-      constexpr int kPB = 4;
-      static_assert(kPre == 2 * kPB, "the residual prefetch covers exactly the first batch of pairs");
-      uint8_t* my_lam = p.comm.base[0];  // this rank's own buffer, picked without a run-time index
+    }
+  } else if (SPLIT) {
+    if (warp >= 2) {
+      cg::cluster_group cluster = cg::this_cluster();
+      const float* peers[8];
 #pragma unroll
-      for (int r = 1; r < kMaxRanks; ++r)
-        if (r == p.comm.rank) my_lam = p.comm.base[r];
-      my_lam += p.comm.lam_off + static_cast<size_t>(parity) * kMaxRanks * p.comm.lam_bytes;
-      for (int c0 = own_lo; c0 < own_hi; c0 += 2 * kPB) {
+      for (int r = 0; r < 8; ++r) peers[r] = cluster.map_shared_rank(red, r < nsplit ? r : 0);
+      // all remote loads of a column are issued together; the sum runs in cluster-rank order (deterministic)
+      auto reduce_col = [&](int c, float& g, float& u) {
+        float pg[8], pu[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          pg[r] = (r < nsplit) ? peers[r][c * 128 + row] : 0.f;
+          if (DUAL) pu[r] = (r < nsplit) ? peers[r][(TN + c) * 128 + row] : 0.f;
+        }
+        g = 0.f;
+        u = 0.f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          g += pg[r];
+          if (DUAL) u += pu[r];
+        }
+      };
+#pragma unroll
+      for (int j = 0; j < kPre; ++j) {
+        const int c = split + j * nsplit;
+        if (c < m_end) {  // warp-uniform
+          float g, u;
+          reduce_col(c, g, u);
+          finish(g, u, c, true, rpre[j]);
+        }
+      }
+      for (int c = split + kPre * nsplit; c < m_end; c += nsplit) {
+        float g, u;
+        reduce_col(c, g, u);
+        finish(g, u, c, true, has_res ? residual_at(p, m_base + c, n) : 0.f);
+      }
+      if (COMM == COMM_NONE) publish_ssq(split, nsplit);
+    }
+  }
+  if (SPLIT) {
+    cg::cluster_group cluster = cg::this_cluster();
+    trace_mark_thread(kTraceGemm, 8, 64);  // reduced and stored
+    cluster.sync();
+    trace_mark_thread(kTraceGemm, 9, 64);  // cluster barrier 2 passed
+  }
+
+  if (COMM == COMM_AR) {
+    if (warp >= 2) {
+      const int p_first = SPLIT ? split : 0, p_step = SPLIT ? nsplit : 1;
+      // Pairs are collected four at a time: the first poll of a chunk issues every (pair, source rank) load before
+      // any word is looked at, so one memory round trip usually brings all 32 words; stragglers are re-polled. The
+      // single reader of a word writes the sentinel back as soon as it has the value (the slot of this parity is
+      // written again two calls later).
+      constexpr int kPB = 4;
+      for (int pi0 = p_first; 2 * pi0 < m_end; pi0 += kPB * p_step) {
         float r0[kPB], r1[kPB];
-        uint32_t val[kPB][kMaxRanks], miss[kPB];
+        uint32_t lo[kPB][kMaxRanks], miss[kPB];
         size_t word[kPB];
 #pragma unroll
         for (int j = 0; j < kPB; ++j) {
-          const int c = c0 + 2 * j;
-          const bool on = in_n && c < own_hi;
-          miss[j] = on ? (1u << p.comm.size) - 1u : 0u;
-          word[j] = (static_cast<size_t>((m_base + c) >> 1) * p.N + n) * 4;
-          // the first batch took its residual values before the accumulator wait (kPre == 2 * kPB)
-          r0[j] = (on && has_res) ? (c0 == own_lo ? rpre[2 * j] : residual_at(p, m_base + c, n)) : 0.f;
-          r1[j] = (on && has_res && c + 1 < m_end) ? (c0 == own_lo ? rpre[2 * j + 1] : residual_at(p, m_base + c + 1, n)) : 0.f;
+          const int pi = pi0 + j * p_step;
+          const bool live = in_n && 2 * pi < m_end;
+          miss[j] = live ? (1u << p.comm.size) - 1u : 0u;
+          word[j] = (static_cast<size_t>(m_base / 2 + pi) * p.N + n) * 4;
+          r0[j] = (live && has_res) ? residual_at(p, m_base + 2 * pi, n) : 0.f;
+          r1[j] = (live && has_res && 2 * pi + 1 < m_end) ? residual_at(p, m_base + 2 * pi + 1, n) : 0.f;
         }
         const long long t0 = clock64();
         bool first_pass = true;
         while (true) {
+          uint32_t got[kPB][kMaxRanks];
+#pragma unroll
+          for (int j = 0; j < kPB; ++j) {
+#pragma unroll
+            for (int src = 0; src < kMaxRanks; ++src) {
+              got[j][src] = kLamportEmpty;
+              if ((miss[j] >> src) & 1u) {
+                asm volatile("ld.volatile.global.u32 %0, [%1];"
+                             : "=r"(got[j][src])
+                             : "l"(lamport_slot(p.comm, p.comm.rank, parity, src) + word[j])
+                             : "memory");
+              }
+            }
+          }
           uint32_t pending = 0u;
 #pragma unroll
           for (int j = 0; j < kPB; ++j) {
 #pragma unroll
             for (int src = 0; src < kMaxRanks; ++src) {
-              if ((miss[j] >> src) & 1u) {
-                asm volatile("ld.volatile.global.u32 %0, [%1];"
-                             : "=r"(val[j][src])
-                             : "l"(my_lam + static_cast<size_t>(src) * p.comm.lam_bytes + word[j])
-                             : "memory");
-              }
-            }
-          }
-#pragma unroll
-          for (int j = 0; j < kPB; ++j) {
-#pragma unroll
-            for (int src = 0; src < kMaxRanks; ++src) {
-              if (((miss[j] >> src) & 1u) && val[j][src] != kLamportEmpty) {
+              if (((miss[j] >> src) & 1u) && got[j][src] != kLamportEmpty) {
+                lo[j][src] = got[j][src];
                 miss[j] &= ~(1u << src);
-                // the word is consumed: put the "empty" pattern back for the call after next
-                asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(my_lam + static_cast<size_t>(src) * p.comm.lam_bytes + word[j]),
+                asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(lamport_slot(p.comm, p.comm.rank, parity, src) + word[j]),
                              "r"(kLamportEmpty)
                              : "memory");
               }
@@ -640,52 +618,51 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           }
           first_pass = false;
         }
-        float g8[8], u8[8], r8[8];
 #pragma unroll
         for (int j = 0; j < kPB; ++j) {
+          const int pi = pi0 + j * p_step;
+          if (2 * pi >= m_end) break;  // warp-uniform
           float v0 = 0.f, v1 = 0.f;
+          if (in_n) {
 #pragma unroll
-          for (int src = 0; src < kMaxRanks; ++src) {  // rank order: every rank computes the same bits
-            if (src < p.comm.size && !((miss[j] >> src) & 1u)) {
-              v0 += bf16_lo(val[j][src]);
-              v1 += bf16_hi(val[j][src]);
+            for (int src = 0; src < kMaxRanks; ++src) {  // rank order: every rank computes the same bits
+              if (src < p.comm.size && !((miss[j] >> src) & 1u)) {
+                v0 += bf16_lo(lo[j][src]);
+                v1 += bf16_hi(lo[j][src]);
+              }
+            }
+            v0 = epilogue_store<false>(p, v0, 0.f, m_base + 2 * pi, n, 1.f, r0[j]);
+            v1 = (2 * pi + 1 < m_end) ? epilogue_store<false>(p, v1, 0.f, m_base + 2 * pi + 1, n, 1.f, r1[j]) : 0.f;
+          }
+          if (p.ssq_out != nullptr) {
+            float s0 = in_n ? v0 * v0 : 0.f, s1 = in_n ? v1 * v1 : 0.f;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+              s0 += __shfl_xor_sync(0xffffffffu, s0, o);
+              s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+            }
+            if (lane == 0) {
+              s_ssq[q][2 * pi] = s0;
+              if (2 * pi + 1 < TN) s_ssq[q][2 * pi + 1] = s1;
             }
           }
-          g8[2 * j] = v0;
-          g8[2 * j + 1] = v1;
-          u8[2 * j] = u8[2 * j + 1] = 0.f;
-          r8[2 * j] = r0[j];
-          r8[2 * j + 1] = r1[j];
         }
-        finish8(g8, u8, r8, c0, own_hi);
       }
-     }
-      publish_ssq(own_lo, own_hi);
-    }
-  } else if (SPLIT) {
-    if (warp >= 2 && has_work) {
-     if (acc_ok && red_ok) {
-      for (int c0 = own_lo; c0 < own_hi; c0 += 8) {  // warp-uniform
-        float g8[8], u8[8], r8[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int c = min(c0 + j, own_lo + cw - 1);  // columns past the owned run repeat the last one (not stored)
-          reduced(c, g8[j], u8[j]);
-          r8[j] = 0.f;
-          if (has_res) r8[j] = (c0 == own_lo) ? rpre[j] : ((c0 + j < own_hi) ? residual_at(p, m_base + c0 + j, n) : 0.f);
+      // publish the sums of squares of the columns this CTA finished (pairs p_first, p_first + p_step, ...)
+      if (p.ssq_out != nullptr) {
+        epi_barrier();
+        for (int c = et; c < m_end; c += 128) {
+          const int pi = c >> 1;
+          if (pi >= p_first && (pi - p_first) % p_step == 0)
+            p.ssq_out[static_cast<size_t>(m_base + c) * gridDim.x + tile_n] = s_ssq[0][c] + s_ssq[1][c] + s_ssq[2][c] + s_ssq[3][c];
         }
-        finish8(g8, u8, r8, c0, own_hi);
       }
-     }
-      if (COMM == COMM_NONE) publish_ssq(own_lo, own_hi);
     }
-  }
-  trace_mark_thread(kTraceGemm, 8, 64);  // reduced and stored
-
-  if (COMM == COMM_AG) {
+  } else if (COMM == COMM_AG) {
     // ---- all-gather: publish this CTA's stores with one flag per peer, wait for the peers' same tile
     const int flag_id = ((tile_n * gridDim.y + tile_m) * (SPLIT ? 8 : 1) + split) % kMaxFlags;
-    if (warp >= 2 && has_work) {
+    const bool has_share = (SPLIT ? split : 0) < m_end;
+    if (warp >= 2 && has_share) {
       epi_barrier();
       if (et < p.comm.size) {
         __threadfence_system();
@@ -702,24 +679,8 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     __syncwarp();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
-  if (SPLIT) cluster_wait_acquire();  // every peer has received what this CTA pushed: its shared memory may go
-  trace_mark_thread(kTraceGemm, 9, 64);
   if (COMM != COMM_NONE && threadIdx.x == 0) finish_call(p.comm, seq, gridDim.x * gridDim.y * gridDim.z);
   trace_mark(kTraceGemm, kTraceEnd);
-}
-
-constexpr int kMaxGemmDevices = 64;
-
-static int sm_count_of_current_device() {
-  static int cached[kMaxGemmDevices] = {};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxGemmDevices) return 148;
-  if (cached[dev] == 0) {
-    int n = 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    cached[dev] = n;
-  }
-  return cached[dev];
 }
 
 template <int TN, bool DUAL, bool SPLIT, int COMM = COMM_NONE>
@@ -727,28 +688,20 @@ static cudaError_t launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, c
                                int m_tiles, int nsplit, cudaStream_t stream) {
   using Cfg = GemmCfg<TN, DUAL>;
   auto kern = gemm_wt_kernel<TN, DUAL, SPLIT, COMM>;
-  const int kblocks_per_cta = ((p.K + 63) / 64 + nsplit - 1) / nsplit;
-  const bool one_wave = static_cast<long long>(n_tiles) * m_tiles * nsplit <= sm_count_of_current_device();
-  int nstages = Cfg::stages(SPLIT, one_wave);
-  if (nstages > kblocks_per_cta) nstages = kblocks_per_cta < 2 ? 2 : kblocks_per_cta;
-  GemmParams pp = p;
-  pp.nstages = nstages;
-  const int smem_now = Cfg::smem_bytes(SPLIT, nstages);
-  constexpr int kSmem = Cfg::smem_bytes(SPLIT, Cfg::stages(SPLIT, true));  // the largest this instantiation asks for
-  static bool configured[kMaxGemmDevices] = {};  // the attribute is a per-device setting
+  static bool configured[64] = {};  // the attribute is a per-device setting
   int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return e;
-  if (dev < 0 || dev >= kMaxGemmDevices) return cudaErrorInvalidDevice;
+  cudaError_t ce = cudaGetDevice(&dev);
+  if (ce != cudaSuccess) return ce;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
   if (!configured[dev]) {
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
-    if (e != cudaSuccess) return e;
+    ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (ce != cudaSuccess) return ce;
     configured[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(n_tiles, m_tiles, nsplit);
   cfg.blockDim = dim3(192, 1, 1);
-  cfg.dynamicSmemBytes = smem_now;
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
   int nattr = 0;
@@ -766,7 +719,7 @@ static cudaError_t launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, c
   }
   cfg.attrs = attr;
   cfg.numAttrs = nattr;
-  return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, pp);
+  return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p);
 }
 
 template <int TN, bool DUAL, int COMM = COMM_NONE>
