@@ -54,12 +54,14 @@ def main():
     peer = PeerTPOps(par, dev, args.hidden, 128256, max_tokens=4096)
     nccl = NcclTPOps(par, dev)
     rows = []
+    torch.manual_seed(1000 + rank)          # activations and weight shards differ per rank ...
+    res_gen = torch.Generator(device=dev).manual_seed(7)   # ... the residual is the same tensor on every rank
     for name, k_full in (("o_proj", args.heads_dim), ("down_proj", args.inter)):
         K = k_full // world
         w = (torch.randn(args.hidden, K, device=dev) * 0.02).bfloat16()
         for M in (1, 8, 32, 64, 512, 2048):
             x = (torch.randn(M, K, device=dev) * 0.5).bfloat16()
-            res = torch.randn(M, args.hidden, device=dev).bfloat16()
+            res = torch.randn(M, args.hidden, device=dev, generator=res_gen).bfloat16()
             t_peer = timed_graph(lambda: peer.row_linear(x, w, residual=res))
             t_nccl = timed_graph(lambda: nccl.row_linear(x, w, residual=res))
             a = peer.row_linear(x, w, residual=res).float()
@@ -71,7 +73,8 @@ def main():
                          "roofline_us": round(max(2 * M * args.hidden * K / 1.6633e15, link_bytes / 770e9) * 1e6, 2)})
     native.check_status(dev)
     if rank == 0:
-        print(json.dumps({"world": world, "rows": rows}))
+        for r in rows:
+            print(json.dumps({"world": world, **r}))
     dist.destroy_process_group()
 
 

@@ -582,15 +582,15 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         const long long t0 = clock64();
         bool first_pass = true;
         while (true) {
-          uint32_t got[kPB][kMaxRanks];
+          // words still missing are (re)loaded straight into their final registers; a word that is still the sentinel
+          // keeps its `miss` bit and is simply loaded again on the next pass
 #pragma unroll
           for (int j = 0; j < kPB; ++j) {
 #pragma unroll
             for (int src = 0; src < kMaxRanks; ++src) {
-              got[j][src] = kLamportEmpty;
               if ((miss[j] >> src) & 1u) {
                 asm volatile("ld.volatile.global.u32 %0, [%1];"
-                             : "=r"(got[j][src])
+                             : "=r"(lo[j][src])
                              : "l"(lamport_slot(p.comm, p.comm.rank, parity, src) + word[j])
                              : "memory");
               }
@@ -601,8 +601,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           for (int j = 0; j < kPB; ++j) {
 #pragma unroll
             for (int src = 0; src < kMaxRanks; ++src) {
-              if (((miss[j] >> src) & 1u) && got[j][src] != kLamportEmpty) {
-                lo[j][src] = got[j][src];
+              if (((miss[j] >> src) & 1u) && lo[j][src] != kLamportEmpty) {
                 miss[j] &= ~(1u << src);
                 asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(lamport_slot(p.comm, p.comm.rank, parity, src) + word[j]),
                              "r"(kLamportEmpty)
