@@ -97,43 +97,55 @@ def run_speculative(args, eng, model, cfg, prompts, dev, world, rank) -> int:
         dcfg = C.draft_llama_16l()
         draft = build_random(dcfg, dev, torch.bfloat16, seed=1)
         draft_eng = Engine(draft, max_batch=B, max_seq_len=P + 2 * K + 64, prefill_chunk=8192)
-    sp = SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=0, min_p=0.0, seed=1)
     dec = GraphSpeculativeDecoder(eng, draft_eng, k=args.spec_k)
-    dec.generate(prompts[:B], sp, max_new_tokens=8)  # warm-up (kernel configuration, allocator)
-    dec.stats = type(dec.stats)()
-    if world > 1:
-        import torch.distributed as dist
 
-        dist.barrier()
-    torch.cuda.synchronize(dev)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    outs = dec.generate(prompts[:B], sp, max_new_tokens=K)
-    e1.record()
-    torch.cuda.synchronize(dev)
-    ms = e0.elapsed_time(e1)
-    emitted = sum(len(o) for o in outs)
-    st = dec.stats.summary()
-    decode_ms = ms - st["prefill_ms"]   # both prefills (target and draft) are timed inside generate and taken out
-    result = {"metric": "speculative_decode_tokens_per_s", "value": round((emitted - B) / (decode_ms / 1e3), 2), "unit": "tokens/s",
+    def one(temperature, top_p):
+        sp = SamplingParams(temperature=temperature, top_p=top_p, top_k=0, min_p=0.0, seed=1)
+        dec.generate(prompts[:B], sp, max_new_tokens=8)  # warm-up (kernel configuration, allocator)
+        dec.stats = type(dec.stats)()
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        outs = dec.generate(prompts[:B], sp, max_new_tokens=K)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        ms = e0.elapsed_time(e1)
+        emitted = sum(len(o) for o in outs)
+        st = dec.stats.summary()
+        decode_ms = ms - st["prefill_ms"]   # both prefills (target and draft) are timed inside generate and taken out
+        return {"temperature": temperature, "top_p": top_p, "decode_tokens_per_s": round((emitted - B) / (decode_ms / 1e3), 2),
+                "total_ms": round(ms, 2), "decode_ms": round(decode_ms, 2), "verify_step_ms_p50": st["verify_ms_p50"],
+                "accepted_per_round": st["accepted_per_step"], "speculative": st}
+
+    # the preset of BASELINE configuration 5 reports the greedy and the T = 0.8 / top-p 0.95 variant side by side
+    variants = [one(0.0, 1.0), one(0.8, 0.95)] if args.config == 5 else [one(args.temperature, args.top_p)]
+    head = variants[0]
+    result = {"metric": "speculative_decode_tokens_per_s", "value": head["decode_tokens_per_s"], "unit": "tokens/s",
               "n_gpus": world, "steps": K, "higher_is_better": True, "dtype": "bf16", "impl": "eredu_b200",
-              "data": "synthetic (random-init target and draft: acceptance of the 16-layer draft is chance level)",
+              "data": "synthetic (random-init target; the 16-layer draft shares the target's embedding, head and first "
+                      "layer by seed only when built so - acceptance of a random draft is chance level)",
               "config": {"model": args.model + "-shaped", "draft": args.spec_draft, "k": args.spec_k, "global_batch": B,
-                         "seq_len": P, "temperature": args.temperature, "top_p": args.top_p, "parallelism": f"tp{world}"},
-              "includes_prefill": False, "total_ms": round(ms, 2), "decode_ms": round(decode_ms, 2),
-              "round_ms_p50": st["verify_ms_p50"], "speculative": st}
+                         "seq_len": P, "parallelism": f"tp{world}"},
+              "includes_prefill": False, "round_ms_p50": head["verify_step_ms_p50"], "variants": variants}
     if rank == 0:
         print(json.dumps(result))
     if world > 1:
         import torch.distributed as dist
 
-        dist.destroy_process_group()
+        dist.barrier()
+        sys.stdout.flush()
+        os._exit(0)
     return 0
 
 
-def run_torch_baseline(args) -> int:
+def run_torch_baseline(args, inline: bool = False):
     """Stand-in for the reference arm that cannot be built here: stock PyTorch operators (cuBLAS GEMMs, library
-    attention, NCCL collectives) on the same shapes, batch, context and timing protocol; decode only."""
+    attention, NCCL collectives) on the same shapes, batch, context and timing protocol; decode only. ``inline``: called
+    from the product arm's process (process group already up); returns the result instead of printing it."""
     import torch
 
     from baseline.torch_llama import TorchLlamaTP
@@ -144,7 +156,7 @@ def run_torch_baseline(args) -> int:
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    if world > 1:
+    if world > 1 and not inline:
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=dev)
@@ -186,13 +198,19 @@ def run_torch_baseline(args) -> int:
         t = torch.tensor([ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
+    line = {"impl": "torch-baseline", "metric": "decode_tokens_per_s", "value": round(B * K / (ms / 1e3), 2),
+            "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(ms / K, 4),
+            "higher_is_better": True, "dtype": "bf16", "data": "synthetic (random weights and cache)",
+            "config": {"model": args.model + "-shaped", "global_batch": B, "seq_len": P, "parallelism": f"tp{world}",
+                       "stack": "F.linear (cuBLAS) + F.scaled_dot_product_attention + NCCL all-reduce / all-gather, CUDA graph",
+                       "kv": "contiguous cache, fixed context of seq_len + 1"}}
+    if inline:
+        del graph, model
+        torch.cuda.synchronize(dev)
+        torch.cuda.empty_cache()
+        return line
     if rank == 0:
-        print(json.dumps({"impl": "torch-baseline", "metric": "decode_tokens_per_s", "value": round(B * K / (ms / 1e3), 2),
-                          "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(ms / K, 4),
-                          "higher_is_better": True, "dtype": "bf16", "data": "synthetic (random weights and cache)",
-                          "config": {"model": args.model + "-shaped", "global_batch": B, "seq_len": P, "parallelism": f"tp{world}",
-                                     "stack": "F.linear (cuBLAS) + F.scaled_dot_product_attention + NCCL all-reduce / all-gather, CUDA graph",
-                                     "kv": "contiguous cache, fixed context of seq_len + 1"}}))
+        print(json.dumps(line))
     # The captured graph holds NCCL kernels: release it and drain the device before the communicator goes away
     # (tearing the process group down under a live graph did not return on eight ranks).
     del graph
@@ -227,7 +245,26 @@ def main() -> int:
                          "(acceptance 1 under greedy: the upper bound and the pure verify/draft step costs)")
     ap.add_argument("--temperature", type=float, default=0.0)
     ap.add_argument("--top-p", type=float, default=0.95)
+    ap.add_argument("--config", type=int, default=0, choices=[0, 2, 3, 4, 5],
+                    help="preset of a benchmark configuration: 2 = Llama-3-8B bf16 (batch 32, prompt 2048; the default), "
+                         "3 = Qwen3-30B-A3B (experts over the GPUs, batch 32, prompt 1024), 4 = Llama-3-70B 4-bit group 64 "
+                         "(batch 8, prompt 4096), 5 = speculative decoding (8B target + 16-layer draft, k = 4, batch 1, prompt 512)")
+    ap.add_argument("--ep-mode", default="replicated", choices=["replicated", "a2a"],
+                    help="sparse models on several GPUs: replicated tokens + summed partial outputs, or token-sharded "
+                         "all-to-all dispatch / combine")
+    ap.add_argument("--ep-backend", default="peer", choices=["peer", "collective"],
+                    help="collectives of the tensor / expert ranks: kernels over NVLink peer memory, or torch.distributed (NCCL)")
+    ap.add_argument("--router-skew", type=float, default=0.0,
+                    help="sparse models: this fraction of the tokens is biased onto 8 hot experts (0 = as routed)")
+    ap.add_argument("--no-baseline", action="store_true", help="skip the in-process baseline arm that fills vs_baseline")
     args = ap.parse_args()
+    if args.config == 3:
+        args.model, args.batch, args.prompt_len = "qwen3-30b-a3b", 32, 1024
+    elif args.config == 4:
+        args.model, args.batch, args.prompt_len, args.quantize, args.group_size = "llama3-70b", 8, 4096, 4, 64
+    elif args.config == 5:
+        args.model, args.batch, args.prompt_len = "llama3-8b", 1, 512
+        args.spec_k = args.spec_k or 4
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
@@ -285,7 +322,14 @@ def main() -> int:
     if world > 1:
         from eredu_b200.parallel import tp
 
-        tp.attach(model, par, max_tokens=8192)
+        tp.attach(model, par, max_tokens=8192, backend="peer" if args.ep_backend == "peer" else "nccl",
+                  ep_mode=args.ep_mode if is_moe else "replicated")
+    if is_moe and args.router_skew > 0:
+        period = max(1, round(1.0 / args.router_skew))
+        hot = torch.arange(8, device=dev)
+        for lw in model.layers:
+            if lw.moe is not None:
+                lw.moe.skew = (period, hot, 30.0)
     eng = Engine(model, max_batch=B, max_seq_len=P + budget, prefill_chunk=8192)
     rng = np.random.default_rng(0)
     prompts = [rng.integers(0, cfg.vocab_size, P).tolist() for _ in range(B)]
@@ -409,6 +453,8 @@ def main() -> int:
         "impl": "eredu_b200",
         "config": {"model": args.model + "-shaped", "global_batch": B,
                    "seq_len": P, "decode_steps": K, "parallelism": f"tp{world}" + (f"+ep{world}" if is_moe else ""),
+                   **({"ep_mode": args.ep_mode, "collectives": args.ep_backend, "router_skew": args.router_skew}
+                      if is_moe else ({"collectives": args.ep_backend} if world > 1 else {})),
                    "kv_page_tokens": 16,
                    "l2": "per-step inputs (weight shard + KV pages) exceed L2; no flush needed",
                    "timing": "CUDA events around K CUDA-graph decode steps, max over ranks"},
@@ -422,12 +468,30 @@ def main() -> int:
         "gpu_launches": launches_per_step * K,
         "launches_per_step": launches_per_step,
     }
+    # ---------------------------------------------------------------- baseline arm in the same process -> vs_baseline
+    if not args.no_baseline:
+        free_gb = torch.cuda.mem_get_info(dev)[0] / 2**30
+        need_gb = (cfg.num_hidden_layers * (cfg.hidden_size * (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * cfg.head_dim
+                                              + cfg.hidden_size * cfg.num_attention_heads * cfg.head_dim
+                                              + 3 * cfg.hidden_size * max(cfg.intermediate_size, 1)) * 2 / world
+                   + 2 * cfg.vocab_size * cfg.hidden_size * 2) / 2**30 + 8
+        if is_moe:
+            result["baseline"] = {"unavailable": "the stock-PyTorch arm covers dense Llama-shaped models; compare --ep-backend collective"}
+        elif free_gb < need_gb:
+            result["baseline"] = {"unavailable": f"bf16 copy of the weights for the stock-PyTorch arm needs {need_gb:.0f} GB, {free_gb:.0f} GB free"}
+        else:
+            base = run_torch_baseline(args, inline=True)
+            result["vs_baseline"] = round(result["value"] / base["value"], 3)
+            result["baseline"] = {"impl": "torch-baseline (stock PyTorch: cuBLAS + SDPA + NCCL, CUDA graph; bf16 weights)",
+                                  "value": base["value"], "ms_per_step": base["ms_per_step"], "what": "value / baseline value"}
     if rank == 0:
         print(json.dumps(result))
     if world > 1:
         import torch.distributed as dist
 
-        dist.destroy_process_group()
+        barrier()
+        sys.stdout.flush()
+        os._exit(0)     # graphs holding NCCL kernels were captured in this process: leave without tearing the group down
     return 0
 
 

@@ -225,7 +225,8 @@ __global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ x, const int
   if (pos >= counts[0]) return;
   const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row_token[pos]) * H);
   uint4* dst = reinterpret_cast<uint4*>(xp + static_cast<size_t>(pos) * H);
-  for (int c = threadIdx.x; c < (H >> 3); c += blockDim.x) dst[c] = src[c];
+  // L2 loads: the rows may have been stored by another GPU into a buffer this SM read before
+  for (int c = threadIdx.x; c < (H >> 3); c += blockDim.x) dst[c] = ld_cg_u4(src + c);
 }
 
 // out[t, :] = (residual[t, :]) + (extra[t, :]) + sum_k w[t,k] * y[route_pos[t*k + slot], :]  (local routes only),
@@ -388,6 +389,227 @@ __global__ void __launch_bounds__(128) moe_combine_ar_kernel(const __nv_bfloat16
   if (threadIdx.x == 0) finish_call(comm, seq, gridDim.x * gridDim.y);
 }
 
+
+// ============================================================================ expert-parallel all-to-all (sharded tokens)
+// The token-sharded form of expert parallelism (the reference's `dispatch_sharded`: a count all-gather with a host sync,
+// four forward and two reverse all_to_all_v exchanges - eredu/src/backend/mlx/runtime/distributed/expert.rs:781-842,
+// 1054-1222) as four kernels over NVLink peer memory with every count kept on the device:
+//   dispatch : the SOURCE rank of a token walks its top-k routes, claims a row in the owner rank's receive area (one
+//              region per source, so a device-side cursor per owner is all the bookkeeping) and stores the hidden row and
+//              {expert id, route index} straight into the owner's memory - the routing permute IS the transfer; the last
+//              CTA publishes the per-owner counts and one flag per owner;
+//   recv_plan: the OWNER waits (bounded) for the flags of all sources, reads the counts and builds the grouped-GEMM plan
+//              over the received rows;
+//   return   : after the expert GEMMs the owner stores every output row into the source's return area at the route's
+//              own slot [token, k] (no atomics; a flag per source follows);
+//   combine  : the source waits for all owners, forms residual + sum_k w_k * row_k in slot order (deterministic), stores
+//              the finished token row into EVERY rank's output (the all-gather that restores replicated activations),
+//              and the kernel ends once the rows of all sources have arrived.
+// Sequence numbers as in the other peer kernels: dispatch, return and combine each advance the communicator by one.
+struct A2AView {
+  long long recv_off;  // [size src][cap][H] bf16   rows received from every source
+  long long meta_off;  // [size src][cap] int2      {global expert id, route index at the source}
+  long long cnt_off;   // [2 parity][size src] int  rows sent by each source in this call
+  long long ret_off;   // [cap][H] bf16             rows returned to this source, slot = its route index
+  long long out_off;   // [2][T_max][H] bf16        gathered token rows (double-buffered by call)
+  long long out_half_bytes;
+  int T, T_src, k, H, E_local, cap;
+  int out_parity;
+};
+
+__device__ __forceinline__ void copy_row16(uint8_t* dst, const uint8_t* src, int bytes, int lane) {
+  for (int i = lane * 16; i < bytes; i += 32 * 16) *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<const uint4*>(src + i);
+}
+
+// grid = max(1, n_own) CTAs of 128 threads; token `blockIdx.x` of this rank's slice, one warp per route.
+__global__ void __launch_bounds__(128) moe_a2a_dispatch_kernel(PeerComm c, A2AView v, const __nv_bfloat16* __restrict__ x_own,
+                                                               const int* __restrict__ ids, int n_own,
+                                                               int* __restrict__ cursor, int* status) {
+  pdl_launch_early();
+  pdl_wait();
+  pdl_launch_dependents();
+  const unsigned int seq = *reinterpret_cast<volatile unsigned int*>(c.seq);
+  const int parity = static_cast<int>(seq & 1u);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x;
+  if (t < n_own) {
+    for (int s = warp; s < v.k; s += 4) {
+      int e = 0, idx = 0;
+      if (lane == 0) {
+        e = ids[t * v.k + s];
+        idx = atomicAdd(&cursor[e / v.E_local], 1);
+      }
+      e = __shfl_sync(0xffffffffu, e, 0);
+      idx = __shfl_sync(0xffffffffu, idx, 0);
+      const int owner = e / v.E_local;
+      if (idx < v.cap) {  // cap = every route of the slice: cannot overflow
+        const size_t row = static_cast<size_t>(c.rank) * v.cap + idx;
+        copy_row16(c.base[owner] + v.recv_off + row * v.H * 2, reinterpret_cast<const uint8_t*>(x_own + static_cast<size_t>(t) * v.H),
+                   v.H * 2, lane);
+        if (lane == 0) *reinterpret_cast<int2*>(c.base[owner] + v.meta_off + row * 8) = make_int2(e, t * v.k + s);
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  __shared__ int s_last;
+  if (threadIdx.x == 0) s_last = (atomicAdd(c.done, 1u) == gridDim.x - 1) ? 1 : 0;
+  __syncthreads();
+  if (s_last) {  // every CTA's rows are out: publish how many each owner got, then the flag
+    __threadfence_system();
+    if (threadIdx.x < c.size) {
+      const int owner = threadIdx.x;
+      const int n = atomicAdd(&cursor[owner], 0);
+      *reinterpret_cast<volatile int*>(c.base[owner] + v.cnt_off + (static_cast<size_t>(parity) * kMaxRanks + c.rank) * 4) = n;
+      cursor[owner] = 0;
+      __threadfence_system();
+      st_release_sys(peer_flag(c, owner, parity, c.rank, 0), seq + 1u);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      *c.done = 0u;
+      __threadfence();
+      *c.seq = seq + 1u;
+    }
+  }
+  (void)status;
+}
+
+// Single CTA (1024 threads). Waits for the dispatch flags of all sources, then plans the local experts over the received
+// rows: flat row r = src * cap + i is a route when i < count[src]. `ids_flat` is scratch [size * cap].
+__global__ void __launch_bounds__(1024) moe_a2a_recv_plan_kernel(PeerComm c, A2AView v, int e0, int e1, int tile,
+                                                                 int* __restrict__ ids_flat, int* __restrict__ seg,
+                                                                 int* __restrict__ route_pos, int* __restrict__ row_token,
+                                                                 int4* __restrict__ work, int n_work_cap, int* __restrict__ counts,
+                                                                 int* status) {
+  pdl_launch_early();
+  pdl_wait();
+  pdl_launch_dependents();
+  const unsigned int want = *reinterpret_cast<volatile unsigned int*>(c.seq);  // the dispatch kernel already advanced it
+  const int parity = static_cast<int>((want - 1u) & 1u);
+  __shared__ int s_cnt[kMaxRanks];
+  if (threadIdx.x < c.size) {
+    wait_flag(c, parity, threadIdx.x, 0, want, status);
+    s_cnt[threadIdx.x] = *reinterpret_cast<volatile int*>(c.base[c.rank] + v.cnt_off + (static_cast<size_t>(parity) * kMaxRanks + threadIdx.x) * 4);
+  }
+  __syncthreads();
+  const int total = c.size * v.cap;
+  const int2* meta = reinterpret_cast<const int2*>(c.base[c.rank] + v.meta_off);
+  for (int r = threadIdx.x; r < total; r += blockDim.x) {
+    const int src = r / v.cap, i = r - src * v.cap;
+    ids_flat[r] = (i < min(s_cnt[src], v.cap)) ? __ldcg(&meta[r].x) : -1;
+  }
+  __syncthreads();
+  plan_block(ids_flat, total, 1, e0, e1, tile, seg, route_pos, row_token, work, n_work_cap, counts);
+}
+
+// grid = size * cap CTAs of 128 threads (one per receive slot). Output row of slot r goes back to its source.
+__global__ void __launch_bounds__(128) moe_a2a_return_kernel(PeerComm c, A2AView v, const __nv_bfloat16* __restrict__ y,
+                                                             const int* __restrict__ route_pos, int* status) {
+  pdl_launch_early();
+  pdl_wait();
+  pdl_launch_dependents();
+  const unsigned int seq = *reinterpret_cast<volatile unsigned int*>(c.seq);
+  const int parity = static_cast<int>(seq & 1u);
+  const int r = blockIdx.x;
+  const int pos = route_pos[r];
+  if (pos >= 0) {
+    const int src = r / v.cap;
+    const int2 m = __ldcg(reinterpret_cast<const int2*>(c.base[c.rank] + v.meta_off) + r);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint8_t* dst = c.base[src] + v.ret_off + static_cast<size_t>(m.y) * v.H * 2;
+    const uint8_t* from = reinterpret_cast<const uint8_t*>(y + static_cast<size_t>(pos) * v.H);
+    const int quarter = (v.H * 2 / 64) * 16;  // each warp copies a quarter of the row (H * 2 bytes, multiple of 64)
+    copy_row16(dst + warp * quarter, from + warp * quarter, quarter, lane);
+  }
+  __threadfence_system();
+  __syncthreads();
+  __shared__ int s_last;
+  if (threadIdx.x == 0) s_last = (atomicAdd(c.done, 1u) == gridDim.x - 1) ? 1 : 0;
+  __syncthreads();
+  if (s_last) {
+    __threadfence_system();
+    if (threadIdx.x < c.size) st_release_sys(peer_flag(c, threadIdx.x, parity, c.rank, 1), seq + 1u);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      *c.done = 0u;
+      __threadfence();
+      *c.seq = seq + 1u;
+    }
+  }
+  (void)status;
+}
+
+// grid = max(1, n_own) CTAs of 128 threads. Token t (local index) -> out[t0 + t] on every rank.
+__global__ void __launch_bounds__(128) moe_a2a_combine_kernel(PeerComm c, A2AView v, const float* __restrict__ weights,
+                                                              const __nv_bfloat16* __restrict__ residual_own,
+                                                              const __nv_bfloat16* __restrict__ extra_own, int n_own, int t0,
+                                                              int* status) {
+  pdl_launch_early();
+  pdl_wait();
+  pdl_launch_dependents();
+  const unsigned int seq = *reinterpret_cast<volatile unsigned int*>(c.seq);  // the return kernel's flags carry this value
+  const int parity = static_cast<int>(seq & 1u);
+  if (threadIdx.x < c.size) wait_flag(c, static_cast<int>((seq - 1u) & 1u), threadIdx.x, 1, seq, status);
+  __syncthreads();
+  const int t = blockIdx.x;
+  if (t < n_own) {
+    const uint8_t* ret = c.base[c.rank] + v.ret_off;
+    for (int ch = threadIdx.x; ch < (v.H >> 3); ch += blockDim.x) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int s = 0; s < v.k; ++s) {  // slot order: the same bits whatever the arrival order was
+        const float w = weights[t * v.k + s];
+        const uint4 q = ld_cg_u4(ret + (static_cast<size_t>(t) * v.k + s) * v.H * 2 + static_cast<size_t>(ch) * 16);
+        const uint32_t u[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          acc[2 * j] += w * bf16_lo(u[j]);
+          acc[2 * j + 1] += w * bf16_hi(u[j]);
+        }
+      }
+      const __nv_bfloat16* adds[2] = {residual_own, extra_own};
+#pragma unroll
+      for (int a = 0; a < 2; ++a) {
+        if (adds[a] != nullptr) {
+          const uint4 q = reinterpret_cast<const uint4*>(adds[a] + static_cast<size_t>(t) * v.H)[ch];
+          const uint32_t u[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            acc[2 * j] += bf16_lo(u[j]);
+            acc[2 * j + 1] += bf16_hi(u[j]);
+          }
+        }
+      }
+      uint4 o;
+      o.x = pack_bf16x2(acc[0], acc[1]);
+      o.y = pack_bf16x2(acc[2], acc[3]);
+      o.z = pack_bf16x2(acc[4], acc[5]);
+      o.w = pack_bf16x2(acc[6], acc[7]);
+      const size_t off = v.out_off + static_cast<size_t>(v.out_parity) * v.out_half_bytes +
+                         (static_cast<size_t>(t0 + t) * v.H) * 2 + static_cast<size_t>(ch) * 16;
+      for (int peer = 0; peer < c.size; ++peer) *reinterpret_cast<uint4*>(c.base[peer] + off) = o;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  __shared__ int s_last;
+  if (threadIdx.x == 0) s_last = (atomicAdd(c.done, 1u) == gridDim.x - 1) ? 1 : 0;
+  __syncthreads();
+  if (s_last) {  // this rank's rows are everywhere: tell everyone, then wait for everyone's rows
+    __threadfence_system();
+    if (threadIdx.x < c.size) {
+      st_release_sys(peer_flag(c, threadIdx.x, parity, c.rank, 2), seq + 1u);
+      wait_flag(c, parity, threadIdx.x, 2, seq + 1u, status);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      *c.done = 0u;
+      __threadfence();
+      *c.seq = seq + 1u;
+    }
+  }
+}
+
 }  // namespace eredu
 
 using namespace eredu;
@@ -458,6 +680,67 @@ extern "C" int eredu_moe_route_plan_gather(const float* logits, const float* sel
   launch_pdl(moe_route_plan_gather_kernel, dim3(1), dim3(1024), 0, stream, logits, sel_bias, ids, weights, T, E, k, scoring,
              renorm, scale, e0, e1, tile, seg, route_pos, row_token, reinterpret_cast<int4*>(work), n_work_cap, counts,
              static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(xp), H);
+  eredu_count_launches(1);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// ---- expert-parallel all-to-all over peer memory. `view`: 13 values {recv_off, meta_off, cnt_off, ret_off, out_off,
+// out_half_bytes, T, T_src, k, H, E_local, cap, out_parity} as int64.
+static A2AView a2a_view(const long long* p) {
+  A2AView v;
+  v.recv_off = p[0];
+  v.meta_off = p[1];
+  v.cnt_off = p[2];
+  v.ret_off = p[3];
+  v.out_off = p[4];
+  v.out_half_bytes = p[5];
+  v.T = static_cast<int>(p[6]);
+  v.T_src = static_cast<int>(p[7]);
+  v.k = static_cast<int>(p[8]);
+  v.H = static_cast<int>(p[9]);
+  v.E_local = static_cast<int>(p[10]);
+  v.cap = static_cast<int>(p[11]);
+  v.out_parity = static_cast<int>(p[12]);
+  return v;
+}
+extern "C" int eredu_moe_a2a_dispatch(const void* comm, const long long* view, const void* x_own, const int* ids, int n_own,
+                                      int* cursor, int* status, cudaStream_t stream) {
+  const PeerComm* c = static_cast<const PeerComm*>(comm);
+  const A2AView v = a2a_view(view);
+  if (c == nullptr || v.H % 32 != 0 || v.k > 32 || v.E_local <= 0) return -1;
+  launch_pdl(moe_a2a_dispatch_kernel, dim3(n_own > 0 ? n_own : 1), dim3(128), 0, stream, *c, v,
+             static_cast<const __nv_bfloat16*>(x_own), ids, n_own, cursor, status);
+  eredu_count_launches(1);
+  return static_cast<int>(cudaGetLastError());
+}
+extern "C" int eredu_moe_a2a_recv_plan(const void* comm, const long long* view, int e0, int e1, int tile, int* ids_flat, int* seg,
+                                       int* route_pos, int* row_token, int* work, int n_work_cap, int* counts, int* status,
+                                       cudaStream_t stream) {
+  const PeerComm* c = static_cast<const PeerComm*>(comm);
+  const A2AView v = a2a_view(view);
+  if (c == nullptr || e1 - e0 > 512 || e1 <= e0) return -1;
+  launch_pdl(moe_a2a_recv_plan_kernel, dim3(1), dim3(1024), 0, stream, *c, v, e0, e1, tile, ids_flat, seg, route_pos, row_token,
+             reinterpret_cast<int4*>(work), n_work_cap, counts, status);
+  eredu_count_launches(1);
+  return static_cast<int>(cudaGetLastError());
+}
+extern "C" int eredu_moe_a2a_return(const void* comm, const long long* view, const void* y, const int* route_pos, int* status,
+                                    cudaStream_t stream) {
+  const PeerComm* c = static_cast<const PeerComm*>(comm);
+  const A2AView v = a2a_view(view);
+  if (c == nullptr) return -1;
+  launch_pdl(moe_a2a_return_kernel, dim3(c->size * v.cap), dim3(128), 0, stream, *c, v, static_cast<const __nv_bfloat16*>(y),
+             route_pos, status);
+  eredu_count_launches(1);
+  return static_cast<int>(cudaGetLastError());
+}
+extern "C" int eredu_moe_a2a_combine(const void* comm, const long long* view, const float* weights, const void* residual_own,
+                                     const void* extra_own, int n_own, int t0, int* status, cudaStream_t stream) {
+  const PeerComm* c = static_cast<const PeerComm*>(comm);
+  const A2AView v = a2a_view(view);
+  if (c == nullptr) return -1;
+  launch_pdl(moe_a2a_combine_kernel, dim3(n_own > 0 ? n_own : 1), dim3(128), 0, stream, *c, v, weights,
+             static_cast<const __nv_bfloat16*>(residual_own), static_cast<const __nv_bfloat16*>(extra_own), n_own, t0, status);
   eredu_count_launches(1);
   return static_cast<int>(cudaGetLastError());
 }

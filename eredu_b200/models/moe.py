@@ -38,6 +38,9 @@ class MoEBlock:
         self.down_bias = down_bias                    # [E_local, H]
         self.act = act
         self.stats = {"calls": 0}
+        # benchmark knob: (period, hot expert ids tensor, bias) - every period-th token gets `bias` added to the router
+        # logits of the hot experts (a skewed-router load: 1 / period of the tokens crowd onto a few experts)
+        self.skew = None
 
     def tensors(self):
         out = [self.router_w, self.w_gate_up, self.w_down]
@@ -60,9 +63,21 @@ class MoEBlock:
             y = (y.float() * torch.sigmoid(x.float() @ self.shared_gate_w.float().t())).to(y.dtype)
         return y
 
+    def router_logits(self, x, row0: int = 0):
+        """fp32 router logits of the rows of x; ``row0`` is the global token index of row 0 (token-sharded callers)."""
+        logits = ops.linear(x, self.router_w, bias=self.router_linear_bias, out_dtype=torch.float32)
+        if self.skew is not None:
+            period, hot, bias = self.skew
+            rows = torch.arange(row0, row0 + x.shape[0], device=x.device)
+            pick = ((rows % period) == 0).to(logits.dtype)[:, None]
+            boost = torch.zeros(logits.shape[1], dtype=logits.dtype, device=x.device)
+            boost[hot] = bias
+            logits = logits + pick * boost[None, :]
+        return logits
+
     def route(self, x):
         cfg = self.cfg
-        logits = ops.linear(x, self.router_w, bias=self.router_linear_bias, out_dtype=torch.float32)
+        logits = self.router_logits(x)
         return moe_ops.route(logits.contiguous(), cfg.num_experts_per_tok, cfg.router_scoring, cfg.norm_topk_prob,
                              cfg.routed_scaling_factor, self.router_bias, cfg.n_group, cfg.topk_group)
 
@@ -97,6 +112,10 @@ class MoEBlock:
     def __call__(self, x, residual=None):
         """x: normalised hidden states [T, H]; returns residual + MoE(x)."""
         self.stats["calls"] += 1
+        a2a = getattr(self, "ep_a2a", None)
+        if a2a is not None and self.ep_size > 1:
+            # token-sharded expert parallelism: routes travel to their expert's owner and back (parallel/ep_a2a.py)
+            return a2a.forward(self, x, residual)
         cache = getattr(self, "expert_cache", None)
         if cache is not None:
             # experts live in host memory behind a bounded device bank: route, then let the cache run the experts
@@ -111,7 +130,7 @@ class MoEBlock:
         if x.is_cuda and x.shape[0] <= 64 and self.cfg.n_group <= 1:
             # decode-sized: routing, expert plan and row gather in one kernel
             cfg = self.cfg
-            logits = ops.linear(x, self.router_w, bias=self.router_linear_bias, out_dtype=torch.float32)
+            logits = self.router_logits(x)
             ids, w, plan, xp = moe_ops.route_plan_gather(logits.contiguous(), x, cfg.num_experts_per_tok, cfg.router_scoring,
                                                          cfg.norm_topk_prob, cfg.routed_scaling_factor, self.router_bias,
                                                          self.e0,

@@ -178,11 +178,12 @@ def route_plan_gather(logits, x, k, scoring, renorm, scale, sel_bias, e0, n_loca
 
 
 def experts_forward(x, ids, weights, w_gate_up, w_down, e0=0, residual=None, extra=None, limit=0.0, rows_cap=None,
-                    comm=None, plan=None, xp=None, gu_bias=None, down_bias=None, act="swiglu"):
+                    comm=None, plan=None, xp=None, gu_bias=None, down_bias=None, act="swiglu", rows_only=False):
     """Local-expert MoE computation. x: [T, H] bf16; ids / weights: [T, k]; w_gate_up: [E_local, 2I, H];
     w_down: [E_local, H, I]. Returns residual + extra + sum over local routes (bf16 [T, H]). With ``comm`` (a peer
     communication context of the expert group) the combine kernel also sums the partial outputs of all ranks:
-    ``extra`` is then counted once per rank that passes it, ``residual`` once in total."""
+    ``extra`` is then counted once per rank that passes it, ``residual`` once in total. ``rows_only`` (CUDA, with a
+    ``plan`` and permuted rows ``xp``): stop after the two grouped GEMMs and return the rows in plan order."""
     if not x.is_cuda:
         out = experts_ref(x, ids, weights, w_gate_up, w_down, e0, limit, gu_bias, down_bias, act)
         if residual is not None:
@@ -191,7 +192,7 @@ def experts_forward(x, ids, weights, w_gate_up, w_down, e0=0, residual=None, ext
             out = out + extra.float()
         return out.to(x.dtype)
     T, H = x.shape
-    k = ids.shape[1]
+    k = ids.shape[1] if ids is not None else 1
     E_local, two_i, _ = w_gate_up.shape
     ungated = act in UNGATED
     inter = two_i if ungated else two_i // 2
@@ -222,6 +223,8 @@ def experts_forward(x, ids, weights, w_gate_up, w_down, e0=0, residual=None, ext
                                          inter, inter, inter, H, E_local * H, H, 0, 0, sm, ptr(st), ptr(down_bias),
                                          H if down_bias is not None else 0, 0, 0.0, stream_ptr(dev))
     check(code, "eredu_gemm_bf16_grouped(down)")
+    if rows_only:      # expert-contiguous output rows (row order of the plan); the caller combines them
+        return y
     out = torch.empty((T, H), dtype=x.dtype, device=dev)
     if comm is not None:
         code = lib().eredu_moe_combine_ar(ptr(y), ptr(plan.route_pos), ptr(weights), ptr(residual), ptr(extra), ptr(out),

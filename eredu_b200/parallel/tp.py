@@ -143,8 +143,10 @@ class NcclTPOps:
         return torch.cat(parts, dim=-1)
 
 
-def attach(model, par, max_tokens: int = 8192, backend: str = "peer"):
-    """Give a tensor-parallel model shard its collective implementation."""
+def attach(model, par, max_tokens: int = 8192, backend: str = "peer", ep_mode: str = "replicated"):
+    """Give a tensor-parallel model shard its collective implementation. ``ep_mode``: how sparse blocks spread over the
+    expert ranks - "replicated" (every rank routes all tokens, partial outputs are summed: the reference's production
+    path) or "a2a" (token-sharded all-to-all dispatch and combine, see :mod:`eredu_b200.parallel.ep_a2a`)."""
     if par.tp_size == 1:
         return model
     if backend == "peer" and model.device.type == "cuda":
@@ -156,4 +158,8 @@ def attach(model, par, max_tokens: int = 8192, backend: str = "peer"):
         from ..models.moe import attach_ep
 
         attach_ep(model, model.tp_ops)
+        if ep_mode == "a2a":
+            from .ep_a2a import attach_ep_a2a
+
+            attach_ep_a2a(model, par, "peer" if (backend == "peer" and model.device.type == "cuda") else "collective", max_tokens)
     return model

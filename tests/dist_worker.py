@@ -210,9 +210,12 @@ def main():
             sd = random_state(cfg, seed=0, std=0.08)
         par = ParallelContext.from_env(ParallelTopology(tensor=world, expert=world, expert_over_tensor=True))
         model = build_from_tensors(cfg, sd.__getitem__, sd.__contains__, dev, dtype, par, moe_factory=make_moe_factory())
-        tp.attach(model, par, max_tokens=256, backend="nccl" if "nccl" in scenario else "peer")
+        tp.attach(model, par, max_tokens=256, backend="nccl" if "nccl" in scenario else "peer",
+                  ep_mode="a2a" if "a2a" in scenario else "replicated")
         eng = Engine(model, max_batch=4, max_seq_len=128)
         result["tokens"] = eng.generate(prompts, sp, max_new_tokens=10)
+        if "a2a" in scenario:
+            result["a2a_calls"] = int(model.ep_a2a.stats["calls"])
         if gpu:
             from eredu_b200.ops import native
 

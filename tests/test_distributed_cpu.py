@@ -193,3 +193,23 @@ def test_deepseek_family_over_tensor_and_expert_ranks(tmp_path):
     want = Engine(model, max_batch=4, max_seq_len=128).generate(prompts, SamplingParams(temperature=0.0), 10)
     for r in res:
         assert r["tokens"] == want
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_all_to_all_matches_single_rank(world, tmp_path):
+    """Token-sharded expert parallelism on CPU ranks (gloo): every rank routes its own slice of the tokens, the routes
+    travel to their expert's owner and back (count exchange, rows and ids forward, rows in reverse, all-gather of the
+    finished token rows), and every rank ends with the tokens of the single-rank model."""
+    from eredu_b200.models.moe import make_moe_factory
+    from dist_worker import moe_cfg
+
+    res = run_ranks("cpu_ep_a2a_nccl", world, tmp_path)
+    cfg = moe_cfg(False)
+    sd = random_state(cfg, seed=0, std=0.08)
+    model = build_from_tensors(cfg, sd.__getitem__, sd.__contains__, "cpu", torch.float32, moe_factory=make_moe_factory())
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 33)]
+    want = Engine(model, max_batch=4, max_seq_len=128).generate(prompts, SamplingParams(temperature=0.0), 10)
+    for r in res:
+        assert r["tokens"] == want and r["a2a_calls"] > 0
+

@@ -81,6 +81,29 @@ def test_expert_parallel_fused_combine_matches_single_gpu(world, tmp_path):
     assert _rel(torch.tensor(nccl[0]["logits"]), ref) <= 0.03
 
 
+@pytest.mark.parametrize("world", [2, 8])
+def test_expert_parallel_all_to_all_matches_single_gpu(world, tmp_path):
+    """Token-sharded expert parallelism: the peer-memory dispatch / combine kernels and the torch.distributed all-to-all
+    baseline against the single-GPU model (prefill of 100 tokens and CUDA-graph decode steps both go through them)."""
+    from eredu_b200.models.moe import make_moe_factory
+
+    _need(world)
+    env = {"NCCL_NVLS_ENABLE": "0"}
+    peer = run_ranks("gpu_ep_a2a_peer", world, tmp_path, extra_env=env)
+    coll = run_ranks("gpu_ep_a2a_nccl", world, tmp_path, extra_env=env)
+    cfg = moe_cfg(True)
+    sd = random_state(cfg, seed=0, std=0.08)
+    model = build_from_tensors(cfg, sd.__getitem__, sd.__contains__, "cuda:0", torch.bfloat16, moe_factory=make_moe_factory())
+    eng = Engine(model, max_batch=4, max_seq_len=128)
+    probe = torch.randint(0, cfg.vocab_size, (100,), generator=torch.Generator().manual_seed(7)).tolist()
+    ref = torch.tensor(probe_logits(eng, model, probe))
+    for r in peer:
+        lg = torch.tensor(r["logits"])
+        assert _rel(lg, ref) <= 0.03 and r["a2a_calls"] > 0
+        assert r["logits"] == peer[0]["logits"] and r["tokens"] == peer[0]["tokens"]
+    assert _rel(torch.tensor(coll[0]["logits"]), ref) <= 0.03
+
+
 @pytest.mark.parametrize("world", [2])
 def test_quantised_tensor_parallel_matches_single_gpu(world, tmp_path):
     """4-bit (group 64) weights quantised per rank slice: row-parallel partials summed by the one-shot all-reduce.
