@@ -326,10 +326,11 @@ def main() -> int:
                   ep_mode=args.ep_mode if is_moe else "replicated")
     if is_moe and args.router_skew > 0:
         period = max(1, round(1.0 / args.router_skew))
-        hot = torch.arange(8, device=dev)
+        boost = torch.zeros(cfg.num_experts, dtype=torch.float32, device=dev)
+        boost[:8] = 30.0        # experts 0..7 are the hot ones (all owned by the first expert rank)
         for lw in model.layers:
             if lw.moe is not None:
-                lw.moe.skew = (period, hot, 30.0)
+                lw.moe.skew = (period, boost)
     eng = Engine(model, max_batch=B, max_seq_len=P + budget, prefill_chunk=8192)
     rng = np.random.default_rng(0)
     prompts = [rng.integers(0, cfg.vocab_size, P).tolist() for _ in range(B)]

@@ -38,8 +38,8 @@ class MoEBlock:
         self.down_bias = down_bias                    # [E_local, H]
         self.act = act
         self.stats = {"calls": 0}
-        # benchmark knob: (period, hot expert ids tensor, bias) - every period-th token gets `bias` added to the router
-        # logits of the hot experts (a skewed-router load: 1 / period of the tokens crowd onto a few experts)
+        # benchmark knob: (period, boost [E] fp32 on the device) - every period-th token gets `boost` added to its router
+        # logits (a skewed-router load: 1 / period of the tokens crowd onto the boosted experts)
         self.skew = None
 
     def tensors(self):
@@ -67,11 +67,9 @@ class MoEBlock:
         """fp32 router logits of the rows of x; ``row0`` is the global token index of row 0 (token-sharded callers)."""
         logits = ops.linear(x, self.router_w, bias=self.router_linear_bias, out_dtype=torch.float32)
         if self.skew is not None:
-            period, hot, bias = self.skew
+            period, boost = self.skew
             rows = torch.arange(row0, row0 + x.shape[0], device=x.device)
             pick = ((rows % period) == 0).to(logits.dtype)[:, None]
-            boost = torch.zeros(logits.shape[1], dtype=logits.dtype, device=x.device)
-            boost[hot] = bias
             logits = logits + pick * boost[None, :]
         return logits
 

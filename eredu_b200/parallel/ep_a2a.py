@@ -229,5 +229,6 @@ def attach_ep_a2a(model, par, backend: str = "peer", max_tokens: int = 8192) -> 
                                lw.moe.w_gate_up.shape[0], max_tokens)
             else:
                 impl = CollectiveA2A(group, dist.get_rank(group), dist.get_world_size(group))
+                model.eager_collectives = True      # split sizes are read on the host: such steps cannot be captured
         lw.moe.ep_a2a = impl
     model.ep_a2a = impl

@@ -454,6 +454,8 @@ class Engine:
             return True    # no attention kernel for this head size: the tensor-operation path reads lengths on the host
         if getattr(m, "residency", None) is not None or getattr(getattr(m, "inner", m), "observer", None) is not None:
             return True
+        if getattr(m, "eager_collectives", False):
+            return True    # a collective of the step reads counts on the host (the torch.distributed all-to-all baseline)
         return any(getattr(getattr(lw, "moe", None), "expert_cache", None) is not None for lw in getattr(m, "layers", []))
 
     def decode_step(self, host_tokens: Optional[torch.Tensor] = None, sync: bool = True) -> Optional[torch.Tensor]:
