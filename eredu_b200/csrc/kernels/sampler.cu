@@ -11,12 +11,11 @@
 // Randomness is position addressed: the uniform for (seed, stream, position, purpose) is a pure
 // function (Philox4x32-10), so batching and scheduling never change committed tokens.
 //
-// One CTA (1024 threads) per logits row. Two kernels: `sampler_kernel` for batches whose rows are all greedy (penalties,
-// mask, argmax) and `sampler_stochastic_kernel` for any mix. The top-k/top-p path selects at most 1024 candidates: the
-// key of the K-th largest logit comes from a 16-round search over the key bits with block-wide counts, the candidates
-// are ordered by rank (position = number of candidates ahead) and scanned. With top-k disabled and top-p < 1 the
-// candidate set is the 1024 largest logits with probabilities normalised over the full vocabulary. With both disabled
-// the kernel samples the full (min-p filtered) vocabulary in index order.
+// One CTA (1024 threads) per logits row. The top-k/top-p path selects at most 1024 candidates with an
+// exact 4-pass radix select (integer histograms: deterministic), sorts them in shared memory and
+// scans them. With top-k disabled and top-p < 1 the candidate set is the 1024 largest logits with
+// probabilities normalised over the full vocabulary. With both disabled the kernel samples the
+// full (min-p filtered) vocabulary in index order.
 #include "../common/launch.h"
 #include "../common/launch_count.h"
 #include "../common/ptx.cuh"
@@ -182,7 +181,14 @@ __device__ __forceinline__ float load_logit(const SamplerParams& p, const float*
 }
 
 __global__ void __launch_bounds__(kSampThreads) sampler_kernel(SamplerParams p) {
-  __shared__ BlockScratch scr;
+  __shared__ __align__(16) BlockScratch scr;
+  __shared__ __align__(16) int hist[256];
+  __shared__ __align__(16) uint32_t cand_key[kCand];
+  __shared__ __align__(16) uint32_t cand_idx[kCand];
+  __shared__ int sh_count;
+  __shared__ uint32_t sh_prefix;
+  __shared__ int sh_krem;
+  __shared__ int sh_pick;
 
   pdl_launch_early();
   trace_mark(kTraceSampler, kTraceStart);
@@ -248,128 +254,6 @@ __global__ void __launch_bounds__(kSampThreads) sampler_kernel(SamplerParams p) 
     return;
   }
 
-  // rows with temperature > 0 belong to sampler_stochastic_kernel; a stray one gets the most likely token
-  if (tid == 0) p.tokens[r] = imax;
-  if (prow != nullptr) {
-    for (int i = tid; i < V; i += kSampThreads) prow[i] = (i == imax) ? 1.f : 0.f;
-  }
-}
-
-// ------------------------------------------------------------------ stochastic rows
-// Sum of three per-thread counters over the block in one pass (results in all threads).
-__device__ __forceinline__ void block_sum3(int& a, int& b, int& c, int* sh /* [3 * 32 + 3] */) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    a += __shfl_xor_sync(0xffffffffu, a, o);
-    b += __shfl_xor_sync(0xffffffffu, b, o);
-    c += __shfl_xor_sync(0xffffffffu, c, o);
-  }
-  __syncthreads();
-  if ((threadIdx.x & 31) == 0) {
-    sh[threadIdx.x >> 5] = a;
-    sh[32 + (threadIdx.x >> 5)] = b;
-    sh[64 + (threadIdx.x >> 5)] = c;
-  }
-  __syncthreads();
-  if (threadIdx.x < 32) {
-    int x = sh[threadIdx.x], y = sh[32 + threadIdx.x], z = sh[64 + threadIdx.x];
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      x += __shfl_xor_sync(0xffffffffu, x, o);
-      y += __shfl_xor_sync(0xffffffffu, y, o);
-      z += __shfl_xor_sync(0xffffffffu, z, o);
-    }
-    if (threadIdx.x == 0) {
-      sh[96] = x;
-      sh[97] = y;
-      sh[98] = z;
-    }
-  }
-  __syncthreads();
-  a = sh[96];
-  b = sh[97];
-  c = sh[98];
-}
-
-// One CTA (1024 threads) per logits row, any mix of greedy and stochastic rows. Construction of the candidate path:
-//   * the key of the K-th largest logit by a 16-round search over the 32 key bits, two bits per round, each round three
-//     block-wide COUNTS (no histogram, no atomics);
-//   * candidates (key >= that key) written at offsets from a block prefix sum of per-thread counts;
-//   * order by RANK: candidate a goes to position #{b ahead of a} (ahead = larger key, ties by smaller index), one pass over
-//     the candidates in shared memory per thread (no comparator network);
-//   * then top-p at temperature 1, min-p, temperature and the categorical draw over the ordered survivors.
-// Every global and shared access is a 4-byte scalar.
-__global__ void __launch_bounds__(kSampThreads) sampler_stochastic_kernel(SamplerParams p) {
-  __shared__ BlockScratch scr;
-  __shared__ int cnt3[3 * 32 + 3];
-  __shared__ uint32_t ukey[kCand];   // unordered candidates
-  __shared__ uint32_t uidx[kCand];
-  __shared__ uint32_t skey[kCand];   // ordered candidates
-  __shared__ uint32_t sidx[kCand];
-  __shared__ int sh_pick;
-
-  pdl_launch_early();
-  trace_mark(kTraceSampler, kTraceStart);
-  pdl_wait();
-  trace_mark(kTraceSampler, kTraceAfterWait);
-  pdl_launch_dependents();
-  const int r = blockIdx.x;
-  const int tid = threadIdx.x;
-  SamplerRow cfg;
-  {  // word by word: a row sits at a multiple of 56 bytes, which is 4-byte but not 8- or 16-byte aligned for odd rows
-    const int* src = reinterpret_cast<const int*>(p.rows + r);
-    int* dst = reinterpret_cast<int*>(&cfg);
-#pragma unroll
-    for (int i = 0; i < static_cast<int>(sizeof(SamplerRow) / 4); ++i) dst[i] = src[i];
-  }
-  float* row = p.logits + static_cast<size_t>(r) * p.V;
-  const uint32_t* allow = p.allow ? p.allow + static_cast<size_t>(r) * p.allow_stride : nullptr;
-  float* prow = p.probs ? p.probs + static_cast<size_t>(r) * p.V : nullptr;
-  const int V = p.V;
-
-  // ---- 1. penalties, in place, once per distinct token of the window
-  if ((cfg.repeat_penalty != 1.f || cfg.frequency_penalty != 0.f || cfg.presence_penalty != 0.f) && cfg.hist_len > 0 &&
-      p.history != nullptr) {
-    const int* h = p.history + static_cast<size_t>(r) * p.hist_stride;
-    const int start = cfg.repeat_last_n < 0 ? 0 : max(0, cfg.hist_len - cfg.repeat_last_n);
-    for (int j = start + tid; j < cfg.hist_len; j += kSampThreads) {
-      const int tok = h[j];
-      if (tok < 0 || tok >= V) continue;
-      int count = 0;
-      bool first = true;
-      for (int q = start; q < cfg.hist_len; ++q) {
-        if (h[q] == tok) {
-          ++count;
-          if (q < j) first = false;
-        }
-      }
-      if (first) {
-        float x = row[tok];
-        if (cfg.repeat_penalty != 1.f) x = x > 0.f ? x / cfg.repeat_penalty : x * cfg.repeat_penalty;
-        x -= cfg.frequency_penalty * static_cast<float>(count) + cfg.presence_penalty;
-        row[tok] = x;
-      }
-    }
-    __syncthreads();
-  }
-
-  // ---- 2. max / argmax
-  float vmax = -INFINITY;
-  int imax = 0x7fffffff;
-  for (int i = tid; i < V; i += kSampThreads) {
-    const float x = load_logit(p, row, allow, i);
-    if (x > vmax) { vmax = x; imax = i; }
-  }
-  block_argmax(vmax, imax, scr);
-  if (imax == 0x7fffffff) imax = 0;
-  if (cfg.temperature == 0.f) {
-    if (tid == 0) p.tokens[r] = imax;
-    if (prow != nullptr) {
-      for (int i = tid; i < V; i += kSampThreads) prow[i] = (i == imax) ? 1.f : 0.f;
-    }
-    return;
-  }
-
   const float inv_t = 1.f / cfg.temperature;
   const bool use_topk = cfg.top_k > 0 && cfg.top_k < V;
   const bool use_topp = cfg.top_p < 1.f;
@@ -377,9 +261,9 @@ __global__ void __launch_bounds__(kSampThreads) sampler_stochastic_kernel(Sample
   const float u = philox_uniform(cfg.seed_lo, cfg.seed_hi, cfg.stream_id, static_cast<uint32_t>(cfg.position), 0u);
 
   if (!use_topk && !use_topp) {
-    // ---- dense: categorical over {x >= min-p threshold} in index order; thread t owns tokens [t * seg, (t + 1) * seg)
+    // ---- dense path: categorical over {x >= min-p threshold} in index order
     const int seg = (V + kSampThreads - 1) / kSampThreads;
-    const int lo = min(V, tid * seg), hi = min(V, lo + seg);
+    const int lo = tid * seg, hi = min(V, lo + seg);
     float local = 0.f;
     for (int i = lo; i < hi; ++i) {
       const float x = load_logit(p, row, allow, i);
@@ -388,6 +272,7 @@ __global__ void __launch_bounds__(kSampThreads) sampler_stochastic_kernel(Sample
     const float incl = block_scan_incl(local, scr);
     const float total = block_sum(local, scr);
     const float target = u * total;
+    // the first thread whose inclusive sum exceeds the target owns the sample
     const int owner = block_min_int((incl > target && local > 0.f) ? tid : kSampThreads, scr);
     if (tid == 0) sh_pick = imax;
     __syncthreads();
@@ -416,59 +301,72 @@ __global__ void __launch_bounds__(kSampThreads) sampler_stochastic_kernel(Sample
     return;
   }
 
-  // ---- 3. key of the K-th largest logit: the largest key v with count(key >= v) >= K
+  // ---- 3. radix select: key of the K-th largest logit
   const int K = use_topk ? min(cfg.top_k, kCand) : min(V, kCand);
-  uint32_t prefix = 0u;
-  for (int bit = 30; bit >= 0; bit -= 2) {
-    const uint32_t c1 = prefix | (1u << bit), c2 = prefix | (2u << bit), c3 = prefix | (3u << bit);
-    int n1 = 0, n2 = 0, n3 = 0;
+  if (tid == 0) { sh_prefix = 0u; sh_krem = K; }
+  __syncthreads();
+  for (int pass = 0; pass < 4; ++pass) {
+    const int shift = 24 - 8 * pass;
+    if (tid < 256) hist[tid] = 0;
+    __syncthreads();
+    const uint32_t prefix = sh_prefix;
+    const uint32_t himask = pass == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
     for (int i = tid; i < V; i += kSampThreads) {
       const uint32_t k = f2key(load_logit(p, row, allow, i));
-      n1 += k >= c1 ? 1 : 0;
-      n2 += k >= c2 ? 1 : 0;
-      n3 += k >= c3 ? 1 : 0;
+      if ((k & himask) == prefix) atomicAdd(&hist[(k >> shift) & 255u], 1);
     }
-    block_sum3(n1, n2, n3, cnt3);
-    prefix = n3 >= K ? c3 : (n2 >= K ? c2 : (n1 >= K ? c1 : prefix));
-  }
-  const uint32_t thr_key = prefix;
-  const uint32_t neg_inf_key = f2key(-INFINITY);
-
-  // ---- 4. candidates at offsets from a prefix sum of per-thread counts, then ordered by rank
-  int mine = 0;
-  for (int i = tid; i < V; i += kSampThreads) {
-    const uint32_t k = f2key(load_logit(p, row, allow, i));
-    mine += (k >= thr_key && k > neg_inf_key) ? 1 : 0;
-  }
-  const float incl_f = block_scan_incl(static_cast<float>(mine), scr);  // counts <= V < 2^24: exact in fp32
-  const int total_c = static_cast<int>(block_sum(static_cast<float>(mine), scr));
-  int slot = static_cast<int>(incl_f) - mine;
-  for (int i = tid; i < V; i += kSampThreads) {
-    const uint32_t k = f2key(load_logit(p, row, allow, i));
-    if (k >= thr_key && k > neg_inf_key) {
-      if (slot < kCand) {
-        ukey[slot] = k;
-        uidx[slot] = static_cast<uint32_t>(i);
+    __syncthreads();
+    if (tid == 0) {
+      int krem = sh_krem;
+      int b = 255;
+      for (; b > 0; --b) {
+        if (hist[b] >= krem) break;
+        krem -= hist[b];
       }
-      ++slot;
+      sh_prefix = prefix | (static_cast<uint32_t>(b) << shift);
+      sh_krem = krem;
+    }
+    __syncthreads();
+  }
+  const uint32_t thr_key = sh_prefix;
+
+  // ---- 4. gather candidates (key >= threshold), sort descending by (key, then smaller index first)
+  if (tid == 0) sh_count = 0;
+  cand_key[tid] = 0u;
+  cand_idx[tid] = 0xFFFFFFFFu;
+  __syncthreads();
+  for (int i = tid; i < V; i += kSampThreads) {
+    const uint32_t k = f2key(load_logit(p, row, allow, i));
+    if (k >= thr_key && k > f2key(-INFINITY)) {
+      const int slot = atomicAdd(&sh_count, 1);
+      if (slot < kCand) {
+        cand_key[slot] = k;
+        cand_idx[slot] = static_cast<uint32_t>(i);
+      }
     }
   }
-  const int ncand = min(total_c, kCand);
   __syncthreads();
-  if (tid < ncand) {
-    const uint32_t ka = ukey[tid], ia = uidx[tid];
-    int rank = 0;
-    for (int j = 0; j < ncand; ++j) {
-      const uint32_t kb = ukey[j], ib = uidx[j];
-      rank += (kb > ka || (kb == ka && ib < ia)) ? 1 : 0;
+  // bitonic sort, descending by key, ties by ascending index (empty slots: key 0 sorts last)
+  for (int k = 2; k <= kCand; k <<= 1) {
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      const int ixj = tid ^ j;
+      if (ixj > tid) {
+        const uint32_t ka = cand_key[tid], kb = cand_key[ixj];
+        const uint32_t ia = cand_idx[tid], ib = cand_idx[ixj];
+        const bool a_before_b = (ka > kb) || (ka == kb && ia < ib);  // a ranks ahead of b
+        const bool desc = (tid & k) == 0;
+        if (desc ? !a_before_b : a_before_b) {
+          cand_key[tid] = kb; cand_idx[tid] = ib;
+          cand_key[ixj] = ka; cand_idx[ixj] = ia;
+        }
+      }
+      __syncthreads();
     }
-    skey[rank] = ka;
-    sidx[rank] = ia;
   }
-  __syncthreads();
+  const int ncand = min(sh_count, kCand);
   const bool valid = tid < ncand;
-  const float x = valid ? key2f(skey[tid]) : -INFINITY;
-  const int tok = valid ? static_cast<int>(sidx[tid]) : 0;
+  const float x = valid ? key2f(cand_key[tid]) : -INFINITY;
+  const int tok = valid ? static_cast<int>(cand_idx[tid]) : 0;
 
   // ---- 5. top-p at temperature 1 on the top-k survivors
   const float p1 = valid ? __expf(x - vmax) : 0.f;
@@ -486,7 +384,7 @@ __global__ void __launch_bounds__(kSampThreads) sampler_stochastic_kernel(Sample
   keep = keep && (x >= minp_thr);
   if (tid == 0) keep = valid;  // the most likely token always survives
 
-  // ---- 6. temperature + categorical over the survivors (ordered)
+  // ---- 6. temperature + categorical over the survivors (sorted order)
   const float w = keep ? __expf((x - vmax) * inv_t) : 0.f;
   const float wcum = block_scan_incl(w, scr);
   const float wtot = block_sum(w, scr);
@@ -496,7 +394,7 @@ __global__ void __launch_bounds__(kSampThreads) sampler_stochastic_kernel(Sample
     pick = kCand - 1 - block_min_int(keep ? (kCand - 1 - tid) : kCand, scr);
     if (pick < 0 || pick >= kCand) pick = 0;
   }
-  if (tid == pick) p.tokens[r] = valid ? tok : imax;
+  if (tid == pick) p.tokens[r] = tok;
   if (prow != nullptr) {
     for (int i = tid; i < V; i += kSampThreads) prow[i] = 0.f;
     __syncthreads();
@@ -644,26 +542,6 @@ extern "C" int eredu_sample(float* logits, const unsigned int* allow, int allow_
   p.probs = probs;
   p.V = V;
   launch_pdl(sampler_kernel, dim3(n_rows), dim3(kSampThreads), 0, stream, p);
-  eredu_count_launches(1);
-  return static_cast<int>(cudaGetLastError());
-}
-
-// Same arguments; rows may have temperature > 0 (top-k / top-p / min-p / categorical draw on the device).
-extern "C" int eredu_sample_stochastic(float* logits, const unsigned int* allow, int allow_stride, const void* rows,
-                                       const int* history, int hist_stride, int* tokens, float* probs, int n_rows, int V,
-                                       cudaStream_t stream) {
-  if (n_rows <= 0) return 0;
-  SamplerParams p;
-  p.logits = logits;
-  p.allow = allow;
-  p.allow_stride = allow_stride;
-  p.rows = static_cast<const SamplerRow*>(rows);
-  p.history = history;
-  p.hist_stride = hist_stride;
-  p.tokens = tokens;
-  p.probs = probs;
-  p.V = V;
-  launch_pdl(sampler_stochastic_kernel, dim3(n_rows), dim3(kSampThreads), 0, stream, p);
   eredu_count_launches(1);
   return static_cast<int>(cudaGetLastError());
 }

@@ -33,7 +33,6 @@ _SIGNATURES = {
     "eredu_launch_count": (L, []),
     "eredu_selftest_bounded_wait": (I, [P, L, P]),
     "eredu_sample": (I, [P, P, I, P, P, I, P, P, I, I, P]),
-    "eredu_sample_stochastic": (I, [P, P, I, P, P, I, P, P, I, I, P]),
     "eredu_spec_verify": (I, [P, P, P, P, P, I, I, I, P]),
 }
 

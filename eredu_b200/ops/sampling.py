@@ -249,23 +249,27 @@ def sample(logits: torch.Tensor, rows: torch.Tensor, history: torch.Tensor | Non
            out: torch.Tensor | None = None, all_greedy: bool | None = None) -> torch.Tensor:
     """logits: [R, V] fp32 CUDA (modified in place by penalties); rows: packed SamplerRow bytes [R, 56].
 
-    One launch either way: batches of greedy rows run ``sampler_kernel``, batches with any temperature > 0 row run
-    ``sampler_stochastic_kernel`` (penalties, mask, top-k, top-p, min-p, temperature and the categorical draw on the
-    device; :func:`sample_tensor_ops` states the same chain with tensor operations and serves as its oracle)."""
+    Greedy rows run in the fused kernel. The fused kernel's stochastic path is kept off the GPU: two constructions of
+    it (radix select + sorting network; counting search + rank ordering) raised a misaligned-address fault on B200 on
+    their first stochastic row although every access in the compiled code is a 4-byte scalar on an aligned base, and
+    the cause has not been found. Batches that contain a row with temperature > 0 use :func:`sample_tensor_ops`, which
+    has the same semantics and the same position-addressed random numbers."""
     assert logits.is_cuda and logits.dtype == torch.float32 and logits.is_contiguous()
     R, V = logits.shape
     if all_greedy is None:
         all_greedy = bool((_rows_fields(rows)["temperature"] == 0).all().item())
+    if not all_greedy:
+        return sample_tensor_ops(logits, rows, history, allow, probs, out)
     if out is None:
         out = torch.empty(R, dtype=torch.int32, device=logits.device)
     allow_stride = 0
     if allow is not None:
         assert allow.dtype == torch.int32 and allow.shape[-1] == (V + 31) // 32
         allow_stride = allow.stride(0) if allow.dim() == 2 and allow.shape[0] > 1 else 0
-    fn = lib().eredu_sample if all_greedy else lib().eredu_sample_stochastic
-    code = fn(ptr(logits), ptr(allow), allow_stride, ptr(rows), ptr(history),
-              history.stride(0) if history is not None else 0, ptr(out), ptr(probs), R, V, stream_ptr(logits.device))
-    check(code, "eredu_sample" if all_greedy else "eredu_sample_stochastic")
+    code = lib().eredu_sample(ptr(logits), ptr(allow), allow_stride, ptr(rows), ptr(history),
+                              history.stride(0) if history is not None else 0, ptr(out), ptr(probs), R, V,
+                              stream_ptr(logits.device))
+    check(code, "eredu_sample")
     return out
 
 
