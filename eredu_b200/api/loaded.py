@@ -47,6 +47,8 @@ class ModelLoadOptions:
     expert_cache: bool = False                   # routed experts in host memory behind a bounded device bank
     expert_cache_device_budget_bytes: Optional[int] = None   # per sparse layer; None: a quarter of the experts
     expert_cache_eviction: str = "lru"
+    expert_cache_scratch_bytes: int = 1 << 30        # permuted activations of one expert-cache pass (longer inputs are sliced)
+    expert_cache_prefill_bank_bytes: int = 1 << 30   # transient expert bank of prompt-sized calls
     embedded_mtp: bool = True                    # bind the checkpoint's own prediction layer (when it has one) as a drafter
 
 
@@ -127,11 +129,12 @@ class LoadedModel:
         if opt.expert_cache and src.cfg.is_moe:
             from ..runtime.expert_cache import attach_expert_cache
 
+            sizing = dict(eviction=opt.expert_cache_eviction, scratch_bytes=opt.expert_cache_scratch_bytes,
+                          prefill_bank_bytes=opt.expert_cache_prefill_bank_bytes)
             if opt.expert_cache_device_budget_bytes:
-                attach_expert_cache(model, device_budget_bytes=opt.expert_cache_device_budget_bytes,
-                                    eviction=opt.expert_cache_eviction)
+                attach_expert_cache(model, device_budget_bytes=opt.expert_cache_device_budget_bytes, **sizing)
             else:
-                attach_expert_cache(model, slots=max(1, src.cfg.num_experts // 4), eviction=opt.expert_cache_eviction)
+                attach_expert_cache(model, slots=max(1, src.cfg.num_experts // 4), **sizing)
         if opt.parallel is not None and opt.parallel.tp_size > 1:
             from ..parallel import tp
 

@@ -102,6 +102,50 @@ def validate_args(a) -> None:
         raise SystemExit("--allow-mixed-revisions conflicts with --require-same-revision")
     if not (a.device == "cpu" or a.device.startswith("gpu:")):
         raise SystemExit("--device must be cpu or gpu:N")
+    # flags of the reference's front end that have no counterpart in this runtime are refused, not silently recorded
+    if a.mtp_draft_device != "target":
+        raise SystemExit("--mtp-draft-device: not supported on this runtime (the prediction head runs on the target's GPU; "
+                         "only 'target' is accepted)")
+    if a.mlx_cache_limit_bytes is not None and a.mlx_cache_limit_bytes <= 0:
+        raise SystemExit("--mlx-cache-limit-bytes must be positive")
+    for flag, val in (("--expert-cache-scratch-bytes", a.expert_cache_scratch_bytes),
+                      ("--expert-cache-prefill-bank-bytes", a.expert_cache_prefill_bank_bytes)):
+        if val <= 0:
+            raise SystemExit(f"{flag} must be positive")
+
+
+def resolve_revision(model_path: str, revision, allow_mixed: bool, require_same: bool) -> str:
+    """``--revision`` for models named by a Hugging Face cache entry (``.../models--org--name``: ``refs/<name>`` holds a
+    commit id, ``snapshots/<commit>`` the files). Nothing is downloaded (eredu-cli/src/main.rs:3139-3230 resolves local
+    cache entries the same way). A plain directory or a GGUF file has no revisions: asking for one is an error, and
+    ``--require-same-revision`` then has nothing to check."""
+    import os
+
+    snaps = os.path.join(model_path, "snapshots")
+    if not os.path.isdir(snaps):
+        if revision is not None:
+            raise SystemExit(f"--revision {revision}: {model_path} is not a Hugging Face cache entry (no snapshots/ directory)")
+        return model_path
+    commits = sorted(os.listdir(snaps))
+    if not commits:
+        raise SystemExit(f"{model_path}: the cache entry has no snapshot")
+    want = revision
+    if want is None:
+        ref = os.path.join(model_path, "refs", "main")
+        want = open(ref).read().strip() if os.path.isfile(ref) else None
+    else:
+        ref = os.path.join(model_path, "refs", want)
+        if os.path.isfile(ref):
+            want = open(ref).read().strip()
+    if want is None:
+        if len(commits) > 1 and not allow_mixed:
+            raise SystemExit(f"{model_path}: several snapshots and no refs/main; pass --revision (or --allow-mixed-revisions "
+                             f"to take the newest)")
+        want = max(commits, key=lambda c: os.path.getmtime(os.path.join(snaps, c)))
+    match = [c for c in commits if c == want or c.startswith(want)]
+    if len(match) != 1:
+        raise SystemExit(f"--revision {revision or want}: no unique snapshot among {commits}")
+    return os.path.join(snaps, match[0])
 
 
 def resolve_sampling(a, generation_config: dict):
@@ -212,7 +256,23 @@ def main(argv=None) -> int:
     from ..runtime.telemetry import ExecutionTelemetry, hardware_profile
 
     model_path, _, quant_suffix = a.model.partition(":")
+    model_path = resolve_revision(model_path, a.revision, a.allow_mixed_revisions, a.require_same_revision)
+    if a.draft_model and a.require_same_revision:
+        # draft and target must come from the same commit when both are cache entries
+        import os
+
+        d = resolve_revision(a.draft_model, a.revision, a.allow_mixed_revisions, True)
+        if os.path.basename(d) != os.path.basename(model_path) and os.path.isdir(os.path.join(a.draft_model, "snapshots")):
+            raise SystemExit("--require-same-revision: draft and target snapshots differ")
+        a.draft_model = d
     device = "cpu" if a.device == "cpu" else "cuda:" + a.device.split(":", 1)[1]
+    if a.mlx_cache_limit_bytes is not None and device != "cpu":
+        # the tensor engine's caching allocator here is PyTorch's: the limit becomes its per-process cap
+        import torch
+
+        idx = int(device.split(":")[1])
+        total = torch.cuda.get_device_properties(idx).total_memory
+        torch.cuda.set_per_process_memory_fraction(min(1.0, a.mlx_cache_limit_bytes / total), idx)
     quant = None
     bits = a.quantize or (int(quant_suffix) if quant_suffix.isdigit() else None)
     if bits:
@@ -312,7 +372,9 @@ def main(argv=None) -> int:
                                                        embedded_mtp=a.mtp_draft_tokens > 0 and not a.draft_model,
                                                        expert_cache=expert_cache,
                                                        expert_cache_device_budget_bytes=ec_budget,
-                                                       expert_cache_eviction=ec_eviction))
+                                                       expert_cache_eviction=ec_eviction,
+                                                       expert_cache_scratch_bytes=a.expert_cache_scratch_bytes,
+                                                       expert_cache_prefill_bank_bytes=a.expert_cache_prefill_bank_bytes))
     load_time = time.perf_counter() - t0
     gen_cfg = lm.tokenizer.generation_config if lm.tokenizer else {}
     sp = resolve_sampling(a, gen_cfg)

@@ -66,3 +66,31 @@ def test_expert_cache_gpu():
     agree = sum(a == b for x, y in zip(ref, got) for a, b in zip(x, y))
     assert agree >= 12      # several passes change the bf16 summation order of a token's routes
     assert caches[0].report()["evictions"] > 0
+
+
+def test_scratch_slices_prefill_bank_and_biases():
+    """A scratch bound slices long inputs, prompt-sized calls run over the transient bank without disturbing the decode
+    bank, and per-expert biases travel with their expert: outputs equal the resident computation every time."""
+    from eredu_b200.ops import moe as M
+
+    torch.manual_seed(0)
+    T, H, I, E, k = 70, 16, 8, 6, 2
+    x = torch.randn(T, H)
+    gu, dn = torch.randn(E, 2 * I, H) * 0.3, torch.randn(E, H, I) * 0.3
+    gub, dnb = torch.randn(E, 2 * I) * 0.1, torch.randn(E, H) * 0.1
+    ids, w = M.route_ref(torch.randn(T, E), k)
+    want = M.experts_ref(x, ids, w, gu, dn, gu_bias=gub, down_bias=dnb)
+    per_route = (2 * H + I) * 4
+    cache = ExpertCache(gu.clone(), dn.clone(), 2, "lru", gu_bias=gub.clone(), down_bias=dnb.clone(),
+                        scratch_bytes=10 * k * per_route)           # ten tokens per slice
+    got = cache.forward(x, ids, w)
+    assert torch.allclose(got, want, atol=1e-5) and cache.stats.calls == 7
+    big = ExpertCache(gu.clone(), dn.clone(), 2, "lru", gu_bias=gub.clone(), down_bias=dnb.clone(),
+                      prefill_bank_bytes=4 * (gu[0].numel() + dn[0].numel()) * 4)
+    big.acquire([0, 1])
+    before = dict(big.slot_of)
+    got = big.forward(x, ids, w)                                      # 70 tokens: prompt-sized, four transient slots
+    assert torch.allclose(got, want, atol=1e-5) and big.slot_of == before and big.stats.passes == 2
+    got1 = big.forward(x[:3], ids[:3], w[:3])                         # decode-sized: the two-slot bank
+    assert torch.allclose(got1, want[:3], atol=1e-5)
+
