@@ -45,57 +45,6 @@ static std::vector<std::pair<int64_t, int64_t>> aligned_partition_units(int64_t 
   return out;
 }
 
-struct Topology {
-  int data = 1, pipeline = 1, tensor = 1, expert = 1;
-  bool expert_over_tensor = false;
-
-  Topology(int d, int p, int t, int e, bool eot) : data(d), pipeline(p), tensor(t), expert(e), expert_over_tensor(eot) {
-    if (d < 1 || p < 1 || t < 1 || e < 1) throw std::invalid_argument("parallel sizes must be >= 1");
-    if (eot && e != t) throw std::invalid_argument("expert_over_tensor requires expert == tensor");
-  }
-  int world() const { return data * pipeline * tensor * (expert_over_tensor ? 1 : expert); }
-  std::map<std::string, int> coordinates(int rank) const {
-    if (rank < 0 || rank >= world()) throw std::out_of_range("rank outside the world");
-    int tp, ep, rest;
-    if (expert_over_tensor) {
-      tp = rank % tensor;
-      rest = rank / tensor;
-      ep = tp;
-    } else {
-      ep = rank % expert;
-      rest = rank / expert;
-      tp = rest % tensor;
-      rest /= tensor;
-    }
-    return {{"data", rest / pipeline}, {"pipeline", rest % pipeline}, {"tensor", tp}, {"expert", ep}};
-  }
-  int rank_for(int d, int p, int t, int e) const {
-    if (expert_over_tensor) {
-      if (e != t) throw std::invalid_argument("expert coordinate aliases the tensor coordinate");
-      return (d * pipeline + p) * tensor + t;
-    }
-    return ((d * pipeline + p) * tensor + t) * expert + e;
-  }
-  std::vector<int> axis_members(int rank, const std::string& axis) const {
-    auto c = coordinates(rank);
-    const int size = axis == "data" ? data : axis == "pipeline" ? pipeline : axis == "tensor" ? tensor : expert;
-    std::vector<int> out;
-    for (int i = 0; i < size; ++i) {
-      auto cc = c;
-      cc[axis] = i;
-      if (expert_over_tensor && (axis == "tensor" || axis == "expert")) cc["tensor"] = cc["expert"] = i;
-      out.push_back(rank_for(cc["data"], cc["pipeline"], cc["tensor"], cc["expert"]));
-    }
-    return out;
-  }
-  std::pair<int64_t, int64_t> layer_range(int rank, int64_t layers) const {
-    return balanced_range(layers, pipeline, coordinates(rank)["pipeline"]);
-  }
-  std::pair<int64_t, int64_t> expert_range(int rank, int64_t experts) const {
-    return balanced_range(experts, expert, coordinates(rank)["expert"]);
-  }
-};
-
 // ============================================================================================ block manager
 // Pages are 16-token KV slabs. Page 0 is reserved (padding target). Sealed (full, immutable) pages can be
 // registered under a content hash for prefix reuse; an unreferenced sealed page stays cached until evicted
@@ -480,15 +429,6 @@ static std::vector<int> resolve_completions(const std::vector<uint32_t>& gathere
 void bind_runtime(py::module_& m) {
   m.def("balanced_contiguous_range", &balanced_range);
   m.def("aligned_partition_units", &aligned_partition_units);
-  py::class_<Topology>(m, "Topology")
-      .def(py::init<int, int, int, int, bool>(), py::arg("data") = 1, py::arg("pipeline") = 1, py::arg("tensor") = 1,
-           py::arg("expert") = 1, py::arg("expert_over_tensor") = false)
-      .def_property_readonly("world_size", &Topology::world)
-      .def("coordinates", &Topology::coordinates)
-      .def("rank_for", &Topology::rank_for)
-      .def("axis_members", &Topology::axis_members)
-      .def("layer_range", &Topology::layer_range)
-      .def("expert_range", &Topology::expert_range);
   py::class_<BlockManager>(m, "BlockManager")
       .def(py::init<int64_t, const std::string&>(), py::arg("num_pages"), py::arg("eviction") = "lru")
       .def("free_pages", &BlockManager::free_pages)

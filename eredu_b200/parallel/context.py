@@ -23,6 +23,10 @@ class ParallelContext:
     coords: dict = field(default_factory=dict)
 
     def __post_init__(self):
+        if self.topology.data != 1:
+            # the axis is declared so that rank arithmetic stays stable, but no execution path replicates requests
+            # over it: fail closed like the reference (eredu/src/backend/mlx/distributed.rs:139-144)
+            raise ValueError("data parallelism is declared but unsupported: run one server per replica instead")
         self.coords = self.topology.coordinates(self.rank)
 
     @classmethod

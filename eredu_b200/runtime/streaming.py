@@ -142,6 +142,8 @@ class CommittedTokenPipeline:
         self.text_out: list[str] = []
         self.reasoning_out: list[str] = []
         self.tool_calls: list[dict] = []
+        self._bare_decided = False
+        self._bare_hold = ""
         self._retarget()
 
     def _retarget(self):
@@ -215,11 +217,36 @@ class CommittedTokenPipeline:
         self.tool_calls.append({"name": name, "arguments": args, "raw": raw})
         self._emit(SemanticEvent("tool_call_end", tool_name=name, tool_index=self.tool_count - 1, arguments=args), out)
         self.state = "text"
+        self._bare_decided = False
         self._retarget()
+
+    def _bare_json_gate(self, text: str, out: list) -> str:
+        """Bare-JSON tool calls (Llama-3 style ``{"name": ..., "parameters": ...}`` with no tags): the reply is a call
+        exactly when its first visible character is ``{`` (the activation rule of runtime/chat/dialect.rs:464-495).
+        Returns the text that the ordinary path still has to see."""
+        if self.state != "text" or self._bare_decided:
+            return text
+        text = self._bare_hold + text
+        self._bare_hold = ""
+        body = text.lstrip()
+        if not body:
+            self._bare_hold = text           # only white space so far: undecided
+            return ""
+        self._bare_decided = True
+        if not body.startswith("{") or (self.max_tools is not None and self.tool_count >= self.max_tools):
+            return text
+        self.state = "tool"
+        self.tool_json = JsonFragmentBuffer()
+        self.tool_count += 1
+        self._emit(SemanticEvent("tool_call_start", tool_index=self.tool_count - 1), out)
+        self._retarget()
+        return body
 
     def _feed(self, text: str, out: list):
         text = self._carry + text
         self._carry = ""
+        if self.plan is not None and getattr(self.plan, "bare_json_tools", False):
+            text = self._bare_json_gate(text, out)
         while text or False:
             released, hit = self.matcher.push(text)
             text = ""
@@ -267,8 +294,8 @@ class CommittedTokenPipeline:
             if tail:
                 self._feed(tail, out)
         if not self.finished or self.finished != FinishReason.STOP_SEQUENCE:
-            held = self._carry + self.matcher.flush()
-            self._carry = ""
+            held = self._bare_hold + self._carry + self.matcher.flush()
+            self._carry = self._bare_hold = ""
             if self.state == "tool" and held:
                 self._tool_fragment(held, out)
             else:

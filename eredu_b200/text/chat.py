@@ -36,6 +36,7 @@ class ParserPlan:
     allow_unparsed_reasoning: bool = False
     dialect: str = "generic"                 # generic | lfm2 | harmony | gemma | inkling | atem (text/dialects.py)
     render_special_tokens: bool = False      # the structural tags are special tokens: the detokeniser must show them
+    bare_json_tools: bool = False            # a reply whose first visible character is "{" is one JSON tool call
 
 
 @dataclass
@@ -101,7 +102,7 @@ def detect_plan(template: str, rendered: str, tools, thinking: str = "auto", all
         if tools:
             plan.tool_open, plan.tool_close = GEMMA_TOOL_OPEN, GEMMA_TOOL_CLOSE
         return plan
-    if "<|tool_call_start|>" in template:
+    if "<|tool_call_start|>" in template or "<|tool_list_start|>" in template:
         plan.dialect, plan.render_special_tokens = "lfm2", True
         plan.tool_open, plan.tool_close = "<|tool_call_start|>", "<|tool_call_end|>"
         return plan
@@ -110,6 +111,10 @@ def detect_plan(template: str, rendered: str, tools, thinking: str = "auto", all
             plan.tool_open, plan.tool_close = "<tool_call>", "</tool_call>"
         elif "[TOOL_CALLS]" in template:
             plan.tool_open, plan.tool_close = "[TOOL_CALLS]", None
+        elif "<|start_header_id|>" in template and '"parameters"' in template:
+            # Llama 3.x: the whole reply is {"name": ..., "parameters": {...}}; <|python_tag|> may precede it
+            plan.bare_json_tools = True
+            plan.tool_open, plan.tool_close = "<|python_tag|>", None
         else:
             plan.tool_open, plan.tool_close = "<tool_call>", "</tool_call>"
     return plan
