@@ -67,9 +67,12 @@ def main():
             a = peer.row_linear(x, w, residual=res).float()
             b = nccl.row_linear(x, w, residual=res).float()
             rel = float((a - b).norm() / b.norm())
-            link_bytes = M * args.hidden * 2 * (world - 1) / world
+            # bytes one rank sends (and receives) over NVLink: the one-shot kernel pushes its whole bf16 partial to every
+            # peer; the two-shot path moves (world-1)/world of it in each of its two phases
+            full = M * args.hidden * 2
+            link_bytes = full * (world - 1) if M <= 64 else 2 * full * (world - 1) / world
             rows.append({"op": name, "M": M, "K_local": K, "fused_us": round(t_peer, 2), "gemm_plus_nccl_us": round(t_nccl, 2),
-                         "speedup": round(t_nccl / t_peer, 2), "rel_diff": rel,
+                         "speedup": round(t_nccl / t_peer, 2), "rel_diff": rel, "nvlink_bytes_per_rank": int(link_bytes),
                          "roofline_us": round(max(2 * M * args.hidden * K / 1.6633e15, link_bytes / 770e9) * 1e6, 2)})
     native.check_status(dev)
     if rank == 0:

@@ -403,16 +403,91 @@ class LoadedModel:
             raise RuntimeError("this checkpoint has no tokenizer")
         return GrammarConstraint(self.tokenizer, kind, spec)
 
+    def _mtp_decoder(self, draft, draft_tokens: int, embedded_mtp: bool = True):
+        """The speculative decoder this model can run: an external draft model, else its own prediction layer."""
+        from ..runtime.speculative import EmbeddedMtpDecoder, SpeculativeDecoder
+
+        if draft_tokens <= 0:
+            return None
+        if draft is not None:
+            return SpeculativeDecoder(self.engine, draft.engine, k=draft_tokens)
+        if embedded_mtp and getattr(self, "mtp", None) is not None:
+            return EmbeddedMtpDecoder(self.engine, self.mtp, k=draft_tokens)
+        return None
+
+    def generate_prepared_chat_mtp_batch(self, prepared: list, sampling: Optional[SamplingParams] = None,
+                                         max_new_tokens: int = 256, on_event=None, draft: Optional["LoadedModel"] = None,
+                                         draft_tokens: int = 3, mtp_options=None, cancellations=None) -> dict:
+        """Several prepared chats as independently progressing speculative lanes over the shared weights
+        (``generate_prepared_chat_mtp_batch``, eredu/src/api/loaded.rs:285): one scheduler request per chat, each with
+        its own cache, sampler stream, semantic parser and statistics. ``on_event(lane, event)``. Returns
+        ``{"results": [per-lane dict as generate_prepared_chat], "scheduler": aggregate scheduler counters}``."""
+        import time
+
+        from ..runtime.mtp_scheduler import MtpScheduler, MtpSchedulerOptions
+        from ..runtime.streaming import FinishReason
+        from ..text.dialects import pipeline_for
+        from ..text.tokenizer import TextDecoder
+
+        if self.tokenizer is None:
+            raise RuntimeError("this checkpoint has no tokenizer")
+        spec = self._mtp_decoder(draft, draft_tokens)
+        if spec is None:
+            raise ValueError("speculative batch generation needs a draft model or a checkpoint with a prediction layer")
+        eos = set(self.eos_ids()) | set(self.tokenizer.eos_ids)
+        sched = MtpScheduler(spec, mtp_options or MtpSchedulerOptions())
+        lanes = []
+        t0 = time.perf_counter()
+        for i, prep in enumerate(prepared):
+            plan = prep.plan
+            show_special = bool(plan is not None and plan.render_special_tokens)
+            cb = (lambda ev, i=i: on_event(i, ev)) if on_event is not None else None
+            pipe = pipeline_for(plan)(TextDecoder(self.tokenizer, skip_special_tokens=not show_special), plan, prep.stop, cb,
+                                      prep.tool_choice.max_parallel_calls)
+            pipe.tools = prep.tools
+            lane = {"pipe": pipe, "tokens": [], "first": None, "prompt": self.tokenizer.encode(prep.prompt)}
+
+            def on_token(tok, lane=lane):
+                if lane["first"] is None:
+                    lane["first"] = time.perf_counter()
+                if tok in eos:
+                    return FinishReason.EOS
+                lane["tokens"].append(tok)
+                lane["pipe"].push(tok)
+                return lane["pipe"].finished or None
+
+            cancel = cancellations[i].is_cancelled if cancellations is not None and cancellations[i] is not None else None
+            sched.submit(lane["prompt"], sampling or SamplingParams(), max_new_tokens, (), on_token, cancel)
+            lanes.append(lane)
+        done = sched.finish()
+        t1 = time.perf_counter()
+        results = []
+        for lane, req in zip(lanes, done.requests):
+            pipe = lane["pipe"]
+            pipe.finish(req.finish_reason or FinishReason.MAX_TOKENS)
+            n = len(lane["tokens"])
+            results.append({"text": "".join(pipe.text_out), "reasoning": "".join(pipe.reasoning_out),
+                            "tool_calls": pipe.tool_calls, "finish_reason": pipe.finished, "tokens": lane["tokens"],
+                            "prompt_tokens": len(lane["prompt"]), "stats": vars(req.stats),
+                            "timing": {"generation_time": req.stats.elapsed,
+                                       "time_to_first_token": (lane["first"] or t1) - t0,
+                                       "token_rate": n / max(1e-9, req.stats.elapsed)}})
+        self.last_speculative_stats = dict(spec.stats.summary(), scheduler=vars(done.scheduler))
+        return {"results": results, "scheduler": vars(done.scheduler)}
+
     def generate_prepared_chat(self, prepared, sampling: Optional[SamplingParams] = None, max_new_tokens: int = 256,
                                on_event=None, cancellation=None, raw: bool = False, mirostat=None, constraint=None,
-                               draft: Optional["LoadedModel"] = None, draft_tokens: int = 3, embedded_mtp: bool = True):
+                               draft: Optional["LoadedModel"] = None, draft_tokens: int = 3, embedded_mtp: bool = True,
+                               mtp_options=None):
         """Generate a reply for a :class:`PreparedChat`, streaming semantic events (reasoning, text, tool-call
         start / arguments / end, finished) to ``on_event`` (``generate_prepared_chat``, api/loaded.rs:154-227).
         ``draft`` (another loaded model with the same vocabulary) turns on speculative decoding with ``draft_tokens``
         proposals per round (``generate_prepared_chat_mtp``, api/loaded.rs:238; the committed tokens are exactly those
         plain decoding would emit). Without a draft model, a checkpoint that carries its own prediction layer
         (``self.mtp``) drafts for itself unless ``embedded_mtp`` is false or ``draft_tokens`` is 0. ``mirostat`` (an :class:`ops.controlled.MirostatV2`) and ``constraint`` (a :class:`GrammarConstraint`, e.g.
-        from :meth:`constraint_for`) switch to the host-driven controlled sampler.
+        from :meth:`constraint_for`) switch to the host-driven controlled sampler. ``mtp_options`` (a
+        :class:`runtime.mtp_scheduler.MtpSchedulerOptions`) runs the speculative request through the fair scheduler:
+        verification submitted asynchronously, optimistic lookahead behind it, adaptive switch-off.
         Returns a dict with text, reasoning, tool_calls, finish_reason, token ids and timing."""
         import time
 
@@ -475,6 +550,17 @@ class LoadedModel:
                       "grammar_complete": FinishReason.GRAMMAR_COMPLETE}.get(why, why)
             if first_token_at[0] is None:
                 first_token_at[0] = time.perf_counter()
+        elif mtp_options is not None and self._mtp_decoder(draft, draft_tokens, embedded_mtp) is not None:
+            from ..runtime.mtp_scheduler import MtpScheduler
+
+            spec = self._mtp_decoder(draft, draft_tokens, embedded_mtp)
+            sched = MtpScheduler(spec, mtp_options)
+            sched.submit(prompt_ids, sampling or SamplingParams(), max_new_tokens, (), lambda tok: on_token(0, tok))
+            done = sched.finish()
+            reason = done.requests[0].finish_reason or FinishReason.MAX_TOKENS
+            self.last_speculative_stats = dict(spec.stats.summary(), scheduler=vars(done.scheduler),
+                                               request=vars(done.requests[0].stats),
+                                               drafter="external" if draft is not None else "embedded")
         elif draft is not None:
             from ..runtime.speculative import SpeculativeDecoder
 

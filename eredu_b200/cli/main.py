@@ -449,9 +449,14 @@ def main(argv=None) -> int:
                                                                   max_seq_len=max(4096, a.max_tokens + 2048)))
         if draft.config.vocab_size != lm.config.vocab_size:
             raise SystemExit("--draft-model must share the target's vocabulary")
+    # speculative requests run through the fair scheduler; the two switches shape its lookahead
+    from ..runtime.mtp_scheduler import MtpSchedulerOptions
+
+    mtp_options = MtpSchedulerOptions(adaptive_lookahead=not a.disable_mtp_adaptive_lookahead).with_lookahead(
+        not a.disable_mtp_lookahead)
     res = lm.generate_prepared_chat(prepared, sp, a.max_tokens, on_event=on_event, raw=a.raw, mirostat=mirostat,
                                     constraint=constraint, draft=draft, draft_tokens=a.mtp_draft_tokens,
-                                    embedded_mtp=a.mtp_draft_tokens > 0)
+                                    embedded_mtp=a.mtp_draft_tokens > 0, mtp_options=mtp_options)
     sys.stdout.write("\n")
     timing = dict(res["timing"], load_time=load_time)
     if a.timing or a.verbose:

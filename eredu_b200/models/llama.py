@@ -189,6 +189,8 @@ class CausalLM:
         else:
             normed, _ = ops.rmsnorm(h, norm_w, cfg.rms_norm_eps, weight_offset=cfg.norm_weight_offset)
         if q is not None:
+            if gated_inter and hasattr(q, "gated"):
+                return q.gated(normed, bias=bias, limit=cfg.swiglu_limit)
             y = q(normed, bias=bias)
             return ops.silu_mul(y, q.out_features // 2, cfg.swiglu_limit) if gated_inter else y
         if gated_inter:

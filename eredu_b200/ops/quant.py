@@ -21,6 +21,7 @@ from .native import F, I, P, check, lib, ptr, status_word, stream_ptr
 
 native.register("eredu_qgemm", I, [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P])
 native.register("eredu_dequant_affine", I, [P, P, P, P, I, I, I, I, P])
+native.register("eredu_qgemv4", I, [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, I, P])
 native.register("eredu_qgemm_fp8", I, [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P])
 native.register("eredu_dequant_fp8", I, [P, P, P, I, I, P])
 
@@ -132,6 +133,7 @@ class QuantLinear:
     def slice_rows(self, r0: int, r1: int) -> "QuantLinear":
         out = object.__new__(QuantLinear)
         out.__dict__.update(self.__dict__)
+        out.__dict__.pop("_dq_t", None)
         out.out_features = r1 - r0
         out.wq = self.wq[r0:r1].contiguous()
         out.scales_t = self.scales_t[:, r0:r1].contiguous()
@@ -143,6 +145,7 @@ class QuantLinear:
         assert k0 % 64 == 0 and k1 % 64 == 0 and k0 % self.group == 0 and k1 % self.group == 0
         out = object.__new__(QuantLinear)
         out.__dict__.update(self.__dict__)
+        out.__dict__.pop("_dq_t", None)
         out.in_features = k1 - k0
         per = 2 if self.kbits == 4 else 1
         out.wq = self.wq[:, k0 // per:k1 // per].contiguous()
@@ -177,6 +180,50 @@ class QuantLinear:
 
     # ------------------------------------------------------------------ forward
     DENSE_FALLBACK_TOKENS = 256
+    GEMV_MAX_TOKENS = 16          # up to here the register-resident decode kernel runs (csrc/kernels/qgemv_mma.cu)
+
+    def decode_table(self) -> Optional[torch.Tensor]:
+        """int32 [K/group, N] for the decode kernel: bf16(16·scale) in the low half, bf16(bias − 16·scale) in the high
+        half of each word (the kernel builds 1 + code/16 in a bf16 mantissa, one fused multiply-add gives the weight).
+        None where that kernel does not apply (8-bit container, group that is no power of two >= 16)."""
+        if self.kbits != 4 or self.group < 16 or self.group & (self.group - 1):
+            return None
+        t = self.__dict__.get("_dq_t")
+        if t is None or t.shape != self.scales_t.shape or t.device != self.scales_t.device:
+            s = self.scales_t.float()
+            lo = (16.0 * s).to(torch.bfloat16).view(torch.int16).to(torch.int32) & 0xFFFF
+            hi = (self.biases_t.float() - 16.0 * s).to(torch.bfloat16).view(torch.int16).to(torch.int32) << 16
+            t = (lo | hi).contiguous()
+            self._dq_t = t
+        return t
+
+    def _gemv(self, x, bias, residual, out, out_dtype, gated: bool, limit: float = 0.0):
+        M, K = x.shape
+        dev = x.device
+        n_out = self.out_features // 2 if gated else self.out_features
+        if out is None:
+            out = torch.empty((M, n_out), dtype=out_dtype, device=dev)
+        dq = self.decode_table()
+        code = lib().eredu_qgemv4(ptr(x), ptr(self.wq), ptr(dq), ptr(out), ptr(residual), ptr(bias), M, self.out_features, K,
+                                  x.stride(0), out.stride(0), residual.stride(0) if residual is not None else 0, self.group,
+                                  1 if out_dtype == torch.float32 else 0, 1 if gated else 0, float(limit), 0, 0,
+                                  _sm_count(dev), stream_ptr(dev))
+        check(code, "eredu_qgemv4")
+        return out
+
+    def _gemv_ok(self, x) -> bool:
+        return (x.is_cuda and x.shape[0] <= self.GEMV_MAX_TOKENS and x.dtype == torch.bfloat16 and x.stride(1) == 1
+                and x.stride(0) % 8 == 0 and self.in_features % 64 == 0 and self.decode_table() is not None)
+
+    def gated(self, x, bias=None, limit: float = 0.0):
+        """silu(x Wgate^T) * (x Wup^T) for a weight that stacks gate rows over up rows: one kernel for decode-sized
+        batches, the projection followed by the activation kernel otherwise."""
+        inter = self.out_features // 2
+        if self._gemv_ok(x) and self.out_features % 2 == 0:
+            return self._gemv(x, bias, None, None, torch.bfloat16, True, limit or 0.0)
+        from .core import silu_mul
+
+        return silu_mul(self(x, bias=bias), inter, limit or 0.0)
 
     def __call__(self, x, bias=None, residual=None, out=None, out_dtype=None):
         if not x.is_cuda:
@@ -189,6 +236,8 @@ class QuantLinear:
         assert K == self.in_features and x.dtype == torch.bfloat16 and x.stride(1) == 1
         out_dtype = out_dtype or torch.bfloat16
         dev = x.device
+        if self._gemv_ok(x) and (out is None or out.stride(1) == 1):
+            return self._gemv(x, bias, residual, out, out_dtype, False)
         if M > self.DENSE_FALLBACK_TOKENS:
             w = torch.empty((N, K), dtype=torch.bfloat16, device=dev)
             check(lib().eredu_dequant_affine(ptr(self.wq), ptr(self.scales_t), ptr(self.biases_t), ptr(w), N, K,

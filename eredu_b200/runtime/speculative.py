@@ -458,6 +458,7 @@ class EmbeddedMtpDecoder(SpeculativeDecoder):
             p_d.append(probs)
             for b, t in enumerate(toks.tolist()):
                 drafted[b].append(int(t))
+        self._last_chain = chain              # pairs with d_k: where an optimistic continuation picks up
         # the head's cache is exact up to the row that paired with the newest committed token; later rows were made from
         # chained hidden states and are rewritten from the target's after the verify pass
         return drafted, p_d, [s.kv_len - (k - 1) for s in dseqs]
