@@ -49,12 +49,18 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--peak-gbs", type=float, default=6650.0)
     ap.add_argument("--group", type=int, default=64)
+    ap.add_argument("--only", default=None, help="run one shape by name (e.g. o, down/tp8)")
+    ap.add_argument("--tokens", type=int, nargs="*", default=[1, 8])
+    ap.add_argument("--plain-launches", type=int, default=0,
+                    help="profiling aid: instead of timing, launch the register kernel this many times outside a graph")
     args = ap.parse_args()
     H, I, QKV = 8192, 28672, 8192 + 2 * 1024
     shapes = [("qkv", QKV, H, False), ("o", H, H, False), ("gate_up", 2 * I, H, True), ("down", H, I, False),
               ("qkv/tp8", QKV // 8, H, False), ("o/tp8", H, H // 8, False), ("gate_up/tp8", 2 * I // 8, H, True),
               ("down/tp8", H, I // 8, False)]
     for name, N, K, gated in shapes:
+        if args.only is not None and name != args.only:
+            continue
         per = N * K // 2 + 2 * 2 * N * (K // args.group)
         copies = max(2, min(16, (2 * L2_BYTES + per - 1) // per))
         torch.manual_seed(0)
@@ -67,12 +73,19 @@ def main():
             q.wq, q.scales_t, q.biases_t = base.wq.clone(), base.scales_t.clone(), base.biases_t.clone()
             lins.append(q)
         deq = base.dequantize(torch.float32)
-        for M in (1, 8, 16):
+        for M in args.tokens:
             x = (torch.randn(M, K, device=DEV) * 0.5).bfloat16()
+            if args.plain_launches:
+                for i in range(args.plain_launches):
+                    q = lins[i % len(lins)]
+                    _ = q.gated(x) if gated else q(x)
+                torch.cuda.synchronize()
+                print(json.dumps({"shape": name, "M": M, "launched": args.plain_launches}))
+                continue
             lin = x.float() @ deq.t()
             ref = torch.nn.functional.silu(lin[:, :N // 2]) * lin[:, N // 2:] if gated else lin
             row = {"shape": name, "N": N, "K": K, "M": M, "swiglu": gated, "weight_sets": copies}
-            for arm, cap in (("register_mma", 16), ("tcgen05", 0)):
+            for arm, cap in (("register_mma", 8), ("tcgen05", 0)):
                 QuantLinear.GEMV_MAX_TOKENS = cap
                 fns = [(lambda q=q: q.gated(x)) if gated else (lambda q=q: q(x)) for q in lins]
                 y = fns[0]()
@@ -81,7 +94,7 @@ def main():
                 row[arm + "_gbs"] = round(per / us / 1e3, 0)
                 row[arm + "_of_peak"] = round(per / us / 1e3 / args.peak_gbs, 3)
                 row[arm + "_rel"] = float((y.float() - ref).norm() / ref.norm())
-            QuantLinear.GEMV_MAX_TOKENS = 16
+            QuantLinear.GEMV_MAX_TOKENS = 8
             row["speedup"] = round(row["tcgen05_us"] / row["register_mma_us"], 2)
             print(json.dumps(row), flush=True)
         del lins, base, deq

@@ -36,6 +36,7 @@ class ModelLoadOptions:
     max_batch: int = 8
     max_seq_len: int = 4096
     kv_pages: Optional[int] = None
+    prefix_cache: bool = False           # later requests lease the published KV pages of an equal prompt prefix
     native_gguf: bool = True                     # keep Q4_K/Q6_K/... blocks and run the native kernels
     use_cuda_graph: Optional[bool] = None
     weight_residency: str = "device"             # "device" | "layerwise_host" | "dense_disk_stream"
@@ -140,7 +141,7 @@ class LoadedModel:
 
             tp.attach(model, opt.parallel)
         engine = Engine(model, max_batch=opt.max_batch, max_seq_len=opt.max_seq_len, num_pages=opt.kv_pages,
-                        use_cuda_graph=opt.use_cuda_graph)
+                        use_cuda_graph=opt.use_cuda_graph, prefix_cache=opt.prefix_cache)
         tokenizer = None
         try:
             from ..text.tokenizer import load_tokenizer

@@ -123,6 +123,16 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
         "r"(smem_u32(bar))
       : "memory");
 }
+__device__ __forceinline__ void tma_load_3d_hint(void* smem_dst, const CUtensorMap* map, int x, int y, int z,
+                                                 uint64_t* bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1, {%2, %3, %4}], [%5], %6;"
+      :
+      : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z),
+        "r"(smem_u32(bar)), "l"(policy)
+      : "memory");
+}
 // Bring a tile into L2 only (no shared-memory destination, no completion to wait for).
 __device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int x, int y) {
   asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(map)),

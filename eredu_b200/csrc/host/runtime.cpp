@@ -141,6 +141,20 @@ class BlockManager {
     return out;
   }
 
+  // Publish the full pages of a sequence for prefix reuse: page i holds tokens [16 i, 16 i + 16). Returns the number
+  // of pages visited (each is now published under its chained hash, or an identical page already was).
+  int64_t seal_prefix(const std::vector<int64_t>& pages, const std::vector<int32_t>& tokens) {
+    uint64_t h = 0;
+    int64_t n = 0;
+    for (size_t i = 0; i + 16 <= tokens.size() && i / 16 < pages.size(); i += 16) {
+      std::vector<int32_t> chunk(tokens.begin() + i, tokens.begin() + i + 16);
+      h = chain_hash(h, chunk);
+      seal(pages[i / 16], h);
+      ++n;
+    }
+    return n;
+  }
+
   int refcount(int64_t page) const { return refs_.at(page); }
 
  private:
@@ -440,6 +454,7 @@ void bind_runtime(py::module_& m) {
       .def("release", &BlockManager::release)
       .def("seal", &BlockManager::seal)
       .def("match_prefix", &BlockManager::match_prefix)
+      .def("seal_prefix", &BlockManager::seal_prefix)
       .def("refcount", &BlockManager::refcount)
       .def_static("chain_hash", &BlockManager::chain_hash);
   py::class_<WorkItem>(m, "WorkItem")

@@ -9,7 +9,9 @@
 //
 // Formats (FMT), both "affine" (w = scale * q + bias per group of 16/32/64/128 along K; contract:
 // eredu/src/backend/mlx/runtime/checkpoint/quantization.rs:1-8,137-232), in a kernel layout made once at load:
-//   QF_AFFINE4: codes [N, K/2] bytes; inside each u32 the eight nibbles are stored as (n0,n2,n4,n6,n1,n3,n5,n7)
+//   QF_AFFINE4: codes tiled as [ceil(N/16)][K/64][16 rows][32 bytes] (a 16-row x 64-column tile is 512 contiguous
+//     bytes, so both this kernel's TMA boxes and the decode kernel's per-warp streams read whole DRAM bursts instead
+//     of 32-byte pieces 4 KB apart); inside each u32 the eight nibbles are stored as (n0,n2,n4,n6,n1,n3,n5,n7)
 //   QF_AFFINE8: codes [N, K] bytes (also the container for 2/3/5/6-bit codes and for GGUF Q5/Q6 blocks)
 //   scales / biases bf16, transposed to [K/group, N] so that a K block's 128 values are contiguous.
 //   QF_FP8: E4M3 bytes [N, K] with one fp32 scale per weight row per 128 input columns, table [K/128, N]
@@ -317,7 +319,8 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
         const int kb = kb0 + it;
         mbar_arrive_expect_tx(&raw_full[s], Cfg::kRaw + Cfg::kBTile + (FMT == QF_FP8 ? p.sb_rows * 512 : 2 * p.sb_rows * 256));
         // packed weights: byte tensor [N, row_bytes]; x coordinate in bytes (a multiple of 32)
-        tma_load_2d_hint(st + kRawOff, &tmQ, kb * QRaw<FMT>::kBox0, tile_n * 128, &raw_full[s], pol_w);
+        if (FMT == QF_AFFINE4) tma_load_3d_hint(st + kRawOff, &tmQ, 0, kb, tile_n * 8, &raw_full[s], pol_w);  // 8 tiles of 16 rows
+        else tma_load_2d_hint(st + kRawOff, &tmQ, kb * QRaw<FMT>::kBox0, tile_n * 128, &raw_full[s], pol_w);
         tma_load_2d_hint(st, &tmX, kb * 64, tile_m * TN, &raw_full[s], pol_x);
         if (p.sb_rows > 0) {
           const int grow = (kb * 64) >> p.group_shift;
@@ -497,7 +500,9 @@ __global__ void __launch_bounds__(256) dequant_matrix_kernel(const uint8_t* __re
   if (n >= p.N) return;
   constexpr int kRowK = FMT == QF_AFFINE4 ? 2 : 1;  // weights per byte
   const size_t row_bytes = static_cast<size_t>(p.K) / kRowK;
-  const uint8_t* src = wq + static_cast<size_t>(n) * row_bytes + static_cast<size_t>(kb) * (64 / kRowK) + half * (32 / kRowK);
+  const uint8_t* src = FMT == QF_AFFINE4
+                           ? wq + (static_cast<size_t>(n >> 4) * (p.K >> 6) + kb) * 512 + (n & 15) * 32 + half * 16
+                           : wq + static_cast<size_t>(n) * row_bytes + static_cast<size_t>(kb) * (64 / kRowK) + half * (32 / kRowK);
   __align__(16) uint8_t raw[64];
   __align__(16) uint8_t tile[128];
   // stage this thread's 32 weights as "row 0, half `half`" of a private one-row tile
@@ -558,7 +563,16 @@ static int qgemm_impl(int fmt, const void* X, const void* wq, const void* scales
   const int row_bytes = fmt == QF_AFFINE4 ? K / 2 : K;
   const int box0 = fmt == QF_AFFINE4 ? 32 : 64;
   CUtensorMap tmQ, tmX;
-  int r = make_tma_2d(&tmQ, wq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, row_bytes, row_bytes, 128, box0, CU_TENSOR_MAP_SWIZZLE_NONE);
+  int r;
+  if (fmt == QF_AFFINE4) {
+    // tiled codes [ceil(N/16)][K/64][16 rows x 32 bytes]: eight consecutive row tiles of one K block are the 128 x 32
+    // byte block the decoder expects, and each of them is one contiguous 512-byte read
+    const uint64_t kb_count = static_cast<uint64_t>(K / 64), tiles = static_cast<uint64_t>((N + 15) / 16);
+    r = make_tma_3d(&tmQ, wq, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, 128, kb_count, tiles, 512, kb_count * 512, 128, 1, 8,
+                    CU_TENSOR_MAP_SWIZZLE_NONE);
+  } else {
+    r = make_tma_2d(&tmQ, wq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, row_bytes, row_bytes, 128, box0, CU_TENSOR_MAP_SWIZZLE_NONE);
+  }
   if (r != 0) return -100 + r;
   r = make_tma_2d(&tmX, X, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, ldx, tn, 64);
   if (r != 0) return -200 + r;
@@ -612,8 +626,8 @@ static int qgemm_impl(int fmt, const void* X, const void* wq, const void* scales
   return static_cast<int>(e);
 }
 
-// Y = X dequant(Wq)^T (+bias) (+residual). `wq`: packed codes in kernel layout ([N, K/2] bytes for 4-bit with the
-// nibbles of every u32 interleaved (n0,n2,n4,n6,n1,n3,n5,n7); [N, K] bytes for 8-bit); scales_t / biases_t: bf16
+// Y = X dequant(Wq)^T (+bias) (+residual). `wq`: packed codes in kernel layout (4-bit: tiles [ceil(N/16)][K/64][16][32]
+// bytes with the nibbles of every u32 interleaved (n0,n2,n4,n6,n1,n3,n5,n7); [N, K] bytes for 8-bit); scales_t / biases_t: bf16
 // [K/group, N]. bits: 4 or 8. K must be a multiple of 64 and of the group size.
 extern "C" int eredu_qgemm(const void* X, const void* wq, const void* scales_t, const void* biases_t, void* Y,
                            const void* residual, const void* bias, int M, int N, int K, int ldx, int ldy, int ldr, int bits,

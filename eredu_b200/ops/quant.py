@@ -21,7 +21,7 @@ from .native import F, I, P, check, lib, ptr, status_word, stream_ptr
 
 native.register("eredu_qgemm", I, [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P])
 native.register("eredu_dequant_affine", I, [P, P, P, P, I, I, I, I, P])
-native.register("eredu_qgemv4", I, [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, I, P])
+native.register("eredu_qgemv4", I, [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, I, I, P, P])
 native.register("eredu_qgemm_fp8", I, [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P])
 native.register("eredu_dequant_fp8", I, [P, P, P, I, I, P])
 
@@ -41,14 +41,30 @@ def unpack_bitstream(packed: torch.Tensor, bits: int) -> torch.Tensor:
     return ((lo | hi) & ((1 << bits) - 1)).to(torch.uint8)
 
 
+def tile_kernel4(by: torch.Tensor) -> torch.Tensor:
+    """Row-major packed bytes [N, K/2] -> kernel tiles [ceil(N/16), K/64, 512]: a tile holds 16 rows x 64 columns
+    (16 x 32 bytes, row-major inside), rows are padded with zero codes to whole tiles."""
+    N, B = by.shape
+    pad = (-N) % 16
+    if pad:
+        by = torch.cat((by, by.new_zeros((pad, B))), 0)
+    return by.view((N + pad) // 16, 16, B // 32, 32).permute(0, 2, 1, 3).contiguous().view((N + pad) // 16, B // 32, 512)
+
+
+def untile_kernel4(wq: torch.Tensor, N: int) -> torch.Tensor:
+    """Kernel tiles -> row-major packed bytes [N, K/2]."""
+    T, KB, _ = wq.shape
+    return wq.view(T, KB, 16, 32).permute(0, 2, 1, 3).reshape(T * 16, KB * 32)[:N]
+
+
 def codes_to_kernel4(codes: torch.Tensor) -> torch.Tensor:
-    """4-bit codes uint8 [N, K] -> kernel-layout bytes [N, K/2]."""
+    """4-bit codes uint8 [N, K] -> kernel layout: nibbles interleaved inside each u32, 16 x 64 tiles (see tile_kernel4)."""
     N, K = codes.shape
     c = codes.view(N, K // 8, 8).to(torch.int32)
     order = torch.tensor(_NIBBLE_ORDER, device=codes.device)
     c = c[:, :, order]  # position p <- logical nibble order[p]
     by = c[:, :, 0::2] | (c[:, :, 1::2] << 4)
-    return by.to(torch.uint8).reshape(N, K // 2).contiguous()
+    return tile_kernel4(by.to(torch.uint8).reshape(N, K // 2))
 
 
 def affine_quantize_tensor(w: torch.Tensor, bits: int, group: int):
@@ -119,7 +135,10 @@ class QuantLinear:
         out.device = first.device
         if same:
             out.kbits, out.bits, out.group = first.kbits, first.bits, first.group
-            out.wq = torch.cat([p.wq for p in parts], 0)
+            if first.kbits == 4 and any(p.out_features % 16 for p in parts[:-1]):
+                out.wq = tile_kernel4(torch.cat([untile_kernel4(p.wq, p.out_features) for p in parts], 0))
+            else:
+                out.wq = torch.cat([p.wq for p in parts], 0)      # whole row tiles (4-bit) or rows (8-bit) stack as they are
             out.scales_t = torch.cat([p.scales_t for p in parts], 1).contiguous()
             out.biases_t = torch.cat([p.biases_t for p in parts], 1).contiguous()
             return out
@@ -135,7 +154,13 @@ class QuantLinear:
         out.__dict__.update(self.__dict__)
         out.__dict__.pop("_dq_t", None)
         out.out_features = r1 - r0
-        out.wq = self.wq[r0:r1].contiguous()
+        if self.kbits == 4:
+            if r0 % 16 == 0 and (r1 % 16 == 0 or r1 == self.out_features):
+                out.wq = self.wq[r0 // 16:(r1 + 15) // 16].contiguous()
+            else:
+                out.wq = tile_kernel4(untile_kernel4(self.wq, self.out_features)[r0:r1])
+        else:
+            out.wq = self.wq[r0:r1].contiguous()
         out.scales_t = self.scales_t[:, r0:r1].contiguous()
         out.biases_t = self.biases_t[:, r0:r1].contiguous()
         return out
@@ -147,8 +172,7 @@ class QuantLinear:
         out.__dict__.update(self.__dict__)
         out.__dict__.pop("_dq_t", None)
         out.in_features = k1 - k0
-        per = 2 if self.kbits == 4 else 1
-        out.wq = self.wq[:, k0 // per:k1 // per].contiguous()
+        out.wq = self.wq[:, k0 // 64:k1 // 64].contiguous() if self.kbits == 4 else self.wq[:, k0:k1].contiguous()
         out.scales_t = self.scales_t[k0 // self.group:k1 // self.group].contiguous()
         out.biases_t = self.biases_t[k0 // self.group:k1 // self.group].contiguous()
         return out
@@ -165,7 +189,7 @@ class QuantLinear:
         if self.kbits == 8:
             return self.wq
         N = self.out_features
-        by = self.wq.view(N, -1, 4).to(torch.int32)  # 4 bytes = 8 kernel positions
+        by = untile_kernel4(self.wq, N).reshape(N, -1, 4).to(torch.int32)  # 4 bytes = 8 kernel positions
         pos = torch.stack((by & 0xF, by >> 4), -1).reshape(N, -1, 8)  # kernel positions 0..7
         inv = torch.empty(8, dtype=torch.long)
         for p, logical in enumerate(_NIBBLE_ORDER):
@@ -180,20 +204,23 @@ class QuantLinear:
 
     # ------------------------------------------------------------------ forward
     DENSE_FALLBACK_TOKENS = 256
-    GEMV_MAX_TOKENS = 16          # up to here the register-resident decode kernel runs (csrc/kernels/qgemv_mma.cu)
+    GEMV_MAX_TOKENS = 8           # up to here the register-resident decode kernel runs (csrc/kernels/qgemv_mma.cu)
 
     def decode_table(self) -> Optional[torch.Tensor]:
-        """int32 [K/group, N] for the decode kernel: bf16(16·scale) in the low half, bf16(bias − 16·scale) in the high
-        half of each word (the kernel builds 1 + code/16 in a bf16 mantissa, one fused multiply-add gives the weight).
-        None where that kernel does not apply (8-bit container, group that is no power of two >= 16)."""
-        if self.kbits != 4 or self.group < 16 or self.group & (self.group - 1):
+        """int32 [ceil(N/16), K/group, 16] for the decode kernel: the bf16 scale in the low half, the bf16 bias in the high
+        half of each word, tiled like the codes (the words of a row tile are contiguous along K). None where that kernel does not apply (8-bit container, group that is no power of two >= 16)."""
+        if self.kbits != 4 or self.group < 16 or self.group > 128 or self.group & (self.group - 1):
             return None
         t = self.__dict__.get("_dq_t")
-        if t is None or t.shape != self.scales_t.shape or t.device != self.scales_t.device:
-            s = self.scales_t.float()
-            lo = (16.0 * s).to(torch.bfloat16).view(torch.int16).to(torch.int32) & 0xFFFF
-            hi = (self.biases_t.float() - 16.0 * s).to(torch.bfloat16).view(torch.int16).to(torch.int32) << 16
-            t = (lo | hi).contiguous()
+        if t is None or t.shape[1] != self.scales_t.shape[0] or t.device != self.scales_t.device:
+            lo = self.scales_t.contiguous().view(torch.int16).to(torch.int32) & 0xFFFF
+            hi = self.biases_t.contiguous().view(torch.int16).to(torch.int32) << 16
+            w = lo | hi                                              # [K/group, N]
+            G, N = w.shape
+            pad = (-N) % 16
+            if pad:
+                w = torch.cat((w, w.new_zeros((G, pad))), 1)      # rows of the padding take scale 0, bias 0
+            t = w.view(G, (N + pad) // 16, 16).permute(1, 0, 2).contiguous()
             self._dq_t = t
         return t
 
@@ -206,8 +233,8 @@ class QuantLinear:
         dq = self.decode_table()
         code = lib().eredu_qgemv4(ptr(x), ptr(self.wq), ptr(dq), ptr(out), ptr(residual), ptr(bias), M, self.out_features, K,
                                   x.stride(0), out.stride(0), residual.stride(0) if residual is not None else 0, self.group,
-                                  1 if out_dtype == torch.float32 else 0, 1 if gated else 0, float(limit), 0, 0,
-                                  _sm_count(dev), stream_ptr(dev))
+                                  1 if out_dtype == torch.float32 else 0, 1 if gated else 0, float(limit), 0, 0, 0,
+                                  _sm_count(dev), ptr(status_word(dev)), stream_ptr(dev))
         check(code, "eredu_qgemv4")
         return out
 
@@ -219,7 +246,7 @@ class QuantLinear:
         """silu(x Wgate^T) * (x Wup^T) for a weight that stacks gate rows over up rows: one kernel for decode-sized
         batches, the projection followed by the activation kernel otherwise."""
         inter = self.out_features // 2
-        if self._gemv_ok(x) and self.out_features % 2 == 0:
+        if self._gemv_ok(x) and self.out_features % 32 == 0:
             return self._gemv(x, bias, None, None, torch.bfloat16, True, limit or 0.0)
         from .core import silu_mul
 

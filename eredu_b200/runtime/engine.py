@@ -38,6 +38,7 @@ class Sequence:
     finished: bool = False
     finish_reason: Optional[str] = None
     slot: int = -1             # row in the decode batch
+    cached_tokens: int = 0     # prompt tokens whose K/V came from published pages of earlier requests
 
     @property
     def total_len(self) -> int:
@@ -46,7 +47,8 @@ class Sequence:
 
 class Engine:
     def __init__(self, model: CausalLM, max_batch: int = 32, max_seq_len: int = 4096, num_pages: Optional[int] = None,
-                 use_cuda_graph: Optional[bool] = None, prefill_chunk: int = 8192, hist_cap: int = 1024):
+                 use_cuda_graph: Optional[bool] = None, prefill_chunk: int = 8192, hist_cap: int = 1024,
+                 prefix_cache: bool = False):
         self.model = model
         self.cfg = model.cfg
         self.device = model.device
@@ -94,6 +96,14 @@ class Engine:
         self.use_graph = self.cuda if use_cuda_graph is None else (use_cuda_graph and self.cuda)
         self.prefill_chunk = prefill_chunk
         self.hist_cap = hist_cap
+        # Prefix reuse over sealed pages (eredu/src/backend/mlx/runtime/cache/kv.rs:2018-2128: immutable sealed blocks
+        # shared by lease): full 16-token pages are published under the chained hash of their tokens when a prompt has
+        # been prefilled and again when the sequence is released; a new request leases the longest published prefix of
+        # its prompt and prefills only the rest. Unreferenced published pages stay cached until the pool needs them
+        # (LRU / LFU eviction inside the block manager). Models with recurrent state cannot resume from pages alone.
+        self.prefix_cache = bool(prefix_cache and hasattr(self.kv.allocator, "match_prefix")
+                                 and not self.kv.has_recurrent_state())
+        self.prefix_stats = {"lookups": 0, "hits": 0, "hit_tokens": 0, "prompt_tokens": 0, "sealed_pages": 0}
         self._next_id = 0
         self._graphs: dict = {}
         self._decode_state = None
@@ -111,7 +121,25 @@ class Engine:
                              f"max_seq_len {self.max_seq_len}")
         # Reserve every page the request can need up front: the block table is then static for the
         # whole decode and the captured graph never needs a host update.
-        seq.pages = list(self.kv.allocator.alloc(PagedKVCache.pages_for(len(seq.prompt) + max_new_tokens)))
+        need = PagedKVCache.pages_for(len(seq.prompt) + max_new_tokens)
+        if self.prefix_cache:
+            # at least one prompt token is always prefilled: its logits choose the first output token
+            usable = (len(seq.prompt) - 1) // PAGE * PAGE
+            leased = list(self.kv.allocator.match_prefix(seq.prompt[:usable])) if usable else []
+            try:
+                seq.pages = leased + list(self.kv.allocator.alloc(need - len(leased)))
+            except RuntimeError:
+                if leased:
+                    self.kv.allocator.release(leased)
+                raise
+            seq.kv_len = seq.cached_tokens = len(leased) * PAGE
+            st = self.prefix_stats
+            st["lookups"] += 1
+            st["hits"] += 1 if leased else 0
+            st["hit_tokens"] += seq.cached_tokens
+            st["prompt_tokens"] += len(seq.prompt)
+            return seq
+        seq.pages = list(self.kv.allocator.alloc(need))
         if self.kv.page_to_slot is not None:
             try:
                 self.kv.bind_state(seq.pages[0])
@@ -121,8 +149,15 @@ class Engine:
                 raise
         return seq
 
+    def publish_pages(self, seq: Sequence) -> None:
+        """Publish the full pages below ``kv_len`` (prompt and committed output) for reuse by later requests."""
+        if self.prefix_cache and seq.pages and seq.kv_len >= PAGE:
+            tokens = (seq.prompt + seq.output)[:seq.kv_len // PAGE * PAGE]
+            self.prefix_stats["sealed_pages"] += int(self.kv.allocator.seal_prefix(seq.pages, tokens))
+
     def release(self, seq: Sequence) -> None:
         if seq.pages:
+            self.publish_pages(seq)
             self.kv.unbind_state(seq.pages[0])
             self.kv.allocator.release(seq.pages)
             seq.pages = []
@@ -230,6 +265,8 @@ class Engine:
         logits = self.model.forward(batch, self.kv)
         for s, n in zip(seqs, lens):
             s.kv_len = n
+            if self.prefix_cache and n == len(s.prompt):
+                self.publish_pages(s)           # concurrent requests with the same system prompt hit from here on
         tokens = None
         if logits is not None:
             tokens = self._sample(logits, seqs, [len(s.prompt) for s in seqs])

@@ -22,7 +22,12 @@ def test_kernel_layout_round_trip_and_device_quantizer_matches_host():
     codes, s, b = affine_quantize_tensor(w, 4, 64)
     ql = QuantLinear(codes, s, b, 4, 64, "cpu")
     assert torch.equal(ql.codes(), codes)
-    assert ql.wq.shape == (16, 256)
+    assert ql.wq.shape == (1, 8, 512)          # one 16-row tile, eight 64-column blocks of 512 bytes
+    # tile (0, kb) holds rows 0..15 x columns 64 kb .. 64 kb + 63: row r of the tile is 32 bytes at offset 32 r
+    from eredu_b200.ops.quant import untile_kernel4
+
+    rows = untile_kernel4(ql.wq, 16)
+    assert torch.equal(ql.wq[0, 3].view(16, 32), rows[:, 96:128])
     hp, hs, hb = H.affine_quantize(w.numpy(), 4, 64, "bf16")
     assert np.array_equal(H.unpack_codes(hp, 4), codes.numpy())
     assert np.allclose(hs, s.float().numpy()) and np.allclose(hb, b.float().numpy())
@@ -33,6 +38,17 @@ def test_kernel_layout_round_trip_and_device_quantizer_matches_host():
     # row / column slices and mixed-width fusion keep every value
     a = ql.slice_rows(4, 12).slice_cols(128, 384)
     assert torch.equal(a.dequantize(), deq[4:12, 128:384])
+    w2 = torch.randn(40, 512) * 0.05
+    big = QuantLinear(*affine_quantize_tensor(w2, 4, 64), 4, 64, "cpu")
+    d2 = big.dequantize()
+    assert big.wq.shape == (3, 8, 512)
+    assert torch.equal(big.slice_rows(16, 40).dequantize(), d2[16:]) and torch.equal(big.slice_rows(16, 32).dequantize(), d2[16:32])
+    assert torch.equal(big.slice_rows(5, 37).dequantize(), d2[5:37])
+    both = QuantLinear.concat_rows([big, ql])                  # 40 rows are no whole number of tiles: repacked
+    assert both.out_features == 56 and torch.equal(both.dequantize(), torch.cat((d2, deq)))
+    even = QuantLinear.concat_rows([ql, big])
+    assert torch.equal(even.dequantize(), torch.cat((deq, d2))) and even.wq.shape == (4, 8, 512)
+    assert big.decode_table().shape == (3, 8, 16) and big.slice_cols(64, 192).decode_table().shape == (3, 2, 16)
     c8, s8, b8 = affine_quantize_tensor(w[:8], 6, 16)
     fused = QuantLinear.concat_rows([ql, QuantLinear(c8, s8, b8, 6, 16, "cpu")])
     assert fused.kbits == 8 and fused.group == 16
@@ -61,14 +77,16 @@ def test_qgemm_matches_dequantized_matmul(bits, group, M):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("wk,ns", [(1, 1), (2, 1), (8, 1), (1, 2), (4, 4), (8, 8), (0, 0)])
-@pytest.mark.parametrize("M,group,gated", [(1, 64, False), (8, 64, True), (5, 32, False), (13, 128, True), (16, 16, False)])
-def test_decode_kernel_every_k_split_against_fp32(wk, ns, M, group, gated):
+@pytest.mark.parametrize("M,group,gated,exact", [(1, 64, False, 0), (8, 64, True, 0), (5, 32, False, 0), (7, 128, True, 0),
+                                                 (8, 16, False, 0), (3, 64, True, 1), (6, 128, False, 1)])
+def test_decode_kernel_every_k_split_against_fp32(wk, ns, M, group, gated, exact):
     """The register-resident decode kernel (mma.sync over codes dequantised in registers) with K split over the warps
-    of a CTA, over a cluster, both, or as the host picks it (0, 0); plain and SwiGLU epilogues; ragged row count."""
-    from eredu_b200.ops.native import lib, ptr, stream_ptr
+    of a CTA, over a cluster, both, or as the host picks it (0, 0); plain and SwiGLU epilogues; ragged row count; the
+    accumulator-side affine map (groups of 64 / 128) and the in-register bf16 dequantisation (small groups, or forced)."""
+    from eredu_b200.ops.native import check_status, lib, ptr, status_word, stream_ptr
 
     torch.manual_seed(wk * 100 + ns * 10 + M)
-    N, K = (2 * 328 if gated else 650), 1536
+    N, K = (2 * 336 if gated else 650), 1536 + 128
     w = (torch.randn(N, K, device="cuda") * 0.05).bfloat16()
     ql = QuantLinear.from_dense(w, 4, group)
     x = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
@@ -77,9 +95,10 @@ def test_decode_kernel_every_k_split_against_fp32(wk, ns, M, group, gated):
     n_out = N // 2 if gated else N
     y = torch.full((M, n_out), float("nan"), dtype=torch.bfloat16, device="cuda")
     code = lib().eredu_qgemv4(ptr(x), ptr(ql.wq), ptr(ql.decode_table()), ptr(y), ptr(res), ptr(bias), M, N, K, x.stride(0),
-                              y.stride(0), 0 if res is None else res.stride(0), group, 0, int(gated), 0.0, wk, ns, 148,
-                              stream_ptr(x.device))
+                              y.stride(0), 0 if res is None else res.stride(0), group, 0, int(gated), 0.0, wk, ns, exact, 148,
+                              ptr(status_word(x.device)), stream_ptr(x.device))
     assert code == 0
+    check_status(x.device)
     lin = x.float() @ ql.dequantize(torch.float32).t() + bias.float()
     ref = torch.nn.functional.silu(lin[:, :n_out]) * lin[:, n_out:] if gated else lin + res.float()
     rel = float((y.float() - ref).norm() / ref.norm())
