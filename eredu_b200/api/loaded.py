@@ -64,6 +64,83 @@ class LoadedModel:
 
     # ------------------------------------------------------------------------------------------ load
     @classmethod
+    def load_execution_plan(cls, path: str | Path, plan, options: Optional[ModelLoadOptions] = None) -> "LoadedModel":
+        """Load a checkpoint the way an :class:`runtime.plan.ExecutionPlan` says (``load_execution_plan``,
+        eredu/src/api/loaded.rs): weight transformation, residency form, expert cache and drafting come from the plan;
+        everything the plan does not name (device, batch, context, ...) comes from ``options``. A plan over several
+        ranks needs ``options.parallel`` bound to a topology of the same shape (one process per GPU); a mismatch is an
+        error, not a silent single-rank load."""
+        import dataclasses
+
+        plan.validate()
+        opt = dataclasses.replace(options) if options is not None else ModelLoadOptions()
+        topo = plan.topology
+        world = int(topo.get("pipeline", 1)) * int(topo.get("tensor", 1)) * (
+            1 if topo.get("expert_over_tensor") else int(topo.get("expert", 1)))
+        if int(topo.get("data", 1)) != 1:
+            raise ValueError("execution plan asks for data parallelism, which is declared but unsupported")
+        if world > 1:
+            par = opt.parallel
+            have = None if par is None else (par.topology.pipeline, par.topology.tensor, par.topology.expert,
+                                             bool(par.topology.expert_over_tensor))
+            want = (int(topo.get("pipeline", 1)), int(topo.get("tensor", 1)), int(topo.get("expert", 1)),
+                    bool(topo.get("expert_over_tensor")))
+            if have != want:
+                raise ValueError(f"execution plan needs the topology (pipeline, tensor, expert, shared) = {want}; "
+                                 f"options.parallel is bound to {have}")
+        wt = plan.weight_transformation
+        if wt.get("mode") in ("affine", "mxfp4") and opt.quantization is None and torch.device(opt.device).type == "cuda":
+            opt.quantization = QuantizationOptions(bits=int(wt.get("bits", 4)), group_size=int(wt.get("group_size", 64)),
+                                                   mode=wt["mode"])
+        mode = plan.residency.get("mode")
+        if mode == "layerwise_host":
+            opt.weight_residency = "layerwise_host"
+            opt.device_layer_window = int(plan.residency.get("device_layer_window", 1))
+        elif mode == "dense_disk_stream":
+            opt.weight_residency = "dense_disk_stream"
+            opt.dense_host_lookahead = max(1, int(plan.residency.get("host_lookahead") or opt.dense_host_lookahead))
+            opt.dense_background_queue = max(1, int(plan.residency.get("background_queue") or opt.dense_background_queue))
+        if plan.residency.get("host_budget_bytes"):
+            opt.host_budget_bytes = int(plan.residency["host_budget_bytes"])
+        if plan.expert_cache:
+            opt.expert_cache = True
+            opt.expert_cache_device_budget_bytes = plan.expert_cache.get("device_budget_bytes") or opt.expert_cache_device_budget_bytes
+            opt.expert_cache_eviction = plan.expert_cache.get("eviction", opt.expert_cache_eviction)
+        opt.mapped_shards = int(plan.max_mapped_shards)
+        opt.embedded_mtp = plan.drafting.get("mode") == "embedded"
+        lm = cls.load(path, opt)
+        lm.execution_plan = plan
+        return lm
+
+    @classmethod
+    def plan_and_load(cls, path: str | Path, options: Optional[ModelLoadOptions] = None, hardware=None, context: int = 4096,
+                      batch: int = 1, allow_quantization: bool = True) -> "LoadedModel":
+        """Inspect the checkpoint header, let the automatic planner choose topology, transformation and residency for
+        this node, and load accordingly (``plan_and_load``, eredu/src/api/loaded.rs). Single-process callers get the
+        single-device plan; a process that is one rank of a group passes ``options.parallel`` and gets the plan of that
+        topology. The chosen plan is kept as ``execution_plan`` on the result."""
+        from ..runtime.plan import AutomaticPlanner, HardwareProfile, estimate_runtime_state, inspect_artifact
+
+        opt = options or ModelLoadOptions()
+        report = inspect_artifact(str(path))
+        if not report.is_loadable:
+            raise ValueError("checkpoint is not loadable: " + "; ".join(f"{i.code}: {i.message}" for i in report.issues))
+        on_cpu = torch.device(opt.device).type != "cuda"
+        hw = hardware or (HardwareProfile(device_count=1, device_memory_bytes=1 << 62, name="cpu") if on_cpu
+                          else HardwareProfile.discover())
+        par = opt.parallel
+        ranks = 1 if par is None else par.topology.tensor
+        hw.device_count = max(1, ranks)                  # this process drives one device of `ranks`
+        prof = estimate_runtime_state(report.config, report.tensor_bytes)
+        plan = AutomaticPlanner(hw).plan(report.config, prof, context=context, batch=batch,
+                                         allow_quantization=allow_quantization and opt.quantization is None and not on_cpu,
+                                         prefer_devices=ranks if ranks > 1 else None)
+        if par is not None and ranks > 1:
+            plan.topology.update({"pipeline": par.topology.pipeline, "expert": par.topology.expert,
+                                  "expert_over_tensor": bool(par.topology.expert_over_tensor)})
+        return cls.load_execution_plan(path, plan, opt)
+
+    @classmethod
     def load(cls, path: str | Path, options: Optional[ModelLoadOptions] = None) -> "LoadedModel":
         opt = options or ModelLoadOptions()
         src = open_checkpoint(path, opt.mapped_shards)

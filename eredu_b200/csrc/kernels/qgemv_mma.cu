@@ -29,6 +29,7 @@
 
 #include "../common/launch.h"
 #include "../common/launch_count.h"
+#include "../common/peer.cuh"
 #include "../common/ptx.cuh"
 #include "../common/trace.cuh"
 
@@ -50,6 +51,8 @@ struct QGemvParams {
   int out_fp32;
   float limit;          // GATED: clamp (0 = off): gate <= limit, |up| <= limit
   int* status;
+  int use_comm;         // row-parallel shard: sum the result over the tensor-parallel group inside the kernel
+  PeerComm comm;
 };
 
 constexpr int kGemvThreads = 256;
@@ -191,6 +194,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) qgemv4_kernel(const QGemvPara
   pdl_wait();
   trace_mark(kTraceQGemm, kTraceAfterWait);
   pdl_launch_dependents();
+  const unsigned int seq = p.use_comm ? *p.comm.seq : 0u;
 
   // activations: token g, the 16 values that match this lane's codes; one chunk (four blocks) ahead in registers
   const __nv_bfloat16* xrow = p.x + static_cast<size_t>(min(g, p.M - 1)) * p.ldx + t * 16;
@@ -311,6 +315,88 @@ __global__ void __launch_bounds__(kGemvThreads, 2) qgemv4_kernel(const QGemvPara
   const int cols = rows_cta / p.ns;
   const int items = p.M * cols;
   const uint32_t red_addr = smem_u32(red);
+  if (!GATED && p.use_comm) {
+    // ---- row-parallel shard: one-shot all-reduce over peer memory in the same kernel. A pair of tokens of one output
+    // column travels as a 4-byte bf16x2 word into the sentinel-initialised slot of every peer (complete once it differs
+    // from the sentinel: no flag, fence or barrier); then this rank sums the words of all ranks in rank order, so every
+    // rank holds the same bits. The word layout and the parity protocol are those of the dense GEMM's fused all-reduce.
+    const int parity = static_cast<int>(seq & 1u);
+    const int pair_items = ((p.M + 1) / 2) * cols;
+    auto local_sum = [&](int m, int c) {
+      float sum = 0.f;
+      if (m >= p.M) return sum;
+      const int off = m * ldn + c;
+      for (int q = 0; q < p.ns; ++q) {
+        if (p.ns > 1) {
+          const uint32_t remote = mapa_shared(red_addr, static_cast<uint32_t>(q));
+          for (int w = 0; w < p.wk; ++w) sum += ld_dsmem_f32(remote + static_cast<uint32_t>(w * plane + off) * 4u);
+        } else {
+          for (int w = 0; w < p.wk; ++w) sum += red[w * plane + off];
+        }
+      }
+      return sum;
+    };
+    for (int idx = threadIdx.x; idx < pair_items; idx += kGemvThreads) {
+      const int pi = idx / cols, c = static_cast<int>(crank) * cols + idx % cols;
+      const int n = blockIdx.x * rows_cta + c;
+      if (n >= p.n_out) continue;
+      const uint32_t packed = lamport_payload(pack_bf16x2(local_sum(2 * pi, c), local_sum(2 * pi + 1, c)));
+      const size_t word = (static_cast<size_t>(pi) * p.N + n) * 4;
+      for (int peer = 0; peer < p.comm.size; ++peer)
+        asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(lamport_slot(p.comm, peer, parity, p.comm.rank) + word), "r"(packed)
+                     : "memory");
+    }
+    for (int idx = threadIdx.x; idx < pair_items; idx += kGemvThreads) {
+      const int pi = idx / cols, c = static_cast<int>(crank) * cols + idx % cols;
+      const int n = blockIdx.x * rows_cta + c;
+      if (n >= p.n_out) continue;
+      const size_t word = (static_cast<size_t>(pi) * p.N + n) * 4;
+      uint32_t got[kMaxRanks];
+      uint32_t miss = (1u << p.comm.size) - 1u;
+      const long long t0 = clock64();
+      bool first_pass = true;
+      while (true) {
+#pragma unroll
+        for (int src = 0; src < kMaxRanks; ++src)
+          if ((miss >> src) & 1u)
+            asm volatile("ld.volatile.global.u32 %0, [%1];"
+                         : "=r"(got[src])
+                         : "l"(lamport_slot(p.comm, p.comm.rank, parity, src) + word)
+                         : "memory");
+#pragma unroll
+        for (int src = 0; src < kMaxRanks; ++src)
+          if (((miss >> src) & 1u) && got[src] != kLamportEmpty) {
+            miss &= ~(1u << src);
+            asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(lamport_slot(p.comm, p.comm.rank, parity, src) + word),
+                         "r"(kLamportEmpty)
+                         : "memory");
+          }
+        if (miss == 0u) break;
+        if (!first_pass && clock64() - t0 > kWaitCycleLimit) {
+          report_status(p.status, kStatusPeerFlagTimeout);
+          break;
+        }
+        first_pass = false;
+      }
+      float v0 = 0.f, v1 = 0.f;
+#pragma unroll
+      for (int src = 0; src < kMaxRanks; ++src)
+        if (src < p.comm.size && !((miss >> src) & 1u)) {
+          v0 += bf16_lo(got[src]);
+          v1 += bf16_hi(got[src]);
+        }
+      const float bv = p.bias != nullptr ? __bfloat162float(p.bias[n]) : 0.f;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int m = 2 * pi + h;
+        if (m >= p.M) break;
+        float out = (h == 0 ? v0 : v1) + bv;
+        if (p.residual != nullptr) out += __bfloat162float(p.residual[static_cast<size_t>(m) * p.ldr + n]);
+        if (p.out_fp32) static_cast<float*>(p.y)[static_cast<size_t>(m) * p.ldy + n] = out;
+        else static_cast<__nv_bfloat16*>(p.y)[static_cast<size_t>(m) * p.ldy + n] = __float2bfloat16(out);
+      }
+    }
+  } else
   for (int idx = threadIdx.x; idx < items; idx += kGemvThreads) {
     const int m = idx / cols, c = static_cast<int>(crank) * cols + idx % cols;
     const int n = blockIdx.x * rows_cta + c;
@@ -355,6 +441,7 @@ __global__ void __launch_bounds__(kGemvThreads, 2) qgemv4_kernel(const QGemvPara
     cluster_arrive_release();
     cluster_wait_acquire();
   }
+  if (p.use_comm && threadIdx.x == 0) finish_call(p.comm, seq, gridDim.x * gridDim.y);
   trace_mark(kTraceQGemm, kTraceEnd);
 }
 
@@ -409,10 +496,12 @@ using namespace eredu;
 // Y = X dequant(Wq)^T (+bias) (+residual), or with gated != 0 Y[M, N/2] = silu(X Wgate^T) * (X Wup^T), for M <= 8.
 // wq: 4-bit codes in the tiled kernel layout ([ceil(N/16)][K/64][16][32] bytes); dq: u32 [K/group, N] holding the bf16
 // scale in the low and the bf16 bias in the high half; group a power of two >= 16; K a multiple of 64. Returns -2 for shapes this
-// kernel does not take (the caller then uses eredu_qgemm).
+// kernel does not take (the caller then uses eredu_qgemm). `comm` (a PeerComm, or null): the rank's result is a partial sum
+// of a row-parallel shard and is summed over the group inside the kernel (bias and residual added once, after the sum).
 extern "C" int eredu_qgemv4(const void* X, const void* wq, const void* dq, void* Y, const void* residual, const void* bias,
                             int M, int N, int K, int ldx, int ldy, int ldr, int group, int out_fp32, int gated, float limit,
-                            int force_wk, int force_ns, int force_exact_bf16, int sm_count, int* status, cudaStream_t stream) {
+                            int force_wk, int force_ns, int force_exact_bf16, int sm_count, const void* comm, int* status,
+                            cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (M > 8 || K % 64 != 0 || group < 16 || group > 128 || (group & (group - 1)) != 0 || K % group != 0 || ldx % 8 != 0)
     return -2;
@@ -436,6 +525,14 @@ extern "C" int eredu_qgemv4(const void* X, const void* wq, const void* dq, void*
   p.out_fp32 = out_fp32;
   p.limit = limit;
   p.status = status;
+  if (comm != nullptr) {
+    // the sum over the group runs in the epilogue; residual and bias are added once, after it
+    const PeerComm* pc = static_cast<const PeerComm*>(comm);
+    if (gated || out_fp32) return -2;
+    if (static_cast<long long>((M + 1) / 2) * N * 4 > pc->lam_bytes) return -2;
+    p.use_comm = 1;
+    p.comm = *pc;
+  }
   // K splits. A warp streams best when it has many K blocks to itself, but an SM wants two CTAs (sixteen warps) to fill
   // its issue slots, small CTAs spread more evenly over the SMs, and every further round of CTAs on an SM pays the fixed
   // costs again (first data from HBM, reduction, epilogue: worth about sixteen K blocks). Estimate for each power-of-two

@@ -22,6 +22,7 @@ from typing import Callable, Optional
 import torch
 
 from .. import ops
+from ..utils import nvtx
 from .config import ModelConfig
 from .rope import rope_tables
 
@@ -168,6 +169,8 @@ class CausalLM:
             return self._linear(lw, role, x, w, bias=bias, residual=residual)
         q = lw.qlin.get(role)
         if q is not None:
+            if hasattr(self.tp_ops, "row_qlinear"):
+                return self.tp_ops.row_qlinear(q, x, residual=residual, bias=bias)
             partial = q(x)
             return self.tp_ops.all_reduce(partial, residual=residual, bias=bias)
         return self.tp_ops.row_linear(x, w, residual=residual, bias=bias)
@@ -327,7 +330,8 @@ class CausalLM:
             nxt = self.layers[i + 1].fold_attn if i + 1 < n else (self.head_folded and self.par.owns_output_head())
             if self.residency is not None:
                 self.residency.acquire(i)
-            h, ssq = self.layer_forward(self.first_layer + i, lw, h, batch, kv, ssq, nxt)
+            with nvtx.annotate(f"layer{self.first_layer + i}"):
+                h, ssq = self.layer_forward(self.first_layer + i, lw, h, batch, kv, ssq, nxt)
             if self.residency is not None:
                 self.residency.release(i)
             if batch.deepstack is not None and self.first_layer + i < len(batch.deepstack):

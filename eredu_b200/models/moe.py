@@ -163,34 +163,45 @@ def make_moe_factory(src=None, router_std_scale: bool = False):
         p = f"model.layers.{li}.mlp."
         dev, dt = model.device, model.dtype
         e0, e1 = par.expert_range(cfg.num_experts) if par.ep_size > 1 else (0, cfg.num_experts)
+        # execution id -> checkpoint id (identity unless the experts are dealt round-robin or by an explicit table)
+        order = par.expert_order(cfg.num_experts) if par.ep_size > 1 else None
+        mine = list(range(e0, e1)) if order is None else order[e0:e1]
+        rows = None if order is None else torch.tensor(order, dtype=torch.long)
+
+        def renamed(t):            # a per-expert tensor (router rows, score biases) in execution order
+            return t if rows is None else t.index_select(0, rows.to(t.device))
+
+        def bank(t):               # this rank's slice of a stacked expert bank
+            return t[e0:e1] if rows is None else t.index_select(0, rows[e0:e1].to(t.device))
+
         mx = f"model.layers.{li}.block_sparse_moe."   # Mixtral naming: w1 = gate, w3 = up, w2 = down
         if has(mx + "gate.weight") and not has(p + "gate.weight"):
-            router = get(mx + "gate.weight").to(device=dev, dtype=dt).contiguous()
+            router = renamed(get(mx + "gate.weight")).to(device=dev, dtype=dt).contiguous()
             gu = torch.stack([torch.cat((get(mx + f"experts.{e}.w1.weight"), get(mx + f"experts.{e}.w3.weight")), 0)
-                              for e in range(e0, e1)], 0).to(device=dev, dtype=dt).contiguous()
-            dn = torch.stack([get(mx + f"experts.{e}.w2.weight") for e in range(e0, e1)], 0).to(device=dev, dtype=dt).contiguous()
+                              for e in mine], 0).to(device=dev, dtype=dt).contiguous()
+            dn = torch.stack([get(mx + f"experts.{e}.w2.weight") for e in mine], 0).to(device=dev, dtype=dt).contiguous()
             block = MoEBlock(cfg, router, gu, dn, e0, cfg.num_experts, ep_size=par.ep_size)
             block._model = model
             block.layer_index = li
             return block
-        if has(p + "router.weight"):
-            return _gpt_oss_block(model, li, get, has, e0, e1)
         nm = f"model.layers.{li}.mixer."
-        if has(nm + "gate.weight"):
-            return _nemotron_block(model, li, get, has, e0, e1)
-        router = get(p + "gate.weight").to(device=dev, dtype=dt).contiguous()
+        if has(p + "router.weight") or has(nm + "gate.weight"):
+            if order is not None:
+                raise NotImplementedError("GPT-OSS and Nemotron-H sparse blocks take the balanced expert assignment only")
+            return _gpt_oss_block(model, li, get, has, e0, e1) if has(p + "router.weight") else _nemotron_block(model, li, get, has, e0, e1)
+        router = renamed(get(p + "gate.weight")).to(device=dev, dtype=dt).contiguous()
         if has(p + "experts.gate_up_proj"):
-            gu = get(p + "experts.gate_up_proj")[e0:e1]
-            dn = get(p + "experts.down_proj")[e0:e1]
+            gu = bank(get(p + "experts.gate_up_proj"))
+            dn = bank(get(p + "experts.down_proj"))
         elif has(p + "experts.gate_exps.weight"):  # GGUF stacked banks
-            g = get(p + "experts.gate_exps.weight")[e0:e1]
-            u = get(p + "experts.up_exps.weight")[e0:e1]
+            g = bank(get(p + "experts.gate_exps.weight"))
+            u = bank(get(p + "experts.up_exps.weight"))
             gu = torch.cat((g, u), dim=1)
-            dn = get(p + "experts.down_exps.weight")[e0:e1]
+            dn = bank(get(p + "experts.down_exps.weight"))
         else:
             gu = torch.stack([torch.cat((get(p + f"experts.{e}.gate_proj.weight"), get(p + f"experts.{e}.up_proj.weight")), 0)
-                              for e in range(e0, e1)], 0)
-            dn = torch.stack([get(p + f"experts.{e}.down_proj.weight") for e in range(e0, e1)], 0)
+                              for e in mine], 0)
+            dn = torch.stack([get(p + f"experts.{e}.down_proj.weight") for e in mine], 0)
         gu = gu.to(device=dev, dtype=dt).contiguous()
         dn = dn.to(device=dev, dtype=dt).contiguous()
         shared = None
@@ -202,7 +213,7 @@ def make_moe_factory(src=None, router_std_scale: bool = False):
         sel_bias = None
         for name in ("expert_bias", "gate.e_score_correction_bias"):   # LFM2-MoE / DeepSeek: selection-only score bias
             if has(p + name):
-                sel_bias = get(p + name).to(device=dev, dtype=torch.float32).contiguous()
+                sel_bias = renamed(get(p + name)).to(device=dev, dtype=torch.float32).contiguous()
         shared_gate = None
         if has(p + "shared_expert_gate.weight"):
             shared_gate = get(p + "shared_expert_gate.weight").to(device=dev, dtype=dt).contiguous()

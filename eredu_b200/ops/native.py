@@ -116,3 +116,47 @@ def check_status(device: torch.device) -> None:
 def check(code: int, what: str) -> None:
     if code != 0:
         raise RuntimeError(f"{what} failed with code {code}")
+
+
+class Completion:
+    """An exact completion of the work submitted to a stream so far (``ExecutionBackend::Completion``,
+    eredu-core/src/execution.rs): a CUDA event plus an asynchronous copy of the device's status word taken at the same
+    point of the stream. ``is_ready`` polls without blocking; ``wait`` blocks and turns a recorded bounded-wait timeout
+    into an exception, so an error surfaces at the completion of the step that raised it and not at some later check.
+    On CPU the work is already done when the object is made."""
+
+    def __init__(self, device=None, stream=None):
+        self.device = torch.device(device) if device is not None else torch.device("cpu")
+        self._event = None
+        self._status = None
+        self._done = self.device.type != "cuda"
+        if not self._done:
+            s = stream or torch.cuda.current_stream(self.device)
+            with torch.cuda.stream(s):
+                self._status = torch.empty(1, dtype=torch.int32).pin_memory()
+                self._status.copy_(status_word(self.device), non_blocking=True)
+                self._event = torch.cuda.Event()
+                self._event.record(s)
+
+    def is_ready(self) -> bool:
+        return self._done or self._event.query()
+
+    def wait(self, timeout_s: float | None = None) -> None:
+        """Blocks until the recorded point is reached (``timeout_s``: poll with that limit and raise TimeoutError)."""
+        if self._done:
+            return
+        if timeout_s is None:
+            self._event.synchronize()
+        else:
+            import time
+
+            t0 = time.monotonic()
+            while not self._event.query():
+                if time.monotonic() - t0 > timeout_s:
+                    raise TimeoutError(f"device work did not complete within {timeout_s} s")
+                time.sleep(0.0002)
+        self._done = True
+        code = int(self._status[0])
+        if code != 0:
+            status_word(self.device).zero_()
+            raise RuntimeError(f"eredu kernel reported status {code}: {STATUS_NAMES.get(code, 'unknown')}")

@@ -21,7 +21,7 @@ from .native import F, I, P, check, lib, ptr, status_word, stream_ptr
 
 native.register("eredu_qgemm", I, [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P])
 native.register("eredu_dequant_affine", I, [P, P, P, P, I, I, I, I, P])
-native.register("eredu_qgemv4", I, [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, I, I, P, P])
+native.register("eredu_qgemv4", I, [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, I, I, P, P, P])
 native.register("eredu_qgemm_fp8", I, [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P])
 native.register("eredu_dequant_fp8", I, [P, P, P, I, I, P])
 
@@ -224,7 +224,7 @@ class QuantLinear:
             self._dq_t = t
         return t
 
-    def _gemv(self, x, bias, residual, out, out_dtype, gated: bool, limit: float = 0.0):
+    def _gemv(self, x, bias, residual, out, out_dtype, gated: bool, limit: float = 0.0, comm=None):
         M, K = x.shape
         dev = x.device
         n_out = self.out_features // 2 if gated else self.out_features
@@ -234,13 +234,20 @@ class QuantLinear:
         code = lib().eredu_qgemv4(ptr(x), ptr(self.wq), ptr(dq), ptr(out), ptr(residual), ptr(bias), M, self.out_features, K,
                                   x.stride(0), out.stride(0), residual.stride(0) if residual is not None else 0, self.group,
                                   1 if out_dtype == torch.float32 else 0, 1 if gated else 0, float(limit), 0, 0, 0,
-                                  _sm_count(dev), ptr(status_word(dev)), stream_ptr(dev))
+                                  _sm_count(dev), comm, ptr(status_word(dev)), stream_ptr(dev))
         check(code, "eredu_qgemv4")
         return out
 
     def _gemv_ok(self, x) -> bool:
         return (x.is_cuda and x.shape[0] <= self.GEMV_MAX_TOKENS and x.dtype == torch.bfloat16 and x.stride(1) == 1
                 and x.stride(0) % 8 == 0 and self.in_features % 64 == 0 and self.decode_table() is not None)
+
+    def row_parallel(self, x, comm, residual=None, bias=None):
+        """This rank's K shard of a row-parallel projection with the sum over the group inside the kernel (``comm``: the
+        peer-memory context of the group). None when the decode kernel does not take the call."""
+        if not self._gemv_ok(x):
+            return None
+        return self._gemv(x, bias, residual, None, torch.bfloat16, False, comm=comm)
 
     def gated(self, x, bias=None, limit: float = 0.0):
         """silu(x Wgate^T) * (x Wup^T) for a weight that stacks gate rows over up rows: one kernel for decode-sized

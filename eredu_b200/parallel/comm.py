@@ -95,6 +95,7 @@ class PeerGroup:
         self.x_off = self.out_off + self.out_bytes
         self.x_bytes = x_bytes
         self.slot_bytes = slot_bytes
+        self.lam_bytes = (slot_bytes // 2 + 255) // 256 * 256     # per (parity, source) slot of the tag-free one-shot words
         torch.cuda.synchronize(device)
         dist.barrier(group=group)  # every peer has mapped every buffer before anyone launches a kernel
 

@@ -21,6 +21,9 @@ class ParallelContext:
     ep_group: object = None
     world_group: object = None
     coords: dict = field(default_factory=dict)
+    # which expert-parallel rank owns which routed expert: "balanced" (contiguous ranges), "round_robin" (expert e on rank
+    # e mod ep), or an explicit owner per expert (ExpertAssignment, eredu/src/backend/mlx/runtime/distributed/expert.rs)
+    expert_assignment: object = "balanced"
 
     def __post_init__(self):
         if self.topology.data != 1:
@@ -90,6 +93,25 @@ class ParallelContext:
 
     def expert_range(self, n_experts: int) -> tuple[int, int]:
         return self.topology.expert_range(self.rank, n_experts)
+
+    def expert_order(self, n_experts: int) -> Optional[list]:
+        """Checkpoint expert ids in execution order, or None for the identity. Execution ids are contiguous per rank
+        (rank r runs execution ids ``expert_range``); a non-contiguous assignment is a renaming applied when the router
+        rows and the expert banks are read, so routing, dispatch and combine kernels never see it. Every rank must own
+        the same number of experts."""
+        a = self.expert_assignment
+        ep = self.ep_size
+        if a == "balanced" or ep == 1:
+            return None
+        if a == "round_robin":
+            owners = [e % ep for e in range(n_experts)]
+        else:
+            owners = [int(o) for o in a]
+            if len(owners) != n_experts:
+                raise ValueError(f"explicit expert assignment names {len(owners)} experts, the model has {n_experts}")
+        if n_experts % ep != 0 or any(owners.count(r) != n_experts // ep for r in range(ep)):
+            raise ValueError("every expert-parallel rank must own the same number of experts")
+        return sorted(range(n_experts), key=lambda e: (owners[e], e))
 
     def owns_embedding(self) -> bool:
         return self.topology.owns_embedding(self.rank)

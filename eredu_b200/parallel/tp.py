@@ -70,6 +70,16 @@ class PeerTPOps:
         combine), or None when the partials do not fit one staging slot."""
         return self.pg.comm if tokens * hidden * 4 <= self.pg.slot_bytes else None
 
+    def row_qlinear(self, q, x, residual=None, bias=None):
+        """Row-parallel projection with quantised weights: decode-sized calls sum over the group in the kernel's epilogue
+        (the same one-shot words as the dense path), larger ones run the local kernel and the peer-memory all-reduce."""
+        M = x.shape[0]
+        if hasattr(q, "row_parallel") and ((M + 1) // 2) * q.out_features * 4 <= self.pg.lam_bytes:
+            y = q.row_parallel(x, self.pg.comm, residual=residual, bias=bias)
+            if y is not None:
+                return y
+        return self.all_reduce(q(x), residual=residual, bias=bias)
+
     def all_reduce(self, partial, residual=None, bias=None):
         """Sum a local bf16 partial over the group (used after quantised row-parallel GEMMs)."""
         M, N = partial.shape

@@ -22,6 +22,7 @@ import torch
 from .. import ops
 from ..models.llama import CausalLM, ForwardBatch
 from ..ops.sampling import ROW_DTYPE, SamplingParams, pack_rows
+from ..utils import nvtx
 from .kv_cache import PAGE, PagedKVCache
 
 
@@ -262,7 +263,8 @@ class Engine:
             max_q_len=max_q,
             logit_rows=self._t(np.asarray(cu[1:], dtype=np.int64) - 1, torch.int64),
         )
-        logits = self.model.forward(batch, self.kv)
+        with nvtx.annotate(f"prefill[{len(seqs)}x{max_q}]"):
+            logits = self.model.forward(batch, self.kv)
         for s, n in zip(seqs, lens):
             s.kv_len = n
             if self.prefix_cache and n == len(s.prompt):
@@ -503,7 +505,9 @@ class Engine:
         """
         st = self._decode_state
         if not self.cuda:
-            return self._decode_step_cpu(st)
+            with nvtx.annotate("decode_step"):
+                return self._decode_step_cpu(st)
+        nvtx.mark("decode_step")
         if host_tokens is not None:
             st["token_ids"].copy_(host_tokens, non_blocking=True)
         if self.use_graph:

@@ -47,6 +47,7 @@ class ParkedSequence:
     state_slot: int = -1                 # gated-delta models: the recurrent-state slot the sequence keeps while parked
     disk_path: Optional[str] = None      # set while the pages live in the disk tier (k_host / v_host are None then)
     order: int = 0                       # park order: the disk tier takes the longest-parked sequences first
+    buffers: tuple = ()                  # the pool buffers behind k_host / v_host (returned to the pool when done)
 
 
 class KVHostTier:
@@ -69,6 +70,10 @@ class KVHostTier:
             os.makedirs(self.opt.live_disk, exist_ok=True)
         self._clock = 0
         self._last_use: dict[int, int] = {}
+        from .host_pool import HostTransferPool, default_pool
+
+        self.pool = default_pool() if self.cuda else HostTransferPool(pin=False)
+        self._retired: list = []
 
     # ------------------------------------------------------------------------------------------ accounting
     def page_bytes(self) -> int:
@@ -105,9 +110,12 @@ class KVHostTier:
         dev = self.engine.device
         idx = torch.as_tensor(seq.pages[:used], dtype=torch.long, device=dev)
         shape = (self.kv.k.shape[0], used) + tuple(self.kv.k.shape[2:])
-        pin = self.cuda
-        k_host = torch.empty(shape, dtype=self.kv.k.dtype, pin_memory=pin)
-        v_host = torch.empty((self.kv.v.shape[0], used) + tuple(self.kv.v.shape[2:]), dtype=self.kv.v.dtype, pin_memory=pin)
+        # staging memory comes from the pinned transfer pool (booked under "kv"): a buffer released by a resume is pinned
+        # already, so steady park / resume traffic costs no page-locking calls
+        self._reap()
+        v_shape = (self.kv.v.shape[0], used) + tuple(self.kv.v.shape[2:])
+        k_buf, k_host = self._host_tensor(shape, self.kv.k.dtype)
+        v_buf, v_host = self._host_tensor(v_shape, self.kv.v.dtype)
         event = None
         if used:
             k_stage = self.kv.k.index_select(1, idx)     # gather on the compute stream: ordered after the last step
@@ -131,7 +139,8 @@ class KVHostTier:
             conv = self.kv.conv_state[:, seq.pages[0]].to("cpu")   # the state is named by the sequence's first page
         self._clock += 1
         self.parked[seq.seq_id] = ParkedSequence(k_host, v_host, used, len(seq.pages), event, conv,
-                                                 self.kv.detach_state(seq.pages[0]) if seq.pages else -1, order=self._clock)
+                                                 self.kv.detach_state(seq.pages[0]) if seq.pages else -1, order=self._clock,
+                                                 buffers=(k_buf, v_buf))
         self.engine.kv.allocator.release(seq.pages)
         seq.pages = []
         self.host_bytes += nbytes
@@ -170,6 +179,9 @@ class KVHostTier:
                 k_dev, v_dev = p.k_host, p.v_host
             self.kv.k.index_copy_(1, idx, k_dev)
             self.kv.v.index_copy_(1, idx, v_dev)
+            self._retire(p.buffers, done if self.cuda else None)
+        else:
+            self._retire(p.buffers, None)
         if p.conv_state is not None:
             self.kv.conv_state[:, pages[0]] = p.conv_state.to(dev)
         self.kv.attach_state(p.state_slot, pages[0])         # gated-delta state stayed in its slot while parked
@@ -191,7 +203,33 @@ class KVHostTier:
                 self._remove(p.disk_path)
             else:
                 self.host_bytes -= p.pages * self.page_bytes()
+                self._retire(p.buffers, p.event)
             self.kv.free_state_slot(p.state_slot)
+
+    # ------------------------------------------------------------------------------------------ pinned staging
+    def _host_tensor(self, shape, dtype):
+        n = 1
+        for d in shape:
+            n *= int(d)
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        buf = self.pool.acquire(max(1, nbytes), "kv")
+        return buf, self.pool.view(buf, shape, dtype)
+
+    def _retire(self, buffers, event) -> None:
+        """Give staging buffers back to the pool once the copy that reads them (``event``) has completed."""
+        if buffers:
+            self._retired.append((tuple(buffers), event))
+            self._reap()
+
+    def _reap(self) -> None:
+        keep = []
+        for bufs, ev in self._retired:
+            if ev is None or ev.query():
+                for b in bufs:
+                    self.pool.release(b)
+            else:
+                keep.append((bufs, ev))
+        self._retired = keep
 
     # ------------------------------------------------------------------------------------------ disk tier
     @staticmethod
@@ -231,6 +269,8 @@ class KVHostTier:
             os.replace(tmp, path)
             nbytes = p.pages * self.page_bytes()
             p.k_host = p.v_host = None
+            self._retire(p.buffers, None)
+            p.buffers = ()
             p.event = None
             p.disk_path = path
             self.host_bytes -= nbytes
@@ -246,8 +286,11 @@ class KVHostTier:
             if not self._spill(self.host_bytes + nbytes - self.opt.host_budget_bytes):
                 return False
         blob = torch.load(p.disk_path, map_location="cpu")
-        p.k_host = blob["k"].pin_memory() if self.cuda else blob["k"]
-        p.v_host = blob["v"].pin_memory() if self.cuda else blob["v"]
+        k_buf, p.k_host = self._host_tensor(tuple(blob["k"].shape), blob["k"].dtype)
+        v_buf, p.v_host = self._host_tensor(tuple(blob["v"].shape), blob["v"].dtype)
+        p.k_host.copy_(blob["k"])
+        p.v_host.copy_(blob["v"])
+        p.buffers = (k_buf, v_buf)
         self._remove(p.disk_path)
         p.disk_path = None
         self.disk_bytes -= nbytes

@@ -55,6 +55,10 @@ def allocator_metrics(device: str = "cpu") -> dict:
                          "reserved_bytes": int(st.get("reserved_bytes.all.current", 0)),
                          "peak_reserved_bytes": int(st.get("reserved_bytes.all.peak", 0)),
                          "allocation_retries": int(st.get("num_alloc_retries", 0))}
+    from .host_pool import _default as pool
+
+    if pool is not None:
+        out["host_transfer_buffers"] = pool.stats()     # pinned staging memory by purpose: active / peak / reuse counts
     try:
         import psutil
 

@@ -209,6 +209,12 @@ def main():
             cfg = moe_cfg(gpu)
             sd = random_state(cfg, seed=0, std=0.08)
         par = ParallelContext.from_env(ParallelTopology(tensor=world, expert=world, expert_over_tensor=True))
+        if "robin" in scenario:
+            par.expert_assignment = "round_robin"
+        elif "explicit" in scenario:
+            # reversed blocks: the first rank owns the last experts
+            per = cfg.num_experts // world
+            par.expert_assignment = [world - 1 - e // per for e in range(cfg.num_experts)]
         model = build_from_tensors(cfg, sd.__getitem__, sd.__contains__, dev, dtype, par, moe_factory=make_moe_factory())
         tp.attach(model, par, max_tokens=256, backend="nccl" if "nccl" in scenario else "peer",
                   ep_mode="a2a" if "a2a" in scenario else "replicated")

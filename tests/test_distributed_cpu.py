@@ -54,6 +54,31 @@ def test_expert_parallel_over_tensor_ranks_matches_single_rank(world, tmp_path):
         assert r["tokens"] == want
 
 
+@pytest.mark.parametrize("scenario", ["cpu_ep_robin_nccl", "cpu_ep_explicit_nccl", "cpu_ep_robin_a2a_nccl"])
+def test_expert_assignments_other_than_contiguous_ranges(scenario, tmp_path):
+    """Round-robin and explicit expert placement are a renaming applied at load (router rows and banks read in execution
+    order): the tokens stay those of the single-rank model, with replicated tokens and with the all-to-all dispatch."""
+    from eredu_b200.models.moe import make_moe_factory
+    from eredu_b200.parallel.context import ParallelContext
+    from eredu_b200.parallel.topology import ParallelTopology
+
+    res = run_ranks(scenario, 2, tmp_path)
+    cfg = moe_cfg(False)
+    sd = random_state(cfg, seed=0, std=0.08)
+    model = build_from_tensors(cfg, sd.__getitem__, sd.__contains__, "cpu", torch.float32, moe_factory=make_moe_factory())
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 33)]
+    want = Engine(model, max_batch=4, max_seq_len=128).generate(prompts, SamplingParams(temperature=0.0), 10)
+    for r in res:
+        assert r["tokens"] == want
+    ctx = ParallelContext(ParallelTopology(tensor=2, expert=2, expert_over_tensor=True), 1)
+    ctx.expert_assignment = "round_robin"
+    assert ctx.expert_order(8) == [0, 2, 4, 6, 1, 3, 5, 7] and ParallelContext(ctx.topology, 0).expert_order(8) is None
+    ctx.expert_assignment = [0, 0, 0, 1, 1, 1, 1, 1]
+    with pytest.raises(ValueError, match="same number"):
+        ctx.expert_order(8)
+
+
 @pytest.mark.parametrize("scenario,world", [("cpu_lfm2_tp_nccl", 2), ("cpu_lfm2_pp", 2)])
 def test_hybrid_family_under_tensor_and_pipeline_parallelism(scenario, world, tmp_path):
     """LFM2: convolution channels and their recurrent state are split over the tensor ranks (row-parallel out_proj
