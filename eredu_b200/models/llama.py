@@ -460,19 +460,21 @@ def shard_attention(cfg: ModelConfig, par, wq, wk, wv, wo, bq=None, bk=None, bv=
     """Tensor-parallel slices of the attention projections; a GQA group is the atomic unit and KV heads are
     replicated when there are fewer of them than ranks (nn/parallel.rs:104-183 defines the group rule; the
     replication extends it to tp > n_kv)."""
-    D = cfg.head_dim
+    from ..parallel.planner import ParallelPlan, attention_groups
+
     tp, r = par.tp_size, par.tp_rank
-    n_q_local, n_kv_local, rep = par.attention_partition(cfg.num_attention_heads, cfg.num_key_value_heads)
-    q0 = r * n_q_local
-    kv0 = (r // rep) * n_kv_local if rep > 1 else r * n_kv_local
-    wq_l = wq[q0 * D:(q0 + n_q_local) * D]
-    wk_l = wk[kv0 * D:(kv0 + n_kv_local) * D]
-    wv_l = wv[kv0 * D:(kv0 + n_kv_local) * D]
-    wo_l = wo[:, q0 * D:(q0 + n_q_local) * D]
+    # the typed plan owns the arithmetic: query-head group, key / value-head group (replicated over tp / n_kv consecutive
+    # ranks when there are fewer heads than ranks), the output projection following the query heads on its inputs
+    plan = ParallelPlan(tp)
+    for g in attention_groups(cfg, tp, "", bias=bq is not None):
+        plan.add(g)
+    wq_l = plan.select("q_proj.weight", wq, r)
+    wk_l = plan.select("k_proj.weight", wk, r)
+    wv_l = plan.select("v_proj.weight", wv, r)
+    wo_l = plan.select("o_proj.weight", wo, r)
     b = None
     if bq is not None:
-        b = torch.cat((bq[q0 * D:(q0 + n_q_local) * D], bk[kv0 * D:(kv0 + n_kv_local) * D],
-                       bv[kv0 * D:(kv0 + n_kv_local) * D]))
+        b = torch.cat((plan.select("q_proj.bias", bq, r), plan.select("k_proj.bias", bk, r), plan.select("v_proj.bias", bv, r)))
     return torch.cat((wq_l, wk_l, wv_l), 0), wo_l, b
 
 
@@ -607,7 +609,12 @@ def _build_ffn(model, cfg, li, p, lw, get, has, up, moe_factory) -> None:
     else:
         wg, wu, wd = (get(p + f"mlp.{n}_proj.weight") for n in ("gate", "up", "down"))
     if tp > 1:
-        wg, wu, wd = _tp_rows(wg, r, tp), _tp_rows(wu, r, tp), _tp_cols(wd, r, tp)
+        from ..parallel.planner import ParallelPlan, feed_forward_group
+
+        plan = ParallelPlan(tp)
+        plan.add(feed_forward_group(cfg, "", intermediate=wg.shape[0]))
+        wg, wu, wd = (plan.select("gate_proj.weight", wg, r), plan.select("up_proj.weight", wu, r),
+                      plan.select("down_proj.weight", wd, r))
     lw.w_gate_up = up(torch.cat((wg, wu), 0))
     lw.w_down = up(wd)
 
