@@ -294,6 +294,99 @@ extern "C" int eredu_allgather(const void* comm, const void* src, long long byte
   return static_cast<int>(cudaGetLastError());
 }
 
+// ------------------------------------------------------------------------------------------ point-to-point messages
+// Pipeline hand-off without the host: a message is copied into the receiver's staging slot with plain peer stores and
+// published with a release store of its sequence number; the receiver waits (bounded), copies it out and acknowledges,
+// which lets the sender reuse that slot two messages later. Both sides are ordinary kernels on the caller's stream,
+// so a pipeline stage's decode step - hand-off included - can be captured in a CUDA graph. Counters live in device
+// memory of the calling rank ([peer][sent | received][channel]); channel 0 owns the slot from its start, channels
+// 1..3 own 4 KB each at its end (token ids and other small control messages).
+constexpr int kP2PChannels = 4;
+constexpr int kP2PAckFlag = 64;
+
+__device__ __forceinline__ long long p2p_channel_offset(const PeerComm& c, int channel) {
+  return channel == 0 ? 0 : c.slot_bytes - 4096LL * channel;
+}
+
+__global__ void __launch_bounds__(512) peer_send_kernel(PeerComm c, int dst, int channel, const uint4* __restrict__ src,
+                                                        long long bytes, unsigned int* counters, unsigned int* done, int* status) {
+  unsigned int* cnt = counters + (dst * 2 + 0) * kP2PChannels + channel;
+  const unsigned int n = *cnt;                      // messages already sent to `dst` on this channel
+  const int parity = static_cast<int>(n & 1u);
+  if (n >= 2u) {
+    // the slot of this parity still holds message n - 2 until the receiver has acknowledged it
+    if (threadIdx.x == 0) wait_flag(c, parity, dst, kP2PAckFlag + channel, n - 1u, status);
+    __syncthreads();
+  }
+  uint4* slot = reinterpret_cast<uint4*>(peer_slot(c, dst, parity, c.rank) + p2p_channel_offset(c, channel));
+  const long long words = bytes >> 4;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < words;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    slot[i] = src[i];
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0 && atomicAdd(done, 1u) == gridDim.x - 1) {
+    *done = 0u;
+    *cnt = n + 1u;
+    st_release_sys(peer_flag(c, dst, parity, c.rank, channel), n + 1u);
+  }
+}
+
+__global__ void __launch_bounds__(512) peer_recv_kernel(PeerComm c, int src, int channel, uint4* __restrict__ dst, long long bytes,
+                                                        unsigned int* counters, unsigned int* done, int* status) {
+  unsigned int* cnt = counters + (src * 2 + 1) * kP2PChannels + channel;
+  const unsigned int m = *cnt;                      // messages already received from `src` on this channel
+  const int parity = static_cast<int>(m & 1u);
+  if (threadIdx.x == 0) wait_flag(c, parity, src, channel, m + 1u, status);
+  __syncthreads();
+  const uint8_t* slot = peer_slot(c, c.rank, parity, src) + p2p_channel_offset(c, channel);
+  const long long words = bytes >> 4;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < words;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    dst[i] = ld_cg_u4(slot + i * 16);
+  __syncthreads();
+  if (threadIdx.x == 0 && atomicAdd(done, 1u) == gridDim.x - 1) {
+    *done = 0u;
+    *cnt = m + 1u;
+    st_release_sys(peer_flag(c, src, parity, c.rank, kP2PAckFlag + channel), m + 1u);   // the sender may reuse the slot
+  }
+}
+
+// `counters`: zero-initialised device words of the calling rank, [kMaxRanks][2][4] message counts followed by two words
+// the kernels use to find their last CTA. bytes: a multiple of 16; channel 0 up to slot_bytes - 12 KB, channels 1..3 up
+// to 4 KB. `peer` is the group rank of the other side.
+static int p2p_check(const PeerComm* c, int peer, int channel, long long bytes) {
+  if (peer < 0 || peer >= c->size || peer == c->rank || channel < 0 || channel >= kP2PChannels || bytes <= 0 || bytes % 16 != 0) return -1;
+  if (bytes > (channel == 0 ? c->slot_bytes - 4096LL * (kP2PChannels - 1) : 4096LL)) return -2;
+  return 0;
+}
+
+extern "C" int eredu_peer_send(const void* comm, int dst, int channel, const void* src, long long bytes, void* counters,
+                               int sm_count, int* status, cudaStream_t stream) {
+  const PeerComm* c = static_cast<const PeerComm*>(comm);
+  const int bad = p2p_check(c, dst, channel, bytes);
+  if (bad != 0) return bad;
+  unsigned int* cnt = static_cast<unsigned int*>(counters);
+  const int grid = comm_grid(bytes / 16, sm_count);
+  peer_send_kernel<<<grid, 512, 0, stream>>>(*c, dst, channel, static_cast<const uint4*>(src), bytes, cnt,
+                                             cnt + kMaxRanks * 2 * kP2PChannels, status);
+  eredu_count_launches(1);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int eredu_peer_recv(const void* comm, int src, int channel, void* dst, long long bytes, void* counters,
+                               int sm_count, int* status, cudaStream_t stream) {
+  const PeerComm* c = static_cast<const PeerComm*>(comm);
+  const int bad = p2p_check(c, src, channel, bytes);
+  if (bad != 0) return bad;
+  unsigned int* cnt = static_cast<unsigned int*>(counters);
+  const int grid = comm_grid(bytes / 16, sm_count);
+  peer_recv_kernel<<<grid, 512, 0, stream>>>(*c, src, channel, static_cast<uint4*>(dst), bytes, cnt,
+                                             cnt + kMaxRanks * 2 * kP2PChannels + 1, status);
+  eredu_count_launches(1);
+  return static_cast<int>(cudaGetLastError());
+}
+
 extern "C" int eredu_peer_barrier(const void* comm, int* status, cudaStream_t stream) {
   const PeerComm* c = static_cast<const PeerComm*>(comm);
   peer_barrier_kernel<<<1, 32, 0, stream>>>(*c, status);

@@ -118,3 +118,43 @@ class PeerGroup:
             for p in self._opened:
                 self.lib.eredu_ipc_close(p)
             self.lib.eredu_peer_free(self.own)
+
+
+class PeerP2P:
+    """Point-to-point messages between the ranks of a group over peer memory (``eredu_peer_send`` / ``eredu_peer_recv``):
+    kernels on the caller's stream, no host synchronisation, valid inside CUDA-graph capture. Both sides of a channel
+    must issue matching calls in the same order; a message is at most ``max_bytes`` (channel 0) or 4 KB (channels 1-3)."""
+
+    CHANNELS = 4
+
+    def __init__(self, group, device: torch.device, max_bytes: int):
+        slot = (int(max_bytes) + 4096 * (self.CHANNELS - 1) + 255) // 256 * 256
+        self.pg = PeerGroup(group, device, slot, 256)
+        self.device = device
+        self.rank, self.size = self.pg.rank, self.pg.size
+        self.max_bytes = int(max_bytes)
+        self.counters = torch.zeros(8 * 2 * self.CHANNELS + 2, dtype=torch.int32, device=device)
+        self.sm = torch.cuda.get_device_properties(device).multi_processor_count
+        self.lib = native.lib()
+
+    def _args(self, t: torch.Tensor):
+        assert t.is_contiguous() and t.device == self.device
+        n = t.numel() * t.element_size()
+        assert n % 16 == 0, "messages are whole 16-byte words: pad the tensor"
+        return t.data_ptr(), n
+
+    def send(self, dst: int, t: torch.Tensor, channel: int = 0) -> None:
+        p, n = self._args(t)
+        st = native.status_word(self.device)
+        native.check(self.lib.eredu_peer_send(self.pg.comm, dst, channel, p, n, self.counters.data_ptr(), self.sm,
+                                              st.data_ptr(), native.stream_ptr(self.device)), "eredu_peer_send")
+
+    def recv(self, src: int, out: torch.Tensor, channel: int = 0) -> torch.Tensor:
+        p, n = self._args(out)
+        st = native.status_word(self.device)
+        native.check(self.lib.eredu_peer_recv(self.pg.comm, src, channel, p, n, self.counters.data_ptr(), self.sm,
+                                              st.data_ptr(), native.stream_ptr(self.device)), "eredu_peer_recv")
+        return out
+
+    def close(self):
+        self.pg.close()

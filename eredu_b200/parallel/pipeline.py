@@ -6,8 +6,12 @@ stage embeds, every stage runs its contiguous layers, the last stage applies the
 last stage and the chosen ids are distributed to the other stages. There is no micro-batch schedule inside one
 forward; different requests can occupy different stages through the scheduler.
 
-The hand-off stays on NCCL p2p (gloo on CPU ranks); with CUDA it is issued on a side stream and ordered with
-events so that the copy engine overlaps the next kernels of the sending stage.
+Two transports. ``nccl``: NCCL p2p (gloo on CPU ranks) with a checked frame header; on CUDA it is issued on a side
+stream and ordered with events so that the copy engine overlaps the next kernels of the sending stage. It needs the
+host at every hop, so decode runs eagerly. ``peer`` (CUDA, one node): decode steps hand activations and sampled ids
+over with kernels that store into the neighbour's staging memory and wait on flags (``parallel.comm.PeerP2P``) - no
+host in the loop, so a stage's whole decode step (its layers, the hand-off, the token feedback) is one CUDA graph.
+Shapes of such steps are fixed by the decode state; prompts still travel over the framed transport.
 """
 from __future__ import annotations
 
@@ -22,8 +26,9 @@ WIRE_MAGIC = 0x45524455  # frames carry [magic, rows, cols] so a desynchronised 
 class _StageModel:
     """Wraps a model shard so that ``forward`` receives from the previous stage and sends to the next one."""
 
-    def __init__(self, model, par):
+    def __init__(self, model, par, p2p=None):
         self.inner = model
+        self.p2p = p2p                # PeerP2P over the pipeline group, or None: every hop goes through torch.distributed
         self.par = par
         self.cfg = model.cfg
         self.device = model.device
@@ -47,6 +52,8 @@ class _StageModel:
     def forward(self, batch, kv):
         M = batch.token_ids.shape[0]
         H = self.cfg.hidden_size
+        if self.p2p is not None and not batch.is_prefill:
+            return self._forward_peer(batch, kv, M, H)
         if self.prev is not None:
             hdr = torch.empty(3, dtype=torch.int64, device=self.device)
             dist.recv(hdr, src=self.prev)
@@ -75,20 +82,67 @@ class _StageModel:
         return None
 
 
+    def _forward_peer(self, batch, kv, M, H):
+        """Decode hop over peer memory: no header, no host. The decode state fixes (M, H) for the life of the graph."""
+        stage = self.par.pp_rank
+        if self.prev is not None:
+            if self._h_in is None or self._h_in.shape[0] != M:
+                self._h_in = torch.empty((M, H), dtype=self.dtype, device=self.device)
+            self.p2p.recv(stage - 1, self._h_in, channel=0)
+            batch.hidden_in = self._h_in
+            self.stats["received"] += 1
+        out = self.inner.forward(batch, kv)
+        if self.next is None:
+            return out
+        self.p2p.send(stage + 1, out.contiguous(), channel=0)
+        self.stats["sent"] += 1
+        self.stats["bytes"] += out.numel() * out.element_size()
+        return None
+
+
 class PipelineRunner:
-    def __init__(self, model, par, max_batch=8, max_seq_len=4096, num_pages=None):
+    def __init__(self, model, par, max_batch=8, max_seq_len=4096, num_pages=None, transport: str = "nccl"):
         self.par = par
-        self.stage = _StageModel(model, par)
+        p2p = None
+        if transport == "peer":
+            if model.device.type != "cuda" or par.pp_size < 2:
+                raise ValueError("the peer-memory transport needs CUDA ranks of one node and at least two stages")
+            from .comm import PeerP2P
+
+            p2p = PeerP2P(par.pp_group, model.device, max_batch * model.cfg.hidden_size * 2)
+        elif transport != "nccl":
+            raise ValueError(f"unknown pipeline transport {transport!r}")
+        self.p2p = p2p
+        self.stage = _StageModel(model, par, p2p)
+        self.stage._h_in = None
         self.engine = Engine(self.stage, max_batch=max_batch, max_seq_len=max_seq_len, num_pages=num_pages,
-                             use_cuda_graph=False)
+                             use_cuda_graph=p2p is not None)
         self.engine.token_sync = self._sync_tokens
         topo = par.topology
         members = topo.axis_members(par.rank, "pipeline")
         self.last_rank = members[-1]
         self.pp_group = par.pp_group
+        self._tok_pad = None
+
+    def _sync_tokens_peer(self, tokens, n):
+        """Sampled ids from the last stage to every other stage as a 16-byte aligned int32 message on channel 1."""
+        dev = self.stage.device
+        words = (n + 3) // 4 * 4
+        if self._tok_pad is None or self._tok_pad.numel() != words:
+            self._tok_pad = torch.zeros(words, dtype=torch.int32, device=dev)
+        last = self.par.pp_size - 1
+        if self.par.pp_rank == last:
+            self._tok_pad[:n].copy_(tokens)
+            for s in range(last):
+                self.p2p.send(s, self._tok_pad, channel=1)
+        else:
+            self.p2p.recv(last, self._tok_pad, channel=1)
+        return self._tok_pad[:n]
 
     def _sync_tokens(self, tokens, n):
         dev = self.stage.device
+        if self.p2p is not None and self.engine._decode_state is not None and self._in_decode():
+            return self._sync_tokens_peer(tokens, n)
         if tokens is None:
             tokens = torch.empty(n, dtype=torch.int32, device=dev)
         else:
@@ -99,3 +153,6 @@ class PipelineRunner:
 
     def generate(self, prompts, sampling=None, max_new_tokens=64, eos_ids=()):
         return self.engine.generate(prompts, sampling, max_new_tokens, eos_ids)
+
+    def _in_decode(self) -> bool:
+        return getattr(self.engine, "_in_decode_body", False)

@@ -475,7 +475,11 @@ class Engine:
         if logits is not None:
             ops.sample(logits, st["rows"], history=st["history"], out=st["sampled"], all_greedy=st["all_greedy"])
         if self.token_sync is not None:
-            st["sampled"].copy_(self.token_sync(st["sampled"] if logits is not None else None, st["B"]))
+            self._in_decode_body = True          # a pipeline runner may hand the ids over with kernels here (graph-safe)
+            try:
+                st["sampled"].copy_(self.token_sync(st["sampled"] if logits is not None else None, st["B"]))
+            finally:
+                self._in_decode_body = False
         hist = st["history"]
         code = ops.native.lib().eredu_decode_advance(
             st["sampled"].data_ptr(), st["token_ids"].data_ptr(), st["positions"].data_ptr(),

@@ -270,8 +270,14 @@ def main():
             from eredu_b200.parallel import tp
 
             tp.attach(model, par, max_tokens=256, backend="nccl" if not gpu else "peer")
-        runner = PipelineRunner(model, par, max_batch=4, max_seq_len=128)
+        runner = PipelineRunner(model, par, max_batch=4, max_seq_len=128, transport="peer" if "peer" in scenario else "nccl")
         result["tokens"] = runner.generate(prompts, sp, max_new_tokens=10)
+        if "peer" in scenario:
+            from eredu_b200.ops import native
+
+            native.check_status(dev)
+            result["graph"] = bool(runner.engine.use_graph)
+            result["hops"] = runner.stage.stats["sent"] + runner.stage.stats["received"]
     dist.barrier()
     with open(f"{out_path}.{rank}", "w") as f:
         json.dump(result, f)

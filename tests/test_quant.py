@@ -96,7 +96,7 @@ def test_decode_kernel_every_k_split_against_fp32(wk, ns, M, group, gated, exact
     y = torch.full((M, n_out), float("nan"), dtype=torch.bfloat16, device="cuda")
     code = lib().eredu_qgemv4(ptr(x), ptr(ql.wq), ptr(ql.decode_table()), ptr(y), ptr(res), ptr(bias), M, N, K, x.stride(0),
                               y.stride(0), 0 if res is None else res.stride(0), group, 0, int(gated), 0.0, wk, ns, exact, 148,
-                              ptr(status_word(x.device)), stream_ptr(x.device))
+                              None, ptr(status_word(x.device)), stream_ptr(x.device))
     assert code == 0
     check_status(x.device)
     lin = x.float() @ ql.dequantize(torch.float32).t() + bias.float()

@@ -128,10 +128,11 @@ def test_quantised_tensor_parallel_matches_single_gpu(world, tmp_path):
         assert _rel(lg, ref) <= 0.03 and r["logits"] == res[0]["logits"]
 
 
-@pytest.mark.parametrize("scenario,world", [("gpu_pp", 2), ("gpu_pp_tp2", 4)])
+@pytest.mark.parametrize("scenario,world", [("gpu_pp", 2), ("gpu_pp_tp2", 4), ("gpu_pp_peer", 2), ("gpu_pp_peer_tp2", 4)])
 def test_pipeline_parallel_gpu(scenario, world, tmp_path):
     """Two pipeline stages (alone and over tensor-parallel pairs): activations travel over NCCL p2p with checked
-    frame headers, the last stage samples and broadcasts; every rank reports the single-GPU tokens."""
+    frame headers, the last stage samples and broadcasts; every rank reports the single-GPU tokens. The ``peer`` variants
+    hand decode activations and sampled ids over with peer-memory kernels, so each stage's decode step is one CUDA graph."""
     _need(world)
     res = run_ranks(scenario, world, tmp_path, extra_env={"NCCL_NVLS_ENABLE": "0"})
     cfg = tiny_cfg(True)
@@ -144,3 +145,6 @@ def test_pipeline_parallel_gpu(scenario, world, tmp_path):
         assert r["tokens"] == res[0]["tokens"]
         agree = sum(a == b for x, y in zip(want, r["tokens"]) for a, b in zip(x, y))
         assert agree >= 14      # bf16: the stage split changes nothing numerically, tensor-parallel sums may flip a late token
+        if "peer" in scenario:
+            # decode hops went over peer memory inside the captured step: every stage ran its decode as a CUDA graph
+            assert r["graph"] and r["hops"] > 0
