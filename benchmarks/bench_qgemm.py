@@ -47,7 +47,7 @@ def timed_graph(fns, reps=3):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--peak-gbs", type=float, default=6650.0)
+    ap.add_argument("--peak-gbs", type=float, default=6548.5, help="copy bandwidth the fractions are quoted against")
     ap.add_argument("--group", type=int, default=64)
     ap.add_argument("--only", default=None, help="run one shape by name (e.g. o, down/tp8)")
     ap.add_argument("--tokens", type=int, nargs="*", default=[1, 8])

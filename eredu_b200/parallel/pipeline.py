@@ -113,6 +113,20 @@ class PipelineRunner:
         elif transport != "nccl":
             raise ValueError(f"unknown pipeline transport {transport!r}")
         self.p2p = p2p
+        # the placed execution DAG is the authority on who owns what: this stage's layers, embedding and head must be
+        # exactly what the plan gives its pipeline coordinate (placement.rs validates before any weight is read; here
+        # the model is already sharded, so a disagreement is a construction error)
+        from .placement import decoder_placement
+
+        self.placement = decoder_placement(model.cfg.num_hidden_layers, par.pp_size, sparse=getattr(model.cfg, "is_moe", False))
+        dec = self.placement.group("decoder")
+        want = dec.local_units(par.pp_rank)
+        have = (model.first_layer, model.last_layer)
+        if want is not None and tuple(want) != have:
+            raise RuntimeError(f"pipeline stage {par.pp_rank} holds layers {have}, the placement assigns {tuple(want)}")
+        if (self.placement.static_owner("embedding") == par.pp_rank) != par.owns_embedding() or \
+                (self.placement.static_owner("output_head") == par.pp_rank) != par.owns_output_head():
+            raise RuntimeError("embedding / output head ownership differs from the placement")
         self.stage = _StageModel(model, par, p2p)
         self.stage._h_in = None
         self.engine = Engine(self.stage, max_batch=max_batch, max_seq_len=max_seq_len, num_pages=num_pages,
