@@ -481,6 +481,8 @@ class ModelConfig:
         for key in ("mtp_num_hidden_layers", "num_nextn_predict_layers"):
             if int(d.get(key, 0) or 0) > 0:
                 cfg.extra[key] = int(d[key])     # checkpoint-embedded prediction layers (drafting only; the decoder ignores them)
+        if d.get("mtp_hybrid_override_pattern"):
+            cfg.extra["mtp_hybrid_override_pattern"] = str(d["mtp_hybrid_override_pattern"])   # Nemotron-H: blocks of one prediction step
         if d.get("_language_model_prefix"):
             cfg.extra["language_model_prefix"] = True   # tensors live under model.language_model.* next to a vision tower
             if d.get("_vision", {}).get("vision_config"):

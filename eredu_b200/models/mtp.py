@@ -9,7 +9,13 @@ Two checkpoint layouts carry such a layer:
   ``[H, 2H]``, the block itself, ``shared_head.norm`` and ``shared_head.head`` (and a copy of the embedding)
   (eredu/src/backend/mlx/architectures/deepseek_v3/layerwise.rs:82-262).
 
-Both compute, for the hidden state ``h_i`` that enters the target's final norm at position i and the token ``t_{i+1}``::
+* Nemotron-H (``num_nextn_predict_layers`` + ``mtp_hybrid_override_pattern`` of ``*`` / ``E`` markers): ``mtp.layers.j`` for
+  the ``P`` blocks of a prediction step (same tensor names as a backbone block), ``enorm`` / ``hnorm`` / ``eh_proj`` on the
+  step's first block, ``final_layernorm`` on its last; embedding and head are the model's own
+  (eredu/src/backend/mlx/architectures/nemotron_h/layerwise.rs:88-330, checkpoint.rs:114-178). The first step's blocks
+  draft at every depth.
+
+All compute, for the hidden state ``h_i`` that enters the target's final norm at position i and the token ``t_{i+1}``::
 
     x = proj(concat(norm_e(embed(t_{i+1})), norm_h(h_i)));  g = block(x) at position i;  logits(t_{i+2}) = head(norm(g))
 
@@ -37,6 +43,14 @@ def _layout(cfg, has) -> Optional[dict]:
     if has("mtp.fc.weight"):
         return {"layer": "mtp.layers.0.", "norm": "mtp.norm.weight", "head": None, "embed": None, "proj": "mtp.fc.weight",
                 "norm_e": "mtp.pre_fc_norm_embedding.weight", "norm_h": "mtp.pre_fc_norm_hidden.weight"}
+    for root in ("mtp.layers.", "model.mtp.layers."):
+        if cfg.model_type == "nemotron_h" and has(root + "0.eh_proj.weight"):
+            pattern = str(cfg.extra.get("mtp_hybrid_override_pattern", ""))
+            if not pattern or any(ch not in "*E" for ch in pattern):
+                raise ValueError("Nemotron-H prediction layers need an mtp_hybrid_override_pattern made of '*' and 'E'")
+            P = len(pattern)
+            return {"layers": root, "pattern": pattern, "norm": f"{root}{P - 1}.final_layernorm.weight", "head": None, "embed": None,
+                    "proj": root + "0.eh_proj.weight", "norm_e": root + "0.enorm.weight", "norm_h": root + "0.hnorm.weight"}
     p = f"model.layers.{L}."
     if has(p + "eh_proj.weight"):
         return {"layer": p, "norm": p + "shared_head.norm.weight",
@@ -66,10 +80,14 @@ class EmbeddedMtp:
         return own + self.model.weight_bytes()
 
 
-def head_config(cfg):
-    """Configuration of the one-layer head model: one full-attention (or latent-attention) block, sparse where the
-    family's later layers are."""
-    extra = {k: v for k, v in cfg.extra.items() if k not in ("mtp_num_hidden_layers", "num_nextn_predict_layers")}
+def head_config(cfg, pattern=None):
+    """Configuration of the head model: one full-attention (or latent-attention) block, sparse where the family's later
+    layers are; for Nemotron-H the blocks its pattern names ('*' attention, 'E' sparse feed-forward)."""
+    extra = {k: v for k, v in cfg.extra.items() if k not in ("mtp_num_hidden_layers", "num_nextn_predict_layers",
+                                                             "mtp_hybrid_override_pattern")}
+    if pattern:
+        marks = {"*": "attention_only", "E": "moe_only"}
+        return dataclasses.replace(cfg, num_hidden_layers=len(pattern), layer_types=[marks[ch] for ch in pattern], extra=extra)
     kw = dict(num_hidden_layers=1, extra=extra)
     if cfg.layer_types:
         kw["layer_types"] = ["full_attention"]
@@ -89,7 +107,10 @@ def build_embedded_mtp(cfg, get: Callable, has: Callable, target, device, dtype,
     from .llama import build_from_tensors
 
     def remap(name: str) -> str:
-        if name.startswith("model.layers.0."):
+        if "layers" in names:                       # several blocks per step: model.layers.j.* -> <root>j.*
+            if name.startswith("model.layers."):
+                return names["layers"] + name[len("model.layers."):]
+        elif name.startswith("model.layers.0."):
             return names["layer"] + name[len("model.layers.0."):]
         if name == "model.norm.weight":
             return names["norm"]
@@ -99,7 +120,7 @@ def build_embedded_mtp(cfg, get: Callable, has: Callable, target, device, dtype,
             return names["embed"]
         return name
 
-    hcfg = head_config(cfg)
+    hcfg = head_config(cfg, names.get("pattern"))
     model = build_from_tensors(hcfg, lambda n: get(remap(n)), lambda n: has(remap(n)), device, dtype, None, moe_factory,
                                quantizer)
     # share what the checkpoint shares: no second copy of the vocabulary matrices on the device

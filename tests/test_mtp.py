@@ -1,4 +1,6 @@
 """Checkpoint-embedded prediction layers (Qwen3-Next ``mtp.*``, DeepSeek-V3 layer L) as the drafter of speculative decoding."""
+import dataclasses
+
 import pytest
 import torch
 
@@ -27,6 +29,22 @@ def with_mtp(family, seed=0):
         sd["mtp.fc.weight"] = torch.randn(H, 2 * H, generator=g) * 0.08
         sd["mtp.pre_fc_norm_embedding.weight"] = torch.randn(H, generator=g) * 0.2
         sd["mtp.pre_fc_norm_hidden.weight"] = torch.randn(H, generator=g) * 0.2
+    elif family == "nemotron_h":
+        from test_nemotron_h import nh_cfg, state_for
+
+        cfg = nh_cfg(num_nextn_predict_layers=1, mtp_hybrid_override_pattern="*E")
+        sd = state_for(cfg, seed)
+        hcfg = head_config(cfg, "*E")
+        head = state_for(hcfg, seed + 100)
+        for k, v in head.items():
+            if k.startswith("model.layers."):
+                sd["mtp.layers." + k[len("model.layers."):]] = v
+        g = torch.Generator().manual_seed(seed + 7)
+        H = cfg.hidden_size
+        sd["mtp.layers.0.enorm.weight"] = torch.rand(H, generator=g) + 0.5
+        sd["mtp.layers.0.hnorm.weight"] = torch.rand(H, generator=g) + 0.5
+        sd["mtp.layers.0.eh_proj.weight"] = torch.randn(H, 2 * H, generator=g) * 0.1
+        sd["mtp.layers.1.final_layernorm.weight"] = torch.rand(H, generator=g) + 0.5
     else:
         from test_deepseek import ds_cfg, state_for
 
@@ -56,6 +74,17 @@ def build(family, seed=0):
     return cfg, sd, target, mtp
 
 
+def test_nemotron_h_prediction_step_has_its_own_block_pattern():
+    cfg, sd, target, mtp = build("nemotron_h")
+    assert cfg.mtp_layers == 1 and mtp is not None and mtp.model.cfg.layer_types == ["attention_only", "moe_only"]
+    assert len(mtp.model.layers) == 2 and mtp.model.layers[1].moe is not None and mtp.model.layers[0].moe is None
+    assert mtp.model.embed is target.embed and mtp.model.lm_head is target.lm_head
+    assert not mtp.model.cfg.extra.get("mtp_hybrid_override_pattern")
+    bad = dataclasses.replace(cfg, extra=dict(cfg.extra, mtp_hybrid_override_pattern="M*"))
+    with pytest.raises(ValueError, match="made of"):
+        build_embedded_mtp(bad, sd.__getitem__, sd.__contains__, target, "cpu", torch.float32, make_moe_factory())
+
+
 @pytest.mark.parametrize("family", ["qwen3_next", "deepseek_v3"])
 def test_head_binding(family):
     cfg, sd, target, mtp = build(family)
@@ -73,7 +102,7 @@ def test_head_binding(family):
     assert x.shape == (2, cfg.hidden_size)
 
 
-@pytest.mark.parametrize("family", ["qwen3_next", "deepseek_v3"])
+@pytest.mark.parametrize("family", ["qwen3_next", "deepseek_v3", "nemotron_h"])
 @pytest.mark.parametrize("k,temperature", [(1, 0.0), (3, 0.0), (2, 0.8)])
 def test_committed_tokens_are_the_targets_own(family, k, temperature):
     cfg, _, target, mtp = build(family)
