@@ -37,8 +37,9 @@ class VisionConfig:
     @classmethod
     def from_dict(cls, d: dict) -> "VisionConfig":
         known = {k: d[k] for k in cls.__dataclass_fields__ if k in d}
-        if "deepstack_visual_indexes" in known:
-            known["deepstack_visual_indexes"] = tuple(known["deepstack_visual_indexes"])
+        # a configuration that does not name DeepStack taps has none (the Qwen3.5 tower: patch embedding, blocks, one
+        # merger); Qwen3-VL configurations always carry the list
+        known["deepstack_visual_indexes"] = tuple(known.get("deepstack_visual_indexes") or ())
         return cls(**known)
 
 

@@ -180,3 +180,49 @@ def test_video_prompt_matches_transformers(tmp_path):
     lm.engine.release(seq)
     assert torch.allclose(got.float().cpu(), out.logits[0, -1], atol=2e-3), float((got.float().cpu() - out.logits[0, -1]).abs().max())
     assert len(lm.generate_multimodal(segments, max_new_tokens=3, min_pixels=64, max_pixels=10**6, video_limits=limits)) >= 1
+
+
+def test_qwen3_5_hybrid_decoder_with_its_vision_tower_matches_transformers(tmp_path):
+    """Qwen3.5 vision-language checkpoints: the gated-delta / attention hybrid decoder under ``model.language_model``, a
+    tower without DeepStack taps under ``model.visual``, three-axis rotary positions on a quarter of the head."""
+    import os
+
+    from safetensors.torch import save_file
+
+    from eredu_b200.api import LoadedModel, ModelLoadOptions
+    from eredu_b200.media import RgbImage
+
+    vision = {k: v for k, v in VISION.items() if k != "deepstack_visual_indexes"}
+    text = dict(vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=4,
+                num_key_value_heads=2, head_dim=32, max_position_embeddings=256, linear_num_value_heads=4, linear_num_key_heads=2,
+                linear_key_head_dim=16, linear_value_head_dim=16, linear_conv_kernel_dim=4, full_attention_interval=4,
+                rope_parameters={"rope_type": "default", "mrope_section": [2, 1, 1], "mrope_interleaved": True,
+                                 "rope_theta": 10000.0, "partial_rotary_factor": 0.25})
+    cfg = transformers.Qwen3_5Config(text_config=text, vision_config=vision, tie_word_embeddings=False, image_token_id=300,
+                                     video_token_id=301, vision_start_token_id=302, vision_end_token_id=303)
+    torch.manual_seed(0)
+    m = transformers.Qwen3_5ForConditionalGeneration(cfg).eval().float()
+    # written by hand under the published tensor names (model.language_model.*, model.visual.*, lm_head.weight)
+    save_file({k: v.contiguous() for k, v in m.state_dict().items()}, os.path.join(tmp_path, "model.safetensors"))
+    cfg.save_pretrained(tmp_path)
+    lm = LoadedModel.load(tmp_path, ModelLoadOptions(device="cpu", max_batch=1, max_seq_len=128))
+    assert lm.vision is not None and lm.vision.cfg.deepstack_visual_indexes == () and lm.config.model_type == "qwen3_5_text"
+    rng = np.random.default_rng(0)
+    img_a = RgbImage(rng.integers(0, 255, (16, 24, 3), dtype=np.uint8))
+    img_b = RgbImage(rng.integers(0, 255, (8, 8, 3), dtype=np.uint8))
+    segments = [[5, 6, 7], img_a, [8, 9], img_b, [10, 11, 12]]
+    ids, mm = lm.multimodal_inputs(segments, min_pixels=64, max_pixels=10**6)
+    pa, ga = image_to_patches(img_a, lm.vision.cfg, 64, 10**6)
+    pb, gb = image_to_patches(img_b, lm.vision.cfg, 64, 10**6)
+    kw = dict(pixel_values=torch.cat((pa, pb)), image_grid_thw=torch.tensor([ga, gb]),
+              mm_token_type_ids=torch.tensor([[1 if t == 300 else 0 for t in ids]]))
+    with torch.no_grad():
+        ref = m(input_ids=torch.tensor([ids]), **kw).logits[0, -1]
+    seq = lm.engine.new_sequence(ids, max_new_tokens=8)
+    got = lm.engine.feed_logits(seq, ids, mm)
+    assert torch.allclose(got.float().cpu(), ref, atol=2e-3), float((got.float().cpu() - ref).abs().max())
+    lm.engine.release(seq)
+    with torch.no_grad():
+        gen = m.generate(input_ids=torch.tensor([ids]), max_new_tokens=5, do_sample=False, **kw)[0, len(ids):].tolist()
+    ours = lm.generate_multimodal(segments, max_new_tokens=5, min_pixels=64, max_pixels=10**6)
+    assert ours == gen[:len(ours)] and len(ours) >= 1
