@@ -247,6 +247,20 @@ class LoadedModel:
                 lm.vision_tokens = {k: vis.get(k) for k in ("image_token_id", "video_token_id", "boi_token_id", "eoi_token_id")}
             except (RuntimeError, KeyError, ValueError) as e:
                 lm.vision, lm.vision_error = None, f"vision tower not loaded: {e}"
+        if vis and vis.get("audio_config") and src.cfg.model_type == "gemma4" \
+                and src.has("model.audio_tower.subsample_conv_projection.input_proj_linear.weight") \
+                and (opt.parallel is None or opt.parallel.owns_embedding()):
+            from ..models.gemma4_audio import Gemma4AudioConfig, Gemma4AudioTower
+
+            try:
+                lm.audio = Gemma4AudioTower(Gemma4AudioConfig.from_dict(vis["audio_config"]), src.get, src.has, device,
+                                            torch.float32 if device.type == "cpu" else dtype)
+                lm.audio_tokens = {"audio_token_id": vis.get("audio_token_id"), "boa_token_id": vis.get("boa_token_id"),
+                                   "eoa_token_id": vis.get("eoa_token_id", vis.get("eoa_token_index"))}
+            except (RuntimeError, KeyError, ValueError) as e:
+                lm.audio, lm.audio_error = None, f"audio tower not loaded: {e}"
+        if lm.vision is not None:
+            pass
         elif vis and src.has("model.visual.patch_embed.proj.weight") and (opt.parallel is None or opt.parallel.owns_embedding()):
             from ..models.qwen_vl import VisionConfig, VisionTower
 
@@ -317,6 +331,9 @@ class LoadedModel:
 
     # ------------------------------------------------------------------------------------------ multimodal
     vision = None          # models.qwen_vl.VisionTower when the checkpoint carries an image tower
+    audio = None           # models.gemma4_audio.Gemma4AudioTower when the checkpoint carries an audio tower
+    audio_tokens: dict = {}
+    audio_error: str = ""
     vision_tokens: dict = {}
     vision_error: str = ""
 
@@ -332,6 +349,8 @@ class LoadedModel:
         from ..media.request import Video
         from ..models.qwen_vl import image_to_patches, mrope_positions, video_to_patches
 
+        if self.config.model_type == "gemma4" and (self.vision is not None or self.audio is not None):
+            return self._gemma4_inputs(segments, wrap, **(image_limits or {}))
         if self.vision is None:
             kinds = sorted({"image" if isinstance(s, RgbImage) else "video" for s in segments if isinstance(s, (RgbImage, Video))})
             if kinds:
@@ -388,13 +407,39 @@ class LoadedModel:
         per-layer inputs), their rows take the tower's soft tokens, and the soft tokens of one image form a
         bidirectional-attention group."""
         from ..media import MultimodalPreparationError, RgbImage
+        from ..media.audio import AudioWaveform, LogMelConfig, LogMelFeatures, extract_log_mel
         from ..models.gemma4_vision import image_to_patches
 
         vt = self.vision_tokens
         pad = int((self.config.extra.get("gemma4") or {}).get("pad_token_id") or 0)
         ids, rows, groups, feats = [], [], [], []
         for seg in segments:
+            if isinstance(seg, (AudioWaveform, LogMelFeatures)) or (isinstance(seg, torch.Tensor) and seg.dim() == 2):
+                # an audio clip is <boa> <audio> x n <eoa>: log-mel frames -> tower -> embedder; its soft tokens attend
+                # causally like text (only vision tokens form bidirectional groups)
+                if self.audio is None:
+                    raise MultimodalPreparationError("this checkpoint has no audio tower"
+                                                     + (f" ({self.audio_error})" if self.audio_error else ""))
+                if isinstance(seg, AudioWaveform):
+                    seg = extract_log_mel(seg, LogMelConfig())
+                mel = torch.as_tensor(seg.values[seg.mask] if isinstance(seg, LogMelFeatures) else seg, dtype=torch.float32)
+                soft = self.audio.forward(mel).to(self.model.dtype)
+                at = self.audio_tokens
+                if wrap and at.get("boa_token_id") is not None:
+                    ids.append(int(at["boa_token_id"]))
+                    groups.append(-1)
+                rows.extend(range(len(ids), len(ids) + soft.shape[0]))
+                ids.extend([pad] * soft.shape[0])
+                groups.extend([-1] * soft.shape[0])
+                feats.append(soft)
+                if wrap and at.get("eoa_token_id") is not None:
+                    ids.append(int(at["eoa_token_id"]))
+                    groups.append(-1)
+                continue
             if isinstance(seg, RgbImage):
+                if self.vision is None:
+                    raise MultimodalPreparationError("this checkpoint has no vision tower"
+                                                     + (f" ({self.vision_error})" if self.vision_error else ""))
                 patches, pos, n = image_to_patches(seg, self.vision.cfg, max_soft_tokens)
                 soft = self.vision.forward(patches, pos)
                 if wrap and vt.get("boi_token_id") is not None:
@@ -415,9 +460,13 @@ class LoadedModel:
                 raise MultimodalPreparationError(f"this model accepts text and images; the request carries {type(seg).__name__}")
         if not feats:
             return ids, None
-        bidir = groups if (self.config.extra.get("gemma4") or {}).get("use_bidirectional_attention") == "vision" else None
-        return ids, {"rows": rows, "values": torch.cat(feats, 0), "deepstack": None, "rope_positions": None, "rope_delta": 0,
-                     "bidir_groups": bidir, "placeholder_id": int(vt["image_token_id"])}
+        bidir = groups if ((self.config.extra.get("gemma4") or {}).get("use_bidirectional_attention") == "vision"
+                           and any(g >= 0 for g in groups)) else None
+        placeholder = vt.get("image_token_id") if vt else None
+        if placeholder is None:
+            placeholder = self.audio_tokens.get("audio_token_id")
+        return ids, {"rows": rows, "values": torch.cat([f.to(feats[0].dtype) for f in feats], 0), "deepstack": None,
+                     "rope_positions": None, "rope_delta": 0, "bidir_groups": bidir, "placeholder_id": int(placeholder)}
 
     def chat_segments(self, messages: list, images: list, placeholder: str = "<|image_pad|>", **template_kwargs) -> list:
         """Render a conversation whose user content lists contain ``{"type": "image"}`` items with the chat template and

@@ -259,7 +259,8 @@ class ModelConfig:
             d["model_type"] = mt
             d["_language_model_prefix"] = True
             d["_vision"] = {k: outer[k] for k in ("vision_config", "image_token_id", "video_token_id", "boi_token_id", "eoi_token_id", "vision_start_token_id",
-                                                  "vision_end_token_id") if k in outer}
+                                                  "vision_end_token_id", "audio_config", "audio_token_id", "boa_token_id", "eoa_token_id",
+                                                  "eoa_token_index") if k in outer}
         # Transformers >= 5 writes RoPE settings as one ``rope_parameters`` object (theta inside it; optionally one
         # object per layer type): fold it back into rope_theta / rope_scaling
         rp = d.get("rope_parameters")
@@ -485,8 +486,8 @@ class ModelConfig:
             cfg.extra["mtp_hybrid_override_pattern"] = str(d["mtp_hybrid_override_pattern"])   # Nemotron-H: blocks of one prediction step
         if d.get("_language_model_prefix"):
             cfg.extra["language_model_prefix"] = True   # tensors live under model.language_model.* next to a vision tower
-            if d.get("_vision", {}).get("vision_config"):
-                cfg.extra["vision"] = d["_vision"]
+            if d.get("_vision", {}).get("vision_config") or d.get("_vision", {}).get("audio_config"):
+                cfg.extra["vision"] = d["_vision"]           # towers next to the decoder: vision and / or audio
         if mt == "mixtral":
             cfg.moe_intermediate_size = cfg.moe_intermediate_size or cfg.intermediate_size
             cfg.router_scoring = "topk_softmax"
