@@ -45,6 +45,9 @@ def main():
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--inter", type=int, default=14336)
     ap.add_argument("--heads_dim", type=int, default=4096)
+    ap.add_argument("--plain-launches", type=int, default=0,
+                    help="profiling aid: launch the fused o_proj kernel this many times for --tokens rows (no graph, no timing)")
+    ap.add_argument("--tokens", type=int, default=32)
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
@@ -55,6 +58,19 @@ def main():
     nccl = NcclTPOps(par, dev)
     rows = []
     torch.manual_seed(1000 + rank)          # activations and weight shards differ per rank ...
+    if args.plain_launches:
+        K = args.heads_dim // world
+        ws = [(torch.randn(args.hidden, K, device=dev) * 0.02).bfloat16() for _ in range(8)]     # distinct weights: cold L2
+        x = (torch.randn(args.tokens, K, device=dev) * 0.5).bfloat16()
+        res = torch.randn(args.tokens, args.hidden, device=dev).bfloat16()
+        for i in range(args.plain_launches):
+            peer.row_linear(x, ws[i % len(ws)], residual=res)
+        torch.cuda.synchronize()
+        native.check_status(dev)
+        if rank == 0:
+            print(json.dumps({"world": world, "M": args.tokens, "K_local": K, "launched": args.plain_launches}))
+        dist.destroy_process_group()
+        return
     res_gen = torch.Generator(device=dev).manual_seed(7)   # ... the residual is the same tensor on every rank
     for name, k_full in (("o_proj", args.heads_dim), ("down_proj", args.inter)):
         K = k_full // world

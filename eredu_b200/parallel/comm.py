@@ -65,13 +65,19 @@ class PeerGroup:
         self.lib = lib
         out_total = ((out_bytes + 255) // 256 * 256) + ((x_bytes + 255) // 256 * 256)
         self.bytes = int(lib.eredu_comm_buffer_bytes(slot_bytes, out_total))
-        own = c_void_p()
-        native.check(lib.eredu_peer_alloc(self.bytes, ctypes.byref(own)), "eredu_peer_alloc")
-        self.own = own.value
+        # Guard words in front of and behind the symmetric buffer: peers write into this allocation with plain stores, so
+        # an index error of a remote kernel would otherwise corrupt silently. `check_canaries` (called on close and by
+        # tests) finds a store that left the buffer.
+        alloc = c_void_p()
+        native.check(lib.eredu_peer_alloc(self.bytes + 2 * self.GUARD, ctypes.byref(alloc)), "eredu_peer_alloc")
+        self._alloc = alloc.value
+        self.own = self._alloc + self.GUARD
+        for off in (0, self.GUARD + self.bytes):
+            view_raw(self._alloc + off, (self.GUARD // 4,), torch.int32, device).fill_(self.CANARY)
         native.check(lib.eredu_comm_init_buffer(self.own, slot_bytes, out_total), "eredu_comm_init_buffer")
         hbytes = lib.eredu_ipc_handle_bytes()
         handle = ctypes.create_string_buffer(hbytes)
-        native.check(lib.eredu_ipc_get_handle(self.own, handle), "cudaIpcGetMemHandle")
+        native.check(lib.eredu_ipc_get_handle(self._alloc, handle), "cudaIpcGetMemHandle")
         handles = [None] * self.size
         dist.all_gather_object(handles, bytes(handle.raw), group=group)
         self.bases = []
@@ -83,7 +89,7 @@ class PeerGroup:
             p = c_void_p()
             native.check(lib.eredu_ipc_open(ctypes.create_string_buffer(h, hbytes), ctypes.byref(p)),
                          f"cudaIpcOpenMemHandle(rank {r})")
-            self.bases.append(p.value)
+            self.bases.append(p.value + self.GUARD)      # the peer's buffer starts behind its front guard
             self._opened.append(p.value)
         self.local_words = torch.zeros(2, dtype=torch.int32, device=device)
         arr = (c_void_p * self.size)(*self.bases)
@@ -98,6 +104,18 @@ class PeerGroup:
         self.lam_bytes = (slot_bytes // 2 + 255) // 256 * 256     # per (parity, source) slot of the tag-free one-shot words
         torch.cuda.synchronize(device)
         dist.barrier(group=group)  # every peer has mapped every buffer before anyone launches a kernel
+
+    GUARD = 4096
+    CANARY = 0x5AC3A55A
+
+    def check_canaries(self) -> None:
+        """Raises when a store (local or from a peer) landed outside this rank's symmetric buffer."""
+        torch.cuda.synchronize(self.device)
+        for name, off in (("front", 0), ("back", self.GUARD + self.bytes)):
+            g = view_raw(self._alloc + off, (self.GUARD // 4,), torch.int32, self.device)
+            bad = int((g != self.CANARY).sum())
+            if bad:
+                raise RuntimeError(f"peer buffer of rank {self.rank}: {bad} guard words behind the {name} edge were overwritten")
 
     def out_view(self, shape, dtype) -> torch.Tensor:
         return view_raw(self.own + self.out_off, shape, dtype, self.device)
@@ -117,7 +135,7 @@ class PeerGroup:
             self.comm = None
             for p in self._opened:
                 self.lib.eredu_ipc_close(p)
-            self.lib.eredu_peer_free(self.own)
+            self.lib.eredu_peer_free(self._alloc)
 
 
 class PeerP2P:

@@ -278,6 +278,14 @@ def main():
             native.check_status(dev)
             result["graph"] = bool(runner.engine.use_graph)
             result["hops"] = runner.stage.stats["sent"] + runner.stage.stats["received"]
+    if gpu:
+        # no kernel of any rank stored outside a peer-memory buffer
+        for holder in (locals().get("model"), getattr(locals().get("runner"), "p2p", None)):
+            pg = getattr(getattr(holder, "tp_ops", holder), "pg", None)
+            if pg is not None and hasattr(pg, "check_canaries"):
+                dist.barrier()
+                pg.check_canaries()
+                result["canaries"] = "intact"
     dist.barrier()
     with open(f"{out_path}.{rank}", "w") as f:
         json.dump(result, f)
