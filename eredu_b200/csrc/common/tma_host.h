@@ -60,4 +60,22 @@ inline int make_tma_3d(CUtensorMap* map, const void* base, CUtensorMapDataType d
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
 }
 
+// 4-D tensor [d3, d2, d1, d0] (d0 innermost) with byte strides for d1..d3; box = [b3, b2, b1, b0].
+inline int make_tma_4d(CUtensorMap* map, const void* base, CUtensorMapDataType dtype, uint64_t d0, uint64_t d1, uint64_t d2,
+                       uint64_t d3, uint64_t stride1_bytes, uint64_t stride2_bytes, uint64_t stride3_bytes, uint32_t b0,
+                       uint32_t b1, uint32_t b2, uint32_t b3, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return -1;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (stride1_bytes & 15) != 0 || (stride2_bytes & 15) != 0 ||
+      (stride3_bytes & 15) != 0)
+    return -2;
+  cuuint64_t gdim[4] = {d0, d1, d2, d3};
+  cuuint64_t gstride[3] = {stride1_bytes, stride2_bytes, stride3_bytes};
+  cuuint32_t box[4] = {b0, b1, b2, b3};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, dtype, 4, const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
 }  // namespace eredu

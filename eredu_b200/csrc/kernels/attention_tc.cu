@@ -1,0 +1,389 @@
+// Prefill attention on the 5th-generation tensor cores: S = Q K^T and O += P V are tcgen05.mma with the accumulators in
+// tensor memory, K / V pages arrive by TMA straight from the paged cache.
+//
+// One CTA = 256 query rows (two tiles of 128, "a" and "b") of one (sequence, query head); keys are walked in tiles of 128
+// (eight 16-token pages). The two query tiles share every K / V tile and alternate on the tensor core, so the softmax of
+// one runs while the MMAs of the other execute.
+//   warp 0      : TMA producer - both Q tiles once, then per key tile sixteen boxes for K and sixteen for V (a page is
+//                 [16 keys x 64 values] per half of the head dimension, 128-byte swizzled); K and V have their own
+//                 two-deep rings, because a K tile is free a whole step before its V tile
+//   warp 1      : MMA issuer (one thread) - S_w = Q_w K_j^T into tile w's score columns, O_w += P_w V_j with P_w read
+//                 from tensor memory (the A operand) and V as it lies in the cache ([key][value], MN-major B operand)
+//   warps 2..5  : softmax of tile a, warps 6..9 of tile b, one query row per thread (TMEM lane = row): the whole score
+//                 row comes into registers with one wait, P = exp2(S * scale - m) goes back as packed bf16 over the
+//                 first 64 score columns. The output accumulator stays in tensor memory; it is rescaled only when a
+//                 row's maximum has grown by more than 2^8 since the scale in use was chosen (the probabilities are
+//                 then at most 256, exact enough in bf16, and the final division by the row sum takes the scale out).
+// TMEM columns: S_a [0,128) | S_b [128,256) | O_a [256,384) | O_b [384,512).
+// Causal masking by position (queries are the last q_len positions of their sequence, so chunked prefill and cached
+// prefixes work); key tiles beyond a query tile's last position are never loaded. CTAs with the most key tiles are
+// scheduled first.
+//
+// Same online-softmax recurrence and semantics as attn_prefill_kernel in attention.cu (which keeps serving sliding
+// windows, sinks and head size 64) and as the reference's blockwise attention (eredu/src/backend/mlx/nn/attention.rs:346-436,
+// runtime/cache/kv.rs:2267-2436). Every wait is bounded; on expiry the status word is set and the CTA leaves through the
+// common exit (TMEM is freed there).
+#include <cuda_bf16.h>
+
+#include "../common/launch.h"
+#include "../common/launch_count.h"
+#include "../common/ptx.cuh"
+#include "../common/tma_host.h"
+#include "../common/trace.cuh"
+
+namespace eredu {
+
+struct AttnTcParams {
+  __nv_bfloat16* out;          // [tokens, n_q, 128]
+  const int* block_table;      // [batch, max_pages]
+  const int* seq_lens;         // kv length after this call, per sequence
+  const int* cu_q;             // [batch + 1] query-row offsets
+  int max_pages;
+  int n_q_heads, n_kv_heads;
+  float scale_log2;
+  int* status;
+};
+
+constexpr int kTcThreads = 320;
+constexpr int kTcTile = 128;            // query rows per tile and keys per tile
+constexpr int kTcRows = 2 * kTcTile;    // query rows per CTA
+constexpr int kTcD = 128;
+constexpr int kTcHalf = 128 * 64 * 2;   // one [128 rows][64 bf16] swizzled half tile: 16 KB
+// shared memory: Q_a, Q_b (2 halves each) | K ring (2 x 2 halves) | V ring (2 x 2 halves) | barriers
+constexpr int kTcSmem = 1024 + 4 * kTcHalf + 4 * kTcHalf + 4 * kTcHalf + 256;
+constexpr float kTcRescale = 8.f;       // log2 units a row maximum may outgrow the scale in use
+
+// MN-major operand tile stored as [k rows][64 bf16] (128-byte rows, 128B swizzle): 64-element blocks along MN are `lbo`
+// bytes apart, 8-row groups along K are 1024 bytes apart. Advancing K by 16 = +2048 bytes on the start address.
+__device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint32_t lbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>(lbo_bytes >> 4) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+constexpr uint32_t kIdescQK = umma_idesc_bf16(128, 128);                 // both operands K-major
+constexpr uint32_t kIdescPV = umma_idesc_bf16(128, 128) | (1u << 16);    // B (= V) MN-major
+
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, int x, int y, int z, int w, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+      :
+      : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(w), "r"(smem_u32(bar))
+      : "memory");
+}
+
+__global__ void __launch_bounds__(kTcThreads, 1)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                       const __grid_constant__ CUtensorMap tmV, const AttnTcParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* q_s = smem;                                                 // tile w at + w * 2 halves
+  uint8_t* k_s = q_s + 4 * kTcHalf;                                    // stage s at + s * 2 halves
+  uint8_t* v_s = k_s + 4 * kTcHalf;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + 4 * kTcHalf);
+  uint64_t* q_full = bars;                  // 1
+  uint64_t* k_full = bars + 1;              // [2]
+  uint64_t* k_empty = bars + 3;             // [2]
+  uint64_t* v_full = bars + 5;              // [2]
+  uint64_t* v_empty = bars + 7;             // [2]
+  uint64_t* s_full = bars + 9;              // [2] per query tile
+  uint64_t* p_full = bars + 11;             // [2] per query tile, 128 arrivals
+  uint64_t* o_final = bars + 13;            // [2] per query tile
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+
+  pdl_launch_early();
+  trace_mark(kTraceAttnPrefill, kTraceStart);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.z, head = blockIdx.y, qt = gridDim.x - 1 - blockIdx.x;     // longest tiles first
+  const int q0 = p.cu_q[b], q_len = p.cu_q[b + 1] - q0;
+  const int kv_len = p.seq_lens[b];
+  const int row0 = qt * kTcRows;
+  if (row0 >= q_len) return;                                            // uniform: before any barrier or allocation
+  const int kv_head = head / (p.n_q_heads / p.n_kv_heads);
+  const int pos0 = kv_len - q_len + row0;                               // position of the CTA's first query row
+  // causal: nothing beyond the position of a tile's last row
+  const int n_a = min(kv_len - 1, pos0 + kTcTile - 1) / kTcTile + 1;
+  const int n_b = row0 + kTcTile < q_len ? min(kv_len - 1, pos0 + kTcRows - 1) / kTcTile + 1 : 0;
+  const int n_tiles = max(n_a, n_b);
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
+      mbar_init(&s_full[s], 1);
+      mbar_init(&p_full[s], 128);
+      mbar_init(&o_final[s], 1);
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  pdl_wait();
+  trace_mark(kTraceAttnPrefill, kTraceAfterWait);
+  pdl_launch_dependents();
+
+  bool ok = true;
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_arrive_expect_tx(q_full, 4 * kTcHalf);
+      for (int w = 0; w < 2; ++w)
+        for (int h = 0; h < 2; ++h)
+          tma_load_3d(q_s + (w * 2 + h) * kTcHalf, &tmQ, h * 64, head, q0 + row0 + w * kTcTile, q_full);
+      const int* pages = p.block_table + static_cast<size_t>(b) * p.max_pages;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j & 1;
+        const uint32_t reuse_parity = ((j >> 1) - 1) & 1;
+        int page[8];
+#pragma unroll
+        for (int pg = 0; pg < 8; ++pg) {
+          const int page_index = j * 8 + pg;
+          page[pg] = page_index < p.max_pages ? pages[page_index] : 0;            // beyond the table: the reserved page (masked)
+        }
+        if (j >= 2) ok = mbar_wait(&k_empty[s], reuse_parity, p.status, kStatusSmemEmptyTimeout);
+        if (!ok) break;
+        mbar_arrive_expect_tx(&k_full[s], 2 * kTcHalf);
+#pragma unroll
+        for (int pg = 0; pg < 8; ++pg)
+          for (int h = 0; h < 2; ++h) tma_load_4d(k_s + (s * 2 + h) * kTcHalf + pg * 2048, &tmK, h * 64, 0, kv_head, page[pg], &k_full[s]);
+        if (j >= 2) ok = mbar_wait(&v_empty[s], reuse_parity, p.status, kStatusSmemEmptyTimeout);
+        if (!ok) break;
+        mbar_arrive_expect_tx(&v_full[s], 2 * kTcHalf);
+#pragma unroll
+        for (int pg = 0; pg < 8; ++pg)
+          for (int h = 0; h < 2; ++h) tma_load_4d(v_s + (s * 2 + h) * kTcHalf + pg * 2048, &tmV, h * 64, 0, kv_head, page[pg], &v_full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t q_addr = smem_u32(q_s);
+      auto issue_s = [&](int w, int j) {
+        const uint32_t qa = q_addr + w * 2 * kTcHalf;
+        const uint32_t ka = smem_u32(k_s + (j & 1) * 2 * kTcHalf);
+        const uint32_t d = tmem + w * 128;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {           // K = head dimension: four 16-steps per 64-wide half
+          const uint32_t off = (kk >> 2) * kTcHalf + (kk & 3) * 32;
+          umma_f16(d, umma_desc_k_sw128(qa + off), umma_desc_k_sw128(ka + off), kIdescQK, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[w]);
+      };
+      auto issue_pv = [&](int w, int j) {
+        const uint32_t va = smem_u32(v_s + (j & 1) * 2 * kTcHalf);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)             // K = keys: P from tensor memory (8 columns per step), V MN-major (2048 bytes per step)
+          umma_f16_ts(tmem + 256 + w * 128, tmem + w * 128 + kk * 8, umma_desc_mn_sw128(va + kk * 2048, kTcHalf), kIdescPV,
+                      (j > 0 || kk > 0) ? 1u : 0u);
+      };
+      ok = mbar_wait(q_full, 0, p.status, kStatusTmaFullTimeout);
+      if (ok) ok = mbar_wait(&k_full[0], 0, p.status, kStatusTmaFullTimeout);
+      if (ok) {
+        tc_fence_after_sync();
+        issue_s(0, 0);
+        if (n_b > 0) issue_s(1, 0);
+        umma_commit(&k_empty[0]);
+      }
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const bool next = j + 1 < n_tiles;
+        bool k_ready = false;
+        ok = mbar_wait(&v_full[j & 1], (j >> 1) & 1, p.status, kStatusTmaFullTimeout);
+        for (int w = 0; w < 2 && ok; ++w) {
+          const int n_w = w == 0 ? n_a : n_b;
+          if (j < n_w) {
+            ok = mbar_wait(&p_full[w], j & 1, p.status, kStatusAccumTimeout);     // P_w(j) is in tensor memory, O_w is rescaled
+            if (!ok) break;
+            tc_fence_after_sync();
+            issue_pv(w, j);
+          }
+          if (w == 1) umma_commit(&v_empty[j & 1]);
+          if (j + 1 < n_w) {
+            if (!k_ready) {
+              ok = mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, p.status, kStatusTmaFullTimeout);
+              if (!ok) break;
+              tc_fence_after_sync();
+              k_ready = true;
+            }
+            issue_s(w, j + 1);
+          } else if (j + 1 == n_w) {
+            umma_commit(&o_final[w]);
+          }
+        }
+        if (ok && next) umma_commit(&k_empty[(j + 1) & 1]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax, one row per thread
+    const int w = (warp - 2) >> 2;                                       // query tile of this warp
+    const int n_w = w == 0 ? n_a : n_b;
+    const int quarter = warp & 3;                                        // TMEM lanes this warp may touch
+    const int row = quarter * 32 + lane;
+    const int tile_row0 = row0 + w * kTcTile;
+    const int tile_pos0 = pos0 + w * kTcTile;
+    const int qpos = tile_pos0 + row;
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t s_addr = tmem + lane_addr + w * 128;
+    const uint32_t o_addr = tmem + lane_addr + 256 + w * 128;
+    float m = 0.f, l = 0.f;
+    for (int j = 0; j < n_w && ok; ++j) {
+      ok = mbar_wait(&s_full[w], j & 1, p.status, kStatusAccumTimeout);
+      if (!ok) break;
+      tc_fence_after_sync();
+      uint32_t sc[8][16];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) tmem_ld16(s_addr + c * 16, sc[c]);
+      tmem_wait_ld();
+      const int key0 = j * kTcTile;
+      const bool diag = key0 + kTcTile - 1 > tile_pos0 || key0 + kTcTile > kv_len;      // some (row, key) of the tile is masked
+      const int visible = min(qpos, kv_len - 1) - key0;                  // keys 0..visible of this tile are seen by this row
+      float mx = -INFINITY;
+      if (!diag) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+#pragma unroll
+          for (int i = 0; i < 16; ++i) mx = fmaxf(mx, __uint_as_float(sc[c][i]));
+      } else {
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            if (c * 16 + i <= visible) mx = fmaxf(mx, __uint_as_float(sc[c][i]));
+      }
+      const float m_new = mx * p.scale_log2;                             // -inf for a fully masked row: every comparison below is false
+      if (j == 0) {
+        m = m_new == -INFINITY ? 0.f : m_new;
+      } else {
+        const bool grow = m_new > m + kTcRescale;
+        if (__any_sync(0xffffffffu, grow)) {                             // O_w(j - 1) is complete: s_full followed it on the tensor core
+          const float alpha = grow ? ex2_approx(m - m_new) : 1.f;
+          if (grow) m = m_new;
+          l *= alpha;
+#pragma unroll 1
+          for (int c = 0; c < 8; ++c) {
+            uint32_t r[16];
+            tmem_ld16(o_addr + c * 16, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st16(o_addr + c * 16, r);
+          }
+        }
+      }
+      float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+      for (int c2 = 0; c2 < 4; ++c2) {
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const int c = c2 * 2 + (i >> 4), e = i & 15;
+          float p0 = ex2_approx(fmaf(__uint_as_float(sc[c][e]), p.scale_log2, -m));
+          float p1 = ex2_approx(fmaf(__uint_as_float(sc[c][e + 1]), p.scale_log2, -m));
+          if (diag) {
+            if (c * 16 + e > visible) p0 = 0.f;
+            if (c * 16 + e + 1 > visible) p1 = 0.f;
+          }
+          sum0 += p0;
+          sum1 += p1;
+          packed[i >> 1] = pack_bf16x2(p0, p1);
+        }
+        tmem_st16(s_addr + c2 * 16, packed);
+      }
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(&p_full[w]);
+      l += sum0 + sum1;
+    }
+    if (ok && n_w > 0) ok = mbar_wait(&o_final[w], 0, p.status, kStatusAccumTimeout);
+    if (ok && n_w > 0) {
+      tc_fence_after_sync();
+      const bool store = tile_row0 + row < q_len;
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(q0 + tile_row0 + row) * p.n_q_heads + head) * kTcD);
+#pragma unroll 1
+      for (int c = 0; c < 8; ++c) {
+        uint32_t r[16];
+        tmem_ld16(o_addr + c * 16, r);
+        tmem_wait_ld();
+        if (store) {
+          uint4 v0, v1;
+          v0.x = pack_bf16x2(__uint_as_float(r[0]) * inv, __uint_as_float(r[1]) * inv);
+          v0.y = pack_bf16x2(__uint_as_float(r[2]) * inv, __uint_as_float(r[3]) * inv);
+          v0.z = pack_bf16x2(__uint_as_float(r[4]) * inv, __uint_as_float(r[5]) * inv);
+          v0.w = pack_bf16x2(__uint_as_float(r[6]) * inv, __uint_as_float(r[7]) * inv);
+          v1.x = pack_bf16x2(__uint_as_float(r[8]) * inv, __uint_as_float(r[9]) * inv);
+          v1.y = pack_bf16x2(__uint_as_float(r[10]) * inv, __uint_as_float(r[11]) * inv);
+          v1.z = pack_bf16x2(__uint_as_float(r[12]) * inv, __uint_as_float(r[13]) * inv);
+          v1.w = pack_bf16x2(__uint_as_float(r[14]) * inv, __uint_as_float(r[15]) * inv);
+          dst[c * 2] = v0;
+          dst[c * 2 + 1] = v1;
+        }
+      }
+    }
+  }
+  // common exit: every role comes here, also after a timed-out wait; the tensor memory goes back
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+  trace_mark(kTraceAttnPrefill, kTraceEnd);
+}
+
+}  // namespace eredu
+
+using namespace eredu;
+
+// Causal prefill attention over the paged cache, head size 128, no sliding window, no sinks. q: [tokens, n_q, 128] bf16
+// (contiguous); k_cache / v_cache: [pages, n_kv, 16, 128] bf16 (contiguous). Same arguments as eredu_attn_prefill
+// otherwise. Returns -2 for shapes it does not take.
+extern "C" int eredu_attn_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
+                                     const int* seq_lens, const int* cu_q, int batch, int total_q, int max_q_len, int max_pages,
+                                     int num_pages, int n_q_heads, int n_kv_heads, int head_dim, float scale, int* status,
+                                     cudaStream_t stream) {
+  if (head_dim != 128 || batch <= 0 || total_q <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads != 0) return -2;
+  CUtensorMap tmQ, tmK, tmV;
+  // q as [tokens][heads][128]: box = 128 tokens x 1 head x 64 values
+  int r = make_tma_3d(&tmQ, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 128, static_cast<uint64_t>(n_q_heads),
+                      static_cast<uint64_t>(total_q), 128 * 2, static_cast<uint64_t>(n_q_heads) * 128 * 2, 64, 1, 128);
+  if (r != 0) return -100 + r;
+  r = make_tma_4d(&tmK, k_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 128, 16, static_cast<uint64_t>(n_kv_heads),
+                  static_cast<uint64_t>(num_pages), 128 * 2, 16 * 128 * 2, static_cast<uint64_t>(n_kv_heads) * 16 * 128 * 2, 64, 16, 1, 1);
+  if (r != 0) return -200 + r;
+  r = make_tma_4d(&tmV, v_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 128, 16, static_cast<uint64_t>(n_kv_heads),
+                  static_cast<uint64_t>(num_pages), 128 * 2, 16 * 128 * 2, static_cast<uint64_t>(n_kv_heads) * 16 * 128 * 2, 64, 16, 1, 1);
+  if (r != 0) return -300 + r;
+  AttnTcParams p = {};
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.block_table = block_table;
+  p.seq_lens = seq_lens;
+  p.cu_q = cu_q;
+  p.max_pages = max_pages;
+  p.n_q_heads = n_q_heads;
+  p.n_kv_heads = n_kv_heads;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmem) != cudaSuccess) return -1;
+    configured[dev] = true;
+  }
+  dim3 grid((max_q_len + kTcRows - 1) / kTcRows, n_q_heads, batch);
+  const cudaError_t e = launch_pdl(attn_prefill_tc_kernel, grid, dim3(kTcThreads), kTcSmem, stream, tmQ, tmK, tmV, p);
+  eredu_count_launches(1);
+  return static_cast<int>(e);
+}

@@ -180,6 +180,33 @@ def test_attention_prefill(D, n_q, n_kv, window):
     assert rel_l2(out, ref) < 1.5e-2
 
 
+@pytest.mark.parametrize("q_lens,kv_lens", [([200, 64, 1, 77], [200, 300, 50, 77]), ([2048], [2048]), ([129, 128, 127], [1000, 128, 513]),
+                                            ([300], [4396])])
+@pytest.mark.parametrize("n_q,n_kv", [(8, 2), (4, 4)])
+def test_attention_prefill_on_tcgen05_matches_reference_and_the_mma_kernel(q_lens, kv_lens, n_q, n_kv, monkeypatch):
+    """The tensor-memory kernel (head size 128, causal, cached prefixes, ragged batches, key tiles that end inside a page
+    table) against the fp32 reference, and against the mma.sync kernel it replaced as a second opinion."""
+    from eredu_b200.ops import core, native
+
+    D = 128
+    B = len(q_lens)
+    kc, vc, bt = _paged_setup(B, kv_lens, n_kv, D, seed=3)
+    q = torch.randn(sum(q_lens), n_q, D, device=DEV).bfloat16()
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), device=DEV, dtype=torch.int32)
+    sl = torch.tensor(kv_lens, device=DEV, dtype=torch.int32)
+    scale = 1 / math.sqrt(D)
+    before = native.launch_count()
+    assert core.TC_PREFILL
+    out = ops.attention_prefill(q, kc, vc, bt, sl, cu, max(q_lens), scale)
+    assert native.launch_count() == before + 1
+    native.check_status(torch.device(DEV))
+    ref = ops.attention_ref(q, kc, vc, bt, sl, q_lens, scale)
+    assert rel_l2(out, ref) < 1.5e-2
+    monkeypatch.setattr(core, "TC_PREFILL", False)
+    old = ops.attention_prefill(q, kc, vc, bt, sl, cu, max(q_lens), scale)
+    assert rel_l2(out, old) < 1.5e-2
+
+
 @pytest.mark.parametrize("D,n_q,n_kv,qps", [(128, 32, 8, 1), (128, 32, 8, 5), (64, 4, 2, 1), (128, 64, 8, 1),
                                             (128, 64, 8, 3), (128, 4, 4, 2)])
 @pytest.mark.parametrize("splits", [1, 3, 8])
