@@ -249,21 +249,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       for (int c = 0; c < 8; ++c) tmem_ld16(s_addr + c * 16, sc[c]);
       tmem_wait_ld();
       const int key0 = j * kTcTile;
-      const bool diag = key0 + kTcTile - 1 > tile_pos0 || key0 + kTcTile > kv_len;      // some (row, key) of the tile is masked
-      const int visible = min(qpos, kv_len - 1) - key0;                  // keys 0..visible of this tile are seen by this row
-      float mx = -INFINITY;
-      if (!diag) {
-#pragma unroll
-        for (int c = 0; c < 8; ++c)
-#pragma unroll
-          for (int i = 0; i < 16; ++i) mx = fmaxf(mx, __uint_as_float(sc[c][i]));
-      } else {
+      if (key0 + kTcTile - 1 > tile_pos0 || key0 + kTcTile > kv_len) {   // some (row, key) of the tile is masked: -inf gives p = 0
+        const int visible = min(qpos, kv_len - 1) - key0;                // keys 0..visible of this tile are seen by this row
 #pragma unroll
         for (int c = 0; c < 8; ++c)
 #pragma unroll
           for (int i = 0; i < 16; ++i)
-            if (c * 16 + i <= visible) mx = fmaxf(mx, __uint_as_float(sc[c][i]));
+            if (c * 16 + i > visible) sc[c][i] = 0xFF800000u;
       }
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains of three-input maxima
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], __uint_as_float(sc[c][i]), __uint_as_float(sc[c][i + 1]));
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_new = mx * p.scale_log2;                             // -inf for a fully masked row: every comparison below is false
       if (j == 0) {
         m = m_new == -INFINITY ? 0.f : m_new;
@@ -284,21 +283,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           }
         }
       }
-      float sum0 = 0.f, sum1 = 0.f;
+      // p = exp2(s * scale - m), two values per FMA / add; sums in four chains
+      const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2), shift2 = pack_f32x2(-m, -m);
+      uint64_t acc[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
       for (int c2 = 0; c2 < 4; ++c2) {
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           const int c = c2 * 2 + (i >> 4), e = i & 15;
-          float p0 = ex2_approx(fmaf(__uint_as_float(sc[c][e]), p.scale_log2, -m));
-          float p1 = ex2_approx(fmaf(__uint_as_float(sc[c][e + 1]), p.scale_log2, -m));
-          if (diag) {
-            if (c * 16 + e > visible) p0 = 0.f;
-            if (c * 16 + e + 1 > visible) p1 = 0.f;
-          }
-          sum0 += p0;
-          sum1 += p1;
+          float t0, t1;
+          unpack_f32x2(fma_f32x2(pack_b32x2(sc[c][e], sc[c][e + 1]), scale2, shift2), t0, t1);
+          const float p0 = ex2_approx(t0), p1 = ex2_approx(t1);
+          acc[(i >> 1) & 3] = add_f32x2(acc[(i >> 1) & 3], pack_f32x2(p0, p1));
           packed[i >> 1] = pack_bf16x2(p0, p1);
         }
         tmem_st16(s_addr + c2 * 16, packed);
@@ -306,7 +303,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(&p_full[w]);
-      l += sum0 + sum1;
+      float s0, s1;
+      unpack_f32x2(add_f32x2(add_f32x2(acc[0], acc[1]), add_f32x2(acc[2], acc[3])), s0, s1);
+      l += s0 + s1;
     }
     if (ok && n_w > 0) ok = mbar_wait(&o_final[w], 0, p.status, kStatusAccumTimeout);
     if (ok && n_w > 0) {
