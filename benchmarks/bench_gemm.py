@@ -3,6 +3,8 @@
     python -m benchmarks.bench_gemm prefill     # prefill-sized shapes against cuBLAS (torch.matmul / addmm)
     python -m benchmarks.bench_gemm chain       # decode-sized GEMMs as a dependent chain inside a CUDA graph
     python -m benchmarks.bench_gemm decode      # the four projections of a decoder layer, TP=1 and TP=8 slices
+    python -m benchmarks.bench_gemm fp8         # block-scaled FP8 weights: FP8 tensor-core kernel against the bf16 kernel
+    python -m benchmarks.bench_gemm fp8 M N K n # profiling aid: n launches of the FP8 kernel on one shape
 
 ``prefill`` covers the dense projections of a Llama-3-8B layer at 2048 and 8192 tokens (and their TP=8 slices):
 plain, + residual, and fused SwiGLU (cuBLAS arm: one GEMM plus ``silu(g) * u`` as PyTorch element-wise ops).
@@ -127,9 +129,54 @@ def one(M: int, N: int, K: int, kind: str = "residual", reps: int = 3):
                       "weight_GBs": round(w.numel() * 2 / us / 1e3, 1)}))
 
 
+def fp8(argv):
+    """Block-FP8 weights at prefill sizes: activation quantisation + FP8 tensor-core GEMM (timed together and the GEMM
+    alone) against the bf16 tcgen05 GEMM on the dequantised weight, with the error of both against the fp32 product."""
+    from eredu_b200.ops.native import lib, ptr, status_word, stream_ptr
+    from eredu_b200.ops.quant import Fp8Linear
+
+    g = torch.Generator(device=DEV).manual_seed(0)
+    if argv:
+        M, N, K, n = (int(a) for a in argv[:4])
+        q = Fp8Linear.from_dense(torch.randn(N, K, device=DEV, generator=g) * 0.03)
+        x = (torch.randn(M, K, device=DEV, generator=g) * 0.5).bfloat16()
+        for _ in range(n):
+            q.tensor_core(x)
+        torch.cuda.synchronize()
+        ops.native.check_status(DEV)
+        print(json.dumps({"M": M, "N": N, "K": K, "launched": n}))
+        return
+    for M, N, K in [(8192, 4096, 4096), (8192, 14336, 4096), (8192, 4096, 14336), (8192, 7168, 2048), (2048, 4096, 4096),
+                    (512, 4096, 4096)]:
+        w = torch.randn(N, K, device=DEV, generator=g) * 0.03
+        q = Fp8Linear.from_dense(w)
+        wd = q.dequantize(torch.bfloat16)
+        x = (torch.randn(M, K, device=DEV, generator=g) * 0.5).bfloat16()
+        ref = x.float() @ q.dequantize().t()
+        y = q.tensor_core(x)
+        yb = ops.linear(x, wd)
+        xq = torch.empty((M, K), dtype=torch.uint8, device=DEV)
+        sx = torch.empty((K // 128, M), dtype=torch.float32, device=DEV)
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=DEV)
+        lib().eredu_fp8_quant_act(ptr(x), x.stride(0), ptr(xq), ptr(sx), M, K, stream_ptr(DEV))
+        gemm_only = lambda: lib().eredu_gemm_fp8_tc(ptr(xq), ptr(sx), ptr(q.wq), ptr(q.block_scales), ptr(out), None, None, M, N, K,  # noqa: E731
+                                                    N, 0, 0, ptr(status_word(DEV)), stream_ptr(DEV))
+        us_all, us_gemm, us_bf16 = _time(lambda: q.tensor_core(x)), _time(gemm_only), _time(lambda: ops.linear(x, wd))
+        flops = 2 * M * N * K
+        print(json.dumps({"M": M, "N": N, "K": K, "fp8_quant_plus_gemm_us": round(us_all, 1), "fp8_gemm_us": round(us_gemm, 1),
+                          "fp8_gemm_tflops": round(flops / us_gemm / 1e6, 1), "bf16_gemm_us": round(us_bf16, 1),
+                          "bf16_tflops": round(flops / us_bf16 / 1e6, 1), "speedup_gemm": round(us_bf16 / us_gemm, 2),
+                          "speedup_with_quant": round(us_bf16 / us_all, 2),
+                          "rel_err_fp8": round(float((y.float() - ref).norm() / ref.norm()), 4),
+                          "rel_err_bf16": round(float((yb.float() - ref).norm() / ref.norm()), 4)}), flush=True)
+    ops.native.check_status(DEV)
+
+
 if __name__ == "__main__":
     mode = sys.argv[1] if len(sys.argv) > 1 else "prefill"
     if mode == "one":
         one(int(sys.argv[2]), int(sys.argv[3]), int(sys.argv[4]), sys.argv[5] if len(sys.argv) > 5 else "residual")
+    elif mode == "fp8":
+        fp8(sys.argv[2:])
     else:
         {"prefill": prefill, "chain": chain, "decode": decode}[mode]()

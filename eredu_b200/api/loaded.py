@@ -530,6 +530,15 @@ class LoadedModel:
             raise RuntimeError("this checkpoint has no tokenizer")
         return GrammarConstraint(self.tokenizer, kind, spec)
 
+    def attach_assistant(self, path) -> None:
+        """Load a Gemma 4 assistant drafter (its own directory) next to this model: speculative generation then drafts
+        with it (``load_gemma4_assistant_model``, eredu/src/backend/mlx/architectures/gemma4/assistant.rs:499)."""
+        from ..models.gemma4_assistant import load_gemma4_assistant
+
+        if "gemma4" not in self.engine.cfg.extra:
+            raise ValueError("an assistant drafter attaches to a Gemma 4 target")
+        self.assistant = load_gemma4_assistant(path, self.engine.model)
+
     def _mtp_decoder(self, draft, draft_tokens: int, embedded_mtp: bool = True):
         """The speculative decoder this model can run: an external draft model, else its own prediction layer."""
         from ..runtime.speculative import EmbeddedMtpDecoder, SpeculativeDecoder
@@ -538,6 +547,10 @@ class LoadedModel:
             return None
         if draft is not None:
             return SpeculativeDecoder(self.engine, draft.engine, k=draft_tokens)
+        if getattr(self, "assistant", None) is not None:
+            from ..runtime.speculative import Gemma4AssistantDecoder
+
+            return Gemma4AssistantDecoder(self.engine, self.assistant, k=draft_tokens)
         if embedded_mtp and getattr(self, "mtp", None) is not None:
             return EmbeddedMtpDecoder(self.engine, self.mtp, k=draft_tokens)
         return None
@@ -687,7 +700,8 @@ class LoadedModel:
             reason = done.requests[0].finish_reason or FinishReason.MAX_TOKENS
             self.last_speculative_stats = dict(spec.stats.summary(), scheduler=vars(done.scheduler),
                                                request=vars(done.requests[0].stats),
-                                               drafter="external" if draft is not None else "embedded")
+                                               drafter="external" if draft is not None else
+                                               "assistant" if getattr(self, "assistant", None) is not None else "embedded")
         elif draft is not None:
             from ..runtime.speculative import SpeculativeDecoder
 

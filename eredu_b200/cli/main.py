@@ -10,6 +10,7 @@ from __future__ import annotations
 import argparse
 import dataclasses
 import json
+import os
 import sys
 import time
 
@@ -248,6 +249,15 @@ def benchmark_candidates(model_path: str, a, candidates: list, prompt: str) -> d
             "candidates": rows, "_selected_plan": candidates[best]}
 
 
+def _is_gemma4_assistant(path) -> bool:
+    """A draft directory whose config.json names the Gemma 4 assistant drafter."""
+    cfg = os.path.join(path, "config.json")
+    if not os.path.isfile(cfg):
+        return False
+    with open(cfg) as f:
+        return str(json.load(f).get("model_type", "")).startswith("gemma4_assistant")
+
+
 def main(argv=None) -> int:
     a = build_parser().parse_args(argv)
     validate_args(a)
@@ -445,10 +455,13 @@ def main(argv=None) -> int:
     if a.draft_model:
         if mirostat is not None:
             raise SystemExit("--draft-model cannot be combined with --mirostat-v2")
-        draft = LoadedModel.load(a.draft_model, ModelLoadOptions(device=device, max_batch=1,
-                                                                  max_seq_len=max(4096, a.max_tokens + 2048)))
-        if draft.config.vocab_size != lm.config.vocab_size:
-            raise SystemExit("--draft-model must share the target's vocabulary")
+        if _is_gemma4_assistant(a.draft_model):
+            lm.attach_assistant(a.draft_model)              # no cache of its own: it reads the target's keys and values
+        else:
+            draft = LoadedModel.load(a.draft_model, ModelLoadOptions(device=device, max_batch=1,
+                                                                      max_seq_len=max(4096, a.max_tokens + 2048)))
+            if draft.config.vocab_size != lm.config.vocab_size:
+                raise SystemExit("--draft-model must share the target's vocabulary")
     # speculative requests run through the fair scheduler; the two switches shape its lookahead
     from ..runtime.mtp_scheduler import MtpSchedulerOptions
 

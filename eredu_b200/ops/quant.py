@@ -24,6 +24,8 @@ native.register("eredu_dequant_affine", I, [P, P, P, P, I, I, I, I, P])
 native.register("eredu_qgemv4", I, [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, I, I, P, P, P])
 native.register("eredu_qgemm_fp8", I, [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P])
 native.register("eredu_dequant_fp8", I, [P, P, P, I, I, P])
+native.register("eredu_fp8_quant_act", I, [P, I, P, P, I, I, P])
+native.register("eredu_gemm_fp8_tc", I, [P, P, P, P, P, P, P, I, I, I, I, I, I, P, P])
 
 _NIBBLE_ORDER = (0, 2, 4, 6, 1, 3, 5, 7)  # kernel position p holds logical nibble _NIBBLE_ORDER[p]
 
@@ -272,6 +274,8 @@ class QuantLinear:
         dev = x.device
         if self._gemv_ok(x) and (out is None or out.stride(1) == 1):
             return self._gemv(x, bias, residual, out, out_dtype, False)
+        if M > self.DENSE_FALLBACK_TOKENS and self.TENSOR_CORE_FP8 and self.block_scales is not None:
+            return self.tensor_core(x, bias=bias, residual=residual, out=out, out_dtype=out_dtype)
         if M > self.DENSE_FALLBACK_TOKENS:
             w = torch.empty((N, K), dtype=torch.bfloat16, device=dev)
             check(lib().eredu_dequant_affine(ptr(self.wq), ptr(self.scales_t), ptr(self.biases_t), ptr(w), N, K,
@@ -293,7 +297,8 @@ class Fp8Linear:
     E4M3 on the device and decoded inside the tcgen05 pipeline; activations stay bf16. The block scales are expanded
     along the output rows into an fp32 table [K/128, N], so row slices and row concatenations need no alignment."""
 
-    DENSE_FALLBACK_TOKENS = 256
+    DENSE_FALLBACK_TOKENS = 256      # above this many tokens the weight-streaming kernel gives way to a GEMM-shaped one
+    TENSOR_CORE_FP8 = True           # ... which is the FP8 tensor-core kernel when the scale table is block-uniform
     bits, kbits, group = 8, 8, 128
 
     def __init__(self, w8: torch.Tensor, block_scale: torch.Tensor, device, row_scales_t: Optional[torch.Tensor] = None):
@@ -310,6 +315,13 @@ class Fp8Linear:
             row_scales_t = block_scale.to(torch.float32).repeat_interleave(128, 0)[:N].t()
         self.scales_t = row_scales_t.to(dev, torch.float32).contiguous()
         assert self.scales_t.shape == (K // 128, N)
+        # The FP8 tensor-core kernel folds one weight scale per 128 x 128 tile: usable when every aligned run of 128 rows
+        # of the (possibly sliced or concatenated) table carries one value per K block.
+        self.block_scales = None
+        if N % 128 == 0:
+            tiles = self.scales_t.view(K // 128, N // 128, 128)
+            if bool((tiles == tiles[..., :1]).all()):
+                self.block_scales = tiles[..., 0].contiguous()
 
     @classmethod
     def from_dense(cls, w: torch.Tensor):
@@ -357,6 +369,8 @@ class Fp8Linear:
         assert K == self.in_features and x.dtype == torch.bfloat16 and x.stride(1) == 1
         out_dtype = out_dtype or torch.bfloat16
         dev = x.device
+        if M > self.DENSE_FALLBACK_TOKENS and self.TENSOR_CORE_FP8 and self.block_scales is not None:
+            return self.tensor_core(x, bias=bias, residual=residual, out=out, out_dtype=out_dtype)
         if M > self.DENSE_FALLBACK_TOKENS:
             w = torch.empty((N, K), dtype=torch.bfloat16, device=dev)
             check(lib().eredu_dequant_fp8(ptr(self.wq), ptr(self.scales_t), ptr(w), N, K, stream_ptr(dev)), "eredu_dequant_fp8")
@@ -369,6 +383,29 @@ class Fp8Linear:
                                      stream_ptr(dev))
         check(code, "eredu_qgemm_fp8")
         return out
+
+
+def _fp8_tensor_core(self, x, bias=None, residual=None, out=None, out_dtype=None):
+    """The GEMM-shaped path of :class:`Fp8Linear`: the activations are quantised to E4M3 with one scale per row per 128
+    columns (``eredu_fp8_quant_act``) and multiplied on the FP8 tensor cores, the scale product folded in per K block
+    (``eredu_gemm_fp8_tc``). Reference: eredu/src/backend/mlx/nn/fp8.rs:291-323 (activation quantisation), :664-742."""
+    M, K = x.shape
+    N = self.out_features
+    dev = x.device
+    out_dtype = out_dtype or torch.bfloat16
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=dev)
+    xq = torch.empty((M, K), dtype=torch.uint8, device=dev)
+    sx = torch.empty((K // 128, M), dtype=torch.float32, device=dev)
+    check(lib().eredu_fp8_quant_act(ptr(x), x.stride(0), ptr(xq), ptr(sx), M, K, stream_ptr(dev)), "eredu_fp8_quant_act")
+    code = lib().eredu_gemm_fp8_tc(ptr(xq), ptr(sx), ptr(self.wq), ptr(self.block_scales), ptr(out), ptr(residual), ptr(bias),
+                                   M, N, K, out.stride(0), residual.stride(0) if residual is not None else 0,
+                                   1 if out_dtype == torch.float32 else 0, ptr(status_word(dev)), stream_ptr(dev))
+    check(code, "eredu_gemm_fp8_tc")
+    return out
+
+
+Fp8Linear.tensor_core = _fp8_tensor_core
 
 
 def make_quantizer(src, opt):

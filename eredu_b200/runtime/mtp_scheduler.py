@@ -169,8 +169,12 @@ class MtpScheduler:
         self.k = decoder.k
         self.cuda = decoder.cuda
         self.embedded = isinstance(decoder, EmbeddedMtpDecoder)
-        # recurrent drafters would need a state snapshot per optimistic step: their lookahead stays off
-        self.lookahead_possible = bool(self.options.lookahead_blocks) and not decoder.d_hybrid
+        # decoders whose next round starts from hidden states of the verify pass (embedded heads, cache-less assistants)
+        self.keeps_hidden = self.embedded or bool(getattr(decoder, "carries_verify_hidden", False))
+        # recurrent drafters would need a state snapshot per optimistic step: their lookahead stays off; so does that of
+        # drafters that say they cannot continue past an unverified block
+        self.lookahead_possible = (bool(self.options.lookahead_blocks) and not decoder.d_hybrid
+                                   and bool(getattr(decoder, "supports_lookahead", True)))
         if self.cuda:
             dev = decoder.t.device
             self.target_stream, self.draft_stream = streams or (torch.cuda.Stream(dev), torch.cuda.Stream(dev))
@@ -315,7 +319,7 @@ class MtpScheduler:
     def _draft(self, req: _Request):
         base = req.tseq.kv_len + 1
         with torch.no_grad(), self._on(self.draft_stream):
-            if self.embedded:
+            if self.keeps_hidden:
                 self.dec._seq_ids = [req.tseq.seq_id]
             pend = {0: req.pending}
             drafted, p_d, ctx = self.dec._propose([req.tseq], [req.dseq], [0], pend, req.sp, [base])
@@ -335,12 +339,12 @@ class MtpScheduler:
         with torch.no_grad(), self._on(self.target_stream):
             if blk["done"] is not None:
                 torch.cuda.current_stream().wait_event(blk["done"])      # the draft distributions come from the other stream
-            if self.embedded:
+            if self.keeps_hidden:
                 dec._seq_ids = [req.tseq.seq_id]
             feed = [[req.last] + blk["drafted"]]
             snap = dec.t.snapshot_state(req.tseq) if dec.t_hybrid else None
             logits = dec._verify_forward([req.tseq], feed)
-            hidden = dec._verify_hidden if self.embedded else None
+            hidden = dec._verify_hidden if self.keeps_hidden else None
             pos = [blk["base"] + j for j in range(k + 1)]
             p_t, t_toks = dec._probs_and_tokens(dec.t, logits, [req.sp] * (k + 1), pos, [req.tseq.seq_id] * (k + 1))
             p_t = p_t.view(1, k + 1, V)
@@ -443,7 +447,7 @@ class MtpScheduler:
                     promoted = True
                 else:
                     st.optimistic_bonus_mismatches += 1
-        if self.embedded:
+        if self.keeps_hidden:
             dec._seq_ids = [req.tseq.seq_id]
             dec._verify_hidden = fl["hidden"]
             if self.cuda:
@@ -545,7 +549,7 @@ class MtpScheduler:
                 torch.cuda.synchronize(self.dec.t.device)
             self.dec.t.release(req.tseq)
             self.dec.d.release(req.dseq)
-            if self.embedded:
+            if self.keeps_hidden:
                 self.dec._pending_hidden.pop(req.tseq.seq_id, None)
             req.tseq = req.dseq = None
 

@@ -480,6 +480,98 @@ class EmbeddedMtpDecoder(SpeculativeDecoder):
         super()._round(tseqs, dseqs, live, outs, pending, last, sp)
 
 
+class _NoDraftEngine:
+    """Stands where a draft engine would for drafters that keep no cache of their own."""
+
+    class _Seq:
+        kv_len = 0
+
+    class _Kv:
+        @staticmethod
+        def has_recurrent_state():
+            return False
+
+    def __init__(self, cfg):
+        self.cfg, self.kv = cfg, self._Kv()
+
+    def new_sequence(self, *a, **k):
+        return self._Seq()
+
+    def release(self, seq):
+        pass
+
+
+class Gemma4AssistantDecoder(SpeculativeDecoder):
+    """Speculative decoding with a Gemma 4 assistant (eredu/src/backend/mlx/architectures/gemma4/mtp.rs): the drafter has
+    no cache, it reads the K / V the target committed. Per request the decoder keeps the target's pre-norm hidden state of
+    the newest cached token; a round's first draft step pairs it with the newest token, later steps chain the drafter's
+    own projection. The verify pass keeps its hidden states, and row ``accepted`` becomes the next round's state."""
+
+    carries_verify_hidden = True
+    supports_lookahead = False
+
+    def __init__(self, target: Engine, assistant, k: Optional[int] = None):
+        k = min(k or assistant.max_proposals, assistant.max_proposals)
+        super().__init__(target, _NoDraftEngine(target.cfg), k)
+        self.assistant = assistant
+        self._pending_hidden: dict = {}
+        self._verify_hidden = None
+        self._last_chain = None
+
+    def _capture(self, store: dict):
+        def prepare(batch):
+            batch.capture_hidden = True
+            store["batch"] = batch
+        return prepare
+
+    def _prefill(self, tseqs, dseqs) -> list:
+        prompts = [list(s.prompt) for s in tseqs]
+        cap: dict = {}
+        logits = self._multi_token_step(self.t, tseqs, prompts, all_rows=False, uniform=False, prepare=self._capture(cap))
+        hidden = cap["batch"].hidden_out
+        ends = np.cumsum([len(p) for p in prompts]) - 1
+        for s, p, e in zip(tseqs, prompts, ends):
+            s.kv_len = len(p)
+            self._pending_hidden[s.seq_id] = hidden[int(e):int(e) + 1].clone()
+        _, toks = self._probs_and_tokens(self.t, logits, [s.sampling for s in tseqs], [len(p) for p in prompts],
+                                         [s.seq_id for s in tseqs])
+        return [int(t) for t in toks.tolist()]
+
+    def _propose(self, tseqs, dseqs, live, pending, sp, base):
+        k, B = self.k, len(tseqs)
+        eng = self.t
+        drafted = [[] for _ in range(B)]
+        p_d = []
+        hidden = torch.cat([self._pending_hidden[s.seq_id] for s in tseqs])
+        tokens = eng._t(np.asarray([pending[i][-1] for i in live], dtype=np.int64), torch.int64)
+        block_table = eng._block_table(tseqs)
+        cache_lens = eng._t(np.asarray([s.kv_len for s in tseqs], dtype=np.int64), torch.int64)
+        for j in range(k):
+            logits, hidden = self.assistant.draft_step(tokens, hidden, eng.kv, block_table, cache_lens, j)
+            probs, toks = self._probs_and_tokens(eng, logits, [sp] * B, [base[b] + j for b in range(B)],
+                                                 [s.seq_id for s in tseqs])
+            p_d.append(probs)
+            tokens = toks.to(torch.int64)
+            for b, t in enumerate(toks.tolist()):
+                drafted[b].append(int(t))
+        return drafted, p_d, None
+
+    def _verify_forward(self, tseqs, feed):
+        cap: dict = {}
+        logits = self._multi_token_step(self.t, tseqs, feed, all_rows=True, uniform=True, prepare=self._capture(cap))
+        self._verify_hidden = cap["batch"].hidden_out.view(len(tseqs), self.k + 1, -1)
+        return logits
+
+    def _settle(self, b, i, a, nxt, dseqs, drafted, pending, ctx):
+        pending[i] = [nxt]
+        # row j of the verify pass belongs to its j-th input: `last`, d_1 .. d_k; the newest cached token is input `a`
+        self._pending_hidden[self._seq_ids[b]] = self._verify_hidden[b, a:a + 1].clone()
+
+    def _round(self, tseqs, dseqs, live, outs, pending, last, sp):
+        self._seq_ids = [s.seq_id for s in tseqs]
+        super()._round(tseqs, dseqs, live, outs, pending, last, sp)
+
+
 class GraphSpeculativeDecoder(SpeculativeDecoder):
     """The speculative round as ONE CUDA graph (GPU only, fixed batch): k draft steps, the target's verify pass over
     k+1 tokens, both samplers and the accept / resample kernel are captured once; a round is a few small

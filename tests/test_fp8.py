@@ -68,7 +68,8 @@ def test_fp8_checkpoint_reads_as_dequantised_weights_on_cpu(tmp_path):
 @pytest.mark.gpu
 @pytest.mark.parametrize("M", [1, 7, 32, 50, 128, 300])
 @pytest.mark.parametrize("N,K", [(640, 1024), (200, 512), (1284, 256)])
-def test_fp8_gemm_matches_dequantised_matmul(M, N, K):
+def test_fp8_gemm_matches_dequantised_matmul(M, N, K, monkeypatch):
+    monkeypatch.setattr(Fp8Linear, "TENSOR_CORE_FP8", False)        # bf16 activations on every path of this test
     torch.manual_seed(M * 7 + N)
     w = (torch.randn(N, K, device="cuda") * 0.05)
     q = Fp8Linear.from_dense(w)
@@ -83,6 +84,67 @@ def test_fp8_gemm_matches_dequantised_matmul(M, N, K):
     ref32 = x.float() @ q.dequantize().t()
     assert float((y32 - ref32).norm() / ref32.norm()) < 5e-3
     from eredu_b200.ops import native
+    native.check_status(torch.device("cuda", torch.cuda.current_device()))
+
+
+def _quantise_rows_ref(x):
+    """1 x 128 dynamic activation quantisation in tensor operations: scale = max(|x|, 1e-4) / 448, E4M3 round to nearest."""
+    M, K = x.shape
+    b = x.float().view(M, K // 128, 128)
+    scale = b.abs().amax(-1).clamp_min(1e-4) / 448.0
+    codes = (b / scale[..., None]).to(torch.float8_e4m3fn)
+    return codes.view(M, K), scale
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M", [257, 512, 1000])
+@pytest.mark.parametrize("N,K", [(640, 1024), (128, 128), (1280, 3072)])
+def test_fp8_tensor_core_gemm_against_the_oracles(M, N, K):
+    """The FP8 tensor-core path: exact against the same quantised operands multiplied in fp32, and inside the native-FP8
+    gates (rel-L2 <= 0.05, cosine >= 0.995) against the unquantised activations."""
+    from eredu_b200.ops import native
+
+    torch.manual_seed(M + N + K)
+    w = torch.randn(N, K, device="cuda") * 0.05
+    w[: N // 2] *= 8.0                                                  # blocks with very different scales
+    q = Fp8Linear.from_dense(w)
+    assert q.block_scales is not None and q.block_scales.shape == (K // 128, N // 128)
+    x = (torch.randn(M, K, device="cuda") * torch.rand(M, 1, device="cuda") * 3).bfloat16()
+    x[:, K // 2:] *= 0.01                                               # and columns blocks of very different magnitude
+    res = torch.randn(M, N, device="cuda").bfloat16()
+    bias = torch.randn(N, device="cuda").bfloat16()
+    y = q.tensor_core(x, bias=bias, residual=res, out_dtype=torch.float32)
+    codes, scale = _quantise_rows_ref(x)
+    xd = (codes.float().view(M, K // 128, 128) * scale[..., None]).view(M, K)
+    same = xd @ q.dequantize().t() + bias.float() + res.float()
+    assert float((y - same).norm() / same.norm()) < 2e-3
+    y16 = q(x)                                                          # the dispatching call takes this path above 256 tokens
+    full = x.float() @ q.dequantize().t()
+    rel = float((y16.float() - full).norm() / full.norm())
+    cos = float(torch.nn.functional.cosine_similarity(y16.float().flatten(), full.flatten(), dim=0))
+    assert rel <= 0.05 and cos >= 0.995, (rel, cos)
+    native.check_status(torch.device("cuda", torch.cuda.current_device()))
+
+
+@pytest.mark.gpu
+def test_fp8_activation_quantiser_matches_the_rule():
+    from eredu_b200.ops import native
+    from eredu_b200.ops.native import lib, ptr, stream_ptr
+
+    torch.manual_seed(3)
+    M, K = 77, 512
+    big = (torch.randn(M, K + 128, device="cuda") * 2).bfloat16()
+    x = big[:, :K]                                                      # a strided view: the row stride is passed
+    x[5] = 0                                                            # an all-zero row takes the floor of the scale
+    xq = torch.empty((M, K), dtype=torch.uint8, device="cuda")
+    sx = torch.empty((K // 128, M), dtype=torch.float32, device="cuda")
+    assert lib().eredu_fp8_quant_act(ptr(x), x.stride(0), ptr(xq), ptr(sx), M, K, stream_ptr(x.device)) == 0
+    codes, scale = _quantise_rows_ref(x)
+    assert torch.allclose(sx.t(), scale, rtol=1e-6)
+    got = xq.view(torch.float8_e4m3fn).float()
+    want = codes.float()
+    assert float((got != want).float().mean()) < 2e-3                   # reciprocal-multiply against divide: rare one-step ties
+    assert float((got - want).abs().max()) <= 32.0
     native.check_status(torch.device("cuda", torch.cuda.current_device()))
 
 
