@@ -156,10 +156,11 @@ def fp8(argv):
         y = q.tensor_core(x)
         yb = ops.linear(x, wd)
         xq = torch.empty((M, K), dtype=torch.uint8, device=DEV)
-        sx = torch.empty((K // 128, M), dtype=torch.float32, device=DEV)
+        ld = (M + 127) // 128 * 128
+        sx = torch.empty((K // 128, ld), dtype=torch.float32, device=DEV)
         out = torch.empty((M, N), dtype=torch.bfloat16, device=DEV)
-        lib().eredu_fp8_quant_act(ptr(x), x.stride(0), ptr(xq), ptr(sx), M, K, stream_ptr(DEV))
-        gemm_only = lambda: lib().eredu_gemm_fp8_tc(ptr(xq), ptr(sx), ptr(q.wq), ptr(q.block_scales), ptr(out), None, None, M, N, K,  # noqa: E731
+        lib().eredu_fp8_quant_act(ptr(x), x.stride(0), ptr(xq), ptr(sx), ld, M, K, stream_ptr(DEV))
+        gemm_only = lambda: lib().eredu_gemm_fp8_tc(ptr(xq), ptr(sx), ld, ptr(q.wq), ptr(q.block_scales), ptr(out), None, None, M, N, K,  # noqa: E731
                                                     N, 0, 0, ptr(status_word(DEV)), stream_ptr(DEV))
         us_all, us_gemm, us_bf16 = _time(lambda: q.tensor_core(x)), _time(gemm_only), _time(lambda: ops.linear(x, wd))
         flops = 2 * M * N * K

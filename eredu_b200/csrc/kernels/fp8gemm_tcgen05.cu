@@ -1,7 +1,7 @@
 // Block-scaled FP8 GEMM on the FP8 tensor cores: Y = (Xq * sx) (Wq * sw)^T (+bias) (+residual).
 //
-//   Xq  E4M3 [M, K] with one fp32 scale per row per 128 input columns, table sx_t [K/128, M] (dynamic quantisation of the
-//       bf16 activations, act_quant_fp8_kernel below: scale = max(|x|, 1e-4) / 448, as the reference's
+//   Xq  E4M3 [M, K] with one fp32 scale per row per 128 input columns, table sx_t [K/128, ld_sx] with ld_sx = M rounded
+//       up to 128 (dynamic quantisation of the bf16 activations, act_quant_fp8_kernel below: scale = max(|x|, 1e-4) / 448, as the reference's
 //       block_fp8_activation_quantization kernel, eredu/src/backend/mlx/nn/fp8.rs:291-323)
 //   Wq  E4M3 [N, K] with one fp32 scale per 128 x 128 block, table sw [K/128, N/128] (the checkpoint's own blocks;
 //       eredu/src/backend/mlx/nn/fp8.rs:330-345 is the decoding rule)
@@ -12,7 +12,9 @@
 // block). Four 128-column buffers rotate, so the tensor core runs up to three K blocks ahead of the folding.
 //
 // One CTA per 128 x 128 output tile (m fastest, so CTAs that are resident together share the B tile in L2):
-//   warp 0      TMA producer: A and B tiles of 128 rows x 128 bytes, 128-byte swizzled, six stages
+//   warp 0      TMA producer: A and B tiles of 128 rows x 128 bytes, 128-byte swizzled, six stages; with every stage the
+//               128 activation scales of that K block (one 512-byte bulk copy into a 16-deep ring: the folding warps read a
+//               K block's scales up to four accumulator buffers after its operand stage was handed back)
 //   warp 1      MMA issuer (one thread)
 //   warps 2..9  folding and store: lane quarter = warp % 4 (rows), column half = (warp - 2) / 4; a thread owns 64
 //               columns of one output row
@@ -28,7 +30,8 @@
 namespace eredu {
 
 struct Fp8GemmParams {
-  const float* sx_t;            // [K/128, M]
+  const float* sx_t;            // [K/128, ld_sx]
+  int ld_sx;                    // M rounded up to a multiple of 128
   const float* sw;              // [K/128, N/128]
   void* y;                      // bf16 or fp32 [M, ldy]
   const __nv_bfloat16* residual;
@@ -42,14 +45,25 @@ struct Fp8GemmParams {
 constexpr int kF8Threads = 320;
 constexpr int kF8Stages = 6;
 constexpr int kF8Tile = 128 * 128;      // one operand tile: 128 rows x 128 E4M3 bytes
-constexpr int kF8Smem = 1024 + kF8Stages * 2 * kF8Tile + 256;
+constexpr int kF8ScaleRing = 16;        // > stages + accumulator buffers
+constexpr int kF8MaxKBlocks = 512;      // weight scales of one tile column, staged once
+constexpr int kF8Smem = 1024 + kF8Stages * 2 * kF8Tile + kF8ScaleRing * 512 + kF8MaxKBlocks * 4 + 256;
+
+__device__ __forceinline__ void f8_bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               :
+               : "r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
 constexpr uint32_t kF8Idesc = umma_idesc_e4m3(128, 128);
 
 __global__ void __launch_bounds__(kF8Threads, 1)
 gemm_fp8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Fp8GemmParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kF8Stages * 2 * kF8Tile);
+  float* sx_s = reinterpret_cast<float*>(smem + kF8Stages * 2 * kF8Tile);       // [ring][128]
+  float* sw_s = sx_s + kF8ScaleRing * 128;                                     // [kblocks]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sw_s + kF8MaxKBlocks);
   uint64_t* full = bars;                        // [stages]
   uint64_t* empty = bars + kF8Stages;           // [stages]
   uint64_t* acc_full = bars + 2 * kF8Stages;    // [4]
@@ -93,7 +107,8 @@ gemm_fp8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         if (kb >= kF8Stages) ok = mbar_wait(&empty[s], ((kb / kF8Stages) - 1) & 1, p.status, kStatusSmemEmptyTimeout);
         if (!ok) break;
         uint8_t* st = smem + s * 2 * kF8Tile;
-        mbar_arrive_expect_tx(&full[s], 2 * kF8Tile);
+        mbar_arrive_expect_tx(&full[s], 2 * kF8Tile + 512);
+        f8_bulk_load(sx_s + (kb % kF8ScaleRing) * 128, p.sx_t + static_cast<size_t>(kb) * p.ld_sx + tile_m * 128, 512, &full[s]);
         tma_load_2d(st, &tmA, kb * 128, tile_m * 128, &full[s]);
         tma_load_2d(st + kF8Tile, &tmB, kb * 128, tile_n * 128, &full[s]);
       }
@@ -123,18 +138,19 @@ gemm_fp8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     float acc[64];
 #pragma unroll
     for (int i = 0; i < 64; ++i) acc[i] = 0.f;
-    float c_next = (live ? p.sx_t[row] : 0.f) * p.sw[tile_n];
+    // this tile column's weight scales: one per K block, staged once by the folding warps themselves
+    for (int i = threadIdx.x - 64; i < kblocks; i += 256) sw_s[i] = p.sw[static_cast<size_t>(i) * n_blocks + tile_n];
+    asm volatile("bar.sync 1, 256;" ::: "memory");
     for (int kb = 0; kb < kblocks && ok; ++kb) {
       const int buf = kb & 3;
-      const float c = c_next;
-      if (kb + 1 < kblocks)
-        c_next = (live ? p.sx_t[static_cast<size_t>(kb + 1) * p.M + row] : 0.f) * p.sw[static_cast<size_t>(kb + 1) * n_blocks + tile_n];
       ok = mbar_wait(&acc_full[buf], (kb >> 2) & 1, p.status, kStatusAccumTimeout);
       if (!ok) break;
       tc_fence_after_sync();
       uint32_t part[4][16];
 #pragma unroll
       for (int h = 0; h < 4; ++h) tmem_ld16(t_addr + buf * 128 + h * 16, part[h]);
+      // acc_full follows the stage's full barrier, so the K block's scales have landed
+      const float c = sx_s[(kb % kF8ScaleRing) * 128 + quarter * 32 + lane] * sw_s[kb];
       tmem_wait_ld();
       tc_fence_before_sync();
       __syncwarp();
@@ -183,7 +199,7 @@ gemm_fp8_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 
 // One warp per (row, 128-column block): 4 bf16 per lane, maximum by shuffles, E4M3 codes and the block's scale.
 __global__ void __launch_bounds__(256) act_quant_fp8_kernel(const __nv_bfloat16* __restrict__ x, int ldx, uint8_t* __restrict__ xq,
-                                                            float* __restrict__ sx_t, int M, int K) {
+                                                            float* __restrict__ sx_t, int ld_sx, int M, int K) {
   pdl_launch_early();
   pdl_wait();
   pdl_launch_dependents();
@@ -199,29 +215,30 @@ __global__ void __launch_bounds__(256) act_quant_fp8_kernel(const __nv_bfloat16*
   const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v0 * inv, v1 * inv), __NV_SATFINITE, __NV_E4M3);
   const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v2 * inv, v3 * inv), __NV_SATFINITE, __NV_E4M3);
   *reinterpret_cast<uint32_t*>(xq + static_cast<size_t>(row) * K + kb * 128 + lane * 4) = lo | (hi << 16);
-  if (lane == 0) sx_t[static_cast<size_t>(kb) * M + row] = scale;
+  if (lane == 0) sx_t[static_cast<size_t>(kb) * ld_sx + row] = scale;
 }
 
 }  // namespace eredu
 
 using namespace eredu;
 
-// Dynamic 1 x 128 quantisation of bf16 activations x [M, K] (row stride ldx) to E4M3 xq [M, K] and scales sx_t [K/128, M].
-extern "C" int eredu_fp8_quant_act(const void* x, int ldx, void* xq, float* sx_t, int M, int K, cudaStream_t stream) {
-  if (M <= 0 || K <= 0 || K % 128 != 0 || ldx % 4 != 0) return -2;
+// Dynamic 1 x 128 quantisation of bf16 activations x [M, K] (row stride ldx) to E4M3 xq [M, K] and scales sx_t [K/128, ld_sx].
+extern "C" int eredu_fp8_quant_act(const void* x, int ldx, void* xq, float* sx_t, int ld_sx, int M, int K, cudaStream_t stream) {
+  if (M <= 0 || K <= 0 || K % 128 != 0 || ldx % 4 != 0 || ld_sx < M) return -2;
   dim3 grid(K / 128, (M + 7) / 8);
   const cudaError_t e = launch_pdl(act_quant_fp8_kernel, grid, dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(x), ldx,
-                                   static_cast<uint8_t*>(xq), sx_t, M, K);
+                                   static_cast<uint8_t*>(xq), sx_t, ld_sx, M, K);
   eredu_count_launches(1);
   return static_cast<int>(e);
 }
 
-// Y [M, N] = (xq * sx) (wq * sw)^T (+bias) (+residual); xq E4M3 [M, K], sx_t fp32 [K/128, M], wq E4M3 [N, K], sw fp32
+// Y [M, N] = (xq * sx) (wq * sw)^T (+bias) (+residual); xq E4M3 [M, K], sx_t fp32 [K/128, ld_sx] (ld_sx: M rounded up to 128), wq E4M3 [N, K], sw fp32
 // [K/128, N/128]; N and K multiples of 128. Returns -2 for shapes it does not take.
-extern "C" int eredu_gemm_fp8_tc(const void* xq, const float* sx_t, const void* wq, const float* sw, void* Y, const void* residual,
+extern "C" int eredu_gemm_fp8_tc(const void* xq, const float* sx_t, int ld_sx, const void* wq, const float* sw, void* Y, const void* residual,
                                  const void* bias, int M, int N, int K, int ldy, int ldr, int out_fp32, int* status,
                                  cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0 || N % 128 != 0 || K % 128 != 0 || ldy % 8 != 0 || (residual != nullptr && ldr % 8 != 0)) return -2;
+  if (K / 128 > kF8MaxKBlocks || ld_sx % 128 != 0 || ld_sx < M) return -2;
   CUtensorMap tmA, tmB;
   int r = make_tma_2d(&tmA, xq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, static_cast<uint64_t>(M), static_cast<uint64_t>(K),
                       static_cast<uint64_t>(K), 128, 128);
@@ -231,6 +248,7 @@ extern "C" int eredu_gemm_fp8_tc(const void* xq, const float* sx_t, const void* 
   if (r != 0) return -200 + r;
   Fp8GemmParams p = {};
   p.sx_t = sx_t;
+  p.ld_sx = ld_sx;
   p.sw = sw;
   p.y = Y;
   p.residual = static_cast<const __nv_bfloat16*>(residual);

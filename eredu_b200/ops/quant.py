@@ -24,8 +24,8 @@ native.register("eredu_dequant_affine", I, [P, P, P, P, I, I, I, I, P])
 native.register("eredu_qgemv4", I, [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, I, I, P, P, P])
 native.register("eredu_qgemm_fp8", I, [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P])
 native.register("eredu_dequant_fp8", I, [P, P, P, I, I, P])
-native.register("eredu_fp8_quant_act", I, [P, I, P, P, I, I, P])
-native.register("eredu_gemm_fp8_tc", I, [P, P, P, P, P, P, P, I, I, I, I, I, I, P, P])
+native.register("eredu_fp8_quant_act", I, [P, I, P, P, I, I, I, P])
+native.register("eredu_gemm_fp8_tc", I, [P, P, I, P, P, P, P, P, I, I, I, I, I, I, P, P])
 
 _NIBBLE_ORDER = (0, 2, 4, 6, 1, 3, 5, 7)  # kernel position p holds logical nibble _NIBBLE_ORDER[p]
 
@@ -396,9 +396,10 @@ def _fp8_tensor_core(self, x, bias=None, residual=None, out=None, out_dtype=None
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=dev)
     xq = torch.empty((M, K), dtype=torch.uint8, device=dev)
-    sx = torch.empty((K // 128, M), dtype=torch.float32, device=dev)
-    check(lib().eredu_fp8_quant_act(ptr(x), x.stride(0), ptr(xq), ptr(sx), M, K, stream_ptr(dev)), "eredu_fp8_quant_act")
-    code = lib().eredu_gemm_fp8_tc(ptr(xq), ptr(sx), ptr(self.wq), ptr(self.block_scales), ptr(out), ptr(residual), ptr(bias),
+    ld = (M + 127) // 128 * 128                  # the GEMM fetches a tile's 128 scales with one aligned bulk copy
+    sx = torch.empty((K // 128, ld), dtype=torch.float32, device=dev)
+    check(lib().eredu_fp8_quant_act(ptr(x), x.stride(0), ptr(xq), ptr(sx), ld, M, K, stream_ptr(dev)), "eredu_fp8_quant_act")
+    code = lib().eredu_gemm_fp8_tc(ptr(xq), ptr(sx), ld, ptr(self.wq), ptr(self.block_scales), ptr(out), ptr(residual), ptr(bias),
                                    M, N, K, out.stride(0), residual.stride(0) if residual is not None else 0,
                                    1 if out_dtype == torch.float32 else 0, ptr(status_word(dev)), stream_ptr(dev))
     check(code, "eredu_gemm_fp8_tc")
