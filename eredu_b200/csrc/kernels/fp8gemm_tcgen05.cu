@@ -19,6 +19,14 @@
 //   warps 2..9  folding and store: lane quarter = warp % 4 (rows), column half = (warp - 2) / 4; a thread owns 64
 //               columns of one output row
 // Every wait is bounded; on expiry the status word is set and the CTA leaves through the common exit.
+//
+// Measured (B200, M = 8192): 1.1-1.3 PFLOP/s, i.e. 0.8-0.98 of this repository's bf16 tcgen05 GEMM on the same shapes, and
+// ahead of it only around 512 tokens. Folding reads every partial tile out of tensor memory once per K block (64 KB per
+// 128 x 128 x 128 block), and that read path, not the tensor pipe (27 % active under ncu) nor instruction issue (27 %),
+// sets the pace: sixteen folding warps with the next block's loads in flight were slower (0.7 PFLOP/s) than these eight.
+// The form that would pass the bf16 kernel keeps the sum over K inside the tensor core with power-of-two block scales
+// (the block-scaled MMA kinds); weight scales of block-FP8 checkpoints are arbitrary fp32 values, so that needs a
+// re-encoding of the weights and is not built.
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 
