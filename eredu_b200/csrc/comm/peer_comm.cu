@@ -43,13 +43,21 @@ __global__ void __launch_bounds__(512) allreduce_twoshot_kernel(PeerComm c, long
   for (long long i = lo + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < hi;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int src = 0; src < c.size; ++src) {
-      const uint4 v = ld_cg_u4(c.base[src] + x_off + i * 16);
-      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+    // every rank's copy is requested before the first one is used: a peer load takes microseconds, and a warp that adds
+    // as it goes has one of them in flight at a time
+    uint4 v[kMaxRanks];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        acc[2 * j] += bf16_lo(u[j]);
-        acc[2 * j + 1] += bf16_hi(u[j]);
+    for (int src = 0; src < kMaxRanks; ++src)
+      if (src < c.size) v[src] = ld_cg_u4(c.base[src] + x_off + i * 16);
+#pragma unroll
+    for (int src = 0; src < kMaxRanks; ++src) {
+      if (src < c.size) {
+        const uint32_t u[4] = {v[src].x, v[src].y, v[src].z, v[src].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          acc[2 * j] += bf16_lo(u[j]);
+          acc[2 * j + 1] += bf16_hi(u[j]);
+        }
       }
     }
     const long long m = i / chunks_per_row;
