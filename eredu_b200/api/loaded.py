@@ -147,6 +147,8 @@ class LoadedModel:
         device = torch.device(opt.device)
         dtype = opt.dtype or (torch.bfloat16 if device.type == "cuda" else torch.float32)
         moe_factory = None
+        if src.cfg.model_type == "deepseek_v4":
+            return cls._load_unpaged(path, src, opt, device, dtype)
         if src.cfg.is_moe:
             from ..models.moe import make_moe_factory
 
@@ -314,6 +316,11 @@ class LoadedModel:
 
         eng = self.engine
         seq = eng.new_sequence(list(prompt_ids), max_new_tokens=1)
+        if not getattr(eng, "paged", True):
+            try:
+                return eng.prefill_logits([seq])[0].float().cpu()
+            finally:
+                eng.release(seq)
         try:
             n = len(seq.prompt)
             p = np.arange(n)
@@ -529,6 +536,36 @@ class LoadedModel:
         if self.tokenizer is None:
             raise RuntimeError("this checkpoint has no tokenizer")
         return GrammarConstraint(self.tokenizer, kind, spec)
+
+    @classmethod
+    def _load_unpaged(cls, path, src, opt, device, dtype):
+        """Families whose cache is not a paged K / V pool run on ``runtime.unpaged.UnpagedEngine`` (text generation, chat,
+        logits; no batching, parallelism, residency tiers, prefix reuse or speculation)."""
+        from ..runtime.unpaged import UnpagedEngine
+
+        par = opt.parallel
+        if par is not None and par.tp_size * par.pp_size * par.ep_size > 1:
+            raise NotImplementedError(f"{src.cfg.model_type}: tensor / pipeline / expert parallelism is not built for this family")
+        if opt.weight_residency != "device" or opt.expert_cache or opt.prefix_cache:
+            raise NotImplementedError(f"{src.cfg.model_type}: weight residency tiers, expert caches and prefix reuse are not built for this family")
+        from ..models.deepseek_v4 import DeepseekV4Config, DeepseekV4Model
+
+        model = DeepseekV4Model(DeepseekV4Config.from_dict(src.cfg.extra["deepseek_v4"]), src.get, src.has, device, dtype)
+        model.par = None
+        engine = UnpagedEngine(model, max_batch=1, max_seq_len=opt.max_seq_len)
+        engine.cfg = src.cfg
+        tokenizer = None
+        try:
+            from ..text.tokenizer import load_tokenizer
+
+            tokenizer = load_tokenizer(path, src)
+        except Exception:
+            tokenizer = None
+        lm = cls(model, engine, src, tokenizer, Path(path))
+        lm.config = src.cfg
+        lm.mtp, lm.mtp_error = None, None
+        lm.vision = lm.audio = None
+        return lm
 
     def attach_assistant(self, path) -> None:
         """Load a Gemma 4 assistant drafter (its own directory) next to this model: speculative generation then drafts

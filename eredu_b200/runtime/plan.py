@@ -21,7 +21,7 @@ from ..models.config import DENSE_TYPES, MOE_TYPES, ModelConfig
 
 EXECUTION_PLAN_SCHEMA_VERSION = 2
 DEFAULT_MAX_MAPPED_SHARDS = 4
-SUPPORTED_TYPES = DENSE_TYPES | {"qwen3_moe", "mixtral", "gpt_oss", "lfm2_moe", "qwen3_next", "qwen3_5", "qwen3_5_text", "qwen3_5_moe", "qwen3_5_moe_text", "nemotron_h", "deepseek_v3", "kimi_linear", "gemma4"}
+SUPPORTED_TYPES = DENSE_TYPES | {"qwen3_moe", "mixtral", "gpt_oss", "lfm2_moe", "qwen3_next", "qwen3_5", "qwen3_5_text", "qwen3_5_moe", "qwen3_5_moe_text", "nemotron_h", "deepseek_v3", "deepseek_v4", "kimi_linear", "gemma4"}
 
 
 # ---------------------------------------------------------------------------------------------- inspection
@@ -74,6 +74,8 @@ def required_tensors(cfg: ModelConfig) -> list[tuple]:
     the final norm and the main input projection of the first layer's operator, under the family's own names."""
     if cfg.model_type in SPEECH_TYPES:
         return [(n,) for n in SPEECH_TYPES[cfg.model_type][1]]
+    if cfg.model_type == "deepseek_v4":
+        return [("embed.weight",), ("norm.weight",), ("layers.0.attn.wq_a.weight",), ("hc_head_fn",)]
     p = "model.layers.0."
     kind = cfg.layer_types[0] if cfg.layer_types else "full_attention"
     if cfg.model_type == "nemotron_h":
