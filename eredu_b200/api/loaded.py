@@ -147,7 +147,7 @@ class LoadedModel:
         device = torch.device(opt.device)
         dtype = opt.dtype or (torch.bfloat16 if device.type == "cuda" else torch.float32)
         moe_factory = None
-        if src.cfg.model_type == "deepseek_v4":
+        if src.cfg.model_type in ("deepseek_v4", "inkling_mm_model"):
             return cls._load_unpaged(path, src, opt, device, dtype)
         if src.cfg.is_moe:
             from ..models.moe import make_moe_factory
@@ -548,9 +548,14 @@ class LoadedModel:
             raise NotImplementedError(f"{src.cfg.model_type}: tensor / pipeline / expert parallelism is not built for this family")
         if opt.weight_residency != "device" or opt.expert_cache or opt.prefix_cache:
             raise NotImplementedError(f"{src.cfg.model_type}: weight residency tiers, expert caches and prefix reuse are not built for this family")
-        from ..models.deepseek_v4 import DeepseekV4Config, DeepseekV4Model
+        if src.cfg.model_type == "inkling_mm_model":
+            from ..models.inkling import InklingConfig, InklingModel
 
-        model = DeepseekV4Model(DeepseekV4Config.from_dict(src.cfg.extra["deepseek_v4"]), src.get, src.has, device, dtype)
+            model = InklingModel(InklingConfig.from_dict(src.cfg.extra["inkling"]), src.get, src.has, device, dtype)
+        else:
+            from ..models.deepseek_v4 import DeepseekV4Config, DeepseekV4Model
+
+            model = DeepseekV4Model(DeepseekV4Config.from_dict(src.cfg.extra["deepseek_v4"]), src.get, src.has, device, dtype)
         model.par = None
         engine = UnpagedEngine(model, max_batch=1, max_seq_len=opt.max_seq_len)
         engine.cfg = src.cfg

@@ -320,6 +320,10 @@ class ModelConfig:
             bos_token_id=d.get("bos_token_id"),
             torch_dtype=str(d.get("torch_dtype", d.get("dtype", "bfloat16"))),
         )
+        if mt == "inkling_mm_model":
+            # the family's own decoder reads the text fields from the raw dictionary (models/inkling.py)
+            cfg.extra["inkling"] = {k: v for k, v in d.items() if not k.startswith("_")}
+            cfg.num_experts = int(d.get("n_routed_experts") or 0)
         if mt == "deepseek_v4":
             # the family's own decoder reads its fields from the raw dictionary (models/deepseek_v4.py)
             cfg.extra["deepseek_v4"] = {k: v for k, v in d.items() if not k.startswith("_")}

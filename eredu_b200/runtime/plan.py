@@ -21,7 +21,7 @@ from ..models.config import DENSE_TYPES, MOE_TYPES, ModelConfig
 
 EXECUTION_PLAN_SCHEMA_VERSION = 2
 DEFAULT_MAX_MAPPED_SHARDS = 4
-SUPPORTED_TYPES = DENSE_TYPES | {"qwen3_moe", "mixtral", "gpt_oss", "lfm2_moe", "qwen3_next", "qwen3_5", "qwen3_5_text", "qwen3_5_moe", "qwen3_5_moe_text", "nemotron_h", "deepseek_v3", "deepseek_v4", "kimi_linear", "gemma4"}
+SUPPORTED_TYPES = DENSE_TYPES | {"qwen3_moe", "mixtral", "gpt_oss", "lfm2_moe", "qwen3_next", "qwen3_5", "qwen3_5_text", "qwen3_5_moe", "qwen3_5_moe_text", "nemotron_h", "deepseek_v3", "deepseek_v4", "inkling_mm_model", "kimi_linear", "gemma4"}
 
 
 # ---------------------------------------------------------------------------------------------- inspection
@@ -76,6 +76,9 @@ def required_tensors(cfg: ModelConfig) -> list[tuple]:
         return [(n,) for n in SPEECH_TYPES[cfg.model_type][1]]
     if cfg.model_type == "deepseek_v4":
         return [("embed.weight",), ("norm.weight",), ("layers.0.attn.wq_a.weight",), ("hc_head_fn",)]
+    if cfg.model_type == "inkling_mm_model":
+        return [("model.embed_tokens.weight", "model.llm.embed.weight"), ("model.norm.weight", "model.llm.norm.weight"),
+                ("model.layers.0.self_attn.r_proj.weight", "model.llm.layers.0.attn.wr_du.weight")]
     p = "model.layers.0."
     kind = cfg.layer_types[0] if cfg.layer_types else "full_attention"
     if cfg.model_type == "nemotron_h":
