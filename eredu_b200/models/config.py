@@ -255,7 +255,7 @@ class ModelConfig:
             mt = d.get("model_type", mt)
             # the language model of a vision-language checkpoint is its text family (text-only use of Qwen3-VL)
             mt = {"qwen3_vl_text": "qwen3", "qwen3_vl_moe_text": "qwen3_moe", "qwen3_vl": "qwen3", "qwen3_vl_moe": "qwen3_moe",
-                  "gemma4_text": "gemma4"}.get(mt, mt)
+                  "gemma4_text": "gemma4", "muse_glimmer_text": "muse_glimmer"}.get(mt, mt)
             d["model_type"] = mt
             d["_language_model_prefix"] = True
             d["_vision"] = {k: outer[k] for k in ("vision_config", "image_token_id", "video_token_id", "boi_token_id", "eoi_token_id", "vision_start_token_id",
@@ -320,6 +320,19 @@ class ModelConfig:
             bos_token_id=d.get("bos_token_id"),
             torch_dtype=str(d.get("torch_dtype", d.get("dtype", "bfloat16"))),
         )
+        if mt == "muse_glimmer":
+            # eredu/src/backend/mlx/architectures/muse_glimmer/mod.rs:197-243: the family's own fields travel as a dict
+            keys = ("post_norm_eps", "layer_types", "layer_rope_theta", "qk_scale_factor", "output_multiplier",
+                    "final_logit_softcapping", "num_experts", "moe_intermediate_size", "num_experts_per_tok", "norm_topk_prob")
+            for k in ("post_norm_eps", "layer_types", "layer_rope_theta", "qk_scale_factor", "output_multiplier", "final_logit_softcapping"):
+                if d.get(k) is None:
+                    raise ValueError(f"Muse-Glimmer text_config lacks {k}")
+            if float(d["final_logit_softcapping"]) <= 0:
+                raise ValueError("Muse-Glimmer final_logit_softcapping must be positive")
+            cfg.extra["muse_glimmer"] = {k: d.get(k) for k in keys}
+            cfg.sliding_window = d.get("sliding_window")
+            cfg.layer_types = list(d["layer_types"])
+            cfg.num_experts = 0
         if mt == "inkling_mm_model":
             # the family's own decoder reads the text fields from the raw dictionary (models/inkling.py)
             cfg.extra["inkling"] = {k: v for k, v in d.items() if not k.startswith("_")}

@@ -223,6 +223,10 @@ class CausalLM:
             from .gemma4 import block_forward as gemma4_block
 
             return gemma4_block(self, li, lw, h, batch, kv), None
+        if lw.block_kind == "muse_glimmer":
+            from .muse_glimmer import block_forward as muse_block
+
+            return muse_block(self, li, lw, h, batch, kv), None
         if lw.block_kind:
             from .nemotron_h import block_forward
 
@@ -316,6 +320,10 @@ class CausalLM:
         if batch.embed_rows is not None and self.par.owns_embedding():
             h = h.index_copy(0, batch.embed_rows, batch.embed_values.to(h.dtype))
             ssq = None                      # the embedding kernel's row sums no longer describe these rows
+        if getattr(self, "mg", None) is not None and self.par.owns_embedding() and batch.hidden_in is None:
+            from .muse_glimmer import _wrms
+
+            h, ssq = _wrms(h, self.cfg.rms_norm_eps).to(h.dtype), None      # Muse-Glimmer normalises the embedding
         if getattr(self, "g4", None) is not None:
             from .gemma4 import per_layer_inputs
 
@@ -366,6 +374,10 @@ class CausalLM:
         cap = (self.cfg.extra.get("gemma4") or {}).get("final_logit_softcapping")
         if cap:
             out = torch.tanh(out / float(cap)) * float(cap)
+        mg = self.cfg.extra.get("muse_glimmer")
+        if mg:
+            cap, mult = float(mg["final_logit_softcapping"]), float(mg["output_multiplier"])
+            out = torch.tanh(out * (mult / cap)) * cap
         return out
 
     def forward(self, batch: ForwardBatch, kv):
@@ -507,6 +519,11 @@ def build_from_tensors(cfg: ModelConfig, get: Callable[[str], torch.Tensor], has
         from .gemma4 import build as build_gemma4
 
         build_gemma4(model, cfg, get, has, up)
+        return model
+    if cfg.model_type == "muse_glimmer":
+        from .muse_glimmer import build as build_muse
+
+        build_muse(model, cfg, get, has, up)
         return model
     for li in range(model.first_layer, model.last_layer):
         p = f"model.layers.{li}."

@@ -1,0 +1,101 @@
+"""Muse-Glimmer text decoder (``model_type: muse_glimmer``; the decoder sits under ``model.language_model.*``).
+
+Behavioural counterpart of eredu/src/backend/mlx/architectures/muse_glimmer/mod.rs (dense text side):
+
+* the token embedding goes through a weight-free RMSNorm (mod.rs:1700-1702);
+* sandwich-normalised blocks: norms before AND after attention and feed-forward, the two "post" norms with their own
+  epsilon; the released checkpoints store ``scale - 1`` in the four block norms ("centered" weights, mod.rs:530-549), the
+  final norm stores its scale as is;
+* attention (mod.rs:864-905, 727-757): weight-free RMSNorm per head on queries and keys, queries times
+  ``qk_scale_factor``, scores times ``1 / sqrt(head_dim)``; rotary embedding only on the layers whose entry in
+  ``layer_rope_theta`` is non-zero; sliding-window layers by ``layer_types``; the attended values are multiplied by
+  ``sigmoid(gate_proj(x))`` before the output projection;
+* SwiGLU feed-forward; logits are ``softcap * tanh(logits * output_multiplier / softcap)`` (mod.rs:551-559).
+
+The key / value cache is an ordinary grouped-query cache, so the family runs on the paged engine (batching, prefix reuse,
+sampling kernels); the block itself is tensor operations around this repository's GEMMs over the paged pool, like the
+Gemma 4 block. Not built: the sparse (routed-expert) variant of the feed-forward, the vision tower and adapter, the
+DFlash / ATEM drafters, tensor parallelism for this family.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from .. import ops
+
+
+def _wrms(x, eps):
+    xf = x.float()
+    return xf * torch.rsqrt(xf.square().mean(-1, keepdim=True) + eps)
+
+
+def _rope(x, positions, inv_freq):
+    ang = positions.float()[:, None] * inv_freq[None, :]
+    cos, sin = torch.cat((ang.cos(), ang.cos()), -1)[:, None, :], torch.cat((ang.sin(), ang.sin()), -1)[:, None, :]
+    half = x.shape[-1] // 2
+    return x * cos + torch.cat((-x[..., half:], x[..., :half]), -1) * sin
+
+
+def build(model, cfg, get, has, up):
+    from .llama import LayerWeights
+    from .rope import rope_tables
+
+    g = cfg.extra["muse_glimmer"]
+    if model.par.tp_size > 1:
+        raise NotImplementedError("tensor parallelism is not built for Muse-Glimmer")
+    if int(g.get("num_experts") or 0) > 0:
+        raise NotImplementedError("the routed-expert variant of Muse-Glimmer is not built")
+    L = cfg.num_hidden_layers
+    thetas = list(g.get("layer_rope_theta") or [cfg.rope_theta] * L)
+    kinds = list(g.get("layer_types") or ["full_attention"] * L)
+    if len(thetas) != L or len(kinds) != L:
+        raise ValueError("Muse-Glimmer layer_rope_theta and layer_types must name every layer")
+    inv, _ = rope_tables(cfg)
+    model.mg = {"inv_freq": inv.to(model.device), "uses_rope": [float(t) != 0.0 for t in thetas],
+                "sliding": [k == "sliding_attention" for k in kinds], "post_eps": float(g.get("post_norm_eps") or cfg.rms_norm_eps),
+                "qk_scale": float(g.get("qk_scale_factor") or 1.0)}
+    for li in range(model.first_layer, model.last_layer):
+        p = f"model.layers.{li}."
+        f32 = lambda n: up(get(p + n), torch.float32)                                  # noqa: E731
+        w = {n: 1.0 + f32(n + ".weight") for n in ("input_layernorm", "post_attention_layernorm", "pre_feedforward_layernorm",
+                                                   "post_feedforward_layernorm")}       # stored centered: scale - 1
+        a = "self_attn."
+        for n in ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj"):
+            w[n] = up(get(p + a + n + ".weight"))
+            w[n + "_b"] = up(get(p + a + n + ".bias")) if has(p + a + n + ".bias") else None
+        w["gate_up"] = up(torch.cat((get(p + "mlp.gate_proj.weight"), get(p + "mlp.up_proj.weight")), 0))
+        w["down"] = up(get(p + "mlp.down_proj.weight"))
+        lw = LayerWeights(attn_norm=w["input_layernorm"], wqkv=None, wo=None, ffn_norm=None)
+        lw.block_kind = "muse_glimmer"
+        lw.extra = w
+        model.layers.append(lw)
+
+
+def block_forward(model, li, lw, h, batch, kv):
+    cfg, w, mg = model.cfg, lw.extra, model.mg
+    eps, dt = cfg.rms_norm_eps, h.dtype
+    M = h.shape[0]
+    Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    x = (_wrms(h, eps) * w["input_layernorm"]).to(dt)
+    q = _wrms(ops.linear(x, w["q_proj"], bias=w["q_proj_b"]).view(M, Hq, D), eps) * mg["qk_scale"]
+    k = _wrms(ops.linear(x, w["k_proj"], bias=w["k_proj_b"]).view(M, Hkv, D), eps)
+    v = ops.linear(x, w["v_proj"], bias=w["v_proj_b"]).view(M, Hkv, D)
+    if mg["uses_rope"][li]:
+        q, k = _rope(q, batch.positions, mg["inv_freq"]), _rope(k, batch.positions, mg["inv_freq"])
+    k_cache, v_cache = kv.layer(li)
+    ok = batch.slots >= 0
+    page, off = batch.slots[ok] // ops.PAGE, batch.slots[ok] % ops.PAGE
+    k_cache[page, :, off] = k[ok].to(k_cache.dtype)
+    v_cache[page, :, off] = v[ok].to(v_cache.dtype)
+    q_lens = (batch.cu_q[1:] - batch.cu_q[:-1]).tolist() if batch.is_prefill else [batch.q_per_seq] * batch.seq_lens.shape[0]
+    attn = ops.attention_ref(q.to(dt), k_cache, v_cache, batch.block_table, batch.seq_lens, q_lens, D ** -0.5,
+                             window=int(cfg.sliding_window or 0) if mg["sliding"][li] else 0)
+    gate = torch.sigmoid(ops.linear(x, w["gate_proj"], bias=w["gate_proj_b"]).float())
+    a = ops.linear((attn.reshape(M, Hq * D).float() * gate).to(dt), w["o_proj"], bias=w["o_proj_b"])
+    h = h + (_wrms(a, mg["post_eps"]) * w["post_attention_layernorm"]).to(dt)
+    y = (_wrms(h, eps) * w["pre_feedforward_layernorm"]).to(dt)
+    gu = ops.linear(y, w["gate_up"]).float()
+    inter = gu.shape[1] // 2
+    y = ops.linear((F.silu(gu[:, :inter]) * gu[:, inter:]).to(dt), w["down"])
+    return h + (_wrms(y, mg["post_eps"]) * w["post_feedforward_layernorm"]).to(dt)

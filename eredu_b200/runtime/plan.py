@@ -21,7 +21,7 @@ from ..models.config import DENSE_TYPES, MOE_TYPES, ModelConfig
 
 EXECUTION_PLAN_SCHEMA_VERSION = 2
 DEFAULT_MAX_MAPPED_SHARDS = 4
-SUPPORTED_TYPES = DENSE_TYPES | {"qwen3_moe", "mixtral", "gpt_oss", "lfm2_moe", "qwen3_next", "qwen3_5", "qwen3_5_text", "qwen3_5_moe", "qwen3_5_moe_text", "nemotron_h", "deepseek_v3", "deepseek_v4", "inkling_mm_model", "kimi_linear", "gemma4"}
+SUPPORTED_TYPES = DENSE_TYPES | {"qwen3_moe", "mixtral", "gpt_oss", "lfm2_moe", "qwen3_next", "qwen3_5", "qwen3_5_text", "qwen3_5_moe", "qwen3_5_moe_text", "nemotron_h", "deepseek_v3", "deepseek_v4", "inkling_mm_model", "muse_glimmer", "kimi_linear", "gemma4"}
 
 
 # ---------------------------------------------------------------------------------------------- inspection
