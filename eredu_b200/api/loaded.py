@@ -37,6 +37,9 @@ class ModelLoadOptions:
     max_seq_len: int = 4096
     kv_pages: Optional[int] = None
     prefix_cache: bool = False           # later requests lease the published KV pages of an equal prompt prefix
+    kv_host_tier_bytes: int = 0          # with prefix_cache: evicted published pages are kept in pinned host memory ...
+    kv_disk_tier_dir: Optional[str] = None   # ... and spilled to files in this directory when the host tier is full
+    kv_disk_tier_bytes: int = 0
     native_gguf: bool = True                     # keep Q4_K/Q6_K/... blocks and run the native kernels
     use_cuda_graph: Optional[bool] = None
     weight_residency: str = "device"             # "device" | "layerwise_host" | "dense_disk_stream"
@@ -220,7 +223,9 @@ class LoadedModel:
 
             tp.attach(model, opt.parallel)
         engine = Engine(model, max_batch=opt.max_batch, max_seq_len=opt.max_seq_len, num_pages=opt.kv_pages,
-                        use_cuda_graph=opt.use_cuda_graph, prefix_cache=opt.prefix_cache)
+                        use_cuda_graph=opt.use_cuda_graph, prefix_cache=opt.prefix_cache,
+                        kv_host_tier_bytes=opt.kv_host_tier_bytes, kv_disk_tier_dir=opt.kv_disk_tier_dir,
+                        kv_disk_tier_bytes=opt.kv_disk_tier_bytes)
         tokenizer = None
         try:
             from ..text.tokenizer import load_tokenizer

@@ -157,6 +157,21 @@ class BlockManager {
 
   int refcount(int64_t page) const { return refs_.at(page); }
 
+  // The page published under `hash` on the device, or -1.
+  int64_t lookup(uint64_t hash) const {
+    auto it = by_hash_.find(hash);
+    return it == by_hash_.end() ? -1 : it->second;
+  }
+
+  // (page, hash) of every published page that was evicted to satisfy an allocation since the last call. The page has
+  // a new owner already, but its old contents stay in device memory until that owner's first write: a lower tier
+  // copies them out before the next forward pass.
+  std::vector<std::pair<int64_t, uint64_t>> take_evicted() {
+    std::vector<std::pair<int64_t, uint64_t>> out;
+    out.swap(evicted_log_);
+    return out;
+  }
+
  private:
   void check(int64_t p) const {
     if (p <= 0 || p >= num_pages_) throw std::out_of_range("page id out of range");
@@ -169,6 +184,7 @@ class BlockManager {
       else if (lfu_ ? (uses_[p] < uses_[best] || (uses_[p] == uses_[best] && stamp_[p] < stamp_[best])) : stamp_[p] < stamp_[best]) best = p;
     }
     cached_.erase(best);
+    if (evicted_log_.size() < 65536) evicted_log_.emplace_back(best, hash_of_[best]);
     by_hash_.erase(hash_of_[best]);
     has_hash_[best] = false;
     uses_[best] = 0;
@@ -185,6 +201,7 @@ class BlockManager {
   std::vector<int64_t> free_;
   std::set<int64_t> cached_;
   std::unordered_map<uint64_t, int64_t> by_hash_;
+  std::vector<std::pair<int64_t, uint64_t>> evicted_log_;
   int64_t clock_ = 0;
 
  public:
@@ -456,6 +473,8 @@ void bind_runtime(py::module_& m) {
       .def("match_prefix", &BlockManager::match_prefix)
       .def("seal_prefix", &BlockManager::seal_prefix)
       .def("refcount", &BlockManager::refcount)
+      .def("lookup", &BlockManager::lookup)
+      .def("take_evicted", &BlockManager::take_evicted)
       .def_static("chain_hash", &BlockManager::chain_hash);
   py::class_<WorkItem>(m, "WorkItem")
       .def_readonly("work_id", &WorkItem::work_id)

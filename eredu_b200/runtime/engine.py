@@ -49,7 +49,7 @@ class Sequence:
 class Engine:
     def __init__(self, model: CausalLM, max_batch: int = 32, max_seq_len: int = 4096, num_pages: Optional[int] = None,
                  use_cuda_graph: Optional[bool] = None, prefill_chunk: int = 8192, hist_cap: int = 1024,
-                 prefix_cache: bool = False):
+                 prefix_cache: bool = False, kv_host_tier_bytes: int = 0, kv_disk_tier_dir=None, kv_disk_tier_bytes: int = 0):
         self.model = model
         self.cfg = model.cfg
         self.device = model.device
@@ -105,6 +105,14 @@ class Engine:
         self.prefix_cache = bool(prefix_cache and hasattr(self.kv.allocator, "match_prefix")
                                  and not self.kv.has_recurrent_state())
         self.prefix_stats = {"lookups": 0, "hits": 0, "hit_tokens": 0, "prompt_tokens": 0, "sealed_pages": 0}
+        # Lower tiers for published pages: evicted pages are demoted to pinned host memory and on to files, and promoted
+        # back when a prompt continues through them (runtime/block_tiers.py).
+        self.block_tiers = None
+        if self.prefix_cache and (kv_host_tier_bytes or (kv_disk_tier_dir and kv_disk_tier_bytes)) \
+                and hasattr(self.kv.allocator, "take_evicted"):
+            from .block_tiers import BlockTierStore
+
+            self.block_tiers = BlockTierStore(self.kv, kv_host_tier_bytes, kv_disk_tier_dir, kv_disk_tier_bytes)
         self._next_id = 0
         self._graphs: dict = {}
         self._decode_state = None
@@ -126,13 +134,18 @@ class Engine:
         if self.prefix_cache:
             # at least one prompt token is always prefilled: its logits choose the first output token
             usable = (len(seq.prompt) - 1) // PAGE * PAGE
-            leased = list(self.kv.allocator.match_prefix(seq.prompt[:usable])) if usable else []
+            if self.block_tiers is not None:
+                leased = self._lease_prefix_through_tiers(seq.prompt[:usable], need)
+            else:
+                leased = list(self.kv.allocator.match_prefix(seq.prompt[:usable])) if usable else []
             try:
                 seq.pages = leased + list(self.kv.allocator.alloc(need - len(leased)))
             except RuntimeError:
                 if leased:
                     self.kv.allocator.release(leased)
                 raise
+            if self.block_tiers is not None:
+                self.block_tiers.demote(self.kv.allocator.take_evicted())
             seq.kv_len = seq.cached_tokens = len(leased) * PAGE
             st = self.prefix_stats
             st["lookups"] += 1
@@ -149,6 +162,40 @@ class Engine:
                 seq.pages = []
                 raise
         return seq
+
+    def _lease_prefix_through_tiers(self, tokens, need: int) -> list:
+        """The longest prefix of ``tokens`` (whole pages) that is published on the device or held in a lower tier: device
+        pages are leased as they are, tier blocks get a fresh device page, are copied into it and published again."""
+        al, tiers = self.kv.allocator, self.block_tiers
+        plan, h = [], 0
+        for i in range(0, len(tokens) // PAGE * PAGE, PAGE):
+            h = al.chain_hash(h, [int(t) for t in tokens[i:i + PAGE]])
+            page = al.lookup(h)
+            if page >= 0:
+                al.retain([page])                     # leased now, so that the allocations below cannot evict it
+                plan.append((h, page, None))
+            elif tiers.where(h) is not None:
+                plan.append((h, -1, tiers.where(h)))
+            else:
+                break
+        pages, promote = [], []
+        try:
+            for h, page, tier in plan:
+                if tier is not None:
+                    if al.free_pages() <= need - len(plan):     # the pool cannot take promoted blocks and the rest of the request
+                        break
+                    page = al.alloc(1)[0]
+                    promote.append((h, page))
+                pages.append(page)
+        finally:
+            tail = [p for _, p, t in plan[len(pages):] if t is None]
+            if tail:
+                al.release(tail)                      # device hits behind a block that could not be promoted
+        tiers.demote(al.take_evicted())               # copy evicted pages out before anything is copied in
+        tiers.promote(promote)
+        for h, page in promote:
+            al.seal(page, h)
+        return pages
 
     def publish_pages(self, seq: Sequence) -> None:
         """Publish the full pages below ``kv_len`` (prompt and committed output) for reuse by later requests."""
