@@ -14,8 +14,8 @@ Behavioural counterpart of eredu/src/backend/mlx/architectures/muse_glimmer/mod.
 
 The key / value cache is an ordinary grouped-query cache, so the family runs on the paged engine (batching, prefix reuse,
 sampling kernels); the block itself is tensor operations around this repository's GEMMs over the paged pool, like the
-Gemma 4 block. Not built: the sparse (routed-expert) variant of the feed-forward, the vision tower and adapter, the
-DFlash / ATEM drafters, tensor parallelism for this family.
+Gemma 4 block. The routed-expert variant of the feed-forward (softmax top-k over fused expert banks) runs as a loop over the
+chosen experts. Not built: the vision tower and adapter, the DFlash / ATEM drafters, tensor parallelism for this family.
 """
 from __future__ import annotations
 
@@ -44,8 +44,7 @@ def build(model, cfg, get, has, up):
     g = cfg.extra["muse_glimmer"]
     if model.par.tp_size > 1:
         raise NotImplementedError("tensor parallelism is not built for Muse-Glimmer")
-    if int(g.get("num_experts") or 0) > 0:
-        raise NotImplementedError("the routed-expert variant of Muse-Glimmer is not built")
+    sparse = int(g.get("num_experts") or 0) > 0
     L = cfg.num_hidden_layers
     thetas = list(g.get("layer_rope_theta") or [cfg.rope_theta] * L)
     kinds = list(g.get("layer_types") or ["full_attention"] * L)
@@ -64,8 +63,14 @@ def build(model, cfg, get, has, up):
         for n in ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj"):
             w[n] = up(get(p + a + n + ".weight"))
             w[n + "_b"] = up(get(p + a + n + ".bias")) if has(p + a + n + ".bias") else None
-        w["gate_up"] = up(torch.cat((get(p + "mlp.gate_proj.weight"), get(p + "mlp.up_proj.weight")), 0))
-        w["down"] = up(get(p + "mlp.down_proj.weight"))
+        if sparse:
+            # Qwen3-style routed experts (mod.rs:932-1040): softmax over all experts, top-k, optional renormalisation;
+            # fused banks [E, 2 I, H] hold the gate rows first
+            w["router"] = f32("mlp.gate.weight")
+            w["egu"], w["edn"] = up(get(p + "mlp.experts.gate_up_proj")), up(get(p + "mlp.experts.down_proj"))
+        else:
+            w["gate_up"] = up(torch.cat((get(p + "mlp.gate_proj.weight"), get(p + "mlp.up_proj.weight")), 0))
+            w["down"] = up(get(p + "mlp.down_proj.weight"))
         lw = LayerWeights(attn_norm=w["input_layernorm"], wqkv=None, wo=None, ffn_norm=None)
         lw.block_kind = "muse_glimmer"
         lw.extra = w
@@ -95,7 +100,21 @@ def block_forward(model, li, lw, h, batch, kv):
     a = ops.linear((attn.reshape(M, Hq * D).float() * gate).to(dt), w["o_proj"], bias=w["o_proj_b"])
     h = h + (_wrms(a, mg["post_eps"]) * w["post_attention_layernorm"]).to(dt)
     y = (_wrms(h, eps) * w["pre_feedforward_layernorm"]).to(dt)
-    gu = ops.linear(y, w["gate_up"]).float()
-    inter = gu.shape[1] // 2
-    y = ops.linear((F.silu(gu[:, :inter]) * gu[:, inter:]).to(dt), w["down"])
+    if "router" in w:
+        g = cfg.extra["muse_glimmer"]
+        probs = torch.softmax(y.float() @ w["router"].t(), -1)
+        top_w, top_i = torch.topk(probs, int(g["num_experts_per_tok"]), dim=-1)
+        if g.get("norm_topk_prob"):
+            top_w = top_w / top_w.sum(-1, keepdim=True)
+        out = torch.zeros((M, cfg.hidden_size), dtype=torch.float32, device=h.device)
+        for e in top_i.unique().tolist():
+            rows, slot = (top_i == e).nonzero(as_tuple=True)
+            eu = ops.linear(y[rows], w["egu"][e]).float()
+            ie = eu.shape[1] // 2
+            out.index_add_(0, rows, ops.linear((F.silu(eu[:, :ie]) * eu[:, ie:]).to(dt), w["edn"][e]).float() * top_w[rows, slot, None])
+        y = out.to(dt)
+    else:
+        gu = ops.linear(y, w["gate_up"]).float()
+        inter = gu.shape[1] // 2
+        y = ops.linear((F.silu(gu[:, :inter]) * gu[:, inter:]).to(dt), w["down"])
     return h + (_wrms(y, mg["post_eps"]) * w["post_feedforward_layernorm"]).to(dt)

@@ -70,7 +70,20 @@ def dense_reference(sd, tokens):
         a = att @ sd[p + "self_attn.o_proj.weight"].t()
         h = h + wrms(a, 1e-5) * (1 + sd[p + "post_attention_layernorm.weight"])
         y = wrms(h, 1e-6) * (1 + sd[p + "pre_feedforward_layernorm.weight"])
-        y = (torch.nn.functional.silu(y @ sd[p + "mlp.gate_proj.weight"].t()) * (y @ sd[p + "mlp.up_proj.weight"].t())) @ sd[p + "mlp.down_proj.weight"].t()
+        if p + "mlp.gate.weight" in sd:                  # routed experts: softmax over all, top-2, renormalised
+            probs = torch.softmax(y @ sd[p + "mlp.gate.weight"].t(), -1)
+            tw, ti = torch.topk(probs, 2)
+            tw = tw / tw.sum(-1, keepdim=True)
+            mix = torch.zeros_like(y)
+            for t in range(T):
+                for j in range(2):
+                    e = int(ti[t, j])
+                    u = y[t] @ sd[p + "mlp.experts.gate_up_proj"][e].t()
+                    half = u.shape[0] // 2
+                    mix[t] += (torch.nn.functional.silu(u[:half]) * u[half:]) @ sd[p + "mlp.experts.down_proj"][e].t() * tw[t, j]
+            y = mix
+        else:
+            y = (torch.nn.functional.silu(y @ sd[p + "mlp.gate_proj.weight"].t()) * (y @ sd[p + "mlp.up_proj.weight"].t())) @ sd[p + "mlp.down_proj.weight"].t()
         h = h + wrms(y, 1e-5) * (1 + sd[p + "post_feedforward_layernorm.weight"])
     h = wrms(h, 1e-6) * sd[root + "norm.weight"]                          # the final norm stores its scale as is
     logits = h @ sd["lm_head.weight"].t()
@@ -113,11 +126,36 @@ def test_matches_the_dense_restatement_and_the_engine_invariants(tmp_path):
     assert both[0][0] == int(want[6].argmax())                   # the first prompt is a prefix of the reference sequence
 
 
+def test_routed_expert_variant_against_a_restatement(tmp_path):
+    sd = state()
+    g = torch.Generator().manual_seed(9)
+    E, I, H = 6, 32, 64
+    root = "model.language_model."
+    for li in range(4):
+        p = f"{root}layers.{li}.mlp."
+        for n in ("gate_proj", "up_proj", "down_proj"):
+            del sd[p + n + ".weight"]
+        sd[p + "gate.weight"] = torch.randn(E, H, generator=g) * 0.5
+        sd[p + "experts.gate_up_proj"] = torch.randn(E, 2 * I, H, generator=g) * 0.2
+        sd[p + "experts.down_proj"] = torch.randn(E, H, I, generator=g) * 0.2
+    text = dict(TEXT, num_experts=E, num_experts_per_tok=2, moe_intermediate_size=I, norm_topk_prob=True, num_hidden_layers=4)
+    save(tmp_path, sd, text)
+    lm = LoadedModel.load(tmp_path, ModelLoadOptions(device="cpu", max_batch=1, max_seq_len=48))
+    tokens = list(range(5, 30))
+    want = dense_reference(sd, tokens)
+    full = lm.prefill_logits(tokens)
+    assert float((full - want[-1]).abs().max()) < 2e-4
+    seq = lm.engine.new_sequence(tokens[:11], max_new_tokens=20)
+    lm.engine.prefill_logits([seq])
+    row = None
+    for t in tokens[11:]:
+        row = lm.engine.step_logits(seq, t)
+    lm.engine.release(seq)
+    assert float((row.float() - want[-1]).abs().max()) < 2e-4
+
+
 def test_variants_that_are_not_built_say_so(tmp_path):
     sd = state()
-    save(tmp_path, sd, dict(TEXT, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=32))
-    with pytest.raises(NotImplementedError, match="routed-expert"):
-        LoadedModel.load(tmp_path, ModelLoadOptions(device="cpu", max_batch=1, max_seq_len=32))
     bad = {k: v for k, v in TEXT.items() if k != "qk_scale_factor"}
     (tmp_path / "config.json").write_text(json.dumps({"model_type": "muse_glimmer", "text_config": bad}))
     from eredu_b200.runtime.plan import inspect_artifact
