@@ -274,9 +274,6 @@ class QuantLinear:
         dev = x.device
         if self._gemv_ok(x) and (out is None or out.stride(1) == 1):
             return self._gemv(x, bias, residual, out, out_dtype, False)
-        if (self.DENSE_FALLBACK_TOKENS < M <= self.TENSOR_CORE_FP8_MAX_TOKENS and self.TENSOR_CORE_FP8
-                and self.block_scales is not None):
-            return self.tensor_core(x, bias=bias, residual=residual, out=out, out_dtype=out_dtype)
         if M > self.DENSE_FALLBACK_TOKENS:
             w = torch.empty((N, K), dtype=torch.bfloat16, device=dev)
             check(lib().eredu_dequant_affine(ptr(self.wq), ptr(self.scales_t), ptr(self.biases_t), ptr(w), N, K,

@@ -162,8 +162,10 @@ def test_dense_and_quantised_wrappers_dry_run(dry_cuda):
         q(torch.randn(300, 256).to(bf))                      # whole-matrix dequant + dense GEMM
     f8 = Fp8Linear.from_dense(w.float())
     f8(x, residual=torch.zeros(8, 384, dtype=bf))
-    f8(torch.randn(300, 256).to(bf), out_dtype=torch.float32)
-    assert {"eredu_qgemm", "eredu_dequant_affine", "eredu_qgemm_fp8", "eredu_dequant_fp8"} <= set(dry_cuda.calls)
+    f8(torch.randn(300, 256).to(bf), out_dtype=torch.float32)        # 256 < tokens <= 1024: the FP8 tensor-core kernel
+    f8(torch.randn(1100, 256).to(bf))                                # beyond: decode the weight once, bf16 GEMM
+    assert {"eredu_qgemm", "eredu_dequant_affine", "eredu_qgemm_fp8", "eredu_dequant_fp8", "eredu_fp8_quant_act",
+            "eredu_gemm_fp8_tc"} <= set(dry_cuda.calls)
 
 
 def test_moe_and_conv_wrappers_dry_run(dry_cuda):

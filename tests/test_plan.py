@@ -23,7 +23,7 @@ def test_inspection_reports(tmp_path):
     g = P.inspect_artifact(tmp_path / "m.gguf")
     assert g.is_loadable and g.format == "gguf" and g.parameter_count == rep.parameter_count
     # unsupported family and missing tensors are errors, found without touching a payload
-    bad = dataclasses.replace(cfg, model_type="muse_glimmer")
+    bad = dataclasses.replace(cfg, model_type="some_future_family")
     ck.save_safetensors_checkpoint(tmp_path / "bad", bad, {k: v for k, v in sd.items() if "embed_tokens" not in k}, torch.float32)
     b = P.inspect_artifact(tmp_path / "bad")
     assert not b.is_loadable and {"unsupported_architecture", "missing_tensor"} <= {i.code for i in b.issues}
