@@ -272,6 +272,38 @@ def main():
             tp.attach(model, par, max_tokens=256, backend="nccl" if not gpu else "peer")
         runner = PipelineRunner(model, par, max_batch=4, max_seq_len=128, transport="peer" if "peer" in scenario else "nccl")
         result["tokens"] = runner.generate(prompts, sp, max_new_tokens=10)
+        if "pcache" in scenario:
+            # every stage persists the K/V of its own layers under its rank directory and resumes from them
+            from eredu_b200.runtime import prompt_cache as PC
+
+            eng = runner.engine
+            long_prompt = prompts[1]
+            cut = 32
+            cache_dir = os.path.join(os.path.dirname(out_path), "pcache")
+
+            def run(seq, n):
+                first = eng.prefill([seq])
+                eng.start_decode([seq], first)
+                out = [int(first[0])]
+                for _ in range(n - 1):
+                    toks = eng.decode_step()
+                    eng.commit(toks)
+                    out.append(int(toks[0]))
+                eng._decode_state = None
+                return out
+
+            s1 = eng.new_sequence(long_prompt[:cut], sp, max_new_tokens=2)
+            eng.prefill([s1])
+            d = PC.save_prompt_cache(eng, s1, cache_dir, "ckpt", block_tokens=16)
+            eng.release(s1)
+            dist.barrier()
+            man = PC.open_prompt_cache(cache_dir, PC.PromptCacheTopology.of(par))
+            result["pcache_layers"] = sorted({b.global_layer for b in man.blocks})
+            result["pcache_dir"] = os.path.basename(str(d))
+            s2 = PC.load_prompt_cache(eng, cache_dir, long_prompt, "ckpt", sp, max_new_tokens=10)
+            result["pcache_cached"] = s2.kv_len
+            result["pcache_tokens"] = run(s2, 10)
+            eng.release(s2)
         if "peer" in scenario:
             from eredu_b200.ops import native
 

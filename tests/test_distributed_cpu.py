@@ -37,6 +37,20 @@ def test_pipeline_parallel_matches_single_rank(scenario, world, tmp_path):
         assert r["tokens"] == want
 
 
+def test_prompt_cache_under_pipeline_parallelism(tmp_path):
+    """Each stage writes the K/V of its own layers under its own rank directory; a later request resumes from the
+    saved prefix on both stages and generates the tokens of an uncached run."""
+    res = run_ranks("cpu_pp_pcache", 2, tmp_path)
+    want = _oracle(10)
+    for rank, r in enumerate(res):
+        assert r["tokens"] == want
+        assert r["pcache_cached"] == 32 and r["pcache_tokens"] == want[1]
+        assert r["pcache_dir"] == f"rank-pp{rank}-tp0-ep0"
+    layers = [set(r["pcache_layers"]) for r in res]
+    assert layers[0] and layers[1] and not layers[0] & layers[1]              # every layer on exactly one stage
+    assert layers[0] | layers[1] == {0, 1}
+
+
 @pytest.mark.parametrize("world", [2, 4])
 def test_expert_parallel_over_tensor_ranks_matches_single_rank(world, tmp_path):
     """Attention tensor-parallel + experts expert-parallel on the same ranks (replicated tokens, partial expert
