@@ -259,7 +259,13 @@ def main():
         from eredu_b200.parallel.pipeline import PipelineRunner
 
         tp_size = 2 if "tp2" in scenario else 1
-        par = ParallelContext.from_env(ParallelTopology(pipeline=world // tp_size, tensor=tp_size))
+        axes = {}
+        if "moe" in scenario:      # three axes: pipeline stages x tensor ranks, experts spread over the tensor ranks
+            cfg = moe_cfg(gpu)
+            sd = random_state(cfg, seed=0, std=0.08)
+            if tp_size > 1:
+                axes = {"expert": tp_size, "expert_over_tensor": True}
+        par = ParallelContext.from_env(ParallelTopology(pipeline=world // tp_size, tensor=tp_size, **axes))
         factory = None
         if cfg.is_moe:
             from eredu_b200.models.moe import make_moe_factory

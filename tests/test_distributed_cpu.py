@@ -37,6 +37,23 @@ def test_pipeline_parallel_matches_single_rank(scenario, world, tmp_path):
         assert r["tokens"] == want
 
 
+@pytest.mark.parametrize("scenario,world", [("cpu_pp_moe", 2), ("cpu_pp_tp2_moe", 4)])
+def test_pipeline_with_expert_and_tensor_axes(scenario, world, tmp_path):
+    """A sparse model over pipeline stages, and over pipeline x tensor ranks with the experts spread over the tensor
+    ranks of every stage (three axes on four ranks): tokens equal the single-rank model's."""
+    from eredu_b200.models.moe import make_moe_factory
+
+    res = run_ranks(scenario, world, tmp_path)
+    cfg = moe_cfg(False)
+    sd = random_state(cfg, seed=0, std=0.08)
+    model = build_from_tensors(cfg, sd.__getitem__, sd.__contains__, "cpu", torch.float32, moe_factory=make_moe_factory())
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 33)]
+    want = Engine(model, max_batch=4, max_seq_len=128).generate(prompts, SamplingParams(temperature=0.0), 10)
+    for r in res:
+        assert r["tokens"] == want
+
+
 def test_prompt_cache_under_pipeline_parallelism(tmp_path):
     """Each stage writes the K/V of its own layers under its own rank directory; a later request resumes from the
     saved prefix on both stages and generates the tokens of an uncached run."""
