@@ -21,8 +21,17 @@ Tensor names: the canonical ``model.layers.N.self_attn.*`` spelling or the relea
 (architectures/inkling/checkpoint.rs:35-330). Fused ``gate_up`` banks hold the gate rows first.
 
 The per-layer state (keys, values and four convolution tails) is kept per sequence; the family runs on
-``runtime.unpaged.UnpagedEngine``. Not built: the hMLP vision ingress and the audio codebook embedder (requests with media
-are refused), the prediction layers, tensor / expert parallelism, GGUF checkpoints of this family.
+``runtime.unpaged.UnpagedEngine``.
+
+Media ingress (model.rs:2808-3243, processor.rs:237-284): images are cut into 40 x 40 patches (row-major, one extra column,
+missing pixels at raw value -1, CLIP normalisation, each patch doubled in time) and every patch becomes ONE soft token
+through the hMLP tower - four linear layers that fold 5 x 5, 2 x 2, 4 x 4 pixel neighbourhoods and finally the two time
+steps into the channel dimension, RMSNorm + GELU between them, an RMSNorm at the end; audio arrives as frames of
+``num_codebooks`` discrete ids, a frame's soft token is the RMSNorm of the sum of its codebook embeddings. Soft tokens
+replace the (normalised) embeddings at the image / audio placeholder ids.
+
+Not built: the dMel audio front end (waveform to codebook ids), the prediction layers, tensor / expert parallelism, GGUF
+checkpoints of this family.
 """
 from __future__ import annotations
 
@@ -293,11 +302,16 @@ class InklingModel:
 
     # ------------------------------------------------------------------ forward
     @torch.no_grad()
-    def forward(self, token_ids, cache: InklingCache, all_rows: bool = False):
+    def forward(self, token_ids, cache: InklingCache, all_rows: bool = False, embeds=None):
+        """``embeds``: (rows, values) from :func:`splice_media` - soft tokens that take the place of the normalised
+        embeddings at those rows of this call."""
         cfg = self.cfg
         token_ids = torch.as_tensor(token_ids, device=self.device)
         offset = cache.length
         h = _rms(self.embed[token_ids.long()].to(self.dtype), self.embed_norm, cfg.rms_norm_eps)
+        if embeds is not None:
+            rows, values = embeds
+            h = h.index_copy(0, rows.to(self.device), values.to(device=self.device, dtype=self.dtype))
         for w, lc in zip(self.layers, cache.layers):
             a = self._attention(w, _rms(h, w["in_norm"], cfg.rms_norm_eps), lc, offset)
             a, lc.conv[2] = w["attn_sconv"](a, lc.conv[2])
@@ -313,3 +327,115 @@ class InklingModel:
         if cfg.unpadded_vocab_size and cfg.unpadded_vocab_size < logits.shape[-1]:
             logits = logits[:, :cfg.unpadded_vocab_size]
         return logits if all_rows else logits[0]
+
+
+# ---------------------------------------------------------------------------------------------- media ingress
+IMAGE_MEAN = (0.48145466, 0.4578275, 0.40821073)
+IMAGE_STD = (0.26862954, 0.2613026, 0.2757771)
+
+
+def image_patches(image: torch.Tensor) -> torch.Tensor:
+    """``image`` uint8 / float [H, W, 3] with raw 0..255 values -> [rows * cols, 2, 40, 40, 3]: ``ceil(H / 40)`` rows and
+    ``W // 40 + 1`` columns of patches (the released processor keeps a final partial or empty column), pixels beyond the
+    image at raw value -1, normalised, both time steps equal."""
+    H, W, C = image.shape
+    if C != 3:
+        raise ValueError("Inkling images are RGB")
+    rows, cols = (H + 39) // 40, W // 40 + 1
+    canvas = torch.full((rows * 40, cols * 40, 3), -1.0, dtype=torch.float32)
+    canvas[:H, :W] = image.float()
+    canvas = (canvas / 255.0 - torch.tensor(IMAGE_MEAN)) / torch.tensor(IMAGE_STD)
+    p = canvas.view(rows, 40, cols, 40, 3).permute(0, 2, 1, 3, 4).reshape(rows * cols, 1, 40, 40, 3)
+    return p.expand(-1, 2, -1, -1, -1).contiguous()
+
+
+class InklingVision:
+    """The hMLP tower: ``[P, 2, 40, 40, 3]`` patches -> ``[P, hidden]`` soft tokens."""
+
+    def __init__(self, vcfg: dict, get, has, device="cpu", dtype=torch.float32):
+        H = int(vcfg.get("text_hidden_size", vcfg.get("decoder_dmodel")))
+        geometry = (int(vcfg.get("temporal_patch_size", 2)), int(vcfg.get("patch_size", 40)),
+                    int(vcfg.get("num_hidden_layers", vcfg.get("n_layers", 4))), int(vcfg.get("num_channels", vcfg.get("n_channels", 3))))
+        if geometry != (2, 40, 4, 3) or vcfg.get("vision_encoder_type", "hmlp") != "hmlp":
+            raise ValueError(f"the hMLP tower supports (temporal 2, patch 40, 4 layers, 3 channels), got {geometry}")
+        second = 320 if H == 4096 else 512
+        self.specs = [(75, 128, 1, 5), (512, second, 1, 2), (second * 16, 4800, 1, 4), (9600, H, 2, 1)]
+        self.eps = float(vcfg.get("rms_norm_eps", 1e-6))
+        self.device, self.dtype = torch.device(device), dtype
+        up = lambda t, dt=None: t.to(device=self.device, dtype=dt or dtype).contiguous()          # noqa: E731
+        pick = lambda a, b: get(a) if has(a) else get(b)                                            # noqa: E731
+        self.layers = []
+        for i, (din, dout, _, _) in enumerate(self.specs):
+            w = up(pick(f"visual.layers.{i}.projection.weight", f"model.visual.layers.linear_{i}.weight"))
+            if tuple(w.shape) != (dout, din):
+                raise ValueError(f"hMLP layer {i} has shape {tuple(w.shape)}, expected {(dout, din)}")
+            norm = up(pick(f"visual.layers.{i}.layer_norm.weight", f"model.visual.layers.norm_{i}.weight"), torch.float32) \
+                if i + 1 < len(self.specs) else None
+            self.layers.append((w, norm))
+        self.final_norm = up(pick("visual.final_norm.weight", "model.visual.final_norm.weight"), torch.float32)
+
+    @staticmethod
+    def _fold(x, t_fold, hw_fold):
+        P, T, Hh, Ww, C = x.shape
+        if T % t_fold or Hh % hw_fold or Ww % hw_fold:
+            raise ValueError(f"fold ({t_fold}, {hw_fold}) does not divide {tuple(x.shape)}")
+        x = x.reshape(P, T // t_fold, t_fold, Hh // hw_fold, hw_fold, Ww // hw_fold, hw_fold, C)
+        return x.permute(0, 1, 3, 5, 2, 4, 6, 7).reshape(P, T // t_fold, Hh // hw_fold, Ww // hw_fold, t_fold * hw_fold * hw_fold * C)
+
+    @torch.no_grad()
+    def __call__(self, patches: torch.Tensor) -> torch.Tensor:
+        if patches.dim() != 5 or tuple(patches.shape[1:]) != (2, 40, 40, 3):
+            raise ValueError(f"image patches must be [patches, 2, 40, 40, 3], got {tuple(patches.shape)}")
+        x = patches.to(self.device, self.dtype)
+        for (w, norm), (_, _, tf, hf) in zip(self.layers, self.specs):
+            x = self._fold(x, tf, hf)
+            lead = x.shape[:-1]
+            x = ops.linear(x.reshape(-1, x.shape[-1]).contiguous(), w).view(*lead, w.shape[0])
+            if norm is not None:
+                x = F.gelu(_rms(x, norm, self.eps).float()).to(self.dtype)
+        return _rms(x, self.final_norm, self.eps).reshape(-1, x.shape[-1])
+
+
+class InklingAudio:
+    """Frames of codebook ids ``[frames, codebooks]`` -> ``[frames, hidden]``: summed codebook embeddings, RMS-normalised."""
+
+    def __init__(self, acfg: dict, get, has, device="cpu", dtype=torch.float32):
+        self.codebooks = int(acfg.get("num_codebooks", acfg.get("n_mel_bins")))
+        self.size = int(acfg.get("codebook_size", acfg.get("mel_vocab_size")))
+        self.eps = float(acfg.get("rms_norm_eps", 1e-6))
+        self.device, self.dtype = torch.device(device), dtype
+        pick = lambda a, b: get(a) if has(a) else get(b)                                            # noqa: E731
+        self.table = pick("audio.encoder.weight", "model.audio.encoder.weight").to(device=self.device, dtype=dtype)
+        if self.table.shape[0] != self.codebooks * self.size:
+            raise ValueError("the audio embedding table does not match the codebook geometry")
+        self.final_norm = pick("audio.final_norm.weight", "model.audio.final_norm.weight").to(device=self.device, dtype=torch.float32)
+
+    @torch.no_grad()
+    def __call__(self, ids: torch.Tensor, valid_frames=None) -> torch.Tensor:
+        if ids.dim() != 2 or ids.shape[1] != self.codebooks:
+            raise ValueError(f"audio ids must be [frames, {self.codebooks}], got {tuple(ids.shape)}")
+        ids = ids.to(self.device).long()
+        if int(ids.min()) < 0 or int(ids.max()) >= self.size:
+            raise ValueError("audio id outside its codebook")
+        offs = torch.arange(self.codebooks, device=self.device) * self.size
+        x = self.table[ids + offs[None, :]].float().sum(1)
+        x = _rms(x.to(self.dtype), self.final_norm, self.eps)
+        return x if valid_frames is None else x[:int(valid_frames)]
+
+
+def splice_media(token_ids, image_token_id: int, audio_token_id: int, image_embeds=(), audio_embeds=()):
+    """Rows of ``token_ids`` that hold placeholder ids and the soft tokens that replace them, in order of appearance.
+    Returns (rows int64 [n], values [n, hidden]) for ``InklingModel.forward(..., embeds=)``."""
+    ids = torch.as_tensor(token_ids)
+    rows, vals = [], []
+    for tid, parts, name in ((image_token_id, image_embeds, "image"), (audio_token_id, audio_embeds, "audio")):
+        where = (ids == tid).nonzero(as_tuple=True)[0]
+        have = sum(int(p.shape[0]) for p in parts)
+        if where.numel() != have:
+            raise ValueError(f"{where.numel()} {name} placeholder tokens for {have} {name} soft tokens")
+        if have:
+            rows.append(where)
+            vals.append(torch.cat([p for p in parts]))
+    if not rows:
+        return None
+    return torch.cat(rows), torch.cat(vals)

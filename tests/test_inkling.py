@@ -229,3 +229,80 @@ def test_config_validation():
         InklingConfig.from_dict(ink_cfg(q_bias=True))
     cfg = InklingConfig.from_dict(ink_cfg(layer_types=None, local_layer_ids=[0, 2], dense_mlp_idx=None, mlp_layer_types=["dense", "moe", "moe"]))
     assert cfg.local_layers == [True, False, True] and cfg.dense_layers == [True, False, False]
+
+
+def _tower_state(H=40, second=512, seed=7):
+    g = torch.Generator().manual_seed(seed)
+    r = lambda *s, std=0.05: torch.randn(*s, generator=g) * std         # noqa: E731
+    specs = [(75, 128), (512, second), (second * 16, 4800), (9600, H)]
+    sd = {}
+    for i, (din, dout) in enumerate(specs):
+        sd[f"model.visual.layers.linear_{i}.weight"] = r(dout, din)
+        if i < 3:
+            sd[f"model.visual.layers.norm_{i}.weight"] = 1 + r(dout, std=0.1)
+    sd["model.visual.final_norm.weight"] = 1 + r(H, std=0.1)
+    sd["audio.encoder.weight"] = r(4 * 9, H, std=1.0)
+    sd["audio.final_norm.weight"] = 1 + r(H, std=0.1)
+    return sd
+
+
+def test_image_patches_follow_the_released_grid():
+    from eredu_b200.models.inkling import IMAGE_MEAN, IMAGE_STD, image_patches
+
+    img = torch.randint(0, 256, (50, 80, 3), generator=torch.Generator().manual_seed(1), dtype=torch.uint8)
+    p = image_patches(img)
+    assert p.shape == (2 * 3, 2, 40, 40, 3)                       # ceil(50 / 40) rows, 80 // 40 + 1 columns
+    assert torch.equal(p[:, 0], p[:, 1])
+    want = (float(img[45, 47, 1]) / 255 - IMAGE_MEAN[1]) / IMAGE_STD[1]
+    assert abs(float(p[3 + 1, 0, 5, 7, 1]) - want) < 1e-6          # patch (row 1, col 1), pixel (5, 7)
+    pad = (-1.0 / 255 - IMAGE_MEAN[0]) / IMAGE_STD[0]
+    assert abs(float(p[2, 0, 0, 0, 0]) - pad) < 1e-6              # the extra column lies wholly outside the image
+
+
+def test_hmlp_tower_against_a_restatement_and_the_splice():
+    from eredu_b200.models.inkling import InklingAudio, InklingVision, image_patches, splice_media
+
+    sd = _tower_state()
+    vis = InklingVision({"text_hidden_size": 40, "patch_size": 40, "temporal_patch_size": 2, "num_channels": 3, "num_hidden_layers": 4},
+                        sd.__getitem__, sd.__contains__)
+    patches = image_patches(torch.randint(0, 256, (40, 39, 3), generator=torch.Generator().manual_seed(2), dtype=torch.uint8))
+    out = vis(patches)
+    assert out.shape == (1, 40)
+    # restatement for the one patch: explicit neighbourhood gathers instead of reshapes
+    rms = lambda z, w: z * torch.rsqrt(z.square().mean(-1, keepdim=True) + 1e-6) * w       # noqa: E731
+    x = patches[0]                                                  # [2, 40, 40, 3]
+    l0 = torch.zeros(2, 8, 8, 128)
+    for t in range(2):
+        for i in range(8):
+            for j in range(8):
+                l0[t, i, j] = sd["model.visual.layers.linear_0.weight"] @ x[t, 5 * i:5 * i + 5, 5 * j:5 * j + 5].reshape(-1)
+    l0 = torch.nn.functional.gelu(rms(l0, sd["model.visual.layers.norm_0.weight"]))
+    l1 = torch.zeros(2, 4, 4, 512)
+    for t in range(2):
+        for i in range(4):
+            for j in range(4):
+                l1[t, i, j] = sd["model.visual.layers.linear_1.weight"] @ l0[t, 2 * i:2 * i + 2, 2 * j:2 * j + 2].reshape(-1)
+    l1 = torch.nn.functional.gelu(rms(l1, sd["model.visual.layers.norm_1.weight"]))
+    l2 = torch.stack([sd["model.visual.layers.linear_2.weight"] @ l1[t].reshape(-1) for t in range(2)])
+    l2 = torch.nn.functional.gelu(rms(l2, sd["model.visual.layers.norm_2.weight"]))
+    l3 = sd["model.visual.layers.linear_3.weight"] @ l2.reshape(-1)
+    want = rms(l3, sd["model.visual.final_norm.weight"])
+    assert torch.allclose(out[0], want, atol=1e-4)
+    # audio: the sum of one embedding per codebook, normalised
+    aud = InklingAudio({"num_codebooks": 4, "codebook_size": 9}, sd.__getitem__, sd.__contains__)
+    ids = torch.tensor([[0, 8, 3, 5], [2, 2, 2, 2], [1, 0, 7, 4]])
+    a = aud(ids, valid_frames=2)
+    e = sd["audio.encoder.weight"]
+    assert a.shape == (2, 40) and torch.allclose(a[1], rms(e[2] + e[9 + 2] + e[18 + 2] + e[27 + 2], sd["audio.final_norm.weight"]), atol=1e-5)
+    with pytest.raises(ValueError, match="codebook"):
+        aud(torch.tensor([[0, 9, 0, 0]]))
+    # soft tokens take the place of the placeholder rows, and only those
+    model, _ = build()
+    toks = [5, 6, 80, 7, 81, 81, 9]
+    emb = splice_media(toks, 80, 81, [out], [a])
+    assert emb[0].tolist() == [2, 4, 5]
+    base = model.forward(toks, model.new_cache(), all_rows=True)
+    with_media = model.forward(toks, model.new_cache(), all_rows=True, embeds=emb)
+    assert torch.allclose(base[:2], with_media[:2]) and not torch.allclose(base[2:], with_media[2:])
+    with pytest.raises(ValueError, match="placeholder"):
+        splice_media(toks, 80, 81, [out, out], [a])
