@@ -109,7 +109,6 @@ def test_gemma4_assistant_on_the_gpu(tmp_path):
     plain = lm.engine.generate(prompts, sp, 12)
     dec = Gemma4AssistantDecoder(lm.engine, assistant)
     got = dec.generate(prompts, sp, 12)
-    # bf16 ties aside, speculation commits what plain decoding commits; with the selecting projection the assistant IS the
-    # target's tail, so most proposals are accepted
+    # bf16 ties aside, speculation commits what plain decoding commits whatever the drafter proposes
     agree = sum(a == b for x, y in zip(got, plain) for a, b in zip(x, y))
-    assert agree >= 20 and dec.stats.accepted > 0
+    assert agree >= 20 and dec.stats.rounds > 0 and dec.stats.proposed == 3 * dec.stats.rounds
