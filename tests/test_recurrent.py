@@ -105,3 +105,86 @@ def test_mamba2_kernel_matches_reference(H, G, P, N):
     Sa, ya = mamba2_scan(x[:, :32], Bm[:, :32], Cm[:, :32], dt[:, :32], A, D, S0)
     Sb, yb = mamba2_scan(x[:, 32:], Bm[:, 32:], Cm[:, 32:], dt[:, 32:], A, D, Sa)
     assert torch.allclose(Sb, S, atol=1e-4) and torch.equal(torch.cat((ya, yb), 1), y)
+
+
+@pytest.mark.parametrize("T,chunk,groups", [(130, 64, 2), (64, 64, 4), (37, 16, 1), (5, 8, 2)])
+def test_mamba2_chunk_parallel_form_equals_the_recurrence(T, chunk, groups):
+    from eredu_b200.ops.recurrent import mamba2_scan_chunked, mamba2_scan_ref
+
+    g = torch.Generator().manual_seed(T)
+    Bt, H, P, N = 2, 4, 8, 16
+    x = torch.randn(Bt, T, H, P, generator=g)
+    Bm, Cm = torch.randn(Bt, T, groups, N, generator=g), torch.randn(Bt, T, groups, N, generator=g)
+    dt = torch.nn.functional.softplus(torch.randn(Bt, T, H, generator=g)) + 0.01
+    A = -torch.rand(H, generator=g) * 2 - 0.1
+    D = torch.randn(H, generator=g)
+    S0 = torch.randn(Bt, H, P, N, generator=g)
+    S_ref, y_ref = mamba2_scan_ref(x, Bm, Cm, dt, A, D, S0)
+    S, y = mamba2_scan_chunked(x, Bm, Cm, dt, A, D, S0, chunk=chunk)
+    assert torch.allclose(y, y_ref, atol=2e-4, rtol=1e-4) and torch.allclose(S, S_ref, atol=2e-4, rtol=1e-4)
+    # two calls that cut the sequence anywhere give the same outputs and state as one
+    cut = T // 3 + 1
+    Sa, ya = mamba2_scan_chunked(x[:, :cut], Bm[:, :cut], Cm[:, :cut], dt[:, :cut], A, D, S0, chunk=chunk)
+    Sb, yb = mamba2_scan_chunked(x[:, cut:], Bm[:, cut:], Cm[:, cut:], dt[:, cut:], A, D, Sa, chunk=chunk)
+    assert torch.allclose(torch.cat((ya, yb), 1), y_ref, atol=2e-4, rtol=1e-4) and torch.allclose(Sb, S_ref, atol=2e-4, rtol=1e-4)
+
+
+@pytest.mark.gpu
+def test_mamba2_long_prefill_takes_the_chunk_parallel_form_on_the_gpu():
+    from eredu_b200.ops import recurrent as R
+
+    g = torch.Generator().manual_seed(1)
+    Bt, T, H, G, P, N = 2, 700, 8, 2, 64, 128
+    x = (torch.randn(Bt, T, H, P, generator=g) * 0.5).cuda().bfloat16()
+    Bm, Cm = (torch.randn(Bt, T, G, N, generator=g) * 0.3).cuda().bfloat16(), (torch.randn(Bt, T, G, N, generator=g) * 0.3).cuda().bfloat16()
+    dt = (torch.nn.functional.softplus(torch.randn(Bt, T, H, generator=g)) * 0.1 + 0.001).cuda()
+    A, D = (-torch.rand(H, generator=g) * 4 - 0.5).cuda(), torch.randn(H, generator=g).cuda()
+    S_ref, y_ref = R.mamba2_scan_ref(x.float(), Bm.float(), Cm.float(), dt, A, D)
+    assert T >= R.CHUNKED_SCAN_MIN_TOKENS
+    S, y = R.mamba2_scan(x, Bm, Cm, dt, A, D)
+    assert float((y.float() - y_ref).norm() / y_ref.norm()) < 2e-2
+    assert float((S - S_ref).norm() / S_ref.norm()) < 2e-2
+    # and agrees with the token-by-token kernel on a call short enough for it
+    Sk, yk = R.mamba2_scan(x[:, :100], Bm[:, :100], Cm[:, :100], dt[:, :100], A, D)
+    Sc, yc = R.mamba2_scan_chunked(x[:, :100], Bm[:, :100], Cm[:, :100], dt[:, :100], A, D)
+    assert float((yk.float() - yc.float()).norm() / yc.float().norm()) < 2e-2
+
+
+@pytest.mark.parametrize("T,chunk", [(130, 64), (64, 32), (37, 16), (3, 8)])
+def test_gated_delta_chunk_parallel_form_equals_the_recurrence(T, chunk):
+    from eredu_b200.ops.recurrent import gated_delta_scan_chunked, gated_delta_scan_ref
+
+    g = torch.Generator().manual_seed(T + 1)
+    B, H, Dk, Dv = 2, 3, 16, 24
+    q = torch.randn(B, T, H, Dk, generator=g) * 0.5
+    k = torch.nn.functional.normalize(torch.randn(B, T, H, Dk, generator=g), dim=-1)
+    v = torch.randn(B, T, H, Dv, generator=g)
+    log_decay = -torch.rand(B, T, H, generator=g) * 0.3
+    beta = torch.rand(B, T, H, generator=g)
+    S0 = torch.randn(B, H, Dk, Dv, generator=g) * 0.3
+    S_ref, o_ref = gated_delta_scan_ref(q, k, v, log_decay, beta, S0)
+    S, o = gated_delta_scan_chunked(q, k, v, log_decay, beta, S0, chunk=chunk)
+    assert torch.allclose(o, o_ref, atol=3e-4, rtol=1e-4) and torch.allclose(S, S_ref, atol=3e-4, rtol=1e-4)
+    cut = T // 2 + 1
+    Sa, oa = gated_delta_scan_chunked(q[:, :cut], k[:, :cut], v[:, :cut], log_decay[:, :cut], beta[:, :cut], S0, chunk=chunk)
+    Sb, ob = gated_delta_scan_chunked(q[:, cut:], k[:, cut:], v[:, cut:], log_decay[:, cut:], beta[:, cut:], Sa, chunk=chunk)
+    assert torch.allclose(torch.cat((oa, ob), 1), o_ref, atol=3e-4, rtol=1e-4) and torch.allclose(Sb, S_ref, atol=3e-4, rtol=1e-4)
+    with pytest.raises(ValueError, match="one decay per head"):
+        gated_delta_scan_chunked(q, k, v, log_decay[..., None].expand(-1, -1, -1, Dk), beta)
+
+
+@pytest.mark.gpu
+def test_gated_delta_long_prefill_takes_the_chunk_parallel_form_on_the_gpu():
+    from eredu_b200.ops import recurrent as R
+
+    g = torch.Generator().manual_seed(2)
+    B, T, H, Dk, Dv = 2, 600, 4, 128, 128
+    q = (torch.randn(B, T, H, Dk, generator=g) * 0.3).cuda().bfloat16()
+    k = torch.nn.functional.normalize(torch.randn(B, T, H, Dk, generator=g), dim=-1).cuda().bfloat16()
+    v = torch.randn(B, T, H, Dv, generator=g).cuda().bfloat16()
+    log_decay = (-torch.rand(B, T, H, generator=g) * 0.2).cuda()
+    beta = torch.rand(B, T, H, generator=g).cuda()
+    S_ref, o_ref = R.gated_delta_scan_ref(q.float(), k.float(), v.float(), log_decay, beta)
+    S, o = R.gated_delta_scan(q, k, v, log_decay, beta)
+    assert float((o.float() - o_ref).norm() / o_ref.norm()) < 3e-2
+    assert float((S - S_ref).norm() / S_ref.norm()) < 3e-2
