@@ -48,8 +48,8 @@ def main():
         Sk, ok = R.gated_delta_scan(q, k, v, ld, beta)
         us_kernel = _time(lambda: R.gated_delta_scan(q, k, v, ld, beta))
         R.CHUNKED_SCAN_MIN_TOKENS = keep
-        Sc, oc = R.gated_delta_scan(q, k, v, ld, beta)
-        us_chunk = _time(lambda: R.gated_delta_scan(q, k, v, ld, beta))
+        Sc, oc = R.gated_delta_scan_chunked(q, k, v, ld, beta)
+        us_chunk = _time(lambda: R.gated_delta_scan_chunked(q, k, v, ld, beta))
         print(json.dumps({"op": "gated_delta", "tokens": T, "heads": H, "kernel_us": round(us_kernel, 1), "chunked_us": round(us_chunk, 1),
                           "speedup": round(us_kernel / us_chunk, 2),
                           "rel_diff": float((ok.float() - oc.float()).norm() / ok.float().norm())}), flush=True)
@@ -62,8 +62,8 @@ def main():
         Sk, yk = R.mamba2_scan(x, Bm, Cm, dt, A, D)
         us_kernel = _time(lambda: R.mamba2_scan(x, Bm, Cm, dt, A, D))
         R.CHUNKED_SCAN_MIN_TOKENS = keep
-        Sc, yc = R.mamba2_scan(x, Bm, Cm, dt, A, D)
-        us_chunk = _time(lambda: R.mamba2_scan(x, Bm, Cm, dt, A, D))
+        Sc, yc = R.mamba2_scan_chunked(x, Bm, Cm, dt, A, D)
+        us_chunk = _time(lambda: R.mamba2_scan_chunked(x, Bm, Cm, dt, A, D))
         print(json.dumps({"op": "mamba2", "tokens": T, "heads": H, "kernel_us": round(us_kernel, 1), "chunked_us": round(us_chunk, 1),
                           "speedup": round(us_kernel / us_chunk, 2),
                           "rel_diff": float((yk.float() - yc.float()).norm() / yk.float().norm())}), flush=True)
