@@ -19,8 +19,8 @@
 // prefixes work); key tiles beyond a query tile's last position are never loaded. CTAs with the most key tiles are
 // scheduled first.
 //
-// Same online-softmax recurrence and semantics as attn_prefill_kernel in attention.cu (which keeps serving sliding
-// windows, sinks and head size 64) and as the reference's blockwise attention (eredu/src/backend/mlx/nn/attention.rs:346-436,
+// Head size 64 or 128, optional sliding window (key tiles before the window are skipped) and sink logits. Same
+// online-softmax recurrence and semantics as attn_prefill_kernel in attention.cu and as the reference's blockwise attention (eredu/src/backend/mlx/nn/attention.rs:346-436,
 // runtime/cache/kv.rs:2267-2436). Every wait is bounded; on expiry the status word is set and the CTA leaves through the
 // common exit (TMEM is freed there).
 #include <cuda_bf16.h>
@@ -38,8 +38,10 @@ struct AttnTcParams {
   const int* block_table;      // [batch, max_pages]
   const int* seq_lens;         // kv length after this call, per sequence
   const int* cu_q;             // [batch + 1] query-row offsets
+  const float* sinks;          // optional [n_q_heads]: logit of a virtual key with zero value (enters the normaliser only)
   int max_pages;
   int n_q_heads, n_kv_heads;
+  int window;                  // 0: none; else a query at position p sees keys in (p - window, p]
   float scale_log2;
   int* status;
 };
@@ -47,10 +49,9 @@ struct AttnTcParams {
 constexpr int kTcThreads = 320;
 constexpr int kTcTile = 128;            // query rows per tile and keys per tile
 constexpr int kTcRows = 2 * kTcTile;    // query rows per CTA
-constexpr int kTcD = 128;
 constexpr int kTcHalf = 128 * 64 * 2;   // one [128 rows][64 bf16] swizzled half tile: 16 KB
-// shared memory: Q_a, Q_b (2 halves each) | K ring (2 x 2 halves) | V ring (2 x 2 halves) | barriers
-constexpr int kTcSmem = 1024 + 4 * kTcHalf + 4 * kTcHalf + 4 * kTcHalf + 256;
+// shared memory: Q_a, Q_b (D / 64 halves each) | K ring (2 x D / 64 halves) | V ring (2 x D / 64 halves) | barriers
+constexpr int tc_smem(int d) { return 1024 + 3 * 2 * (d / 64) * kTcHalf + 256; }
 constexpr float kTcRescale = 8.f;       // log2 units a row maximum may outgrow the scale in use
 
 // MN-major operand tile stored as [k rows][64 bf16] (128-byte rows, 128B swizzle): 64-element blocks along MN are `lbo`
@@ -65,7 +66,6 @@ __device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint3
   return d;
 }
 constexpr uint32_t kIdescQK = umma_idesc_bf16(128, 128);                 // both operands K-major
-constexpr uint32_t kIdescPV = umma_idesc_bf16(128, 128) | (1u << 16);    // B (= V) MN-major
 
 __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, int x, int y, int z, int w, uint64_t* bar) {
   asm volatile(
@@ -75,15 +75,18 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+template <int D>
 __global__ void __launch_bounds__(kTcThreads, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                        const __grid_constant__ CUtensorMap tmV, const AttnTcParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint8_t* q_s = smem;                                                 // tile w at + w * 2 halves
-  uint8_t* k_s = q_s + 4 * kTcHalf;                                    // stage s at + s * 2 halves
-  uint8_t* v_s = k_s + 4 * kTcHalf;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + 4 * kTcHalf);
+  constexpr int NH = D / 64;                                           // 64-wide halves of the head dimension
+  constexpr uint32_t kIdescPV = umma_idesc_bf16(128, D) | (1u << 16);  // B (= V) MN-major, N = head dimension
+  uint8_t* q_s = smem;                                                 // tile w at + w * NH halves
+  uint8_t* k_s = q_s + 2 * NH * kTcHalf;                               // stage s at + s * NH halves
+  uint8_t* v_s = k_s + 2 * NH * kTcHalf;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + 2 * NH * kTcHalf);
   uint64_t* q_full = bars;                  // 1
   uint64_t* k_full = bars + 1;              // [2]
   uint64_t* k_empty = bars + 3;             // [2]
@@ -108,6 +111,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   const int n_a = min(kv_len - 1, pos0 + kTcTile - 1) / kTcTile + 1;
   const int n_b = row0 + kTcTile < q_len ? min(kv_len - 1, pos0 + kTcRows - 1) / kTcTile + 1 : 0;
   const int n_tiles = max(n_a, n_b);
+  // sliding window: key tiles that lie wholly before the window of a tile's FIRST row are skipped
+  const int j0_a = p.window > 0 ? max(0, pos0 - p.window + 1) / kTcTile : 0;
+  const int j0_b = p.window > 0 ? max(0, pos0 + kTcTile - p.window + 1) / kTcTile : 0;
+  const int j0 = n_b > 0 ? min(j0_a, j0_b) : j0_a;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -141,96 +148,103 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      mbar_arrive_expect_tx(q_full, 4 * kTcHalf);
+      mbar_arrive_expect_tx(q_full, 2 * NH * kTcHalf);
       for (int w = 0; w < 2; ++w)
-        for (int h = 0; h < 2; ++h)
-          tma_load_3d(q_s + (w * 2 + h) * kTcHalf, &tmQ, h * 64, head, q0 + row0 + w * kTcTile, q_full);
+        for (int h = 0; h < NH; ++h)
+          tma_load_3d(q_s + (w * NH + h) * kTcHalf, &tmQ, h * 64, head, q0 + row0 + w * kTcTile, q_full);
       const int* pages = p.block_table + static_cast<size_t>(b) * p.max_pages;
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int s = j & 1;
-        const uint32_t reuse_parity = ((j >> 1) - 1) & 1;
+      for (int jj = 0; j0 + jj < n_tiles && ok; ++jj) {
+        const int j = j0 + jj;                                           // key tile; jj counts this CTA's iterations
+        const int s = jj & 1;
+        const uint32_t reuse_parity = ((jj >> 1) - 1) & 1;
         int page[8];
 #pragma unroll
         for (int pg = 0; pg < 8; ++pg) {
           const int page_index = j * 8 + pg;
           page[pg] = page_index < p.max_pages ? pages[page_index] : 0;            // beyond the table: the reserved page (masked)
         }
-        if (j >= 2) ok = mbar_wait(&k_empty[s], reuse_parity, p.status, kStatusSmemEmptyTimeout);
+        if (jj >= 2) ok = mbar_wait(&k_empty[s], reuse_parity, p.status, kStatusSmemEmptyTimeout);
         if (!ok) break;
-        mbar_arrive_expect_tx(&k_full[s], 2 * kTcHalf);
+        mbar_arrive_expect_tx(&k_full[s], NH * kTcHalf);
 #pragma unroll
         for (int pg = 0; pg < 8; ++pg)
-          for (int h = 0; h < 2; ++h) tma_load_4d(k_s + (s * 2 + h) * kTcHalf + pg * 2048, &tmK, h * 64, 0, kv_head, page[pg], &k_full[s]);
-        if (j >= 2) ok = mbar_wait(&v_empty[s], reuse_parity, p.status, kStatusSmemEmptyTimeout);
+          for (int h = 0; h < NH; ++h) tma_load_4d(k_s + (s * NH + h) * kTcHalf + pg * 2048, &tmK, h * 64, 0, kv_head, page[pg], &k_full[s]);
+        if (jj >= 2) ok = mbar_wait(&v_empty[s], reuse_parity, p.status, kStatusSmemEmptyTimeout);
         if (!ok) break;
-        mbar_arrive_expect_tx(&v_full[s], 2 * kTcHalf);
+        mbar_arrive_expect_tx(&v_full[s], NH * kTcHalf);
 #pragma unroll
         for (int pg = 0; pg < 8; ++pg)
-          for (int h = 0; h < 2; ++h) tma_load_4d(v_s + (s * 2 + h) * kTcHalf + pg * 2048, &tmV, h * 64, 0, kv_head, page[pg], &v_full[s]);
+          for (int h = 0; h < NH; ++h) tma_load_4d(v_s + (s * NH + h) * kTcHalf + pg * 2048, &tmV, h * 64, 0, kv_head, page[pg], &v_full[s]);
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       const uint32_t q_addr = smem_u32(q_s);
-      auto issue_s = [&](int w, int j) {
-        const uint32_t qa = q_addr + w * 2 * kTcHalf;
-        const uint32_t ka = smem_u32(k_s + (j & 1) * 2 * kTcHalf);
+      // jj: this CTA's iteration (selects the K / V stage); tile w is active on key tiles [first_w, n_w)
+      const int first[2] = {j0_a, j0_b}, last[2] = {n_a, n_b};
+      auto issue_s = [&](int w, int jj) {
+        const uint32_t qa = q_addr + w * NH * kTcHalf;
+        const uint32_t ka = smem_u32(k_s + (jj & 1) * NH * kTcHalf);
         const uint32_t d = tmem + w * 128;
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {           // K = head dimension: four 16-steps per 64-wide half
+        for (int kk = 0; kk < D / 16; ++kk) {      // K = head dimension: four 16-steps per 64-wide half
           const uint32_t off = (kk >> 2) * kTcHalf + (kk & 3) * 32;
           umma_f16(d, umma_desc_k_sw128(qa + off), umma_desc_k_sw128(ka + off), kIdescQK, kk > 0 ? 1u : 0u);
         }
         umma_commit(&s_full[w]);
       };
-      auto issue_pv = [&](int w, int j) {
-        const uint32_t va = smem_u32(v_s + (j & 1) * 2 * kTcHalf);
+      auto issue_pv = [&](int w, int jj, bool fresh) {
+        const uint32_t va = smem_u32(v_s + (jj & 1) * NH * kTcHalf);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)             // K = keys: P from tensor memory (8 columns per step), V MN-major (2048 bytes per step)
           umma_f16_ts(tmem + 256 + w * 128, tmem + w * 128 + kk * 8, umma_desc_mn_sw128(va + kk * 2048, kTcHalf), kIdescPV,
-                      (j > 0 || kk > 0) ? 1u : 0u);
+                      (!fresh || kk > 0) ? 1u : 0u);
       };
+      auto active = [&](int w, int j) { return j >= first[w] && j < last[w]; };
       ok = mbar_wait(q_full, 0, p.status, kStatusTmaFullTimeout);
       if (ok) ok = mbar_wait(&k_full[0], 0, p.status, kStatusTmaFullTimeout);
       if (ok) {
         tc_fence_after_sync();
-        issue_s(0, 0);
-        if (n_b > 0) issue_s(1, 0);
+        if (active(0, j0)) issue_s(0, 0);
+        if (active(1, j0)) issue_s(1, 0);
         umma_commit(&k_empty[0]);
       }
-      for (int j = 0; j < n_tiles && ok; ++j) {
+      int done[2] = {0, 0};                        // softmax rounds completed per tile: parity of p_full
+      for (int jj = 0; j0 + jj < n_tiles && ok; ++jj) {
+        const int j = j0 + jj;
         const bool next = j + 1 < n_tiles;
         bool k_ready = false;
-        ok = mbar_wait(&v_full[j & 1], (j >> 1) & 1, p.status, kStatusTmaFullTimeout);
+        ok = mbar_wait(&v_full[jj & 1], (jj >> 1) & 1, p.status, kStatusTmaFullTimeout);
         for (int w = 0; w < 2 && ok; ++w) {
-          const int n_w = w == 0 ? n_a : n_b;
-          if (j < n_w) {
-            ok = mbar_wait(&p_full[w], j & 1, p.status, kStatusAccumTimeout);     // P_w(j) is in tensor memory, O_w is rescaled
+          if (active(w, j)) {
+            ok = mbar_wait(&p_full[w], done[w] & 1, p.status, kStatusAccumTimeout);   // P_w(j) is in tensor memory, O_w is rescaled
             if (!ok) break;
             tc_fence_after_sync();
-            issue_pv(w, j);
+            issue_pv(w, jj, done[w] == 0);
+            ++done[w];
           }
-          if (w == 1) umma_commit(&v_empty[j & 1]);
-          if (j + 1 < n_w) {
+          if (w == 1) umma_commit(&v_empty[jj & 1]);
+          if (active(w, j + 1)) {
             if (!k_ready) {
-              ok = mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, p.status, kStatusTmaFullTimeout);
+              ok = mbar_wait(&k_full[(jj + 1) & 1], ((jj + 1) >> 1) & 1, p.status, kStatusTmaFullTimeout);
               if (!ok) break;
               tc_fence_after_sync();
               k_ready = true;
             }
-            issue_s(w, j + 1);
-          } else if (j + 1 == n_w) {
+            issue_s(w, jj + 1);
+          } else if (j + 1 == last[w]) {
             umma_commit(&o_final[w]);
           }
         }
-        if (ok && next) umma_commit(&k_empty[(j + 1) & 1]);
+        if (ok && next) umma_commit(&k_empty[(jj + 1) & 1]);
       }
     }
   } else {
     // ------------------------------------------------------------------ softmax, one row per thread
     const int w = (warp - 2) >> 2;                                       // query tile of this warp
     const int n_w = w == 0 ? n_a : n_b;
+    const int j0_w = w == 0 ? j0_a : j0_b;
     const int quarter = warp & 3;                                        // TMEM lanes this warp may touch
     const int row = quarter * 32 + lane;
     const int tile_row0 = row0 + w * kTcTile;
@@ -240,8 +254,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     const uint32_t s_addr = tmem + lane_addr + w * 128;
     const uint32_t o_addr = tmem + lane_addr + 256 + w * 128;
     float m = 0.f, l = 0.f;
-    for (int j = 0; j < n_w && ok; ++j) {
-      ok = mbar_wait(&s_full[w], j & 1, p.status, kStatusAccumTimeout);
+    for (int j = j0_w; j < n_w && ok; ++j) {
+      const int it = j - j0_w;                                           // this tile's round: parity of its barriers
+      ok = mbar_wait(&s_full[w], it & 1, p.status, kStatusAccumTimeout);
       if (!ok) break;
       tc_fence_after_sync();
       uint32_t sc[8][16];
@@ -249,13 +264,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       for (int c = 0; c < 8; ++c) tmem_ld16(s_addr + c * 16, sc[c]);
       tmem_wait_ld();
       const int key0 = j * kTcTile;
-      if (key0 + kTcTile - 1 > tile_pos0 || key0 + kTcTile > kv_len) {   // some (row, key) of the tile is masked: -inf gives p = 0
-        const int visible = min(qpos, kv_len - 1) - key0;                // keys 0..visible of this tile are seen by this row
+      const bool before = p.window > 0 && key0 <= tile_pos0 + kTcTile - 1 - p.window;     // some row's window starts inside or after this tile
+      if (key0 + kTcTile - 1 > tile_pos0 || key0 + kTcTile > kv_len || before) {   // some (row, key) of the tile is masked: -inf gives p = 0
+        const int visible = min(qpos, kv_len - 1) - key0;                // keys hidden .. visible of this tile are seen by this row
+        const int hidden = p.window > 0 ? qpos - p.window + 1 - key0 : 0;
 #pragma unroll
         for (int c = 0; c < 8; ++c)
 #pragma unroll
           for (int i = 0; i < 16; ++i)
-            if (c * 16 + i > visible) sc[c][i] = 0xFF800000u;
+            if (c * 16 + i > visible || c * 16 + i < hidden) sc[c][i] = 0xFF800000u;
       }
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains of three-input maxima
 #pragma unroll
@@ -264,7 +281,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         for (int i = 0; i < 16; i += 2) mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], __uint_as_float(sc[c][i]), __uint_as_float(sc[c][i + 1]));
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_new = mx * p.scale_log2;                             // -inf for a fully masked row: every comparison below is false
-      if (j == 0) {
+      if (it == 0) {
         m = m_new == -INFINITY ? 0.f : m_new;
       } else {
         const bool grow = m_new > m + kTcRescale;
@@ -311,10 +328,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     if (ok && n_w > 0) {
       tc_fence_after_sync();
       const bool store = tile_row0 + row < q_len;
+      if (p.sinks != nullptr) l += ex2_approx(p.sinks[head] * 1.4426950408889634f - m);
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(q0 + tile_row0 + row) * p.n_q_heads + head) * kTcD);
+      uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(q0 + tile_row0 + row) * p.n_q_heads + head) * D);
 #pragma unroll 1
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < D / 16; ++c) {
         uint32_t r[16];
         tmem_ld16(o_addr + c * 16, r);
         tmem_wait_ld();
@@ -345,44 +363,54 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 
 using namespace eredu;
 
-// Causal prefill attention over the paged cache, head size 128, no sliding window, no sinks. q: [tokens, n_q, 128] bf16
-// (contiguous); k_cache / v_cache: [pages, n_kv, 16, 128] bf16 (contiguous). Same arguments as eredu_attn_prefill
-// otherwise. Returns -2 for shapes it does not take.
+// Causal prefill attention over the paged cache, head size 64 or 128, optional sliding window and sink logits.
+// q: [tokens, n_q, D] bf16 (contiguous); k_cache / v_cache: [pages, n_kv, 16, D] bf16 (contiguous); sinks: fp32 [n_q] or
+// null. Same arguments as eredu_attn_prefill otherwise. Returns -2 for shapes it does not take.
+template <int D>
+static int launch_attn_tc(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnTcParams& p, dim3 grid,
+                          cudaStream_t stream) {
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (cudaFuncSetAttribute(attn_prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc_smem(D)) != cudaSuccess) return -1;
+    configured[dev] = true;
+  }
+  return static_cast<int>(launch_pdl(attn_prefill_tc_kernel<D>, grid, dim3(kTcThreads), tc_smem(D), stream, tmQ, tmK, tmV, p));
+}
+
 extern "C" int eredu_attn_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
-                                     const int* seq_lens, const int* cu_q, int batch, int total_q, int max_q_len, int max_pages,
-                                     int num_pages, int n_q_heads, int n_kv_heads, int head_dim, float scale, int* status,
-                                     cudaStream_t stream) {
-  if (head_dim != 128 || batch <= 0 || total_q <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads != 0) return -2;
+                                     const int* seq_lens, const int* cu_q, const float* sinks, int batch, int total_q, int max_q_len,
+                                     int max_pages, int num_pages, int n_q_heads, int n_kv_heads, int head_dim, int window, float scale,
+                                     int* status, cudaStream_t stream) {
+  if ((head_dim != 128 && head_dim != 64) || batch <= 0 || total_q <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads != 0 || window < 0)
+    return -2;
+  const uint64_t D = static_cast<uint64_t>(head_dim);
   CUtensorMap tmQ, tmK, tmV;
-  // q as [tokens][heads][128]: box = 128 tokens x 1 head x 64 values
-  int r = make_tma_3d(&tmQ, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 128, static_cast<uint64_t>(n_q_heads),
-                      static_cast<uint64_t>(total_q), 128 * 2, static_cast<uint64_t>(n_q_heads) * 128 * 2, 64, 1, 128);
+  // q as [tokens][heads][D]: box = 128 tokens x 1 head x 64 values
+  int r = make_tma_3d(&tmQ, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, D, static_cast<uint64_t>(n_q_heads),
+                      static_cast<uint64_t>(total_q), D * 2, static_cast<uint64_t>(n_q_heads) * D * 2, 64, 1, 128);
   if (r != 0) return -100 + r;
-  r = make_tma_4d(&tmK, k_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 128, 16, static_cast<uint64_t>(n_kv_heads),
-                  static_cast<uint64_t>(num_pages), 128 * 2, 16 * 128 * 2, static_cast<uint64_t>(n_kv_heads) * 16 * 128 * 2, 64, 16, 1, 1);
+  r = make_tma_4d(&tmK, k_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, D, 16, static_cast<uint64_t>(n_kv_heads),
+                  static_cast<uint64_t>(num_pages), D * 2, 16 * D * 2, static_cast<uint64_t>(n_kv_heads) * 16 * D * 2, 64, 16, 1, 1);
   if (r != 0) return -200 + r;
-  r = make_tma_4d(&tmV, v_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 128, 16, static_cast<uint64_t>(n_kv_heads),
-                  static_cast<uint64_t>(num_pages), 128 * 2, 16 * 128 * 2, static_cast<uint64_t>(n_kv_heads) * 16 * 128 * 2, 64, 16, 1, 1);
+  r = make_tma_4d(&tmV, v_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, D, 16, static_cast<uint64_t>(n_kv_heads),
+                  static_cast<uint64_t>(num_pages), D * 2, 16 * D * 2, static_cast<uint64_t>(n_kv_heads) * 16 * D * 2, 64, 16, 1, 1);
   if (r != 0) return -300 + r;
   AttnTcParams p = {};
   p.out = static_cast<__nv_bfloat16*>(out);
   p.block_table = block_table;
   p.seq_lens = seq_lens;
   p.cu_q = cu_q;
+  p.sinks = sinks;
   p.max_pages = max_pages;
   p.n_q_heads = n_q_heads;
   p.n_kv_heads = n_kv_heads;
+  p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
-  static bool configured[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !configured[dev]) {
-    if (cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmem) != cudaSuccess) return -1;
-    configured[dev] = true;
-  }
   dim3 grid((max_q_len + kTcRows - 1) / kTcRows, n_q_heads, batch);
-  const cudaError_t e = launch_pdl(attn_prefill_tc_kernel, grid, dim3(kTcThreads), kTcSmem, stream, tmQ, tmK, tmV, p);
+  const int e = head_dim == 128 ? launch_attn_tc<128>(tmQ, tmK, tmV, p, grid, stream) : launch_attn_tc<64>(tmQ, tmK, tmV, p, grid, stream);
   eredu_count_launches(1);
-  return static_cast<int>(e);
+  return e;
 }

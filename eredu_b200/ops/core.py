@@ -242,7 +242,7 @@ def attention_ref(q, k_cache, v_cache, block_table, seq_lens, q_lens, scale, win
     return out
 
 
-TC_PREFILL = _environ.get("EREDU_TC_PREFILL", "1") != "0"      # head size 128, no window, no sinks: the tcgen05 kernel
+TC_PREFILL = _environ.get("EREDU_TC_PREFILL", "1") != "0"      # head size 64 / 128: the tcgen05 kernel (else the mma.sync one)
 
 
 def attention_prefill(q, k_cache, v_cache, block_table, seq_lens, cu_q, max_q_len, scale, window=0, sinks=None,
@@ -255,13 +255,14 @@ def attention_prefill(q, k_cache, v_cache, block_table, seq_lens, cu_q, max_q_le
     if out is None:
         out = torch.empty_like(q)
     B = seq_lens.shape[0]
-    if (TC_PREFILL and q.shape[2] == 128 and window == 0 and sinks is None and k_cache.is_contiguous() and v_cache.is_contiguous()
-            and k_cache.shape[2] == 16 and k_cache.shape[3] == 128 and v_cache.shape == k_cache.shape and out.is_contiguous()):
+    if (TC_PREFILL and q.shape[2] in (64, 128) and k_cache.is_contiguous() and v_cache.is_contiguous()
+            and k_cache.shape[2] == 16 and k_cache.shape[3] == q.shape[2] and v_cache.shape == k_cache.shape and out.is_contiguous()
+            and (sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous()))):
         # tcgen05 kernel (csrc/kernels/attention_tc.cu): QK^T and PV on the 5th-generation tensor cores, pages by TMA
         code = lib().eredu_attn_prefill_tc(ptr(q), ptr(k_cache), ptr(v_cache), ptr(out), ptr(block_table), ptr(seq_lens),
-                                           ptr(cu_q), B, q.shape[0], max_q_len, block_table.stride(0), k_cache.shape[0],
-                                           q.shape[1], k_cache.shape[1], 128, scale, ptr(status_word(q.device)),
-                                           stream_ptr(q.device))
+                                           ptr(cu_q), ptr(sinks), B, q.shape[0], max_q_len, block_table.stride(0),
+                                           k_cache.shape[0], q.shape[1], k_cache.shape[1], q.shape[2], int(window), scale,
+                                           ptr(status_word(q.device)), stream_ptr(q.device))
         check(code, "eredu_attn_prefill_tc")
         return out
     code = lib().eredu_attn_prefill(ptr(q), ptr(k_cache), ptr(v_cache), ptr(out), ptr(block_table), ptr(seq_lens),

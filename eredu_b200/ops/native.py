@@ -24,7 +24,7 @@ _SIGNATURES = {
     "eredu_attn_decode": (I, [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P]),
     "eredu_peer_send": (I, [P, I, I, P, L, P, I, P, P]),
     "eredu_peer_recv": (I, [P, I, I, P, L, P, I, P, P]),
-    "eredu_attn_prefill_tc": (I, [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, P]),
+    "eredu_attn_prefill_tc": (I, [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P, P]),
     "eredu_attn_decode_scratch_elems": (None, [I, I, I, I, I, POINTER(L), POINTER(L)]),
     "eredu_attn_decode_rope": (I, [P, I, P, P, P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, F, F, F, P]),
     "eredu_rmsnorm": (I, [P, P, P, P, P, I, I, F, F, P]),

@@ -180,6 +180,30 @@ def test_attention_prefill(D, n_q, n_kv, window):
     assert rel_l2(out, ref) < 1.5e-2
 
 
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("window,with_sinks", [(0, True), (100, False), (128, True), (700, False), (1, False)])
+def test_attention_prefill_on_tcgen05_with_windows_sinks_and_head_size_64(D, window, with_sinks):
+    """The same kernel with a sliding window (key tiles before the window are skipped, windows that start inside a tile
+    are masked), sink logits in the normaliser, and head size 64."""
+    from eredu_b200.ops import core, native
+
+    q_lens, kv_lens = [300, 129, 5, 700], [900, 129, 260, 700]
+    n_q, n_kv = 8, 2
+    kc, vc, bt = _paged_setup(len(q_lens), kv_lens, n_kv, D, seed=5)
+    q = torch.randn(sum(q_lens), n_q, D, device=DEV).bfloat16()
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), device=DEV, dtype=torch.int32)
+    sl = torch.tensor(kv_lens, device=DEV, dtype=torch.int32)
+    sinks = torch.randn(n_q, device=DEV) if with_sinks else None
+    scale = 1 / math.sqrt(D)
+    before = native.launch_count()
+    assert core.TC_PREFILL
+    out = ops.attention_prefill(q, kc, vc, bt, sl, cu, max(q_lens), scale, window=window, sinks=sinks)
+    assert native.launch_count() == before + 1
+    native.check_status(torch.device(DEV))
+    ref = ops.attention_ref(q, kc, vc, bt, sl, q_lens, scale, window=window, sinks=sinks)
+    assert rel_l2(out, ref) < 1.5e-2
+
+
 @pytest.mark.parametrize("q_lens,kv_lens", [([200, 64, 1, 77], [200, 300, 50, 77]), ([2048], [2048]), ([129, 128, 127], [1000, 128, 513]),
                                             ([300], [4396])])
 @pytest.mark.parametrize("n_q,n_kv", [(8, 2), (4, 4)])
