@@ -208,12 +208,17 @@ class ModelResourceProfile:
     expert_bytes: int = 0             # part of weight_bytes that belongs to routed experts
     workspace_bytes: int = 2 << 30    # activations, logits, collective buffers, allocator slack
     state_bytes_per_sequence: int = 0  # hybrid models: fixed recurrent / convolution state of one sequence
+    windowed_bytes_per_token: int = 0  # families whose layers differ in width: bytes kept per token only inside ``sliding_window``
+    #                                    (then ``kv_bytes_per_token`` counts what grows with the whole context and ``sliding_layers`` is 0)
 
 
 def estimate_runtime_state(cfg: ModelConfig, weight_bytes: Optional[int] = None, cache_dtype_bytes: int = 2) -> ModelResourceProfile:
     """KV bytes per token and static weight bytes of a decoder (``estimate_runtime_state``, capability.rs)."""
     H, D = cfg.hidden_size, cfg.head_dim
     L = cfg.num_hidden_layers
+    family = _family_profile(cfg, weight_bytes, cache_dtype_bytes)
+    if family is not None:
+        return family
     # only softmax-attention layers keep K/V per token; convolution and gated-delta layers keep a fixed state
     stateful = [li for li in range(L) if cfg.layer_is_conv(li) or cfg.layer_has_recurrent_state(li)]
     attn_layers = sum(1 for li in range(L) if cfg.layer_has_kv(li))
@@ -249,11 +254,63 @@ def estimate_runtime_state(cfg: ModelConfig, weight_bytes: Optional[int] = None,
                                 int(wb * share), state_bytes_per_sequence=int(state))
 
 
+def _family_profile(cfg: ModelConfig, weight_bytes, b: int):
+    """Cache formulas of the families whose layers do not share one K/V width (per-family formulas of the reference's
+    capability.rs): bytes that grow with the whole context, bytes kept only inside the window, fixed state."""
+    L = cfg.num_hidden_layers
+    H = cfg.hidden_size
+    if cfg.model_type == "gemma4":
+        from ..models.gemma4 import geometry
+
+        grow = win = 0
+        for sliding, D, nkv, k_eq_v, donor in geometry(cfg):
+            if donor is not None:
+                continue                                      # the KV-sharing tail reads an earlier layer's pages
+            per = (1 if k_eq_v else 2) * nkv * D * b
+            if sliding:
+                win += per
+            else:
+                grow += per
+        wb = weight_bytes if weight_bytes is not None else 0
+        return ModelResourceProfile(int(wb), int(grow), L, 0, int(cfg.sliding_window or 0), 0, windowed_bytes_per_token=int(win))
+    if cfg.model_type == "deepseek_v4":
+        g = cfg.extra["deepseek_v4"]
+        D, Di = int(g["head_dim"]), int(g["index_head_dim"])
+        ratios = [int(r) for r in (g.get("compress_ratios") or [0] * L)][:L]
+        win = L * D * b                                       # one shared key = value head per layer, inside the window
+        grow = sum((D + (Di if r == 4 else 0)) * b / r for r in ratios if r)          # pooled streams: one token per r
+        # open pooling windows and the overlap halves: at most 2 r rows of up to 2 D (+ 2 Di) fp32 values per layer
+        state = sum(2 * r * (2 * D + (2 * Di if r == 4 else 0)) * 4 for r in ratios if r)
+        wb = weight_bytes if weight_bytes is not None else 0
+        return ModelResourceProfile(int(wb), int(grow), L, 0, int(g.get("sliding_window") or 128), 0,
+                                    state_bytes_per_sequence=int(state), windowed_bytes_per_token=int(win))
+    if cfg.model_type == "inkling_mm_model":
+        from ..models.inkling import InklingConfig
+
+        ic = InklingConfig.from_dict(cfg.extra["inkling"])
+        grow = win = state = 0
+        for li in range(L):
+            hq, hkv, D = ic.heads(ic.local_layers[li])
+            per = 2 * hkv * D * b
+            if ic.local_layers[li]:
+                win += per
+            else:
+                grow += per
+            state += (ic.sconv_kernel_size - 1) * (2 * hkv * D + 2 * H) * 4          # four convolution tails per layer
+        wb = weight_bytes if weight_bytes is not None else 0
+        return ModelResourceProfile(int(wb), int(grow), L, 0, int(ic.sliding_window_size), 0, state_bytes_per_sequence=int(state),
+                                    windowed_bytes_per_token=int(win))
+    return None
+
+
 def kv_bytes_for(profile: ModelResourceProfile, context: int, batch: int) -> int:
     """KV pool bytes for ``batch`` sequences of ``context`` tokens (sliding layers hold at most their window)."""
     per_layer = profile.kv_bytes_per_token // max(1, profile.layers)
     full = profile.layers - profile.sliding_layers
     tokens_sliding = min(context, profile.sliding_window) if profile.sliding_window else context
+    if profile.windowed_bytes_per_token:
+        return batch * (profile.kv_bytes_per_token * context + profile.windowed_bytes_per_token * tokens_sliding
+                        + profile.state_bytes_per_sequence)
     return batch * (per_layer * (full * context + profile.sliding_layers * tokens_sliding) + profile.state_bytes_per_sequence)
 
 

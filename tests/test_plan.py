@@ -132,3 +132,38 @@ def test_inspection_knows_every_family_layout(tmp_path):
     (bad / "config.json").write_text(json.dumps({"model_type": "kimi_linear", "hidden_size": 64, "num_hidden_layers": 2}))
     rep = inspect_artifact(bad)
     assert not rep.is_loadable and rep.issues[0].code == "invalid_config"
+
+
+def test_cache_formulas_of_families_with_mixed_layer_widths():
+    """Gemma 4 (two head geometries, a KV-sharing tail), DeepSeek-V4 (windowed keys + pooled streams) and Inkling (sliding
+    layers with their own heads, convolution tails): what grows with the context, what saturates at the window."""
+    import sys
+    from pathlib import Path
+
+    sys.path.insert(0, str(Path(__file__).parent))
+    from test_deepseek_v4 import v4_cfg
+    from test_inkling import ink_cfg
+
+    from eredu_b200.models.config import ModelConfig
+
+    v4 = ModelConfig.from_hf_dict(dict(v4_cfg(), model_type="deepseek_v4"))
+    prof = P.estimate_runtime_state(v4, weight_bytes=1000)
+    # ratios [0, 3, 4, 4], head 16, index head 8, window 6, bf16 cache: 4 layers x 16 x 2 bytes inside the window;
+    # pooled: 16/3 + 2 x (16 + 8)/4 values per token
+    assert prof.windowed_bytes_per_token == 4 * 16 * 2 and prof.sliding_window == 6
+    assert prof.kv_bytes_per_token == int((16 / 3 + 2 * 24 / 4) * 2)
+    short, long = P.kv_bytes_for(prof, 6, 1), P.kv_bytes_for(prof, 6000, 1)
+    assert long - short == prof.kv_bytes_per_token * (6000 - 6)             # only the pooled streams keep growing
+    ink = ModelConfig.from_hf_dict(ink_cfg())
+    prof = P.estimate_runtime_state(ink, weight_bytes=1000)
+    # layers: sliding (1 kv head x 8), full (2 x 8), sliding; window 5; four convolution tails of 2 rows per layer
+    assert prof.kv_bytes_per_token == 2 * 2 * 8 * 2 and prof.windowed_bytes_per_token == 2 * (2 * 1 * 8 * 2)
+    assert prof.state_bytes_per_sequence == (2 * (2 * 1 * 8 + 2 * 40) * 4) * 2 + 2 * (2 * 2 * 8 + 2 * 40) * 4
+    from test_hf_parity import G4
+    import transformers
+
+    g4 = ModelConfig.from_hf_dict(transformers.Gemma4TextConfig(**dict(G4, num_kv_shared_layers=3, hidden_size_per_layer_input=0,
+                                                                       attention_k_eq_v=False, enable_moe_block=False)).to_dict())
+    prof = P.estimate_runtime_state(g4, weight_bytes=1000)
+    # six layers [s, s, f] x 2, the last three share: two sliding layers (2 kv x 16) and one global (2 kv x 32) own a cache
+    assert prof.windowed_bytes_per_token == 2 * (2 * 2 * 16 * 2) and prof.kv_bytes_per_token == 2 * 2 * 32 * 2
