@@ -100,7 +100,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   pdl_launch_early();
   trace_mark(kTraceAttnPrefill, kTraceStart);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = blockIdx.z, head = blockIdx.y, qt = gridDim.x - 1 - blockIdx.x;     // longest tiles first
+  // heads vary fastest: the first wave holds the longest query tiles of every head (longest-first balances the causal
+  // triangle), and neighbouring CTAs are query heads of one key / value head reading the same pages
+  const int b = blockIdx.z, head = blockIdx.x, qt = gridDim.y - 1 - blockIdx.y;
   const int q0 = p.cu_q[b], q_len = p.cu_q[b + 1] - q0;
   const int kv_len = p.seq_lens[b];
   const int row0 = qt * kTcRows;
@@ -409,7 +411,7 @@ extern "C" int eredu_attn_prefill_tc(const void* q, const void* k_cache, const v
   p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
-  dim3 grid((max_q_len + kTcRows - 1) / kTcRows, n_q_heads, batch);
+  dim3 grid(n_q_heads, (max_q_len + kTcRows - 1) / kTcRows, batch);
   const int e = head_dim == 128 ? launch_attn_tc<128>(tmQ, tmK, tmV, p, grid, stream) : launch_attn_tc<64>(tmQ, tmK, tmV, p, grid, stream);
   eredu_count_launches(1);
   return e;
