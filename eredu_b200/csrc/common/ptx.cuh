@@ -237,6 +237,18 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       : "memory");
 }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// 2^x on the FMA pipe for x <= ~100: round to the nearest integer n with the 1.5 * 2^23 trick, a cubic for 2^f on
+// f = x - n in [-0.5, 0.5] (relative error below 1e-3: finer than bf16), and n added into the exponent field. Takes the
+// pressure off the special-function unit (16 results per clock and SM) where a kernel is bound by exponentials.
+__device__ __forceinline__ float ex2_poly(float x) {
+  x = fmaxf(x, -126.f);
+  const float t = x + 12582912.f;
+  const float f = x - (t - 12582912.f);
+  float p = fmaf(f, 0.0555041087f, 0.2402265070f);
+  p = fmaf(p, f, 0.6931471806f);
+  p = fmaf(p, f, 1.0f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
 // Three-input maximum and the two-wide fp32 FMA / add of sm_100 (one instruction for a pair held in a 64-bit register).
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;

@@ -52,6 +52,13 @@ constexpr int kTcRows = 2 * kTcTile;    // query rows per CTA
 constexpr int kTcHalf = 128 * 64 * 2;   // one [128 rows][64 bf16] swizzled half tile: 16 KB
 // shared memory: Q_a, Q_b (D / 64 halves each) | K ring (2 x D / 64 halves) | V ring (2 x D / 64 halves) | barriers
 constexpr int tc_smem(int d) { return 1024 + 3 * 2 * (d / 64) * kTcHalf + 256; }
+// A quarter of the exponentials as a polynomial on the FMA pipe (build option). Measured slower here (1153 against 1192
+// TFLOP/s at 32k tokens, 1112 against 1170 at 8k): the softmax warps are bound by instruction issue, not by the
+// special-function unit, so the extra FMA-pipe instructions cost more than the unit they relieve.
+#ifndef EREDU_ATTN_POLY_EXP
+#define EREDU_ATTN_POLY_EXP 0
+#endif
+constexpr bool kTcPolyExp = EREDU_ATTN_POLY_EXP != 0;
 constexpr float kTcRescale = 8.f;       // log2 units a row maximum may outgrow the scale in use
 
 // MN-major operand tile stored as [k rows][64 bf16] (128-byte rows, 128B swizzle): 64-element blocks along MN are `lbo`
@@ -313,7 +320,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           const int c = c2 * 2 + (i >> 4), e = i & 15;
           float t0, t1;
           unpack_f32x2(fma_f32x2(pack_b32x2(sc[c][e], sc[c][e + 1]), scale2, shift2), t0, t1);
-          const float p0 = ex2_approx(t0), p1 = ex2_approx(t1);
+          // every fourth pair takes the polynomial on the FMA pipe instead of the special-function unit
+          const bool poly = kTcPolyExp && ((i >> 1) & 3) == 3;
+          const float p0 = poly ? ex2_poly(t0) : ex2_approx(t0), p1 = poly ? ex2_poly(t1) : ex2_approx(t1);
           acc[(i >> 1) & 3] = add_f32x2(acc[(i >> 1) & 3], pack_f32x2(p0, p1));
           packed[i >> 1] = pack_bf16x2(p0, p1);
         }
