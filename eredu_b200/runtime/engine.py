@@ -113,6 +113,7 @@ class Engine:
             from .block_tiers import BlockTierStore
 
             self.block_tiers = BlockTierStore(self.kv, kv_host_tier_bytes, kv_disk_tier_dir, kv_disk_tier_bytes)
+            self.kv.block_tiers = self.block_tiers      # every allocation path demotes what it evicts (kv.alloc)
         self._next_id = 0
         self._graphs: dict = {}
         self._decode_state = None
@@ -139,13 +140,11 @@ class Engine:
             else:
                 leased = list(self.kv.allocator.match_prefix(seq.prompt[:usable])) if usable else []
             try:
-                seq.pages = leased + list(self.kv.allocator.alloc(need - len(leased)))
+                seq.pages = leased + self.kv.alloc(need - len(leased))
             except RuntimeError:
                 if leased:
                     self.kv.allocator.release(leased)
                 raise
-            if self.block_tiers is not None:
-                self.block_tiers.demote(self.kv.allocator.take_evicted())
             seq.kv_len = seq.cached_tokens = len(leased) * PAGE
             st = self.prefix_stats
             st["lookups"] += 1
@@ -153,7 +152,7 @@ class Engine:
             st["hit_tokens"] += seq.cached_tokens
             st["prompt_tokens"] += len(seq.prompt)
             return seq
-        seq.pages = list(self.kv.allocator.alloc(need))
+        seq.pages = self.kv.alloc(need)
         if self.kv.page_to_slot is not None:
             try:
                 self.kv.bind_state(seq.pages[0])
@@ -184,15 +183,14 @@ class Engine:
                 if tier is not None:
                     if al.free_pages() <= need - len(plan):     # the pool cannot take promoted blocks and the rest of the request
                         break
-                    page = al.alloc(1)[0]
+                    page = self.kv.alloc(1)[0]
                     promote.append((h, page))
                 pages.append(page)
         finally:
             tail = [p for _, p, t in plan[len(pages):] if t is None]
             if tail:
                 al.release(tail)                      # device hits behind a block that could not be promoted
-        tiers.demote(al.take_evicted())               # copy evicted pages out before anything is copied in
-        tiers.promote(promote)
+        tiers.promote(promote)                        # evicted pages were copied out as they were allocated (kv.alloc)
         for h, page in promote:
             al.seal(page, h)
         return pages

@@ -72,6 +72,15 @@ class PagedKVCache:
         self._la_index: dict = {}
         self._free_state_slots: list[int] = []
 
+    def alloc(self, n: int) -> list:
+        """Pages from the allocator. When lower tiers are attached (``block_tiers``), published pages that this
+        allocation evicted are copied out at once - their contents are intact only until the new owner's first write."""
+        pages = list(self.allocator.alloc(n))
+        tiers = getattr(self, "block_tiers", None)
+        if tiers is not None:
+            tiers.demote(self.allocator.take_evicted())
+        return pages
+
     def enable_linear_attention_state(self, layers, slots: int, conv_hist: int, conv_channels: int, heads: int, dk: int, dv: int):
         dev, dt = self.k.device, self.k.dtype
         self._la_index = {li: i for i, li in enumerate(layers)}

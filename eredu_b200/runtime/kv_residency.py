@@ -160,7 +160,7 @@ class KVHostTier:
         if p.disk_path is not None and not self._unspill(p):
             self.stats["refused"] += 1
             return False
-        pages = list(self.kv.allocator.alloc(p.reserved_pages))
+        pages = self.kv.alloc(p.reserved_pages)
         dev = self.engine.device
         if p.pages:
             idx = torch.as_tensor(pages[:p.pages], dtype=torch.long, device=dev)
