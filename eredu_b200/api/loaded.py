@@ -592,6 +592,10 @@ class LoadedModel:
 
         if draft_tokens <= 0:
             return None
+        if not getattr(self.engine, "paged", True):
+            if draft is not None:
+                raise NotImplementedError("speculative decoding needs the paged engine; this model family runs without a drafter")
+            return None
         if draft is not None:
             return SpeculativeDecoder(self.engine, draft.engine, k=draft_tokens)
         if getattr(self, "assistant", None) is not None:

@@ -88,6 +88,8 @@ class Server:
     def __init__(self, engine: Engine, transport=None, max_step_tokens: int = 8192, max_waiting: int = 1024,
                  prefill_chunk: int = 2048, penalties: bool = False, fault_hook: Optional[Callable[[str, int], bool]] = None,
                  kv_tier=None):
+        if not getattr(engine, "paged", True):
+            raise NotImplementedError("continuous batching needs the paged engine; this model family runs one sequence at a time")
         self.engine = engine
         self.transport = transport
         self.kv_tier = kv_tier   # KVHostTier: running requests are parked in host memory when the page pool runs out
