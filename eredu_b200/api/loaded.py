@@ -577,6 +577,12 @@ class LoadedModel:
         lm.vision = lm.audio = None
         return lm
 
+    def attach_dflash(self, path) -> None:
+        """Load a DFlash block drafter (the assistant released with Muse-Glimmer) next to this model."""
+        from ..models.dflash import load_dflash
+
+        self.dflash = load_dflash(path, self.engine.device, self.engine.model.dtype)
+
     def attach_assistant(self, path) -> None:
         """Load a Gemma 4 assistant drafter (its own directory) next to this model: speculative generation then drafts
         with it (``load_gemma4_assistant_model``, eredu/src/backend/mlx/architectures/gemma4/assistant.rs:499)."""
@@ -602,6 +608,10 @@ class LoadedModel:
             from ..runtime.speculative import Gemma4AssistantDecoder
 
             return Gemma4AssistantDecoder(self.engine, self.assistant, k=draft_tokens)
+        if getattr(self, "dflash", None) is not None:
+            from ..runtime.speculative import DFlashDecoder
+
+            return DFlashDecoder(self.engine, self.dflash, k=draft_tokens)
         if embedded_mtp and getattr(self, "mtp", None) is not None:
             return EmbeddedMtpDecoder(self.engine, self.mtp, k=draft_tokens)
         return None
@@ -752,7 +762,8 @@ class LoadedModel:
             self.last_speculative_stats = dict(spec.stats.summary(), scheduler=vars(done.scheduler),
                                                request=vars(done.requests[0].stats),
                                                drafter="external" if draft is not None else
-                                               "assistant" if getattr(self, "assistant", None) is not None else "embedded")
+                                               "assistant" if getattr(self, "assistant", None) is not None else
+                                               "dflash" if getattr(self, "dflash", None) is not None else "embedded")
         elif draft is not None:
             from ..runtime.speculative import SpeculativeDecoder
 

@@ -249,13 +249,17 @@ def benchmark_candidates(model_path: str, a, candidates: list, prompt: str) -> d
             "candidates": rows, "_selected_plan": candidates[best]}
 
 
-def _is_gemma4_assistant(path) -> bool:
-    """A draft directory whose config.json names the Gemma 4 assistant drafter."""
+def _draft_model_type(path) -> str:
     cfg = os.path.join(path, "config.json")
     if not os.path.isfile(cfg):
-        return False
+        return ""
     with open(cfg) as f:
-        return str(json.load(f).get("model_type", "")).startswith("gemma4_assistant")
+        return str(json.load(f).get("model_type", ""))
+
+
+def _is_gemma4_assistant(path) -> bool:
+    """A draft directory whose config.json names the Gemma 4 assistant drafter."""
+    return _draft_model_type(path).startswith("gemma4_assistant")
 
 
 def main(argv=None) -> int:
@@ -457,6 +461,8 @@ def main(argv=None) -> int:
             raise SystemExit("--draft-model cannot be combined with --mirostat-v2")
         if _is_gemma4_assistant(a.draft_model):
             lm.attach_assistant(a.draft_model)              # no cache of its own: it reads the target's keys and values
+        elif _draft_model_type(a.draft_model) == "muse_glimmer_assistant":
+            lm.attach_dflash(a.draft_model)                 # block drafter conditioned on the target's layer outputs
         else:
             draft = LoadedModel.load(a.draft_model, ModelLoadOptions(device=device, max_batch=1,
                                                                       max_seq_len=max(4096, a.max_tokens + 2048)))

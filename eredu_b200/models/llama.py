@@ -58,6 +58,9 @@ class ForwardBatch:
     # embedded prediction heads: keep the hidden state that enters the final norm (all rows) in ``hidden_out``
     capture_hidden: bool = False
     hidden_out: Optional[torch.Tensor] = None
+    # block drafters that condition on intermediate activations: the outputs of these layers (all rows) land in ``layer_hidden``
+    capture_layers: Optional[tuple] = None
+    layer_hidden: Optional[dict] = None
 
 
 @dataclass
@@ -342,6 +345,10 @@ class CausalLM:
                 h, ssq = self.layer_forward(self.first_layer + i, lw, h, batch, kv, ssq, nxt)
             if self.residency is not None:
                 self.residency.release(i)
+            if batch.capture_layers is not None and self.first_layer + i in batch.capture_layers:
+                if batch.layer_hidden is None:
+                    batch.layer_hidden = {}
+                batch.layer_hidden[self.first_layer + i] = h
             if batch.deepstack is not None and self.first_layer + i < len(batch.deepstack):
                 h = h.index_add(0, batch.embed_rows, batch.deepstack[self.first_layer + i].to(h.dtype))
                 ssq = None

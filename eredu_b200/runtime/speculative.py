@@ -572,6 +572,101 @@ class Gemma4AssistantDecoder(SpeculativeDecoder):
         super()._round(tseqs, dseqs, live, outs, pending, last, sp)
 
 
+class DFlashDecoder(SpeculativeDecoder):
+    """Speculative decoding with a DFlash block drafter (eredu/src/backend/mlx/architectures/muse_glimmer/mtp.rs): the
+    target's passes keep the outputs of the drafter's ``target_layer_ids`` for every token they feed; per request the
+    decoder holds the drafter's encoded context and the states of tokens that were committed since it was last extended.
+    A round extends the context, runs ONE drafter pass over ``[newest token, mask x k]`` and reads all k proposal
+    distributions from it through the target's head; the verify pass is the usual one."""
+
+    carries_verify_hidden = True
+    supports_lookahead = False
+
+    def __init__(self, target: Engine, dflash, k: Optional[int] = None):
+        k = min(k or dflash.max_proposals, dflash.max_proposals)
+        super().__init__(target, _NoDraftEngine(target.cfg), k)
+        if dflash.cfg.hidden_size != target.cfg.hidden_size:
+            raise ValueError("the drafter's width differs from the target's")
+        if max(dflash.cfg.target_layer_ids) >= target.cfg.num_hidden_layers:
+            raise ValueError("the drafter conditions on layers the target does not have")
+        self.dflash = dflash
+        self.ids = tuple(dflash.cfg.target_layer_ids)
+        self._ctx: dict = {}                 # seq_id -> DFlashContext
+        self._pending_hidden: dict = {}      # seq_id -> [n, H * layers] states of committed tokens not yet in the context
+        self._verify_hidden = None
+        self._last_chain = None
+
+    def _capture(self, store: dict):
+        def prepare(batch):
+            batch.capture_layers = self.ids
+            store["batch"] = batch
+        return prepare
+
+    def _states(self, batch):
+        return torch.cat([batch.layer_hidden[i] for i in self.ids], -1)
+
+    def _prefill(self, tseqs, dseqs) -> list:
+        from ..models.dflash import DFlashContext
+
+        prompts = [list(s.prompt) for s in tseqs]
+        cap: dict = {}
+        logits = self._multi_token_step(self.t, tseqs, prompts, all_rows=False, uniform=False, prepare=self._capture(cap))
+        states = self._states(cap["batch"])
+        off = 0
+        for s, p in zip(tseqs, prompts):
+            s.kv_len = len(p)
+            self._ctx[s.seq_id] = DFlashContext()
+            self._pending_hidden[s.seq_id] = states[off:off + len(p)].clone()
+            off += len(p)
+        _, toks = self._probs_and_tokens(self.t, logits, [s.sampling for s in tseqs], [len(p) for p in prompts],
+                                         [s.seq_id for s in tseqs])
+        return [int(t) for t in toks.tolist()]
+
+    def _propose(self, tseqs, dseqs, live, pending, sp, base):
+        k, B = self.k, len(tseqs)
+        eng = self.t
+        model = eng.model
+        rows = []
+        for b, s in enumerate(tseqs):
+            ctx = self.dflash.extend_context(self._ctx[s.seq_id], self._pending_hidden[s.seq_id], s.kv_len)
+            self._ctx[s.seq_id] = ctx
+            self._pending_hidden[s.seq_id] = self._pending_hidden[s.seq_id][:0]
+            ids = torch.tensor([pending[live[b]][-1]] + [self.dflash.cfg.mask_token_id] * k, device=eng.device)
+            rows.append(self.dflash.propose(model.embed[ids.long()], ctx))            # [k, H]
+        # the proposal states carry the drafter's own final norm: they go through the target's output head and logit
+        # scaling only, not through the target's final norm
+        logits = ops.linear(torch.cat(rows).to(model.dtype).contiguous(), model.lm_head, out_dtype=torch.float32)
+        mg = eng.cfg.extra.get("muse_glimmer")
+        if mg:
+            cap, mult = float(mg["final_logit_softcapping"]), float(mg["output_multiplier"])
+            logits = torch.tanh(logits * (mult / cap)) * cap
+        logits = logits.view(B, k, -1)
+        drafted = [[] for _ in range(B)]
+        p_d = []
+        for j in range(k):
+            probs, toks = self._probs_and_tokens(eng, logits[:, j].contiguous(), [sp] * B, [base[b] + j for b in range(B)],
+                                                 [s.seq_id for s in tseqs])
+            p_d.append(probs)
+            for b, t in enumerate(toks.tolist()):
+                drafted[b].append(int(t))
+        return drafted, p_d, None
+
+    def _verify_forward(self, tseqs, feed):
+        cap: dict = {}
+        logits = self._multi_token_step(self.t, tseqs, feed, all_rows=True, uniform=True, prepare=self._capture(cap))
+        self._verify_hidden = self._states(cap["batch"]).view(len(tseqs), self.k + 1, -1)
+        return logits
+
+    def _settle(self, b, i, a, nxt, dseqs, drafted, pending, ctx):
+        pending[i] = [nxt]
+        # the verify pass fed `last`, d_1 .. d_k: inputs 0 .. a are now cached, their states join the context next round
+        self._pending_hidden[self._seq_ids[b]] = self._verify_hidden[b, :a + 1].clone()
+
+    def _round(self, tseqs, dseqs, live, outs, pending, last, sp):
+        self._seq_ids = [s.seq_id for s in tseqs]
+        super()._round(tseqs, dseqs, live, outs, pending, last, sp)
+
+
 class GraphSpeculativeDecoder(SpeculativeDecoder):
     """The speculative round as ONE CUDA graph (GPU only, fixed batch): k draft steps, the target's verify pass over
     k+1 tokens, both samplers and the accept / resample kernel are captured once; a round is a few small
