@@ -18,7 +18,8 @@ Behavioural counterpart of eredu/src/backend/mlx/architectures/inkling/model.rs 
   vocabulary (model.rs:2769-2806).
 
 Tensor names: the canonical ``model.layers.N.self_attn.*`` spelling or the released ``model.llm.layers.N.attn.*`` one
-(architectures/inkling/checkpoint.rs:35-330). Fused ``gate_up`` banks hold the gate rows first.
+(architectures/inkling/checkpoint.rs:35-330). Canonical fused ``gate_up`` banks hold the gate rows first; the released
+``w13`` tensors interleave gate and up rows and are de-interleaved at load.
 
 The per-layer state (keys, values and four convolution tails) is kept per sequence; the family runs on
 ``runtime.unpaged.UnpagedEngine``.
@@ -192,6 +193,17 @@ class InklingModel:
         def present(canonical, released):
             return has(canonical) or has(released)
 
+        def fused(canonical, released, axis):
+            """A gate / up bank as [gate rows; up rows]: the canonical tensors hold that, the released ``w13`` tensors
+            interleave them row by row - gate on the even rows, up on the odd ones (layerwise.rs:2312-2337, 3987-4003)."""
+            if has(canonical):
+                return get(canonical)
+            t = get(released)
+            if t.shape[axis] % 2:
+                raise ValueError(f"{released} has an odd interleaved width")
+            idx = torch.cat((torch.arange(0, t.shape[axis], 2), torch.arange(1, t.shape[axis], 2)))
+            return t.index_select(axis, idx)
+
         f32 = lambda c, r: up(fetch(c, r), torch.float32)                                           # noqa: E731
         self.embed = up(fetch("model.embed_tokens.weight", "model.llm.embed.weight"))
         self.embed_norm = f32("model.embed_norm.weight", "model.llm.embed_norm.weight")
@@ -218,10 +230,10 @@ class InklingModel:
             w["attn_sconv"] = _ShortConv(f32(c + "attn_sconv.weight", r + "attn_sconv.weight"))
             w["mlp_sconv"] = _ShortConv(f32(c + "mlp_sconv.weight", r + "mlp_sconv.weight"))
             if cfg.dense_layers[li]:
-                if present(c + "dense.gate_proj.weight", r + "mlp.w13_dn.weight") and has(c + "dense.gate_proj.weight"):
+                if has(c + "dense.gate_proj.weight"):
                     gu = torch.cat((get(c + "dense.gate_proj.weight"), get(c + "dense.up_proj.weight")), 0)
                 else:
-                    gu = get(r + "mlp.w13_dn.weight")
+                    gu = fused(c + "dense.gate_up_proj.weight", r + "mlp.w13_dn.weight", 0)
                 w["dense_gu"] = up(gu)
                 w["dense_dn"] = up(fetch(c + "dense.down_proj.weight", r + "mlp.w2_md.weight"))
                 w["dense_scale"] = f32(c + "dense_global_scale", r + "mlp.global_scale") \
@@ -230,9 +242,9 @@ class InklingModel:
                 w["router"] = f32(c + "moe.router.weight", r + "mlp.gate.weight")
                 w["router_bias"] = f32(c + "moe.router.bias", r + "mlp.gate.bias")
                 w["router_scale"] = f32(c + "moe.router.global_scale", r + "mlp.gate.global_scale")
-                w["egu"] = up(fetch(c + "moe.experts.gate_up_proj", r + "mlp.experts.w13_weight"))
+                w["egu"] = up(fused(c + "moe.experts.gate_up_proj", r + "mlp.experts.w13_weight", 1))
                 w["edn"] = up(fetch(c + "moe.experts.down_proj", r + "mlp.experts.w2_weight"))
-                w["sgu"] = up(fetch(c + "moe.shared_experts.gate_up_proj", r + "mlp.shared_experts.shared_w13_weight"))
+                w["sgu"] = up(fused(c + "moe.shared_experts.gate_up_proj", r + "mlp.shared_experts.shared_w13_weight", 1))
                 w["sdn"] = up(fetch(c + "moe.shared_experts.down_proj", r + "mlp.shared_experts.shared_w2_weight"))
             self.layers.append(w)
 

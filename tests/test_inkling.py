@@ -70,10 +70,13 @@ def ink_state(cfg: InklingConfig, released=False, seed=0):
         if k in ren:
             out[ren[k]] = v
             continue
-        if ".dense.gate_proj." in k:
+        if ".dense.gate_proj." in k:          # the released packing interleaves gate (even rows) and up (odd rows)
             li = k.split(".")[2]
-            out[f"model.llm.layers.{li}.mlp.w13_dn.weight"] = torch.cat((v, sd[k.replace("gate_proj", "up_proj")]), 0)
+            out[f"model.llm.layers.{li}.mlp.w13_dn.weight"] = torch.stack((v, sd[k.replace("gate_proj", "up_proj")]), 1).flatten(0, 1)
             continue
+        if k.endswith("experts.gate_up_proj"):
+            half = v.shape[1] // 2
+            v = torch.stack((v[:, :half], v[:, half:]), 2).flatten(1, 2)
         if ".dense.up_proj." in k:
             continue
         n = k.replace("model.layers.", "model.llm.layers.")
