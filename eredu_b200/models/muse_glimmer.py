@@ -13,9 +13,11 @@ Behavioural counterpart of eredu/src/backend/mlx/architectures/muse_glimmer/mod.
 * SwiGLU feed-forward; logits are ``softcap * tanh(logits * output_multiplier / softcap)`` (mod.rs:551-559).
 
 The key / value cache is an ordinary grouped-query cache, so the family runs on the paged engine (batching, prefix reuse,
-sampling kernels); the block itself is tensor operations around this repository's GEMMs over the paged pool, like the
-Gemma 4 block. The routed-expert variant of the feed-forward (softmax top-k over fused expert banks) runs as a loop over the
-chosen experts. Not built: the vision tower and adapter, the DFlash / ATEM drafters, tensor parallelism for this family.
+sampling kernels); the block is tensor operations around this repository's GEMMs over the paged pool, with the attention
+kernels (tcgen05 prefill, split-KV decode) for head sizes 64 and 128; the dense variant's decode step is captured in a
+CUDA graph. The routed-expert variant of the feed-forward (softmax top-k over fused expert banks) runs as a loop over
+the chosen experts and decodes eagerly. Not built: the vision tower and adapter, the ATEM drafter, tensor parallelism
+for this family.
 """
 from __future__ import annotations
 
@@ -89,13 +91,25 @@ def block_forward(model, li, lw, h, batch, kv):
     if mg["uses_rope"][li]:
         q, k = _rope(q, batch.positions, mg["inv_freq"]), _rope(k, batch.positions, mg["inv_freq"])
     k_cache, v_cache = kv.layer(li)
-    ok = batch.slots >= 0
-    page, off = batch.slots[ok] // ops.PAGE, batch.slots[ok] % ops.PAGE
-    k_cache[page, :, off] = k[ok].to(k_cache.dtype)
-    v_cache[page, :, off] = v[ok].to(v_cache.dtype)
-    q_lens = (batch.cu_q[1:] - batch.cu_q[:-1]).tolist() if batch.is_prefill else [batch.q_per_seq] * batch.seq_lens.shape[0]
-    attn = ops.attention_ref(q.to(dt), k_cache, v_cache, batch.block_table, batch.seq_lens, q_lens, D ** -0.5,
-                             window=int(cfg.sliding_window or 0) if mg["sliding"][li] else 0)
+    # rows without a slot (padding of a captured decode batch) land in page 0, which no sequence owns: the scatter
+    # keeps a fixed shape, so the step can be captured in a CUDA graph
+    slot = batch.slots.clamp_min(0)
+    page, off = slot // ops.PAGE, slot % ops.PAGE
+    k_cache[page, :, off] = k.to(k_cache.dtype)
+    v_cache[page, :, off] = v.to(v_cache.dtype)
+    window = int(cfg.sliding_window or 0) if mg["sliding"][li] else 0
+    if h.is_cuda and D in ops.KERNEL_HEAD_DIMS and dt == torch.bfloat16:
+        # head sizes with attention kernels: tcgen05 prefill, split-KV decode (the cache rows were written above)
+        qc = q.to(dt).contiguous()
+        if batch.is_prefill:
+            attn = ops.attention_prefill(qc, k_cache, v_cache, batch.block_table, batch.seq_lens, batch.cu_q, batch.max_q_len,
+                                         D ** -0.5, window=window)
+        else:
+            attn = ops.attention_decode(qc, k_cache, v_cache, batch.block_table, batch.seq_lens, batch.q_per_seq, D ** -0.5,
+                                        splits=batch.splits, window=window, scratch=batch.scratch)
+    else:
+        q_lens = (batch.cu_q[1:] - batch.cu_q[:-1]).tolist() if batch.is_prefill else [batch.q_per_seq] * batch.seq_lens.shape[0]
+        attn = ops.attention_ref(q.to(dt), k_cache, v_cache, batch.block_table, batch.seq_lens, q_lens, D ** -0.5, window=window)
     gate = torch.sigmoid(ops.linear(x, w["gate_proj"], bias=w["gate_proj_b"]).float())
     a = ops.linear((attn.reshape(M, Hq * D).float() * gate).to(dt), w["o_proj"], bias=w["o_proj_b"])
     h = h + (_wrms(a, mg["post_eps"]) * w["post_attention_layernorm"]).to(dt)

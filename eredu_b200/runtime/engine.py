@@ -542,6 +542,8 @@ class Engine:
             return True    # no attention kernel for this head size: the tensor-operation path reads lengths on the host
         if getattr(m, "residency", None) is not None or getattr(getattr(m, "inner", m), "observer", None) is not None:
             return True
+        if int((self.cfg.extra.get("muse_glimmer") or {}).get("num_experts") or 0) > 0:
+            return True    # the routed experts of this family are grouped on the host
         if getattr(m, "eager_collectives", False):
             return True    # a collective of the step reads counts on the host (the torch.distributed all-to-all baseline)
         return any(getattr(getattr(lw, "moe", None), "expert_cache", None) is not None for lw in getattr(m, "layers", []))

@@ -17,10 +17,10 @@ TEXT = dict(model_type="muse_glimmer_text", hidden_size=64, num_hidden_layers=4,
             output_multiplier=0.6, final_logit_softcapping=20.0)
 
 
-def state(seed=0):
+def state(seed=0, D=16):
     g = torch.Generator().manual_seed(seed)
     r = lambda *s, std=0.2: torch.randn(*s, generator=g) * std          # noqa: E731
-    H, I, D, Hq, Hkv = 64, 96, 16, 4, 2
+    H, I, Hq, Hkv = 64, 96, 4, 2
     root = "model.language_model."
     sd = {root + "embed_tokens.weight": r(200, H, std=1.0), root + "norm.weight": 1 + r(H, std=0.1), "lm_head.weight": r(200, H, std=0.5)}
     for li in range(4):
@@ -34,9 +34,9 @@ def state(seed=0):
     return sd
 
 
-def dense_reference(sd, tokens):
+def dense_reference(sd, tokens, D=16):
     """The whole sequence at once, every step written out."""
-    H, D, Hq, Hkv = 64, 16, 4, 2
+    H, Hq, Hkv = 64, 4, 2
     root = "model.language_model."
     wrms = lambda z, eps: z * torch.rsqrt(z.square().mean(-1, keepdim=True) + eps)        # noqa: E731
     T = len(tokens)

@@ -51,16 +51,26 @@ def test_inkling_on_the_gpu_matches_its_cpu_run():
     assert _close(got, want, 0.08)
 
 
-def test_muse_glimmer_on_the_gpu_engine(tmp_path):
+@pytest.mark.parametrize("head_dim", [16, 64])
+def test_muse_glimmer_on_the_gpu_engine(tmp_path, head_dim, monkeypatch):
+    """Head size 16 runs the tensor-operation attention, 64 the attention kernels (tcgen05 prefill, split-KV decode)."""
+    import test_muse_glimmer as T
     from eredu_b200.api import LoadedModel, ModelLoadOptions
-    from test_muse_glimmer import TEXT, dense_reference, save, state
+    from test_muse_glimmer import dense_reference, save, state
 
-    sd = state()
-    save(tmp_path, sd)
+    sd = state(D=head_dim)
+    save(tmp_path, sd, dict(T.TEXT, head_dim=head_dim))
     lm = LoadedModel.load(tmp_path, ModelLoadOptions(device="cuda", max_batch=2, max_seq_len=64))
     tokens = torch.randint(0, 200, (21,), generator=torch.Generator().manual_seed(1)).tolist()
-    want = dense_reference(sd, tokens)
+    want = dense_reference(sd, tokens, D=head_dim)
     assert _close(lm.prefill_logits(tokens), want[-1], 0.08)
+    seq = lm.engine.new_sequence(tokens[:9], max_new_tokens=16)           # prefill, then decode-shaped steps
+    lm.engine.prefill_logits([seq])
+    row = None
+    for t in tokens[9:]:
+        row = lm.engine.step_logits(seq, t)
+    lm.engine.release(seq)
+    assert _close(row, want[-1], 0.08)
     out = lm.generate([tokens[:9], tokens[4:17]], SamplingParams(temperature=0.0), 6)
     assert [len(o) for o in out] == [6, 6]
     from eredu_b200.ops import native
