@@ -361,6 +361,8 @@ class LoadedModel:
         from ..media.request import Video
         from ..models.qwen_vl import image_to_patches, mrope_positions, video_to_patches
 
+        if self.config.model_type == "inkling_mm_model":
+            return self._inkling_inputs(segments)
         if self.config.model_type == "gemma4" and (self.vision is not None or self.audio is not None):
             return self._gemma4_inputs(segments, wrap, **(image_limits or {}))
         if self.vision is None:
@@ -480,6 +482,51 @@ class LoadedModel:
         return ids, {"rows": rows, "values": torch.cat([f.to(feats[0].dtype) for f in feats], 0), "deepstack": None,
                      "rope_positions": None, "rope_delta": 0, "bidir_groups": bidir, "placeholder_id": int(placeholder)}
 
+    def _inkling_inputs(self, segments: list):
+        """Typed prompt parts of the Inkling family (``prepare_typed_input``, eredu/src/backend/mlx/architectures/inkling/
+        layerwise.rs:2680-2760): text (``str`` or token ids), ``media.RgbImage`` (one placeholder per 40 x 40 patch, the
+        hMLP tower's soft tokens), ``{"audio_ids": [frames, codebooks]}`` with an optional ``"valid_frames"`` (summed
+        codebook embeddings) and ready ``{"image_embeds": ...}`` / ``{"audio_embeds": ...}`` rows of the decoder's width.
+        Returns (token_ids, (rows, values)) for ``UnpagedEngine.feed_logits``."""
+        from ..media import MultimodalPreparationError, RgbImage
+        import numpy as np
+
+        from ..models.inkling import image_patches
+
+        extra = {**self.config.extra["inkling"], **self.config.extra.get("vision", {})}   # nested configs keep them outside
+        image_id, audio_id = int(extra.get("image_token_id", 200054)), int(extra.get("audio_token_id", 200053))
+        hidden = int(self.engine.model.cfg.hidden_size)
+        ids, rows, vals = [], [], []
+
+        def soft(token, emb):
+            if emb.dim() != 2 or emb.shape[1] != hidden:
+                raise MultimodalPreparationError(f"media embeddings must be [tokens, {hidden}], got {tuple(emb.shape)}")
+            rows.extend(range(len(ids), len(ids) + emb.shape[0]))
+            ids.extend([token] * emb.shape[0])
+            vals.append(emb.to(self.engine.device, self.engine.model.dtype))
+
+        for seg in segments:
+            if isinstance(seg, str):
+                ids.extend(self.encode(seg))
+            elif isinstance(seg, RgbImage):
+                if self.vision is None:
+                    raise MultimodalPreparationError("Inkling image input requires vision_config and vision weights")
+                soft(image_id, self.vision(image_patches(torch.from_numpy(np.ascontiguousarray(seg.pixels)))))
+            elif isinstance(seg, dict) and "audio_ids" in seg:
+                if self.audio is None:
+                    raise MultimodalPreparationError("Inkling audio input requires audio_config and audio weights")
+                soft(audio_id, self.audio(torch.as_tensor(seg["audio_ids"]), seg.get("valid_frames")))
+            elif isinstance(seg, dict) and ("image_embeds" in seg or "audio_embeds" in seg):
+                kind = "image_embeds" if "image_embeds" in seg else "audio_embeds"
+                soft(image_id if kind == "image_embeds" else audio_id, torch.as_tensor(seg[kind]))
+            elif isinstance(seg, (list, tuple)):
+                ids.extend(int(t) for t in seg)
+            else:
+                raise MultimodalPreparationError(f"Inkling input does not support parts of type {type(seg).__name__}")
+        if not rows:
+            return ids, None
+        return ids, (torch.tensor(rows, dtype=torch.int64), torch.cat(vals))
+
     def chat_segments(self, messages: list, images: list, placeholder: str = "<|image_pad|>", **template_kwargs) -> list:
         """Render a conversation whose user content lists contain ``{"type": "image"}`` items with the chat template and
         cut the prompt at the template's image placeholders: text pieces interleaved with ``images`` in order (for
@@ -575,6 +622,15 @@ class LoadedModel:
         lm.config = src.cfg
         lm.mtp, lm.mtp_error = None, None
         lm.vision = lm.audio = None
+        if src.cfg.model_type == "inkling_mm_model":
+            from ..models.inkling import InklingAudio, InklingVision
+
+            raw = {**src.cfg.extra["inkling"], **src.cfg.extra.get("vision", {})}
+            hidden = int(model.cfg.hidden_size)
+            if raw.get("vision_config") and (src.has("visual.final_norm.weight") or src.has("model.visual.final_norm.weight")):
+                lm.vision = InklingVision({"text_hidden_size": hidden, **raw["vision_config"]}, src.get, src.has, device, dtype)
+            if raw.get("audio_config") and (src.has("audio.encoder.weight") or src.has("model.audio.encoder.weight")):
+                lm.audio = InklingAudio(raw["audio_config"], src.get, src.has, device, dtype)
         return lm
 
     def attach_dflash(self, path) -> None:

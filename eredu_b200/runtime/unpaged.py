@@ -64,6 +64,15 @@ class UnpagedEngine:
         return rows
 
     @torch.no_grad()
+    def feed_logits(self, seq, token_ids, multimodal=None):
+        """Feeds ``token_ids`` with soft tokens at some rows (``multimodal``: (rows, values), the family's media ingress);
+        returns the logits after the last one."""
+        out = self.model.forward(list(token_ids), seq.cache) if multimodal is None else \
+            self.model.forward(list(token_ids), seq.cache, embeds=multimodal)
+        seq.kv_len += len(token_ids)
+        return out
+
+    @torch.no_grad()
     def step_logits(self, seq, token: int):
         out = self.model.forward([int(token)], seq.cache)
         seq.kv_len += 1

@@ -309,3 +309,56 @@ def test_hmlp_tower_against_a_restatement_and_the_splice():
     assert torch.allclose(base[:2], with_media[:2]) and not torch.allclose(base[2:], with_media[2:])
     with pytest.raises(ValueError, match="placeholder"):
         splice_media(toks, 80, 81, [out, out], [a])
+
+
+def test_media_parts_through_the_public_api(tmp_path):
+    """An image, audio frames and ready embeddings between text parts: the API's typed parts give the same logits as the
+    decoder fed with the spliced soft tokens, and a text-only checkpoint refuses media."""
+    import numpy as np
+    from safetensors.torch import save_file
+
+    from eredu_b200.api import LoadedModel, ModelLoadOptions
+    from eredu_b200.media import MultimodalPreparationError, RgbImage
+    from eredu_b200.models.inkling import InklingAudio, InklingVision, image_patches, splice_media
+
+    raw = ink_cfg(vocab_size=90)
+    raw.update(image_token_id=80, audio_token_id=81,
+               vision_config={"patch_size": 40, "temporal_patch_size": 2, "num_channels": 3, "num_hidden_layers": 4},
+               audio_config={"num_codebooks": 4, "codebook_size": 9})
+    cfg = InklingConfig.from_dict(raw)
+    sd = {**ink_state(cfg), **_tower_state()}
+    save_file({k: v.contiguous() for k, v in sd.items()}, str(tmp_path / "model.safetensors"))
+    (tmp_path / "config.json").write_text(json.dumps(raw))
+    lm = LoadedModel.load(tmp_path, ModelLoadOptions(device="cpu", max_batch=1, max_seq_len=64))
+    assert lm.vision is not None and lm.audio is not None
+    pixels = np.random.default_rng(3).integers(0, 256, (40, 39, 3), dtype=np.uint8)
+    frames = torch.tensor([[0, 8, 3, 5], [2, 2, 2, 2], [1, 0, 7, 4]])
+    ready = torch.randn(2, 40, generator=torch.Generator().manual_seed(5))
+    segments = [[4, 5, 6], RgbImage(pixels), [7], {"audio_ids": frames, "valid_frames": 2}, {"image_embeds": ready}, [9, 10]]
+    ids, (rows, values) = lm.multimodal_inputs(segments)
+    assert ids == [4, 5, 6, 80, 7, 81, 81, 80, 80, 9, 10] and rows.tolist() == [3, 5, 6, 7, 8]
+    # the same prompt by hand: towers, then the splice in order of appearance per modality
+    vis = InklingVision({"text_hidden_size": 40, **raw["vision_config"]}, sd.__getitem__, sd.__contains__)
+    aud = InklingAudio(raw["audio_config"], sd.__getitem__, sd.__contains__)
+    img = vis(image_patches(torch.from_numpy(pixels)))
+    emb = splice_media(ids, 80, 81, image_embeds=[img, ready], audio_embeds=[aud(frames, 2)])
+    direct = InklingModel(cfg, sd.__getitem__, sd.__contains__)
+    want = direct.forward(ids, direct.new_cache(), embeds=emb)
+    seq = lm.engine.new_sequence(ids, SamplingParams(temperature=0.0), 4)
+    got = lm.engine.feed_logits(seq, ids, (rows, values))
+    assert torch.allclose(got, want, atol=1e-5)
+    out = lm.generate_multimodal(segments, SamplingParams(temperature=0.0), max_new_tokens=3)
+    assert out[0] == int(want.argmax()) or int(want.argmax()) == 2       # id 2 ends the sequence
+    plain = direct.forward(ids, direct.new_cache())
+    assert not torch.allclose(plain, want, atol=1e-3)                    # the soft tokens are what the decoder saw
+    with pytest.raises(MultimodalPreparationError, match="media embeddings"):
+        lm.multimodal_inputs([{"audio_embeds": torch.zeros(2, 8)}])
+    # a checkpoint without towers
+    text_dir = tmp_path / "text"
+    text_dir.mkdir()
+    raw_t = ink_cfg()
+    save_file({k: v.contiguous() for k, v in ink_state(InklingConfig.from_dict(raw_t)).items()}, str(text_dir / "model.safetensors"))
+    (text_dir / "config.json").write_text(json.dumps(raw_t))
+    lm_t = LoadedModel.load(text_dir, ModelLoadOptions(device="cpu", max_batch=1, max_seq_len=64))
+    with pytest.raises(MultimodalPreparationError, match="vision_config"):
+        lm_t.multimodal_inputs([RgbImage(pixels)])
