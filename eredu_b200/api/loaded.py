@@ -266,6 +266,17 @@ class LoadedModel:
                                    "eoa_token_id": vis.get("eoa_token_id", vis.get("eoa_token_index"))}
             except (RuntimeError, KeyError, ValueError) as e:
                 lm.audio, lm.audio_error = None, f"audio tower not loaded: {e}"
+        if vis and src.cfg.model_type == "muse_glimmer" and src.has("model.vision_tower.patch_embedder.patch_embedding.weight") \
+                and (opt.parallel is None or opt.parallel.owns_embedding()):
+            from ..models.muse_glimmer_vision import load_muse_glimmer_vision, load_processor
+
+            try:
+                lm.vision = load_muse_glimmer_vision(vis, src.cfg.hidden_size, src.get, src.has, device,
+                                                     torch.float32 if device.type == "cpu" else dtype)
+                lm.vision_tokens = {k: vis.get(k) for k in ("image_token_id", "video_token_id")}
+                lm.vision_processor = load_processor(path)
+            except (RuntimeError, KeyError, ValueError) as e:
+                lm.vision, lm.vision_error = None, f"vision tower not loaded: {e}"
         if lm.vision is not None:
             pass
         elif vis and src.has("model.visual.patch_embed.proj.weight") and (opt.parallel is None or opt.parallel.owns_embedding()):
@@ -363,6 +374,8 @@ class LoadedModel:
 
         if self.config.model_type == "inkling_mm_model":
             return self._inkling_inputs(segments)
+        if self.config.model_type == "muse_glimmer" and self.vision is not None:
+            return self._muse_glimmer_inputs(segments, wrap, (video_limits or {}).get("frame_count"))
         if self.config.model_type == "gemma4" and (self.vision is not None or self.audio is not None):
             return self._gemma4_inputs(segments, wrap, **(image_limits or {}))
         if self.vision is None:
@@ -481,6 +494,53 @@ class LoadedModel:
             placeholder = self.audio_tokens.get("audio_token_id")
         return ids, {"rows": rows, "values": torch.cat([f.to(feats[0].dtype) for f in feats], 0), "deepstack": None,
                      "rope_positions": None, "rope_delta": 0, "bidir_groups": bidir, "placeholder_id": int(placeholder)}
+
+    def _muse_glimmer_inputs(self, segments: list, wrap: bool, frame_count=None):
+        """Muse-Glimmer prompt parts (``prepare_input``, eredu/src/backend/mlx/architectures/muse_glimmer/processor.rs:
+        190-310): an image becomes ``<|image_start|>``, one placeholder per merged patch, ``<|image_end|>``; a video
+        becomes ``<|vid_start|>`` and, per temporal group, ``Time: x.xs``, its placeholders and a frame separator (the
+        last group closes with ``<|vid_end|>``). ``wrap=False`` leaves the marker text to the caller's template."""
+        from ..media import MultimodalPreparationError, RgbImage
+        from ..media.request import Video
+        from ..models.muse_glimmer_vision import image_to_patches, video_to_groups
+
+        image_cfg, video_cfg = self.vision_processor
+        vt, m = self.vision_tokens, self.vision.cfg.merge_size
+        ids, rows, patches, grids = [], [], [], []
+        mark = (lambda text: ids.extend(self.encode(text))) if wrap else (lambda text: None)
+
+        def media(token, p, grid):
+            if token is None:
+                raise MultimodalPreparationError("this checkpoint declares no placeholder token for that medium")
+            n = grid[0] * (grid[1] // m) * (grid[2] // m)
+            rows.extend(range(len(ids), len(ids) + n))
+            ids.extend([int(token)] * n)
+            patches.append(p)
+            grids.append(grid)
+
+        for seg in segments:
+            if isinstance(seg, str):
+                ids.extend(self.encode(seg))
+            elif isinstance(seg, RgbImage):
+                mark("<|image_start|>")
+                media(vt.get("image_token_id"), *image_to_patches(seg, image_cfg))
+                mark("<|image_end|>")
+            elif isinstance(seg, Video):
+                groups = video_to_groups(seg, video_cfg, frame_count)
+                mark("<|vid_start|>")
+                for gi, (seconds, p, grid) in enumerate(groups):
+                    mark(f"Time: {seconds:.1f}s")
+                    media(vt.get("video_token_id"), p, grid)
+                    mark("<|vid_end|>" if gi + 1 == len(groups) else "<|vid_frame_separator|>")
+            elif isinstance(seg, (list, tuple)):
+                ids.extend(int(t) for t in seg)
+            else:
+                raise MultimodalPreparationError(f"Muse-Glimmer processor does not support parts of type {type(seg).__name__}")
+        if not rows:
+            return ids, None
+        values = self.vision(torch.cat(patches), grids)
+        return ids, {"rows": torch.tensor(rows, dtype=torch.int64), "values": values, "deepstack": None,
+                     "rope_positions": None, "rope_delta": 0}
 
     def _inkling_inputs(self, segments: list):
         """Typed prompt parts of the Inkling family (``prepare_typed_input``, eredu/src/backend/mlx/architectures/inkling/

@@ -260,7 +260,7 @@ class ModelConfig:
             d["_language_model_prefix"] = True
             d["_vision"] = {k: outer[k] for k in ("vision_config", "image_token_id", "video_token_id", "boi_token_id", "eoi_token_id", "vision_start_token_id",
                                                   "vision_end_token_id", "audio_config", "audio_token_id", "boa_token_id", "eoa_token_id",
-                                                  "eoa_token_index") if k in outer}
+                                                  "eoa_token_index", "projector_hidden_size", "out_hidden_size") if k in outer}
         # Transformers >= 5 writes RoPE settings as one ``rope_parameters`` object (theta inside it; optionally one
         # object per layer type): fold it back into rope_theta / rope_scaling
         rp = d.get("rope_parameters")

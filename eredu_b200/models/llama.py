@@ -320,13 +320,14 @@ class CausalLM:
                 h = ops.embedding(batch.token_ids, self.embed, 0, self.cfg.embedding_scale)
         else:
             h = batch.hidden_in
-        if batch.embed_rows is not None and self.par.owns_embedding():
-            h = h.index_copy(0, batch.embed_rows, batch.embed_values.to(h.dtype))
-            ssq = None                      # the embedding kernel's row sums no longer describe these rows
         if getattr(self, "mg", None) is not None and self.par.owns_embedding() and batch.hidden_in is None:
             from .muse_glimmer import _wrms
 
-            h, ssq = _wrms(h, self.cfg.rms_norm_eps).to(h.dtype), None      # Muse-Glimmer normalises the embedding
+            # Muse-Glimmer normalises the token embeddings; tower rows arrive normalised and take their places after it
+            h, ssq = _wrms(h, self.cfg.rms_norm_eps).to(h.dtype), None
+        if batch.embed_rows is not None and self.par.owns_embedding():
+            h = h.index_copy(0, batch.embed_rows, batch.embed_values.to(h.dtype))
+            ssq = None                      # the embedding kernel's row sums no longer describe these rows
         if getattr(self, "g4", None) is not None:
             from .gemma4 import per_layer_inputs
 

@@ -16,8 +16,8 @@ The key / value cache is an ordinary grouped-query cache, so the family runs on 
 sampling kernels); the block is tensor operations around this repository's GEMMs over the paged pool, with the attention
 kernels (tcgen05 prefill, split-KV decode) for head sizes 64 and 128; the dense variant's decode step is captured in a
 CUDA graph. The routed-expert variant of the feed-forward (softmax top-k over fused expert banks) runs as a loop over
-the chosen experts and decodes eagerly. Not built: the vision tower and adapter, the ATEM drafter, tensor parallelism
-for this family.
+the chosen experts and decodes eagerly. The vision tower lives in ``muse_glimmer_vision.py``. Not built: the ATEM drafter, tensor
+parallelism for this family.
 """
 from __future__ import annotations
 

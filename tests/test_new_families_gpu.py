@@ -122,3 +122,19 @@ def test_gemma4_assistant_on_the_gpu(tmp_path):
     # bf16 ties aside, speculation commits what plain decoding commits whatever the drafter proposes
     agree = sum(a == b for x, y in zip(got, plain) for a, b in zip(x, y))
     assert agree >= 20 and dec.stats.rounds > 0 and dec.stats.proposed == 3 * dec.stats.rounds
+
+
+def test_muse_glimmer_vision_tower_on_the_gpu():
+    """The tower in bf16 on the GPU (this repository's GEMMs, fused attention per window) against its fp32 CPU run."""
+    from eredu_b200.models.muse_glimmer_vision import MuseGlimmerVision, MuseVisionConfig
+    from test_muse_glimmer_vision import LANG, PROJ, VISION, tower_state
+
+    sd = tower_state()
+    cfg = MuseVisionConfig.from_dict(VISION, LANG, PROJ)
+    cpu = MuseGlimmerVision(cfg, sd.__getitem__, sd.__contains__)
+    gpu = MuseGlimmerVision(cfg, sd.__getitem__, sd.__contains__, "cuda", torch.bfloat16)
+    grids = [(1, 8, 12), (2, 4, 6)]
+    patches = torch.randn(96 + 48, 96, generator=torch.Generator().manual_seed(4))
+    want, got = cpu(patches, grids), gpu(patches, grids)
+    assert got.shape == want.shape == (24 + 12, LANG) and got.is_cuda
+    assert _close(got, want, 0.06)
