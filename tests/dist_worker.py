@@ -116,15 +116,19 @@ def main():
         g = torch.Generator().manual_seed(0)
         prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 33)]
 
-    if "g4" in scenario:        # Gemma 4 from a checkpoint directory (EREDU_TEST_CKPT): per-type head geometry, sandwich norms
+    if "g4" in scenario or "ckpt" in scenario:   # a checkpoint directory (EREDU_TEST_CKPT): Gemma 4, Muse-Glimmer
         from eredu_b200.formats.checkpoint import open_checkpoint
 
         src = open_checkpoint(os.environ["EREDU_TEST_CKPT"])
         cfg = src.cfg
 
+        # the decoder of a vision-language checkpoint sits under model.language_model.*
+        nested = src.has("model.language_model.embed_tokens.weight")
+        name = (lambda n: "model.language_model." + n[len("model."):] if n.startswith("model.") else n) if nested else (lambda n: n)
+
         class _Tensors:
-            __getitem__ = staticmethod(src.get)
-            __contains__ = staticmethod(src.has)
+            __getitem__ = staticmethod(lambda n: src.get(name(n)))
+            __contains__ = staticmethod(lambda n: src.has(name(n)))
 
         sd = _Tensors()
         g = torch.Generator().manual_seed(0)

@@ -177,6 +177,41 @@ def test_gemma4_tensor_parallel(variant, tmp_path, monkeypatch):
         assert r["tokens"] == want
 
 
+@pytest.mark.parametrize("variant,world", [("dense", 2), ("routed", 4)])
+def test_muse_glimmer_tensor_parallel(variant, world, tmp_path, monkeypatch):
+    """Muse-Glimmer over tensor ranks: query heads and the output gate split, key / value heads split (two ranks) or
+    replicated (four ranks, two heads), feed-forward and expert rows split, sums taken before the sandwich norms."""
+    from eredu_b200.api import LoadedModel, ModelLoadOptions
+    from test_muse_glimmer import save, state
+
+    sd = state()
+    if variant == "routed":
+        gen = torch.Generator().manual_seed(9)
+        for li in range(4):
+            p = f"model.language_model.layers.{li}.mlp."
+            for n in ("gate_proj", "up_proj", "down_proj"):
+                del sd[p + n + ".weight"]
+            sd[p + "gate.weight"] = torch.randn(6, 64, generator=gen) * 0.5
+            sd[p + "experts.gate_up_proj"] = torch.randn(6, 64, 64, generator=gen) * 0.2
+            sd[p + "experts.down_proj"] = torch.randn(6, 64, 32, generator=gen) * 0.2
+        from test_muse_glimmer import TEXT
+
+        text = dict(TEXT, num_experts=6, num_experts_per_tok=2, norm_topk_prob=True, moe_intermediate_size=32)
+    else:
+        from test_muse_glimmer import TEXT as text
+    ckpt = tmp_path / "ckpt"
+    ckpt.mkdir()
+    save(ckpt, sd, text)
+    monkeypatch.setenv("EREDU_TEST_CKPT", str(ckpt))
+    res = run_ranks("cpu_ckpt_tp_nccl", world, tmp_path)
+    lm = LoadedModel.load(ckpt, ModelLoadOptions(device="cpu", max_batch=4, max_seq_len=128))
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, lm.config.vocab_size, (n,), generator=g).tolist() for n in (9, 33)]
+    want = lm.engine.generate(prompts, SamplingParams(temperature=0.0), 12)
+    for r in res:
+        assert r["tokens"] == want
+
+
 @pytest.mark.parametrize("family", ["nemo", "qnext", "dsv3", "kimi"])
 def test_hybrid_and_latent_families_under_pipeline_parallelism(family, tmp_path):
     """Two pipeline stages: every stage keeps the K/V pages and recurrent states of its own layers only, activations

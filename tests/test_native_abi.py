@@ -296,7 +296,8 @@ def test_whole_model_forward_dry_run(dry_cuda, family):
     calls = set(dry_cuda.calls)
     assert {"eredu_gemm_bf16", "eredu_rmsnorm"} <= calls
     if family not in ("deepseek_v3", "kimi_linear"):     # latent attention has no kernel: tensor operations around the GEMMs
-        assert {"eredu_attn_prefill", "eredu_rope_kv"} <= calls
+        assert "eredu_rope_kv" in calls
+        assert calls & {"eredu_attn_prefill", "eredu_attn_prefill_tc"}     # the second is the tcgen05 kernel (16-token pages)
         assert calls & {"eredu_attn_decode", "eredu_attn_decode_rope"}      # the second fuses the rotation into the decode kernel
     if family in ("qwen3_moe", "gpt_oss", "qwen3_next", "nemotron_h", "deepseek_v3", "kimi_linear"):
         assert "eredu_gemm_bf16_grouped" in calls
