@@ -48,6 +48,7 @@ int dtype_bytes(const std::string& d) {
   if (d == "F32" || d == "I32" || d == "U32") return 4;
   if (d == "F16" || d == "BF16" || d == "I16" || d == "U16") return 2;
   if (d == "I8" || d == "U8" || d == "BOOL" || d == "F8_E4M3" || d == "F8_E5M2" || d == "F8_E8M0") return 1;
+  if (d == "F4") return 1;  // two E2M1 codes per byte: such a tensor is carried with its last axis counted in bytes
   throw std::runtime_error("safetensors: unknown dtype " + d);
 }
 
@@ -205,6 +206,12 @@ class SafetensorsStore {
       t.shard = shard;
       t.dtype = e["dtype"].cast<std::string>();
       t.shape = e["shape"].cast<std::vector<int64_t>>();
+      if (t.dtype == "F4") {
+        // the header counts 4-bit elements; two share a byte along the last axis
+        if (t.shape.empty() || t.shape.back() % 2 != 0)
+          throw std::runtime_error("safetensors: F4 tensor " + name + " needs an even last dimension");
+        t.shape.back() /= 2;
+      }
       py::sequence off = e["data_offsets"];
       t.begin = off[0].cast<uint64_t>();
       t.end = off[1].cast<uint64_t>();

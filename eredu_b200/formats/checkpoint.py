@@ -33,7 +33,7 @@ _ST_DTYPES = {torch.float32: "F32", torch.float16: "F16", torch.bfloat16: "BF16"
 _ST_TO_TORCH = {"F32": torch.float32, "F16": torch.float16, "BF16": torch.bfloat16, "I32": torch.int32,
                 "I64": torch.int64, "U8": torch.uint8, "I8": torch.int8, "BOOL": torch.bool, "F64": torch.float64,
                 "I16": torch.int16, "U32": torch.int32, "U16": torch.int16, "F8_E4M3": torch.float8_e4m3fn,
-                "F8_E5M2": torch.float8_e5m2, "F8_E8M0": torch.uint8}
+                "F8_E5M2": torch.float8_e5m2, "F8_E8M0": torch.uint8, "F4": torch.uint8}
 
 # ---------------------------------------------------------------------------------------------- names
 _LAYER_MAP = {
@@ -255,10 +255,29 @@ class SafetensorsSource(TensorSource):
         ``<base>.weight`` F8_E4M3 + ``<base>.weight_scale_inv`` [ceil(N/128), ceil(K/128)]), else None."""
         if not name.endswith(".weight"):
             return None
-        for suffix in ("_scale_inv", "_scale"):
-            if name + suffix in self._keys and self.store.info(name)["dtype"] == "F8_E4M3":
-                return name + suffix
+        # ``<base>.scale`` is the sibling form of checkpoints that keep the inference layout (DeepSeek-V4)
+        for sname in (name + "_scale_inv", name + "_scale", name[:-len("weight")] + "scale"):
+            if sname in self._keys and self.store.info(name)["dtype"] == "F8_E4M3":
+                return sname
         return None
+
+    def mxfp4_scale_name(self, name: str) -> Optional[str]:
+        """Name of the block-exponent tensor of a microscaling FP4 weight: ``<base>.weight`` holds two E2M1 codes per byte
+        ([N, K / 2], stored as F4 or as plain bytes), ``<base>.scale`` one E8M0 exponent per 32 weights ([N, K / 32]) - the
+        expert banks of DeepSeek-V4 (``expert_dtype: fp4``; eredu/src/backend/mlx/architectures/deepseek_v4/
+        layerwise.rs:2207-2222 views the same bytes as 32-bit code words of a group-32 MXFP4 matrix). Else None."""
+        if not name.endswith(".weight"):
+            return None
+        sname = name[:-len("weight")] + "scale"
+        if sname not in self._keys:
+            return None
+        w, sc = self.store.info(name), self.store.info(sname)
+        if w["dtype"] not in ("F4", "I8", "U8") or sc["dtype"] not in ("F8_E8M0", "U8"):
+            return None
+        ws, ss = list(w["shape"]), list(sc["shape"])
+        if len(ws) != 2 or len(ss) != 2 or ws[0] != ss[0] or ws[1] * 2 != ss[1] * 32:
+            return None
+        return sname
 
     def to_fp8(self, name: str):
         """(E4M3 bytes as uint8 [N, K], fp32 block scales [ceil(N/128), ceil(K/128)]) of a block-scaled weight.
@@ -279,6 +298,12 @@ class SafetensorsSource(TensorSource):
             N, K = w.shape
             full = sc.repeat_interleave(128, 0)[:N].repeat_interleave(128, 1)[:, :K]
             return w.view(torch.float8_e4m3fn).to(torch.float32) * full
+        sname = self.mxfp4_scale_name(name)
+        if sname is not None:
+            # two E2M1 codes per byte (low nibble first), one power-of-two scale per 32 weights -> dense fp32
+            codes = np.ascontiguousarray(self._wrap(self.store.tensor(name), "U8").numpy())
+            exps = np.ascontiguousarray(self._wrap(self.store.tensor(sname), "U8").numpy())
+            return torch.from_numpy(np.asarray(H.mxfp4_dequantize(codes.view(np.uint32), exps)))
         qi = self.quant_info(name)
         if qi is not None and qi["kind"] == "affine":
             # MLX-LM packed tensor: uint32 code words + per-group scales / biases -> dense fp32 (w = scale * q + bias)

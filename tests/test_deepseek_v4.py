@@ -253,3 +253,57 @@ def test_a_checkpoint_directory_is_inspected_loaded_and_generates(tmp_path):
 
     with pytest.raises(NotImplementedError, match="prefix reuse"):
         LoadedModel.load(tmp_path, ModelLoadOptions(device="cpu", max_batch=1, max_seq_len=64, prefix_cache=True))
+
+
+def test_released_low_precision_tensors_decode_at_load(tmp_path):
+    """The inference-layout checkpoint keeps expert banks as microscaling FP4 (two E2M1 codes per byte + one E8M0
+    exponent per 32 weights in ``<base>.scale``) and other projections as E4M3 with 128 x 128 block scales in the same
+    sibling tensor: both decode when read, and the loaded model equals the one built from the decoded values."""
+    import json
+
+    import numpy as np
+    from safetensors.torch import save_file
+
+    from eredu_b200.api import LoadedModel, ModelLoadOptions
+    from eredu_b200.formats.checkpoint import open_checkpoint
+    from eredu_b200.lib import _eredu_host as H
+
+    raw = dict(v4_cfg(hidden_size=128, moe_intermediate_size=64, head_dim=32, qk_rope_head_dim=16, q_lora_rank=64, o_lora_rank=32,
+                      vocab_size=256, index_head_dim=16), model_type="deepseek_v4", architectures=["DeepseekV4ForCausalLM"],
+               eos_token_id=1, expert_dtype="fp4")
+    cfg = DeepseekV4Config.from_dict(raw)
+    sd = v4_state(cfg)
+    stored, dense = {}, {}
+    e2m1 = torch.tensor([0, 0.5, 1, 1.5, 2, 3, 4, 6, -0.0, -0.5, -1, -1.5, -2, -3, -4, -6])
+    for k, v in sd.items():
+        if ".ffn.experts." in k and k.endswith(".weight"):
+            packed, exps = H.mxfp4_quantize(np.ascontiguousarray(v.float().numpy()))
+            codes = torch.from_numpy(np.asarray(packed).view(np.uint8).copy())                 # [N, K / 2]
+            exps = torch.from_numpy(np.asarray(exps).copy())                                    # [N, K / 32]
+            # even experts use the 4-bit storage type (the file then counts 4-bit elements), odd ones plain bytes
+            as_f4 = int(k.split(".experts.")[1].split(".")[0]) % 2 == 0
+            stored[k], stored[k[:-len("weight")] + "scale"] = (codes.view(torch.float4_e2m1fn_x2) if as_f4 else codes), exps
+            lo, hi = e2m1[(codes & 15).long()], e2m1[(codes >> 4).long()]
+            vals = torch.stack((lo, hi), -1).flatten(1)                                         # the low nibble comes first
+            dense[k] = vals * torch.pow(2.0, exps.float() - 127.0).repeat_interleave(32, 1)
+        elif k.endswith("attn.wq_b.weight"):
+            scale = torch.pow(2.0, torch.randint(-3, 1, ((v.shape[0] + 127) // 128, (v.shape[1] + 127) // 128)).float())
+            full = scale.repeat_interleave(128, 0)[:v.shape[0]].repeat_interleave(128, 1)[:, :v.shape[1]]
+            q = (v / full).to(torch.float8_e4m3fn)
+            stored[k], stored[k[:-len("weight")] + "scale"] = q, scale
+            dense[k] = q.float() * full
+        else:
+            stored[k] = dense[k] = v
+    save_file({k: v.contiguous() for k, v in stored.items()}, str(tmp_path / "model.safetensors"))
+    (tmp_path / "config.json").write_text(json.dumps(raw))
+    src = open_checkpoint(tmp_path)
+    name = "layers.1.ffn.experts.2.w1.weight"
+    assert src.mxfp4_scale_name(name) == "layers.1.ffn.experts.2.w1.scale" and torch.equal(src.get(name), dense[name])
+    assert src.store.info(name)["dtype"] == "F4" and src.store.info(name.replace(".2.", ".3."))["dtype"] == "U8"
+    assert torch.equal(src.get(name.replace(".2.", ".3.")), dense[name.replace(".2.", ".3.")])
+    assert float((dense[name] - sd[name]).abs().max()) < 0.3 * float(sd[name].abs().max())      # a 4-bit rendering of the weights
+    assert torch.equal(src.get("layers.0.attn.wq_b.weight"), dense["layers.0.attn.wq_b.weight"])
+    lm = LoadedModel.load(tmp_path, ModelLoadOptions(device="cpu", max_batch=1, max_seq_len=64))
+    direct = DeepseekV4Model(cfg, dense.__getitem__, dense.__contains__)
+    prompt = list(range(7, 25))
+    assert torch.allclose(lm.prefill_logits(prompt), direct.forward(prompt, direct.new_cache()), atol=1e-5)
