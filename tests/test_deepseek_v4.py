@@ -296,6 +296,10 @@ def test_released_low_precision_tensors_decode_at_load(tmp_path):
             stored[k] = dense[k] = v
     save_file({k: v.contiguous() for k, v in stored.items()}, str(tmp_path / "model.safetensors"))
     (tmp_path / "config.json").write_text(json.dumps(raw))
+    from eredu_b200.runtime.plan import inspect_artifact
+
+    report = inspect_artifact(tmp_path)
+    assert report.is_loadable, [(i.code, i.message) for i in report.issues]
     src = open_checkpoint(tmp_path)
     name = "layers.1.ffn.experts.2.w1.weight"
     assert src.mxfp4_scale_name(name) == "layers.1.ffn.experts.2.w1.scale" and torch.equal(src.get(name), dense[name])
