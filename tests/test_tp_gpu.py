@@ -148,3 +148,25 @@ def test_pipeline_parallel_gpu(scenario, world, tmp_path):
         if "peer" in scenario:
             # decode hops went over peer memory inside the captured step: every stage ran its decode as a CUDA graph
             assert r["graph"] and r["hops"] > 0
+
+
+def test_muse_glimmer_tensor_parallel_on_gpus(tmp_path, monkeypatch):
+    """Muse-Glimmer (head size 64: attention kernels, decode step in a CUDA graph) on two GPUs - split heads, output gate
+    and feed-forward rows, peer-memory all-reduce before each sandwich norm - against the single-GPU model."""
+    _need(2)
+    from eredu_b200.api import LoadedModel, ModelLoadOptions
+    from test_muse_glimmer import TEXT, save, state
+
+    ckpt = tmp_path / "ckpt"
+    ckpt.mkdir()
+    save(ckpt, state(D=64), dict(TEXT, head_dim=64))
+    monkeypatch.setenv("EREDU_TEST_CKPT", str(ckpt))
+    res = run_ranks("gpu_ckpt_tp_peer", 2, tmp_path, extra_env={"NCCL_NVLS_ENABLE": "0"})
+    lm = LoadedModel.load(ckpt, ModelLoadOptions(device="cuda:0", max_batch=4, max_seq_len=128))
+    probe = torch.randint(0, lm.config.vocab_size, (100,), generator=torch.Generator().manual_seed(7)).tolist()
+    ref = torch.tensor(probe_logits(lm.engine, lm.engine.model, probe))
+    for r in res:
+        lg = torch.tensor(r["logits"])
+        assert _rel(lg, ref) <= 0.03
+        assert r["logits"] == res[0]["logits"] and r["tokens"] == res[0]["tokens"]
+        assert all(len(t) == 12 for t in r["tokens"])
