@@ -715,8 +715,11 @@ class LoadedModel:
         if draft_tokens <= 0:
             return None
         if not getattr(self.engine, "paged", True):
+            # the request scheduler drives paged lanes; an unpaged target drafts through UnpagedSpeculativeDecoder
+            # (generate_prepared_chat without scheduler options)
             if draft is not None:
-                raise NotImplementedError("speculative decoding needs the paged engine; this model family runs without a drafter")
+                raise NotImplementedError("the speculative request scheduler needs the paged engine; pass the draft without "
+                                          "scheduler options to run this family's draft-and-verify decoder")
             return None
         if draft is not None:
             return SpeculativeDecoder(self.engine, draft.engine, k=draft_tokens)
@@ -882,8 +885,10 @@ class LoadedModel:
                                                "dflash" if getattr(self, "dflash", None) is not None else "embedded")
         elif draft is not None:
             from ..runtime.speculative import SpeculativeDecoder
+            from ..runtime.unpaged import UnpagedSpeculativeDecoder
 
-            spec = SpeculativeDecoder(self.engine, draft.engine, k=draft_tokens)
+            spec = (SpeculativeDecoder if getattr(self.engine, "paged", True) else UnpagedSpeculativeDecoder)(
+                self.engine, draft.engine, k=draft_tokens)
             spec.generate([prompt_ids], sampling or SamplingParams(), max_new_tokens, eos_ids=(), on_token=on_token)
             reason = spec.last_finish_reasons[0] or FinishReason.MAX_TOKENS
             self.last_speculative_stats = spec.stats.summary()
