@@ -138,3 +138,27 @@ def test_muse_glimmer_vision_tower_on_the_gpu():
     want, got = cpu(patches, grids), gpu(patches, grids)
     assert got.shape == want.shape == (24 + 12, LANG) and got.is_cuda
     assert _close(got, want, 0.06)
+
+
+def test_unpaged_speculative_decoder_on_the_gpu():
+    """Inkling in bf16 on the GPU with a one-layer draft: rounds run on the device (caches cloned and restored there) and
+    every emitted token is the target's own choice at its position, so the output has the requested length and the
+    first token equals plain generation's (later ones may differ where bf16 multi-token and single-token passes tie)."""
+    from eredu_b200.models.inkling import InklingConfig, InklingModel
+    from eredu_b200.runtime.unpaged import UnpagedEngine, UnpagedSpeculativeDecoder
+    from test_inkling import ink_cfg, ink_state
+
+    def engine(seed, **over):
+        cfg = InklingConfig.from_dict(ink_cfg(hidden_size=64, head_dim=16, swa_head_dim=16, d_rel=8, **over))
+        sd = ink_state(cfg, seed=seed)
+        return UnpagedEngine(InklingModel(cfg, sd.__getitem__, sd.__contains__, "cuda", torch.bfloat16), max_seq_len=128)
+
+    target, draft = engine(0), engine(1, num_hidden_layers=1, layer_types=["full_attention"], dense_mlp_idx=0)
+    sp = SamplingParams(temperature=0.0)
+    prompt = list(range(5, 19))
+    want = target.generate([prompt], sp, 12)[0]
+    spec = UnpagedSpeculativeDecoder(target, draft, k=3)
+    got = spec.generate([prompt], sp, 12)[0]
+    assert len(got) == 12 and got[0] == want[0]
+    s = spec.stats.summary()
+    assert s["rounds"] >= 3 and s["proposed"] >= s["accepted"]
